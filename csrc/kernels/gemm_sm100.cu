@@ -1,0 +1,468 @@
+// bf16 GEMM for sm_100a: D[M,N] = A[M,K] * B[N,K]^T with fp32 accumulation in TMEM.
+//
+// Design (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor tiles into a STAGES-deep smem ring
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (128 x BN x 16) from smem
+//               descriptors; accumulators live in TMEM, double-buffered (2 x BN columns)
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator, apply the fused epilogue
+//               (bias, GELU, GELU-backward multiply, residual, cast) and store, while
+//               the MMA warp already works on the next tile in the other TMEM buffer.
+// Both operands may be K-major (contraction contiguous) or MN-major (the output index
+// contiguous), so forward (x W^T), dgrad (dy W) and wgrad (dy^T x) all run without a
+// transpose pass. Split-K with fp32 atomic accumulation keeps all SMs busy on wgrad.
+//
+// Replaces the reference's tiled SGEMM source string
+// (crates/torsh-backend/src/kernel_generation/types/cuda_compiler.rs:104-167) and its
+// unwired cuBLAS call (crates/torsh-backend/src/cuda/backend.rs:695-726).
+#include "host_util.h"
+#include "sm100.cuh"
+
+namespace tb {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int A_TILE_BYTES = BM * BK * 2;
+constexpr int GEMM_THREADS = 192;
+
+enum : int {
+  EPI_BIAS = 1,          // += bias[n] (bf16)
+  EPI_GELU = 2,          // tanh-GELU after bias
+  EPI_RESIDUAL = 4,      // += residual[m,n] (bf16) after activation
+  EPI_OUT_F32 = 8,       // D is fp32 (default bf16)
+  EPI_ATOMIC = 16,       // fp32 atomic accumulate into D (split-K / grad accumulation)
+  EPI_STORE_PREACT = 32, // also store the pre-activation (after bias) as bf16
+  EPI_MUL_DGELU = 64,    // *= gelu'(aux[m,n]) (aux = forward pre-activation, bf16)
+  EPI_ACCUM = 128,       // D = D + result (non-atomic read-modify-write)
+  EPI_RASTER_M = 256,    // walk tiles with m fastest (B panel shared by concurrent CTAs)
+};
+
+struct GemmParams {
+  int M, N, K;
+  int ldd, ldr;
+  void* D;
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  __nv_bfloat16* preact;
+  const __nv_bfloat16* aux;
+  int flags;
+  int split_k;
+  int tiles_m, tiles_n;
+  int kb_total, kb_per_split;
+  int* status;
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int B_TILE_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+  static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
+  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+  static constexpr int ALLOC = TOTAL + 1024;  // slack for manual 1024-byte alignment
+};
+
+__device__ __forceinline__ void decode_work(const GemmParams& p, int work, int& m_t, int& n_t,
+                                            int& kb0, int& kb1) {
+  int tile = work / p.split_k;
+  int ks = work - tile * p.split_k;
+  if (p.flags & EPI_RASTER_M) {
+    n_t = tile / p.tiles_m;
+    m_t = tile - n_t * p.tiles_m;
+  } else {
+    m_t = tile / p.tiles_n;
+    n_t = tile - m_t * p.tiles_n;
+  }
+  kb0 = ks * p.kb_per_split;
+  kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+}
+
+template <int BN, int A_MAJOR, int B_MAJOR, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const GemmParams p) {
+  using L = SmemLayout<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = (uint64_t*)(smem + L::BAR_OFFSET);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tmem_full = empty + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_ptr = (uint32_t*)(tmem_empty + 2);
+  volatile int* abort_flag = (volatile int*)(tmem_ptr + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_work = p.tiles_m * p.tiles_n * p.split_k;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_ptr, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_ptr;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&map_a);
+      tma_prefetch_desc(&map_b);
+      int s = 0;
+      uint32_t phase = 0;
+      for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
+        int m_t, n_t, kb0, kb1;
+        decode_work(p, work, m_t, n_t, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          mbar_wait(&empty[s], phase ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
+          uint8_t* sa = smem + s * L::STAGE_BYTES;
+          uint8_t* sb = sa + A_TILE_BYTES;
+          mbar_expect_tx(&full[s], L::STAGE_BYTES);
+          if (A_MAJOR == 0) {
+            tma_load_2d(sa, &map_a, &full[s], kb * BK, m_t * BM);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_2d(sa + c * (64 * BK * 2), &map_a, &full[s], m_t * BM + c * 64, kb * BK);
+          }
+          if (B_MAJOR == 0) {
+            tma_load_2d(sb, &map_b, &full[s], kb * BK, n_t * BN);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (64 * BK * 2), &map_b, &full[s], n_t * BN + c * 64, kb * BK);
+          }
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (*abort_flag) {
+        // give copies still in flight time to land before the CTA's smem is released
+        uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MAJOR, B_MAJOR);
+      int s = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
+        int m_t, n_t, kb0, kb1;
+        decode_work(p, work, m_t, n_t, kb0, kb1);
+        mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_EMPTY);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          mbar_wait(&full[s], phase, abort_flag, p.status, TB_ERR_WAIT_FULL);
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t b_base = a_base + A_TILE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = (A_MAJOR == 0)
+                                       ? make_smem_desc_sw128(a_base + k * 32, 16, 1024)
+                                       : make_smem_desc_sw128(a_base + k * 2048, 64 * BK * 2, 1024);
+            const uint64_t bdesc = (B_MAJOR == 0)
+                                       ? make_smem_desc_sw128(b_base + k * 32, 16, 1024)
+                                       : make_smem_desc_sw128(b_base + k * 2048, 64 * BK * 2, 1024);
+            umma_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+        umma_commit(&tmem_full[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps)
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const int flags = p.flags;
+    for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
+      int m_t, n_t, kb0, kb1;
+      decode_work(p, work, m_t, n_t, kb0, kb1);
+      mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
+      tc_fence_after();
+      const int row = m_t * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const bool add_bias = (flags & EPI_BIAS) && (kb0 == 0);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        const int n0 = n_t * BN + c0;
+        if (n0 >= p.N) break;  // uniform across the warp
+        uint32_t v[32];
+        tmem_ld32(tmem_base + acc * BN + c0 + ((uint32_t)(q * 32) << 16), v);
+        tmem_wait_ld();
+        if (!row_ok) continue;
+        float f[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+        const bool full_chunk = (n0 + 32 <= p.N);
+        const size_t off = (size_t)row * p.ldd + n0;
+        if (full_chunk && (p.ldd & 7) == 0) {
+          if (add_bias) {
+            const uint4* bp = reinterpret_cast<const uint4*>(p.bias + n0);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 b = __ldg(bp + g);
+              uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                f[g * 8 + e * 2] += bf16_lo(w[e]);
+                f[g * 8 + e * 2 + 1] += bf16_hi(w[e]);
+              }
+            }
+          }
+          if (flags & EPI_STORE_PREACT) {
+            uint4* pp = reinterpret_cast<uint4*>(p.preact + off);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 o;
+              o.x = pack_bf16x2(f[g * 8 + 0], f[g * 8 + 1]);
+              o.y = pack_bf16x2(f[g * 8 + 2], f[g * 8 + 3]);
+              o.z = pack_bf16x2(f[g * 8 + 4], f[g * 8 + 5]);
+              o.w = pack_bf16x2(f[g * 8 + 6], f[g * 8 + 7]);
+              pp[g] = o;
+            }
+          }
+          if (flags & EPI_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) f[j] = gelu_tanh(f[j]);
+          }
+          if (flags & EPI_MUL_DGELU) {
+            const uint4* ap = reinterpret_cast<const uint4*>(p.aux + off);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 a = ap[g];
+              uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                f[g * 8 + e * 2] *= gelu_tanh_grad(bf16_lo(w[e]));
+                f[g * 8 + e * 2 + 1] *= gelu_tanh_grad(bf16_hi(w[e]));
+              }
+            }
+          }
+          if (flags & EPI_RESIDUAL) {
+            const uint4* rp =
+                reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldr + n0);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 a = rp[g];
+              uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                f[g * 8 + e * 2] += bf16_lo(w[e]);
+                f[g * 8 + e * 2 + 1] += bf16_hi(w[e]);
+              }
+            }
+          }
+          if (flags & EPI_OUT_F32) {
+            float* dp = reinterpret_cast<float*>(p.D) + off;
+            if (flags & EPI_ATOMIC) {
+#pragma unroll
+              for (int g = 0; g < 8; ++g)
+                asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dp + g * 4),
+                             "f"(f[g * 4]), "f"(f[g * 4 + 1]), "f"(f[g * 4 + 2]),
+                             "f"(f[g * 4 + 3])
+                             : "memory");
+            } else {
+              float4* d4 = reinterpret_cast<float4*>(dp);
+#pragma unroll
+              for (int g = 0; g < 8; ++g) {
+                float4 o = make_float4(f[g * 4], f[g * 4 + 1], f[g * 4 + 2], f[g * 4 + 3]);
+                if (flags & EPI_ACCUM) {
+                  float4 old = d4[g];
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                d4[g] = o;
+              }
+            }
+          } else {
+            uint4* d4 = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + off);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              if (flags & EPI_ACCUM) {
+                uint4 a = d4[g];
+                uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  f[g * 8 + e * 2] += bf16_lo(w[e]);
+                  f[g * 8 + e * 2 + 1] += bf16_hi(w[e]);
+                }
+              }
+              uint4 o;
+              o.x = pack_bf16x2(f[g * 8 + 0], f[g * 8 + 1]);
+              o.y = pack_bf16x2(f[g * 8 + 2], f[g * 8 + 3]);
+              o.z = pack_bf16x2(f[g * 8 + 4], f[g * 8 + 5]);
+              o.w = pack_bf16x2(f[g * 8 + 6], f[g * 8 + 7]);
+              d4[g] = o;
+            }
+          }
+        } else {
+          // ragged edge / unaligned leading dimension: scalar path
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int n = n0 + j;
+            if (n >= p.N) continue;
+            float x = f[j];
+            if (add_bias) x += __bfloat162float(p.bias[n]);
+            if (flags & EPI_STORE_PREACT) p.preact[off + j] = __float2bfloat16(x);
+            if (flags & EPI_GELU) x = gelu_tanh(x);
+            if (flags & EPI_MUL_DGELU) x *= gelu_tanh_grad(__bfloat162float(p.aux[off + j]));
+            if (flags & EPI_RESIDUAL)
+              x += __bfloat162float(p.residual[(size_t)row * p.ldr + n]);
+            if (flags & EPI_OUT_F32) {
+              float* dp = reinterpret_cast<float*>(p.D) + off + j;
+              if (flags & EPI_ATOMIC)
+                atomicAdd(dp, x);
+              else
+                *dp = (flags & EPI_ACCUM) ? (*dp + x) : x;
+            } else {
+              __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + off + j;
+              if (flags & EPI_ACCUM) x += __bfloat162float(*dp);
+              *dp = __float2bfloat16(x);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN, int A_MAJOR, int B_MAJOR, int STAGES>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
+                       cudaStream_t stream) {
+  using L = SmemLayout<BN, STAGES>;
+  auto kern = gemm_bf16_kernel<BN, A_MAJOR, B_MAJOR, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    TB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::ALLOC));
+    configured = true;
+  }
+  int total = p.tiles_m * p.tiles_n * p.split_k;
+  int grid = total < sm_count() ? total : sm_count();
+  kern<<<grid, GEMM_THREADS, L::ALLOC, stream>>>(ma, mb, p);
+  TB_CUDA_CHECK(cudaGetLastError());
+  return TB_LAUNCH_OK;
+}
+
+}  // namespace tb
+
+using namespace tb;
+
+// D[M,N] = op(A) * op(B)^T with the fused epilogue selected by `flags`.
+//   a_major = 0: A is stored [M, K] (row stride lda);  1: A is stored [K, M] (row stride lda)
+//   b_major = 0: B is stored [N, K] (row stride ldb);  1: B is stored [K, N] (row stride ldb)
+// lda / ldb must be multiples of 8 elements and the base pointers 16-byte aligned (TMA).
+// `bn` selects the tile width (128 or 256); 0 lets the launcher choose.
+TB_EXPORT int tb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int a_major,
+                           int b_major, int lda, int ldb, int ldd, const void* bias,
+                           const void* residual, int ldr, void* preact, const void* aux, int flags,
+                           int split_k, int bn, int* status, cudaStream_t stream) {
+  if (!A || !B || !D || M <= 0 || N <= 0 || K <= 0) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: null pointer or empty shape");
+  if ((lda & 7) || (ldb & 7)) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: lda/ldb must be multiples of 8 (got %d, %d)", lda, ldb);
+  if ((flags & EPI_BIAS) && !bias) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: EPI_BIAS without bias");
+  if ((flags & EPI_RESIDUAL) && !residual) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: EPI_RESIDUAL without residual");
+  if ((flags & EPI_STORE_PREACT) && !preact) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: EPI_STORE_PREACT without buffer");
+  if ((flags & EPI_MUL_DGELU) && !aux) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: EPI_MUL_DGELU without aux");
+  if ((flags & EPI_ATOMIC) && !(flags & EPI_OUT_F32)) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: EPI_ATOMIC needs fp32 output");
+  if (split_k < 1) split_k = 1;
+  if (split_k > 1 && !(flags & EPI_ATOMIC)) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: split_k > 1 needs EPI_ATOMIC");
+  if (bn == 0) {
+    // 256-wide tiles halve the smem traffic per FLOP; fall back to 128 when that
+    // leaves SMs idle.
+    long t256 = (long)((M + BM - 1) / BM) * ((N + 255) / 256) * split_k;
+    bn = (N > 128 && t256 >= sm_count()) ? 256 : 128;
+  }
+  if (bn != 128 && bn != 256) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: bn must be 128 or 256");
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.ldd = ldd; p.ldr = ldr;
+  p.D = D;
+  p.bias = (const __nv_bfloat16*)bias;
+  p.residual = (const __nv_bfloat16*)residual;
+  p.preact = (__nv_bfloat16*)preact;
+  p.aux = (const __nv_bfloat16*)aux;
+  p.flags = flags;
+  p.tiles_m = (M + BM - 1) / BM;
+  p.tiles_n = (N + bn - 1) / bn;
+  p.kb_total = (K + BK - 1) / BK;
+  if (split_k > p.kb_total) split_k = p.kb_total;
+  p.kb_per_split = (p.kb_total + split_k - 1) / split_k;
+  split_k = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
+  p.split_k = split_k;
+  p.status = status;
+
+  CUtensorMap ma, mb;
+  {
+    uint64_t dims[2], str[1];
+    uint32_t box[2];
+    if (a_major == 0) { dims[0] = K; dims[1] = M; box[0] = BK; box[1] = BM; }
+    else              { dims[0] = M; dims[1] = K; box[0] = 64; box[1] = BK; }
+    str[0] = (uint64_t)lda * 2;
+    int r = make_tmap(&ma, A, 2, 2, dims, str, box);
+    if (r) return r;
+    if (b_major == 0) { dims[0] = K; dims[1] = N; box[0] = BK; box[1] = bn; }
+    else              { dims[0] = N; dims[1] = K; box[0] = 64; box[1] = BK; }
+    str[0] = (uint64_t)ldb * 2;
+    r = make_tmap(&mb, B, 2, 2, dims, str, box);
+    if (r) return r;
+  }
+
+#define TB_DISPATCH(BN_, ST_)                                                          \
+  do {                                                                                 \
+    if (a_major == 0 && b_major == 0) return launch_gemm<BN_, 0, 0, ST_>(ma, mb, p, stream); \
+    if (a_major == 0 && b_major == 1) return launch_gemm<BN_, 0, 1, ST_>(ma, mb, p, stream); \
+    if (a_major == 1 && b_major == 1) return launch_gemm<BN_, 1, 1, ST_>(ma, mb, p, stream); \
+    if (a_major == 1 && b_major == 0) return launch_gemm<BN_, 1, 0, ST_>(ma, mb, p, stream); \
+  } while (0)
+  if (bn == 256) TB_DISPATCH(256, 4);
+  else TB_DISPATCH(128, 6);
+#undef TB_DISPATCH
+  TB_FAIL(TB_E_ARG, "tb_gemm_bf16: unsupported major combination");
+}
+
+TB_EXPORT const char* tb_last_error() { return tb::last_error_buf(); }

@@ -1,0 +1,251 @@
+// LayerNorm and RMSNorm forward / backward for sm_100a.
+//
+// One CTA walks rows (grid-stride); each thread owns up to VPT 16-byte vectors of the row and
+// keeps them in registers, so every element is read from HBM exactly once per pass. Row
+// statistics use two block reductions (mean, then centred variance) for accuracy. The backward
+// keeps per-thread fp32 partial sums of d(gamma) / d(beta) for its own columns across all rows of
+// the CTA and flushes them once with atomics into fp32 gradient buffers.
+//
+// Semantics follow the reference layers: LayerNorm eps 1e-5 (biased variance) and
+// RMSNorm y = x / sqrt(mean(x^2) + eps) * w with eps 1e-6
+// (crates/torsh-nn/src/layers/normalization/layer_group/mod.rs:491-514,539-623).
+#include "common.cuh"
+#include "host_util.h"
+
+namespace tb {
+
+template <typename T, int VPT, bool RMS>
+__global__ void norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+                                const T* __restrict__ beta, T* __restrict__ y,
+                                float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows,
+                                int H, float eps) {
+  constexpr int N = Vec16<T>::N;
+  __shared__ float scratch[32];
+  const int nvec = H / N;
+  Vec16<T> g[VPT], b[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+      g[i].load_nc(gamma + v * N);
+      if (!RMS && beta) b[i].load_nc(beta + v * N);
+    }
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const T* xr = x + (size_t)row * H;
+    float f[VPT][N];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        Vec16<T> t;
+        t.load(xr + v * N);
+        t.get(f[i]);
+#pragma unroll
+        for (int j = 0; j < N; ++j) s += RMS ? f[i][j] * f[i][j] : f[i][j];
+      }
+    }
+    float mean = 0.f, rstd;
+    if (RMS) {
+      float ms = block_sum(s, scratch) / H;
+      rstd = rsqrtf(ms + eps);
+    } else {
+      mean = block_sum(s, scratch) / H;
+      float sq = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        int v = threadIdx.x + i * blockDim.x;
+        if (v < nvec) {
+#pragma unroll
+          for (int j = 0; j < N; ++j) {
+            float d = f[i][j] - mean;
+            sq += d * d;
+          }
+        }
+      }
+      float var = block_sum(sq, scratch) / H;
+      rstd = rsqrtf(var + eps);
+    }
+    if (threadIdx.x == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    T* yr = y + (size_t)row * H;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        float gf[N], bf[N], o[N];
+        g[i].get(gf);
+        if (!RMS && beta) b[i].get(bf);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          float xh = (f[i][j] - mean) * rstd;
+          o[j] = xh * gf[j] + ((!RMS && beta) ? bf[j] : 0.f);
+        }
+        Vec16<T> t;
+        t.set(o);
+        t.store(yr + v * N);
+      }
+    }
+  }
+}
+
+// dx = rstd * (dy*g - mean(dy*g) - xhat * mean(dy*g*xhat))      (LayerNorm)
+// dx = rstd * (dy*g - xhat * mean(dy*g*xhat))                   (RMSNorm, xhat = x*rstd)
+// Optionally dx += dres (gradient arriving through the residual branch).
+template <typename T, int VPT, bool RMS>
+__global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                const T* __restrict__ gamma, const float* __restrict__ mean_in,
+                                const float* __restrict__ rstd_in, const T* __restrict__ dres,
+                                T* __restrict__ dx, float* __restrict__ dgamma,
+                                float* __restrict__ dbeta, int rows, int H) {
+  constexpr int N = Vec16<T>::N;
+  __shared__ float scratch[32];
+  const int nvec = H / N;
+  float gf[VPT][N], dg[VPT][N], db[VPT][N];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int v = threadIdx.x + i * blockDim.x;
+#pragma unroll
+    for (int j = 0; j < N; ++j) dg[i][j] = db[i][j] = gf[i][j] = 0.f;
+    if (v < nvec) {
+      Vec16<T> t;
+      t.load_nc(gamma + v * N);
+      t.get(gf[i]);
+    }
+  }
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float xh[VPT][N], dyg[VPT][N];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        Vec16<T> tx, td;
+        tx.load(x + (size_t)row * H + v * N);
+        td.load(dy + (size_t)row * H + v * N);
+        float xf[N], df[N];
+        tx.get(xf);
+        td.get(df);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          xh[i][j] = (xf[j] - mean) * rstd;
+          dyg[i][j] = df[j] * gf[i][j];
+          dg[i][j] += df[j] * xh[i][j];
+          db[i][j] += df[j];
+          s1 += dyg[i][j];
+          s2 += dyg[i][j] * xh[i][j];
+        }
+      }
+    }
+    if (!RMS) s1 = block_sum(s1, scratch) / H; else s1 = 0.f;
+    s2 = block_sum(s2, scratch) / H;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        float o[N];
+        if (dres) {
+          Vec16<T> tr;
+          tr.load(dres + (size_t)row * H + v * N);
+          tr.get(o);
+        } else {
+#pragma unroll
+          for (int j = 0; j < N; ++j) o[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < N; ++j) o[j] += rstd * (dyg[i][j] - s1 - xh[i][j] * s2);
+        Vec16<T> t;
+        t.set(o);
+        t.store(dx + (size_t)row * H + v * N);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int v = threadIdx.x + i * blockDim.x;
+    if (v < nvec) {
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        if (dgamma) atomicAdd(dgamma + v * N + j, dg[i][j]);
+        if (!RMS && dbeta) atomicAdd(dbeta + v * N + j, db[i][j]);
+      }
+    }
+  }
+}
+
+template <typename T, bool RMS>
+static int norm_fwd_launch(const void* x, const void* gamma, const void* beta, void* y, float* mean,
+                           float* rstd, int rows, int H, float eps, cudaStream_t st) {
+  constexpr int N = Vec16<T>::N;
+  if (H % N) TB_FAIL(TB_E_ARG, "norm: H=%d must be a multiple of %d", H, N);
+  int nvec = H / N;
+  int grid = rows < sm_count() * 8 ? rows : sm_count() * 8;
+#define TB_NF(VPT_)                                                                                 \
+  {                                                                                                 \
+    int threads = ((nvec + VPT_ - 1) / VPT_ + 31) / 32 * 32;                                        \
+    norm_fwd_kernel<T, VPT_, RMS><<<grid, threads, 0, st>>>((const T*)x, (const T*)gamma,           \
+                                                             (const T*)beta, (T*)y, mean, rstd,     \
+                                                             rows, H, eps);                         \
+  }
+  if (nvec <= 256) TB_NF(1) else if (nvec <= 1024) TB_NF(2) else if (nvec <= 4096) TB_NF(4) else
+    TB_FAIL(TB_E_ARG, "norm: H=%d too large", H);
+#undef TB_NF
+  TB_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+template <typename T, bool RMS>
+static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, const float* mean,
+                           const float* rstd, const void* dres, void* dx, float* dgamma,
+                           float* dbeta, int rows, int H, cudaStream_t st) {
+  constexpr int N = Vec16<T>::N;
+  if (H % N) TB_FAIL(TB_E_ARG, "norm: H=%d must be a multiple of %d", H, N);
+  int nvec = H / N;
+  int grid = rows < sm_count() * 4 ? rows : sm_count() * 4;
+#define TB_NB(VPT_)                                                                               \
+  {                                                                                               \
+    int threads = ((nvec + VPT_ - 1) / VPT_ + 31) / 32 * 32;                                      \
+    norm_bwd_kernel<T, VPT_, RMS><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x,            \
+                                                             (const T*)gamma, mean, rstd,         \
+                                                             (const T*)dres, (T*)dx, dgamma,      \
+                                                             dbeta, rows, H);                     \
+  }
+  if (nvec <= 256) TB_NB(1) else if (nvec <= 1024) TB_NB(2) else if (nvec <= 4096) TB_NB(4) else
+    TB_FAIL(TB_E_ARG, "norm: H=%d too large", H);
+#undef TB_NB
+  TB_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace tb
+using namespace tb;
+
+// dtype: 0 = bf16, 1 = fp32. rms: 0 = LayerNorm, 1 = RMSNorm. beta / mean may be null.
+TB_EXPORT int tb_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
+                          float* rstd, int rows, int H, float eps, int rms, int dtype,
+                          cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (dtype == 0)
+    return rms ? norm_fwd_launch<bf16, true>(x, gamma, beta, y, mean, rstd, rows, H, eps, st)
+               : norm_fwd_launch<bf16, false>(x, gamma, beta, y, mean, rstd, rows, H, eps, st);
+  return rms ? norm_fwd_launch<float, true>(x, gamma, beta, y, mean, rstd, rows, H, eps, st)
+             : norm_fwd_launch<float, false>(x, gamma, beta, y, mean, rstd, rows, H, eps, st);
+}
+
+// dgamma / dbeta are fp32 buffers that the kernel ACCUMULATES into (zero them for a fresh
+// gradient). dres (optional) is added to dx.
+TB_EXPORT int tb_norm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
+                          const float* rstd, const void* dres, void* dx, float* dgamma,
+                          float* dbeta, int rows, int H, int rms, int dtype, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (dtype == 0)
+    return rms ? norm_bwd_launch<bf16, true>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, rows, H, st)
+               : norm_bwd_launch<bf16, false>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, rows, H, st);
+  return rms ? norm_bwd_launch<float, true>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, rows, H, st)
+             : norm_bwd_launch<float, false>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, rows, H, st);
+}

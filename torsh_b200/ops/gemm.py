@@ -1,0 +1,98 @@
+"""bf16 tensor-core GEMM (tcgen05 / TMEM / TMA) with fused epilogues.
+
+``gemm(a, b, ...)`` computes ``D[M,N] = A · Bᵀ`` where each operand may be stored K-major
+(contraction index contiguous) or MN-major (output index contiguous); that covers the three
+products of a linear layer (forward ``x Wᵀ``, dgrad ``dy W``, wgrad ``dyᵀ x``) without a transpose
+pass. Kernel: ``csrc/kernels/gemm_sm100.cu``. The reference's matmul is a 2-D naive triple loop
+(``crates/torsh-tensor/src/advanced_ops.rs:1000-1042``).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .. import _native as nv
+
+EPI_BIAS = 1
+EPI_GELU = 2
+EPI_RESIDUAL = 4
+EPI_OUT_F32 = 8
+EPI_ATOMIC = 16
+EPI_STORE_PREACT = 32
+EPI_MUL_DGELU = 64
+EPI_ACCUM = 128
+EPI_RASTER_M = 256
+
+_configured = False
+
+
+def _lib():
+    global _configured
+    lib = nv.require_cuda()
+    if not _configured:
+        lib.tb_gemm_bf16.restype = ctypes.c_int
+        lib.tb_gemm_bf16.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 8 + [ctypes.c_void_p] * 2 + [
+            ctypes.c_int] + [ctypes.c_void_p] * 2 + [ctypes.c_int] * 3 + [ctypes.c_void_p] * 2
+        _configured = True
+    return lib
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_major: int = 0, b_major: int = 0, out: torch.Tensor | None = None,
+         bias: torch.Tensor | None = None, gelu: bool = False, residual: torch.Tensor | None = None,
+         preact_out: torch.Tensor | None = None, dgelu_aux: torch.Tensor | None = None, out_dtype=torch.bfloat16,
+         atomic: bool = False, accumulate: bool = False, split_k: int = 1, bn: int = 0,
+         raster_m: bool | None = None) -> torch.Tensor:
+    """``D = op(A) · op(B)ᵀ`` on the 5th-gen tensor cores.
+
+    a_major=0: ``a`` is ``[M, K]``; a_major=1: ``a`` is ``[K, M]`` (i.e. Aᵀ stored row-major).
+    b_major=0: ``b`` is ``[N, K]``; b_major=1: ``b`` is ``[K, N]``.
+    """
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_cuda and b.is_cuda
+    assert a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+    if a_major == 0:
+        M, K = a.shape
+    else:
+        K, M = a.shape
+    if b_major == 0:
+        N, Kb = b.shape
+    else:
+        Kb, N = b.shape
+    assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+    flags = 0
+    if out is None:
+        out = (torch.zeros if atomic else torch.empty)((M, N), dtype=out_dtype, device=a.device)
+    assert out.shape == (M, N) and out.stride(1) == 1
+    if out.dtype == torch.float32:
+        flags |= EPI_OUT_F32
+    else:
+        assert out.dtype == torch.bfloat16
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == N
+        flags |= EPI_BIAS
+    if gelu:
+        flags |= EPI_GELU
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and residual.stride(1) == 1
+        flags |= EPI_RESIDUAL
+    if preact_out is not None:
+        assert preact_out.dtype == torch.bfloat16 and preact_out.shape == (M, N) and preact_out.stride(0) == out.stride(0)
+        flags |= EPI_STORE_PREACT
+    if dgelu_aux is not None:
+        assert dgelu_aux.dtype == torch.bfloat16 and dgelu_aux.shape == (M, N) and dgelu_aux.stride(0) == out.stride(0)
+        flags |= EPI_MUL_DGELU
+    if atomic:
+        flags |= EPI_ATOMIC
+    if accumulate:
+        flags |= EPI_ACCUM
+    if raster_m is None:
+        raster_m = N > 4 * M or (N >= 16384 and N > M)
+    if raster_m:
+        flags |= EPI_RASTER_M
+    st = nv.status_word(a.device)
+    rc = _lib().tb_gemm_bf16(
+        a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a_major, b_major, a.stride(0), b.stride(0),
+        out.stride(0), nv.ptr(bias), nv.ptr(residual), residual.stride(0) if residual is not None else 0,
+        nv.ptr(preact_out), nv.ptr(dgelu_aux), flags, split_k, bn, st.data_ptr(), nv.stream_ptr())
+    nv.check(rc, "tb_gemm_bf16")
+    return out
