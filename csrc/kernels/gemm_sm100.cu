@@ -401,6 +401,7 @@ TB_EXPORT int tb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, 
                            int b_major, int lda, int ldb, int ldd, const void* bias,
                            const void* residual, int ldr, void* preact, const void* aux, int flags,
                            int split_k, int bn, int* status, cudaStream_t stream) {
+  TB_ENSURE_DEVICE();
   if (!A || !B || !D || M <= 0 || N <= 0 || K <= 0) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: null pointer or empty shape");
   if ((lda & 7) || (ldb & 7)) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: lda/ldb must be multiples of 8 (got %d, %d)", lda, ldb);
   if ((flags & EPI_BIAS) && !bias) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: EPI_BIAS without bias");
@@ -464,5 +465,8 @@ TB_EXPORT int tb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, 
 #undef TB_DISPATCH
   TB_FAIL(TB_E_ARG, "tb_gemm_bf16: unsupported major combination");
 }
+
+// Records the device that subsequent launches (from any thread) must run on.
+TB_EXPORT void tb_set_device(int device) { tb::g_device().store(device); }
 
 TB_EXPORT const char* tb_last_error() { return tb::last_error_buf(); }

@@ -6,6 +6,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #define TB_EXPORT extern "C" __attribute__((visibility("default")))
 
 namespace tb {
@@ -35,6 +37,29 @@ inline char* last_error_buf() {
     if (_e != cudaSuccess)                                                               \
       TB_FAIL(tb::TB_E_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),     \
               __FILE__, __LINE__);                                                       \
+  } while (0)
+
+// The library links the CUDA runtime statically, so its notion of "current device" is separate
+// from the one of the process that loaded it, and it starts at device 0 in every new thread
+// (autograd worker threads included). tb_set_device records the device the caller works on; every
+// launcher makes it current on its own thread before touching the runtime or the driver.
+inline std::atomic<int>& g_device() {
+  static std::atomic<int> d{0};
+  return d;
+}
+inline int ensure_device() {
+  static thread_local int bound = -1;
+  const int want = g_device().load(std::memory_order_relaxed);
+  if (bound != want) {
+    TB_CUDA_CHECK(cudaSetDevice(want));
+    TB_CUDA_CHECK(cudaFree(0));  // binds the primary context to this thread
+    bound = want;
+  }
+  return 0;
+}
+#define TB_ENSURE_DEVICE()                       \
+  do {                                           \
+    if (int _r = tb::ensure_device()) return _r; \
   } while (0)
 
 inline int sm_count() {

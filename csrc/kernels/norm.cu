@@ -229,6 +229,7 @@ using namespace tb;
 TB_EXPORT int tb_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
                           float* rstd, int rows, int H, float eps, int rms, int dtype,
                           cudaStream_t st) {
+  TB_ENSURE_DEVICE();
   if (rows <= 0) return 0;
   if (dtype == 0)
     return rms ? norm_fwd_launch<bf16, true>(x, gamma, beta, y, mean, rstd, rows, H, eps, st)
@@ -242,6 +243,7 @@ TB_EXPORT int tb_norm_fwd(const void* x, const void* gamma, const void* beta, vo
 TB_EXPORT int tb_norm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, const void* dres, void* dx, float* dgamma,
                           float* dbeta, int rows, int H, int rms, int dtype, cudaStream_t st) {
+  TB_ENSURE_DEVICE();
   if (rows <= 0) return 0;
   if (dtype == 0)
     return rms ? norm_bwd_launch<bf16, true>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, rows, H, st)

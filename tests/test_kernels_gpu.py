@@ -1,0 +1,271 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).abs().max() / b.float().abs().max().clamp(min=1e-6)).item()
+
+
+# ------------------------------------------------------------------ GEMM
+@pytest.mark.parametrize("am,bm", [(0, 0), (0, 1), (1, 1), (1, 0)])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (384, 640, 320), (200, 328, 136), (1024, 1024, 512)])
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_majors(am, bm, shape, bn):
+    from torsh_b200.ops.gemm import gemm
+    M, N, K = shape
+    torch.manual_seed(1)
+    a = torch.randn((M, K) if am == 0 else (K, M), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((N, K) if bm == 0 else (K, N), device=DEV, dtype=torch.bfloat16)
+    out = gemm(a, b, a_major=am, b_major=bm, bn=bn)
+    A = a.float() if am == 0 else a.float().t()
+    B = b.float() if bm == 0 else b.float().t()
+    assert _rel(out, A @ B.t()) < 1e-2
+
+
+def test_gemm_epilogues():
+    from torsh_b200.ops.gemm import gemm
+    torch.manual_seed(2)
+    M, N, K = 512, 768, 256
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    res = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    pre = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    out = gemm(a, b, bias=bias, gelu=True, residual=res, preact_out=pre)
+    u = a.float() @ b.float().t() + bias.float()
+    ref = torch.nn.functional.gelu(u, approximate="tanh") + res.float()
+    assert _rel(out, ref) < 1e-2 and _rel(pre, u) < 1e-2
+    out2 = gemm(a, b, dgelu_aux=pre)
+    uu = pre.float().requires_grad_(True)
+    torch.nn.functional.gelu(uu, approximate="tanh").sum().backward()
+    assert _rel(out2, (a.float() @ b.float().t()) * uu.grad) < 1e-2
+    # ragged N (scalar epilogue path) and fp32 accumulate
+    b3 = torch.randn(100, K, device=DEV, dtype=torch.bfloat16)
+    o3 = torch.ones(M, 100, device=DEV, dtype=torch.float32)
+    gemm(a, b3, out=o3, accumulate=True)
+    assert _rel(o3, a.float() @ b3.float().t() + 1.0) < 1e-2
+
+
+def test_gemm_splitk_atomic_wgrad():
+    from torsh_b200.ops.gemm import gemm
+    torch.manual_seed(3)
+    T = 4096
+    dy = torch.randn(T, 512, device=DEV, dtype=torch.bfloat16)
+    x = torch.randn(T, 384, device=DEV, dtype=torch.bfloat16)
+    g = torch.zeros(512, 384, device=DEV, dtype=torch.float32)
+    gemm(dy, x, a_major=1, b_major=1, out=g, atomic=True, split_k=8)
+    gemm(dy, x, a_major=1, b_major=1, out=g, atomic=True, split_k=8)
+    assert _rel(g, 2 * dy.float().t() @ x.float()) < 1e-4
+
+
+# ------------------------------------------------------------------ norms
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("H", [256, 1024, 4096])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_fwd_bwd(dtype, H, rms):
+    from torsh_b200.ops.norm import layer_norm, rms_norm
+    torch.manual_seed(4)
+    rows = 333
+    x = torch.randn(rows, H, device=DEV, dtype=dtype, requires_grad=True)
+    w = (torch.randn(H, device=DEV) * 0.2 + 1).to(dtype).requires_grad_(True)
+    b = None if rms else (torch.randn(H, device=DEV) * 0.1).to(dtype).requires_grad_(True)
+    dy = torch.randn(rows, H, device=DEV, dtype=dtype)
+    y = rms_norm(x, w, 1e-6) if rms else layer_norm(x, w, b, 1e-5)
+    y.backward(dy)
+    xf, wf = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    if rms:
+        yr = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * wf
+    else:
+        bf = b.detach().float().requires_grad_(True)
+        yr = torch.nn.functional.layer_norm(xf, (H,), wf, bf, 1e-5)
+    yr.backward(dy.float())
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    assert _rel(y, yr) < tol and _rel(x.grad, xf.grad) < tol and _rel(w.grad, wf.grad) < tol
+    if not rms:
+        assert _rel(b.grad, bf.grad) < tol
+
+
+# ------------------------------------------------------------------ softmax / cross-entropy
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("C", [1000, 4097, 50304])
+def test_softmax_and_log_softmax(dtype, C):
+    from torsh_b200.ops.softmax import log_softmax, softmax
+    torch.manual_seed(5)
+    x = (torch.randn(37, C, device=DEV) * 3).to(dtype).requires_grad_(True)
+    dy = torch.randn(37, C, device=DEV, dtype=dtype)
+    for fn, ref in ((softmax, torch.softmax), (log_softmax, torch.log_softmax)):
+        x.grad = None
+        y = fn(x, -1)
+        y.backward(dy)
+        xf = x.detach().float().requires_grad_(True)
+        yr = ref(xf, -1)
+        yr.backward(dy.float())
+        tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+        assert _rel(y, yr) < tol and _rel(x.grad, xf.grad) < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_cross_entropy_padded_vocab(dtype):
+    from torsh_b200.ops.softmax import cross_entropy
+    torch.manual_seed(6)
+    rows, V, Vp = 256, 50257, 50304
+    lg = (torch.randn(rows, Vp, device=DEV) * 2).to(dtype).requires_grad_(True)
+    tg = torch.randint(0, V, (rows,), device=DEV)
+    tg[5] = -100
+    loss = cross_entropy(lg, tg, num_classes=V)
+    loss.backward()
+    lf = lg.detach().float()[:, :V].requires_grad_(True)
+    lr = torch.nn.functional.cross_entropy(lf, tg, ignore_index=-100)
+    lr.backward()
+    assert abs(loss.item() - lr.item()) < 2e-3 * abs(lr.item())
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    assert _rel(lg.grad[:, :V], lf.grad) < tol
+    assert lg.grad[:, V:].abs().max().item() == 0.0
+    # fused-backward contract
+    lg2 = lg.detach().clone().requires_grad_(True)
+    tg2 = tg.clone()
+    tg2[5] = 7
+    l2 = cross_entropy(lg2, tg2, num_classes=V, root_scale=0.5)
+    l2.backward()
+    lf2 = lg.detach().float()[:, :V].requires_grad_(True)
+    (0.5 * torch.nn.functional.cross_entropy(lf2, tg2)).backward()
+    assert _rel(lg2.grad[:, :V], lf2.grad) < tol
+
+
+# ------------------------------------------------------------------ elementwise / reduce / embedding / rope
+def test_unary_binary_reduce():
+    from torsh_b200.ops import elementwise as ew
+    torch.manual_seed(7)
+    for dtype in (torch.bfloat16, torch.float32):
+        x = torch.randn(1000, 77, device=DEV, dtype=dtype)
+        tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+        for op, ref in ew._TORCH_UNARY.items():
+            xi = x.abs() + 0.1 if op in ("log", "sqrt", "rsqrt") else x
+            assert _rel(ew.unary_raw(op, xi), ref(xi.float())) < tol, op
+        y = torch.randn_like(x)
+        for op, ref in ew._TORCH_BINARY.items():
+            yi = y.abs() + 0.5 if op == "div" else y
+            assert _rel(ew.binary_raw(op, x, yi), ref(x.float(), yi.float())) < tol, op
+        assert _rel(ew.binary_raw("mul", x, 2.5), x.float() * 2.5) < tol
+        x3 = torch.randn(6, 130, 50, device=DEV, dtype=dtype)
+        for dim in (0, 1, 2):
+            for op in ("sum", "max", "min", "mean"):
+                r = getattr(x3.float(), op)(dim)
+                r = r.values if op in ("max", "min") else r
+                assert _rel(ew.reduce(op, x3, dim), r) < (3e-2 if dtype == torch.bfloat16 else 1e-4), (op, dim)
+
+
+def test_activation_grads_swiglu_rope_embedding():
+    from torsh_b200.ops import elementwise as ew
+    torch.manual_seed(8)
+    x = torch.randn(64, 512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn(64, 512, device=DEV, dtype=torch.bfloat16)
+    for fn, ref in ((ew.gelu, lambda t: torch.nn.functional.gelu(t, approximate="tanh")), (ew.silu, torch.nn.functional.silu),
+                    (ew.relu, torch.relu), (ew.tanh, torch.tanh), (ew.sigmoid, torch.sigmoid)):
+        x.grad = None
+        fn(x).backward(dy)
+        xf = x.detach().float().requires_grad_(True)
+        ref(xf).backward(dy.float())
+        assert _rel(x.grad, xf.grad) < 3e-2
+    x.grad = None
+    y = ew.swiglu(x)
+    y.backward(dy[:, :256])
+    xf = x.detach().float().requires_grad_(True)
+    yr = xf[:, :256] * torch.nn.functional.silu(xf[:, 256:])
+    yr.backward(dy[:, :256].float())
+    assert _rel(y, yr) < 2e-2 and _rel(x.grad, xf.grad) < 3e-2
+    q = torch.randn(2, 100, 4, 128, device=DEV, dtype=torch.float32, requires_grad=True)
+    r = ew.rope(q, 10000.0)
+    assert _rel(r, ew._rope_torch(q.detach(), 10000.0, 0, False)) < 1e-4
+    r.backward(torch.ones_like(r))
+    assert _rel(q.grad, ew._rope_torch(torch.ones_like(q), 10000.0, 0, True)) < 1e-4
+    wte = torch.randn(500, 64, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    wpe = torch.randn(32, 64, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, 500, (4, 32), device=DEV)
+    e = ew.embedding(ids, wte, wpe)
+    ref = wte.detach().float()[ids] + wpe.detach().float()[None]
+    assert _rel(e, ref) < 1e-2
+    e.backward(torch.ones_like(e))
+    cnt = torch.bincount(ids.reshape(-1), minlength=500).float()
+    assert _rel(wte.grad[:, 0], cnt) < 1e-2 and _rel(wpe.grad, torch.full_like(wpe, 4.0)) < 1e-2
+
+
+# ------------------------------------------------------------------ linear / MLP autograd
+def test_linear_and_mlp_autograd():
+    from torsh_b200.ops.linear import linear, mlp_gelu
+    torch.manual_seed(9)
+    x = torch.randn(4, 96, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    for layout in ("nk", "kn"):
+        w = (torch.randn((384, 256) if layout == "nk" else (256, 384), device=DEV) * 0.05).to(torch.bfloat16).requires_grad_(True)
+        b = torch.randn(384, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+        x.grad = None
+        y = linear(x, w, b, layout=layout)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        xf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+        yr = torch.nn.functional.linear(xf, wf if layout == "nk" else wf.t(), bf)
+        yr.backward(dy.float())
+        assert _rel(y, yr) < 1e-2 and _rel(x.grad, xf.grad) < 1e-2 and _rel(w.grad, wf.grad) < 1e-2 and _rel(b.grad, bf.grad) < 1e-2
+    w1 = (torch.randn(1024, 256, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_(True)
+    b1 = torch.randn(1024, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w2 = (torch.randn(256, 1024, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_(True)
+    b2 = torch.randn(256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    x.grad = None
+    y = mlp_gelu(x, w1, b1, w2, b2, residual=x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    fs = [t.detach().float().requires_grad_(True) for t in (x, w1, b1, w2, b2)]
+    yr = torch.nn.functional.linear(torch.nn.functional.gelu(torch.nn.functional.linear(fs[0], fs[1], fs[2]), approximate="tanh"), fs[3], fs[4]) + fs[0]
+    yr.backward(dy.float())
+    assert _rel(y, yr) < 2e-2
+    for got, ref in zip((x, w1, b1, w2, b2), fs):
+        assert _rel(got.grad, ref.grad) < 3e-2
+    # main_grad accumulation path
+    w = (torch.randn(384, 256, device=DEV) * 0.05).to(torch.bfloat16).requires_grad_(True)
+    w.main_grad = torch.zeros(384, 256, device=DEV, dtype=torch.float32)
+    y = linear(x, w, None)
+    y.backward(torch.ones_like(y))
+    assert w.grad is None
+    ref = torch.ones(4 * 96, 384, device=DEV).t() @ x.detach().float().reshape(-1, 256)
+    assert _rel(w.main_grad, ref) < 1e-3
+
+
+# ------------------------------------------------------------------ attention
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("causal", [True, False])
+@pytest.mark.parametrize("S", [128, 384, 200])
+def test_flash_attention_fwd_bwd(D, causal, S):
+    from torsh_b200.ops.attention import _sdpa_reference, flash_attention
+    torch.manual_seed(10)
+    B, H = 2, 3
+    q, k, v = (torch.randn(B, S, H, D, device=DEV, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+    o = flash_attention(q, k, v, causal=causal)
+    do = torch.randn_like(o)
+    o.backward(do)
+    qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    orf = _sdpa_reference(qf, kf, vf, causal, 1.0 / math.sqrt(D))
+    orf.backward(do.float())
+    assert _rel(o, orf) < 2e-2
+    assert _rel(q.grad, qf.grad) < 3e-2 and _rel(k.grad, kf.grad) < 3e-2 and _rel(v.grad, vf.grad) < 3e-2
+
+
+def test_flash_attention_qkvpacked():
+    from torsh_b200.ops.attention import _sdpa_reference, flash_attention_qkvpacked
+    torch.manual_seed(11)
+    B, S, H, D = 2, 256, 4, 64
+    E = H * D
+    qkv = torch.randn(B * S, 3 * E, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    o = flash_attention_qkvpacked(qkv, B, S, H, D, causal=True)
+    do = torch.randn_like(o)
+    o.backward(do)
+    f = qkv.detach().float().requires_grad_(True)
+    q, k, v = (f[:, i * E:(i + 1) * E].reshape(B, S, H, D) for i in range(3))
+    orf = _sdpa_reference(q, k, v, True, 1.0 / math.sqrt(D)).reshape(B * S, E)
+    orf.backward(do.float())
+    assert _rel(o, orf) < 2e-2 and _rel(qkv.grad, f.grad) < 3e-2

@@ -30,7 +30,7 @@ NVCC_FLAGS = [
     "-O3", "-std=c++17", "-lineinfo",
     "--use_fast_math",
     "-Xcompiler", "-fPIC,-fvisibility=hidden",
-    "--expt-relaxed-constexpr",
+    "--expt-relaxed-constexpr", "--extended-lambda",
 ]
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-pthread", "-Wall"]
 

@@ -79,7 +79,17 @@ def check(rc: int, what: str = "") -> None:
         raise NativeError(f"{what} failed (rc={rc}): {msg}")
 
 
+_bound_device = -1
+
+
 def stream_ptr(stream: torch.cuda.Stream | None = None) -> c_void_p:
+    """Raw handle of the launch stream. Also tells the native library which device is current
+    (its statically linked CUDA runtime keeps its own per-thread device)."""
+    global _bound_device
+    d = torch.cuda.current_device()
+    if d != _bound_device:
+        cuda().tb_set_device(d)
+        _bound_device = d
     s = stream if stream is not None else torch.cuda.current_stream()
     return c_void_p(s.cuda_stream)
 
