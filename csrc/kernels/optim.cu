@@ -1,6 +1,8 @@
 // Fused multi-tensor optimizer kernels for sm_100a: AdamW / Adam, SGD-momentum, LAMB,
 // gradient norm, clip / unscale with inf check, zero.
 //
+// tb_adam_multi's `dyn` (optional, 3 floats on the device: lr, 1-beta1^t, 1-beta2^t) overrides the
+// by-value scalars, so that a step captured in a CUDA graph keeps advancing.
 // All kernels take a device-resident table of tensors (pointers + length) and a block map
 // (tensor index, chunk index per CTA), so one launch updates every parameter of a model; a flat
 // FSDP shard is simply a table with one entry. State is fp32 (master weights, exp_avg,
@@ -44,8 +46,14 @@ struct AdamArgs {
 //        3 = exp_avg, 4 = exp_avg_sq, 5 = max_exp_avg_sq (amsgrad only)
 __global__ void __launch_bounds__(MT_THREADS)
 adam_kernel(const MtEntry* __restrict__ table, const int* __restrict__ blk_tensor,
-            const int* __restrict__ blk_chunk, AdamArgs a, const float* __restrict__ found_inf) {
+            const int* __restrict__ blk_chunk, AdamArgs a, const float* __restrict__ found_inf,
+            const float* __restrict__ dyn) {
   if (found_inf && *found_inf != 0.f) return;  // AMP: skip the step on overflow
+  if (dyn) {  // step-dependent scalars read from device memory so a captured graph stays valid
+    a.lr = dyn[0];
+    a.bc1 = dyn[1];
+    a.bc2 = dyn[2];
+  }
   const MtEntry e = table[blk_tensor[blockIdx.x]];
   const long base = (long)blk_chunk[blockIdx.x] * MT_CHUNK;
   const long end = min(e.n, base + MT_CHUNK);
@@ -264,11 +272,12 @@ TB_EXPORT int tb_mt_chunk() { return MT_CHUNK; }
 TB_EXPORT int tb_adam_multi(const void* table, const int* blk_tensor, const int* blk_chunk,
                             int nblocks, float lr, float beta1, float beta2, float eps, float wd,
                             float bc1, float bc2, float grad_scale, int decoupled, int amsgrad,
-                            int gdtype, int zero_grad, const float* found_inf, cudaStream_t st) {
+                            int gdtype, int zero_grad, const float* found_inf, const float* dyn,
+                            cudaStream_t st) {
   TB_ENSURE_DEVICE();
   if (nblocks <= 0) return 0;
   AdamArgs a{lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale, decoupled, amsgrad, gdtype, zero_grad};
-  adam_kernel<<<nblocks, MT_THREADS, 0, st>>>((const MtEntry*)table, blk_tensor, blk_chunk, a, found_inf);
+  adam_kernel<<<nblocks, MT_THREADS, 0, st>>>((const MtEntry*)table, blk_tensor, blk_chunk, a, found_inf, dyn);
   TB_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

@@ -18,6 +18,7 @@ _lock = threading.Lock()
 _cuda_lib = None
 _host_lib = None
 _status = {}
+launch_count = 0  # kernels of this library launched so far (incremented by the op wrappers)
 
 c_void_p, c_int, c_float, c_long, c_size_t = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_int64, ctypes.c_size_t
 

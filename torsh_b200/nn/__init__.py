@@ -1,0 +1,8 @@
+"""Neural-network layers, containers, initialisers and the functional API."""
+from . import functional, init
+from .layers import *  # noqa: F401,F403
+from .layers import _ADOPTED
+from .module import (DynamicGraph, FunctionModule, LazyModule, Module, ModuleDict, ModuleList, ModuleMixin, Parameter,
+                     ParameterDict, ParameterList, Sequential)
+
+F = functional

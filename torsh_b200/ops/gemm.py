@@ -95,4 +95,5 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_major: int = 0, b_major: int = 0
         out.stride(0), nv.ptr(bias), nv.ptr(residual), residual.stride(0) if residual is not None else 0,
         nv.ptr(preact_out), nv.ptr(dgelu_aux), flags, split_k, bn, st.data_ptr(), nv.stream_ptr())
     nv.check(rc, "tb_gemm_bf16")
+    nv.launch_count += 1
     return out
