@@ -15,7 +15,6 @@
 #include <cstdio>
 #include <cstdlib>
 #include <map>
-#include <sstream>
 
 #include "bincode.h"
 #include "host_api.h"
@@ -75,7 +74,6 @@ static std::string json_escape(const std::string& s) {
   return o;
 }
 
-thread_local std::string g_err;
 
 }  // namespace tsh
 using namespace tsh;
@@ -168,7 +166,7 @@ TSH_EXPORT int tsh_trsh_decode(const uint8_t* buf, uint64_t len, char** meta_jso
       throw std::runtime_error(m);
     }
     Reader r(buf + 28, ms);
-    std::ostringstream js;
+    struct J { std::string s; J& operator<<(const char* c) { s += c; return *this; } J& operator<<(const std::string& c) { s += c; return *this; } J& operator<<(uint64_t v) { s += std::to_string(v); return *this; } std::string str() const { return s; } } js;
     js << "{\"shape\":[";
     uint64_t nd = r.varu();
     for (uint64_t i = 0; i < nd; ++i) js << (i ? "," : "") << r.varu();

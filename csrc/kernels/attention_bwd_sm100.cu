@@ -325,27 +325,31 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   }
 }
 
-// delta[b, h, s] = sum_d O[b, s, h, d] * dO[b, s, h, d]; one warp per (token, head).
+// delta[b, h, s] = sum_d O[b, s, h, d] * dO[b, s, h, d]. Each thread reads one 16-byte vector of O
+// and dO (8 elements); the D/8 lanes of a (token, head) pair combine with shuffles.
+template <int D>
 __global__ void fa_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
-                                float* __restrict__ delta, int B, int S, int H, int D, long o_stride,
-                                long do_stride) {
-  const long w = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+                                float* __restrict__ delta, int B, int S, int H, long o_stride, long do_stride) {
+  constexpr int LPG = D / 8;  // lanes per (token, head)
+  const long gid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long pair = gid / LPG;
+  const int sub = (int)(gid % LPG);
   const long total = (long)B * S * H;
-  if (w >= total) return;
-  const int hh = (int)(w % H);
-  const long tok = w / H;
-  const __nv_bfloat16* o = O + tok * o_stride + (long)hh * D;
-  const __nv_bfloat16* d = dO + tok * do_stride + (long)hh * D;
   float s = 0.f;
-  for (int i = lane * 2; i < D; i += 64) {
-    __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(o + i);
-    __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(d + i);
-    s += __bfloat162float(a.x) * __bfloat162float(c.x) + __bfloat162float(a.y) * __bfloat162float(c.y);
+  int hh = 0;
+  long tok = 0;
+  if (pair < total) {
+    hh = (int)(pair % H);
+    tok = pair / H;
+    const uint4 a = *reinterpret_cast<const uint4*>(O + tok * o_stride + (long)hh * D + sub * 8);
+    const uint4 c = *reinterpret_cast<const uint4*>(dO + tok * do_stride + (long)hh * D + sub * 8);
+    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, cw[4] = {c.x, c.y, c.z, c.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s += bf16_lo(aw[i]) * bf16_lo(cw[i]) + bf16_hi(aw[i]) * bf16_hi(cw[i]);
   }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
-  if (lane == 0) {
+  for (int off = LPG / 2; off > 0; off >>= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  if (pair < total && sub == 0) {
     const long bb = tok / S, ss = tok % S;
     delta[(bb * H + hh) * S + ss] = s;
   }
@@ -397,8 +401,13 @@ TB_EXPORT int tb_flash_attn_bwd(const void* q, const void* k, const void* v, con
   if ((r = make_bshd_map_bwd(&mk, k, B, S, H, D, kv_stride))) return r;
   if ((r = make_bshd_map_bwd(&mv, v, B, S, H, D, kv_stride))) return r;
   if ((r = make_bshd_map_bwd(&mdo, dout, B, S, H, D, do_stride))) return r;
-  const long nwarps = (long)B * S * H;
-  fa_delta_kernel<<<(unsigned)((nwarps * 32 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, B, S, H, D, o_stride, do_stride);
+  if ((o_stride & 7) || (do_stride & 7) || ((uintptr_t)o & 15) || ((uintptr_t)dout & 15))
+    TB_FAIL(TB_E_ARG, "flash_attn_bwd: o / dout must be 16-byte aligned with strides that are multiples of 8");
+  const long nthreads = (long)B * S * H * (D / 8);
+  if (D == 64)
+    fa_delta_kernel<64><<<(unsigned)((nthreads + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, B, S, H, o_stride, do_stride);
+  else
+    fa_delta_kernel<128><<<(unsigned)((nthreads + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, B, S, H, o_stride, do_stride);
   TB_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, sizeof(float) * (size_t)B * S * H * D, st));
   FaBwdParams p{lse, delta, dq_acc, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, B, S, H, dqkv_stride, scale, causal, status};
   const int n_blk = (S + 127) / 128;

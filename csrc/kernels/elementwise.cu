@@ -179,16 +179,49 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict_
 }
 
 // out[c] += sum_r x[r, c] (fp32 accumulate, atomics across row blocks): bias gradients.
+// Block = 32 x 8 threads: x-threads own one 16-byte vector of columns each, y-threads split the
+// rows of the block; partial sums meet in shared memory, one atomic per column per block.
 template <typename T>
 __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ out, long rows, int cols,
                               long ld, int rows_per_block) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= cols) return;
+  constexpr int N = Vec16<T>::N;
+  __shared__ float part[8][32 * N + 1];
+  const int c0 = (blockIdx.x * 32 + threadIdx.x) * N;
   const long r0 = (long)blockIdx.y * rows_per_block;
   const long r1 = min(rows, r0 + rows_per_block);
-  float s = 0.f;
-  for (long r = r0; r < r1; ++r) s += to_f<T>(x[r * ld + c]);
-  atomicAdd(out + c, s);
+  float acc[N];
+#pragma unroll
+  for (int j = 0; j < N; ++j) acc[j] = 0.f;
+  const bool vec_ok = (c0 + N <= cols) && ((ld % N) == 0) && (((uintptr_t)x & 15) == 0);
+  if (c0 < cols) {
+    for (long r = r0 + threadIdx.y; r < r1; r += 8) {
+      if (vec_ok) {
+        Vec16<T> t;
+        t.load(x + r * ld + c0);
+        float f[N];
+        t.get(f);
+#pragma unroll
+        for (int j = 0; j < N; ++j) acc[j] += f[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+          if (c0 + j < cols) acc[j] += to_f<T>(x[r * ld + c0 + j]);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < N; ++j) part[threadIdx.y][threadIdx.x * N + j] = acc[j];
+  __syncthreads();
+  const int tid = threadIdx.y * 32 + threadIdx.x;
+  for (int c = tid; c < 32 * N; c += 256) {
+    const int col = blockIdx.x * 32 * N + c;
+    if (col < cols) {
+      float s = 0.f;
+#pragma unroll
+      for (int y = 0; y < 8; ++y) s += part[y][c];
+      atomicAdd(out + col, s);
+    }
+  }
 }
 
 template <typename T>
@@ -276,10 +309,16 @@ TB_EXPORT int tb_swiglu_bwd(const void* dy, const void* x, void* dx, long rows, 
 TB_EXPORT int tb_colsum(const void* x, float* out, long rows, int cols, long ld, int dtype, cudaStream_t st) {
   TB_ENSURE_DEVICE();
   if (rows <= 0 || cols <= 0) return 0;
-  int rpb = 256;
-  dim3 grid((cols + 127) / 128, (unsigned)((rows + rpb - 1) / rpb));
-  if (dtype == 0) colsum_kernel<bf16><<<grid, 128, 0, st>>>((const bf16*)x, out, rows, cols, ld, rpb);
-  else colsum_kernel<float><<<grid, 128, 0, st>>>((const float*)x, out, rows, cols, ld, rpb);
+  const int N = dtype == 0 ? 8 : 4;
+  const int cols_per_block = 32 * N;
+  const int col_blocks = (cols + cols_per_block - 1) / cols_per_block;
+  // enough row blocks to fill the GPU about twice, at least 64 rows each
+  long want = (2L * sm_count() + col_blocks - 1) / col_blocks;
+  long rpb = (rows + want - 1) / want;
+  if (rpb < 64) rpb = 64;
+  dim3 grid(col_blocks, (unsigned)((rows + rpb - 1) / rpb)), block(32, 8);
+  if (dtype == 0) colsum_kernel<bf16><<<grid, block, 0, st>>>((const bf16*)x, out, rows, cols, ld, (int)rpb);
+  else colsum_kernel<float><<<grid, block, 0, st>>>((const float*)x, out, rows, cols, ld, (int)rpb);
   TB_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

@@ -100,7 +100,7 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
                                 const T* __restrict__ gamma, const float* __restrict__ mean_in,
                                 const float* __restrict__ rstd_in, const T* __restrict__ dres,
                                 T* __restrict__ dx, float* __restrict__ dgamma,
-                                float* __restrict__ dbeta, int rows, int H) {
+                                float* __restrict__ dbeta, float* __restrict__ partial, int rows, int H) {
   constexpr int N = Vec16<T>::N;
   __shared__ float scratch[32];
   const int nvec = H / N;
@@ -165,18 +165,52 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
       }
     }
   }
+  // Per-CTA partial sums: written to the workspace (reduced by norm_bwd_reduce_kernel, no atomic
+  // contention) or, without a workspace, added straight into the gradient with atomics.
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     int v = threadIdx.x + i * blockDim.x;
     if (v < nvec) {
+      if (partial) {
+        float* pg = partial + (size_t)blockIdx.x * 2 * H + v * N;
 #pragma unroll
-      for (int j = 0; j < N; ++j) {
-        if (dgamma) atomicAdd(dgamma + v * N + j, dg[i][j]);
-        if (!RMS && dbeta) atomicAdd(dbeta + v * N + j, db[i][j]);
+        for (int j = 0; j < N; j += 4) {
+          *reinterpret_cast<float4*>(pg + j) = make_float4(dg[i][j], dg[i][j + 1], dg[i][j + 2], dg[i][j + 3]);
+          if (!RMS) *reinterpret_cast<float4*>(pg + H + j) = make_float4(db[i][j], db[i][j + 1], db[i][j + 2], db[i][j + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          if (dgamma) atomicAdd(dgamma + v * N + j, dg[i][j]);
+          if (!RMS && dbeta) atomicAdd(dbeta + v * N + j, db[i][j]);
+        }
       }
     }
   }
 }
+
+// dgamma[c] += sum_b partial[b][0][c]; dbeta[c] += sum_b partial[b][1][c]
+__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dgamma,
+                                       float* __restrict__ dbeta, int nblk, int H) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  const int which = blockIdx.y;  // 0 = gamma, 1 = beta
+  float* out = which == 0 ? dgamma : dbeta;
+  if (!out) return;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  const float* p = partial + (size_t)which * H + c;
+  int b = 0;
+  for (; b + 4 <= nblk; b += 4) {
+    s0 += p[(size_t)(b + 0) * 2 * H];
+    s1 += p[(size_t)(b + 1) * 2 * H];
+    s2 += p[(size_t)(b + 2) * 2 * H];
+    s3 += p[(size_t)(b + 3) * 2 * H];
+  }
+  for (; b < nblk; ++b) s0 += p[(size_t)b * 2 * H];
+  out[c] += (s0 + s1) + (s2 + s3);
+}
+
+static inline int norm_bwd_grid(int rows) { return rows < sm_count() * 4 ? rows : sm_count() * 4; }
 
 template <typename T, bool RMS>
 static int norm_fwd_launch(const void* x, const void* gamma, const void* beta, void* y, float* mean,
@@ -202,22 +236,26 @@ static int norm_fwd_launch(const void* x, const void* gamma, const void* beta, v
 template <typename T, bool RMS>
 static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, const float* mean,
                            const float* rstd, const void* dres, void* dx, float* dgamma,
-                           float* dbeta, int rows, int H, cudaStream_t st) {
+                           float* dbeta, float* partial, int rows, int H, cudaStream_t st) {
   constexpr int N = Vec16<T>::N;
   if (H % N) TB_FAIL(TB_E_ARG, "norm: H=%d must be a multiple of %d", H, N);
   int nvec = H / N;
-  int grid = rows < sm_count() * 4 ? rows : sm_count() * 4;
+  int grid = norm_bwd_grid(rows);
 #define TB_NB(VPT_)                                                                               \
   {                                                                                               \
     int threads = ((nvec + VPT_ - 1) / VPT_ + 31) / 32 * 32;                                      \
     norm_bwd_kernel<T, VPT_, RMS><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x,            \
                                                              (const T*)gamma, mean, rstd,         \
                                                              (const T*)dres, (T*)dx, dgamma,      \
-                                                             dbeta, rows, H);                     \
+                                                             dbeta, partial, rows, H);            \
   }
   if (nvec <= 256) TB_NB(1) else if (nvec <= 1024) TB_NB(2) else if (nvec <= 4096) TB_NB(4) else
     TB_FAIL(TB_E_ARG, "norm: H=%d too large", H);
 #undef TB_NB
+  if (partial) {
+    dim3 rgrid((H + 255) / 256, RMS ? 1 : 2);
+    norm_bwd_reduce_kernel<<<rgrid, 256, 0, st>>>(partial, dgamma, dbeta, grid, H);
+  }
   TB_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
@@ -238,16 +276,26 @@ TB_EXPORT int tb_norm_fwd(const void* x, const void* gamma, const void* beta, vo
              : norm_fwd_launch<float, false>(x, gamma, beta, y, mean, rstd, rows, H, eps, st);
 }
 
+// Number of fp32 elements of scratch memory tb_norm_bwd wants for (rows, H).
+TB_EXPORT long tb_norm_bwd_workspace(int rows, int H) {
+  if (rows <= 0) return 0;
+  if (tb::ensure_device()) return 0;
+  return (long)norm_bwd_grid(rows) * 2 * H;
+}
+
 // dgamma / dbeta are fp32 buffers that the kernel ACCUMULATES into (zero them for a fresh
-// gradient). dres (optional) is added to dx.
+// gradient). dres (optional) is added to dx. `partial` is scratch memory of
+// tb_norm_bwd_workspace(rows, H) floats holding per-CTA partial sums that a second kernel
+// reduces; with partial == null the partial sums are added with atomics instead (slower).
 TB_EXPORT int tb_norm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, const void* dres, void* dx, float* dgamma,
-                          float* dbeta, int rows, int H, int rms, int dtype, cudaStream_t st) {
+                          float* dbeta, float* partial, int rows, int H, int rms, int dtype,
+                          cudaStream_t st) {
   TB_ENSURE_DEVICE();
   if (rows <= 0) return 0;
   if (dtype == 0)
-    return rms ? norm_bwd_launch<bf16, true>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, rows, H, st)
-               : norm_bwd_launch<bf16, false>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, rows, H, st);
-  return rms ? norm_bwd_launch<float, true>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, rows, H, st)
-             : norm_bwd_launch<float, false>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, rows, H, st);
+    return rms ? norm_bwd_launch<bf16, true>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, partial, rows, H, st)
+               : norm_bwd_launch<bf16, false>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, partial, rows, H, st);
+  return rms ? norm_bwd_launch<float, true>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, partial, rows, H, st)
+             : norm_bwd_launch<float, false>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, partial, rows, H, st);
 }

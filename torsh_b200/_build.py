@@ -100,7 +100,7 @@ def build_host(verbose: bool = False) -> Path:
         list(ex.map(lambda c: _run(c, verbose), jobs))
     out = LIBDIR / "libtorsh_b200_host.so"
     if srcs and (jobs or not out.exists()):
-        _run([cxx, "-shared", "-o", str(out), *map(str, objs), "-pthread", "-lz"], verbose)
+        _run([cxx, "-shared", "-o", str(out), *map(str, objs), "-pthread", "-lz", "-ldl", "-Wl,-Bsymbolic", "-Wl,--exclude-libs,ALL"], verbose)
     return out
 
 

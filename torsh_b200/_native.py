@@ -38,7 +38,7 @@ def _load(name: str, build_fn: str):
         getattr(_build, build_fn)()
     if not path.exists():
         raise NativeError(f"{path} is missing: run `python -m torsh_b200._build`")
-    return ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
+    return ctypes.CDLL(str(path), mode=ctypes.RTLD_LOCAL)
 
 
 def cuda():

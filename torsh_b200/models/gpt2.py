@@ -126,8 +126,10 @@ class GPT2Block(nn.Module):
         self.mlp = GPT2MLP(cfg)
 
     def forward(self, x, B: int, S: int):
-        x = self.attn(self.ln_1(x), x, B, S)
-        return self.mlp(self.ln_2(x), x)
+        h, x = norm_ops.layer_norm_fork(x, self.ln_1.weight, self.ln_1.bias, self.ln_1.eps)
+        x = self.attn(h, x, B, S)
+        h, x = norm_ops.layer_norm_fork(x, self.ln_2.weight, self.ln_2.bias, self.ln_2.eps)
+        return self.mlp(h, x)
 
 
 class GPT2Model(nn.Module):

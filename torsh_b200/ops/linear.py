@@ -15,27 +15,30 @@ from ._dispatch import kernel_ok
 from .gemm import gemm
 
 
-def _split_k(m_out: int, n_out: int, k: int) -> int:
-    tiles = ((m_out + 127) // 128) * ((n_out + 127) // 128)
+def _wgrad_plan(m_out: int, n_out: int, k: int) -> tuple[int, int]:
+    """(tile width, split-K factor) for a weight-gradient GEMM: wide tiles when the output is wide
+    enough, and enough K-splits that the work units fill the 148 SMs about twice."""
+    bn = 256 if n_out >= 256 else 128
+    tiles = ((m_out + 127) // 128) * ((n_out + bn - 1) // bn)
     kb = (k + 63) // 64
     want = max(1, (296 + tiles - 1) // tiles)
-    return max(1, min(want, kb // 4 if kb >= 8 else 1))
+    return bn, max(1, min(want, kb // 8 if kb >= 16 else 1))
 
 
 def _wgrad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor, layout: str):
     """dW for y = x Wᵀ (nk) or y = x W (kn). Returns a grad tensor, or None after accumulating into main_grad."""
     a, b = (dy2, x2) if layout == "nk" else (x2, dy2)
     m_out, n_out, k = a.shape[1], b.shape[1], a.shape[0]
-    sk = _split_k(m_out, n_out, k)
+    bn, sk = _wgrad_plan(m_out, n_out, k)
     mg = getattr(weight, "main_grad", None)
     if mg is not None:
-        gemm(a, b, a_major=1, b_major=1, out=mg, atomic=True, split_k=sk, bn=128)
+        gemm(a, b, a_major=1, b_major=1, out=mg, atomic=True, split_k=sk, bn=bn)
         return None
     if sk > 1:
         g = torch.zeros(m_out, n_out, dtype=torch.float32, device=a.device)
-        gemm(a, b, a_major=1, b_major=1, out=g, atomic=True, split_k=sk, bn=128)
+        gemm(a, b, a_major=1, b_major=1, out=g, atomic=True, split_k=sk, bn=bn)
         return g.to(weight.dtype)
-    return gemm(a, b, a_major=1, b_major=1)
+    return gemm(a, b, a_major=1, b_major=1, bn=bn)
 
 
 def _bgrad(dy2: torch.Tensor, bias: torch.Tensor):
