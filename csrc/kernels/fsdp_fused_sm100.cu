@@ -1,0 +1,172 @@
+// FSDP step kernel for sm_100a: gradient reduce-scatter FUSED with the sharded AdamW update and
+// with the all-gather of the updated bf16 parameters, in one launch over NVSwitch peer memory.
+//
+// Layout. One "unit" (a transformer block, or the whole model) is a contiguous range of the flat
+// parameter space. Every rank holds, in symmetric memory, the full fp32 gradient range of the unit
+// (what its own backward produced) and the full bf16 parameter range; it owns 1/world of the range
+// (its shard) for which it keeps fp32 master weights and the two Adam moments locally.
+//
+// Per 8 elements of its shard a thread does:
+//   g      = multimem.ld_reduce(grad)            the switch sums all ranks' copies (reduce-scatter)
+//   p,m,v  = AdamW(master, m, v, g / world)      fp32 state stays local and sharded
+//   multimem.st(param_bf16, bf16(p))             the switch writes every rank's copy (all-gather)
+// and, after the exit barrier, every rank clears its own copy of the unit's gradient range.
+// Without NVLS the same dataflow uses plain peer loads and peer stores.
+// NVLink traffic per rank and step: 4 B x shard in (reduced), 2 B x shard out (replicated by the
+// switch) - the minimum for a reduce-scatter plus all-gather - and no separate NCCL kernels,
+// no bucket copies, no second pass over the optimizer state.
+//
+// AdamW arithmetic follows crates/torsh-optim/src/adam.rs:809-950 (decoupled decay first, both
+// moments bias-corrected). The reference's FSDP "reduce-scatter" is all_reduce + slice followed by
+// shard -= grad (crates/torsh-distributed/src/fsdp.rs:373-419).
+#include "comm.cuh"
+#include "common.cuh"
+#include "host_util.h"
+
+namespace tb {
+
+constexpr int FSDP_THREADS = 512;
+constexpr int FSDP_MAX_BLOCKS = 64;
+
+struct FsdpArgs {
+  PeerTable grads;   // symmetric fp32 gradient buffer (full flat range)
+  PeerTable params;  // symmetric bf16 parameter buffer (full flat range)
+  PeerTable flags;   // symmetric flag buffer
+  char* grad_mc;     // multicast addresses (null: plain peer memory)
+  char* param_mc;
+  float* master;     // local shard state, indexed from 0
+  float* exp_avg;
+  float* exp_avg_sq;
+  long unit_off;     // element offset of the unit inside the flat range
+  long unit_len;     // elements in the unit (multiple of 8 * world)
+  long state_off;    // element offset of this unit's shard inside the local shard arrays
+  int rank, world;
+  const uint32_t* epoch_ptr;
+  float lr, beta1, beta2, eps, wd, bc1, bc2, grad_scale;
+  const float* dyn;  // optional device scalars (lr, bc1, bc2) for CUDA-graph replay
+  int* status;
+};
+
+template <bool NVLS>
+__global__ void __launch_bounds__(FSDP_THREADS)
+fsdp_rs_adamw_ag_kernel(FsdpArgs a) {
+  const uint32_t epoch = *a.epoch_ptr;
+  if (a.dyn) {
+    a.lr = a.dyn[0];
+    a.bc1 = a.dyn[1];
+    a.bc2 = a.dyn[2];
+  }
+  // every rank's backward has finished writing this unit's gradients
+  cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch, a.status);
+  const long shard = a.unit_len / a.world;
+  const long g0 = a.unit_off + (long)a.rank * shard;  // my shard inside the flat range
+  const long nvec = shard / 8;
+  const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long v = tid; v < nvec; v += nthreads) {
+    const long ge = g0 + v * 8;          // flat element index
+    const long se = a.state_off + v * 8; // local state index
+    float g[8];
+    if (NVLS) {
+      float4 x = multimem_ld_reduce_f32x4(a.grad_mc + ge * 4);
+      float4 y = multimem_ld_reduce_f32x4(a.grad_mc + ge * 4 + 16);
+      g[0] = x.x; g[1] = x.y; g[2] = x.z; g[3] = x.w; g[4] = y.x; g[5] = y.y; g[6] = y.z; g[7] = y.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] = 0.f;
+      for (int p = 0; p < a.world; ++p) {
+        const int q = (a.rank + p) % a.world;
+        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.grads.ptr[q]) + ge);
+        float4 x = src[0], y = src[1];
+        g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w; g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
+      }
+    }
+    float w[8], m[8], s[8];
+    *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(a.master + se);
+    *reinterpret_cast<float4*>(w + 4) = *reinterpret_cast<const float4*>(a.master + se + 4);
+    *reinterpret_cast<float4*>(m) = *reinterpret_cast<const float4*>(a.exp_avg + se);
+    *reinterpret_cast<float4*>(m + 4) = *reinterpret_cast<const float4*>(a.exp_avg + se + 4);
+    *reinterpret_cast<float4*>(s) = *reinterpret_cast<const float4*>(a.exp_avg_sq + se);
+    *reinterpret_cast<float4*>(s + 4) = *reinterpret_cast<const float4*>(a.exp_avg_sq + se + 4);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gi = g[j] * a.grad_scale;
+      float p = w[j];
+      p -= a.lr * a.wd * p;
+      m[j] = a.beta1 * m[j] + (1.f - a.beta1) * gi;
+      s[j] = a.beta2 * s[j] + (1.f - a.beta2) * gi * gi;
+      p -= a.lr * (m[j] / a.bc1) / (sqrtf(s[j] / a.bc2) + a.eps);
+      w[j] = p;
+    }
+    *reinterpret_cast<float4*>(a.master + se) = *reinterpret_cast<float4*>(w);
+    *reinterpret_cast<float4*>(a.master + se + 4) = *reinterpret_cast<float4*>(w + 4);
+    *reinterpret_cast<float4*>(a.exp_avg + se) = *reinterpret_cast<float4*>(m);
+    *reinterpret_cast<float4*>(a.exp_avg + se + 4) = *reinterpret_cast<float4*>(m + 4);
+    *reinterpret_cast<float4*>(a.exp_avg_sq + se) = *reinterpret_cast<float4*>(s);
+    *reinterpret_cast<float4*>(a.exp_avg_sq + se + 4) = *reinterpret_cast<float4*>(s + 4);
+    const uint4 o = make_uint4(pack_bf16x2(w[0], w[1]), pack_bf16x2(w[2], w[3]), pack_bf16x2(w[4], w[5]),
+                               pack_bf16x2(w[6], w[7]));
+    if (NVLS) {
+      multimem_st_16(a.param_mc + ge * 2, o);
+    } else {
+      for (int p = 0; p < a.world; ++p) {
+        const int q = (a.rank + p) % a.world;
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.params.ptr[q]) + ge) = o;
+      }
+    }
+  }
+  // all shards of the unit have been reduced everywhere and every parameter copy is complete
+  cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch + 1, a.status);
+  // Clear my own copy of the gradient for the next accumulation. This CTA's exit barrier only proves
+  // that the CTAs with the same index on the other ranks are done reading, so it clears exactly the
+  // vectors those CTAs read: the same vector indices, in every rank's shard.
+  float* gmine = reinterpret_cast<float*>(a.grads.ptr[a.rank]) + a.unit_off;
+  for (int q = 0; q < a.world; ++q) {
+    float4* gz = reinterpret_cast<float4*>(gmine + (long)q * shard);
+    for (long v = tid; v < nvec; v += nthreads) {
+      gz[2 * v] = make_float4(0.f, 0.f, 0.f, 0.f);
+      gz[2 * v + 1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+}
+
+__global__ void fsdp_bump_epoch_kernel(uint32_t* e) { *e += 1; }
+
+}  // namespace tb
+using namespace tb;
+
+// grads / params / flags: per-rank base pointers of the three symmetric buffers.
+// unit_off, unit_len in elements; unit_len must be a multiple of 8 * world and unit_off of 8.
+// master / exp_avg / exp_avg_sq: local fp32 shard arrays; this unit's shard starts at state_off.
+TB_EXPORT int tb_fsdp_rs_adamw_ag(const void* const* grads, const void* const* params, const void* const* flags,
+                                  void* grad_mc, void* param_mc, float* master, float* exp_avg, float* exp_avg_sq,
+                                  long unit_off, long unit_len, long state_off, int rank, int world,
+                                  const unsigned* epoch_ptr, float lr, float beta1, float beta2, float eps, float wd,
+                                  float bc1, float bc2, float grad_scale, const float* dyn, int nblocks, int* status,
+                                  cudaStream_t st) {
+  TB_ENSURE_DEVICE();
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) TB_FAIL(TB_E_ARG, "fsdp step: bad rank/world");
+  if (unit_len % (8L * world) || unit_off % 8 || state_off % 8)
+    TB_FAIL(TB_E_ARG, "fsdp step: unit_len (%ld) must be a multiple of 8*world, offsets of 8", unit_len);
+  if ((grad_mc == nullptr) != (param_mc == nullptr)) TB_FAIL(TB_E_ARG, "fsdp step: give both multicast addresses or none");
+  FsdpArgs a;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    a.grads.ptr[i] = i < world ? const_cast<void*>(grads[i]) : nullptr;
+    a.params.ptr[i] = i < world ? const_cast<void*>(params[i]) : nullptr;
+    a.flags.ptr[i] = i < world ? const_cast<void*>(flags[i]) : nullptr;
+  }
+  a.grad_mc = static_cast<char*>(grad_mc);
+  a.param_mc = static_cast<char*>(param_mc);
+  a.master = master; a.exp_avg = exp_avg; a.exp_avg_sq = exp_avg_sq;
+  a.unit_off = unit_off; a.unit_len = unit_len; a.state_off = state_off;
+  a.rank = rank; a.world = world; a.epoch_ptr = epoch_ptr;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.wd = wd; a.bc1 = bc1; a.bc2 = bc2;
+  a.grad_scale = grad_scale; a.dyn = dyn; a.status = status;
+  if (nblocks < 1) nblocks = 1;
+  if (nblocks > FSDP_MAX_BLOCKS) nblocks = FSDP_MAX_BLOCKS;
+  if (grad_mc) fsdp_rs_adamw_ag_kernel<true><<<nblocks, FSDP_THREADS, 0, st>>>(a);
+  else fsdp_rs_adamw_ag_kernel<false><<<nblocks, FSDP_THREADS, 0, st>>>(a);
+  fsdp_bump_epoch_kernel<<<1, 1, 0, st>>>(const_cast<uint32_t*>(epoch_ptr));
+  TB_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,161 @@
+"""Multi-rank checks run under torch.distributed.run (one process per GPU).
+
+  python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29531 \
+      tests/dist/check_collectives.py [collectives] [fsdp] [bench]
+Exit code 0 means every selected check passed on every rank.
+"""
+import os
+import sys
+import time
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+import torch
+import torch.distributed as dist
+
+
+def log(*a):
+    if dist.get_rank() == 0:
+        print(*a, flush=True)
+
+
+def check_collectives(dev):
+    from torsh_b200 import _native as nv
+    from torsh_b200.parallel.collectives import FusedCollectives
+    from torsh_b200.parallel.symm import SymmetricBuffer
+    rank, world = dist.get_rank(), dist.get_world_size()
+    fc = FusedCollectives(nblocks=32)
+    ok = True
+    for dtype in (torch.float32, torch.bfloat16):
+        n = 1 << 20
+        buf = SymmetricBuffer(n, dtype)
+        log(f"multicast available: {buf.has_multicast}")
+        modes = ["one_shot", "two_shot"]
+        for use_nvls in ([True, False] if buf.has_multicast else [False]):
+            fc.use_nvls = use_nvls
+            for mode in modes:
+                numel = 4096 * 8 if mode == "one_shot" else n
+                g = torch.Generator(device=dev).manual_seed(100 + rank)
+                x = torch.randn(numel, device=dev, dtype=dtype, generator=g)
+                ref = x.float().clone()
+                dist.all_reduce(ref)
+                buf.tensor[:numel].copy_(x)
+                fc.all_reduce_(buf, numel=numel, scale=0.5, mode=mode)
+                torch.cuda.synchronize()
+                nv.check_status()
+                err = (buf.tensor[:numel].float() - 0.5 * ref).abs().max().item()
+                tol = 0.05 if dtype == torch.bfloat16 else 1e-4
+                log(f"all_reduce {dtype} {mode} nvls={use_nvls}: max err {err:.5f}")
+                ok &= err < tol
+            # all-gather
+            chunk = n // world
+            buf.tensor.zero_()
+            buf.tensor[rank * chunk:(rank + 1) * chunk] = rank + 1
+            fc.all_gather_(buf, chunk)
+            torch.cuda.synchronize()
+            nv.check_status()
+            exp = torch.arange(1, world + 1, device=dev).repeat_interleave(chunk).to(dtype)
+            ok &= torch.equal(buf.tensor, exp)
+            log(f"all_gather {dtype} nvls={use_nvls}: {'ok' if torch.equal(buf.tensor, exp) else 'MISMATCH'}")
+            # reduce-scatter
+            g = torch.Generator(device=dev).manual_seed(200 + rank)
+            x = torch.randn(n, device=dev, dtype=dtype, generator=g)
+            ref = x.float().clone()
+            dist.all_reduce(ref)
+            buf.tensor.copy_(x)
+            out = fc.reduce_scatter(buf, chunk, scale=1.0 / world)
+            torch.cuda.synchronize()
+            nv.check_status()
+            err = (out.float() - ref[rank * chunk:(rank + 1) * chunk] / world).abs().max().item()
+            log(f"reduce_scatter {dtype} nvls={use_nvls}: max err {err:.5f}")
+            ok &= err < (0.05 if dtype == torch.bfloat16 else 1e-4)
+    # bandwidth of the two-shot all-reduce vs NCCL (device-timed, max over ranks)
+    fc.use_nvls = None
+    for nbytes in (1 << 20, 1 << 24, 1 << 28):
+        n = nbytes // 2
+        buf = SymmetricBuffer(n, torch.bfloat16)
+        x = torch.randn(n, device=dev, dtype=torch.bfloat16)
+        for name, fn in (("fused", lambda: fc.all_reduce_(buf, mode="two_shot")), ("nccl", lambda: dist.all_reduce(x))):
+            for _ in range(3):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            dist.barrier(); torch.cuda.synchronize()
+            e0.record()
+            for _ in range(10):
+                fn()
+            e1.record(); torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / 10], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            busbw = nbytes * 2 * (world - 1) / world / (t.item() * 1e-3) / 1e9
+            log(f"all_reduce {nbytes >> 20} MiB {name}: {t.item() * 1e3:.1f} us, bus bw {busbw:.0f} GB/s")
+        nv.check_status()
+    return ok
+
+
+def check_fsdp(dev):
+    """2+ ranks of the fused FSDP step must reproduce a single-process AdamW run on the global batch."""
+    from torsh_b200 import _native as nv
+    from torsh_b200.engine import CausalLMTrainer
+    from torsh_b200.models import GPT2Config, GPTForCausalLM
+    from torsh_b200.parallel.fsdp import FlatFSDP, FsdpConfig
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cfg = GPT2Config.tiny()
+    B, S, steps = 4, 128, 6
+    data = torch.randint(0, cfg.vocab_size, (world * B, S + 1), generator=torch.Generator().manual_seed(7))
+    ok = True
+    ref_losses = None
+    for overlap, use_graph in ((False, False), (True, False), (True, True)):
+        torch.manual_seed(0)
+        model = GPTForCausalLM(cfg).to(dev)
+        eng = FlatFSDP(config=FsdpConfig(overlap=overlap))
+        tr = CausalLMTrainer(model, lr=1e-3, weight_decay=0.01, batch_size=B, seq_len=S, use_graph=use_graph,
+                             warmup_eager=2, parallel=eng)
+        mine = data[rank * B:(rank + 1) * B]
+        x, y = mine[:, :-1].contiguous().pin_memory(), mine[:, 1:].contiguous().pin_memory()
+        losses = []
+        for _ in range(steps):
+            l = torch.tensor([tr.step(x, y)], device=dev)
+            dist.all_reduce(l)
+            losses.append(l.item() / world)
+        torch.cuda.synchronize()
+        nv.check_status()
+        # parameters must be bit-identical on every rank
+        flat = tr.flat.lowp.float()
+        mx = flat.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        mn = flat.clone(); dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+        same = torch.equal(mx, mn)
+        log(f"fsdp overlap={overlap} graph={use_graph}: losses {[round(v, 4) for v in losses]} params identical={same}")
+        ok &= same and losses[-1] < losses[0] - 0.5
+        if ref_losses is None:
+            # single-process oracle on the global batch (rank 0's GPU, plain flat AdamW)
+            torch.manual_seed(0)
+            m1 = GPTForCausalLM(cfg).to(dev)
+            t1 = CausalLMTrainer(m1, lr=1e-3, weight_decay=0.01, batch_size=world * B, seq_len=S, use_graph=False)
+            gx, gy = data[:, :-1].contiguous().pin_memory(), data[:, 1:].contiguous().pin_memory()
+            ref_losses = [t1.step(gx, gy) for _ in range(steps)]
+            log(f"single-process oracle: {[round(v, 4) for v in ref_losses]}")
+        for a, b in zip(losses, ref_losses):
+            ok &= abs(a - b) < 0.03 * abs(b)
+    return ok
+
+
+def main():
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    what = sys.argv[1:] or ["collectives", "fsdp"]
+    ok = True
+    if "collectives" in what:
+        ok &= check_collectives(dev)
+    if "fsdp" in what:
+        ok &= check_fsdp(dev)
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    log("ALL CHECKS PASSED" if flag.item() == 1 else "CHECKS FAILED")
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 1 else 1)
+
+
+if __name__ == "__main__":
+    main()
