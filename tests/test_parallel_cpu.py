@@ -1,0 +1,134 @@
+"""CPU tests of the host-side parallel logic: planner arithmetic, stores, gloo ranks running DDP."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def test_bucket_assignment_largest_first():
+    from torsh_b200.parallel import planner
+    mb = 1024 * 1024
+    sizes = [1 * mb, 20 * mb, 3 * mb, 10 * mb, 10 * mb, 4 * mb]
+    got = planner.assign_buckets(sizes, 25 * mb)
+    # sorted desc: 20,10,10,4,3,1 -> [20] | [10,10,4] | [3,1]
+    assert got == [2, 0, 2, 1, 1, 1]
+    assert planner.assign_buckets([], 25 * mb) == []
+
+
+def test_shard_ranges_cover_everything():
+    from torsh_b200.parallel import planner
+    from torsh_b200.parallel.fsdp import shard_range
+    for numel, world in ((10, 4), (1000, 8), (7, 8), (64, 2)):
+        prev = 0
+        for r in range(world):
+            s, e = planner.shard_range(numel, world, r)
+            assert (s, e) == shard_range(numel, world, r) and s == prev
+            base, rem = divmod(numel, world)
+            assert e - s == base + (1 if r < rem else 0)
+            prev = e
+        assert prev == numel
+
+
+def test_rank_mapping_reference_and_tp_fastest():
+    from torsh_b200.parallel import planner
+    dp, tp, pp = 1, 4, 2
+    # reference rule: rank = dp*(tp*pp) + tp*pp_size + pp (pp fastest)
+    assert planner.rank_of(0, 1, 1, dp, tp, pp) == 3
+    assert planner.rank_of(0, 1, 1, dp, tp, pp, tp_fastest=True) == 5
+    for order in (False, True):
+        seen = set()
+        for r in range(dp * tp * pp):
+            c = planner.coords_of(r, dp, tp, pp, order)
+            assert planner.rank_of(*c, dp, tp, pp, order) == r
+            seen.add(c)
+        assert len(seen) == 8
+
+
+def test_pipeline_schedules():
+    from torsh_b200.parallel import planner
+    S, M = 4, 8
+    for stage in range(S):
+        a = planner.pipeline_schedule("1f1b", stage, S, M)
+        assert [m for k, m in a if k == "F"] == list(range(M)) and [m for k, m in a if k == "B"] == list(range(M))
+        warm = min(S - stage - 1, M)
+        assert all(k == "F" for k, _ in a[:warm]) and planner.pipeline_peak_inflight("1f1b", stage, S, M) == warm + 1
+        done_f = set()
+        for k, m in a:
+            if k == "F":
+                done_f.add(m)
+            else:
+                assert m in done_f
+    g = planner.pipeline_schedule("gpipe", 0, S, M)
+    assert g[:M] == [("F", i) for i in range(M)] and planner.pipeline_peak_inflight("gpipe", 0, S, M) == M
+
+
+def test_memory_and_file_store(tmp_path):
+    from torsh_b200.parallel.store import FileStore, MemoryStore
+    for st in (MemoryStore(), FileStore(tmp_path / "kv")):
+        st.set("a", b"1")
+        assert st.get("a") == b"1" and st.contains("a") and st.num_keys() == 1
+        assert st.add("n", 2) == 2 and st.add("n", 3) == 5
+        assert st.compare_and_swap("a", b"0", b"2") is False and st.compare_and_swap("a", b"1", b"2") is True
+        st.wait(["a"], 1.0)
+        with pytest.raises(Exception):
+            st.wait(["zz"], 0.05)
+        st.delete("a")
+        assert st.get("a") is None
+
+
+def _ddp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torsh_b200.parallel.ddp import BucketConfig, DistributedDataParallel
+        torch.manual_seed(0)
+        net = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4), torch.nn.Linear(4, 4))
+        for p in net[3].parameters():  # unused branch: parameters that never receive a gradient
+            pass
+        ddp = DistributedDataParallel(net, bucket_config=BucketConfig(max_bucket_size_mb=0.002))
+        g = torch.Generator().manual_seed(10 + rank)
+        x = torch.randn(8, 16, generator=g)
+        y = net[2](net[1](net[0](x))).pow(2).mean()   # skips net[3]
+        y.backward()
+        ddp.sync_gradients()
+        # oracle: average of per-rank gradients computed independently
+        grads = []
+        for r in range(world):
+            torch.manual_seed(0)
+            ref = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4), torch.nn.Linear(4, 4))
+            xr = torch.randn(8, 16, generator=torch.Generator().manual_seed(10 + r))
+            ref[2](ref[1](ref[0](xr))).pow(2).mean().backward()
+            grads.append([p.grad.clone() if p.grad is not None else torch.zeros_like(p) for p in ref.parameters()])
+        ok = True
+        for i, p in enumerate(net.parameters()):
+            exp = sum(gr[i] for gr in grads) / world
+            ok &= torch.allclose(p.grad, exp, atol=1e-6)
+        st = ddp.get_sync_stats()
+        ok &= st["unused_parameters"] == 2 and len(ddp.buckets) >= 2 and st["buckets_reduced"] == len(ddp.buckets)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ddp_two_gloo_ranks_average_gradients():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ddp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(30)
+    assert sorted(res) == [(0, True), (1, True)]
