@@ -201,6 +201,46 @@ reducescatter_kernel(const CommArgs a, T* __restrict__ out) {
   cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch + 1, a.status);
 }
 
+// Second half of GEMM -> reduce-scatter: once every rank has finished adding its partial tiles into
+// this rank's accumulation buffer (entry barrier), convert it to the bf16 output (+ bias, + residual),
+// clear it for the next use, and hold everybody until all buffers are clear again (exit barrier).
+template <typename TA>
+__global__ void __launch_bounds__(COMM_THREADS)
+rs_finalize_kernel(const CommArgs a, TA* __restrict__ acc, const bf16* __restrict__ bias,
+                   const bf16* __restrict__ residual, bf16* __restrict__ out, long rows, int N) {
+  const uint32_t epoch = *a.epoch_ptr;
+  cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch, a.status);
+  const long nvec = rows * N / 8;
+  for (long v = (long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long)gridDim.x * blockDim.x) {
+    const long e = v * 8;
+    const int c = (int)(e % N);
+    float f[8];
+    if (sizeof(TA) == 4) {
+      float4 x = reinterpret_cast<float4*>(acc + e)[0], y = reinterpret_cast<float4*>(acc + e)[1];
+      f[0] = x.x; f[1] = x.y; f[2] = x.z; f[3] = x.w; f[4] = y.x; f[5] = y.y; f[6] = y.z; f[7] = y.w;
+      reinterpret_cast<float4*>(acc + e)[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      reinterpret_cast<float4*>(acc + e)[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    } else {
+      Acc<bf16>::load(acc + e, f);
+      *reinterpret_cast<uint4*>(acc + e) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (bias) {
+      float b[8];
+      Acc<bf16>::load(bias + c, b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += b[j];
+    }
+    if (residual) {
+      float r[8];
+      Acc<bf16>::load(residual + e, r);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += r[j];
+    }
+    *reinterpret_cast<uint4*>(out + e) = Acc<bf16>::pack(f);
+  }
+  cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch + 1, a.status);
+}
+
 // Runs after a collective on the same stream: the next launch sees a fresh pair of barrier values.
 __global__ void bump_epoch_kernel(uint32_t* e) { *e += 1; }
 
@@ -290,6 +330,25 @@ TB_EXPORT int tb_reducescatter(const void* const* bufs, const void* const* flags
     if (use_nvls) reducescatter_kernel<float, true><<<nblocks, COMM_THREADS, 0, st>>>(a, (float*)out);
     else reducescatter_kernel<float, false><<<nblocks, COMM_THREADS, 0, st>>>(a, (float*)out);
   }
+  bump_epoch_kernel<<<1, 1, 0, st>>>(const_cast<uint32_t*>(epoch_ptr));
+  TB_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// acc: this rank's accumulation buffer [rows, N] (contiguous; fp32 when acc_f32 else bf16).
+// out: bf16 [rows, N]; bias [N] and residual [rows, N] are optional.
+TB_EXPORT int tb_rs_finalize(const void* const* flags, int rank, int world, const unsigned* epoch_ptr, void* acc,
+                             int acc_f32, const void* bias, const void* residual, void* out, long rows, int N,
+                             int nblocks, int* status, cudaStream_t st) {
+  TB_ENSURE_DEVICE();
+  if (N % 8) TB_FAIL(TB_E_ARG, "rs_finalize: N must be a multiple of 8");
+  CommArgs a;
+  const void* none[MAX_RANKS] = {nullptr};
+  if (int r = fill_args(a, none, flags, nullptr, rank, world, epoch_ptr, 0, 0, 1.f, status)) return r;
+  if (nblocks < 1) nblocks = 1;
+  if (nblocks > COMM_MAX_BLOCKS) nblocks = COMM_MAX_BLOCKS;
+  if (acc_f32) rs_finalize_kernel<float><<<nblocks, COMM_THREADS, 0, st>>>(a, (float*)acc, (const bf16*)bias, (const bf16*)residual, (bf16*)out, rows, N);
+  else rs_finalize_kernel<bf16><<<nblocks, COMM_THREADS, 0, st>>>(a, (bf16*)acc, (const bf16*)bias, (const bf16*)residual, (bf16*)out, rows, N);
   bump_epoch_kernel<<<1, 1, 0, st>>>(const_cast<uint32_t*>(epoch_ptr));
   TB_CUDA_CHECK(cudaGetLastError());
   return 0;

@@ -14,6 +14,7 @@
 // Replaces the reference's tiled SGEMM source string
 // (crates/torsh-backend/src/kernel_generation/types/cuda_compiler.rs:104-167) and its
 // unwired cuBLAS call (crates/torsh-backend/src/cuda/backend.rs:695-726).
+#include "comm.cuh"
 #include "host_util.h"
 #include "sm100.cuh"
 
@@ -49,6 +50,23 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int kb_total, kb_per_split;
   int* status;
+  // ---- tensor-parallel fusions (all zero / null for a plain GEMM) --------------------------------
+  // GEMM -> reduce-scatter: output row r belongs to rank r / rs_rows; the epilogue adds the tile
+  // straight into that rank's accumulation buffer rs_dst[owner] (bf16x2 or fp32 reductions over
+  // NVLink), so the transfer of a tile overlaps the math of the next one.
+  int rs_rows;
+  void* rs_dst[MAX_RANKS];
+  // all-gather -> GEMM: the first ag_ctas CTAs copy the peers' A shards (ag_rows rows of K elements
+  // each, contiguous) into the local full A that map_a describes, 128-row tile by tile, and publish
+  // a ready flag per tile; the GEMM CTAs start on the local shard and consume tiles as they land.
+  int ag_ctas, ag_rows;
+  const void* ag_src[MAX_RANKS];
+  void* ag_dst;
+  uint32_t* ag_ready;        // local, one word per m-tile; ready when >= the launch's epoch
+  void* flag_tbl[MAX_RANKS]; // symmetric flag buffer (cross-rank barriers of the copy CTAs)
+  const uint32_t* epoch_ptr;
+  int rank, world;
+  int m_rot;                 // m-tiles are visited starting at this tile (own shard first / last)
 };
 
 template <int BN, int STAGES>
@@ -72,8 +90,87 @@ __device__ __forceinline__ void decode_work(const GemmParams& p, int work, int& 
     m_t = tile / p.tiles_n;
     n_t = tile - m_t * p.tiles_n;
   }
+  if (p.m_rot) {
+    m_t += p.m_rot;
+    if (m_t >= p.tiles_m) m_t -= p.tiles_m;
+  }
   kb0 = ks * p.kb_per_split;
   kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+}
+
+// Bounded wait on a flag in this GPU's own memory (written by a copy CTA of the same launch).
+__device__ __forceinline__ bool wait_flag_ge_gpu(const uint32_t* flag, uint32_t target, int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if ((int32_t)(v - target) >= 0) return true;
+    if ((++spins & 31u) == 0u && globaltimer_ns() - t0 > TB_PEER_WAIT_LIMIT_NS) {
+      if (status) atomicCAS(status, 0, TB_ERR_WAIT_PEER);
+      return false;
+    }
+  }
+}
+
+// Copy role of the all-gather -> GEMM kernel. One thread per CTA streams the peers' A shards through
+// a shared-memory ring with bulk async copies (peer memory -> smem -> local memory), nearest peer
+// first, and publishes one ready flag per 128-row tile. SMEM_BYTES of the CTA's dynamic shared
+// memory serve as the ring; `bars` are mbarriers placed after it.
+template <int SMEM_BYTES>
+__device__ __forceinline__ void ag_copy_role(const GemmParams& p, uint8_t* smem, uint64_t* bars,
+                                             volatile int* abort_flag) {
+  constexpr int PIECE = 16384;
+  constexpr int NBUF = SMEM_BYTES / PIECE < 8 ? SMEM_BYTES / PIECE : 8;
+  const uint32_t epoch = *p.epoch_ptr;
+  PeerTable flags;
+#pragma unroll
+  for (int i = 0; i < MAX_RANKS; ++i) flags.ptr[i] = p.flag_tbl[i];
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int b = 0; b < NBUF; ++b) mbar_init(&bars[b], 1);
+    fence_barrier_init();
+  }
+  // every rank's shard is complete once its kernel has started (stream order on that rank)
+  cta_barrier_all_ranks(flags, blockIdx.x, p.rank, p.world, 2 * epoch, p.status);
+  if (threadIdx.x == 0) {
+    const long tile_bytes = (long)BM * p.K * 2;
+    const int tiles_per_rank = p.ag_rows / BM;
+    const int pieces = (int)(tile_bytes / PIECE);  // launcher guarantees divisibility
+    uint32_t phase = 0;
+    for (int step = 1; step < p.world; ++step) {
+      const int q = (p.rank + step) % p.world;
+      for (int t = blockIdx.x; t < tiles_per_rank; t += p.ag_ctas) {
+        const char* src = reinterpret_cast<const char*>(p.ag_src[q]) + (long)t * tile_bytes;
+        char* dst = reinterpret_cast<char*>(p.ag_dst) + ((long)q * tiles_per_rank + t) * tile_bytes;
+        for (int i0 = 0; i0 < pieces; i0 += NBUF) {
+          const int n = min(NBUF, pieces - i0);
+          for (int b = 0; b < n; ++b) {
+            mbar_expect_tx(&bars[b], PIECE);
+            bulk_load(smem + b * PIECE, src + (long)(i0 + b) * PIECE, PIECE, &bars[b]);
+          }
+          for (int b = 0; b < n; ++b) {
+            mbar_wait(&bars[b], phase, abort_flag, p.status, TB_ERR_WAIT_FULL);
+            bulk_store(dst + (long)(i0 + b) * PIECE, smem + b * PIECE, PIECE);
+          }
+          bulk_commit();
+          bulk_wait_read_all();  // the ring may be refilled
+          phase ^= 1;
+        }
+        bulk_wait_all();  // the tile is in local memory
+        __threadfence();
+        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ag_ready + q * tiles_per_rank + t), "r"(epoch)
+                     : "memory");
+      }
+    }
+    if (*abort_flag) {
+      uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 2000000ull) {
+      }
+    }
+  }
+  // peers may overwrite their shards only after everybody has copied them
+  cta_barrier_all_ranks(flags, blockIdx.x, p.rank, p.world, 2 * epoch + 1, p.status);
 }
 
 template <int BN, int A_MAJOR, int B_MAJOR, int STAGES>
@@ -94,6 +191,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   const int lane = threadIdx.x & 31;
   const int total_work = p.tiles_m * p.tiles_n * p.split_k;
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+
+  if (p.ag_ctas > 0 && (int)blockIdx.x < p.ag_ctas) {
+    ag_copy_role<L::BAR_OFFSET>(p, smem, full, abort_flag);
+    return;
+  }
+  // GEMM CTAs are numbered from 0 after the copy CTAs
+  const int worker = (int)blockIdx.x - p.ag_ctas;
+  const int nworkers = (int)gridDim.x - p.ag_ctas;
+  const uint32_t ag_epoch = p.ag_ctas > 0 ? *p.epoch_ptr : 0u;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -123,9 +229,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tma_prefetch_desc(&map_b);
       int s = 0;
       uint32_t phase = 0;
-      for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
+      for (int work = worker; work < total_work; work += nworkers) {
         int m_t, n_t, kb0, kb1;
         decode_work(p, work, m_t, n_t, kb0, kb1);
+        if (p.ag_ctas > 0 && (m_t * BM) / p.ag_rows != p.rank) {
+          // rows of a peer: wait (bounded) until the copy CTAs have landed this 128-row tile locally
+          if (!*abort_flag && !wait_flag_ge_gpu(p.ag_ready + m_t, ag_epoch, p.status)) *abort_flag = 1;
+          fence_proxy_async_all();
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           mbar_wait(&empty[s], phase ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
           uint8_t* sa = smem + s * L::STAGE_BYTES;
@@ -166,7 +277,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
+      for (int work = worker; work < total_work; work += nworkers) {
         int m_t, n_t, kb0, kb1;
         decode_work(p, work, m_t, n_t, kb0, kb1);
         mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_EMPTY);
@@ -206,7 +317,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     int acc = 0;
     uint32_t acc_phase = 0;
     const int flags = p.flags;
-    for (int work = blockIdx.x; work < total_work; work += gridDim.x) {
+    for (int work = worker; work < total_work; work += nworkers) {
       int m_t, n_t, kb0, kb1;
       decode_work(p, work, m_t, n_t, kb0, kb1);
       mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
@@ -227,6 +338,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
         const bool full_chunk = (n0 + 32 <= p.N);
         const size_t off = (size_t)row * p.ldd + n0;
+        if (p.rs_rows > 0) {
+          // GEMM -> reduce-scatter: add this row segment into the owner's buffer over NVLink
+          const int owner = row / p.rs_rows;
+          const size_t roff = (size_t)(row - owner * p.rs_rows) * p.ldd + n0;
+          if (flags & EPI_OUT_F32) {
+            float* dp = reinterpret_cast<float*>(p.rs_dst[owner]) + roff;
+#pragma unroll
+            for (int g = 0; g < 8; ++g)
+              asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dp + g * 4),
+                           "f"(f[g * 4]), "f"(f[g * 4 + 1]), "f"(f[g * 4 + 2]), "f"(f[g * 4 + 3])
+                           : "memory");
+          } else {
+            __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) + roff;
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dp + g * 8),
+                           "r"(pack_bf16x2(f[g * 8 + 0], f[g * 8 + 1])), "r"(pack_bf16x2(f[g * 8 + 2], f[g * 8 + 3])),
+                           "r"(pack_bf16x2(f[g * 8 + 4], f[g * 8 + 5])), "r"(pack_bf16x2(f[g * 8 + 6], f[g * 8 + 7]))
+                           : "memory");
+          }
+          continue;
+        }
         if (full_chunk && (p.ldd & 7) == 0) {
           if (add_bias) {
             const uint4* bp = reinterpret_cast<const uint4*>(p.bias + n0);
@@ -382,7 +515,9 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
     configured = true;
   }
   int total = p.tiles_m * p.tiles_n * p.split_k;
-  int grid = total < sm_count() ? total : sm_count();
+  int workers = sm_count() - p.ag_ctas;  // copy CTAs and GEMM CTAs must all be resident at once
+  if (workers < 1) TB_FAIL(TB_E_ARG, "gemm: too many copy CTAs");
+  int grid = (total < workers ? total : workers) + p.ag_ctas;
   kern<<<grid, GEMM_THREADS, L::ALLOC, stream>>>(ma, mb, p);
   TB_CUDA_CHECK(cudaGetLastError());
   return TB_LAUNCH_OK;
@@ -397,11 +532,59 @@ using namespace tb;
 //   b_major = 0: B is stored [N, K] (row stride ldb);  1: B is stored [K, N] (row stride ldb)
 // lda / ldb must be multiples of 8 elements and the base pointers 16-byte aligned (TMA).
 // `bn` selects the tile width (128 or 256); 0 lets the launcher choose.
+struct TpFusion {
+  int kind = 0;  // 0 none, 1 GEMM -> reduce-scatter, 2 all-gather -> GEMM
+  int rank = 0, world = 1;
+  const void* const* peers = nullptr;   // kind 1: per-rank accumulation buffers; kind 2: per-rank A shards
+  const void* const* flags = nullptr;   // kind 2: symmetric flag buffers
+  const unsigned* epoch_ptr = nullptr;  // kind 2
+  unsigned* ready = nullptr;            // kind 2: local per-tile flags
+  int copy_ctas = 0;                    // kind 2
+};
+
+static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, int K, int a_major,
+                         int b_major, int lda, int ldb, int ldd, const void* bias,
+                         const void* residual, int ldr, void* preact, const void* aux, int flags,
+                         int split_k, int bn, int* status, cudaStream_t stream, const TpFusion& tp);
+
 TB_EXPORT int tb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, int K, int a_major,
                            int b_major, int lda, int ldb, int ldd, const void* bias,
                            const void* residual, int ldr, void* preact, const void* aux, int flags,
                            int split_k, int bn, int* status, cudaStream_t stream) {
   TB_ENSURE_DEVICE();
+  return gemm_dispatch(A, B, D, M, N, K, a_major, b_major, lda, ldb, ldd, bias, residual, ldr, preact, aux, flags,
+                       split_k, bn, status, stream, TpFusion{});
+}
+
+// Row-parallel linear with sequence parallelism: partial = A[M, K_local] * B[N, K_local]^T is
+// reduce-scattered along M inside the epilogue. dst[r] is rank r's accumulation buffer
+// [M / world, ldd] (bf16 or fp32 per `out_f32`), which must be zero (or hold the value to add to)
+// before ANY rank launches; a cross-rank barrier must follow before the owner reads it.
+TB_EXPORT int tb_gemm_rs(const void* A, const void* B, const void* const* dst, int M, int N, int K, int b_major,
+                         int lda, int ldb, int ldd, int out_f32, int rank, int world, int bn, int* status,
+                         cudaStream_t stream) {
+  TB_ENSURE_DEVICE();
+  if (world < 1 || world > MAX_RANKS || M % (128 * world)) TB_FAIL(TB_E_ARG, "gemm_rs: M=%d must be a multiple of 128*world", M);
+  if (N % 32 || ldd % 8) TB_FAIL(TB_E_ARG, "gemm_rs: N must be a multiple of 32 and ldd of 8");
+  TpFusion tp;
+  tp.kind = 1; tp.rank = rank; tp.world = world; tp.peers = dst;
+  return gemm_dispatch(A, B, const_cast<void*>(dst[rank]), M, N, K, 0, b_major, lda, ldb, ldd, nullptr, nullptr, 0,
+                       nullptr, nullptr, out_f32 ? EPI_OUT_F32 : 0, 1, bn, status, stream, tp);
+}
+
+// Column-parallel linear with sequence parallelism: D[M, N] = gather(A)[M, K] * B[N, K]^T where rank r
+// owns rows [r*M/world, (r+1)*M/world) of A. a_full is the local [M, K] staging matrix (contiguous,
+// lda = K) whose own-rank rows already hold this rank's shard; shards[r] is rank r's shard
+// [M/world, K] (contiguous; may point into that rank's a_full). ready: local uint32 [M/128].
+TB_EXPORT int tb_ag_gemm(void* a_full, const void* const* shards, const void* const* flag_bufs,
+                         const unsigned* epoch_ptr, unsigned* ready, const void* B, void* D, int M, int N, int K,
+                         int b_major, int ldb, int ldd, const void* bias, int flags, int rank, int world,
+                         int copy_ctas, int bn, int* status, cudaStream_t stream);
+
+static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, int K, int a_major,
+                         int b_major, int lda, int ldb, int ldd, const void* bias,
+                         const void* residual, int ldr, void* preact, const void* aux, int flags,
+                         int split_k, int bn, int* status, cudaStream_t stream, const TpFusion& tp) {
   if (!A || !B || !D || M <= 0 || N <= 0 || K <= 0) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: null pointer or empty shape");
   if ((lda & 7) || (ldb & 7)) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: lda/ldb must be multiples of 8 (got %d, %d)", lda, ldb);
   if ((flags & EPI_BIAS) && !bias) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: EPI_BIAS without bias");
@@ -419,7 +602,7 @@ TB_EXPORT int tb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, 
   }
   if (bn != 128 && bn != 256) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: bn must be 128 or 256");
 
-  GemmParams p;
+  GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.ldd = ldd; p.ldr = ldr;
   p.D = D;
@@ -436,6 +619,26 @@ TB_EXPORT int tb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, 
   split_k = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
   p.split_k = split_k;
   p.status = status;
+  p.rank = tp.rank;
+  p.world = tp.world;
+  if (tp.kind == 1) {
+    p.rs_rows = M / tp.world;
+    for (int i = 0; i < tp.world; ++i) p.rs_dst[i] = const_cast<void*>(tp.peers[i]);
+    // start with the tiles of the next rank and finish with the own rows: spreads the NVLink
+    // traffic of the ranks over different destinations at any moment
+    p.m_rot = ((tp.rank + 1) % tp.world) * (p.rs_rows / BM);
+  } else if (tp.kind == 2) {
+    p.ag_ctas = tp.copy_ctas;
+    p.ag_rows = M / tp.world;
+    for (int i = 0; i < tp.world; ++i) {
+      p.ag_src[i] = tp.peers[i];
+      p.flag_tbl[i] = const_cast<void*>(tp.flags[i]);
+    }
+    p.ag_dst = const_cast<void*>(A);
+    p.ag_ready = tp.ready;
+    p.epoch_ptr = tp.epoch_ptr;
+    p.m_rot = tp.rank * (p.ag_rows / BM);  // own shard first
+  }
 
   CUtensorMap ma, mb;
   {
@@ -464,6 +667,30 @@ TB_EXPORT int tb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, 
   else TB_DISPATCH(128, 6);
 #undef TB_DISPATCH
   TB_FAIL(TB_E_ARG, "tb_gemm_bf16: unsupported major combination");
+}
+
+__global__ void gemm_bump_epoch_kernel(uint32_t* e) { *e += 1; }
+
+TB_EXPORT int tb_ag_gemm(void* a_full, const void* const* shards, const void* const* flag_bufs,
+                         const unsigned* epoch_ptr, unsigned* ready, const void* B, void* D, int M, int N, int K,
+                         int b_major, int ldb, int ldd, const void* bias, int flags, int rank, int world,
+                         int copy_ctas, int bn, int* status, cudaStream_t stream) {
+  TB_ENSURE_DEVICE();
+  if (world < 1 || world > MAX_RANKS || M % (128 * world)) TB_FAIL(TB_E_ARG, "ag_gemm: M=%d must be a multiple of 128*world", M);
+  if (((long)128 * K * 2) % 16384) TB_FAIL(TB_E_ARG, "ag_gemm: K=%d must be a multiple of 64", K);
+  if (copy_ctas < 1) copy_ctas = 16;
+  if (copy_ctas > 64) copy_ctas = 64;
+  if (world == 1) copy_ctas = 0;
+  TpFusion tp;
+  tp.kind = world > 1 ? 2 : 0;
+  tp.rank = rank; tp.world = world; tp.peers = shards; tp.flags = flag_bufs; tp.epoch_ptr = epoch_ptr; tp.ready = ready;
+  tp.copy_ctas = copy_ctas;
+  int r = gemm_dispatch(a_full, B, D, M, N, K, 0, b_major, K, ldb, ldd, bias, nullptr, 0, nullptr, nullptr, flags, 1,
+                        bn, status, stream, tp);
+  if (r) return r;
+  if (world > 1) gemm_bump_epoch_kernel<<<1, 1, 0, stream>>>(const_cast<unsigned*>(epoch_ptr));
+  TB_CUDA_CHECK(cudaGetLastError());
+  return 0;
 }
 
 // Records the device that subsequent launches (from any thread) must run on.
