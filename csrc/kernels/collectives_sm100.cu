@@ -112,31 +112,45 @@ allreduce_kernel(const CommArgs a) {
   long b0, b1;
   slice_of(a.n, a.world, a.rank, N, b0, b1);
   const long nvec = (b1 - b0) / N;
-  for (long v = tid; v < nvec; v += nthreads) {
-    const long eoff = a.byte_off + (b0 + v * N) * (long)sizeof(T);
-    float f[N];
-    if (MODE == 1) {
-      Acc<T>::mc_reduce(a.mc + eoff, f);
-    } else {
+  constexpr int U = 4;  // vectors in flight per thread
+  for (long v0 = tid; v0 < nvec; v0 += nthreads * U) {
+    float f[U][N];
+    long eoff[U];
 #pragma unroll
-      for (int j = 0; j < N; ++j) f[j] = 0.f;
-      for (int p = 0; p < a.world; ++p) {
-        const int q = (a.rank + p) % a.world;
-        float g[N];
-        Acc<T>::load(reinterpret_cast<const char*>(a.bufs.ptr[q]) + eoff, g);
+    for (int u = 0; u < U; ++u) {
+      const long v = v0 + (long)u * nthreads;
+      eoff[u] = a.byte_off + (b0 + v * N) * (long)sizeof(T);
+      if (v < nvec) {
+        if (MODE == 1) {
+          Acc<T>::mc_reduce(a.mc + eoff[u], f[u]);
+        } else {
 #pragma unroll
-        for (int j = 0; j < N; ++j) f[j] += g[j];
+          for (int j = 0; j < N; ++j) f[u][j] = 0.f;
+          for (int p = 0; p < a.world; ++p) {
+            const int q = (a.rank + p) % a.world;
+            float g[N];
+            Acc<T>::load(reinterpret_cast<const char*>(a.bufs.ptr[q]) + eoff[u], g);
+#pragma unroll
+            for (int j = 0; j < N; ++j) f[u][j] += g[j];
+          }
+        }
       }
     }
 #pragma unroll
-    for (int j = 0; j < N; ++j) f[j] *= a.scale;
-    const uint4 o = Acc<T>::pack(f);
-    if (MODE == 1) {
-      multimem_st_16(a.mc + eoff, o);
-    } else {
-      for (int p = 0; p < a.world; ++p) {
-        const int q = (a.rank + p) % a.world;
-        *reinterpret_cast<uint4*>(reinterpret_cast<char*>(a.bufs.ptr[q]) + eoff) = o;
+    for (int u = 0; u < U; ++u) {
+      const long v = v0 + (long)u * nthreads;
+      if (v < nvec) {
+#pragma unroll
+        for (int j = 0; j < N; ++j) f[u][j] *= a.scale;
+        const uint4 o = Acc<T>::pack(f[u]);
+        if (MODE == 1) {
+          multimem_st_16(a.mc + eoff[u], o);
+        } else {
+          for (int p = 0; p < a.world; ++p) {
+            const int q = (a.rank + p) % a.world;
+            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(a.bufs.ptr[q]) + eoff[u]) = o;
+          }
+        }
       }
     }
   }
@@ -201,28 +215,35 @@ reducescatter_kernel(const CommArgs a, T* __restrict__ out) {
   cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch + 1, a.status);
 }
 
-// Second half of GEMM -> reduce-scatter: once every rank has finished adding its partial tiles into
-// this rank's accumulation buffer (entry barrier), convert it to the bf16 output (+ bias, + residual),
-// clear it for the next use, and hold everybody until all buffers are clear again (exit barrier).
+// Second half of GEMM -> reduce-scatter: once every rank has stored its partial tiles into this rank's
+// slot buffer ([world][rows][N]; entry barrier), sum the slots in fp32, add bias / residual, write the
+// bf16 output, and hold everybody until all slot buffers have been read (exit barrier), after which
+// they may be rewritten.
 template <typename TA>
 __global__ void __launch_bounds__(COMM_THREADS)
-rs_finalize_kernel(const CommArgs a, TA* __restrict__ acc, const bf16* __restrict__ bias,
+rs_finalize_kernel(const CommArgs a, const TA* __restrict__ acc, const bf16* __restrict__ bias,
                    const bf16* __restrict__ residual, bf16* __restrict__ out, long rows, int N) {
   const uint32_t epoch = *a.epoch_ptr;
   cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch, a.status);
   const long nvec = rows * N / 8;
+  const long slot = rows * N;
   for (long v = (long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long)gridDim.x * blockDim.x) {
     const long e = v * 8;
     const int c = (int)(e % N);
     float f[8];
-    if (sizeof(TA) == 4) {
-      float4 x = reinterpret_cast<float4*>(acc + e)[0], y = reinterpret_cast<float4*>(acc + e)[1];
-      f[0] = x.x; f[1] = x.y; f[2] = x.z; f[3] = x.w; f[4] = y.x; f[5] = y.y; f[6] = y.z; f[7] = y.w;
-      reinterpret_cast<float4*>(acc + e)[0] = make_float4(0.f, 0.f, 0.f, 0.f);
-      reinterpret_cast<float4*>(acc + e)[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-    } else {
-      Acc<bf16>::load(acc + e, f);
-      *reinterpret_cast<uint4*>(acc + e) = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) f[j] = 0.f;
+    for (int s = 0; s < a.world; ++s) {
+      float g[8];
+      if (sizeof(TA) == 4) {
+        const float4* src = reinterpret_cast<const float4*>(acc + s * slot + e);
+        float4 x = src[0], y = src[1];
+        g[0] = x.x; g[1] = x.y; g[2] = x.z; g[3] = x.w; g[4] = y.x; g[5] = y.y; g[6] = y.z; g[7] = y.w;
+      } else {
+        Acc<bf16>::load(acc + s * slot + e, g);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += g[j];
     }
     if (bias) {
       float b[8];
@@ -335,7 +356,7 @@ TB_EXPORT int tb_reducescatter(const void* const* bufs, const void* const* flags
   return 0;
 }
 
-// acc: this rank's accumulation buffer [rows, N] (contiguous; fp32 when acc_f32 else bf16).
+// acc: this rank's slot buffer [world][rows][N] (contiguous; fp32 when acc_f32 else bf16).
 // out: bf16 [rows, N]; bias [N] and residual [rows, N] are optional.
 TB_EXPORT int tb_rs_finalize(const void* const* flags, int rank, int world, const unsigned* epoch_ptr, void* acc,
                              int acc_f32, const void* bias, const void* residual, void* out, long rows, int N,
@@ -347,8 +368,8 @@ TB_EXPORT int tb_rs_finalize(const void* const* flags, int rank, int world, cons
   if (int r = fill_args(a, none, flags, nullptr, rank, world, epoch_ptr, 0, 0, 1.f, status)) return r;
   if (nblocks < 1) nblocks = 1;
   if (nblocks > COMM_MAX_BLOCKS) nblocks = COMM_MAX_BLOCKS;
-  if (acc_f32) rs_finalize_kernel<float><<<nblocks, COMM_THREADS, 0, st>>>(a, (float*)acc, (const bf16*)bias, (const bf16*)residual, (bf16*)out, rows, N);
-  else rs_finalize_kernel<bf16><<<nblocks, COMM_THREADS, 0, st>>>(a, (bf16*)acc, (const bf16*)bias, (const bf16*)residual, (bf16*)out, rows, N);
+  if (acc_f32) rs_finalize_kernel<float><<<nblocks, COMM_THREADS, 0, st>>>(a, (const float*)acc, (const bf16*)bias, (const bf16*)residual, (bf16*)out, rows, N);
+  else rs_finalize_kernel<bf16><<<nblocks, COMM_THREADS, 0, st>>>(a, (const bf16*)acc, (const bf16*)bias, (const bf16*)residual, (bf16*)out, rows, N);
   bump_epoch_kernel<<<1, 1, 0, st>>>(const_cast<uint32_t*>(epoch_ptr));
   TB_CUDA_CHECK(cudaGetLastError());
   return 0;

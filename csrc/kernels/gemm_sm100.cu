@@ -51,9 +51,9 @@ struct GemmParams {
   int kb_total, kb_per_split;
   int* status;
   // ---- tensor-parallel fusions (all zero / null for a plain GEMM) --------------------------------
-  // GEMM -> reduce-scatter: output row r belongs to rank r / rs_rows; the epilogue adds the tile
-  // straight into that rank's accumulation buffer rs_dst[owner] (bf16x2 or fp32 reductions over
-  // NVLink), so the transfer of a tile overlaps the math of the next one.
+  // GEMM -> reduce-scatter: output row r belongs to rank r / rs_rows; the epilogue stores the tile
+  // straight into this rank's slot of that rank's buffer rs_dst[owner] ([world][rs_rows][ldd], bf16
+  // or fp32) over NVLink, so the transfer of a tile overlaps the math of the next one.
   int rs_rows;
   void* rs_dst[MAX_RANKS];
   // all-gather -> GEMM: the first ag_ctas CTAs copy the peers' A shards (ag_rows rows of K elements
@@ -339,24 +339,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const bool full_chunk = (n0 + 32 <= p.N);
         const size_t off = (size_t)row * p.ldd + n0;
         if (p.rs_rows > 0) {
-          // GEMM -> reduce-scatter: add this row segment into the owner's buffer over NVLink
+          // GEMM -> reduce-scatter: store this row segment into this rank's slot of the owner's
+          // buffer ([world][rs_rows][ldd]) with plain 16-byte stores over NVLink; the owner sums
+          // the slots afterwards. Plain stores run at link rate, remote atomics do not.
           const int owner = row / p.rs_rows;
-          const size_t roff = (size_t)(row - owner * p.rs_rows) * p.ldd + n0;
+          const size_t roff = ((size_t)p.rank * p.rs_rows + (row - owner * p.rs_rows)) * p.ldd + n0;
           if (flags & EPI_OUT_F32) {
-            float* dp = reinterpret_cast<float*>(p.rs_dst[owner]) + roff;
+            float4* dp = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.rs_dst[owner]) + roff);
 #pragma unroll
-            for (int g = 0; g < 8; ++g)
-              asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dp + g * 4),
-                           "f"(f[g * 4]), "f"(f[g * 4 + 1]), "f"(f[g * 4 + 2]), "f"(f[g * 4 + 3])
-                           : "memory");
+            for (int g = 0; g < 8; ++g) dp[g] = make_float4(f[g * 4], f[g * 4 + 1], f[g * 4 + 2], f[g * 4 + 3]);
           } else {
-            __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) + roff;
+            uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) + roff);
 #pragma unroll
             for (int g = 0; g < 4; ++g)
-              asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dp + g * 8),
-                           "r"(pack_bf16x2(f[g * 8 + 0], f[g * 8 + 1])), "r"(pack_bf16x2(f[g * 8 + 2], f[g * 8 + 3])),
-                           "r"(pack_bf16x2(f[g * 8 + 4], f[g * 8 + 5])), "r"(pack_bf16x2(f[g * 8 + 6], f[g * 8 + 7]))
-                           : "memory");
+              dp[g] = make_uint4(pack_bf16x2(f[g * 8 + 0], f[g * 8 + 1]), pack_bf16x2(f[g * 8 + 2], f[g * 8 + 3]),
+                                 pack_bf16x2(f[g * 8 + 4], f[g * 8 + 5]), pack_bf16x2(f[g * 8 + 6], f[g * 8 + 7]));
           }
           continue;
         }
@@ -557,9 +554,10 @@ TB_EXPORT int tb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, 
 }
 
 // Row-parallel linear with sequence parallelism: partial = A[M, K_local] * B[N, K_local]^T is
-// reduce-scattered along M inside the epilogue. dst[r] is rank r's accumulation buffer
-// [M / world, ldd] (bf16 or fp32 per `out_f32`), which must be zero (or hold the value to add to)
-// before ANY rank launches; a cross-rank barrier must follow before the owner reads it.
+// reduce-scattered along M inside the epilogue. dst[r] is rank r's slot buffer
+// [world][M / world][ldd] (bf16 or fp32 per `out_f32`): rank s writes slot s of the owner of each
+// row. A cross-rank barrier must follow before the owner sums its slots (tb_rs_finalize), and the
+// slots may be rewritten only after every owner has finished reading.
 TB_EXPORT int tb_gemm_rs(const void* A, const void* B, const void* const* dst, int M, int N, int K, int b_major,
                          int lda, int ldb, int ldd, int out_f32, int rank, int world, int bn, int* status,
                          cudaStream_t stream) {

@@ -132,3 +132,52 @@ def test_ddp_two_gloo_ranks_average_gradients():
     for p in procs:
         p.join(30)
     assert sorted(res) == [(0, True), (1, True)]
+
+
+def _pp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torsh_b200.parallel.pipeline import PipelineConfig, PipelineParallel, ScheduleType, create_pipeline_stages
+        torch.manual_seed(0)
+        layers = [torch.nn.Linear(8, 8), torch.nn.Tanh(), torch.nn.Linear(8, 8), torch.nn.Tanh(), torch.nn.Linear(8, 4)]
+        full = torch.nn.Sequential(*layers)
+        x = torch.randn(8, 8, generator=torch.Generator().manual_seed(1))
+        y = torch.randn(8, 4, generator=torch.Generator().manual_seed(2))
+        # oracle on the un-split model: mean over 4 micro-batches of the micro-batch MSE
+        ref = torch.nn.Sequential(*[torch.nn.Linear(8, 8), torch.nn.Tanh(), torch.nn.Linear(8, 8), torch.nn.Tanh(), torch.nn.Linear(8, 4)])
+        ref.load_state_dict(full.state_dict())
+        loss_ref = sum(torch.nn.functional.mse_loss(ref(a), b) for a, b in zip(x.chunk(4), y.chunk(4))) / 4
+        loss_ref.backward()
+        ok = True
+        for sched in (ScheduleType.ONE_F_ONE_B, ScheduleType.GPIPE):
+            full.zero_grad()
+            stages = create_pipeline_stages(list(full), world)
+            shape = (2, 8)
+            pp = PipelineParallel(stages[rank], config=PipelineConfig(num_micro_batches=4, schedule=sched),
+                                  activation_shape=shape)
+            loss = pp.train_step(x if rank == 0 else None, y if rank == world - 1 else None, torch.nn.functional.mse_loss)
+            if rank == world - 1:
+                ok &= abs(loss.item() - loss_ref.item()) < 1e-5
+            mine = dict(stages[rank].named_parameters())
+            refp = dict(ref.named_parameters())
+            offset = sum(len(s) for s in stages[:rank])
+            for name, p in mine.items():
+                idx, leaf = name.split(".")
+                ok &= torch.allclose(p.grad, refp[f"{int(idx) + offset}.{leaf}"].grad, atol=1e-5)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_pipeline_two_gloo_ranks_match_unsplit_model():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(30)
+    assert sorted(res) == [(0, True), (1, True)]

@@ -100,7 +100,7 @@ def _gemm_rs(tpc: TPContext, tag: str, x: torch.Tensor, w: torch.Tensor, b_major
     N = w.shape[0] if b_major == 0 else w.shape[1]
     rows = M // tpc.world
     acc_dtype = torch.float32 if tpc.cfg.rs_fp32 else torch.bfloat16
-    buf = tpc.staging(tag, rows * N, acc_dtype)  # zero on allocation, re-zeroed by every finalize
+    buf = tpc.staging(tag, tpc.world * rows * N, acc_dtype)  # one slot per source rank
     st = nv.status_word(x.device)
     call("tb_gemm_rs", [P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, P], x.data_ptr(), w.data_ptr(), buf.ptr_array, M,
          N, K, b_major, x.stride(0), w.stride(0), N, int(tpc.cfg.rs_fp32), tpc.rank, tpc.world, 0, st.data_ptr(),
