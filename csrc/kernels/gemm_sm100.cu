@@ -76,7 +76,11 @@ struct SmemLayout {
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
-  static constexpr int ALLOC = TOTAL + 1024;  // slack for manual 1024-byte alignment
+  // staging rows of the GEMM -> reduce-scatter epilogue: 4 warps x 32 rows x 144 B (128 B + pad)
+  static constexpr int RS_ROW_PITCH = 144;
+  static constexpr int RS_OFF = (TOTAL + 127) / 128 * 128;
+  static constexpr int RS_BYTES = 4 * 32 * RS_ROW_PITCH;
+  static constexpr int ALLOC = RS_OFF + RS_BYTES + 1024;  // + slack for manual 1024-byte alignment
 };
 
 __device__ __forceinline__ void decode_work(const GemmParams& p, int work, int& m_t, int& n_t,
@@ -339,21 +343,36 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const bool full_chunk = (n0 + 32 <= p.N);
         const size_t off = (size_t)row * p.ldd + n0;
         if (p.rs_rows > 0) {
-          // GEMM -> reduce-scatter: store this row segment into this rank's slot of the owner's
-          // buffer ([world][rs_rows][ldd]) with plain 16-byte stores over NVLink; the owner sums
-          // the slots afterwards. Plain stores run at link rate, remote atomics do not.
+          // GEMM -> reduce-scatter: this thread's row segment goes into this rank's slot of the owner's
+          // buffer ([world][rs_rows][ldd]). It is first packed into a private shared-memory row and then
+          // leaves as ONE 128-byte bulk async store, so NVLink sees full-size write bursts instead of
+          // thirty-two scattered 16-byte stores per instruction; the copy engine works while the thread
+          // already unpacks the next chunk.
           const int owner = row / p.rs_rows;
-          const size_t roff = ((size_t)p.rank * p.rs_rows + (row - owner * p.rs_rows)) * p.ldd + n0;
+          const size_t rbase = ((size_t)p.rank * p.rs_rows + (row - owner * p.rs_rows)) * p.ldd;
+          uint8_t* srow = smem + L::RS_OFF + (q * 32 + lane) * L::RS_ROW_PITCH;
           if (flags & EPI_OUT_F32) {
-            float4* dp = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.rs_dst[owner]) + roff);
+            bulk_wait_read_all();  // my previous store has finished reading this row
+            float4* s4 = reinterpret_cast<float4*>(srow);
 #pragma unroll
-            for (int g = 0; g < 8; ++g) dp[g] = make_float4(f[g * 4], f[g * 4 + 1], f[g * 4 + 2], f[g * 4 + 3]);
+            for (int g = 0; g < 8; ++g) s4[g] = make_float4(f[g * 4], f[g * 4 + 1], f[g * 4 + 2], f[g * 4 + 3]);
+            fence_proxy_async_smem();
+            bulk_store(reinterpret_cast<float*>(p.rs_dst[owner]) + rbase + n0, srow, 128);
+            bulk_commit();
           } else {
-            uint4* dp = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) + roff);
+            const int half = (c0 >> 5) & 1;
+            if (half == 0) bulk_wait_read_all();
+            uint4* s4 = reinterpret_cast<uint4*>(srow + half * 64);
 #pragma unroll
             for (int g = 0; g < 4; ++g)
-              dp[g] = make_uint4(pack_bf16x2(f[g * 8 + 0], f[g * 8 + 1]), pack_bf16x2(f[g * 8 + 2], f[g * 8 + 3]),
+              s4[g] = make_uint4(pack_bf16x2(f[g * 8 + 0], f[g * 8 + 1]), pack_bf16x2(f[g * 8 + 2], f[g * 8 + 3]),
                                  pack_bf16x2(f[g * 8 + 4], f[g * 8 + 5]), pack_bf16x2(f[g * 8 + 6], f[g * 8 + 7]));
+            if (half == 1 || n0 + 32 >= p.N || c0 + 32 >= BN) {
+              fence_proxy_async_smem();
+              bulk_store(reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) + rbase + (n0 - half * 32), srow,
+                         (half + 1) * 64);
+              bulk_commit();
+            }
           }
           continue;
         }
@@ -491,6 +510,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         acc_phase ^= 1;
       }
     }
+    if (p.rs_rows > 0) bulk_wait_all();  // every row this thread sent has landed in its owner's memory
   }
 
   tc_fence_before();
