@@ -299,3 +299,59 @@ TB_EXPORT int tb_norm_bwd(const void* dy, const void* x, const void* gamma, cons
   return rms ? norm_bwd_launch<float, true>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, partial, rows, H, st)
              : norm_bwd_launch<float, false>(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, partial, rows, H, st);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of tb_norm_bwd (declared in csrc/include/torsh_b200_noalloc.h).
+//
+// tb_norm_bwd needs scratch memory for its per-CTA partial sums and expects the caller to provide
+// it. Some callers cannot: code running inside a CUDA-graph capture or a real-time serving loop must
+// not touch an allocator, and a plain C / FFI host has no caching allocator to ask. For them the
+// scratch lives in the library image itself, in a file-scope device array of fixed size. Every GPU
+// that loads the library holds these 8 MiB until the process exits.
+//
+// Rules that follow from sharing one array:
+//  * the request is refused (TB_E_TOO_LARGE) when it needs more than the array holds;
+//  * the array keeps whatever the previous call left in it. Nothing has to start at zero here: every
+//    partial-sum row that the reduce kernel reads is fully overwritten by the CTA that owns it;
+//  * two calls whose kernels overlap on the GPU (different streams, or graphs replayed concurrently)
+//    race on the array. Issue them on one stream, or serialise them with events.
+// The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that
+// device current) and caches it; make that first call before any stream capture begins.
+namespace tb {
+constexpr long NOALLOC_SCRATCH_FLOATS = 2L * 1024 * 1024;  // 8 MiB
+static __device__ __align__(256) float g_norm_bwd_scratch[NOALLOC_SCRATCH_FLOATS];
+// In host code the name above is only a handle for the symbol, never a device address.
+static float* g_norm_bwd_scratch_dev[64] = {nullptr};
+
+static int noalloc_scratch_ptr(float** out) {
+  int dev = 0;
+  TB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) TB_FAIL(TB_E_ARG, "tb_norm_bwd_static: device index %d out of range", dev);
+  if (!g_norm_bwd_scratch_dev[dev]) {
+    float* p = nullptr;
+    TB_CUDA_CHECK(cudaGetSymbolAddress((void**)&p, g_norm_bwd_scratch));
+    if (!p) TB_FAIL(TB_E_CUDA, "tb_norm_bwd_static: cudaGetSymbolAddress returned a null address");
+    g_norm_bwd_scratch_dev[dev] = p;
+  }
+  *out = g_norm_bwd_scratch_dev[dev];
+  return 0;
+}
+}  // namespace tb
+
+TB_EXPORT long tb_norm_bwd_static_capacity() { return tb::NOALLOC_SCRATCH_FLOATS; }
+
+TB_EXPORT int tb_norm_bwd_static(const void* dy, const void* x, const void* gamma, const float* mean,
+                                 const float* rstd, const void* dres, void* dx, float* dgamma, float* dbeta,
+                                 int rows, int H, int rms, int dtype, cudaStream_t st) {
+  TB_ENSURE_DEVICE();
+  if (rows <= 0) return 0;
+  const long need = (long)tb::norm_bwd_grid(rows) * 2 * H;
+  if (need > tb::NOALLOC_SCRATCH_FLOATS)
+    TB_FAIL(tb::TB_E_TOO_LARGE,
+            "tb_norm_bwd_static: rows=%d, H=%d needs %ld floats of scratch, the built-in array holds %ld; "
+            "use tb_norm_bwd with caller-provided scratch",
+            rows, H, need, tb::NOALLOC_SCRATCH_FLOATS);
+  float* scratch = nullptr;
+  if (int r = tb::noalloc_scratch_ptr(&scratch)) return r;
+  return tb_norm_bwd(dy, x, gamma, mean, rstd, dres, dx, dgamma, dbeta, scratch, rows, H, rms, dtype, st);
+}
