@@ -1,0 +1,201 @@
+"""Datasets, samplers and the DataLoader (``crates/torsh-data``).
+
+``DataLoaderConfig`` defaults follow ``crates/torsh-data/src/dataloader/mod.rs:128-160`` (batch_size 1, shuffle
+false, num_workers 0, pin_memory false, drop_last false, prefetch_buffer_size 0, persistent_workers false).
+``DistributedSampler`` follows ``crates/torsh-data/src/sampler/distributed.rs:194-330``: pad by wrap-around (or drop
+the tail), Fisher-Yates shuffle with seed 42 by default, and each rank takes a CONTIGUOUS block
+``[rank*k, (rank+1)*k)`` (not a strided one). Batches can be staged through pinned host buffers and copied to the
+device on a side stream (``PrefetchToDevice``), the role of ``dataloader/memory.rs`` and ``prefetch.rs``.
+"""
+from __future__ import annotations
+
+import math
+import random
+from dataclasses import dataclass
+
+import torch
+from torch.utils.data import (BatchSampler, ConcatDataset, Dataset, IterableDataset, RandomSampler, Sampler,
+                              SequentialSampler, Subset, TensorDataset, WeightedRandomSampler, random_split)
+from torch.utils.data import DataLoader as _TorchLoader
+from torch.utils.data import default_collate
+
+
+@dataclass
+class DataLoaderConfig:
+    batch_size: int = 1
+    shuffle: bool = False
+    num_workers: int = 0
+    pin_memory: bool = False
+    drop_last: bool = False
+    timeout: float | None = None
+    generator: int | None = None
+    prefetch_buffer_size: int = 0
+    persistent_workers: bool = False
+
+
+class DataLoader(_TorchLoader):
+    """``DataLoader(dataset, config)`` or PyTorch-style keyword arguments."""
+
+    def __init__(self, dataset, config: DataLoaderConfig | None = None, **kw):
+        if config is not None:
+            g = torch.Generator().manual_seed(config.generator) if config.generator is not None else None
+            kw = dict(batch_size=config.batch_size, shuffle=config.shuffle, num_workers=config.num_workers,
+                      pin_memory=config.pin_memory, drop_last=config.drop_last, timeout=config.timeout or 0,
+                      generator=g, persistent_workers=config.persistent_workers and config.num_workers > 0,
+                      prefetch_factor=config.prefetch_buffer_size if (config.prefetch_buffer_size and config.num_workers) else None,
+                      **kw)
+        super().__init__(dataset, **kw)
+
+
+class DistributedSampler(Sampler):
+    def __init__(self, num_samples: int, num_replicas: int, rank: int, shuffle: bool = True, seed: int = 42,
+                 drop_last: bool = False):
+        if not 0 <= rank < num_replicas:
+            raise ValueError(f"rank {rank} not in [0, {num_replicas})")
+        self.n, self.replicas, self.rank, self.shuffle, self.seed, self.drop_last = num_samples, num_replicas, rank, shuffle, seed, drop_last
+        self.epoch = 0
+        self.per_replica = num_samples // num_replicas if drop_last else math.ceil(num_samples / num_replicas)
+        self.total = self.per_replica * num_replicas
+
+    def with_generator(self, seed: int):
+        self.seed = seed
+        return self
+
+    def set_epoch(self, epoch: int):
+        self.epoch = epoch
+
+    def indices(self) -> list[int]:
+        idx = list(range(self.n))
+        if self.shuffle:
+            rng = random.Random(self.seed + self.epoch)
+            for i in range(len(idx) - 1, 0, -1):  # Fisher-Yates
+                j = rng.randint(0, i)
+                idx[i], idx[j] = idx[j], idx[i]
+        if self.drop_last:
+            idx = idx[: self.total]
+        else:
+            k = 0
+            while len(idx) < self.total:  # wrap-around padding
+                idx.append(idx[k])
+                k += 1
+        return idx[self.rank * self.per_replica:(self.rank + 1) * self.per_replica]
+
+    def __iter__(self):
+        return iter(self.indices())
+
+    def __len__(self):
+        return self.per_replica
+
+
+class CachedDataset(Dataset):
+    """Memoises items of a slow dataset (``crates/torsh-data/src/dataset/types.rs``)."""
+
+    def __init__(self, base: Dataset, max_items: int | None = None):
+        self.base, self.cache, self.max_items = base, {}, max_items
+
+    def __len__(self):
+        return len(self.base)
+
+    def __getitem__(self, i):
+        if i not in self.cache:
+            if self.max_items is not None and len(self.cache) >= self.max_items:
+                self.cache.pop(next(iter(self.cache)))
+            self.cache[i] = self.base[i]
+        return self.cache[i]
+
+
+class MemoryMappedDataset(Dataset):
+    """Fixed-shape records in a flat binary file, read through ``numpy.memmap``."""
+
+    def __init__(self, path, dtype, record_shape):
+        import numpy as np
+        self.arr = np.memmap(path, dtype=dtype, mode="r")
+        self.record_shape = tuple(record_shape)
+        self.rec = int(math.prod(self.record_shape))
+        self.n = self.arr.size // self.rec
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, i):
+        import numpy as np
+        return torch.from_numpy(np.array(self.arr[i * self.rec:(i + 1) * self.rec]).reshape(self.record_shape))
+
+
+class StreamingDataset(IterableDataset):
+    """Wraps a generator factory; each worker sees every ``num_workers``-th item."""
+
+    def __init__(self, make_iter):
+        self.make_iter = make_iter
+
+    def __iter__(self):
+        info = torch.utils.data.get_worker_info()
+        it = self.make_iter()
+        if info is None:
+            yield from it
+        else:
+            for i, x in enumerate(it):
+                if i % info.num_workers == info.id:
+                    yield x
+
+
+class SyntheticTokenDataset(Dataset):
+    """Uniform random token ids with next-token targets (benchmark data)."""
+
+    def __init__(self, vocab_size: int, seq_len: int, length: int, seed: int = 0):
+        self.v, self.s, self.n, self.seed = vocab_size, seq_len, length, seed
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, i):
+        g = torch.Generator().manual_seed(self.seed * 1_000_003 + i)
+        t = torch.randint(0, self.v, (self.s + 1,), generator=g)
+        return t[:-1], t[1:]
+
+
+class PrefetchToDevice:
+    """Iterates a loader one batch ahead: pinned staging + H2D copy on a side stream."""
+
+    def __init__(self, loader, device):
+        self.loader, self.device = loader, torch.device(device)
+        self.stream = torch.cuda.Stream() if self.device.type == "cuda" else None
+
+    def _move(self, batch):
+        if isinstance(batch, torch.Tensor):
+            if self.stream is not None and not batch.is_pinned():
+                batch = batch.pin_memory()
+            return batch.to(self.device, non_blocking=True)
+        if isinstance(batch, (list, tuple)):
+            return type(batch)(self._move(b) for b in batch)
+        if isinstance(batch, dict):
+            return {k: self._move(v) for k, v in batch.items()}
+        return batch
+
+    def __iter__(self):
+        it = iter(self.loader)
+        nxt = None
+
+        def fetch():
+            try:
+                b = next(it)
+            except StopIteration:
+                return None
+            if self.stream is None:
+                return self._move(b)
+            with torch.cuda.stream(self.stream):
+                return self._move(b)
+
+        nxt = fetch()
+        while nxt is not None:
+            if self.stream is not None:
+                torch.cuda.current_stream().wait_stream(self.stream)
+            cur, nxt = nxt, fetch()
+            yield cur
+
+    def __len__(self):
+        return len(self.loader)
+
+
+def collate(batch):
+    return default_collate(batch)
