@@ -1,0 +1,107 @@
+#!/usr/bin/env python
+"""Kernel micro-benchmarks (device-timed with CUDA events) and the small cases used for ncu captures.
+
+  python bench/kernels.py gemm --m 8192 --n 4096 --k 4096 [--a-major 0 --b-major 0 --bn 256]
+  python bench/kernels.py attn_fwd | attn_bwd --batch 4 --seq 2048 --heads 16 --dim 64
+  python bench/kernels.py layernorm | xent | adamw
+Each run prints achieved TFLOP/s or GB/s and the fraction of the measured peak in MEASURED_PEAKS.json
+(fallback 6.65 TB/s, 1.59 PFLOP/s when that file is absent).
+"""
+import argparse
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import torch
+
+
+def peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timeit(fn, iters, flush):
+    for _ in range(3):
+        fn()
+    e = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    torch.cuda.synchronize()
+    for a, b in e:
+        flush.add_(1.0)  # 256 MB write: evicts the 126 MB L2 between timed iterations
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) for a, b in e)
+    return ts[len(ts) // 2]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "layernorm", "xent", "adamw"])
+    ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=4096); ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--a-major", type=int, default=0); ap.add_argument("--b-major", type=int, default=0); ap.add_argument("--bn", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=4); ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=16); ap.add_argument("--dim", type=int, default=64)
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    from torsh_b200 import _native as nv
+    dev = "cuda"
+    hbm, tf, kind = peaks()
+    flush = torch.zeros(64 * 1024 * 1024, device=dev)
+    torch.manual_seed(0)
+    if a.what == "gemm":
+        from torsh_b200.ops.gemm import gemm
+        A = torch.randn((a.m, a.k) if a.a_major == 0 else (a.k, a.m), device=dev, dtype=torch.bfloat16)
+        B = torch.randn((a.n, a.k) if a.b_major == 0 else (a.k, a.n), device=dev, dtype=torch.bfloat16)
+        out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+        ms = timeit(lambda: gemm(A, B, a_major=a.a_major, b_major=a.b_major, out=out, bn=a.bn), a.iters, flush)
+        t = 2.0 * a.m * a.n * a.k / ms / 1e9
+        print(f"gemm {a.m}x{a.n}x{a.k} majors {a.a_major}{a.b_major}: {ms*1e3:.1f} us, {t:.0f} TFLOP/s = {t/tf:.2f} of {kind} bf16 peak")
+    elif a.what in ("attn_fwd", "attn_bwd"):
+        from torsh_b200.ops.attention import flash_attention
+        q, k, v = (torch.randn(a.batch, a.seq, a.heads, a.dim, device=dev, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
+        fl = 4.0 * a.batch * a.heads * a.seq * a.seq * a.dim * 0.5
+        if a.what == "attn_fwd":
+            with torch.no_grad():
+                ms = timeit(lambda: flash_attention(q, k, v, causal=True), a.iters, flush)
+        else:
+            o = flash_attention(q, k, v, causal=True)
+            do = torch.randn_like(o)
+            ms = timeit(lambda: o.backward(do, retain_graph=True), a.iters, flush)
+            fl *= 2.5
+        t = fl / ms / 1e9
+        print(f"{a.what} B{a.batch} S{a.seq} H{a.heads} D{a.dim} causal: {ms*1e3:.1f} us, {t:.0f} TFLOP/s = {t/tf:.2f} of {kind} bf16 peak")
+    elif a.what == "layernorm":
+        from torsh_b200.ops.norm import layer_norm
+        x = torch.randn(a.m, a.n, device=dev, dtype=torch.bfloat16)
+        w, b = torch.ones(a.n, device=dev, dtype=torch.bfloat16), torch.zeros(a.n, device=dev, dtype=torch.bfloat16)
+        with torch.no_grad():
+            ms = timeit(lambda: layer_norm(x, w, b), a.iters, flush)
+        gb = 2.0 * x.numel() * 2 / ms / 1e6
+        print(f"layernorm fwd {a.m}x{a.n}: {ms*1e3:.1f} us, {gb:.0f} GB/s = {gb/hbm:.2f} of {kind} copy bandwidth")
+    elif a.what == "xent":
+        from torsh_b200.ops.softmax import cross_entropy
+        lg = torch.randn(a.m, 50304, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        tg = torch.randint(0, 50257, (a.m,), device=dev)
+        ms = timeit(lambda: cross_entropy(lg, tg, num_classes=50257, inplace_grad=False, root_scale=1.0), a.iters, flush)
+        gb = 2.0 * lg.numel() * 2 / ms / 1e6
+        print(f"cross-entropy fwd+bwd {a.m}x50304: {ms*1e3:.1f} us, {gb:.0f} GB/s = {gb/hbm:.2f} of {kind} copy bandwidth")
+    else:
+        from torsh_b200.optim import FlatAdamW, FlatParameters
+        p = torch.nn.Parameter(torch.randn(a.m * a.n, device=dev))
+        flat = FlatParameters([p])
+        opt = FlatAdamW(flat)
+        flat.grad.normal_()
+        ms = timeit(lambda: opt.step(), a.iters, flush)
+        gb = flat.total * 30.0 / ms / 1e6
+        print(f"fused AdamW {flat.total/1e6:.0f}M params: {ms*1e3:.1f} us, {gb:.0f} GB/s = {gb/hbm:.2f} of {kind} copy bandwidth")
+    torch.cuda.synchronize()
+    nv.check_status()
+
+
+if __name__ == "__main__":
+    main()
