@@ -1,4 +1,42 @@
-"""Model zoo."""
+"""Model zoo and registry (``crates/torsh-models/src/lib.rs:9-43``)."""
 from .gpt2 import GPT2Config, GPT2LMHeadModel, GPT2Model, GPTForCausalLM
+from .llama import LlamaConfig, LlamaForCausalLM, LlamaModel
+from .resnet import BasicBlock, BottleneckBlock, ResNet, ResNetConfig, SEBlock
+from .transformer_zoo import (BertConfig, BertForMaskedLM, BertForSequenceClassification, BertModel, EncoderBlock,
+                              EncoderConfig, EncoderDecoderModel, RobertaModel, Seq2SeqConfig, T5Model, ViTConfig,
+                              VisionTransformer)
 
-__all__ = ["GPT2Config", "GPT2Model", "GPTForCausalLM", "GPT2LMHeadModel"]
+_REGISTRY = {
+    "gpt2": lambda **kw: GPTForCausalLM(GPT2Config.small(**kw)),
+    "gpt2-medium": lambda **kw: GPTForCausalLM(GPT2Config.medium(**kw)),
+    "gpt2-large": lambda **kw: GPTForCausalLM(GPT2Config.large(**kw)),
+    "gpt2-xl": lambda **kw: GPTForCausalLM(GPT2Config.xl(**kw)),
+    "llama-7b": lambda **kw: LlamaModel(LlamaConfig.llama_7b(**kw)),
+    "resnet18": lambda **kw: ResNet(ResNetConfig.resnet18(**kw)),
+    "resnet34": lambda **kw: ResNet(ResNetConfig.resnet34(**kw)),
+    "resnet50": lambda **kw: ResNet(ResNetConfig.resnet50(**kw)),
+    "resnet101": lambda **kw: ResNet(ResNetConfig.resnet101(**kw)),
+    "resnet152": lambda **kw: ResNet(ResNetConfig.resnet152(**kw)),
+    "resnext50_32x4d": lambda **kw: ResNet(ResNetConfig.resnext50_32x4d(**kw)),
+    "wide_resnet50_2": lambda **kw: ResNet(ResNetConfig.wide_resnet50_2(**kw)),
+    "vit_b_16": lambda **kw: VisionTransformer(ViTConfig.vit_b_16(**kw)),
+    "vit_l_16": lambda **kw: VisionTransformer(ViTConfig.vit_l_16(**kw)),
+    "bert-base": lambda **kw: BertModel(BertConfig.bert_base(**kw)),
+    "bert-large": lambda **kw: BertModel(BertConfig.bert_large(**kw)),
+    "roberta-base": lambda **kw: BertModel(BertConfig.roberta_base(**kw)),
+    "t5-base": lambda **kw: EncoderDecoderModel(Seq2SeqConfig(**kw)),
+}
+
+
+def list_models() -> list[str]:
+    return sorted(_REGISTRY)
+
+
+def create_model(name: str, **kw):
+    if name not in _REGISTRY:
+        raise KeyError(f"unknown model {name!r}; available: {list_models()}")
+    return _REGISTRY[name](**kw)
+
+
+def register_model(name: str, factory) -> None:
+    _REGISTRY[name] = factory
