@@ -1,0 +1,248 @@
+"""CPU tests of the API breadth: optimizers, schedulers, autograd utilities, data, formats, fault tolerance, MoE."""
+import math
+
+import pytest
+import torch
+
+
+def test_reference_optimizer_arithmetic():
+    """AdamW / SGD / LAMB against hand-written restatements of the reference formulas."""
+    from torsh_b200 import optim as O
+    torch.manual_seed(0)
+    w0, g = torch.randn(7), torch.randn(7)
+    # AdamW: decay, moments, both bias corrections, eps outside the sqrt of v-hat
+    p = torch.nn.Parameter(w0.clone()); p.grad = g.clone()
+    O.AdamW([p], lr=0.1, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01).step()
+    w = w0 - 0.1 * 0.01 * w0
+    m, v = 0.1 * g, 0.001 * g * g
+    exp = w - 0.1 * (m / 0.1) / ((v / 0.001).sqrt() + 1e-8)
+    assert torch.allclose(p.data, exp, atol=1e-6)
+    # SGD nesterov with weight decay, buffer starting at zero
+    p = torch.nn.Parameter(w0.clone()); p.grad = g.clone()
+    O.SGD([p], lr=0.1, momentum=0.9, weight_decay=0.1, nesterov=True).step()
+    d = g + 0.1 * w0
+    buf = d.clone()
+    assert torch.allclose(p.data, w0 - 0.1 * (d + 0.9 * buf), atol=1e-6)
+    with pytest.raises(ValueError):
+        O.SGD([p], lr=0.1, momentum=0.0, nesterov=True)
+    # LAMB: coupled decay before the moments, trust ratio clamped to <= 1
+    p = torch.nn.Parameter(w0.clone()); p.grad = g.clone()
+    O.LAMB([p], lr=0.1, weight_decay=0.01).step()
+    gg = g + 0.01 * w0
+    u = ((0.1 * gg) / 0.1) / (((0.001 * gg * gg) / 0.001).sqrt() + 1e-6)
+    trust = min(w0.norm().item() / u.norm().item(), 1.0)
+    assert torch.allclose(p.data, w0 - 0.1 * trust * u, atol=1e-6)
+
+
+@pytest.mark.parametrize("name", ["Lion", "AdaBelief", "AdaBound", "Yogi", "LARS", "FTRL", "SophiaG", "ScheduleFreeSGD",
+                                  "Prodigy", "Adagrad", "RMSprop", "NAdam", "RAdam", "Adamax", "Adadelta"])
+def test_optimizer_zoo_descends(name):
+    from torsh_b200 import optim as O
+    w = torch.nn.Parameter(torch.tensor([3.0, -2.0]))
+    kw = {"Lion": dict(lr=1e-2), "LARS": dict(lr=0.5, eta=0.1), "FTRL": dict(lr=0.5), "Adadelta": dict(lr=5.0),
+          "ScheduleFreeSGD": dict(lr=0.1), "Prodigy": {}}.get(name, dict(lr=5e-2))
+    opt = getattr(O, name)([w], **kw)
+    start = (w ** 2).sum().item()
+    for _ in range(150):
+        opt.zero_grad()
+        (w ** 2).sum().backward()
+        opt.step()
+    assert (w ** 2).sum().item() < 0.6 * start
+
+
+def test_lr_schedulers():
+    from torsh_b200 import optim as O
+    from torsh_b200.optim import lr_scheduler as S
+    def lrs(make, n):
+        opt = O.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1.0)
+        s = make(opt)
+        out = []
+        for _ in range(n):
+            out.append(opt.get_lr()[0])
+            s.step()
+        return out
+    assert lrs(lambda o: S.StepLR(o, 2, 0.5), 5) == [1.0, 1.0, 0.5, 0.5, 0.25]
+    assert lrs(lambda o: S.MultiStepLR(o, [1, 3], 0.1), 4) == pytest.approx([1.0, 0.1, 0.1, 0.01])
+    c = lrs(lambda o: S.CosineAnnealingLR(o, 10), 11)
+    assert c[5] == pytest.approx(0.5) and c[10] == pytest.approx(0.0, abs=1e-9)
+    w = lrs(lambda o: S.PolynomialDecayWithWarmup(o, 4, 10), 10)
+    assert w[:4] == pytest.approx([0.25, 0.5, 0.75, 1.0]) and w[-1] < w[4]
+    oc = lrs(lambda o: S.OneCycleLR(o, max_lr=1.0, total_steps=20), 20)
+    assert max(oc) == pytest.approx(1.0, abs=1e-6) and oc[0] == pytest.approx(0.04) and oc[-1] < 1e-3
+    opt = O.SGD([torch.nn.Parameter(torch.zeros(1))], lr=1.0)
+    p = S.ReduceLROnPlateau(opt, factor=0.5, patience=1)
+    for m in (1.0, 1.0, 1.0, 1.0):
+        p.step(m)
+    assert opt.get_lr()[0] == 0.5
+
+
+def test_autograd_utilities():
+    from torsh_b200 import autograd as A
+    a = torch.nn.Parameter(torch.ones(4)); a.grad = torch.full((4,), 3.0)
+    n = A.clip_grad_norm([a], 1.0)
+    assert n.item() == pytest.approx(6.0) and a.grad.norm().item() == pytest.approx(1.0, rel=1e-4)
+    A.clip_grad_value([a], 0.1)
+    assert a.grad.max().item() <= 0.1 + 1e-7
+    x = torch.randn(3, dtype=torch.double, requires_grad=True)
+    assert A.gradcheck(lambda t: (t ** 3).sum(), (x,))
+    ng = A.numerical_gradient(lambda t: (t ** 2).sum(), torch.tensor([1.0, -2.0]))
+    assert torch.allclose(ng, torch.tensor([2.0, -4.0], dtype=torch.double), atol=1e-5)
+    assert A.CheckpointScheduler(A.CheckpointStrategy.SQRT).plan(9) == [False, True, True] * 3
+    assert A.has_nan_or_inf(torch.tensor([1.0, float("nan")])) and not A.has_nan_or_inf(torch.ones(2))
+    with A.no_grad():
+        assert not A.is_grad_enabled()
+
+
+def test_distributed_sampler_contiguous_blocks():
+    from torsh_b200.data import DistributedSampler
+    parts = [DistributedSampler(10, 4, r, shuffle=False).indices() for r in range(4)]
+    assert parts[0] == [0, 1, 2] and parts[3] == [9, 0, 1]                     # wrap-around padding, contiguous blocks
+    sh = [DistributedSampler(10, 2, r, shuffle=True) for r in range(2)]
+    assert sorted(sh[0].indices() + sh[1].indices()) == list(range(10))
+    assert sh[0].indices() == DistributedSampler(10, 2, 0, shuffle=True, seed=42).indices()
+    d = DistributedSampler(10, 4, 0, shuffle=False, drop_last=True)
+    assert len(d) == 2 and d.indices() == [0, 1]
+
+
+def test_dataloader_config_and_prefetch():
+    from torsh_b200.data import DataLoader, DataLoaderConfig, PrefetchToDevice, SyntheticTokenDataset
+    ds = SyntheticTokenDataset(100, 8, 10)
+    dl = DataLoader(ds, DataLoaderConfig(batch_size=4, drop_last=False))
+    batches = list(PrefetchToDevice(dl, "cpu"))
+    assert [b[0].shape[0] for b in batches] == [4, 4, 2] and torch.equal(batches[0][0][0, 1:], batches[0][1][0, :-1])
+
+
+def test_model_state_and_checkpoint_roundtrip(tmp_path):
+    from torsh_b200 import nn, optim
+    from torsh_b200.serialize import checkpoint as ck, model_state as ms
+    m = nn.Sequential(nn.Linear(4, 3), nn.ReLU(), nn.Linear(3, 2))
+    st = ms.model_state(m, {"hidden": 3, "name": "mlp", "p": 0.5, "flag": True, "dims": [4, 3, 2]})
+    ms.save_json(st, tmp_path / "a.json"); ms.save_binary(st, tmp_path / "a.bin"); ms.save_safetensors(st, tmp_path / "a.st")
+    for back in (ms.load_json(tmp_path / "a.json"), ms.load_binary(tmp_path / "a.bin"), ms.load_safetensors(tmp_path / "a.st")):
+        m2 = nn.Sequential(nn.Linear(4, 3), nn.ReLU(), nn.Linear(3, 2))
+        ms.load_model_state(m2, back)
+        assert all(torch.equal(a, b) for a, b in zip(m.state_dict().values(), m2.state_dict().values()))
+        assert back["config"]["dims"] == [4, 3, 2] and back["metadata"]["version"] == "1.0.0"
+    o = optim.AdamW(m.parameters())
+    m(torch.randn(2, 4)).sum().backward(); o.step()
+    mgr = ck.CheckpointManager(tmp_path / "ck", max_to_keep=2)
+    for s in range(4):
+        mgr.save(m, o, epoch=0, global_step=s, metric=1.0 / (s + 1))
+    assert sorted(p.name for p in (tmp_path / "ck").iterdir()) == ["checkpoint_best.torsh", "checkpoint_epoch_0_step_2.torsh", "checkpoint_epoch_0_step_3.torsh"]
+    c = mgr.load()
+    m3 = nn.Sequential(nn.Linear(4, 3), nn.ReLU(), nn.Linear(3, 2)); o3 = optim.AdamW(m3.parameters())
+    ck.restore_into(c, m3, o3)
+    assert torch.equal(m3[0].weight, m[0].weight) and o3.state[m3[0].weight]["step"] == 1
+    dm = ck.DistributedCheckpointManager(tmp_path / "d", rank=1, world_size=2)
+    dm.save(10, 1, {"flat": torch.arange(8.0)})
+    (tmp_path / "d" / "checkpoint_step_12_rank_1.json").write_text("{corrupt")
+    assert dm.latest_step() == 12
+    from torsh_b200.core.error import TorshDistributedError
+    with pytest.raises(TorshDistributedError):
+        dm.load()
+    assert torch.equal(dm.load(10)["model_state"]["flat"], torch.arange(8.0))
+
+
+def test_module_state_dict_rules():
+    from torsh_b200 import nn
+    from torsh_b200.core.error import TorshError
+    m = nn.Sequential(nn.Linear(2, 2), nn.BatchNorm1d(2))
+    sd = m.torsh_state_dict()
+    assert set(sd) == {"0.weight", "0.bias", "1.weight", "1.bias"}        # parameters only, no running stats
+    with pytest.raises(TorshError, match="missing"):
+        m.load_torsh_state_dict({"0.weight": sd["0.weight"]}, strict=True)
+    m.load_torsh_state_dict({"0.weight": sd["0.weight"]}, strict=False)
+    with pytest.raises(TorshError, match="ShapeMismatch"):
+        m.load_torsh_state_dict({**sd, "0.bias": torch.zeros(3)})
+    assert m.num_parameters() == 10 and m.freeze().num_parameters(trainable_only=True) == 0
+
+
+def test_retry_circuit_breaker_health_and_injection():
+    from torsh_b200.core.error import TorshDistributedError
+    from torsh_b200.parallel import fault_tolerance as ft
+    now = [0.0]
+    cb = ft.CircuitBreaker(failure_threshold=2, success_threshold=2, timeout_s=10, clock=lambda: now[0])
+    cb.record_failure(); assert cb.allow()
+    cb.record_failure(); assert cb.state is ft.CircuitState.OPEN and not cb.allow()
+    now[0] = 11; assert cb.allow() and cb.state is ft.CircuitState.HALF_OPEN
+    cb.record_success(); cb.record_success(); assert cb.state is ft.CircuitState.CLOSED
+    inj = ft.FaultInjector(); inj.add(ft.FaultKind.NETWORK_FAILURE, 1.0, max_count=2)
+    calls = []
+    ex = ft.RetryExecutor(ft.RetryConfig(max_attempts=3, initial_delay_s=0.0), sleep=lambda s: None)
+    assert ex.execute(inj.wrap(lambda: calls.append(1) or "ok")) == "ok" and ex.stats["retries"] == 2
+    inj.add(ft.FaultKind.PROCESS_CRASH, 1.0)                               # not retryable: fails at once
+    with pytest.raises(TorshDistributedError, match="ProcessFailure"):
+        ft.RetryExecutor(sleep=lambda s: None).execute(inj.wrap(lambda: None))
+    hc = ft.HealthChecker(timeout_s=5, clock=lambda: now[0])
+    hc.heartbeat(0); now[0] += 6; hc.heartbeat(1)
+    assert hc.unhealthy() == [0]
+
+
+def test_elastic_manager_detects_dead_and_new_workers():
+    from torsh_b200.parallel import fault_tolerance as ft
+    from torsh_b200.parallel.store import MemoryStore
+    st = MemoryStore()
+    for r in (0, 1):
+        st.set(f"hb/{r}", repr(1000.0).encode())
+    saved = []
+    mgr = ft.ElasticTrainingManager(st, 0, 2, ft.ElasticConfig(max_workers=4, heartbeat_timeout_s=10), on_checkpoint=lambda: saved.append(1))
+    assert mgr.check_scaling_needs(now=1005.0) is None
+    st.set("hb/0", repr(1020.0).encode())                                      # rank 1 went silent
+    assert mgr.check_scaling_needs(now=1021.0) is ft.ScalingEvent.WORKER_FAILURE and saved == [1]
+    assert mgr.state is ft.ElasticState.SCALING
+    mgr.complete_scaling()
+    assert mgr.world_size == 1 and mgr.state is ft.ElasticState.STABLE and mgr.generation == 1
+    st.set("hb/1", repr(1030.0).encode()); st.set("hb/0", repr(1030.0).encode())
+    assert mgr.check_scaling_needs(now=1031.0) is ft.ScalingEvent.WORKER_JOIN
+
+
+def test_compression_and_error_feedback():
+    from torsh_b200.parallel import compression as C
+    torch.manual_seed(0)
+    g = torch.randn(64, 32)
+    for comp, tol in ((C.TopK(0.25), None), (C.Quantization(8), 0.02), (C.SignSGD(), None), (C.Ternary(), None), (C.PowerSGD(8), None)):
+        back = comp.decompress(comp.compress(g), g.shape)
+        assert back.shape == g.shape
+        if tol:
+            assert (back - g).abs().max() < tol * (g.max() - g.min())
+    ef = C.ErrorFeedback(C.TopK(0.1))
+    total = torch.zeros_like(g)
+    for _ in range(30):
+        _, approx = ef.compress("w", g)
+        total += approx
+    assert ((total / 30 - g).norm() / g.norm()).item() < 0.35                   # residuals are eventually transmitted
+
+
+def test_moe_router_capacity_and_layer():
+    from torsh_b200.parallel.expert_parallel import ExpertParallelismConfig, MoELayer, TopKRouter
+    torch.manual_seed(0)
+    cfg = ExpertParallelismConfig(num_experts=4, top_k=2, capacity_factor=1.0)
+    r = TopKRouter(16, cfg)
+    x = torch.randn(32, 16)
+    idx, w, keep, slot, aux = r(x)
+    assert r.capacity(32) == 16 and idx.shape == (32, 2) and torch.allclose(w.sum(-1), torch.ones(32))
+    for e in range(4):
+        assert ((idx == e) & keep).sum().item() <= 16
+    layer = MoELayer(16, 32, cfg)
+    y, aux = layer(x.requires_grad_(True))
+    (y.sum() + aux).backward()
+    assert y.shape == x.shape and layer.w1.grad is not None and layer.router.gate.grad is not None
+
+
+def test_ring_all_reduce_host_oracle():
+    from torsh_b200.parallel.collectives import ring_all_reduce_host
+    bufs = [torch.arange(10.0) * (r + 1) for r in range(3)]
+    ring_all_reduce_host(bufs)
+    for b in bufs:
+        assert torch.equal(b, torch.arange(10.0) * 6)
+
+
+def test_models_forward_shapes():
+    from torsh_b200 import models as M
+    assert M.VisionTransformer(M.ViTConfig.vit_tiny())(torch.randn(2, 3, 32, 32)).shape == (2, 10)
+    ids = torch.randint(0, 1000, (2, 16))
+    assert M.BertForMaskedLM(M.BertConfig.tiny())(ids).shape == (2, 16, 1000)
+    assert M.EncoderDecoderModel(M.Seq2SeqConfig.tiny())(ids, ids).shape == (2, 16, 1000)
+    assert M.ResNet.resnet18(7)(torch.randn(1, 3, 64, 64)).shape == (1, 7)
+    lm = M.LlamaModel(M.LlamaConfig.tiny())
+    assert lm(ids).shape == (2, 16, 1024) and "resnet50" in M.list_models()
