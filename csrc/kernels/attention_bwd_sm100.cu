@@ -10,7 +10,8 @@
 // operand (dQ) and as the MN-major A operand (dK, dV) - no transposes anywhere. Q, dO, K, V tiles
 // are the TMA-loaded tiles themselves, used K-major or MN-major as each product needs.
 // TMEM: S | dP (128 cols each) | dV | dK (D each) | dQ partial (D; aliases S when D = 128).
-// Warps 0-3 compute (thread = query row = TMEM lane), warp 4 issues MMAs, warp 5 drives TMA.
+// Warps 0-7 compute (two threads per query row = TMEM lane, each owning half of the columns), warp 8
+// issues MMAs, warp 9 drives TMA.
 //
 // The reference has no attention backward at all (its autograd tape covers only
 // add/sub/mul/matmul/pow/mean/sum: crates/torsh-tensor/src/core_ops/types.rs:1497-1658).
@@ -19,7 +20,7 @@
 
 namespace tb {
 
-constexpr int FB_THREADS = 192;
+constexpr int FB_THREADS = 320;  // 8 compute warps + MMA warp + TMA warp
 
 struct FaBwdParams {
   const float* LSE;    // [B, H, S]
@@ -99,15 +100,15 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(ds_full, 128);
+    mbar_init(ds_full, 256);
     mbar_init(pds_empty, 1);
     mbar_init(dq_full, 1);
-    mbar_init(dq_empty, 128);
+    mbar_init(dq_empty, 256);
     mbar_init(dkv_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_ptr, 512);
     tmem_relinquish();
   }
@@ -116,7 +117,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
 
-  if (warp == 5) {
+  if (warp == 9) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&map_q);
@@ -150,7 +151,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, 0, 0);
@@ -211,9 +212,12 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       umma_commit(dkv_full);
     }
   } else {
-    // ---------------------------------------------------------------- compute (4 warps)
-    const int row = warp * 32 + lane;
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    // ---------------------------------------------------------------- compute (8 warps)
+    // Two warps per group of 32 rows: warps 0-3 take key columns 0-63 (and the first half of the
+    // dQ / dK / dV columns), warps 4-7 the rest; no exchange is needed, L and delta are per row.
+    const int half = warp >> 2;
+    const int row = (warp & 3) * 32 + lane;
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
     uint8_t* p_smem = smem + L::P_OFF;
     uint8_t* ds_smem = smem + L::DS_OFF;
@@ -232,7 +236,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       mbar_wait(pds_empty, (t & 1) ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t sv[32], dv[32];
         tmem_ld32(tmem_base + TM_S + c * 32 + lane_off, sv);
         tmem_ld32(tmem_base + TM_DP + c * 32 + lane_off, dv);
@@ -269,7 +273,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       tc_fence_after();
       float* dq_row = p.dQ_acc + ((size_t)b * p.S + (q_ok ? qi : 0)) * ((size_t)p.H * D) + (size_t)h * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t v[32];
         tmem_ld32(tmem_base + TM_DQ + c * 32 + lane_off, v);
         tmem_wait_ld();
@@ -293,7 +297,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     __nv_bfloat16* dk_row = p.dK + ((size_t)b * p.S + (kv_ok ? kvi : 0)) * p.dkv_stride + (size_t)h * D;
     __nv_bfloat16* dv_row = p.dV + ((size_t)b * p.S + (kv_ok ? kvi : 0)) * p.dkv_stride + (size_t)h * D;
 #pragma unroll 1
-    for (int c = 0; c < D / 32; ++c) {
+    for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
       uint32_t kvv[32], vvv[32];
       tmem_ld32(tmem_base + TM_DK + c * 32 + lane_off, kvv);
       tmem_ld32(tmem_base + TM_DV + c * 32 + lane_off, vvv);
@@ -319,7 +323,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }

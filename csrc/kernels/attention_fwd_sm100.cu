@@ -1,12 +1,13 @@
 // Flash attention forward for sm_100a (tcgen05 / TMEM / TMA), causal or full, head dim 64 or 128.
 //
-// One CTA per (batch, head, 128-query block), 192 threads:
-//   warps 0-3  softmax: thread t owns query row t (= TMEM lane t). Reads S = Q K^T from TMEM,
-//              online softmax in fp32 (exp2, running max / sum), writes P as packed bf16 back to
-//              TMEM, accumulates O in registers from the per-block P V partials.
-//   warp 4     MMA issuer (one thread): S[j+1] = Q K[j+1]^T is issued before waiting for P[j],
+// One CTA per (batch, head, 128-query block), 320 threads:
+//   warps 0-7  softmax: two threads per query row (= TMEM lane), each owning half of the key
+//              columns of a score block and half of the output columns. Read S = Q K^T from TMEM,
+//              online softmax in fp32 (exp2, running max / sum), write P as packed bf16 back to
+//              TMEM, accumulate O in registers from the per-block P V partials.
+//   warp 8     MMA issuer (one thread): S[j+1] = Q K[j+1]^T is issued before waiting for P[j],
 //              so the tensor core works on the next block while the softmax warps run.
-//   warp 5     TMA producer (one thread): Q once, K / V tiles through 2-deep rings.
+//   warp 9     TMA producer (one thread): Q once, K / V tiles through 2-deep rings.
 // TMEM (512 columns): S0 | S1 (128 each, fp32) | P0 | P1 (64 each, bf16 pairs) | O partial (D).
 // Memory is O(S): nothing of size S x S is ever written. Q, K, V are addressed through 4-D tensor
 // maps [B, S, H, D] with arbitrary token stride, so the fused QKV projection output is consumed
@@ -22,7 +23,7 @@ namespace tb {
 
 constexpr int FA_BM = 128;
 constexpr int FA_BN = 128;
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;  // 8 softmax warps + MMA warp + TMA warp
 
 struct FaFwdParams {
   __nv_bfloat16* O;  // [B*S, o_stride] with head h at column h*D
@@ -43,7 +44,8 @@ struct FaFwdSmem {
   static constexpr int BAR_OFF = 5 * TILE;
   // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_full, o_empty
   static constexpr int NBARS = 15;
-  static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
+  static constexpr int XMAX_OFF = BAR_OFF + NBARS * 8 + 16;   // float [2][2][128]: row-max / row-sum exchange
+  static constexpr int TOTAL = XMAX_OFF + 2 * 2 * 128 * 4;
   static constexpr int ALLOC = TOTAL + 1024;
 };
 
@@ -68,6 +70,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   uint64_t* o_empty = bars + 14;
   uint32_t* tmem_ptr = (uint32_t*)(bars + L::NBARS);
   volatile int* abort_flag = (volatile int*)(tmem_ptr + 1);
+  volatile float* xmax = (volatile float*)(smem + L::XMAX_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qb = (p.S + FA_BM - 1) / FA_BM;
@@ -87,14 +90,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&p_full[i], 256);
     }
     mbar_init(o_full, 1);
-    mbar_init(o_empty, 128);
+    mbar_init(o_empty, 256);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc(tmem_ptr, 512);
     tmem_relinquish();
   }
@@ -103,7 +106,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr;
 
-  if (warp == 5) {
+  if (warp == 9) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&map_q);
@@ -132,7 +135,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
       }
     }
-  } else if (warp == 4) {
+  } else if (warp == 8) {
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(128, FA_BN, 0, 0);
@@ -173,23 +176,30 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       }
     }
   } else {
-    // ---------------------------------------------------------------- softmax (4 warps)
-    const int row = warp * 32 + lane;          // row inside the query block = TMEM lane
-    const int qi = q0 + row;                   // global query index
-    const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+    // ---------------------------------------------------------------- softmax (8 warps)
+    // Two warps share each group of 32 query rows: warps 0-3 take key columns 0-63 of every score
+    // block and the first half of the output columns, warps 4-7 the other halves. Two warps per
+    // scheduler keep the exp2 / convert stream issuing while the partner waits on TMEM or the
+    // special-function unit. The row maximum is the only value the two halves must agree on per
+    // block (one shared-memory exchange + one named barrier); the row sums meet once at the end.
+    const int half = warp >> 2;                 // 0: columns 0-63, 1: columns 64-127
+    const int row = (warp & 3) * 32 + lane;     // row inside the query block = TMEM lane
+    const int qi = q0 + row;                    // global query index
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
+    constexpr int DH = D / 2;                   // output columns owned by this thread
     float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
-    float o[D];
+    float o[DH];
 #pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    for (int i = 0; i < DH; ++i) o[i] = 0.f;
 
     auto accumulate_o = [&](int jdone) {
       mbar_wait(o_full, jdone & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < DH / 32; ++c) {
         uint32_t v[32];
-        tmem_ld32(tmem_base + TM_O + c * 32 + lane_off, v);
+        tmem_ld32(tmem_base + TM_O + half * DH + c * 32 + lane_off, v);
         tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
@@ -200,49 +210,57 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
 
     for (int j = 0; j < n_kv; ++j) {
       const int s = j & 1;
-      const int kv0 = j * FA_BN;
-      const bool need_mask = (p.causal && kv0 + FA_BN - 1 > q0) || (kv0 + FA_BN > p.S);
+      const int kv0 = j * FA_BN + half * 64;   // first key column of this thread's half
+      const bool need_mask = (p.causal && j * FA_BN + FA_BN - 1 > q0) || (j * FA_BN + FA_BN > p.S);
       const int col_limit = p.causal ? min(qi, p.S - 1) : p.S - 1;  // last visible key index
       mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
-      const uint32_t ts = tmem_base + TM_S + s * 128 + lane_off;
-      float mx = m;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(ts + c * 32, v);
-        tmem_wait_ld();
+      const uint32_t ts = tmem_base + TM_S + s * 128 + half * 64 + lane_off;
+      uint32_t v0[32], v1[32];
+      tmem_ld32(ts, v0);
+      tmem_ld32(ts + 32, v1);
+      tmem_wait_ld();
+      float mx = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[i]);
-          if (need_mask && kv0 + c * 32 + i > col_limit) x = -INFINITY;
-          mx = fmaxf(mx, x);
+      for (int i = 0; i < 32; ++i) {
+        float x0 = __uint_as_float(v0[i]), x1 = __uint_as_float(v1[i]);
+        if (need_mask) {
+          if (kv0 + i > col_limit) x0 = -INFINITY;
+          if (kv0 + 32 + i > col_limit) x1 = -INFINITY;
         }
+        mx = fmaxf(mx, fmaxf(x0, x1));
       }
+      xmax[(j & 1) * 256 + half * 128 + row] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mx = fmaxf(m, fmaxf(mx, xmax[(j & 1) * 256 + (half ^ 1) * 128 + row]));
       const float msafe = (mx == -INFINITY) ? 0.f : mx;
       const float alpha = exp2f((m - msafe) * sl2);
       const float moff = msafe * sl2;
       float rowsum = 0.f;
-      const uint32_t tp = tmem_base + TM_P + s * 64 + lane_off;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(ts + c * 32, v);
-        tmem_wait_ld();
-        uint32_t pk[16];
+      const uint32_t tp = tmem_base + TM_P + s * 64 + half * 32 + lane_off;
+      uint32_t pk[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float x0 = __uint_as_float(v[2 * i]), x1 = __uint_as_float(v[2 * i + 1]);
-          float p0 = exp2f(x0 * sl2 - moff), p1 = exp2f(x1 * sl2 - moff);
-          if (need_mask) {
-            if (kv0 + c * 32 + 2 * i > col_limit) p0 = 0.f;
-            if (kv0 + c * 32 + 2 * i + 1 > col_limit) p1 = 0.f;
-          }
-          rowsum += p0 + p1;
-          pk[i] = pack_bf16x2(p0, p1);
+      for (int i = 0; i < 16; ++i) {
+        float p0 = exp2f(__uint_as_float(v0[2 * i]) * sl2 - moff), p1 = exp2f(__uint_as_float(v0[2 * i + 1]) * sl2 - moff);
+        if (need_mask) {
+          if (kv0 + 2 * i > col_limit) p0 = 0.f;
+          if (kv0 + 2 * i + 1 > col_limit) p1 = 0.f;
         }
-        tmem_st16(tp + c * 16, pk);
+        rowsum += p0 + p1;
+        pk[i] = pack_bf16x2(p0, p1);
       }
+      tmem_st16(tp, pk);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float p0 = exp2f(__uint_as_float(v1[2 * i]) * sl2 - moff), p1 = exp2f(__uint_as_float(v1[2 * i + 1]) * sl2 - moff);
+        if (need_mask) {
+          if (kv0 + 32 + 2 * i > col_limit) p0 = 0.f;
+          if (kv0 + 32 + 2 * i + 1 > col_limit) p1 = 0.f;
+        }
+        rowsum += p0 + p1;
+        pk[i] = pack_bf16x2(p0, p1);
+      }
+      tmem_st16(tp + 16, pk);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[s]);
@@ -252,11 +270,15 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       alpha_prev = alpha;
     }
     accumulate_o(n_kv - 1);
+    // the two halves of a row add their partial sums
+    xmax[half * 128 + row] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += xmax[(half ^ 1) * 128 + row];
     if (qi < p.S) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = p.O + ((size_t)b * p.S + qi) * p.o_stride + (size_t)h * D;
+      __nv_bfloat16* orow = p.O + ((size_t)b * p.S + qi) * p.o_stride + (size_t)h * D + half * DH;
 #pragma unroll
-      for (int g = 0; g < D / 8; ++g) {
+      for (int g = 0; g < DH / 8; ++g) {
         uint4 w;
         w.x = pack_bf16x2(o[g * 8 + 0] * inv, o[g * 8 + 1] * inv);
         w.y = pack_bf16x2(o[g * 8 + 2] * inv, o[g * 8 + 3] * inv);
@@ -264,13 +286,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         w.w = pack_bf16x2(o[g * 8 + 6] * inv, o[g * 8 + 7] * inv);
         reinterpret_cast<uint4*>(orow)[g] = w;
       }
-      if (p.LSE) p.LSE[((size_t)b * p.H + h) * p.S + qi] = (l > 0.f) ? (m * p.scale + logf(l)) : -INFINITY;
+      if (p.LSE && half == 0) p.LSE[((size_t)b * p.H + h) * p.S + qi] = (l > 0.f) ? (m * p.scale + logf(l)) : -INFINITY;
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }

@@ -1,0 +1,189 @@
+"""Profiler: scoped events, CUDA-event device timing, NVTX ranges, Chrome-trace / JSON / Prometheus export.
+
+Reference: global ``Profiler`` + RAII ``ScopeGuard`` recording ``ProfileEvent{name, category, start_us, duration_us,
+thread_id, op_count, flops, bytes}`` (``crates/torsh-profiler/src/core/profiler.rs:14-240``, ``core/scope.rs``), macros
+``profile_block! / profile_cuda! / profile_tensor_op!`` (``src/macros.rs:21-417``), Chrome-trace export
+(``src/chrome_trace.rs:10-68``); its CUDA side only records what it is told (``src/cuda.rs:21-437``). Here a scope on a
+CUDA device brackets the region with CUDA events (resolved lazily, no sync inside the region) and pushes an NVTX
+range; ``CommunicationProfiler`` keeps per-collective records with achieved bandwidth
+(``crates/torsh-distributed/src/profiling.rs:14-619``).
+"""
+from __future__ import annotations
+
+import functools
+import json
+import os
+import threading
+import time
+from contextlib import contextmanager
+from dataclasses import asdict, dataclass, field
+
+import torch
+
+
+@dataclass
+class ProfileEvent:
+    name: str
+    category: str
+    start_us: float
+    duration_us: float
+    thread_id: int
+    device_us: float | None = None
+    op_count: int = 0
+    flops: float = 0.0
+    bytes: float = 0.0
+    args: dict = field(default_factory=dict)
+
+
+class Profiler:
+    _global = None
+
+    def __init__(self, enabled: bool = True, use_cuda: bool | None = None, nvtx: bool = True):
+        self.enabled = enabled
+        self.use_cuda = torch.cuda.is_available() if use_cuda is None else use_cuda
+        self.nvtx = nvtx and self.use_cuda
+        self.events: list[ProfileEvent] = []
+        self._pending: list = []
+        self._lock = threading.Lock()
+        self._t0 = time.perf_counter()
+
+    @classmethod
+    def global_(cls) -> "Profiler":
+        if cls._global is None:
+            cls._global = cls(enabled=os.environ.get("TORSH_PROFILE", "0") not in ("0", ""))
+        return cls._global
+
+    @contextmanager
+    def scope(self, name: str, category: str = "op", flops: float = 0.0, bytes: float = 0.0, **args):
+        if not self.enabled:
+            yield
+            return
+        ev = None
+        if self.use_cuda:
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
+            if self.nvtx:
+                torch.cuda.nvtx.range_push(name)
+        t0 = time.perf_counter()
+        try:
+            yield
+        finally:
+            dur = (time.perf_counter() - t0) * 1e6
+            if ev is not None:
+                ev[1].record()
+                if self.nvtx:
+                    torch.cuda.nvtx.range_pop()
+            e = ProfileEvent(name, category, (t0 - self._t0) * 1e6, dur, threading.get_ident(), None, 1, flops, bytes, args)
+            with self._lock:
+                self.events.append(e)
+                if ev is not None:
+                    self._pending.append((e, ev))
+
+    def profile(self, name: str | None = None, category: str = "fn"):
+        def deco(fn):
+            @functools.wraps(fn)
+            def wrapped(*a, **kw):
+                with self.scope(name or fn.__qualname__, category):
+                    return fn(*a, **kw)
+            return wrapped
+        return deco
+
+    def resolve(self):
+        """Synchronise once and fill in the device durations of all finished scopes."""
+        if self._pending:
+            torch.cuda.synchronize()
+            for e, (a, b) in self._pending:
+                e.device_us = a.elapsed_time(b) * 1e3
+            self._pending.clear()
+
+    def summary(self) -> dict:
+        self.resolve()
+        out: dict = {}
+        for e in self.events:
+            s = out.setdefault(e.name, {"count": 0, "host_us": 0.0, "device_us": 0.0, "flops": 0.0, "bytes": 0.0})
+            s["count"] += 1
+            s["host_us"] += e.duration_us
+            s["device_us"] += e.device_us or 0.0
+            s["flops"] += e.flops
+            s["bytes"] += e.bytes
+        for s in out.values():
+            t = (s["device_us"] or s["host_us"]) * 1e-6
+            s["tflops"] = s["flops"] / t / 1e12 if t > 0 and s["flops"] else 0.0
+            s["gbps"] = s["bytes"] / t / 1e9 if t > 0 and s["bytes"] else 0.0
+        return out
+
+    def export_chrome_trace(self, path):
+        self.resolve()
+        tr = [{"name": e.name, "cat": e.category, "ph": "X", "ts": e.start_us, "dur": e.device_us or e.duration_us,
+               "pid": os.getpid(), "tid": e.thread_id % 100000, "args": e.args} for e in self.events]
+        with open(path, "w") as f:
+            json.dump({"traceEvents": tr, "displayTimeUnit": "us"}, f)
+
+    def export_json(self, path):
+        self.resolve()
+        with open(path, "w") as f:
+            json.dump([asdict(e) for e in self.events], f, indent=1)
+
+    def prometheus_text(self, prefix: str = "torsh") -> str:
+        lines = []
+        for name, s in self.summary().items():
+            lab = name.replace('"', "'")
+            lines.append(f'{prefix}_scope_count{{name="{lab}"}} {s["count"]}')
+            lines.append(f'{prefix}_scope_device_seconds{{name="{lab}"}} {s["device_us"] * 1e-6:.9f}')
+            lines.append(f'{prefix}_scope_host_seconds{{name="{lab}"}} {s["host_us"] * 1e-6:.9f}')
+        return "\n".join(lines) + "\n"
+
+    def clear(self):
+        self.events.clear()
+        self._pending.clear()
+
+
+def profile_block(name: str, category: str = "block", **kw):
+    """``profile_block!`` equivalent on the global profiler."""
+    return Profiler.global_().scope(name, category, **kw)
+
+
+@dataclass
+class CommunicationEvent:
+    op_type: str
+    rank: int
+    bytes: int
+    duration_us: float
+    algo: str = ""
+
+
+class CommunicationProfiler:
+    def __init__(self, rank: int = 0):
+        self.rank, self.events = rank, []
+
+    @contextmanager
+    def record(self, op_type: str, nbytes: int, algo: str = ""):
+        if torch.cuda.is_available():
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            yield
+            b.record()
+            b.synchronize()
+            us = a.elapsed_time(b) * 1e3
+        else:
+            t0 = time.perf_counter()
+            yield
+            us = (time.perf_counter() - t0) * 1e6
+        self.events.append(CommunicationEvent(op_type, self.rank, nbytes, us, algo))
+
+    def stats(self) -> dict:
+        out = {}
+        for e in self.events:
+            s = out.setdefault(e.op_type, {"count": 0, "bytes": 0, "us": []})
+            s["count"] += 1
+            s["bytes"] += e.bytes
+            s["us"].append(e.duration_us)
+        for s in out.values():
+            u = sorted(s.pop("us"))
+            s["p50_us"], s["p99_us"] = u[len(u) // 2], u[min(len(u) - 1, int(len(u) * 0.99))]
+            s["gbps"] = s["bytes"] / (sum(u) * 1e-6) / 1e9 if sum(u) > 0 else 0.0
+        return out
+
+    def export_json(self, path):
+        with open(path, "w") as f:
+            json.dump({"events": [asdict(e) for e in self.events], "stats": self.stats()}, f, indent=1)
