@@ -270,10 +270,11 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       alpha_prev = alpha;
     }
     accumulate_o(n_kv - 1);
-    // the two halves of a row add their partial sums
-    xmax[half * 128 + row] = l;
+    // the two halves of a row add their partial sums, through the exchange buffer that the last block did
+    // not use (its readers may still be behind this thread)
+    xmax[(n_kv & 1) * 256 + half * 128 + row] = l;
     asm volatile("bar.sync 1, 256;" ::: "memory");
-    l += xmax[(half ^ 1) * 128 + row];
+    l += xmax[(n_kv & 1) * 256 + (half ^ 1) * 128 + row];
     if (qi < p.S) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* orow = p.O + ((size_t)b * p.S + qi) * p.o_stride + (size_t)h * D + half * DH;

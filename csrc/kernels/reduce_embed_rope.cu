@@ -114,6 +114,33 @@ __global__ void embedding_bwd_kernel(const long* __restrict__ ids, const T* __re
   }
 }
 
+// Message passing without the [E, F] message tensor: out[dst[e], :] += w[e] * x[src[e], :] for every edge e.
+// One thread owns four consecutive features of one edge and issues one 16-byte vector reduction
+// (red.global.add.v4.f32), so each edge row costs F/4 atomics. The CUDA string the reference emits for the
+// same step adds into the output without atomics (crates/torsh-graph/src/jit.rs:405-450). src == nullptr reads
+// row e of x (plain scatter-add); w == nullptr is weight 1. Indices outside [0, n_src) / [0, n_dst) are skipped.
+template <typename T>
+__global__ void gnn_scatter_kernel(const T* __restrict__ x, const long* __restrict__ src,
+                                   const long* __restrict__ dst, const float* __restrict__ w,
+                                   float* __restrict__ out, long E, int F, long n_src, long n_dst) {
+  const int fq = F >> 2;
+  const long total = E * fq;
+  const long stride = (long)gridDim.x * blockDim.x;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    const long e = idx / fq;
+    const int c = (int)(idx - e * fq) << 2;
+    const long s = src ? src[e] : e;
+    const long d = dst[e];
+    if (s < 0 || s >= n_src || d < 0 || d >= n_dst) continue;
+    const float we = w ? w[e] : 1.f;
+    const T* xp = x + s * F + c;
+    float4 v = make_float4(to_f<T>(xp[0]) * we, to_f<T>(xp[1]) * we, to_f<T>(xp[2]) * we, to_f<T>(xp[3]) * we);
+    float* op = out + d * F + c;
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(op), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
+                 : "memory");
+  }
+}
+
 // Rotary embedding on x [B, S, heads, D] (in place allowed). Adjacent pairs (2i, 2i+1) rotate by
 // pos * base^(-2i/D): the pairing and frequency rule of RotaryPositionalEmbedding
 // (crates/torsh-nn/src/layers/embedding.rs:372-430), whose rotate step is a no-op in the
@@ -192,6 +219,18 @@ TB_EXPORT int tb_embedding_bwd(const long* ids, const void* dout, float* dwte, f
   long total = tokens * H;
   if (dtype == 0) embedding_bwd_kernel<bf16><<<grid_for(total), 256, 0, st>>>(ids, (const bf16*)dout, dwte, dwpe, tokens, H, seq, vocab);
   else embedding_bwd_kernel<float><<<grid_for(total), 256, 0, st>>>(ids, (const float*)dout, dwte, dwpe, tokens, H, seq, vocab);
+  TB_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+TB_EXPORT int tb_gnn_scatter(const void* x, const long* src, const long* dst, const float* w, float* out, long E,
+                             int F, long n_src, long n_dst, int dtype, cudaStream_t st) {
+  TB_ENSURE_DEVICE();
+  if (E <= 0) return 0;
+  if (F % 4) TB_FAIL(TB_E_ARG, "gnn_scatter: feature count must be a multiple of 4");
+  if (((uintptr_t)out & 15) != 0) TB_FAIL(TB_E_ARG, "gnn_scatter: output must be 16-byte aligned");
+  long total = E * (F / 4);
+  if (dtype == 0) gnn_scatter_kernel<bf16><<<grid_for(total), 256, 0, st>>>((const bf16*)x, src, dst, w, out, E, F, n_src, n_dst);
+  else gnn_scatter_kernel<float><<<grid_for(total), 256, 0, st>>>((const float*)x, src, dst, w, out, E, F, n_src, n_dst);
   TB_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

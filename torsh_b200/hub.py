@@ -1,0 +1,154 @@
+"""Model hub and packaging (``crates/torsh-hub``, ``crates/torsh-package``).
+
+``LocalHub`` is a directory-backed registry (publish / fetch / list / search, versioned entries with SHA-256 integrity
+and a JSON model card); remote download is refused when no network is reachable rather than silently skipped.
+``Package`` is a torch.package-like archive: a zip with a manifest (name, version, dependencies, per-file SHA-256),
+optional zlib compression and an HMAC-SHA256 signature over the manifest (the reference signs with ed25519, which
+needs a library that is not in this image)."""
+from __future__ import annotations
+
+import hashlib
+import hmac
+import json
+import shutil
+import time
+import zipfile
+from pathlib import Path
+
+
+def sha256_file(path) -> str:
+    h = hashlib.sha256()
+    with open(path, "rb") as f:
+        for chunk in iter(lambda: f.read(1 << 20), b""):
+            h.update(chunk)
+    return h.hexdigest()
+
+
+class LocalHub:
+    def __init__(self, root):
+        self.root = Path(root)
+        self.root.mkdir(parents=True, exist_ok=True)
+        self.index_path = self.root / "index.json"
+
+    def _index(self) -> dict:
+        return json.loads(self.index_path.read_text()) if self.index_path.exists() else {}
+
+    def publish(self, name: str, path, version: str | None = None, card: dict | None = None) -> dict:
+        idx = self._index()
+        version = version or f"v{len(idx.get(name, {})) + 1}"
+        dst = self.root / name.replace("/", "__") / version
+        dst.mkdir(parents=True, exist_ok=True)
+        f = dst / Path(path).name
+        shutil.copyfile(path, f)
+        entry = {"file": str(f.relative_to(self.root)), "sha256": sha256_file(f), "size": f.stat().st_size,
+                 "published": time.time(), "card": card or {}}
+        idx.setdefault(name, {})[version] = entry
+        self.index_path.write_text(json.dumps(idx, indent=1))
+        return {"name": name, "version": version, **entry}
+
+    def list(self) -> list[str]:
+        return [f"{n}@{v}" for n, vs in sorted(self._index().items()) for v in vs]
+
+    def search(self, query: str) -> list[str]:
+        q = query.lower()
+        return [e for e in self.list() if q in e.lower()]
+
+    def fetch(self, name: str, version: str | None = None, output=None) -> Path:
+        idx = self._index()
+        if name not in idx:
+            if "://" in name or name.count("/") == 1:
+                raise ConnectionError(f"{name!r} is not in the local hub and no network is reachable")
+            raise KeyError(name)
+        version = version or sorted(idx[name])[-1]
+        e = idx[name][version]
+        src = self.root / e["file"]
+        if sha256_file(src) != e["sha256"]:
+            raise IOError(f"integrity check failed for {name}@{version}")
+        if output:
+            Path(output).parent.mkdir(parents=True, exist_ok=True)
+            shutil.copyfile(src, output)
+            return Path(output)
+        return src
+
+    def load(self, name: str, version: str | None = None):
+        """Fetch, decode and instantiate: the card's ``architecture`` names a registry entry."""
+        from . import models
+        from .serialize import model_state as ms
+        st = ms.load_binary(self.fetch(name, version))
+        m = models.create_model(st["metadata"]["architecture"])
+        ms.load_model_state(m, st, strict=False)
+        return m
+
+
+class Package:
+    MANIFEST = "MANIFEST.json"
+
+    def __init__(self, name: str, version: str = "0.1.0", dependencies: dict | None = None):
+        self.name, self.version, self.dependencies = name, version, dependencies or {}
+        self.files: dict[str, bytes] = {}
+
+    def add_bytes(self, arcname: str, data: bytes): self.files[arcname] = data
+    def add_file(self, path, arcname: str | None = None): self.files[arcname or Path(path).name] = Path(path).read_bytes()
+    def add_source(self, module_name: str, source: str): self.files[f"code/{module_name.replace('.', '/')}.py"] = source.encode()
+
+    def add_model(self, model, arcname="model.trsm", architecture=None):
+        from .serialize import model_state as ms
+        self.files[arcname] = ms.encode_binary(ms.model_state(model, architecture=architecture))
+
+    def manifest(self) -> dict:
+        return {"name": self.name, "version": self.version, "dependencies": self.dependencies, "format": 1,
+                "files": {k: {"sha256": hashlib.sha256(v).hexdigest(), "size": len(v)} for k, v in sorted(self.files.items())}}
+
+    def save(self, path, compress: bool = True, key: bytes | None = None) -> None:
+        man = json.dumps(self.manifest(), sort_keys=True).encode()
+        with zipfile.ZipFile(path, "w", zipfile.ZIP_DEFLATED if compress else zipfile.ZIP_STORED) as z:
+            z.writestr(self.MANIFEST, man)
+            if key is not None:
+                z.writestr("SIGNATURE", hmac.new(key, man, hashlib.sha256).hexdigest())
+            for k, v in self.files.items():
+                z.writestr(k, v)
+
+    @classmethod
+    def load(cls, path, key: bytes | None = None) -> "Package":
+        with zipfile.ZipFile(path) as z:
+            man_raw = z.read(cls.MANIFEST)
+            man = json.loads(man_raw)
+            if key is not None:
+                sig = z.read("SIGNATURE").decode() if "SIGNATURE" in z.namelist() else ""
+                if not hmac.compare_digest(sig, hmac.new(key, man_raw, hashlib.sha256).hexdigest()):
+                    raise PermissionError("package signature does not verify")
+            pkg = cls(man["name"], man["version"], man["dependencies"])
+            for k, meta in man["files"].items():
+                data = z.read(k)
+                if hashlib.sha256(data).hexdigest() != meta["sha256"]:
+                    raise IOError(f"{k}: checksum mismatch")
+                pkg.files[k] = data
+        return pkg
+
+    def import_module(self, module_name: str):
+        import types
+        src = self.files[f"code/{module_name.replace('.', '/')}.py"].decode()
+        mod = types.ModuleType(module_name)
+        exec(compile(src, f"<package {self.name}:{module_name}>", "exec"), mod.__dict__)
+        return mod
+
+
+def resolve_dependencies(requirements: dict[str, str], available: dict[str, list[str]]) -> dict[str, str]:
+    """Pick the highest available version satisfying each ``>=x`` / ``==x`` / ``^x`` requirement."""
+    key = lambda v: tuple(int(p) for p in v.split("."))
+    out = {}
+    for name, req in requirements.items():
+        cands = sorted(available.get(name, []), key=key)
+        if req.startswith("=="):
+            ok = [v for v in cands if v == req[2:]]
+        elif req.startswith(">="):
+            ok = [v for v in cands if key(v) >= key(req[2:])]
+        elif req.startswith("^"):
+            base = key(req[1:])
+            ok = [v for v in cands if key(v) >= base and key(v)[0] == base[0]]
+        else:
+            ok = cands
+        if not ok:
+            raise LookupError(f"no version of {name} satisfies {req!r} (have {cands})")
+        out[name] = ok[-1]
+    return out

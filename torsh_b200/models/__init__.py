@@ -7,6 +7,7 @@ from .transformer_zoo import (BertConfig, BertForMaskedLM, BertForSequenceClassi
                               VisionTransformer)
 
 _REGISTRY = {
+    "gpt2-tiny": lambda **kw: GPTForCausalLM(GPT2Config.tiny(**kw)),
     "gpt2": lambda **kw: GPTForCausalLM(GPT2Config.small(**kw)),
     "gpt2-medium": lambda **kw: GPTForCausalLM(GPT2Config.medium(**kw)),
     "gpt2-large": lambda **kw: GPTForCausalLM(GPT2Config.large(**kw)),

@@ -51,13 +51,13 @@ class GPT2Config:
         return (self.vocab_size + 63) // 64 * 64
 
     @classmethod
-    def small(cls, **kw): return cls(n_embd=768, n_layer=12, n_head=12, **kw)
+    def small(cls, **kw): return cls(**{**dict(n_embd=768, n_layer=12, n_head=12), **kw})
     @classmethod
-    def medium(cls, **kw): return cls(n_embd=1024, n_layer=24, n_head=16, **kw)
+    def medium(cls, **kw): return cls(**{**dict(n_embd=1024, n_layer=24, n_head=16), **kw})
     @classmethod
-    def large(cls, **kw): return cls(n_embd=1280, n_layer=36, n_head=20, **kw)
+    def large(cls, **kw): return cls(**{**dict(n_embd=1280, n_layer=36, n_head=20), **kw})
     @classmethod
-    def xl(cls, **kw): return cls(n_embd=1600, n_layer=48, n_head=25, **kw)
+    def xl(cls, **kw): return cls(**{**dict(n_embd=1600, n_layer=48, n_head=25), **kw})
 
     @classmethod
     def tiny(cls, **kw):

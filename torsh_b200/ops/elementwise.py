@@ -260,3 +260,52 @@ def colsum_into(x2d: torch.Tensor, out_f32: torch.Tensor) -> None:
              x2d.stride(0), dtype_code(x2d), nv.stream_ptr())
     else:
         out_f32.add_(x2d.float().sum(0))
+
+
+def _gnn_scatter_raw(x, src, dst, w, n_dst):
+    out = torch.zeros(n_dst, x.shape[1], dtype=torch.float32, device=x.device)
+    E = dst.numel()
+    call("tb_gnn_scatter", [P, P, P, P, P, L, I, L, L, I, P], x.data_ptr(), nv.ptr(src), dst.data_ptr(), nv.ptr(w),
+         out.data_ptr(), E, x.shape[1], x.shape[0], n_dst, dtype_code(x), nv.stream_ptr())
+    return out
+
+
+class _GnnScatterFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, src, dst, w, n_dst):
+        ctx.save_for_backward(src, dst, w, x if (w is not None and w.requires_grad) else None)
+        ctx.n_src, ctx.xdtype = x.shape[0], x.dtype
+        return _gnn_scatter_raw(x, src, dst, w, n_dst).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dout):
+        src, dst, w, x = ctx.saved_tensors
+        dout = aligned(dout.contiguous())
+        E = dst.numel()
+        if src is None:  # out[dst[e]] += w[e] x[e]  →  dx[e] = w[e] dout[dst[e]]
+            dx = dout[dst]
+            if w is not None:
+                dx = dx * w[:, None].to(dx.dtype)
+        else:            # dx[src[e]] += w[e] dout[dst[e]]: the same kernel with the roles of the index lists swapped
+            dx = _gnn_scatter_raw(dout, dst, src, w, ctx.n_src).to(ctx.xdtype)
+        dw = None
+        if x is not None:
+            xs = x if src is None else x[src]
+            dw = (xs.float() * dout[dst].float()).sum(1)
+        return dx, None, None, dw, None
+
+
+def gnn_scatter(x: torch.Tensor, dst: torch.Tensor, n_dst: int, src: torch.Tensor | None = None,
+                weight: torch.Tensor | None = None) -> torch.Tensor:
+    """``out[dst[e]] += weight[e] * x[src[e]]`` (``src=None``: row ``e`` of ``x``; ``weight=None``: 1), fp32 accumulation.
+
+    The gather, the edge weight and the scatter-add are one kernel, so the ``[E, F]`` message tensor of a
+    message-passing layer is never written."""
+    if kernel_ok(x) and x.dim() == 2 and x.shape[1] % 4 == 0 and dst.is_cuda:
+        x = aligned(x.contiguous())
+        w = None if weight is None else weight.float().contiguous()
+        return _GnnScatterFn.apply(x, None if src is None else src.contiguous(), dst.contiguous(), w, n_dst)
+    m = x if src is None else x[src]
+    if weight is not None:
+        m = m * weight[:, None].to(m.dtype)
+    return torch.zeros(n_dst, *x.shape[1:], dtype=x.dtype, device=x.device).index_add_(0, dst, m)

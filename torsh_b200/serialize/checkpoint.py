@@ -128,7 +128,7 @@ def restore_into(ck: dict, model: torch.nn.Module, optimizer=None, strict: bool 
             if n in o["velocity_states"]:
                 st["exp_avg_sq"] = torch.from_numpy(o["velocity_states"][n]).reshape(p.shape).to(p.device)
             if n in o["step_counts"]:
-                st["step"] = o["step_counts"][n]
+                st["step"] = torch.tensor(float(o["step_counts"][n]))
 
 
 class CheckpointManager:
