@@ -1,0 +1,186 @@
+"""Caching-pool logic on the host-memory instance, and the domain libraries that need no GPU."""
+import math
+
+import pytest
+import torch
+
+
+def test_pool_rounding_reuse_split_merge():
+    from torsh_b200.core.runtime import HostPool
+    p = HostPool()
+    assert p.round_size(1) == 512 and p.round_size(513) == 1024 and p.round_size((1 << 20) + 1) == 2 << 20 and p.round_size((2 << 20) + 1) == 4 << 20
+    a = p.alloc(1000)
+    b = p.alloc(3000)
+    s = p.stats()
+    assert s["raw_allocs"] == 1 and s["segments"] == 1 and s["reserved_bytes"] == 2 << 20      # both from one 2 MiB segment
+    assert s["allocated_bytes"] == 1024 + 3072 and p.size_of(a) == 1024
+    assert p.free(a) and not p.free(a)                                                          # double free refused
+    c = p.alloc(900)                                                                            # reuses a's block
+    assert c == a and p.stats()["cache_hits"] >= 1
+    # another stream never reuses this stream's cached blocks
+    p.free(c)
+    d = p.alloc(900, stream=7)
+    assert d != a and p.stats()["segments"] == 2
+    p.free(b); p.free(d)
+    assert p.stats()["allocated_bytes"] == 0 and p.stats()["merges"] >= 2
+    assert p.release_cached() == 4 << 20 and p.stats()["reserved_bytes"] == 0 and p.stats()["segments"] == 0
+    p.close()
+
+
+def test_pool_large_blocks_limit_and_oom_retry():
+    from torsh_b200.core.runtime import HostPool
+    MB = 1 << 20
+    p = HostPool(raw_budget=64 * MB)
+    big = p.alloc(30 * MB)
+    assert p.size_of(big) == 30 * MB
+    p.free(big)
+    small_large = p.alloc(4 * MB)                      # best fit takes the cached 30 MiB block and splits it
+    st = p.stats()
+    assert small_large == big and st["splits"] >= 1 and st["raw_allocs"] == 1
+    other = p.alloc(20 * MB)                           # served by the 26 MiB remainder
+    assert p.stats()["raw_allocs"] == 1
+    p.free(small_large); p.free(other)
+    assert p.fragmentation() == 0.0
+    # the raw allocator has 34 MiB left: a 40 MiB request fails once, the cache is released, the retry succeeds
+    x = p.alloc(40 * MB)
+    st = p.stats()
+    assert x and st["oom_retries"] == 1 and st["raw_frees"] == 1
+    assert p.alloc(40 * MB) is None                    # genuinely out of budget
+    assert p.pressure(64 * MB) == "low" and p.pressure(44 * MB) == "high"
+    p.free(x)
+    q = HostPool(limit=8 * MB)
+    y = q.alloc(6 * MB)
+    assert y and q.alloc(6 * MB) is None
+    q.free(y)
+    assert q.alloc(8 * MB)                             # cached 6 MiB segment is released to stay under the limit
+    p.close(); q.close()
+
+
+def test_cluster_and_sparse_and_graph():
+    from torsh_b200 import cluster, graph as G, sparse as sp
+    torch.manual_seed(0)
+    x = torch.cat([torch.randn(40, 2) + 6, torch.randn(40, 2) - 6])
+    true = torch.cat([torch.zeros(40), torch.ones(40)]).long()
+    for lab in (cluster.kmeans(x, 2)[0], cluster.dbscan(x, 2.5, 3), cluster.GaussianMixture(2).fit(x).predict(x),
+                cluster.spectral_clustering(x, 2, 0.05), cluster.agglomerative(x[::4], 2)):
+        assert cluster.adjusted_rand_index(lab, true[:: len(true) // len(lab)]) > 0.99
+    assert cluster.silhouette_score(x, true) > 0.8
+    d = torch.randn(8, 12) * (torch.rand(8, 12) > 0.6)
+    b = torch.randn(12, 5)
+    coo = sp.CooTensor.from_dense(d)
+    for t in (coo, coo.to_csr(), coo.to_csc(), sp.BsrTensor.from_dense(d, 4), sp.EllTensor.from_dense(d)):
+        assert torch.allclose(t.to_dense(), d) and torch.allclose(t.matmul(b), d @ b, atol=1e-5)
+    assert torch.allclose(sp.DiaTensor.from_dense(d).to_dense(), d)
+    lin = torch.nn.Linear(12, 8)
+    sl = sp.SparseLinear(lin, 0.5)
+    assert sl(torch.randn(3, 12)).shape == (3, 8) and abs(sl.values.numel() - 48) <= 1
+    data = G.stochastic_block_model()
+    conv = G.GCNConv(16, 4)
+    A = torch.zeros(80, 80); A[data.edge_index[1], data.edge_index[0]] = 1; A += torch.eye(80)
+    dg = A.sum(1)
+    assert torch.allclose(conv(data.x, data.edge_index), (dg.rsqrt()[:, None] * A * dg.rsqrt()[None]) @ conv.lin(data.x) + conv.bias, atol=1e-5)
+    for layer in (G.SAGEConv(16, 8), G.GATConv(16, 8, heads=2), G.GINConv(torch.nn.Linear(16, 8))):
+        out = layer(data.x, data.edge_index)
+        out.sum().backward()
+        assert out.shape[0] == 80 and torch.isfinite(out).all()
+    batch = G.GraphData.collate([data, data])
+    assert G.global_mean_pool(batch.x, batch.batch).shape == (2, 16)
+
+
+def test_signal_series_linalg_quantization():
+    from torsh_b200 import linalg, quantization as Q, series as S, signal
+    torch.manual_seed(0)
+    s = torch.sin(torch.arange(4096) * 0.05)
+    assert torch.allclose(signal.istft(signal.stft(s), length=4096), s, atol=1e-4)
+    a, d = signal.haar_dwt(s)
+    assert torch.allclose(signal.haar_idwt(a, d), s, atol=1e-6)
+    assert signal.mel_filterbank(40, 512, 16000).shape == (40, 257)
+    lp = signal.lfilter_fir(torch.sin(torch.arange(2048.) * 3.0), signal.firwin(63, 0.1))
+    assert lp[100:].abs().max() < 0.05                     # a tone far above the cut-off is removed
+    t = torch.arange(240.)
+    x = 0.05 * t + torch.sin(2 * math.pi * t / 12)
+    dec = S.seasonal_decompose(x, 12)
+    assert dec.residual[12:-12].abs().max() < 0.05
+    assert (S.ssa(x, 24, 3) - x).abs().mean() < 0.05
+    coef = S.fit_ar(x, 13)
+    assert (S.forecast_ar(x, coef, 3) - (0.05 * torch.arange(240., 243) + torch.sin(2 * math.pi * torch.arange(240., 243) / 12))).abs().max() < 0.05
+    kf = S.KalmanFilter(torch.tensor([[1., 1.], [0., 1.]]), torch.tensor([[1., 0.]]), 1e-4 * torch.eye(2), torch.tensor([[0.1]]))
+    xs = kf.filter((0.5 * t[:60])[:, None])
+    assert abs(xs[-1, 1].item() - 0.5) < 0.02 and kf.smooth().shape == (60, 2)
+    A = torch.randn(20, 20); A = A @ A.T + torch.eye(20)
+    assert torch.allclose(linalg.matrix_sqrt(A) @ linalg.matrix_sqrt(A), A, atol=1e-3)
+    assert torch.allclose(linalg.conjugate_gradient(A, torch.ones(20), 200), torch.linalg.solve(A, torch.ones(20)), atol=1e-3)
+    low = torch.randn(50, 6) @ torch.randn(6, 40)
+    u, sv, vh = linalg.randomized_svd(low, 6)
+    assert torch.allclose((u * sv) @ vh, low, atol=1e-3)
+    w = torch.randn(64, 256)
+    q, qp = Q.quantize_per_channel(w)
+    assert Q.sqnr_db(w, Q.dequantize(q, qp)) > 38
+    q4, sc = Q.quantize_groupwise(w, 128, 4)
+    assert q4.shape == (64, 128) and Q.sqnr_db(w, Q.dequantize_groupwise(q4, sc, 128, 4)) > 15
+    m = torch.nn.Sequential(torch.nn.Linear(256, 64), torch.nn.ReLU(), torch.nn.Linear(64, 8))
+    xi = torch.randn(4, 256)
+    ref = m(xi)
+    import copy
+    assert Q.sqnr_db(ref, Q.quantize_model(copy.deepcopy(m))(xi)) > 35
+    qat = Q.prepare_qat(copy.deepcopy(m))
+    qat(xi).sum().backward()
+
+
+def test_fx_jit_hub_package_tensorboard_cli(tmp_path):
+    import torch.nn.functional as F
+    from torsh_b200 import cli, fx, hub, jit
+    from torsh_b200.utils import tensorboard as tbw
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w, self.b, self.g = torch.nn.Parameter(torch.randn(32, 16)), torch.nn.Parameter(torch.zeros(32)), torch.nn.Parameter(torch.ones(32))
+
+        def forward(self, x, r):
+            h = F.gelu(F.linear(x, self.w, self.b), approximate="tanh")
+            a, b = torch.relu(x), torch.relu(x)
+            _dead = a * 3
+            return F.layer_norm(h + r, (32,), self.g, None, 1e-5) + (a + b).sum()
+    m = M()
+    x, r = torch.randn(4, 16), torch.randn(4, 32)
+    gm = fx.symbolic_trace(m)
+    stats = fx.PassManager.default().run(gm)
+    assert stats["cse"] == 1 and stats["fusion"] == 2 and stats["dce"] >= 1
+    assert torch.allclose(gm(x, r), m(x, r), atol=1e-5)
+    assert "digraph" in fx.to_dot(gm) and len(fx.partition_by_cost(gm, 2)) == 2
+    seq = torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.GELU(approximate="tanh"), torch.nn.Linear(8, 2))
+    c = jit.script(seq)
+    assert c.stats["fusion"] == 1 and torch.allclose(c(torch.ones(3, 8)), seq(torch.ones(3, 8)), atol=1e-6)
+    # hub + package
+    f = tmp_path / "w.bin"; f.write_bytes(b"abc" * 100)
+    reg = hub.LocalHub(tmp_path / "hub")
+    reg.publish("org/model", f)
+    assert reg.list() == ["org/model@v1"] and reg.fetch("org/model").read_bytes() == f.read_bytes()
+    with pytest.raises(ConnectionError):
+        reg.fetch("someone/remote")
+    pkg = hub.Package("demo", "1.2.0", {"torsh": ">=0.1.0"})
+    pkg.add_source("demo.mod", "VALUE = 41 + 1\n"); pkg.add_bytes("data.bin", b"\x00\x01")
+    pkg.save(tmp_path / "demo.tpkg", key=b"k")
+    back = hub.Package.load(tmp_path / "demo.tpkg", key=b"k")
+    assert back.import_module("demo.mod").VALUE == 42 and back.files["data.bin"] == b"\x00\x01"
+    with pytest.raises(PermissionError):
+        hub.Package.load(tmp_path / "demo.tpkg", key=b"wrong")
+    assert hub.resolve_dependencies({"a": "^1.2.0", "b": ">=0.3.0"}, {"a": ["1.1.0", "1.4.2", "2.0.0"], "b": ["0.2.0", "0.9.1"]}) == {"a": "1.4.2", "b": "0.9.1"}
+    # tensorboard
+    with tbw.SummaryWriter(str(tmp_path / "tb")) as w:
+        for i in range(3):
+            w.add_scalar("loss", 1.0 / (i + 1), i)
+        w.add_histogram("w", torch.randn(50), 1); w.add_text("note", "hi")
+    ev = tbw.read_events(w.path)
+    assert [e[0] for e in ev] == [0, 1, 2] and abs(ev[1][2] - 0.5) < 1e-7 and tbw.crc32c(b"123456789") == 0xE3069283
+    # CLI
+    out = tmp_path / "run"
+    assert cli.main(["train", "start", "--model", "gpt2-tiny", "--steps", "3", "--seq", "16", "--batch-size", "2", "--output", str(out), "--device", "cpu"]) == 0
+    assert cli.main(["train", "resume", "--model", "gpt2-tiny", "--steps", "1", "--seq", "16", "--batch-size", "2", "--output", str(out), "--device", "cpu"]) == 0
+    import json
+    assert json.loads((out / "run.json").read_text())["step"] == 4
+    assert cli.main(["model", "create", "--name", "gpt2-tiny", "-o", str(tmp_path / "m.trsm")]) == 0
+    assert cli.main(["model", "convert", str(tmp_path / "m.trsm"), "-o", str(tmp_path / "m.safetensors")]) == 0
+    assert cli.main(["model", "validate", str(tmp_path / "m.safetensors")]) == 0
+    assert cli.main(["info"]) == 0 and cli.main(["init", str(tmp_path / "proj")]) == 0

@@ -1,0 +1,80 @@
+"""Native device runtime on a B200: pools, streams, events, CUDA-graph cache."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_device_info_and_occupancy():
+    from torsh_b200.core import runtime as rt
+    info = rt.device_info()
+    assert info.sm_count >= 100 and info.capability[0] >= 10 and info.tmem_columns == 512
+    assert info.smem_per_block_optin >= 200 * 1024 and info.total_memory > 100 << 30
+    n, lim = rt.occupancy(192, 128, 200 * 1024)
+    assert n == 1 and lim == "shared memory"
+    n, lim = rt.occupancy(256, 32, 0)
+    assert n >= 4
+
+
+def test_device_and_pinned_pool_roundtrip():
+    from torsh_b200.core import runtime as rt
+    pool = rt.DeviceMemoryPool
+    base = pool.stats()
+    buf = pool.alloc(3 << 20)
+    t = buf.tensor((1 << 18,), torch.float32)
+    t.fill_(2.5)
+    assert t.sum().item() == 2.5 * (1 << 18)
+    s1 = pool.stats()
+    assert s1["allocated_bytes"] - base["allocated_bytes"] == 4 << 20
+    p0 = buf.ptr
+    del t
+    buf.free()
+    again = pool.alloc(4 << 20)
+    assert again.ptr == p0 and pool.stats()["cache_hits"] > base["cache_hits"]
+    again.free()
+    assert pool.empty_cache() >= 4 << 20 and pool.pressure() == "low"
+    pin = rt.PinnedBuffer(1 << 20)
+    h = pin.tensor((1 << 18,), torch.float32)
+    h.copy_(torch.arange(1 << 18, dtype=torch.float32))
+    d = torch.empty(1 << 18, device="cuda")
+    pin.copy_to_device_async(d)
+    torch.cuda.synchronize()
+    assert torch.equal(d.cpu(), torch.arange(1 << 18, dtype=torch.float32))
+    pin.free()
+
+
+def test_stream_pool_events_and_graph_cache():
+    from torsh_b200.core import runtime as rt
+    from torsh_b200.ops import elementwise as ew
+    sp = rt.StreamPool(2)
+    hi, lo = sp.get(rt.HIGH), sp.get(rt.LOW)
+    assert sp.priority(hi) <= sp.priority(lo)
+    raws = {sp.get_raw(rt.NORMAL) for _ in range(6)}
+    assert len(raws) == 2                                  # round robin over a pool of two
+    x = torch.randn(1 << 20, device="cuda")
+    y = torch.empty_like(x)
+    e0, e1 = rt.Event(True), rt.Event(True)
+    hi.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(hi):
+        e0.record(hi)
+        ew.unary_raw("relu", x, out=y)
+        e1.record(hi)
+    e1.synchronize()
+    assert e1.query() and e0.elapsed_ms(e1) > 0 and torch.equal(y, torch.relu(x))
+    e0.release(); e1.release()
+    e2 = rt.Event(True)
+    assert rt.Event.pool_stats()["reused"] >= 1
+    e2.release()
+    # capture two of this library's kernels into a cached graph and replay it on new data
+    gc = rt.GraphCache()
+    key = gc.key("relu-then-square", tuple(x.shape))
+    z = torch.empty_like(x)
+    if not gc.has(key):
+        gc.capture(key, lambda: (ew.unary_raw("relu", x, out=y), ew.unary_raw("square", y, out=z)))
+    assert gc.has(key) and gc.node_count(key) == 2
+    x.copy_(torch.randn_like(x))
+    gc.launch(key)
+    torch.cuda.synchronize()
+    assert torch.allclose(z, torch.relu(x) ** 2)
+    assert gc.stats()["entries"] >= 1
+    gc.clear()
