@@ -301,3 +301,110 @@ def test_gnn_scatter_fwd_bwd(dtype):
     dg = A.sum(1)
     want = (dg.rsqrt()[:, None] * A * dg.rsqrt()[None]) @ conv.lin(xf) + conv.bias
     assert _rel(conv(xf, ei), want) < 1e-4
+
+
+# ------------------------------------------------------------------ conv / BatchNorm / pooling (channels-last)
+@pytest.mark.parametrize("geom", [(3, 64, 7, 2, 3, 34), (64, 64, 1, 1, 0, 20), (64, 128, 3, 1, 1, 19), (128, 128, 3, 2, 1, 18),
+                                  (256, 512, 1, 2, 0, 14)])
+def test_conv2d_nhwc_fwd_bwd(geom):
+    from torsh_b200.ops.conv import conv2d_nhwc
+    ci, co, k, stride, pad, hw = geom
+    torch.manual_seed(3)
+    x = torch.randn(4, hw, hw + 3, ci, device=DEV, dtype=torch.bfloat16, requires_grad=ci != 3)
+    w = (torch.randn(co, ci, k, k, device=DEV) * (2.0 / (ci * k * k)) ** 0.5).requires_grad_()
+    y = conv2d_nhwc(x, w, stride, pad)
+    xr = x.detach().float().permute(0, 3, 1, 2).requires_grad_()
+    wr = w.detach().to(torch.bfloat16).float().requires_grad_()
+    ref = torch.nn.functional.conv2d(xr, wr, None, stride, pad)
+    assert y.shape == ref.permute(0, 2, 3, 1).shape and _rel(y, ref.permute(0, 2, 3, 1)) < 1.5e-2
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref.backward(g.float().permute(0, 3, 1, 2))
+    assert _rel(w.grad, wr.grad) < 1.5e-2
+    if ci != 3:
+        assert _rel(x.grad, xr.grad.permute(0, 2, 3, 1)) < 1.5e-2
+
+
+@pytest.mark.parametrize("relu,res", [(False, False), (True, False), (True, True)])
+def test_batch_norm_nhwc_fwd_bwd(relu, res):
+    from torsh_b200.ops.conv import batch_norm_nhwc
+    torch.manual_seed(4)
+    N, H, W, C = 8, 13, 11, 136
+    x = (torch.randn(N, H, W, C, device=DEV) * 2 + 0.5).to(torch.bfloat16).requires_grad_()
+    r = torch.randn(N, H, W, C, device=DEV, dtype=torch.bfloat16).requires_grad_() if res else None
+    bn = torch.nn.BatchNorm2d(C).to(DEV)
+    with torch.no_grad():
+        bn.weight.uniform_(0.5, 1.5); bn.bias.normal_()
+    ref_bn = torch.nn.BatchNorm2d(C).to(DEV)
+    ref_bn.load_state_dict(bn.state_dict())
+    y = batch_norm_nhwc(x, bn, residual=r, relu=relu)
+    xr = x.detach().float().permute(0, 3, 1, 2).requires_grad_()
+    rr = r.detach().float().permute(0, 3, 1, 2).requires_grad_() if res else None
+    z = ref_bn(xr) + (rr if res else 0)
+    ref = torch.relu(z) if relu else z
+    assert _rel(y, ref.permute(0, 2, 3, 1)) < 1e-2
+    assert torch.allclose(bn.running_mean, ref_bn.running_mean, atol=2e-3) and torch.allclose(bn.running_var, ref_bn.running_var, rtol=2e-2)
+    g = torch.randn_like(y)
+    # mask the oracle's gradient with the kernel's own ReLU decision so rounding at the kink does not count
+    y.backward(g)
+    gm = g.float() * ((y.detach() > 0) if relu else 1)
+    z.backward(gm.permute(0, 3, 1, 2))
+    assert _rel(x.grad, xr.grad.permute(0, 2, 3, 1)) < 2e-2
+    assert _rel(bn.weight.grad, ref_bn.weight.grad) < 2e-2 and _rel(bn.bias.grad, ref_bn.bias.grad) < 2e-2
+    if res:
+        assert _rel(r.grad, rr.grad.permute(0, 2, 3, 1)) < 1e-2
+    bn.eval(); ref_bn.eval()
+    assert _rel(batch_norm_nhwc(x.detach(), bn, relu=relu), (torch.relu(ref_bn(xr)) if relu else ref_bn(xr)).permute(0, 2, 3, 1)) < 1e-2
+
+
+def test_pooling_nhwc():
+    from torsh_b200.ops.conv import global_avg_pool_nhwc, max_pool_nhwc
+    torch.manual_seed(5)
+    x = torch.relu(torch.randn(4, 17, 15, 64, device=DEV)).to(torch.bfloat16).requires_grad_()   # many ties at zero
+    y = max_pool_nhwc(x, 3, 2, 1)
+    xr = x.detach().float().permute(0, 3, 1, 2).requires_grad_()
+    ref = torch.nn.functional.max_pool2d(xr, 3, 2, 1)
+    assert torch.equal(y.float(), ref.permute(0, 2, 3, 1))
+    g = torch.randn_like(y)
+    y.backward(g)
+    ref.backward(g.float().permute(0, 3, 1, 2))
+    assert _rel(x.grad, xr.grad.permute(0, 2, 3, 1)) < 1e-2
+    x2 = torch.randn(6, 7, 7, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    a = global_avg_pool_nhwc(x2)
+    assert _rel(a, x2.detach().float().mean((1, 2))) < 1e-2
+    a.backward(torch.ones_like(a))
+    assert _rel(x2.grad, torch.full_like(x2, 1 / 49)) < 1e-2
+
+
+def test_resnet_kernel_path_matches_torch_layers():
+    """Oracle: the fp32 PyTorch layers. A random-init BatchNorm network amplifies bf16 rounding, so the yardstick for
+    "close enough" is PyTorch's own bf16 autocast run of the same model: the kernel path must track fp32 as well as
+    that does (gradient direction per parameter), and exactly at the head."""
+    from torsh_b200.models import ResNet, ResNetConfig
+    torch.manual_seed(6)
+    m = ResNet(ResNetConfig(layers=(1, 1, 1, 1), num_classes=16)).to(DEV)
+    x = torch.randn(16, 3, 96, 96, device=DEV)
+    tgt = torch.randint(0, 16, (16,), device=DEV)
+
+    def run(mode):
+        m.zero_grad()
+        for b in m.modules():
+            if isinstance(b, torch.nn.BatchNorm2d):
+                b.reset_running_stats()
+        m.use_kernels = mode == "kernel"
+        if mode == "autocast":
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = torch.nn.functional.cross_entropy(m(x).float(), tgt)
+        else:
+            loss = torch.nn.functional.cross_entropy(m(x), tgt)
+        loss.backward()
+        return loss.item(), {n: p.grad.clone().float() for n, p in m.named_parameters()}
+
+    cos = lambda a, b: torch.nn.functional.cosine_similarity(a.flatten(), b.flatten(), dim=0).item()
+    lk, gk = run("kernel")
+    lf, gf = run("fp32")
+    _, ga = run("autocast")
+    assert abs(lk - lf) < 0.02 * abs(lf) + 0.02
+    bad = {n: (round(cos(gk[n], gf[n]), 3), round(cos(ga[n], gf[n]), 3)) for n in gk if cos(gk[n], gf[n]) < cos(ga[n], gf[n]) - 0.04}
+    assert not bad, bad
+    assert cos(gk["fc.weight"], gf["fc.weight"]) > 0.999 and cos(gk["layer4.0.bn3.weight"], gf["layer4.0.bn3.weight"]) > 0.99

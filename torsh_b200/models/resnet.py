@@ -4,6 +4,11 @@ torchvision-v1 layout as in the reference: 7Ã—7/2 conv (pad 3, no bias) â†’ BN â
 stages (``[3,4,6,3]`` bottlenecks for ResNet-50; 1Ã—1 conv + BN down-sample when the stride or the channel count
 changes) â†’ adaptive average pool â†’ ``Linear(2048, classes)``; options: SE blocks, dropout, ResNeXt ``groups`` /
 ``width_per_group``. Convolutions use Kaiming-normal (fan-out) init and run in channels-last.
+
+On a GPU (plain ResNets: no groups, no SE) the forward pass runs channels-last bf16 end to end on the sm_100a kernels of
+``torsh_b200.ops.conv``: every convolution is a tcgen05 GEMM, BatchNorm + ReLU (+ the residual add that closes a block)
+is one fused pass, and parameters stay fp32 (bf16 autocast recipe).  ``model.use_kernels = False`` keeps PyTorch's
+layers.
 """
 from __future__ import annotations
 
@@ -12,6 +17,7 @@ from dataclasses import dataclass, field
 import torch
 
 from .. import nn
+from ..ops import conv as cv
 
 
 @dataclass
@@ -73,6 +79,11 @@ class BasicBlock(nn.Module):
             out = self.se(out)
         return torch.relu(out + idt)
 
+    def forward_nhwc(self, x):
+        idt = x if self.downsample is None else _down_nhwc(self.downsample, x)
+        out = cv.batch_norm_nhwc(_conv_nhwc(self.conv1, x), self.bn1, relu=True)
+        return cv.batch_norm_nhwc(_conv_nhwc(self.conv2, out), self.bn2, residual=idt, relu=True)
+
 
 class BottleneckBlock(nn.Module):
     expansion = 4
@@ -97,6 +108,20 @@ class BottleneckBlock(nn.Module):
         if self.se is not None:
             out = self.se(out)
         return torch.relu(out + idt)
+
+    def forward_nhwc(self, x):
+        idt = x if self.downsample is None else _down_nhwc(self.downsample, x)
+        out = cv.batch_norm_nhwc(_conv_nhwc(self.conv1, x), self.bn1, relu=True)
+        out = cv.batch_norm_nhwc(_conv_nhwc(self.conv2, out), self.bn2, relu=True)
+        return cv.batch_norm_nhwc(_conv_nhwc(self.conv3, out), self.bn3, residual=idt, relu=True)
+
+
+def _conv_nhwc(conv: torch.nn.Conv2d, x):
+    return cv.conv2d_nhwc(x, conv.weight, conv.stride[0], conv.padding[0])
+
+
+def _down_nhwc(seq, x):
+    return cv.batch_norm_nhwc(_conv_nhwc(seq[0], x), seq[1])
 
 
 class ResNet(nn.Module):
@@ -144,7 +169,29 @@ class ResNet(nn.Module):
         x = self.maxpool(torch.relu(self.bn1(self.conv1(x))))
         return self.layer4(self.layer3(self.layer2(self.layer1(x))))
 
+    use_kernels = True
+
+    def _kernel_path(self, x) -> bool:
+        return (self.use_kernels and x.is_cuda and self.config.groups == 1 and not self.config.use_se
+                and self.config.width_per_group % 8 == 0)
+
+    def forward_nhwc(self, x):
+        """Channels-last bf16 pass; ``x`` is ``[N, 3, H, W]`` (any float dtype).  Returns fp32 logits."""
+        from ..ops.linear import linear
+        x = x.permute(0, 2, 3, 1).to(torch.bfloat16).contiguous()
+        x = cv.batch_norm_nhwc(_conv_nhwc(self.conv1, x), self.bn1, relu=True)
+        x = cv.max_pool_nhwc(x, 3, 2, 1)
+        for stage in (self.layer1, self.layer2, self.layer3, self.layer4):
+            for blk in stage:
+                x = blk.forward_nhwc(x)
+        x = cv.global_avg_pool_nhwc(x)
+        if self.dropout is not None:
+            x = self.dropout(x)
+        return linear(x, self.fc.weight.to(torch.bfloat16), self.fc.bias.to(torch.bfloat16)).float()
+
     def forward(self, x):
+        if self._kernel_path(x):
+            return self.forward_nhwc(x)
         x = torch.flatten(self.avgpool(self.forward_features(x)), 1)
         if self.dropout is not None:
             x = self.dropout(x)

@@ -44,7 +44,7 @@ def fn(name: str, argtypes):
     return f
 
 
-_KERNELS_PER_CALL = {"tb_flash_attn_bwd": 3, "tb_lamb_multi": 2}
+_KERNELS_PER_CALL = {"tb_flash_attn_bwd": 3, "tb_lamb_multi": 2, "tb_bn_fwd": 3, "tb_bn_bwd": 3}
 
 
 def call(name: str, argtypes, *args):
