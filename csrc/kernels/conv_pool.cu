@@ -7,6 +7,8 @@
 // reduce + one apply pass backward. The reference runs these layers through host loops or cuDNN calls
 // (crates/torsh-backend/src/cuda/cudnn/operations.rs:99-1319; crates/torsh-nn/src/layers/normalization.rs) and its
 // own conv2d / batchnorm2d / maxpool2d launchers are empty (crates/torsh-backend/src/cuda/kernels/mod.rs:20-330).
+#include <type_traits>
+
 #include "common.cuh"
 #include "host_util.h"
 
@@ -18,25 +20,35 @@ struct ConvGeom {
 };
 
 // cols[m, (kh*KW + kw)*C + c] = x[n, ho*stride - pad + kh, wo*stride - pad + kw, c], zero outside the image.
-// One thread moves 16 bytes (8 channels) when C % 8 == 0.
+// One thread moves V channels: 16 bytes when C % 8 == 0, 8 bytes when C % 4 == 0 (the stem with its 3 input
+// channels padded to 4). Columns between KH*KW*C and the row pitch are zero-filled by the last tap's threads.
+template <int V>
 __global__ void im2col_vec_kernel(const bf16* __restrict__ x, bf16* __restrict__ cols, ConvGeom g) {
-  const int c8 = g.C >> 3;
-  const long per_row = (long)g.KH * g.KW * c8;
+  typedef typename std::conditional<V == 8, uint4, uint2>::type vec_t;
+  const int cv = g.C / V;
+  const int K = g.KH * g.KW * g.C;
+  const int tail = (int)(g.ld - K) / V;  // zero vectors after the last tap
+  const long per_row = (long)g.KH * g.KW * cv + tail;
   const long total = (long)g.N * g.Ho * g.Wo * per_row;
   const long stride = (long)gridDim.x * blockDim.x;
   for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
     const long m = idx / per_row;
     int r = (int)(idx - m * per_row);
-    const int tap = r / c8, c = (r - tap * c8) << 3;
+    vec_t v;
+    memset(&v, 0, sizeof(v));
+    if (r >= g.KH * g.KW * cv) {
+      *reinterpret_cast<vec_t*>(cols + m * g.ld + K + (long)(r - g.KH * g.KW * cv) * V) = v;
+      continue;
+    }
+    const int tap = r / cv, c = (r - tap * cv) * V;
     const int kh = tap / g.KW, kw = tap - kh * g.KW;
     const int wo = (int)(m % g.Wo);
     const long t = m / g.Wo;
     const int ho = (int)(t % g.Ho), n = (int)(t / g.Ho);
     const int h = ho * g.stride - g.pad + kh, w = wo * g.stride - g.pad + kw;
-    uint4 v = make_uint4(0, 0, 0, 0);
     if (h >= 0 && h < g.H && w >= 0 && w < g.W)
-      v = __ldg(reinterpret_cast<const uint4*>(x + (((long)n * g.H + h) * g.W + w) * g.C + c));
-    *reinterpret_cast<uint4*>(cols + m * g.ld + (long)tap * g.C + c) = v;
+      v = __ldg(reinterpret_cast<const vec_t*>(x + (((long)n * g.H + h) * g.W + w) * g.C + c));
+    *reinterpret_cast<vec_t*>(cols + m * g.ld + (long)tap * g.C + c) = v;
   }
 }
 // Any C (the 3-channel stem): one thread per column-matrix element, pad columns written as zero.
@@ -293,6 +305,201 @@ __global__ void bn_param_grad_kernel(const float* __restrict__ sums, float* __re
   dgamma[c] += sums[C + c];
 }
 
+// ---- fast BatchNorm forms for C/8 a power of two <= 256 (every ResNet width): a thread keeps one group of 8
+// channels for its whole life, so the per-channel constants sit in registers and a row costs one 16-byte load per
+// operand; 256 / (C/8) rows are in flight per block iteration and there is no integer division in the loop.
+struct BnMap {
+  int cv, r_in, rpb;  // channel-vector index, row inside the block's row group, rows per block iteration
+};
+__device__ __forceinline__ BnMap bn_map(int c8) {
+  BnMap m;
+  m.cv = threadIdx.x & (c8 - 1);
+  m.r_in = threadIdx.x / c8;
+  m.rpb = blockDim.x / c8;
+  return m;
+}
+// Sum the per-thread partials of threads that share a channel group and add them to sums[] with one atomic per
+// channel per block. part: shared [2][256][9] floats.
+__device__ __forceinline__ void bn_block_reduce(float (&s)[8], float (&q)[8], float* part, float* sums, int C, int c8,
+                                                const BnMap& m) {
+  float* p0 = part;
+  float* p1 = part + 256 * 9;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    p0[threadIdx.x * 9 + j] = s[j];
+    p1[threadIdx.x * 9 + j] = q[j];
+  }
+  __syncthreads();
+  // thread t < 2*C handles (which = t / C, channel = t % C); loops when 2*C > blockDim
+  for (int t = threadIdx.x; t < 2 * C; t += blockDim.x) {
+    const int which = t / C, ch = t - which * C;
+    const int cv = ch >> 3, j = ch & 7;
+    const float* src = which ? p1 : p0;
+    float a = 0.f;
+    for (int r = 0; r < m.rpb; ++r) a += src[(r * c8 + cv) * 9 + j];
+    atomicAdd(sums + which * C + ch, a);
+  }
+}
+__global__ void __launch_bounds__(256) bn_stats_fast_kernel(const bf16* __restrict__ x, float* __restrict__ sums,
+                                                            long rows, int C) {
+  __shared__ float part[2 * 256 * 9];
+  const int c8 = C >> 3;
+  const BnMap m = bn_map(c8);
+  float s[8], q[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s[j] = q[j] = 0.f;
+  const bf16* xp = x + (long)m.cv * 8;
+  for (long r = (long)blockIdx.x * m.rpb + m.r_in; r < rows; r += (long)gridDim.x * m.rpb) {
+    Vec16<bf16> v;
+    v.load_nc(xp + r * C);
+    float f[8];
+    v.get(f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      s[j] += f[j];
+      q[j] += f[j] * f[j];
+    }
+  }
+  bn_block_reduce(s, q, part, sums, C, c8, m);
+}
+__global__ void __launch_bounds__(256) bn_apply_fast_kernel(const bf16* __restrict__ x, const bf16* __restrict__ res,
+                                                            bf16* __restrict__ y, const float* __restrict__ mean,
+                                                            const float* __restrict__ rstd,
+                                                            const float* __restrict__ gamma,
+                                                            const float* __restrict__ beta, long rows, int C,
+                                                            int relu) {
+  const int c8 = C >> 3;
+  const BnMap m = bn_map(c8);
+  float sc[8], sh[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = m.cv * 8 + j;
+    sc[j] = rstd[c] * gamma[c];
+    sh[j] = beta[c] - mean[c] * sc[j];
+  }
+  const long off = (long)m.cv * 8;
+  for (long r = (long)blockIdx.x * m.rpb + m.r_in; r < rows; r += (long)gridDim.x * m.rpb) {
+    Vec16<bf16> v;
+    v.load_nc(x + r * C + off);
+    float f[8];
+    v.get(f);
+    if (res) {
+      Vec16<bf16> rv;
+      rv.load_nc(res + r * C + off);
+      float rr[8];
+      rv.get(rr);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = fmaf(f[j], sc[j], sh[j]) + rr[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = fmaf(f[j], sc[j], sh[j]);
+    }
+    if (relu) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+    }
+    v.set(f);
+    v.store(y + r * C + off);
+  }
+}
+__global__ void __launch_bounds__(256) bn_bwd_reduce_fast_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y,
+                                                                 const bf16* __restrict__ x,
+                                                                 const float* __restrict__ mean,
+                                                                 const float* __restrict__ rstd,
+                                                                 float* __restrict__ sums, long rows, int C, int relu) {
+  __shared__ float part[2 * 256 * 9];
+  const int c8 = C >> 3;
+  const BnMap m = bn_map(c8);
+  float s[8], q[8], mu[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    s[j] = q[j] = 0.f;
+    mu[j] = mean[m.cv * 8 + j];
+  }
+  const long off = (long)m.cv * 8;
+  for (long r = (long)blockIdx.x * m.rpb + m.r_in; r < rows; r += (long)gridDim.x * m.rpb) {
+    Vec16<bf16> vg, vx;
+    vg.load_nc(dy + r * C + off);
+    vx.load_nc(x + r * C + off);
+    float g[8], xf[8];
+    vg.get(g);
+    vx.get(xf);
+    if (relu) {
+      Vec16<bf16> vy;
+      vy.load_nc(y + r * C + off);
+      float yf[8];
+      vy.get(yf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (yf[j] <= 0.f) g[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      s[j] += g[j];
+      q[j] = fmaf(g[j], xf[j] - mu[j], q[j]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) q[j] *= rstd[m.cv * 8 + j];
+  bn_block_reduce(s, q, part, sums, C, c8, m);
+}
+__global__ void __launch_bounds__(256) bn_bwd_apply_fast_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y,
+                                                                const bf16* __restrict__ x,
+                                                                const float* __restrict__ mean,
+                                                                const float* __restrict__ rstd,
+                                                                const float* __restrict__ gamma,
+                                                                const float* __restrict__ sums, bf16* __restrict__ dx,
+                                                                bf16* __restrict__ dres, long rows, int C, int relu) {
+  const int c8 = C >> 3;
+  const BnMap m = bn_map(c8);
+  // dx = a * g + b * x + d with a = gamma*rstd, b = -a * rstd * sum_gx / rows, d = -a * sum_g / rows - b * mean
+  float a[8], b[8], d[8];
+  const float inv = 1.f / (float)rows;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int c = m.cv * 8 + j;
+    a[j] = gamma[c] * rstd[c];
+    b[j] = -a[j] * rstd[c] * sums[C + c] * inv;
+    d[j] = -a[j] * sums[c] * inv - b[j] * mean[c];
+  }
+  const long off = (long)m.cv * 8;
+  for (long r = (long)blockIdx.x * m.rpb + m.r_in; r < rows; r += (long)gridDim.x * m.rpb) {
+    Vec16<bf16> vg, vx;
+    vg.load_nc(dy + r * C + off);
+    vx.load_nc(x + r * C + off);
+    float g[8], xf[8];
+    vg.get(g);
+    vx.get(xf);
+    if (relu) {
+      Vec16<bf16> vy;
+      vy.load_nc(y + r * C + off);
+      float yf[8];
+      vy.get(yf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (yf[j] <= 0.f) g[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) xf[j] = fmaf(a[j], g[j], fmaf(b[j], xf[j], d[j]));
+    vx.set(xf);
+    vx.store(dx + r * C + off);
+    if (dres) {
+      vg.set(g);
+      vg.store(dres + r * C + off);
+    }
+  }
+}
+static inline bool bn_fast_ok(int C) {
+  const int c8 = C >> 3;
+  return (C & 7) == 0 && c8 >= 1 && c8 <= 256 && (c8 & (c8 - 1)) == 0;
+}
+static inline int bn_fast_grid(long rows, int C) {
+  const long rpb = 256 / (C >> 3);
+  long blocks = (rows + rpb - 1) / rpb;
+  const long cap = (long)sm_count() * 8;
+  return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
 // ------------------------------------------------------------------------------------------------ pooling
 // Max pooling k x k / stride / pad over NHWC; idx records which tap won (first maximum in row-major tap order, the
 // choice torch makes), so the backward pass is an exact gather.
@@ -441,8 +648,11 @@ TB_EXPORT int tb_im2col_nhwc(const void* x, void* cols, int N, int H, int W, int
   if (g.Ho <= 0 || g.Wo <= 0) TB_FAIL(TB_E_ARG, "im2col: empty output");
   if (ld < (long)KH * KW * C || (ld & 7)) TB_FAIL(TB_E_ARG, "im2col: row pitch %ld too small or not a multiple of 8", ld);
   const long rows = (long)N * g.Ho * g.Wo;
-  if ((C & 7) == 0 && al16(x) && al16(cols) && ld == (long)KH * KW * C) {
-    im2col_vec_kernel<<<grid_1d(rows * KH * KW * (C >> 3)), 256, 0, st>>>((const bf16*)x, (bf16*)cols, g);
+  const long K = (long)KH * KW * C;
+  if ((C & 7) == 0 && al16(x) && al16(cols) && ((ld - K) & 7) == 0) {
+    im2col_vec_kernel<8><<<grid_1d(rows * (KH * KW * (C >> 3) + (ld - K) / 8)), 256, 0, st>>>((const bf16*)x, (bf16*)cols, g);
+  } else if ((C & 3) == 0 && al16(x) && al16(cols) && ((ld - K) & 3) == 0) {
+    im2col_vec_kernel<4><<<grid_1d(rows * (KH * KW * (C >> 2) + (ld - K) / 4)), 256, 0, st>>>((const bf16*)x, (bf16*)cols, g);
   } else {
     im2col_scalar_kernel<<<grid_1d(rows * ld), 256, 0, st>>>((const bf16*)x, (bf16*)cols, g);
   }
@@ -476,12 +686,19 @@ TB_EXPORT int tb_bn_fwd(const void* x, const void* res, void* y, float* sums, fl
   if (rows <= 0 || C <= 0) return 0;
   if ((C & 7) || !al16(x) || !al16(y) || (res && !al16(res))) TB_FAIL(TB_E_ARG, "bn_fwd: C %% 8 and 16-byte alignment required");
   TB_CUDA_CHECK(cudaMemsetAsync(sums, 0, sizeof(float) * 2 * C, st));
-  dim3 grid;
-  int rpb;
-  bn_grid(rows, C, &grid, &rpb);
-  bn_stats_kernel<<<grid, dim3(32, 8), 0, st>>>((const bf16*)x, sums, rows, C, rpb);
-  bn_finalize_kernel<<<(C + 255) / 256, 256, 0, st>>>(sums, mean, rstd, run_mean, run_var, rows, C, eps, momentum);
-  bn_apply_kernel<<<grid_1d(rows * (C >> 3)), 256, 0, st>>>((const bf16*)x, (const bf16*)res, (bf16*)y, mean, rstd, gamma, beta, rows, C, relu);
+  if (bn_fast_ok(C)) {
+    const int g = bn_fast_grid(rows, C);
+    bn_stats_fast_kernel<<<g, 256, 0, st>>>((const bf16*)x, sums, rows, C);
+    bn_finalize_kernel<<<(C + 255) / 256, 256, 0, st>>>(sums, mean, rstd, run_mean, run_var, rows, C, eps, momentum);
+    bn_apply_fast_kernel<<<g, 256, 0, st>>>((const bf16*)x, (const bf16*)res, (bf16*)y, mean, rstd, gamma, beta, rows, C, relu);
+  } else {
+    dim3 grid;
+    int rpb;
+    bn_grid(rows, C, &grid, &rpb);
+    bn_stats_kernel<<<grid, dim3(32, 8), 0, st>>>((const bf16*)x, sums, rows, C, rpb);
+    bn_finalize_kernel<<<(C + 255) / 256, 256, 0, st>>>(sums, mean, rstd, run_mean, run_var, rows, C, eps, momentum);
+    bn_apply_kernel<<<grid_1d(rows * (C >> 3)), 256, 0, st>>>((const bf16*)x, (const bf16*)res, (bf16*)y, mean, rstd, gamma, beta, rows, C, relu);
+  }
   TB_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
@@ -491,7 +708,10 @@ TB_EXPORT int tb_bn_apply(const void* x, const void* res, void* y, const float* 
   TB_ENSURE_DEVICE();
   if (rows <= 0) return 0;
   if ((C & 7) || !al16(x) || !al16(y) || (res && !al16(res))) TB_FAIL(TB_E_ARG, "bn_apply: C %% 8 and 16-byte alignment required");
-  bn_apply_kernel<<<grid_1d(rows * (C >> 3)), 256, 0, st>>>((const bf16*)x, (const bf16*)res, (bf16*)y, mean, rstd, gamma, beta, rows, C, relu);
+  if (bn_fast_ok(C))
+    bn_apply_fast_kernel<<<bn_fast_grid(rows, C), 256, 0, st>>>((const bf16*)x, (const bf16*)res, (bf16*)y, mean, rstd, gamma, beta, rows, C, relu);
+  else
+    bn_apply_kernel<<<grid_1d(rows * (C >> 3)), 256, 0, st>>>((const bf16*)x, (const bf16*)res, (bf16*)y, mean, rstd, gamma, beta, rows, C, relu);
   TB_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
@@ -504,11 +724,17 @@ TB_EXPORT int tb_bn_bwd(const void* dy, const void* y, const void* x, const floa
   if ((C & 7) || !al16(dy) || !al16(x) || !al16(dx) || (relu && !al16(y)) || (dres && !al16(dres)))
     TB_FAIL(TB_E_ARG, "bn_bwd: C %% 8 and 16-byte alignment required");
   TB_CUDA_CHECK(cudaMemsetAsync(sums, 0, sizeof(float) * 2 * C, st));
-  dim3 grid;
-  int rpb;
-  bn_grid(rows, C, &grid, &rpb);
-  bn_bwd_reduce_kernel<<<grid, dim3(32, 8), 0, st>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, mean, rstd, sums, rows, C, relu, rpb);
-  bn_bwd_apply_kernel<<<grid_1d(rows * (C >> 3)), 256, 0, st>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, mean, rstd, gamma, sums, (bf16*)dx, (bf16*)dres, rows, C, relu);
+  if (bn_fast_ok(C)) {
+    const int g = bn_fast_grid(rows, C);
+    bn_bwd_reduce_fast_kernel<<<g, 256, 0, st>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, mean, rstd, sums, rows, C, relu);
+    bn_bwd_apply_fast_kernel<<<g, 256, 0, st>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, mean, rstd, gamma, sums, (bf16*)dx, (bf16*)dres, rows, C, relu);
+  } else {
+    dim3 grid;
+    int rpb;
+    bn_grid(rows, C, &grid, &rpb);
+    bn_bwd_reduce_kernel<<<grid, dim3(32, 8), 0, st>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, mean, rstd, sums, rows, C, relu, rpb);
+    bn_bwd_apply_kernel<<<grid_1d(rows * (C >> 3)), 256, 0, st>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, mean, rstd, gamma, sums, (bf16*)dx, (bf16*)dres, rows, C, relu);
+  }
   bn_param_grad_kernel<<<(C + 255) / 256, 256, 0, st>>>(sums, dgamma, dbeta, C);
   TB_CUDA_CHECK(cudaGetLastError());
   return 0;

@@ -99,6 +99,11 @@ def conv2d_nhwc(x: torch.Tensor, weight: torch.Tensor, stride: int = 1, padding:
     """``x``: ``[N, H, W, Ci]`` bf16; ``weight``: ``[Co, Ci, KH, KW]`` (any float dtype / memory format); no bias,
     no groups, no dilation.  Returns ``[N, Ho, Wo, Co]`` bf16."""
     if kernel_ok(x) and x.dtype == torch.bfloat16 and weight.shape[0] % 8 == 0:
+        if x.shape[-1] % 4:
+            # odd channel counts (the 3-channel stem): pad to a multiple of 4 so im2col moves 8-byte vectors
+            extra = 4 - x.shape[-1] % 4
+            x = torch.nn.functional.pad(x, (0, extra))
+            weight = torch.nn.functional.pad(weight, (0, 0, 0, 0, 0, extra))
         return _Conv2dFn.apply(x.contiguous(), weight, stride, padding)
     y = torch.nn.functional.conv2d(x.permute(0, 3, 1, 2).to(weight.dtype), weight, None, stride, padding)
     return y.permute(0, 2, 3, 1).to(x.dtype)
