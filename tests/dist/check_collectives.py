@@ -209,6 +209,44 @@ def check_tp(dev):
     return ok
 
 
+def check_ddp(dev):
+    """Fused bucket all-reduce (x 1/world) launched from autograd hooks: every rank's gradients must equal the
+    average, over ranks, of the gradients a plain copy of the model produces on each rank's own batch."""
+    from torsh_b200 import _native as nv
+    from torsh_b200.parallel.ddp import DistributedDataParallel
+    rank, world = dist.get_rank(), dist.get_world_size()
+    torch.manual_seed(7)
+    make = lambda: torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.GELU(), torch.nn.Linear(512, 512), torch.nn.GELU(),
+                                       torch.nn.Linear(512, 64)).to(dev)
+    model, ref = make(), make()
+    ref.load_state_dict(model.state_dict())
+    ddp = DistributedDataParallel(model, bucket_cap_mb=0.6)          # several buckets
+    ok = len(ddp.buckets) >= 2
+    for step in range(3):
+        torch.manual_seed(100 + step)
+        xs = torch.randn(world, 32, 256, device=dev)
+        ys = torch.randn(world, 32, 64, device=dev)
+        loss = torch.nn.functional.mse_loss(ddp(xs[rank]), ys[rank])
+        loss.backward()
+        ddp.sync_gradients()
+        ref.zero_grad()
+        for r in range(world):
+            (torch.nn.functional.mse_loss(ref(xs[r]), ys[r]) / world).backward()
+        for (n, p), q in zip(model.named_parameters(), ref.parameters()):
+            err = (p.grad - q.grad).abs().max().item() / (q.grad.abs().max().item() + 1e-12)
+            if err > 1e-4:
+                ok = False
+                log(f"ddp step {step} {n}: rel err {err:.2e}")
+        with torch.no_grad():
+            for p, q in zip(model.parameters(), ref.parameters()):
+                p.add_(p.grad, alpha=-0.1)
+                q.add_(q.grad, alpha=-0.1)
+        ddp.zero_grad()
+    nv.check_status()
+    log(f"ddp: {len(ddp.buckets)} buckets, stats {ddp.get_sync_stats()} -> {'ok' if ok else 'FAILED'}")
+    return ok
+
+
 def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -222,6 +260,8 @@ def main():
         ok &= check_fsdp(dev)
     if "tp" in what:
         ok &= check_tp(dev)
+    if "ddp" in what:
+        ok &= check_ddp(dev)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     log("ALL CHECKS PASSED" if flag.item() == 1 else "CHECKS FAILED")
