@@ -119,6 +119,14 @@ class LlamaModel(nn.Module):
             w[: cfg.vocab_size].normal_(0.0, cfg.initializer_range)
             self.lm_head = nn.Parameter(w)
 
+    def replicated_parameters(self):
+        """Parameters every tensor-parallel rank holds in full but feeds with its own token shard (norm weights, the
+        embedding): their gradients are partial sums and must be all-reduced over the TP group."""
+        out = [p for n, p in self.named_parameters() if "norm" in n]
+        if self.first_stage:
+            out.append(self.embed)
+        return out
+
     def _shard_tokens(self, x):
         if self.tp is None or self.tp.world == 1:
             return x
@@ -136,6 +144,10 @@ class LlamaModel(nn.Module):
             x = blk(x, B, S)
         if not self.last_stage:
             return x
+        return self.head(x, B, S, targets)
+
+    def head(self, x, B: int, S: int, targets: torch.Tensor | None = None):
+        """Final norm + LM head (+ fused cross-entropy when ``targets`` is given) on the last stage's hidden states."""
         h = norm_ops.rms_norm(x, self.norm.weight, self.cfg.rms_eps)
         if self.tp is not None and self.tp.world > 1:
             from ..parallel.tensor_parallel import _AllGatherRows

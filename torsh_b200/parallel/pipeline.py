@@ -51,6 +51,9 @@ class PipelineParallel:
         self.act_shape, self.act_dtype = activation_shape, activation_dtype
         self.device = next(stage_module.parameters()).device
         self.stats = {"sends": 0, "recvs": 0, "bubbles": 0}
+        # called as hook(micro_batch_index, in_flight_slot) before each forward: lets layers that keep per-micro-batch
+        # buffers (the fused tensor-parallel layers) switch to the slot of this micro-batch
+        self.micro_batch_hook = None
 
     @property
     def is_first(self):
@@ -104,6 +107,8 @@ class PipelineParallel:
                     x = xs[mb]
                 else:
                     x = self._exchange(pending, self.prev, self.cfg.base_tag + mb).requires_grad_(True)
+                if self.micro_batch_hook is not None:
+                    self.micro_batch_hook(mb, mb % max(self.num_stages, 1))
                 out = self.module(x)
                 if self.is_last:
                     loss = loss_fn(out, ys[mb]) / M if loss_fn is not None else out.mean() / M

@@ -45,6 +45,7 @@ class TensorParallelConfig:
     async_communication: bool = True
     copy_ctas: int = 16
     rs_fp32: bool = False  # accumulate the reduce-scatter in fp32 (2x the NVLink bytes of bf16)
+    fused: bool = True     # False: NCCL collectives + library GEMMs (the comparison arm of the benchmarks)
 
 
 class TPContext:
@@ -55,7 +56,10 @@ class TPContext:
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
         self.cfg = config or TensorParallelConfig(tp_size=self.world)
-        self.ctx = CommContext(self.group)
+        self.ctx = CommContext(self.group) if (self.cfg.fused and self.world > 1) else None
+        # Pipeline schedules keep several micro-batches in flight; a column-parallel layer saves its gathered input
+        # (a view of a staging buffer) for the weight gradient, so each in-flight micro-batch needs its own buffer.
+        self.slot = 0
         self._bufs: dict = {}
         self._ready: dict = {}
 
@@ -113,13 +117,13 @@ def _gemm_rs(tpc: TPContext, tag: str, x: torch.Tensor, w: torch.Tensor, b_major
 
 
 def _fused_ok(tpc, *ts):
-    return tpc is not None and tpc.world > 1 and all(t is None or (t.is_cuda and t.dtype == torch.bfloat16) for t in ts)
+    return tpc is not None and tpc.world > 1 and tpc.cfg.fused and all(t is None or (t.is_cuda and t.dtype == torch.bfloat16) for t in ts)
 
 
 class _ColumnParallelSP(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x_shard, weight, bias, tpc, tag, gelu):
-        y, x_full = _ag_gemm(tpc, tag + ".fwd", x_shard.contiguous(), weight, 0, bias, gelu)
+        y, x_full = _ag_gemm(tpc, f"{tag}.fwd.s{tpc.slot}", x_shard.contiguous(), weight, 0, bias, gelu)
         assert not gelu, "use the un-fused activation with column-parallel layers that need a backward"
         ctx.save_for_backward(x_full, weight)
         ctx.tpc, ctx.tag, ctx.bias = tpc, tag, bias
@@ -155,38 +159,50 @@ class _RowParallelSP(torch.autograd.Function):
 
 
 # ---- reference algebra with torch.distributed collectives (CPU path and oracle) --------------------------
+def _all_gather_rows(x, group):
+    w = dist.get_world_size(group)
+    x = x.contiguous()
+    if x.is_cuda:
+        out = torch.empty(w * x.shape[0], *x.shape[1:], dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, x, group=group)
+        return out
+    outs = [torch.empty_like(x) for _ in range(w)]
+    dist.all_gather(outs, x, group=group)
+    return torch.cat(outs, 0)
+
+
+def _reduce_scatter_rows(x, group):
+    w, r = dist.get_world_size(group), dist.get_rank(group)
+    rows = x.shape[0] // w
+    if x.is_cuda:
+        out = torch.empty(rows, *x.shape[1:], dtype=x.dtype, device=x.device)
+        dist.reduce_scatter_tensor(out, x.contiguous(), group=group)
+        return out
+    x = x.contiguous().clone()          # gloo has no reduce-scatter
+    dist.all_reduce(x, group=group)
+    return x[r * rows:(r + 1) * rows].clone()
+
+
 class _AllGatherRows(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
         ctx.group = group
-        outs = [torch.empty_like(x) for _ in range(dist.get_world_size(group))]
-        dist.all_gather(outs, x.contiguous(), group=group)
-        return torch.cat(outs, 0)
+        return _all_gather_rows(x, group)
 
     @staticmethod
     def backward(ctx, dy):
-        w, r = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
-        dy = dy.contiguous().clone()
-        dist.all_reduce(dy, group=ctx.group)
-        rows = dy.shape[0] // w
-        return dy[r * rows:(r + 1) * rows], None
+        return _reduce_scatter_rows(dy, ctx.group), None
 
 
 class _ReduceScatterRows(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
         ctx.group = group
-        w, r = dist.get_world_size(group), dist.get_rank(group)
-        x = x.contiguous().clone()
-        dist.all_reduce(x, group=group)
-        rows = x.shape[0] // w
-        return x[r * rows:(r + 1) * rows].clone()
+        return _reduce_scatter_rows(x, group)
 
     @staticmethod
     def backward(ctx, dy):
-        outs = [torch.empty_like(dy) for _ in range(dist.get_world_size(ctx.group))]
-        dist.all_gather(outs, dy.contiguous(), group=ctx.group)
-        return torch.cat(outs, 0), None
+        return _all_gather_rows(dy, ctx.group), None
 
 
 _layer_id = [0]
