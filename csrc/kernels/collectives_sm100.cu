@@ -219,20 +219,50 @@ reducescatter_kernel(const CommArgs a, T* __restrict__ out) {
 // slot buffer ([world][rows][N]; entry barrier), sum the slots in fp32, add bias / residual, write the
 // bf16 output, and hold everybody until all slot buffers have been read (exit barrier), after which
 // they may be rewritten.
+//
+// The sum is a local HBM-bound pass, so it runs on a grid that fills the GPU (all CTAs resident), while the two
+// cross-rank barriers involve one CTA only: CTA 0 performs the entry barrier and then publishes the epoch in
+// local_sync[0]; the other CTAs wait (bounded) for that word. The CTA that finishes last (counter in
+// local_sync[1], reset by that CTA) performs the exit barrier.
 template <typename TA>
 __global__ void __launch_bounds__(COMM_THREADS)
 rs_finalize_kernel(const CommArgs a, const TA* __restrict__ acc, const bf16* __restrict__ bias,
-                   const bf16* __restrict__ residual, bf16* __restrict__ out, long rows, int N) {
+                   const bf16* __restrict__ residual, bf16* __restrict__ out, long rows, int N,
+                   uint32_t* __restrict__ local_sync) {
   const uint32_t epoch = *a.epoch_ptr;
-  cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch, a.status);
-  const long nvec = rows * N / 8;
+  __shared__ int s_last;
+  if (blockIdx.x == 0) {
+    cta_barrier_all_ranks(a.flags, 0, a.rank, a.world, 2 * epoch, a.status);
+    if (threadIdx.x == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(local_sync), "r"(epoch) : "memory");
+  } else {
+    if (threadIdx.x == 0) {
+      const uint64_t t0 = globaltimer_ns();
+      uint32_t spins = 0;
+      while (true) {
+        uint32_t v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(local_sync) : "memory");
+        if ((int32_t)(v - epoch) >= 0) break;
+        if ((++spins & 31u) == 0u) {
+          if (a.status && *((volatile int*)a.status) != 0) break;
+          if (globaltimer_ns() - t0 > TB_PEER_WAIT_LIMIT_NS) {
+            if (a.status) atomicCAS(a.status, 0, TB_ERR_WAIT_PEER);
+            break;
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  const uint32_t nvec = (uint32_t)(rows * N / 8);
+  const uint32_t vec_per_row = (uint32_t)N / 8;
   const long slot = rows * N;
-  for (long v = (long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long)gridDim.x * blockDim.x) {
-    const long e = v * 8;
-    const int c = (int)(e % N);
+  for (uint32_t v = blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += gridDim.x * blockDim.x) {
+    const long e = (long)v * 8;
+    const int c = (int)(v % vec_per_row) * 8;
     float f[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) f[j] = 0.f;
+#pragma unroll 4
     for (int s = 0; s < a.world; ++s) {
       float g[8];
       if (sizeof(TA) == 4) {
@@ -259,7 +289,15 @@ rs_finalize_kernel(const CommArgs a, const TA* __restrict__ acc, const bf16* __r
     }
     *reinterpret_cast<uint4*>(out + e) = Acc<bf16>::pack(f);
   }
-  cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch + 1, a.status);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t done = atomicAdd(local_sync + 1, 1u);
+    s_last = (done == gridDim.x - 1);
+    if (s_last) local_sync[1] = 0;
+  }
+  __syncthreads();
+  if (s_last) cta_barrier_all_ranks(a.flags, 0, a.rank, a.world, 2 * epoch + 1, a.status);
 }
 
 // Runs after a collective on the same stream: the next launch sees a fresh pair of barrier values.
@@ -360,16 +398,19 @@ TB_EXPORT int tb_reducescatter(const void* const* bufs, const void* const* flags
 // out: bf16 [rows, N]; bias [N] and residual [rows, N] are optional.
 TB_EXPORT int tb_rs_finalize(const void* const* flags, int rank, int world, const unsigned* epoch_ptr, void* acc,
                              int acc_f32, const void* bias, const void* residual, void* out, long rows, int N,
-                             int nblocks, int* status, cudaStream_t st) {
+                             unsigned* local_sync, int* status, cudaStream_t st) {
   TB_ENSURE_DEVICE();
   if (N % 8) TB_FAIL(TB_E_ARG, "rs_finalize: N must be a multiple of 8");
+  if (!local_sync) TB_FAIL(TB_E_ARG, "rs_finalize: local_sync (2 zero-initialised words) is required");
+  if (rows * N / 8 >= (1L << 31)) TB_FAIL(TB_E_TOO_LARGE, "rs_finalize: more than 2^31 vectors");
   CommArgs a;
   const void* none[MAX_RANKS] = {nullptr};
   if (int r = fill_args(a, none, flags, nullptr, rank, world, epoch_ptr, 0, 0, 1.f, status)) return r;
-  if (nblocks < 1) nblocks = 1;
-  if (nblocks > COMM_MAX_BLOCKS) nblocks = COMM_MAX_BLOCKS;
-  if (acc_f32) rs_finalize_kernel<float><<<nblocks, COMM_THREADS, 0, st>>>(a, (const float*)acc, (const bf16*)bias, (const bf16*)residual, (bf16*)out, rows, N);
-  else rs_finalize_kernel<bf16><<<nblocks, COMM_THREADS, 0, st>>>(a, (const bf16*)acc, (const bf16*)bias, (const bf16*)residual, (bf16*)out, rows, N);
+  // every CTA must be resident at once (CTAs wait on CTA 0): at most two 512-thread CTAs per SM
+  long want = (rows * N / 8 + COMM_THREADS - 1) / COMM_THREADS;
+  int nblocks = (int)(want < 1 ? 1 : (want > 2L * sm_count() ? 2L * sm_count() : want));
+  if (acc_f32) rs_finalize_kernel<float><<<nblocks, COMM_THREADS, 0, st>>>(a, (const float*)acc, (const bf16*)bias, (const bf16*)residual, (bf16*)out, rows, N, local_sync);
+  else rs_finalize_kernel<bf16><<<nblocks, COMM_THREADS, 0, st>>>(a, (const bf16*)acc, (const bf16*)bias, (const bf16*)residual, (bf16*)out, rows, N, local_sync);
   bump_epoch_kernel<<<1, 1, 0, st>>>(const_cast<uint32_t*>(epoch_ptr));
   TB_CUDA_CHECK(cudaGetLastError());
   return 0;

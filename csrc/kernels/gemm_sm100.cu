@@ -16,6 +16,9 @@
 // unwired cuBLAS call (crates/torsh-backend/src/cuda/backend.rs:695-726).
 #include "comm.cuh"
 #include "host_util.h"
+#include <stdlib.h>
+#include <string.h>
+
 #include "sm100.cuh"
 
 namespace tb {
@@ -67,6 +70,7 @@ struct GemmParams {
   const uint32_t* epoch_ptr;
   int rank, world;
   int m_rot;                 // m-tiles are visited starting at this tile (own shard first / last)
+  int tma_store;             // bf16 output leaves through shared memory + TMA tensor stores (out_maps)
 };
 
 template <int BN, int STAGES>
@@ -76,12 +80,31 @@ struct SmemLayout {
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
   // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
   static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
-  // staging rows of the GEMM -> reduce-scatter epilogue: 4 warps x 32 rows x 144 B (128 B + pad)
+  // Epilogue staging, 1024-byte aligned. bf16 outputs: 4 warps x 2 buffers x (32 rows x 128 B, 128B-swizzled),
+  // each buffer leaves as one TMA tensor store. The fp32 reduce-scatter epilogue uses the same bytes as
+  // 4 warps x 32 private rows of 144 B (128 B + pad).
   static constexpr int RS_ROW_PITCH = 144;
-  static constexpr int RS_OFF = (TOTAL + 127) / 128 * 128;
-  static constexpr int RS_BYTES = 4 * 32 * RS_ROW_PITCH;
+  static constexpr int RS_OFF = (TOTAL + 1023) / 1024 * 1024;
+  static constexpr int EPI_OFF = RS_OFF;
+  static constexpr int EPI_WARP_BYTES = 2 * 32 * 128;
+  static constexpr int RS_BYTES = 4 * EPI_WARP_BYTES;
   static constexpr int ALLOC = RS_OFF + RS_BYTES + 1024;  // + slack for manual 1024-byte alignment
+  static_assert(4 * 32 * RS_ROW_PITCH <= RS_BYTES, "fp32 reduce-scatter rows must fit the staging region");
+  static_assert(ALLOC <= 232448, "shared memory budget of one CTA exceeded");
 };
+
+// Output tensor maps of the TMA-store epilogue: [0] for a plain GEMM, one per destination rank for the
+// GEMM -> reduce-scatter kernel (box 64 columns x 32 rows, 128-byte swizzle).
+struct OutMaps {
+  CUtensorMap m[MAX_RANKS];
+};
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x),
+               "r"(y), "r"(smem_u32(smem_src))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_wait_read_le1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
 __device__ __forceinline__ void decode_work(const GemmParams& p, int work, int& m_t, int& n_t,
                                             int& kb0, int& kb1) {
@@ -177,10 +200,72 @@ __device__ __forceinline__ void ag_copy_role(const GemmParams& p, uint8_t* smem,
   cta_barrier_all_ranks(flags, blockIdx.x, p.rank, p.world, 2 * epoch + 1, p.status);
 }
 
+// Elementwise part of the epilogue on one thread's 32 consecutive output columns (a full, 16-byte aligned chunk):
+// + bias, store of the pre-activation, tanh-GELU, multiply by GELU'(aux), + residual.
+__device__ __forceinline__ void epi_math(const GemmParams& p, int flags, bool add_bias, int row, int n0, size_t off,
+                                         float (&f)[32]) {
+    if (add_bias) {
+      const uint4* bp = reinterpret_cast<const uint4*>(p.bias + n0);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 b = __ldg(bp + g);
+        uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          f[g * 8 + e * 2] += bf16_lo(w[e]);
+          f[g * 8 + e * 2 + 1] += bf16_hi(w[e]);
+        }
+      }
+    }
+    if (flags & EPI_STORE_PREACT) {
+      uint4* pp = reinterpret_cast<uint4*>(p.preact + off);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 o;
+        o.x = pack_bf16x2(f[g * 8 + 0], f[g * 8 + 1]);
+        o.y = pack_bf16x2(f[g * 8 + 2], f[g * 8 + 3]);
+        o.z = pack_bf16x2(f[g * 8 + 4], f[g * 8 + 5]);
+        o.w = pack_bf16x2(f[g * 8 + 6], f[g * 8 + 7]);
+        pp[g] = o;
+      }
+    }
+    if (flags & EPI_GELU) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) f[j] = gelu_tanh(f[j]);
+    }
+    if (flags & EPI_MUL_DGELU) {
+      const uint4* ap = reinterpret_cast<const uint4*>(p.aux + off);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 a = ap[g];
+        uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          f[g * 8 + e * 2] *= gelu_tanh_grad(bf16_lo(w[e]));
+          f[g * 8 + e * 2 + 1] *= gelu_tanh_grad(bf16_hi(w[e]));
+        }
+      }
+    }
+    if (flags & EPI_RESIDUAL) {
+      const uint4* rp =
+          reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldr + n0);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint4 a = rp[g];
+        uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          f[g * 8 + e * 2] += bf16_lo(w[e]);
+          f[g * 8 + e * 2 + 1] += bf16_hi(w[e]);
+        }
+      }
+    }
+}
+
 template <int BN, int A_MAJOR, int B_MAJOR, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                 const GemmParams p) {
+                 const __grid_constant__ OutMaps out_maps, const GemmParams p) {
   using L = SmemLayout<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -320,6 +405,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t epi_cnt = 0;  // 64-column groups this warp has staged so far (selects the staging buffer)
     const int flags = p.flags;
     for (int work = worker; work < total_work; work += nworkers) {
       int m_t, n_t, kb0, kb1;
@@ -336,6 +422,44 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         uint32_t v[32];
         tmem_ld32(tmem_base + acc * BN + c0 + ((uint32_t)(q * 32) << 16), v);
         tmem_wait_ld();
+        if (p.tma_store) {
+          // bf16 output through shared memory: every lane packs its row's 32 columns into a 128B-swizzled
+          // 32 x 64 staging tile; after the second half lane 0 sends the tile with one TMA tensor store
+          // (rows >= M are clipped by the tensor map). N % 64 == 0 here, so every chunk is full.
+          const int half = (c0 >> 5) & 1;
+          uint8_t* sbuf = smem + L::EPI_OFF + q * L::EPI_WARP_BYTES + (epi_cnt & 1) * 4096;
+          if (half == 0) {
+            if (lane == 0) bulk_wait_read_le1();  // the store that last read this buffer has finished
+            __syncwarp();
+          }
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = __uint_as_float(v[j]);
+          if (row_ok && p.rs_rows == 0) epi_math(p, flags, add_bias, row, n0, (size_t)row * p.ldd + n0, f);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int chunk = half * 4 + g;
+            *reinterpret_cast<uint4*>(sbuf + lane * 128 + ((chunk ^ (lane & 7)) << 4)) =
+                make_uint4(pack_bf16x2(f[g * 8 + 0], f[g * 8 + 1]), pack_bf16x2(f[g * 8 + 2], f[g * 8 + 3]),
+                           pack_bf16x2(f[g * 8 + 4], f[g * 8 + 5]), pack_bf16x2(f[g * 8 + 6], f[g * 8 + 7]));
+          }
+          if (half == 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              const int row0 = m_t * BM + q * 32;
+              if (p.rs_rows > 0) {
+                const int owner = row0 / p.rs_rows;
+                tma_store_2d(&out_maps.m[owner], sbuf, n0 - 32, p.rank * p.rs_rows + (row0 - owner * p.rs_rows));
+              } else {
+                tma_store_2d(&out_maps.m[0], sbuf, n0 - 32, row0);
+              }
+              bulk_commit();
+            }
+            ++epi_cnt;
+          }
+          continue;
+        }
         if (!row_ok) continue;
         float f[32];
 #pragma unroll
@@ -377,62 +501,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           continue;
         }
         if (full_chunk && (p.ldd & 7) == 0) {
-          if (add_bias) {
-            const uint4* bp = reinterpret_cast<const uint4*>(p.bias + n0);
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 b = __ldg(bp + g);
-              uint32_t w[4] = {b.x, b.y, b.z, b.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                f[g * 8 + e * 2] += bf16_lo(w[e]);
-                f[g * 8 + e * 2 + 1] += bf16_hi(w[e]);
-              }
-            }
-          }
-          if (flags & EPI_STORE_PREACT) {
-            uint4* pp = reinterpret_cast<uint4*>(p.preact + off);
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 o;
-              o.x = pack_bf16x2(f[g * 8 + 0], f[g * 8 + 1]);
-              o.y = pack_bf16x2(f[g * 8 + 2], f[g * 8 + 3]);
-              o.z = pack_bf16x2(f[g * 8 + 4], f[g * 8 + 5]);
-              o.w = pack_bf16x2(f[g * 8 + 6], f[g * 8 + 7]);
-              pp[g] = o;
-            }
-          }
-          if (flags & EPI_GELU) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) f[j] = gelu_tanh(f[j]);
-          }
-          if (flags & EPI_MUL_DGELU) {
-            const uint4* ap = reinterpret_cast<const uint4*>(p.aux + off);
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 a = ap[g];
-              uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                f[g * 8 + e * 2] *= gelu_tanh_grad(bf16_lo(w[e]));
-                f[g * 8 + e * 2 + 1] *= gelu_tanh_grad(bf16_hi(w[e]));
-              }
-            }
-          }
-          if (flags & EPI_RESIDUAL) {
-            const uint4* rp =
-                reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldr + n0);
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              uint4 a = rp[g];
-              uint32_t w[4] = {a.x, a.y, a.z, a.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                f[g * 8 + e * 2] += bf16_lo(w[e]);
-                f[g * 8 + e * 2 + 1] += bf16_hi(w[e]);
-              }
-            }
-          }
+          epi_math(p, flags, add_bias, row, n0, off, f);
           if (flags & EPI_OUT_F32) {
             float* dp = reinterpret_cast<float*>(p.D) + off;
             if (flags & EPI_ATOMIC) {
@@ -510,7 +579,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         acc_phase ^= 1;
       }
     }
-    if (p.rs_rows > 0) bulk_wait_all();  // every row this thread sent has landed in its owner's memory
+    if (p.rs_rows > 0 || p.tma_store) bulk_wait_all();  // everything this thread sent has left shared memory and landed
   }
 
   tc_fence_before();
@@ -522,7 +591,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 }
 
 template <int BN, int A_MAJOR, int B_MAJOR, int STAGES>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p,
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const OutMaps& om, const GemmParams& p,
                        cudaStream_t stream) {
   using L = SmemLayout<BN, STAGES>;
   auto kern = gemm_bf16_kernel<BN, A_MAJOR, B_MAJOR, STAGES>;
@@ -535,7 +604,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
   int workers = sm_count() - p.ag_ctas;  // copy CTAs and GEMM CTAs must all be resident at once
   if (workers < 1) TB_FAIL(TB_E_ARG, "gemm: too many copy CTAs");
   int grid = (total < workers ? total : workers) + p.ag_ctas;
-  kern<<<grid, GEMM_THREADS, L::ALLOC, stream>>>(ma, mb, p);
+  kern<<<grid, GEMM_THREADS, L::ALLOC, stream>>>(ma, mb, om, p);
   TB_CUDA_CHECK(cudaGetLastError());
   return TB_LAUNCH_OK;
 }
@@ -674,12 +743,38 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
     if (r) return r;
   }
 
+  // TMA-store epilogue: bf16 output, whole 64-column groups, 16-byte aligned rows and operands
+  OutMaps om;
+  memset(&om, 0, sizeof(om));
+  {
+    static const bool enabled = [] {
+      const char* e = getenv("TB_GEMM_TMA_STORE");
+      return !(e && e[0] == '0');
+    }();
+    auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
+    bool ok = enabled && !(flags & (EPI_OUT_F32 | EPI_ACCUM | EPI_ATOMIC)) && (N % 64) == 0 && (ldd & 7) == 0 &&
+              split_k == 1 && (!bias || al16(bias)) && (!residual || (al16(residual) && (ldr & 7) == 0)) &&
+              (!preact || al16(preact)) && (!aux || al16(aux));
+    uint64_t dims[2], str[1] = {(uint64_t)ldd * 2};
+    uint32_t box[2] = {64, 32};
+    if (ok && tp.kind == 1) {
+      dims[0] = (uint64_t)N;
+      dims[1] = (uint64_t)tp.world * (uint64_t)(M / tp.world);
+      for (int i = 0; i < tp.world && ok; ++i) ok = al16(tp.peers[i]) && make_tmap(&om.m[i], tp.peers[i], 2, 2, dims, str, box) == 0;
+    } else if (ok) {
+      dims[0] = (uint64_t)N;
+      dims[1] = (uint64_t)M;
+      ok = al16(D) && make_tmap(&om.m[0], D, 2, 2, dims, str, box) == 0;
+    }
+    p.tma_store = ok ? 1 : 0;
+  }
+
 #define TB_DISPATCH(BN_, ST_)                                                          \
   do {                                                                                 \
-    if (a_major == 0 && b_major == 0) return launch_gemm<BN_, 0, 0, ST_>(ma, mb, p, stream); \
-    if (a_major == 0 && b_major == 1) return launch_gemm<BN_, 0, 1, ST_>(ma, mb, p, stream); \
-    if (a_major == 1 && b_major == 1) return launch_gemm<BN_, 1, 1, ST_>(ma, mb, p, stream); \
-    if (a_major == 1 && b_major == 0) return launch_gemm<BN_, 1, 0, ST_>(ma, mb, p, stream); \
+    if (a_major == 0 && b_major == 0) return launch_gemm<BN_, 0, 0, ST_>(ma, mb, om, p, stream); \
+    if (a_major == 0 && b_major == 1) return launch_gemm<BN_, 0, 1, ST_>(ma, mb, om, p, stream); \
+    if (a_major == 1 && b_major == 1) return launch_gemm<BN_, 1, 1, ST_>(ma, mb, om, p, stream); \
+    if (a_major == 1 && b_major == 0) return launch_gemm<BN_, 1, 0, ST_>(ma, mb, om, p, stream); \
   } while (0)
   if (bn == 256) TB_DISPATCH(256, 4);
   else TB_DISPATCH(128, 6);

@@ -60,6 +60,8 @@ class TPContext:
         # Pipeline schedules keep several micro-batches in flight; a column-parallel layer saves its gathered input
         # (a view of a staging buffer) for the weight gradient, so each in-flight micro-batch needs its own buffer.
         self.slot = 0
+        # [go flag, done counter] of the wide-grid finalize kernel (CTA 0 releases the others after the cross-rank barrier)
+        self.local_sync = torch.zeros(2, dtype=torch.int32, device="cuda") if self.ctx is not None else None
         self._bufs: dict = {}
         self._ready: dict = {}
 
@@ -110,9 +112,9 @@ def _gemm_rs(tpc: TPContext, tag: str, x: torch.Tensor, w: torch.Tensor, b_major
          N, K, b_major, x.stride(0), w.stride(0), N, int(tpc.cfg.rs_fp32), tpc.rank, tpc.world, 0, st.data_ptr(),
          nv.stream_ptr())
     out = torch.empty(rows, N, dtype=torch.bfloat16, device=x.device)
-    call("tb_rs_finalize", [P, I, I, P, P, I, P, P, P, L, I, I, P, P], tpc.ctx.flags.ptr_array, tpc.rank, tpc.world,
+    call("tb_rs_finalize", [P, I, I, P, P, I, P, P, P, L, I, P, P, P], tpc.ctx.flags.ptr_array, tpc.rank, tpc.world,
          tpc.ctx.epoch.data_ptr(), buf.tensor.data_ptr(), int(tpc.cfg.rs_fp32), nv.ptr(bias), nv.ptr(residual),
-         out.data_ptr(), rows, N, 32, st.data_ptr(), nv.stream_ptr())
+         out.data_ptr(), rows, N, tpc.local_sync.data_ptr(), st.data_ptr(), nv.stream_ptr())
     return out
 
 
