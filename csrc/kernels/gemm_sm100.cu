@@ -65,7 +65,9 @@ struct GemmParams {
   int ag_ctas, ag_rows;
   const void* ag_src[MAX_RANKS];
   void* ag_dst;
-  uint32_t* ag_ready;        // local, one word per m-tile; ready when >= the launch's epoch
+  uint32_t* ag_ready;        // local: [tiles_m] ready words (ready when >= the launch's epoch), then [tiles_m]
+                             // arrival counters of the copy CTAs that share a tile
+  int ag_split;              // copy CTAs per 128-row tile (each moves 1/ag_split of the tile's bytes)
   void* flag_tbl[MAX_RANKS]; // symmetric flag buffer (cross-rank barriers of the copy CTAs)
   const uint32_t* epoch_ptr;
   int rank, world;
@@ -161,35 +163,66 @@ __device__ __forceinline__ void ag_copy_role(const GemmParams& p, uint8_t* smem,
   // every rank's shard is complete once its kernel has started (stream order on that rank)
   cta_barrier_all_ranks(flags, blockIdx.x, p.rank, p.world, 2 * epoch, p.status);
   if (threadIdx.x == 0) {
+    // Work units: (peer, 128-row tile, part), peers nearest first, ag_split parts per tile so that a short shard
+    // still keeps every copy CTA busy; this CTA takes the units blockIdx.x, blockIdx.x + ag_ctas, ... Their 16 KB
+    // pieces form one stream that is pipelined through the ring: up to NBUF - 1 peer loads are in flight while the
+    // piece that has landed is written to local memory; a buffer is refilled as soon as the store that read it has
+    // released it (stores retire in order).
     const long tile_bytes = (long)BM * p.K * 2;
     const int tiles_per_rank = p.ag_rows / BM;
-    const int pieces = (int)(tile_bytes / PIECE);  // launcher guarantees divisibility
-    uint32_t phase = 0;
-    for (int step = 1; step < p.world; ++step) {
-      const int q = (p.rank + step) % p.world;
-      for (int t = blockIdx.x; t < tiles_per_rank; t += p.ag_ctas) {
-        const char* src = reinterpret_cast<const char*>(p.ag_src[q]) + (long)t * tile_bytes;
-        char* dst = reinterpret_cast<char*>(p.ag_dst) + ((long)q * tiles_per_rank + t) * tile_bytes;
-        for (int i0 = 0; i0 < pieces; i0 += NBUF) {
-          const int n = min(NBUF, pieces - i0);
-          for (int b = 0; b < n; ++b) {
-            mbar_expect_tx(&bars[b], PIECE);
-            bulk_load(smem + b * PIECE, src + (long)(i0 + b) * PIECE, PIECE, &bars[b]);
-          }
-          for (int b = 0; b < n; ++b) {
-            mbar_wait(&bars[b], phase, abort_flag, p.status, TB_ERR_WAIT_FULL);
-            bulk_store(dst + (long)(i0 + b) * PIECE, smem + b * PIECE, PIECE);
-          }
-          bulk_commit();
-          bulk_wait_read_all();  // the ring may be refilled
-          phase ^= 1;
-        }
-        bulk_wait_all();  // the tile is in local memory
+    const int split = p.ag_split;
+    const int ppu = (int)(tile_bytes / PIECE) / split;  // pieces per unit; launcher guarantees divisibility
+    const int units = (p.world - 1) * tiles_per_rank * split;
+    const int my_units = (int)blockIdx.x < units ? (units - (int)blockIdx.x + p.ag_ctas - 1) / p.ag_ctas : 0;
+    const long total = (long)my_units * ppu;
+    const int pieces = ppu;  // a unit is complete after its last piece
+    auto locate = [&](long g, const char*& src, char*& dst, int& q, int& t, int& piece) {
+      const int ui = (int)(g / ppu);
+      piece = (int)(g - (long)ui * ppu);
+      const int u = (int)blockIdx.x + ui * p.ag_ctas;
+      const int part = u % split;
+      t = (u / split) % tiles_per_rank;
+      const int step = 1 + u / (split * tiles_per_rank);
+      q = (p.rank + step) % p.world;
+      const long off = (long)t * tile_bytes + ((long)part * ppu + piece) * PIECE;
+      src = reinterpret_cast<const char*>(p.ag_src[q]) + off;
+      dst = reinterpret_cast<char*>(p.ag_dst) + (long)q * tiles_per_rank * tile_bytes + off;
+    };
+    auto issue_load = [&](long g) {
+      const char* src; char* dst; int q, t, piece;
+      locate(g, src, dst, q, t, piece);
+      const int b = (int)(g % NBUF);
+      mbar_expect_tx(&bars[b], PIECE);
+      bulk_load(smem + b * PIECE, src, PIECE, &bars[b]);
+    };
+    long next_load = 0;
+    for (; next_load < total && next_load < NBUF; ++next_load) issue_load(next_load);
+    for (long i = 0; i < total; ++i) {
+      const char* src; char* dst; int q, t, piece;
+      locate(i, src, dst, q, t, piece);
+      const int b = (int)(i % NBUF);
+      mbar_wait(&bars[b], (uint32_t)((i / NBUF) & 1), abort_flag, p.status, TB_ERR_WAIT_FULL);
+      bulk_store(dst, smem + b * PIECE, PIECE);
+      bulk_commit();
+      if (i >= 1 && next_load < total) {
+        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // the store of piece i - 1 has read its buffer
+        issue_load(next_load);                                        // piece i - 1 + NBUF goes into that buffer
+        ++next_load;
+      }
+      if (piece == pieces - 1) {
+        bulk_wait_all();  // this part of the tile is in local memory
         __threadfence();
-        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ag_ready + q * tiles_per_rank + t), "r"(epoch)
-                     : "memory");
+        const int tile = q * tiles_per_rank + t;
+        uint32_t* cnt = p.ag_ready + p.tiles_m + tile;
+        uint32_t arrived;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(cnt) : "memory");
+        if (arrived == (uint32_t)split - 1) {  // last part: reset the counter for the next launch, publish the tile
+          *cnt = 0;
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ag_ready + tile), "r"(epoch) : "memory");
+        }
       }
     }
+    bulk_wait_all();
     if (*abort_flag) {
       uint64_t t0 = globaltimer_ns();
       while (globaltimer_ns() - t0 < 2000000ull) {
@@ -723,6 +756,13 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
     }
     p.ag_dst = const_cast<void*>(A);
     p.ag_ready = tp.ready;
+    {
+      // parts per tile: enough that every copy CTA has work, a power of two that divides the K/64 pieces of a tile
+      const int tiles_remote = (tp.world - 1) * (p.ag_rows / BM);
+      int split = 1;
+      while (split < 8 && tiles_remote * split < 2 * tp.copy_ctas && ((K / 64) % (split * 2)) == 0) split *= 2;
+      p.ag_split = split;
+    }
     p.epoch_ptr = tp.epoch_ptr;
     p.m_rot = tp.rank * (p.ag_rows / BM);  // own shard first
   }

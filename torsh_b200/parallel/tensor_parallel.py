@@ -43,7 +43,7 @@ class TensorParallelConfig:
     sequence_parallel: bool = True
     communication_backend: str = "nvswitch"
     async_communication: bool = True
-    copy_ctas: int = 16
+    copy_ctas: int = 0     # CTAs that pull peer shards in all-gather -> GEMM (0: 16 for two ranks, 32 beyond)
     rs_fp32: bool = False  # accumulate the reduce-scatter in fp32 (2x the NVLink bytes of bf16)
     fused: bool = True     # False: NCCL collectives + library GEMMs (the comparison arm of the benchmarks)
 
@@ -90,12 +90,13 @@ def _ag_gemm(tpc: TPContext, tag: str, x_shard: torch.Tensor, w: torch.Tensor, b
     a_full[tpc.rank * rows:(tpc.rank + 1) * rows].copy_(x_shard)
     shards = (ctypes.c_void_p * 8)(*[p + r * rows * K * 2 for r, p in enumerate(buf.peer_ptrs)] + [0] * (8 - tpc.world))
     y = torch.empty(M, N, dtype=torch.bfloat16, device=x_shard.device)
-    ready = tpc.ready_flags(tag, M // 128, x_shard.device)
+    ready = tpc.ready_flags(tag, 2 * (M // 128), x_shard.device)   # ready words, then arrival counters
     flags = (EPI_BIAS if bias is not None else 0) | (EPI_GELU if gelu else 0)
     st = nv.status_word(x_shard.device)
     call("tb_ag_gemm", [P, P, P, P, P, P, P, I, I, I, I, I, I, P, I, I, I, I, I, P, P], a_full.data_ptr(), shards,
          tpc.ctx.flags.ptr_array, tpc.ctx.epoch.data_ptr(), ready.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
-         b_major, w.stride(0), y.stride(0), nv.ptr(bias), flags, tpc.rank, tpc.world, tpc.cfg.copy_ctas, 0,
+         b_major, w.stride(0), y.stride(0), nv.ptr(bias), flags, tpc.rank, tpc.world,
+         tpc.cfg.copy_ctas or (16 if tpc.world <= 2 else 32), 0,
          st.data_ptr(), nv.stream_ptr())
     return y, a_full
 
