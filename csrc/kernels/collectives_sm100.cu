@@ -20,7 +20,7 @@
 namespace tb {
 
 constexpr int COMM_THREADS = 512;
-constexpr int COMM_MAX_BLOCKS = 64;  // flag slots per symmetric flag buffer
+constexpr int COMM_MAX_BLOCKS = 320;  // flag slots per symmetric flag buffer (one per CTA: two CTAs per SM and some)
 
 struct CommArgs {
   PeerTable bufs;    // symmetric data buffer
@@ -168,14 +168,26 @@ allgather_kernel(const CommArgs a, int elem_bytes) {
   const long nvec = bytes / 16;
   const long base = a.byte_off + (long)a.rank * bytes;
   const char* src = reinterpret_cast<const char*>(a.bufs.ptr[a.rank]) + base;
-  for (long v = (long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long)gridDim.x * blockDim.x) {
-    const uint4 x = *reinterpret_cast<const uint4*>(src + v * 16);
-    if (NVLS) {
-      multimem_st_16(a.mc + base + v * 16, x);
-    } else {
-      for (int p = 1; p < a.world; ++p) {
-        const int q = (a.rank + p) % a.world;
-        *reinterpret_cast<uint4*>(reinterpret_cast<char*>(a.bufs.ptr[q]) + base + v * 16) = x;
+  constexpr int U = 4;  // vectors in flight per thread
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long v0 = (long)blockIdx.x * blockDim.x + threadIdx.x; v0 < nvec; v0 += nthreads * U) {
+    uint4 x[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long v = v0 + (long)u * nthreads;
+      if (v < nvec) x[u] = *reinterpret_cast<const uint4*>(src + v * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long v = v0 + (long)u * nthreads;
+      if (v >= nvec) continue;
+      if (NVLS) {
+        multimem_st_16(a.mc + base + v * 16, x[u]);
+      } else {
+        for (int p = 1; p < a.world; ++p) {
+          const int q = (a.rank + p) % a.world;
+          *reinterpret_cast<uint4*>(reinterpret_cast<char*>(a.bufs.ptr[q]) + base + v * 16) = x[u];
+        }
       }
     }
   }
@@ -192,24 +204,36 @@ reducescatter_kernel(const CommArgs a, T* __restrict__ out) {
   cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch, a.status);
   const long nvec = a.n / N;
   const long base = a.byte_off + (long)a.rank * a.n * (long)sizeof(T);
-  for (long v = (long)blockIdx.x * blockDim.x + threadIdx.x; v < nvec; v += (long)gridDim.x * blockDim.x) {
-    float f[N];
-    if (NVLS) {
-      Acc<T>::mc_reduce(a.mc + base + v * 16, f);
-    } else {
+  constexpr int U = 4;  // vectors in flight per thread
+  const long nthreads = (long)gridDim.x * blockDim.x;
+  for (long v0 = (long)blockIdx.x * blockDim.x + threadIdx.x; v0 < nvec; v0 += nthreads * U) {
+    float f[U][N];
 #pragma unroll
-      for (int j = 0; j < N; ++j) f[j] = 0.f;
-      for (int p = 0; p < a.world; ++p) {
-        const int q = (a.rank + p) % a.world;
-        float g[N];
-        Acc<T>::load(reinterpret_cast<const char*>(a.bufs.ptr[q]) + base + v * 16, g);
+    for (int u = 0; u < U; ++u) {
+      const long v = v0 + (long)u * nthreads;
+      if (v >= nvec) continue;
+      if (NVLS) {
+        Acc<T>::mc_reduce(a.mc + base + v * 16, f[u]);
+      } else {
 #pragma unroll
-        for (int j = 0; j < N; ++j) f[j] += g[j];
+        for (int j = 0; j < N; ++j) f[u][j] = 0.f;
+        for (int p = 0; p < a.world; ++p) {
+          const int q = (a.rank + p) % a.world;
+          float g[N];
+          Acc<T>::load(reinterpret_cast<const char*>(a.bufs.ptr[q]) + base + v * 16, g);
+#pragma unroll
+          for (int j = 0; j < N; ++j) f[u][j] += g[j];
+        }
       }
     }
 #pragma unroll
-    for (int j = 0; j < N; ++j) f[j] *= a.scale;
-    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out) + v * 16) = Acc<T>::pack(f);
+    for (int u = 0; u < U; ++u) {
+      const long v = v0 + (long)u * nthreads;
+      if (v >= nvec) continue;
+#pragma unroll
+      for (int j = 0; j < N; ++j) f[u][j] *= a.scale;
+      *reinterpret_cast<uint4*>(reinterpret_cast<char*>(out) + v * 16) = Acc<T>::pack(f[u]);
+    }
   }
   // peers may overwrite their chunks only after everyone has read them
   cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch + 1, a.status);

@@ -202,13 +202,24 @@ P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 class FusedCollectives:
     """In-kernel collectives on a :class:`SymmetricBuffer` (P2P loads/stores or NVLS multimem)."""
 
-    def __init__(self, group=None, nblocks: int = 32, use_nvls: bool | None = None):
+    def __init__(self, group=None, nblocks: int | None = None, use_nvls: bool | None = None):
         self.ctx = CommContext(group)
         self.rank, self.world, self.nblocks = self.ctx.rank, self.ctx.world, nblocks
         self.use_nvls = use_nvls
 
+    def _blocks(self, nbytes: int) -> int:
+        """CTAs for a message: one per 64 KB, at least 8, at most two per SM (enough loads in flight to fill NVLink)."""
+        if self.nblocks is not None:
+            return self.nblocks
+        return max(8, min(296, nbytes // 65536))
+
     def _nvls(self, buf: SymmetricBuffer) -> bool:
-        return buf.has_multicast if self.use_nvls is None else (self.use_nvls and buf.has_multicast)
+        """In-switch reduction / multicast by default only beyond two ranks: with two, a multicast store also returns
+        the sender's own copy and a multimem load also fetches the local half through the switch, so plain peer
+        loads / stores move half the bytes over each link."""
+        if self.use_nvls is None:
+            return buf.has_multicast and self.world > 2
+        return self.use_nvls and buf.has_multicast
 
     def all_reduce_(self, buf: SymmetricBuffer, numel: int | None = None, offset: int = 0, scale: float = 1.0,
                     mode: str | None = None):
@@ -223,7 +234,7 @@ class FusedCollectives:
         st = nv.status_word(t.device)
         call("tb_allreduce", [P, P, P, I, I, P, L, L, I, F, I, I, P, P], buf.ptr_array, self.ctx.flags.ptr_array,
              buf.mc(m == 1), self.rank, self.world, self.ctx.epoch.data_ptr(), offset * t.element_size(), n,
-             0 if t.dtype == torch.bfloat16 else 1, float(scale), m, self.nblocks, st.data_ptr(), nv.stream_ptr())
+             0 if t.dtype == torch.bfloat16 else 1, float(scale), m, self._blocks(nbytes), st.data_ptr(), nv.stream_ptr())
         return t
 
     def all_gather_(self, buf: SymmetricBuffer, chunk_numel: int, offset: int = 0):
@@ -233,7 +244,7 @@ class FusedCollectives:
         st = nv.status_word(t.device)
         call("tb_allgather", [P, P, P, I, I, P, L, L, I, I, I, P, P], buf.ptr_array, self.ctx.flags.ptr_array,
              buf.mc(nvls), self.rank, self.world, self.ctx.epoch.data_ptr(), offset * t.element_size(), chunk_numel,
-             t.element_size(), int(nvls), self.nblocks, st.data_ptr(), nv.stream_ptr())
+             t.element_size(), int(nvls), self._blocks(chunk_numel * t.element_size()), st.data_ptr(), nv.stream_ptr())
         return t
 
     def reduce_scatter(self, buf: SymmetricBuffer, chunk_numel: int, out: torch.Tensor | None = None, offset: int = 0,
@@ -247,5 +258,5 @@ class FusedCollectives:
         call("tb_reducescatter", [P, P, P, I, I, P, L, L, I, F, I, P, I, P, P], buf.ptr_array,
              self.ctx.flags.ptr_array, buf.mc(nvls), self.rank, self.world, self.ctx.epoch.data_ptr(),
              offset * t.element_size(), chunk_numel, 0 if t.dtype == torch.bfloat16 else 1, float(scale), int(nvls),
-             out.data_ptr(), self.nblocks, st.data_ptr(), nv.stream_ptr())
+             out.data_ptr(), self._blocks(chunk_numel * t.element_size()), st.data_ptr(), nv.stream_ptr())
         return out

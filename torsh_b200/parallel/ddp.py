@@ -43,7 +43,7 @@ class OverlapConfig:
 class DistributedDataParallel(Module):
     def __init__(self, module: torch.nn.Module, process_group=None, bucket_cap_mb: float = 25.0,
                  bucket_config: BucketConfig | None = None, overlap_config: OverlapConfig | None = None,
-                 broadcast_buffers: bool = True, comm_blocks: int = 32, use_nvls: bool | None = None):
+                 broadcast_buffers: bool = True, comm_blocks: int | None = 64, use_nvls: bool | None = None):
         super().__init__()
         self.module = module
         self.group = getattr(process_group, "group", process_group) or dist.group.WORLD

@@ -21,7 +21,7 @@ import torch
 import torch.distributed as dist
 
 MAX_RANKS = 8
-FLAG_SLOTS = 64
+FLAG_SLOTS = 320   # one cross-rank barrier slot per CTA of a collective kernel (COMM_MAX_BLOCKS in the CUDA source)
 
 
 class SymmetricBuffer:
