@@ -181,3 +181,55 @@ def test_pipeline_two_gloo_ranks_match_unsplit_model():
     for p in procs:
         p.join(30)
     assert sorted(res) == [(0, True), (1, True)]
+
+
+def test_rpc_parameter_server_scheduler_integrations():
+    import torch
+    from torsh_b200.parallel import comm_scheduler as cs
+    from torsh_b200.parallel import integrations as ig
+    from torsh_b200.parallel import parameter_server as ps
+    from torsh_b200.parallel import rpc
+    from torsh_b200.parallel.store import MemoryStore
+    store = MemoryStore()
+    rpc.init_rpc("w0", store)
+    try:
+        store.set("rpc/peer", store.get("rpc/w0"))            # a second name for the same server: calls to it use TCP
+        rpc.register_function("add", lambda a, b: a + b)
+        rpc.register_function("mk", lambda n: torch.arange(n, dtype=torch.bfloat16))
+        assert torch.equal(rpc.rpc_sync("peer", "add", (torch.ones(3), 2)), torch.full((3,), 3.0))
+        assert rpc.rpc_async("peer", "add", (1, 2)).result(10) == 3
+        ref = rpc.remote("peer", "mk", (4,))
+        assert ref.to_here().dtype == torch.bfloat16 and ref.rpc_sync("sum").item() == 6 and rpc.delete_rref(ref)
+        try:
+            rpc.rpc_sync("peer", "nope")
+            raise AssertionError("unregistered function must fail")
+        except RuntimeError as e:
+            assert "not registered" in str(e)
+        srv = ps.ParameterServer(ps.ParameterServerConfig(learning_rate=0.5, max_staleness=0))
+        srv.serve()
+        m = torch.nn.Linear(2, 1)
+        w0 = m.weight.detach().clone()
+        cl = ps.ParameterServerClient("peer")
+        cl.register_module(m)
+        assert cl.sync(m) == 2 and cl.sync(m) == 0
+        m(torch.ones(1, 2)).sum().backward()
+        cl.push_gradients(m)
+        stale = dict(cl.versions)
+        assert cl.sync(m) == 2 and torch.allclose(m.weight, w0 - 0.5 * torch.ones(1, 2))
+        cl.versions = {k: v for k, v in stale.items()}
+        cl.push_gradients(m); cl.push_gradients(m)             # the second push is one version behind: rejected
+        assert srv.stats["rejected"] >= 1
+    finally:
+        rpc.shutdown()
+    sch = cs.CommunicationScheduler()
+    release = sch.pause()
+    futs = [sch.submit(lambda i=i: i, nbytes=10, priority=p, name=n) for i, (p, n) in
+            enumerate([(cs.Priority.LOW, "prefetch"), (cs.Priority.HIGH, "bucket"), (cs.Priority.NORMAL, "other")])]
+    release(); sch.drain()
+    assert sch.order[1:4] == ["bucket", "other", "prefetch"] and [f.result() for f in futs] == [0, 1, 2]
+    sch.shutdown()
+    plan = ig.from_deepspeed({"zero_optimization": {"stage": 3, "offload_optimizer": {"device": "cpu"}}, "bf16": {"enabled": True},
+                              "gradient_clipping": 1.0, "gradient_accumulation_steps": 4})
+    assert (plan.strategy, plan.sharding, plan.cpu_offload, plan.param_dtype, plan.grad_accum) == ("zero_offload", "full_shard", True, "bf16", 4)
+    assert ig.from_fairscale({"wrapper": "pipe", "balance": [2, 2, 2], "chunks": 8}).pipeline_stages == 3
+    assert ig.from_horovod({"fusion_threshold_mb": 32, "compression": "fp16"}).bucket_mb == 32

@@ -1,0 +1,104 @@
+"""Import of third-party training configurations (``crates/torsh-distributed/src/{deepspeed,fairscale,horovod}_integration.rs``):
+DeepSpeed JSON (ZeRO stage, offload, fp16 / bf16, gradient clipping, batch sizes), FairScale (OSS / ShardedDDP / FSDP /
+Pipe) and Horovod (fusion threshold, cycle time, compression) settings are mapped onto this framework's own
+``FsdpConfig`` / ``BucketConfig`` / ``PipelineConfig`` / optimizer options."""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field
+from pathlib import Path
+
+
+@dataclass
+class TrainingPlan:
+    strategy: str = "ddp"                  # ddp | fsdp | zero_offload | pipeline
+    sharding: str = "no_shard"             # no_shard | shard_grad_op | full_shard
+    cpu_offload: bool = False
+    param_dtype: str = "fp32"
+    loss_scale: float | None = None
+    bucket_mb: float = 25.0
+    grad_clip: float | None = None
+    micro_batch: int | None = None
+    grad_accum: int = 1
+    optimizer: dict = field(default_factory=dict)
+    pipeline_stages: int = 1
+    micro_batches: int = 1
+    compression: str | None = None
+    notes: list = field(default_factory=list)
+
+    def fsdp_config(self):
+        from .fsdp import FsdpConfig, ShardingStrategy
+        m = {"full_shard": ShardingStrategy.FULL_SHARD, "shard_grad_op": ShardingStrategy.SHARD_GRAD_OP, "no_shard": ShardingStrategy.NO_SHARD}
+        return FsdpConfig(sharding_strategy=m[self.sharding], cpu_offload=self.cpu_offload)
+
+    def bucket_config(self):
+        from .ddp import BucketConfig
+        return BucketConfig(max_bucket_size_mb=self.bucket_mb)
+
+
+def _load(cfg):
+    if isinstance(cfg, (str, Path)):
+        return json.loads(Path(cfg).read_text())
+    return dict(cfg)
+
+
+def from_deepspeed(cfg) -> TrainingPlan:
+    c = _load(cfg)
+    z = c.get("zero_optimization", {})
+    stage = int(z.get("stage", 0))
+    plan = TrainingPlan()
+    plan.sharding = {0: "no_shard", 1: "shard_grad_op", 2: "shard_grad_op", 3: "full_shard"}[stage]
+    plan.strategy = "ddp" if stage == 0 else "fsdp"
+    if stage == 1:
+        plan.notes.append("ZeRO-1 (optimizer-state sharding only) runs as shard_grad_op")
+    off = (z.get("offload_optimizer", {}).get("device", "none") != "none") or (z.get("offload_param", {}).get("device", "none") != "none")
+    plan.cpu_offload = off
+    if off:
+        plan.strategy = "zero_offload"
+    if c.get("bf16", {}).get("enabled"):
+        plan.param_dtype = "bf16"
+    elif c.get("fp16", {}).get("enabled"):
+        plan.param_dtype = "fp16"
+        ls = c["fp16"].get("loss_scale", 0)
+        plan.loss_scale = float(ls) if ls else 2.0 ** c["fp16"].get("initial_scale_power", 16)
+    if "reduce_bucket_size" in z:
+        plan.bucket_mb = float(z["reduce_bucket_size"]) * 4 / 2**20 if z["reduce_bucket_size"] < 1e9 else 25.0
+    plan.grad_clip = c.get("gradient_clipping")
+    plan.micro_batch = c.get("train_micro_batch_size_per_gpu")
+    plan.grad_accum = int(c.get("gradient_accumulation_steps", 1))
+    opt = c.get("optimizer", {})
+    if opt:
+        plan.optimizer = {"type": opt.get("type", "AdamW"), **opt.get("params", {})}
+    return plan
+
+
+def from_fairscale(cfg) -> TrainingPlan:
+    c = _load(cfg)
+    plan = TrainingPlan()
+    kind = c.get("wrapper", "ddp").lower()
+    if kind in ("oss", "sharded_ddp", "shardedddp"):
+        plan.strategy, plan.sharding = "fsdp", "shard_grad_op"
+    elif kind == "fsdp":
+        plan.strategy = "fsdp"
+        plan.sharding = "full_shard" if c.get("reshard_after_forward", True) else "shard_grad_op"
+        plan.cpu_offload = bool(c.get("move_params_to_cpu") or c.get("cpu_offload"))
+        if c.get("mixed_precision"):
+            plan.param_dtype = "bf16" if c.get("compute_dtype", "bf16") in ("bf16", "bfloat16") else "fp16"
+    elif kind == "pipe":
+        plan.strategy = "pipeline"
+        plan.pipeline_stages = len(c.get("balance", [1]))
+        plan.micro_batches = int(c.get("chunks", 1))
+    plan.bucket_mb = float(c.get("bucket_cap_mb", 25.0))
+    return plan
+
+
+def from_horovod(cfg) -> TrainingPlan:
+    c = _load(cfg)
+    plan = TrainingPlan(strategy="ddp")
+    plan.bucket_mb = float(c.get("fusion_threshold_mb", c.get("HOROVOD_FUSION_THRESHOLD", 64 * 2**20) / 2**20 if "HOROVOD_FUSION_THRESHOLD" in c else 64.0))
+    comp = str(c.get("compression", "none")).lower()
+    plan.compression = None if comp == "none" else comp
+    if comp == "fp16":
+        plan.notes.append("fp16 gradient compression maps to bf16 bucket all-reduce with fp32 accumulation")
+    plan.grad_accum = int(c.get("backward_passes_per_step", 1))
+    return plan
