@@ -24,7 +24,7 @@ _TORCH = {"float32": torch.float32, "float64": torch.float64, "float16": torch.f
 def _enc(o):
     if isinstance(o, torch.Tensor):
         t = o.detach().cpu().contiguous()
-        raw = t.view(torch.uint8).numpy().tobytes() if t.dtype == torch.bfloat16 else t.numpy().tobytes()
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.dtype == torch.bfloat16 else t.numpy().tobytes()
         return {"__t": str(t.dtype).replace("torch.", ""), "s": list(t.shape), "b": raw}
     if isinstance(o, RRef):
         return {"__rref": o.id, "o": o.owner}
