@@ -418,6 +418,33 @@ TB_EXPORT int tb_reducescatter(const void* const* bufs, const void* const* flags
   return 0;
 }
 
+// One thread waits until *flag >= target or `limit_ns` nanoseconds have passed; on expiry it records
+// TB_ERR_WAIT_PEER in the status word and returns, like every cross-GPU wait in this library. It lets a test (or a
+// health check) see the time-out path with a flag that nothing sets, without a peer and without stalling the GPU for
+// longer than the stated limit (at most one second is accepted).
+__global__ void wait_probe_kernel(const uint32_t* flag, uint32_t target, unsigned long long limit_ns, int* status,
+                                  unsigned long long* waited_ns) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if ((int32_t)(ld_acquire_sys(flag) - target) >= 0) break;
+    if ((++spins & 31u) == 0u && globaltimer_ns() - t0 > limit_ns) {
+      if (status) atomicCAS(status, 0, TB_ERR_WAIT_PEER);
+      break;
+    }
+  }
+  if (waited_ns) *waited_ns = globaltimer_ns() - t0;
+}
+TB_EXPORT int tb_wait_probe(const unsigned* flag, unsigned target, unsigned long long limit_ns, int* status,
+                            unsigned long long* waited_ns, cudaStream_t st) {
+  TB_ENSURE_DEVICE();
+  if (!flag) TB_FAIL(TB_E_ARG, "wait_probe: null flag");
+  if (limit_ns > 1000000000ull) TB_FAIL(TB_E_TOO_LARGE, "wait_probe: the limit may not exceed one second");
+  wait_probe_kernel<<<1, 1, 0, st>>>(flag, target, limit_ns, status, waited_ns);
+  TB_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
 // acc: this rank's slot buffer [world][rows][N] (contiguous; fp32 when acc_f32 else bf16).
 // out: bf16 [rows, N]; bias [N] and residual [rows, N] are optional.
 TB_EXPORT int tb_rs_finalize(const void* const* flags, int rank, int world, const unsigned* epoch_ptr, void* acc,

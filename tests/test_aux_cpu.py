@@ -1,0 +1,162 @@
+"""Auxiliary subsystems on the CPU: optimizer checkpoints, monitoring, debug checks, property-based fuzzing of the
+host-side planners and codecs."""
+import threading
+
+import numpy as np
+import pytest
+import torch
+from hypothesis import given, settings
+from hypothesis import strategies as st
+
+
+def test_optimizer_checkpoint_roundtrip_and_rotation(tmp_path):
+    from torsh_b200.optim import checkpointing as ck
+    m = torch.nn.Linear(4, 3)
+    opt = torch.optim.AdamW(m.parameters(), lr=1e-2)
+    mgr = ck.OptimizerCheckpointManager(ck.CheckpointConfig(str(tmp_path), max_checkpoints=2, checkpoint_frequency=2, save_gradients=True))
+    for step in range(1, 7):
+        m(torch.ones(2, 4)).sum().backward()
+        opt.step()
+        mgr.step()
+        if mgr.should_checkpoint():
+            mgr.save(m, opt, loss=float(step), epoch=0)
+        opt.zero_grad()
+    files = sorted(p.name for p in tmp_path.glob("checkpoint_step_*.bin"))
+    assert files == ["checkpoint_step_4.bin", "checkpoint_step_6.bin"]
+    latest = mgr.load_latest()
+    assert latest["metadata"]["step"] == 6 and latest["metadata"]["loss"] == 6.0 and latest["metadata"]["epoch"] == 0
+    assert abs(latest["metadata"]["learning_rate"] - 1e-2) < 1e-9 and len(latest["metadata"]["model_hash"]) == 16
+    m2 = torch.nn.Linear(4, 3)
+    opt2 = torch.optim.AdamW(m2.parameters(), lr=1e-2)
+    m2(torch.ones(2, 4)).sum().backward(); opt2.step()          # create state slots
+    mgr2 = ck.OptimizerCheckpointManager(ck.CheckpointConfig(str(tmp_path)))
+    assert mgr2.last_checkpoint_step == 6
+    mgr2.restore(mgr2.load_latest(), m2, opt2)
+    assert all(torch.equal(a, b) for a, b in zip(m.parameters(), m2.parameters()))
+    for p, q in zip(m.parameters(), m2.parameters()):
+        assert torch.allclose(opt.state[p]["exp_avg_sq"], opt2.state[q]["exp_avg_sq"])
+    # byte layout of the head of the encoding: step varint, timestamp varint, Option<f32> tag + value
+    blob = ck.encode({"metadata": {"step": 5, "timestamp": 7, "loss": 1.0, "learning_rate": 0.5}, "optimizer_state": None})
+    assert blob[:7] == bytes([5, 7, 1]) + np.float32(1.0).tobytes() and blob[7:11] == np.float32(0.5).tobytes()
+    assert blob[11:] == bytes([0, 0, 0, 0, 0, 0])              # five absent options + ... (epoch, norm, hash, state, grads, params)
+
+
+def test_monitoring_alerts_and_prometheus():
+    from torsh_b200.parallel.monitoring import AlertThresholds, DistributedMonitor, MetricsCollector
+    from torsh_b200.parallel.store import MemoryStore
+    store = MemoryStore()
+    mons = [DistributedMonitor(MetricsCollector(), AlertThresholds(straggler_ratio=1.2), rank=r, world_size=3, store=store) for r in range(3)]
+    for r, mon in enumerate(mons):
+        for _ in range(6):
+            mon.c.record_step(10.0 * (2.0 if r == 2 else 1.0), tokens=1000, comm_ms=2.0, loss=1.0)
+        mon.publish()
+    agg = mons[0].aggregate()
+    assert agg["stragglers"] == [2]
+    mons[0].c.record_step(40.0, comm_ms=30.0)
+    kinds = {a.kind for a in mons[0].check()}
+    assert {"step_time", "comm_share"} <= kinds
+    text = mons[0].c.export_prometheus()
+    assert "torsh_training_step_ms 40.0" in text and "torsh_training_steps_total 7.0" in text
+    assert mons[0].c.summary("training/step_ms")["max"] == 40.0
+
+
+def test_debug_checks():
+    from torsh_b200.utils import debug
+    t = torch.tensor([1.0, float("nan"), float("inf"), -float("inf")])
+    rep = debug.nan_inf_report(t)
+    assert (rep["nan"], rep["pos_inf"], rep["neg_inf"], rep["first_bad"]) == (1, 1, 1, 1)
+    with pytest.raises(debug.NonFiniteError):
+        debug.check_finite(t)
+    net = torch.nn.Sequential(torch.nn.Linear(2, 2), torch.nn.ReLU())
+    with torch.no_grad():
+        net[0].weight.fill_(float("nan"))
+    with pytest.raises(debug.NonFiniteError, match="Linear"):
+        with debug.detect_non_finite(net):
+            net(torch.ones(1, 2))
+    v = debug.LockOrderValidator()
+    a, b = v.lock(1, "a"), v.lock(2, "b")
+    with a, b:
+        pass
+    with pytest.raises(debug.LockOrderError):
+        with b:
+            a.acquire()
+    held = v.lock(3, "held")
+    held.acquire()
+    err = []
+    th = threading.Thread(target=lambda: err.append(pytest.raises(TimeoutError, held.acquire, 0.05)))
+    th.start(); th.join()
+    held.release()
+    assert err
+    buf = torch.zeros(256)
+    payload, check = debug.add_guards(buf, 16)
+    payload.fill_(1.0); check()
+    buf[3] = 7.0
+    with pytest.raises(RuntimeError):
+        check()
+    w = torch.nn.Linear(3, 3)
+    opt = torch.optim.SGD(w.parameters(), lr=0.1)
+
+    def step():
+        opt.zero_grad(); w(torch.ones(2, 3)).sum().backward(); opt.step()
+    assert debug.deterministic_replay(step, lambda: list(w.parameters()),
+                                      lambda snap: [p.data.copy_(s) for p, s in zip(w.parameters(), snap)])
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.lists(st.integers(1, 1 << 22), min_size=1, max_size=40), st.integers(1, 64))
+def test_fuzz_bucket_assignment_covers_every_parameter_once(sizes, cap_mb):
+    from torsh_b200.parallel import planner
+    cap = cap_mb << 20
+    assign = planner.assign_buckets([s * 4 for s in sizes], cap)
+    assert len(assign) == len(sizes) and min(assign) == 0 and set(assign) == set(range(max(assign) + 1))
+    for b in set(assign):
+        members = [sizes[i] * 4 for i, a in enumerate(assign) if a == b]
+        assert sum(members) <= cap or len(members) == 1
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(0, 1 << 30), st.integers(1, 8))
+def test_fuzz_shard_ranges_partition_the_buffer(numel, world):
+    from torsh_b200.parallel.fsdp import shard_range
+    pos = 0
+    for r in range(world):
+        lo, hi = shard_range(numel, world, r)
+        assert lo == min(pos, numel) or lo == pos
+        assert lo <= hi <= max(numel, hi)
+        pos = hi
+    assert pos >= numel
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.lists(st.tuples(st.integers(1, 1 << 24), st.integers(0, 3)), min_size=1, max_size=60))
+def test_fuzz_pool_never_overlaps_live_blocks(ops):
+    from torsh_b200.core.runtime import HostPool
+    pool = HostPool()
+    live = {}
+    for size, stream in ops:
+        p = pool.alloc(size, stream)
+        assert p and p % 64 == 0
+        real = pool.size_of(p)
+        for q, (n, _) in live.items():
+            assert p + real <= q or q + n <= p, "overlapping blocks"
+        live[p] = (real, stream)
+        if len(live) > 8:
+            victim = next(iter(live))
+            assert pool.free(victim)
+            live.pop(victim)
+    assert pool.stats()["allocated_bytes"] == sum(n for n, _ in live.values())
+    for p in list(live):
+        pool.free(p)
+    pool.release_cached()
+    assert pool.stats()["reserved_bytes"] == 0
+    pool.close()
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.lists(st.integers(1, 9), min_size=0, max_size=4), st.sampled_from([torch.float32, torch.float64, torch.int64, torch.bfloat16]))
+def test_fuzz_trsh_roundtrip(shape, dtype):
+    from torsh_b200.serialize import trsh
+    n = int(np.prod(shape)) if shape else 1
+    t = (torch.arange(n, dtype=torch.float32).reshape(shape) * 0.5 - 3).to(dtype)
+    back, meta = trsh.decode_trsh(trsh.encode_trsh(t))
+    assert back.dtype == t.dtype and tuple(back.shape) == tuple(t.shape) and torch.equal(back, t)

@@ -78,3 +78,32 @@ def test_stream_pool_events_and_graph_cache():
     assert torch.allclose(z, torch.relu(x) ** 2)
     assert gc.stats()["entries"] >= 1
     gc.clear()
+
+
+def test_bounded_wait_reports_timeout_and_context_survives():
+    """A flag that nothing sets: the wait gives up after its limit, records the error in the status word, the host
+    turns it into KernelTimeout, and the next launches on the same context work."""
+    import ctypes
+
+    from torsh_b200 import _native as nv
+    from torsh_b200.ops import elementwise as ew
+    lib = nv.require_cuda()
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    waited = torch.zeros(1, dtype=torch.int64, device="cuda")
+    st = nv.status_word()
+    st.zero_()
+    lib.tb_wait_probe.argtypes = [ctypes.c_void_p, ctypes.c_uint, ctypes.c_ulonglong, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    # satisfied wait: no error
+    flag.fill_(5)
+    nv.check(lib.tb_wait_probe(flag.data_ptr(), 5, 50_000_000, st.data_ptr(), waited.data_ptr(), nv.stream_ptr()), "wait_probe")
+    nv.check_status()
+    # a flag nobody sets, 50 ms limit
+    flag.zero_()
+    nv.check(lib.tb_wait_probe(flag.data_ptr(), 1, 50_000_000, st.data_ptr(), waited.data_ptr(), nv.stream_ptr()), "wait_probe")
+    with pytest.raises(nv.KernelTimeout, match="peer"):
+        nv.check_status()
+    assert 45e6 < waited.item() < 500e6
+    nv.check_status()                                   # the status word was reset
+    x = torch.randn(1024, device="cuda")
+    assert torch.equal(ew.unary_raw("relu", x), torch.relu(x))
+    assert lib.tb_wait_probe(flag.data_ptr(), 1, 2_000_000_000, st.data_ptr(), None, nv.stream_ptr()) != 0   # > 1 s refused

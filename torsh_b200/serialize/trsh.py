@@ -56,7 +56,8 @@ def encode_trsh(t: torch.Tensor, compression_level: int = 0, metadata: dict | No
     lib = _lib()
     src = t.detach().cpu().contiguous()
     dt = from_torch_dtype(src.dtype)
-    raw = src.view(torch.uint8).numpy().tobytes() if src.dtype != torch.bool else src.to(torch.uint8).numpy().tobytes()
+    flat = src.reshape(-1)   # a zero-dim tensor cannot be re-viewed as bytes
+    raw = flat.view(torch.uint8).numpy().tobytes() if src.dtype != torch.bool else flat.to(torch.uint8).numpy().tobytes()
     dims = (ctypes.c_int64 * max(src.dim(), 1))(*src.shape)
     kv = []
     for k, v in sorted((metadata or {}).items()):
