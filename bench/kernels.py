@@ -4,6 +4,8 @@
   python bench/kernels.py gemm --m 8192 --n 4096 --k 4096 [--a-major 0 --b-major 0 --bn 256]
   python bench/kernels.py attn_fwd | attn_bwd --batch 4 --seq 2048 --heads 16 --dim 64
   python bench/kernels.py layernorm | xent | adamw
+  python bench/kernels.py bn --batch 64 --hw 56 --channels 256        # BatchNorm2d fwd and bwd, channels-last bf16
+  python bench/kernels.py conv --batch 64 --hw 56 --channels 64 --ksize 3 # conv fwd (im2col + GEMM) and bwd
 Each run prints achieved TFLOP/s or GB/s and the fraction of the measured peak in MEASURED_PEAKS.json
 (fallback 6.65 TB/s, 1.59 PFLOP/s when that file is absent).
 """
@@ -41,12 +43,15 @@ def timeit(fn, iters, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "layernorm", "xent", "adamw"])
+    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "layernorm", "xent", "adamw", "bn", "conv"])
+    ap.add_argument("--hw", type=int, default=56); ap.add_argument("--channels", type=int, default=256)
+    ap.add_argument("--cout", type=int, default=0); ap.add_argument("--ksize", type=int, default=3); ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=4096); ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--a-major", type=int, default=0); ap.add_argument("--b-major", type=int, default=0); ap.add_argument("--bn", type=int, default=0)
     ap.add_argument("--batch", type=int, default=4); ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=16); ap.add_argument("--dim", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--split-k", type=int, default=1, help="gemm: K splits (implies fp32 atomic accumulation, the weight-gradient path)")
     a = ap.parse_args()
     from torsh_b200 import _native as nv
     dev = "cuda"
@@ -57,10 +62,14 @@ def main():
         from torsh_b200.ops.gemm import gemm
         A = torch.randn((a.m, a.k) if a.a_major == 0 else (a.k, a.m), device=dev, dtype=torch.bfloat16)
         B = torch.randn((a.n, a.k) if a.b_major == 0 else (a.k, a.n), device=dev, dtype=torch.bfloat16)
-        out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
-        ms = timeit(lambda: gemm(A, B, a_major=a.a_major, b_major=a.b_major, out=out, bn=a.bn), a.iters, flush)
+        if a.split_k > 1:
+            out = torch.zeros(a.m, a.n, device=dev, dtype=torch.float32)
+            ms = timeit(lambda: gemm(A, B, a_major=a.a_major, b_major=a.b_major, out=out, bn=a.bn, atomic=True, split_k=a.split_k), a.iters, flush)
+        else:
+            out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+            ms = timeit(lambda: gemm(A, B, a_major=a.a_major, b_major=a.b_major, out=out, bn=a.bn), a.iters, flush)
         t = 2.0 * a.m * a.n * a.k / ms / 1e9
-        print(f"gemm {a.m}x{a.n}x{a.k} majors {a.a_major}{a.b_major}: {ms*1e3:.1f} us, {t:.0f} TFLOP/s = {t/tf:.2f} of {kind} bf16 peak")
+        print(f"gemm {a.m}x{a.n}x{a.k} majors {a.a_major}{a.b_major} bn {a.bn} split_k {a.split_k}: {ms*1e3:.1f} us, {t:.0f} TFLOP/s = {t/tf:.2f} of {kind} bf16 peak")
     elif a.what in ("attn_fwd", "attn_bwd"):
         from torsh_b200.ops.attention import flash_attention
         q, k, v = (torch.randn(a.batch, a.seq, a.heads, a.dim, device=dev, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))
@@ -90,6 +99,36 @@ def main():
         ms = timeit(lambda: cross_entropy(lg, tg, num_classes=50257, inplace_grad=False, root_scale=1.0), a.iters, flush)
         gb = 2.0 * lg.numel() * 2 / ms / 1e6
         print(f"cross-entropy fwd+bwd {a.m}x50304: {ms*1e3:.1f} us, {gb:.0f} GB/s = {gb/hbm:.2f} of {kind} copy bandwidth")
+    elif a.what == "bn":
+        from torsh_b200.ops.conv import batch_norm_nhwc
+        C = a.channels
+        x = torch.randn(a.batch, a.hw, a.hw, C, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        r = torch.randn_like(x)
+        bn = torch.nn.BatchNorm2d(C).to(dev)
+        nbytes = x.numel() * 2
+        with torch.no_grad():
+            ms = timeit(lambda: batch_norm_nhwc(x, bn, residual=r, relu=True), a.iters, flush)
+        gb = 4.0 * nbytes / ms / 1e6      # statistics read x; apply reads x and the residual, writes y
+        print(f"batchnorm fwd (+residual, +relu) {a.batch}x{a.hw}x{a.hw}x{C}: {ms*1e3:.1f} us, {gb:.0f} GB/s = {gb/hbm:.2f} of {kind} copy bandwidth")
+        y = batch_norm_nhwc(x, bn, residual=r, relu=True)
+        dy = torch.randn_like(y)
+        ms = timeit(lambda: y.backward(dy, retain_graph=True), a.iters, flush)
+        gb = 8.0 * nbytes / ms / 1e6      # reduce reads dy, y, x; apply reads them again and writes dx and the residual gradient
+        print(f"batchnorm bwd {a.batch}x{a.hw}x{a.hw}x{C}: {ms*1e3:.1f} us, {gb:.0f} GB/s = {gb/hbm:.2f} of {kind} copy bandwidth")
+    elif a.what == "conv":
+        from torsh_b200.ops.conv import conv2d_nhwc
+        C, Co, k = a.channels, (a.cout or a.channels), a.ksize
+        x = torch.randn(a.batch, a.hw, a.hw, C, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        w = (torch.randn(Co, C, k, k, device=dev) * (2.0 / (C * k * k)) ** 0.5).requires_grad_()
+        with torch.no_grad():
+            ms = timeit(lambda: conv2d_nhwc(x, w, a.stride, k // 2), a.iters, flush)
+        ho = (a.hw + 2 * (k // 2) - k) // a.stride + 1
+        fl = 2.0 * a.batch * ho * ho * Co * C * k * k
+        print(f"conv {k}x{k}/{a.stride} fwd {a.batch}x{a.hw}x{a.hw}x{C}->{Co}: {ms*1e3:.1f} us, {fl/ms/1e9:.0f} TFLOP/s = {fl/ms/1e9/tf:.2f} of {kind} bf16 peak")
+        y = conv2d_nhwc(x, w, a.stride, k // 2)
+        dy = torch.randn_like(y)
+        ms = timeit(lambda: y.backward(dy, retain_graph=True), a.iters, flush)
+        print(f"conv {k}x{k}/{a.stride} bwd (dgrad + wgrad): {ms*1e3:.1f} us, {2*fl/ms/1e9:.0f} TFLOP/s = {2*fl/ms/1e9/tf:.2f} of {kind} bf16 peak")
     else:
         from torsh_b200.optim import FlatAdamW, FlatParameters
         p = torch.nn.Parameter(torch.randn(a.m * a.n, device=dev))

@@ -308,6 +308,8 @@ __global__ void bn_param_grad_kernel(const float* __restrict__ sums, float* __re
 // ---- fast BatchNorm forms for C/8 a power of two <= 256 (every ResNet width): a thread keeps one group of 8
 // channels for its whole life, so the per-channel constants sit in registers and a row costs one 16-byte load per
 // operand; 256 / (C/8) rows are in flight per block iteration and there is no integer division in the loop.
+constexpr int BN_U = 4;   // rows in flight per thread, forward kernels
+constexpr int BN_UB = 2;  // rows in flight per thread, backward kernels (three operands per row)
 struct BnMap {
   int cv, r_in, rpb;  // channel-vector index, row inside the block's row group, rows per block iteration
 };
@@ -349,15 +351,22 @@ __global__ void __launch_bounds__(256) bn_stats_fast_kernel(const bf16* __restri
 #pragma unroll
   for (int j = 0; j < 8; ++j) s[j] = q[j] = 0.f;
   const bf16* xp = x + (long)m.cv * 8;
-  for (long r = (long)blockIdx.x * m.rpb + m.r_in; r < rows; r += (long)gridDim.x * m.rpb) {
-    Vec16<bf16> v;
-    v.load_nc(xp + r * C);
-    float f[8];
-    v.get(f);
+  const long step = (long)gridDim.x * m.rpb;
+  for (long r = (long)blockIdx.x * m.rpb + m.r_in; r < rows; r += step * BN_U) {
+    Vec16<bf16> v[BN_U];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      s[j] += f[j];
-      q[j] += f[j] * f[j];
+    for (int u = 0; u < BN_U; ++u)
+      if (r + u * step < rows) v[u].load_nc(xp + (r + u * step) * C);
+#pragma unroll
+    for (int u = 0; u < BN_U; ++u) {
+      if (r + u * step >= rows) break;
+      float f[8];
+      v[u].get(f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        s[j] += f[j];
+        q[j] += f[j] * f[j];
+      }
     }
   }
   bn_block_reduce(s, q, part, sums, C, c8, m);
@@ -378,28 +387,39 @@ __global__ void __launch_bounds__(256) bn_apply_fast_kernel(const bf16* __restri
     sh[j] = beta[c] - mean[c] * sc[j];
   }
   const long off = (long)m.cv * 8;
-  for (long r = (long)blockIdx.x * m.rpb + m.r_in; r < rows; r += (long)gridDim.x * m.rpb) {
-    Vec16<bf16> v;
-    v.load_nc(x + r * C + off);
-    float f[8];
-    v.get(f);
-    if (res) {
-      Vec16<bf16> rv;
-      rv.load_nc(res + r * C + off);
-      float rr[8];
-      rv.get(rr);
+  const long step = (long)gridDim.x * m.rpb;
+  for (long r = (long)blockIdx.x * m.rpb + m.r_in; r < rows; r += step * BN_U) {
+    Vec16<bf16> v[BN_U], rv[BN_U];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = fmaf(f[j], sc[j], sh[j]) + rr[j];
-    } else {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = fmaf(f[j], sc[j], sh[j]);
+    for (int u = 0; u < BN_U; ++u) {
+      const long ru = r + u * step;
+      if (ru < rows) {
+        v[u].load_nc(x + ru * C + off);
+        if (res) rv[u].load_nc(res + ru * C + off);
+      }
     }
-    if (relu) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+    for (int u = 0; u < BN_U; ++u) {
+      const long ru = r + u * step;
+      if (ru >= rows) break;
+      float f[8];
+      v[u].get(f);
+      if (res) {
+        float rr[8];
+        rv[u].get(rr);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = fmaf(f[j], sc[j], sh[j]) + rr[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = fmaf(f[j], sc[j], sh[j]);
+      }
+      if (relu) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = fmaxf(f[j], 0.f);
+      }
+      v[u].set(f);
+      v[u].store(y + ru * C + off);
     }
-    v.set(f);
-    v.store(y + r * C + off);
   }
 }
 __global__ void __launch_bounds__(256) bn_bwd_reduce_fast_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y,
@@ -417,26 +437,36 @@ __global__ void __launch_bounds__(256) bn_bwd_reduce_fast_kernel(const bf16* __r
     mu[j] = mean[m.cv * 8 + j];
   }
   const long off = (long)m.cv * 8;
-  for (long r = (long)blockIdx.x * m.rpb + m.r_in; r < rows; r += (long)gridDim.x * m.rpb) {
-    Vec16<bf16> vg, vx;
-    vg.load_nc(dy + r * C + off);
-    vx.load_nc(x + r * C + off);
-    float g[8], xf[8];
-    vg.get(g);
-    vx.get(xf);
-    if (relu) {
-      Vec16<bf16> vy;
-      vy.load_nc(y + r * C + off);
-      float yf[8];
-      vy.get(yf);
+  const long step = (long)gridDim.x * m.rpb;
+  for (long r = (long)blockIdx.x * m.rpb + m.r_in; r < rows; r += step * BN_UB) {
+    Vec16<bf16> vg[BN_UB], vx[BN_UB], vy[BN_UB];
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (yf[j] <= 0.f) g[j] = 0.f;
+    for (int u = 0; u < BN_UB; ++u) {
+      const long ru = r + u * step;
+      if (ru < rows) {
+        vg[u].load_nc(dy + ru * C + off);
+        vx[u].load_nc(x + ru * C + off);
+        if (relu) vy[u].load_nc(y + ru * C + off);
+      }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      s[j] += g[j];
-      q[j] = fmaf(g[j], xf[j] - mu[j], q[j]);
+    for (int u = 0; u < BN_UB; ++u) {
+      if (r + u * step >= rows) break;
+      float g[8], xf[8];
+      vg[u].get(g);
+      vx[u].get(xf);
+      if (relu) {
+        float yf[8];
+        vy[u].get(yf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (yf[j] <= 0.f) g[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        s[j] += g[j];
+        q[j] = fmaf(g[j], xf[j] - mu[j], q[j]);
+      }
     }
   }
 #pragma unroll
@@ -463,29 +493,40 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_fast_kernel(const bf16* __re
     d[j] = -a[j] * sums[c] * inv - b[j] * mean[c];
   }
   const long off = (long)m.cv * 8;
-  for (long r = (long)blockIdx.x * m.rpb + m.r_in; r < rows; r += (long)gridDim.x * m.rpb) {
-    Vec16<bf16> vg, vx;
-    vg.load_nc(dy + r * C + off);
-    vx.load_nc(x + r * C + off);
-    float g[8], xf[8];
-    vg.get(g);
-    vx.get(xf);
-    if (relu) {
-      Vec16<bf16> vy;
-      vy.load_nc(y + r * C + off);
-      float yf[8];
-      vy.get(yf);
+  const long step = (long)gridDim.x * m.rpb;
+  for (long r = (long)blockIdx.x * m.rpb + m.r_in; r < rows; r += step * BN_UB) {
+    Vec16<bf16> vg[BN_UB], vx[BN_UB], vy[BN_UB];
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (yf[j] <= 0.f) g[j] = 0.f;
+    for (int u = 0; u < BN_UB; ++u) {
+      const long ru = r + u * step;
+      if (ru < rows) {
+        vg[u].load_nc(dy + ru * C + off);
+        vx[u].load_nc(x + ru * C + off);
+        if (relu) vy[u].load_nc(y + ru * C + off);
+      }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) xf[j] = fmaf(a[j], g[j], fmaf(b[j], xf[j], d[j]));
-    vx.set(xf);
-    vx.store(dx + r * C + off);
-    if (dres) {
-      vg.set(g);
-      vg.store(dres + r * C + off);
+    for (int u = 0; u < BN_UB; ++u) {
+      const long ru = r + u * step;
+      if (ru >= rows) break;
+      float g[8], xf[8];
+      vg[u].get(g);
+      vx[u].get(xf);
+      if (relu) {
+        float yf[8];
+        vy[u].get(yf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (yf[j] <= 0.f) g[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) xf[j] = fmaf(a[j], g[j], fmaf(b[j], xf[j], d[j]));
+      vx[u].set(xf);
+      vx[u].store(dx + ru * C + off);
+      if (dres) {
+        vg[u].set(g);
+        vg[u].store(dres + ru * C + off);
+      }
     }
   }
 }
