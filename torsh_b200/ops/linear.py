@@ -21,10 +21,9 @@ def _wgrad_plan(m_out: int, n_out: int, k: int) -> tuple[int, int]:
     bn = 256 if n_out >= 256 else 128
     tiles = ((m_out + 127) // 128) * ((n_out + bn - 1) // bn)
     kb = (k + 63) // 64
-    # measured on B200 (K = 8192): the best split keeps tiles x splits within two waves of the 148 SMs and never
-    # exceeds 4 (32 tiles -> 4, 96 -> 3, 128 -> 2); deeper splits only add fp32 atomic traffic
-    want = max(1, min(4, 296 // max(tiles, 1)))
-    return bn, max(1, min(want, kb // 8 if kb >= 16 else 1))
+    # measured on B200: the best split keeps tiles x splits within two waves of the 148 SMs and leaves every split
+    # at least 32 K-blocks (K = 8192: 32 tiles -> 4, 96 -> 3, 128 -> 2); deeper splits only add fp32 atomic traffic
+    return bn, max(1, min(296 // max(tiles, 1), kb // 32))
 
 
 def _wgrad(dy2: torch.Tensor, x2: torch.Tensor, weight: torch.Tensor, layout: str):
