@@ -246,3 +246,85 @@ def test_models_forward_shapes():
     assert M.ResNet.resnet18(7)(torch.randn(1, 3, 64, 64)).shape == (1, 7)
     lm = M.LlamaModel(M.LlamaConfig.tiny())
     assert lm(ids).shape == (2, 16, 1024) and "resnet50" in M.list_models()
+
+
+def test_extra_layers_amp_and_second_order_optimizers():
+    import warnings
+
+    import torch
+
+    import torsh_b200 as tb
+    from torsh_b200 import nn
+    from torsh_b200.optim import mixed_precision as mp
+    from torsh_b200.optim import second_order as so
+    torch.manual_seed(0)
+    x = torch.randn(4, 8, 10, 10)
+    for layer in (nn.DepthwiseSeparableConv2d(8, 16), nn.WeightStandardizedConv2d(8, 16, 3, padding=1), nn.BatchRenorm2d(8),
+                  nn.VirtualBatchNorm2d(8), nn.SwitchableNorm2d(8), nn.StochasticDepth(0.5), nn.DropBlock2d(0.2, 3),
+                  nn.MBConvBlock(8, 8), nn.DenseBlock(8, 4, 2)):
+        y = layer(x)
+        assert y.shape[0] == 4 and torch.isfinite(y).all(), type(layer).__name__
+        layer.eval()
+        assert torch.isfinite(layer(x)).all()
+    assert nn.GlobalAvgPool2d()(x).shape == (4, 8) and nn.GlobalMaxPool2d()(x).shape == (4, 8)
+    sn = nn.SwitchableNorm2d(8)
+    with torch.no_grad():
+        sn.mean_w.copy_(torch.tensor([-50.0, -50.0, 50.0])); sn.var_w.copy_(sn.mean_w)     # pure batch-norm mixture
+    assert torch.allclose(sn(x), torch.nn.functional.batch_norm(x, None, None, training=True), atol=1e-4)
+    q, k, v = torch.randn(2, 5, 6), torch.randn(2, 7, 6), torch.randn(2, 7, 6)
+    out, att = nn.AdditiveAttention(6, 6, 12)(q, k, v)
+    assert out.shape == (2, 5, 6) and torch.allclose(att.sum(-1), torch.ones(2, 5))
+    assert nn.MultiplicativeAttention(6, 6)(q, k, v)[0].shape == (2, 5, 6)
+    assert nn.CrossAttention(16, 6, heads=4)(torch.randn(2, 5, 16), k).shape == (2, 5, 16)
+    fa = nn.FlexAttention(16, heads=2, pattern="sliding_window", window=3)
+    m = fa.mask(6, "cpu")
+    assert m[5, 3] and not m[5, 2] and not m[2, 3] and fa(torch.randn(2, 6, 16)).shape == (2, 6, 16)
+    assert nn.RelativePositionBias(4)(5, 7).shape == (4, 5, 7)
+    assert nn.interpolate_positions(torch.arange(8.0)[:, None].expand(8, 3), 15)[7].allclose(torch.full((3,), 3.5))
+    xm, ym = nn.mixup(x, torch.tensor([0, 1, 2, 3]), 0.4, num_classes=4)
+    assert xm.shape == x.shape and torch.allclose(ym.sum(1), torch.ones(4))
+    xc, yc = nn.cutmix(x, torch.tensor([0, 1, 2, 3]), 1.0, num_classes=4)
+    assert xc.shape == x.shape and torch.allclose(yc.sum(1), torch.ones(4))
+    # loss scaling: overflow skips the step and halves the scale, clean steps grow it back
+    lin = torch.nn.Linear(4, 2)
+    opt = torch.optim.SGD(lin.parameters(), lr=0.1)
+    sc = mp.GradScaler(init_scale=1024.0, growth_interval=2)
+    taken = []
+    for i in range(4):
+        opt.zero_grad()
+        sc.scale(lin(torch.ones(2, 4)).sum()).backward()
+        assert torch.allclose(lin.bias.grad, torch.full((2,), 2.0 * sc.get_scale()))
+        if i == 1:
+            lin.weight.grad[0, 0] = float("inf")
+        w_before = lin.weight.detach().clone()
+        taken.append(sc.step(opt))
+        assert torch.equal(lin.weight, w_before) == (not taken[-1])
+    assert taken == [True, False, True, True] and sc.get_scale() == 1024.0 and sc.stats["backoffs"] == 1
+    half = torch.nn.Linear(4, 2).to(torch.bfloat16)
+    mo = mp.MixedPrecisionOptimizer(half.parameters(), torch.optim.SGD, mp.BF16Config(), lr=0.1)
+    half(torch.ones(2, 4, dtype=torch.bfloat16)).sum().backward()
+    assert mo.step() and mo.masters[0].dtype == torch.float32 and half.weight.dtype == torch.bfloat16
+    # curvature-aware optimizers reduce a least-squares loss
+    X = torch.randn(64, 8); Y = X @ torch.randn(8, 3)
+
+    def fit(make, steps=60, graph=False, closure=False):
+        torch.manual_seed(1)
+        m = torch.nn.Linear(8, 3)
+        o = make(m)
+        l0 = ((m(X) - Y) ** 2).mean().item()
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            for _ in range(steps):
+                if closure:
+                    o.step(lambda: ((m(X) - Y) ** 2).mean())
+                    continue
+                o.zero_grad()
+                ((m(X) - Y) ** 2).mean().backward(create_graph=graph)
+                o.step()
+        return ((m(X) - Y) ** 2).mean().item() / l0
+    assert fit(lambda m: so.Shampoo(m.parameters(), lr=0.3, update_freq=1)) < 1e-3
+    assert fit(lambda m: so.AdaHessian(m.parameters(), lr=0.1), graph=True) < 1e-2
+    assert fit(lambda m: so.KFAC(m, lr=0.5, damping=0.1)) < 1e-6
+    assert fit(lambda m: so.NewtonCG(m.parameters()), steps=4, closure=True) < 1e-8
+    assert fit(lambda m: so.YellowFin(m.parameters(), lr=0.01), steps=200) < 0.05
+    assert tb.optim.ElasticAveragingSGD and tb.optim.DistributedOptimizer and tb.optim.AsyncSGD
