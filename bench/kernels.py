@@ -51,6 +51,7 @@ def main():
     ap.add_argument("--batch", type=int, default=4); ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=16); ap.add_argument("--dim", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--compare", action="store_true", help="gemm: also time torch.matmul on the same operands")
     ap.add_argument("--split-k", type=int, default=1, help="gemm: K splits (implies fp32 atomic accumulation, the weight-gradient path)")
     a = ap.parse_args()
     from torsh_b200 import _native as nv
@@ -69,6 +70,12 @@ def main():
             out = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
             ms = timeit(lambda: gemm(A, B, a_major=a.a_major, b_major=a.b_major, out=out, bn=a.bn), a.iters, flush)
         t = 2.0 * a.m * a.n * a.k / ms / 1e9
+        if a.compare:
+            Am = A if a.a_major == 0 else A.t()
+            Bm = B.t() if a.b_major == 0 else B
+            ref = torch.empty(a.m, a.n, device=dev, dtype=torch.bfloat16)
+            msl = timeit(lambda: torch.matmul(Am, Bm, out=ref), a.iters, flush)
+            print(f"  torch.matmul (cuBLAS) same shape: {msl*1e3:.1f} us, {2.0*a.m*a.n*a.k/msl/1e9:.0f} TFLOP/s")
         print(f"gemm {a.m}x{a.n}x{a.k} majors {a.a_major}{a.b_major} bn {a.bn} split_k {a.split_k}: {ms*1e3:.1f} us, {t:.0f} TFLOP/s = {t/tf:.2f} of {kind} bf16 peak")
     elif a.what in ("attn_fwd", "attn_bwd"):
         from torsh_b200.ops.attention import flash_attention

@@ -194,7 +194,23 @@ __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ out, 
   for (int j = 0; j < N; ++j) acc[j] = 0.f;
   const bool vec_ok = (c0 + N <= cols) && ((ld % N) == 0) && (((uintptr_t)x & 15) == 0);
   if (c0 < cols) {
-    for (long r = r0 + threadIdx.y; r < r1; r += 8) {
+    long r = r0 + threadIdx.y;
+    if (vec_ok) {
+      // four rows in flight per thread
+      for (; r + 24 < r1; r += 32) {
+        Vec16<T> t[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) t[u].load_nc(x + (r + 8 * u) * ld + c0);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          float f[N];
+          t[u].get(f);
+#pragma unroll
+          for (int j = 0; j < N; ++j) acc[j] += f[j];
+        }
+      }
+    }
+    for (; r < r1; r += 8) {
       if (vec_ok) {
         Vec16<T> t;
         t.load(x + r * ld + c0);
