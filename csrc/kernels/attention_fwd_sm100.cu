@@ -1,13 +1,16 @@
 // Flash attention forward for sm_100a (tcgen05 / TMEM / TMA), causal or full, head dim 64 or 128.
 //
-// One CTA per (batch, head, 128-query block), 320 threads:
+// Persistent CTAs (one per SM) walk the (batch, head, 128-query block) tiles, heaviest causal tiles first; the
+// three roles keep running counters across tiles, so the TMA warp already loads the next tile's Q / K / V and the
+// MMA warp already issues its first Q K^T while the softmax warps still normalise and store the previous tile.
+// 320 threads:
 //   warps 0-7  softmax: two threads per query row (= TMEM lane), each owning half of the key
 //              columns of a score block and half of the output columns. Read S = Q K^T from TMEM,
 //              online softmax in fp32 (exp2, running max / sum), write P as packed bf16 back to
 //              TMEM, accumulate O in registers from the per-block P V partials.
 //   warp 8     MMA issuer (one thread): S[j+1] = Q K[j+1]^T is issued before waiting for P[j],
 //              so the tensor core works on the next block while the softmax warps run.
-//   warp 9     TMA producer (one thread): Q once, K / V tiles through 2-deep rings.
+//   warp 9     TMA producer (one thread): Q through a 2-deep ring (one slot per tile), K / V tiles through 2-deep rings.
 // TMEM (512 columns): S0 | S1 (128 each, fp32) | P0 | P1 (64 each, bf16 pairs) | O partial (D).
 // Memory is O(S): nothing of size S x S is ever written. Q, K, V are addressed through 4-D tensor
 // maps [B, S, H, D] with arbitrary token stride, so the fused QKV projection output is consumed
@@ -38,14 +41,14 @@ struct FaFwdParams {
 template <int D>
 struct FaFwdSmem {
   static constexpr int TILE = 128 * D * 2;       // one Q / K / V tile
-  static constexpr int Q_OFF = 0;
-  static constexpr int K_OFF = TILE;             // 2 stages
-  static constexpr int V_OFF = 3 * TILE;         // 2 stages
-  static constexpr int BAR_OFF = 5 * TILE;
-  // q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_full, o_empty
-  static constexpr int NBARS = 15;
-  static constexpr int XMAX_OFF = BAR_OFF + NBARS * 8 + 16;   // float [2][2][128]: row-max / row-sum exchange
-  static constexpr int TOTAL = XMAX_OFF + 2 * 2 * 128 * 4;
+  static constexpr int Q_OFF = 0;                // 2 stages
+  static constexpr int K_OFF = 2 * TILE;         // 2 stages
+  static constexpr int V_OFF = 4 * TILE;         // 2 stages
+  static constexpr int BAR_OFF = 6 * TILE;
+  // q_full[2], q_empty[2], k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_full, o_empty
+  static constexpr int NBARS = 18;
+  static constexpr int XMAX_OFF = BAR_OFF + NBARS * 8 + 16;   // float [3][2][128]: row-max (2 buffers) / row-sum exchange
+  static constexpr int TOTAL = XMAX_OFF + 3 * 2 * 128 * 4;
   static constexpr int ALLOC = TOTAL + 1024;
 };
 
@@ -60,31 +63,32 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + L::BAR_OFF);
   uint64_t* q_full = bars;
-  uint64_t* k_full = bars + 1;
-  uint64_t* k_empty = bars + 3;
-  uint64_t* v_full = bars + 5;
-  uint64_t* v_empty = bars + 7;
-  uint64_t* s_full = bars + 9;
-  uint64_t* p_full = bars + 11;
-  uint64_t* o_full = bars + 13;
-  uint64_t* o_empty = bars + 14;
+  uint64_t* q_empty = bars + 2;
+  uint64_t* k_full = bars + 4;
+  uint64_t* k_empty = bars + 6;
+  uint64_t* v_full = bars + 8;
+  uint64_t* v_empty = bars + 10;
+  uint64_t* s_full = bars + 12;
+  uint64_t* p_full = bars + 14;
+  uint64_t* o_full = bars + 16;
+  uint64_t* o_empty = bars + 17;
   uint32_t* tmem_ptr = (uint32_t*)(bars + L::NBARS);
   volatile int* abort_flag = (volatile int*)(tmem_ptr + 1);
   volatile float* xmax = (volatile float*)(smem + L::XMAX_OFF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qb = (p.S + FA_BM - 1) / FA_BM;
-  // heavy (late) query blocks first so the causal triangle balances across SMs
-  const int qb = n_qb - 1 - (int)(blockIdx.x % n_qb);
-  const int bh = blockIdx.x / n_qb;
-  const int h = bh % p.H, b = bh / p.H;
-  const int q0 = qb * FA_BM;
   const int n_kv_all = (p.S + FA_BN - 1) / FA_BN;
-  const int n_kv = p.causal ? min(n_kv_all, qb + 1) : n_kv_all;
+  const int BH = p.B * p.H;
+  const int n_tiles = n_qb * BH;
+  // tile t -> (query block, batch*head): heavy (late) query blocks first, so the causal triangle balances over the SMs
+  auto tile_qb = [&](int t) { return n_qb - 1 - t / BH; };
+  auto tile_nkv = [&](int t) { return p.causal ? min(n_kv_all, tile_qb(t) + 1) : n_kv_all; };
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
     for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1);
@@ -112,22 +116,29 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       tma_prefetch_desc(&map_q);
       tma_prefetch_desc(&map_k);
       tma_prefetch_desc(&map_v);
-      mbar_expect_tx(q_full, L::TILE);
-#pragma unroll
-      for (int c = 0; c < KCH; ++c) tma_load_4d(smem + L::Q_OFF + c * 16384, &map_q, q_full, c * 64, h, q0, b);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
-        mbar_expect_tx(&k_full[s], L::TILE);
+      uint32_t it = 0, tcount = 0;  // K/V blocks and tiles handled so far by this CTA
+      for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++tcount) {
+        const int bh = t % BH, h = bh % p.H, b = bh / p.H, q0 = tile_qb(t) * FA_BM, n_kv = tile_nkv(t);
+        const int qs = tcount & 1;
+        mbar_wait(&q_empty[qs], ((tcount >> 1) & 1) ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
+        mbar_expect_tx(&q_full[qs], L::TILE);
 #pragma unroll
         for (int c = 0; c < KCH; ++c)
-          tma_load_4d(smem + L::K_OFF + s * L::TILE + c * 16384, &map_k, &k_full[s], c * 64, h, j * FA_BN, b);
-        mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
-        mbar_expect_tx(&v_full[s], L::TILE);
+          tma_load_4d(smem + L::Q_OFF + qs * L::TILE + c * 16384, &map_q, &q_full[qs], c * 64, h, q0, b);
+        for (int j = 0; j < n_kv; ++j, ++it) {
+          const int s = it & 1;
+          const uint32_t ph = (it >> 1) & 1;
+          mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
+          mbar_expect_tx(&k_full[s], L::TILE);
 #pragma unroll
-        for (int c = 0; c < KCH; ++c)
-          tma_load_4d(smem + L::V_OFF + s * L::TILE + c * 16384, &map_v, &v_full[s], c * 64, h, j * FA_BN, b);
+          for (int c = 0; c < KCH; ++c)
+            tma_load_4d(smem + L::K_OFF + s * L::TILE + c * 16384, &map_k, &k_full[s], c * 64, h, j * FA_BN, b);
+          mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
+          mbar_expect_tx(&v_full[s], L::TILE);
+#pragma unroll
+          for (int c = 0; c < KCH; ++c)
+            tma_load_4d(smem + L::V_OFF + s * L::TILE + c * 16384, &map_v, &v_full[s], c * 64, h, j * FA_BN, b);
+        }
       }
       if (*abort_flag) {
         uint64_t t0 = globaltimer_ns();
@@ -140,31 +151,55 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     if (lane == 0) {
       constexpr uint32_t idesc_qk = make_idesc_bf16(128, FA_BN, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, 0, 1);
-      const uint32_t q_base = smem_u32(smem + L::Q_OFF);
-      auto issue_qk = [&](int j) {
-        const int s = j & 1;
-        mbar_wait(&k_full[s], (j >> 1) & 1, abort_flag, p.status, TB_ERR_WAIT_FULL);
+      // Two cursors over the same flattened (tile, K/V block) sequence: `a` issues S = Q K^T, `b` issues O = P V one
+      // block behind, so the score MMA of the next block (possibly of the next tile) runs while the softmax warps work.
+      struct Cursor {
+        int t, j, n_kv;
+        uint32_t it, tcount;
+      };
+      auto advance = [&](Cursor& c) {
+        ++c.it;
+        if (++c.j == c.n_kv) {
+          c.t += gridDim.x;
+          ++c.tcount;
+          c.j = 0;
+          c.n_kv = c.t < n_tiles ? tile_nkv(c.t) : 0;
+        }
+      };
+      auto issue_qk = [&](const Cursor& c) {
+        const int s = c.it & 1, qs = c.tcount & 1;
+        if (c.j == 0) mbar_wait(&q_full[qs], (c.tcount >> 1) & 1, abort_flag, p.status, TB_ERR_WAIT_FULL);
+        mbar_wait(&k_full[s], (c.it >> 1) & 1, abort_flag, p.status, TB_ERR_WAIT_FULL);
         tc_fence_after();
+        const uint32_t q_base = smem_u32(smem + L::Q_OFF + qs * L::TILE);
         const uint32_t k_base = smem_u32(smem + L::K_OFF + s * L::TILE);
 #pragma unroll
-        for (int c = 0; c < KCH; ++c)
+        for (int ch = 0; ch < KCH; ++ch)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_ss(tmem_base + TM_S + s * 128,
-                    make_smem_desc_sw128(q_base + c * 16384 + k * 32, 16, 1024),
-                    make_smem_desc_sw128(k_base + c * 16384 + k * 32, 16, 1024), idesc_qk,
-                    (c | k) ? 1u : 0u);
+                    make_smem_desc_sw128(q_base + ch * 16384 + k * 32, 16, 1024),
+                    make_smem_desc_sw128(k_base + ch * 16384 + k * 32, 16, 1024), idesc_qk,
+                    (ch | k) ? 1u : 0u);
         umma_commit(&s_full[s]);
         umma_commit(&k_empty[s]);
+        if (c.j == c.n_kv - 1) umma_commit(&q_empty[qs]);  // last score MMA of the tile: its Q slot may be refilled
       };
-      mbar_wait(q_full, 0, abort_flag, p.status, TB_ERR_WAIT_FULL);
-      issue_qk(0);
-      for (int j = 0; j < n_kv; ++j) {
-        const int s = j & 1;
-        if (j + 1 < n_kv) issue_qk(j + 1);
-        mbar_wait(&p_full[s], (j >> 1) & 1, abort_flag, p.status, TB_ERR_WAIT_MISC);
-        mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, p.status, TB_ERR_WAIT_FULL);
-        mbar_wait(o_empty, (j & 1) ^ 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_EMPTY);
+      Cursor a{(int)blockIdx.x, 0, 0, 0u, 0u}, bcur{(int)blockIdx.x, 0, 0, 0u, 0u};
+      a.n_kv = bcur.n_kv = a.t < n_tiles ? tile_nkv(a.t) : 0;
+      if (a.t < n_tiles) {
+        issue_qk(a);
+        advance(a);
+      }
+      while (bcur.t < n_tiles) {
+        if (a.t < n_tiles) {
+          issue_qk(a);
+          advance(a);
+        }
+        const int s = bcur.it & 1;
+        mbar_wait(&p_full[s], (bcur.it >> 1) & 1, abort_flag, p.status, TB_ERR_WAIT_MISC);
+        mbar_wait(&v_full[s], (bcur.it >> 1) & 1, abort_flag, p.status, TB_ERR_WAIT_FULL);
+        mbar_wait(o_empty, (bcur.it & 1) ^ 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_EMPTY);
         tc_fence_after();
         const uint32_t v_base = smem_u32(smem + L::V_OFF + s * L::TILE);
 #pragma unroll
@@ -173,6 +208,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
                   make_smem_desc_sw128(v_base + kk * 2048, 16384, 1024), idesc_pv, kk ? 1u : 0u);
         umma_commit(o_full);
         umma_commit(&v_empty[s]);
+        advance(bcur);
       }
     }
   } else {
@@ -184,17 +220,20 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     // block (one shared-memory exchange + one named barrier); the row sums meet once at the end.
     const int half = warp >> 2;                 // 0: columns 0-63, 1: columns 64-127
     const int row = (warp & 3) * 32 + lane;     // row inside the query block = TMEM lane
-    const int qi = q0 + row;                    // global query index
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
     constexpr int DH = D / 2;                   // output columns owned by this thread
+    uint32_t it = 0;                            // K/V blocks handled so far by this CTA (all tiles)
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x) {
+    const int bh = t % BH, h = bh % p.H, b = bh / p.H, q0 = tile_qb(t) * FA_BM, n_kv = tile_nkv(t);
+    const int qi = q0 + row;                    // global query index
     float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
     float o[DH];
 #pragma unroll
     for (int i = 0; i < DH; ++i) o[i] = 0.f;
 
-    auto accumulate_o = [&](int jdone) {
-      mbar_wait(o_full, jdone & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
+    auto accumulate_o = [&](uint32_t it_done) {
+      mbar_wait(o_full, it_done & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
 #pragma unroll
       for (int c = 0; c < DH / 32; ++c) {
@@ -208,12 +247,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       mbar_arrive(o_empty);
     };
 
-    for (int j = 0; j < n_kv; ++j) {
-      const int s = j & 1;
+    for (int j = 0; j < n_kv; ++j, ++it) {
+      const int s = it & 1;
       const int kv0 = j * FA_BN + half * 64;   // first key column of this thread's half
       const bool need_mask = (p.causal && j * FA_BN + FA_BN - 1 > q0) || (j * FA_BN + FA_BN > p.S);
       const int col_limit = p.causal ? min(qi, p.S - 1) : p.S - 1;  // last visible key index
-      mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
+      mbar_wait(&s_full[s], (it >> 1) & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
       const uint32_t ts = tmem_base + TM_S + s * 128 + half * 64 + lane_off;
       uint32_t v0[32], v1[32];
@@ -230,9 +269,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         }
         mx = fmaxf(mx, fmaxf(x0, x1));
       }
-      xmax[(j & 1) * 256 + half * 128 + row] = mx;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      mx = fmaxf(m, fmaxf(mx, xmax[(j & 1) * 256 + (half ^ 1) * 128 + row]));
+      xmax[s * 256 + half * 128 + row] = mx;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");  // only the two warps that share these rows
+      mx = fmaxf(m, fmaxf(mx, xmax[s * 256 + (half ^ 1) * 128 + row]));
       const float msafe = (mx == -INFINITY) ? 0.f : mx;
       const float alpha = exp2f((m - msafe) * sl2);
       const float moff = msafe * sl2;
@@ -266,15 +305,15 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       mbar_arrive(&p_full[s]);
       l = l * alpha + rowsum;
       m = mx;
-      if (j > 0) accumulate_o(j - 1);
+      if (j > 0) accumulate_o(it - 1);
       alpha_prev = alpha;
     }
-    accumulate_o(n_kv - 1);
-    // the two halves of a row add their partial sums, through the exchange buffer that the last block did
-    // not use (its readers may still be behind this thread)
-    xmax[(n_kv & 1) * 256 + half * 128 + row] = l;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    l += xmax[(n_kv & 1) * 256 + (half ^ 1) * 128 + row];
+    accumulate_o(it - 1);
+    // the two halves of a row add their partial sums through a third exchange buffer: the row-max buffers may
+    // already be in use by a faster thread's next block or next tile
+    xmax[512 + half * 128 + row] = l;
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");
+    l += xmax[512 + (half ^ 1) * 128 + row];
     if (qi < p.S) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* orow = p.O + ((size_t)b * p.S + qi) * p.o_stride + (size_t)h * D + half * DH;
@@ -289,6 +328,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       }
       if (p.LSE && half == 0) p.LSE[((size_t)b * p.H + h) * p.S + qi] = (l > 0.f) ? (m * p.scale + logf(l)) : -INFINITY;
     }
+    }  // tile loop
   }
 
   tc_fence_before();
@@ -326,7 +366,8 @@ TB_EXPORT int tb_flash_attn_fwd(const void* q, const void* k, const void* v, voi
   if ((r = make_bshd_map(&mv, v, B, S, H, D, kv_stride))) return r;
   FaFwdParams p{(__nv_bfloat16*)o, lse, B, S, H, o_stride, scale, causal, status};
   const int n_qb = (S + FA_BM - 1) / FA_BM;
-  const long grid = (long)n_qb * B * H;
+  const long tiles = (long)n_qb * B * H;
+  const long grid = tiles < sm_count() ? tiles : sm_count();  // persistent CTAs, one per SM
   if (D == 64) {
     static bool cfg = false;
     if (!cfg) { TB_CUDA_CHECK(cudaFuncSetAttribute(fa_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaFwdSmem<64>::ALLOC)); cfg = true; }
