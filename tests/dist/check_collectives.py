@@ -247,6 +247,55 @@ def check_ddp(dev):
     return ok
 
 
+def check_moe(dev):
+    """Peer-memory MoE dispatch / combine against a dense evaluation of the same routing with all experts local."""
+    from torsh_b200 import _native as nv
+    from torsh_b200.parallel.expert_parallel import ExpertParallelismConfig, MoELayer
+    rank, world = dist.get_rank(), dist.get_world_size()
+    H, Fh, E, T = 256, 512, 4 * world, 192
+    cfg = ExpertParallelismConfig(num_experts=E, top_k=2, capacity_factor=float(E))      # no token is dropped
+    torch.manual_seed(5)
+    layer = MoELayer(H, Fh, cfg, group=dist.group.WORLD).to(dev).to(torch.bfloat16)
+    with torch.no_grad():                                  # same router everywhere, experts differ per rank
+        torch.manual_seed(50 + rank)
+        layer.w1.normal_(0, 0.05); layer.w2.normal_(0, 0.05)
+    torch.manual_seed(500 + rank)
+    x = torch.randn(T, H, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    dy = torch.randn(T, H, device=dev, dtype=torch.bfloat16)
+    y, aux = layer(x)
+    (y.float() * dy.float()).sum().backward()
+    torch.cuda.synchronize()
+    nv.check_status()
+    got = [y.detach().float(), x.grad.float(), layer.router.gate.grad.float(), layer.w1.grad.float(), layer.w2.grad.float()]
+    # dense oracle in fp32 with every expert's weights gathered
+    w1 = [torch.empty_like(layer.w1.data) for _ in range(world)]; w2 = [torch.empty_like(layer.w2.data) for _ in range(world)]
+    dist.all_gather(w1, layer.w1.data); dist.all_gather(w2, layer.w2.data)
+    W1 = torch.cat(w1).float().requires_grad_(); W2 = torch.cat(w2).float().requires_grad_()
+    xr = x.detach().float().requires_grad_()
+    gate = layer.router.gate.detach().float().requires_grad_()
+    probs = torch.softmax(xr.to(torch.bfloat16).float() @ gate.t(), -1)
+    wts, idx = probs.topk(2, -1)
+    wts = wts / wts.sum(-1, keepdim=True)
+    ref = torch.zeros(T, H, device=dev)
+    for k in range(2):
+        for e in range(E):
+            m = idx[:, k] == e
+            if m.any():
+                h = torch.nn.functional.gelu(xr[m] @ W1[e]) @ W2[e]
+                ref = ref.index_add(0, m.nonzero().flatten(), wts[m, k, None] * h)
+    (ref * dy.float()).sum().backward()
+    dW1, dW2 = W1.grad.clone(), W2.grad.clone()
+    dist.all_reduce(dW1); dist.all_reduce(dW2)
+    el = E // world
+    want = [ref.detach(), xr.grad, gate.grad, dW1[rank * el:(rank + 1) * el], dW2[rank * el:(rank + 1) * el]]
+    ok = True
+    for name, a, b in zip(("y", "dx", "dgate", "dW1", "dW2"), got, want):
+        rel = ((a - b).abs().max() / b.abs().max().clamp(min=1e-6)).item()
+        log(f"moe {name}: rel err {rel:.4f}")
+        ok &= rel < 0.06
+    return ok
+
+
 def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -262,6 +311,8 @@ def main():
         ok &= check_tp(dev)
     if "ddp" in what:
         ok &= check_ddp(dev)
+    if "moe" in what:
+        ok &= check_moe(dev)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     log("ALL CHECKS PASSED" if flag.item() == 1 else "CHECKS FAILED")
