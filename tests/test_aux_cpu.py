@@ -160,3 +160,37 @@ def test_fuzz_trsh_roundtrip(shape, dtype):
     t = (torch.arange(n, dtype=torch.float32).reshape(shape) * 0.5 - 3).to(dtype)
     back, meta = trsh.decode_trsh(trsh.encode_trsh(t))
     assert back.dtype == t.dtype and tuple(back.shape) == tuple(t.shape) and torch.equal(back, t)
+
+
+def test_streaming_tensor_file_and_function_registry(tmp_path):
+    from torsh_b200.autograd import functions as fn
+    from torsh_b200.serialize.streaming import LazyTensor, StreamingReader, StreamingWriter
+    m = torch.nn.Sequential(torch.nn.Linear(5, 7), torch.nn.BatchNorm1d(7))
+    path = tmp_path / "model.trsx"
+    with StreamingWriter(path) as w:
+        w.write_state_dict(m.state_dict())
+        w.write("extra/bf16", torch.arange(6, dtype=torch.bfloat16).reshape(2, 3))
+        with pytest.raises(KeyError):
+            w.write("0.weight", torch.zeros(1))
+    with StreamingReader(path) as r:
+        assert "0.weight" in r and r.shape("0.weight") == (7, 5) and len(r) == len(m.state_dict()) + 1 and r.loads == 0
+        lazy = LazyTensor(r, "extra/bf16")
+        assert lazy.shape == (2, 3) and r.loads == 0 and lazy.get().dtype == torch.bfloat16 and r.loads == 1
+        m2 = torch.nn.Sequential(torch.nn.Linear(5, 7), torch.nn.BatchNorm1d(7))
+        assert r.load_into(m2) == []
+        assert all(torch.equal(a, b) for a, b in zip(m.state_dict().values(), m2.state_dict().values()))
+    reg = fn.FunctionRegistry()
+    reg.register("square", forward=lambda ctx, x: (ctx.save_for_backward(x), x * x)[1],
+                 backward=lambda ctx, g: 2 * ctx.saved_tensors[0] * g)
+    reg.register("double", forward=lambda ctx, x: 2 * x, backward=lambda ctx, g: 2 * g)
+    x = torch.tensor([3.0], requires_grad=True)
+    reg.compose("square", "double")(x).backward()
+    assert x.grad.item() == 12.0 and reg.names() == ["double", "square"]
+    with pytest.raises(KeyError):
+        reg.get("nope")
+    ev = [dict(name="step", start_us=0, duration_us=100), dict(name="fwd", start_us=0, duration_us=40),
+          dict(name="gemm", start_us=5, duration_us=20), dict(name="bwd", start_us=40, duration_us=50)]
+    lines = fn.folded_stacks(ev)
+    assert lines == ["step 10", "step;bwd 50", "step;fwd 20", "step;fwd;gemm 20"]
+    diff = fn.differential(lines, ["step 10", "step;bwd 80", "step;fwd 20"])
+    assert diff[0] == ("step;bwd", 50, 80)
