@@ -93,6 +93,9 @@ def main():
     ap.add_argument("--model", default="gpt2-medium", choices=["gpt2-medium", "gpt2-small", "gpt2-tiny"])
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=1024)
+    ap.add_argument("--fsdp-comm-blocks", type=int, default=0, help="CTAs of the fused FSDP kernel while it overlaps backward")
+    ap.add_argument("--fsdp-no-overlap", action="store_true", help="run every FSDP unit after backward instead of from hooks")
+    ap.add_argument("--fsdp-nvls", type=int, default=None, help="1 / 0: force NVLS multimem on / off in the fused FSDP kernel")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -126,7 +129,15 @@ def main():
     parallel = None
     if world > 1:
         from torsh_b200.parallel.fsdp import FlatFSDP
-        parallel = FlatFSDP(dist.group.WORLD)
+        from torsh_b200.parallel.fsdp import FsdpConfig
+        fc = FsdpConfig()
+        if args.fsdp_comm_blocks:
+            fc.comm_blocks = args.fsdp_comm_blocks
+        if args.fsdp_no_overlap:
+            fc.overlap = False
+        if args.fsdp_nvls is not None:
+            fc.use_nvls = bool(args.fsdp_nvls)
+        parallel = FlatFSDP(dist.group.WORLD, fc)
     trainer = CausalLMTrainer(model, lr=3e-4, weight_decay=0.01, batch_size=B, seq_len=S,
                               use_graph=not args.no_graph, parallel=parallel)
 

@@ -26,7 +26,7 @@
 namespace tb {
 
 constexpr int FSDP_THREADS = 512;
-constexpr int FSDP_MAX_BLOCKS = 64;
+constexpr int FSDP_MAX_BLOCKS = 320;  // one cross-rank barrier slot per CTA (the flag buffer has 320 slots)
 
 struct FsdpArgs {
   PeerTable grads;   // symmetric fp32 gradient buffer (full flat range)
