@@ -73,6 +73,12 @@ struct GemmParams {
   int rank, world;
   int m_rot;                 // m-tiles are visited starting at this tile (own shard first / last)
   int tma_store;             // bf16 output leaves through shared memory + TMA tensor stores (out_maps)
+  // Implicit-GEMM 3x3 / stride 1 / pad 1 convolution over a channels-last activation [N, H, W, C] (map_a is then a
+  // 4-D map with box {64, W, TH, TN}): an M tile is TN images x TH full image rows (TN * TH * W <= 128 rows, which
+  // are consecutive rows of the [N*H*W, Cout] output), K runs over 9 taps x C/64 channel chunks, and tap (kh, kw)
+  // simply shifts the box by (kh - 1, kw - 1); the zero fill of out-of-range coordinates is the padding.
+  int conv;                  // 0 off, 1 forward (B K-major [Cout, 9*C]), 2 input gradient (taps flipped, B MN-major)
+  int cv_H, cv_W, cv_TH, cv_TN, cv_tiles_h, cv_cchunks, cv_a_bytes, cv_N;
 };
 
 template <int BN, int STAGES>
@@ -125,6 +131,15 @@ __device__ __forceinline__ void decode_work(const GemmParams& p, int work, int& 
   }
   kb0 = ks * p.kb_per_split;
   kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+}
+
+// Convolution mode: first output row and number of valid rows of M tile m_t.
+__device__ __forceinline__ void conv_tile(const GemmParams& p, int m_t, int& n0, int& h0, long& base_row, int& valid) {
+  const int it = m_t / p.cv_tiles_h, ht = m_t - it * p.cv_tiles_h;
+  n0 = it * p.cv_TN;
+  h0 = ht * p.cv_TH;
+  base_row = ((long)n0 * p.cv_H + h0) * p.cv_W;
+  valid = min(p.cv_TN, p.cv_N - n0) * min(p.cv_TH, p.cv_H - h0) * p.cv_W;
 }
 
 // Bounded wait on a flag in this GPU's own memory (written by a copy CTA of the same launch).
@@ -363,8 +378,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           mbar_wait(&empty[s], phase ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
           uint8_t* sa = smem + s * L::STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
-          mbar_expect_tx(&full[s], L::STAGE_BYTES);
-          if (A_MAJOR == 0) {
+          mbar_expect_tx(&full[s], p.conv ? (uint32_t)(p.cv_a_bytes + L::B_TILE_BYTES) : (uint32_t)L::STAGE_BYTES);
+          if (A_MAJOR == 0 && p.conv) {
+            const int tap = kb / p.cv_cchunks, cc = kb - tap * p.cv_cchunks;
+            const int kh = tap / 3, kw = tap - kh * 3;
+            int n0, h0, valid;
+            long base_row;
+            conv_tile(p, m_t, n0, h0, base_row, valid);
+            tma_load_4d(sa, &map_a, &full[s], cc * 64, kw - 1, h0 + kh - 1, n0);
+          } else if (A_MAJOR == 0) {
             tma_load_2d(sa, &map_a, &full[s], kb * BK, m_t * BM);
           } else {
 #pragma unroll
@@ -373,6 +395,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           if (B_MAJOR == 0) {
             tma_load_2d(sb, &map_b, &full[s], kb * BK, n_t * BN);
+          } else if (p.conv == 2) {
+            // input gradient: weights [Cout, 9 * Cin] read MN-major; tap t of the gradient pairs with tap 8 - t of the
+            // forward filter, whose Cin columns start at (8 - t) * Cin; the K rows are the Cout chunk
+            const int tap = kb / p.cv_cchunks, cc = kb - tap * p.cv_cchunks;
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sb + c * (64 * BK * 2), &map_b, &full[s], (8 - tap) * p.N + n_t * BN + c * 64, cc * BK);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c)
@@ -445,8 +474,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       decode_work(p, work, m_t, n_t, kb0, kb1);
       mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
-      const int row = m_t * BM + q * 32 + lane;
-      const bool row_ok = row < p.M;
+      int row = m_t * BM + q * 32 + lane;
+      bool row_ok = row < p.M;
+      if (p.conv) {
+        int n0, h0, valid;
+        long base_row;
+        conv_tile(p, m_t, n0, h0, base_row, valid);
+        row = (int)base_row + q * 32 + lane;
+        row_ok = (q * 32 + lane) < valid;
+      }
       const bool add_bias = (flags & EPI_BIAS) && (kb0 == 0);
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -659,6 +695,8 @@ struct TpFusion {
   const unsigned* epoch_ptr = nullptr;  // kind 2
   unsigned* ready = nullptr;            // kind 2: local per-tile flags
   int copy_ctas = 0;                    // kind 2
+  // implicit-GEMM convolution (kind 3): A is the channels-last activation [cv_n, cv_h, cv_w, K / 9]
+  int cv_n = 0, cv_h = 0, cv_w = 0, cv_mode = 0;
 };
 
 static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, int K, int a_major,
@@ -673,6 +711,21 @@ TB_EXPORT int tb_gemm_bf16(const void* A, const void* B, void* D, int M, int N, 
   TB_ENSURE_DEVICE();
   return gemm_dispatch(A, B, D, M, N, K, a_major, b_major, lda, ldb, ldd, bias, residual, ldr, preact, aux, flags,
                        split_k, bn, status, stream, TpFusion{});
+}
+
+// 3x3 / stride 1 / pad 1 convolution as an implicit GEMM (no im2col buffer). x: channels-last bf16 [n, h, w, c] with
+// c % 64 == 0 and w <= 128. mode 1 (forward): wmat = [cout, 9*c] (taps row-major, channels innermost), y = [n*h*w, cout].
+// mode 2 (input gradient): x is the output gradient [n, h, w, cout_fwd] (so c = cout_fwd), wmat is the SAME forward
+// matrix [cout_fwd, 9*cin] and y = [n*h*w, cin]; `cout` is then the number of output columns cin.
+TB_EXPORT int tb_conv3x3_gemm(const void* x, const void* wmat, void* y, int n, int h, int w, int c, int cout, int mode,
+                              int ldw, int ldy, int bn, int* status, cudaStream_t stream) {
+  TB_ENSURE_DEVICE();
+  if (mode != 1 && mode != 2) TB_FAIL(TB_E_ARG, "conv3x3_gemm: mode must be 1 (forward) or 2 (input gradient)");
+  TpFusion tp;
+  tp.kind = 3;
+  tp.cv_n = n; tp.cv_h = h; tp.cv_w = w; tp.cv_mode = mode;
+  return gemm_dispatch(x, wmat, y, n * h * w, cout, 9 * c, 0, mode == 1 ? 0 : 1, c, ldw, ldy, nullptr, nullptr, 0, nullptr,
+                       nullptr, 0, 1, bn, status, stream, tp);
 }
 
 // Row-parallel linear with sequence parallelism: partial = A[M, K_local] * B[N, K_local]^T is
@@ -741,6 +794,21 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
   p.status = status;
   p.rank = tp.rank;
   p.world = tp.world;
+  if (tp.kind == 3) {
+    const int C = K / 9, H = tp.cv_h, W = tp.cv_w, Nimg = tp.cv_n;
+    if (a_major != 0 || K != 9 * C || (C & 63) || W > 128 || H < 1 || W < 1 || M != Nimg * H * W)
+      TB_FAIL(TB_E_ARG, "conv gemm: needs K-major A, channels %% 64 == 0, W <= 128 and M = N*H*W");
+    if (split_k != 1 || (flags & (EPI_ATOMIC | EPI_ACCUM))) TB_FAIL(TB_E_ARG, "conv gemm: no split-K / accumulate");
+    p.conv = tp.cv_mode;
+    p.cv_H = H; p.cv_W = W; p.cv_N = Nimg;
+    if (H * W <= 128) { p.cv_TH = H; p.cv_TN = 128 / (H * W); }
+    else              { p.cv_TH = 128 / W; p.cv_TN = 1; }
+    if (p.cv_TN > Nimg) p.cv_TN = Nimg;
+    p.cv_tiles_h = (H + p.cv_TH - 1) / p.cv_TH;
+    p.cv_cchunks = C / 64;
+    p.cv_a_bytes = 128 * W * p.cv_TH * p.cv_TN;
+    p.tiles_m = ((Nimg + p.cv_TN - 1) / p.cv_TN) * p.cv_tiles_h;
+  }
   if (tp.kind == 1) {
     p.rs_rows = M / tp.world;
     for (int i = 0; i < tp.world; ++i) p.rs_dst[i] = const_cast<void*>(tp.peers[i]);
@@ -771,12 +839,22 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
   {
     uint64_t dims[2], str[1];
     uint32_t box[2];
-    if (a_major == 0) { dims[0] = K; dims[1] = M; box[0] = BK; box[1] = BM; }
-    else              { dims[0] = M; dims[1] = K; box[0] = 64; box[1] = BK; }
-    str[0] = (uint64_t)lda * 2;
-    int r = make_tmap(&ma, A, 2, 2, dims, str, box);
+    int r;
+    if (tp.kind == 3) {
+      const uint64_t C = (uint64_t)K / 9;
+      uint64_t d4[4] = {C, (uint64_t)tp.cv_w, (uint64_t)tp.cv_h, (uint64_t)tp.cv_n};
+      uint64_t s4[3] = {C * 2, (uint64_t)tp.cv_w * C * 2, (uint64_t)tp.cv_h * tp.cv_w * C * 2};
+      uint32_t b4[4] = {64, (uint32_t)tp.cv_w, (uint32_t)p.cv_TH, (uint32_t)p.cv_TN};
+      r = make_tmap(&ma, A, 2, 4, d4, s4, b4);
+    } else {
+      if (a_major == 0) { dims[0] = K; dims[1] = M; box[0] = BK; box[1] = BM; }
+      else              { dims[0] = M; dims[1] = K; box[0] = 64; box[1] = BK; }
+      str[0] = (uint64_t)lda * 2;
+      r = make_tmap(&ma, A, 2, 2, dims, str, box);
+    }
     if (r) return r;
     if (b_major == 0) { dims[0] = K; dims[1] = N; box[0] = BK; box[1] = bn; }
+    else if (tp.kind == 3) { dims[0] = (uint64_t)9 * N; dims[1] = (uint64_t)K / 9; box[0] = 64; box[1] = BK; }
     else              { dims[0] = N; dims[1] = K; box[0] = 64; box[1] = BK; }
     str[0] = (uint64_t)ldb * 2;
     r = make_tmap(&mb, B, 2, 2, dims, str, box);
@@ -792,7 +870,7 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
       return !(e && e[0] == '0');
     }();
     auto al16 = [](const void* q) { return ((uintptr_t)q & 15) == 0; };
-    bool ok = enabled && !(flags & (EPI_OUT_F32 | EPI_ACCUM | EPI_ATOMIC)) && (N % 64) == 0 && (ldd & 7) == 0 &&
+    bool ok = enabled && tp.kind != 3 && !(flags & (EPI_OUT_F32 | EPI_ACCUM | EPI_ATOMIC)) && (N % 64) == 0 && (ldd & 7) == 0 &&
               split_k == 1 && (!bias || al16(bias)) && (!residual || (al16(residual) && (ldr & 7) == 0)) &&
               (!preact || al16(preact)) && (!aux || al16(aux));
     uint64_t dims[2], str[1] = {(uint64_t)ldd * 2};

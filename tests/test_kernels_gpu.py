@@ -305,7 +305,8 @@ def test_gnn_scatter_fwd_bwd(dtype):
 
 # ------------------------------------------------------------------ conv / BatchNorm / pooling (channels-last)
 @pytest.mark.parametrize("geom", [(3, 64, 7, 2, 3, 34), (64, 64, 1, 1, 0, 20), (64, 128, 3, 1, 1, 19), (128, 128, 3, 2, 1, 18),
-                                  (256, 512, 1, 2, 0, 14)])
+                                  (256, 512, 1, 2, 0, 14), (128, 64, 3, 1, 1, 5), (256, 256, 3, 1, 1, 14), (64, 64, 3, 1, 1, 56),
+                                  (64, 72, 3, 1, 1, 9)])
 def test_conv2d_nhwc_fwd_bwd(geom):
     from torsh_b200.ops.conv import conv2d_nhwc
     ci, co, k, stride, pad, hw = geom

@@ -45,6 +45,20 @@ def _im2col(x, kh, kw, stride, pad, kpad):
     return cols
 
 
+def _conv3x3_gemm(x, wm, cout, mode):
+    """Implicit-GEMM 3x3/1/1 convolution (mode 1) or its input gradient (mode 2): no column matrix is written."""
+    n, h, w, c = x.shape
+    y = torch.empty(n * h * w, cout, dtype=torch.bfloat16, device=x.device)
+    st = nv.status_word(x.device)
+    call("tb_conv3x3_gemm", [P, P, P, I, I, I, I, I, I, I, I, I, P, P], x.data_ptr(), wm.data_ptr(), y.data_ptr(), n, h, w, c,
+         cout, mode, wm.stride(0), cout, 0, st.data_ptr(), nv.stream_ptr())
+    return y
+
+
+def _implicit_ok(c, co, kh, kw, stride, pad, w):
+    return kh == 3 and kw == 3 and stride == 1 and pad == 1 and c % 64 == 0 and co % 64 == 0 and w <= 128
+
+
 def _wgrad_split(m_out, n_out, k):
     bn = 256 if n_out >= 256 else 128
     tiles = ((m_out + 127) // 128) * ((n_out + bn - 1) // bn)
@@ -64,23 +78,33 @@ class _Conv2dFn(torch.autograd.Function):
         kpad = (k + 7) // 8 * 8
         ho, wo = _out_hw(h, w, kh, stride, pad)
         direct = kh == 1 and kw == 1 and stride == 1 and pad == 0
+        implicit = _implicit_ok(c, co, kh, kw, stride, pad, w)
         wm = _weight_matrix(weight, kpad)
-        a = x.reshape(n * h * w, c) if direct else _im2col(x, kh, kw, stride, pad, kpad)
-        y = gemm(a, wm)
+        if implicit:
+            a = x                                    # the column matrix is rebuilt in backward for the weight gradient only
+            y = _conv3x3_gemm(x, wm, co, 1)
+        else:
+            a = x.reshape(n * h * w, c) if direct else _im2col(x, kh, kw, stride, pad, kpad)
+            y = gemm(a, wm)
         ctx.save_for_backward(a, wm)
-        ctx.geom = (n, h, w, c, co, kh, kw, stride, pad, ho, wo, k, kpad, direct)
+        ctx.geom = (n, h, w, c, co, kh, kw, stride, pad, ho, wo, k, kpad, direct, implicit)
         ctx.wshape, ctx.wdtype = weight.shape, weight.dtype
         return y.view(n, ho, wo, co)
 
     @staticmethod
     def backward(ctx, dy):
         a, wm = ctx.saved_tensors
-        n, h, w, c, co, kh, kw, stride, pad, ho, wo, k, kpad, direct = ctx.geom
+        n, h, w, c, co, kh, kw, stride, pad, ho, wo, k, kpad, direct, implicit = ctx.geom
         dy2 = dy.reshape(n * ho * wo, co)
         if not dy2.is_contiguous():
             dy2 = dy2.contiguous()
         dx = dw = None
-        if ctx.needs_input_grad[0]:
+        if implicit:
+            if ctx.needs_input_grad[0]:
+                dx = _conv3x3_gemm(dy2.view(n, ho, wo, co), wm, c, 2).view(n, h, w, c)
+            if ctx.needs_input_grad[1]:
+                a = _im2col(a, kh, kw, stride, pad, kpad)
+        elif ctx.needs_input_grad[0]:
             dcols = gemm(dy2, wm, b_major=1)                       # [M, Kpad] = dy · W
             if direct:
                 dx = dcols.view(n, h, w, c)
