@@ -77,7 +77,10 @@ struct GemmParams {
   // 4-D map with box {64, W, TH, TN}): an M tile is TN images x TH full image rows (TN * TH * W <= 128 rows, which
   // are consecutive rows of the [N*H*W, Cout] output), K runs over 9 taps x C/64 channel chunks, and tap (kh, kw)
   // simply shifts the box by (kh - 1, kw - 1); the zero fill of out-of-range coordinates is the padding.
-  int conv;                  // 0 off, 1 forward (B K-major [Cout, 9*C]), 2 input gradient (taps flipped, B MN-major)
+  int conv;                  // 0 off, 1 forward (B K-major [Cout, 9*C]), 2 input gradient (taps flipped, B MN-major),
+                             // 3 weight gradient: D[Cout, 9*Cin] += dy^T x_shifted, K runs over pixel blocks of
+                             // TN images x TH image rows (<= 64 pixels; unused K rows of a stage stay zero), both
+                             // operands are 4-D boxes read MN-major, every 64-column chunk of B carries its own tap
   int cv_H, cv_W, cv_TH, cv_TN, cv_tiles_h, cv_cchunks, cv_a_bytes, cv_N;
 };
 
@@ -350,6 +353,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     *abort_flag = 0;
     fence_barrier_init();
   }
+  if (p.conv == 3) {
+    // K rows of a stage that the (shorter than 64-pixel) boxes never write must read as zero
+    uint4* z = reinterpret_cast<uint4*>(smem);
+    for (int i = threadIdx.x; i < L::BAR_OFFSET / 16; i += blockDim.x) z[i] = make_uint4(0, 0, 0, 0);
+    fence_proxy_async_smem();
+  }
   if (warp == 1) {
     tmem_alloc(tmem_ptr, TMEM_COLS);
     tmem_relinquish();
@@ -378,7 +387,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           mbar_wait(&empty[s], phase ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
           uint8_t* sa = smem + s * L::STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
-          mbar_expect_tx(&full[s], p.conv ? (uint32_t)(p.cv_a_bytes + L::B_TILE_BYTES) : (uint32_t)L::STAGE_BYTES);
+          mbar_expect_tx(&full[s], p.conv == 3 ? (uint32_t)(p.cv_a_bytes * (BM / 64 + BN / 64))
+                                  : p.conv ? (uint32_t)(p.cv_a_bytes + L::B_TILE_BYTES) : (uint32_t)L::STAGE_BYTES);
           if (A_MAJOR == 0 && p.conv) {
             const int tap = kb / p.cv_cchunks, cc = kb - tap * p.cv_cchunks;
             const int kh = tap / 3, kw = tap - kh * 3;
@@ -388,6 +398,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             tma_load_4d(sa, &map_a, &full[s], cc * 64, kw - 1, h0 + kh - 1, n0);
           } else if (A_MAJOR == 0) {
             tma_load_2d(sa, &map_a, &full[s], kb * BK, m_t * BM);
+          } else if (p.conv == 3) {
+            const int it = kb / p.cv_tiles_h, ht = kb - it * p.cv_tiles_h;
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)
+              tma_load_4d(sa + c * (64 * BK * 2), &map_a, &full[s], m_t * BM + c * 64, 0, ht * p.cv_TH, it * p.cv_TN);
           } else {
 #pragma unroll
             for (int c = 0; c < BM / 64; ++c)
@@ -395,6 +410,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
           }
           if (B_MAJOR == 0) {
             tma_load_2d(sb, &map_b, &full[s], kb * BK, n_t * BN);
+          } else if (p.conv == 3) {
+            const int it = kb / p.cv_tiles_h, ht = kb - it * p.cv_tiles_h;
+            const int cin = p.N / 9;
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) {
+              const int col = n_t * BN + c * 64;
+              const int tap = min(col / cin, 8);          // chunks past the last tap load something harmless
+              const int ci0 = col - (col / cin) * cin;
+              const int kh = tap / 3, kw = tap - kh * 3;
+              tma_load_4d(sb + c * (64 * BK * 2), &map_b, &full[s], ci0, kw - 1, ht * p.cv_TH + kh - 1, it * p.cv_TN);
+            }
           } else if (p.conv == 2) {
             // input gradient: weights [Cout, 9 * Cin] read MN-major; tap t of the gradient pairs with tap 8 - t of the
             // forward filter, whose Cin columns start at (8 - t) * Cin; the K rows are the Cout chunk
@@ -476,7 +502,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tc_fence_after();
       int row = m_t * BM + q * 32 + lane;
       bool row_ok = row < p.M;
-      if (p.conv) {
+      if (p.conv == 1 || p.conv == 2) {
         int n0, h0, valid;
         long base_row;
         conv_tile(p, m_t, n0, h0, base_row, valid);
@@ -728,6 +754,19 @@ TB_EXPORT int tb_conv3x3_gemm(const void* x, const void* wmat, void* y, int n, i
                        nullptr, 0, 1, bn, status, stream, tp);
 }
 
+// Weight gradient of the 3x3 / stride 1 / pad 1 convolution without a column matrix: dw[cout, 9*cin] (fp32,
+// ACCUMULATED with atomics, taps row-major, channels innermost) += dy^T [cout, pixels] * shifted x [pixels, 9*cin].
+// dy: [n, h, w, cout], x: [n, h, w, cin] channels-last bf16, cin % 64 == 0, w <= 64.
+TB_EXPORT int tb_conv3x3_wgrad(const void* dy, const void* x, float* dw, int n, int h, int w, int cin, int cout, int lddw,
+                               int split_k, int bn, int* status, cudaStream_t stream) {
+  TB_ENSURE_DEVICE();
+  TpFusion tp;
+  tp.kind = 4;
+  tp.cv_n = n; tp.cv_h = h; tp.cv_w = w;
+  return gemm_dispatch(dy, x, dw, cout, 9 * cin, n * h * w, 1, 1, cout, cin, lddw, nullptr, nullptr, 0, nullptr, nullptr,
+                       EPI_OUT_F32 | EPI_ATOMIC, split_k < 1 ? 1 : split_k, bn, status, stream, tp);
+}
+
 // Row-parallel linear with sequence parallelism: partial = A[M, K_local] * B[N, K_local]^T is
 // reduce-scattered along M inside the epilogue. dst[r] is rank r's slot buffer
 // [world][M / world][ldd] (bf16 or fp32 per `out_f32`): rank s writes slot s of the owner of each
@@ -809,6 +848,25 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
     p.cv_a_bytes = 128 * W * p.cv_TH * p.cv_TN;
     p.tiles_m = ((Nimg + p.cv_TN - 1) / p.cv_TN) * p.cv_tiles_h;
   }
+  if (tp.kind == 4) {
+    // weight gradient: M = Cout, N = 9 * Cin, the K loop runs over pixel blocks
+    const int H = tp.cv_h, W = tp.cv_w, Nimg = tp.cv_n, cin = N / 9;
+    if (a_major != 1 || b_major != 1 || N != 9 * cin || (cin & 63) || (M & 7) || W > 64 || H < 1)
+      TB_FAIL(TB_E_ARG, "conv wgrad: needs Cin %% 64 == 0, W <= 64");
+    if (!(flags & EPI_ATOMIC)) TB_FAIL(TB_E_ARG, "conv wgrad: fp32 atomic accumulation only");
+    p.conv = 3;
+    p.cv_H = H; p.cv_W = W; p.cv_N = Nimg;
+    if (H * W <= 64) { p.cv_TH = H; p.cv_TN = 64 / (H * W); }
+    else             { p.cv_TH = 64 / W; p.cv_TN = 1; }
+    if (p.cv_TN > Nimg) p.cv_TN = Nimg;
+    p.cv_tiles_h = (H + p.cv_TH - 1) / p.cv_TH;
+    p.cv_a_bytes = 128 * W * p.cv_TH * p.cv_TN;   // bytes of one 64-column chunk box
+    p.kb_total = ((Nimg + p.cv_TN - 1) / p.cv_TN) * p.cv_tiles_h;
+    if (split_k > p.kb_total) split_k = p.kb_total;
+    p.kb_per_split = (p.kb_total + split_k - 1) / split_k;
+    split_k = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;
+    p.split_k = split_k;
+  }
   if (tp.kind == 1) {
     p.rs_rows = M / tp.world;
     for (int i = 0; i < tp.world; ++i) p.rs_dst[i] = const_cast<void*>(tp.peers[i]);
@@ -840,6 +898,18 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
     uint64_t dims[2], str[1];
     uint32_t box[2];
     int r;
+    if (tp.kind == 4) {
+      uint32_t b4[4] = {64, (uint32_t)tp.cv_w, (uint32_t)p.cv_TH, (uint32_t)p.cv_TN};
+      uint64_t da[4] = {(uint64_t)M, (uint64_t)tp.cv_w, (uint64_t)tp.cv_h, (uint64_t)tp.cv_n};
+      uint64_t sa4[3] = {(uint64_t)lda * 2, (uint64_t)tp.cv_w * lda * 2, (uint64_t)tp.cv_h * tp.cv_w * lda * 2};
+      r = make_tmap(&ma, A, 2, 4, da, sa4, b4);
+      if (r) return r;
+      const uint64_t cin = (uint64_t)N / 9;
+      uint64_t db[4] = {cin, (uint64_t)tp.cv_w, (uint64_t)tp.cv_h, (uint64_t)tp.cv_n};
+      uint64_t sb4[3] = {(uint64_t)ldb * 2, (uint64_t)tp.cv_w * ldb * 2, (uint64_t)tp.cv_h * tp.cv_w * ldb * 2};
+      r = make_tmap(&mb, B, 2, 4, db, sb4, b4);
+      if (r) return r;
+    } else
     if (tp.kind == 3) {
       const uint64_t C = (uint64_t)K / 9;
       uint64_t d4[4] = {C, (uint64_t)tp.cv_w, (uint64_t)tp.cv_h, (uint64_t)tp.cv_n};
@@ -853,12 +923,15 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
       r = make_tmap(&ma, A, 2, 2, dims, str, box);
     }
     if (r) return r;
+    if (tp.kind == 4) { /* both maps were built above */ }
+    else {
     if (b_major == 0) { dims[0] = K; dims[1] = N; box[0] = BK; box[1] = bn; }
     else if (tp.kind == 3) { dims[0] = (uint64_t)9 * N; dims[1] = (uint64_t)K / 9; box[0] = 64; box[1] = BK; }
     else              { dims[0] = N; dims[1] = K; box[0] = 64; box[1] = BK; }
     str[0] = (uint64_t)ldb * 2;
     r = make_tmap(&mb, B, 2, 2, dims, str, box);
     if (r) return r;
+    }
   }
 
   // TMA-store epilogue: bf16 output, whole 64-column groups, 16-byte aligned rows and operands

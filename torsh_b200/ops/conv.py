@@ -103,6 +103,17 @@ class _Conv2dFn(torch.autograd.Function):
             if ctx.needs_input_grad[0]:
                 dx = _conv3x3_gemm(dy2.view(n, ho, wo, co), wm, c, 2).view(n, h, w, c)
             if ctx.needs_input_grad[1]:
+                if w <= 64:
+                    # dW = dy^T * shifted x, accumulated over pixel blocks straight from the two activations
+                    kb = n * ((h + max(64 // w, 1) - 1) // max(64 // w, 1)) if h * w > 64 else (n + 64 // (h * w) - 1) // (64 // (h * w))
+                    tiles = ((co + 127) // 128) * ((kpad + 255) // 256)
+                    sk = max(1, min(296 // max(tiles, 1), kb // 16))
+                    g = torch.zeros(co, kpad, dtype=torch.float32, device=dy.device)
+                    st = nv.status_word(dy.device)
+                    call("tb_conv3x3_wgrad", [P, P, P, I, I, I, I, I, I, I, I, P, P], dy2.data_ptr(), a.data_ptr(), g.data_ptr(),
+                         n, h, w, c, co, kpad, sk, 0, st.data_ptr(), nv.stream_ptr())
+                    dw = g[:, :k].reshape(co, kh, kw, c).permute(0, 3, 1, 2).to(ctx.wdtype)
+                    return dx, dw, None, None
                 a = _im2col(a, kh, kw, stride, pad, kpad)
         elif ctx.needs_input_grad[0]:
             dcols = gemm(dy2, wm, b_major=1)                       # [M, Kpad] = dy · W
