@@ -388,3 +388,106 @@ TB_EXPORT int tb_rt_occupancy(int threads, int regs_per_thread, uint64_t smem_by
   *limiter = lim;  // 0 threads, 1 registers, 2 shared memory, 3 CTA slots
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------- profiler
+// Scoped ranges: tb_prof_push(name, stream) opens an NVTX range (visible to Nsight tools) and records a CUDA event;
+// tb_prof_pop records the closing event. tb_prof_collect synchronises the events and returns
+// (name, depth, host start in microseconds since the first push, device duration in microseconds) per closed range.
+// Role of the reference's ScopeGuard / CudaProfiler / NvtxRange, which only record host timestamps
+// (crates/torsh-profiler/src/core/scope.rs, src/cuda.rs:21-437).
+#include <nvtx3/nvToolsExt.h>
+
+#include <chrono>
+#include <string>
+
+namespace tb {
+namespace {
+struct ProfRange {
+  std::string name;
+  int depth;
+  double host_us;
+  cudaEvent_t e0, e1;
+  bool closed;
+};
+struct ProfState {
+  std::mutex mu;
+  std::vector<ProfRange> ranges;
+  std::vector<size_t> open;
+  std::chrono::steady_clock::time_point t0;
+  bool started = false, enabled = true;
+};
+ProfState& prof() {
+  static ProfState* s = new ProfState();
+  return *s;
+}
+}  // namespace
+}  // namespace tb
+
+TB_EXPORT void tb_prof_enable(int on) { prof().enabled = on != 0; }
+TB_EXPORT int tb_prof_push(const char* name, cudaStream_t st) {
+  ProfState& s = prof();
+  if (!s.enabled) return 0;
+  TB_ENSURE_DEVICE();
+  nvtxRangePushA(name);
+  std::lock_guard<std::mutex> g(s.mu);
+  if (!s.started) {
+    s.t0 = std::chrono::steady_clock::now();
+    s.started = true;
+  }
+  ProfRange r;
+  r.name = name;
+  r.depth = (int)s.open.size();
+  r.host_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - s.t0).count();
+  r.closed = false;
+  TB_CUDA_CHECK(cudaEventCreate(&r.e0));
+  TB_CUDA_CHECK(cudaEventCreate(&r.e1));
+  TB_CUDA_CHECK(cudaEventRecord(r.e0, st));
+  s.open.push_back(s.ranges.size());
+  s.ranges.push_back(r);
+  return 0;
+}
+TB_EXPORT int tb_prof_pop(cudaStream_t st) {
+  ProfState& s = prof();
+  if (!s.enabled) return 0;
+  TB_ENSURE_DEVICE();
+  nvtxRangePop();
+  std::lock_guard<std::mutex> g(s.mu);
+  if (s.open.empty()) TB_FAIL(TB_E_ARG, "prof_pop without a matching push");
+  ProfRange& r = s.ranges[s.open.back()];
+  s.open.pop_back();
+  TB_CUDA_CHECK(cudaEventRecord(r.e1, st));
+  r.closed = true;
+  return 0;
+}
+// Fills up to `cap` records; names are copied into name_buf (64 bytes each). Returns the number of records and
+// clears them.
+TB_EXPORT int tb_prof_collect(char* name_buf, int* depth, double* host_us, float* device_us, int cap) {
+  ProfState& s = prof();
+  if (ensure_device()) return 0;
+  std::lock_guard<std::mutex> g(s.mu);
+  int n = 0;
+  std::vector<ProfRange> keep;
+  for (ProfRange& r : s.ranges) {
+    if (!r.closed) {
+      keep.push_back(r);
+      continue;
+    }
+    if (n < cap) {
+      float ms = 0.f;
+      cudaEventSynchronize(r.e1);
+      cudaEventElapsedTime(&ms, r.e0, r.e1);
+      snprintf(name_buf + 64 * n, 64, "%s", r.name.c_str());
+      depth[n] = r.depth;
+      host_us[n] = r.host_us;
+      device_us[n] = ms * 1000.f;
+      ++n;
+    }
+    cudaEventDestroy(r.e0);
+    cudaEventDestroy(r.e1);
+  }
+  // indices of still-open ranges shift: rebuild
+  s.open.clear();
+  for (size_t i = 0; i < keep.size(); ++i) s.open.push_back(i);
+  s.ranges.swap(keep);
+  return n;
+}

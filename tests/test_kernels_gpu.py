@@ -409,3 +409,41 @@ def test_resnet_kernel_path_matches_torch_layers():
     bad = {n: (round(cos(gk[n], gf[n]), 3), round(cos(ga[n], gf[n]), 3)) for n in gk if cos(gk[n], gf[n]) < cos(ga[n], gf[n]) - 0.04}
     assert not bad, bad
     assert cos(gk["fc.weight"], gf["fc.weight"]) > 0.999 and cos(gk["layer4.0.bn3.weight"], gf["layer4.0.bn3.weight"]) > 0.99
+
+
+# ------------------------------------------------------------------ gradient compression + native profiler ranges
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_compression_kernels_match_cpu_arithmetic(dtype):
+    from torsh_b200.parallel import compression as cp
+    torch.manual_seed(12)
+    g = torch.randn(100_003, device=DEV).to(dtype)
+    q, sc = cp.Int8BlockQuantization().compress(g)
+    qc, scc = cp.Int8BlockQuantization().compress(g.cpu())
+    assert torch.allclose(sc.cpu(), scc, rtol=1e-6) and (q.cpu().int() - qc.int()).abs().max() <= 1
+    back = cp.Int8BlockQuantization().decompress((q, sc), g.shape, dtype)
+    assert (back.float() - g.float()).abs().max() <= sc.max() * 0.51 + 0.02
+    bits, s, n = cp.PackedSignSGD().compress(g)
+    bc, scpu, _ = cp.PackedSignSGD().compress(g.cpu())
+    assert torch.equal(bits.cpu(), bc) and abs(s.item() - scpu.item()) < 1e-3 * scpu.item()
+    sg = cp.PackedSignSGD().decompress((bits, s, n), g.shape, dtype)
+    assert torch.equal(sg > 0, g >= 0)
+    idx, vals = cp.threshold_sparsify(g, 2.5)
+    want = (g.float().abs() > 2.5).nonzero().flatten()
+    order = idx.long().argsort()
+    assert torch.equal(idx.long()[order], want) and torch.equal(vals[order], g.float()[want])
+
+
+def test_native_profiler_ranges():
+    from torsh_b200.ops import elementwise as ew
+    from torsh_b200.utils.profiler import DeviceRangeProfiler
+    prof = DeviceRangeProfiler()
+    x = torch.randn(1 << 22, device=DEV)
+    with prof.range("step"):
+        with prof.range("relu"):
+            ew.unary_raw("relu", x)
+        with prof.range("exp"):
+            ew.unary_raw("exp", x)
+    rec = prof.collect()
+    by = {r["name"]: r for r in rec}
+    assert set(by) == {"step", "relu", "exp"} and by["step"]["depth"] == 0 and by["relu"]["depth"] == 1
+    assert by["step"]["device_us"] >= by["relu"]["device_us"] > 0 and "traceEvents" in prof.chrome_trace()

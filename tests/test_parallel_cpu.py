@@ -233,3 +233,30 @@ def test_rpc_parameter_server_scheduler_integrations():
     assert (plan.strategy, plan.sharding, plan.cpu_offload, plan.param_dtype, plan.grad_accum) == ("zero_offload", "full_shard", True, "bf16", 4)
     assert ig.from_fairscale({"wrapper": "pipe", "balance": [2, 2, 2], "chunks": 8}).pipeline_stages == 3
     assert ig.from_horovod({"fusion_threshold_mb": 32, "compression": "fp16"}).bucket_mb == 32
+
+
+def test_native_watchdog_and_cpu_compressors():
+    import time
+
+    import torch
+    from torsh_b200.parallel import compression as cp
+    from torsh_b200.parallel.fault_tolerance import NativeWatchdog
+    from torsh_b200.parallel.store import MemoryStore
+    store = MemoryStore()
+    a = NativeWatchdog(store, 0, 3, interval_s=0.02, timeout_s=0.25)
+    b = NativeWatchdog(store, 1, 3, interval_s=0.02, timeout_s=0.25)      # rank 2 never joins
+    time.sleep(0.5)
+    assert a.beats() > 5 and a.failed_ranks() == [2] and b.failed_ranks() == [2]
+    b.stop()                                                               # rank 1 exits between steps
+    time.sleep(0.5)
+    assert a.failed_ranks() == [1, 2]
+    a.stop()
+    g = torch.randn(5000)
+    q, sc = cp.Int8BlockQuantization().compress(g)
+    back = cp.Int8BlockQuantization().decompress((q, sc), g.shape)
+    assert q.dtype == torch.int8 and sc.numel() == 5 and (back - g).abs().max() <= sc.max() * 0.5 + 1e-6
+    payload = cp.PackedSignSGD().compress(g)
+    sg = cp.PackedSignSGD().decompress(payload, g.shape)
+    assert payload[0].numel() == 157 and torch.equal(sg > 0, g >= 0) and torch.allclose(sg.abs(), g.abs().mean().expand_as(g))
+    idx, vals = cp.threshold_sparsify(g, 2.0)
+    assert torch.equal(idx.long(), (g.abs() > 2.0).nonzero().flatten()) and torch.equal(vals, g[idx.long()])

@@ -278,3 +278,60 @@ class FaultInjector:
             self.maybe_fail()
             return fn(*a, **kw)
         return wrapped
+
+
+
+class NativeWatchdog:
+    """Native heartbeat thread (``csrc/host/watchdog.cpp``): beats through a store every ``interval_s`` and reports the
+    ranks whose counter has not moved for ``timeout_s``.  It keeps beating while Python is blocked in a collective."""
+
+    def __init__(self, store, rank: int, world_size: int, interval_s: float = 1.0, timeout_s: float = 10.0, prefix: str = "hb"):
+        import ctypes
+
+        from .. import _native as nv
+        self.store, self.rank, self.world, self.prefix = store, rank, world_size, prefix
+        lib = nv.host()
+        PUB = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_longlong, ctypes.c_void_p)
+        READ = ctypes.CFUNCTYPE(ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p)
+
+        def publish(r, counter, _ctx):
+            try:
+                store.set(f"{prefix}/{r}", str(counter).encode())
+            except Exception:
+                pass
+
+        def read(r, _ctx):
+            try:
+                v = store.get(f"{prefix}/{r}")
+                return int(v) if v else -1
+            except Exception:
+                return -1
+        self._pub, self._read = PUB(publish), READ(read)          # keep the callbacks alive
+        lib.tsh_watchdog_start.restype = ctypes.c_void_p
+        lib.tsh_watchdog_start.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_double, ctypes.c_double, PUB, READ, ctypes.c_void_p]
+        lib.tsh_watchdog_failed.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
+        lib.tsh_watchdog_beats.restype, lib.tsh_watchdog_beats.argtypes = ctypes.c_longlong, [ctypes.c_void_p]
+        lib.tsh_watchdog_stop.argtypes = [ctypes.c_void_p]
+        self._lib, self._ct = lib, ctypes
+        self._h = lib.tsh_watchdog_start(rank, world_size, interval_s, timeout_s, self._pub, self._read, None)
+        if not self._h:
+            raise ValueError("bad watchdog arguments")
+
+    def failed_ranks(self) -> list[int]:
+        buf = (self._ct.c_int * self.world)()
+        self._lib.tsh_watchdog_failed(self._h, buf)
+        return [r for r in range(self.world) if buf[r]]
+
+    def beats(self) -> int:
+        return self._lib.tsh_watchdog_beats(self._h)
+
+    def stop(self) -> None:
+        if self._h:
+            self._lib.tsh_watchdog_stop(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.stop()
+        except Exception:
+            pass

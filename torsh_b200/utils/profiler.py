@@ -187,3 +187,45 @@ class CommunicationProfiler:
     def export_json(self, path):
         with open(path, "w") as f:
             json.dump({"events": [asdict(e) for e in self.events], "stats": self.stats()}, f, indent=1)
+
+
+
+class DeviceRangeProfiler:
+    """Native scoped ranges (``csrc/kernels/runtime.cu``): every range is an NVTX range for Nsight tools and a pair of
+    CUDA events on the launching stream; ``collect()`` returns device durations, ``chrome_trace()`` the trace JSON."""
+
+    def __init__(self):
+        import ctypes
+
+        from .. import _native as nv
+        self._nv, self._ct = nv, ctypes
+        self._lib = nv.require_cuda()
+        self._lib.tb_prof_push.argtypes = [ctypes.c_char_p, ctypes.c_void_p]
+        self._lib.tb_prof_pop.argtypes = [ctypes.c_void_p]
+        self.records: list[dict] = []
+
+    def range(self, name: str):
+        prof = self
+
+        class _R:
+            def __enter__(self_inner):
+                prof._nv.check(prof._lib.tb_prof_push(name.encode()[:63], prof._nv.stream_ptr()), "prof_push")
+
+            def __exit__(self_inner, *a):
+                prof._nv.check(prof._lib.tb_prof_pop(prof._nv.stream_ptr()), "prof_pop")
+        return _R()
+
+    def collect(self, cap: int = 4096) -> list[dict]:
+        ct = self._ct
+        names = ct.create_string_buffer(64 * cap)
+        depth, host, dev = (ct.c_int * cap)(), (ct.c_double * cap)(), (ct.c_float * cap)()
+        n = self._lib.tb_prof_collect(names, depth, host, dev, cap)
+        out = [{"name": names.raw[64 * i: 64 * i + 64].split(b"\0", 1)[0].decode(), "depth": depth[i], "host_us": host[i],
+                "device_us": dev[i]} for i in range(n)]
+        self.records += out
+        return out
+
+    def chrome_trace(self) -> str:
+        import json
+        return json.dumps({"traceEvents": [{"name": r["name"], "ph": "X", "ts": r["host_us"], "dur": r["device_us"], "pid": 0,
+                                            "tid": r["depth"], "cat": "cuda"} for r in self.records]})
