@@ -37,6 +37,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--dense-head", action="store_true",
+                    help="every TP rank computes all logits (default: vocabulary-parallel head and loss)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -71,8 +73,13 @@ def main():
     torch.manual_seed(1234 + mp.pp_rank * 100 + mp.tp_rank)
     with torch.device(dev):
         model = LlamaModel(cfg, tp=tpc, layer_range=mp.layer_range(), first_stage=mesh.is_first_stage,
-                           last_stage=mesh.is_last_stage)
+                           last_stage=mesh.is_last_stage, vocab_parallel=not args.dense_head)
     model = model.to(torch.bfloat16)
+    if tpc is not None:
+        # parameters that every tensor-parallel rank holds in full start from rank 0's values
+        src = dist.get_global_rank(mesh.tp_group, 0)
+        for p in model.replicated_parameters() + ([model.lm_head] if hasattr(model, "lm_head") else []):
+            dist.broadcast(p.data, src=src, group=mesh.tp_group)
     opt = AdamW(model.parameters(), lr=1e-4, weight_decay=0.01)
     B, S, M = 1, args.seq, args.micro_batches
 
@@ -148,8 +155,9 @@ def main():
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = t.item()
-    last = torch.tensor([loss.item() if loss is not None else 0.0], device=dev)
+    last = torch.tensor([loss.item() if loss is not None else 0.0, first if first is not None else 0.0], device=dev)
     dist.all_reduce(last, op=dist.ReduceOp.MAX)
+    last, first_all = last[0], last[1].item()
     tokens = dp * M * B * S * args.steps
     n_params = args.layers * (4 * args.hidden ** 2 + 3 * args.hidden * args.ffn) + 2 * args.vocab * args.hidden
     if rank == 0:
@@ -160,10 +168,10 @@ def main():
             "model_tflops_per_gpu": 6 * n_params * tokens / (ms / 1e3) / world / 1e12,
             "data": "synthetic (uniform random token ids, N(0,0.02) init)",
             "config": {"layers": args.layers, "d_model": args.hidden, "heads": args.heads, "ffn": args.ffn, "vocab": args.vocab,
-                       "seq_len": S, "micro_batches": M, "parallelism": f"tp{args.tp}(sp) x pp{args.pp}(1f1b) x dp{dp}",
+                       "seq_len": S, "micro_batches": M, "head": "dense" if args.dense_head else "vocab-parallel", "parallelism": f"tp{args.tp}(sp) x pp{args.pp}(1f1b) x dp{dp}",
                        "params_b": round(n_params / 1e9, 2)},
             "clocks": clocks, "gpu_launches": per_step * args.steps, "launches_per_step": per_step,
-            "loss_last": last.item()}))
+            "loss_after_warmup": first_all, "loss_last": last.item()}))
     dist.barrier()
     dist.destroy_process_group()
     return 0

@@ -422,19 +422,30 @@ __global__ void __launch_bounds__(256) bn_apply_fast_kernel(const bf16* __restri
     }
   }
 }
-__global__ void __launch_bounds__(256) bn_bwd_reduce_fast_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y,
+template <int RELU>
+__global__ void __launch_bounds__(256, RELU == 2 ? 3 : 4) bn_bwd_reduce_fast_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y,
                                                                  const bf16* __restrict__ x,
                                                                  const float* __restrict__ mean,
                                                                  const float* __restrict__ rstd,
-                                                                 float* __restrict__ sums, long rows, int C, int relu) {
+                                                                 const float* __restrict__ gamma,
+                                                                 const float* __restrict__ beta,
+                                                                 float* __restrict__ sums, long rows, int C) {
+  constexpr int relu = RELU;
+  // relu == 1: mask from the saved output y; relu == 2: no residual was added, so the mask is recomputed from x with
+  // the forward's own fused multiply-add (one tensor less to read)
   __shared__ float part[2 * 256 * 9];
   const int c8 = C >> 3;
   const BnMap m = bn_map(c8);
-  float s[8], q[8], mu[8];
+  float s[8], q[8], mu[8], sc[8], sh[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     s[j] = q[j] = 0.f;
     mu[j] = mean[m.cv * 8 + j];
+    sc[j] = sh[j] = 0.f;
+    if (relu == 2) {
+      sc[j] = rstd[m.cv * 8 + j] * gamma[m.cv * 8 + j];
+      sh[j] = beta[m.cv * 8 + j] - mu[j] * sc[j];
+    }
   }
   const long off = (long)m.cv * 8;
   const long step = (long)gridDim.x * m.rpb;
@@ -446,7 +457,7 @@ __global__ void __launch_bounds__(256) bn_bwd_reduce_fast_kernel(const bf16* __r
       if (ru < rows) {
         vg[u].load_nc(dy + ru * C + off);
         vx[u].load_nc(x + ru * C + off);
-        if (relu) vy[u].load_nc(y + ru * C + off);
+        if (relu == 1) vy[u].load_nc(y + ru * C + off);
       }
     }
 #pragma unroll
@@ -455,12 +466,16 @@ __global__ void __launch_bounds__(256) bn_bwd_reduce_fast_kernel(const bf16* __r
       float g[8], xf[8];
       vg[u].get(g);
       vx[u].get(xf);
-      if (relu) {
+      if (relu == 1) {
         float yf[8];
         vy[u].get(yf);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           if (yf[j] <= 0.f) g[j] = 0.f;
+      } else if (relu == 2) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (fmaf(xf[j], sc[j], sh[j]) <= 0.f) g[j] = 0.f;
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -473,17 +488,20 @@ __global__ void __launch_bounds__(256) bn_bwd_reduce_fast_kernel(const bf16* __r
   for (int j = 0; j < 8; ++j) q[j] *= rstd[m.cv * 8 + j];
   bn_block_reduce(s, q, part, sums, C, c8, m);
 }
-__global__ void __launch_bounds__(256) bn_bwd_apply_fast_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y,
+template <int RELU>
+__global__ void __launch_bounds__(256, 3) bn_bwd_apply_fast_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y,
                                                                 const bf16* __restrict__ x,
                                                                 const float* __restrict__ mean,
                                                                 const float* __restrict__ rstd,
                                                                 const float* __restrict__ gamma,
+                                                                const float* __restrict__ beta,
                                                                 const float* __restrict__ sums, bf16* __restrict__ dx,
-                                                                bf16* __restrict__ dres, long rows, int C, int relu) {
+                                                                bf16* __restrict__ dres, long rows, int C) {
+  constexpr int relu = RELU;
   const int c8 = C >> 3;
   const BnMap m = bn_map(c8);
   // dx = a * g + b * x + d with a = gamma*rstd, b = -a * rstd * sum_gx / rows, d = -a * sum_g / rows - b * mean
-  float a[8], b[8], d[8];
+  float a[8], b[8], d[8], sh[8];
   const float inv = 1.f / (float)rows;
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
@@ -491,6 +509,7 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_fast_kernel(const bf16* __re
     a[j] = gamma[c] * rstd[c];
     b[j] = -a[j] * rstd[c] * sums[C + c] * inv;
     d[j] = -a[j] * sums[c] * inv - b[j] * mean[c];
+    sh[j] = relu == 2 ? beta[c] - mean[c] * a[j] : 0.f;   // forward: y = relu(fma(x, a, sh))
   }
   const long off = (long)m.cv * 8;
   const long step = (long)gridDim.x * m.rpb;
@@ -502,7 +521,7 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_fast_kernel(const bf16* __re
       if (ru < rows) {
         vg[u].load_nc(dy + ru * C + off);
         vx[u].load_nc(x + ru * C + off);
-        if (relu) vy[u].load_nc(y + ru * C + off);
+        if (relu == 1) vy[u].load_nc(y + ru * C + off);
       }
     }
 #pragma unroll
@@ -512,12 +531,16 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_fast_kernel(const bf16* __re
       float g[8], xf[8];
       vg[u].get(g);
       vx[u].get(xf);
-      if (relu) {
+      if (relu == 1) {
         float yf[8];
         vy[u].get(yf);
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           if (yf[j] <= 0.f) g[j] = 0.f;
+      } else if (relu == 2) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (fmaf(xf[j], a[j], sh[j]) <= 0.f) g[j] = 0.f;
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) xf[j] = fmaf(a[j], g[j], fmaf(b[j], xf[j], d[j]));
@@ -758,17 +781,30 @@ TB_EXPORT int tb_bn_apply(const void* x, const void* res, void* y, const float* 
 }
 // dgamma / dbeta (fp32 [C]) are accumulated into; dres may be null; y is read only when relu != 0.
 TB_EXPORT int tb_bn_bwd(const void* dy, const void* y, const void* x, const float* mean, const float* rstd,
-                        const float* gamma, float* sums, void* dx, void* dres, float* dgamma, float* dbeta, long rows,
-                        int C, int relu, cudaStream_t st) {
+                        const float* gamma, const float* beta, float* sums, void* dx, void* dres, float* dgamma,
+                        float* dbeta, long rows, int C, int relu, cudaStream_t st) {
   TB_ENSURE_DEVICE();
   if (rows <= 0 || C <= 0) return 0;
-  if ((C & 7) || !al16(dy) || !al16(x) || !al16(dx) || (relu && !al16(y)) || (dres && !al16(dres)))
+  // relu: 0 none, 1 mask from the saved output y. With y == null (allowed when the forward added no residual) the
+  // register-resident kernels recompute the mask from x, gamma and beta instead.
+  if (relu && !y) {
+    if (dres || !beta || !bn_fast_ok(C)) TB_FAIL(TB_E_ARG, "bn_bwd: the ReLU mask can be recomputed only without a residual, with beta, and for power-of-two channel groups");
+    relu = 2;
+  }
+  if ((C & 7) || !al16(dy) || !al16(x) || !al16(dx) || (relu == 1 && !al16(y)) || (dres && !al16(dres)))
     TB_FAIL(TB_E_ARG, "bn_bwd: C %% 8 and 16-byte alignment required");
   TB_CUDA_CHECK(cudaMemsetAsync(sums, 0, sizeof(float) * 2 * C, st));
   if (bn_fast_ok(C)) {
     const int g = bn_fast_grid(rows, C);
-    bn_bwd_reduce_fast_kernel<<<g, 256, 0, st>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, mean, rstd, sums, rows, C, relu);
-    bn_bwd_apply_fast_kernel<<<g, 256, 0, st>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, mean, rstd, gamma, sums, (bf16*)dx, (bf16*)dres, rows, C, relu);
+#define TB_BN_BWD_FAST(R)                                                                                              \
+  bn_bwd_reduce_fast_kernel<R><<<g, 256, 0, st>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, mean, rstd, gamma,  \
+                                                  beta, sums, rows, C);                                                \
+  bn_bwd_apply_fast_kernel<R><<<g, 256, 0, st>>>((const bf16*)dy, (const bf16*)y, (const bf16*)x, mean, rstd, gamma,   \
+                                                 beta, sums, (bf16*)dx, (bf16*)dres, rows, C)
+    if (relu == 2) { TB_BN_BWD_FAST(2); }
+    else if (relu == 1) { TB_BN_BWD_FAST(1); }
+    else { TB_BN_BWD_FAST(0); }
+#undef TB_BN_BWD_FAST
   } else {
     dim3 grid;
     int rpb;

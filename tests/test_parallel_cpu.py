@@ -260,3 +260,79 @@ def test_native_watchdog_and_cpu_compressors():
     assert payload[0].numel() == 157 and torch.equal(sg > 0, g >= 0) and torch.allclose(sg.abs(), g.abs().mean().expand_as(g))
     idx, vals = cp.threshold_sparsify(g, 2.0)
     assert torch.equal(idx.long(), (g.abs() > 2.0).nonzero().flatten()) and torch.equal(vals, g[idx.long()])
+
+
+def _llama_tp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torsh_b200.models.llama import LlamaConfig, LlamaModel
+        from torsh_b200.parallel.tensor_parallel import TensorParallelConfig, TPContext
+        cfg = LlamaConfig(vocab_size=300, hidden_size=64, intermediate_size=128, num_layers=2, num_heads=4, max_seq_len=32)
+        torch.manual_seed(0)
+        ref = LlamaModel(cfg)
+        ids = torch.randint(0, cfg.vocab_size, (2, 17), generator=torch.Generator().manual_seed(5))
+        inp, tgt = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+        loss_ref = ref(inp, targets=tgt)
+        loss_ref.backward()
+        E, F = cfg.hidden_size, cfg.intermediate_size
+        sl = lambda t, n: t[rank * n // world:(rank + 1) * n // world]
+        ok = True
+        for vocab_parallel in (False, True):
+            tpc = TPContext(dist.group.WORLD, TensorParallelConfig(tp_size=world, fused=False))
+            m = LlamaModel(cfg, tp=tpc, vocab_parallel=vocab_parallel)
+            with torch.no_grad():
+                m.embed.copy_(ref.embed)
+                m.norm.weight.copy_(ref.norm.weight)
+                for a, b in zip(m.layers, ref.layers):
+                    a.input_norm.weight.copy_(b.input_norm.weight)
+                    a.post_attn_norm.weight.copy_(b.post_attn_norm.weight)
+                    wq = b.qkv.weight
+                    a.qkv.weight.copy_(torch.cat([sl(wq[:E], E), sl(wq[E:2 * E], E), sl(wq[2 * E:], E)]))
+                    wg = b.gate_up.weight
+                    a.gate_up.weight.copy_(torch.cat([sl(wg[:F], F), sl(wg[F:], F)]))
+                    a.o.weight.copy_(b.o.weight[:, rank * E // world:(rank + 1) * E // world])
+                    a.down.weight.copy_(b.down.weight[:, rank * F // world:(rank + 1) * F // world])
+                if vocab_parallel:
+                    vp = m.lm_head_tp.weight.shape[0]
+                    full = torch.zeros(vp * world, E)
+                    full[: cfg.vocab_size] = ref.lm_head[: cfg.vocab_size]
+                    m.lm_head_tp.weight.copy_(full[rank * vp:(rank + 1) * vp])
+                else:
+                    m.lm_head.copy_(ref.lm_head)
+            loss = m(inp, targets=tgt)
+            loss.backward()
+            for p in m.replicated_parameters():
+                dist.all_reduce(p.grad)
+            ok &= abs(loss.item() - loss_ref.item()) < 1e-5
+            ok &= torch.allclose(m.embed.grad, ref.embed.grad, atol=1e-6)
+            ok &= torch.allclose(m.norm.weight.grad, ref.norm.weight.grad, atol=1e-6)
+            g = ref.layers[0].qkv.weight.grad
+            ok &= torch.allclose(m.layers[0].qkv.weight.grad, torch.cat([sl(g[:E], E), sl(g[E:2 * E], E), sl(g[2 * E:], E)]), atol=1e-6)
+            ok &= torch.allclose(m.layers[1].down.weight.grad, ref.layers[1].down.weight.grad[:, rank * F // world:(rank + 1) * F // world], atol=1e-6)
+            if vocab_parallel:
+                hg = torch.zeros(vp * world, E)
+                hg[: cfg.vocab_size] = ref.lm_head.grad[: cfg.vocab_size]
+                ok &= torch.allclose(m.lm_head_tp.weight.grad, hg[rank * vp:(rank + 1) * vp], atol=1e-6)
+                logits = m(inp)
+                ok &= torch.allclose(logits, ref(inp), atol=1e-5)
+            else:
+                ok &= torch.allclose(m.lm_head.grad, ref.lm_head.grad, atol=1e-6)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_llama_tensor_parallel_heads_match_single_process_model():
+    """Dense (replicated) and vocabulary-parallel LM heads under 2-way tensor + sequence parallelism give the loss and
+    the gradients of the unsplit model."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_llama_tp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(30)
+    assert sorted(res) == [(0, True), (1, True)]

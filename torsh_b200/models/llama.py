@@ -104,9 +104,13 @@ class LlamaModel(nn.Module):
     final norm and the LM head)."""
 
     def __init__(self, cfg: LlamaConfig, tp=None, layer_range: range | None = None, first_stage: bool = True,
-                 last_stage: bool = True):
+                 last_stage: bool = True, vocab_parallel: bool = False):
         super().__init__()
         self.cfg, self.tp, self.first_stage, self.last_stage = cfg, tp, first_stage, last_stage
+        # vocab_parallel: the LM head is split over the tensor-parallel ranks by vocabulary rows (column-parallel
+        # linear fed by the token shards) and the loss is computed without gathering the logits; otherwise every
+        # rank computes all logits from the gathered hidden states
+        self.vocab_parallel = bool(vocab_parallel and tp is not None and tp.world > 1)
         layers = layer_range if layer_range is not None else range(cfg.num_layers)
         if first_stage:
             w = torch.zeros(cfg.padded_vocab, cfg.hidden_size)
@@ -115,9 +119,14 @@ class LlamaModel(nn.Module):
         self.layers = nn.ModuleList([LlamaBlock(cfg, tp) for _ in layers])
         if last_stage:
             self.norm = nn.RMSNorm(cfg.hidden_size, cfg.rms_eps)
-            w = torch.zeros(cfg.padded_vocab, cfg.hidden_size)
-            w[: cfg.vocab_size].normal_(0.0, cfg.initializer_range)
-            self.lm_head = nn.Parameter(w)
+            if self.vocab_parallel:
+                from ..parallel.tensor_parallel import ColumnParallelLinear
+                vp = (cfg.vocab_size + 128 * tp.world - 1) // (128 * tp.world) * (128 * tp.world)
+                self.lm_head_tp = ColumnParallelLinear(cfg.hidden_size, vp, bias=False, tp=tp, init_std=cfg.initializer_range)
+            else:
+                w = torch.zeros(cfg.padded_vocab, cfg.hidden_size)
+                w[: cfg.vocab_size].normal_(0.0, cfg.initializer_range)
+                self.lm_head = nn.Parameter(w)
 
     def replicated_parameters(self):
         """Parameters every tensor-parallel rank holds in full but feeds with its own token shard (norm weights, the
@@ -149,9 +158,16 @@ class LlamaModel(nn.Module):
     def head(self, x, B: int, S: int, targets: torch.Tensor | None = None):
         """Final norm + LM head (+ fused cross-entropy when ``targets`` is given) on the last stage's hidden states."""
         h = norm_ops.rms_norm(x, self.norm.weight, self.cfg.rms_eps)
+        if self.vocab_parallel:
+            from ..parallel.tensor_parallel import _gather_cols, vocab_parallel_cross_entropy
+            logits_local = self.lm_head_tp(h)                       # [B*S, V/tp]: all tokens, this rank's vocabulary rows
+            if targets is None:
+                full = torch.cat(_gather_cols(logits_local, self.tp.group), -1)
+                return full.view(B, S, -1)[..., : self.cfg.vocab_size]
+            return vocab_parallel_cross_entropy(logits_local, targets, self.tp.group, self.cfg.vocab_size)
         if self.tp is not None and self.tp.world > 1:
-            from ..parallel.tensor_parallel import _AllGatherRows
-            h = _AllGatherRows.apply(h, self.tp.group)
+            from ..parallel.tensor_parallel import _AllGatherRowsReplicated
+            h = _AllGatherRowsReplicated.apply(h, self.tp.group)
         logits = lin_ops.linear(h, self.lm_head, None)
         if targets is None:
             return logits.view(B, S, -1)[..., : self.cfg.vocab_size]

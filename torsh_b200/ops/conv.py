@@ -159,13 +159,16 @@ class _BatchNormFn(torch.autograd.Function):
         call("tb_bn_fwd", [P, P, P, P, P, P, P, P, P, P, L, I, F, F, I, P], x.data_ptr(), nv.ptr(residual), y.data_ptr(),
              sums.data_ptr(), mean.data_ptr(), rstd.data_ptr(), g32.data_ptr(), b32.data_ptr(), nv.ptr(run_mean),
              nv.ptr(run_var), rows, c, eps, momentum, int(relu), nv.stream_ptr())
-        ctx.save_for_backward(x, y if relu else None, mean, rstd, g32)
+        # without a residual the backward recomputes the ReLU mask from x, so the output need not be kept for it
+        c8 = c // 8
+        recompute = relu and residual is None and c8 <= 256 and (c8 & (c8 - 1)) == 0
+        ctx.save_for_backward(x, y if (relu and not recompute) else None, mean, rstd, g32, b32)
         ctx.relu, ctx.has_res, ctx.pdtype = relu, residual is not None, gamma.dtype
         return y
 
     @staticmethod
     def backward(ctx, dy):
-        x, y, mean, rstd, g32 = ctx.saved_tensors
+        x, y, mean, rstd, g32, b32 = ctx.saved_tensors
         c = x.shape[-1]
         rows = x.numel() // c
         dy = dy.contiguous()
@@ -173,8 +176,8 @@ class _BatchNormFn(torch.autograd.Function):
         dres = torch.empty_like(x) if ctx.has_res else None
         sums = torch.empty(2 * c, dtype=torch.float32, device=x.device)
         dgb = torch.zeros(2, c, dtype=torch.float32, device=x.device)
-        call("tb_bn_bwd", [P, P, P, P, P, P, P, P, P, P, P, L, I, I, P], dy.data_ptr(), nv.ptr(y), x.data_ptr(),
-             mean.data_ptr(), rstd.data_ptr(), g32.data_ptr(), sums.data_ptr(), dx.data_ptr(), nv.ptr(dres),
+        call("tb_bn_bwd", [P, P, P, P, P, P, P, P, P, P, P, P, L, I, I, P], dy.data_ptr(), nv.ptr(y), x.data_ptr(),
+             mean.data_ptr(), rstd.data_ptr(), g32.data_ptr(), b32.data_ptr(), sums.data_ptr(), dx.data_ptr(), nv.ptr(dres),
              dgb[0].data_ptr(), dgb[1].data_ptr(), rows, c, int(ctx.relu), nv.stream_ptr())
         return dx, dgb[0].to(ctx.pdtype), dgb[1].to(ctx.pdtype), dres, None, None, None, None, None
 

@@ -197,6 +197,23 @@ class _AllGatherRows(torch.autograd.Function):
         return _reduce_scatter_rows(dy, ctx.group), None
 
 
+class _AllGatherRowsReplicated(torch.autograd.Function):
+    """All-gather along tokens for a consumer that every rank evaluates in full on the gathered rows (a replicated
+    head and loss): each rank's upstream gradient is already the complete one, so the backward keeps this rank's
+    rows instead of summing ``world`` identical copies."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _all_gather_rows(x, group)
+
+    @staticmethod
+    def backward(ctx, dy):
+        w, r = dist.get_world_size(ctx.group), dist.get_rank(ctx.group)
+        rows = dy.shape[0] // w
+        return dy[r * rows:(r + 1) * rows].contiguous(), None
+
+
 class _ReduceScatterRows(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, group):
@@ -322,3 +339,48 @@ def create_column_parallel_linear(in_features, out_features, tp=None, **kw):
 
 def create_row_parallel_linear(in_features, out_features, tp=None, **kw):
     return RowParallelLinear(in_features, out_features, tp=tp, **kw)
+
+
+
+class _VocabParallelCrossEntropy(torch.autograd.Function):
+    """Mean cross-entropy over a vocabulary whose logits are split column-wise over the group: each rank holds
+    ``logits[:, rank * Vp : (rank + 1) * Vp]``.  Three all-reduces of per-token scalars (max, sum of exponentials, target
+    logit) replace the all-gather of the logits; the backward is local: ``(softmax - onehot) / tokens`` on this rank's
+    columns.  Columns at or beyond ``num_classes`` (vocabulary padding) are ignored."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, group, num_classes):
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        T, Vp = logits.shape
+        lo = rank * Vp
+        lg = logits.float()
+        valid = (torch.arange(Vp, device=logits.device) + lo) < num_classes
+        lg = lg.masked_fill(~valid, float("-inf"))
+        m = lg.max(1).values
+        dist.all_reduce(m, op=dist.ReduceOp.MAX, group=group)
+        e = torch.exp(lg - m[:, None])
+        ssum = e.sum(1)
+        dist.all_reduce(ssum, group=group)
+        tl = targets - lo
+        mine = (tl >= 0) & (tl < Vp)
+        tlogit = torch.where(mine, lg.gather(1, tl.clamp(0, Vp - 1)[:, None])[:, 0], torch.zeros_like(m))
+        dist.all_reduce(tlogit, group=group)
+        loss = (torch.log(ssum) + m - tlogit).mean()
+        ctx.save_for_backward(e, ssum, tl, mine)
+        ctx.dtype = logits.dtype
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        e, ssum, tl, mine = ctx.saved_tensors
+        T, Vp = e.shape
+        p = e / ssum[:, None]
+        rows = torch.arange(T, device=e.device)[mine]
+        p[rows, tl[mine]] -= 1.0
+        return (p * (g / T)).to(ctx.dtype), None, None, None
+
+
+def vocab_parallel_cross_entropy(logits_local: torch.Tensor, targets: torch.Tensor, group=None, num_classes: int | None = None):
+    group = group if group is not None else dist.group.WORLD
+    V = logits_local.shape[1] * dist.get_world_size(group)
+    return _VocabParallelCrossEntropy.apply(logits_local, targets.reshape(-1), group, num_classes or V)
