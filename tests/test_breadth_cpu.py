@@ -328,3 +328,54 @@ def test_extra_layers_amp_and_second_order_optimizers():
     assert fit(lambda m: so.NewtonCG(m.parameters()), steps=4, closure=True) < 1e-8
     assert fit(lambda m: so.YellowFin(m.parameters(), lr=0.01), steps=200) < 0.05
     assert tb.optim.ElasticAveragingSGD and tb.optim.DistributedOptimizer and tb.optim.AsyncSGD
+
+
+def test_trust_region_and_natural_gradient_reach_quadratic_minimum():
+    from torsh_b200.optim import NaturalGradient, TrustRegion
+    torch.manual_seed(0)
+    A = torch.randn(6, 6)
+    A = A @ A.T + torch.eye(6)
+    b = torch.randn(6)
+    xs = torch.linalg.solve(A, b)
+    best = float(0.5 * xs @ A @ xs - b @ xs)
+    x = torch.zeros(6, requires_grad=True)
+    opt = TrustRegion([x], delta=1.0)
+    for _ in range(15):
+        loss = opt.step(lambda: 0.5 * x @ A @ x - b @ x)
+    assert abs(float(loss) - best) < 1e-4
+    w = torch.zeros(6, requires_grad=True)
+    opt = NaturalGradient([w], lr=0.1, full_below=10)
+    first = None
+    for _ in range(200):
+        opt.zero_grad()
+        loss = 0.5 * w @ A @ w - b @ w
+        loss.backward()
+        opt.step()
+        first = first if first is not None else float(loss.detach())
+    assert float(loss.detach()) < first - 0.5 * (first - best)
+
+
+def test_remaining_nn_layers():
+    from torsh_b200 import nn
+    torch.manual_seed(0)
+    att = nn.LocationBasedAttention(8, 6, 16)
+    out, align = att(torch.randn(2, 8), torch.randn(2, 10, 6), torch.randn(2, 10, 5))
+    assert out.shape == (2, 5) and torch.allclose(align.sum(-1), torch.ones(2), atol=1e-6)
+    xm, ym = nn.Mixup(0.2, 5)(torch.randn(4, 3, 8, 8), torch.randint(0, 5, (4,)))
+    assert xm.shape == (4, 3, 8, 8) and torch.allclose(ym.sum(-1), torch.ones(4), atol=1e-6)
+    xc, yc = nn.CutMix(1.0, 5)(torch.randn(4, 3, 8, 8), torch.randint(0, 5, (4,)))
+    assert torch.allclose(yc.sum(-1), torch.ones(4), atol=1e-6)
+    x = torch.randn(1, 5, 2, 8)
+    pi = nn.PositionInterpolation(8, 16, 64)
+    assert torch.allclose(pi(x).norm(), x.norm(), atol=1e-5)                   # rotations keep the norm
+    full = nn.PositionInterpolation(8, 16, 16)
+    assert torch.allclose(pi(x, offset=0)[:, 4], full(x[:, 4:5], offset=1)[:, 0], atol=1e-5)   # position 4 / 4 = 1
+    ws = nn.WeightStandardization(torch.nn.Conv2d(3, 4, 3))
+    assert ws(torch.randn(1, 3, 8, 8)).shape == (1, 4, 6, 6)
+    sn = nn.SpectralNorm(torch.nn.Linear(4, 4))
+    for _ in range(30):
+        sn(torch.randn(2, 4))
+    assert abs(float(torch.linalg.matrix_norm(sn.weight.detach(), 2)) - 1.0) < 0.05
+    wn = nn.WeightNorm(torch.nn.Linear(4, 3))
+    assert wn(torch.randn(2, 4)).shape == (2, 3)
+    assert nn.LazyLinear(3)(torch.randn(2, 7)).shape == (2, 3)

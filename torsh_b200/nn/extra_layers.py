@@ -298,3 +298,99 @@ class GlobalAvgPool2d(Module):
 
 class GlobalMaxPool2d(Module):
     def forward(self, x): return x.amax((2, 3))
+
+
+class LocationBasedAttention(Module):
+    """Location-aware scoring (``crates/torsh-nn/src/layers/attention.rs``): the previous alignment is convolved along
+    time and enters the additive score, ``vᵀ tanh(W_q q + W_k k + W_f (F * a_prev))``."""
+
+    def __init__(self, q_dim, k_dim, hidden, conv_channels: int = 32, kernel_size: int = 31):
+        super().__init__()
+        self.wq, self.wk = torch.nn.Linear(q_dim, hidden, bias=False), torch.nn.Linear(k_dim, hidden, bias=False)
+        self.loc = torch.nn.Conv1d(1, conv_channels, kernel_size, padding=kernel_size // 2, bias=False)
+        self.wf, self.v = torch.nn.Linear(conv_channels, hidden, bias=False), torch.nn.Linear(hidden, 1, bias=False)
+
+    def forward(self, q, k, v, prev_alignment=None, mask=None):
+        """``q``: ``[B, q_dim]`` (one decoder step); ``k, v``: ``[B, T, ·]``; ``prev_alignment``: ``[B, T]``."""
+        b, t, _ = k.shape
+        if prev_alignment is None:
+            prev_alignment = torch.zeros(b, t, device=k.device, dtype=k.dtype)
+        f = self.loc(prev_alignment[:, None]).transpose(1, 2)               # [B, T, conv_channels]
+        s = self.v(torch.tanh(self.wq(q)[:, None] + self.wk(k) + self.wf(f))).squeeze(-1)
+        if mask is not None:
+            s = s.masked_fill(~mask, float("-inf"))
+        a = torch.softmax(s, -1)
+        return (a[:, None] @ v).squeeze(1), a
+
+
+class Mixup(Module):
+    """Batch-level mixup as a module (``crates/torsh-nn/src/layers/regularization``); identity in eval mode."""
+
+    def __init__(self, alpha: float = 0.2, num_classes: int | None = None):
+        super().__init__()
+        self.alpha, self.num_classes = alpha, num_classes
+
+    def forward(self, x, y):
+        if not self.training:
+            return x, (F.one_hot(y, self.num_classes).float() if self.num_classes else y)
+        return mixup(x, y, self.alpha, self.num_classes)
+
+
+class CutMix(Module):
+    def __init__(self, alpha: float = 1.0, num_classes: int | None = None):
+        super().__init__()
+        self.alpha, self.num_classes = alpha, num_classes
+
+    def forward(self, x, y):
+        if not self.training:
+            return x, (F.one_hot(y, self.num_classes).float() if self.num_classes else y)
+        return cutmix(x, y, self.alpha, self.num_classes)
+
+
+class PositionInterpolation(Module):
+    """Rotary embedding whose positions are scaled by ``train_len / target_len`` so a model trained on ``train_len``
+    tokens addresses ``target_len`` (``crates/torsh-nn/src/layers/embedding.rs``: position interpolation)."""
+
+    def __init__(self, head_dim: int, train_len: int, target_len: int, base: float = 10000.0):
+        super().__init__()
+        self.scale = min(1.0, train_len / float(target_len))
+        inv = 1.0 / (base ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+        self.register_buffer("inv_freq", inv, persistent=False)
+
+    def forward(self, x, offset: int = 0):
+        """``x``: ``[B, S, H, D]``; rotates pairs ``(x[2i], x[2i+1])`` by the scaled position angle."""
+        s = x.shape[1]
+        pos = (torch.arange(s, device=x.device, dtype=torch.float32) + offset) * self.scale
+        ang = pos[:, None] * self.inv_freq.to(x.device)[None]
+        cos, sin = ang.cos()[None, :, None], ang.sin()[None, :, None]
+        xf = x.float()
+        a, b = xf[..., 0::2], xf[..., 1::2]
+        return torch.stack([a * cos - b * sin, a * sin + b * cos], -1).flatten(-2).to(x.dtype)
+
+
+class WeightStandardization(Module):
+    """Wraps a convolution / linear layer and standardises its weight per output unit on every forward."""
+
+    def __init__(self, module: torch.nn.Module, eps: float = 1e-5):
+        super().__init__()
+        self.module, self.eps = module, eps
+
+    def forward(self, x):
+        w = self.module.weight
+        dims = tuple(range(1, w.dim()))
+        ws = (w - w.mean(dims, keepdim=True)) / (w.var(dims, keepdim=True, unbiased=False) + self.eps).sqrt()
+        return torch.func.functional_call(self.module, {"weight": ws}, (x,), strict=False)
+
+
+def WeightNorm(module: torch.nn.Module, name: str = "weight", dim: int = 0):
+    """``w = g · v / ‖v‖`` re-parametrisation (``crates/torsh-nn/src/layers/normalization``: weight norm)."""
+    return torch.nn.utils.parametrizations.weight_norm(module, name, dim)
+
+
+def SpectralNorm(module: torch.nn.Module, name: str = "weight", n_power_iterations: int = 1, eps: float = 1e-12):
+    """Divides the weight by its largest singular value, tracked by power iteration."""
+    return torch.nn.utils.parametrizations.spectral_norm(module, name, n_power_iterations, eps)
+
+
+LazyLinear = torch.nn.LazyLinear
+LazyConv2d = torch.nn.LazyConv2d

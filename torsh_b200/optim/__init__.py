@@ -9,4 +9,4 @@ from . import checkpointing, distributed, mixed_precision, second_order
 from .distributed import AsyncSGD, DistributedOptimizer, ElasticAveragingSGD
 from .mixed_precision import (AutocastModel, BF16Config, BF16Trainer, DynamicLossScaler, GradScaler, MixedPrecisionConfig,
                               MixedPrecisionOptimizer, MixedPrecisionTrainer)
-from .second_order import KFAC, AdaHessian, NewtonCG, Shampoo, YellowFin
+from .second_order import KFAC, AdaHessian, NaturalGradient, NewtonCG, Shampoo, TrustRegion, YellowFin

@@ -220,3 +220,104 @@ class YellowFin(torch.optim.Optimizer):
                 buf.mul_(g["mu"]).add_(p.grad, alpha=-g["lr"])
                 p.add_(buf)
         return loss
+
+
+def _flat(ts):
+    return torch.cat([t.reshape(-1) for t in ts])
+
+
+class TrustRegion:
+    """Trust-region Newton method with the Steihaug conjugate-gradient sub-problem
+    (``crates/torsh-optim/src/trust_region.rs``): minimise the quadratic model inside a ball of radius ``delta``,
+    accept the step when the actual / predicted reduction ratio exceeds ``eta`` and grow or shrink the radius."""
+
+    def __init__(self, params, delta=1.0, max_delta=10.0, eta=0.1, cg_iters=20):
+        self.params = [p for p in params if p.requires_grad]
+        self.delta, self.max_delta, self.eta, self.cg_iters = delta, max_delta, eta, cg_iters
+
+    def _to_boundary(self, x, d):
+        a, b, c = d @ d, 2 * (x @ d), x @ x - self.delta ** 2
+        tau = (-b + (b * b - 4 * a * c).clamp(min=0).sqrt()) / (2 * a).clamp(min=1e-30)
+        return x + tau * d
+
+    def step(self, closure):
+        loss = closure()
+        grads = torch.autograd.grad(loss, self.params, create_graph=True)
+        g = _flat(grads)
+
+        def hvp(v):
+            return _flat(torch.autograd.grad(g, self.params, grad_outputs=v, retain_graph=True))
+        gd = g.detach()
+        x, r = torch.zeros_like(gd), gd.clone()
+        d = -r
+        for _ in range(self.cg_iters):
+            hd = hvp(d)
+            dhd = d @ hd
+            if dhd <= 0:                                  # negative curvature: walk to the boundary
+                x = self._to_boundary(x, d)
+                break
+            alpha = (r @ r) / dhd
+            xn = x + alpha * d
+            if xn.norm() >= self.delta:
+                x = self._to_boundary(x, d)
+                break
+            rn = r + alpha * hd
+            x = xn
+            if rn.norm() < 1e-10:
+                break
+            d, r = -rn + ((rn @ rn) / (r @ r)) * d, rn
+        predicted = -(gd @ x + 0.5 * (x @ hvp(x)))
+        with torch.no_grad():
+            off = 0
+            for q in self.params:
+                q.add_(x[off:off + q.numel()].view_as(q)); off += q.numel()
+        new_loss = closure().detach()
+        rho = float((loss.detach() - new_loss) / predicted.clamp(min=1e-30))
+        if rho < 0.25:
+            self.delta *= 0.25
+        elif rho > 0.75 and float(x.norm()) >= 0.99 * self.delta:
+            self.delta = min(2 * self.delta, self.max_delta)
+        if rho <= self.eta:                               # reject: undo the step
+            with torch.no_grad():
+                off = 0
+                for q in self.params:
+                    q.sub_(x[off:off + q.numel()].view_as(q)); off += q.numel()
+            return loss.detach()
+        return new_loss
+
+    def zero_grad(self):
+        for p in self.params:
+            p.grad = None
+
+
+class NaturalGradient(torch.optim.Optimizer):
+    """Natural-gradient descent with a running diagonal (or, for small tensors, full) empirical Fisher
+    (``crates/torsh-optim/src/natural_gradient.rs``): ``F ← β F + (1-β) g gᵀ``, ``p -= lr (F + λ I)⁻¹ g``."""
+
+    def __init__(self, params, lr=0.1, beta=0.95, damping=1e-3, full_below: int = 0):
+        super().__init__(params, dict(lr=lr, beta=beta, damping=damping, full_below=full_below))
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for grp in self.param_groups:
+            for p in grp["params"]:
+                if p.grad is None:
+                    continue
+                g = p.grad.float().reshape(-1)
+                st = self.state[p]
+                st["t"] = st.get("t", 0) + 1
+                deb = 1 - grp["beta"] ** st["t"]
+                if g.numel() <= grp["full_below"]:
+                    f = st.setdefault("fisher", torch.zeros(g.numel(), g.numel(), device=g.device))
+                    f.mul_(grp["beta"]).add_(torch.outer(g, g), alpha=1 - grp["beta"])
+                    nat = torch.linalg.solve(f / deb + grp["damping"] * torch.eye(g.numel(), device=g.device), g)
+                else:
+                    f = st.setdefault("fisher_diag", torch.zeros_like(g))
+                    f.mul_(grp["beta"]).addcmul_(g, g, value=1 - grp["beta"])
+                    nat = g / (f / deb + grp["damping"])
+                p.add_(nat.view_as(p).to(p.dtype), alpha=-grp["lr"])
+        return loss
