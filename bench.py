@@ -11,8 +11,8 @@ Synthetic uniform-random token ids, random-init N(0, 0.02) weights.
       --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
 
 Prints ONE JSON line on rank 0. `value` is device-timed (CUDA events, max over ranks) over exactly K
-steps; `e2e` times the same K steps through `CausalLMTrainer.step`, including the pinned-host → device
-copy of every batch and the device → host read of the loss.
+steps; `e2e` times the same K steps through `CausalLMTrainer.step_async` (one step in flight), including the
+pinned-host → device copy of every batch and the device → host read of every step's loss.
 """
 from __future__ import annotations
 
@@ -174,10 +174,22 @@ def main():
     # ---- end-to-end region: K steps through step(): H2D of the batch + D2H of the loss every step
     barrier()
     t0 = time.perf_counter()
+    pending = None
+    marks = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     for i in range(args.steps):
-        losses.append(trainer.step(ids_host[args.warmup + i], tgt_host[args.warmup + i]))
+        # one step in flight: step i is staged and launched, then the loss of step i - 1 is read
+        marks[i][0].record()
+        nxt = trainer.step_async(ids_host[args.warmup + i], tgt_host[args.warmup + i])
+        marks[i][1].record()
+        if pending is not None:
+            losses.append(pending.value())
+        pending = nxt
+    losses.append(pending.value())
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
+    # how long the device sat idle between consecutive steps of the end-to-end region
+    idle_ms = sum(marks[i][1].elapsed_time(marks[i + 1][0]) for i in range(args.steps - 1)) / max(1, args.steps - 1)
+    busy_ms = sum(a.elapsed_time(b) for a, b in marks) / args.steps
     clocks = sampler.stop()
     nv.check_status()
 
@@ -202,6 +214,7 @@ def main():
                        "l2": "working set per step (>10 GB) far exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                    "device_busy_ms_per_step": busy_ms, "device_idle_ms_between_steps": idle_ms,
                     "h2d_bytes_per_step": trainer.h2d_bytes_per_step, "d2h_bytes_per_step": trainer.d2h_bytes_per_step},
             "gpu_launches": trainer.launches_per_step * args.steps,
             "launches_per_step": trainer.launches_per_step,

@@ -43,6 +43,7 @@ def timeit(fn, iters, flush):
 
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--no-residual", action="store_true", help="bn: BatchNorm + ReLU without a residual input")
     ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "layernorm", "xent", "adamw", "bn", "conv"])
     ap.add_argument("--hw", type=int, default=56); ap.add_argument("--channels", type=int, default=256)
     ap.add_argument("--cout", type=int, default=0); ap.add_argument("--ksize", type=int, default=3); ap.add_argument("--stride", type=int, default=1)
@@ -110,17 +111,19 @@ def main():
         from torsh_b200.ops.conv import batch_norm_nhwc
         C = a.channels
         x = torch.randn(a.batch, a.hw, a.hw, C, device=dev, dtype=torch.bfloat16, requires_grad=True)
-        r = torch.randn_like(x)
+        r = None if a.no_residual else torch.randn_like(x)
         bn = torch.nn.BatchNorm2d(C).to(dev)
         nbytes = x.numel() * 2
         with torch.no_grad():
             ms = timeit(lambda: batch_norm_nhwc(x, bn, residual=r, relu=True), a.iters, flush)
-        gb = 4.0 * nbytes / ms / 1e6      # statistics read x; apply reads x and the residual, writes y
+        gb = (3.0 if r is None else 4.0) * nbytes / ms / 1e6      # statistics read x; apply reads x (and the residual), writes y
         print(f"batchnorm fwd (+residual, +relu) {a.batch}x{a.hw}x{a.hw}x{C}: {ms*1e3:.1f} us, {gb:.0f} GB/s = {gb/hbm:.2f} of {kind} copy bandwidth")
         y = batch_norm_nhwc(x, bn, residual=r, relu=True)
         dy = torch.randn_like(y)
         ms = timeit(lambda: y.backward(dy, retain_graph=True), a.iters, flush)
-        gb = 8.0 * nbytes / ms / 1e6      # reduce reads dy, y, x; apply reads them again and writes dx and the residual gradient
+        # reduce reads dy, y, x; apply reads them again and writes dx and the residual gradient; without a residual the
+        # mask is recomputed from x: dy, x twice and dx
+        gb = (5.0 if r is None else 8.0) * nbytes / ms / 1e6
         print(f"batchnorm bwd {a.batch}x{a.hw}x{a.hw}x{C}: {ms*1e3:.1f} us, {gb:.0f} GB/s = {gb/hbm:.2f} of {kind} copy bandwidth")
     elif a.what == "conv":
         from torsh_b200.ops.conv import conv2d_nhwc

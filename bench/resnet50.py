@@ -125,11 +125,42 @@ def main():
     barrier()
     dev_ms = e0.elapsed_time(e1)
     barrier()
+    # end to end: batch i + 1 is copied from pinned memory on a side stream while step i runs; the loss of step i is
+    # copied to pinned memory behind the step and read after step i + 1 has been launched (every loss is read)
+    copy_stream = torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    xbuf = [torch.empty_like(x_dev) for _ in range(2)]
+    ybuf = [torch.empty_like(y_dev) for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    loss_host = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
+    loss_done = [torch.cuda.Event() for _ in range(2)]
+
+    def stage(i):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[i % 2])
+            xbuf[i % 2].copy_(x_host[i % nb], non_blocking=True)
+            ybuf[i % 2].copy_(y_host[i % nb], non_blocking=True)
+            ready[i % 2].record()
+
+    for ev in consumed:
+        ev.record()
     t0 = time.perf_counter()
+    stage(0)
+    last = None
     for i in range(args.steps):
-        xb = x_host[i % nb].to(dev, non_blocking=True)
-        yb = y_host[i % nb].to(dev, non_blocking=True)
-        last = step(xb, yb).item()
+        if i + 1 < args.steps:
+            stage(i + 1)
+        main.wait_event(ready[i % 2])
+        loss = step(xbuf[i % 2], ybuf[i % 2])
+        consumed[i % 2].record()
+        loss_host[i % 2].copy_(loss.detach().float(), non_blocking=True)
+        loss_done[i % 2].record()
+        if i > 0:
+            loss_done[(i - 1) % 2].synchronize()
+            last = float(loss_host[(i - 1) % 2])
+    loss_done[(args.steps - 1) % 2].synchronize()
+    last = float(loss_host[(args.steps - 1) % 2])
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop()

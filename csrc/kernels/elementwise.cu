@@ -196,7 +196,19 @@ __global__ void colsum_kernel(const T* __restrict__ x, float* __restrict__ out, 
   if (c0 < cols) {
     long r = r0 + threadIdx.y;
     if (vec_ok) {
-      // four rows in flight per thread
+      // eight, then four rows in flight per thread
+      for (; r + 56 < r1; r += 64) {
+        Vec16<T> t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) t[u].load_nc(x + (r + 8 * u) * ld + c0);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          float f[N];
+          t[u].get(f);
+#pragma unroll
+          for (int j = 0; j < N; ++j) acc[j] += f[j];
+        }
+      }
       for (; r + 24 < r1; r += 32) {
         Vec16<T> t[4];
 #pragma unroll
@@ -328,8 +340,8 @@ TB_EXPORT int tb_colsum(const void* x, float* out, long rows, int cols, long ld,
   const int N = dtype == 0 ? 8 : 4;
   const int cols_per_block = 32 * N;
   const int col_blocks = (cols + cols_per_block - 1) / cols_per_block;
-  // enough row blocks to fill the GPU about twice, at least 64 rows each
-  long want = (2L * sm_count() + col_blocks - 1) / col_blocks;
+  // enough row blocks for about six CTAs per SM (the loads of one thread cover 64 rows at a time), at least 64 rows each
+  long want = (6L * sm_count() + col_blocks - 1) / col_blocks;
   long rpb = (rows + want - 1) / want;
   if (rpb < 64) rpb = 64;
   dim3 grid(col_blocks, (unsigned)((rows + rpb - 1) / rpb)), block(32, 8);

@@ -39,6 +39,35 @@ def test_gpt2_tiny_training_matches_fp32_oracle():
     assert got[-1] < got[0] - 1.0
 
 
+def test_pipelined_steps_return_the_same_losses_as_synchronous_steps():
+    """``step_async`` with one step in flight (loss read one step late) follows the trajectory of ``step``."""
+    from torsh_b200.engine import CausalLMTrainer
+    from torsh_b200.models import GPT2Config, GPTForCausalLM
+    cfg = GPT2Config.tiny()
+    g = torch.Generator().manual_seed(1)
+    batches = [torch.randint(0, cfg.vocab_size, (8, 129), generator=g) for _ in range(10)]
+    xs = [b[:, :-1].contiguous().pin_memory() for b in batches]
+    ys = [b[:, 1:].contiguous().pin_memory() for b in batches]
+    runs = []
+    for pipelined in (False, True):
+        torch.manual_seed(0)
+        tr = CausalLMTrainer(GPTForCausalLM(cfg).to("cuda"), lr=3e-4, batch_size=8, seq_len=128, use_graph=True, warmup_eager=2)
+        if not pipelined:
+            runs.append([tr.step(x, y) for x, y in zip(xs, ys)])
+            continue
+        out, pending = [], None
+        for x, y in zip(xs, ys):
+            nxt = tr.step_async(x, y)
+            if pending is not None:
+                out.append(pending.value())
+            pending = nxt
+        out.append(pending.value())
+        runs.append(out)
+    assert len(runs[1]) == 10
+    for a, b in zip(*runs):
+        assert abs(a - b) < 2e-2 * abs(a), runs      # atomics in split-K make the two runs differ in the last bits
+
+
 def test_layernorm_params_receive_gradient_through_flat_buffers():
     from torsh_b200.models import GPT2Config, GPTForCausalLM
     from torsh_b200.optim import FlatParameters

@@ -16,7 +16,21 @@ from . import _native as nv
 from .optim.flat import FlatAdamW, FlatParameters
 
 
+class PendingLoss:
+    """The loss of a step that may still be running: :meth:`value` waits for that step's device→host copy only."""
+
+    def __init__(self, buf: torch.Tensor, event):
+        self._buf, self._event = buf, event
+
+    def value(self) -> float:
+        if self._event is not None:
+            self._event.synchronize()
+        return float(self._buf)
+
+
 class CausalLMTrainer:
+    PIPELINE_SLOTS = 4
+
     def __init__(self, model, *, lr: float = 3e-4, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01,
                  batch_size: int, seq_len: int, use_graph: bool = True, warmup_eager: int = 2, grad_accum: int = 1,
                  parallel=None):
@@ -36,6 +50,10 @@ class CausalLMTrainer:
         self.static_targets = torch.zeros(batch_size, seq_len, dtype=torch.int64, device=self.device)
         self.static_loss = torch.zeros((), dtype=torch.float32, device=self.device)
         self.loss_host = torch.zeros((), dtype=torch.float32).pin_memory() if self.device.type == "cuda" else torch.zeros(())
+        cuda = self.device.type == "cuda"
+        self._loss_ring = [torch.zeros((), dtype=torch.float32).pin_memory() if cuda else torch.zeros(())
+                           for _ in range(self.PIPELINE_SLOTS)]
+        self._loss_events = [torch.cuda.Event() if cuda else None for _ in range(self.PIPELINE_SLOTS)]
         self.graph = None
         self.steps_done = 0
         self.launches_per_step = 0
@@ -85,3 +103,17 @@ class CausalLMTrainer:
             torch.cuda.current_stream().synchronize()
             return float(self.loss_host)
         return float(self.static_loss)
+
+    def step_async(self, ids: torch.Tensor, targets: torch.Tensor) -> PendingLoss:
+        """Like :meth:`step`, but returns at once with a handle on the loss, so the host can stage and launch the next
+        step while this one runs (read the handle one step late and the device never idles between steps). ``ids`` and
+        ``targets`` must stay untouched until the step has run; at most ``PIPELINE_SLOTS`` handles may be unread."""
+        self.static_ids.copy_(ids, non_blocking=True)
+        self.static_targets.copy_(targets, non_blocking=True)
+        self.step_device_only()
+        slot = self.steps_done % self.PIPELINE_SLOTS
+        buf, ev = self._loss_ring[slot], self._loss_events[slot]
+        buf.copy_(self.static_loss, non_blocking=True)
+        if ev is not None:
+            ev.record()
+        return PendingLoss(buf, ev)

@@ -14,6 +14,8 @@ host loops.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from .. import _native as nv
@@ -145,6 +147,10 @@ def conv2d_nhwc(x: torch.Tensor, weight: torch.Tensor, stride: int = 1, padding:
     return y.permute(0, 2, 3, 1).to(x.dtype)
 
 
+# TORSH_BN_RECOMPUTE_MASK=0 keeps the output for the backward's ReLU mask instead of recomputing it from x
+_BN_RECOMPUTE_MASK = os.environ.get("TORSH_BN_RECOMPUTE_MASK", "1") != "0"
+
+
 class _BatchNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, gamma, beta, residual, run_mean, run_var, eps, momentum, relu):
@@ -161,7 +167,7 @@ class _BatchNormFn(torch.autograd.Function):
              nv.ptr(run_var), rows, c, eps, momentum, int(relu), nv.stream_ptr())
         # without a residual the backward recomputes the ReLU mask from x, so the output need not be kept for it
         c8 = c // 8
-        recompute = relu and residual is None and c8 <= 256 and (c8 & (c8 - 1)) == 0
+        recompute = relu and residual is None and c8 <= 256 and (c8 & (c8 - 1)) == 0 and _BN_RECOMPUTE_MASK
         ctx.save_for_backward(x, y if (relu and not recompute) else None, mean, rstd, g32, b32)
         ctx.relu, ctx.has_res, ctx.pdtype = relu, residual is not None, gamma.dtype
         return y

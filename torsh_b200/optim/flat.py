@@ -67,7 +67,7 @@ class FlatAdamW:
         self.step_count = 0
         self.param_groups = [{"lr": lr, "params": flat.params}]
         self.dyn = torch.zeros(3, dtype=torch.float32, device=flat.device)
-        self._dyn_host = torch.zeros(3, dtype=torch.float32)
+        self._dyn_host = torch.zeros(8, 3, dtype=torch.float32)
         if flat.device.type == "cuda":
             self._dyn_host = self._dyn_host.pin_memory()
 
@@ -81,10 +81,12 @@ class FlatAdamW:
         """Host part of a step: advance the step count and upload lr and the two bias corrections.
         Runs outside any CUDA graph; :meth:`launch` is the capturable device part."""
         self.step_count += 1
-        self._dyn_host[0] = self.param_groups[0]["lr"]
-        self._dyn_host[1] = 1.0 - self.betas[0] ** self.step_count
-        self._dyn_host[2] = 1.0 - self.betas[1] ** self.step_count
-        self.dyn.copy_(self._dyn_host, non_blocking=True)
+        # one pinned row per step in flight: the asynchronous upload of an earlier step may not have run yet
+        row = self._dyn_host[self.step_count % self._dyn_host.shape[0]]
+        row[0] = self.param_groups[0]["lr"]
+        row[1] = 1.0 - self.betas[0] ** self.step_count
+        row[2] = 1.0 - self.betas[1] ** self.step_count
+        self.dyn.copy_(row, non_blocking=True)
 
     def step(self, grad_scale: float = 1.0, zero_grad: bool = True):
         self.prepare_step()

@@ -153,7 +153,7 @@ class ShardedAdamW:
         self.param_groups = [{"lr": lr, "params": flat.params}]
         self.step_count = 0
         self.dyn = torch.zeros(3, dtype=torch.float32, device=flat.device)
-        self._dyn_host = torch.zeros(3, dtype=torch.float32).pin_memory()
+        self._dyn_host = torch.zeros(8, 3, dtype=torch.float32).pin_memory()
 
     def get_lr(self):
         return [self.param_groups[0]["lr"]]
@@ -163,10 +163,12 @@ class ShardedAdamW:
 
     def prepare_step(self):
         self.step_count += 1
-        self._dyn_host[0] = self.param_groups[0]["lr"]
-        self._dyn_host[1] = 1.0 - self.betas[0] ** self.step_count
-        self._dyn_host[2] = 1.0 - self.betas[1] ** self.step_count
-        self.dyn.copy_(self._dyn_host, non_blocking=True)
+        # one pinned row per step in flight: the asynchronous upload of an earlier step may not have run yet
+        row = self._dyn_host[self.step_count % self._dyn_host.shape[0]]
+        row[0] = self.param_groups[0]["lr"]
+        row[1] = 1.0 - self.betas[0] ** self.step_count
+        row[2] = 1.0 - self.betas[1] ** self.step_count
+        self.dyn.copy_(row, non_blocking=True)
 
     def zero_grad(self, set_to_none: bool = False):
         self.flat.zero_grad()
