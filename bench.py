@@ -50,14 +50,22 @@ class ClockSampler:
 
     def _pump(self):
         for ln in self.proc.stdout:
-            self.lines.append(ln.strip())
+            self.lines.append((time.perf_counter(), ln.strip()))
 
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
+        return self.window(float("-inf"), float("inf"))
+
+    def window(self, t0: float, t1: float) -> dict:
+        """Statistics of the samples that arrived between two ``time.perf_counter()`` instants."""
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         sm, mx, reasons = [], None, set()
-        for ln in self.lines:
+        for ts, ln in list(self.lines):
+            if not (t0 <= ts <= t1 + 0.05):
+                continue
             f = [x.strip() for x in ln.split(",")]
             if len(f) < 8:
                 continue
@@ -96,6 +104,8 @@ def main():
     ap.add_argument("--fsdp-comm-blocks", type=int, default=0, help="CTAs of the fused FSDP kernel while it overlaps backward")
     ap.add_argument("--fsdp-no-overlap", action="store_true", help="run every FSDP unit after backward instead of from hooks")
     ap.add_argument("--fsdp-nvls", type=int, default=None, help="1 / 0: force NVLS multimem on / off in the fused FSDP kernel")
+    ap.add_argument("--fsdp-single", action="store_true",
+                    help="diagnostic: run the FSDP engine in a one-rank group on one GPU (its kernels without any peer)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -113,8 +123,11 @@ def main():
             return 2
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
+    if world > 1 or args.fsdp_single:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29517")
+        os.environ.setdefault("RANK", "0")
+        os.environ.setdefault("WORLD_SIZE", "1")
         dist.init_process_group("nccl", device_id=dev)
 
     from torsh_b200 import _native as nv
@@ -127,7 +140,7 @@ def main():
     torch.manual_seed(1234)
     model = GPTForCausalLM(cfg).to(dev)
     parallel = None
-    if world > 1:
+    if world > 1 or args.fsdp_single:
         from torsh_b200.parallel.fsdp import FlatFSDP
         from torsh_b200.parallel.fsdp import FsdpConfig
         fc = FsdpConfig()
@@ -154,24 +167,15 @@ def main():
         torch.cuda.synchronize()
 
     # ---- warm-up (eager steps, graph capture, first replays) through the public step() call
+    sampler = ClockSampler(local_rank)      # one nvidia-smi process for the whole run; the regions pick their samples
+    sampler.start()
     losses = []
     for i in range(args.warmup):
         losses.append(trainer.step(ids_host[i], tgt_host[i]))
     nv.check_status()
 
-    # ---- device-timed region: K steps on resident batches (kernel-only number)
-    sampler = ClockSampler(local_rank)
-    sampler.start()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        trainer.step_device_only()
-    e1.record()
-    barrier()
-    dev_ms = e0.elapsed_time(e1)
-
-    # ---- end-to-end region: K steps through step(): H2D of the batch + D2H of the loss every step
+    # ---- end-to-end region (first: it is the headline): K steps through step_async(), H2D of the batch + D2H of the
+    #      loss every step
     barrier()
     t0 = time.perf_counter()
     pending = None
@@ -190,7 +194,21 @@ def main():
     # how long the device sat idle between consecutive steps of the end-to-end region
     idle_ms = sum(marks[i][1].elapsed_time(marks[i + 1][0]) for i in range(args.steps - 1)) / max(1, args.steps - 1)
     busy_ms = sum(a.elapsed_time(b) for a, b in marks) / args.steps
-    clocks = sampler.stop()
+    e2e_clocks = sampler.window(t0, time.perf_counter())
+
+    # ---- device-timed region: K steps on resident batches (kernel-only number)
+    barrier()
+    t_dev0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        trainer.step_device_only()
+    e1.record()
+    barrier()
+    dev_ms = e0.elapsed_time(e1)
+    clocks = sampler.window(t_dev0, time.perf_counter())
+    sampler.stop()
+
     nv.check_status()
 
     t = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
@@ -209,19 +227,20 @@ def main():
             "config": {"model": args.model, "layers": cfg.n_layer, "d_model": cfg.n_embd, "heads": cfg.n_head,
                        "ffn": cfg.inner, "vocab": cfg.vocab_size, "global_batch": world * B, "micro_batch_per_gpu": B,
                        "seq_len": S, "optimizer": "AdamW fp32 master weights", "dropout": 0.0,
-                       "parallelism": f"fsdp{world}" if world > 1 else "single",
+                       "parallelism": f"fsdp{world}" if parallel is not None else "single",
                        "cuda_graph": trainer.graph is not None,
                        "l2": "working set per step (>10 GB) far exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "device_busy_ms_per_step": busy_ms, "device_idle_ms_between_steps": idle_ms,
+                    "clocks": e2e_clocks,
                     "h2d_bytes_per_step": trainer.h2d_bytes_per_step, "d2h_bytes_per_step": trainer.d2h_bytes_per_step},
             "gpu_launches": trainer.launches_per_step * args.steps,
             "launches_per_step": trainer.launches_per_step,
             "loss_first": losses[0], "loss_last": losses[-1],
         }
         print(json.dumps(out))
-    if world > 1:
+    if dist.is_initialized():
         dist.destroy_process_group()
     return 0
 

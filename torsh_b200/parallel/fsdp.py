@@ -195,6 +195,10 @@ class FlatFSDP:
     # ---- construction -----------------------------------------------------------------------------
     def flatten(self, model: torch.nn.Module, units=None) -> ShardedFlatParameters:
         units = units or default_units(model, self.cfg.min_num_params)
+        if not self.cfg.overlap:
+            # nothing runs before backward has finished, so the whole model is ONE unit: one launch, one pair of
+            # cross-rank barriers and one pass at full width instead of a barrier-separated kernel per block
+            units = [[p for u in units for p in u]]
         flat = ShardedFlatParameters(units, self.group)
         self._flat = flat
         if self.cfg.overlap:
