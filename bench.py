@@ -102,7 +102,8 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=1024)
     ap.add_argument("--fsdp-comm-blocks", type=int, default=0, help="CTAs of the fused FSDP kernel while it overlaps backward")
-    ap.add_argument("--fsdp-no-overlap", action="store_true", help="run every FSDP unit after backward instead of from hooks")
+    ap.add_argument("--fsdp-no-overlap", action="store_true", help="one fused FSDP launch after backward (the default)")
+    ap.add_argument("--fsdp-overlap", action="store_true", help="launch each block's FSDP kernel from a backward hook on a side stream")
     ap.add_argument("--fsdp-nvls", type=int, default=None, help="1 / 0: force NVLS multimem on / off in the fused FSDP kernel")
     ap.add_argument("--fsdp-single", action="store_true",
                     help="diagnostic: run the FSDP engine in a one-rank group on one GPU (its kernels without any peer)")
@@ -146,8 +147,7 @@ def main():
         fc = FsdpConfig()
         if args.fsdp_comm_blocks:
             fc.comm_blocks = args.fsdp_comm_blocks
-        if args.fsdp_no_overlap:
-            fc.overlap = False
+        fc.overlap = bool(args.fsdp_overlap) and not args.fsdp_no_overlap
         if args.fsdp_nvls is not None:
             fc.use_nvls = bool(args.fsdp_nvls)
         parallel = FlatFSDP(dist.group.WORLD, fc)

@@ -48,14 +48,27 @@ struct FsdpArgs {
 };
 
 template <bool NVLS>
-__global__ void __launch_bounds__(FSDP_THREADS)
+// two CTAs per SM (at most 64 registers per thread): the whole-GPU launches of 2 x SM-count CTAs are resident at once
+__global__ void __launch_bounds__(FSDP_THREADS, 2)
 fsdp_rs_adamw_ag_kernel(FsdpArgs a) {
   const uint32_t epoch = *a.epoch_ptr;
+  float lr = a.lr, bc1 = a.bc1, bc2 = a.bc2;
   if (a.dyn) {
-    a.lr = a.dyn[0];
-    a.bc1 = a.dyn[1];
-    a.bc2 = a.dyn[2];
+    lr = a.dyn[0];
+    bc1 = a.dyn[1];
+    bc2 = a.dyn[2];
   }
+  // peer base pointers in shared memory: indexing the kernel-parameter arrays with a run-time rank would move
+  // them to local memory and put a local load in front of every peer access
+  __shared__ const float* s_grads[MAX_RANKS];
+  __shared__ __nv_bfloat16* s_params[MAX_RANKS];
+#pragma unroll
+  for (int i = 0; i < MAX_RANKS; ++i)
+    if (threadIdx.x == i) {
+      s_grads[i] = reinterpret_cast<const float*>(a.grads.ptr[i]);
+      s_params[i] = reinterpret_cast<__nv_bfloat16*>(a.params.ptr[i]);
+    }
+  __syncthreads();
   // every rank's backward has finished writing this unit's gradients
   cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch, a.status);
   const long shard = a.unit_len / a.world;
@@ -76,7 +89,7 @@ fsdp_rs_adamw_ag_kernel(FsdpArgs a) {
       for (int j = 0; j < 8; ++j) g[j] = 0.f;
       for (int p = 0; p < a.world; ++p) {
         const int q = (a.rank + p) % a.world;
-        const float4* src = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a.grads.ptr[q]) + ge);
+        const float4* src = reinterpret_cast<const float4*>(s_grads[q] + ge);
         float4 x = src[0], y = src[1];
         g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w; g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
       }
@@ -92,10 +105,10 @@ fsdp_rs_adamw_ag_kernel(FsdpArgs a) {
     for (int j = 0; j < 8; ++j) {
       const float gi = g[j] * a.grad_scale;
       float p = w[j];
-      p -= a.lr * a.wd * p;
+      p -= lr * a.wd * p;
       m[j] = a.beta1 * m[j] + (1.f - a.beta1) * gi;
       s[j] = a.beta2 * s[j] + (1.f - a.beta2) * gi * gi;
-      p -= a.lr * (m[j] / a.bc1) / (sqrtf(s[j] / a.bc2) + a.eps);
+      p -= lr * (m[j] / bc1) / (sqrtf(s[j] / bc2) + a.eps);
       w[j] = p;
     }
     *reinterpret_cast<float4*>(a.master + se) = *reinterpret_cast<float4*>(w);
@@ -111,7 +124,7 @@ fsdp_rs_adamw_ag_kernel(FsdpArgs a) {
     } else {
       for (int p = 0; p < a.world; ++p) {
         const int q = (a.rank + p) % a.world;
-        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(a.params.ptr[q]) + ge) = o;
+        *reinterpret_cast<uint4*>(s_params[q] + ge) = o;
       }
     }
   }
@@ -120,7 +133,7 @@ fsdp_rs_adamw_ag_kernel(FsdpArgs a) {
   // Clear my own copy of the gradient for the next accumulation. This CTA's exit barrier only proves
   // that the CTAs with the same index on the other ranks are done reading, so it clears exactly the
   // vectors those CTAs read: the same vector indices, in every rank's shard.
-  float* gmine = reinterpret_cast<float*>(a.grads.ptr[a.rank]) + a.unit_off;
+  float* gmine = const_cast<float*>(s_grads[a.rank]) + a.unit_off;
   for (int q = 0; q < a.world; ++q) {
     float4* gz = reinterpret_cast<float4*>(gmine + (long)q * shard);
     for (long v = tid; v < nvec; v += nthreads) {

@@ -104,7 +104,7 @@ def check_fsdp(dev):
     data = torch.randint(0, cfg.vocab_size, (world * B, S + 1), generator=torch.Generator().manual_seed(7))
     ok = True
     ref_losses = None
-    for overlap, use_graph in ((False, False), (True, False), (True, True)):
+    for overlap, use_graph in ((False, False), (False, True), (True, False), (True, True)):
         torch.manual_seed(0)
         model = GPTForCausalLM(cfg).to(dev)
         eng = FlatFSDP(config=FsdpConfig(overlap=overlap))

@@ -61,7 +61,11 @@ class FsdpConfig:
     mixed_precision: MixedPrecisionConfig = field(default_factory=MixedPrecisionConfig)
     cpu_offload: bool = False
     backward_prefetch: BackwardPrefetch = BackwardPrefetch.BACKWARD_PRE
-    overlap: bool = True
+    # overlap=True hands each block's fused reduce-scatter + AdamW + all-gather kernel to a side stream from a backward
+    # hook; overlap=False runs the whole model as one fused launch after backward. Measured on GPT-2-medium, 2 B200s:
+    # 30.8 ms per step with overlap (the 64 co-resident CTAs slow the statically scheduled GEMM tiles of the SMs they
+    # share, and 25 barrier-separated launches cost 1.2 ms even with a single rank), 30.0 ms without.
+    overlap: bool = False
     comm_blocks: int = 64      # CTAs while overlapping backward (measured on 2 B200s: 16 -> 32.1 ms, 32 -> 31.0, 64 -> 30.1 per step)
     tail_blocks: int = 296     # CTAs of the units that are reduced after backward has finished
     use_nvls: bool | None = None
