@@ -35,6 +35,8 @@ def main():
     ap.add_argument("--image", type=int, default=224)
     ap.add_argument("--impl", default="ours", choices=["ours", "torch"])
     ap.add_argument("--model", default="resnet50")
+    ap.add_argument("--ddp-no-overlap", action="store_true", help="reduce all gradient buckets after backward instead of from hooks")
+    ap.add_argument("--ddp-comm-blocks", type=int, default=64, help="CTAs of the fused bucket all-reduce kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -63,8 +65,9 @@ def main():
         model.use_kernels = True
         net = model
         if world > 1:
-            from torsh_b200.parallel.ddp import DistributedDataParallel
-            net = DistributedDataParallel(model, bucket_cap_mb=25.0)
+            from torsh_b200.parallel.ddp import DistributedDataParallel, OverlapConfig
+            net = DistributedDataParallel(model, bucket_cap_mb=25.0, comm_blocks=args.ddp_comm_blocks,
+                                          overlap_config=OverlapConfig(enabled=not args.ddp_no_overlap))
         opt = SGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
 
         def step(x, y):
