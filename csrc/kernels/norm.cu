@@ -31,19 +31,32 @@ __global__ void norm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ g
       if (!RMS && beta) b[i].load_nc(beta + v * N);
     }
   }
+  // the next row's vectors are requested before this row's reductions, so their latency hides behind the block sums
+  Vec16<T> nxt[VPT];
+  if ((int)blockIdx.x < rows) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) nxt[i].load(x + (size_t)blockIdx.x * H + v * N);
+    }
+  }
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const T* xr = x + (size_t)row * H;
     float f[VPT][N];
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       int v = threadIdx.x + i * blockDim.x;
       if (v < nvec) {
-        Vec16<T> t;
-        t.load(xr + v * N);
-        t.get(f[i]);
+        nxt[i].get(f[i]);
 #pragma unroll
         for (int j = 0; j < N; ++j) s += RMS ? f[i][j] * f[i][j] : f[i][j];
+      }
+    }
+    if (row + (int)gridDim.x < rows) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        int v = threadIdx.x + i * blockDim.x;
+        if (v < nvec) nxt[i].load(x + (size_t)(row + gridDim.x) * H + v * N);
       }
     }
     float mean = 0.f, rstd;
@@ -116,21 +129,33 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
       t.get(gf[i]);
     }
   }
+  // the next row's vectors are requested before this row's reductions, so their latency hides behind the block sums
+  Vec16<T> nx[VPT], nd[VPT], nr[VPT];
+  auto request = [&](int row) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int v = threadIdx.x + i * blockDim.x;
+      if (v < nvec) {
+        nx[i].load(x + (size_t)row * H + v * N);
+        nd[i].load(dy + (size_t)row * H + v * N);
+        if (dres) nr[i].load(dres + (size_t)row * H + v * N);
+      }
+    }
+  };
+  if ((int)blockIdx.x < rows) request(blockIdx.x);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float mean = RMS ? 0.f : mean_in[row];
     const float rstd = rstd_in[row];
-    float xh[VPT][N], dyg[VPT][N];
+    float xh[VPT][N], dyg[VPT][N], res[VPT][N];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       int v = threadIdx.x + i * blockDim.x;
       if (v < nvec) {
-        Vec16<T> tx, td;
-        tx.load(x + (size_t)row * H + v * N);
-        td.load(dy + (size_t)row * H + v * N);
         float xf[N], df[N];
-        tx.get(xf);
-        td.get(df);
+        nx[i].get(xf);
+        nd[i].get(df);
+        if (dres) nr[i].get(res[i]);
 #pragma unroll
         for (int j = 0; j < N; ++j) {
           xh[i][j] = (xf[j] - mean) * rstd;
@@ -142,6 +167,7 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
         }
       }
     }
+    if (row + (int)gridDim.x < rows) request(row + gridDim.x);
     if (!RMS) s1 = block_sum(s1, scratch) / H; else s1 = 0.f;
     s2 = block_sum(s2, scratch) / H;
 #pragma unroll
@@ -149,14 +175,8 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
       int v = threadIdx.x + i * blockDim.x;
       if (v < nvec) {
         float o[N];
-        if (dres) {
-          Vec16<T> tr;
-          tr.load(dres + (size_t)row * H + v * N);
-          tr.get(o);
-        } else {
 #pragma unroll
-          for (int j = 0; j < N; ++j) o[j] = 0.f;
-        }
+        for (int j = 0; j < N; ++j) o[j] = dres ? res[i][j] : 0.f;
 #pragma unroll
         for (int j = 0; j < N; ++j) o[j] += rstd * (dyg[i][j] - s1 - xh[i][j] * s2);
         Vec16<T> t;
