@@ -53,7 +53,7 @@ def main():
     ap.add_argument("--heads", type=int, default=16); ap.add_argument("--dim", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--compare", action="store_true", help="gemm: also time torch.matmul on the same operands")
-    ap.add_argument("--split-k", type=int, default=1, help="gemm: K splits (implies fp32 atomic accumulation, the weight-gradient path)")
+    ap.add_argument("--split-k", type=int, default=1, help="gemm: K splits, -1 = stream-K (implies fp32 atomic accumulation, the weight-gradient path)")
     a = ap.parse_args()
     from torsh_b200 import _native as nv
     dev = "cuda"
@@ -64,7 +64,7 @@ def main():
         from torsh_b200.ops.gemm import gemm
         A = torch.randn((a.m, a.k) if a.a_major == 0 else (a.k, a.m), device=dev, dtype=torch.bfloat16)
         B = torch.randn((a.n, a.k) if a.b_major == 0 else (a.k, a.n), device=dev, dtype=torch.bfloat16)
-        if a.split_k > 1:
+        if a.split_k != 1:
             out = torch.zeros(a.m, a.n, device=dev, dtype=torch.float32)
             ms = timeit(lambda: gemm(A, B, a_major=a.a_major, b_major=a.b_major, out=out, bn=a.bn, atomic=True, split_k=a.split_k), a.iters, flush)
         else:

@@ -52,6 +52,7 @@ struct GemmParams {
   int split_k;
   int tiles_m, tiles_n;
   int kb_total, kb_per_split;
+  int stream_k;  // 1: workers own equal contiguous ranges of (tile, K-block) units instead of whole K-splits
   int* status;
   // ---- tensor-parallel fusions (all zero / null for a plain GEMM) --------------------------------
   // GEMM -> reduce-scatter: output row r belongs to rank r / rs_rows; the epilogue stores the tile
@@ -117,6 +118,20 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
 }
 __device__ __forceinline__ void bulk_wait_read_le1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
+__device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int& m_t, int& n_t) {
+  if (p.flags & EPI_RASTER_M) {
+    n_t = tile / p.tiles_m;
+    m_t = tile - n_t * p.tiles_m;
+  } else {
+    m_t = tile / p.tiles_n;
+    n_t = tile - m_t * p.tiles_n;
+  }
+  if (p.m_rot) {
+    m_t += p.m_rot;
+    if (m_t >= p.tiles_m) m_t -= p.tiles_m;
+  }
+}
+
 __device__ __forceinline__ void decode_work(const GemmParams& p, int work, int& m_t, int& n_t,
                                             int& kb0, int& kb1) {
   int tile = work / p.split_k;
@@ -135,6 +150,41 @@ __device__ __forceinline__ void decode_work(const GemmParams& p, int work, int& 
   kb0 = ks * p.kb_per_split;
   kb1 = min(p.kb_total, kb0 + p.kb_per_split);
 }
+
+// The sequence of (tile, K-block range) pieces of one worker CTA; the TMA, MMA and epilogue roles each walk their own
+// copy and see the same sequence. Split-K mode: work units worker, worker + nworkers, ... Stream-K mode (atomic fp32
+// output only): the tiles x K-blocks units are cut into nworkers equal contiguous ranges, so every CTA does the same
+// number of K-blocks whatever the tile count; a range that crosses a tile boundary becomes two pieces, and each
+// piece adds its partial product into the output.
+struct WorkIter {
+  int pos, end, stride;
+  __device__ __forceinline__ WorkIter(const GemmParams& p, int worker, int nworkers) {
+    if (p.stream_k) {
+      const long units = (long)p.tiles_m * p.tiles_n * p.kb_total;
+      pos = (int)(units * worker / nworkers);
+      end = (int)(units * (worker + 1) / nworkers);
+      stride = 0;
+    } else {
+      pos = worker;
+      end = p.tiles_m * p.tiles_n * p.split_k;
+      stride = nworkers;
+    }
+  }
+  __device__ __forceinline__ bool next(const GemmParams& p, int& m_t, int& n_t, int& kb0, int& kb1) {
+    if (pos >= end) return false;
+    if (p.stream_k) {
+      const int tile = pos / p.kb_total;
+      kb0 = pos - tile * p.kb_total;
+      kb1 = min(p.kb_total, kb0 + (end - pos));
+      decode_tile(p, tile, m_t, n_t);
+      pos += kb1 - kb0;
+    } else {
+      decode_work(p, pos, m_t, n_t, kb0, kb1);
+      pos += stride;
+    }
+    return true;
+  }
+};
 
 // Convolution mode: first output row and number of valid rows of M tile m_t.
 __device__ __forceinline__ void conv_tile(const GemmParams& p, int m_t, int& n0, int& h0, long& base_row, int& valid) {
@@ -329,7 +379,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_work = p.tiles_m * p.tiles_n * p.split_k;
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
 
   if (p.ag_ctas > 0 && (int)blockIdx.x < p.ag_ctas) {
@@ -375,9 +424,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tma_prefetch_desc(&map_b);
       int s = 0;
       uint32_t phase = 0;
-      for (int work = worker; work < total_work; work += nworkers) {
-        int m_t, n_t, kb0, kb1;
-        decode_work(p, work, m_t, n_t, kb0, kb1);
+      WorkIter it(p, worker, nworkers);
+      int m_t, n_t, kb0, kb1;
+      while (it.next(p, m_t, n_t, kb0, kb1)) {
         if (p.ag_ctas > 0 && (m_t * BM) / p.ag_rows != p.rank) {
           // rows of a peer: wait (bounded) until the copy CTAs have landed this 128-row tile locally
           if (!*abort_flag && !wait_flag_ge_gpu(p.ag_ready + m_t, ag_epoch, p.status)) *abort_flag = 1;
@@ -454,9 +503,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      for (int work = worker; work < total_work; work += nworkers) {
-        int m_t, n_t, kb0, kb1;
-        decode_work(p, work, m_t, n_t, kb0, kb1);
+      WorkIter it(p, worker, nworkers);
+      int m_t, n_t, kb0, kb1;
+      while (it.next(p, m_t, n_t, kb0, kb1)) {
         mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_EMPTY);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -495,9 +544,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint32_t acc_phase = 0;
     uint32_t epi_cnt = 0;  // 64-column groups this warp has staged so far (selects the staging buffer)
     const int flags = p.flags;
-    for (int work = worker; work < total_work; work += nworkers) {
-      int m_t, n_t, kb0, kb1;
-      decode_work(p, work, m_t, n_t, kb0, kb1);
+    WorkIter it(p, worker, nworkers);
+    int m_t, n_t, kb0, kb1;
+    while (it.next(p, m_t, n_t, kb0, kb1)) {
       mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
       int row = m_t * BM + q * 32 + lane;
@@ -695,10 +744,10 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const OutMa
     TB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::ALLOC));
     configured = true;
   }
-  int total = p.tiles_m * p.tiles_n * p.split_k;
+  long total = (long)p.tiles_m * p.tiles_n * (p.stream_k ? p.kb_total : p.split_k);
   int workers = sm_count() - p.ag_ctas;  // copy CTAs and GEMM CTAs must all be resident at once
   if (workers < 1) TB_FAIL(TB_E_ARG, "gemm: too many copy CTAs");
-  int grid = (total < workers ? total : workers) + p.ag_ctas;
+  int grid = (int)(total < workers ? total : workers) + p.ag_ctas;
   kern<<<grid, GEMM_THREADS, L::ALLOC, stream>>>(ma, mb, om, p);
   TB_CUDA_CHECK(cudaGetLastError());
   return TB_LAUNCH_OK;
@@ -804,8 +853,12 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
   if ((flags & EPI_STORE_PREACT) && !preact) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: EPI_STORE_PREACT without buffer");
   if ((flags & EPI_MUL_DGELU) && !aux) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: EPI_MUL_DGELU without aux");
   if ((flags & EPI_ATOMIC) && !(flags & EPI_OUT_F32)) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: EPI_ATOMIC needs fp32 output");
+  // split_k == -1: stream-K (every CTA gets the same number of K-blocks; partial tiles meet through fp32 atomics)
+  const bool stream_k = split_k == -1;
+  if (stream_k && (!(flags & EPI_ATOMIC) || tp.kind != 0)) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: stream-K needs EPI_ATOMIC and no fused collective");
   if (split_k < 1) split_k = 1;
   if (split_k > 1 && !(flags & EPI_ATOMIC)) TB_FAIL(TB_E_ARG, "tb_gemm_bf16: split_k > 1 needs EPI_ATOMIC");
+  if (bn == 0 && stream_k) bn = N > 128 ? 256 : 128;
   if (bn == 0) {
     // 256-wide tiles halve the smem traffic per FLOP; fall back to 128 when that
     // leaves SMs idle.
@@ -830,6 +883,7 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
   p.kb_per_split = (p.kb_total + split_k - 1) / split_k;
   split_k = (p.kb_total + p.kb_per_split - 1) / p.kb_per_split;  // no empty split
   p.split_k = split_k;
+  p.stream_k = stream_k ? 1 : 0;
   p.status = status;
   p.rank = tp.rank;
   p.world = tp.world;

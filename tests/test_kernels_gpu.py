@@ -64,6 +64,26 @@ def test_gemm_splitk_atomic_wgrad():
     assert _rel(g, 2 * dy.float().t() @ x.float()) < 1e-4
 
 
+@pytest.mark.parametrize("shape", [(512, 384, 4096), (4096, 1024, 8192), (1024, 1024, 8192), (200, 72, 1000), (50304, 1024, 2048)])
+@pytest.mark.parametrize("majors", [(1, 1), (0, 0)])
+def test_gemm_stream_k_matches_fp32(shape, majors):
+    """split_k=-1: equal K-block ranges per CTA, pieces of a tile meet through fp32 atomics (and a bias enters once)."""
+    from torsh_b200.ops.gemm import gemm
+    torch.manual_seed(7)
+    M, N, K = shape
+    am, bm = majors
+    a = torch.randn((K, M) if am else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((K, N) if bm else (N, K), device=DEV, dtype=torch.bfloat16)
+    ref = (a.float().t() if am else a.float()) @ (b.float() if bm else b.float().t())
+    g = torch.ones(M, N, device=DEV, dtype=torch.float32)
+    gemm(a, b, a_major=am, b_major=bm, out=g, atomic=True, split_k=-1)
+    assert _rel(g, ref + 1.0) < 1e-4
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    g.zero_()
+    gemm(a, b, a_major=am, b_major=bm, out=g, atomic=True, split_k=-1, bias=bias)
+    assert _rel(g, ref + bias.float()) < 1e-4
+
+
 # ------------------------------------------------------------------ norms
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("H", [256, 1024, 4096])
