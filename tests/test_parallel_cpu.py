@@ -336,3 +336,51 @@ def test_llama_tensor_parallel_heads_match_single_process_model():
     for p in procs:
         p.join(30)
     assert sorted(res) == [(0, True), (1, True)]
+
+
+def _coll_variants_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torsh_b200.parallel import collectives as C
+        ok = True
+        base = torch.arange(10, dtype=torch.float32)
+        total = sum(base * (r + 1) for r in range(world))
+        t = base * (rank + 1)
+        ok &= torch.allclose(C.hierarchical_all_reduce(t.clone(), 2), total)
+        ok &= torch.allclose(C.hierarchical_all_reduce(t.clone(), 2, C.ReduceOp.MEAN), total / world)
+        ok &= torch.allclose(C.ring_all_reduce(t.clone()), total)
+        ok &= torch.allclose(C.pipelined_all_reduce(t.clone(), chunk_bytes=12), total)
+        ts = [t.clone() * k for k in (1, 2, 3)]
+        C.double_buffered_all_reduce(ts)
+        ok &= all(torch.allclose(x, total * k) for x, k in zip(ts, (1, 2, 3)))
+        for src in (0, 3):
+            b = torch.full((5,), float(rank))
+            C.tree_broadcast(b, src)
+            ok &= bool((b == src).all())
+        gm = C.GroupManager.for_group()
+        std = gm.create_standard_groups(2)
+        ok &= std["nodes"] == 2 and std["node"] == rank // 2 and gm.groups["leaders/2"].ranks == [0, 2]
+        ok &= gm.groups["node1/2"].local_rank(3) == 1 and gm.groups["node1/2"].global_rank(0) == 2
+        batch = C.NcclBatch()
+        x, y = t.clone(), torch.full((3,), float(rank))
+        got = torch.empty(4)
+        batch.all_reduce(x).broadcast(y, 1).send(torch.full((4,), float(rank)), (rank + 1) % world).recv(got, (rank - 1) % world)
+        ok &= len(batch) == 4 and batch.execute() == 4
+        ok &= torch.allclose(x, total) and bool((y == 1).all()) and bool((got == (rank - 1) % world).all())
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_collective_variants_four_gloo_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_coll_variants_worker, args=(r, 4, port, q)) for r in range(4)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(30)
+    assert sorted(res) == [(r, True) for r in range(4)]

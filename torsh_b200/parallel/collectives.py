@@ -195,6 +195,211 @@ def ring_all_reduce_host(buffers: list[torch.Tensor]) -> None:
             flat[(r + 1) % n][bounds[c][0]:bounds[c][1]] = v
 
 
+def ring_all_reduce(t: torch.Tensor, op: ReduceOp = ReduceOp.SUM, group=None) -> torch.Tensor:
+    """Bandwidth-optimal ring (``collectives.rs``: ``ring_all_reduce``): a reduce-scatter followed by an all-gather.
+    On one NVSwitch box NCCL / the fused kernels pick the algorithm; the explicit form exists for API parity."""
+    g = _g(group)
+    w = dist.get_world_size(g)
+    if w == 1:
+        return t
+    flat = t.reshape(-1)
+    pad = (-flat.numel()) % w
+    buf = torch.cat([flat, flat.new_zeros(pad)]) if pad else flat.clone()
+    shard = reduce_scatter(buf, op, g)
+    out = all_gather_into_tensor(shard, g)
+    flat.copy_(out[:flat.numel()])
+    return t
+
+
+def hierarchical_all_reduce(t: torch.Tensor, ranks_per_node: int, op: ReduceOp = ReduceOp.SUM, group=None,
+                            _groups: dict | None = None) -> torch.Tensor:
+    """Two-level all-reduce (``collectives.rs``: ``hierarchical_all_reduce(ranks_per_node)``): reduce inside each node,
+    all-reduce among the node leaders, broadcast inside each node. ``GroupManager.create_standard_groups`` builds the
+    sub-groups once; they are cached per (group, ranks_per_node)."""
+    g = _g(group)
+    w, r = dist.get_world_size(g), dist.get_rank(g)
+    if ranks_per_node <= 1 or ranks_per_node >= w or w % ranks_per_node:
+        return all_reduce(t, op, g)
+    gm = GroupManager.for_group(g)
+    std = gm.create_standard_groups(ranks_per_node)
+    local, leaders = std["local"], std["leaders"]
+    leader_rank = (r // ranks_per_node) * ranks_per_node
+    mean = op is ReduceOp.MEAN
+    top = ReduceOp.SUM if mean else op
+    dist.reduce(t, dst=dist.get_global_rank(g, leader_rank), op=top.to_torch(), group=local)
+    if r == leader_rank:
+        dist.all_reduce(t, op=top.to_torch(), group=leaders)
+    dist.broadcast(t, src=dist.get_global_rank(g, leader_rank), group=local)
+    if mean:
+        t.div_(w)
+    return t
+
+
+def tree_broadcast(t: torch.Tensor, src: int = 0, group=None) -> torch.Tensor:
+    """Binomial-tree broadcast with point-to-point messages (``collectives.rs``: ``tree_broadcast``): log2(world)
+    rounds; in round k the ranks that already hold the data send to the rank ``2^k`` places further (relative to
+    ``src``)."""
+    g = _g(group)
+    w, r = dist.get_world_size(g), dist.get_rank(g)
+    rel = (r - src) % w
+    k = 1
+    while k < w:
+        if rel < k and rel + k < w:
+            dist.send(t, dist.get_global_rank(g, (rel + k + src) % w), group=g)
+        elif k <= rel < 2 * k:
+            dist.recv(t, dist.get_global_rank(g, (rel - k + src) % w), group=g)
+        k *= 2
+    return t
+
+
+def pipelined_all_reduce(t: torch.Tensor, chunk_bytes: int = 4 << 20, op: ReduceOp = ReduceOp.SUM, group=None) -> torch.Tensor:
+    """All-reduce in chunks issued asynchronously, so chunk i+1 is on the wire while chunk i completes
+    (``collectives.rs``: ``pipelined_all_reduce``)."""
+    g = _g(group)
+    flat = t.reshape(-1)
+    per = max(1, chunk_bytes // t.element_size())
+    works = [dist.all_reduce(flat[i:i + per], op=op.to_torch(), group=g, async_op=True) for i in range(0, flat.numel(), per)]
+    for wk in works:
+        wk.wait()
+    if op is ReduceOp.MEAN:
+        flat.div_(dist.get_world_size(g))
+    return t
+
+
+def double_buffered_all_reduce(tensors: list[torch.Tensor], op: ReduceOp = ReduceOp.SUM, group=None) -> list[torch.Tensor]:
+    """Two staging buffers alternate: while buffer A is being reduced, the next tensor is packed into buffer B and the
+    previous result is unpacked (``collectives.rs``: ``double_buffered_all_reduce``)."""
+    g = _g(group)
+    if not tensors:
+        return tensors
+    cap = max(x.numel() for x in tensors)
+    bufs = [tensors[0].new_empty(cap) for _ in range(2)]
+    pending = None                       # (work, buffer index, tensor)
+    for i, x in enumerate(tensors):
+        b = bufs[i % 2][:x.numel()]
+        b.copy_(x.reshape(-1))
+        wk = dist.all_reduce(b, op=op.to_torch(), group=g, async_op=True)
+        if pending is not None:
+            pw, pb, px = pending
+            pw.wait()
+            px.copy_(pb.view_as(px))
+        pending = (wk, b, x)
+    pw, pb, px = pending
+    pw.wait()
+    px.copy_(pb.view_as(px))
+    if op is ReduceOp.MEAN:
+        for x in tensors:
+            x.div_(dist.get_world_size(g))
+    return tensors
+
+
+class CommunicationGroup:
+    """Global ↔ local rank maps of one sub-group (``collectives.rs:16-229``)."""
+
+    def __init__(self, name: str, ranks: list[int], pg=None):
+        self.name, self.ranks, self.pg = name, list(ranks), pg
+        self._local = {g: i for i, g in enumerate(self.ranks)}
+
+    def local_rank(self, global_rank: int) -> int | None:
+        return self._local.get(global_rank)
+
+    def global_rank(self, local_rank: int) -> int:
+        return self.ranks[local_rank]
+
+    def contains(self, global_rank: int) -> bool:
+        return global_rank in self._local
+
+    def size(self) -> int:
+        return len(self.ranks)
+
+
+class GroupManager:
+    """Creates and caches sub-groups of a process group (``GroupManager::create_standard_groups``): per node a
+    ``local`` group, one ``leaders`` group of the first rank of every node, and ``world``. ``dist.new_group`` is
+    collective, so every rank creates every group in the same order."""
+
+    _by_group: dict = {}
+
+    def __init__(self, group=None):
+        self.group = _g(group)
+        self.groups: dict[str, CommunicationGroup] = {}
+        self._std: dict[int, dict] = {}
+
+    @classmethod
+    def for_group(cls, group=None) -> "GroupManager":
+        g = _g(group)
+        key = id(g)
+        if key not in cls._by_group:
+            cls._by_group[key] = cls(g)
+        return cls._by_group[key]
+
+    def create_group(self, name: str, ranks: list[int]) -> CommunicationGroup:
+        if name in self.groups:
+            return self.groups[name]
+        pg = dist.new_group([dist.get_global_rank(self.group, r) for r in ranks])
+        cg = CommunicationGroup(name, ranks, pg)
+        self.groups[name] = cg
+        return cg
+
+    def create_standard_groups(self, ranks_per_node: int) -> dict:
+        if ranks_per_node in self._std:
+            return self._std[ranks_per_node]
+        w, r = dist.get_world_size(self.group), dist.get_rank(self.group)
+        nodes = w // ranks_per_node
+        local = None
+        for n in range(nodes):
+            cg = self.create_group(f"node{n}/{ranks_per_node}", list(range(n * ranks_per_node, (n + 1) * ranks_per_node)))
+            if cg.contains(r):
+                local = cg.pg
+        leaders = self.create_group(f"leaders/{ranks_per_node}", [n * ranks_per_node for n in range(nodes)])
+        self._std[ranks_per_node] = {"local": local, "leaders": leaders.pg, "world": self.group,
+                                     "node": r // ranks_per_node, "nodes": nodes}
+        return self._std[ranks_per_node]
+
+
+class CollectiveBatch:
+    """Queues collectives and issues them together (``crates/torsh-distributed/src/nccl_ops.rs:519-670``: ``NcclBatch``):
+    point-to-point ops go out as one ``batch_isend_irecv`` (one NCCL group call), the others asynchronously; ``execute``
+    waits for all of them."""
+
+    def __init__(self, group=None):
+        self.group = _g(group)
+        self._p2p, self._coll = [], []
+
+    def all_reduce(self, t, op: ReduceOp = ReduceOp.SUM):
+        self._coll.append(lambda: dist.all_reduce(t, op=op.to_torch(), group=self.group, async_op=True)); return self
+
+    def broadcast(self, t, src: int = 0):
+        self._coll.append(lambda: dist.broadcast(t, src=dist.get_global_rank(self.group, src), group=self.group, async_op=True)); return self
+
+    def all_gather(self, out: torch.Tensor, t: torch.Tensor):
+        self._coll.append(lambda: dist.all_gather_into_tensor(out, t, group=self.group, async_op=True)
+                          if t.is_cuda else dist.all_gather(list(out.chunk(dist.get_world_size(self.group))), t, group=self.group, async_op=True))
+        return self
+
+    def send(self, t, dst: int):
+        self._p2p.append(dist.P2POp(dist.isend, t, dist.get_global_rank(self.group, dst), self.group)); return self
+
+    def recv(self, t, src: int):
+        self._p2p.append(dist.P2POp(dist.irecv, t, dist.get_global_rank(self.group, src), self.group)); return self
+
+    def __len__(self):
+        return len(self._p2p) + len(self._coll)
+
+    def execute(self) -> int:
+        works = [f() for f in self._coll]
+        if self._p2p:
+            works += dist.batch_isend_irecv(self._p2p)
+        for wk in works:
+            wk.wait()
+        n = len(works)
+        self._p2p, self._coll = [], []
+        return n
+
+
+NcclBatch = CollectiveBatch
+
+
 # ------------------------------------------------------------------------------------ fused kernels
 P, I, L, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_int64, ctypes.c_float
 
