@@ -194,3 +194,176 @@ def test_streaming_tensor_file_and_function_registry(tmp_path):
     assert lines == ["step 10", "step;bwd 50", "step;fwd 20", "step;fwd;gemm 20"]
     diff = fn.differential(lines, ["step 10", "step;bwd 80", "step;fwd 20"])
     assert diff[0] == ("step;bwd", 50, 80)
+
+
+def _fake_redis(server_sock, stop):
+    """A few Redis commands over RESP2, enough for the store client: GET SET(PX) DEL EXISTS INCRBY KEYS EVAL(cas)."""
+    import time as _t
+    data, expiry = {}, {}
+
+    def alive(k):
+        if k in expiry and _t.monotonic() >= expiry[k]:
+            data.pop(k, None); expiry.pop(k, None)
+        return k in data
+
+    def bulk(v):
+        return b"$-1\r\n" if v is None else b"$%d\r\n" % len(v) + v + b"\r\n"
+
+    server_sock.settimeout(0.2)
+    conns = []
+    while not stop.is_set():
+        try:
+            c, _ = server_sock.accept()
+        except OSError:
+            continue
+        conns.append(c)
+        f = c.makefile("rb")
+        while not stop.is_set():
+            line = f.readline()
+            if not line:
+                break
+            n = int(line[1:-2])
+            args = []
+            for _ in range(n):
+                ln = int(f.readline()[1:-2])
+                args.append(f.read(ln + 2)[:-2])
+            cmd = args[0].upper()
+            if cmd == b"SET":
+                data[args[1]] = args[2]
+                expiry.pop(args[1], None)
+                if len(args) >= 5 and args[3].upper() == b"PX":
+                    expiry[args[1]] = _t.monotonic() + int(args[4]) / 1000
+                c.sendall(b"+OK\r\n")
+            elif cmd == b"GET":
+                c.sendall(bulk(data[args[1]] if alive(args[1]) else None))
+            elif cmd == b"EXISTS":
+                c.sendall(b":%d\r\n" % int(alive(args[1])))
+            elif cmd == b"DEL":
+                c.sendall(b":%d\r\n" % int(data.pop(args[1], None) is not None))
+            elif cmd == b"INCRBY":
+                v = int(data.get(args[1], b"0")) + int(args[2])
+                data[args[1]] = str(v).encode()
+                c.sendall(b":%d\r\n" % v)
+            elif cmd == b"KEYS":
+                ks = [k for k in list(data) if alive(k) and k.startswith(args[1][:-1])]
+                c.sendall(b"*%d\r\n" % len(ks) + b"".join(bulk(k) for k in ks))
+            elif cmd == b"EVAL":
+                key, has, exp, val = args[3], args[4], args[5], args[6]
+                cur = data[key] if alive(key) else None
+                ok = (has == b"0" and cur is None) or (has == b"1" and cur == exp)
+                if ok:
+                    data[key] = val
+                c.sendall(b":%d\r\n" % int(ok))
+            else:
+                c.sendall(b"-ERR unknown command\r\n")
+    for c in conns:
+        c.close()
+
+
+def test_redis_store_speaks_resp_to_a_fake_server():
+    import socket, threading, time
+    from torsh_b200.parallel.store import create_store
+    from torsh_b200.core.error import TorshDistributedError
+    srv = socket.socket(); srv.bind(("127.0.0.1", 0)); srv.listen(4)
+    stop = threading.Event()
+    th = threading.Thread(target=_fake_redis, args=(srv, stop), daemon=True); th.start()
+    st = create_store("redis", host="127.0.0.1", port=srv.getsockname()[1], prefix="t/")
+    try:
+        st.set("a", b"\x00bin\r\nary")
+        assert st.get("a") == b"\x00bin\r\nary" and st.contains("a") and st.get("nope") is None
+        assert st.add("n", 2) == 2 and st.add("n", 3) == 5
+        assert st.compare_and_swap("c", None, b"1") and not st.compare_and_swap("c", None, b"2")
+        assert st.compare_and_swap("c", b"1", b"3") and st.get("c") == b"3"
+        assert st.num_keys() == 3
+        st.set_with_expiry("ttl", b"x", 0.05)
+        assert st.contains("ttl"); time.sleep(0.1); assert not st.contains("ttl")
+        threading.Timer(0.05, lambda: st2.set("late", b"1")).start()
+        st2 = st
+        st.wait(["late"], timeout=2.0)
+        with pytest.raises(TorshDistributedError):
+            st.wait(["never"], timeout=0.05)
+        assert st.delete("a") and not st.contains("a")
+    finally:
+        st.close(); stop.set(); th.join(2); srv.close()
+
+
+def test_connection_pool_reuses_sockets_and_retries():
+    import socket, threading
+    from torsh_b200.parallel.connection import ConnectionPool, RetryPolicy, retry
+    from torsh_b200.core.error import TorshDistributedError
+    srv = socket.socket(); srv.bind(("127.0.0.1", 0)); srv.listen(8)
+    port = srv.getsockname()[1]
+    stop = threading.Event()
+
+    def echo():
+        srv.settimeout(0.2)
+        def serve(c):
+            while True:
+                d = c.recv(4)
+                if not d:
+                    break
+                c.sendall(d[::-1])
+            c.close()
+        while not stop.is_set():
+            try:
+                c, _ = srv.accept()
+            except OSError:
+                continue
+            threading.Thread(target=serve, args=(c,), daemon=True).start()
+    th = threading.Thread(target=echo, daemon=True); th.start()
+    pool = ConnectionPool(max_per_peer=2, policy=RetryPolicy(max_retries=2, initial_delay_s=0.01, timeout_s=2.0))
+    try:
+        assert pool.request("127.0.0.1", port, b"abcd", 4) == b"dcba"
+        assert pool.request("127.0.0.1", port, b"wxyz", 4) == b"zyxw"
+        s = pool.stats[("127.0.0.1", port)]
+        assert (s.connects, s.reuses, s.bytes_sent, s.bytes_received) == (1, 1, 8, 8) and pool.idle_count("127.0.0.1", port) == 1
+        with pytest.raises(RuntimeError):
+            with pool.connection("127.0.0.1", port):
+                raise RuntimeError("boom")
+        assert pool.idle_count("127.0.0.1", port) == 0          # the socket of a failed block is not reused
+        calls, slept = [], []
+        def flaky():
+            calls.append(1)
+            if len(calls) < 3:
+                raise OSError("down")
+            return "up"
+        assert retry(flaky, RetryPolicy(max_retries=3, initial_delay_s=0.01), sleep=slept.append) == "up" and slept == [0.01, 0.02]
+        with pytest.raises(TorshDistributedError):
+            retry(lambda: (_ for _ in ()).throw(OSError("x")), RetryPolicy(max_retries=1, initial_delay_s=0.0), sleep=lambda d: None)
+    finally:
+        pool.close(); stop.set(); th.join(2); srv.close()
+
+
+def test_more_compressors_and_nccl_scheduler():
+    import torch
+    from torsh_b200.parallel.compression import Bimodal, CountSketch, EF21, LayerwiseAdaptive, NaturalCompression, TopK
+    from torsh_b200.parallel.comm_scheduler import CollectiveAlgorithm, NcclScheduler, Priority
+    torch.manual_seed(0)
+    g = torch.zeros(2000)
+    g[torch.randperm(2000)[:20]] = torch.randn(20) * 10
+    cs = CountSketch(5, 4096)
+    a, b = cs.compress(g)[0], cs.compress(2 * g)[0]
+    assert torch.allclose(cs.decompress((a + b,), g.shape), 3 * g, atol=1e-4)          # sketches add up across ranks
+    x = torch.randn(100000)
+    nc = NaturalCompression()
+    r = nc.decompress(nc.compress(x), x.shape)
+    assert abs(float((r - x).mean())) < 0.01 and float((r / x).min()) >= 0.5 and float((r / x).max()) <= 2.0
+    bm = Bimodal()
+    assert float(torch.nn.functional.cosine_similarity(bm.decompress(bm.compress(x), x.shape), x, dim=0)) > 0.9
+    la = LayerwiseAdaptive()
+    assert [la.choose(t)[0] for t in (torch.randn(100), torch.randn(2048, 1024), torch.randn(100000))] == ["none", "powersgd", "topk"]
+    small = torch.randn(100)
+    assert torch.equal(la.decompress(la.compress(small), small.shape), small)
+    ef, gg = EF21(TopK(0.1)), torch.randn(1000)
+    for _ in range(40):
+        _, h = ef.compress("w", gg)
+    assert float((h - gg).norm() / gg.norm()) < 1e-3
+    s = NcclScheduler(num_streams=2, fusion_bytes=1000, world=8, has_multicast=True)
+    for i in range(5):
+        s.enqueue(f"g{i}", 300, lambda i=i: i)
+    s.enqueue("big", 1 << 22, lambda: "big", priority=Priority.CRITICAL)
+    assert s.flush() == ["big", 0, 1, 2, 3, 4]
+    assert s.log[0] == (0, ["big"], CollectiveAlgorithm.NVLS) and s.log[1][1] == ["g0", "g1", "g2"] and s.log[1][0] == 1
+    assert s.stats["fused_groups"] == 2 and s.stats["fused_ops"] == 5
+    assert NcclScheduler(world=16, ranks_per_node=8).choose_algorithm(1 << 20) is CollectiveAlgorithm.HIERARCHICAL
+    assert NcclScheduler(world=2).choose_algorithm(1 << 20) is CollectiveAlgorithm.TWO_SHOT_PEER

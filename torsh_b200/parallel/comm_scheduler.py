@@ -105,3 +105,95 @@ class CommunicationScheduler:
             self._stop = True
             self._cv.notify()
         self._thread.join(5)
+
+
+class CollectiveAlgorithm(enum.Enum):
+    """``crates/torsh-distributed/src/nccl_optimization.rs``: ring / tree / hierarchical selection. On one NVSwitch box
+    the device-side choice is between the one-shot kernel (latency-bound sizes), the two-shot kernel over peer memory,
+    and the in-switch (NVLS ``multimem``) reduction."""
+    ONE_SHOT = "one_shot"
+    TWO_SHOT_PEER = "two_shot_peer"
+    NVLS = "nvls"
+    RING = "ring"
+    TREE = "tree"
+    HIERARCHICAL = "hierarchical"
+
+
+@dataclass
+class _PendingOp:
+    name: str
+    nbytes: int
+    priority: Priority
+    fn: Callable
+    fusable: bool = True
+
+
+class NcclScheduler:
+    """Multi-stream collective scheduler with op fusion (``nccl_optimization.rs:22-1170``: ``NcclScheduler``,
+    ``FusedNcclOp``): ops are queued, small fusable ops of equal priority are merged until ``fusion_bytes``, every
+    (fused) op goes to the least-loaded of ``num_streams`` streams, and the algorithm is chosen from the message size
+    and the topology. Streams are CUDA streams when a GPU is present, otherwise plain counters (the logic is the same
+    and is what the CPU tests drive)."""
+
+    def __init__(self, num_streams: int = 2, fusion_bytes: int = 4 << 20, world: int = 1, ranks_per_node: int | None = None,
+                 has_multicast: bool = False, streams=None):
+        self.num_streams, self.fusion_bytes, self.world = num_streams, fusion_bytes, world
+        self.ranks_per_node = ranks_per_node or world
+        self.has_multicast = has_multicast
+        self.streams = streams
+        self.load = [0] * num_streams                # bytes queued per stream
+        self.queue: list[_PendingOp] = []
+        self.stats = {"ops": 0, "fused_groups": 0, "fused_ops": 0, "bytes": 0, "per_stream": [0] * num_streams}
+        self.log: list[tuple[int, list[str], CollectiveAlgorithm]] = []
+
+    def choose_algorithm(self, nbytes: int) -> CollectiveAlgorithm:
+        if self.world > self.ranks_per_node:
+            return CollectiveAlgorithm.HIERARCHICAL if nbytes >= (256 << 10) else CollectiveAlgorithm.TREE
+        if nbytes <= (128 << 10):
+            return CollectiveAlgorithm.ONE_SHOT
+        if self.has_multicast and self.world > 2:
+            return CollectiveAlgorithm.NVLS
+        return CollectiveAlgorithm.TWO_SHOT_PEER
+
+    def enqueue(self, name: str, nbytes: int, fn: Callable, priority: Priority = Priority.NORMAL, fusable: bool = True):
+        self.queue.append(_PendingOp(name, nbytes, priority, fn, fusable))
+        self.stats["ops"] += 1
+
+    def _groups(self) -> list[list[_PendingOp]]:
+        ops = sorted(self.queue, key=lambda o: int(o.priority))       # stable: submission order inside a priority
+        groups: list[list[_PendingOp]] = []
+        for op in ops:
+            last = groups[-1] if groups else None
+            if (last is not None and op.fusable and last[0].fusable and last[0].priority == op.priority
+                    and sum(o.nbytes for o in last) + op.nbytes <= self.fusion_bytes):
+                last.append(op)
+            else:
+                groups.append([op])
+        return groups
+
+    def flush(self) -> list:
+        """Issue everything queued; returns the results of the ops in issue order."""
+        results = []
+        for grp in self._groups():
+            nbytes = sum(o.nbytes for o in grp)
+            sid = min(range(self.num_streams), key=lambda i: self.load[i])
+            self.load[sid] += nbytes
+            alg = self.choose_algorithm(nbytes)
+            self.log.append((sid, [o.name for o in grp], alg))
+            if len(grp) > 1:
+                self.stats["fused_groups"] += 1
+                self.stats["fused_ops"] += len(grp)
+            self.stats["bytes"] += nbytes
+            self.stats["per_stream"][sid] += 1
+            if self.streams is not None:
+                import torch
+                with torch.cuda.stream(self.streams[sid]):
+                    results.extend(o.fn() for o in grp)
+            else:
+                results.extend(o.fn() for o in grp)
+        self.queue.clear()
+        return results
+
+    def complete(self, stream_id: int, nbytes: int):
+        """Bookkeeping when a stream has drained ``nbytes`` (called from an event callback or after a synchronise)."""
+        self.load[stream_id] = max(0, self.load[stream_id] - nbytes)

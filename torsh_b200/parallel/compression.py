@@ -220,3 +220,122 @@ class ErrorFeedback:
         approx = self.c.decompress(payload, acc.shape, acc.dtype, acc.device)
         self.residual[name] = acc - approx
         return payload, approx
+
+
+class CountSketch(Compressor):
+    """Sketching (``gradient_compression.rs``: ``Sketching``): ``rows`` independent count sketches of ``cols`` buckets
+    (sign hash × bucket hash); an element is recovered as the median over rows of ``sign · bucket``. Sketches are
+    linear, so the sketches of all ranks can be summed before decoding."""
+
+    def __init__(self, rows: int = 5, cols: int = 4096, seed: int = 0):
+        self.rows, self.cols, self.seed, self._tables = rows, cols, seed, {}
+
+    def _hashes(self, n: int, device):
+        key = (n, str(device))
+        if key not in self._tables:
+            gen = torch.Generator().manual_seed(self.seed)
+            bucket = torch.randint(0, self.cols, (self.rows, n), generator=gen)
+            sign = torch.randint(0, 2, (self.rows, n), generator=gen) * 2 - 1
+            self._tables[key] = (bucket.to(device), sign.to(device))
+        return self._tables[key]
+
+    def compress(self, g):
+        flat = g.reshape(-1).float()
+        bucket, sign = self._hashes(flat.numel(), flat.device)
+        sk = torch.zeros(self.rows, self.cols, device=flat.device)
+        sk.scatter_add_(1, bucket, sign * flat[None])
+        return (sk,)
+
+    def decompress(self, payload, shape, dtype=torch.float32, device=None):
+        sk = payload[0]
+        n = math.prod(shape)
+        bucket, sign = self._hashes(n, sk.device)
+        est = sk.gather(1, bucket) * sign
+        return est.median(0).values.to(dtype).view(shape)
+
+
+class NaturalCompression(Compressor):
+    """Natural compression: every value is rounded, without bias, to one of the two neighbouring powers of two, so only
+    sign and exponent (9 bits) travel."""
+
+    def __init__(self, seed: int = 0):
+        self.gen = torch.Generator().manual_seed(seed)
+
+    def compress(self, g):
+        a = g.abs().float().clamp(min=1e-38)
+        e = torch.floor(torch.log2(a))
+        lo = torch.exp2(e)
+        p_up = (a - lo) / lo                                   # in [0, 1): probability of rounding up to 2^(e+1)
+        up = torch.rand(a.shape, generator=self.gen).to(a.device) < p_up
+        exp = (e + up.float()).clamp(-126, 127).to(torch.int8)
+        sign = torch.where(g == 0, torch.zeros_like(exp), torch.sign(g).to(torch.int8))
+        return exp, sign
+
+    def decompress(self, payload, shape, dtype=torch.float32, device=None):
+        exp, sign = payload
+        return (torch.exp2(exp.float()) * sign.float()).to(dtype).view(shape)
+
+
+class Bimodal(Compressor):
+    """Two-level quantisation (``Bimodal``): values are split at the mean magnitude into a "small" and a "large" mode and
+    each element is replaced by the mean magnitude of its mode, keeping its sign: 2 bits per element plus two scalars."""
+
+    def compress(self, g):
+        a = g.abs().float()
+        t = a.mean()
+        big = a > t
+        m_small = a[~big].mean() if (~big).any() else a.new_zeros(())
+        m_big = a[big].mean() if big.any() else a.new_zeros(())
+        code = (big.to(torch.uint8) << 1) | (g >= 0).to(torch.uint8)
+        return code, torch.stack([m_small, m_big])
+
+    def decompress(self, payload, shape, dtype=torch.float32, device=None):
+        code, modes = payload
+        mag = modes[(code >> 1).long()]
+        sign = (code & 1).float() * 2 - 1
+        return (mag * sign).to(dtype).view(shape)
+
+
+class LayerwiseAdaptive(Compressor):
+    """Chooses the compressor per tensor from its size and density (``LayerwiseAdaptive``): small tensors travel
+    uncompressed, matrices above ``lowrank_numel`` use PowerSGD, the rest Top-K with a ratio that grows with the
+    tensor's kurtosis-free sparsity estimate (share of elements below a tenth of the mean magnitude)."""
+
+    def __init__(self, small_numel: int = 4096, lowrank_numel: int = 1 << 20, base_ratio: float = 0.01, rank: int = 4):
+        self.small, self.lowrank, self.base, self.psgd = small_numel, lowrank_numel, base_ratio, PowerSGD(rank)
+
+    def choose(self, g: torch.Tensor):
+        if g.numel() <= self.small:
+            return "none", None
+        if g.dim() >= 2 and g.numel() >= self.lowrank:
+            return "powersgd", self.psgd
+        a = g.abs()
+        sparse_share = float((a < 0.1 * a.mean()).float().mean())
+        ratio = min(0.25, max(self.base, self.base * (1.0 + 4.0 * (1.0 - sparse_share))))
+        return "topk", TopK(ratio)
+
+    def compress(self, g):
+        kind, c = self.choose(g)
+        return (kind, g.clone()) if c is None else (kind, c.compress(g), c)
+
+    def decompress(self, payload, shape, dtype=torch.float32, device=None):
+        if payload[0] == "none":
+            return payload[1].to(dtype).view(shape)
+        return payload[2].decompress(payload[1], shape, dtype, device)
+
+
+class EF21:
+    """EF21 (``gradient_compression.rs``: ``EF21``): every rank keeps a state ``h``; it sends ``c = C(g - h)`` and sets
+    ``h += c``; the receivers track the same ``h``, so the estimate of the gradient is ``h`` itself."""
+
+    def __init__(self, compressor: Compressor):
+        self.c, self.h = compressor, {}
+
+    def compress(self, name: str, g: torch.Tensor):
+        h = self.h.get(name)
+        if h is None:
+            h = torch.zeros_like(g)
+        payload = self.c.compress(g - h)
+        h = h + self.c.decompress(payload, g.shape, g.dtype, g.device)
+        self.h[name] = h
+        return payload, h

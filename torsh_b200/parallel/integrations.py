@@ -102,3 +102,42 @@ def from_horovod(cfg) -> TrainingPlan:
         plan.notes.append("fp16 gradient compression maps to bf16 bucket all-reduce with fp32 accumulation")
     plan.grad_accum = int(c.get("backward_passes_per_step", 1))
     return plan
+
+
+def from_ray(cfg) -> TrainingPlan:
+    """Ray Train ``ScalingConfig`` / ``TorchConfig`` (``crates/torsh-distributed/src/ray_integration.rs``): workers map to
+    ranks, ``use_gpu`` and ``resources_per_worker`` to one process per GPU; elastic / fault-tolerance settings become notes
+    for ``parallel.fault_tolerance``."""
+    c = _load(cfg)
+    sc = c.get("scaling_config", c)
+    plan = TrainingPlan(strategy="ddp")
+    workers = int(sc.get("num_workers", 1))
+    plan.notes.append(f"world size {workers} (one process per GPU)")
+    if not sc.get("use_gpu", True):
+        plan.notes.append("CPU workers requested: gloo backend")
+    tc = c.get("torch_config", {})
+    if str(tc.get("backend", "nccl")).lower() != "nccl":
+        plan.notes.append(f"backend {tc.get('backend')} requested; NCCL / fused NVSwitch kernels are used on GPUs")
+    fc = c.get("failure_config", {})
+    if fc.get("max_failures"):
+        plan.notes.append(f"max_failures {fc['max_failures']}: use fault_tolerance.ElasticTrainingManager with checkpoint restarts")
+    strat = str(c.get("strategy", "ddp")).lower()
+    if strat in ("fsdp", "zero3", "deepspeed"):
+        plan.strategy, plan.sharding = "fsdp", "full_shard"
+    return plan
+
+
+def from_dask(cfg) -> TrainingPlan:
+    """Dask cluster description (``crates/torsh-distributed/src/dask_integration.rs``): ``n_workers`` ×
+    ``threads_per_worker`` with a GPU per worker (dask-cuda); data-parallel with the batch split over workers."""
+    c = _load(cfg)
+    plan = TrainingPlan(strategy="ddp")
+    plan.notes.append(f"world size {int(c.get('n_workers', 1))}")
+    if int(c.get("threads_per_worker", 1)) > 1:
+        plan.notes.append("threads_per_worker > 1: one training process per GPU is used; extra threads serve the data loader")
+    if c.get("memory_limit"):
+        plan.notes.append(f"host memory limit {c['memory_limit']} applies to the pinned staging pools")
+    chunk = c.get("chunk_size")
+    if chunk:
+        plan.micro_batches = max(1, int(c.get("batch_size", chunk)) // int(chunk))
+    return plan

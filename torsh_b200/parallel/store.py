@@ -297,12 +297,119 @@ class FileStore(Store):
             os.unlink(lock)
 
 
+class RedisStore(Store):
+    """Store on a Redis server, spoken over a plain socket in RESP2 (``crates/torsh-distributed/src/store/redis.rs:87-586``;
+    no client library is needed). Keys get a ``prefix``; ``compare_and_swap`` runs a small Lua script so that it is
+    atomic on the server; ``wait`` polls with back-off."""
+
+    _CAS = ("local cur = redis.call('GET', KEYS[1]); "
+            "if (ARGV[1] == '0' and cur == false) or (ARGV[1] == '1' and cur == ARGV[2]) then "
+            "redis.call('SET', KEYS[1], ARGV[3]); return 1 else return 0 end")
+
+    def __init__(self, host: str = "127.0.0.1", port: int = 6379, prefix: str = "torsh/", timeout: float = 30.0,
+                 password: str | None = None, db: int = 0):
+        import socket
+        self.prefix, self.timeout = prefix, timeout
+        self._lock = threading.Lock()
+        self._sock = socket.create_connection((host, port), timeout=timeout)
+        self._rf = self._sock.makefile("rb")
+        if password:
+            self._cmd("AUTH", password)
+        if db:
+            self._cmd("SELECT", str(db))
+
+    # ---- RESP2 ---------------------------------------------------------------------------------------
+    @staticmethod
+    def _enc(*parts) -> bytes:
+        out = [b"*%d\r\n" % len(parts)]
+        for p in parts:
+            b = p if isinstance(p, (bytes, bytearray)) else str(p).encode()
+            out.append(b"$%d\r\n" % len(b) + bytes(b) + b"\r\n")
+        return b"".join(out)
+
+    def _read(self):
+        line = self._rf.readline()
+        if not line:
+            raise TorshDistributedError.communication_error("redis: connection closed")
+        kind, rest = line[:1], line[1:-2]
+        if kind == b"+":
+            return rest
+        if kind == b"-":
+            raise TorshDistributedError.communication_error("redis: " + rest.decode(errors="replace"))
+        if kind == b":":
+            return int(rest)
+        if kind == b"$":
+            n = int(rest)
+            if n < 0:
+                return None
+            data = self._rf.read(n + 2)
+            return data[:-2]
+        if kind == b"*":
+            n = int(rest)
+            return None if n < 0 else [self._read() for _ in range(n)]
+        raise TorshDistributedError.communication_error(f"redis: bad reply type {kind!r}")
+
+    def _cmd(self, *parts):
+        with self._lock:
+            self._sock.sendall(self._enc(*parts))
+            return self._read()
+
+    def _k(self, key: str) -> str:
+        return self.prefix + key
+
+    # ---- Store ---------------------------------------------------------------------------------------
+    def set(self, key, value, ttl=None):
+        if ttl is None:
+            self._cmd("SET", self._k(key), value)
+        else:
+            self._cmd("SET", self._k(key), value, "PX", max(1, int(ttl * 1000)))
+
+    def get(self, key):
+        return self._cmd("GET", self._k(key))
+
+    def contains(self, key):
+        return self._cmd("EXISTS", self._k(key)) == 1
+
+    def delete(self, key):
+        return self._cmd("DEL", self._k(key)) == 1
+
+    def num_keys(self):
+        return len(self._cmd("KEYS", self.prefix + "*") or [])
+
+    def add(self, key, delta):
+        return int(self._cmd("INCRBY", self._k(key), int(delta)))
+
+    def compare_and_swap(self, key, expected, value):
+        return self._cmd("EVAL", self._CAS, 1, self._k(key), "0" if expected is None else "1",
+                         b"" if expected is None else expected, value) == 1
+
+    def wait(self, keys, timeout: float = 30.0):
+        deadline, delay = time.monotonic() + timeout, 0.001
+        keys = [keys] if isinstance(keys, str) else list(keys)
+        while True:
+            if all(self.contains(k) for k in keys):
+                return
+            if time.monotonic() >= deadline:
+                raise TorshDistributedError.operation_timeout(f"redis wait for {keys} timed out after {timeout}s")
+            time.sleep(delay)
+            delay = min(delay * 2, 0.05)
+
+    def close(self):
+        try:
+            self._rf.close()
+            self._sock.close()
+        except OSError:
+            pass
+
+
 def create_store(kind: str, **kw) -> Store:
-    """Factory (``crates/torsh-distributed/src/store/mod.rs:28``): ``tcp``, ``file``, ``memory``."""
+    """Factory (``crates/torsh-distributed/src/store/mod.rs:28``): ``tcp``, ``file``, ``memory``, ``redis``."""
+    if kind == "redis":
+        return RedisStore(**kw)
     if kind == "tcp":
         return TCPStore(**kw)
     if kind == "file":
         return FileStore(**kw)
     if kind == "memory":
         return MemoryStore()
-    raise TorshDistributedError.configuration_error(f"unknown store kind {kind!r} (redis is not built here)")
+    raise TorshDistributedError.configuration_error(f"unknown store kind {kind!r}")
