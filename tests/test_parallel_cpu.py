@@ -318,6 +318,21 @@ def _llama_tp_worker(rank, world, port, q):
                 ok &= torch.allclose(logits, ref(inp), atol=1e-5)
             else:
                 ok &= torch.allclose(m.lm_head.grad, ref.lm_head.grad, atol=1e-6)
+        # ParallelAttention: heads split over the ranks, token-sharded input and output
+        from torsh_b200.parallel.tensor_parallel import ParallelAttention
+        Hh, B, S = 4, 2, 8
+        torch.manual_seed(1)
+        wqkv, wo = torch.randn(3 * E, E) * 0.1, torch.randn(E, E) * 0.1
+        x = torch.randn(B * S, E)
+        qf, kf, vf = ((x @ wqkv[i * E:(i + 1) * E].t()).view(B, S, Hh, E // Hh).transpose(1, 2) for i in range(3))
+        ref_out = torch.nn.functional.scaled_dot_product_attention(qf, kf, vf, is_causal=True).transpose(1, 2).reshape(B * S, E) @ wo.t()
+        pa = ParallelAttention(E, Hh, tp=TPContext(dist.group.WORLD, TensorParallelConfig(tp_size=world, fused=False)))
+        with torch.no_grad():
+            pa.qkv.weight.copy_(torch.cat([sl(wqkv[:E], E), sl(wqkv[E:2 * E], E), sl(wqkv[2 * E:], E)]))
+            pa.out.weight.copy_(wo[:, rank * E // world:(rank + 1) * E // world])
+        rows = B * S // world
+        got = pa(x[rank * rows:(rank + 1) * rows], B, S)
+        ok &= torch.allclose(got, ref_out[rank * rows:(rank + 1) * rows], atol=1e-5)
         q.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()
@@ -384,3 +399,45 @@ def test_collective_variants_four_gloo_ranks():
     for p in procs:
         p.join(30)
     assert sorted(res) == [(r, True) for r in range(4)]
+
+
+def _cp_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torsh_b200.parallel.context_parallel import ring_attention, ulysses_attention
+        B, S, H, D = 2, 24, 4, 8
+        g = torch.Generator().manual_seed(3)
+        full = [torch.randn(B, S, H, D, generator=g, dtype=torch.float64).requires_grad_() for _ in range(3)]
+        dy = torch.randn(B, S, H, D, generator=g, dtype=torch.float64)
+        n = S // world
+        sl = slice(rank * n, (rank + 1) * n)
+        ok = True
+        for causal in (False, True):
+            qf, kf, vf = (t.transpose(1, 2) for t in full)
+            ref = torch.nn.functional.scaled_dot_product_attention(qf, kf, vf, is_causal=causal).transpose(1, 2)
+            gref = torch.autograd.grad(ref, full, dy)
+            for fn in (ulysses_attention, ring_attention):
+                loc = [t.detach()[:, sl].clone().requires_grad_() for t in full]
+                out = fn(*loc, causal=causal)
+                ok &= torch.allclose(out, ref[:, sl].to(out.dtype), atol=1e-5)
+                gl = torch.autograd.grad(out, loc, dy[:, sl].to(out.dtype))
+                for a, b in zip(gl, gref):
+                    ok &= torch.allclose(a, b[:, sl].to(a.dtype), atol=1e-5)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_context_parallel_attention_matches_full_attention(world):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_cp_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(30)
+    assert sorted(res) == [(r, True) for r in range(world)]

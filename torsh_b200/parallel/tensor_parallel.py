@@ -322,6 +322,32 @@ class ParallelEmbedding(Module):
         return out
 
 
+class ParallelAttention(Module):
+    """Self-attention with the heads split over the tensor-parallel group
+    (``crates/torsh-distributed/src/tensor_parallel.rs:95-137``: ``ParallelAttention``, ``AttentionHead`` strategy):
+    a column-parallel QKV projection laid out per rank as ``[q | k | v]`` of the local heads, attention over the local
+    heads, and a row-parallel output projection. With sequence parallelism the input and the output are this rank's
+    ``B*S/tp`` token rows; the all-gather sits in front of the QKV GEMM and the reduce-scatter behind the projection."""
+
+    def __init__(self, embed_dim: int, num_heads: int, tp: TPContext | None = None, group=None, causal: bool = True,
+                 bias: bool = False, init_std: float = 0.02):
+        super().__init__()
+        self.qkv = ColumnParallelLinear(embed_dim, 3 * embed_dim, bias=bias, tp=tp, group=group, init_std=init_std)
+        self.out = RowParallelLinear(embed_dim, embed_dim, bias=bias, tp=tp, group=group, init_std=init_std)
+        world = self.qkv.world
+        if num_heads % world:
+            raise ValueError(f"heads ({num_heads}) must divide by the tensor-parallel size ({world})")
+        self.local_heads, self.head_dim, self.causal = num_heads // world, embed_dim // num_heads, causal
+
+    def forward(self, x_shard, B: int, S: int, residual=None):
+        from ..ops import attention as attn_ops
+        H, D = self.local_heads, self.head_dim
+        qkv = self.qkv(x_shard)                                            # [B*S, 3*H*D]: all tokens, local heads
+        q, k, v = (qkv[:, i * H * D:(i + 1) * H * D].reshape(B, S, H, D) for i in range(3))
+        ctx = attn_ops.flash_attention(q, k, v, causal=self.causal).reshape(B * S, H * D)
+        return self.out(ctx, residual=residual)
+
+
 def split_tensor_for_tp(t: torch.Tensor, dim: int, rank: int, world: int) -> torch.Tensor:
     """``crates/torsh-distributed/src/tensor_parallel.rs:801-901``."""
     return t.chunk(world, dim)[rank].contiguous()
