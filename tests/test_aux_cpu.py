@@ -367,3 +367,21 @@ def test_more_compressors_and_nccl_scheduler():
     assert s.stats["fused_groups"] == 2 and s.stats["fused_ops"] == 5
     assert NcclScheduler(world=16, ranks_per_node=8).choose_algorithm(1 << 20) is CollectiveAlgorithm.HIERARCHICAL
     assert NcclScheduler(world=2).choose_algorithm(1 << 20) is CollectiveAlgorithm.TWO_SHOT_PEER
+
+
+def test_bottleneck_detector_ranks_findings():
+    from torsh_b200.parallel.monitoring import BottleneckDetector, BottleneckType, Severity, StepSample
+    d = BottleneckDetector(window=10)
+    for step in range(10):
+        d.record(StepSample(rank=0, step_ms=100, compute_ms=50, exposed_comm_ms=40, data_wait_ms=1, mem_used_frac=0.5))
+        d.record(StepSample(rank=1, step_ms=130, compute_ms=50, exposed_comm_ms=40, data_wait_ms=1, mem_used_frac=0.95))
+    found = d.analyze()
+    kinds = [b.kind for b in found]
+    assert BottleneckType.COMMUNICATION in kinds and [int(b.severity) for b in found] == sorted((int(b.severity) for b in found), reverse=True)
+    assert [b for b in found if b.kind is BottleneckType.COMMUNICATION][0].severity >= Severity.MEDIUM
+    assert BottleneckType.LOAD_IMBALANCE in kinds and BottleneckType.MEMORY in kinds and BottleneckType.DATA_LOADING not in kinds
+    assert [b for b in found if b.kind is BottleneckType.LOAD_IMBALANCE][0].ranks == [1]
+    assert all(b.remediation for b in found)
+    quiet = BottleneckDetector()
+    quiet.record(StepSample(rank=0, step_ms=100, compute_ms=95))
+    assert [b.kind for b in quiet.analyze()] == [BottleneckType.COMPUTE]

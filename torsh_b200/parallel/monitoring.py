@@ -4,6 +4,7 @@ and Prometheus-text export, and a monitor that checks alert thresholds (step-tim
 memory, stragglers across ranks) and aggregates per-rank summaries on rank 0 through a store."""
 from __future__ import annotations
 
+import enum
 import json
 import statistics
 import time
@@ -127,3 +128,115 @@ class DistributedMonitor:
             for r in out["stragglers"]:
                 self.alerts.append(Alert("straggler", f"rank {r} averages {means[r]:.1f} ms vs median {med:.1f} ms", means[r] / med))
         return out
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Bottleneck detection (``crates/torsh-distributed/src/bottleneck_detection.rs:16-717``: types, severity, remediation)
+class BottleneckType(enum.Enum):
+    COMMUNICATION = "communication"
+    COMPUTE = "compute"
+    MEMORY = "memory"
+    DATA_LOADING = "data_loading"
+    LOAD_IMBALANCE = "load_imbalance"
+    HOST_LAUNCH = "host_launch"
+    POWER_CAP = "power_cap"
+
+
+class Severity(enum.IntEnum):
+    LOW = 1
+    MEDIUM = 2
+    HIGH = 3
+    CRITICAL = 4
+
+
+@dataclass
+class Bottleneck:
+    kind: BottleneckType
+    severity: Severity
+    evidence: str
+    remediation: list[str]
+    ranks: list[int] = field(default_factory=list)
+
+
+@dataclass
+class StepSample:
+    """What one rank measured for one step (milliseconds unless stated)."""
+    rank: int
+    step_ms: float
+    compute_ms: float = 0.0
+    exposed_comm_ms: float = 0.0            # communication time that was NOT hidden behind compute
+    data_wait_ms: float = 0.0               # time the step waited for its batch
+    device_idle_ms: float = 0.0             # gaps between kernels (host could not launch fast enough)
+    mem_used_frac: float = 0.0
+    sm_mhz: float | None = None
+    sm_max_mhz: float | None = None
+
+
+class BottleneckDetector:
+    """Turns a window of per-rank step samples into a ranked list of bottlenecks with remediation hints."""
+
+    def __init__(self, window: int = 50, comm_frac: float = 0.15, data_frac: float = 0.05, idle_frac: float = 0.05,
+                 mem_frac: float = 0.92, imbalance: float = 0.10, clock_frac: float = 0.90):
+        self.window, self.samples = window, []
+        self.t = dict(comm=comm_frac, data=data_frac, idle=idle_frac, mem=mem_frac, imb=imbalance, clk=clock_frac)
+
+    def record(self, s: StepSample):
+        self.samples.append(s)
+        del self.samples[:-self.window * 64]
+
+    @staticmethod
+    def _sev(x: float, lo: float) -> Severity:
+        r = x / lo
+        return Severity.CRITICAL if r >= 4 else Severity.HIGH if r >= 2.5 else Severity.MEDIUM if r >= 1.5 else Severity.LOW
+
+    def analyze(self) -> list[Bottleneck]:
+        if not self.samples:
+            return []
+        by_rank: dict[int, list[StepSample]] = {}
+        for s in self.samples:
+            by_rank.setdefault(s.rank, []).append(s)
+        mean = lambda xs: sum(xs) / max(len(xs), 1)
+        step = {r: mean([s.step_ms for s in v[-self.window:]]) for r, v in by_rank.items()}
+        tot = mean(list(step.values())) or 1e-9
+        frac = lambda attr: mean([mean([getattr(s, attr) for s in v[-self.window:]]) for v in by_rank.values()]) / tot
+        out: list[Bottleneck] = []
+        c = frac("exposed_comm_ms")
+        if c > self.t["comm"]:
+            out.append(Bottleneck(BottleneckType.COMMUNICATION, self._sev(c, self.t["comm"]),
+                                  f"{c:.0%} of the step is exposed communication",
+                                  ["use the fused compute + collective kernels (all-gather→GEMM, GEMM→reduce-scatter)",
+                                   "raise the gradient bucket size so fewer launches pay the barrier latency",
+                                   "check that NVLS is enabled beyond two ranks"]))
+        d = frac("data_wait_ms")
+        if d > self.t["data"]:
+            out.append(Bottleneck(BottleneckType.DATA_LOADING, self._sev(d, self.t["data"]),
+                                  f"{d:.0%} of the step waits for input batches",
+                                  ["prefetch batches on a copy stream from pinned memory", "add loader workers"]))
+        i = frac("device_idle_ms")
+        if i > self.t["idle"]:
+            out.append(Bottleneck(BottleneckType.HOST_LAUNCH, self._sev(i, self.t["idle"]),
+                                  f"the device idles {i:.0%} of the step between kernels",
+                                  ["capture the step in a CUDA graph", "use step_async so the host runs one step ahead"]))
+        m = max(mean([s.mem_used_frac for s in v[-self.window:]]) for v in by_rank.values())
+        if m > self.t["mem"]:
+            out.append(Bottleneck(BottleneckType.MEMORY, self._sev(m, self.t["mem"]) if m < 0.99 else Severity.CRITICAL,
+                                  f"device memory is {m:.0%} full",
+                                  ["shard optimizer state and parameters (FSDP)", "checkpoint activations", "lower the micro-batch"]))
+        if len(step) > 1:
+            slow = max(step, key=step.get)
+            spread = (step[slow] - min(step.values())) / tot
+            if spread > self.t["imb"]:
+                out.append(Bottleneck(BottleneckType.LOAD_IMBALANCE, self._sev(spread, self.t["imb"]),
+                                      f"rank {slow} is {spread:.0%} of a step slower than the fastest rank",
+                                      ["rebalance pipeline stages or expert capacity", "check that rank's clocks and neighbours"],
+                                      ranks=[slow]))
+        clk = [(s.sm_mhz / s.sm_max_mhz, s.rank) for s in self.samples[-self.window:] if s.sm_mhz and s.sm_max_mhz]
+        if clk and mean([c for c, _ in clk]) < self.t["clk"]:
+            out.append(Bottleneck(BottleneckType.POWER_CAP, Severity.LOW,
+                                  f"SM clocks average {mean([c for c, _ in clk]):.0%} of maximum",
+                                  ["expected under the board power cap during dense GEMMs; compare time x MHz, not time"],
+                                  ranks=sorted({r for _, r in clk})))
+        if not out and frac("compute_ms") > 0.8:
+            out.append(Bottleneck(BottleneckType.COMPUTE, Severity.LOW, "the step is compute-bound",
+                                  ["profile the top kernels against the tensor-core and HBM rooflines"]))
+        return sorted(out, key=lambda b: -int(b.severity))
