@@ -296,6 +296,38 @@ def check_moe(dev):
     return ok
 
 
+def check_canaries(dev):
+    """Run with TORSH_SYMM_CANARIES=1: every symmetric buffer carries guard bytes; after the fused collectives have run
+    over the whole payload on every rank the guards must be untouched."""
+    from torsh_b200 import _native as nv
+    from torsh_b200.parallel.collectives import FusedCollectives
+    from torsh_b200.parallel.symm import SymmetricBuffer
+    rank, world = dist.get_rank(), dist.get_world_size()
+    fc = FusedCollectives(nblocks=32)
+    n = 1 << 18
+    ok = True
+    for dtype in (torch.float32, torch.bfloat16):
+        buf = SymmetricBuffer(n, dtype)
+        ok &= buf.guard_bytes == 256
+        for use_nvls in ([True, False] if buf.has_multicast else [False]):
+            fc.use_nvls = use_nvls
+            x = torch.full((n,), float(rank + 1), device=dev, dtype=dtype)
+            buf.tensor.copy_(x)
+            fc.all_reduce_(buf, numel=n, scale=1.0, mode="two_shot")
+            torch.cuda.synchronize()
+            ok &= bool((buf.tensor.float() == world * (world + 1) / 2).all())
+            chunk = n // world
+            fc.all_gather_(buf, chunk)
+            fc.reduce_scatter(buf, chunk, scale=1.0)
+            torch.cuda.synchronize()
+            nv.check_status()
+            dist.barrier()
+            good = buf.check_canaries() and fc.ctx.flags.check_canaries()
+            log(f"canaries {dtype} nvls={use_nvls}: {'intact' if good else 'OVERWRITTEN'}")
+            ok &= good
+    return ok
+
+
 def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -313,6 +345,8 @@ def main():
         ok &= check_ddp(dev)
     if "moe" in what:
         ok &= check_moe(dev)
+    if "canaries" in what:
+        ok &= check_canaries(dev)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     log("ALL CHECKS PASSED" if flag.item() == 1 else "CHECKS FAILED")

@@ -11,13 +11,14 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("what", ["collectives", "fsdp", "tp", "ddp", "moe"])
+@pytest.mark.parametrize("what", ["collectives", "fsdp", "tp", "ddp", "moe", "canaries"])
 def test_multi_rank(what):
     n = min(torch.cuda.device_count(), 8)
     n = 8 if n >= 8 else (4 if n >= 4 else 2)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", "29541", os.path.join(ROOT, "tests", "dist", "check_collectives.py"), what]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    env = dict(os.environ, TORSH_SYMM_CANARIES="1") if what == "canaries" else None
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     sys.stdout.write(r.stdout[-4000:])
     sys.stderr.write(r.stderr[-2000:])
     assert r.returncode == 0 and "ALL CHECKS PASSED" in r.stdout

@@ -16,11 +16,14 @@ host-side bookkeeping. Collectives that may run concurrently need separate conte
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
 
 MAX_RANKS = 8
+GUARD_BYTES = 256
+CANARY_BYTE = 0xA5
 FLAG_SLOTS = 320   # one cross-rank barrier slot per CTA of a collective kernel (COMM_MAX_BLOCKS in the CUDA source)
 
 
@@ -37,18 +40,38 @@ class SymmetricBuffer:
             symm_mem.enable_symm_mem_for_group(self.group.group_name)
         except Exception:
             pass
-        self.tensor = symm_mem.empty(numel, dtype=dtype, device=dev)
+        # TORSH_SYMM_CANARIES=1 puts 256 guard bytes with a fixed pattern in front of and behind the payload of every
+        # symmetric buffer; check_canaries() tells whether a kernel of this or another rank wrote outside its range
+        self.guard_bytes = GUARD_BYTES if os.environ.get("TORSH_SYMM_CANARIES", "0") == "1" else 0
+        es = torch.empty((), dtype=dtype).element_size()
+        g = self.guard_bytes // es
+        self._raw = symm_mem.empty(numel + 2 * g, dtype=dtype, device=dev)
+        self.tensor = self._raw[g:g + numel]
         if zero:
             self.tensor.zero_()
-        self.handle = symm_mem.rendezvous(self.tensor, self.group)
-        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if g:
+            self._raw.view(torch.uint8)[:self.guard_bytes].fill_(CANARY_BYTE)
+            self._raw.view(torch.uint8)[self.guard_bytes + numel * es:].fill_(CANARY_BYTE)
+        self.handle = symm_mem.rendezvous(self._raw, self.group)
+        self.peer_ptrs = [int(p) + self.guard_bytes for p in self.handle.buffer_ptrs]
         try:
-            self.multicast_ptr = int(self.handle.multicast_ptr or 0)
+            mc = int(self.handle.multicast_ptr or 0)
+            self.multicast_ptr = mc + self.guard_bytes if mc else 0
         except Exception:
             self.multicast_ptr = 0
         self._ptr_array = (ctypes.c_void_p * MAX_RANKS)(*(self.peer_ptrs + [0] * (MAX_RANKS - self.world)))
         torch.cuda.synchronize()
         dist.barrier(self.group)
+
+    def check_canaries(self) -> bool:
+        """True when the guard bytes around the payload are intact (always True when canaries are off)."""
+        if not self.guard_bytes:
+            return True
+        raw = self._raw.view(torch.uint8)
+        es = self._raw.element_size()
+        front = raw[:self.guard_bytes]
+        back = raw[self.guard_bytes + self.tensor.numel() * es:]
+        return bool((front == CANARY_BYTE).all().item()) and bool((back == CANARY_BYTE).all().item())
 
     @property
     def ptr_array(self):
