@@ -385,3 +385,69 @@ def test_bottleneck_detector_ranks_findings():
     quiet = BottleneckDetector()
     quiet.record(StepSample(rank=0, step_ms=100, compute_ms=95))
     assert [b.kind for b in quiet.analyze()] == [BottleneckType.COMPUTE]
+
+
+def test_edge_federated_coordination():
+    import torch
+    from torsh_b200.parallel import edge as E
+    mgr = E.EdgeComputingManager(E.FederatedLearningConfig(clients_per_round=2, selection=E.ClientSelectionStrategy.RESOURCE_AWARE))
+    for i, (fl, bat) in enumerate([(1e11, 1.0), (5e11, 0.9), (9e11, 0.1), (2e11, 0.8)]):
+        mgr.register_device(E.EdgeDevice(f"d{i}", flops=fl, battery=bat, num_samples=100 * (i + 1)))
+    assert mgr.select_clients(0) == ["d1", "d3"]                       # d2 is strongest but below the battery floor
+    mgr.update_device_status("d1", E.DeviceStatus.OFFLINE)
+    assert "d1" not in mgr.select_clients(1)
+    ups = [{"w": torch.full((3,), 1.0)}, {"w": torch.full((3,), 4.0)}]
+    fed = E.FederatedLearningCoordinator(E.FederatedLearningConfig())
+    assert torch.allclose(fed.aggregate_updates(ups, num_samples=[100, 300])["w"], torch.full((3,), 3.25))
+    med = E.FederatedLearningCoordinator(E.FederatedLearningConfig(aggregation=E.AggregationStrategy.MEDIAN))
+    outlier = ups + [{"w": torch.full((3,), 1000.0)}]
+    assert torch.allclose(med.aggregate_updates(outlier)["w"], torch.full((3,), 4.0))
+    nova = E.FederatedLearningCoordinator(E.FederatedLearningConfig(algorithm=E.FederatedAlgorithm.FED_NOVA, aggregation=E.AggregationStrategy.SIMPLE_AVERAGE))
+    assert torch.allclose(nova.aggregate_updates([{"w": torch.tensor([2.0])}, {"w": torch.tensor([8.0])}], local_steps=[1, 4])["w"], torch.tensor([5.0]))
+    priv = E.PrivacyManager(E.PrivacyConfig(clip_norm=1.0, noise_multiplier=0.0))
+    assert abs(float(priv.clip({"w": torch.full((4,), 10.0)})["w"].norm()) - 1.0) < 1e-5
+    loc, glob = {"w": torch.ones(2, requires_grad=True)}, {"w": torch.zeros(2)}
+    assert abs(float(fed.proximal_term(loc, glob)) - 0.5 * 0.01 * 2) < 1e-7
+    assert E.adaptive_params(200).compression_ratio == 1.0 and E.adaptive_params(1).sync_every == 4
+    bm = E.BandwidthMonitor()
+    bm.record_measurement("d0", 10, when=0.0); bm.record_measurement("d0", 30, when=100.0)
+    assert bm.get_average_bandwidth("d0", 5, now=120.0) == 20 and bm.get_average_bandwidth("d0", 1, now=120.0) == 30
+    h = E.HierarchicalTrainingCoordinator()
+    assert h.assign_device_tier(E.EdgeDevice("p")) is E.TrainingTier.DEVICE
+    assert h.assign_device_tier(E.EdgeDevice("e", device_type=E.DeviceType.EDGE_SERVER)) is E.TrainingTier.EDGE
+    assert h.assign_device_tier(E.EdgeDevice("c", flops=2e15)) is E.TrainingTier.CLOUD and h.get_tier_devices(E.TrainingTier.CLOUD) == ["c"]
+
+
+def test_rdma_verbs_model():
+    import torch
+    from torsh_b200.parallel import rdma as R
+    fab = R.LoopbackFabric()
+    a, b = R.RdmaEndpoint(0, fab), R.RdmaEndpoint(1, fab)
+    mr = b.register(torch.zeros(10))
+    ro = b.register(torch.arange(4.0), R.MemoryAccess(remote_write=False))
+    assert a.post(R.RdmaOperation.WRITE, 1, mr.rkey, torch.ones(3)).status is R.CompletionStatus.NOT_CONNECTED
+    a.connect(1)
+    assert a.post(R.RdmaOperation.WRITE, 1, mr.rkey, torch.ones(3), remote_offset=2).status is R.CompletionStatus.SUCCESS
+    assert mr.tensor.tolist() == [0, 0, 1, 1, 1, 0, 0, 0, 0, 0]
+    got = torch.empty(4)
+    assert a.post(R.RdmaOperation.READ, 1, ro.rkey, got).status is R.CompletionStatus.SUCCESS and got.tolist() == [0, 1, 2, 3]
+    assert a.post(R.RdmaOperation.WRITE, 1, ro.rkey, torch.ones(1)).status is R.CompletionStatus.REMOTE_ACCESS_ERROR
+    assert a.post(R.RdmaOperation.WRITE, 1, mr.rkey, torch.ones(20)).status is R.CompletionStatus.LOCAL_LENGTH_ERROR
+    assert a.post(R.RdmaOperation.READ, 1, 999999, got).status is R.CompletionStatus.INVALID_KEY
+    cnt = b.register(torch.zeros(1, dtype=torch.int64))
+    assert a.post(R.RdmaOperation.ATOMIC_FAA, 1, cnt.rkey, value=5).result == 0 and int(cnt.tensor[0]) == 5
+    assert a.post(R.RdmaOperation.ATOMIC_CAS, 1, cnt.rkey, compare=4, value=9).result == 5 and int(cnt.tensor[0]) == 5
+    assert a.post(R.RdmaOperation.ATOMIC_CAS, 1, cnt.rkey, compare=5, value=9).result == 5 and int(cnt.tensor[0]) == 9
+    big = b.register(torch.zeros(100))
+    sched = R.RdmaTensorScheduler(a, max_wr_elems=32)
+    wcs = sched.write_tensor(torch.arange(100.0).view(10, 10), 1, big.rkey)
+    assert len(wcs) == 4 and torch.equal(big.tensor, torch.arange(100.0))
+    back = torch.empty(50)
+    sched.read_tensor(back, 1, big.rkey, remote_offset=50)
+    assert torch.equal(back, torch.arange(50.0, 100.0))
+    assert (a.stats.writes, a.stats.atomics, a.stats.errors, a.stats.reads) == (5, 3, 4, 3) and len(a.poll(100)) == 15
+    pool = R.RdmaMemoryPool(b, sizes=(16, 64), per_class=1)
+    r1 = pool.acquire(10); r2 = pool.acquire(10); r3 = pool.acquire(10)
+    assert (r1.length, r2.length, r3.length) == (16, 64, 10) and pool.stats == {"hits": 2, "misses": 1}
+    pool.release(r1)
+    assert pool.acquire(16) is r1
