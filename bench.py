@@ -105,6 +105,7 @@ def main():
     ap.add_argument("--fsdp-no-overlap", action="store_true", help="one fused FSDP launch after backward (the default)")
     ap.add_argument("--fsdp-overlap", action="store_true", help="launch each block's FSDP kernel from a backward hook on a side stream")
     ap.add_argument("--fsdp-nvls", type=int, default=None, help="1 / 0: force NVLS multimem on / off in the fused FSDP kernel")
+    ap.add_argument("--fsdp-coarse", type=int, default=0, help="with --fsdp-overlap: merge the per-block units into this many groups")
     ap.add_argument("--fsdp-single", action="store_true",
                     help="diagnostic: run the FSDP engine in a one-rank group on one GPU (its kernels without any peer)")
     args = ap.parse_args()
@@ -148,6 +149,7 @@ def main():
         if args.fsdp_comm_blocks:
             fc.comm_blocks = args.fsdp_comm_blocks
         fc.overlap = bool(args.fsdp_overlap) and not args.fsdp_no_overlap
+        fc.coarse_units = args.fsdp_coarse
         if args.fsdp_nvls is not None:
             fc.use_nvls = bool(args.fsdp_nvls)
         parallel = FlatFSDP(dist.group.WORLD, fc)

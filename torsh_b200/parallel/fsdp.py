@@ -66,6 +66,7 @@ class FsdpConfig:
     # 30.8 ms per step with overlap (the 64 co-resident CTAs slow the statically scheduled GEMM tiles of the SMs they
     # share, and 25 barrier-separated launches cost 1.2 ms even with a single rank), 30.0 ms without.
     overlap: bool = False
+    coarse_units: int = 0      # with overlap: merge the per-block units into this many groups (0 = one unit per block)
     comm_blocks: int = 64      # CTAs while overlapping backward (measured on 2 B200s: 16 -> 32.1 ms, 32 -> 31.0, 64 -> 30.1 per step)
     tail_blocks: int = 296     # CTAs of the units that are reduced after backward has finished
     use_nvls: bool | None = None
@@ -203,6 +204,13 @@ class FlatFSDP:
             # nothing runs before backward has finished, so the whole model is ONE unit: one launch, one pair of
             # cross-rank barriers and one pass at full width instead of a barrier-separated kernel per block
             units = [[p for u in units for p in u]]
+        elif self.cfg.coarse_units and len(units) > 2:
+            # merge the per-block units (units[1:], in depth order) into a few contiguous groups: the deepest group is
+            # handed to the comm stream when backward has passed its first block and overlaps the rest of backward
+            k = min(self.cfg.coarse_units, len(units) - 1)
+            blocks = units[1:]
+            per = (len(blocks) + k - 1) // k
+            units = [units[0]] + [[p for u in blocks[i:i + per] for p in u] for i in range(0, len(blocks), per)]
         flat = ShardedFlatParameters(units, self.group)
         self._flat = flat
         if self.cfg.overlap:
@@ -216,7 +224,9 @@ class FlatFSDP:
     def _install_hooks(self, model, units):
         """When the gradient w.r.t. a unit's input exists, every parameter gradient of that unit has been
         launched: hand the unit to the comm stream at that point."""
-        first_param_to_unit = {id(u[0]): i for i, u in enumerate(units) if i > 0 and u}
+        # with coarse groups the shallowest one finishes with backward itself: it runs afterwards at full width
+        first = 2 if self.cfg.coarse_units else 1
+        first_param_to_unit = {id(u[0]): i for i, u in enumerate(units) if i >= first and u}
         for m in model.modules():
             if isinstance(m, torch.nn.ModuleList):
                 for child in m:
