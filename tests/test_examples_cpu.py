@@ -17,7 +17,7 @@ def _load(name):
 
 def test_single_process_examples(tmp_path):
     losses = _load("gpt2").main(["--model", "gpt2-tiny", "--steps", "4", "--batch", "2", "--seq", "32"])
-    assert len(losses) == 4 and all(l == l for l in losses)
+    assert len(losses) == 4 and all(l == l for l in losses) and losses[-1] < losses[0] - 0.05
     losses = _load("resnet").main(["--model", "resnet18", "--steps", "2", "--image", "32", "--batch", "4"])
     assert losses[1] < losses[0] * 1.5
     assert _load("checkpointing").main([str(tmp_path)]) is True

@@ -11,6 +11,7 @@ from . import ops  # noqa: E402,F401
 from .ops import attention, elementwise, gemm, linear, multi_tensor, norm, softmax  # noqa: E402,F401
 from . import autograd, data, models, nn, optim, parallel, serialize  # noqa: E402,F401
 from . import parallel as distributed  # noqa: E402,F401
+from . import engine  # noqa: E402,F401
 from .tensor import *  # noqa: E402,F401,F403
 from .tensor import Tensor  # noqa: E402,F401
 from .autograd import enable_grad, no_grad, set_grad_enabled  # noqa: E402,F401

@@ -102,6 +102,11 @@ class FlatAdamW:
                          weight_decay=self.weight_decay, step=max(self.step_count, 1), decoupled=True,
                          grad_dtype=torch.float32, grad_scale=grad_scale, zero_grad=zero_grad, dyn=self.dyn)
             return
+        # without the kernels autograd leaves gradients in p.grad instead of accumulating them into main_grad
+        for prm in f.params:
+            if prm.grad is not None:
+                prm.main_grad.add_(prm.grad.to(prm.main_grad.dtype))
+                prm.grad = None
         b1, b2 = self.betas
         g = f.grad * grad_scale
         w = f.master
