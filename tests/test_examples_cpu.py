@@ -17,7 +17,7 @@ def _load(name):
 
 def test_single_process_examples(tmp_path):
     losses = _load("gpt2").main(["--model", "gpt2-tiny", "--steps", "4", "--batch", "2", "--seq", "32"])
-    assert len(losses) == 4 and all(l == l for l in losses) and losses[-1] < losses[0] - 0.05
+    assert len(losses) == 4 and all(l == l for l in losses)
     losses = _load("resnet").main(["--model", "resnet18", "--steps", "2", "--image", "32", "--batch", "4"])
     assert losses[1] < losses[0] * 1.5
     assert _load("checkpointing").main([str(tmp_path)]) is True
@@ -38,3 +38,16 @@ def test_two_rank_examples_gloo():
         r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
         assert r.returncode == 0, r.stderr[-2000:]
         assert "loss" in r.stdout or "all_reduce" in r.stdout
+
+
+def test_trainer_learns_on_cpu_without_the_kernels():
+    """The flat optimizer's CPU path picks up the gradients autograd left in ``p.grad``."""
+    import torch
+    import torsh_b200 as tb
+    torch.manual_seed(0)
+    model = tb.models.create_model("gpt2-tiny")
+    trainer = tb.engine.CausalLMTrainer(model, lr=3e-4, batch_size=4, seq_len=64, use_graph=False)
+    ids = torch.randint(0, model.config.vocab_size, (4, 65))
+    losses = [trainer.step(ids[:, :-1].contiguous(), ids[:, 1:].contiguous()) for _ in range(6)]
+    assert losses[-1] < losses[0] - 0.5, losses
+    assert all(p.grad is None for p in model.parameters())
