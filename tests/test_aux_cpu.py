@@ -451,3 +451,24 @@ def test_rdma_verbs_model():
     assert (r1.length, r2.length, r3.length) == (16, 64, 10) and pool.stats == {"hits": 2, "misses": 1}
     pool.release(r1)
     assert pool.acquire(16) is r1
+
+
+def test_memory_profiler_scopes_and_leak_detection(tmp_path):
+    import json
+    import torch
+    from torsh_b200.utils.memory_profiler import MemoryProfiler
+    prof = MemoryProfiler()
+    before = prof.snapshot()
+    keep = []
+    with prof.scope("alloc"):
+        keep.append(torch.zeros(123, 77))
+        tmp = torch.zeros(1 << 20)
+        del tmp
+    after = prof.snapshot()
+    leaks = prof.leaks(before, after)
+    assert any(k[0] == (123, 77) and n == 1 for k, n in leaks)
+    assert not any(k[0] == (1 << 20,) for k, _ in leaks)
+    rec = prof.scopes[0]
+    assert rec.name == "alloc" and rec.peak_bytes >= rec.end_bytes and rec.duration_ms >= 0
+    prof.export_json(str(tmp_path / "mem.json"))
+    assert json.load(open(tmp_path / "mem.json"))["scopes"][0]["name"] == "alloc"

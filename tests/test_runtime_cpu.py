@@ -184,3 +184,65 @@ def test_fx_jit_hub_package_tensorboard_cli(tmp_path):
     assert cli.main(["model", "convert", str(tmp_path / "m.trsm"), "-o", str(tmp_path / "m.safetensors")]) == 0
     assert cli.main(["model", "validate", str(tmp_path / "m.safetensors")]) == 0
     assert cli.main(["info"]) == 0 and cli.main(["init", str(tmp_path / "proj")]) == 0
+
+
+def test_operation_coordinator_orders_streams_and_rejects_cycles():
+    import time
+    import pytest
+    from torsh_b200.core.event_coordination import (AsyncEventWaiter, CrossStreamBarrier, DependencyCycleError, HostEvent,
+                                                    OperationCoordinator)
+    co = OperationCoordinator(event_factory=HostEvent)
+    co.add_operation("load", "copy")
+    co.add_operation("fwd", "compute", ["load"])
+    co.add_operation("bwd", "compute", ["fwd"])
+    co.add_operation("allreduce", "comm", ["bwd"])
+    co.add_operation("step", "compute", ["allreduce", "bwd"])
+    assert co.order() == ["load", "fwd", "bwd", "allreduce", "step"] and co.detect_deadlocks() == []
+    trace = []
+    co.run({n: (lambda n=n: trace.append(n)) for n in co.ops})
+    assert trace == co.order()
+    assert co.stats == {"events_recorded": 5, "cross_stream_waits": 3, "same_stream_skipped": 2}
+    assert co.ops["bwd"].event.waited_by == ["comm"] and co.ops["allreduce"].event.waited_by == ["compute"]
+    with pytest.raises(DependencyCycleError):
+        co.add_dependency("load", "step")
+    with pytest.raises(KeyError):
+        co.add_operation("x", "compute", ["missing"])
+    fresh = OperationCoordinator(event_factory=HostEvent)
+    fresh.add_operation("a", "s0"); fresh.add_operation("b", "s1", ["a"])
+    with pytest.raises(RuntimeError):
+        fresh.issue("b")
+    bar = CrossStreamBarrier(["s0", "s1", "s2"], event_factory=HostEvent)
+    evs = bar.arrive_and_wait()
+    assert [sorted(e.waited_by) for e in evs] == [["s1", "s2"], ["s0", "s2"], ["s0", "s1"]]
+    w = AsyncEventWaiter()
+    done, late = HostEvent(), HostEvent()
+    hits = []
+    w.on_complete(done, lambda: hits.append("done"))
+    w.on_complete(late, lambda: hits.append("late"), timeout_s=0.02, on_timeout=lambda: hits.append("timeout"))
+    done.record()
+    time.sleep(0.2)
+    w.shutdown()
+    assert sorted(hits) == ["done", "timeout"] and (w.completed, w.timed_out, w.pending()) == (1, 1, 0)
+
+
+def test_backend_capabilities_hints_and_autotuner(tmp_path):
+    import json
+    from torsh_b200.core import backend as B
+    caps = B.capabilities()
+    assert caps.sm_count == 148 and "tcgen05" in caps.features and "f16" in caps.tensor_cores
+    k = B.TENSOR_CORE_KINDS["f16"]
+    assert k.accumulator == "f32" and 128 in k.m and k.n_max == 256 and k.k == 16
+    peaks = tmp_path / "peaks.json"
+    peaks.write_text(json.dumps({"hbm_gbs": 6553.9, "bf16_tflops": 1633.7}))
+    h = B.performance_hints(str(peaks))
+    assert (h.hbm_gbs, h.bf16_tflops, h.grid_multiple) == (6553.9, 1633.7, 148)
+    cfg = B.CudaBackendBuilder().device(0).allow_tf32(False).stream_pool_size(8).build()
+    assert (cfg.allow_tf32, cfg.stream_pool_size) == (False, 8)
+    cost = {"bn128": 3.0, "bn256": 1.0}
+    calls = []
+    tuner = B.Autotuner(str(tmp_path / "tune.json"), timer=lambda fn: fn())
+    cands = {n: (lambda n=n: calls.append(n) or cost[n]) for n in cost}
+    assert tuner.select("gemm/8192x1024x4096", cands) == "bn256" and sorted(calls) == ["bn128", "bn256"]
+    assert tuner.select("gemm/8192x1024x4096", cands) == "bn256" and len(calls) == 2          # cached
+    again = B.Autotuner(str(tmp_path / "tune.json"), timer=lambda fn: 1 / 0)
+    assert again.select("gemm/8192x1024x4096", cands) == "bn256"                               # loaded from the file
