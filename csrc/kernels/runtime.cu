@@ -162,6 +162,40 @@ TB_EXPORT int tb_rt_memcpy_async(void* dst, const void* src, uint64_t bytes, cud
   TB_CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, st));
   return 0;
 }
+// Unified (managed) memory: one pointer valid on host and device; pages migrate on demand, or ahead of use with
+// tb_rt_managed_prefetch. device < 0 means the host.
+TB_EXPORT void* tb_rt_managed_alloc(uint64_t bytes) {
+  if (ensure_device()) return nullptr;
+  void* p = nullptr;
+  if (cudaMallocManaged(&p, bytes, cudaMemAttachGlobal) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  return p;
+}
+TB_EXPORT int tb_rt_managed_free(void* p) {
+  TB_CUDA_CHECK(cudaFree(p));
+  return 0;
+}
+TB_EXPORT int tb_rt_managed_prefetch(const void* p, uint64_t bytes, int device, cudaStream_t st) {
+  TB_ENSURE_DEVICE();
+  cudaMemLocation loc{};
+  loc.type = device < 0 ? cudaMemLocationTypeHost : cudaMemLocationTypeDevice;
+  loc.id = device < 0 ? 0 : device;
+  TB_CUDA_CHECK(cudaMemPrefetchAsync_v2(p, bytes, loc, 0, st));
+  return 0;
+}
+// advice: 0 = read-mostly, 1 = preferred location, 2 = accessed by (the device, or the host when device < 0)
+TB_EXPORT int tb_rt_managed_advise(const void* p, uint64_t bytes, int advice, int device) {
+  TB_ENSURE_DEVICE();
+  cudaMemLocation loc{};
+  loc.type = device < 0 ? cudaMemLocationTypeHost : cudaMemLocationTypeDevice;
+  loc.id = device < 0 ? 0 : device;
+  const cudaMemoryAdvise a = advice == 0 ? cudaMemAdviseSetReadMostly
+                             : advice == 1 ? cudaMemAdviseSetPreferredLocation : cudaMemAdviseSetAccessedBy;
+  TB_CUDA_CHECK(cudaMemAdvise_v2(p, bytes, a, loc));
+  return 0;
+}
 TB_EXPORT int tb_rt_memset_async(void* dst, int value, uint64_t bytes, cudaStream_t st) {
   TB_ENSURE_DEVICE();
   TB_CUDA_CHECK(cudaMemsetAsync(dst, value, bytes, st));

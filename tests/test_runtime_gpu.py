@@ -107,3 +107,23 @@ def test_bounded_wait_reports_timeout_and_context_survives():
     x = torch.randn(1024, device="cuda")
     assert torch.equal(ew.unary_raw("relu", x), torch.relu(x))
     assert lib.tb_wait_probe(flag.data_ptr(), 1, 2_000_000_000, st.data_ptr(), None, nv.stream_ptr()) != 0   # > 1 s refused
+
+
+def test_unified_buffer_is_visible_from_host_and_device():
+    import torch
+    from torsh_b200.core import runtime as rt
+    n = 1 << 20
+    buf = rt.UnifiedBuffer(n * 4)
+    host = buf.host_view((n,), torch.float32)
+    host.copy_(torch.arange(n, dtype=torch.float32))
+    buf.advise(rt.UnifiedBuffer.READ_MOSTLY)
+    buf.prefetch()                                       # pages move to the GPU ahead of the copy
+    dev = torch.empty(n, device="cuda")
+    buf.copy_to(dev)
+    torch.cuda.synchronize()
+    assert torch.equal(dev.cpu(), torch.arange(n, dtype=torch.float32))
+    buf.prefetch(-1)
+    torch.cuda.synchronize()
+    assert float(host[12345]) == 12345.0
+    del host
+    buf.free()

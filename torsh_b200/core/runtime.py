@@ -40,6 +40,10 @@ def _lib():
         lib.tb_rt_pinned_free.argtypes = [vp]
         lib.tb_rt_memcpy_async.argtypes = [vp, vp, u64, vp]
         lib.tb_rt_memset_async.argtypes = [vp, ctypes.c_int, u64, vp]
+        lib.tb_rt_managed_alloc.restype, lib.tb_rt_managed_alloc.argtypes = vp, [u64]
+        lib.tb_rt_managed_free.argtypes = [vp]
+        lib.tb_rt_managed_prefetch.argtypes = [vp, u64, ctypes.c_int, vp]
+        lib.tb_rt_managed_advise.argtypes = [vp, u64, ctypes.c_int, ctypes.c_int]
         lib.tb_rt_stream_get.restype, lib.tb_rt_stream_get.argtypes = vp, [ctypes.c_int, ctypes.c_int]
         for f in ("tb_rt_stream_priority", "tb_rt_stream_sync", "tb_rt_stream_query"):
             getattr(lib, f).argtypes = [vp]
@@ -201,6 +205,51 @@ class PinnedBuffer:
 
     @staticmethod
     def stats() -> dict: return _stats(_lib().tb_rt_pinned_stats)
+
+
+class UnifiedBuffer:
+    """Managed memory (``crates/torsh-backend/src/cuda/unified_buffer.rs``, ``backend.rs:464-629``): one allocation that
+    the host and the device address through the same pointer. ``host_view`` is a CPU tensor over it; ``prefetch`` moves
+    the pages ahead of use and ``advise`` sets read-mostly / preferred-location / accessed-by hints. Device kernels take
+    ``ptr`` (or a tensor made by a kernel-side wrapper); synchronise before reading on the other side."""
+
+    READ_MOSTLY, PREFERRED_LOCATION, ACCESSED_BY = 0, 1, 2
+
+    def __init__(self, nbytes: int):
+        self.nbytes, self.ptr = nbytes, _lib().tb_rt_managed_alloc(nbytes)
+        if not self.ptr:
+            raise MemoryError(f"managed memory: cannot allocate {nbytes} bytes")
+
+    def host_view(self, shape, dtype=torch.uint8) -> torch.Tensor:
+        ct = (ctypes.c_uint8 * self.nbytes).from_address(self.ptr)
+        t = torch.frombuffer(ct, dtype=torch.uint8)
+        t = (t.view(dtype) if dtype != torch.uint8 else t).reshape(shape)
+        t._managed_owner = self
+        return t
+
+    def prefetch(self, device: int | None = None, stream=None) -> None:
+        """``device=None``: the current GPU; ``device=-1``: back to the host."""
+        dev = torch.cuda.current_device() if device is None else device
+        nv.check(_lib().tb_rt_managed_prefetch(self.ptr, self.nbytes, dev, nv.stream_ptr(stream)), "managed_prefetch")
+
+    def advise(self, advice: int, device: int | None = None) -> None:
+        dev = torch.cuda.current_device() if device is None else device
+        nv.check(_lib().tb_rt_managed_advise(self.ptr, self.nbytes, advice, dev), "managed_advise")
+
+    def copy_to(self, dst: torch.Tensor, stream=None) -> None:
+        nv.check(_lib().tb_rt_memcpy_async(dst.data_ptr(), self.ptr, min(self.nbytes, dst.numel() * dst.element_size()),
+                                           nv.stream_ptr(stream)), "memcpy_async")
+
+    def free(self):
+        if self.ptr:
+            _lib().tb_rt_managed_free(self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
 
 
 class HostPool:
