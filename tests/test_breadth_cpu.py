@@ -379,3 +379,17 @@ def test_remaining_nn_layers():
     wn = nn.WeightNorm(torch.nn.Linear(4, 3))
     assert wn(torch.randn(2, 4)).shape == (2, 3)
     assert nn.LazyLinear(3)(torch.randn(2, 7)).shape == (2, 3)
+
+
+def test_amp_context_policy_and_saturation():
+    from torsh_b200.optim.mixed_precision import AmpContext, GradientScaler, GradScaler, MixedPrecisionConfig
+    assert GradientScaler is GradScaler
+    cfg = MixedPrecisionConfig()
+    amp = AmpContext(cfg)
+    assert amp.dtype_for("matmul") == cfg.dtype and amp.dtype_for("softmax", cfg.dtype) == torch.float32
+    assert amp.dtype_for("relu", cfg.dtype) == cfg.dtype and amp.dtype_for("matmul", torch.int64) == torch.int64
+    a, b = amp.cast("matmul", torch.ones(2, 2), torch.ones(2, 2))
+    assert a.dtype == cfg.dtype and b.dtype == cfg.dtype and amp.stats["casts"] == 2
+    half = AmpContext(cfg, overrides={"matmul": torch.float16})
+    big = half.cast("matmul", torch.tensor([1e6, -1e6, 1.0]))
+    assert big.dtype == torch.float16 and torch.isfinite(big).all() and half.stats["saturated"] == 2

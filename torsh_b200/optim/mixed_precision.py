@@ -170,3 +170,54 @@ class MixedPrecisionTrainer:
 
 
 BF16Trainer = lambda model, optimizer, **kw: MixedPrecisionTrainer(model, optimizer, BF16Config(), **kw)  # noqa: E731
+
+
+class AmpContext:
+    """Per-operation precision policy (``crates/torsh-backend/src/cuda/mixed_precision.rs:13-494``: ``AmpContext``):
+    contractions run in the low-precision dtype, reductions / normalisations / losses in fp32, everything else keeps its
+    input dtype; ``cast`` applies the policy to an operation's inputs and ``saturate`` clamps to the target's finite range
+    before a down-cast (fp16 overflows at 65504)."""
+
+    LOW = {"matmul", "linear", "conv2d", "conv1d", "bmm", "attention", "embedding"}
+    FP32 = {"softmax", "log_softmax", "layer_norm", "rms_norm", "batch_norm", "cross_entropy", "mse_loss", "sum", "mean",
+            "exp", "log", "pow", "norm"}
+
+    def __init__(self, config: MixedPrecisionConfig | None = None, overrides: dict | None = None):
+        self.cfg = config or MixedPrecisionConfig()
+        self.overrides = dict(overrides or {})
+        self.stats = {"casts": 0, "saturated": 0}
+
+    def dtype_for(self, op: str, input_dtype: torch.dtype = torch.float32) -> torch.dtype:
+        if op in self.overrides:
+            return self.overrides[op]
+        if not self.cfg.enabled or not input_dtype.is_floating_point:
+            return input_dtype
+        if op in self.LOW:
+            return self.cfg.dtype
+        if op in self.FP32:
+            return torch.float32
+        return input_dtype
+
+    def saturate(self, t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        if not dtype.is_floating_point or torch.finfo(dtype).max >= torch.finfo(t.dtype).max:
+            return t
+        lim = torch.finfo(dtype).max
+        over = t.abs() > lim
+        if bool(over.any()):
+            self.stats["saturated"] += int(over.sum())
+            t = t.clamp(-lim, lim)
+        return t
+
+    def cast(self, op: str, *tensors):
+        out = []
+        for t in tensors:
+            if isinstance(t, torch.Tensor) and t.is_floating_point():
+                dt = self.dtype_for(op, t.dtype)
+                if dt != t.dtype:
+                    self.stats["casts"] += 1
+                    t = self.saturate(t, dt).to(dt)
+            out.append(t)
+        return out[0] if len(out) == 1 else tuple(out)
+
+
+GradientScaler = GradScaler
