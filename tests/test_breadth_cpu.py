@@ -393,3 +393,19 @@ def test_amp_context_policy_and_saturation():
     half = AmpContext(cfg, overrides={"matmul": torch.float16})
     big = half.cast("matmul", torch.tensor([1e6, -1e6, 1.0]))
     assert big.dtype == torch.float16 and torch.isfinite(big).all() and half.stats["saturated"] == 2
+
+
+def test_arrow_parquet_roundtrip_and_gated_formats(tmp_path):
+    from torsh_b200.core.error import TorshError
+    from torsh_b200.serialize import data_science as ds
+    ts = {"w": torch.randn(3, 4), "ids": torch.arange(6).reshape(2, 3), "h": torch.randn(5).to(torch.bfloat16)}
+    for save, load, ext in ((ds.save_parquet, ds.load_parquet, "parquet"), (ds.save_arrow, ds.load_arrow, "arrow")):
+        p = str(tmp_path / f"t.{ext}")
+        save(ts, p)
+        back = load(p)
+        assert all(back[k].dtype == ts[k].dtype and back[k].shape == ts[k].shape and torch.equal(back[k], ts[k]) for k in ts)
+    try:
+        import h5py  # noqa: F401
+    except ImportError:
+        with pytest.raises(TorshError):
+            ds.save_hdf5(ts, str(tmp_path / "t.h5"))

@@ -102,14 +102,18 @@ def decode_trsh(buf: bytes) -> tuple[torch.Tensor, dict]:
 
 def _format_of(path: Path) -> str:
     ext = path.suffix.lower()
-    return {".trsh": "binary", ".bin": "binary", ".torsh": "binary", ".json": "json", ".npy": "numpy"}.get(ext, "binary")
+    return {".trsh": "binary", ".bin": "binary", ".torsh": "binary", ".json": "json", ".npy": "numpy", ".parquet": "parquet",
+            ".arrow": "arrow", ".feather": "arrow", ".h5": "hdf5", ".hdf5": "hdf5"}.get(ext, "binary")
 
 
 def save_tensor(t: torch.Tensor, path, compression_level: int = 0, metadata: dict | None = None) -> None:
     """``Tensor::save(path, opts)``: the format follows the file extension."""
     path = Path(path)
     fmt = _format_of(path)
-    if fmt == "binary":
+    if fmt in ("parquet", "arrow", "hdf5"):
+        from . import data_science as ds
+        {"parquet": ds.save_parquet, "arrow": ds.save_arrow, "hdf5": ds.save_hdf5}[fmt]({"tensor": t}, str(path))
+    elif fmt == "binary":
         path.write_bytes(encode_trsh(t, compression_level, metadata))
     elif fmt == "json":
         src = t.detach().cpu()
@@ -126,6 +130,9 @@ def save_tensor(t: torch.Tensor, path, compression_level: int = 0, metadata: dic
 def load_tensor(path) -> torch.Tensor:
     path = Path(path)
     fmt = _format_of(path)
+    if fmt in ("parquet", "arrow", "hdf5"):
+        from . import data_science as ds
+        return {"parquet": ds.load_parquet, "arrow": ds.load_arrow, "hdf5": ds.load_hdf5}[fmt](str(path))["tensor"]
     if fmt == "binary":
         return decode_trsh(path.read_bytes())[0]
     if fmt == "json":
