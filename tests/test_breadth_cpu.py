@@ -409,3 +409,39 @@ def test_arrow_parquet_roundtrip_and_gated_formats(tmp_path):
     except ImportError:
         with pytest.raises(TorshError):
             ds.save_hdf5(ts, str(tmp_path / "t.h5"))
+
+
+def test_tensor_runtime_helpers():
+    import gc
+    from torsh_b200 import tensor_utils as tu
+    pool = tu.GlobalMemoryPool(max_per_key=1)
+    a = pool.acquire((3, 5))
+    ptr = a.tensor.data_ptr()
+    assert a.tensor.shape == (3, 5)
+    a.release()
+    with pool.acquire((4, 4)) as t:                       # 15 and 16 elements share the 16-element class
+        assert t.data_ptr() == ptr and t.shape == (4, 4)
+    assert pool.stats["hits"] == 1 and pool.stats["misses"] == 1
+    cache = tu.LockFreeCache(capacity=2)
+    cache.put("a", 1); cache.put("b", 2); cache.put("c", 3)
+    assert cache.get("a") is None and cache.get("c") == 3 and len(cache) == 2 and cache.get_or_insert("d", lambda: 4) == 4
+    calls = []
+    ab = tu.AutoBatcher(lambda b: (calls.append(b.shape[0]), b * 2)[1], max_batch=4, max_wait_s=0.05)
+    futs = [ab.submit(torch.full((2,), float(i))) for i in range(6)]
+    outs = [f.result(5) for f in futs]
+    ab.shutdown()
+    assert all(torch.equal(o, torch.full((2,), 2.0 * i)) for i, o in enumerate(outs)) and sum(calls) == 6 and max(calls) <= 4
+    ao = tu.AsyncOps(2)
+    assert [int(x) for x in ao.map(lambda v: v.sum(), [torch.ones(3), torch.ones(5)])] == [3, 5]
+    ao.shutdown()
+    log = tu.OperationLog()
+    with log.record("matmul", torch.ones(2, 3), torch.ones(3, 4), flops=48):
+        torch.ones(2, 3) @ torch.ones(3, 4)
+    assert log.summary()["matmul"]["count"] == 1 and log.records[0].shapes == [(2, 3), (3, 4)]
+    tr = tu.TensorTracker()
+    keep = tr.track(torch.zeros(10), "act")
+    tmp = tr.track(torch.zeros(100), "act")
+    assert tr.live_bytes("act") == 440
+    del tmp
+    gc.collect()
+    assert tr.live_bytes("act") == 40 and (tr.created, tr.freed) == (2, 1) and keep is not None
