@@ -472,3 +472,29 @@ def test_memory_profiler_scopes_and_leak_detection(tmp_path):
     assert rec.name == "alloc" and rec.peak_bytes >= rec.end_bytes and rec.duration_ms >= 0
     prof.export_json(str(tmp_path / "mem.json"))
     assert json.load(open(tmp_path / "mem.json"))["scopes"][0]["name"] == "alloc"
+
+
+def test_structured_and_audit_logging_and_degradation(tmp_path):
+    import json
+    from torsh_b200.utils.logging import AuditLog, GracefulDegradation, StructuredLogger
+    log = StructuredLogger(str(tmp_path / "run.jsonl"), rank=3)
+    with log.span("epoch0"):
+        with log.span("step1", step=1):
+            log.info("loss", value=2.5)
+    log.debug("hidden")
+    lines = [json.loads(ln) for ln in open(tmp_path / "run.jsonl")]
+    assert [r["event"] for r in lines] == ["loss", "span_end", "span_end"] and lines[0]["span"] == "epoch0/step1"
+    assert lines[0]["rank"] == 3 and lines[1]["step"] == 1 and lines[1]["duration_ms"] >= 0
+    audit = AuditLog(str(tmp_path / "audit.jsonl"))
+    audit.append("rank0", "checkpoint_saved", step=10)
+    audit.append("rank0", "lr_changed", old=1e-3, new=5e-4)
+    assert audit.verify()
+    again = AuditLog(str(tmp_path / "audit.jsonl"))
+    assert again.verify() and len(again.records) == 2
+    again.records[0]["details"]["step"] = 11
+    assert not again.verify()
+    calls = []
+    gd = GracefulDegradation(log, disable_after=2)
+    gd.add("kernel", lambda x: (calls.append("k"), 1 / 0)[1]).add("torch", lambda x: (calls.append("t"), x + 1)[1])
+    assert [gd.run(1), gd.run(2), gd.run(3)] == [2, 3, 4]
+    assert calls == ["k", "t", "k", "t", "t"] and gd.used == ["torch"] * 3          # the kernel level is skipped after two failures

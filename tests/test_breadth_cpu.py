@@ -445,3 +445,40 @@ def test_tensor_runtime_helpers():
     del tmp
     gc.collect()
     assert tr.live_bytes("act") == 40 and (tr.created, tr.freed) == (2, 1) and keep is not None
+
+
+def test_distributed_grad_accumulator_and_sync_scheduler():
+    import threading
+    from torsh_b200.autograd.distributed import DistributedGradAccumulator, GradientSyncScheduler, NetworkHealth
+    from torsh_b200.parallel.compression import TopK
+    torch.manual_seed(0)
+    lin, head = torch.nn.Linear(4, 4), torch.nn.Linear(4, 2)
+    acc = DistributedGradAccumulator()
+    acc.add_param_group("body", lin.parameters(), priority=5)
+    acc.add_param_group("head", head.parameters(), priority=1, compressor=TopK(1.0))
+    xs = [torch.randn(3, 4) for _ in range(2)]
+    for x in xs:
+        head(lin(x)).sum().backward()
+        acc.accumulate()
+    assert lin.weight.grad is None
+    acc.step()
+    ref_l, ref_h = torch.nn.Linear(4, 4), torch.nn.Linear(4, 2)
+    ref_l.load_state_dict(lin.state_dict()); ref_h.load_state_dict(head.state_dict())
+    (sum(ref_h(ref_l(x)).sum() for x in xs) / 2).backward()
+    assert torch.allclose(lin.weight.grad, ref_l.weight.grad, atol=1e-6) and torch.allclose(head.bias.grad, ref_h.bias.grad, atol=1e-6)
+    assert acc.stats["syncs"] == 2 and acc.stats["compressed"] == 2
+    health = NetworkHealth()
+    sched = GradientSyncScheduler(max_concurrent=1, health=health)
+    gate = threading.Event()
+    first = sched.schedule("gate", gate.wait, priority=0)
+    hs = [sched.schedule(n, lambda: None, nbytes=1000, priority=p) for n, p in (("low", 9), ("high", 1), ("mid", 5))]
+    bad = sched.schedule("bad", lambda: 1 / 0, priority=20)
+    gate.set()
+    assert first.wait(5) and all(h.wait(5) for h in hs)
+    with pytest.raises(ZeroDivisionError):
+        bad.wait(5)
+    sched.shutdown()
+    assert sched.order == ["gate", "high", "mid", "low", "bad"] and health.failures == 1 and health.successes == 4
+    slow = NetworkHealth()
+    slow.record(10_000_000, 1.0)
+    assert slow.should_compress(min_gbs=1.0) and not NetworkHealth().should_compress()
