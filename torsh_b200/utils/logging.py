@@ -121,5 +121,5 @@ class GracefulDegradation:
                 last = e
                 self.failures[name] += 1
                 if self.logger:
-                    self.logger.warning("degraded", level=name, error=repr(e), consecutive=self.failures[name])
+                    self.logger.warning("degraded", implementation=name, error=repr(e), consecutive=self.failures[name])
         raise RuntimeError(f"every implementation failed; last error: {last!r}")
