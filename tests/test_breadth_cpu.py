@@ -482,3 +482,31 @@ def test_distributed_grad_accumulator_and_sync_scheduler():
     slow = NetworkHealth()
     slow.record(10_000_000, 1.0)
     assert slow.should_compress(min_gbs=1.0) and not NetworkHealth().should_compress()
+
+
+def test_vision_zoo_builds_and_backpropagates():
+    from torsh_b200.models import create_model, list_models, vision_zoo as V
+    torch.manual_seed(0)
+    x = torch.randn(2, 3, 64, 64)
+    small = {"alexnet": V.AlexNet(10), "vgg": V.VGG(11, True, 10, width=0.125, hidden=64), "densenet": V.DenseNet((2, 2), 8, 16, 10),
+             "mobilenet": V.MobileNetV2(10, 0.25), "efficientnet": V.EfficientNet(10, 0.25, 0.5),
+             "convnext": V.ConvNeXt((1, 1, 1, 1), (8, 16, 32, 64), 10),
+             "swin": V.SwinTransformer(16, (2, 2), (2, 4), window=4, patch=4, num_classes=10)}
+    for name, m in small.items():
+        y = m(x)
+        assert y.shape == (2, 10), name
+        y.sum().backward()
+        assert all(p.grad is not None for p in m.parameters() if p.requires_grad), name
+    n = lambda m: sum(p.numel() for p in m.parameters())
+    assert abs(n(create_model("swin_t")) - 28.29e6) < 0.05e6 and abs(n(create_model("convnext_tiny")) - 28.59e6) < 0.05e6
+    assert abs(n(create_model("densenet121")) - 7.98e6) < 0.02e6 and abs(n(create_model("mobilenet_v2")) - 3.50e6) < 0.02e6
+    assert {"alexnet", "vgg16_bn", "efficientnet_b0"} <= set(list_models())
+
+
+def test_sentencepiece_tokenizer_roundtrip():
+    pytest.importorskip("sentencepiece")
+    from torsh_b200.text import SentencePieceTokenizer
+    corpus = ["the quick brown fox jumps over the lazy dog"] * 50 + ["pack my box with five dozen liquor jugs"] * 50
+    tok = SentencePieceTokenizer.train(corpus, vocab_size=60)
+    ids = tok.encode("the quick brown dog", add_eos=True)
+    assert tok.decode(ids) == "the quick brown dog" and max(ids) < tok.vocab_size and "".join(tok.tokenize("lazy dog")).replace("▁", " ").strip() == "lazy dog"

@@ -5,6 +5,7 @@ from .resnet import BasicBlock, BottleneckBlock, ResNet, ResNetConfig, SEBlock
 from .transformer_zoo import (BertConfig, BertForMaskedLM, BertForSequenceClassification, BertModel, EncoderBlock,
                               EncoderConfig, EncoderDecoderModel, RobertaModel, Seq2SeqConfig, T5Model, ViTConfig,
                               VisionTransformer)
+from .vision_zoo import AlexNet, ConvNeXt, DenseNet, EfficientNet, MobileNetV2, SwinTransformer, VGG
 
 _REGISTRY = {
     "gpt2-tiny": lambda **kw: GPTForCausalLM(GPT2Config.tiny(**kw)),
@@ -26,6 +27,16 @@ _REGISTRY = {
     "bert-large": lambda **kw: BertModel(BertConfig.bert_large(**kw)),
     "roberta-base": lambda **kw: BertModel(BertConfig.roberta_base(**kw)),
     "t5-base": lambda **kw: EncoderDecoderModel(Seq2SeqConfig(**kw)),
+    "alexnet": lambda **kw: AlexNet(**kw),
+    "vgg11": lambda **kw: VGG(11, **kw), "vgg16": lambda **kw: VGG(16, **kw), "vgg16_bn": lambda **kw: VGG(16, True, **kw),
+    "vgg19": lambda **kw: VGG(19, **kw),
+    "densenet121": lambda **kw: DenseNet((6, 12, 24, 16), **kw), "densenet169": lambda **kw: DenseNet((6, 12, 32, 32), **kw),
+    "mobilenet_v2": lambda **kw: MobileNetV2(**kw),
+    "efficientnet_b0": lambda **kw: EfficientNet(**kw),
+    "convnext_tiny": lambda **kw: ConvNeXt((3, 3, 9, 3), (96, 192, 384, 768), **kw),
+    "convnext_small": lambda **kw: ConvNeXt((3, 3, 27, 3), (96, 192, 384, 768), **kw),
+    "swin_t": lambda **kw: SwinTransformer(96, (2, 2, 6, 2), (3, 6, 12, 24), **kw),
+    "swin_s": lambda **kw: SwinTransformer(96, (2, 2, 18, 2), (3, 6, 12, 24), **kw),
 }
 
 

@@ -141,3 +141,40 @@ def beam_search(step_fn, start_ids: torch.Tensor, beam: int = 4, max_new: int = 
         if all(d for _, _, d in beams):
             break
     return beams[0][0][0]
+
+
+class SentencePieceTokenizer:
+    """Unigram / BPE sub-word tokenizer backed by the ``sentencepiece`` package
+    (``crates/torsh-text/src/tokenization``: SentencePiece): ``train`` writes a model from raw text, ``encode`` /
+    ``decode`` use it. Raises ``ImportError`` with the package name when it is missing."""
+
+    def __init__(self, model_file: str | None = None, model_proto: bytes | None = None):
+        import sentencepiece as spm
+        self.sp = spm.SentencePieceProcessor(model_file=model_file, model_proto=model_proto)
+
+    @classmethod
+    def train(cls, texts, vocab_size: int = 256, model_type: str = "unigram", model_prefix: str | None = None, **kw):
+        import io
+        import sentencepiece as spm
+        buf = io.BytesIO()
+        spm.SentencePieceTrainer.train(sentence_iterator=iter(texts), model_writer=buf, vocab_size=vocab_size,
+                                       model_type=model_type, hard_vocab_limit=False, minloglevel=2, **kw)
+        if model_prefix:
+            with open(model_prefix + ".model", "wb") as f:
+                f.write(buf.getvalue())
+        return cls(model_proto=buf.getvalue())
+
+    @property
+    def vocab_size(self) -> int:
+        return self.sp.get_piece_size()
+
+    def encode(self, text: str, add_bos: bool = False, add_eos: bool = False) -> list[int]:
+        ids = self.sp.encode(text)
+        return ([self.sp.bos_id()] if add_bos and self.sp.bos_id() >= 0 else []) + ids + \
+            ([self.sp.eos_id()] if add_eos and self.sp.eos_id() >= 0 else [])
+
+    def decode(self, ids) -> str:
+        return self.sp.decode([int(i) for i in ids])
+
+    def tokenize(self, text: str) -> list[str]:
+        return self.sp.encode(text, out_type=str)
