@@ -510,3 +510,26 @@ def test_sentencepiece_tokenizer_roundtrip():
     tok = SentencePieceTokenizer.train(corpus, vocab_size=60)
     ids = tok.encode("the quick brown dog", add_eos=True)
     assert tok.decode(ids) == "the quick brown dog" and max(ids) < tok.vocab_size and "".join(tok.tokenize("lazy dog")).replace("▁", " ").strip() == "lazy dog"
+
+
+def test_package_ed25519_signature_and_aes_gcm(tmp_path):
+    pytest.importorskip("cryptography")
+    from torsh_b200 import hub
+    sk, pk = hub.generate_signing_key()
+    other_sk, other_pk = hub.generate_signing_key()
+    pkg = hub.Package("demo", "1.2.3")
+    pkg.add_bytes("weights.bin", b"\x00\x01" * 100)
+    pkg.add_source("demo.mod", "VALUE = 41 + 1\n")
+    enc = bytes(range(32))
+    path = str(tmp_path / "demo.tpkg")
+    pkg.save(path, signing_key=sk, encryption_key=enc)
+    back = hub.Package.load(path, public_key=pk, encryption_key=enc)
+    assert back.files["weights.bin"] == b"\x00\x01" * 100 and back.import_module("demo.mod").VALUE == 42
+    with pytest.raises(PermissionError):
+        hub.Package.load(path, public_key=other_pk, encryption_key=enc)
+    with pytest.raises(PermissionError):
+        hub.Package.load(path, public_key=pk)                                  # encrypted, no key given
+    with pytest.raises(PermissionError):
+        hub.Package.load(path, public_key=pk, encryption_key=bytes(32))        # wrong key
+    import zipfile
+    assert b"VALUE" not in zipfile.ZipFile(path).read("code/demo/mod.py")      # contents are sealed

@@ -80,6 +80,41 @@ class LocalHub:
         return m
 
 
+def _ed25519_private(k):
+    from cryptography.hazmat.primitives.asymmetric.ed25519 import Ed25519PrivateKey
+    return k if isinstance(k, Ed25519PrivateKey) else Ed25519PrivateKey.from_private_bytes(bytes(k))
+
+
+def _ed25519_public(k):
+    from cryptography.hazmat.primitives.asymmetric.ed25519 import Ed25519PublicKey
+    return k if isinstance(k, Ed25519PublicKey) else Ed25519PublicKey.from_public_bytes(bytes(k))
+
+
+def generate_signing_key() -> tuple[bytes, bytes]:
+    """New Ed25519 key pair as raw bytes ``(private 32 B, public 32 B)``."""
+    from cryptography.hazmat.primitives import serialization as ser
+    from cryptography.hazmat.primitives.asymmetric.ed25519 import Ed25519PrivateKey
+    sk = Ed25519PrivateKey.generate()
+    return (sk.private_bytes(ser.Encoding.Raw, ser.PrivateFormat.Raw, ser.NoEncryption()),
+            sk.public_key().public_bytes(ser.Encoding.Raw, ser.PublicFormat.Raw))
+
+
+def _seal(key: bytes, name: str, data: bytes) -> bytes:
+    import os as _os
+    from cryptography.hazmat.primitives.ciphers.aead import AESGCM
+    nonce = _os.urandom(12)
+    return nonce + AESGCM(key).encrypt(nonce, data, name.encode())          # the file name is authenticated too
+
+
+def _open(key: bytes, name: str, blob: bytes) -> bytes:
+    from cryptography.exceptions import InvalidTag
+    from cryptography.hazmat.primitives.ciphers.aead import AESGCM
+    try:
+        return AESGCM(key).decrypt(blob[:12], blob[12:], name.encode())
+    except InvalidTag:
+        raise PermissionError(f"{name}: decryption failed (wrong key or modified data)") from None
+
+
 class Package:
     MANIFEST = "MANIFEST.json"
 
@@ -99,17 +134,25 @@ class Package:
         return {"name": self.name, "version": self.version, "dependencies": self.dependencies, "format": 1,
                 "files": {k: {"sha256": hashlib.sha256(v).hexdigest(), "size": len(v)} for k, v in sorted(self.files.items())}}
 
-    def save(self, path, compress: bool = True, key: bytes | None = None) -> None:
-        man = json.dumps(self.manifest(), sort_keys=True).encode()
+    def save(self, path, compress: bool = True, key: bytes | None = None, signing_key=None,
+             encryption_key: bytes | None = None) -> None:
+        """``key``: shared secret for an HMAC-SHA256 signature. ``signing_key``: an Ed25519 private key (object or 32 raw
+        bytes) for a public-key signature over the manifest (``crates/torsh-package``: ed25519). ``encryption_key``:
+        16 / 24 / 32 bytes; file contents are sealed with AES-GCM (the manifest, which holds the plaintext hashes, is not)."""
+        man_d = self.manifest()
+        man_d["encrypted"] = encryption_key is not None
+        man = json.dumps(man_d, sort_keys=True).encode()
         with zipfile.ZipFile(path, "w", zipfile.ZIP_DEFLATED if compress else zipfile.ZIP_STORED) as z:
             z.writestr(self.MANIFEST, man)
             if key is not None:
                 z.writestr("SIGNATURE", hmac.new(key, man, hashlib.sha256).hexdigest())
+            if signing_key is not None:
+                z.writestr("SIGNATURE.ed25519", _ed25519_private(signing_key).sign(man))
             for k, v in self.files.items():
-                z.writestr(k, v)
+                z.writestr(k, _seal(encryption_key, k, v) if encryption_key is not None else v)
 
     @classmethod
-    def load(cls, path, key: bytes | None = None) -> "Package":
+    def load(cls, path, key: bytes | None = None, public_key=None, encryption_key: bytes | None = None) -> "Package":
         with zipfile.ZipFile(path) as z:
             man_raw = z.read(cls.MANIFEST)
             man = json.loads(man_raw)
@@ -117,9 +160,21 @@ class Package:
                 sig = z.read("SIGNATURE").decode() if "SIGNATURE" in z.namelist() else ""
                 if not hmac.compare_digest(sig, hmac.new(key, man_raw, hashlib.sha256).hexdigest()):
                     raise PermissionError("package signature does not verify")
+            if public_key is not None:
+                from cryptography.exceptions import InvalidSignature
+                if "SIGNATURE.ed25519" not in z.namelist():
+                    raise PermissionError("package carries no Ed25519 signature")
+                try:
+                    _ed25519_public(public_key).verify(z.read("SIGNATURE.ed25519"), man_raw)
+                except InvalidSignature:
+                    raise PermissionError("package signature does not verify") from None
+            if man.get("encrypted") and encryption_key is None:
+                raise PermissionError("package is encrypted: an encryption key is needed")
             pkg = cls(man["name"], man["version"], man["dependencies"])
             for k, meta in man["files"].items():
                 data = z.read(k)
+                if man.get("encrypted"):
+                    data = _open(encryption_key, k, data)
                 if hashlib.sha256(data).hexdigest() != meta["sha256"]:
                     raise IOError(f"{k}: checksum mismatch")
                 pkg.files[k] = data
