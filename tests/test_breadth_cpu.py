@@ -533,3 +533,26 @@ def test_package_ed25519_signature_and_aes_gcm(tmp_path):
         hub.Package.load(path, public_key=pk, encryption_key=bytes(32))        # wrong key
     import zipfile
     assert b"VALUE" not in zipfile.ZipFile(path).read("code/demo/mod.py")      # contents are sealed
+
+
+def test_gradient_free_optimizers_minimise_a_quadratic():
+    from torsh_b200.optim import BayesianOptimizer, EvolutionStrategy, NelderMead, RandomSearch
+    target = torch.tensor([1.0, -2.0, 0.5])
+    f = lambda x: float(((x - target) ** 2).sum())
+    nm = NelderMead(torch.zeros(3))
+    for _ in range(200):
+        v = nm.step(f)
+    assert v < 1e-6 and torch.allclose(nm.best_x, target, atol=1e-2)
+    es = EvolutionStrategy(torch.zeros(3), sigma=1.0, seed=1)
+    for _ in range(120):
+        v = es.step(f)
+    assert v < 1e-3
+    rs = RandomSearch(torch.zeros(3), sigma=0.3, seed=2)
+    for _ in range(60):
+        v = rs.step(f)
+    assert v < 0.1
+    bo = BayesianOptimizer([(-3, 3)] * 2, seed=3)
+    g = lambda x: float(((x - torch.tensor([1.0, -1.0])) ** 2).sum())
+    for _ in range(40):
+        v = bo.step(g)
+    assert v < 0.15 and bo.best_x.shape == (2,)
