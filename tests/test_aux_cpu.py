@@ -498,3 +498,24 @@ def test_structured_and_audit_logging_and_degradation(tmp_path):
     gd.add("kernel", lambda x: (calls.append("k"), 1 / 0)[1]).add("torch", lambda x: (calls.append("t"), x + 1)[1])
     assert [gd.run(1), gd.run(2), gd.run(3)] == [2, 3, 4]
     assert calls == ["k", "t", "k", "t", "t"] and gd.used == ["torch"] * 3          # the kernel level is skipped after two failures
+
+
+def test_fairness_metrics_and_experiment_writers(tmp_path):
+    import json, os
+    import torch
+    from torsh_b200.utils import metrics as M
+    pred = torch.tensor([1, 1, 0, 0, 1, 0, 0, 0])
+    group = torch.tensor([0, 0, 0, 0, 1, 1, 1, 1])
+    target = torch.tensor([1, 0, 1, 0, 1, 1, 0, 0])
+    assert abs(M.demographic_parity_difference(pred, group) - 0.25) < 1e-6
+    assert abs(M.disparate_impact_ratio(pred, group) - 0.5) < 1e-6
+    assert abs(M.equalized_odds_difference(pred, target, group) - 0.5) < 1e-6      # FPR 0.5 vs 0.0
+    ml = M.MLflowWriter(str(tmp_path / "mlruns"))
+    ml.log_param("lr", 3e-4); ml.set_tag("model", "gpt2"); ml.log_metric("loss", 2.5, 1); ml.log_metric("loss", 2.0, 2)
+    lines = open(os.path.join(ml.dir, "metrics", "loss")).read().split("\n")
+    assert len(lines) == 3 and lines[1].split()[1:] == ["2.0", "2"] and open(os.path.join(ml.dir, "params", "lr")).read() == "0.0003"
+    assert "run_id: " + ml.run_id in open(os.path.join(ml.dir, "meta.yaml")).read()
+    wb = M.WandbOfflineWriter(str(tmp_path / "wandb"), config={"lr": 1e-3})
+    wb.log({"loss": 1.5}); wb.log({"loss": 1.25, "acc": 0.5})
+    hist = [json.loads(l) for l in open(os.path.join(wb.dir, "wandb-history.jsonl"))]
+    assert [h["_step"] for h in hist] == [1, 2] and json.load(open(os.path.join(wb.dir, "wandb-summary.json")))["acc"] == 0.5

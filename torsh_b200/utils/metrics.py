@@ -125,3 +125,91 @@ class MetricsLogger:
             self._srv.shutdown()
         if self._f:
             self._f.close()
+
+
+# ------------------------------------------------------------------------------------------------------------ fairness
+def demographic_parity_difference(pred: torch.Tensor, group: torch.Tensor) -> float:
+    """Largest gap between groups in the rate of positive predictions (``crates/torsh-metrics``: fairness)."""
+    rates = [pred[group == g].float().mean().item() for g in group.unique()]
+    return max(rates) - min(rates)
+
+
+def equalized_odds_difference(pred: torch.Tensor, target: torch.Tensor, group: torch.Tensor) -> float:
+    """Largest gap between groups in true-positive rate or false-positive rate."""
+    gaps = []
+    for label in (1, 0):
+        rates = []
+        for g in group.unique():
+            m = (group == g) & (target == label)
+            if m.any():
+                rates.append(pred[m].float().mean().item())
+        if rates:
+            gaps.append(max(rates) - min(rates))
+    return max(gaps) if gaps else 0.0
+
+
+def disparate_impact_ratio(pred: torch.Tensor, group: torch.Tensor) -> float:
+    rates = [pred[group == g].float().mean().item() for g in group.unique()]
+    return min(rates) / max(max(rates), 1e-12)
+
+
+# ------------------------------------------------------------------------------------------------- experiment writers
+class MLflowWriter:
+    """Writes the MLflow file-store layout without the mlflow package: ``<root>/<experiment_id>/<run_id>/`` with
+    ``metrics/<key>`` (lines ``timestamp_ms value step``), ``params/<key>``, ``tags/<key>`` and ``meta.yaml`` files, which
+    ``mlflow ui --backend-store-uri <root>`` reads."""
+
+    def __init__(self, root: str, experiment: str = "0", run_name: str = "run"):
+        import os
+        import time
+        import uuid
+        self.run_id = uuid.uuid4().hex
+        self.dir = os.path.join(root, experiment, self.run_id)
+        for sub in ("metrics", "params", "tags", "artifacts"):
+            os.makedirs(os.path.join(self.dir, sub), exist_ok=True)
+        start = int(time.time() * 1000)
+        with open(os.path.join(root, experiment, "meta.yaml"), "w") as f:
+            f.write(f"artifact_location: {os.path.join(root, experiment)}\nexperiment_id: '{experiment}'\nlifecycle_stage: active\nname: Default\n")
+        with open(os.path.join(self.dir, "meta.yaml"), "w") as f:
+            f.write(f"artifact_uri: {os.path.join(self.dir, 'artifacts')}\nend_time: null\nexperiment_id: '{experiment}'\n"
+                    f"lifecycle_stage: active\nrun_id: {self.run_id}\nrun_name: {run_name}\nstart_time: {start}\nstatus: 1\n")
+
+    def _write(self, sub, key, text, mode):
+        import os
+        with open(os.path.join(self.dir, sub, key.replace("/", "_")), mode) as f:
+            f.write(text)
+
+    def log_param(self, key: str, value): self._write("params", key, str(value), "w")
+    def set_tag(self, key: str, value): self._write("tags", key, str(value), "w")
+
+    def log_metric(self, key: str, value: float, step: int = 0):
+        import time
+        self._write("metrics", key, f"{int(time.time() * 1000)} {float(value)} {int(step)}\n", "a")
+
+
+class WandbOfflineWriter:
+    """History and summary files in the layout of an offline W&B run directory (``wandb-history.jsonl``,
+    ``wandb-summary.json``, ``config.yaml``) for later upload or inspection; needs no wandb package."""
+
+    def __init__(self, root: str, project: str = "torsh", config: dict | None = None):
+        import os
+        import time
+        self.dir = os.path.join(root, f"offline-run-{time.strftime('%Y%m%d_%H%M%S')}-{os.getpid()}", "files")
+        os.makedirs(self.dir, exist_ok=True)
+        self.summary, self._step = {}, 0
+        with open(os.path.join(self.dir, "config.yaml"), "w") as f:
+            f.write(f"wandb_project:\n  value: {project}\n")
+            for k, v in (config or {}).items():
+                f.write(f"{k}:\n  value: {v}\n")
+
+    def log(self, metrics: dict, step: int | None = None):
+        import json
+        import os
+        import time
+        self._step = self._step + 1 if step is None else step
+        rec = {**{k: float(v) for k, v in metrics.items()}, "_step": self._step, "_timestamp": time.time()}
+        with open(os.path.join(self.dir, "wandb-history.jsonl"), "a") as f:
+            f.write(json.dumps(rec) + "\n")
+        self.summary.update(rec)
+        with open(os.path.join(self.dir, "wandb-summary.json"), "w") as f:
+            json.dump(self.summary, f)
