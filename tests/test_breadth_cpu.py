@@ -556,3 +556,33 @@ def test_gradient_free_optimizers_minimise_a_quadratic():
     for _ in range(40):
         v = bo.step(g)
     assert v < 0.15 and bo.best_x.shape == (2,)
+
+
+def test_vision_extras():
+    from torsh_b200.vision import extras as X
+    torch.manual_seed(0)
+    conv = torch.nn.Conv2d(3, 8, 3, padding=1)
+    model = torch.nn.Sequential(conv, torch.nn.ReLU(), torch.nn.AdaptiveAvgPool2d(1), torch.nn.Flatten(), torch.nn.Linear(8, 5))
+    x = torch.randn(2, 3, 16, 16)
+    assert X.saliency(model, x).shape == (2, 16, 16)
+    cam = X.GradCAM(model, conv)
+    m = cam(x)
+    cam.close()
+    assert m.shape == (2, 16, 16) and float(m.min()) >= 0 and float(m.max()) <= 1.0 + 1e-6
+    tgt = torch.tensor([1, 3])
+    ig = X.integrated_gradients(model, x, tgt, steps=64)
+    diff = model(x).gather(1, tgt[:, None])[:, 0] - model(torch.zeros_like(x)).gather(1, tgt[:, None])[:, 0]
+    assert torch.allclose(ig.flatten(1).sum(1), diff.detach(), atol=2e-2)                     # completeness
+    video = torch.arange(12.0).view(12, 1, 1, 1).expand(12, 3, 4, 4)
+    assert X.sample_frames(video, 4)[:, 0, 0, 0].tolist() == [1.0, 4.0, 7.0, 10.0] and float(X.frame_difference(video).mean()) == 1.0
+    assert X.Conv3dClassifier(7, 4)(torch.randn(2, 3, 4, 16, 16)).shape == (2, 7)
+    lo = torch.rand(1, 3, 8, 8)
+    assert X.SRCNN(2)(lo).shape == (1, 3, 16, 16) and X.ESPCN(3)(lo).shape == (1, 3, 24, 24) and X.psnr(lo, lo) == float("inf")
+    feats = torch.nn.Sequential(torch.nn.Conv2d(3, 4, 3, padding=1), torch.nn.ReLU(), torch.nn.Conv2d(4, 4, 3, padding=1), torch.nn.ReLU())
+    crit = X.StyleTransferLoss(feats)
+    img = torch.rand(1, 3, 8, 8, requires_grad=True)
+    total, cl, sl = crit(img, torch.rand(1, 3, 8, 8), torch.rand(1, 3, 8, 8))
+    total.backward()
+    assert img.grad is not None and float(cl) > 0 and float(sl) > 0
+    same, c0, s0 = crit(img.detach(), img.detach(), img.detach())
+    assert float(same) < 1e-10
