@@ -586,3 +586,18 @@ def test_vision_extras():
     assert img.grad is not None and float(cl) > 0 and float(sl) > 0
     same, c0, s0 = crit(img.detach(), img.detach(), img.detach())
     assert float(same) < 1e-10
+
+
+def test_dsr_and_rle_sparse_formats():
+    from torsh_b200.sparse import DsrTensor, RleTensor
+    d = torch.tensor([[0.0, 2.0, 0.0], [0.0, 0.0, 0.0], [1.0, 0.0, 3.0]])
+    dsr = DsrTensor.from_dense(d)
+    assert dsr.nnz() == 3 and dsr.get(2, 2) == 3.0 and torch.equal(dsr.to_dense(), d)
+    dsr.set(1, 1, 5.0); dsr.set(0, 1, 0.0)
+    assert dsr.nnz() == 3 and dsr.get(1, 1) == 5.0 and torch.equal(dsr.to_csr().to_dense(), dsr.to_dense())
+    assert torch.allclose(dsr.matmul(torch.ones(3)), dsr.to_dense().sum(1))
+    mask = torch.zeros(8, 8, dtype=torch.int64)
+    mask[2:5, :] = 7
+    rle = RleTensor.from_dense(mask)
+    assert rle.values.tolist() == [0, 7, 0] and rle.lengths.tolist() == [16, 24, 24] and torch.equal(rle.to_dense(), mask)
+    assert rle.compression_ratio() > 10

@@ -167,6 +167,76 @@ class EllTensor:
         return out
 
 
+class DsrTensor:
+    """Dynamic sparse rows (``crates/torsh-sparse``: DSR): one ``{column: value}`` map per row, cheap to update in place
+    while a pattern is being built; convert to CSR for arithmetic."""
+
+    def __init__(self, shape: tuple[int, int], dtype=torch.float32):
+        self.shape, self.dtype = tuple(shape), dtype
+        self.rows: list[dict[int, float]] = [dict() for _ in range(shape[0])]
+
+    @staticmethod
+    def from_dense(d: torch.Tensor) -> "DsrTensor":
+        out = DsrTensor(tuple(d.shape), d.dtype)
+        for r, c in (d != 0).nonzero().tolist():
+            out.rows[r][c] = float(d[r, c])
+        return out
+
+    def set(self, r: int, c: int, v: float):
+        if v == 0:
+            self.rows[r].pop(c, None)
+        else:
+            self.rows[r][c] = float(v)
+
+    def get(self, r: int, c: int) -> float:
+        return self.rows[r].get(c, 0.0)
+
+    def nnz(self) -> int:
+        return sum(len(r) for r in self.rows)
+
+    def to_dense(self) -> torch.Tensor:
+        out = torch.zeros(self.shape, dtype=self.dtype)
+        for r, row in enumerate(self.rows):
+            for c, v in row.items():
+                out[r, c] = v
+        return out
+
+    def to_csr(self) -> "CsrTensor":
+        return CooTensor.from_dense(self.to_dense()).to_csr()
+
+    def matmul(self, b: torch.Tensor) -> torch.Tensor:
+        return self.to_dense().to(b.dtype) @ b
+
+
+@dataclass
+class RleTensor:
+    """Run-length encoding of a flattened tensor (``crates/torsh-sparse``: RLE): pairs of (value, run length); compact for
+    masks and label maps with long constant runs."""
+    values: torch.Tensor
+    lengths: torch.Tensor
+    shape: tuple
+
+    @staticmethod
+    def from_dense(d: torch.Tensor) -> "RleTensor":
+        flat = d.reshape(-1)
+        if flat.numel() == 0:
+            return RleTensor(flat, torch.zeros(0, dtype=torch.int64), tuple(d.shape))
+        change = torch.ones(flat.numel(), dtype=torch.bool)
+        change[1:] = flat[1:] != flat[:-1]
+        starts = change.nonzero()[:, 0]
+        lengths = torch.diff(torch.cat([starts, torch.tensor([flat.numel()])]))
+        return RleTensor(flat[starts], lengths, tuple(d.shape))
+
+    def to_dense(self) -> torch.Tensor:
+        return torch.repeat_interleave(self.values, self.lengths).reshape(self.shape)
+
+    def compression_ratio(self) -> float:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n / max(self.values.numel() * 2, 1)
+
+
 class SparseLinear(torch.nn.Module):
     """Linear layer whose weight is held as COO non-zeros (trainable values, fixed pattern)."""
 
