@@ -601,3 +601,13 @@ def test_dsr_and_rle_sparse_formats():
     rle = RleTensor.from_dense(mask)
     assert rle.values.tolist() == [0, 7, 0] and rle.lengths.tolist() == [16, 24, 24] and torch.equal(rle.to_dense(), mask)
     assert rle.compression_ratio() > 10
+
+
+def test_weight_gradient_plan_picks_stream_k_only_for_badly_filled_waves():
+    from torsh_b200.ops.linear import _wgrad_plan
+    # (output rows, output cols, K) -> (tile width, split): -1 = stream-K
+    assert _wgrad_plan(4096, 1024, 8192) == (256, -1)        # 128 tiles x 2 splits fill 256 of 296 slots
+    assert _wgrad_plan(1024, 1024, 8192) == (256, -1)        # 32 tiles x 4 splits fill 128 of 148
+    assert _wgrad_plan(3072, 1024, 8192) == (256, 3)         # 96 x 3 = 288 of 296: uniform splits are fine
+    assert _wgrad_plan(50304, 1024, 8192) == (256, 1)        # many tiles per CTA: keep round-robin tiles (L2 reuse)
+    assert _wgrad_plan(64, 64, 256)[1] == 1                  # short K: no split at all
