@@ -611,3 +611,25 @@ def test_weight_gradient_plan_picks_stream_k_only_for_badly_filled_waves():
     assert _wgrad_plan(3072, 1024, 8192) == (256, 3)         # 96 x 3 = 288 of 296: uniform splits are fine
     assert _wgrad_plan(50304, 1024, 8192) == (256, 1)        # many tiles per CTA: keep round-robin tiles (L2 reuse)
     assert _wgrad_plan(64, 64, 256)[1] == 1                  # short K: no split at all
+
+
+def test_tabular_and_audio_datasets(tmp_path):
+    from torsh_b200.data import AudioDataset, TabularDataset
+    cols = {"age": [20, 30, 40, 50], "income": [1.0, 2.0, 3.0, 4.0], "city": ["a", "b", "a", "c"], "y": [0, 1, 0, 1]}
+    ds = TabularDataset(cols, "y", categorical=["city"])
+    num, cat, y = ds[2]
+    assert len(ds) == 4 and num.shape == (2,) and cat.tolist() == [0] and int(y) == 0 and ds.cardinalities() == [3]
+    assert torch.allclose(ds.num.mean(0), torch.zeros(2), atol=1e-6) and torch.allclose(ds.num.std(0, unbiased=False), torch.ones(2), atol=1e-5)
+    p = tmp_path / "t.csv"
+    p.write_text("age,city,y\n20,a,0\n30,b,1\n")
+    assert len(TabularDataset.from_csv(str(p), "y", categorical=["city"])) == 2
+    import pyarrow as pa, pyarrow.parquet as pq
+    pq.write_table(pa.table(cols), str(tmp_path / "t.parquet"))
+    assert TabularDataset.from_parquet(str(tmp_path / "t.parquet"), "y", categorical=["city"]).cardinalities() == [3]
+    au = AudioDataset.synthetic(8, classes=3, num_samples=1024, n_fft=256)
+    spec, label = au[0]
+    assert spec.shape[0] == 129 and 0 <= label < 3
+    peak = spec.mean(1).argmax().item() * 8000 / 256
+    assert abs(peak - 220.0 * (label + 1)) < 40                               # the spectrogram peaks at the class's tone
+    raw = AudioDataset([torch.ones(10)], [1], num_samples=16)
+    assert raw[0][0].shape == (16,) and float(raw[0][0][12]) == 0.0

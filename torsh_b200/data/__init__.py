@@ -199,3 +199,87 @@ class PrefetchToDevice:
 
 def collate(batch):
     return default_collate(batch)
+
+
+# ----------------------------------------------------------------------------------------- tabular / audio / columnar
+class TabularDataset(Dataset):
+    """Rows of numeric and categorical columns (``crates/torsh-data``: tabular datasets): numeric columns are
+    standardised with statistics of the data given at construction, categorical ones mapped to integer codes.
+    ``__getitem__`` returns ``(numeric [F], categorical [C], target)``."""
+
+    def __init__(self, columns: dict, target: str, categorical=(), standardize: bool = True):
+        self.target_name, self.categorical = target, list(categorical)
+        self.numeric = [c for c in columns if c != target and c not in self.categorical]
+        n = len(columns[target])
+        num = torch.tensor([[float(columns[c][i]) for c in self.numeric] for i in range(n)], dtype=torch.float32).reshape(n, len(self.numeric))
+        self.mean = num.mean(0) if standardize and n else torch.zeros(len(self.numeric))
+        self.std = num.std(0, unbiased=False).clamp(min=1e-8) if standardize and n else torch.ones(len(self.numeric))
+        self.num = (num - self.mean) / self.std
+        self.vocab = {c: {v: i for i, v in enumerate(sorted(set(columns[c]), key=str))} for c in self.categorical}
+        self.cat = torch.tensor([[self.vocab[c][columns[c][i]] for c in self.categorical] for i in range(n)],
+                                dtype=torch.int64).reshape(n, len(self.categorical))
+        t = columns[target]
+        self.y = torch.tensor(t) if not isinstance(t, torch.Tensor) else t
+
+    @classmethod
+    def from_csv(cls, path: str, target: str, categorical=(), **kw):
+        import csv
+        with open(path, newline="") as f:
+            rows = list(csv.DictReader(f))
+        cols = {k: [r[k] for r in rows] for k in rows[0]}
+        for k in cols:
+            if k not in categorical:
+                cols[k] = [float(v) for v in cols[k]]
+        return cls(cols, target, categorical, **kw)
+
+    @classmethod
+    def from_parquet(cls, path: str, target: str, categorical=(), **kw):
+        import pyarrow.parquet as pq
+        table = pq.read_table(path)
+        return cls({name: table.column(name).to_pylist() for name in table.column_names}, target, categorical, **kw)
+
+    def cardinalities(self) -> list[int]:
+        return [len(self.vocab[c]) for c in self.categorical]
+
+    def __len__(self):
+        return len(self.y)
+
+    def __getitem__(self, i):
+        return self.num[i], self.cat[i], self.y[i]
+
+
+class AudioDataset(Dataset):
+    """Waveforms with labels (``crates/torsh-data``: audio datasets): clips are cropped or zero-padded to ``num_samples``
+    and optionally turned into log-mel-free log-magnitude spectrograms (``n_fft``, ``hop``). Sources are in-memory tensors
+    or ``.npy`` files; ``synthetic`` makes labelled sine mixtures for tests and examples."""
+
+    def __init__(self, waveforms, labels, sample_rate: int = 16000, num_samples: int | None = None, n_fft: int | None = None,
+                 hop: int | None = None):
+        self.items, self.labels, self.sr = list(waveforms), list(labels), sample_rate
+        self.num_samples, self.n_fft, self.hop = num_samples, n_fft, hop or (n_fft // 4 if n_fft else None)
+
+    @classmethod
+    def synthetic(cls, n: int = 32, classes: int = 4, sample_rate: int = 8000, seconds: float = 0.25, seed: int = 0, **kw):
+        g = torch.Generator().manual_seed(seed)
+        t = torch.arange(int(sample_rate * seconds)) / sample_rate
+        labels = torch.randint(0, classes, (n,), generator=g).tolist()
+        waves = [torch.sin(2 * torch.pi * (220.0 * (c + 1)) * t) + 0.05 * torch.randn(t.shape, generator=g) for c in labels]
+        return cls(waves, labels, sample_rate, **kw)
+
+    def _load(self, item):
+        if isinstance(item, str):
+            import numpy as np
+            return torch.from_numpy(np.load(item)).float()
+        return item.float()
+
+    def __len__(self):
+        return len(self.items)
+
+    def __getitem__(self, i):
+        w = self._load(self.items[i]).reshape(-1)
+        if self.num_samples is not None:
+            w = w[: self.num_samples] if w.numel() >= self.num_samples else torch.nn.functional.pad(w, (0, self.num_samples - w.numel()))
+        if self.n_fft:
+            spec = torch.stft(w, self.n_fft, self.hop, window=torch.hann_window(self.n_fft), return_complex=True).abs()
+            w = torch.log1p(spec)
+        return w, self.labels[i]
