@@ -246,3 +246,33 @@ def test_backend_capabilities_hints_and_autotuner(tmp_path):
     assert tuner.select("gemm/8192x1024x4096", cands) == "bn256" and len(calls) == 2          # cached
     again = B.Autotuner(str(tmp_path / "tune.json"), timer=lambda fn: 1 / 0)
     assert again.select("gemm/8192x1024x4096", cands) == "bn256"                               # loaded from the file
+
+
+def test_native_token_loader_is_deterministic_and_in_order(tmp_path):
+    import numpy as np
+    import torch
+    from torsh_b200.data import NativeTokenLoader
+    tokens = np.arange(5000, dtype=np.uint16)
+    path = tmp_path / "tokens.bin"
+    tokens.tofile(path)
+
+    def take(n, **kw):
+        ld = NativeTokenLoader(str(path), batch=4, seq=16, slots=3, workers=3, seed=7, pin=False, **kw)
+        out = []
+        for _ in range(n):
+            x, y = next(ld)
+            out.append((ld.batch_number, x.clone(), y.clone()))
+        count = ld.num_tokens
+        ld.close()
+        return out, count
+    a, count = take(10)
+    b, _ = take(10)
+    other, _ = take(3, rank=1)
+    assert count == 5000 and [n for n, _, _ in a] == list(range(10))
+    for (_, xa, ya), (_, xb, yb) in zip(a, b):
+        assert torch.equal(xa, xb) and torch.equal(ya, yb)
+    x0, y0 = a[0][1], a[0][2]
+    assert x0.shape == (4, 16) and torch.equal(y0[:, :-1], x0[:, 1:]) and torch.equal(y0, x0 + 1)     # windows of arange
+    assert not torch.equal(other[0][1], x0)                                                           # ranks draw different windows
+    with pytest.raises(OSError):
+        NativeTokenLoader(str(tmp_path / "missing.bin"), batch=1, seq=4, pin=False)

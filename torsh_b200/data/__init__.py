@@ -283,3 +283,67 @@ class AudioDataset(Dataset):
             spec = torch.stft(w, self.n_fft, self.hop, window=torch.hann_window(self.n_fft), return_complex=True).abs()
             w = torch.log1p(spec)
         return w, self.labels[i]
+
+
+class NativeTokenLoader:
+    """Batches of token windows cut from a memory-mapped token file by native worker threads
+    (``csrc/host/token_loader.cpp``): ``[batch, seq + 1]`` int64 windows land in a ring of (pinned, when a GPU is
+    present) host buffers; iteration yields ``(inputs, targets)`` views of the current buffer, which stays valid until the
+    next batch is requested. Deterministic in ``(seed, rank)``; ranks read disjoint random streams."""
+
+    def __init__(self, path: str, batch: int, seq: int, token_bytes: int = 2, slots: int = 4, workers: int = 2, seed: int = 0,
+                 rank: int = 0, world: int = 1, pin: bool | None = None, timeout_s: float = 30.0):
+        import ctypes
+
+        from .. import _native as nv
+        self.lib = nv.host()
+        L = self.lib
+        L.tsh_tokens_open.restype = ctypes.c_void_p
+        L.tsh_tokens_open.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                      ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_ulonglong, ctypes.c_int, ctypes.c_int]
+        L.tsh_tokens_next.argtypes = [ctypes.c_void_p, ctypes.c_double, ctypes.POINTER(ctypes.c_longlong)]
+        L.tsh_tokens_release.argtypes = [ctypes.c_void_p, ctypes.c_int]
+        L.tsh_tokens_count.restype, L.tsh_tokens_count.argtypes = ctypes.c_longlong, [ctypes.c_void_p]
+        L.tsh_tokens_filled.restype, L.tsh_tokens_filled.argtypes = ctypes.c_longlong, [ctypes.c_void_p]
+        L.tsh_tokens_close.argtypes = [ctypes.c_void_p]
+        pin = torch.cuda.is_available() if pin is None else pin
+        self.buffers = [torch.zeros(batch, seq + 1, dtype=torch.int64) for _ in range(slots)]
+        if pin:
+            self.buffers = [b.pin_memory() for b in self.buffers]
+        ptrs = (ctypes.c_void_p * slots)(*[b.data_ptr() for b in self.buffers])
+        self.h = L.tsh_tokens_open(str(path).encode(), token_bytes, batch, seq, slots, ptrs, workers, seed, rank, world)
+        if not self.h:
+            L.tsh_last_error.restype = ctypes.c_char_p
+            raise OSError((L.tsh_last_error() or b"token loader: open failed").decode())
+        self.timeout_s, self._held, self.batch_number = timeout_s, None, -1
+
+    @property
+    def num_tokens(self) -> int:
+        return self.lib.tsh_tokens_count(self.h)
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        import ctypes
+        if self._held is not None:
+            self.lib.tsh_tokens_release(self.h, self._held)
+            self._held = None
+        n = ctypes.c_longlong()
+        slot = self.lib.tsh_tokens_next(self.h, self.timeout_s, ctypes.byref(n))
+        if slot < 0:
+            raise TimeoutError(f"no batch within {self.timeout_s}s")
+        self._held, self.batch_number = slot, n.value
+        buf = self.buffers[slot]
+        return buf[:, :-1], buf[:, 1:]
+
+    def close(self):
+        if getattr(self, "h", None):
+            self.lib.tsh_tokens_close(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
