@@ -27,6 +27,8 @@ def test_single_process_examples(tmp_path):
     assert out.tolist() == [3.0, 3.0, 3.0] and losses[-1] < 0.05 * losses[0]
     assert _load("mnist").main(["--epochs", "2", "--samples", "256"])[-1] > 0.5
     assert _load("stream_management").main([]) in ("cpu", "cuda")
+    losses = _load("train_from_tokens").main(["--steps", "10"])
+    assert len(losses) == 10 and losses[-1] < losses[0] - 1.0
 
 
 def test_two_rank_examples_gloo():

@@ -288,14 +288,18 @@ class AudioDataset(Dataset):
 class NativeTokenLoader:
     """Batches of token windows cut from a memory-mapped token file by native worker threads
     (``csrc/host/token_loader.cpp``): ``[batch, seq + 1]`` int64 windows land in a ring of (pinned, when a GPU is
-    present) host buffers; iteration yields ``(inputs, targets)`` views of the current buffer, which stays valid until the
-    next batch is requested. Deterministic in ``(seed, rank)``; ranks read disjoint random streams."""
+    present) host buffers; iteration yields ``(inputs, targets)`` views of the current buffer. A buffer goes back to the
+    workers ``hold`` batches later (default 1: it stays valid until the call after the next one), which covers an
+    asynchronous host→device copy of a training loop that keeps one step in flight. Deterministic in ``(seed, rank)``;
+    ranks read disjoint random streams."""
 
     def __init__(self, path: str, batch: int, seq: int, token_bytes: int = 2, slots: int = 4, workers: int = 2, seed: int = 0,
-                 rank: int = 0, world: int = 1, pin: bool | None = None, timeout_s: float = 30.0):
+                 rank: int = 0, world: int = 1, pin: bool | None = None, timeout_s: float = 30.0, hold: int = 1):
         import ctypes
 
         from .. import _native as nv
+        if slots < hold + 2:
+            raise ValueError(f"slots ({slots}) must be at least hold + 2 ({hold + 2})")
         self.lib = nv.host()
         L = self.lib
         L.tsh_tokens_open.restype = ctypes.c_void_p
@@ -315,7 +319,7 @@ class NativeTokenLoader:
         if not self.h:
             L.tsh_last_error.restype = ctypes.c_char_p
             raise OSError((L.tsh_last_error() or b"token loader: open failed").decode())
-        self.timeout_s, self._held, self.batch_number = timeout_s, None, -1
+        self.timeout_s, self._held, self.batch_number, self.hold = timeout_s, [], -1, hold
 
     @property
     def num_tokens(self) -> int:
@@ -326,14 +330,14 @@ class NativeTokenLoader:
 
     def __next__(self):
         import ctypes
-        if self._held is not None:
-            self.lib.tsh_tokens_release(self.h, self._held)
-            self._held = None
+        while len(self._held) > self.hold:
+            self.lib.tsh_tokens_release(self.h, self._held.pop(0))
         n = ctypes.c_longlong()
         slot = self.lib.tsh_tokens_next(self.h, self.timeout_s, ctypes.byref(n))
         if slot < 0:
             raise TimeoutError(f"no batch within {self.timeout_s}s")
-        self._held, self.batch_number = slot, n.value
+        self._held.append(slot)
+        self.batch_number = n.value
         buf = self.buffers[slot]
         return buf[:, :-1], buf[:, 1:]
 
