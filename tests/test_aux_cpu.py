@@ -519,3 +519,24 @@ def test_fairness_metrics_and_experiment_writers(tmp_path):
     wb.log({"loss": 1.5}); wb.log({"loss": 1.25, "acc": 0.5})
     hist = [json.loads(l) for l in open(os.path.join(wb.dir, "wandb-history.jsonl"))]
     assert [h["_step"] for h in hist] == [1, 2] and json.load(open(os.path.join(wb.dir, "wandb-summary.json")))["acc"] == 0.5
+
+
+def test_bench_clock_sampler_windows():
+    import os, sys, time
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import bench
+    s = bench.ClockSampler(0)
+    assert s.window(0, 1)["reasons"] == ["nvidia-smi unavailable"]                 # never started
+    s.proc = type("P", (), {"terminate": lambda self: None})()
+    now = time.perf_counter()
+    s.lines = [(now - 1.0, "0, 1900, 1965, 800, Not Active, Not Active, Not Active, Active"),
+               (now, "0, 1800, 1965, 900, Not Active, Not Active, Not Active, Not Active"),
+               (now, "garbage")]
+    first, second = s.window(now - 2, now - 0.5), s.window(now - 0.5, now + 1)
+    assert (first["sm_mhz"], first["reasons"], first["samples"]) == (1900.0, ["sw_power_cap"], 1)
+    assert (second["sm_mhz"], second["reasons"], second["sm_max_mhz"]) == (1800.0, [], 1965.0)
+    assert s.stop()["samples"] == 2
+    import json, subprocess
+    out = subprocess.run([sys.executable, os.path.join(os.path.dirname(bench.__file__), "bench.py"), "--impl", "reference"],
+                         capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0 and json.loads(out.stdout.strip().splitlines()[-1])["impl"] == "reference"
