@@ -2,6 +2,7 @@
 // runs its workers against a consumer, and the TCP-store-free pieces are created and destroyed concurrently. Built and
 // run by tests/test_native_tsan_cpu.py with -fsanitize=thread; any data race makes the program exit non-zero.
 #include <atomic>
+#include <chrono>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -26,7 +27,16 @@ void tsh_store_client_close(void* h);
 int tsh_store_set(void* h, const char* key, const uint8_t* val, uint64_t n, int64_t ttl_secs);
 int tsh_store_add(void* h, const char* key, int64_t delta, int64_t* result);
 int tsh_store_wait(void* h, const char** keys, int nkeys, int timeout_ms);
+void* tsh_watchdog_start(int rank, int world, double interval_s, double timeout_s, void (*publish)(int, long long, void*),
+                         long long (*read)(int, void*), void* ctx);
+int tsh_watchdog_failed(void* h, int* out);
+long long tsh_watchdog_beats(void* h);
+void tsh_watchdog_stop(void* h);
 }
+
+static std::atomic<long long> g_beats[2];
+static void publish_beat(int rank, long long c, void*) { g_beats[rank].store(c); }
+static long long read_beat(int rank, void*) { return g_beats[rank].load() ? g_beats[rank].load() : -1; }
 
 int main(int argc, char** argv) {
   if (argc < 2) return 2;
@@ -97,6 +107,17 @@ int main(int argc, char** argv) {
     });
   for (auto& t : cs) t.join();
   tsh_store_server_stop(srv);
+  // ---- watchdog: two ranks beat through shared counters; rank 1 stops and rank 0 must report it as failed
+  void* w0 = tsh_watchdog_start(0, 2, 0.01, 0.15, publish_beat, read_beat, nullptr);
+  void* w1 = tsh_watchdog_start(1, 2, 0.01, 0.15, publish_beat, read_beat, nullptr);
+  std::this_thread::sleep_for(std::chrono::milliseconds(100));
+  int failed[2] = {0, 0};
+  if (tsh_watchdog_failed(w0, failed) != 0) bad++;                  // nobody has failed yet
+  tsh_watchdog_stop(w1);
+  std::this_thread::sleep_for(std::chrono::milliseconds(400));
+  if (tsh_watchdog_failed(w0, failed) != 1 || failed[1] != 1) bad++;
+  if (tsh_watchdog_beats(w0) < 10) bad++;
+  tsh_watchdog_stop(w0);
   std::printf("host race check: %d inconsistencies\n", bad.load());
   return bad.load() ? 1 : 0;
 }

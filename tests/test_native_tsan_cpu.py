@@ -14,7 +14,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def test_host_runtime_has_no_data_races_under_tsan(tmp_path):
     exe = str(tmp_path / "host_race_check")
     srcs = [os.path.join(ROOT, "tests", "native", "host_race_check.cpp"), os.path.join(ROOT, "csrc", "host", "mempool.cpp"),
-            os.path.join(ROOT, "csrc", "host", "token_loader.cpp"), os.path.join(ROOT, "csrc", "host", "tcp_store.cpp")]
+            os.path.join(ROOT, "csrc", "host", "token_loader.cpp"), os.path.join(ROOT, "csrc", "host", "tcp_store.cpp"),
+            os.path.join(ROOT, "csrc", "host", "watchdog.cpp")]
     cmd = ["g++", "-std=c++17", "-O1", "-g", "-fsanitize=thread", "-pthread", "-I", os.path.join(ROOT, "csrc", "include"),
            "-I", os.path.join(ROOT, "csrc", "host"), *srcs, "-o", exe]
     build = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
