@@ -24,9 +24,15 @@ def sha256_file(path) -> str:
     return h.hexdigest()
 
 
+def default_hub_dir() -> Path:
+    """``TORSH_HUB_DIR``, else ``TORSH_MODEL_CACHE``, else ``~/.cache/torsh/hub`` (the reference's environment names)."""
+    import os
+    return Path(os.environ.get("TORSH_HUB_DIR") or os.environ.get("TORSH_MODEL_CACHE") or Path.home() / ".cache" / "torsh" / "hub")
+
+
 class LocalHub:
-    def __init__(self, root):
-        self.root = Path(root)
+    def __init__(self, root=None):
+        self.root = Path(root) if root is not None else default_hub_dir()
         self.root.mkdir(parents=True, exist_ok=True)
         self.index_path = self.root / "index.json"
 
