@@ -441,3 +441,48 @@ def test_context_parallel_attention_matches_full_attention(world):
     for p in procs:
         p.join(30)
     assert sorted(res) == [(r, True) for r in range(world)]
+
+
+def _zero1_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torsh_b200.optim.distributed import ZeroRedundancyOptimizer
+        torch.manual_seed(0)
+        make = lambda: torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Tanh(), torch.nn.Linear(16, 4))
+        model, ref = make(), make()
+        ref.load_state_dict(model.state_dict())
+        opt = ZeroRedundancyOptimizer(model.parameters(), torch.optim.Adam, lr=1e-2)
+        ref_opt = torch.optim.Adam(ref.parameters(), lr=1e-2)
+        for step in range(4):
+            xs = [torch.randn(6, 8, generator=torch.Generator().manual_seed(100 * step + r)) for r in range(world)]
+            opt.zero_grad()
+            model(xs[rank]).pow(2).mean().backward()
+            for p in model.parameters():                      # what DDP would have done
+                dist.all_reduce(p.grad)
+                p.grad.div_(world)
+            opt.step()
+            ref_opt.zero_grad()
+            (sum(ref(x).pow(2).mean() for x in xs) / world).backward()
+            ref_opt.step()
+        ok = all(torch.allclose(a, b, atol=1e-6) for a, b in zip(model.parameters(), ref.parameters()))
+        total_state = sum(2 * p.numel() * 4 for p in model.parameters())
+        ok &= 0 < opt.state_bytes() < total_state                       # this rank holds only its share of the moments
+        ok &= sorted(opt.consolidate_state_dict()) == list(range(len(list(model.parameters()))))
+        ok &= sum(opt.partition_sizes) == sum(p.numel() for p in model.parameters())
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_zero_redundancy_optimizer_matches_plain_adam():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_zero1_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(30)
+    assert sorted(res) == [(0, True), (1, True)]

@@ -104,3 +104,69 @@ class ElasticAveragingSGD:
     def zero_grad(self):
         for p in self.params:
             p.grad = None
+
+
+class ZeroRedundancyOptimizer:
+    """Optimizer-state sharding (ZeRO stage 1 / FairScale OSS; the reference's ``ShardGradOp`` bookkeeping in
+    ``crates/torsh-distributed/src/fsdp.rs:72-81``): parameters are dealt to ranks greedily by size, every rank builds the
+    inner optimizer over its own share only (so Adam moments exist once across the group), and after ``step`` each
+    owner broadcasts its updated parameters as one flat message. Gradients must already be averaged (DDP)."""
+
+    def __init__(self, params, optimizer_class, group=None, **defaults):
+        self.group = group
+        self.params = [p for p in params if p.requires_grad]
+        self.world = _world(group)
+        self.rank = dist.get_rank(group) if self.world > 1 else 0
+        order = sorted(range(len(self.params)), key=lambda i: -self.params[i].numel())
+        load = [0] * self.world
+        self.owner = [0] * len(self.params)
+        for i in order:                                   # largest first onto the least loaded rank
+            r = min(range(self.world), key=lambda k: load[k])
+            self.owner[i] = r
+            load[r] += self.params[i].numel()
+        self.partition_sizes = load
+        mine = [p for p, o in zip(self.params, self.owner) if o == self.rank]
+        # a rank that owns nothing still needs a valid optimizer object
+        self.inner = optimizer_class(mine if mine else [torch.zeros(1, requires_grad=True)], **defaults)
+        self.param_groups = self.inner.param_groups
+
+    def zero_grad(self, set_to_none: bool = True):
+        for p in self.params:
+            if set_to_none:
+                p.grad = None
+            elif p.grad is not None:
+                p.grad.zero_()
+
+    @torch.no_grad()
+    def step(self):
+        self.inner.step()
+        if self.world == 1:
+            return
+        for r in range(self.world):
+            owned = [p for p, o in zip(self.params, self.owner) if o == r]
+            if not owned:
+                continue
+            flat = torch.cat([p.detach().reshape(-1) for p in owned])
+            dist.broadcast(flat, src=dist.get_global_rank(self.group, r) if self.group is not None else r, group=self.group)
+            if r != self.rank:
+                off = 0
+                for p in owned:
+                    p.copy_(flat[off:off + p.numel()].view_as(p))
+                    off += p.numel()
+
+    def state_bytes(self) -> int:
+        """Bytes of optimizer state held by THIS rank."""
+        return sum(v.numel() * v.element_size() for st in self.inner.state.values() for v in st.values() if isinstance(v, torch.Tensor))
+
+    def consolidate_state_dict(self) -> dict:
+        """Gather every rank's shard of the optimizer state on all ranks (for checkpointing)."""
+        mine = {i: {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in self.inner.state.get(p, {}).items()}
+                for i, (p, o) in enumerate(zip(self.params, self.owner)) if o == self.rank}
+        if self.world == 1:
+            return mine
+        out = [None] * self.world
+        dist.all_gather_object(out, mine, group=self.group)
+        merged = {}
+        for part in out:
+            merged.update(part)
+        return merged

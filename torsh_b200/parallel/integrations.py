@@ -50,7 +50,7 @@ def from_deepspeed(cfg) -> TrainingPlan:
     plan.sharding = {0: "no_shard", 1: "shard_grad_op", 2: "shard_grad_op", 3: "full_shard"}[stage]
     plan.strategy = "ddp" if stage == 0 else "fsdp"
     if stage == 1:
-        plan.notes.append("ZeRO-1 (optimizer-state sharding only) runs as shard_grad_op")
+        plan.notes.append("ZeRO-1 (optimizer-state sharding only): DDP + optim.distributed.ZeroRedundancyOptimizer")
     off = (z.get("offload_optimizer", {}).get("device", "none") != "none") or (z.get("offload_param", {}).get("device", "none") != "none")
     plan.cpu_offload = off
     if off:
