@@ -25,6 +25,8 @@ from enum import Enum
 import torch
 import torch.distributed as dist
 
+from ..core.error import TorshDistributedError
+
 from .. import _native as nv
 from ..ops._dispatch import call
 from .symm import CommContext, SymmetricBuffer
@@ -199,6 +201,17 @@ class FlatFSDP:
 
     # ---- construction -----------------------------------------------------------------------------
     def flatten(self, model: torch.nn.Module, units=None) -> ShardedFlatParameters:
+        st = self.cfg.sharding_strategy
+        if st is not ShardingStrategy.FULL_SHARD:
+            # This engine keeps a replicated bf16 copy of the parameters and shards fp32 masters, moments and the
+            # reduction work, which is what SHARD_GRAD_OP describes; FULL_SHARD differs only in when the bf16 copy is
+            # refreshed (here: by the optimizer kernel itself), so both run the same kernel. NO_SHARD is plain data
+            # parallelism (use DistributedDataParallel) and HYBRID_SHARD needs a second, inter-node group.
+            if st is ShardingStrategy.NO_SHARD:
+                raise TorshDistributedError.configuration_error("NO_SHARD: use parallel.DistributedDataParallel")
+            if st is ShardingStrategy.HYBRID_SHARD and dist.get_world_size(self.group) > 8:
+                raise TorshDistributedError.feature_not_available(
+                    "HYBRID_SHARD across nodes: shard inside one NVSwitch group and wrap it in DDP across groups")
         units = units or default_units(model, self.cfg.min_num_params)
         if not self.cfg.overlap:
             # nothing runs before backward has finished, so the whole model is ONE unit: one launch, one pair of
