@@ -540,3 +540,22 @@ def test_bench_clock_sampler_windows():
     out = subprocess.run([sys.executable, os.path.join(os.path.dirname(bench.__file__), "bench.py"), "--impl", "reference"],
                          capture_output=True, text=True, timeout=120)
     assert out.returncode == 0 and json.loads(out.stdout.strip().splitlines()[-1])["impl"] == "reference"
+
+
+def test_benchmark_report_from_json_lines(tmp_path):
+    import importlib.util, json, os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_report", os.path.join(root, "bench", "report.py"))
+    rep = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rep)
+    base = {"metric": "tokens/sec", "unit": "tokens/s", "ms_per_step": 29.0, "clocks": {"sm_mhz": 1900, "sm_max_mhz": 1965, "reasons": ["sw_power_cap"]},
+            "e2e": {"value": 281000.0}, "config": {"model": "gpt2-medium"}}
+    f1, f2 = tmp_path / "n1.json", tmp_path / "n2.json"
+    f1.write_text("noise\n" + json.dumps({**base, "value": 280000.0, "n_gpus": 1}) + "\n")
+    f2.write_text(json.dumps({**base, "value": 554400.0, "n_gpus": 2}) + "\n" + json.dumps({"impl": "reference", "unavailable": "no toolchain"}) + "\n")
+    out = tmp_path / "r.html"
+    runs = rep.main([str(f1), str(f2), "--out", str(out)])
+    assert len(runs) == 3 and abs(rep.scaling(runs)["tokens/sec|ours"][2] - 0.99) < 1e-9
+    page = out.read_text()
+    assert "554,400 tokens/s" in page and "2 GPUs 99.0%" in page and "no toolchain" in page
+    assert "| ours | tokens/sec | 1 |" in rep.to_markdown(runs)
