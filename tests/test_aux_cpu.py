@@ -559,3 +559,25 @@ def test_benchmark_report_from_json_lines(tmp_path):
     page = out.read_text()
     assert "554,400 tokens/s" in page and "2 GPUs 99.0%" in page and "no toolchain" in page
     assert "| ours | tokens/sec | 1 |" in rep.to_markdown(runs)
+
+
+def test_core_profiling_helpers(tmp_path):
+    import torch
+    from torsh_b200.utils.profiler import OperationTrace, PerfRegressionDetector, PerformanceProfiler, profile_closure
+    out, ms = profile_closure(lambda a, b: a @ b, torch.ones(8, 8), torch.ones(8, 8), name="mm", repeats=3)
+    assert float(out[0, 0]) == 8.0 and ms >= 0
+    pp = PerformanceProfiler()
+    for _ in range(5):
+        with pp.time("step"):
+            torch.ones(16).sum()
+    st = pp.stats("step")
+    assert st["count"] == 5 and st["min_ms"] <= st["p50_ms"] <= st["max_ms"] and pp.stats("none") == {"count": 0}
+    tr = OperationTrace()
+    with tr.trace_operation("block", torch.ones(2, 3)):
+        with tr.trace_operation("matmul", torch.ones(2, 3), torch.ones(3, 4)):
+            pass
+    assert [(d, n) for d, n, _ in tr.events] == [(0, "block"), (1, "matmul")] and "  matmul" in tr.format()
+    det = PerfRegressionDetector(str(tmp_path / "base.json"), tolerance=0.1)
+    assert det.check("gemm", 10.0)["status"] == "new" and det.check("gemm", 10.5)["status"] == "ok"
+    assert det.check("gemm", 12.0)["status"] == "regression" and det.check("gemm", 8.0)["status"] == "improvement"
+    assert PerfRegressionDetector(str(tmp_path / "base.json")).baselines["gemm"] == 8.0

@@ -229,3 +229,107 @@ class DeviceRangeProfiler:
         import json
         return json.dumps({"traceEvents": [{"name": r["name"], "ph": "X", "ts": r["host_us"], "dur": r["device_us"], "pid": 0,
                                             "tid": r["depth"], "cat": "cuda"} for r in self.records]})
+
+
+# ------------------------------------------------------------------------------------------------ core profiling API
+def profile_closure(fn, *args, name: str | None = None, repeats: int = 1, **kwargs):
+    """``crates/torsh-core/src/profiling.rs``: run ``fn`` under the global profiler and return ``(result, mean ms)``;
+    on a GPU the time is taken after a synchronise so that it covers the launched work."""
+    import time as _time
+
+    import torch
+    label = name or getattr(fn, "__name__", "closure")
+    out, t0 = None, _time.perf_counter()
+    with profile_block(label, category="closure"):
+        for _ in range(repeats):
+            out = fn(*args, **kwargs)
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+    return out, (_time.perf_counter() - t0) * 1e3 / repeats
+
+
+class PerformanceProfiler:
+    """Named timers with call counts and simple statistics (``PerformanceProfiler`` of ``torsh-core``)."""
+
+    def __init__(self):
+        self.samples: dict[str, list[float]] = {}
+
+    def time(self, name: str):
+        import contextlib
+        import time as _time
+
+        @contextlib.contextmanager
+        def cm():
+            t0 = _time.perf_counter()
+            try:
+                yield
+            finally:
+                self.samples.setdefault(name, []).append((_time.perf_counter() - t0) * 1e3)
+        return cm()
+
+    def stats(self, name: str) -> dict:
+        xs = sorted(self.samples.get(name, []))
+        if not xs:
+            return {"count": 0}
+        return {"count": len(xs), "mean_ms": sum(xs) / len(xs), "min_ms": xs[0], "max_ms": xs[-1],
+                "p50_ms": xs[len(xs) // 2], "p95_ms": xs[min(len(xs) - 1, int(0.95 * len(xs)))]}
+
+    def report(self) -> dict:
+        return {k: self.stats(k) for k in self.samples}
+
+
+class OperationTrace:
+    """``trace_operation`` (``crates/torsh-core/src/op_trace.rs``): a bounded, nestable trace of operations with inputs'
+    shapes and dtypes; ``format()`` prints the call tree."""
+
+    def __init__(self, capacity: int = 4096):
+        self.capacity, self.events, self._depth = capacity, [], 0
+
+    def trace_operation(self, name: str, *tensors):
+        import contextlib
+
+        @contextlib.contextmanager
+        def cm():
+            if len(self.events) < self.capacity:
+                self.events.append((self._depth, name, [(tuple(t.shape), str(t.dtype)) for t in tensors if hasattr(t, "shape")]))
+            self._depth += 1
+            try:
+                yield
+            finally:
+                self._depth -= 1
+        return cm()
+
+    def format(self) -> str:
+        return "\n".join("  " * d + f"{n} {sig}" for d, n, sig in self.events)
+
+
+class PerfRegressionDetector:
+    """Compares fresh timings with stored baselines (``perf_regression`` of ``torsh-core`` / the profiler crate's regression
+    detection): a measurement slower than ``baseline x (1 + tolerance)`` is a regression; baselines live in a JSON file and
+    improve monotonically when ``update_on_improvement`` is set."""
+
+    def __init__(self, path: str | None = None, tolerance: float = 0.10, update_on_improvement: bool = True):
+        import json
+        import os
+        self.path, self.tolerance, self.update = path, tolerance, update_on_improvement
+        self.baselines: dict[str, float] = {}
+        if path and os.path.exists(path):
+            with open(path) as f:
+                self.baselines = json.load(f)
+
+    def check(self, name: str, value_ms: float) -> dict:
+        base = self.baselines.get(name)
+        if base is None:
+            self.baselines[name] = value_ms
+            verdict = {"name": name, "status": "new", "baseline_ms": None, "value_ms": value_ms, "ratio": None}
+        else:
+            ratio = value_ms / base
+            status = "regression" if ratio > 1 + self.tolerance else "improvement" if ratio < 1 - self.tolerance else "ok"
+            if status == "improvement" and self.update:
+                self.baselines[name] = value_ms
+            verdict = {"name": name, "status": status, "baseline_ms": base, "value_ms": value_ms, "ratio": ratio}
+        if self.path:
+            import json
+            with open(self.path, "w") as f:
+                json.dump(self.baselines, f, indent=1)
+        return verdict
