@@ -633,3 +633,30 @@ def test_tabular_and_audio_datasets(tmp_path):
     assert abs(peak - 220.0 * (label + 1)) < 40                               # the spectrogram peaks at the class's tone
     raw = AudioDataset([torch.ones(10)], [1], num_samples=16)
     assert raw[0][0].shape == (16,) and float(raw[0][0][12]) == 0.0
+
+
+def test_hub_hf_gpt2_import_and_access_control(tmp_path, monkeypatch):
+    transformers = pytest.importorskip("transformers")
+    from torsh_b200 import hub, models
+    torch.manual_seed(0)
+    hf = transformers.GPT2LMHeadModel(transformers.GPT2Config(vocab_size=1024, n_positions=128, n_embd=256, n_layer=4, n_head=4,
+                                                              resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)).eval()
+    ours = models.create_model("gpt2-tiny").eval()
+    unused = hub.import_hf_gpt2(hf.state_dict(), ours)
+    assert all(("attn.bias" in k or "masked_bias" in k or k == "lm_head.weight") for k in unused)
+    ids = torch.randint(0, 1024, (2, 16))
+    with torch.no_grad():
+        ref = hf(ids).logits
+        got = ours(ids)
+    got = got[..., :1024] if got.shape[-1] > 1024 else got
+    assert torch.allclose(got.float(), ref, atol=2e-4), float((got.float() - ref).abs().max())
+    acl = hub.AccessControl(tmp_path / "acl.json")
+    acl.grant("alice-token", "write", prefixes=("team-a/",))
+    acl.grant("root-token", "admin")
+    assert acl.allowed("read", "team-a/gpt2", "alice-token") and acl.allowed("write", "team-a/gpt2", "alice-token")
+    assert not acl.allowed("write", "team-b/gpt2", "alice-token") and not acl.allowed("admin", "team-a/x", "alice-token")
+    monkeypatch.setenv("TORSH_HUB_TOKEN", "root-token")
+    assert hub.AccessControl(tmp_path / "acl.json").allowed("admin", "anything")
+    acl.revoke("alice-token")
+    with pytest.raises(PermissionError):
+        acl.require("read", "team-a/gpt2", "alice-token")

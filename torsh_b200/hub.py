@@ -213,3 +213,75 @@ def resolve_dependencies(requirements: dict[str, str], available: dict[str, list
             raise LookupError(f"no version of {name} satisfies {req!r} (have {cands})")
         out[name] = ok[-1]
     return out
+
+
+# -------------------------------------------------------------------------------------- Hugging Face checkpoint import
+_HF_GPT2_TRANSPOSED = ("attn.c_attn.weight", "attn.c_proj.weight", "mlp.c_fc.weight", "mlp.c_proj.weight")
+
+
+def import_hf_gpt2(hf_state: dict, model) -> list[str]:
+    """Copy a Hugging Face GPT-2 ``state_dict`` into a :class:`torsh_b200.models.GPTForCausalLM`
+    (``crates/torsh-hub``: Hugging Face integration). HF stores the four projection weights of a block as ``Conv1D``
+    (``[in, out]``) and the embeddings as ``wte.weight`` / ``wpe.weight``; here linear weights are ``[out, in]`` and the
+    embeddings are plain parameters. Returns the HF keys that were not used (attention-mask buffers, a tied ``lm_head``)."""
+    import torch
+    own = dict(model.named_parameters())
+    used = set()
+    with torch.no_grad():
+        for name, p in own.items():
+            key = name + ".weight" if name in ("transformer.wte", "transformer.wpe") else name
+            if key not in hf_state:
+                raise KeyError(f"checkpoint has no tensor for {name!r} (looked for {key!r})")
+            src = hf_state[key]
+            if name.endswith(_HF_GPT2_TRANSPOSED):
+                src = src.t()
+            if name == "transformer.wte" and src.shape[0] < p.shape[0]:       # vocabulary padded to a tile multiple
+                p[: src.shape[0]].copy_(src.to(p.dtype))
+            else:
+                if tuple(src.shape) != tuple(p.shape):
+                    raise ValueError(f"{name}: checkpoint shape {tuple(src.shape)} != model shape {tuple(p.shape)}")
+                p.copy_(src.to(p.dtype))
+            used.add(key)
+    return sorted(k for k in hf_state if k not in used)
+
+
+class AccessControl:
+    """Token-based access to hub entries (``crates/torsh-hub``: access control): tokens are stored as SHA-256 digests
+    with a role (``read`` / ``write`` / ``admin``) and optional name prefixes; the environment variable
+    ``TORSH_HUB_TOKEN`` supplies the caller's token when none is passed."""
+
+    ROLES = {"read": 1, "write": 2, "admin": 3}
+
+    def __init__(self, path=None):
+        self.path = Path(path) if path else None
+        self.tokens: dict[str, dict] = json.loads(self.path.read_text()) if self.path and self.path.exists() else {}
+
+    def _save(self):
+        if self.path:
+            self.path.write_text(json.dumps(self.tokens, indent=1))
+
+    @staticmethod
+    def _digest(token: str) -> str:
+        return hashlib.sha256(token.encode()).hexdigest()
+
+    def grant(self, token: str, role: str = "read", prefixes: tuple[str, ...] = ("",)):
+        if role not in self.ROLES:
+            raise ValueError(f"unknown role {role!r}")
+        self.tokens[self._digest(token)] = {"role": role, "prefixes": list(prefixes)}
+        self._save()
+
+    def revoke(self, token: str):
+        self.tokens.pop(self._digest(token), None)
+        self._save()
+
+    def allowed(self, action: str, name: str, token: str | None = None) -> bool:
+        import os
+        token = token if token is not None else os.environ.get("TORSH_HUB_TOKEN", "")
+        e = self.tokens.get(self._digest(token))
+        if e is None:
+            return False
+        return self.ROLES[e["role"]] >= self.ROLES[action] and any(name.startswith(p) for p in e["prefixes"])
+
+    def require(self, action: str, name: str, token: str | None = None):
+        if not self.allowed(action, name, token):
+            raise PermissionError(f"token may not {action} {name!r}")
