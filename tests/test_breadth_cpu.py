@@ -660,3 +660,23 @@ def test_hub_hf_gpt2_import_and_access_control(tmp_path, monkeypatch):
     acl.revoke("alice-token")
     with pytest.raises(PermissionError):
         acl.require("read", "team-a/gpt2", "alice-token")
+
+
+def test_hub_hf_llama_import_matches_transformers_logits():
+    transformers = pytest.importorskip("transformers")
+    from torsh_b200 import hub
+    from torsh_b200.models.llama import LlamaConfig, LlamaModel
+    torch.manual_seed(0)
+    hc = transformers.LlamaConfig(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                  num_attention_heads=4, num_key_value_heads=4, max_position_embeddings=64, rms_norm_eps=1e-6,
+                                  rope_theta=10000.0, attention_bias=False, tie_word_embeddings=False)
+    hf = transformers.LlamaForCausalLM(hc).eval()
+    ours = LlamaModel(LlamaConfig(vocab_size=320, hidden_size=64, intermediate_size=128, num_layers=2, num_heads=4, max_seq_len=64)).eval()
+    assert hub.import_hf_llama(hf.state_dict(), ours) == []
+    ids = torch.randint(0, 320, (2, 16))
+    with torch.no_grad():
+        assert torch.allclose(ours(ids).float(), hf(ids).logits, atol=1e-5)
+    gqa = transformers.LlamaForCausalLM(transformers.LlamaConfig(vocab_size=320, hidden_size=64, intermediate_size=128, num_hidden_layers=1,
+                                                                 num_attention_heads=4, num_key_value_heads=2)).state_dict()
+    with pytest.raises(ValueError):
+        hub.import_hf_llama(gqa, LlamaModel(LlamaConfig(vocab_size=320, hidden_size=64, intermediate_size=128, num_layers=1, num_heads=4, max_seq_len=64)))

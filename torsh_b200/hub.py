@@ -285,3 +285,45 @@ class AccessControl:
     def require(self, action: str, name: str, token: str | None = None):
         if not self.allowed(action, name, token):
             raise PermissionError(f"token may not {action} {name!r}")
+
+
+def import_hf_llama(hf_state: dict, model) -> list[str]:
+    """Copy a Hugging Face Llama ``state_dict`` (multi-head attention, no grouped KV) into a
+    :class:`torsh_b200.models.LlamaModel` built without tensor parallelism. Three layout differences are bridged:
+    the fused ``qkv`` (``[q | k | v]``) and ``gate_up`` (``[up | gate]``: the gate is the second half) projections, and
+    the rotary convention — HF rotates the pairs ``(i, i + D/2)`` of a head, this package the adjacent pairs
+    ``(2i, 2i + 1)`` — so the rows of the query and key projections are interleaved per head. Returns unused HF keys."""
+    import torch
+    cfg = model.cfg
+    E, H, D = cfg.hidden_size, cfg.num_heads, cfg.head_dim
+
+    def interleave(w):                                    # [H*D, E] rows (i, i + D/2) -> (2i, 2i + 1) inside every head
+        return w.view(H, 2, D // 2, E).transpose(1, 2).reshape(H * D, E)
+
+    used = set()
+
+    def take(key):
+        if key not in hf_state:
+            raise KeyError(f"checkpoint has no tensor {key!r}")
+        used.add(key)
+        return hf_state[key]
+
+    with torch.no_grad():
+        emb = take("model.embed_tokens.weight")
+        model.embed[: emb.shape[0]].copy_(emb.to(model.embed.dtype))
+        for i, blk in enumerate(model.layers):
+            pre = f"model.layers.{i}."
+            if take(pre + "self_attn.k_proj.weight").shape[0] != E:
+                raise ValueError("grouped-query attention checkpoints are not supported by this importer")
+            q, k, v = (take(pre + f"self_attn.{n}_proj.weight") for n in ("q", "k", "v"))
+            blk.qkv.weight.copy_(torch.cat([interleave(q), interleave(k), v]).to(blk.qkv.weight.dtype))
+            blk.o.weight.copy_(take(pre + "self_attn.o_proj.weight").to(blk.o.weight.dtype))
+            blk.gate_up.weight.copy_(torch.cat([take(pre + "mlp.up_proj.weight"), take(pre + "mlp.gate_proj.weight")]).to(blk.gate_up.weight.dtype))
+            blk.down.weight.copy_(take(pre + "mlp.down_proj.weight").to(blk.down.weight.dtype))
+            blk.input_norm.weight.copy_(take(pre + "input_layernorm.weight").to(blk.input_norm.weight.dtype))
+            blk.post_attn_norm.weight.copy_(take(pre + "post_attention_layernorm.weight").to(blk.post_attn_norm.weight.dtype))
+        model.norm.weight.copy_(take("model.norm.weight").to(model.norm.weight.dtype))
+        head = hf_state.get("lm_head.weight", emb)
+        used.add("lm_head.weight")
+        model.lm_head[: head.shape[0]].copy_(head.to(model.lm_head.dtype))
+    return sorted(k for k in hf_state if k not in used)
