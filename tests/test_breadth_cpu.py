@@ -680,3 +680,20 @@ def test_hub_hf_llama_import_matches_transformers_logits():
                                                                  num_attention_heads=4, num_key_value_heads=2)).state_dict()
     with pytest.raises(ValueError):
         hub.import_hf_llama(gqa, LlamaModel(LlamaConfig(vocab_size=320, hidden_size=64, intermediate_size=128, num_layers=1, num_heads=4, max_seq_len=64)))
+
+
+def test_hub_hf_bert_import_matches_transformers_hidden_states():
+    transformers = pytest.importorskip("transformers")
+    from torsh_b200 import hub
+    from torsh_b200.models.transformer_zoo import BertConfig, BertModel
+    torch.manual_seed(0)
+    hc = transformers.BertConfig(vocab_size=100, hidden_size=32, num_hidden_layers=2, num_attention_heads=2, intermediate_size=64,
+                                 max_position_embeddings=64, hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    hf = transformers.BertModel(hc).eval()
+    ours = BertModel(BertConfig(vocab_size=100, hidden_size=32, num_layers=2, num_heads=2, intermediate_size=64,
+                                max_position_embeddings=64, dropout=0.0)).eval()
+    assert hub.import_hf_bert(hf.state_dict(), ours) == []
+    ids = torch.randint(1, 100, (2, 10))
+    with torch.no_grad():
+        ref, (hidden, pooled) = hf(ids), ours(ids)
+    assert torch.allclose(hidden, ref.last_hidden_state, atol=1e-5) and torch.allclose(pooled, ref.pooler_output, atol=1e-5)

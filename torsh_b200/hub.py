@@ -327,3 +327,44 @@ def import_hf_llama(hf_state: dict, model) -> list[str]:
         used.add("lm_head.weight")
         model.lm_head[: head.shape[0]].copy_(head.to(model.lm_head.dtype))
     return sorted(k for k in hf_state if k not in used)
+
+
+def import_hf_bert(hf_state: dict, model) -> list[str]:
+    """Copy a Hugging Face ``BertModel`` ``state_dict`` into :class:`torsh_b200.models.BertModel` (post-norm encoder with a
+    fused ``in_proj`` for query / key / value). Returns the HF keys that were not used (position-id buffers)."""
+    import torch
+    used = set()
+
+    def take(key):
+        if key not in hf_state:
+            raise KeyError(f"checkpoint has no tensor {key!r}")
+        used.add(key)
+        return hf_state[key]
+
+    def put(dst, *keys):
+        src = torch.cat([take(k) for k in keys]) if len(keys) > 1 else take(keys[0])
+        if tuple(src.shape) != tuple(dst.shape):
+            raise ValueError(f"{keys[0]}: checkpoint shape {tuple(src.shape)} != model shape {tuple(dst.shape)}")
+        dst.copy_(src.to(dst.dtype))
+
+    with torch.no_grad():
+        e = "embeddings."
+        put(model.word_embeddings.weight, e + "word_embeddings.weight")
+        pos = take(e + "position_embeddings.weight")
+        model.position_embeddings.weight[: pos.shape[0]].copy_(pos)
+        put(model.token_type_embeddings.weight, e + "token_type_embeddings.weight")
+        put(model.emb_norm.weight, e + "LayerNorm.weight")
+        put(model.emb_norm.bias, e + "LayerNorm.bias")
+        for i, layer in enumerate(model.layers):
+            p = f"encoder.layer.{i}."
+            a = p + "attention.self."
+            put(layer.attn.in_proj_weight, a + "query.weight", a + "key.weight", a + "value.weight")
+            put(layer.attn.in_proj_bias, a + "query.bias", a + "key.bias", a + "value.bias")
+            for ours, theirs in ((layer.attn.out_proj, "attention.output.dense"), (layer.ln1, "attention.output.LayerNorm"),
+                                 (layer.fc1, "intermediate.dense"), (layer.fc2, "output.dense"), (layer.ln2, "output.LayerNorm")):
+                put(ours.weight, p + theirs + ".weight")
+                put(ours.bias, p + theirs + ".bias")
+        if hasattr(model, "pooler") and "pooler.dense.weight" in hf_state:
+            put(model.pooler.weight, "pooler.dense.weight")
+            put(model.pooler.bias, "pooler.dense.bias")
+    return sorted(k for k in hf_state if k not in used)
