@@ -697,3 +697,20 @@ def test_hub_hf_bert_import_matches_transformers_hidden_states():
     with torch.no_grad():
         ref, (hidden, pooled) = hf(ids), ours(ids)
     assert torch.allclose(hidden, ref.last_hidden_state, atol=1e-5) and torch.allclose(pooled, ref.pooler_output, atol=1e-5)
+
+
+def test_hub_hf_vit_import_matches_transformers_logits():
+    transformers = pytest.importorskip("transformers")
+    from torsh_b200 import hub
+    from torsh_b200.models.transformer_zoo import ViTConfig, VisionTransformer
+    torch.manual_seed(0)
+    hc = transformers.ViTConfig(image_size=32, patch_size=8, hidden_size=32, num_hidden_layers=2, num_attention_heads=2,
+                                intermediate_size=64, num_labels=5, layer_norm_eps=1e-6, hidden_dropout_prob=0.0,
+                                attention_probs_dropout_prob=0.0)
+    hf = transformers.ViTForImageClassification(hc).eval()
+    ours = VisionTransformer(ViTConfig(image_size=32, patch_size=8, hidden_size=32, num_layers=2, num_heads=2, intermediate_size=64,
+                                       num_classes=5, layer_norm_eps=1e-6)).eval()
+    assert hub.import_hf_vit(hf.state_dict(), ours) == []
+    x = torch.randn(2, 3, 32, 32)
+    with torch.no_grad():
+        assert torch.allclose(ours(x), hf(x).logits, atol=1e-5)

@@ -368,3 +368,43 @@ def import_hf_bert(hf_state: dict, model) -> list[str]:
             put(model.pooler.weight, "pooler.dense.weight")
             put(model.pooler.bias, "pooler.dense.bias")
     return sorted(k for k in hf_state if k not in used)
+
+
+def import_hf_vit(hf_state: dict, model) -> list[str]:
+    """Copy a Hugging Face ``ViTForImageClassification`` ``state_dict`` into :class:`torsh_b200.models.VisionTransformer`
+    (pre-norm blocks, fused query / key / value projection)."""
+    import torch
+    used = set()
+
+    def take(key):
+        if key not in hf_state:
+            raise KeyError(f"checkpoint has no tensor {key!r}")
+        used.add(key)
+        return hf_state[key]
+
+    def put(dst, *keys):
+        src = torch.cat([take(k) for k in keys]) if len(keys) > 1 else take(keys[0])
+        if tuple(src.shape) != tuple(dst.shape):
+            raise ValueError(f"{keys[0]}: checkpoint shape {tuple(src.shape)} != model shape {tuple(dst.shape)}")
+        dst.copy_(src.to(dst.dtype))
+
+    with torch.no_grad():
+        e = "vit.embeddings."
+        put(model.cls_token, e + "cls_token")
+        put(model.pos_embed, e + "position_embeddings")
+        put(model.patch_embed.weight, e + "patch_embeddings.projection.weight")
+        put(model.patch_embed.bias, e + "patch_embeddings.projection.bias")
+        for i, b in enumerate(model.blocks):
+            p = f"vit.encoder.layer.{i}."
+            a = p + "attention.attention."
+            put(b.attn.in_proj_weight, a + "query.weight", a + "key.weight", a + "value.weight")
+            put(b.attn.in_proj_bias, a + "query.bias", a + "key.bias", a + "value.bias")
+            for ours, theirs in ((b.attn.out_proj, "attention.output.dense"), (b.ln1, "layernorm_before"),
+                                 (b.fc1, "intermediate.dense"), (b.fc2, "output.dense"), (b.ln2, "layernorm_after")):
+                put(ours.weight, p + theirs + ".weight")
+                put(ours.bias, p + theirs + ".bias")
+        put(model.norm.weight, "vit.layernorm.weight")
+        put(model.norm.bias, "vit.layernorm.bias")
+        put(model.head.weight, "classifier.weight")
+        put(model.head.bias, "classifier.bias")
+    return sorted(k for k in hf_state if k not in used)
