@@ -714,3 +714,17 @@ def test_hub_hf_vit_import_matches_transformers_logits():
     x = torch.randn(2, 3, 32, 32)
     with torch.no_grad():
         assert torch.allclose(ours(x), hf(x).logits, atol=1e-5)
+
+
+def test_resnet_state_dict_is_interchangeable_with_torchvision():
+    tv = pytest.importorskip("torchvision")
+    from torsh_b200.models import create_model
+    torch.manual_seed(0)
+    for name in ("resnet18", "resnet50"):
+        ref = getattr(tv.models, name)().eval()
+        ours = create_model(name).eval()
+        assert list(ours.state_dict()) == list(ref.state_dict())
+        ours.load_state_dict(ref.state_dict())
+        x = torch.randn(2, 3, 64, 64)
+        with torch.no_grad():
+            assert torch.allclose(ours(x), ref(x), atol=1e-4), name
