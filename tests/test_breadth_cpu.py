@@ -728,3 +728,21 @@ def test_resnet_state_dict_is_interchangeable_with_torchvision():
         x = torch.randn(2, 3, 64, 64)
         with torch.no_grad():
             assert torch.allclose(ours(x), ref(x), atol=1e-4), name
+
+
+def test_vision_zoo_reproduces_torchvision_logits():
+    tv = pytest.importorskip("torchvision")
+    from torsh_b200.models import create_model
+    torch.manual_seed(0)
+    x = torch.randn(1, 3, 96, 96)
+    for name, by_key in (("alexnet", True), ("vgg16_bn", True), ("densenet121", False), ("mobilenet_v2", False)):
+        ref = getattr(tv.models, name)().eval()
+        ours = create_model(name).eval()
+        if by_key:
+            ours.load_state_dict(ref.state_dict())
+        else:                               # same tensors in the same order under different names
+            mine = ours.state_dict()
+            assert [tuple(v.shape) for v in mine.values()] == [tuple(v.shape) for v in ref.state_dict().values()], name
+            ours.load_state_dict(dict(zip(mine.keys(), ref.state_dict().values())))
+        with torch.no_grad():
+            assert torch.allclose(ours(x), ref(x), atol=1e-4), name
