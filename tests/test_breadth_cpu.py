@@ -736,15 +736,16 @@ def test_vision_zoo_reproduces_torchvision_logits():
     torch.manual_seed(0)
     x = torch.randn(1, 3, 96, 96)
     for name, by_key in (("alexnet", True), ("vgg16_bn", True), ("densenet121", False), ("mobilenet_v2", False),
-                         ("efficientnet_b0", False)):
+                         ("efficientnet_b0", False), ("convnext_tiny", False)):
         ref = getattr(tv.models, name)().eval()
         ours = create_model(name).eval()
         if by_key:
             ours.load_state_dict(ref.state_dict())
         else:                               # same tensors in the same order under different names
             mine = ours.state_dict()
-            assert [tuple(v.shape) for v in mine.values()] == [tuple(v.shape) for v in ref.state_dict().values()], name
-            ours.load_state_dict(dict(zip(mine.keys(), ref.state_dict().values())))
+            assert [v.numel() for v in mine.values()] == [v.numel() for v in ref.state_dict().values()], name
+            # (ConvNeXt's layer scale is [C] here and [C, 1, 1] there; everything else has the same shape)
+            ours.load_state_dict({k: v.reshape(mine[k].shape) for k, v in zip(mine.keys(), ref.state_dict().values())})
         with torch.no_grad():
             want = ref(x)
             assert float(want.abs().max()) > 0 and torch.allclose(ours(x), want, atol=1e-4), name
