@@ -1,11 +1,13 @@
 #!/usr/bin/env python
 """Constructed baseline: GPT-2-medium training step with stock PyTorch only (cuBLAS GEMMs, SDPA flash
-attention, fused AdamW, `torch.distributed.fsdp` + NCCL when launched on more than one GPU).
+attention, fused AdamW, FSDP2 `fully_shard` + NCCL when launched on more than one GPU).
 
 Same shapes, synthetic data, dtype policy (bf16 compute, fp32 master weights) and timing rules as the
-repository's bench.py; none of this package's kernels or engine are imported.
+repository's bench.py; none of this package's kernels or engine are imported. The logits reach the loss in bf16
+(no fp32 copy of the [tokens, vocab] matrix). `--compile` wraps the model in `torch.compile`; bench.py runs both
+variants and keeps the faster one.
 
-  python baseline/gpt2_torch.py --steps 10 --warmup 4
+  python baseline/gpt2_torch.py --steps 20 --warmup 4 [--compile]
   python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 baseline/gpt2_torch.py --gpus 8
 """
 import argparse
@@ -51,13 +53,14 @@ class GPT2(nn.Module):
         for b in self.h:
             x = b(x)
         logits = F.linear(self.ln_f(x), self.wte.weight)
-        return F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), targets.reshape(-1))
+        with torch.autocast("cuda", enabled=False):   # autocast would widen the [tokens, vocab] logits to fp32
+            return F.cross_entropy(logits.view(-1, logits.shape[-1]), targets.reshape(-1))
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--compile", action="store_true")
     a = ap.parse_args()
@@ -70,11 +73,13 @@ def main():
     B, S = 8, 1024
     model = GPT2().to(dev)
     if world > 1:
-        from torch.distributed.fsdp import FullyShardedDataParallel as FSDP, MixedPrecision, ShardingStrategy
-        from torch.distributed.fsdp.wrap import ModuleWrapPolicy
-        model = FSDP(model, auto_wrap_policy=ModuleWrapPolicy({Block}), sharding_strategy=ShardingStrategy.FULL_SHARD,
-                     mixed_precision=MixedPrecision(param_dtype=torch.bfloat16, reduce_dtype=torch.float32),
-                     device_id=dev, use_orig_params=True)
+        # FSDP2 with its defaults (full shard, reshard after forward, prefetching), one unit per block + the root;
+        # fp32 parameters are the master weights, compute and all-gathers in bf16, gradient reduction in fp32
+        from torch.distributed.fsdp import MixedPrecisionPolicy, fully_shard
+        mp = MixedPrecisionPolicy(param_dtype=torch.bfloat16, reduce_dtype=torch.float32)
+        for blk in model.h:
+            fully_shard(blk, mp_policy=mp)
+        fully_shard(model, mp_policy=mp)
         ctx = torch.autocast("cuda", enabled=False)
     else:
         ctx = torch.autocast("cuda", dtype=torch.bfloat16)

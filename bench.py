@@ -91,6 +91,43 @@ def reference_arm(args):
     return 0
 
 
+def _child_env(port_offset: int) -> dict:
+    """Environment of a child benchmark process of this rank: same RANK / WORLD_SIZE / LOCAL_RANK, its own rendezvous
+    port, and none of the launcher's agent-store settings (the child ranks form their own process group)."""
+    env = {k: v for k, v in os.environ.items() if not k.startswith("TORCHELASTIC_")}
+    env["MASTER_ADDR"] = "127.0.0.1"
+    env["MASTER_PORT"] = str(int(os.environ.get("MASTER_PORT", "29517")) + port_offset)
+    env.setdefault("RANK", "0"); env.setdefault("WORLD_SIZE", "1"); env.setdefault("LOCAL_RANK", "0")
+    return env
+
+
+def run_child(argv: list[str], port_offset: int, timeout_s: float) -> dict:
+    """Runs one benchmark script as a child of EVERY rank (the children rendezvous among themselves) and returns the
+    JSON line its rank 0 printed, or ``{"failed": reason}``. Never raises: a broken extra arm must not cost the
+    headline number."""
+    t0 = time.perf_counter()
+    try:
+        r = subprocess.run([sys.executable] + argv, env=_child_env(port_offset), capture_output=True, text=True,
+                           timeout=timeout_s, cwd=REPO)
+    except subprocess.TimeoutExpired:
+        return {"failed": f"timed out after {timeout_s:.0f} s"}
+    except OSError as e:
+        return {"failed": str(e)}
+    out = None
+    for ln in r.stdout.splitlines():
+        ln = ln.strip()
+        if ln.startswith("{") and ln.endswith("}"):
+            try:
+                out = json.loads(ln)
+            except json.JSONDecodeError:
+                pass
+    if r.returncode != 0:
+        return {"failed": f"exit code {r.returncode}: {r.stderr.strip().splitlines()[-1][:200] if r.stderr.strip() else ''}"}
+    out = out or {}
+    out["wall_s"] = round(time.perf_counter() - t0, 1)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -106,12 +143,43 @@ def main():
     ap.add_argument("--fsdp-overlap", action="store_true", help="launch each block's FSDP kernel from a backward hook on a side stream")
     ap.add_argument("--fsdp-nvls", type=int, default=None, help="1 / 0: force NVLS multimem on / off in the fused FSDP kernel")
     ap.add_argument("--fsdp-coarse", type=int, default=0, help="with --fsdp-overlap: merge the per-block units into this many groups")
+    ap.add_argument("--fsdp-strategy", default="full_shard", choices=["full_shard", "shard_grad_op", "no_shard"],
+                    help="full_shard: 1/N of every weight resident, un-shard fused into each block's first GEMM, "
+                         "reduce-scatter + AdamW per block under backward; shard_grad_op: replicated bf16 parameters and "
+                         "gradients, sharded optimizer, one fused reduce-scatter + AdamW + all-gather launch")
+    ap.add_argument("--fsdp-no-fuse-gather", action="store_true", help="full_shard: stand-alone gather kernels instead of the fused GEMM")
+    ap.add_argument("--fsdp-gather-ctas", type=int, default=0)
+    ap.add_argument("--fsdp-rs-blocks", type=int, default=0)
     ap.add_argument("--fsdp-single", action="store_true",
                     help="diagnostic: run the FSDP engine in a one-rank group on one GPU (its kernels without any peer)")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the constructed PyTorch baseline arm (child processes)")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the ResNet-50 DDP and Llama 3-D secondary benchmarks")
+    ap.add_argument("--budget-s", type=float, default=float(os.environ.get("TORSH_BENCH_BUDGET_S", "700")),
+                    help="wall-clock budget of the whole invocation; extra arms that no longer fit are skipped")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
     args.warmup = max(args.warmup, 3)
+    t_start = time.perf_counter()
+    headline = args.model == "gpt2-medium" and not args.fsdp_single and not args.no_graph
+    left = lambda: args.budget_s - (time.perf_counter() - t_start)
+
+    # ---- constructed baseline (stock PyTorch: cuBLAS, SDPA, fused AdamW, FSDP2 over NCCL) as child processes on the
+    #      same GPUs, BEFORE this process creates its CUDA context; eager and torch.compile variants, the faster wins
+    baseline = None
+    if headline and not args.no_baseline:
+        base_cmd = [os.path.join(REPO, "baseline", "gpt2_torch.py"), "--gpus", str(args.gpus), "--steps",
+                    str(max(args.steps, 20)), "--warmup", "4"]
+        arms = {"eager": run_child(base_cmd, 11, min(300.0, max(left() - 200, 60)))}
+        if left() > 420:
+            arms["compile"] = run_child(base_cmd + ["--compile"], 12, min(330.0, left() - 200))
+        ok = {k: v for k, v in arms.items() if "value" in v}
+        if ok:
+            best = max(ok, key=lambda k: ok[k]["value"])
+            baseline = {"variant": best, "value": ok[best]["value"], "ms_per_step": ok[best]["ms_per_step"],
+                        "e2e_value": ok[best]["e2e"]["value"], "arms": {k: (v.get("value") or v.get("failed")) for k, v in arms.items()}}
+        else:
+            baseline = {"variant": None, "arms": {k: v.get("failed") for k, v in arms.items()}}
 
     import torch
     import torch.distributed as dist
@@ -143,9 +211,13 @@ def main():
     model = GPTForCausalLM(cfg).to(dev)
     parallel = None
     if world > 1 or args.fsdp_single:
-        from torsh_b200.parallel.fsdp import FlatFSDP
-        from torsh_b200.parallel.fsdp import FsdpConfig
-        fc = FsdpConfig()
+        from torsh_b200.parallel.fsdp import FlatFSDP, FsdpConfig, ShardingStrategy
+        fc = FsdpConfig(sharding_strategy=ShardingStrategy(args.fsdp_strategy))
+        fc.fuse_gather = not args.fsdp_no_fuse_gather
+        if args.fsdp_gather_ctas:
+            fc.gather_ctas = args.fsdp_gather_ctas
+        if args.fsdp_rs_blocks:
+            fc.rs_blocks = args.fsdp_rs_blocks
         if args.fsdp_comm_blocks:
             fc.comm_blocks = args.fsdp_comm_blocks
         fc.overlap = bool(args.fsdp_overlap) and not args.fsdp_no_overlap
@@ -212,6 +284,7 @@ def main():
     sampler.stop()
 
     nv.check_status()
+    h2d_bytes, d2h_bytes = trainer.h2d_bytes_per_step, trainer.d2h_bytes_per_step
 
     t = torch.tensor([dev_ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -220,6 +293,65 @@ def main():
     tokens = world * B * S * args.steps
     value = tokens / (dev_ms / 1e3)
     e2e = tokens / (e2e_ms / 1e3)
+
+    # ---- multi-GPU correctness evidence taken after the timed steps
+    checks = None
+    if parallel is not None and world > 1:
+        checks = {"status_word": 0}   # nv.check_status() above would have raised otherwise
+        from torsh_b200.parallel.fsdp import FullShardParameters
+        flat = trainer.flat
+        vec = flat.full_lowp().float() if isinstance(flat, FullShardParameters) else flat.lowp.float()
+        # (full shard: the gathered weights are the same bytes on every rank by construction; the test bites on the
+        # replicated small parameters and, for the other strategies, on every rank's copy of every parameter)
+        mx, mn = vec.clone(), vec.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX); dist.all_reduce(mn, op=dist.ReduceOp.MIN)
+        checks["params_identical_across_ranks"] = bool(torch.equal(mx, mn))
+        # loss of the first timed step against a one-GPU evaluation is not repeated here (it needs the global batch on
+        # one device); the per-rank losses of step 0 are identical functions of the same weights:
+        l0 = torch.tensor([losses[0]], dtype=torch.float64, device=dev)
+        l0max, l0min = l0.clone(), l0.clone()
+        dist.all_reduce(l0max, op=dist.ReduceOp.MAX); dist.all_reduce(l0min, op=dist.ReduceOp.MIN)
+        checks["step0_loss_min_max_over_ranks"] = [l0min.item(), l0max.item()]
+        checks["step0_loss_expected_ln_vocab"] = round(float(__import__("math").log(cfg.vocab_size)), 4)
+        ll = torch.tensor([losses[-1]], dtype=torch.float64, device=dev)
+        dist.all_reduce(ll)
+        checks["last_loss_mean_over_ranks"] = ll.item() / world
+        del vec, mx, mn
+
+    # ---- secondary benchmarks (child processes on the same GPUs, after this process has released its memory)
+    secondary = None
+    if headline and not args.no_secondary:
+        launches_per_step, strategy = trainer.launches_per_step, (parallel.strategy.value if parallel is not None else "none")
+        mem_report = parallel.memory_report() if parallel is not None else None
+        graph_on = trainer.graph is not None
+        del trainer, model, parallel
+        if dist.is_initialized():
+            dist.barrier()
+        import gc
+        gc.collect(); torch.cuda.empty_cache()
+        secondary = {}
+        rn = os.path.join(REPO, "bench", "resnet50.py")
+        if left() > 150:
+            ours = run_child([rn, "--gpus", str(world), "--steps", "10", "--warmup", "3"], 21, min(200.0, left() - 60))
+            base = run_child([rn, "--gpus", str(world), "--steps", "10", "--warmup", "3", "--impl", "torch"], 22, min(200.0, max(left() - 40, 30))) if left() > 90 else {"failed": "no time left"}
+            secondary["resnet50_ddp"] = {
+                "metric": "images/s (ResNet-50, batch 256/GPU, bf16, SGD 0.9, DDP 25 MB buckets)",
+                "value": ours.get("value"), "e2e_value": (ours.get("e2e") or {}).get("value"), "ms_per_step": ours.get("ms_per_step"),
+                "baseline_value": base.get("value"), "ratio": (ours["value"] / base["value"]) if ours.get("value") and base.get("value") else None,
+                "failed": ours.get("failed") or base.get("failed")}
+        if world == 8 and left() > 260:
+            ll3 = os.path.join(REPO, "bench", "llama_3d.py")
+            ours = run_child([ll3, "--tp", "4", "--pp", "2", "--steps", "10", "--warmup", "3"], 23, min(240.0, left() - 130))
+            base = run_child([ll3, "--tp", "4", "--pp", "2", "--steps", "10", "--warmup", "3", "--impl", "nccl"], 24, min(240.0, max(left() - 20, 30))) if left() > 120 else {"failed": "no time left"}
+            secondary["llama7b_tp4_pp2"] = {
+                "metric": "tokens/s (Llama-style 7B, seq 4096, TP4(+SP) x PP2 1F1B, 8 micro-batches)",
+                "value": ours.get("value"), "e2e_value": (ours.get("e2e") or {}).get("value"), "ms_per_step": ours.get("ms_per_step"),
+                "baseline_value": base.get("value"), "ratio": (ours["value"] / base["value"]) if ours.get("value") and base.get("value") else None,
+                "failed": ours.get("failed") or base.get("failed")}
+    else:
+        launches_per_step, strategy = trainer.launches_per_step, (parallel.strategy.value if parallel is not None else "none")
+        mem_report = parallel.memory_report() if parallel is not None else None
+        graph_on = trainer.graph is not None
     if rank == 0:
         out = {
             "metric": "tokens/sec (GPT-2-medium training step, device-timed, max over ranks)",
@@ -229,17 +361,25 @@ def main():
             "config": {"model": args.model, "layers": cfg.n_layer, "d_model": cfg.n_embd, "heads": cfg.n_head,
                        "ffn": cfg.inner, "vocab": cfg.vocab_size, "global_batch": world * B, "micro_batch_per_gpu": B,
                        "seq_len": S, "optimizer": "AdamW fp32 master weights", "dropout": 0.0,
-                       "parallelism": f"fsdp{world}" if parallel is not None else "single",
-                       "cuda_graph": trainer.graph is not None,
+                       "parallelism": f"fsdp{world}" if strategy != "none" else "single",
+                       "sharding": strategy,
+                       "memory_per_rank": mem_report,
+                       "cuda_graph": graph_on,
                        "l2": "working set per step (>10 GB) far exceeds the 126 MB L2; no explicit flush"},
             "clocks": clocks,
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "device_busy_ms_per_step": busy_ms, "device_idle_ms_between_steps": idle_ms,
                     "clocks": e2e_clocks,
-                    "h2d_bytes_per_step": trainer.h2d_bytes_per_step, "d2h_bytes_per_step": trainer.d2h_bytes_per_step},
-            "gpu_launches": trainer.launches_per_step * args.steps,
-            "launches_per_step": trainer.launches_per_step,
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
+            "gpu_launches": launches_per_step * args.steps,
+            "launches_per_step": launches_per_step,
             "loss_first": losses[0], "loss_last": losses[-1],
+            # the constructed baseline of this very invocation (same GPUs, child processes, run first)
+            "vs_constructed_baseline": None if baseline is None else {
+                **baseline,
+                "value_ratio": (value / baseline["value"]) if baseline.get("value") else None,
+                "e2e_ratio": (e2e / baseline["e2e_value"]) if baseline.get("e2e_value") else None},
+            "checks": checks, "secondary": secondary,
         }
         print(json.dumps(out))
     if dist.is_initialized():

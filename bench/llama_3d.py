@@ -34,7 +34,7 @@ def main():
     ap.add_argument("--vocab", type=int, default=32000)
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--micro-batches", type=int, default=8)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="fused", choices=["fused", "nccl"])
     ap.add_argument("--dense-head", action="store_true",
@@ -105,11 +105,22 @@ def main():
     loss_fn = lambda h, y: model.head(h, B, S, y)
     replicated = model.replicated_parameters() if args.tp > 1 else []
 
+    # a fresh batch of M micro-batches for every step (warm-up, device-timed and end-to-end steps all differ), generated
+    # once in pinned host memory; the device-timed region reads resident copies, the end-to-end region copies each
+    # step's batch from the host and reads the loss back
+    import time
     g = torch.Generator().manual_seed(99 + mp.dp_rank)
-    ids = torch.randint(0, args.vocab, (M, S + 1), generator=g).to(dev)
-    inp, tgt = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    nb = args.warmup + 2 * args.steps
+    ids_host = torch.randint(0, args.vocab, (nb, M, S + 1), generator=g).pin_memory()
+    ids_dev = ids_host.to(dev)
+    inp_buf = torch.empty(M, S, dtype=torch.int64, device=dev)
+    tgt_buf = torch.empty(M, S, dtype=torch.int64, device=dev)
 
-    def step():
+    def step(i, from_host=False):
+        src = ids_host[i] if from_host else ids_dev[i]
+        inp_buf.copy_(src[:, :-1], non_blocking=True)
+        tgt_buf.copy_(src[:, 1:], non_blocking=True)
+        inp, tgt = inp_buf, tgt_buf
         if pipe is not None:
             loss = pipe.train_step(inp if mesh.is_first_stage else None, tgt if mesh.is_last_stage else None, loss_fn)
         else:
@@ -135,8 +146,8 @@ def main():
         torch.cuda.synchronize()
 
     launches0 = nv.launch_count
-    for _ in range(args.warmup):
-        loss = step()
+    for i in range(args.warmup):
+        loss = step(i)
     per_step = (nv.launch_count - launches0) // args.warmup
     first = loss.item() if loss is not None else None
     nv.check_status()
@@ -145,16 +156,24 @@ def main():
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for _ in range(args.steps):
-        loss = step()
+    for i in range(args.steps):
+        loss = step(args.warmup + i)
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
+    # end to end: every step copies its batch from pinned host memory and the last stage reads the loss back
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        loss = step(args.warmup + args.steps + i, from_host=True)
+        if loss is not None:
+            loss_value = loss.item()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop()
     nv.check_status()
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = t.item()
+    ms, e2e_ms = t.tolist()
     last = torch.tensor([loss.item() if loss is not None else 0.0, first if first is not None else 0.0], device=dev)
     dist.all_reduce(last, op=dist.ReduceOp.MAX)
     last, first_all = last[0], last[1].item()
@@ -170,6 +189,8 @@ def main():
             "config": {"layers": args.layers, "d_model": args.hidden, "heads": args.heads, "ffn": args.ffn, "vocab": args.vocab,
                        "seq_len": S, "micro_batches": M, "head": "dense" if args.dense_head else "vocab-parallel", "parallelism": f"tp{args.tp}(sp) x pp{args.pp}(1f1b) x dp{dp}",
                        "params_b": round(n_params / 1e9, 2)},
+            "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
+                    "h2d_bytes_per_step": M * (S + 1) * 8, "d2h_bytes_per_step": 4},
             "clocks": clocks, "gpu_launches": per_step * args.steps, "launches_per_step": per_step,
             "loss_after_warmup": first_all, "loss_last": last.item()}))
     dist.barrier()

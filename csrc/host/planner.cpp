@@ -81,6 +81,36 @@ TSH_EXPORT int tsh_pipeline_schedule(int schedule, int stage, int num_stages, in
   return n;
 }
 
+// Interleaved 1F1B over virtual stages: every rank holds `num_chunks` model chunks (chunk c of rank r is virtual stage
+// c * num_stages + r), so a micro-batch crosses every rank num_chunks times and the pipeline bubble shrinks by that
+// factor. Needs num_micro % num_stages == 0. actions[3*i] = kind (0 forward, 1 backward), [3*i+1] = micro-batch,
+// [3*i+2] = chunk. Forward step k of a rank works on chunk (k / P) % V of micro-batch (k / (P*V)) * P + k % P;
+// backward steps visit the chunks in reverse. Warm-up is (P - r - 1) * 2 + (V - 1) * P forwards, then one forward
+// and one backward alternate, then the remaining backwards. Returns the number of actions (2 * M * V) or -1.
+// The reference names this schedule and runs plain 1F1B for it (crates/torsh-distributed/src/pipeline.rs:343-347).
+TSH_EXPORT int tsh_pipeline_schedule_interleaved(int stage, int num_stages, int num_micro, int num_chunks,
+                                                 int32_t* actions, int cap) {
+  const int P = num_stages, V = num_chunks, M = num_micro;
+  if (stage < 0 || stage >= P || M <= 0 || V < 1 || M % P != 0 || cap < 2 * M * V) return -1;
+  const int total = M * V;
+  int n = 0;
+  auto push = [&](int kind, int k) {
+    const int group = k / (P * V), in_group = k % (P * V);
+    int chunk = in_group / P;
+    if (kind == 1) chunk = V - 1 - chunk;
+    actions[3 * n] = kind;
+    actions[3 * n + 1] = group * P + in_group % P;
+    actions[3 * n + 2] = chunk;
+    ++n;
+  };
+  int warm = std::min((P - stage - 1) * 2 + (V - 1) * P, total);
+  int f = 0, b = 0;
+  for (int i = 0; i < warm; ++i) push(0, f++);
+  while (f < total) { push(0, f++); push(1, b++); }
+  while (b < total) push(1, b++);
+  return n;
+}
+
 // Peak number of activations a stage holds under the schedule (for the memory planner).
 TSH_EXPORT int tsh_pipeline_peak_inflight(int schedule, int stage, int num_stages, int num_micro) {
   std::vector<int32_t> a(4 * (size_t)std::max(num_micro, 1));

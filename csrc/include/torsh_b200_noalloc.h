@@ -14,8 +14,10 @@
  *    (both in floats); otherwise the call returns TB_E_TOO_LARGE (-4) and tb_last_error() says why.
  *  - All calls on a device share the one array: calls whose kernels may overlap on the GPU race.
  *    Keep them on one stream or order them with events.
- *  - The first call on each device resolves the array's device address (with that device current).
- *    Make it once before any stream capture starts.
+ *  - The first call on each device resolves the array's device address (with that device current),
+ *    and the first call of every host thread selects the device for that thread (cudaSetDevice, which
+ *    creates the device's context if the process has none yet). Make one call per host thread and
+ *    device before any stream capture starts.
  *  - No cudaMalloc, cudaFree or other allocating routine is called, on any path.
  */
 #ifndef TORSH_B200_NOALLOC_H

@@ -53,6 +53,30 @@ struct FaBwdSmem {
   static constexpr int ALLOC = TOTAL + 1024;
 };
 
+// P = exp2(S * sl2 - L) and dS = P * (dP - delta) * scale for 32 scores of one row, both packed to bf16 pairs. The
+// scale-and-shift steps run as packed two-wide fp32 instructions; MASK is a template parameter so that blocks away from
+// the diagonal and the ragged edge carry no compare / select instructions.
+template <bool MASK>
+__device__ __forceinline__ void fa_bwd_p_ds(const uint32_t (&sv)[32], const uint32_t (&dv)[32], float sl2, float Lr,
+                                            float scale, float dr, int kvbase, int col_limit, uint32_t (&pp)[16],
+                                            uint32_t (&dd)[16]) {
+  const float2 s2 = make_float2(sl2, sl2), l2 = make_float2(-Lr, -Lr);
+  const float2 c2 = make_float2(scale, scale), d2 = make_float2(-dr * scale, -dr * scale);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 t = __ffma2_rn(make_float2(__uint_as_float(sv[2 * i]), __uint_as_float(sv[2 * i + 1])), s2, l2);
+    float2 e = make_float2(exp2f(t.x), exp2f(t.y));
+    if (MASK) {
+      if (kvbase + 2 * i > col_limit) e.x = 0.f;
+      if (kvbase + 2 * i + 1 > col_limit) e.y = 0.f;
+    }
+    const float2 g = __ffma2_rn(make_float2(__uint_as_float(dv[2 * i]), __uint_as_float(dv[2 * i + 1])), c2, d2);
+    const float2 ds = __fmul2_rn(e, g);
+    pp[i] = pack_bf16x2(e.x, e.y);
+    dd[i] = pack_bf16x2(ds.x, ds.y);
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(FB_THREADS, 1)
 fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -134,12 +158,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         const int s = t % QST;
         const uint32_t ph = (t / QST) & 1;
         const int qrow0 = (i0 + t) * 128;
-        mbar_wait(&q_empty[s], ph ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
+        // once a wait has given up, nothing more is loaded: loads without a free slot would pile transaction counts
+        // on one barrier beyond its range
+        if (!mbar_wait(&q_empty[s], ph ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY)) break;
         mbar_expect_tx(&q_full[s], L::TILE);
 #pragma unroll
         for (int c = 0; c < KCH; ++c)
           tma_load_4d(smem + L::Q_OFF + s * L::TILE + c * 16384, &map_q, &q_full[s], c * 64, h, qrow0, b);
-        mbar_wait(&do_empty[s], ph ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
+        if (!mbar_wait(&do_empty[s], ph ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY)) break;
         mbar_expect_tx(&do_full[s], L::TILE);
 #pragma unroll
         for (int c = 0; c < KCH; ++c)
@@ -242,19 +268,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         tmem_ld32(tmem_base + TM_DP + c * 32 + lane_off, dv);
         tmem_wait_ld();
         uint32_t pp[16], dd[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          float p0 = exp2f(__uint_as_float(sv[2 * i]) * sl2 - Lr);
-          float p1 = exp2f(__uint_as_float(sv[2 * i + 1]) * sl2 - Lr);
-          if (need_mask) {
-            if (kv0 + c * 32 + 2 * i > col_limit) p0 = 0.f;
-            if (kv0 + c * 32 + 2 * i + 1 > col_limit) p1 = 0.f;
-          }
-          float d0 = p0 * (__uint_as_float(dv[2 * i]) - dr) * p.scale;
-          float d1 = p1 * (__uint_as_float(dv[2 * i + 1]) - dr) * p.scale;
-          pp[i] = pack_bf16x2(p0, p1);
-          dd[i] = pack_bf16x2(d0, d1);
-        }
+        if (need_mask) fa_bwd_p_ds<true>(sv, dv, sl2, Lr, p.scale, dr, kv0 + c * 32, col_limit, pp, dd);
+        else fa_bwd_p_ds<false>(sv, dv, sl2, Lr, p.scale, dr, kv0 + c * 32, col_limit, pp, dd);
         // columns c*32 .. c*32+31 = four 16-byte chunks of sub-tile c/2 (64 keys per sub-tile)
         const int sub = c >> 1;
 #pragma unroll

@@ -52,6 +52,54 @@ struct FaFwdSmem {
   static constexpr int ALLOC = TOTAL + 1024;
 };
 
+// max of three fp32 values in one instruction (sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// Row maximum over this thread's 64 scores (two 32-column TMEM loads). MASK is a template parameter so that the
+// unmasked blocks (all but the diagonal and the ragged last one) carry no compare / select instructions at all.
+template <bool MASK>
+__device__ __forceinline__ float fa_row_max(const uint32_t (&v0)[32], const uint32_t (&v1)[32], int kv0, int col_limit) {
+  float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < 32; i += 2) {
+    float a0 = __uint_as_float(v0[i]), a1 = __uint_as_float(v0[i + 1]);
+    float b0 = __uint_as_float(v1[i]), b1 = __uint_as_float(v1[i + 1]);
+    if (MASK) {
+      if (kv0 + i > col_limit) a0 = -INFINITY;
+      if (kv0 + i + 1 > col_limit) a1 = -INFINITY;
+      if (kv0 + 32 + i > col_limit) b0 = -INFINITY;
+      if (kv0 + 32 + i + 1 > col_limit) b1 = -INFINITY;
+    }
+    m0 = fmax3(m0, a0, a1);
+    m1 = fmax3(m1, b0, b1);
+  }
+  return fmaxf(m0, m1);
+}
+
+// p = exp2(s * sl2 - moff) for 32 scores, packed to bf16 pairs; the scale-and-shift and the row sum run as packed
+// two-wide fp32 instructions (fma.rn.f32x2 / add.f32x2), so each pair costs one FFMA2, two MUFU.EX2, one FADD2 and
+// one pack.
+template <bool MASK>
+__device__ __forceinline__ void fa_exp_pack(const uint32_t (&v)[32], float sl2, float moff, int kvbase, int col_limit,
+                                            uint32_t (&pk)[16], float2& rowsum) {
+  const float2 s2 = make_float2(sl2, sl2), o2 = make_float2(-moff, -moff);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float2 t = __ffma2_rn(make_float2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1])), s2, o2);
+    float2 e = make_float2(exp2f(t.x), exp2f(t.y));
+    if (MASK) {
+      if (kvbase + 2 * i > col_limit) e.x = 0.f;
+      if (kvbase + 2 * i + 1 > col_limit) e.y = 0.f;
+    }
+    rowsum = __fadd2_rn(rowsum, e);
+    pk[i] = pack_bf16x2(e.x, e.y);
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -117,10 +165,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       tma_prefetch_desc(&map_k);
       tma_prefetch_desc(&map_v);
       uint32_t it = 0, tcount = 0;  // K/V blocks and tiles handled so far by this CTA
-      for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, ++tcount) {
+      // once a wait has given up, nothing more is loaded: loads without a free slot would pile transaction counts on
+      // one barrier beyond its range
+      for (int t = blockIdx.x; t < n_tiles && !*abort_flag; t += gridDim.x, ++tcount) {
         const int bh = t % BH, h = bh % p.H, b = bh / p.H, q0 = tile_qb(t) * FA_BM, n_kv = tile_nkv(t);
         const int qs = tcount & 1;
-        mbar_wait(&q_empty[qs], ((tcount >> 1) & 1) ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
+        if (!mbar_wait(&q_empty[qs], ((tcount >> 1) & 1) ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY)) break;
         mbar_expect_tx(&q_full[qs], L::TILE);
 #pragma unroll
         for (int c = 0; c < KCH; ++c)
@@ -128,12 +178,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         for (int j = 0; j < n_kv; ++j, ++it) {
           const int s = it & 1;
           const uint32_t ph = (it >> 1) & 1;
-          mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
+          if (!mbar_wait(&k_empty[s], ph ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY)) break;
           mbar_expect_tx(&k_full[s], L::TILE);
 #pragma unroll
           for (int c = 0; c < KCH; ++c)
             tma_load_4d(smem + L::K_OFF + s * L::TILE + c * 16384, &map_k, &k_full[s], c * 64, h, j * FA_BN, b);
-          mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
+          if (!mbar_wait(&v_empty[s], ph ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY)) break;
           mbar_expect_tx(&v_full[s], L::TILE);
 #pragma unroll
           for (int c = 0; c < KCH; ++c)
@@ -240,8 +290,14 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
         uint32_t v[32];
         tmem_ld32(tmem_base + TM_O + half * DH + c * 32 + lane_off, v);
         tmem_wait_ld();
+        const float2 a2 = make_float2(alpha_prev, alpha_prev);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+        for (int i = 0; i < 32; i += 2) {
+          const float2 r = __ffma2_rn(make_float2(o[c * 32 + i], o[c * 32 + i + 1]), a2,
+                                      make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+          o[c * 32 + i] = r.x;
+          o[c * 32 + i + 1] = r.y;
+        }
       }
       tc_fence_before();
       mbar_arrive(o_empty);
@@ -259,47 +315,23 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       tmem_ld32(ts, v0);
       tmem_ld32(ts + 32, v1);
       tmem_wait_ld();
-      float mx = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float x0 = __uint_as_float(v0[i]), x1 = __uint_as_float(v1[i]);
-        if (need_mask) {
-          if (kv0 + i > col_limit) x0 = -INFINITY;
-          if (kv0 + 32 + i > col_limit) x1 = -INFINITY;
-        }
-        mx = fmaxf(mx, fmaxf(x0, x1));
-      }
+      float mx = need_mask ? fa_row_max<true>(v0, v1, kv0, col_limit) : fa_row_max<false>(v0, v1, kv0, col_limit);
       xmax[s * 256 + half * 128 + row] = mx;
       asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");  // only the two warps that share these rows
-      mx = fmaxf(m, fmaxf(mx, xmax[s * 256 + (half ^ 1) * 128 + row]));
+      mx = fmax3(m, mx, xmax[s * 256 + (half ^ 1) * 128 + row]);
       const float msafe = (mx == -INFINITY) ? 0.f : mx;
       const float alpha = exp2f((m - msafe) * sl2);
       const float moff = msafe * sl2;
-      float rowsum = 0.f;
+      float2 rs2 = make_float2(0.f, 0.f);
       const uint32_t tp = tmem_base + TM_P + s * 64 + half * 32 + lane_off;
       uint32_t pk[16];
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float p0 = exp2f(__uint_as_float(v0[2 * i]) * sl2 - moff), p1 = exp2f(__uint_as_float(v0[2 * i + 1]) * sl2 - moff);
-        if (need_mask) {
-          if (kv0 + 2 * i > col_limit) p0 = 0.f;
-          if (kv0 + 2 * i + 1 > col_limit) p1 = 0.f;
-        }
-        rowsum += p0 + p1;
-        pk[i] = pack_bf16x2(p0, p1);
-      }
+      if (need_mask) fa_exp_pack<true>(v0, sl2, moff, kv0, col_limit, pk, rs2);
+      else fa_exp_pack<false>(v0, sl2, moff, kv0, col_limit, pk, rs2);
       tmem_st16(tp, pk);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float p0 = exp2f(__uint_as_float(v1[2 * i]) * sl2 - moff), p1 = exp2f(__uint_as_float(v1[2 * i + 1]) * sl2 - moff);
-        if (need_mask) {
-          if (kv0 + 32 + 2 * i > col_limit) p0 = 0.f;
-          if (kv0 + 32 + 2 * i + 1 > col_limit) p1 = 0.f;
-        }
-        rowsum += p0 + p1;
-        pk[i] = pack_bf16x2(p0, p1);
-      }
+      if (need_mask) fa_exp_pack<true>(v1, sl2, moff, kv0 + 32, col_limit, pk, rs2);
+      else fa_exp_pack<false>(v1, sl2, moff, kv0 + 32, col_limit, pk, rs2);
       tmem_st16(tp + 16, pk);
+      const float rowsum = rs2.x + rs2.y;
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[s]);

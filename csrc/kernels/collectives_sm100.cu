@@ -79,7 +79,8 @@ __global__ void __launch_bounds__(COMM_THREADS)
 allreduce_kernel(const CommArgs a) {
   constexpr int N = Acc<T>::N;
   const uint32_t epoch = *a.epoch_ptr;
-  cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch, a.status);
+  // a failed entry barrier means some peer's data is not known to be complete: touch nothing
+  if (!cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch, a.status)) return;
   const long tid = (long)blockIdx.x * blockDim.x + threadIdx.x;
   const long nthreads = (long)gridDim.x * blockDim.x;
   if (MODE == 0) {
@@ -100,7 +101,8 @@ allreduce_kernel(const CommArgs a) {
         for (int j = 0; j < N; ++j) acc[cnt][j] += f[j];
       }
     }
-    cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch + 1, a.status);
+    // without the second barrier a peer may still be reading this rank's copy: leave it as it is
+    if (!cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch + 1, a.status)) return;
     cnt = 0;
     for (long v = tid; v < nvec && cnt < 4; v += nthreads, ++cnt) {
 #pragma unroll
@@ -163,7 +165,7 @@ template <bool NVLS>
 __global__ void __launch_bounds__(COMM_THREADS)
 allgather_kernel(const CommArgs a, int elem_bytes) {
   const uint32_t epoch = *a.epoch_ptr;
-  cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch, a.status);
+  if (!cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch, a.status)) return;
   const long bytes = a.n * elem_bytes;  // launcher guarantees a multiple of 16
   const long nvec = bytes / 16;
   const long base = a.byte_off + (long)a.rank * bytes;
@@ -201,7 +203,7 @@ __global__ void __launch_bounds__(COMM_THREADS)
 reducescatter_kernel(const CommArgs a, T* __restrict__ out) {
   constexpr int N = Acc<T>::N;
   const uint32_t epoch = *a.epoch_ptr;
-  cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch, a.status);
+  if (!cta_barrier_all_ranks(a.flags, blockIdx.x, a.rank, a.world, 2 * epoch, a.status)) return;
   const long nvec = a.n / N;
   const long base = a.byte_off + (long)a.rank * a.n * (long)sizeof(T);
   constexpr int U = 4;  // vectors in flight per thread
@@ -277,6 +279,8 @@ rs_finalize_kernel(const CommArgs a, const TA* __restrict__ acc, const bf16* __r
     }
     __syncthreads();
   }
+  // the slots are complete only if the entry barrier went through; otherwise leave the output alone
+  if (a.status && *((volatile int*)a.status) != 0) return;
   const uint32_t nvec = (uint32_t)(rows * N / 8);
   const uint32_t vec_per_row = (uint32_t)N / 8;
   const long slot = rows * N;

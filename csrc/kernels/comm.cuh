@@ -8,7 +8,8 @@
 // own flags[slot][q] >= epoch for every q, with acquire loads. Each slot belongs to one CTA (or
 // one logical barrier), each word has a single writer, values only grow, so no reset is needed.
 // Every wait is bounded (about one second): on expiry the kernel records TB_ERR_WAIT_PEER in the
-// launch's status word and carries on, so a dead or late peer can never hang the GPU.
+// launch's status word and the barrier reports failure, so a dead or late peer can never hang the GPU
+// and the caller can skip the work that depended on the peers.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -58,18 +59,23 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* flag, uint32_t targ
 // Cross-rank barrier for the calling CTA on flag slot `slot`. All threads of the CTA must call it.
 // `flags` is the peer table of the flag arrays, `epoch` the value of this barrier instance.
 // Orders all prior global writes of this CTA (to any GPU) before the peers' subsequent reads.
-__device__ __forceinline__ void cta_barrier_all_ranks(const PeerTable& flags, int slot, int rank, int world,
+// Returns true when every peer arrived; false (the same value in every thread of the CTA) when a wait
+// ran out or the launch's status word was already set. A caller whose ENTRY barrier failed must not
+// touch peer data: the peers' buffers may be half written, and nothing orders this rank against them.
+__device__ __forceinline__ bool cta_barrier_all_ranks(const PeerTable& flags, int slot, int rank, int world,
                                                       uint32_t epoch, int* status) {
   __syncthreads();
+  int ok = 1;
   if (threadIdx.x < world) {
     fence_sys();
     uint32_t* remote = reinterpret_cast<uint32_t*>(flags.ptr[threadIdx.x]) + (size_t)slot * MAX_RANKS + rank;
     st_release_sys(remote, epoch);
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(flags.ptr[rank]) + (size_t)slot * MAX_RANKS + threadIdx.x;
-    wait_flag_ge(mine, epoch, status);
+    ok = wait_flag_ge(mine, epoch, status) ? 1 : 0;
+    if (status && *((volatile int*)status) != 0) ok = 0;  // an earlier wait of this launch (any CTA) gave up
     fence_sys();
   }
-  __syncthreads();
+  return __syncthreads_and(ok) != 0;
 }
 
 // ---------------------------------------------------------------- multimem (NVLS)

@@ -15,6 +15,7 @@
 // (crates/torsh-backend/src/kernel_generation/types/cuda_compiler.rs:104-167) and its
 // unwired cuBLAS call (crates/torsh-backend/src/cuda/backend.rs:695-726).
 #include "comm.cuh"
+#include "fsdp_gather.cuh"
 #include "host_util.h"
 #include <stdlib.h>
 #include <string.h>
@@ -83,6 +84,13 @@ struct GemmParams {
                              // TN images x TH image rows (<= 64 pixels; unused K rows of a stage stay zero), both
                              // operands are 4-D boxes read MN-major, every 64-column chunk of B carries its own tap
   int cv_H, cv_W, cv_TH, cv_TN, cv_tiles_h, cv_cchunks, cv_a_bytes, cv_N;
+  // FSDP un-shard fused into the unit's first GEMM: the first ag_ctas CTAs pull every rank's shard of the unit into
+  // the local unit buffer (fsdp_gather.cuh) while the GEMM CTAs work; B lies inside that buffer at byte offset
+  // wg_b_off with rows of wg_ldb_bytes, and the TMA producer waits for the chunks that cover each B tile (K-major B:
+  // BN whole rows per tile; MN-major B: 64 whole rows per K block) before loading it.
+  int wg_on;
+  long wg_b_off, wg_ldb_bytes;
+  GatherArgs wg;
 };
 
 template <int BN, int STAGES>
@@ -228,9 +236,10 @@ __device__ __forceinline__ void ag_copy_role(const GemmParams& p, uint8_t* smem,
     for (int b = 0; b < NBUF; ++b) mbar_init(&bars[b], 1);
     fence_barrier_init();
   }
-  // every rank's shard is complete once its kernel has started (stream order on that rank)
-  cta_barrier_all_ranks(flags, blockIdx.x, p.rank, p.world, 2 * epoch, p.status);
-  if (threadIdx.x == 0) {
+  // every rank's shard is complete once its kernel has started (stream order on that rank); without that
+  // guarantee (a peer late beyond the wait limit) nothing is copied and the GEMM side gives up on its first flag
+  const bool entry_ok = cta_barrier_all_ranks(flags, blockIdx.x, p.rank, p.world, 2 * epoch, p.status);
+  if (entry_ok && threadIdx.x == 0) {
     // Work units: (peer, 128-row tile, part), peers nearest first, ag_split parts per tile so that a short shard
     // still keeps every copy CTA busy; this CTA takes the units blockIdx.x, blockIdx.x + ag_ctas, ... Their 16 KB
     // pieces form one stream that is pipelined through the ring: up to NBUF - 1 peer loads are in flight while the
@@ -263,6 +272,31 @@ __device__ __forceinline__ void ag_copy_role(const GemmParams& p, uint8_t* smem,
       mbar_expect_tx(&bars[b], PIECE);
       bulk_load(smem + b * PIECE, src, PIECE, &bars[b]);
     };
+    // A part of a tile is published once the stores of all its pieces have completed. Stores complete in order, so
+    // instead of draining the store queue at every part boundary (a full write round trip every few pieces),
+    // publication runs LAG pieces behind the store just issued.
+    constexpr int LAG = 16;  // a global write takes a few microseconds to complete: keep many stores in flight
+    long pub = 0;  // every part that ends before piece `pub` has been published
+    auto publish_upto = [&](long done) {  // stores of pieces [0, done) are complete
+      bool fenced = false;
+      while (pub + pieces <= done) {
+        const char* src; char* dst; int q, t, piece;
+        locate(pub + pieces - 1, src, dst, q, t, piece);
+        if (!fenced) {
+          __threadfence();
+          fenced = true;
+        }
+        const int tile = q * tiles_per_rank + t;
+        uint32_t* cnt = p.ag_ready + p.tiles_m + tile;
+        uint32_t arrived;
+        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(cnt) : "memory");
+        if (arrived == (uint32_t)split - 1) {  // last part: reset the counter for the next launch, publish the tile
+          *cnt = 0;
+          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ag_ready + tile), "r"(epoch) : "memory");
+        }
+        pub += pieces;
+      }
+    };
     long next_load = 0;
     for (; next_load < total && next_load < NBUF; ++next_load) issue_load(next_load);
     for (long i = 0; i < total; ++i) {
@@ -277,20 +311,13 @@ __device__ __forceinline__ void ag_copy_role(const GemmParams& p, uint8_t* smem,
         issue_load(next_load);                                        // piece i - 1 + NBUF goes into that buffer
         ++next_load;
       }
-      if (piece == pieces - 1) {
-        bulk_wait_all();  // this part of the tile is in local memory
-        __threadfence();
-        const int tile = q * tiles_per_rank + t;
-        uint32_t* cnt = p.ag_ready + p.tiles_m + tile;
-        uint32_t arrived;
-        asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(arrived) : "l"(cnt) : "memory");
-        if (arrived == (uint32_t)split - 1) {  // last part: reset the counter for the next launch, publish the tile
-          *cnt = 0;
-          asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ag_ready + tile), "r"(epoch) : "memory");
-        }
+      if (i >= LAG) {
+        asm volatile("cp.async.bulk.wait_group %0;" ::"n"(LAG) : "memory");
+        publish_upto(i - LAG + 1);
       }
     }
     bulk_wait_all();
+    publish_upto(total);
     if (*abort_flag) {
       uint64_t t0 = globaltimer_ns();
       while (globaltimer_ns() - t0 < 2000000ull) {
@@ -382,7 +409,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
 
   if (p.ag_ctas > 0 && (int)blockIdx.x < p.ag_ctas) {
-    ag_copy_role<L::BAR_OFFSET>(p, smem, full, abort_flag);
+    if (p.wg_on) unit_gather_role<L::BAR_OFFSET>(p.wg, (int)blockIdx.x, smem, full, abort_flag);
+    else ag_copy_role<L::BAR_OFFSET>(p, smem, full, abort_flag);
     return;
   }
   // GEMM CTAs are numbered from 0 after the copy CTAs
@@ -426,14 +454,34 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       WorkIter it(p, worker, nworkers);
       int m_t, n_t, kb0, kb1;
-      while (it.next(p, m_t, n_t, kb0, kb1)) {
-        if (p.ag_ctas > 0 && (m_t * BM) / p.ag_rows != p.rank) {
+      // FSDP weight gather: chunks of the unit buffer this thread has already seen ready (indices below 64)
+      uint64_t wg_seen = 0;
+      auto wg_wait = [&](long byte0, long byte1) {
+        const int c0 = (int)(byte0 / p.wg.chunk_bytes), c1 = (int)((byte1 - 1) / p.wg.chunk_bytes);
+        bool waited = false;
+        for (int c = c0; c <= c1; ++c) {
+          if (c < 64 && ((wg_seen >> c) & 1ull)) continue;
+          if (!*abort_flag && !wait_ready_gpu(p.wg.ready + c, ag_epoch, p.status)) *abort_flag = 1;
+          if (c < 64) wg_seen |= 1ull << c;
+          waited = true;
+        }
+        if (waited) fence_proxy_async_all();  // the chunk was written through the async proxy of another CTA
+      };
+      // Once any wait of this thread has given up (abort flag), nothing more is loaded: loads issued without a free
+      // stage would pile transaction counts on one barrier beyond its range. The MMA and epilogue roles see the flag
+      // too, stop waiting and drain their finite loops on whatever the stages hold.
+      while (!*abort_flag && it.next(p, m_t, n_t, kb0, kb1)) {
+        if (p.wg_on && B_MAJOR == 0)
+          wg_wait(p.wg_b_off + (long)n_t * BN * p.wg_ldb_bytes, p.wg_b_off + (long)min(p.N, (n_t + 1) * BN) * p.wg_ldb_bytes);
+        if (!p.wg_on && p.ag_ctas > 0 && (m_t * BM) / p.ag_rows != p.rank) {
           // rows of a peer: wait (bounded) until the copy CTAs have landed this 128-row tile locally
           if (!*abort_flag && !wait_flag_ge_gpu(p.ag_ready + m_t, ag_epoch, p.status)) *abort_flag = 1;
           fence_proxy_async_all();
         }
         for (int kb = kb0; kb < kb1; ++kb) {
-          mbar_wait(&empty[s], phase ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
+          if (p.wg_on && B_MAJOR == 1)
+            wg_wait(p.wg_b_off + (long)kb * BK * p.wg_ldb_bytes, p.wg_b_off + (long)min(p.K, (kb + 1) * BK) * p.wg_ldb_bytes);
+          if (*abort_flag || !mbar_wait(&empty[s], phase ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY)) break;
           uint8_t* sa = smem + s * L::STAGE_BYTES;
           uint8_t* sb = sa + A_TILE_BYTES;
           mbar_expect_tx(&full[s], p.conv == 3 ? (uint32_t)(p.cv_a_bytes * (BM / 64 + BN / 64))
@@ -772,6 +820,9 @@ struct TpFusion {
   int copy_ctas = 0;                    // kind 2
   // implicit-GEMM convolution (kind 3): A is the channels-last activation [cv_n, cv_h, cv_w, K / 9]
   int cv_n = 0, cv_h = 0, cv_w = 0, cv_mode = 0;
+  // FSDP unit gather fused into this GEMM (kind 5): B lies at byte offset wg_b_off of the unit buffer wg.dst
+  GatherArgs wg{};
+  long wg_b_off = 0;
 };
 
 static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, int K, int a_major,
@@ -945,6 +996,19 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
     }
     p.epoch_ptr = tp.epoch_ptr;
     p.m_rot = tp.rank * (p.ag_rows / BM);  // own shard first
+  } else if (tp.kind == 5) {
+    if (split_k != 1 || stream_k) TB_FAIL(TB_E_ARG, "fsdp_ag_gemm: no split-K");
+    const long b_bytes = (long)(b_major == 0 ? N : K) * ldb * 2;
+    const long unit_bytes = (long)tp.wg.world * tp.wg.cpr * tp.wg.chunk_bytes;
+    if (tp.wg_b_off < 0 || tp.wg_b_off + b_bytes > unit_bytes || (const char*)B != (const char*)tp.wg.dst + tp.wg_b_off)
+      TB_FAIL(TB_E_ARG, "fsdp_ag_gemm: B must lie inside the unit buffer at the given offset");
+    p.ag_ctas = tp.wg.ctas;
+    p.wg_on = 1;
+    p.wg = tp.wg;
+    p.wg.status = status;
+    p.wg_b_off = tp.wg_b_off;
+    p.wg_ldb_bytes = (long)ldb * 2;
+    p.epoch_ptr = tp.wg.epoch_ptr;
   }
 
   CUtensorMap ma, mb;
@@ -1028,6 +1092,57 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
 }
 
 __global__ void gemm_bump_epoch_kernel(uint32_t* e) { *e += 1; }
+
+// Checks and fills the description of one unit gather (shared by the fused and the stand-alone launcher).
+int tb_fill_gather(tb::GatherArgs& g, const void* const* shards, void* unit_buf, const void* const* flag_bufs,
+                   const unsigned* epoch_ptr, unsigned* ready, int chunk_bytes, int cpr, int first_chunk, int rank,
+                   int world, int ctas, int* status) {
+  if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) TB_FAIL(TB_E_ARG, "fsdp gather: bad rank/world %d/%d", rank, world);
+  if (chunk_bytes < GATHER_PIECE || (chunk_bytes & (chunk_bytes - 1))) TB_FAIL(TB_E_ARG, "fsdp gather: chunk bytes (%d) must be a power of two >= 16384", chunk_bytes);
+  if (cpr < 1 || first_chunk < 0 || first_chunk >= world * cpr) TB_FAIL(TB_E_ARG, "fsdp gather: bad chunk counts");
+  if (!unit_buf || !ready || !epoch_ptr || ((uintptr_t)unit_buf & 15)) TB_FAIL(TB_E_ARG, "fsdp gather: null or unaligned buffer");
+  if (ctas < 1 || ctas > 128) TB_FAIL(TB_E_ARG, "fsdp gather: copy CTAs must be in [1, 128]");
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    g.src[i] = i < world ? shards[i] : nullptr;
+    g.flag_tbl[i] = i < world ? const_cast<void*>(flag_bufs[i]) : nullptr;
+    if (i < world && (!shards[i] || ((uintptr_t)shards[i] & 15))) TB_FAIL(TB_E_ARG, "fsdp gather: null or unaligned shard");
+  }
+  g.dst = unit_buf; g.epoch_ptr = epoch_ptr; g.ready = ready; g.chunk_bytes = chunk_bytes; g.cpr = cpr;
+  g.first = first_chunk; g.ctas = ctas; g.rank = rank; g.world = world; g.status = status;
+  return 0;
+}
+
+// The GEMM that first consumes an FSDP unit, fused with the unit's un-shard: D = epilogue(A * op(B)^T) as tb_gemm_bf16,
+// where B lives at byte offset b_off of the local unit buffer `unit_buf` that `copy_ctas` extra CTAs fill from every
+// rank's shard (shards[r]: rank r's cpr chunks of chunk_bytes each, in symmetric memory) while the GEMM CTAs compute;
+// the chunk that holds the start of B is fetched first. ready: local uint32 [2 * world * cpr], zero before first use.
+// When the kernel has finished, the whole unit is in unit_buf. One communication context (flag_bufs, epoch_ptr) per
+// stream; the launch bumps its epoch.
+TB_EXPORT int tb_fsdp_ag_gemm(const void* A, const void* B, void* D, int M, int N, int K, int a_major, int b_major,
+                              int lda, int ldb, int ldd, const void* bias, const void* residual, int ldr, void* preact,
+                              const void* aux, int flags, int bn, const void* const* shards, void* unit_buf,
+                              const void* const* flag_bufs, const unsigned* epoch_ptr, unsigned* ready, int chunk_bytes,
+                              int cpr, long b_off, int rank, int world, int copy_ctas, int* status,
+                              cudaStream_t stream) {
+  TB_ENSURE_DEVICE();
+  if (flags & (EPI_ATOMIC | EPI_ACCUM)) TB_FAIL(TB_E_ARG, "fsdp_ag_gemm: plain outputs only");
+  if (ldb != (b_major == 0 ? K : N)) TB_FAIL(TB_E_ARG, "fsdp_ag_gemm: B must be contiguous (ldb %d)", ldb);
+  TpFusion tp;
+  tp.kind = 5;
+  if (copy_ctas < 1) copy_ctas = 16;
+  if (copy_ctas > 64) copy_ctas = 64;
+  int r = tb_fill_gather(tp.wg, shards, unit_buf, flag_bufs, epoch_ptr, ready, chunk_bytes, cpr,
+                         (int)(b_off / chunk_bytes) % (world * cpr > 0 ? world * cpr : 1), rank, world, copy_ctas, status);
+  if (r) return r;
+  tp.wg_b_off = b_off;
+  tp.rank = rank; tp.world = world;
+  r = gemm_dispatch(A, B, D, M, N, K, a_major, b_major, lda, ldb, ldd, bias, residual, ldr, preact, aux, flags, 1, bn,
+                    status, stream, tp);
+  if (r) return r;
+  gemm_bump_epoch_kernel<<<1, 1, 0, stream>>>(const_cast<unsigned*>(epoch_ptr));
+  TB_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
 
 TB_EXPORT int tb_ag_gemm(void* a_full, const void* const* shards, const void* const* flag_bufs,
                          const unsigned* epoch_ptr, unsigned* ready, const void* B, void* D, int M, int N, int K,

@@ -51,8 +51,9 @@ inline int ensure_device() {
   static thread_local int bound = -1;
   const int want = g_device().load(std::memory_order_relaxed);
   if (bound != want) {
+    // cudaSetDevice initialises the device's primary context and makes it current on this thread (CUDA 12
+    // semantics); no allocation routine is involved, which the allocation-free entry points rely on
     TB_CUDA_CHECK(cudaSetDevice(want));
-    TB_CUDA_CHECK(cudaFree(0));  // binds the primary context to this thread
     bound = want;
   }
   return 0;

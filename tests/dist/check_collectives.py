@@ -93,21 +93,36 @@ def check_collectives(dev):
 
 
 def check_fsdp(dev):
-    """2+ ranks of the fused FSDP step must reproduce a single-process AdamW run on the global batch."""
+    """2+ ranks of every FSDP strategy must reproduce a single-process AdamW run on the global batch: the loss of every
+    step within 0.2 % of the oracle's, parameters bit-identical on every rank, and after six steps every weight matrix
+    within 1 % (relative L2) of the oracle's. Element-wise equality with the oracle is not expected: the gradient sums
+    are formed in a different order, and AdamW turns the rounding noise of gradients that are zero in exact arithmetic
+    (the key bias of an attention layer) into full-size steps."""
     from torsh_b200 import _native as nv
     from torsh_b200.engine import CausalLMTrainer
     from torsh_b200.models import GPT2Config, GPTForCausalLM
-    from torsh_b200.parallel.fsdp import FlatFSDP, FsdpConfig
+    from torsh_b200.parallel.fsdp import FlatFSDP, FsdpConfig, ShardingStrategy
     rank, world = dist.get_rank(), dist.get_world_size()
     cfg = GPT2Config.tiny()
     B, S, steps = 4, 128, 6
     data = torch.randint(0, cfg.vocab_size, (world * B, S + 1), generator=torch.Generator().manual_seed(7))
     ok = True
-    ref_losses = None
-    for overlap, use_graph in ((False, False), (False, True), (True, False), (True, True)):
+    # single-process oracle on the global batch (this rank's GPU, plain flat AdamW)
+    torch.manual_seed(0)
+    m1 = GPTForCausalLM(cfg).to(dev)
+    t1 = CausalLMTrainer(m1, lr=1e-3, weight_decay=0.01, batch_size=world * B, seq_len=S, use_graph=False)
+    gx, gy = data[:, :-1].contiguous().pin_memory(), data[:, 1:].contiguous().pin_memory()
+    ref_losses = [t1.step(gx, gy) for _ in range(steps)]
+    ref_params = {n: p.detach().float().clone() for n, p in m1.named_parameters()}
+    log(f"single-process oracle: {[round(v, 4) for v in ref_losses]}")
+    FS, SGO, NS = ShardingStrategy.FULL_SHARD, ShardingStrategy.SHARD_GRAD_OP, ShardingStrategy.NO_SHARD
+    cases = [(SGO, dict(overlap=False), False), (SGO, dict(overlap=False), True), (SGO, dict(overlap=True), False),
+             (SGO, dict(overlap=True), True), (FS, dict(fuse_gather=True), False), (FS, dict(fuse_gather=True), True),
+             (FS, dict(fuse_gather=False), True), (NS, dict(), True)]
+    for strategy, kw, use_graph in cases:
         torch.manual_seed(0)
         model = GPTForCausalLM(cfg).to(dev)
-        eng = FlatFSDP(config=FsdpConfig(overlap=overlap))
+        eng = FlatFSDP(config=FsdpConfig(sharding_strategy=strategy, **kw))
         tr = CausalLMTrainer(model, lr=1e-3, weight_decay=0.01, batch_size=B, seq_len=S, use_graph=use_graph,
                              warmup_eager=2, parallel=eng)
         mine = data[rank * B:(rank + 1) * B]
@@ -119,23 +134,27 @@ def check_fsdp(dev):
             losses.append(l.item() / world)
         torch.cuda.synchronize()
         nv.check_status()
-        # parameters must be bit-identical on every rank
-        flat = tr.flat.lowp.float()
+        if strategy is FS:
+            got = {n: v.float() for n, v in tr.flat.full_state_dict(model).items()}
+            flat = torch.cat([v.reshape(-1) for v in got.values()])
+        else:
+            got = {n: p.detach().float() for n, p in model.named_parameters()}
+            flat = tr.flat.lowp.float()
         mx = flat.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         mn = flat.clone(); dist.all_reduce(mn, op=dist.ReduceOp.MIN)
         same = torch.equal(mx, mn)
-        log(f"fsdp overlap={overlap} graph={use_graph}: losses {[round(v, 4) for v in losses]} params identical={same}")
-        ok &= same and losses[-1] < losses[0] - 0.5
-        if ref_losses is None:
-            # single-process oracle on the global batch (rank 0's GPU, plain flat AdamW)
-            torch.manual_seed(0)
-            m1 = GPTForCausalLM(cfg).to(dev)
-            t1 = CausalLMTrainer(m1, lr=1e-3, weight_decay=0.01, batch_size=world * B, seq_len=S, use_graph=False)
-            gx, gy = data[:, :-1].contiguous().pin_memory(), data[:, 1:].contiguous().pin_memory()
-            ref_losses = [t1.step(gx, gy) for _ in range(steps)]
-            log(f"single-process oracle: {[round(v, 4) for v in ref_losses]}")
-        for a, b in zip(losses, ref_losses):
-            ok &= abs(a - b) < 0.03 * abs(b)
+        worst = 0.0
+        for n, v in got.items():
+            r = ref_params[n]
+            if r.dim() >= 2:
+                worst = max(worst, ((v - r).norm() / r.norm().clamp(min=1e-12)).item())
+        tag = f"{strategy.value} {kw} graph={use_graph}"
+        log(f"fsdp {tag}: losses {[round(v, 4) for v in losses]} identical across ranks={same} "
+            f"max relative L2 distance of a weight from the oracle {worst:.5f}; memory {eng.memory_report()}")
+        ok &= same and losses[-1] < losses[0] - 0.5 and worst <= 1e-2
+        for a_, b_ in zip(losses, ref_losses):
+            ok &= abs(a_ - b_) < 2e-3 * abs(b_)
+        del tr, eng, model
     return ok
 
 

@@ -128,7 +128,7 @@ def test_model_state_and_checkpoint_roundtrip(tmp_path):
     mgr = ck.CheckpointManager(tmp_path / "ck", max_to_keep=2)
     for s in range(4):
         mgr.save(m, o, epoch=0, global_step=s, metric=1.0 / (s + 1))
-    assert sorted(p.name for p in (tmp_path / "ck").iterdir()) == ["checkpoint_best.torsh", "checkpoint_epoch_0_step_2.torsh", "checkpoint_epoch_0_step_3.torsh"]
+    assert sorted(p.name for p in (tmp_path / "ck").iterdir()) == ["model_best.torsh", "model_epoch_0_step_2.torsh", "model_epoch_0_step_3.torsh"]
     c = mgr.load()
     m3 = nn.Sequential(nn.Linear(4, 3), nn.ReLU(), nn.Linear(3, 2)); o3 = optim.AdamW(m3.parameters())
     ck.restore_into(c, m3, o3)
@@ -749,3 +749,94 @@ def test_vision_zoo_reproduces_torchvision_logits():
         with torch.no_grad():
             want = ref(x)
             assert float(want.abs().max()) > 0 and torch.allclose(ours(x), want, atol=1e-4), name
+
+
+def test_torsh_checkpoint_golden_bytes():
+    """The ``.torsh`` payload, built by hand from the bincode "standard" rules (varint lengths, option tag bytes,
+    little-endian floats) for the reference's ``ModelCheckpoint`` field order and types
+    (``crates/torsh-nn/src/checkpoint.rs:24-113``)."""
+    import gzip
+    import struct
+    from torsh_b200.serialize import checkpoint as ck
+    doc = {"state_dict": {"w": [1.0, -2.0]}, "parameter_shapes": {"w": [2, 1]},
+           "metadata": {"model_name": "m", "model_version": "v1", "torsh_version": "0.1.3", "timestamp": "2026-01-01T00:00:00+00:00",
+                        "epoch": 3, "global_step": None, "best_metric": 0.5, "custom": {"k": "v"}},
+           "optimizer_state": {"optimizer_type": "SGD", "learning_rate": 0.1, "momentum_states": {"w": [0.25, 0.5]},
+                               "velocity_states": {}, "step_counts": {"w": 300}, "custom_state": {"c": [1.5]}},
+           "training_stats": {"train_losses": [1.0], "val_losses": [], "train_accuracies": [], "val_accuracies": [],
+                              "learning_rates": [0.1], "epoch_durations": [], "custom_metrics": {"f1": [0.75]}}}
+    f32 = lambda *v: struct.pack("<%df" % len(v), *v)
+    f64 = lambda *v: struct.pack("<%dd" % len(v), *v)
+    s = lambda t: bytes([len(t)]) + t.encode()
+    exp = b"".join([
+        b"\x01", s("w"), b"\x02", f32(1.0, -2.0),                      # state_dict
+        b"\x01", s("w"), b"\x02\x02\x01",                              # parameter_shapes
+        s("m"), s("v1"), s("0.1.3"), s("2026-01-01T00:00:00+00:00"),   # metadata strings (timestamp is a String)
+        b"\x01\x03", b"\x00", b"\x01", f64(0.5),                       # epoch Some(3), global_step None, best_metric Some
+        b"\x01", s("k"), s("v"),                                       # custom
+        b"\x01", s("SGD"), f64(0.1),                                   # optimizer_state Some
+        b"\x01", s("w"), b"\x02", f32(0.25, 0.5), b"\x00",             # momentum, velocity (empty)
+        b"\x01", s("w"), b"\xfb", struct.pack("<H", 300),              # step_counts: 300 needs the u16 varint form
+        b"\x01", s("c"), b"\x01", f32(1.5),                            # custom_state: Vec<f32> values
+        b"\x01", b"\x01", f64(1.0), b"\x00\x00\x00", b"\x01", f64(0.1), b"\x00",   # training_stats Some: six Vec<f64>
+        b"\x01", s("f1"), b"\x01", f64(0.75)])                         # custom_metrics
+    blob = ck.encode_checkpoint(doc)
+    assert gzip.decompress(blob) == exp
+    back = ck.decode_checkpoint(blob)
+    assert back["metadata"]["epoch"] == 3 and back["metadata"]["global_step"] is None
+    assert back["optimizer_state"]["step_counts"] == {"w": 300} and back["training_stats"]["custom_metrics"] == {"f1": [0.75]}
+    assert ck.CheckpointManager.__init__.__defaults__[0] == "model"
+
+
+def test_flat_adamw_resume_continues_the_loss_curve(tmp_path):
+    """Save master weights, moments and step count of the flat fused AdamW (its CPU path), restore into a fresh model and
+    optimizer, and get the same losses as the uninterrupted run."""
+    from torsh_b200.optim.flat import FlatAdamW, FlatParameters
+    from torsh_b200.serialize import checkpoint as ck
+
+    def make():
+        torch.manual_seed(3)
+        m = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Tanh(), torch.nn.Linear(16, 1))
+        return m, FlatAdamW(FlatParameters(m.parameters(), lowp_dtype=torch.float32), lr=1e-2)
+
+    x, y = torch.randn(32, 8, generator=torch.Generator().manual_seed(1)), torch.randn(32, 1, generator=torch.Generator().manual_seed(2))
+
+    def run(m, o, n):
+        out = []
+        for _ in range(n):
+            loss = (m(x) - y).pow(2).mean()
+            loss.backward()
+            o.step()
+            out.append(loss.item())
+        return out
+
+    m, o = make()
+    full = run(m, o, 8)
+    m1, o1 = make()
+    first = run(m1, o1, 4)
+    mgr = ck.CheckpointManager(tmp_path)
+    mgr.save(m1, o1, global_step=4)
+    m2, o2 = make()
+    run(m2, o2, 1)                      # a different state that the restore must fully replace
+    ck.restore_into(mgr.load(), m2, o2)
+    assert o2.step_count == 4
+    rest = run(m2, o2, 4)
+    assert first == full[:4] and all(abs(a - b) < 1e-6 for a, b in zip(rest, full[4:]))
+    sd = o1.state_dict()
+    m3, o3 = make()
+    o3.load_state_dict(sd)
+    assert torch.equal(o3.flat.master, o1.flat.master) and torch.equal(o3.flat.lowp, o1.flat.lowp) and o3.step_count == 4
+
+
+def test_trainer_raises_when_the_device_status_word_is_set():
+    """A failed cross-rank wait leaves a code in the device status word; the step's loss handle must raise instead of
+    letting training continue (here with host stand-ins for the pinned copies)."""
+    from torsh_b200 import _native as nv
+    from torsh_b200.engine import PendingLoss, _raise_on_status
+    ok = PendingLoss(torch.tensor(1.5), None, torch.zeros(4, dtype=torch.int32), None)
+    assert ok.value() == 1.5
+    bad = PendingLoss(torch.tensor(1.5), None, torch.tensor([105, 0, 0, 0], dtype=torch.int32), torch.ones(4, dtype=torch.int32))
+    with pytest.raises(nv.KernelTimeout, match="peer"):
+        bad.value()
+    with pytest.raises(nv.KernelTimeout):
+        _raise_on_status(101, None)

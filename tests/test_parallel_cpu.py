@@ -121,6 +121,54 @@ def _ddp_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+def _ddp_accum_worker(rank, world, port, q):
+    """Two micro-batches per step: the first under no_sync(), the second synchronising; the result must be the
+    rank-average of the per-rank sums. A second synchronising backward without sync_gradients() must raise."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torsh_b200.parallel.ddp import BucketConfig, DistributedDataParallel
+        torch.manual_seed(0)
+        net = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4))
+        ddp = DistributedDataParallel(net, bucket_config=BucketConfig(max_bucket_size_mb=0.002))
+        xs = [torch.randn(8, 16, generator=torch.Generator().manual_seed(100 * r + m)) for r in range(world) for m in range(2)]
+        mine = xs[2 * rank:2 * rank + 2]
+        with ddp.no_sync():
+            ddp(mine[0]).pow(2).mean().backward()
+        ddp(mine[1]).pow(2).mean().backward()
+        ddp.sync_gradients()
+        torch.manual_seed(0)
+        ref = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.Tanh(), torch.nn.Linear(32, 4))
+        for x in xs:
+            ref(x).pow(2).mean().backward()
+        ok = all(torch.allclose(p.grad, pr.grad / world, atol=1e-6) for p, pr in zip(net.parameters(), ref.parameters()))
+        # misuse: two synchronising backward passes in one step
+        ddp.zero_grad()
+        ddp(mine[0]).pow(2).mean().backward()
+        raised = False
+        try:
+            ddp(mine[1]).pow(2).mean().backward()
+        except RuntimeError as e:
+            raised = "no_sync" in str(e)
+        ddp.sync_gradients()
+        q.put((rank, bool(ok and raised)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ddp_gradient_accumulation_with_no_sync():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ddp_accum_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(30)
+    assert sorted(res) == [(0, True), (1, True)]
+
+
 def test_ddp_two_gloo_ranks_average_gradients():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -150,12 +198,13 @@ def _pp_worker(rank, world, port, q):
         loss_ref = sum(torch.nn.functional.mse_loss(ref(a), b) for a, b in zip(x.chunk(4), y.chunk(4))) / 4
         loss_ref.backward()
         ok = True
-        for sched in (ScheduleType.ONE_F_ONE_B, ScheduleType.GPIPE):
+        for sched, overlap in ((ScheduleType.ONE_F_ONE_B, True), (ScheduleType.GPIPE, True), (ScheduleType.ONE_F_ONE_B, False)):
             full.zero_grad()
             stages = create_pipeline_stages(list(full), world)
             shape = (2, 8)
-            pp = PipelineParallel(stages[rank], config=PipelineConfig(num_micro_batches=4, schedule=sched),
+            pp = PipelineParallel(stages[rank], config=PipelineConfig(num_micro_batches=4, schedule=sched, overlap=overlap),
                                   activation_shape=shape)
+            ok &= (len(pp._links) == 2) == overlap
             loss = pp.train_step(x if rank == 0 else None, y if rank == world - 1 else None, torch.nn.functional.mse_loss)
             if rank == world - 1:
                 ok &= abs(loss.item() - loss_ref.item()) < 1e-5
@@ -175,6 +224,92 @@ def test_pipeline_two_gloo_ranks_match_unsplit_model():
     q = ctx.Queue()
     port = _free_port()
     procs = [ctx.Process(target=_pp_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(30)
+    assert sorted(res) == [(0, True), (1, True)]
+
+
+def test_interleaved_schedule_covers_every_virtual_stage_in_dependency_order():
+    from torsh_b200.parallel import planner
+    P, M, V = 4, 8, 2
+    per_rank = [planner.pipeline_schedule_interleaved(r, P, M, V) for r in range(P)]
+    for r, acts in enumerate(per_rank):
+        assert len(acts) == 2 * M * V
+        assert sorted((mb, c) for k, mb, c in acts if k == "F") == sorted((mb, c) for mb in range(M) for c in range(V))
+        assert sorted((mb, c) for k, mb, c in acts if k == "B") == sorted((mb, c) for mb in range(M) for c in range(V))
+        warm = min((P - r - 1) * 2 + (V - 1) * P, M * V)
+        assert all(k == "F" for k, _, _ in acts[:warm]) and acts[warm + 1][0] == "B"
+        seen = set()
+        for k, mb, c in acts:
+            if k == "F":
+                assert c == 0 or (mb, c - 1) in seen      # a chunk runs after the rank's previous chunk of that micro-batch
+                seen.add((mb, c))
+            else:
+                assert (mb, c) in seen
+    # executing the four ranks in lock step never blocks: every receive has its matching send earlier in global order
+    pos = [0] * P
+    done = set()
+    progressed = True
+    while progressed:
+        progressed = False
+        for r in range(P):
+            while pos[r] < len(per_rank[r]):
+                k, mb, c = per_rank[r][pos[r]]
+                vs = c * P + r
+                need = ("F", mb, vs - 1) if (k == "F" and vs > 0) else (("B", mb, vs + 1) if (k == "B" and vs < P * V - 1) else None)
+                if k == "B" and vs == P * V - 1:
+                    need = ("F", mb, vs)
+                if need is not None and need not in done:
+                    break
+                done.add((k, mb, vs))
+                pos[r] += 1
+                progressed = True
+    assert all(pos[r] == len(per_rank[r]) for r in range(P))
+    with pytest.raises(ValueError):
+        planner.pipeline_schedule_interleaved(0, 4, 6, 2)
+
+
+def _pp_interleaved_worker(rank, world, port, q):
+    """Two ranks, two chunks each (virtual stages 0..3), four micro-batches: loss and every gradient must equal the
+    unsplit model's."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torsh_b200.parallel.pipeline import PipelineConfig, PipelineParallel, ScheduleType
+        torch.manual_seed(0)
+        mk = lambda: [torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.Tanh()) for _ in range(3)] + [torch.nn.Sequential(torch.nn.Linear(8, 8))]
+        full = mk()
+        ref = mk()
+        for a, b in zip(ref, full):
+            a.load_state_dict(b.state_dict())
+        x = torch.randn(8, 8, generator=torch.Generator().manual_seed(1))
+        y = torch.randn(8, 8, generator=torch.Generator().manual_seed(2))
+        run = lambda t: ref[3](ref[2](ref[1](ref[0](t))))
+        loss_ref = sum(torch.nn.functional.mse_loss(run(a), b) for a, b in zip(x.chunk(4), y.chunk(4))) / 4
+        loss_ref.backward()
+        chunks = [full[rank], full[rank + world]]          # virtual stage = chunk * world + rank
+        pp = PipelineParallel(chunks, config=PipelineConfig(num_micro_batches=4, schedule=ScheduleType.INTERLEAVED_ONE_F_ONE_B),
+                              activation_shape=(2, 8))
+        loss = pp.train_step(x if rank == 0 else None, y if rank == world - 1 else None, torch.nn.functional.mse_loss)
+        ok = len(pp._links) == 4
+        if rank == world - 1:
+            ok &= abs(loss.item() - loss_ref.item()) < 1e-5
+        for c, vs in enumerate((rank, rank + world)):
+            for p, pr in zip(chunks[c].parameters(), ref[vs].parameters()):
+                ok &= torch.allclose(p.grad, pr.grad, atol=1e-5)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_interleaved_pipeline_two_gloo_ranks_match_unsplit_model():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_pp_interleaved_worker, args=(r, 2, port, q)) for r in range(2)]
     for p in procs:
         p.start()
     res = [q.get(timeout=120) for _ in procs]

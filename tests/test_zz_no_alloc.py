@@ -68,6 +68,19 @@ def test_static_scratch_entry_point_matches_regular_one(dtype, rms):
         for a, b in zip(*outs):
             denom = b.abs().max().clamp(min=1e-6)
             assert ((a - b).abs().max() / denom).item() < tol
+        # and against a plain fp32 PyTorch evaluation of the same backward
+        xf = x.float().requires_grad_(True)
+        gf = gamma.float().requires_grad_(True)
+        bf = beta.float().requires_grad_(True)
+        if rms:
+            yf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * gf
+        else:
+            yf = torch.nn.functional.layer_norm(xf, (H,), gf, bf, 1e-5)
+        yf.backward(dy.float())
+        ref = (xf.grad + dres.float(), gf.grad, None if rms else bf.grad)
+        for a, r in zip(outs[1], ref):
+            if r is not None:
+                assert ((a - r).abs().max() / r.abs().max().clamp(min=1e-6)).item() < tol
 
 
 def test_static_scratch_rejects_oversized_requests():

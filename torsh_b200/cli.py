@@ -216,9 +216,10 @@ def cmd_train(a, cfg):
     step0 = 0
     if dev.type == "cuda" and lm:
         from .engine import CausalLMTrainer
-        trainer = CausalLMTrainer(model, lr=lr)
+        seq_len = min(a.seq, getattr(model.config, "n_positions", a.seq))
+        trainer = CausalLMTrainer(model, lr=lr, batch_size=bs, seq_len=seq_len, use_graph=False)
         step_fn = lambda ids, tgt: trainer.step(ids, tgt)
-        opt = None
+        opt = trainer.opt   # flat fused AdamW: checkpoints carry its master weights, moments and step count
     else:
         opt = torch.optim.AdamW(model.parameters(), lr=lr)
 
@@ -234,7 +235,8 @@ def cmd_train(a, cfg):
             ck = mgr.load()
             restore_into(ck, model, opt, strict=False)
             step0 = ck["metadata"]["global_step"]
-    seq = a.seq
+    seq = min(a.seq, getattr(model.config, "n_positions", a.seq)) if lm else a.seq
+    host_batches = dev.type == "cuda" and lm   # the trainer copies each batch from (pinned) host memory itself
     if lm:
         ds = SyntheticTokenDataset(model.config.vocab_size, seq, a.steps * bs, seed=0)
     history, t0 = [], time.time()
@@ -243,7 +245,8 @@ def cmd_train(a, cfg):
             break
         if lm:
             rows = [ds[(step - step0) * bs + i] for i in range(bs)]
-            x = torch.stack([r[0] for r in rows]).to(dev); y = torch.stack([r[1] for r in rows]).to(dev)
+            x = torch.stack([r[0] for r in rows]); y = torch.stack([r[1] for r in rows])
+            x, y = (x.pin_memory(), y.pin_memory()) if host_batches else (x.to(dev), y.to(dev))
         else:
             x = torch.randn(bs, 3, a.image, a.image, device=dev); y = torch.randint(0, 10, (bs,), device=dev)
         loss = float(step_fn(x, y))

@@ -16,15 +16,28 @@ from . import _native as nv
 from .optim.flat import FlatAdamW, FlatParameters
 
 
-class PendingLoss:
-    """The loss of a step that may still be running: :meth:`value` waits for that step's device→host copy only."""
+def _raise_on_status(code: int, status_dev) -> None:
+    """A bounded device-side wait of the step ran out (a peer rank late by more than the limit, a broken pipeline):
+    the kernels skipped the work that depended on it, so the optimizer state is intact but the step did not happen
+    on every rank. Stop here rather than let the next step run without cross-rank synchronisation."""
+    if code != 0:
+        if status_dev is not None:
+            status_dev.zero_()
+        raise nv.KernelTimeout(f"device status {code}: {nv._STATUS_NAMES.get(code, 'unknown')} (training step aborted)")
 
-    def __init__(self, buf: torch.Tensor, event):
-        self._buf, self._event = buf, event
+
+class PendingLoss:
+    """The loss of a step that may still be running: :meth:`value` waits for that step's device→host copy only and
+    raises :class:`KernelTimeout` if a kernel of that step recorded an error in the device status word."""
+
+    def __init__(self, buf: torch.Tensor, event, status_host=None, status_dev=None):
+        self._buf, self._event, self._status_host, self._status_dev = buf, event, status_host, status_dev
 
     def value(self) -> float:
         if self._event is not None:
             self._event.synchronize()
+        if self._status_host is not None:
+            _raise_on_status(int(self._status_host[0]), self._status_dev)
         return float(self._buf)
 
 
@@ -54,14 +67,21 @@ class CausalLMTrainer:
         self._loss_ring = [torch.zeros((), dtype=torch.float32).pin_memory() if cuda else torch.zeros(())
                            for _ in range(self.PIPELINE_SLOTS)]
         self._loss_events = [torch.cuda.Event() if cuda else None for _ in range(self.PIPELINE_SLOTS)]
+        # the device status word travels to the host next to the loss of every step (4 more bytes)
+        self._status_dev = nv.status_word(self.device) if cuda else None
+        self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory() if cuda else None
+        self._status_ring = [torch.zeros(4, dtype=torch.int32).pin_memory() if cuda else None
+                             for _ in range(self.PIPELINE_SLOTS)]
         self.graph = None
         self.steps_done = 0
         self.launches_per_step = 0
         self.h2d_bytes_per_step = 2 * batch_size * seq_len * 8
-        self.d2h_bytes_per_step = 4
+        self.d2h_bytes_per_step = 4 + (16 if cuda else 0)
 
     # ---- the device work of one step ------------------------------------------------------------
     def _device_step(self):
+        if self.parallel is not None and hasattr(self.parallel, "begin_step"):
+            self.parallel.begin_step()
         loss = self.model(self.static_ids, self.static_targets, loss_scale=1.0 / self.grad_accum)
         loss.backward()
         self.static_loss.copy_(loss.detach())
@@ -100,7 +120,9 @@ class CausalLMTrainer:
         self.step_device_only()
         if self.device.type == "cuda":
             self.loss_host.copy_(self.static_loss, non_blocking=True)
+            self._status_host.copy_(self._status_dev, non_blocking=True)
             torch.cuda.current_stream().synchronize()
+            _raise_on_status(int(self._status_host[0]), self._status_dev)
             return float(self.loss_host)
         return float(self.static_loss)
 
@@ -114,6 +136,9 @@ class CausalLMTrainer:
         slot = self.steps_done % self.PIPELINE_SLOTS
         buf, ev = self._loss_ring[slot], self._loss_events[slot]
         buf.copy_(self.static_loss, non_blocking=True)
+        sh = self._status_ring[slot]
+        if sh is not None:
+            sh.copy_(self._status_dev, non_blocking=True)
         if ev is not None:
             ev.record()
-        return PendingLoss(buf, ev)
+        return PendingLoss(buf, ev, sh, self._status_dev)

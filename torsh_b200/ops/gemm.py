@@ -34,6 +34,10 @@ def _lib():
         lib.tb_gemm_bf16.restype = ctypes.c_int
         lib.tb_gemm_bf16.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 8 + [ctypes.c_void_p] * 2 + [
             ctypes.c_int] + [ctypes.c_void_p] * 2 + [ctypes.c_int] * 3 + [ctypes.c_void_p] * 2
+        lib.tb_fsdp_ag_gemm.restype = ctypes.c_int
+        lib.tb_fsdp_ag_gemm.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 8 + [ctypes.c_void_p] * 2 + [
+            ctypes.c_int] + [ctypes.c_void_p] * 2 + [ctypes.c_int] * 2 + [ctypes.c_void_p] * 5 + [ctypes.c_int] * 2 + [
+            ctypes.c_int64] + [ctypes.c_int] * 3 + [ctypes.c_void_p] * 2
         _configured = True
     return lib
 
@@ -90,6 +94,19 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_major: int = 0, b_major: int = 0
     if raster_m:
         flags |= EPI_RASTER_M
     st = nv.status_word(a.device)
+    # FSDP full shard: the first GEMM that reads a weight of a unit whose un-shard is pending performs that un-shard
+    # itself (copy CTAs of the same launch pull the shards while the tiles are computed)
+    unit = getattr(b, "_tb_fsdp_unit", None)
+    if unit is not None:
+        g = unit[0].take_pending_gather(unit[1], b, fusable=(a_major == 0 and not atomic and not accumulate and split_k == 1))
+        if g is not None:
+            rc = _lib().tb_fsdp_ag_gemm(
+                a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a_major, b_major, a.stride(0), b.stride(0),
+                out.stride(0), nv.ptr(bias), nv.ptr(residual), residual.stride(0) if residual is not None else 0,
+                nv.ptr(preact_out), nv.ptr(dgelu_aux), flags, bn, *g, st.data_ptr(), nv.stream_ptr())
+            nv.check(rc, "tb_fsdp_ag_gemm")
+            nv.launch_count += 2
+            return out
     rc = _lib().tb_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a_major, b_major, a.stride(0), b.stride(0),
         out.stride(0), nv.ptr(bias), nv.ptr(residual), residual.stride(0) if residual is not None else 0,

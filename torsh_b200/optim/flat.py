@@ -123,6 +123,25 @@ class FlatAdamW:
     def zero_grad(self, set_to_none: bool = False):
         self.flat.zero_grad()
 
+    def state_dict(self) -> dict:
+        """fp32 master weights, both moments, the step count and the learning rate (flat tensors on the CPU)."""
+        f = self.flat
+        return {"step_count": self.step_count, "lr": self.param_groups[0]["lr"], "total": f.total,
+                "master": f.master.detach().cpu().clone(), "exp_avg": f.exp_avg.detach().cpu().clone(),
+                "exp_avg_sq": f.exp_avg_sq.detach().cpu().clone()}
+
+    @torch.no_grad()
+    def load_state_dict(self, sd: dict):
+        """Restores the master weights FIRST and refreshes the bf16 parameters from them: a restore that wrote only the
+        bf16 views would be undone by the next step, which rewrites them from the master copy."""
+        f = self.flat
+        if int(sd.get("total", f.total)) != f.total:
+            raise ValueError(f"optimizer state has {sd.get('total')} elements, this model has {f.total}")
+        f.master.copy_(sd["master"]); f.exp_avg.copy_(sd["exp_avg"]); f.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        f.lowp.copy_(f.master)
+        self.step_count = int(sd["step_count"])
+        self.param_groups[0]["lr"] = sd.get("lr", self.param_groups[0]["lr"])
+
     def grad_sq_norm(self) -> torch.Tensor:
         f = self.flat
         out = torch.zeros(1, dtype=torch.float32, device=f.device)

@@ -15,6 +15,7 @@ result in place on every rank. CPU tensors (gloo) take the same bucket path with
 """
 from __future__ import annotations
 
+import contextlib
 from dataclasses import dataclass
 
 import torch
@@ -64,6 +65,12 @@ class DistributedDataParallel(Module):
                     dist.broadcast(b.data, 0, group=self.group)
         self._ready = [0] * len(self.buckets)
         self._launched = [False] * len(self.buckets)
+        # False inside no_sync(): backward passes only accumulate locally (gradient accumulation over micro-batches)
+        self.require_backward_grad_sync = True
+        # the device status word of the step before is read (no host wait) at the next sync_gradients()
+        self._status_host = torch.zeros(4, dtype=torch.int32).pin_memory() if self.on_gpu else None
+        self._status_event = torch.cuda.Event() if self.on_gpu else None
+        self._status_queued = False
         for i, p in enumerate(self.params):
             p.register_post_accumulate_grad_hook(self._make_hook(i))
 
@@ -121,6 +128,13 @@ class DistributedDataParallel(Module):
                 view = self.flat_grad[self._offs[i]:self._offs[i] + p.numel()].view(p.shape)
                 view.copy_(p.grad)
                 p.grad = view
+            if not self.require_backward_grad_sync:
+                return  # no_sync(): the gradient stays a local sum; the synchronising backward reduces it
+            if self._launched[k]:
+                # the bucket was already averaged over the ranks in this step: adding another local gradient to it
+                # would give avg(first) + local(second), different on every rank
+                raise RuntimeError("DistributedDataParallel: a second backward() before sync_gradients(); run the "
+                                   "earlier micro-batches of an accumulation step under no_sync()")
             self._ready[k] += 1
             if self._ready[k] == len(self.buckets[k]) and self.overlap_cfg.enabled:
                 self._reduce_bucket(k)
@@ -148,6 +162,18 @@ class DistributedDataParallel(Module):
     def forward(self, *args, **kwargs):
         return self.module(*args, **kwargs)
 
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Backward passes inside this context accumulate gradients locally without any reduction; the first backward
+        after it (followed by :meth:`sync_gradients`) reduces the accumulated sum. The reference reduces only in its
+        explicit ``sync_gradients`` (``ddp.rs:555-672``), which gives the same accumulation semantics."""
+        old = self.require_backward_grad_sync
+        self.require_backward_grad_sync = False
+        try:
+            yield
+        finally:
+            self.require_backward_grad_sync = old
+
     def sync_gradients(self):
         """Finish the step's gradient synchronisation: reduce buckets whose hooks did not all fire (unused
         parameters), in ascending order on every rank, and join the comm stream. Call after ``backward()``."""
@@ -158,9 +184,28 @@ class DistributedDataParallel(Module):
                 self._reduce_bucket(k)
         if self.comm_stream is not None:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
+        self._check_device_status()
         self._ready = [0] * len(self.buckets)
         self._launched = [False] * len(self.buckets)
         self.stats["steps"] += 1
+
+    def _check_device_status(self):
+        """Raises :class:`KernelTimeout` when a collective kernel of the PREVIOUS step recorded a failed cross-rank wait
+        (it then skipped its reduction), and queues the copy of this step's status word; no host wait on the new step."""
+        if self.fused is None:
+            return
+        from .. import _native as nv
+        if self._status_queued:
+            self._status_event.synchronize()   # a whole step old: already complete
+            code = int(self._status_host[0])
+            if code != 0:
+                nv.status_word(self.device).zero_()
+                self._status_queued = False
+                raise nv.KernelTimeout(f"device status {code}: {nv._STATUS_NAMES.get(code, 'unknown')} "
+                                       f"(gradient all-reduce of the previous step did not complete on every rank)")
+        self._status_host.copy_(nv.status_word(self.device), non_blocking=True)
+        self._status_event.record()
+        self._status_queued = True
 
     def zero_grad(self, set_to_none: bool = False):
         """Keeps the gradient views alive (zeroing the flat buffer) so that no copy is ever needed."""

@@ -20,6 +20,7 @@ def _lib():
         lib.tsh_coords_of.argtypes = [i] * 5 + [ctypes.POINTER(i)] * 3
         lib.tsh_pipeline_schedule.argtypes = [i, i, i, i, ctypes.POINTER(ctypes.c_int32), i]
         lib.tsh_pipeline_peak_inflight.argtypes = [i, i, i, i]
+        lib.tsh_pipeline_schedule_interleaved.argtypes = [i, i, i, i, ctypes.POINTER(ctypes.c_int32), i]
         _cfg = True
     return lib
 
@@ -60,6 +61,17 @@ def pipeline_schedule(schedule: str, stage: int, num_stages: int, num_micro: int
     if n < 0:
         raise ValueError("bad pipeline schedule arguments")
     return [("F" if buf[2 * i] == 0 else "B", buf[2 * i + 1]) for i in range(n)]
+
+
+def pipeline_schedule_interleaved(stage: int, num_stages: int, num_micro: int, num_chunks: int) -> list[tuple[str, int, int]]:
+    """``[("F" | "B", micro_batch, chunk), ...]`` of the interleaved 1F1B schedule over ``num_chunks`` virtual stages per
+    rank (``num_micro`` must be a multiple of ``num_stages``)."""
+    cap = 2 * num_micro * num_chunks
+    buf = (ctypes.c_int32 * (3 * cap))()
+    n = _lib().tsh_pipeline_schedule_interleaved(stage, num_stages, num_micro, num_chunks, buf, cap)
+    if n < 0:
+        raise ValueError("interleaved schedule: num_micro must be a positive multiple of num_stages")
+    return [("F" if buf[3 * i] == 0 else "B", buf[3 * i + 1], buf[3 * i + 2]) for i in range(n)]
 
 
 def pipeline_peak_inflight(schedule: str, stage: int, num_stages: int, num_micro: int) -> int:
