@@ -235,12 +235,12 @@ TB_EXPORT int tb_fsdp_rs_adamw(const void* const* grads, const void* const* flag
 }
 
 namespace tb {
-constexpr int GATHER_SMEM = 8 * GATHER_PIECE;
+constexpr int GATHER_SMEM = 12 * GATHER_PIECE;
 __global__ void __launch_bounds__(32, 1) fsdp_unit_gather_kernel(const GatherArgs g) {
   extern __shared__ uint8_t gsm_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)gsm_raw + 127) & ~(uintptr_t)127);
   uint64_t* bars = (uint64_t*)(smem + GATHER_SMEM);
-  volatile int* abort_flag = (volatile int*)(bars + 8);
+  volatile int* abort_flag = (volatile int*)(bars + 12);
   unit_gather_role<GATHER_SMEM>(g, (int)blockIdx.x, smem, bars, abort_flag);
 }
 }  // namespace tb
@@ -261,7 +261,7 @@ TB_EXPORT int tb_fsdp_unit_gather(const void* const* shards, void* unit_buf, con
   if (int r = tb_fill_gather(g, shards, unit_buf, flag_bufs, epoch_ptr, ready, chunk_bytes, cpr, 0, rank, world, ctas, status))
     return r;
   static bool configured = false;
-  constexpr int SMEM = GATHER_SMEM + 8 * 8 + 16 + 128;
+  constexpr int SMEM = GATHER_SMEM + 12 * 8 + 16 + 128;
   if (!configured) {
     TB_CUDA_CHECK(cudaFuncSetAttribute(fsdp_unit_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     configured = true;

@@ -5,7 +5,7 @@
 // [q * cpr, (q + 1) * cpr) of it in its persistent shard (symmetric memory, so every rank can read every shard).
 // The gather PULLS: each rank copies all chunks - its own included - into its private full-size unit buffer with
 // bulk async copies (peer memory -> shared memory -> local memory), one elected thread per copy CTA driving a ring of
-// 16 KB pieces. Chunks are fetched in the order first, first + 1, ... (wrapping), so the matrix that the consuming GEMM
+// 16 KB pieces (half of the ring loading, half storing). Chunks are fetched in the order first, first + 1, ... (wrapping), so the matrix that the consuming GEMM
 // needs first arrives first; a chunk's ready word is published (release, gpu scope) once all its parts have landed,
 // and the GEMM's TMA producer waits (bounded) on the words that cover the tile it is about to load.
 //
@@ -55,12 +55,13 @@ __device__ __forceinline__ bool wait_ready_gpu(const uint32_t* flag, uint32_t ta
 }
 
 // Copy role. `cta` is this CTA's index among the g.ctas copy CTAs; `smem` points at SMEM_BYTES of ring space
-// (16-byte aligned), `bars` at 8 mbarriers, `abort_flag` at a CTA-local word. Every thread of the CTA calls it.
+// (16-byte aligned), `bars` at 12 mbarriers, `abort_flag` at a CTA-local word. Every thread of the CTA calls it.
 template <int SMEM_BYTES>
 __device__ __forceinline__ void unit_gather_role(const GatherArgs& g, int cta, uint8_t* smem, uint64_t* bars,
                                                  volatile int* abort_flag) {
   constexpr int PIECE = GATHER_PIECE;
-  constexpr int NBUF = SMEM_BYTES / PIECE < 8 ? SMEM_BYTES / PIECE : 8;
+  constexpr int NBUF = SMEM_BYTES / PIECE < 12 ? SMEM_BYTES / PIECE : 12;
+  constexpr int STORES = NBUF / 2;  // stores allowed to be reading their buffers at once; the other buffers are being loaded
   static_assert(NBUF >= 2, "the gather ring needs at least two 16 KB buffers");
   const uint32_t epoch = *g.epoch_ptr;
   PeerTable flags;
@@ -135,10 +136,11 @@ __device__ __forceinline__ void unit_gather_role(const GatherArgs& g, int cta, u
       mbar_wait(&bars[b], (uint32_t)((i / NBUF) & 1), abort_flag, g.status, TB_ERR_WAIT_FULL);
       bulk_store(dst, smem + b * PIECE, PIECE);
       bulk_commit();
-      if (i >= 1 && next_load < total) {
-        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // the store of piece i - 1 has read its buffer
-        issue_load(next_load);                                        // piece i - 1 + NBUF goes into that buffer
-        ++next_load;
+      if (next_load < total) {
+        // at most STORES stores still read their buffers, so the stores of pieces <= i - STORES have released theirs:
+        // refill those buffers (piece j + NBUF goes into the buffer of piece j)
+        asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(STORES) : "memory");
+        while (next_load < total && next_load <= i - STORES + NBUF) issue_load(next_load++);
       }
       if (i >= LAG) {
         asm volatile("cp.async.bulk.wait_group %0;" ::"n"(LAG) : "memory");

@@ -226,7 +226,8 @@ template <int SMEM_BYTES>
 __device__ __forceinline__ void ag_copy_role(const GemmParams& p, uint8_t* smem, uint64_t* bars,
                                              volatile int* abort_flag) {
   constexpr int PIECE = 16384;
-  constexpr int NBUF = SMEM_BYTES / PIECE < 8 ? SMEM_BYTES / PIECE : 8;
+  constexpr int NBUF = SMEM_BYTES / PIECE < 12 ? SMEM_BYTES / PIECE : 12;
+  constexpr int STORES = NBUF / 2;  // stores allowed to be reading their buffers at once; the other buffers are being loaded
   const uint32_t epoch = *p.epoch_ptr;
   PeerTable flags;
 #pragma unroll
@@ -306,10 +307,11 @@ __device__ __forceinline__ void ag_copy_role(const GemmParams& p, uint8_t* smem,
       mbar_wait(&bars[b], (uint32_t)((i / NBUF) & 1), abort_flag, p.status, TB_ERR_WAIT_FULL);
       bulk_store(dst, smem + b * PIECE, PIECE);
       bulk_commit();
-      if (i >= 1 && next_load < total) {
-        asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");  // the store of piece i - 1 has read its buffer
-        issue_load(next_load);                                        // piece i - 1 + NBUF goes into that buffer
-        ++next_load;
+      if (next_load < total) {
+        // at most STORES stores still read their buffers, so the stores of pieces <= i - STORES have released theirs:
+        // refill those buffers (piece j + NBUF goes into the buffer of piece j)
+        asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(STORES) : "memory");
+        while (next_load < total && next_load <= i - STORES + NBUF) issue_load(next_load++);
       }
       if (i >= LAG) {
         asm volatile("cp.async.bulk.wait_group %0;" ::"n"(LAG) : "memory");

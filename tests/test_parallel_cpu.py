@@ -621,3 +621,105 @@ def test_zero_redundancy_optimizer_matches_plain_adam():
     for p in procs:
         p.join(30)
     assert sorted(res) == [(0, True), (1, True)]
+
+
+def _zero3_worker(rank, world, port, q):
+    """ZeRO-3 + CPU offload on two gloo ranks must follow a single-process AdamW run on the global batch."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torsh_b200.parallel.zero_offload import (AutoMemoryStrategy, CpuCompressionMethod, Zero3CpuOffloadManager,
+                                                      Zero3OffloadConfig)
+
+        class Net(torch.nn.Module):
+            def __init__(self):
+                super().__init__()
+                self.inp = torch.nn.Linear(6, 16)
+                self.h = torch.nn.ModuleList([torch.nn.Sequential(torch.nn.Linear(16, 16), torch.nn.Tanh()) for _ in range(5)])
+                self.out = torch.nn.Linear(16, 3)
+
+            def forward(self, x):
+                x = self.inp(x)
+                for l in self.h:
+                    x = l(x)
+                return self.out(x)
+
+        xs = torch.randn(8, 6, generator=torch.Generator().manual_seed(5))
+        ys = torch.randn(8, 3, generator=torch.Generator().manual_seed(6))
+        torch.manual_seed(0)
+        ref = Net()
+        opt = torch.optim.AdamW(ref.parameters(), lr=1e-2, weight_decay=0.01)
+        ref_losses = []
+        for _ in range(4):
+            loss = torch.nn.functional.mse_loss(ref(xs), ys)
+            opt.zero_grad(); loss.backward(); opt.step()
+            ref_losses.append(loss.item())
+        ok = True
+        layer_bytes = 16 * 16 * 4 + 16 * 4
+        for strategy, budget_layers, prefetch in ((AutoMemoryStrategy.EXTREME, 2, 1), (AutoMemoryStrategy.CONSERVATIVE, 8, 16)):
+            torch.manual_seed(0)
+            net = Net()
+            cfg = Zero3OffloadConfig(gpu_param_budget_gb=budget_layers * (layer_bytes + 64) / 2 ** 30, prefetch_buffer_size=prefetch,
+                                     auto_memory_management=strategy)
+            mgr = Zero3CpuOffloadManager(net, list(net.h), config=cfg, lr=1e-2, weight_decay=0.01)
+            assert all(not pt.resident for pt in mgr.partitions)          # parameters start offloaded
+            mine = slice(rank * 4, rank * 4 + 4)
+            losses = []
+            for _ in range(4):
+                loss = torch.nn.functional.mse_loss(net(xs[mine]), ys[mine])
+                loss.backward()
+                mgr.step()
+                l = loss.detach().clone(); dist.all_reduce(l)
+                losses.append(l.item() / world)
+            ok &= all(abs(a - b) < 1e-5 for a, b in zip(losses, ref_losses))
+            sd = mgr.gather_state_dict()
+            ok &= all(torch.allclose(sd[n], p.detach(), atol=1e-5) for n, p in ref.named_parameters())
+            st = mgr.stats.as_dict()
+            ok &= st["h2d_bytes"] > 0 and st["d2h_bytes"] > 0 and st["steps"] == 4
+            if strategy is AutoMemoryStrategy.EXTREME:
+                ok &= st["releases"] >= 5 * 2 * 4 and mgr.gpu_param_bytes() == 0     # every layer offloaded after every use
+            ok &= mgr.memory_report()["host_state_bytes"] > 0
+        # lossy host compression: bf16 transfer copies, fp32 masters -> still trains, parameters within bf16 rounding
+        torch.manual_seed(0)
+        net = Net()
+        mgr = Zero3CpuOffloadManager(net, list(net.h), config=Zero3OffloadConfig(cpu_compression=CpuCompressionMethod.BF16), lr=1e-2, weight_decay=0.01)
+        first = last = None
+        for i in range(4):
+            loss = torch.nn.functional.mse_loss(net(xs[rank * 4:rank * 4 + 4]), ys[rank * 4:rank * 4 + 4])
+            loss.backward(); mgr.step()
+            l = loss.detach().clone(); dist.all_reduce(l)
+            first = l.item() / world if first is None else first
+            last = l.item() / world
+        ok &= last < first and abs(last - ref_losses[-1]) < 5e-3
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_zero3_cpu_offload_two_gloo_ranks_match_single_process():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_zero3_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(30)
+    assert sorted(res) == [(0, True), (1, True)]
+
+
+def test_zero3_config_and_rank_mapping():
+    from torsh_b200.parallel.zero_offload import AutoMemoryStrategy, CpuCompressionMethod, Zero3OffloadConfig, Zero3RankMapping
+    c = Zero3OffloadConfig()
+    assert (c.offload_params, c.offload_grads, c.offload_optimizer_states, c.cpu_memory_budget_gb, c.gpu_param_budget_gb,
+            c.prefetch_buffer_size, c.async_prefetch, c.overlap_computation, c.pin_memory) == (True, True, True, 32.0, 2.0, 16, True, True, True)
+    assert c.auto_memory_management is AutoMemoryStrategy.AGGRESSIVE and AutoMemoryStrategy.AGGRESSIVE.pressure_threshold() == 0.6
+    assert CpuCompressionMethod.BF16.ratio() == 0.5 and CpuCompressionMethod.BF16.is_lossy() and not CpuCompressionMethod.LOSSLESS.is_lossy()
+    assert Zero3OffloadConfig(cpu_compression=CpuCompressionMethod.FP16).effective_cpu_memory_budget() == 64 * 2 ** 30
+    with pytest.raises(ValueError):
+        Zero3OffloadConfig(cpu_compression=CpuCompressionMethod.INT8).validate()
+    m = Zero3RankMapping(1, 4)
+    assert m.owned_partitions(10) == [1, 5, 9] and m.owned_partition_count(10) == 3 and m.get_parameter_owner(6) == 2
+    assert m.global_to_local_partition(5) == 1 and m.global_to_local_partition(6) is None and m.local_to_global_partition(2) == 9
+    assert m.communication_group([0, 4, 5]) == [0, 1]
