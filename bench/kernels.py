@@ -44,7 +44,7 @@ def timeit(fn, iters, flush):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--no-residual", action="store_true", help="bn: BatchNorm + ReLU without a residual input")
-    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "layernorm", "xent", "adamw", "bn", "conv"])
+    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "layernorm", "xent", "adamw", "bn", "conv", "fsdp_gather"])
     ap.add_argument("--hw", type=int, default=56); ap.add_argument("--channels", type=int, default=256)
     ap.add_argument("--cout", type=int, default=0); ap.add_argument("--ksize", type=int, default=3); ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=4096); ap.add_argument("--k", type=int, default=4096)
@@ -78,6 +78,53 @@ def main():
             msl = timeit(lambda: torch.matmul(Am, Bm, out=ref), a.iters, flush)
             print(f"  torch.matmul (cuBLAS) same shape: {msl*1e3:.1f} us, {2.0*a.m*a.n*a.k/msl/1e9:.0f} TFLOP/s")
         print(f"gemm {a.m}x{a.n}x{a.k} majors {a.a_major}{a.b_major} bn {a.bn} split_k {a.split_k}: {ms*1e3:.1f} us, {t:.0f} TFLOP/s = {t/tf:.2f} of {kind} bf16 peak")
+    elif a.what == "fsdp_gather":
+        # One rank, no peer: the FSDP un-shard machinery on local memory (the NVLink share is measured by bench.py on
+        # several GPUs). Times the stand-alone gather of one GPT-2-medium block (24 MB) for several copy-CTA counts, the
+        # QKV GEMM alone, and the same GEMM with the gather fused in (copy CTAs + per-chunk ready words).
+        import ctypes
+        from torsh_b200.ops.gemm import _lib, gemm
+        lib = _lib()
+        P, I = ctypes.c_void_p, ctypes.c_int
+        lib.tb_fsdp_unit_gather.restype = I
+        lib.tb_fsdp_unit_gather.argtypes = [P] * 5 + [I] * 5 + [P] * 2
+        chunk, cpr = 512 * 1024, 48
+        shard = torch.randn(chunk * cpr // 2, device=dev, dtype=torch.bfloat16)
+        unit = torch.zeros_like(shard)
+        flags = torch.zeros(320 * 8, device=dev, dtype=torch.int32)
+        epoch = torch.ones(1, device=dev, dtype=torch.int32)
+        ready = torch.zeros(2 * cpr, device=dev, dtype=torch.int32)
+        arr = lambda t: (ctypes.c_void_p * 8)(t.data_ptr(), *([0] * 7))
+        shards, flag_tbl = arr(shard), arr(flags)
+        st = nv.status_word(torch.device(dev))
+        for ctas in (16, 32, 64, 96, 128):
+            def run():
+                rc = lib.tb_fsdp_unit_gather(shards, unit.data_ptr(), flag_tbl, epoch.data_ptr(), ready.data_ptr(), chunk, cpr, 0, 1,
+                                             ctas, st.data_ptr(), nv.stream_ptr())
+                assert rc == 0, lib.tb_last_error()
+            ms = timeit(run, a.iters, flush)
+            nv.check_status()
+            assert torch.equal(unit, shard)
+            gb = 2 * shard.numel() * 2 / ms / 1e6
+            print(f"stand-alone gather, 24 MB unit, {ctas:3d} copy CTAs: {ms*1e3:.1f} us, {gb:.0f} GB/s read+write = {gb/hbm:.2f} of {kind} copy bandwidth")
+        M, N, K = a.m, 3072, 1024
+        A = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+        Bw = unit[: N * K].view(N, K)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        ms0 = timeit(lambda: gemm(A, Bw, out=out), a.iters, flush)
+        print(f"QKV GEMM alone {M}x{N}x{K}: {ms0*1e3:.1f} us, {2.0*M*N*K/ms0/1e9:.0f} TFLOP/s")
+        ref = out.clone()
+        for ctas in (8, 16, 32):
+            def run():
+                rc = lib.tb_fsdp_ag_gemm(A.data_ptr(), Bw.data_ptr(), out.data_ptr(), M, N, K, 0, 0, K, K, N, None, None, 0, None, None, 0, 0,
+                                         shards, unit.data_ptr(), flag_tbl, epoch.data_ptr(), ready.data_ptr(), chunk, cpr, 0, 0, 1, ctas,
+                                         st.data_ptr(), nv.stream_ptr())
+                assert rc == 0, lib.tb_last_error()
+            unit.zero_()
+            ms = timeit(run, a.iters, flush)
+            nv.check_status()
+            assert torch.equal(unit, shard) and torch.equal(out, ref)
+            print(f"QKV GEMM with the 24 MB un-shard fused in, {ctas:2d} copy CTAs: {ms*1e3:.1f} us ({ms/ms0:.2f} x the GEMM alone)")
     elif a.what in ("attn_fwd", "attn_bwd"):
         from torsh_b200.ops.attention import flash_attention
         q, k, v = (torch.randn(a.batch, a.seq, a.heads, a.dim, device=dev, dtype=torch.bfloat16, requires_grad=True) for _ in range(3))

@@ -47,8 +47,8 @@ struct FaBwdSmem {
   static constexpr int DS_OFF = P_OFF + 32768;
   static constexpr int BAR_OFF = DS_OFF + 32768;
   // kv_full, q_full[2], q_empty[2], do_full[2], do_empty[2], s_full, dp_full, ds_full,
-  // pds_empty, dq_full, dq_empty, dkv_full
-  static constexpr int NBARS = 16;
+  // pds_empty, dq_full, dq_empty, dkv_full, s_free, dp_free
+  static constexpr int NBARS = 18;
   static constexpr int TOTAL = BAR_OFF + NBARS * 8 + 16;
   static constexpr int ALLOC = TOTAL + 1024;
 };
@@ -102,6 +102,14 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
   uint64_t* dq_full = bars + 13;
   uint64_t* dq_empty = bars + 14;
   uint64_t* dkv_full = bars + 15;
+  uint64_t* s_free = bars + 16;    // compute warps have read S of the current block out of TMEM (head dim 64 only)
+  uint64_t* dp_free = bars + 17;   // ... and dP
+  // Head dim 64 runs software-pipelined: the score MMAs of query block t + 1 are issued as soon as the compute warps
+  // have copied S[t] / dP[t] into registers, so the tensor core works on block t + 1 while they evaluate the
+  // exponentials of block t, and the dQ partial of block t is drained (TMEM -> fp32 reductions) after the compute of
+  // block t + 1, when its MMAs have long finished. With head dim 128 dQ shares TMEM columns with S, which forbids the
+  // early issue, and the blocks run one after the other.
+  constexpr bool PIPELINED = (D == 64);
   uint32_t* tmem_ptr = (uint32_t*)(bars + L::NBARS);
   volatile int* abort_flag = (volatile int*)(tmem_ptr + 1);
 
@@ -129,6 +137,8 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     mbar_init(dq_full, 1);
     mbar_init(dq_empty, 256);
     mbar_init(dkv_full, 1);
+    mbar_init(s_free, 256);
+    mbar_init(dp_free, 256);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -188,13 +198,13 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       const uint32_t p_base = smem_u32(smem + L::P_OFF);
       const uint32_t ds_base = smem_u32(smem + L::DS_OFF);
       mbar_wait(kv_full, 0, abort_flag, p.status, TB_ERR_WAIT_FULL);
-      for (int t = 0; t < n_it; ++t) {
+      // S = Q_t K^T and dP = dO_t V^T of query block t (each waits for its TMEM columns when pipelined)
+      auto issue_scores = [&](int t) {
         const int s = t % QST;
         const uint32_t ph = (t / QST) & 1;
         const uint32_t q_base = smem_u32(smem + L::Q_OFF + s * L::TILE);
         const uint32_t do_base = smem_u32(smem + L::DO_OFF + s * L::TILE);
-        // when dQ aliases S (D = 128) the previous dQ partial must be drained first
-        if (D == 128 && t > 0) mbar_wait(dq_empty, (t - 1) & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_EMPTY);
+        if (PIPELINED && t > 0) mbar_wait(s_free, (t - 1) & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_EMPTY);
         mbar_wait(&q_full[s], ph, abort_flag, p.status, TB_ERR_WAIT_FULL);
         tc_fence_after();
 #pragma unroll
@@ -204,6 +214,7 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             umma_ss(tmem_base + TM_S, make_smem_desc_sw128(q_base + c * 16384 + k * 32, 16, 1024),
                     make_smem_desc_sw128(k_base + c * 16384 + k * 32, 16, 1024), idesc_s, (c | k) ? 1u : 0u);
         umma_commit(s_full);
+        if (PIPELINED && t > 0) mbar_wait(dp_free, (t - 1) & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_EMPTY);
         mbar_wait(&do_full[s], ph, abort_flag, p.status, TB_ERR_WAIT_FULL);
         tc_fence_after();
 #pragma unroll
@@ -213,6 +224,19 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
             umma_ss(tmem_base + TM_DP, make_smem_desc_sw128(do_base + c * 16384 + k * 32, 16, 1024),
                     make_smem_desc_sw128(v_base + c * 16384 + k * 32, 16, 1024), idesc_s, (c | k) ? 1u : 0u);
         umma_commit(dp_full);
+      };
+      if (PIPELINED && n_it > 0) issue_scores(0);
+      for (int t = 0; t < n_it; ++t) {
+        const int s = t % QST;
+        const uint32_t q_base = smem_u32(smem + L::Q_OFF + s * L::TILE);
+        const uint32_t do_base = smem_u32(smem + L::DO_OFF + s * L::TILE);
+        if (PIPELINED) {
+          if (t + 1 < n_it) issue_scores(t + 1);   // runs on the tensor core while the compute warps work on block t
+        } else {
+          // when dQ aliases S (D = 128) the previous dQ partial must be drained first
+          if (t > 0) mbar_wait(dq_empty, (t - 1) & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_EMPTY);
+          issue_scores(t);
+        }
         // P and dS are in shared memory once the compute warps arrive here
         mbar_wait(ds_full, t & 1, abort_flag, p.status, TB_ERR_WAIT_MISC);
         tc_fence_after();
@@ -248,6 +272,30 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
     uint8_t* p_smem = smem + L::P_OFF;
     uint8_t* ds_smem = smem + L::DS_OFF;
     const int sw = row & 7;
+    // dQ partial of query block tt: TMEM -> fp32 reductions into the global accumulator
+    auto drain_dq = [&](int tt) {
+      const int qd = (i0 + tt) * 128 + row;
+      const bool ok = qd < p.S;
+      mbar_wait(dq_full, tt & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
+      tc_fence_after();
+      float* dq_row = p.dQ_acc + ((size_t)b * p.S + (ok ? qd : 0)) * ((size_t)p.H * D) + (size_t)h * D;
+#pragma unroll 1
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + TM_DQ + c * 32 + lane_off, v);
+        tmem_wait_ld();
+        if (ok) {
+#pragma unroll
+          for (int g = 0; g < 8; ++g)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + g * 4),
+                         "f"(__uint_as_float(v[g * 4])), "f"(__uint_as_float(v[g * 4 + 1])),
+                         "f"(__uint_as_float(v[g * 4 + 2])), "f"(__uint_as_float(v[g * 4 + 3]))
+                         : "memory");
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(dq_empty);
+    };
     for (int t = 0; t < n_it; ++t) {
       const int qi = (i0 + t) * 128 + row;
       const bool q_ok = qi < p.S;
@@ -257,17 +305,32 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       const bool need_mask = (p.causal && (i0 + t) == jb) || (kv0 + 128 > p.S);
       const int col_limit = p.causal ? min(qi, p.S - 1) : p.S - 1;
       mbar_wait(s_full, t & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
+      tc_fence_after();
+      // this thread's 64 score columns go to registers at once, so that the tensor core may overwrite S
+      uint32_t sv0[32], sv1[32];
+      tmem_ld32(tmem_base + TM_S + (half * 2) * 32 + lane_off, sv0);
+      tmem_ld32(tmem_base + TM_S + (half * 2 + 1) * 32 + lane_off, sv1);
+      tmem_wait_ld();
+      if (PIPELINED) {
+        tc_fence_before();
+        mbar_arrive(s_free);
+      }
       mbar_wait(dp_full, t & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
       // the previous iteration's MMAs must be done reading P / dS from shared memory
       mbar_wait(pds_empty, (t & 1) ^ 1, abort_flag, p.status, TB_ERR_WAIT_EMPTY);
       tc_fence_after();
-#pragma unroll 1
-      for (int c = half * 2; c < half * 2 + 2; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld32(tmem_base + TM_S + c * 32 + lane_off, sv);
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
+        uint32_t dv[32];
         tmem_ld32(tmem_base + TM_DP + c * 32 + lane_off, dv);
         tmem_wait_ld();
+        if (PIPELINED && cc == 1) {
+          tc_fence_before();
+          mbar_arrive(dp_free);
+        }
         uint32_t pp[16], dd[16];
+        const uint32_t (&sv)[32] = cc == 0 ? sv0 : sv1;
         if (need_mask) fa_bwd_p_ds<true>(sv, dv, sl2, Lr, p.scale, dr, kv0 + c * 32, col_limit, pp, dd);
         else fa_bwd_p_ds<false>(sv, dv, sl2, Lr, p.scale, dr, kv0 + c * 32, col_limit, pp, dd);
         // columns c*32 .. c*32+31 = four 16-byte chunks of sub-tile c/2 (64 keys per sub-tile)
@@ -283,27 +346,13 @@ fa_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(ds_full);
-      // dQ partial for this (query block, key block) pair
-      mbar_wait(dq_full, t & 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
-      tc_fence_after();
-      float* dq_row = p.dQ_acc + ((size_t)b * p.S + (q_ok ? qi : 0)) * ((size_t)p.H * D) + (size_t)h * D;
-#pragma unroll 1
-      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + TM_DQ + c * 32 + lane_off, v);
-        tmem_wait_ld();
-        if (q_ok) {
-#pragma unroll
-          for (int g = 0; g < 8; ++g)
-            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dq_row + c * 32 + g * 4),
-                         "f"(__uint_as_float(v[g * 4])), "f"(__uint_as_float(v[g * 4 + 1])),
-                         "f"(__uint_as_float(v[g * 4 + 2])), "f"(__uint_as_float(v[g * 4 + 3]))
-                         : "memory");
-        }
+      if (PIPELINED) {
+        if (t > 0) drain_dq(t - 1);   // finished long ago: the MMAs of block t - 1 ran under this block's exponentials
+      } else {
+        drain_dq(t);
       }
-      tc_fence_before();
-      mbar_arrive(dq_empty);
     }
+    if (PIPELINED && n_it > 0) drain_dq(n_it - 1);
     // dK, dV of this key block: thread = key row
     mbar_wait(dkv_full, 0, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
     tc_fence_after();

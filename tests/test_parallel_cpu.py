@@ -723,3 +723,89 @@ def test_zero3_config_and_rank_mapping():
     assert m.owned_partitions(10) == [1, 5, 9] and m.owned_partition_count(10) == 3 and m.get_parameter_owner(6) == 2
     assert m.global_to_local_partition(5) == 1 and m.global_to_local_partition(6) is None and m.local_to_global_partition(2) == 9
     assert m.communication_group([0, 4, 5]) == [0, 1]
+
+
+def test_moe_load_balancer_strategies_and_hierarchical_gate():
+    from torsh_b200.parallel import expert_parallel as ep
+    cfg = ep.ExpertParallelismConfig(num_experts=8, rebalancing_threshold=0.3)
+    lb = ep.LoadBalancer(cfg)
+    skew = [400, 300, 100, 50, 50, 40, 30, 30]               # two hot experts
+    for _ in range(9):
+        lb.update_expert_load(skew, sum(skew))
+    assert lb.rebalancing_count == 0                          # never within the first ten updates
+    for _ in range(3):
+        lb.update_expert_load(skew, sum(skew))
+    assert lb.rebalancing_count == 1 and lb.last_strategy is ep.RebalancingStrategy.EXPERT_MIGRATION
+    assert [m.source_expert_id for m in lb.pending_migrations] == [0, 1] and [m.target_expert_id for m in lb.pending_migrations] == [3, 4]
+    assert lb.pending_migrations[0].priority >= lb.pending_migrations[1].priority
+    before = lb.expert_loads[0]
+    m = lb.process_pending_migrations()
+    assert m.migration_type is ep.MigrationType.LOAD_REDISTRIBUTION and lb.expert_loads[0] == pytest.approx(before * 0.7)
+    # routing adjustment: under 0.8 of the mean load -> x1.2, above 1.2 -> x0.8, then decay towards 1
+    lb.trigger_rebalancing(ep.RebalancingStrategy.ROUTING_ADJUSTMENT)
+    assert lb.get_routing_adjustment(1) == 0.8 and lb.get_routing_adjustment(7) == 1.2
+    lb.decay_routing_adjustments()
+    assert lb.get_routing_adjustment(1) == pytest.approx(0.8 * 0.95 + 0.05) and lb.get_routing_adjustment(99) == 1.0
+    lb.trigger_rebalancing(ep.RebalancingStrategy.CAPACITY_REALLOCATION)
+    assert lb.expert_capacities[1] == 1.25 and lb.expert_capacities[7] == 0.75
+    st = lb.get_stats()
+    assert st.rebalancing_count == 3 and not st.is_well_balanced() and st.load_cv() > 0.5
+    assert ep.RebalancingStrategy.EXPERT_MIGRATION.disruption_level() == 0.7 and not ep.RebalancingStrategy.EXPERT_MIGRATION.supports_rollback()
+    assert ep.MigrationType.DEVICE_MIGRATION.requires_parameter_copy() and ep.MigrationType.EXPERT_CONSOLIDATION.complexity() == 4
+    # hierarchical gate: ceil(sqrt(E)) groups, probabilities of a token sum to one, only real experts get mass
+    torch.manual_seed(0)
+    gate = ep.GateNetwork(16, 10)
+    assert gate.num_groups == 4 and gate.experts_per_group == 3 and gate.get_hierarchy_stats()["total_capacity"] == 12
+    x = torch.randn(5, 7, 16)
+    pr = gate(x)
+    assert pr.shape == (5, 7, 10) and torch.allclose(pr.sum(-1), torch.ones(5, 7), atol=1e-5) and (pr >= 0).all()
+    gp = torch.softmax(x.reshape(-1, 16) @ gate.group_router, -1)
+    el = x.reshape(-1, 16) @ gate.expert_routers[1]
+    ref = gp[:, 1:2] * torch.softmax(el, -1)                  # group 1 holds experts 3, 4, 5
+    assert torch.allclose(pr.reshape(-1, 10)[:, 3:6], ref, atol=1e-6)
+    # a router with the hierarchical gate and the balancer routes and trains
+    layer = ep.MoELayer(16, 32, ep.ExpertParallelismConfig(num_experts=4, top_k=2, hierarchical_gate=True, enable_load_balancing=True))
+    y, aux = layer(torch.randn(12, 16))
+    (y.sum() + aux).backward()
+    assert layer.router.gate_network.group_router.grad is not None and layer.router.load_balancer.load_history
+
+
+def _moe_migration_worker(rank, world, port, q):
+    """Swapping the homes of two experts that live on different ranks must leave the layer's function unchanged."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torsh_b200.parallel import expert_parallel as ep
+        torch.manual_seed(10 + rank)                           # every rank owns different experts
+        layer = ep.MoELayer(16, 32, ep.ExpertParallelismConfig(num_experts=4, top_k=2, drop_tokens=False))
+        for prm in layer.router.parameters():
+            dist.broadcast(prm.data, 0)                        # the gate is replicated
+        x = torch.randn(12, 16, generator=torch.Generator().manual_seed(rank))
+        y0, _ = layer(x)
+        w1_before = layer.w1.data.clone()
+        m1 = torch.arange(layer.e_local, dtype=torch.float32).add(10 * rank).view(-1, 1).repeat(1, 3)   # stands for an optimizer moment
+        layer.swap_experts(0, 3, extra_stacks=[m1])            # expert 0 lives on rank 0, expert 3 on rank 1
+        ok = layer.expert_sharding_map()[0] == (1, 1) and layer.expert_sharding_map()[3] == (0, 0)
+        ok &= not torch.equal(layer.w1.data, w1_before)
+        ok &= m1[0 if rank == 0 else 1, 0].item() == (11.0 if rank == 0 else 0.0)
+        y1, _ = layer(x)
+        ok &= torch.allclose(y0, y1, atol=1e-6)
+        layer.swap_experts(0, 1)                               # now both on rank 1 -> local swap there
+        y2, _ = layer(x)
+        ok &= torch.allclose(y0, y2, atol=1e-6)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_moe_expert_migration_keeps_the_function():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_moe_migration_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(30)
+    assert sorted(res) == [(0, True), (1, True)]
