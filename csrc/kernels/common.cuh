@@ -75,3 +75,23 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 __host__ __device__ inline int ceil_div(long a, long b) { return (int)((a + b - 1) / b); }
 
 }  // namespace tb
+
+// ---------------------------------------------------------------- device-side index checks
+// Kernels that index memory with values they read from tensors (token ids, class targets, expert slots, graph
+// edges) never follow a bad index: they skip or clamp it. With checks enabled (TORSH_KERNEL_CHECKS=1 ->
+// tb_set_kernel_checks) they also record TB_ERR_BAD_INDEX in the device status word, which the host turns into an
+// exception at its next status read; there is no trap and no assert, the context stays usable. Every translation unit
+// that includes this header has its own copy of the pointer; tb_set_kernel_checks sets them all.
+#define TB_KERNEL_CHECK_WORD 1
+namespace tb {
+constexpr int TB_ERR_BAD_INDEX = 108;
+static __device__ int* d_check_word = nullptr;
+__device__ __forceinline__ void report_bad_index() {
+  int* w = d_check_word;
+  if (w) atomicCAS(w, 0, TB_ERR_BAD_INDEX);
+}
+// Host: point this translation unit's check word at `word` (null switches the reports off).
+static inline cudaError_t set_check_word_this_tu(int* word) {
+  return cudaMemcpyToSymbol(d_check_word, &word, sizeof(word));
+}
+}  // namespace tb

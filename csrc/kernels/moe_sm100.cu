@@ -47,7 +47,10 @@ __global__ void moe_scatter_kernel(const MoeArgs a, const bf16* __restrict__ src
   for (long p = wid; p < (long)a.T * a.K; p += nwarps) {
     if (!a.keep[p]) continue;
     const long e = a.expert[p], s = a.slot[p];
-    if (e < 0 || e >= (long)a.e_local * a.world || s < 0 || s >= a.C) continue;
+    if (e < 0 || e >= (long)a.e_local * a.world || s < 0 || s >= a.C) {
+      if (lane == 0) report_bad_index();
+      continue;
+    }
     const long t = p / a.K;
     const float sc = a.w ? a.w[p] : 1.f;
     const bf16* sp = src + t * a.H;
@@ -191,5 +194,10 @@ TB_EXPORT int tb_comm_barrier(const void* const* flags, int rank, int world, uns
   for (int i = 0; i < MAX_RANKS; ++i) f.ptr[i] = i < world ? const_cast<void*>(flags[i]) : nullptr;
   comm_barrier_kernel<<<1, 32, 0, st>>>(f, rank, world, epoch_ptr, status);
   TB_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int tb_set_check_word_moe(int* word) {
+  TB_CUDA_CHECK(tb::set_check_word_this_tu(word));
   return 0;
 }

@@ -81,7 +81,10 @@ __global__ void embedding_fwd_kernel(const long* __restrict__ ids, const T* __re
     long t = idx / hv;
     int c = (int)(idx - t * hv) * N;
     long id = ids[t];
-    if (id < 0 || id >= vocab) id = 0;
+    if (id < 0 || id >= vocab) {
+      if (c == 0) report_bad_index();
+      id = 0;
+    }
     Vec16<T> a;
     a.load(wte + id * H + c);
     if (wpe) {
@@ -110,6 +113,7 @@ __global__ void embedding_bwd_kernel(const long* __restrict__ ids, const T* __re
     float g = to_f<T>(dout[idx]);
     long id = ids[t];
     if (dwte && id >= 0 && id < vocab) atomicAdd(dwte + id * H + c, g);
+    else if (dwte && c == 0) report_bad_index();
     if (dwpe) atomicAdd(dwpe + (long)(t % seq) * H + c, g);
   }
 }
@@ -131,7 +135,10 @@ __global__ void gnn_scatter_kernel(const T* __restrict__ x, const long* __restri
     const int c = (int)(idx - e * fq) << 2;
     const long s = src ? src[e] : e;
     const long d = dst[e];
-    if (s < 0 || s >= n_src || d < 0 || d >= n_dst) continue;
+    if (s < 0 || s >= n_src || d < 0 || d >= n_dst) {
+      if (c == 0) report_bad_index();
+      continue;
+    }
     const float we = w ? w[e] : 1.f;
     const T* xp = x + s * F + c;
     float4 v = make_float4(to_f<T>(xp[0]) * we, to_f<T>(xp[1]) * we, to_f<T>(xp[2]) * we, to_f<T>(xp[3]) * we);
@@ -200,6 +207,16 @@ TB_EXPORT int tb_sum_f32(const float* x, float* out, long n, float scale, cudaSt
   TB_CUDA_CHECK(cudaGetLastError());
   return 0;
 }
+// Device-side index checks (see common.cuh): `word` is the device status word, or null to switch the reports off.
+int tb_set_check_word_xent(int* word);
+int tb_set_check_word_moe(int* word);
+TB_EXPORT int tb_set_kernel_checks(int* word) {
+  TB_ENSURE_DEVICE();
+  TB_CUDA_CHECK(set_check_word_this_tu(word));
+  if (int r = tb_set_check_word_xent(word)) return r;
+  return tb_set_check_word_moe(word);
+}
+
 TB_EXPORT int tb_embedding_fwd(const long* ids, const void* wte, const void* wpe, void* out, long tokens,
                                int H, int seq, long vocab, int dtype, cudaStream_t st) {
   TB_ENSURE_DEVICE();

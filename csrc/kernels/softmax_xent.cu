@@ -106,6 +106,7 @@ xent_kernel(const T* __restrict__ logits, const long* __restrict__ targets,
     const T* xr = logits + (size_t)row * ld;
     const long tgt = targets[row];
     const bool ignored = (tgt == ignore_index) || tgt < 0 || tgt >= C;
+    if (ignored && tgt != ignore_index && threadIdx.x == 0) report_bad_index();   // a target outside [0, C) that is not the ignore value
     float m = load_row_max<T, CACHE>(xr, srow, C, scratch);
     float s = 0.f;
     for (int i = threadIdx.x; i < C; i += blockDim.x) s += __expf(row_get<T, CACHE>(xr, srow, i) - m);
@@ -231,4 +232,9 @@ TB_EXPORT int tb_cross_entropy(const void* logits, const long* targets, float* l
   if (ld < C) TB_FAIL(TB_E_ARG, "tb_cross_entropy: ld (%ld) < C (%d)", ld, C);
   return dtype == 0 ? xent_launch<bf16>(logits, targets, loss_rows, lse_rows, dlogits, rows, C, ld, scale, ignore_index, st)
                     : xent_launch<float>(logits, targets, loss_rows, lse_rows, dlogits, rows, C, ld, scale, ignore_index, st);
+}
+
+int tb_set_check_word_xent(int* word) {
+  TB_CUDA_CHECK(tb::set_check_word_this_tu(word));
+  return 0;
 }

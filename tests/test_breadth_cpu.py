@@ -840,3 +840,171 @@ def test_trainer_raises_when_the_device_status_word_is_set():
         bad.value()
     with pytest.raises(nv.KernelTimeout):
         _raise_on_status(101, None)
+
+
+def test_clip_whisper_wav2vec2_reproduce_transformers_outputs():
+    """Random-init Hugging Face models of small size, weights imported, same inputs: the outputs must agree."""
+    transformers = pytest.importorskip("transformers")
+    from torsh_b200 import hub
+    from torsh_b200.models import audio, multimodal
+    torch.manual_seed(0)
+    # ---- CLIP
+    hc = transformers.CLIPConfig(
+        text_config=dict(vocab_size=300, hidden_size=48, intermediate_size=96, num_hidden_layers=2, num_attention_heads=4,
+                         max_position_embeddings=16, eos_token_id=299, projection_dim=32),
+        vision_config=dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, image_size=32,
+                           patch_size=8, projection_dim=32), projection_dim=32)
+    hf = transformers.CLIPModel(hc).eval()
+    ours = multimodal.CLIPModel(multimodal.CLIPConfig.tiny()).eval()
+    assert hub.import_hf_clip(hf.state_dict(), ours) == []
+    ids = torch.randint(0, 298, (3, 16)); ids[:, 9] = 299
+    px = torch.randn(3, 3, 32, 32)
+    with torch.no_grad():
+        ref = hf(input_ids=ids, pixel_values=px)
+        li, lt = ours(ids, px)
+    assert torch.allclose(li, ref.logits_per_image, atol=2e-4) and torch.allclose(lt, ref.logits_per_text, atol=2e-4)
+    assert torch.allclose(ours.encode_image(px), ref.image_embeds / ref.image_embeds.norm(dim=-1, keepdim=True), atol=1e-5)
+    # ---- Whisper encoder
+    wc = transformers.WhisperConfig(vocab_size=200, num_mel_bins=16, encoder_layers=2, encoder_attention_heads=4, decoder_layers=1,
+                                    decoder_attention_heads=4, decoder_ffn_dim=128, encoder_ffn_dim=128, d_model=64,
+                                    max_source_positions=50, max_target_positions=32, pad_token_id=0, bos_token_id=1, eos_token_id=2,
+                                    decoder_start_token_id=1)
+    hw = transformers.WhisperModel(wc).eval()
+    enc = audio.WhisperEncoder(audio.WhisperConfig.tiny()).eval()
+    assert hub.import_hf_whisper_encoder(hw.state_dict(), enc) == []
+    mel = torch.randn(2, 16, 100)
+    with torch.no_grad():
+        assert torch.allclose(enc(mel), hw.encoder(mel).last_hidden_state, atol=2e-4)
+    assert torch.allclose(audio.sinusoids(50, 64), hw.encoder.embed_positions.weight, atol=1e-6)
+    # ---- Wav2Vec2 (base layout: group norm after the first convolution, post-norm encoder)
+    vc = transformers.Wav2Vec2Config(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+                                     conv_dim=(32, 32, 32), conv_kernel=(10, 3, 2), conv_stride=(5, 2, 2), num_conv_pos_embeddings=16,
+                                     num_conv_pos_embedding_groups=4, hidden_dropout=0.0, attention_dropout=0.0, feat_proj_dropout=0.0,
+                                     layerdrop=0.0, mask_time_prob=0.0, feat_extract_norm="group", do_stable_layer_norm=False)
+    hv = transformers.Wav2Vec2Model(vc).eval()
+    w2v = audio.Wav2Vec2Model(audio.Wav2Vec2Config.tiny()).eval()
+    left = hub.import_hf_wav2vec2(hv.state_dict(), w2v)
+    assert all(k.startswith(("masked_spec_embed", "quantizer", "project_")) for k in left)
+    wav = torch.randn(2, 4000)
+    with torch.no_grad():
+        assert torch.allclose(w2v(wav), hv(wav).last_hidden_state, atol=3e-4)
+    assert w2v.frames(4000) == w2v(wav).shape[1]
+
+
+def test_lora_adapters_prefix_and_freezing():
+    from torsh_b200.models import fine_tuning as ft
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 8))
+    x = torch.randn(5, 16)
+    y0 = net(x)
+    wrapped = ft.apply_lora(net, target=r"^(0|2)$", rank=4, alpha=8.0)
+    assert wrapped == ["0", "2"] and torch.allclose(net(x), y0)                 # B starts at zero: identical function
+    s = ft.trainable_summary(net)
+    assert s["trainable"] == 4 * 16 + 32 * 4 + 4 * 32 + 8 * 4 and s["fraction"] < 0.5
+    opt = torch.optim.SGD([p for p in net.parameters() if p.requires_grad], lr=0.5)
+    for _ in range(3):
+        loss = (net(x) - 1).pow(2).mean(); opt.zero_grad(); loss.backward(); opt.step()
+    assert net[0].base.weight.grad is None and not torch.allclose(net(x), y0)
+    y1 = net(x)
+    assert ft.merge_lora(net) == 2 and torch.allclose(net(x), y1, atol=1e-5)    # folded into the base weights
+    net[0].unmerge()
+    assert torch.allclose(net(x), y1, atol=1e-5) and set(ft.lora_state_dict(net)) == {"0.lora_A", "0.lora_B", "2.lora_A", "2.lora_B"}
+    # extract: the rank-r factors of a rank-r difference reproduce it
+    base = torch.randn(12, 10)
+    delta = torch.randn(12, 3) @ torch.randn(3, 10)
+    A, B = ft.extract_lora(base, base + delta, rank=3, alpha=6.0)
+    assert torch.allclose((6.0 / 3) * B @ A, delta, atol=1e-4)
+    # AdaLoRA: pruning singular values removes their contribution
+    ada = ft.AdaLoRALinear(torch.nn.Linear(6, 6), rank=4)
+    with torch.no_grad():
+        ada.lora_E.copy_(torch.tensor([3.0, 0.1, -2.0, 0.01]))
+    ada.prune_to(2)
+    assert ada.rank_mask.tolist() == [1, 0, 1, 0] and ada.orthogonality_penalty() >= 0
+    # adapters start as the identity; prefix encoder shapes
+    enc = torch.nn.Sequential(torch.nn.Linear(8, 8), torch.nn.Linear(8, 8))
+    z = torch.randn(3, 8)
+    z0 = enc(z)
+    assert ft.insert_adapters(enc, r"[01]", hidden=8, reduction_factor=2) == ["0", "1"] and torch.allclose(enc(z), z0)
+    assert ft.PrefixEncoder(3, 5, 8, reparam_hidden=16)().shape == (3, 5, 8) and ft.PrefixEncoder(3, 5, 8)().shape == (3, 5, 8)
+    # layer-wise rates, progressive unfreezing, EWC
+    from torsh_b200.models import BertModel, BertConfig
+    bert = BertModel(BertConfig.tiny())
+    groups = ft.layerwise_lr_groups(bert, 1e-3, 0.5)
+    lrs = sorted(g["lr"] for g in groups)
+    assert lrs == [1e-3 * 0.25, 1e-3 * 0.5, 1e-3] and sum(len(g["params"]) for g in groups) == len(list(bert.parameters()))
+    un = ft.ProgressiveUnfreezer(bert, every=2)
+    assert not bert.layers[1].fc1.weight.requires_grad and [un.step() for _ in range(4)] == [None, 1, None, 0]
+    assert bert.layers[0].fc1.weight.requires_grad
+    assert ft.freeze_parameters(bert, [r"embeddings"], keep=[r"position"]) == 2
+    lin = torch.nn.Linear(4, 1)
+    ewc = ft.EWCPenalty(lin, lam=2.0)
+    lin(torch.ones(1, 4)).sum().backward(); ewc.accumulate()
+    with torch.no_grad():
+        lin.weight.add_(1.0)
+    assert ewc.penalty().item() == pytest.approx(0.5 * 2.0 * 4 * 1.0)            # Fisher = 1 on each weight, moved by 1
+
+
+def test_model_merging_sharding_surgery_distillation_pruning():
+    from torsh_b200.models import model_utils as mu
+    mk = lambda v: {"w": torch.full((2, 2), float(v)), "n": torch.tensor(3)}
+    M = mu.ModelMerger
+    assert M().merge_models([mk(1), mk(3)])["w"][0, 0] == 2 and M().merge_models([mk(1), mk(3)])["n"] == 3
+    assert M(mu.MergeStrategy.WEIGHTED_AVERAGE, weights=[0.25, 0.75]).merge_models([mk(0), mk(4)])["w"][0, 0] == 3
+    assert M(mu.MergeStrategy.EMA, alpha=0.5).merge_models([mk(0), mk(4), mk(8)])["w"][0, 0] == 5
+    assert M(mu.MergeStrategy.MAX_MAGNITUDE).merge_models([mk(1), mk(-3)])["w"][0, 0] == -3
+    assert M(mu.MergeStrategy.TASK_ARITHMETIC, base=mk(1), scaling=0.5).merge_models([mk(3), mk(5)])["w"][0, 0] == 1 + 0.5 * (2 + 4)
+    with pytest.raises(ValueError):
+        M(mu.MergeStrategy.WEIGHTED_AVERAGE, weights=[0.5, 0.6])
+    a, b = torch.tensor([1.0, 0.0]), torch.tensor([0.0, 1.0])
+    assert torch.allclose(mu.slerp(a, b, 0.5), torch.tensor([0.5 ** 0.5, 0.5 ** 0.5]), atol=1e-6)
+    ties = M(mu.MergeStrategy.TIES, base={"w": torch.zeros(4)}, density=0.5).merge_models(
+        [{"w": torch.tensor([1.0, -0.1, 2.0, 0.0])}, {"w": torch.tensor([3.0, 0.2, -4.0, 0.1])}])["w"]
+    assert ties.tolist() == [2.0, 0.0, -4.0, 0.0]           # small entries trimmed, sign elected by total mass, agreeing entries averaged
+    soup = mu.ModelSoup()
+    for v in (1, 2, 9):
+        soup.add_model(mk(v))
+    assert soup.uniform_soup()["w"][0, 0] == 4
+    assert soup.greedy_soup(lambda sd: -abs(sd["w"][0, 0].item() - 1.5))["w"][0, 0] == 1.5      # the outlier is left out
+    # sharding plans
+    net = torch.nn.Sequential(*[torch.nn.Linear(8, 8) for _ in range(4)])
+    sh = mu.ModelSharder(mu.ShardingStrategy.PIPELINE, 2)
+    parts = sh.shard_model(net)
+    assert sorted(parts[0]) == ["0.bias", "0.weight", "1.bias", "1.weight"] and sh.get_stats(parts).balance_ratio() == 1.0
+    tp = mu.ModelSharder(mu.ShardingStrategy.TENSOR_PARALLEL, 4).shard_model(net)
+    assert tp[0]["0.weight"].shape == (2, 8) and tp[3]["0.bias"].shape == (8,)
+    z3 = mu.ModelSharder(mu.ShardingStrategy.ZERO_STAGE3, 3).shard_model(net)
+    assert sum(p["0.weight"].numel() for p in z3) == 64
+    # surgery
+    sg = mu.ModelSurgeon(net)
+    sg.replace_layer("1", torch.nn.Linear(8, 8, bias=False), copy_weights=True)
+    sg.insert_after("2", torch.nn.ReLU()); sg.remove_layer("3")
+    assert isinstance(net[3], torch.nn.Identity) and isinstance(net[2], torch.nn.Sequential) and sg.stats()["operations"] == 3
+    donor = torch.nn.Sequential(torch.nn.Linear(8, 8))
+    sg.graft("0", donor, "0")
+    assert net[0] is donor[0]
+    # distillation
+    dt = mu.DistillationTrainer(mu.DistillationConfig(mu.DistillationStrategy.MULTI_LEVEL, temperature=2.0, alpha=0.5))
+    s, t = torch.randn(4, 5), torch.randn(4, 5)
+    out = dt.compute_distillation_loss(s, t, labels=torch.tensor([0, 1, 2, 3]), student_feats={"h": torch.randn(4, 6)},
+                                       teacher_feats={"h": torch.randn(4, 6)}, student_attn=[torch.rand(4, 2, 3, 3)], teacher_attn=[torch.rand(4, 2, 3, 3)])
+    assert set(out) == {"distillation", "hard", "feature", "attention", "total"} and dt.response_loss(t, t).abs() < 1e-6
+    assert dt.relation_loss(s, s) == 0 and mu.compression_ratio(100, 25) == 4
+    # pruning
+    lin = torch.nn.Sequential(torch.nn.Linear(10, 10))
+    st = mu.ModelPruner(mu.PruningConfig(sparsity=0.3)).prune_model(lin)
+    assert st["overall_sparsity"] == pytest.approx(0.3) and mu.calculate_sparsity(lin[0].weight) == pytest.approx(0.3)
+    lin2 = torch.nn.Sequential(torch.nn.Linear(10, 10))
+    pr = mu.ModelPruner(mu.PruningConfig(sparsity=0.5, structured=True))
+    pr.prune_model(lin2)
+    assert (lin2[0].weight.abs().sum(1) == 0).sum() == 5
+    with torch.no_grad():
+        lin2[0].weight.add_(1.0)
+    pr.apply_masks(lin2)
+    assert (lin2[0].weight.abs().sum(1) == 0).sum() == 5
+    sched = mu.ModelPruner(mu.PruningConfig(sparsity=0.8, schedule="polynomial", steps=4, power=1.0))
+    assert [round(sched.current_sparsity(), 2) for sched.step_count in range(5)] == [0.0, 0.2, 0.4, 0.6, 0.8]
+    for method in (mu.PruningMethod.LAMP, mu.PruningMethod.RANDOM):
+        l3 = torch.nn.Sequential(torch.nn.Linear(6, 6))
+        assert mu.ModelPruner(mu.PruningConfig(sparsity=0.5, method=method)).prune_model(l3)["overall_sparsity"] == pytest.approx(0.5)
+    ens = mu.Ensemble([torch.nn.Linear(3, 2), torch.nn.Linear(3, 2)], mode="prob")
+    assert torch.allclose(ens(torch.randn(4, 3)).sum(-1), torch.ones(4), atol=1e-6)

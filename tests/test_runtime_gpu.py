@@ -127,3 +127,41 @@ def test_unified_buffer_is_visible_from_host_and_device():
     assert float(host[12345]) == 12345.0
     del host
     buf.free()
+
+
+def test_device_side_index_checks_report_through_the_status_word():
+    """With the checks on, a token id outside the vocabulary and a class target outside [0, C) leave code 108 in the
+    status word (the kernels skip the access either way, nothing traps); with the checks off the same calls stay silent."""
+    from torsh_b200 import _native as nv
+    from torsh_b200.ops import elementwise as ew
+    from torsh_b200.ops import softmax as sm
+    dev = torch.device("cuda", torch.cuda.current_device())
+    wte = torch.randn(64, 32, device=dev, dtype=torch.bfloat16)
+    good = torch.randint(0, 64, (2, 8), device=dev)
+    bad = good.clone()
+    bad[1, 3] = 64
+    logits = torch.randn(16, 40, device=dev, dtype=torch.bfloat16)
+    tgt_bad = torch.randint(0, 40, (16,), device=dev)
+    tgt_bad[5] = 41
+    torch.cuda.synchronize()
+    nv.check_status()
+    nv.enable_kernel_checks(True)
+    try:
+        ew.embedding(good, wte, None)
+        torch.cuda.synchronize()
+        nv.check_status()                                    # in-range ids: silent
+        out = ew.embedding(bad, wte, None)
+        torch.cuda.synchronize()
+        with pytest.raises(nv.KernelCheckFailed, match="108"):
+            nv.check_status()
+        assert torch.equal(out[1, 3], wte[0])                # the bad id was clamped, not followed
+        sm.cross_entropy(logits, tgt_bad)
+        torch.cuda.synchronize()
+        with pytest.raises(nv.KernelCheckFailed):
+            nv.check_status()
+    finally:
+        nv.enable_kernel_checks(False)
+    ew.embedding(bad, wte, None)
+    sm.cross_entropy(logits, tgt_bad)
+    torch.cuda.synchronize()
+    nv.check_status()                                        # checks off: the same calls leave no code

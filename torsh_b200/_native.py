@@ -31,6 +31,11 @@ class KernelTimeout(RuntimeError):
     """A bounded device-side wait ran out; the kernel set its status word and returned."""
 
 
+class KernelCheckFailed(RuntimeError):
+    """A device-side check (``TORSH_KERNEL_CHECKS=1``) found an index outside its range; the kernel skipped the access,
+    recorded the code in the status word and carried on."""
+
+
 def _load(name: str, build_fn: str):
     path = _LIBDIR / name
     if not path.exists() and os.environ.get("TORSH_B200_NO_AUTOBUILD") != "1":
@@ -107,7 +112,25 @@ def status_word(device: torch.device | int | None = None) -> torch.Tensor:
     if st is None:
         st = torch.zeros(4, dtype=torch.int32, device=torch.device("cuda", key))
         _status[key] = st
+        from .core.runtime_config import RuntimeConfig
+        if RuntimeConfig.global_().kernel_checks:
+            enable_kernel_checks(True, key)
     return st
+
+
+def enable_kernel_checks(on: bool = True, device: int | None = None) -> None:
+    """Switches the device-side index checks on or off: kernels that index memory with values read from tensors (token
+    ids, class targets, expert slots, graph edges) then record code 108 in the status word when an index is out of range
+    (they skip or clamp such an index either way). Default from ``TORSH_KERNEL_CHECKS``; the reference's counterpart is
+    its debug-only validation layer (``crates/torsh-core/src/debug_validation.rs``)."""
+    key = torch.cuda.current_device() if device is None else device
+    lib = cuda()
+    lib.tb_set_kernel_checks.restype = ctypes.c_int
+    lib.tb_set_kernel_checks.argtypes = [ctypes.c_void_p]
+    with torch.cuda.device(key):
+        stream_ptr()
+        word = status_word(key).data_ptr() if on else None
+        check(lib.tb_set_kernel_checks(word), "tb_set_kernel_checks")
 
 
 _STATUS_NAMES = {
@@ -118,6 +141,7 @@ _STATUS_NAMES = {
     105: "a flag owned by a peer GPU never arrived",
     106: "a device-side wait ran out",
     107: "bad kernel argument detected on the device",
+    108: "an index read from a tensor was outside its range (device-side check)",
 }
 
 
@@ -128,4 +152,5 @@ def check_status(device=None, reset: bool = True) -> None:
     if code != 0:
         if reset:
             st.zero_()
-        raise KernelTimeout(f"device status {code}: {_STATUS_NAMES.get(code, 'unknown')}")
+        exc = KernelCheckFailed if code in (107, 108) else KernelTimeout
+        raise exc(f"device status {code}: {_STATUS_NAMES.get(code, 'unknown')}")

@@ -23,7 +23,8 @@ def _raise_on_status(code: int, status_dev) -> None:
     if code != 0:
         if status_dev is not None:
             status_dev.zero_()
-        raise nv.KernelTimeout(f"device status {code}: {nv._STATUS_NAMES.get(code, 'unknown')} (training step aborted)")
+        exc = nv.KernelCheckFailed if code in (107, 108) else nv.KernelTimeout
+        raise exc(f"device status {code}: {nv._STATUS_NAMES.get(code, 'unknown')} (training step aborted)")
 
 
 class PendingLoss:

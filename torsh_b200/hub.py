@@ -408,3 +408,112 @@ def import_hf_vit(hf_state: dict, model) -> list[str]:
         put(model.head.weight, "classifier.weight")
         put(model.head.bias, "classifier.bias")
     return sorted(k for k in hf_state if k not in used)
+
+
+def _hf_copier(hf_state: dict):
+    """``(take, put, unused)`` helpers shared by the Hugging Face importers below."""
+    import torch
+    used = set()
+
+    def take(key):
+        if key not in hf_state:
+            raise KeyError(f"checkpoint has no tensor {key!r}")
+        used.add(key)
+        return hf_state[key]
+
+    def put(dst, *keys, zero_missing: bool = False):
+        parts = []
+        for k in keys:
+            if zero_missing and k not in hf_state:
+                parts.append(None)
+            else:
+                parts.append(take(k))
+        if any(p is None for p in parts):
+            n = dst.shape[0] // len(parts)
+            parts = [torch.zeros(n, *dst.shape[1:], dtype=dst.dtype) if p is None else p for p in parts]
+        src = torch.cat(parts) if len(parts) > 1 else parts[0]
+        if tuple(src.shape) != tuple(dst.shape):
+            raise ValueError(f"{keys[0]}: checkpoint shape {tuple(src.shape)} != model shape {tuple(dst.shape)}")
+        dst.copy_(src.to(dst.dtype))
+
+    return take, put, lambda: sorted(k for k in hf_state if k not in used)
+
+
+def _put_attention_block(put, block, p: str, attn: str, ln1: str, fc1: str, fc2: str, ln2: str, q="q_proj", k="k_proj", v="v_proj",
+                         out="out_proj"):
+    a = p + attn + "."
+    put(block.attn.in_proj_weight, a + q + ".weight", a + k + ".weight", a + v + ".weight")
+    put(block.attn.in_proj_bias, a + q + ".bias", a + k + ".bias", a + v + ".bias", zero_missing=True)   # Whisper keys have no bias
+    for ours, theirs in ((block.attn.out_proj, attn + "." + out), (block.ln1, ln1), (block.fc1, fc1), (block.fc2, fc2), (block.ln2, ln2)):
+        put(ours.weight, p + theirs + ".weight")
+        put(ours.bias, p + theirs + ".bias")
+
+
+def import_hf_clip(hf_state: dict, model) -> list[str]:
+    """Copy a Hugging Face ``CLIPModel`` ``state_dict`` into :class:`torsh_b200.models.multimodal.CLIPModel`."""
+    import torch
+    take, put, unused = _hf_copier(hf_state)
+    with torch.no_grad():
+        v, t = "vision_model.", "text_model."
+        put(model.vision.patch_embed.weight, v + "embeddings.patch_embedding.weight")
+        put(model.vision.class_embedding, v + "embeddings.class_embedding")
+        put(model.vision.position_embedding, v + "embeddings.position_embedding.weight")
+        for ours, theirs in ((model.vision.pre_ln, "pre_layrnorm"), (model.vision.post_ln, "post_layernorm")):
+            put(ours.weight, v + theirs + ".weight"); put(ours.bias, v + theirs + ".bias")
+        for i, b in enumerate(model.vision.layers):
+            _put_attention_block(put, b, f"{v}encoder.layers.{i}.", "self_attn", "layer_norm1", "mlp.fc1", "mlp.fc2", "layer_norm2")
+        put(model.text.token_embedding.weight, t + "embeddings.token_embedding.weight")
+        put(model.text.position_embedding, t + "embeddings.position_embedding.weight")
+        for i, b in enumerate(model.text.layers):
+            _put_attention_block(put, b, f"{t}encoder.layers.{i}.", "self_attn", "layer_norm1", "mlp.fc1", "mlp.fc2", "layer_norm2")
+        put(model.text.final_ln.weight, t + "final_layer_norm.weight"); put(model.text.final_ln.bias, t + "final_layer_norm.bias")
+        put(model.visual_projection.weight, "visual_projection.weight")
+        put(model.text_projection.weight, "text_projection.weight")
+        put(model.logit_scale, "logit_scale")
+    return [k for k in unused() if not k.endswith("position_ids")]
+
+
+def import_hf_whisper_encoder(hf_state: dict, encoder, prefix: str = "encoder.") -> list[str]:
+    """Copy the encoder of a Hugging Face ``WhisperModel`` into :class:`torsh_b200.models.audio.WhisperEncoder`. The key
+    projection of Whisper has no bias; the fused ``in_proj_bias`` gets zeros there. Returns unused encoder keys."""
+    import torch
+    sub = {k[len(prefix):]: v for k, v in hf_state.items() if k.startswith(prefix)}
+    take, put, unused = _hf_copier(sub)
+    with torch.no_grad():
+        for ours, theirs in ((encoder.conv1, "conv1"), (encoder.conv2, "conv2"), (encoder.ln_post, "layer_norm")):
+            put(ours.weight, theirs + ".weight"); put(ours.bias, theirs + ".bias")
+        put(encoder.embed_positions, "embed_positions.weight")
+        for i, b in enumerate(encoder.layers):
+            _put_attention_block(put, b, f"layers.{i}.", "self_attn", "self_attn_layer_norm", "fc1", "fc2", "final_layer_norm")
+    return unused()
+
+
+def import_hf_wav2vec2(hf_state: dict, model) -> list[str]:
+    """Copy a Hugging Face ``Wav2Vec2Model`` ``state_dict`` into :class:`torsh_b200.models.audio.Wav2Vec2Model`. The
+    positional convolution is stored weight-normalised (magnitude ``g`` per kernel position and direction ``v``); the
+    effective weight ``g * v / ||v||`` is materialised here. Quantizer / masking tensors of the pre-training head are
+    returned as unused."""
+    import torch
+    take, put, unused = _hf_copier(hf_state)
+    with torch.no_grad():
+        fe = "feature_extractor.conv_layers."
+        for i, conv in enumerate(model.feature_extractor.convs):
+            put(conv.weight, f"{fe}{i}.conv.weight")
+            if conv.bias is not None:
+                put(conv.bias, f"{fe}{i}.conv.bias")
+        for i, nrm in enumerate(model.feature_extractor.norms):
+            put(nrm.weight, f"{fe}{i}.layer_norm.weight"); put(nrm.bias, f"{fe}{i}.layer_norm.bias")
+        put(model.feat_norm.weight, "feature_projection.layer_norm.weight"); put(model.feat_norm.bias, "feature_projection.layer_norm.bias")
+        put(model.feat_proj.weight, "feature_projection.projection.weight"); put(model.feat_proj.bias, "feature_projection.projection.bias")
+        pc = "encoder.pos_conv_embed.conv."
+        if pc + "parametrizations.weight.original0" in hf_state:
+            g, v = take(pc + "parametrizations.weight.original0"), take(pc + "parametrizations.weight.original1")
+        else:
+            g, v = take(pc + "weight_g"), take(pc + "weight_v")
+        model.pos_conv.weight.copy_(g * v / v.norm(dim=(0, 1), keepdim=True))      # weight norm over dim 2 (kernel position)
+        put(model.pos_conv.bias, pc + "bias")
+        put(model.enc_norm.weight, "encoder.layer_norm.weight"); put(model.enc_norm.bias, "encoder.layer_norm.bias")
+        for i, b in enumerate(model.layers):
+            _put_attention_block(put, b, f"encoder.layers.{i}.", "attention", "layer_norm", "feed_forward.intermediate_dense",
+                                 "feed_forward.output_dense", "final_layer_norm")
+    return unused()

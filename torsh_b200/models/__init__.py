@@ -6,6 +6,10 @@ from .transformer_zoo import (BertConfig, BertForMaskedLM, BertForSequenceClassi
                               EncoderConfig, EncoderDecoderModel, RobertaModel, Seq2SeqConfig, T5Model, ViTConfig,
                               VisionTransformer)
 from .vision_zoo import AlexNet, ConvNeXt, DenseNet, EfficientNet, MobileNetV2, SwinTransformer, VGG
+from .audio import (HubertModel, Wav2Vec2Config, Wav2Vec2ForCTC, Wav2Vec2Model, WavLMModel, WhisperConfig, WhisperEncoder,
+                    WhisperModel)
+from .multimodal import ALIGNModel, CLIPConfig, CLIPModel, DualEncoder
+from . import fine_tuning, model_utils
 
 _REGISTRY = {
     "gpt2-tiny": lambda **kw: GPTForCausalLM(GPT2Config.tiny(**kw)),
@@ -37,6 +41,13 @@ _REGISTRY = {
     "convnext_small": lambda **kw: ConvNeXt((3, 3, 27, 3), (96, 192, 384, 768), **kw),
     "swin_t": lambda **kw: SwinTransformer(96, (2, 2, 6, 2), (3, 6, 12, 24), **kw),
     "swin_s": lambda **kw: SwinTransformer(96, (2, 2, 18, 2), (3, 6, 12, 24), **kw),
+    "wav2vec2-base": lambda **kw: Wav2Vec2Model(Wav2Vec2Config.base(**kw)),
+    "wav2vec2-large": lambda **kw: Wav2Vec2Model(Wav2Vec2Config.large(**kw)),
+    "hubert-base": lambda **kw: HubertModel(Wav2Vec2Config.base(**kw)),
+    "whisper-tiny": lambda **kw: WhisperModel(WhisperConfig.tiny_en(**kw)),
+    "whisper-base": lambda **kw: WhisperModel(WhisperConfig.base(**kw)),
+    "whisper-small": lambda **kw: WhisperModel(WhisperConfig.small(**kw)),
+    "clip-vit-b-32": lambda **kw: CLIPModel(CLIPConfig.vit_b_32()),
 }
 
 

@@ -46,7 +46,8 @@ class EncoderBlock(nn.Module):
     def _mlp(self, x):
         if self.cfg.activation == "gelu" and not (self.training and self.cfg.dropout > 0):
             return lin_ops.mlp_gelu(x, self.fc1.weight, self.fc1.bias, self.fc2.weight, self.fc2.bias)
-        act = torch.nn.functional.gelu if self.cfg.activation == "gelu" else torch.relu
+        act = {"gelu": torch.nn.functional.gelu, "relu": torch.relu, "silu": torch.nn.functional.silu,
+               "quick_gelu": lambda t: t * torch.sigmoid(1.702 * t)}[self.cfg.activation]
         return self.fc2(self.drop(act(self.fc1(x))))
 
     def forward(self, x, key_padding_mask=None, memory=None, memory_mask=None):
