@@ -147,9 +147,14 @@ def main():
                     help="full_shard: 1/N of every weight resident, un-shard fused into each block's first GEMM, "
                          "reduce-scatter + AdamW per block under backward; shard_grad_op: replicated bf16 parameters and "
                          "gradients, sharded optimizer, one fused reduce-scatter + AdamW + all-gather launch")
-    ap.add_argument("--fsdp-no-fuse-gather", action="store_true", help="full_shard: stand-alone gather kernels instead of the fused GEMM")
+    ap.add_argument("--fsdp-gather", default="copy_engine", choices=["copy_engine", "fused", "kernel"],
+                    help="full_shard: how blocks are un-sharded (DMA prefetch on a side stream / inside the first GEMM / stand-alone kernel)")
+    ap.add_argument("--fsdp-no-fuse-gather", action="store_true", help="same as --fsdp-gather kernel")
+    ap.add_argument("--fsdp-overlap-rs", action="store_true", help="full_shard: per-block reduce-scatter + AdamW on a side stream")
     ap.add_argument("--fsdp-gather-ctas", type=int, default=0)
     ap.add_argument("--fsdp-rs-blocks", type=int, default=0)
+    ap.add_argument("--fsdp-rs-threads", type=int, default=0)
+    ap.add_argument("--fsdp-no-overlap-rs", action="store_true", help="full_shard: each block's reduce-scatter + AdamW on the main stream at full width")
     ap.add_argument("--fsdp-single", action="store_true",
                     help="diagnostic: run the FSDP engine in a one-rank group on one GPU (its kernels without any peer)")
     ap.add_argument("--no-baseline", action="store_true", help="skip the constructed PyTorch baseline arm (child processes)")
@@ -213,11 +218,15 @@ def main():
     if world > 1 or args.fsdp_single:
         from torsh_b200.parallel.fsdp import FlatFSDP, FsdpConfig, ShardingStrategy
         fc = FsdpConfig(sharding_strategy=ShardingStrategy(args.fsdp_strategy))
-        fc.fuse_gather = not args.fsdp_no_fuse_gather
+        fc.gather_mode = "kernel" if args.fsdp_no_fuse_gather else args.fsdp_gather
+        fc.fuse_gather = fc.gather_mode == "fused"
         if args.fsdp_gather_ctas:
             fc.gather_ctas = args.fsdp_gather_ctas
         if args.fsdp_rs_blocks:
             fc.rs_blocks = args.fsdp_rs_blocks
+        if args.fsdp_rs_threads:
+            fc.rs_threads = args.fsdp_rs_threads
+        fc.overlap_rs = args.fsdp_overlap_rs and not args.fsdp_no_overlap_rs
         if args.fsdp_comm_blocks:
             fc.comm_blocks = args.fsdp_comm_blocks
         fc.overlap = bool(args.fsdp_overlap) and not args.fsdp_no_overlap

@@ -28,6 +28,8 @@
 // AdamW arithmetic follows crates/torsh-optim/src/adam.rs:809-950 (decoupled decay first, both
 // moments bias-corrected). The reference's FSDP "reduce-scatter" is all_reduce + slice followed by
 // shard -= grad (crates/torsh-distributed/src/fsdp.rs:373-419).
+#include <stdlib.h>
+
 #include "comm.cuh"
 #include "common.cuh"
 #include "fsdp_gather.cuh"
@@ -172,8 +174,9 @@ static int fsdp_step_launch(const void* const* grads, const void* const* params,
                             void* param_shard, long unit_off, long unit_len, long state_off, int rank, int world,
                             const unsigned* epoch_ptr, float lr, float beta1, float beta2, float eps, float wd,
                             float bc1, float bc2, float grad_scale, const float* dyn, int nblocks, int* status,
-                            cudaStream_t st) {
+                            cudaStream_t st, int threads = FSDP_THREADS) {
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) TB_FAIL(TB_E_ARG, "fsdp step: bad rank/world");
+  if (threads < 64 || threads > FSDP_THREADS || threads % 32) TB_FAIL(TB_E_ARG, "fsdp step: threads per CTA must be a multiple of 32 in [64, 512]");
   if (unit_len % (8L * world) || unit_off % 8 || state_off % 8)
     TB_FAIL(TB_E_ARG, "fsdp step: unit_len (%ld) must be a multiple of 8*world, offsets of 8", unit_len);
   const bool full_shard = param_shard != nullptr;
@@ -196,8 +199,8 @@ static int fsdp_step_launch(const void* const* grads, const void* const* params,
   if (nblocks < 1) nblocks = 1;
   if (nblocks > FSDP_MAX_BLOCKS) nblocks = FSDP_MAX_BLOCKS;
   if (full_shard) {
-    if (grad_mc) fsdp_rs_adamw_ag_kernel<true, false><<<nblocks, FSDP_THREADS, 0, st>>>(a);
-    else fsdp_rs_adamw_ag_kernel<false, false><<<nblocks, FSDP_THREADS, 0, st>>>(a);
+    if (grad_mc) fsdp_rs_adamw_ag_kernel<true, false><<<nblocks, threads, 0, st>>>(a);
+    else fsdp_rs_adamw_ag_kernel<false, false><<<nblocks, threads, 0, st>>>(a);
   } else {
     if (grad_mc) fsdp_rs_adamw_ag_kernel<true, true><<<nblocks, FSDP_THREADS, 0, st>>>(a);
     else fsdp_rs_adamw_ag_kernel<false, true><<<nblocks, FSDP_THREADS, 0, st>>>(a);
@@ -226,22 +229,24 @@ TB_EXPORT int tb_fsdp_rs_adamw(const void* const* grads, const void* const* flag
                                float* exp_avg, float* exp_avg_sq, void* param_shard, long grad_off, long unit_len,
                                long state_off, int rank, int world, const unsigned* epoch_ptr, float lr, float beta1,
                                float beta2, float eps, float wd, float grad_scale, const float* dyn, int nblocks,
-                               int* status, cudaStream_t st) {
+                               int threads, int* status, cudaStream_t st) {
   TB_ENSURE_DEVICE();
   if (!param_shard) TB_FAIL(TB_E_ARG, "fsdp step: null parameter shard");
+  // `threads` per CTA: small CTAs (128 threads = 8 K registers) fit next to the CTAs of the backward kernels they overlap
   return fsdp_step_launch(grads, nullptr, flags, grad_mc, nullptr, master, exp_avg, exp_avg_sq, param_shard, grad_off,
                           unit_len, state_off, rank, world, epoch_ptr, lr, beta1, beta2, eps, wd, 1.f, 1.f, grad_scale,
-                          dyn, nblocks, status, st);
+                          dyn, nblocks, status, st, threads > 0 ? threads : FSDP_THREADS);
 }
 
 namespace tb {
 constexpr int GATHER_SMEM = 12 * GATHER_PIECE;
+template <int PIECE>
 __global__ void __launch_bounds__(32, 1) fsdp_unit_gather_kernel(const GatherArgs g) {
   extern __shared__ uint8_t gsm_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)gsm_raw + 127) & ~(uintptr_t)127);
   uint64_t* bars = (uint64_t*)(smem + GATHER_SMEM);
   volatile int* abort_flag = (volatile int*)(bars + 12);
-  unit_gather_role<GATHER_SMEM>(g, (int)blockIdx.x, smem, bars, abort_flag);
+  unit_gather_role<GATHER_SMEM, PIECE>(g, (int)blockIdx.x, smem, bars, abort_flag);
 }
 }  // namespace tb
 
@@ -263,10 +268,16 @@ TB_EXPORT int tb_fsdp_unit_gather(const void* const* shards, void* unit_buf, con
   static bool configured = false;
   constexpr int SMEM = GATHER_SMEM + 12 * 8 + 16 + 128;
   if (!configured) {
-    TB_CUDA_CHECK(cudaFuncSetAttribute(fsdp_unit_gather_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    TB_CUDA_CHECK(cudaFuncSetAttribute(fsdp_unit_gather_kernel<16384>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    TB_CUDA_CHECK(cudaFuncSetAttribute(fsdp_unit_gather_kernel<32768>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    TB_CUDA_CHECK(cudaFuncSetAttribute(fsdp_unit_gather_kernel<65536>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     configured = true;
   }
-  fsdp_unit_gather_kernel<<<ctas, 32, SMEM, st>>>(g);
+  // piece size of the copy ring (experiment knob: TB_GATHER_PIECE_KB = 16, 32 or 64)
+  static const int piece_kb = [] { const char* e = getenv("TB_GATHER_PIECE_KB"); return e ? atoi(e) : 16; }();
+  if (piece_kb == 64 && chunk_bytes % 65536 == 0) fsdp_unit_gather_kernel<65536><<<ctas, 32, SMEM, st>>>(g);
+  else if (piece_kb == 32 && chunk_bytes % 32768 == 0) fsdp_unit_gather_kernel<32768><<<ctas, 32, SMEM, st>>>(g);
+  else fsdp_unit_gather_kernel<16384><<<ctas, 32, SMEM, st>>>(g);
   fsdp_bump_epoch_kernel<<<1, 1, 0, st>>>(const_cast<uint32_t*>(epoch_ptr));
   TB_CUDA_CHECK(cudaGetLastError());
   return 0;

@@ -28,6 +28,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int A_TILE_BYTES = BM * BK * 2;
 constexpr int GEMM_THREADS = 192;
+constexpr int SCHED_DEPTH = 4;   // work indices the producer may publish ahead of the slowest consumer role
 
 enum : int {
   EPI_BIAS = 1,          // += bias[n] (bf16)
@@ -54,6 +55,11 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int kb_total, kb_per_split;
   int stream_k;  // 1: workers own equal contiguous ranges of (tile, K-block) units instead of whole K-splits
+  // Dynamic tile scheduler: sched[0] is the launch's work counter, sched[1] counts CTAs that have drawn their last item
+  // (the last one resets both). Null: work items are dealt round-robin. A CTA starts with item `worker` and draws every
+  // further item from the counter, so a CTA that starts late or shares its SM with another kernel simply takes fewer
+  // tiles instead of holding the launch back.
+  unsigned* sched;
   int* status;
   // ---- tensor-parallel fusions (all zero / null for a plain GEMM) --------------------------------
   // GEMM -> reduce-scatter: output row r belongs to rank r / rs_rows; the epilogue stores the tile
@@ -93,13 +99,15 @@ struct GemmParams {
   GatherArgs wg;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int GBUFS = 0>
 struct SmemLayout {
   static constexpr int B_TILE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
   static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem ptr, abort flag
-  static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+  // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem ptr, abort flag, then the dynamic scheduler's
+  // sched_full[SCHED_DEPTH], sched_empty[SCHED_DEPTH] and its ring of work indices
+  static constexpr int SCHED_OFFSET = BAR_OFFSET + (2 * STAGES + 4) * 8 + 16;
+  static constexpr int TOTAL = SCHED_OFFSET + 2 * SCHED_DEPTH * 8 + SCHED_DEPTH * 4;
   // Epilogue staging, 1024-byte aligned. bf16 outputs: 4 warps x 2 buffers x (32 rows x 128 B, 128B-swizzled),
   // each buffer leaves as one TMA tensor store. The fp32 reduce-scatter epilogue uses the same bytes as
   // 4 warps x 32 private rows of 144 B (128 B + pad).
@@ -108,7 +116,13 @@ struct SmemLayout {
   static constexpr int EPI_OFF = RS_OFF;
   static constexpr int EPI_WARP_BYTES = 2 * 32 * 128;
   static constexpr int RS_BYTES = 4 * EPI_WARP_BYTES;
-  static constexpr int ALLOC = RS_OFF + RS_BYTES + 1024;  // + slack for manual 1024-byte alignment
+  // Ring of the FSDP gather warp (GBUFS pieces of 16 KB, their mbarriers and the warp's own abort word); 0 without it
+  static constexpr int GATHER_OFF = RS_OFF + RS_BYTES;
+  static constexpr int GATHER_BYTES = GBUFS ? GBUFS * GATHER_PIECE + 128 : 0;
+  // No slack for a manual round-up: the dynamic shared-memory window is declared 1024-byte aligned (the kernel checks
+  // it and refuses to run otherwise). The kilobyte this saves is what lets a small CTA of another kernel (the FSDP
+  // reduce-scatter, 128 bytes of shared memory + the 1 KB the system reserves per CTA) share an SM with a GEMM CTA.
+  static constexpr int ALLOC = RS_OFF + RS_BYTES + GATHER_BYTES;
   static_assert(4 * 32 * RS_ROW_PITCH <= RS_BYTES, "fp32 reduce-scatter rows must fit the staging region");
   static_assert(ALLOC <= 232448, "shared memory budget of one CTA exceeded");
 };
@@ -191,6 +205,70 @@ struct WorkIter {
       pos += stride;
     }
     return true;
+  }
+};
+
+// Work source of one role under either scheduler. Static: the WorkIter sequence. Dynamic: the TMA producer thread
+// draws work indices (its first one is its worker number, later ones come from the global counter, fetched one item
+// ahead so the atomic's latency hides behind the current tile's loads) and publishes them through a shared-memory
+// ring; the MMA thread and the four epilogue warps read the ring. -1 ends the sequence.
+struct TileSource {
+  WorkIter st;
+  bool dyn;
+  int k;            // items taken so far
+  int total;
+  int cur, nxt;     // producer only
+  volatile int* ring;
+  uint64_t *sfull, *sempty;
+  __device__ __forceinline__ TileSource(const GemmParams& p, int worker, int nworkers, uint8_t* sched_smem)
+      : st(p, worker, nworkers), dyn(p.sched != nullptr), k(0), total(p.tiles_m * p.tiles_n * p.split_k), cur(worker), nxt(-1),
+        raw(0), drew(false) {
+    sfull = (uint64_t*)sched_smem;
+    sempty = sfull + SCHED_DEPTH;
+    ring = (volatile int*)(sempty + SCHED_DEPTH);
+  }
+  // producer: returns the next work index or -1 and publishes it to the other roles. The draw for the item AFTER the
+  // returned one is issued here and only looked at in the next call, i.e. after this tile's loads have been issued, so
+  // the atomic's round trip never sits in front of a load.
+  unsigned raw;
+  bool drew;
+  __device__ __forceinline__ int produce(const GemmParams& p, int nworkers, volatile int* abort_flag) {
+    int w;
+    if (k == 0) {
+      w = cur < total ? cur : -1;
+      drew = false;
+    } else if (drew) {
+      const long d = (long)nworkers + raw;
+      w = d < total ? (int)d : -1;
+      if (w < 0 && atomicAdd(p.sched + 1, 1u) == gridDim.x - p.ag_ctas - 1u) {  // every CTA has drawn its last item
+        p.sched[0] = 0;
+        p.sched[1] = 0;
+      }
+    } else {
+      w = -1;
+    }
+    drew = false;
+    if (w >= 0 && !*abort_flag) {
+      raw = atomicAdd(p.sched, 1u);
+      drew = true;
+    }
+    const int slot = k % SCHED_DEPTH;
+    if (k >= SCHED_DEPTH) mbar_wait(&sempty[slot], ((k / SCHED_DEPTH) & 1) ^ 1, abort_flag, p.status, TB_ERR_WAIT_MISC);
+    ring[slot] = *abort_flag ? -1 : w;
+    mbar_arrive(&sfull[slot]);
+    ++k;
+    return *abort_flag ? -1 : w;
+  }
+  // consumer (one thread per role instance reads; warps broadcast themselves)
+  __device__ __forceinline__ int consume(const GemmParams& p, volatile int* abort_flag) {
+    const int slot = k % SCHED_DEPTH;
+    if (!mbar_wait(&sfull[slot], (k / SCHED_DEPTH) & 1, abort_flag, p.status, TB_ERR_WAIT_MISC)) return -1;
+    const int w = ring[slot];
+    ++k;
+    return w;
+  }
+  __device__ __forceinline__ void release(int items_done) {  // consumer: item (items_done - 1) has been read
+    mbar_arrive(&sempty[(items_done - 1) % SCHED_DEPTH]);
   }
 };
 
@@ -392,13 +470,20 @@ __device__ __forceinline__ void epi_math(const GemmParams& p, int flags, bool ad
     }
 }
 
-template <int BN, int A_MAJOR, int B_MAJOR, int STAGES>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// GBUFS > 0: a seventh warp (threads 192..223) of EVERY CTA gathers its share of an FSDP unit through a ring of GBUFS 16 KB
+// pieces while the CTA computes (the pipeline then has fewer stages to make room): the un-shard uses the bulk-copy engine
+// of all SMs and costs the GEMM no SM.
+template <int BN, int A_MAJOR, int B_MAJOR, int STAGES, int GBUFS = 0>
+__global__ void __launch_bounds__(GBUFS ? GEMM_THREADS + 32 : GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __grid_constant__ OutMaps out_maps, const GemmParams p) {
-  using L = SmemLayout<BN, STAGES>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  using L = SmemLayout<BN, STAGES, GBUFS>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if (smem_u32(smem) & 1023u) {  // the 128-byte swizzle of the TMA tiles needs this alignment; never seen, but never assumed
+    if (threadIdx.x == 0 && p.status) atomicCAS(p.status, 0, TB_ERR_BAD_ARG);
+    return;
+  }
   uint64_t* full = (uint64_t*)(smem + L::BAR_OFFSET);
   uint64_t* empty = full + STAGES;
   uint64_t* tmem_full = empty + STAGES;
@@ -411,14 +496,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
 
   if (p.ag_ctas > 0 && (int)blockIdx.x < p.ag_ctas) {
-    if (p.wg_on) unit_gather_role<L::BAR_OFFSET>(p.wg, (int)blockIdx.x, smem, full, abort_flag);
-    else ag_copy_role<L::BAR_OFFSET>(p, smem, full, abort_flag);
+    ag_copy_role<L::BAR_OFFSET>(p, smem, full, abort_flag);
     return;
   }
   // GEMM CTAs are numbered from 0 after the copy CTAs
   const int worker = (int)blockIdx.x - p.ag_ctas;
   const int nworkers = (int)gridDim.x - p.ag_ctas;
-  const uint32_t ag_epoch = p.ag_ctas > 0 ? *p.epoch_ptr : 0u;
+  const uint32_t ag_epoch = (p.ag_ctas > 0 || p.wg_on) ? *p.epoch_ptr : 0u;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -428,6 +512,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
       mbar_init(&tmem_empty[a], 4);
+    }
+    {
+      uint64_t* sb = (uint64_t*)(smem + L::SCHED_OFFSET);
+      for (int d = 0; d < SCHED_DEPTH; ++d) {
+        mbar_init(&sb[d], 1);                // published by the producer thread
+        mbar_init(&sb[SCHED_DEPTH + d], 5);  // read by the MMA thread and the four epilogue warps
+      }
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -454,7 +545,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       tma_prefetch_desc(&map_b);
       int s = 0;
       uint32_t phase = 0;
-      WorkIter it(p, worker, nworkers);
+      TileSource it(p, worker, nworkers, smem + L::SCHED_OFFSET);
+      auto next_work = [&](int& m_t, int& n_t, int& kb0, int& kb1) -> bool {
+        if (!it.dyn) return it.st.next(p, m_t, n_t, kb0, kb1);
+        const int w = it.produce(p, nworkers, abort_flag);
+        if (w < 0) return false;
+        decode_work(p, w, m_t, n_t, kb0, kb1);
+        return true;
+      };
       int m_t, n_t, kb0, kb1;
       // FSDP weight gather: chunks of the unit buffer this thread has already seen ready (indices below 64)
       uint64_t wg_seen = 0;
@@ -472,7 +570,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       // Once any wait of this thread has given up (abort flag), nothing more is loaded: loads issued without a free
       // stage would pile transaction counts on one barrier beyond its range. The MMA and epilogue roles see the flag
       // too, stop waiting and drain their finite loops on whatever the stages hold.
-      while (!*abort_flag && it.next(p, m_t, n_t, kb0, kb1)) {
+      while (!*abort_flag && next_work(m_t, n_t, kb0, kb1)) {
         if (p.wg_on && B_MAJOR == 0)
           wg_wait(p.wg_b_off + (long)n_t * BN * p.wg_ldb_bytes, p.wg_b_off + (long)min(p.N, (n_t + 1) * BN) * p.wg_ldb_bytes);
         if (!p.wg_on && p.ag_ctas > 0 && (m_t * BM) / p.ag_rows != p.rank) {
@@ -539,6 +637,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
       }
       if (*abort_flag) {
+        if (it.dyn) {   // the other roles must not wait for a work index that will never come
+          int a, b, c, d;
+          next_work(a, b, c, d);
+        }
         // give copies still in flight time to land before the CTA's smem is released
         uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 2000000ull) {
@@ -553,9 +655,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      WorkIter it(p, worker, nworkers);
+      TileSource it(p, worker, nworkers, smem + L::SCHED_OFFSET);
+      auto next_work = [&](int& m_t, int& n_t, int& kb0, int& kb1) -> bool {
+        if (!it.dyn) return it.st.next(p, m_t, n_t, kb0, kb1);
+        const int w = it.consume(p, abort_flag);
+        it.release(it.k);
+        if (w < 0) return false;
+        decode_work(p, w, m_t, n_t, kb0, kb1);
+        return true;
+      };
       int m_t, n_t, kb0, kb1;
-      while (it.next(p, m_t, n_t, kb0, kb1)) {
+      while (next_work(m_t, n_t, kb0, kb1)) {
         mbar_wait(&tmem_empty[acc], acc_phase ^ 1, abort_flag, p.status, TB_ERR_WAIT_TMEM_EMPTY);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -587,6 +697,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         }
       }
     }
+  } else if (GBUFS > 0 && warp == 6) {
+    // ------------------------------------------------------------ FSDP gather warp
+    uint8_t* gsm = smem + L::GATHER_OFF;
+    uint64_t* gbars = (uint64_t*)(gsm + GBUFS * GATHER_PIECE);
+    unit_gather_warp<(GBUFS > 0 ? GBUFS : 2)>(p.wg, (int)blockIdx.x, (int)gridDim.x, gsm, gbars, (volatile int*)(gbars + GBUFS));
   } else {
     // ------------------------------------------------------------ epilogue (4 warps)
     const int q = warp & 3;  // TMEM lane quarter this warp may access
@@ -594,9 +709,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     uint32_t acc_phase = 0;
     uint32_t epi_cnt = 0;  // 64-column groups this warp has staged so far (selects the staging buffer)
     const int flags = p.flags;
-    WorkIter it(p, worker, nworkers);
+    TileSource it(p, worker, nworkers, smem + L::SCHED_OFFSET);
+    auto next_work = [&](int& m_t, int& n_t, int& kb0, int& kb1) -> bool {
+      if (!it.dyn) return it.st.next(p, m_t, n_t, kb0, kb1);
+      int w = 0;
+      if (lane == 0) {
+        w = it.consume(p, abort_flag);
+        it.release(it.k);
+      } else {
+        ++it.k;
+      }
+      w = __shfl_sync(0xffffffffu, w, 0);
+      if (w < 0) return false;
+      decode_work(p, w, m_t, n_t, kb0, kb1);
+      return true;
+    };
     int m_t, n_t, kb0, kb1;
-    while (it.next(p, m_t, n_t, kb0, kb1)) {
+    while (next_work(m_t, n_t, kb0, kb1)) {
       mbar_wait(&tmem_full[acc], acc_phase, abort_flag, p.status, TB_ERR_WAIT_TMEM_FULL);
       tc_fence_after();
       int row = m_t * BM + q * 32 + lane;
@@ -784,11 +913,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
   }
 }
 
-template <int BN, int A_MAJOR, int B_MAJOR, int STAGES>
+// Counters of the dynamic tile scheduler: SCHED_SLOTS pairs (work counter, finished-CTA counter), all zero between
+// launches (the last CTA of a launch resets its pair). Consecutive launches take consecutive pairs, so launches that run
+// concurrently on different streams never share one; a pair is reused SCHED_SLOTS launches later.
+constexpr int SCHED_SLOTS = 1024;
+static __device__ unsigned g_sched_counters[2 * SCHED_SLOTS];
+
+static int sched_pair(unsigned** out) {
+  static unsigned* base[64] = {nullptr};
+  static std::atomic<unsigned> seq{0};
+  int dev = 0;
+  TB_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) TB_FAIL(TB_E_ARG, "gemm: device index %d out of range", dev);
+  if (!base[dev]) {
+    unsigned* p = nullptr;
+    TB_CUDA_CHECK(cudaGetSymbolAddress((void**)&p, g_sched_counters));
+    base[dev] = p;
+  }
+  *out = base[dev] + 2 * (seq.fetch_add(1, std::memory_order_relaxed) % SCHED_SLOTS);
+  return 0;
+}
+
+template <int BN, int A_MAJOR, int B_MAJOR, int STAGES, int GBUFS = 0>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const OutMaps& om, const GemmParams& p,
                        cudaStream_t stream) {
-  using L = SmemLayout<BN, STAGES>;
-  auto kern = gemm_bf16_kernel<BN, A_MAJOR, B_MAJOR, STAGES>;
+  using L = SmemLayout<BN, STAGES, GBUFS>;
+  auto kern = gemm_bf16_kernel<BN, A_MAJOR, B_MAJOR, STAGES, GBUFS>;
   static bool configured = false;
   if (!configured) {
     TB_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::ALLOC));
@@ -798,7 +948,14 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const OutMa
   int workers = sm_count() - p.ag_ctas;  // copy CTAs and GEMM CTAs must all be resident at once
   if (workers < 1) TB_FAIL(TB_E_ARG, "gemm: too many copy CTAs");
   int grid = (int)(total < workers ? total : workers) + p.ag_ctas;
-  kern<<<grid, GEMM_THREADS, L::ALLOC, stream>>>(ma, mb, om, p);
+  GemmParams q = p;
+  // more than one wave of work items and no order the fused collectives rely on: deal the items dynamically
+  static const bool dyn_enabled = [] { const char* e = getenv("TB_GEMM_DYNAMIC"); return !(e && e[0] == '0'); }();
+  q.sched = nullptr;
+  if (dyn_enabled && !p.stream_k && p.ag_ctas == 0 && total > workers) {
+    if (int r = sched_pair(&q.sched)) return r;
+  }
+  kern<<<grid, GBUFS ? GEMM_THREADS + 32 : GEMM_THREADS, L::ALLOC, stream>>>(ma, mb, om, q);
   TB_CUDA_CHECK(cudaGetLastError());
   return TB_LAUNCH_OK;
 }
@@ -1004,8 +1161,7 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
     const long unit_bytes = (long)tp.wg.world * tp.wg.cpr * tp.wg.chunk_bytes;
     if (tp.wg_b_off < 0 || tp.wg_b_off + b_bytes > unit_bytes || (const char*)B != (const char*)tp.wg.dst + tp.wg_b_off)
       TB_FAIL(TB_E_ARG, "fsdp_ag_gemm: B must lie inside the unit buffer at the given offset");
-    p.ag_ctas = tp.wg.ctas;
-    p.wg_on = 1;
+    p.wg_on = 1;      // gathered by the seventh warp of every CTA (no dedicated copy CTAs)
     p.wg = tp.wg;
     p.wg.status = status;
     p.wg_b_off = tp.wg_b_off;
@@ -1087,6 +1243,15 @@ static int gemm_dispatch(const void* A, const void* B, void* D, int M, int N, in
     if (a_major == 1 && b_major == 1) return launch_gemm<BN_, 1, 1, ST_>(ma, mb, om, p, stream); \
     if (a_major == 1 && b_major == 0) return launch_gemm<BN_, 1, 0, ST_>(ma, mb, om, p, stream); \
   } while (0)
+  if (tp.kind == 5) {
+    // one pipeline stage less than the plain GEMM: its 48 / 64 KB hold the gather warp's three-piece ring
+    if (bn == 256) {
+      if (b_major == 0) return launch_gemm<256, 0, 0, 3, 3>(ma, mb, om, p, stream);
+      return launch_gemm<256, 0, 1, 3, 3>(ma, mb, om, p, stream);
+    }
+    if (b_major == 0) return launch_gemm<128, 0, 0, 4, 3>(ma, mb, om, p, stream);
+    return launch_gemm<128, 0, 1, 4, 3>(ma, mb, om, p, stream);
+  }
   if (bn == 256) TB_DISPATCH(256, 4);
   else TB_DISPATCH(128, 6);
 #undef TB_DISPATCH
@@ -1131,8 +1296,8 @@ TB_EXPORT int tb_fsdp_ag_gemm(const void* A, const void* B, void* D, int M, int 
   if (ldb != (b_major == 0 ? K : N)) TB_FAIL(TB_E_ARG, "fsdp_ag_gemm: B must be contiguous (ldb %d)", ldb);
   TpFusion tp;
   tp.kind = 5;
-  if (copy_ctas < 1) copy_ctas = 16;
-  if (copy_ctas > 64) copy_ctas = 64;
+  if (a_major != 0) TB_FAIL(TB_E_ARG, "fsdp_ag_gemm: A must be K-major");
+  copy_ctas = 1;  // unused: every CTA of the launch carries a gather warp
   int r = tb_fill_gather(tp.wg, shards, unit_buf, flag_bufs, epoch_ptr, ready, chunk_bytes, cpr,
                          (int)(b_off / chunk_bytes) % (world * cpr > 0 ? world * cpr : 1), rank, world, copy_ctas, status);
   if (r) return r;
@@ -1165,6 +1330,15 @@ TB_EXPORT int tb_ag_gemm(void* a_full, const void* const* shards, const void* co
   if (r) return r;
   if (world > 1) gemm_bump_epoch_kernel<<<1, 1, 0, stream>>>(const_cast<unsigned*>(epoch_ptr));
   TB_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// After a kernel gave up on a wait (status word set) its scheduler counters may not have been reset: clear them all.
+TB_EXPORT int tb_gemm_reset_scheduler(cudaStream_t stream) {
+  TB_ENSURE_DEVICE();
+  unsigned* p = nullptr;
+  TB_CUDA_CHECK(cudaGetSymbolAddress((void**)&p, tb::g_sched_counters));
+  TB_CUDA_CHECK(cudaMemsetAsync(p, 0, sizeof(unsigned) * 2 * tb::SCHED_SLOTS, stream));
   return 0;
 }
 

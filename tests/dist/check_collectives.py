@@ -117,8 +117,9 @@ def check_fsdp(dev):
     log(f"single-process oracle: {[round(v, 4) for v in ref_losses]}")
     FS, SGO, NS = ShardingStrategy.FULL_SHARD, ShardingStrategy.SHARD_GRAD_OP, ShardingStrategy.NO_SHARD
     cases = [(SGO, dict(overlap=False), False), (SGO, dict(overlap=False), True), (SGO, dict(overlap=True), False),
-             (SGO, dict(overlap=True), True), (FS, dict(fuse_gather=True), False), (FS, dict(fuse_gather=True), True),
-             (FS, dict(fuse_gather=False), True), (NS, dict(), True)]
+             (SGO, dict(overlap=True), True), (FS, dict(), False), (FS, dict(), True), (FS, dict(overlap_rs=True), True),
+             (FS, dict(gather_mode="fused", fuse_gather=True), False), (FS, dict(gather_mode="fused", fuse_gather=True), True),
+             (FS, dict(gather_mode="kernel", fuse_gather=False, overlap_rs=True), True), (NS, dict(), True)]
     for strategy, kw, use_graph in cases:
         torch.manual_seed(0)
         model = GPTForCausalLM(cfg).to(dev)

@@ -152,5 +152,11 @@ def check_status(device=None, reset: bool = True) -> None:
     if code != 0:
         if reset:
             st.zero_()
+            try:   # a kernel that gave up may have left its tile-scheduler counters non-zero
+                f = cuda().tb_gemm_reset_scheduler
+                f.restype, f.argtypes = ctypes.c_int, [ctypes.c_void_p]
+                f(stream_ptr())
+            except Exception:
+                pass
         exc = KernelCheckFailed if code in (107, 108) else KernelTimeout
         raise exc(f"device status {code}: {_STATUS_NAMES.get(code, 'unknown')}")

@@ -92,10 +92,21 @@ class FsdpConfig:
     tail_blocks: int = 296     # CTAs of the units that are reduced after backward has finished
     use_nvls: bool | None = None
     # ---- FULL_SHARD only
-    fuse_gather: bool = True   # un-shard a block inside the first GEMM that reads it (False: stand-alone gather in the hook)
+    # How a block is un-sharded. "copy_engine": the DMA engines pull every rank's shard into the next block's buffer on a
+    # side stream while the current block computes (no SM, no cross-rank barrier); "fused": inside the first GEMM that
+    # reads the block (a copy warp in every CTA of that GEMM, per-chunk ready words); "kernel": a stand-alone gather
+    # kernel right before the block. Measured on GPT-2-medium the DMA prefetch is the fastest: see the FSDP notes.
+    gather_mode: str = "copy_engine"
+    fuse_gather: bool = True   # gather_mode "fused" (True) / "kernel" (False) when gather_mode is not "copy_engine"
     gather_ctas: int = 16      # copy CTAs inside that GEMM
     root_gather_ctas: int = 96 # copy CTAs of a stand-alone gather
-    rs_blocks: int = 32        # CTAs of a block's reduce-scatter + AdamW kernel while it runs under the backward pass
+    rs_blocks: int = 64        # CTAs of a block's reduce-scatter + AdamW kernel while it runs under the backward pass
+    rs_threads: int = 128      # ... and threads per CTA: 128 threads (8 K registers, no shared memory to speak of) fit on an SM
+                               # next to a CTA of any backward kernel, so the overlap takes no SM away from them
+    overlap_rs: bool = False   # True: each block's reduce-scatter + AdamW on a side stream under the next block's backward;
+                               # False: on the main stream at full width (measured faster: the side-stream CTAs hold whole
+                               # SMs away from the statically resident backward kernels for longer than the kernel takes
+                               # when it has the GPU to itself)
     replica_group: object = None  # HYBRID_SHARD: the group that links the replicas of this rank's shard
 
 
@@ -450,7 +461,7 @@ _SIG = [ctypes.c_void_p] * 8 + [ctypes.c_int64] * 3 + [ctypes.c_int] * 2 + [ctyp
 
 
 _SIG_FS = [ctypes.c_void_p] * 7 + [ctypes.c_int64] * 3 + [ctypes.c_int] * 2 + [ctypes.c_void_p] + [ctypes.c_float] * 6 + [
-    ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
 _SIG_GATHER = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 5 + [ctypes.c_void_p] * 2
 
 
@@ -473,6 +484,11 @@ class FlatFSDP:
         self._opt = None
         # FULL_SHARD state
         self.ctx_main = None                         # gathers (main stream)
+        self.copy_stream = torch.cuda.Stream()       # DMA prefetch of the next block's parameters
+        self._prefetched: dict[int, torch.cuda.Event] = {}
+        self._resident: dict[int, int] = {}          # rotating buffer -> the block it holds, within one step
+        self._direction = 1                          # +1 while the forward pass walks the blocks, -1 in backward
+        self._comm_used = False
         self._pending_gather: int | None = None
         self._rs_done: dict[int, torch.cuda.Event] = {}
         self._begun = False
@@ -591,13 +607,51 @@ class FlatFSDP:
                 f"(set FsdpConfig.fuse_gather=False)")
         if not self._flat.layouts[ui].params:
             return
+        if self.cfg.gather_mode == "copy_engine":
+            return self._await_prefetch(ui)
         if self.cfg.fuse_gather:
             self._pending_gather = ui
         else:
             self._gather_unit(ui, self.cfg.root_gather_ctas)
 
+    # ---- FULL_SHARD: DMA prefetch ----------------------------------------------------------------------
+    def _prefetch(self, ui: int):
+        """Queue the un-shard of block `ui` on the copy stream: one device-to-device copy per rank's shard, executed by
+        the copy engines. It may start once the block that used the same rotating buffer last has finished (the copy
+        stream waits for everything queued on the compute stream so far). No cross-rank barrier is needed: a rank's
+        shard is only rewritten by that block's reduce-scatter + AdamW kernel, whose entry barrier every rank reaches
+        after it has consumed this gather."""
+        f = self._flat
+        if ui < 1 or ui >= len(f.layouts) or not f.layouts[ui].params or ui in self._prefetched:
+            return
+        lay, so = f.layouts[ui], f.shard_offsets[ui]
+        buf = f.unit_buffer(ui)
+        cur = torch.cuda.current_stream()
+        self.copy_stream.wait_stream(cur)
+        with torch.cuda.stream(self.copy_stream):
+            for k in range(self.world):
+                q = (self.rank + k) % self.world          # own shard first, then the peers in ring order
+                src = f.shard_buf.peer_tensor(q)[so:so + lay.shard]
+                buf[q * lay.shard:(q + 1) * lay.shard].copy_(src, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self.copy_stream)
+        self._prefetched[ui] = ev
+        self._resident.pop(f.slot(ui), None)
+
+    def _await_prefetch(self, ui: int):
+        slot = self._flat.slot(ui)
+        if ui in self._prefetched:
+            torch.cuda.current_stream().wait_event(self._prefetched.pop(ui))
+        elif self._resident.get(slot) != ui:       # else: still whole from the forward pass (the deepest block)
+            self._prefetch(ui)
+            torch.cuda.current_stream().wait_event(self._prefetched.pop(ui))
+        self._resident[slot] = ui
+        # the neighbour in the direction of travel goes to the other rotating buffer while this block computes
+        self._prefetch(ui + self._direction)
+
     def _fs_pre_forward(self, ui: int):
         def hook(module, args):
+            self._direction = 1
             self._arm_gather(ui)
             if torch.is_grad_enabled():
                 for a in args:
@@ -623,6 +677,7 @@ class FlatFSDP:
         if ev is not None:
             # the unit that used this gradient buffer last (two blocks deeper) must have been reduced and cleared
             torch.cuda.current_stream().wait_event(ev)
+        self._direction = -1
         self._arm_gather(ui)
 
     def take_pending_gather(self, ui: int, weight: torch.Tensor, fusable: bool = True):
@@ -660,7 +715,7 @@ class FlatFSDP:
         self._begun = True
         self._gather_unit(0, self.cfg.root_gather_ctas)
 
-    def _rs_unit(self, ui: int, stream, blocks: int):
+    def _rs_unit(self, ui: int, stream, blocks: int, threads: int = 512):
         f, o = self._flat, self._opt
         lay = f.layouts[ui]
         if not lay.params:
@@ -671,7 +726,7 @@ class FlatFSDP:
         call("tb_fsdp_rs_adamw", _SIG_FS, gbuf.ptr_array, self.ctx.flags.ptr_array, gbuf.mc(nvls), f.master.data_ptr(),
              f.exp_avg.data_ptr(), f.exp_avg_sq.data_ptr(), f.shard_lowp.data_ptr(), 0, lay.length, f.shard_offsets[ui],
              self.rank, self.world, self.ctx.epoch.data_ptr(), o.param_groups[0]["lr"], o.betas[0], o.betas[1], o.eps,
-             o.weight_decay, 1.0 / self._grad_divisor(), o.dyn.data_ptr(), blocks, st.data_ptr(), nv.stream_ptr(stream))
+             o.weight_decay, 1.0 / self._grad_divisor(), o.dyn.data_ptr(), blocks, threads, st.data_ptr(), nv.stream_ptr(stream))
 
     def _grad_divisor(self) -> int:
         rg = self.cfg.replica_group
@@ -685,9 +740,13 @@ class FlatFSDP:
         cur = torch.cuda.current_stream()
         if self.cfg.replica_group is not None:
             dist.all_reduce(self._flat.grad_buffer(ui).tensor[:self._flat.layouts[ui].length], group=self.cfg.replica_group)
+        if not self.cfg.overlap_rs:
+            self._rs_unit(ui, cur, self.cfg.tail_blocks)
+            return
+        self._comm_used = True
         self.comm_stream.wait_stream(cur)
         with torch.cuda.stream(self.comm_stream):
-            self._rs_unit(ui, self.comm_stream, self.cfg.rs_blocks)
+            self._rs_unit(ui, self.comm_stream, self.cfg.rs_blocks, self.cfg.rs_threads)
             ev = torch.cuda.Event()
             ev.record(self.comm_stream)
         self._rs_done[self._flat.slot(ui)] = ev
@@ -695,8 +754,13 @@ class FlatFSDP:
     def _full_shard_step(self, flat: FullShardParameters, opt):
         cur = torch.cuda.current_stream()
         todo = sorted((u for u in range(1, len(flat.layouts)) if u not in self._launched), reverse=True)
-        if self._launched:
+        if self._comm_used:
             cur.wait_stream(self.comm_stream)
+            self._comm_used = False
+        for ev in self._prefetched.values():      # a prefetch nobody consumed (e.g. past the first block in backward)
+            cur.wait_event(ev)
+        self._prefetched.clear()
+        self._resident.clear()                    # the shards change below
         rg = self.cfg.replica_group
         for u in todo + [0]:
             if rg is not None:

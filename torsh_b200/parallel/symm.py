@@ -73,6 +73,15 @@ class SymmetricBuffer:
         back = raw[self.guard_bytes + self.tensor.numel() * es:]
         return bool((front == CANARY_BYTE).all().item()) and bool((back == CANARY_BYTE).all().item())
 
+    def peer_tensor(self, rank: int) -> torch.Tensor:
+        """Rank ``rank``'s copy of the payload as a tensor of this process (peer-mapped memory): usable as the source or
+        destination of copies and as a kernel operand, not by library kernels."""
+        if rank == self.rank:
+            return self.tensor
+        g = self.guard_bytes // self._raw.element_size()
+        full = self.handle.get_buffer(rank, (self._raw.numel(),), self._raw.dtype, 0)
+        return full[g:g + self.tensor.numel()]
+
     @property
     def ptr_array(self):
         """``void* [8]`` for the launchers."""
