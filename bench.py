@@ -226,7 +226,7 @@ def main():
             fc.rs_blocks = args.fsdp_rs_blocks
         if args.fsdp_rs_threads:
             fc.rs_threads = args.fsdp_rs_threads
-        fc.overlap_rs = args.fsdp_overlap_rs and not args.fsdp_no_overlap_rs
+        fc.overlap_rs = True if args.fsdp_overlap_rs else (False if args.fsdp_no_overlap_rs else None)
         if args.fsdp_comm_blocks:
             fc.comm_blocks = args.fsdp_comm_blocks
         fc.overlap = bool(args.fsdp_overlap) and not args.fsdp_no_overlap

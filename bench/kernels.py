@@ -44,7 +44,7 @@ def timeit(fn, iters, flush):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--no-residual", action="store_true", help="bn: BatchNorm + ReLU without a residual input")
-    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "layernorm", "xent", "adamw", "bn", "conv", "fsdp_gather"])
+    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "layernorm", "layernorm_bwd", "xent", "adamw", "bn", "conv", "fsdp_gather"])
     ap.add_argument("--hw", type=int, default=56); ap.add_argument("--channels", type=int, default=256)
     ap.add_argument("--cout", type=int, default=0); ap.add_argument("--ksize", type=int, default=3); ap.add_argument("--stride", type=int, default=1)
     ap.add_argument("--m", type=int, default=8192); ap.add_argument("--n", type=int, default=4096); ap.add_argument("--k", type=int, default=4096)
@@ -147,6 +147,16 @@ def main():
             ms = timeit(lambda: layer_norm(x, w, b), a.iters, flush)
         gb = 2.0 * x.numel() * 2 / ms / 1e6
         print(f"layernorm fwd {a.m}x{a.n}: {ms*1e3:.1f} us, {gb:.0f} GB/s = {gb/hbm:.2f} of {kind} copy bandwidth")
+    elif a.what == "layernorm_bwd":
+        from torsh_b200.ops.norm import layer_norm
+        x = torch.randn(a.m, a.n, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        w = torch.ones(a.n, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        b = torch.zeros(a.n, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        y = layer_norm(x, w, b)
+        dy = torch.randn_like(y)
+        ms = timeit(lambda: torch.autograd.grad(y, (x, w, b), dy, retain_graph=True), a.iters, flush)
+        gb = 3.0 * x.numel() * 2 / ms / 1e6          # dy and x in, dx out
+        print(f"layernorm bwd {a.m}x{a.n} (incl. the weight-gradient reduction): {ms*1e3:.1f} us, {gb:.0f} GB/s = {gb/hbm:.2f} of {kind} copy bandwidth")
     elif a.what == "xent":
         from torsh_b200.ops.softmax import cross_entropy
         lg = torch.randn(a.m, 50304, device=dev, dtype=torch.bfloat16, requires_grad=True)

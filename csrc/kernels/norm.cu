@@ -209,6 +209,208 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Warp-per-row forms for rows of at most 32 * VPL 16-byte vectors (H <= 2048 bf16, 1024 fp32). A warp owns a row: its
+// statistics are two shuffle reductions with no block barrier, eight rows are in flight per CTA and the next row of
+// every warp is requested before the current one is reduced. With one CTA per row a 2 KB row left too few bytes in
+// flight per SM and two block barriers per row on the critical path (0.43 of the copy bandwidth at 32768 x 1024).
+constexpr int NORM_WARPS = 8;
+
+template <typename T, int VPL, bool RMS>
+__global__ void __launch_bounds__(NORM_WARPS * 32, VPL <= 4 ? 2 : 1) norm_fwd_warp_kernel(
+    const T* __restrict__ x, const T* __restrict__ gamma, const T* __restrict__ beta, T* __restrict__ y,
+    float* __restrict__ mean_out, float* __restrict__ rstd_out, int rows, int H, float eps) {
+  constexpr int N = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int nvec = H / N;
+  const int nwarps = gridDim.x * NORM_WARPS;
+  Vec16<T> g[VPL], b[VPL], nxt[VPL];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+      g[i].load_nc(gamma + v * N);
+      if (!RMS && beta) b[i].load_nc(beta + v * N);
+    }
+  }
+  int row = blockIdx.x * NORM_WARPS + (threadIdx.x >> 5);
+  if (row < rows) {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+      if (lane + 32 * i < nvec) nxt[i].load(x + (size_t)row * H + (lane + 32 * i) * N);
+  }
+  const float inv_h = 1.f / (float)H;
+  for (; row < rows; row += nwarps) {
+    float f[VPL][N];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      if (lane + 32 * i < nvec) {
+        nxt[i].get(f[i]);
+#pragma unroll
+        for (int j = 0; j < N; ++j) s += RMS ? f[i][j] * f[i][j] : f[i][j];
+      }
+    }
+    if (row + nwarps < rows) {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i)
+        if (lane + 32 * i < nvec) nxt[i].load(x + (size_t)(row + nwarps) * H + (lane + 32 * i) * N);
+    }
+    float mean = 0.f, rstd;
+    if (RMS) {
+      rstd = rsqrtf(warp_sum(s) * inv_h + eps);
+    } else {
+      mean = warp_sum(s) * inv_h;
+      float sq = 0.f;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        if (lane + 32 * i < nvec) {
+#pragma unroll
+          for (int j = 0; j < N; ++j) {
+            const float d = f[i][j] - mean;
+            sq += d * d;
+          }
+        }
+      }
+      rstd = rsqrtf(warp_sum(sq) * inv_h + eps);
+    }
+    if (lane == 0) {
+      if (mean_out) mean_out[row] = mean;
+      if (rstd_out) rstd_out[row] = rstd;
+    }
+    T* yr = y + (size_t)row * H;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float gf[N], bf[N], o[N];
+        g[i].get(gf);
+        if (!RMS && beta) b[i].get(bf);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          o[j] = (f[i][j] - mean) * rstd * gf[j];
+          if (!RMS && beta) o[j] += bf[j];
+        }
+        Vec16<T> t;
+        t.set(o);
+        t.store(yr + v * N);
+      }
+    }
+  }
+}
+
+// Same arithmetic as norm_bwd_kernel. Every lane keeps fp32 partial sums of d(gamma) / d(beta) for its own columns
+// over all rows of its warp; the CTA's eight warps then add theirs in shared memory (2 * H floats) and the CTA writes
+// one partial row of the workspace (or adds into the gradients with atomics when there is none).
+template <typename T, int VPL, bool RMS>
+__global__ void __launch_bounds__(NORM_WARPS * 32) norm_bwd_warp_kernel(
+    const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ gamma, const float* __restrict__ mean_in,
+    const float* __restrict__ rstd_in, const T* __restrict__ dres, T* __restrict__ dx, float* __restrict__ dgamma,
+    float* __restrict__ dbeta, float* __restrict__ partial, int rows, int H) {
+  constexpr int N = Vec16<T>::N;
+  extern __shared__ float nb_sums[];  // [2][H]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nvec = H / N;
+  const int nwarps = gridDim.x * NORM_WARPS;
+  float gf[VPL][N], dg[VPL][N], db[VPL][N];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) dg[i][j] = db[i][j] = gf[i][j] = 0.f;
+    if (lane + 32 * i < nvec) {
+      Vec16<T> t;
+      t.load_nc(gamma + (lane + 32 * i) * N);
+      t.get(gf[i]);
+    }
+  }
+  Vec16<T> nx[VPL], nd[VPL], nr[VPL];
+  auto request = [&](int r) {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        nx[i].load(x + (size_t)r * H + v * N);
+        nd[i].load(dy + (size_t)r * H + v * N);
+        if (dres) nr[i].load(dres + (size_t)r * H + v * N);
+      }
+    }
+  };
+  int row = blockIdx.x * NORM_WARPS + warp;
+  if (row < rows) request(row);
+  const float inv_h = 1.f / (float)H;
+  for (; row < rows; row += nwarps) {
+    const float mean = RMS ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float xh[VPL][N], dyg[VPL][N], res[VPL][N];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      if (lane + 32 * i < nvec) {
+        float xf[N], df[N];
+        nx[i].get(xf);
+        nd[i].get(df);
+        if (dres) nr[i].get(res[i]);
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+          xh[i][j] = (xf[j] - mean) * rstd;
+          dyg[i][j] = df[j] * gf[i][j];
+          dg[i][j] += df[j] * xh[i][j];
+          db[i][j] += df[j];
+          s1 += dyg[i][j];
+          s2 += dyg[i][j] * xh[i][j];
+        }
+      }
+    }
+    if (row + nwarps < rows) request(row + nwarps);
+    s1 = RMS ? 0.f : warp_sum(s1) * inv_h;
+    s2 = warp_sum(s2) * inv_h;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        float o[N];
+#pragma unroll
+        for (int j = 0; j < N; ++j) o[j] = (dres ? res[i][j] : 0.f) + rstd * (dyg[i][j] - s1 - xh[i][j] * s2);
+        Vec16<T> t;
+        t.set(o);
+        t.store(dx + (size_t)row * H + v * N);
+      }
+    }
+  }
+  // the eight warps take turns adding their column sums into shared memory
+  for (int w = 0; w < NORM_WARPS; ++w) {
+    if (warp == w) {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int v = lane + 32 * i;
+        if (v < nvec) {
+#pragma unroll
+          for (int j = 0; j < N; ++j) {
+            float* pg = nb_sums + v * N + j;
+            if (w == 0) {
+              pg[0] = dg[i][j];
+              pg[H] = db[i][j];
+            } else {
+              pg[0] += dg[i][j];
+              pg[H] += db[i][j];
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  for (int c = threadIdx.x; c < H; c += blockDim.x) {
+    if (partial) {
+      partial[(size_t)blockIdx.x * 2 * H + c] = nb_sums[c];
+      if (!RMS) partial[(size_t)blockIdx.x * 2 * H + H + c] = nb_sums[H + c];
+    } else {
+      if (dgamma) atomicAdd(dgamma + c, nb_sums[c]);
+      if (!RMS && dbeta) atomicAdd(dbeta + c, nb_sums[H + c]);
+    }
+  }
+}
+
 // dgamma[c] += sum_b partial[b][0][c]; dbeta[c] += sum_b partial[b][1][c].
 // A CTA owns 32 columns; its 32 x 32 threads split the nblk partial rows 32 ways (coalesced 128-byte reads), then
 // the 32 row-groups meet in shared memory. With hundreds of partial rows a one-thread-per-column loop is a chain of
@@ -244,6 +446,20 @@ static int norm_fwd_launch(const void* x, const void* gamma, const void* beta, v
   constexpr int N = Vec16<T>::N;
   if (H % N) TB_FAIL(TB_E_ARG, "norm: H=%d must be a multiple of %d", H, N);
   int nvec = H / N;
+  if (nvec <= 32 * 8) {
+    // resident CTAs only (two per SM up to four vectors per lane, one above): every warp then streams several rows
+    // with the next one already requested
+    const int want = (rows + NORM_WARPS - 1) / NORM_WARPS;
+    const int cap = sm_count() * (nvec <= 128 ? 2 : 1);
+    const int wgrid = want < cap ? want : cap;
+#define TB_NFW(VPL_)                                                                                                  \
+  norm_fwd_warp_kernel<T, VPL_, RMS><<<wgrid, NORM_WARPS * 32, 0, st>>>((const T*)x, (const T*)gamma, (const T*)beta, \
+                                                                        (T*)y, mean, rstd, rows, H, eps);
+    if (nvec <= 32) TB_NFW(1) else if (nvec <= 64) TB_NFW(2) else if (nvec <= 128) TB_NFW(4) else TB_NFW(8)
+#undef TB_NFW
+    TB_CUDA_CHECK(cudaGetLastError());
+    return 0;
+  }
   int grid = rows < sm_count() * 8 ? rows : sm_count() * 8;
 #define TB_NF(VPT_)                                                                                 \
   {                                                                                                 \
@@ -267,6 +483,24 @@ static int norm_bwd_launch(const void* dy, const void* x, const void* gamma, con
   if (H % N) TB_FAIL(TB_E_ARG, "norm: H=%d must be a multiple of %d", H, N);
   int nvec = H / N;
   int grid = norm_bwd_grid(rows);
+  if (nvec <= 32 * 4) {  // eight vectors per lane would spill: wider rows keep the CTA-per-row kernel
+    // never more CTAs than the cap above: the workspace (also the fixed one of tb_norm_bwd_static) is sized for it
+    const int want = (rows + NORM_WARPS - 1) / NORM_WARPS;
+    const int cap = sm_count() * (nvec <= 32 ? 3 : 1);  // resident CTAs: 80 / 158 / 255 registers per thread
+    const int wgrid = want < (cap < grid ? cap : grid) ? want : (cap < grid ? cap : grid);
+    const size_t smem = (size_t)2 * H * sizeof(float);
+#define TB_NBW(VPL_)                                                                                           \
+  norm_bwd_warp_kernel<T, VPL_, RMS><<<wgrid, NORM_WARPS * 32, smem, st>>>(                                    \
+      (const T*)dy, (const T*)x, (const T*)gamma, mean, rstd, (const T*)dres, (T*)dx, dgamma, dbeta, partial, rows, H);
+    if (nvec <= 32) TB_NBW(1) else if (nvec <= 64) TB_NBW(2) else TB_NBW(4)
+#undef TB_NBW
+    if (partial) {
+      dim3 rgrid((H + 31) / 32, RMS ? 1 : 2);
+      norm_bwd_reduce_kernel<<<rgrid, dim3(32, 32), 0, st>>>(partial, dgamma, dbeta, wgrid, H);
+    }
+    TB_CUDA_CHECK(cudaGetLastError());
+    return 0;
+  }
 #define TB_NB(VPT_)                                                                               \
   {                                                                                               \
     int threads = ((nvec + VPT_ - 1) / VPT_ + 31) / 32 * 32;                                      \
