@@ -37,6 +37,8 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--pp-blocking", action="store_true",
+                    help="pipeline transfers as blocking paired exchanges (default: per-link groups, sends not waited for)")
     ap.add_argument("--dense-head", action="store_true",
                     help="every TP rank computes all logits (default: vocabulary-parallel head and loss)")
     args = ap.parse_args()
@@ -98,7 +100,8 @@ def main():
     stage = Stage(model)
     rows = B * S // args.tp if args.tp > 1 else B * S
     pipe = PipelineParallel(stage, group=mesh.pp_group,
-                            config=PipelineConfig(num_micro_batches=M, schedule=ScheduleType.ONE_F_ONE_B),
+                            config=PipelineConfig(num_micro_batches=M, schedule=ScheduleType.ONE_F_ONE_B,
+                                                  overlap=not args.pp_blocking, measure_idle=True),
                             activation_shape=(rows, args.hidden), activation_dtype=torch.bfloat16) if args.pp > 1 else None
     if pipe is not None and tpc is not None:
         pipe.micro_batch_hook = lambda mb, slot: setattr(tpc, "slot", slot)
@@ -171,6 +174,9 @@ def main():
     e2e_ms = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop()
     nv.check_status()
+    # device time of the last step that no forward / backward action covered: the pipeline bubble plus exposed transfers
+    idle = torch.tensor([pipe.idle_ms() or 0.0 if pipe is not None else 0.0], dtype=torch.float64, device=dev)
+    dist.all_reduce(idle, op=dist.ReduceOp.MAX)
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = t.tolist()
@@ -191,6 +197,8 @@ def main():
                        "params_b": round(n_params / 1e9, 2)},
             "e2e": {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": M * (S + 1) * 8, "d2h_bytes_per_step": 4},
+            "pipeline": {"transfers": "blocking pairs" if args.pp_blocking else "per-link groups, asynchronous sends",
+                         "idle_ms_last_step_max_over_ranks": idle.item()},
             "clocks": clocks, "gpu_launches": per_step * args.steps, "launches_per_step": per_step,
             "loss_after_warmup": first_all, "loss_last": last.item()}))
     dist.barrier()

@@ -42,7 +42,13 @@ class PipelineConfig:
     # for until the end of the step, so transfers run on the link's own stream under this stage's compute.
     # overlap=False: sends and the receive they are paired with travel as one blocking batch.
     overlap: bool = True
-    recv_lookahead: int = 2
+    # How many actions ahead of its use a receive may be posted. A receive is never posted before every action of THIS
+    # rank that the incoming tensor depends on has been issued (the forward of the same micro-batch for a gradient, the
+    # previous chunk's forward for a wrapped-around activation). On CUDA the default is 0 (post where the tensor is
+    # consumed): an NCCL receive is a kernel that holds SMs while it waits, and the persistent GEMMs of the action that
+    # runs meanwhile deal their tiles statically to one CTA per SM, so a parked receive stalls them until the sender
+    # delivers (and deadlocks when the sender is waiting for this rank's output). None = 2 on CPU, 0 on CUDA.
+    recv_lookahead: int | None = None
     measure_idle: bool = False   # record events around every action; idle_ms() then gives the device idle time of the last step
 
 
@@ -176,9 +182,21 @@ class PipelineParallel:
         timing = self.cfg.measure_idle and self.device.type == "cuda"
         marks = []
 
-        def post_recv(i):
+        index_of = {a: j for j, a in enumerate(acts)}
+        lookahead = self.cfg.recv_lookahead
+        if lookahead is None:
+            lookahead = 0 if self.device.type == "cuda" else 2
+
+        def own_dependency(j):
+            """Index of the last action of this rank that the tensor received for action j depends on (-1: none)."""
+            kind, mb, c = acts[j]
+            if kind == "B":
+                return index_of[("F", mb, c)]
+            return index_of[("F", mb, c - 1)] if c > 0 else -1
+
+        def post_recv(i, issued=-1):
             spec = self._recv_spec(acts[i])
-            if spec is None or i in posted:
+            if spec is None or i in posted or own_dependency(i) > issued:
                 return
             kind, src, tag = spec
             buf = torch.empty(self.act_shape, dtype=self.act_dtype, device=self.device)
@@ -191,11 +209,10 @@ class PipelineParallel:
             sends.append((dist.isend(t, dst, group=grp, tag=tag), t))   # the tensor stays referenced until the send is done
             self.stats["sends"] += 1
 
-        for j in range(min(self.cfg.recv_lookahead, len(acts))):
-            post_recv(j)
         for i, (kind, mb, c) in enumerate(acts):
-            if i + self.cfg.recv_lookahead < len(acts):
-                post_recv(i + self.cfg.recv_lookahead)
+            # actions 0 .. i-1 have been issued: post what may be posted up to `lookahead` actions ahead
+            for j in range(i, min(i + lookahead, len(acts) - 1) + 1):
+                post_recv(j, issued=i - 1)
             got = None
             if i in posted:
                 w, got = posted.pop(i)
