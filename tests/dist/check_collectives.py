@@ -348,6 +348,49 @@ def check_canaries(dev):
     return ok
 
 
+def check_native_heap(dev):
+    """The package's own symmetric heap (cuMemCreate blocks exchanged as file descriptors, cuMemMap of every peer, one
+    multicast object): peers see each other's writes, the fused collectives run on its blocks through peer loads and
+    through the multicast address, blocks are released collectively."""
+    from torsh_b200 import _native as nv
+    from torsh_b200.parallel.collectives import FusedCollectives
+    from torsh_b200.parallel.symm import SymmetricBuffer
+    rank, world = dist.get_rank(), dist.get_world_size()
+    os.environ["TORSH_SYMM_BACKEND"] = "native"
+    ok = True
+    try:
+        n = 1 << 20
+        buf = SymmetricBuffer(n, torch.float32)
+        ok &= buf.native and bool((buf.tensor == 0).all())
+        buf.tensor.fill_(float(rank + 1))
+        torch.cuda.synchronize()
+        dist.barrier()
+        for q in range(world):
+            got = buf.peer_tensor(q)
+            ok &= bool((got == float(q + 1)).all())
+        dist.barrier()
+        fc = FusedCollectives(nblocks=32)          # its flag buffer comes from the native heap too
+        for use_nvls in ([False, True] if buf.has_multicast else [False]):
+            fc.use_nvls = use_nvls
+            buf.tensor.fill_(float(rank + 1))
+            torch.cuda.synchronize()
+            dist.barrier()
+            fc.all_reduce_(buf, numel=n, scale=1.0, mode="two_shot")
+            torch.cuda.synchronize()
+            nv.check_status()
+            good = bool((buf.tensor == world * (world + 1) / 2).all())
+            log(f"native heap all-reduce nvls={use_nvls}: {'ok' if good else 'WRONG'} (multicast address {'yes' if buf.has_multicast else 'no'})")
+            ok &= good
+            dist.barrier()
+        torch.cuda.synchronize()
+        dist.barrier()
+        buf.release()
+        ok &= buf.tensor is None
+    finally:
+        os.environ["TORSH_SYMM_BACKEND"] = "torch"
+    return ok
+
+
 def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -367,6 +410,8 @@ def main():
         ok &= check_moe(dev)
     if "canaries" in what:
         ok &= check_canaries(dev)
+    if "native_heap" in what:
+        ok &= check_native_heap(dev)
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     log("ALL CHECKS PASSED" if flag.item() == 1 else "CHECKS FAILED")

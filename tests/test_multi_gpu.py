@@ -11,7 +11,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("what", ["collectives", "fsdp", "tp", "ddp", "moe", "canaries"])
+@pytest.mark.parametrize("what", ["collectives", "fsdp", "tp", "ddp", "moe", "canaries", "native_heap"])
 def test_multi_rank(what):
     n = min(torch.cuda.device_count(), 8)
     n = 8 if n >= 8 else (4 if n >= 4 else 2)
