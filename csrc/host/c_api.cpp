@@ -3,6 +3,10 @@
 // reference arithmetic (crates/torsh-optim/src/sgd.rs:443-610, adam.rs:809-950). This is the portable surface other
 // language bindings link against; GPU work goes through the Python package.
 #include <algorithm>
+#include <atomic>
+#include <chrono>
+#include <map>
+#include <string>
 #include <cmath>
 #include <cstring>
 #include <functional>
@@ -12,9 +16,35 @@
 #include "host_api.h"
 #include "torsh.h"
 
+// Tensor storage is counted: torsh_get_memory_usage / torsh_get_peak_memory_usage report the bytes held by live
+// tensors of this library (the reference keeps the same two counters, crates/torsh-ffi/src/c_api/utils.rs).
+static std::atomic<size_t> g_mem_now{0}, g_mem_peak{0};
+template <typename T>
+struct CountingAlloc {
+  using value_type = T;
+  CountingAlloc() = default;
+  template <typename U>
+  CountingAlloc(const CountingAlloc<U>&) {}
+  T* allocate(size_t n) {
+    const size_t now = g_mem_now.fetch_add(n * sizeof(T)) + n * sizeof(T);
+    size_t peak = g_mem_peak.load();
+    while (now > peak && !g_mem_peak.compare_exchange_weak(peak, now)) {
+    }
+    return static_cast<T*>(::operator new(n * sizeof(T)));
+  }
+  void deallocate(T* p, size_t n) {
+    g_mem_now.fetch_sub(n * sizeof(T));
+    ::operator delete(p);
+  }
+  template <typename U>
+  bool operator==(const CountingAlloc<U>&) const { return true; }
+  template <typename U>
+  bool operator!=(const CountingAlloc<U>&) const { return false; }
+};
+
 struct TorshTensor {
   std::vector<int64_t> shape;
-  std::vector<float> data;
+  std::vector<float, CountingAlloc<float>> data;
   int64_t numel() const {
     int64_t n = 1;
     for (auto d : shape) n *= d;
@@ -356,3 +386,154 @@ EXPORT TorshStatus torsh_optimizer_zero_grad(TorshOptimizer* o) {
   return 0;
 }
 EXPORT void torsh_optimizer_free(TorshOptimizer* o) { delete o; }
+
+// ---- the rest of the reference's C surface (crates/torsh-ffi/src/c_api/{tensor,tensor_math,neural,optimizer,utils}.rs) -----
+namespace {
+int g_threads = 1;
+bool g_autocast = false, g_debug = false, g_profiling = false;
+std::chrono::steady_clock::time_point g_prof_start;
+std::string g_prof_json;
+struct StandaloneState {            // optimizers created without layers step explicit tensors (torsh_*_step_inplace)
+  float lr, b1, b2, eps;
+};
+}  // namespace
+
+EXPORT void torsh_clear_last_error(void) { g_err.clear(); }
+EXPORT int torsh_has_error(void) { return g_err.empty() ? 0 : 1; }
+EXPORT int torsh_get_device_type(void) { return 0; }  // 0 = host: the C surface computes on the host
+EXPORT int torsh_get_device_id(void) { return 0; }
+EXPORT size_t torsh_cuda_device_memory(int) { return 0; }
+EXPORT const char* torsh_cuda_device_name(int) { return ""; }
+EXPORT size_t torsh_get_memory_usage(void) { return g_mem_now.load(); }
+EXPORT size_t torsh_get_peak_memory_usage(void) { return g_mem_peak.load(); }
+EXPORT TorshStatus torsh_reset_memory_tracking(void) {
+  g_mem_peak.store(g_mem_now.load());
+  return 0;
+}
+EXPORT int torsh_get_num_threads(void) { return g_threads; }
+EXPORT TorshStatus torsh_set_num_threads(int n) {
+  if (n < 1) { g_err = "thread count must be positive"; return 1; }
+  g_threads = n;
+  return 0;
+}
+EXPORT TorshStatus torsh_set_autocast(int e) { g_autocast = e != 0; return 0; }
+EXPORT int torsh_is_autocast_enabled(void) { return g_autocast ? 1 : 0; }
+EXPORT TorshStatus torsh_set_debug_mode(int e) { g_debug = e != 0; return 0; }
+EXPORT int torsh_is_debug_mode_enabled(void) { return g_debug ? 1 : 0; }
+EXPORT TorshStatus torsh_start_profiling(void) {
+  g_profiling = true;
+  g_prof_start = std::chrono::steady_clock::now();
+  return 0;
+}
+// JSON object {"elapsed_ms": ..., "memory_bytes": ..., "peak_memory_bytes": ...}; the string stays valid until the next call.
+EXPORT const char* torsh_stop_profiling(void) {
+  if (!g_profiling) return "";
+  g_profiling = false;
+  const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - g_prof_start).count();
+  g_prof_json = "{\"elapsed_ms\": " + std::to_string(ms) + ", \"memory_bytes\": " + std::to_string(g_mem_now.load()) +
+                ", \"peak_memory_bytes\": " + std::to_string(g_mem_peak.load()) + "}";
+  return g_prof_json.c_str();
+}
+
+EXPORT size_t torsh_tensor_size(const TorshTensor* t) { return t ? (size_t)t->numel() : 0; }
+EXPORT TorshTensor* torsh_tensor_scalar(float v) {
+  auto* t = new TorshTensor();
+  t->data = {v};
+  return t;
+}
+EXPORT TorshTensor* torsh_tensor_eye(size_t n) {
+  int64_t shape[2] = {(int64_t)n, (int64_t)n};
+  TorshTensor* t = make(shape, 2, 0.f);
+  if (t) for (size_t i = 0; i < n; ++i) t->data[i * n + i] = 1.f;
+  return t;
+}
+EXPORT TorshTensor* torsh_tensor_linspace(double start, double end, size_t steps) {
+  if (steps == 0) return fail("linspace: steps must be positive");
+  int64_t shape[1] = {(int64_t)steps};
+  TorshTensor* t = make(shape, 1, 0.f);
+  if (t) for (size_t i = 0; i < steps; ++i) t->data[i] = (float)(steps == 1 ? start : start + (end - start) * (double)i / (double)(steps - 1));
+  return t;
+}
+EXPORT TorshTensor* torsh_tensor_sub_scalar(const TorshTensor* a, float s) { return unary(a, [s](float x) { return x - s; }); }
+EXPORT TorshTensor* torsh_tensor_div_scalar(const TorshTensor* a, float s) {
+  if (s == 0.f) return fail("division by zero");
+  return unary(a, [s](float x) { return x / s; });
+}
+EXPORT TorshTensor* torsh_tensor_tan(const TorshTensor* a) { return unary(a, [](float x) { return std::tan(x); }); }
+// result = a * b element-wise into an existing tensor of the same shape.
+EXPORT TorshStatus torsh_tensor_multiply(const TorshTensor* a, const TorshTensor* b, TorshTensor* result) {
+  if (!a || !b || !result) { g_err = "null tensor"; return 1; }
+  if (a->shape != b->shape || a->shape != result->shape) { g_err = "shape mismatch"; return 2; }
+  for (size_t i = 0; i < a->data.size(); ++i) result->data[i] = a->data[i] * b->data[i];
+  return 0;
+}
+static TorshTensor* extreme_dim(const TorshTensor* a, int dim, bool want_max) {
+  if (!a) return fail("null tensor");
+  const int nd = (int)a->shape.size();
+  if (nd == 0) return reduce_all(a, want_max ? 2 : 3);
+  if (dim < 0) dim += nd;
+  if (dim < 0 || dim >= nd) return fail("dimension out of range");
+  int64_t outer = 1, inner = 1;
+  const int64_t n = a->shape[dim];
+  if (n == 0) return fail("cannot reduce an empty dimension");
+  for (int i = 0; i < dim; ++i) outer *= a->shape[i];
+  for (int i = dim + 1; i < nd; ++i) inner *= a->shape[i];
+  auto* o = new TorshTensor();
+  o->shape = a->shape;
+  o->shape.erase(o->shape.begin() + dim);
+  o->data.assign((size_t)(outer * inner), 0.f);
+  for (int64_t u = 0; u < outer; ++u)
+    for (int64_t v = 0; v < inner; ++v) {
+      float best = a->data[(u * n) * inner + v];
+      for (int64_t k = 1; k < n; ++k) {
+        const float x = a->data[(u * n + k) * inner + v];
+        best = want_max ? std::max(best, x) : std::min(best, x);
+      }
+      o->data[u * inner + v] = best;
+    }
+  return o;
+}
+// The reference ignores `dim` here and returns the global extreme (tensor_math.rs); this reduces along `dim`.
+EXPORT TorshTensor* torsh_tensor_max_dim(const TorshTensor* a, int dim) { return extreme_dim(a, dim, true); }
+EXPORT TorshTensor* torsh_tensor_min_dim(const TorshTensor* a, int dim) { return extreme_dim(a, dim, false); }
+// target += alpha * source
+EXPORT TorshStatus torsh_tensor_axpy_inplace(TorshTensor* target, const TorshTensor* source, float alpha) {
+  if (!target || !source) { g_err = "null tensor"; return 1; }
+  if (target->data.size() != source->data.size()) { g_err = "shape mismatch"; return 2; }
+  for (size_t i = 0; i < target->data.size(); ++i) target->data[i] += alpha * source->data[i];
+  return 0;
+}
+// One Adam step on explicit tensors (no weight decay), bias-corrected with `step` (1-based).
+EXPORT TorshStatus torsh_tensor_adam_step_inplace(TorshTensor* param, const TorshTensor* grad, TorshTensor* m, TorshTensor* v,
+                                                  float lr, float beta1, float beta2, float eps, int64_t step) {
+  if (!param || !grad || !m || !v) { g_err = "null tensor"; return 1; }
+  const size_t n = param->data.size();
+  if (grad->data.size() != n || m->data.size() != n || v->data.size() != n) { g_err = "shape mismatch"; return 2; }
+  if (step < 1) { g_err = "step must be >= 1"; return 1; }
+  const float c1 = 1.f - std::pow(beta1, (float)step), c2 = 1.f - std::pow(beta2, (float)step);
+  for (size_t i = 0; i < n; ++i) {
+    const float g = grad->data[i];
+    m->data[i] = beta1 * m->data[i] + (1.f - beta1) * g;
+    v->data[i] = beta2 * v->data[i] + (1.f - beta2) * g * g;
+    param->data[i] -= lr * (m->data[i] / c1) / (std::sqrt(v->data[i] / c2) + eps);
+  }
+  return 0;
+}
+
+// Reference-named constructors / accessors: a "module" of the C surface is the linear layer.
+EXPORT TorshModule* torsh_linear_create(size_t in_features, size_t out_features, bool bias) {
+  return torsh_linear_new((int64_t)in_features, (int64_t)out_features, bias ? 1 : 0);
+}
+EXPORT size_t torsh_linear_get_input_features(const TorshModule* m) { return m ? (size_t)m->in : 0; }
+EXPORT size_t torsh_linear_get_output_features(const TorshModule* m) { return m ? (size_t)m->out : 0; }
+EXPORT void torsh_module_free(TorshModule* m) { delete m; }
+EXPORT TorshOptimizer* torsh_sgd_create(float lr) { return torsh_sgd_new(lr, 0.f, 0.f, 0); }
+EXPORT TorshOptimizer* torsh_adam_create(float lr, float beta1, float beta2, float eps) {
+  return torsh_adam_new(lr, beta1, beta2, eps, 0.f, 0);
+}
+// Steps the parameters registered with torsh_optimizer_add_linear (the reference's version is a no-op that returns
+// success, optimizer.rs); refuses an optimizer of the other kind.
+EXPORT TorshStatus torsh_sgd_step(TorshOptimizer* o) {
+  if (!o || o->kind != 0) { g_err = "not an SGD optimizer"; return 1; }
+  return torsh_optimizer_step(o);
+}

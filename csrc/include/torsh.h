@@ -6,6 +6,7 @@
  * the calling thread. Handles are opaque and must be released with the matching *_free. */
 #ifndef TORSH_H
 #define TORSH_H
+#include <stdbool.h>
 #include <stddef.h>
 #include <stdint.h>
 
@@ -87,6 +88,49 @@ TorshStatus torsh_optimizer_add_linear(TorshOptimizer* o, TorshLinear* l);
 TorshStatus torsh_optimizer_step(TorshOptimizer* o);
 TorshStatus torsh_optimizer_zero_grad(TorshOptimizer* o);
 void torsh_optimizer_free(TorshOptimizer* o);
+
+
+/* ---- remaining names of the reference's C surface ---- */
+typedef TorshLinear TorshModule; /* the only module kind of the C surface */
+void torsh_clear_last_error(void);
+int torsh_has_error(void);
+int torsh_get_device_type(void); /* 0 = host */
+int torsh_get_device_id(void);
+size_t torsh_cuda_device_memory(int device_id);
+const char* torsh_cuda_device_name(int device_id);
+size_t torsh_get_memory_usage(void);      /* bytes held by live tensors */
+size_t torsh_get_peak_memory_usage(void);
+TorshStatus torsh_reset_memory_tracking(void);
+int torsh_get_num_threads(void);
+TorshStatus torsh_set_num_threads(int n);
+TorshStatus torsh_set_autocast(int enabled);
+int torsh_is_autocast_enabled(void);
+TorshStatus torsh_set_debug_mode(int enabled);
+int torsh_is_debug_mode_enabled(void);
+TorshStatus torsh_start_profiling(void);
+const char* torsh_stop_profiling(void); /* JSON summary, valid until the next call */
+
+size_t torsh_tensor_size(const TorshTensor* t);
+TorshTensor* torsh_tensor_scalar(float value);
+TorshTensor* torsh_tensor_eye(size_t n);
+TorshTensor* torsh_tensor_linspace(double start, double end, size_t steps);
+TorshTensor* torsh_tensor_sub_scalar(const TorshTensor* a, float s);
+TorshTensor* torsh_tensor_div_scalar(const TorshTensor* a, float s);
+TorshTensor* torsh_tensor_tan(const TorshTensor* a);
+TorshStatus torsh_tensor_multiply(const TorshTensor* a, const TorshTensor* b, TorshTensor* result);
+TorshTensor* torsh_tensor_max_dim(const TorshTensor* a, int dim);
+TorshTensor* torsh_tensor_min_dim(const TorshTensor* a, int dim);
+TorshStatus torsh_tensor_axpy_inplace(TorshTensor* target, const TorshTensor* source, float alpha);
+TorshStatus torsh_tensor_adam_step_inplace(TorshTensor* param, const TorshTensor* grad, TorshTensor* m, TorshTensor* v, float lr,
+                                           float beta1, float beta2, float eps, int64_t step);
+
+TorshModule* torsh_linear_create(size_t in_features, size_t out_features, bool bias);
+size_t torsh_linear_get_input_features(const TorshModule* m);
+size_t torsh_linear_get_output_features(const TorshModule* m);
+void torsh_module_free(TorshModule* m);
+TorshOptimizer* torsh_sgd_create(float lr);
+TorshOptimizer* torsh_adam_create(float lr, float beta1, float beta2, float eps);
+TorshStatus torsh_sgd_step(TorshOptimizer* o);
 
 #ifdef __cplusplus
 }
