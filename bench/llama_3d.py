@@ -174,6 +174,11 @@ def main():
     e2e_ms = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop()
     nv.check_status()
+    # Python time to queue ONE step on an idle device (back to back the launch queue fills and hides it)
+    t1 = time.perf_counter()
+    step(args.warmup)
+    host_issue_ms = (time.perf_counter() - t1) * 1e3
+    barrier()
     # device time of the last step that no forward / backward action covered: the pipeline bubble plus exposed transfers
     idle = torch.tensor([pipe.idle_ms() or 0.0 if pipe is not None else 0.0], dtype=torch.float64, device=dev)
     dist.all_reduce(idle, op=dist.ReduceOp.MAX)
@@ -200,6 +205,7 @@ def main():
             "pipeline": {"transfers": "blocking pairs" if args.pp_blocking else "per-link groups, asynchronous sends",
                          "idle_ms_last_step_max_over_ranks": idle.item()},
             "clocks": clocks, "gpu_launches": per_step * args.steps, "launches_per_step": per_step,
+            "host_issue_ms_per_step": host_issue_ms,
             "loss_after_warmup": first_all, "loss_last": last.item()}))
     dist.barrier()
     dist.destroy_process_group()

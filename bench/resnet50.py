@@ -35,10 +35,12 @@ def main():
     ap.add_argument("--image", type=int, default=224)
     ap.add_argument("--impl", default="ours", choices=["ours", "torch"])
     ap.add_argument("--model", default="resnet50")
+    ap.add_argument("--no-graph", action="store_true", help="issue every launch of the step from Python instead of replaying one CUDA graph")
     ap.add_argument("--ddp-no-overlap", action="store_true", help="reduce all gradient buckets after backward instead of from hooks")
     ap.add_argument("--ddp-comm-blocks", type=int, default=64, help="CTAs of the fused bucket all-reduce kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.graph = not args.no_graph and args.impl == "ours"
 
     import torch
     import torch.distributed as dist
@@ -68,7 +70,8 @@ def main():
             from torsh_b200.parallel.ddp import DistributedDataParallel, OverlapConfig
             net = DistributedDataParallel(model, bucket_cap_mb=25.0, comm_blocks=args.ddp_comm_blocks,
                                           overlap_config=OverlapConfig(enabled=not args.ddp_no_overlap))
-        opt = SGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4)
+        # under a graph the gradients must keep their addresses: the SGD kernel clears them in the pass that reads them
+        opt = SGD(model.parameters(), lr=0.1, momentum=0.9, weight_decay=1e-4, zero_grad_in_step=args.graph and world == 1)
 
         def step(x, y):
             logits = net(x)
@@ -79,7 +82,7 @@ def main():
             opt.step()
             if world > 1:
                 net.zero_grad()
-            else:
+            elif not args.graph:
                 opt.zero_grad(set_to_none=True)
             return loss
     else:
@@ -110,11 +113,19 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    graphed = None
     launches0 = nv.launch_count
+    if args.impl == "ours" and args.graph:
+        # the whole step (forward, backward with its hook-launched bucket all-reduces, SGD) as one CUDA graph
+        from torsh_b200.engine import GraphedStep
+        eager_step = step
+        graphed = GraphedStep(eager_step, [torch.empty_like(x_dev), torch.empty_like(y_dev)], warmup=2)
+        step = lambda x, y: graphed(x, y)
+        args.warmup = max(args.warmup, 4)
     for i in range(args.warmup):
         loss = step(x_dev, y_dev)
     first = loss.item()
-    per_step_launches = (nv.launch_count - launches0) // args.warmup
+    per_step_launches = graphed.launches_per_step if graphed is not None else (nv.launch_count - launches0) // args.warmup
     if args.impl == "ours":
         nv.check_status()
     sampler = ClockSampler(local_rank)
@@ -127,6 +138,11 @@ def main():
     e1.record()
     barrier()
     dev_ms = e0.elapsed_time(e1)
+    # Python time to queue ONE step on an idle device (with steps queued back to back the launch queue fills up and
+    # the host is held to the device's pace, whatever it could do alone)
+    t_issue = time.perf_counter()
+    loss = step(x_dev, y_dev)
+    host_issue_ms = (time.perf_counter() - t_issue) * 1e3
     barrier()
     # end to end: batch i + 1 is copied from pinned memory on a side stream while step i runs; the loss of step i is
     # copied to pinned memory behind the step and read after step i + 1 has been launched (every loss is read)
@@ -187,6 +203,9 @@ def main():
             "e2e": {"value": images / (e2e_ms / 1e3), "unit": "images/s", "ms_per_step": e2e_ms / args.steps,
                     "h2d_bytes_per_step": x_host[0].numel() * 2 + y_host[0].numel() * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": per_step_launches * args.steps, "launches_per_step": per_step_launches,
+            "cuda_graph": bool(graphed is not None and graphed.graph is not None),
+            "cuda_graph_error": graphed.error if graphed is not None else None,
+            "host_issue_ms_per_step": host_issue_ms,
             "loss_first": first, "loss_last": last}))
     if world > 1:
         dist.barrier()

@@ -143,3 +143,59 @@ class CausalLMTrainer:
         if ev is not None:
             ev.record()
         return PendingLoss(buf, ev, sh, self._status_dev)
+
+
+class GraphedStep:
+    """Any training step as one CUDA graph: ``fn(*static_inputs)`` is run eagerly ``warmup`` times on a side stream
+    (so lazily created state exists), captured once, and replayed by every later call after its inputs have been copied
+    into the static buffers. The step's side-stream work (gradient-bucket all-reduces launched from autograd hooks)
+    is captured with it as long as those streams fork from and join the capturing stream; this package's collectives
+    keep their barrier epoch on the device for exactly that reason. ``outputs`` are the tensors ``fn`` returned at
+    capture time and are overwritten by every replay. If the capture fails the step stays eager and ``error`` says why.
+
+    The reference's counterpart is its CUDA-graph layer (crates/torsh-backend/src/cuda/graph/mod.rs), which records
+    kernel nodes by hand; here stream capture records whatever the step launches."""
+
+    def __init__(self, fn, static_inputs, warmup: int = 2, enabled: bool = True):
+        self.fn, self.static_inputs = fn, list(static_inputs)
+        self.graph, self.outputs, self.error = None, None, None
+        self.launches_per_step = 0
+        self._left = max(int(warmup), 1)
+        self.enabled = enabled and torch.cuda.is_available()
+        self._side = torch.cuda.Stream() if self.enabled else None
+
+    def __call__(self, *inputs):
+        for dst, src in zip(self.static_inputs, inputs):
+            if dst is not src:
+                dst.copy_(src, non_blocking=True)
+        if not self.enabled or self.error is not None:
+            return self.fn(*self.static_inputs)
+        if self.graph is not None:
+            self.graph.replay()
+            return self.outputs
+        if self._left > 0:
+            # warm-up on a side stream, as stream capture later runs on one: autograd remembers the stream a gradient
+            # was first accumulated on and would otherwise tie the legacy default stream into the capture
+            self._left -= 1
+            n0 = nv.launch_count
+            cur = torch.cuda.current_stream()
+            self._side.wait_stream(cur)
+            with torch.cuda.stream(self._side):
+                out = self.fn(*self.static_inputs)
+            cur.wait_stream(self._side)
+            self.launches_per_step = nv.launch_count - n0
+            return out
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(graph):
+                out = self.fn(*self.static_inputs)
+        except Exception as e:                      # a step that cannot be captured keeps running eagerly
+            import traceback
+            self.error = f"{type(e).__name__}: {e}"
+            self.error_detail = traceback.format_exc()
+            torch.cuda.synchronize()
+            return self.fn(*self.static_inputs)
+        self.graph, self.outputs = graph, out
+        self.graph.replay()
+        return self.outputs

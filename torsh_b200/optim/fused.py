@@ -138,7 +138,10 @@ class Adam(AdamW):
 
 class SGD(_Base):
     def __init__(self, params, lr: float = 0.01, momentum: float = 0.0, dampening: float = 0.0,
-                 weight_decay: float = 0.0, nesterov: bool = False, found_inf=None):
+                 weight_decay: float = 0.0, nesterov: bool = False, found_inf=None, zero_grad_in_step: bool = False):
+        # zero_grad_in_step: the update kernel clears each gradient in the pass that reads it, so the gradients keep
+        # their addresses from step to step (what a captured CUDA graph needs) and no separate zeroing pass runs
+        self.zero_grad_in_step = zero_grad_in_step
         if nesterov and (momentum <= 0 or dampening != 0):
             raise ValueError("Nesterov momentum requires a momentum and zero dampening")
         super().__init__(params, dict(lr=lr, momentum=momentum, dampening=dampening, weight_decay=weight_decay,
@@ -168,7 +171,8 @@ class SGD(_Base):
                     rows.append((lowp, master, grad, st.get("momentum_buffer")))
                 tt = mt.TensorTable.cached(self._tables, (gi, gdt), rows, ps[0].device)
                 mt.sgd_step(tt, lr=g["lr"], momentum=mu, dampening=g["dampening"], weight_decay=g["weight_decay"],
-                            nesterov=g["nesterov"], grad_dtype=gdt, found_inf=self.found_inf)
+                            nesterov=g["nesterov"], grad_dtype=gdt, found_inf=self.found_inf,
+                            zero_grad=self.zero_grad_in_step)
             for p in cpu:
                 st = self.state[p]
                 w = p.data.float()

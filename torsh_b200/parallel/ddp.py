@@ -192,8 +192,8 @@ class DistributedDataParallel(Module):
     def _check_device_status(self):
         """Raises :class:`KernelTimeout` when a collective kernel of the PREVIOUS step recorded a failed cross-rank wait
         (it then skipped its reduction), and queues the copy of this step's status word; no host wait on the new step."""
-        if self.fused is None:
-            return
+        if self.fused is None or torch.cuda.is_current_stream_capturing():
+            return      # inside a CUDA-graph capture the owner of the graph reads the status word after its replays
         from .. import _native as nv
         if self._status_queued:
             self._status_event.synchronize()   # a whole step old: already complete
