@@ -210,11 +210,13 @@ TB_EXPORT int tb_sum_f32(const float* x, float* out, long n, float scale, cudaSt
 // Device-side index checks (see common.cuh): `word` is the device status word, or null to switch the reports off.
 int tb_set_check_word_xent(int* word);
 int tb_set_check_word_moe(int* word);
+int tb_set_check_word_quant_sparse(int* word);
 TB_EXPORT int tb_set_kernel_checks(int* word) {
   TB_ENSURE_DEVICE();
   TB_CUDA_CHECK(set_check_word_this_tu(word));
   if (int r = tb_set_check_word_xent(word)) return r;
-  return tb_set_check_word_moe(word);
+  if (int r = tb_set_check_word_moe(word)) return r;
+  return tb_set_check_word_quant_sparse(word);
 }
 
 TB_EXPORT int tb_embedding_fwd(const long* ids, const void* wte, const void* wpe, void* out, long tokens,

@@ -1008,3 +1008,46 @@ def test_model_merging_sharding_surgery_distillation_pruning():
         assert mu.ModelPruner(mu.PruningConfig(sparsity=0.5, method=method)).prune_model(l3)["overall_sparsity"] == pytest.approx(0.5)
     ens = mu.Ensemble([torch.nn.Linear(3, 2), torch.nn.Linear(3, 2)], mode="prob")
     assert torch.allclose(ens(torch.randn(4, 3)).sum(-1), torch.ones(4), atol=1e-6)
+
+
+def test_int4_int8_and_csr_cpu_paths():
+    """The quantised layers and the CSR class give the same answers through their PyTorch fallbacks on a CPU."""
+    from torsh_b200 import quantization as Q
+    from torsh_b200.sparse import CudaSparseTensor, CooTensor, prune_magnitude
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(256, 48)
+    ql = Q.Int4Linear(lin, group=64)
+    x = torch.randn(5, 256)
+    w = ql.dequantized_weight()
+    assert (w - lin.weight).abs().max() <= 0.5 * ql.scales.max() + 1e-6
+    assert torch.allclose(ql(x), x @ w.t() + lin.bias, atol=1e-5)
+    q, s = Q.quantize_int8_rowwise(x)
+    assert (Q.dequantize_int8_rowwise(q, s) - x).abs().max() <= 0.5 * s.max() + 1e-6
+    a = prune_magnitude(torch.randn(40, 60), 0.85)
+    sp = CudaSparseTensor.from_dense(a)
+    b = torch.randn(60, 9)
+    assert torch.allclose(sp @ b, a @ b, atol=1e-5) and torch.equal(sp.to_dense(), a)
+    assert torch.equal(CudaSparseTensor.from_coo(CooTensor.from_dense(a)).to_dense(), a)
+    assert torch.equal(sp.transpose().to_dense(), a.t()) and sp.nnz == int((a != 0).sum())
+
+
+def test_lstm_and_grouped_conv_cpu_paths():
+    """KernelLSTM shares torch.nn.LSTM's parameters and semantics; the grouped / depthwise front ends agree with
+    torch.nn.functional.conv2d on a CPU."""
+    from torsh_b200.ops.conv import depthwise_conv2d_nhwc, grouped_conv2d_nhwc
+    from torsh_b200.ops.rnn import KernelLSTM
+    torch.manual_seed(0)
+    ref = torch.nn.LSTM(12, 20, num_layers=2)
+    mine = KernelLSTM(12, 20, num_layers=2)
+    mine.load_state_dict(ref.state_dict())
+    x = torch.randn(7, 3, 12)
+    out, (h, c) = mine(x)
+    out_r, (h_r, c_r) = ref(x)
+    assert torch.allclose(out, out_r, atol=1e-5) and torch.allclose(h, h_r, atol=1e-5) and torch.allclose(c, c_r, atol=1e-5)
+    xi = torch.randn(2, 9, 9, 16)
+    wd = torch.randn(16, 1, 3, 3)
+    yr = torch.nn.functional.conv2d(xi.permute(0, 3, 1, 2), wd, None, 1, 1, groups=16).permute(0, 2, 3, 1)
+    assert torch.allclose(depthwise_conv2d_nhwc(xi, wd, None, 1, 1), yr, atol=1e-5)
+    wg = torch.randn(8, 4, 3, 3)
+    yg = torch.nn.functional.conv2d(xi.permute(0, 3, 1, 2), wg, None, 1, 1, groups=4).permute(0, 2, 3, 1)
+    assert torch.allclose(grouped_conv2d_nhwc(xi, wg, None, 1, 1, groups=4), yg, atol=1e-4)

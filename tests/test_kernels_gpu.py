@@ -496,3 +496,118 @@ def test_native_profiler_ranges():
     by = {r["name"]: r for r in rec}
     assert set(by) == {"step", "relu", "exp"} and by["step"]["depth"] == 0 and by["relu"]["depth"] == 1
     assert by["step"]["device_us"] >= by["relu"]["device_us"] > 0 and "traceEvents" in prof.chrome_trace()
+
+
+# ------------------------------------------------------------------ quantised / sparse
+@pytest.mark.parametrize("group", [32, 64, 128, 256])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_int4_groupwise_kernels_match_reference(group, dtype):
+    from torsh_b200 import quantization as Q
+    torch.manual_seed(0)
+    w = (torch.randn(96, 512, device=DEV) * 0.05).to(dtype)
+    q, s = Q.quantize_groupwise(w, group, 4)
+    q_ref, s_ref = Q.quantize_groupwise(w.float().cpu(), group, 4)       # the plain PyTorch formulation
+    assert q.dtype == torch.int8 and q.shape == (96, 256) and s.shape == (96, 512 // group)
+    assert torch.allclose(s.cpu(), s_ref, rtol=1e-6, atol=0)
+    same = (q.cpu() == q_ref).float().mean().item()
+    assert same > 0.99        # bytes hold two codes; values within rounding of a .5 tie may land on the neighbouring code
+    d = Q.dequantize_groupwise(q, s, group, 4, dtype=torch.float32)
+    d_ref = Q.dequantize_groupwise(q.cpu(), s.cpu(), group, 4)
+    assert torch.equal(d.cpu(), d_ref)
+    assert ((d - w.float()).abs() <= 0.505 * s.repeat_interleave(group, -1) + 1e-7).all()
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 8])
+def test_int4_linear_matches_dequantised_matmul(M):
+    from torsh_b200 import quantization as Q
+    torch.manual_seed(1)
+    lin = torch.nn.Linear(1024, 384).to(DEV)
+    ql = Q.Int4Linear(lin, group=128)
+    x = torch.randn(M, 1024, device=DEV, dtype=torch.bfloat16)
+    y = ql(x)
+    ref = x.float() @ ql.dequantized_weight(torch.float32).t() + lin.bias.float()
+    assert y.shape == (M, 384) and _rel_elem(y, ref) < 1e-2
+    big = torch.randn(32, 1024, device=DEV, dtype=torch.bfloat16)        # the dequantise + GEMM route
+    assert _rel_elem(ql(big), big.float() @ ql.dequantized_weight(torch.float32).t() + lin.bias.float()) < 2e-2
+
+
+def test_int8_rowwise_kernels():
+    from torsh_b200 import quantization as Q
+    torch.manual_seed(2)
+    x = torch.randn(300, 777, device=DEV, dtype=torch.bfloat16)
+    q, s = Q.quantize_int8_rowwise(x)
+    assert torch.allclose(s, x.float().abs().amax(-1) / 127, rtol=1e-6)
+    ref = (x.float() / s[:, None]).round().clamp(-127, 127)
+    assert ((q.float() - ref).abs() <= 1).all() and ((q.float() == ref).float().mean() > 0.99)
+    d = Q.dequantize_int8_rowwise(q, s, torch.float32)
+    assert torch.equal(d, q.float() * s[:, None])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n", [1, 7, 128, 200])
+def test_csr_spmm_matches_dense(dtype, n):
+    from torsh_b200.sparse import CudaSparseTensor, prune_magnitude
+    torch.manual_seed(3)
+    a = prune_magnitude(torch.randn(333, 517, device=DEV), 0.93)
+    a[5] = 0                                                               # an empty row
+    sp = CudaSparseTensor.from_dense(a)
+    b = torch.randn(517, n, device=DEV).to(dtype)
+    out = sp @ b
+    ref = a.double() @ b.double()
+    assert out.dtype == dtype and _rel_elem(out, ref) < (1e-5 if dtype == torch.float32 else 1e-2)
+    assert torch.equal(sp.to_dense(), a) and torch.equal(sp.transpose().to_dense(), a.t())
+    v = torch.randn(517, device=DEV)
+    assert _rel_elem(sp @ v, a.double() @ v.double()) < 1e-5
+
+
+# ------------------------------------------------------------------ LSTM, depthwise / grouped convolution
+@pytest.mark.parametrize("T,B,I,H", [(5, 4, 64, 128), (12, 16, 256, 256)])
+def test_lstm_layer_matches_torch(T, B, I, H):
+    from torsh_b200.ops.rnn import KernelLSTM
+    torch.manual_seed(0)
+    ref = torch.nn.LSTM(I, H, num_layers=2).to(DEV)
+    mine = KernelLSTM(I, H, num_layers=2).to(DEV)
+    mine.load_state_dict(ref.state_dict())
+    mine = mine.to(torch.bfloat16)
+    x = (torch.randn(T, B, I, device=DEV) * 0.5)
+    xb = x.to(torch.bfloat16).requires_grad_(True)
+    xr = x.to(torch.bfloat16).float().requires_grad_(True)
+    for p in ref.parameters():
+        p.data = p.data.to(torch.bfloat16).float()         # same rounded weights on both sides
+    out, (hT, cT) = mine(xb)
+    out_r, (hT_r, cT_r) = ref(xr)
+    assert _rel(out, out_r) < 3e-2 and _rel(hT, hT_r) < 3e-2 and _rel(cT, cT_r) < 3e-2
+    g = torch.randn_like(out_r)
+    out.backward(g.to(torch.bfloat16))
+    out_r.backward(g)
+    assert _rel(xb.grad, xr.grad) < 5e-2
+    for (n, p), (_, q) in zip(mine.named_parameters(), ref.named_parameters()):
+        assert _rel(p.grad, q.grad) < 5e-2, n
+
+
+@pytest.mark.parametrize("k,stride,pad", [(3, 1, 1), (3, 2, 1), (5, 1, 2), (7, 1, 3), (3, 2, 0)])
+def test_depthwise_conv_matches_torch(k, stride, pad):
+    from torsh_b200.ops.conv import depthwise_conv2d_nhwc
+    torch.manual_seed(1)
+    n, h, w, c = 3, 19, 23, 72
+    x = torch.randn(n, h, w, c, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    wt = (torch.randn(c, 1, k, k, device=DEV) * 0.2).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(c, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    y = depthwise_conv2d_nhwc(x, wt, b, stride, pad)
+    xf, wf, bf = (t.detach().float().requires_grad_(True) for t in (x, wt, b))
+    yr = torch.nn.functional.conv2d(xf.permute(0, 3, 1, 2), wf, bf, stride, pad, groups=c).permute(0, 2, 3, 1)
+    assert y.shape == yr.shape and _rel(y, yr) < 1e-2
+    g = torch.randn_like(yr)
+    y.backward(g.to(torch.bfloat16))
+    yr.backward(g.to(torch.bfloat16).float())
+    assert _rel(x.grad, xf.grad) < 1e-2 and _rel(wt.grad, wf.grad) < 1e-2 and _rel(b.grad, bf.grad) < 1e-2
+
+
+def test_grouped_conv_matches_torch():
+    from torsh_b200.ops.conv import grouped_conv2d_nhwc
+    torch.manual_seed(2)
+    x = torch.randn(2, 14, 14, 128, device=DEV).to(torch.bfloat16)
+    wt = (torch.randn(256, 32, 3, 3, device=DEV) * 0.05).to(torch.bfloat16)
+    y = grouped_conv2d_nhwc(x, wt, None, 1, 1, groups=4)
+    yr = torch.nn.functional.conv2d(x.float().permute(0, 3, 1, 2), wt.float(), None, 1, 1, groups=4).permute(0, 2, 3, 1)
+    assert _rel(y, yr) < 1e-2

@@ -165,3 +165,34 @@ def test_device_side_index_checks_report_through_the_status_word():
     sm.cross_entropy(logits, tgt_bad)
     torch.cuda.synchronize()
     nv.check_status()                                        # checks off: the same calls leave no code
+
+
+def test_graphed_step_replays_a_training_step():
+    """A small ResNet training step captured by GraphedStep gives the same parameters as the same steps run eagerly."""
+    import copy
+    from torsh_b200.engine import GraphedStep
+    from torsh_b200.models import create_model
+    from torsh_b200.optim.fused import SGD
+    torch.manual_seed(0)
+    base = create_model("resnet18").cuda().train()
+    base.use_kernels = True
+    x = torch.randn(8, 3, 64, 64, device="cuda").to(torch.bfloat16)
+    y = torch.randint(0, 1000, (8,), device="cuda")
+    results = []
+    for graphed in (False, True):
+        model = copy.deepcopy(base)
+        opt = SGD(model.parameters(), lr=1e-3, momentum=0.9, zero_grad_in_step=True)   # small steps: the comparison stays well conditioned
+
+        def step(x, y):
+            loss = torch.nn.functional.cross_entropy(model(x), y)
+            loss.backward()
+            opt.step()
+            return loss
+        gs = GraphedStep(step, [torch.empty_like(x), torch.empty_like(y)], warmup=2, enabled=graphed)
+        losses = [float(gs(x, y).detach()) for _ in range(6)]
+        assert (gs.graph is not None) == graphed and gs.error is None
+        results.append((losses, [p.detach().float().clone() for p in model.parameters()]))
+    (l0, p0), (l1, p1) = results
+    assert all(abs(a - b) <= 2e-2 * max(abs(a), 1.0) for a, b in zip(l0, l1))
+    for a, b in zip(p0, p1):
+        assert ((a - b).norm() / a.norm().clamp(min=1e-6)).item() < 2e-2

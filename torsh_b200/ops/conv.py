@@ -267,3 +267,80 @@ def global_avg_pool_nhwc(x: torch.Tensor) -> torch.Tensor:
     if kernel_ok(x) and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
         return _AvgPoolFn.apply(x.contiguous())
     return x.float().mean((1, 2)).to(x.dtype)
+
+
+# ---- depthwise and grouped convolution ---------------------------------------------------------------------------
+class _DepthwiseFn(torch.autograd.Function):
+    """x [N, H, W, C] bf16, w [K, K, C] bf16 (taps major, channels contiguous), bias [C] bf16 or None."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, stride, padding):
+        n, h, wd, c = x.shape
+        k = w.shape[0]
+        ho, wo = _out_hw(h, wd, k, stride, padding)
+        y = torch.empty(n, ho, wo, c, dtype=torch.bfloat16, device=x.device)
+        call("tb_dwconv_fwd", [P, P, P, P] + [I] * 9 + [P], x.data_ptr(), w.data_ptr(), nv.ptr(bias), y.data_ptr(), n, h, wd, c,
+             ho, wo, k, stride, padding, nv.stream_ptr())
+        ctx.save_for_backward(x, w)
+        ctx.cfg = (stride, padding, bias is not None)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        stride, padding, has_bias = ctx.cfg
+        n, h, wd, c = x.shape
+        k = w.shape[0]
+        dy = dy.contiguous()
+        ho, wo = dy.shape[1], dy.shape[2]
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x)
+            call("tb_dwconv_dgrad", [P, P, P] + [I] * 9 + [P], dy.data_ptr(), w.data_ptr(), dx.data_ptr(), n, h, wd, c, ho, wo, k,
+                 stride, padding, nv.stream_ptr())
+        if ctx.needs_input_grad[1] or (has_bias and ctx.needs_input_grad[2]):
+            gw = torch.zeros(k, k, c, dtype=torch.float32, device=x.device)
+            gb = torch.zeros(c, dtype=torch.float32, device=x.device) if has_bias else None
+            call("tb_dwconv_wgrad", [P, P, P, P] + [I] * 9 + [P], x.data_ptr(), dy.data_ptr(), gw.data_ptr(), nv.ptr(gb), n, h, wd, c,
+                 ho, wo, k, stride, padding, nv.stream_ptr())
+            dw = gw.to(w.dtype)
+            db = None if gb is None else gb.to(torch.bfloat16)
+        return dx, dw, db, None, None
+
+
+def depthwise_conv2d_nhwc(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, stride: int = 1,
+                          padding: int = 0) -> torch.Tensor:
+    """Depthwise convolution (groups == channels), channels-last. ``x`` is ``[N, H, W, C]``, ``weight`` has PyTorch's
+    ``[C, 1, K, K]`` layout. bf16 with C a multiple of 8 runs on the kernels (`tb_dwconv_*`); anything else goes through
+    ``torch.nn.functional.conv2d``."""
+    c = x.shape[-1]
+    k = weight.shape[-1]
+    if kernel_ok(x) and x.dtype == torch.bfloat16 and c % 8 == 0 and weight.shape[0] == c and weight.shape[1] == 1 \
+            and weight.shape[2] == weight.shape[3]:
+        w = weight.reshape(c, k, k).permute(1, 2, 0).to(torch.bfloat16).contiguous()       # [K, K, C]; autograd tracks the permute
+        b = None if bias is None else bias.to(torch.bfloat16).contiguous()
+        return _DepthwiseFn.apply(x.contiguous(), w, b, stride, padding)
+    y = torch.nn.functional.conv2d(x.permute(0, 3, 1, 2).to(weight.dtype), weight, bias, stride, padding, groups=c)
+    return y.permute(0, 2, 3, 1).to(x.dtype)
+
+
+def grouped_conv2d_nhwc(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None, stride: int = 1,
+                        padding: int = 0, groups: int = 1) -> torch.Tensor:
+    """Convolution with channel groups, channels-last: groups == 1 is :func:`conv2d_nhwc`, groups == C the depthwise kernel,
+    anything between runs one tensor-core convolution per group on its channel slice and concatenates the results (the
+    cuDNN `group_count` path of the reference, crates/torsh-backend/src/cuda/cudnn/operations.rs:364)."""
+    c = x.shape[-1]
+    if groups == 1:
+        y = conv2d_nhwc(x, weight, stride, padding)
+        return y if bias is None else y + bias.to(y.dtype)
+    if groups == c and weight.shape[1] == 1:
+        return depthwise_conv2d_nhwc(x, weight, bias, stride, padding)
+    if c % groups or weight.shape[0] % groups:
+        raise ValueError(f"channels ({c}) and filters ({weight.shape[0]}) must be multiples of groups ({groups})")
+    cg, og = c // groups, weight.shape[0] // groups
+    outs = []
+    for g in range(groups):
+        xg = x[..., g * cg:(g + 1) * cg].contiguous()
+        outs.append(conv2d_nhwc(xg, weight[g * og:(g + 1) * og], stride, padding))
+    y = torch.cat(outs, -1)
+    return y if bias is None else y + bias.to(y.dtype)

@@ -62,9 +62,24 @@ def quantize_per_channel(t, axis=0, bits=8, symmetric=True):
     return quantize(t, qp), qp
 
 
+def _int4_kernel_ok(t: torch.Tensor, group: int) -> bool:
+    return (t.is_cuda and t.dtype in (torch.bfloat16, torch.float32) and group in (32, 64, 128, 256)
+            and t.shape[-1] % group == 0)
+
+
 def quantize_groupwise(w: torch.Tensor, group: int = 128, bits: int = 4):
     """Symmetric group-wise quantization along the last dim; returns int8 codes (INT4 values packed two per byte when
-    ``bits == 4``) and per-group scales."""
+    ``bits == 4``) and per-group scales. On a GPU the INT4 case is one kernel (`tb_quantize_int4_group`)."""
+    if bits == 4 and _int4_kernel_ok(w, group):
+        from . import _native as nv
+        from .ops import _dispatch as dp
+        wc = w.contiguous()
+        rows = wc.numel() // wc.shape[-1]
+        q = torch.empty(*wc.shape[:-1], wc.shape[-1] // 2, dtype=torch.int8, device=w.device)
+        scale = torch.empty(*wc.shape[:-1], wc.shape[-1] // group, dtype=torch.float32, device=w.device)
+        dp.call("tb_quantize_int4_group", [dp.P, dp.I, dp.P, dp.P, dp.L, dp.I, dp.I, dp.P], wc.data_ptr(),
+                0 if wc.dtype == torch.bfloat16 else 1, q.data_ptr(), scale.data_ptr(), rows, wc.shape[-1], group, nv.stream_ptr())
+        return q, scale
     g = w.reshape(*w.shape[:-1], -1, group)
     qmax = (1 << (bits - 1)) - 1
     scale = g.abs().amax(-1, keepdim=True).clamp(min=1e-12) / qmax
@@ -74,7 +89,17 @@ def quantize_groupwise(w: torch.Tensor, group: int = 128, bits: int = 4):
     return q, scale.squeeze(-1)
 
 
-def dequantize_groupwise(q, scale, group=128, bits=4):
+def dequantize_groupwise(q, scale, group=128, bits=4, dtype: torch.dtype = torch.float32):
+    if bits == 4 and q.is_cuda and group in (32, 64, 128, 256) and dtype in (torch.bfloat16, torch.float32):
+        from . import _native as nv
+        from .ops import _dispatch as dp
+        qc, sc = q.contiguous(), scale.contiguous().float()
+        cols = qc.shape[-1] * 2
+        rows = qc.numel() // qc.shape[-1]
+        out = torch.empty(*qc.shape[:-1], cols, dtype=dtype, device=q.device)
+        dp.call("tb_dequantize_int4_group", [dp.P, dp.P, dp.P, dp.I, dp.L, dp.I, dp.I, dp.P], qc.data_ptr(), sc.data_ptr(),
+                out.data_ptr(), 0 if dtype == torch.bfloat16 else 1, rows, cols, group, nv.stream_ptr())
+        return out
     if bits == 4:
         lo = ((q << 4).to(torch.int8) >> 4)
         hi = q >> 4
@@ -167,6 +192,68 @@ class QuantizedLinear(nn.Module):
 
     def forward(self, x):
         return nn.functional.linear(x, (self.qweight.to(x.dtype) * self.scale[:, None].to(x.dtype)), self.bias)
+
+
+class Int4Linear(nn.Module):
+    """Weight-only INT4 linear layer: group-wise symmetric codes, two per byte, with fp32 scales (4.25 bits per weight
+    at group 128). Up to 8 activation rows go through the fused kernel that reads the packed weights once and never
+    materialises them (`tb_int4_linear`, the decoding case); larger batches dequantise to bf16 and use the GEMM."""
+
+    def __init__(self, lin: nn.Linear, group: int = 128):
+        super().__init__()
+        self.in_features, self.out_features, self.group = lin.in_features, lin.out_features, group
+        q, s = quantize_groupwise(lin.weight.detach(), group, 4)
+        self.register_buffer("qweight", q.contiguous())
+        self.register_buffer("scales", s.contiguous().float())
+        self.bias = None if lin.bias is None else nn.Parameter(lin.bias.detach().clone(), requires_grad=False)
+
+    def dequantized_weight(self, dtype=torch.float32) -> torch.Tensor:
+        return dequantize_groupwise(self.qweight, self.scales, self.group, 4, dtype=dtype) if self.qweight.is_cuda \
+            else dequantize_groupwise(self.qweight, self.scales, self.group, 4).to(dtype)
+
+    def forward(self, x):
+        x2 = x.reshape(-1, self.in_features)
+        if x2.is_cuda and x2.shape[0] <= 8 and self.in_features % 8 == 0:
+            from . import _native as nv
+            from .ops import _dispatch as dp
+            xb = x2.to(torch.bfloat16).contiguous()
+            y = torch.empty(x2.shape[0], self.out_features, dtype=torch.bfloat16, device=x.device)
+            b = None if self.bias is None else self.bias.to(torch.bfloat16).contiguous()
+            dp.call("tb_int4_linear", [dp.P, dp.P, dp.P, dp.P, dp.P, dp.I, dp.I, dp.I, dp.I, dp.P], xb.data_ptr(),
+                    self.qweight.data_ptr(), self.scales.data_ptr(), 0 if b is None else b.data_ptr(), y.data_ptr(),
+                    x2.shape[0], self.out_features, self.in_features, self.group, nv.stream_ptr())
+            return y.to(x.dtype).reshape(*x.shape[:-1], self.out_features)
+        w = self.dequantized_weight(x.dtype if x.dtype in (torch.bfloat16, torch.float32) else torch.float32)
+        return torch.nn.functional.linear(x, w.to(x.dtype), None if self.bias is None else self.bias.to(x.dtype))
+
+
+def quantize_int8_rowwise(x: torch.Tensor):
+    """Per-row symmetric INT8: (codes int8 [rows, cols], scale fp32 [rows]); one kernel on a GPU."""
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    if x2.is_cuda and x2.dtype in (torch.bfloat16, torch.float32):
+        from . import _native as nv
+        from .ops import _dispatch as dp
+        q = torch.empty(x2.shape, dtype=torch.int8, device=x.device)
+        s = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device)
+        dp.call("tb_quantize_int8_row", [dp.P, dp.I, dp.P, dp.P, dp.I, dp.I, dp.P], x2.data_ptr(),
+                0 if x2.dtype == torch.bfloat16 else 1, q.data_ptr(), s.data_ptr(), x2.shape[0], x2.shape[1], nv.stream_ptr())
+        return q.reshape(x.shape), s.reshape(x.shape[:-1])
+    s = x2.float().abs().amax(-1).clamp(min=1e-12) / 127
+    q = (x2.float() / s[:, None]).round().clamp(-127, 127).to(torch.int8)
+    return q.reshape(x.shape), s.reshape(x.shape[:-1])
+
+
+def dequantize_int8_rowwise(q: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    q2 = q.reshape(-1, q.shape[-1]).contiguous()
+    if q2.is_cuda and dtype in (torch.bfloat16, torch.float32):
+        from . import _native as nv
+        from .ops import _dispatch as dp
+        out = torch.empty(q2.shape, dtype=dtype, device=q.device)
+        sc = scale.reshape(-1).contiguous().float()
+        dp.call("tb_dequantize_int8_row", [dp.P, dp.P, dp.P, dp.I, dp.I, dp.I, dp.P], q2.data_ptr(), sc.data_ptr(), out.data_ptr(),
+                0 if dtype == torch.bfloat16 else 1, q2.shape[0], q2.shape[1], nv.stream_ptr())
+        return out.reshape(q.shape)
+    return (q2.float() * scale.reshape(-1, 1).float()).to(dtype).reshape(q.shape)
 
 
 def quantize_model(model: nn.Module, bits=8) -> nn.Module:

@@ -237,6 +237,76 @@ class RleTensor:
         return n / max(self.values.numel() * 2, 1)
 
 
+class CudaSparseTensor:
+    """CSR matrix resident on a GPU with its products computed by this package's kernel (`tb_csr_spmm`: one warp per
+    row and 128-column tile, fp32 accumulation). Values are fp32; the dense operand and the result are bf16 or fp32.
+    The reference's `CudaSparseTensor` (crates/torsh-sparse/src/gpu.rs:13-250) declares the same operations over a
+    cuSPARSE wrapper. On a CPU tensor the same class computes through the COO path, so code is portable."""
+
+    def __init__(self, indptr: torch.Tensor, indices: torch.Tensor, values: torch.Tensor, shape: tuple[int, int]):
+        self.indptr = indptr.to(torch.int32).contiguous()
+        self.indices = indices.to(torch.int32).contiguous()
+        self.values = values.float().contiguous()
+        self.shape = (int(shape[0]), int(shape[1]))
+
+    @classmethod
+    def from_dense(cls, dense: torch.Tensor) -> "CudaSparseTensor":
+        d = dense.detach().float()
+        nz = d.nonzero()                                   # row-major order: already sorted by (row, column)
+        indptr = torch.zeros(d.shape[0] + 1, dtype=torch.int64, device=d.device)
+        indptr[1:] = torch.bincount(nz[:, 0], minlength=d.shape[0]).cumsum(0)
+        return cls(indptr, nz[:, 1], d[nz[:, 0], nz[:, 1]], tuple(d.shape))
+
+    @classmethod
+    def from_coo(cls, coo: "CooTensor") -> "CudaSparseTensor":
+        order = torch.argsort(coo.rows * coo.shape[1] + coo.cols)
+        rows, cols, vals = coo.rows[order], coo.cols[order], coo.values[order]
+        counts = torch.bincount(rows, minlength=coo.shape[0])
+        indptr = torch.zeros(coo.shape[0] + 1, dtype=torch.int64, device=rows.device)
+        indptr[1:] = counts.cumsum(0)
+        return cls(indptr, cols, vals, coo.shape)
+
+    @property
+    def nnz(self) -> int:
+        return self.values.numel()
+
+    @property
+    def device(self):
+        return self.values.device
+
+    def to(self, device) -> "CudaSparseTensor":
+        return CudaSparseTensor(self.indptr.to(device), self.indices.to(device), self.values.to(device), self.shape)
+
+    def to_dense(self) -> torch.Tensor:
+        rows = torch.repeat_interleave(torch.arange(self.shape[0], device=self.device), self.indptr.long().diff())
+        out = torch.zeros(self.shape, dtype=torch.float32, device=self.device)
+        out.index_put_((rows, self.indices.long()), self.values, accumulate=True)
+        return out
+
+    def transpose(self) -> "CudaSparseTensor":
+        rows = torch.repeat_interleave(torch.arange(self.shape[0], device=self.device), self.indptr.long().diff())
+        return CudaSparseTensor.from_coo(CooTensor(self.indices.long(), rows, self.values, (self.shape[1], self.shape[0])))
+
+    def matmul(self, b: torch.Tensor) -> torch.Tensor:
+        """self [M, K] @ b [K, N] (or [K]) -> dense [M, N] in b's dtype."""
+        vec = b.dim() == 1
+        b2 = (b[:, None] if vec else b).contiguous()
+        if b2.shape[0] != self.shape[1]:
+            raise ValueError(f"shape mismatch: {self.shape} @ {tuple(b.shape)}")
+        if self.values.is_cuda and b2.is_cuda and b2.dtype in (torch.bfloat16, torch.float32):
+            from . import _native as nv
+            from .ops import _dispatch as dp
+            out = torch.empty(self.shape[0], b2.shape[1], dtype=b2.dtype, device=b2.device)
+            dp.call("tb_csr_spmm", [dp.P, dp.P, dp.P, dp.P, dp.P, dp.I, dp.I, dp.I, dp.I, dp.P], self.indptr.data_ptr(),
+                    self.indices.data_ptr(), self.values.data_ptr(), b2.data_ptr(), out.data_ptr(), self.shape[0], self.shape[1],
+                    b2.shape[1], 0 if b2.dtype == torch.bfloat16 else 1, nv.stream_ptr())
+        else:
+            out = (self.to_dense() @ b2.float()).to(b2.dtype)
+        return out[:, 0] if vec else out
+
+    __matmul__ = matmul
+
+
 class SparseLinear(torch.nn.Module):
     """Linear layer whose weight is held as COO non-zeros (trainable values, fixed pattern)."""
 
