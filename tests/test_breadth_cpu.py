@@ -1051,3 +1051,96 @@ def test_lstm_and_grouped_conv_cpu_paths():
     wg = torch.randn(8, 4, 3, 3)
     yg = torch.nn.functional.conv2d(xi.permute(0, 3, 1, 2), wg, None, 1, 1, groups=4).permute(0, 2, 3, 1)
     assert torch.allclose(grouped_conv2d_nhwc(xi, wg, None, 1, 1, groups=4), yg, atol=1e-4)
+
+
+def test_loss_family_values_and_gradients():
+    """Every loss of the functional family: closed-form values on small cases, PyTorch parity where a torch loss exists,
+    and a finite gradient."""
+    import math
+    from torsh_b200.nn import losses as L
+    torch.manual_seed(0)
+    assert len(L.__all__) >= 28
+    logits = torch.randn(6, 5, requires_grad=True)
+    tgt = torch.tensor([0, 1, 2, 3, 4, 0])
+    assert torch.allclose(L.cross_entropy(logits, tgt), torch.nn.functional.cross_entropy(logits, tgt))
+    assert torch.allclose(L.cross_entropy_with_label_smoothing(logits, tgt, 0.1),
+                          torch.nn.functional.cross_entropy(logits, tgt, label_smoothing=0.1), atol=1e-6)
+    assert torch.allclose(L.nll_loss(logits.log_softmax(-1), tgt), L.cross_entropy(logits, tgt))
+    x, y = torch.rand(4, 3), (torch.rand(4, 3) > 0.5).float()
+    assert torch.allclose(L.binary_cross_entropy_with_logits(torch.logit(x), y), L.binary_cross_entropy(x, y), atol=1e-5)
+    assert torch.allclose(L.focal_loss(torch.logit(x), y, alpha=0.5, gamma=0.0), 0.5 * L.binary_cross_entropy(x, y), atol=1e-5)
+    a, b = torch.randn(5, 8), torch.randn(5, 8)
+    assert torch.allclose(L.mse_loss(a, b), ((a - b) ** 2).mean()) and torch.allclose(L.l1_loss(a, b, "sum"), (a - b).abs().sum())
+    assert torch.allclose(L.smooth_l1_loss(a, b, 1.0), L.huber_loss(a, b, 1.0))
+    var = torch.rand(5, 8) + 0.1
+    assert torch.allclose(L.gaussian_nll_loss(a, b, var), (0.5 * (var.log() + (a - b) ** 2 / var)).mean(), atol=1e-6)
+    assert torch.allclose(L.poisson_nll_loss(a, b.abs()), (a.exp() - b.abs() * a).mean(), atol=1e-6)
+    lab = torch.tensor([1., -1., 1., -1., 1.])
+    assert torch.allclose(L.cosine_embedding_loss(a, a, torch.ones(5)), torch.zeros(()), atol=1e-6)
+    assert torch.allclose(L.margin_ranking_loss(a[:, 0], b[:, 0], lab, 0.5), (-lab * (a[:, 0] - b[:, 0]) + 0.5).clamp_min(0).mean())
+    assert L.hinge_embedding_loss(a[:, 0].abs(), lab, 1.0) >= 0 and L.multi_margin_loss(logits, tgt) >= 0
+    n = torch.randn(5, 8)
+    assert torch.allclose(L.triplet_margin_loss(a, b, n), L.triplet_margin_with_distance_loss(a, b, n), atol=1e-5)
+    assert torch.allclose(L.contrastive_loss(a, a, torch.ones(5)), torch.zeros(()), atol=1e-9)
+    p, q = torch.softmax(torch.randn(4, 6), -1), torch.softmax(torch.randn(4, 6), -1)
+    assert torch.allclose(L.kl_div(q.log(), p, "sum"), (p * (p.log() - q.log())).sum(), atol=1e-6)
+    js = L.js_divergence(p, q, "none")
+    assert (js >= -1e-7).all() and (js <= math.log(2) + 1e-6).all() and torch.allclose(L.js_divergence(p, p), torch.zeros(()), atol=1e-6)
+    assert torch.allclose(L.js_divergence(p, q), L.js_divergence(q, p), atol=1e-6)
+    assert torch.allclose(L.cross_entropy_continuous(p, p, "sum"), L.entropy_loss(p, "sum"), atol=1e-6)
+    u = torch.full((1, 4), 0.25)
+    assert torch.allclose(L.entropy_loss(u, "sum"), torch.tensor(math.log(4)), atol=1e-6)
+    assert L.mutual_information_loss(torch.full((16,), 3.0), torch.zeros(16)) < -2.9      # critic separates the two sets
+    lp = torch.randn(12, 2, 5).log_softmax(-1)
+    ctc = L.ctc_loss(lp, torch.tensor([[1, 2], [3, 3]]), torch.tensor([12, 12]), torch.tensor([2, 2]))
+    assert torch.isfinite(ctc) and ctc > 0
+    assert torch.allclose(L.wasserstein_loss(torch.ones(4), torch.zeros(4)), torch.tensor(-1.0))
+    gsamp = torch.randn(3, 2, 4)
+    gsamp = gsamp / gsamp.flatten(1).norm(dim=1)[:, None, None]
+    assert torch.allclose(L.gradient_penalty_loss(gsamp, 10.0), torch.zeros(()), atol=1e-9)
+    assert torch.allclose(L.gradient_penalty_loss(2 * gsamp, 10.0), torch.tensor(10.0), atol=1e-4)
+    seq = torch.arange(10.0).reshape(1, 10, 1)
+    assert torch.allclose(L.temporal_consistency_loss(seq, 2.0), torch.tensor(2.0))
+    pred = torch.randn(2, 4, 7, requires_grad=True)
+    tg2 = torch.randint(0, 7, (2, 4))
+    att = torch.softmax(torch.randn(2, 4, 5), -1)
+    base = L.seq2seq_loss_with_attention(pred, tg2)
+    assert torch.allclose(base, torch.nn.functional.cross_entropy(pred.reshape(8, 7), tg2.reshape(8)))
+    withreg = L.seq2seq_loss_with_attention(pred, tg2, att, 0.5)
+    assert torch.allclose(withreg - base, 0.5 * (1 - att.sum(1)).pow(2).sum(-1).mean(), atol=1e-6)
+    (L.cross_entropy(logits, tgt) + withreg).backward()
+    assert torch.isfinite(logits.grad).all() and torch.isfinite(pred.grad).all()
+
+
+def test_spectral_family():
+    import math
+    from torsh_b200 import signal as S
+    torch.manual_seed(0)
+    x = torch.randn(3, 256)
+    assert torch.allclose(S.ifft(S.fft(x)).real, x, atol=1e-5) and torch.allclose(S.irfft(S.rfft(x), 256), x, atol=1e-5)
+    img = torch.randn(2, 16, 16)
+    assert torch.allclose(S.ifftn(S.fftn(img)).real, img, atol=1e-5) and S.rfft2(img).shape == (2, 16, 9) and S.rfftn(img).shape[-1] == 9
+    assert torch.allclose(S.fft2(img), S.fftn(img, dim=(-2, -1)), atol=1e-5)
+    assert torch.allclose(S.ihfft(x[0]), S.rfft(x[0]).conj() / 256, atol=1e-6) and S.hfft(S.ihfft(x[0]), 256).shape == (256,)
+    for htk in (True, False):
+        f = torch.tensor([0.0, 440.0, 1000.0, 4000.0, 8000.0], dtype=torch.float64)
+        assert torch.allclose(S.mel_to_hz(S.hz_to_mel(f, htk), htk), f, atol=1e-6)
+    assert abs(float(S.hz_to_mel(1000.0)) - 999.99) < 0.1
+    sr, t = 16000, torch.arange(16000) / 16000
+    tone = torch.sin(2 * math.pi * 1000 * t)
+    spec = S.spectrogram(tone, 512, 128)
+    cen = S.spectral_centroid(spec, sr)
+    assert abs(float(cen[5:-5].mean()) - 1000) < 40 and abs(float(S.spectral_rolloff(spec, sr, 0.85)[5:-5].mean()) - 1000) < 80
+    mel = S.mel_spectrogram(tone, sr, 512, 128, n_mels=40, log=True)
+    assert mel.shape[0] == 40 and torch.isfinite(mel).all()
+    band = int(mel[:, 10].argmax())
+    centre = float(S.mel_to_hz(torch.linspace(float(S.hz_to_mel(0.0)), float(S.hz_to_mel(8000.0)), 42)[band + 1]))
+    assert abs(centre - 1000) < 150
+    assert torch.allclose(S.create_mel_filterbank(40, 512, sr), S.mel_filterbank(40, 512, sr))
+    X = S.stft_complete(x[0], 64, 16)
+    assert torch.allclose(S.istft_complete(X, 64, 16, length=256), x[0], atol=1e-4)
+    # cepstrum of an impulse train with period 32 has its first rahmonic at quefrency 32
+    e = torch.zeros(256); e[::32] = 1.0
+    c = S.cepstrum(e + 1e-3 * torch.randn(256))
+    assert int(c[8:128].argmax()) + 8 == 32
+    assert torch.equal(S.generate_window("hann", 16), S.window("hann", 16))

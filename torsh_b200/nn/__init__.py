@@ -1,5 +1,5 @@
 """Neural-network layers, containers, initialisers and the functional API."""
-from . import functional, init
+from . import functional, init, losses
 from .layers import *  # noqa: F401,F403
 from .layers import _ADOPTED
 from .extra_layers import *  # noqa: F401,F403
