@@ -93,8 +93,9 @@ allreduce_kernel(const CommArgs a) {
     for (long v = tid; v < nvec && cnt < 4; v += nthreads, ++cnt) {
 #pragma unroll
       for (int j = 0; j < N; ++j) acc[cnt][j] = 0.f;
-      for (int p = 0; p < a.world; ++p) {
-        const int q = (a.rank + p) % a.world;
+      // copies are added in rank order 0, 1, ... on EVERY rank: a rank-rotated order would give each rank a differently
+      // rounded sum beyond two ranks, and replicated parameters stepped with those sums would drift apart
+      for (int q = 0; q < a.world; ++q) {
         float f[N];
         Acc<T>::load(reinterpret_cast<const char*>(a.bufs.ptr[q]) + a.byte_off + v * N * sizeof(T), f);
 #pragma unroll

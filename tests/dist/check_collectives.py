@@ -45,8 +45,14 @@ def check_collectives(dev):
                 nv.check_status()
                 err = (buf.tensor[:numel].float() - 0.5 * ref).abs().max().item()
                 tol = 0.05 if dtype == torch.bfloat16 else 1e-4
-                log(f"all_reduce {dtype} {mode} nvls={use_nvls}: max err {err:.5f}")
-                ok &= err < tol
+                # every rank must hold the same bits: replicated parameters are stepped with these sums
+                got = buf.tensor[:numel].float().clone()
+                hi, lo = got.clone(), got.clone()
+                dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+                dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+                same = torch.equal(hi, lo)
+                log(f"all_reduce {dtype} {mode} nvls={use_nvls}: max err {err:.5f}, identical on all ranks: {same}")
+                ok &= err < tol and same
             # all-gather
             chunk = n // world
             buf.tensor.zero_()
@@ -209,7 +215,7 @@ def check_tp(dev):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 
-    for M in (4096, 16384):
+    for M in (4096, 16384, 32768):
         for NK in (4096, 8192):
             rows = M // world
             xs = torch.randn(rows, NK, device=dev, dtype=torch.bfloat16)
