@@ -1,5 +1,6 @@
 """Auxiliary subsystems on the CPU: optimizer checkpoints, monitoring, debug checks, property-based fuzzing of the
 host-side planners and codecs."""
+import os
 import threading
 
 import numpy as np
@@ -662,3 +663,28 @@ def test_profiler_exporters_grafana_cloudwatch_streaming_ci_and_monitor(tmp_path
     assert s["samples"] >= 2 and s["power_w_mean"] == 750.0 and s["temp_c_max"] == 61.0 and s["sm_mhz_median"] == 1845.0
     assert s["throttle_reason_bits"] == 4 and s["energy_j"] > 0 and calls == ["init"]
     assert ex.PowerThermalMonitor(nvml=None).summary() == {"samples": 0} or True
+
+
+def test_kernel_generator_emits_compilable_source_and_portable_results(tmp_path, monkeypatch):
+    """The run-time generator: expression -> CUDA source that nvcc accepts for sm_100a (content-addressed cache), and
+    the same expression evaluated with PyTorch ops on CPU tensors."""
+    import shutil
+    from torsh_b200.core import kernel_gen as kg
+    monkeypatch.setenv("TORSH_JIT_DIR", str(tmp_path))
+    f = kg.FusedElementwise(lambda a, b: kg.maximum(a * kg.tanh(b) - 2.0, kg.exp(-kg.square(a))) / (1.0 + kg.relu(b)), 2)
+    src = f.source(torch.bfloat16)
+    assert "fused_kernel" in src and all(f"launch_{v}" in src for v in kg.VARIANTS) and "__nv_bfloat16" in src
+    assert f.expr.n_inputs() == 2 and f.expr.key().startswith("div(max(")
+    a, b = torch.randn(2, 777)
+    ref = torch.maximum(a * torch.tanh(b) - 2.0, torch.exp(-a * a)) / (1.0 + torch.relu(b))
+    assert torch.allclose(f(a, b), ref, atol=1e-6)
+    if shutil.which("nvcc") or os.path.exists("/usr/local/cuda/bin/nvcc"):
+        lib = kg.compile_source(src)
+        assert lib.exists() and lib.stat().st_size > 10_000
+        stamp = lib.stat().st_mtime_ns
+        assert kg.compile_source(src) == lib and lib.stat().st_mtime_ns == stamp        # unchanged source: no rebuild
+    sel = kg.KernelSelector()
+    sel.tuner.timer = lambda fn: {"t256_u1": 3.0, "t256_u2": 1.0, "t512_u2": 2.0, "t128_u4": 4.0}[fn()]
+    assert sel.choose("k", 1 << 20, lambda name: name) == "t256_u2" and "k|2^20" in sel.tuner.table
+    with pytest.raises(ValueError):
+        kg.Expr._wrap(float("inf")).code("j")

@@ -611,3 +611,45 @@ def test_grouped_conv_matches_torch():
     y = grouped_conv2d_nhwc(x, wt, None, 1, 1, groups=4)
     yr = torch.nn.functional.conv2d(x.float().permute(0, 3, 1, 2), wt.float(), None, 1, 1, groups=4).permute(0, 2, 3, 1)
     assert _rel(y, yr) < 1e-2
+
+
+# ------------------------------------------------------------------ run-time generated kernels
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n", [8, 1000, 1 << 20, (1 << 20) + 13])
+def test_generated_fused_elementwise_kernel(dtype, n, tmp_path, monkeypatch):
+    from torsh_b200.core import kernel_gen as kg
+    monkeypatch.setenv("TORSH_JIT_DIR", str(tmp_path))
+    f = kg.FusedElementwise(lambda a, b, c: kg.where(kg.greater(a, 0.0), a * kg.sigmoid(b) + 0.5,
+                                                    kg.gelu_tanh(c) / (1.0 + kg.absolute(b))), 3)
+    torch.manual_seed(n)
+    a, b, c = (torch.randn(n, device=DEV).to(dtype) for _ in range(3))
+    out = f(a, b, c)
+    af, bf, cf = a.float(), b.float(), c.float()
+    ref = torch.where(af > 0, af * torch.sigmoid(bf) + 0.5, torch.nn.functional.gelu(cf, approximate="tanh") / (1 + bf.abs()))
+    assert out.dtype == dtype and out.shape == a.shape
+    assert _rel_elem(out, ref) < (1e-2 if dtype == torch.bfloat16 else 1e-4)
+    if n >= 1 << 20:
+        table = kg.default_selector().tuner.table
+        assert any(k.startswith(f.expr.key()) for k in table)          # a variant was measured and remembered
+
+
+def test_gemm_measured_tile_selection():
+    """With autotuning on, every candidate tile / raster choice is timed once per shape, the winner is remembered and
+    the product is unchanged."""
+    from torsh_b200.ops import gemm as G
+    torch.manual_seed(5)
+    a = torch.randn(2048, 1024, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(3072, 1024, device=DEV, dtype=torch.bfloat16)
+    ref = G.gemm(a, b)
+    tuner = G.gemm_autotune(True)
+    try:
+        out = G.gemm(a, b)
+        key = "gemm|2048x3072x1024|a0b0|f0"
+        assert key in tuner.table and set(tuner.table[key].times_ms) == {"bn128_r0", "bn128_r1", "bn256_r0", "bn256_r1"}
+        assert tuner.table[key].choice == min(tuner.table[key].times_ms, key=tuner.table[key].times_ms.get)
+        assert _rel_elem(out, a.float() @ b.float().t()) < 1e-2 and _rel_elem(out, ref) < 1e-2
+        n = len(tuner.table)
+        G.gemm(a, b)
+        assert len(tuner.table) == n                       # second call: table hit, no new measurement
+    finally:
+        G.gemm_autotune(False)

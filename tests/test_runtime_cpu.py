@@ -276,3 +276,41 @@ def test_native_token_loader_is_deterministic_and_in_order(tmp_path):
     assert not torch.equal(other[0][1], x0)                                                           # ranks draw different windows
     with pytest.raises(OSError):
         NativeTokenLoader(str(tmp_path / "missing.bin"), batch=1, seq=4, pin=False)
+
+
+def test_multi_stream_orchestrator_plans_and_issues_with_few_events():
+    """Critical-path list scheduling beats round-robin on a fork-join graph with one long branch, same-stream edges
+    need no event, and issue order respects every dependency."""
+    from torsh_b200.core.stream_orchestrator import MultiStreamOrchestrator
+
+    class FakeStream:
+        def __init__(self, name): self.name = name
+
+    log = []
+
+    def build(policy):
+        o = MultiStreamOrchestrator([FakeStream("s0"), FakeStream("s1")], policy=policy)
+        o.add("load", lambda: log.append("load"), cost=1)
+        o.add("long1", lambda: log.append("long1"), cost=6, deps=("load",))
+        o.add("long2", lambda: log.append("long2"), cost=6, deps=("long1",))
+        for i in range(4):
+            o.add(f"short{i}", lambda i=i: log.append(f"short{i}"), cost=2, deps=("load",))
+        o.add("join", lambda: log.append("join"), cost=1, deps=("long2", "short0", "short1", "short2", "short3"))
+        return o
+    cp, rr, ll = build("critical_path").plan(), build("round_robin").plan(), build("least_loaded").plan()
+    assert cp.makespan == 14.0                      # load + the two long tasks + join: the critical path itself
+    assert rr.makespan > cp.makespan and ll.makespan >= cp.makespan
+    assert cp.assignment["long1"] == cp.assignment["long2"] == cp.assignment["load"]     # the chain stays on one stream
+    assert cp.order.index("long1") < cp.order.index("short0")
+    o = build("critical_path")
+    log.clear()
+    res = o.run()
+    assert set(res) == set(o.tasks) and log[0] == "load" and log[-1] == "join" and log.index("long1") < log.index("long2")
+    st = o.coordinator.stats
+    assert st["events_recorded"] == 8 and st["cross_stream_waits"] == cp.cross_stream_edges
+    assert st["same_stream_skipped"] + st["cross_stream_waits"] == 1 + 1 + 4 + 5
+    o.join()
+    with pytest.raises(KeyError):
+        build("round_robin").add("x", deps=("nope",))
+    with pytest.raises(ValueError):
+        MultiStreamOrchestrator([FakeStream("a")], policy="magic")

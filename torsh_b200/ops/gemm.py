@@ -26,6 +26,32 @@ EPI_RASTER_M = 256
 
 _configured = False
 
+# ---- measured tile selection --------------------------------------------------------------------------------------
+# Off by default: the launcher's heuristic (BN 256 unless the grid would be short, rasterise along M for wide outputs)
+# is what the benchmarks run. `gemm_autotune(True)` or TORSH_GEMM_AUTOTUNE=1 times the candidates (BN 128 / 256 x both
+# raster orders) once per problem shape on the caller's tensors and remembers the winner; TORSH_GEMM_TUNE_FILE keeps
+# the table across runs. Accumulating / atomic products and launches inside a CUDA-graph capture are never timed.
+_autotune = None
+
+
+def gemm_autotune(on: bool = True, path: str | None = None):
+    """Switches measured tile selection on or off; returns the tuner (its ``table`` maps shape keys to choices)."""
+    global _autotune
+    if not on:
+        _autotune = None
+        return None
+    import os
+    from ..core.backend import Autotuner
+    _autotune = Autotuner(path or os.environ.get("TORSH_GEMM_TUNE_FILE"), warmup=1, iters=3)
+    return _autotune
+
+
+def _env_autotune():
+    import os
+    if _autotune is None and os.environ.get("TORSH_GEMM_AUTOTUNE", "0") == "1":
+        gemm_autotune(True)
+    return _autotune
+
 
 def _lib():
     global _configured
@@ -89,6 +115,20 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_major: int = 0, b_major: int = 0
         flags |= EPI_ATOMIC
     if accumulate:
         flags |= EPI_ACCUM
+    tuner = _env_autotune()
+    if (tuner is not None and bn == 0 and raster_m is None and not atomic and not accumulate and split_k == 1
+            and getattr(b, "_tb_fsdp_unit", None) is None and not torch.cuda.is_current_stream_capturing()):
+        key = f"gemm|{M}x{N}x{K}|a{a_major}b{b_major}|f{flags}"
+        rec = tuner.table.get(key)
+        if rec is None:
+            kw = dict(a_major=a_major, b_major=b_major, out=out, bias=bias, gelu=gelu, residual=residual, preact_out=preact_out,
+                      dgelu_aux=dgelu_aux)
+            cands = {f"bn{tbn}_r{int(r)}": (lambda tbn=tbn, r=r: gemm(a, b, bn=tbn, raster_m=r, **kw))
+                     for tbn in (128, 256) for r in (False, True)}
+            choice = tuner.select(key, cands)
+        else:
+            choice = rec.choice
+        bn, raster_m = int(choice[2:5]), choice.endswith("_r1")
     if raster_m is None:
         raster_m = N > 4 * M or (N >= 16384 and N > M)
     if raster_m:
