@@ -1144,3 +1144,92 @@ def test_spectral_family():
     c = S.cepstrum(e + 1e-3 * torch.randn(256))
     assert int(c[8:128].argmax()) + 8 == 32
     assert torch.equal(S.generate_window("hann", 16), S.window("hann", 16))
+
+
+def test_text_generation_metrics_datasets_embeddings(tmp_path):
+    import json
+    import math
+    from torsh_b200.text import Vocab, WhitespaceTokenizer
+    from torsh_b200.text import datasets as D, embeddings as E, generation as G, metrics as M
+    V = 10
+
+    def step(ids):                                   # toy LM: strongly prefers last + 1, weakly last + 2
+        l = torch.full((ids.shape[0], V), -6.0)
+        r = torch.arange(ids.shape[0])
+        l[r, (ids[:, -1] + 1) % V] = 4.0
+        l[r, (ids[:, -1] + 2) % V] = 3.0
+        return l
+    assert G.TextGenerator(G.GenerationConfig(max_length=8, eos_token_id=7)).generate(step, [2, 3]) == [2, 3, 4, 5, 6, 7]
+    beams = G.BeamSearchDecoder(3, 7, 1.0, eos_token_id=None).search(step, torch.tensor([0]))
+    assert beams[0].tokens == [0, 1, 2, 3, 4, 5, 6] and beams[0].score > beams[1].score and len(beams) == 3
+    s = G.TextSampler(seed=0)
+    logits = torch.tensor([0.0, 5.0, 4.0, -3.0])
+    assert s.greedy_sample(logits) == 1 and s.top_k_sample(logits, 1) == 1 and s.top_p_sample(logits, 0.5) == 1
+    draws = {s.top_k_top_p_sample(logits, 2, 1.0, 1.0) for _ in range(40)}
+    assert draws == {1, 2}
+    pen = G.RepetitionPenalty.apply(torch.tensor([2.0, -2.0, 1.0]), [0, 1], 2.0)
+    assert pen.tolist() == [1.0, -4.0, 1.0]
+    f = G.NGramRepetitionFilter(2)
+    assert f.banned([1, 2, 3, 1]) == {2} and f.filter_logits(torch.zeros(5), [1, 2, 3, 1])[2] == float("-inf")
+    sampled = G.TextGenerator(G.GenerationConfig(max_length=12, do_sample=True, top_k=2, temperature=0.7, seed=3, no_repeat_ngram_size=2)).generate(step, [0])
+    grams = list(zip(sampled, sampled[1:]))
+    assert len(sampled) == 12 and len(set(grams[1:])) == len(grams[1:])
+    # metrics
+    ref, cand = "the cat sat on the mat".split(), "the cat sat on a mat".split()
+    assert M.bleu([ref], [[ref]]) == 1.0 and 0.5 < M.sentence_bleu(cand, [ref]) < 1.0 and M.bleu([["x"]], [[ref]]) == 0.0
+    assert M.rouge_n(cand, ref, 1)["f1"] == pytest.approx(5 / 6) and M.rouge_l(cand, ref)["recall"] == pytest.approx(5 / 6)
+    assert M.edit_distance("kitten", "sitting") == 3 and M.word_error_rate("a b c", "a x c d") == pytest.approx(0.5)
+    lg = torch.zeros(4, 8)
+    assert M.perplexity(lg, torch.tensor([1, 2, 3, 4])) == pytest.approx(8.0, rel=1e-5)
+    assert M.token_overlap_f1(cand, ref)["precision"] == pytest.approx(5 / 6)
+    table = torch.eye(12)
+    emb = lambda toks: table[[hash(t) % 12 for t in toks]]
+    assert M.embedding_match_score(ref, ref, emb)["f1"] == pytest.approx(1.0)
+    # datasets
+    (tmp_path / "c.csv").write_text("text,label\nGood film,pos\nBad film,neg\nGreat   FUN movie,pos\n")
+    tok = WhitespaceTokenizer()
+    vocab = Vocab.build(["good film bad great fun movie"])
+    pipe = D.PreprocessingPipeline(D.PreprocessingConfig(max_length=3), tok, vocab)
+    ds = D.ClassificationDataset(tmp_path / "c.csv", pipeline=pipe)
+    assert len(ds) == 3 and ds.num_classes == 2 and ds.label_names == ["neg", "pos"] and ds[2] == (vocab.encode(["great", "fun", "movie"]), 1)
+    (tmp_path / "c.jsonl").write_text("\n".join(json.dumps({"text": t, "label": l}) for t, l in [("a b", 1), ("c", 0)]))
+    assert D.ClassificationDataset(tmp_path / "c.jsonl")[0] == ("a b", 1)
+    batches = list(D.BatchIterator(D.CachedDataset(ds), 2, pad_id=0, bucket=True))
+    assert batches[0]["input_ids"].shape == (2, 2) and batches[0]["labels"].tolist() == [1, 0] and batches[1]["lengths"].tolist() == [3]
+    lm = D.LanguageModelingDataset(list(range(20)), block_size=4, stride=4)
+    x, y = lm[1]
+    assert len(lm) == 4 and x.tolist() == [4, 5, 6, 7] and y.tolist() == [5, 6, 7, 8]
+    (tmp_path / "train.de").write_text("ein hund\n\nzwei katzen\n")
+    (tmp_path / "train.en").write_text("a dog\n\ntwo cats\n")
+    tr = D.multi30k(tmp_path, "train")
+    assert len(tr) == 2 and tr[1] == ("zwei katzen", "two cats")
+    (tmp_path / "ner.conll").write_text("-DOCSTART- O\n\nJohn B-PER\nsmiles O\n\nParis B-LOC\n")
+    ner = D.SequenceLabelingDataset(tmp_path / "ner.conll")
+    assert len(ner) == 2 and ner[0] == (["John", "smiles"], ["B-PER", "O"]) and ner.tag_names == ["B-LOC", "B-PER", "O"]
+    (tmp_path / "train.csv").write_text('"3","Title","Stocks rise"\n"1","T2","Match won"\n')
+    ag = D.ag_news(tmp_path, "train")
+    assert len(ag) == 2 and ag[0] == ("Stocks rise", 1)
+    (tmp_path / "wiki.train.tokens").write_text(" = Title = \n the quick brown fox jumps over the lazy dog again and again \n")
+    wt = D.wikitext(tmp_path, "train", block_size=4)
+    assert len(wt) >= 2 and wt[0][0].shape == (4,)
+    with pytest.raises(FileNotFoundError):
+        D.ag_news(tmp_path / "nope")
+    ids, mask, lens = D.pad_sequences([[1, 2, 3], [4]], pad_id=9)
+    assert ids.tolist() == [[1, 2, 3], [4, 9, 9]] and mask.tolist() == [[True, True, True], [True, False, False]] and lens.tolist() == [3, 1]
+    # embeddings
+    (tmp_path / "glove.txt").write_text("3 4\ngood 1 0 0 0\nfilm 0 1 0 0\nzzz 0 0 1 0\n")
+    w = E.EmbeddingUtils.load_pretrained_embeddings(tmp_path / "glove.txt", vocab)
+    assert w.shape == (len(vocab), 4) and w[vocab["good"]].tolist() == [1, 0, 0, 0] and w.found == 2
+    toks, mat = E.EmbeddingUtils.load_pretrained_embeddings(tmp_path / "glove.txt")
+    assert toks == ["good", "film", "zzz"] and mat.shape == (3, 4)
+    we = E.WordEmbedding.from_pretrained(w)
+    assert not we.emb.weight.requires_grad and torch.equal(we(torch.tensor([vocab["film"]]))[0], w[vocab["film"]])
+    pe = E.PositionalEncoding(8, 32)
+    z = torch.zeros(2, 5, 8)
+    assert torch.allclose(pe(z)[0, 0], torch.tensor([0., 1.] * 4)) and torch.allclose(pe(z, offset=3)[0, 0], pe.pe[3])
+    ce = E.CombinedEmbeddings(len(vocab), 8, max_len=16, dropout=0.0)
+    out = ce(torch.tensor([[1, 2, 3]]), torch.tensor([[0, 0, 1]]))
+    assert out.shape == (1, 3, 8) and abs(float(out.mean())) < 1e-5
+    ee = torch.tensor([[1., 0.], [0.9, 0.1], [0., 1.]])
+    assert E.EmbeddingUtils.most_similar(ee, 0, 1)[0][0] == 1 and E.EmbeddingUtils.cosine_similarity(ee, 0, 2) == 0.0
+    assert E.EmbeddingUtils.xavier_uniform_embeddings(10, 4).abs().max() <= math.sqrt(6 / 14) + 1e-6

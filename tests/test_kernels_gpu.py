@@ -616,9 +616,9 @@ def test_grouped_conv_matches_torch():
 # ------------------------------------------------------------------ run-time generated kernels
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("n", [8, 1000, 1 << 20, (1 << 20) + 13])
-def test_generated_fused_elementwise_kernel(dtype, n, tmp_path, monkeypatch):
+def test_generated_fused_elementwise_kernel(dtype, n, tmp_path_factory, monkeypatch):
     from torsh_b200.core import kernel_gen as kg
-    monkeypatch.setenv("TORSH_JIT_DIR", str(tmp_path))
+    monkeypatch.setenv("TORSH_JIT_DIR", str(tmp_path_factory.getbasetemp() / "jit"))     # one compile per dtype for all sizes
     f = kg.FusedElementwise(lambda a, b, c: kg.where(kg.greater(a, 0.0), a * kg.sigmoid(b) + 0.5,
                                                     kg.gelu_tanh(c) / (1.0 + kg.absolute(b))), 3)
     torch.manual_seed(n)
