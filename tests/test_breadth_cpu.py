@@ -1233,3 +1233,100 @@ def test_text_generation_metrics_datasets_embeddings(tmp_path):
     ee = torch.tensor([[1., 0.], [0.9, 0.1], [0., 1.]])
     assert E.EmbeddingUtils.most_similar(ee, 0, 1)[0][0] == 1 and E.EmbeddingUtils.cosine_similarity(ee, 0, 2) == 0.0
     assert E.EmbeddingUtils.xavier_uniform_embeddings(10, 4).abs().max() <= math.sqrt(6 / 14) + 1e-6
+
+
+def test_vision_detection_and_image_io(tmp_path):
+    from torsh_b200.vision import box_iou, detection as Det, io as VIO
+    torch.manual_seed(0)
+    # anchors, coding, matching
+    ag = Det.AnchorGenerator(sizes=(32, 64), ratios=(0.5, 1.0, 2.0), scales=(1.0,))
+    anchors = ag([(4, 4), (2, 2)], [8, 16])
+    assert anchors.shape == (4 * 4 * 3 + 2 * 2 * 3, 4) and ag.num_anchors == 3
+    a0 = anchors[1]                                       # ratio 1 at the first cell: a 32 x 32 box centred at (4, 4)
+    assert torch.allclose(a0, torch.tensor([-12., -12., 20., 20.]))
+    coder = Det.BoxCoder()
+    gt = torch.tensor([[2., 3., 30., 40.], [10., 10., 20., 28.]])
+    sel = anchors[:2]
+    assert torch.allclose(coder.decode(coder.encode(gt, sel), sel), gt, atol=1e-4)
+    m = Det.match_anchors(anchors, gt)
+    assert set(m.tolist()) <= {-2, -1, 0, 1} and (m == 0).any() and (m == 1).any()
+    assert (Det.match_anchors(anchors, torch.zeros(0, 4)) == -1).all()
+    # post-processing
+    boxes = torch.tensor([[0., 0., 10., 10.], [1., 1., 11., 11.], [50., 50., 60., 60.]])
+    scores = torch.tensor([[0.9, 0.0], [0.8, 0.0], [0.1, 0.7]])
+    dets = Det.postprocess(boxes, scores, 0.05, 0.5, 10, (64, 64))
+    assert [(d.label, round(d.score, 2)) for d in dets] == [(0, 0.9), (1, 0.7), (0, 0.1)]
+    assert dets[0].box.area() == 100.0 and dets[0].box.center() == (5.0, 5.0)
+    # detectors: shapes, losses decrease under a few steps, detections decode
+    net = Det.retinanet_tiny(3)
+    img = torch.randn(2, 3, 64, 64)
+    cls, reg, anc = net(img)
+    assert cls.shape == (2, anc.shape[0], 3) and reg.shape == (2, anc.shape[0], 4)
+    assert torch.sigmoid(cls).mean() < 0.05                  # focal-loss prior: everything starts as background
+    targets = [{"boxes": torch.tensor([[8., 8., 40., 40.]]), "labels": torch.tensor([1])},
+               {"boxes": torch.tensor([[20., 16., 60., 50.], [4., 30., 30., 62.]]), "labels": torch.tensor([0, 2])}]
+    opt = torch.optim.Adam(net.parameters(), 1e-3)
+    first = last = None
+    for _ in range(12):
+        l = net.loss(img, targets)
+        tot = l["classification"] + l["regression"]
+        opt.zero_grad(); tot.backward(); opt.step()
+        first = float(tot) if first is None else first
+        last = float(tot)
+    assert last < first
+    net.eval()
+    assert all(isinstance(d, Det.Detection) for d in net.detect(img, score_thresh=0.0, top_k=5)[0])
+    ssd = Det.ssd_tiny(4).eval()
+    c2, r2, a2 = ssd(img)
+    assert c2.shape == (2, a2.shape[0], 5) and len(ssd.detect(img, score_thresh=0.0, top_k=7)[1]) == 7
+    pred = torch.zeros(1, 2, 4, 4, 5 + 3)
+    yb, ys = Det.decode_yolo_grid(pred, [(10., 20.), (30., 30.)], stride=8)
+    assert yb.shape == (1, 32, 4) and ys.shape == (1, 32, 3) and torch.allclose(ys, torch.full_like(ys, 0.25))
+    assert torch.allclose(yb[0, 0], torch.tensor([4 - 5., 4 - 10., 4 + 5., 4 + 10.]))     # sigmoid(0): centre of cell 0, anchor size
+    # image IO round trips in every format
+    io = VIO.VisionIO().with_caching(True, 4)
+    rgb = (torch.rand(3, 13, 17) * 255).to(torch.uint8)
+    for ext in ("png", "ppm", "bmp", "npy"):
+        io.save_image(rgb, tmp_path / f"a.{ext}")
+        assert torch.equal(io.load_image(tmp_path / f"a.{ext}"), rgb), ext
+    grey = (torch.rand(1, 9, 5) * 255).to(torch.uint8)
+    io.save_image(grey, tmp_path / "g.pgm"); io.save_image(grey, tmp_path / "g.png")
+    assert torch.equal(io.load_image(tmp_path / "g.pgm"), grey) and torch.equal(io.load_image(tmp_path / "g.png"), grey)
+    rgba = (torch.rand(4, 6, 6) * 255).to(torch.uint8)
+    io.save_image(rgba, tmp_path / "t.png")
+    assert torch.equal(io.load_image(tmp_path / "t.png"), rgba)
+    io.save_image(torch.full((3, 4, 4), 0.5), tmp_path / "f.png")
+    assert int(io.load_image(tmp_path / "f.png")[0, 0, 0]) == 128
+    # a PNG whose scan lines use the Sub / Up / Average / Paeth filters decodes to the same pixels
+    import struct, zlib
+    arr = rgb.permute(1, 2, 0).numpy().astype(int)
+    h, w, c = arr.shape
+    flat = arr.reshape(h, w * c)
+    raw = bytearray()
+    for y in range(h):
+        f = [1, 2, 3, 4][y % 4]
+        raw.append(f)
+        for i in range(w * c):
+            a = flat[y, i - c] if i >= c else 0
+            b = flat[y - 1, i] if y else 0
+            cc = flat[y - 1, i - c] if (y and i >= c) else 0
+            p = a + b - cc
+            paeth = a if (abs(p - a) <= abs(p - b) and abs(p - a) <= abs(p - cc)) else (b if abs(p - b) <= abs(p - cc) else cc)
+            pred = {1: a, 2: b, 3: (a + b) // 2, 4: paeth}[f]
+            raw.append((flat[y, i] - pred) & 255)
+    png = (b"\\x89PNG\\r\\n\\x1a\\n".decode("unicode_escape").encode("latin1") + VIO._png_chunk(b"IHDR", struct.pack(">IIBBBBB", w, h, 8, 2, 0, 0, 0))
+           + VIO._png_chunk(b"IDAT", zlib.compress(bytes(raw))) + VIO._png_chunk(b"IEND", b""))
+    assert torch.equal(VIO.decode_png(png), rgb)
+    (tmp_path / "bad.png").write_bytes(b"not an image")
+    res = io.load_images_from_dir(tmp_path)
+    assert not res.all_successful() and len(res.failed) == 1 and "bad.png" in res.failed[0][0] and 0.8 < res.success_rate() < 1.0
+    assert len(io.load_images_with_pattern(tmp_path, "a.*").ok) == 4
+    conv = io.batch_convert_format([tmp_path / "a.png", tmp_path / "g.pgm"], tmp_path / "out", "bmp")
+    assert conv.all_successful() and torch.equal(io.load_image(tmp_path / "out" / "a.bmp"), rgb)
+    saved = io.batch_save_images([rgb, grey], tmp_path / "batch", fmt="png")
+    assert saved.all_successful() and (tmp_path / "batch" / "img_00001.png").exists()
+    info = io.get_image_info(tmp_path / "a.png")
+    assert (info.width, info.height, info.channels, info.format) == (17, 13, 3, "png") and info.file_size > 0
+    assert io.is_supported_image("x.PNG") and not io.is_supported_image("x.gif") and "png" in io.supported_formats()
+    VIO.configure_global_io(io)
+    assert VIO.global_io() is io
