@@ -1330,3 +1330,153 @@ def test_vision_detection_and_image_io(tmp_path):
     assert io.is_supported_image("x.PNG") and not io.is_supported_image("x.gif") and "png" in io.supported_formats()
     VIO.configure_global_io(io)
     assert VIO.global_io() is io
+
+
+def test_rl_models_learn_a_two_armed_bandit_chain():
+    """DQN with replay and a target net, PPO with GAE and A3C n-step loss each improve on a tiny deterministic task:
+    state = one-hot position on a 4-cell line, action 1 moves right (+1 reward at the end), action 0 ends the episode."""
+    import random
+    from torsh_b200.models import create_model, rl
+    torch.manual_seed(0)
+    rng = random.Random(0)
+
+    def env_step(pos, a):
+        if a == 0:
+            return pos, 0.0, True
+        return pos + 1, (1.0 if pos + 1 == 3 else 0.0), pos + 1 == 3
+    onehot = lambda p: torch.eye(4)[p]
+    q, tgt = rl.DQN(rl.DQNConfig(4, 2, (32,), dueling=True)), rl.DQN(rl.DQNConfig(4, 2, (32,), dueling=True))
+    tgt.load_state_dict(q.state_dict())
+    buf, opt = rl.ReplayBuffer(500, 4), torch.optim.Adam(q.parameters(), 5e-3)
+    for ep in range(150):
+        pos, done = 0, False
+        while not done:
+            a = q.act(onehot(pos), epsilon=0.3, rng=rng)
+            npos, r, done = env_step(pos, a)
+            buf.push(onehot(pos), a, r, onehot(min(npos, 3)), done)
+            pos = npos
+        if len(buf) >= 32:
+            for _ in range(2):
+                loss = q.td_loss(tgt, buf.sample(32))
+                opt.zero_grad(); loss.backward(); opt.step()
+        if ep % 10 == 0:
+            tgt.load_state_dict(q.state_dict())
+    assert all(q.act(onehot(p), epsilon=0.0) == 1 for p in range(3))               # learned to walk right
+    # GAE on a known trajectory
+    adv, ret = rl.gae(torch.tensor([0., 0., 1.]), torch.zeros(3), torch.tensor([0., 0., 1.]), 5.0, gamma=0.5, lam=1.0)
+    assert torch.allclose(ret, torch.tensor([0.25, 0.5, 1.0])) and torch.allclose(adv, ret)
+    ppo = create_model("ppo", state_dim=4, action_dim=2, hidden=(32,))
+    popt = torch.optim.Adam(ppo.parameters(), 1e-2)
+    def rollout():
+        S, A, LP, R, V, D = [], [], [], [], [], []
+        for _ in range(16):
+            pos, done = 0, False
+            while not done:
+                a, lp, v = ppo.act(onehot(pos)[None])
+                npos, r, done = env_step(pos, int(a))
+                S.append(onehot(pos)); A.append(int(a)); LP.append(float(lp)); R.append(r); V.append(float(v)); D.append(done)
+                pos = npos
+        return torch.stack(S), torch.tensor(A), torch.tensor(LP), torch.tensor(R), torch.tensor(V), torch.tensor(D)
+    first = None
+    for it in range(30):
+        S, A, LP, R, V, D = rollout()
+        first = float(R.sum()) if first is None else first
+        adv, ret = rl.gae(R, V, D, 0.0, ppo.cfg.gamma, ppo.cfg.lam)
+        for _ in range(4):
+            l = ppo.loss(S, A, LP, adv, ret)
+            popt.zero_grad(); l["total"].backward(); popt.step()
+    assert float(rollout()[3].sum()) > max(first, 8.0)                             # most of 16 episodes reach the goal
+    a3c = create_model("a3c", state_dim=4, action_dim=2, hidden=32)
+    l0 = a3c.loss(torch.eye(4)[:3], torch.tensor([1, 1, 1]), torch.tensor([0., 0., 1.]))
+    l0.backward()
+    assert torch.isfinite(l0) and all(p.grad is not None for p in a3c.parameters())
+    cont = rl.PPO(rl.PPOConfig(3, 2, (16,), continuous=True))
+    a, lp, v = cont.act(torch.randn(5, 3))
+    assert a.shape == (5, 2) and lp.shape == (5,) and v.shape == (5,)
+
+
+def test_video_generative_few_shot_and_3d_models():
+    from torsh_b200.models import create_model, few_shot as FS, generative as G, list_models, video as VD, vision_3d as V3
+    torch.manual_seed(0)
+    assert {"dqn", "slowfast", "vae", "diffusion_unet", "pointnet2", "video_transformer"} <= set(list_models())
+    clip = torch.randn(2, 3, 8, 64, 64)
+    for m in (VD.ResNet3D(VD.ResNet3DConfig(num_classes=5, widths=(8, 16), depths=(1, 1))),
+              VD.SlowFast(VD.SlowFastConfig(num_classes=5, widths=(16, 32))),
+              VD.VideoTransformer(VD.VideoTransformerConfig(num_classes=5, dim=32, depth=1))):
+        out = m(clip)
+        out.sum().backward()
+        assert out.shape == (2, 5) and all(p.grad is not None for p in m.parameters() if p.requires_grad)
+    # VAE: the ELBO falls; eval mode is deterministic
+    x = torch.rand(8, 3, 32, 32)
+    vae = create_model("vae", latent_dim=8, widths=(8, 16))
+    opt = torch.optim.Adam(vae.parameters(), 2e-3)
+    losses = []
+    for _ in range(15):
+        l = vae.loss(x)["total"]
+        opt.zero_grad(); l.backward(); opt.step(); losses.append(float(l))
+    assert losses[-1] < losses[0]
+    vae.eval()
+    assert torch.equal(vae(x)[0], vae(x)[0]) and vae.sample(3).shape == (3, 3, 32, 32)
+    # GAN: shapes, both objectives, gradient penalty is differentiable w.r.t. the discriminator
+    gan = G.GAN(G.GANConfig(latent_dim=16, width=8))
+    fake = gan.generate(4)
+    assert fake.shape == (4, 3, 32, 32) and fake.abs().max() <= 1
+    assert gan.discriminator_loss(x[:4] * 2 - 1, fake) > 0 and torch.isfinite(gan.generator_loss(fake, wasserstein=True))
+    gan.gradient_penalty(x[:4] * 2 - 1, fake).backward()
+    assert any(p.grad is not None and p.grad.abs().sum() > 0 for p in gan.discriminator.parameters())
+    # diffusion: schedules, q_sample limits, loss falls, both samplers return finite images
+    cfg = G.DiffusionConfig(width=8, timesteps=50)
+    diff = G.GaussianDiffusion(cfg)
+    assert (diff.alphas_bar[1:] < diff.alphas_bar[:-1]).all() and G.GaussianDiffusion(G.DiffusionConfig(schedule="cosine")).alphas_bar[-1] < 1e-3
+    x0, noise = x * 2 - 1, torch.randn_like(x)
+    assert torch.allclose(diff.q_sample(x0, torch.zeros(8, dtype=torch.long), noise), x0, atol=0.05)
+    unet = G.DiffusionUNet(cfg)
+    dopt = torch.optim.Adam(unet.parameters(), 2e-3)
+    gen = torch.Generator().manual_seed(0)
+    hist = []
+    for _ in range(25):
+        l = diff.loss(unet, x0, gen)
+        dopt.zero_grad(); l.backward(); dopt.step(); hist.append(float(l))
+    assert sum(hist[-5:]) < sum(hist[:5])
+    assert torch.isfinite(diff.sample(unet, (2, 3, 32, 32), steps=5, eta=0.0)).all() and diff.sample(unet, (1, 3, 32, 32)).shape == (1, 3, 32, 32)
+    # few-shot: clusters in 2-D; prototypes classify them, MAML / Reptile adapt a linear model
+    centers = torch.tensor([[4., 0.], [-4., 0.], [0., 4.], [0., -4.], [4., 4.], [-4., -4.]])
+    y = torch.arange(6).repeat_interleave(12)
+    xs = centers[y] + 0.3 * torch.randn(72, 2)
+    fcfg = FS.FewShotConfig(n_way=3, k_shot=2, n_query=4, inner_lr=0.5, inner_steps=3)
+    ds = FS.FewShotDataset(xs, y, fcfg)
+    ep = ds.sample_episode()
+    assert ep.support_x.shape == (6, 2) and ep.query_y.tolist() == [0] * 4 + [1] * 4 + [2] * 4
+    proto = FS.PrototypicalNetwork(torch.nn.Identity(), fcfg)
+    assert FS.FewShotEvaluator(ds, 20).evaluate(proto).mean_accuracy > 0.95
+    for metric in ("cosine", "manhattan"):
+        assert FS.pairwise_distance(xs[:3], xs[:3], metric).diagonal().abs().max() < 1e-5
+    lin = torch.nn.Linear(2, 3)
+    maml = FS.MAML(lin, fcfg)
+    mopt = torch.optim.Adam(lin.parameters(), 1e-2)
+    for _ in range(30):
+        l, _ = maml.meta_loss(ds.sample_episode())
+        mopt.zero_grad(); l.backward(); mopt.step()
+    ev = FS.FewShotEvaluator(ds, 20).evaluate(lambda e: torch.func.functional_call(lin, maml.adapt(e, create_graph=False), (e.query_x,)))
+    assert ev.mean_accuracy > 0.8 and ev.episodes == 20 and ev.ci95 >= 0
+    rep = FS.Reptile(torch.nn.Linear(2, 3), fcfg, meta_lr=0.3)
+    accs = [rep.meta_step(ds.sample_episode()) for _ in range(20)]
+    assert sum(accs[-5:]) / 5 > 0.7
+    with pytest.raises(ValueError):
+        FS.FewShotDataset(xs, y, FS.FewShotConfig(n_way=7))
+    # 3-D: PointNet is invariant to point order, transforms start at the identity, FPS / ball query do what they say
+    pts = torch.randn(2, 64, 3)
+    pn = V3.PointNet().eval()
+    perm = torch.randperm(64)
+    assert torch.allclose(pn(pts)[0], pn(pts[:, perm])[0], atol=1e-5)
+    assert torch.allclose(V3.TransformNet(3).eval()(pts.transpose(1, 2)), torch.eye(3).expand(2, 3, 3))
+    assert V3.orthogonality_regularizer(torch.eye(4)[None]) == 0
+    line = torch.stack([torch.arange(10.), torch.zeros(10), torch.zeros(10)], -1)[None]
+    assert V3.farthest_point_sampling(line, 3)[0].tolist() == [0, 9, 4] or V3.farthest_point_sampling(line, 3)[0].tolist() == [0, 9, 5]
+    bq = V3.ball_query(line, line[:, [0, 9]], radius=1.5, k=3)
+    assert bq[0, 0].tolist() == [0, 1, 0] and sorted(bq[0, 1].tolist()) == [8, 9, 9]
+    p2 = V3.PointNetPlusPlus(V3.PointNetPlusPlusConfig(num_classes=4, centers=(16, 4), k=8))
+    out = p2(pts)
+    out.sum().backward()
+    assert out.shape == (2, 4) and V3.CNN3D()(torch.randn(2, 1, 16, 16, 16)).shape == (2, 10)
+    assert torch.isfinite(V3.PointNet().loss(pts, torch.tensor([1, 2])))

@@ -9,7 +9,7 @@ from .vision_zoo import AlexNet, ConvNeXt, DenseNet, EfficientNet, MobileNetV2, 
 from .audio import (HubertModel, Wav2Vec2Config, Wav2Vec2ForCTC, Wav2Vec2Model, WavLMModel, WhisperConfig, WhisperEncoder,
                     WhisperModel)
 from .multimodal import ALIGNModel, CLIPConfig, CLIPModel, DualEncoder
-from . import fine_tuning, model_utils
+from . import few_shot, fine_tuning, generative, model_utils, rl, video, vision_3d
 
 _REGISTRY = {
     "gpt2-tiny": lambda **kw: GPTForCausalLM(GPT2Config.tiny(**kw)),
@@ -48,6 +48,15 @@ _REGISTRY = {
     "whisper-base": lambda **kw: WhisperModel(WhisperConfig.base(**kw)),
     "whisper-small": lambda **kw: WhisperModel(WhisperConfig.small(**kw)),
     "clip-vit-b-32": lambda **kw: CLIPModel(CLIPConfig.vit_b_32()),
+    "dqn": lambda **kw: rl.DQN(rl.DQNConfig(**kw)), "ppo": lambda **kw: rl.PPO(rl.PPOConfig(**kw)), "a3c": lambda **kw: rl.A3C(rl.A3CConfig(**kw)),
+    "resnet3d_18": lambda **kw: video.ResNet3D(video.ResNet3DConfig(**kw)),
+    "slowfast": lambda **kw: video.SlowFast(video.SlowFastConfig(**kw)),
+    "video_transformer": lambda **kw: video.VideoTransformer(video.VideoTransformerConfig(**kw)),
+    "vae": lambda **kw: generative.VAE(generative.VAEConfig(**kw)), "gan": lambda **kw: generative.GAN(generative.GANConfig(**kw)),
+    "diffusion_unet": lambda **kw: generative.DiffusionUNet(generative.DiffusionConfig(**kw)),
+    "cnn3d": lambda **kw: vision_3d.CNN3D(vision_3d.CNN3DConfig(**kw)),
+    "pointnet": lambda **kw: vision_3d.PointNet(vision_3d.PointNetConfig(**kw)),
+    "pointnet2": lambda **kw: vision_3d.PointNetPlusPlus(vision_3d.PointNetPlusPlusConfig(**kw)),
 }
 
 
