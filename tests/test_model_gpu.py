@@ -80,3 +80,32 @@ def test_layernorm_params_receive_gradient_through_flat_buffers():
     for name, p in model.named_parameters():
         assert p.grad is None, name
         assert p.main_grad.abs().sum().item() > 0, f"{name} got no gradient"
+
+
+def test_gpt2_kernel_path_matches_transformers_on_gpu():
+    """An independent implementation as the oracle: Hugging Face's GPT-2 in fp32 on the GPU against this package's bf16
+    kernel path loaded with the same weights: logits, loss and the gradient of the token embedding."""
+    transformers = pytest.importorskip("transformers")
+    from torsh_b200 import hub, models
+    torch.manual_seed(0)
+    hf = transformers.GPT2LMHeadModel(transformers.GPT2Config(vocab_size=1024, n_positions=128, n_embd=256, n_layer=4, n_head=4,
+                                                              resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)).cuda().train()
+    ours = models.create_model("gpt2-tiny")
+    hub.import_hf_gpt2({k: v.cpu() for k, v in hf.state_dict().items()}, ours)
+    ours = ours.cuda().to(torch.bfloat16).train()
+    ids = torch.randint(0, 1024, (4, 129), device="cuda")
+    x, y = ids[:, :-1].contiguous(), ids[:, 1:].contiguous()
+    out = hf(x, labels=None).logits.float()
+    ref_loss = torch.nn.functional.cross_entropy(out.reshape(-1, 1024), y.reshape(-1))
+    ref_loss.backward()
+    logits = ours(x)
+    logits = logits[..., :1024].float()
+    err = (logits - out).abs().max() / out.abs().max()
+    assert err < 3e-2, float(err)
+    loss = ours(x, y)
+    assert abs(float(loss) - float(ref_loss)) < 2e-2 * float(ref_loss)
+    loss.backward()
+    wte = next(p for n, p in ours.named_parameters() if "wte" in n or "tok" in n)
+    g = (wte.main_grad if getattr(wte, "main_grad", None) is not None else wte.grad).float()[:1024]
+    gr = hf.transformer.wte.weight.grad.float()
+    assert ((g - gr).norm() / gr.norm()) < 5e-2
