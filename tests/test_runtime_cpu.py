@@ -314,3 +314,79 @@ def test_multi_stream_orchestrator_plans_and_issues_with_few_events():
         build("round_robin").add("x", deps=("nope",))
     with pytest.raises(ValueError):
         MultiStreamOrchestrator([FakeStream("a")], policy="magic")
+
+
+def test_core_storage_memory_formats_chunking_telemetry_health(tmp_path):
+    import json
+    from torsh_b200.core import storage as S, telemetry as T
+    # memory formats agree with torch's strides
+    shape = (2, 3, 4, 5)
+    assert S.MemoryFormat.CONTIGUOUS.strides(shape) == torch.empty(shape).stride()
+    assert S.MemoryFormat.CHANNELS_LAST.strides(shape) == torch.empty(shape).to(memory_format=torch.channels_last).stride()
+    s5 = (2, 3, 4, 5, 6)
+    assert S.MemoryFormat.CHANNELS_LAST_3D.strides(s5) == torch.empty(s5).to(memory_format=torch.channels_last_3d).stride()
+    assert S.MemoryFormat.of(torch.empty(shape).to(memory_format=torch.channels_last)) is S.MemoryFormat.CHANNELS_LAST
+    assert S.MemoryFormat.of(torch.empty(4, 6).t()) is S.MemoryFormat.STRIDED
+    with pytest.raises(ValueError):
+        S.MemoryFormat.CHANNELS_LAST.strides((2, 3, 4))
+    # storages
+    before = S.registry.total_bytes()
+    st = S.Storage.aligned(1000, torch.float32, alignment=256)
+    assert st.tensor.data_ptr() % 256 == 0 and len(st) == 1000 and S.registry.total_bytes() == before + 4000
+    v = st.view((2, 3, 4, 5), fmt=S.MemoryFormat.CHANNELS_LAST)
+    v.zero_(); v[1, 2, 3, 4] = 7.0
+    assert st.tensor[1 * 60 + 3 * 15 + 4 * 3 + 2] == 7.0 and S.is_aligned(v, 256)      # NHWC position of (n=1, c=2, h=3, w=4)
+    with pytest.raises(ValueError):
+        st.view((40, 40))
+    m = S.Storage.mapped(tmp_path / "w.bin", 16, torch.int32, create=True)
+    m.tensor.copy_(torch.arange(16, dtype=torch.int32)); m.flush()
+    again = S.Storage.mapped(tmp_path / "w.bin", 16, torch.int32)
+    assert again.tensor.tolist() == list(range(16)) and S.registry.info["mapped"].live >= 2
+    assert S.Storage.shared(8).tensor.is_shared()
+    del st
+    import gc; gc.collect()
+    assert S.registry.info["aligned"].peak_bytes >= 4000
+    # chunking
+    cfg = S.TensorChunkConfig(S.ChunkingStrategy.COMPUTE_INTENSIVE)
+    n = cfg.compute_chunk_size(148 * 1024 * 64, 4)
+    assert n % 64 == 0 and len(cfg.chunks(148 * 1024 * 64, 4)) == 148
+    mem = S.TensorChunkConfig(S.ChunkingStrategy.MEMORY_INTENSIVE).compute_chunk_size(1 << 30, 2)
+    assert mem * 2 <= (126 << 20) // 4 and S.TensorChunkConfig(S.ChunkingStrategy.CACHE_FRIENDLY).compute_chunk_size(10, 4) == 10
+    ch = S.TensorChunkConfig(S.ChunkingStrategy.CUSTOM, custom_bytes=4096).chunks(2500, 4)
+    assert ch[0] == (0, 1024) and ch[-1] == (2048, 2500)
+    # telemetry
+    lines = []
+    tel = T.TelemetrySystem(T.TelemetryConfig(min_level=T.LogLevel.INFO, max_events=3, sink=lines.append))
+    assert tel.log(T.LogLevel.DEBUG, "hidden") is None
+    root = tel.start_span("step")
+    with tel.span("forward", parent_id=root) as sid:
+        tel.span_add_attribute(sid, "tokens", 8192)
+        tel.span_add_event(sid, "graph_replay", launches=634)
+        tel.log(T.LogLevel.INFO, "running", module="engine", span_id=sid, step=3)
+    with pytest.raises(ValueError):
+        with tel.span("bad", parent_id=root):
+            raise ValueError("boom")
+    tel.end_span(root)
+    names = [m.name for m in tel.finished]
+    assert names == ["forward", "bad", "step"] and tel.finished[0].parent_id == root and tel.finished[0].attributes["tokens"] == 8192
+    assert tel.finished[0].events[0]["name"] == "graph_replay" and tel.finished[2].duration_s >= tel.finished[0].duration_s
+    rec = json.loads(lines[0])
+    assert rec["level"] == "INFO" and rec["module"] == "engine" and rec["step"] == 3 and rec["span_id"] == sid
+    err = tel.get_events(T.LogLevel.ERROR)[0]
+    assert err.error_code is T.ErrorCode.INVALID_ARGUMENT and json.loads(err.format_structured())["error_code"] == 1001
+    for i in range(5):
+        tel.log(T.LogLevel.WARN, f"w{i}")
+    assert len(tel.events) == 3 and tel.dropped >= 2
+    assert T.ErrorCode.from_exception(FileNotFoundError()) is T.ErrorCode.IO and T.ErrorCode.from_exception(KeyError()) is T.ErrorCode.INTERNAL
+    # health
+    hc = T.HealthChecker()
+    hc.register("store", lambda: True)
+    rep = hc.check_health()
+    assert {c.name for c in rep.checks} == {"host_memory", "device", "kernel_status", "store"} and rep.status.is_operational()
+    hc.register("disk", lambda: (_ for _ in ()).throw(OSError("disk gone")))
+    rep = hc.check_health()
+    assert rep.status is T.HealthStatus.UNHEALTHY and not hc.is_ready() and hc.is_alive() and hc.count == 2
+    bad = rep.failing_checks()
+    assert any(c.name == "disk" and c.error_code is T.ErrorCode.IO for c in bad) and "disk" in rep.summary()
+    js = json.loads(rep.to_json())
+    assert js["http"] == 503 and js["status"] == "unhealthy" and len(js["checks"]) == 5
