@@ -1480,3 +1480,57 @@ def test_video_generative_few_shot_and_3d_models():
     out.sum().backward()
     assert out.shape == (2, 4) and V3.CNN3D()(torch.randn(2, 1, 16, 16, 16)).shape == (2, 10)
     assert torch.isfinite(V3.PointNet().loss(pts, torch.tensor([1, 2])))
+
+
+def test_data_formats_tfrecord_idx_cifar_image_folder(tmp_path):
+    import pickle
+    import numpy as np
+    from torsh_b200.data import formats as F
+    from torsh_b200.vision.io import VisionIO
+    # CRC-32C test vector (RFC 3720) and record round trip with corruption detection
+    assert F.crc32c(b"123456789") == 0xE3069283 and F.crc32c(b"\x00" * 32) == 0x8A9136AA
+    exs = [{"image": b"\x01\x02\x03", "label": [7], "weights": [0.5, -1.25], "name": "a"},
+           {"image": b"", "label": [-3, 1 << 40], "weights": [1e-3], "name": "bb"}]
+    with F.TFRecordWriter(tmp_path / "d.tfrecord") as w:
+        for e in exs:
+            w.write(F.encode_example(e))
+    got = list(F.TFRecordDataset(tmp_path / "d.tfrecord"))
+    assert got[0]["image"] == [b"\x01\x02\x03"] and got[0]["label"] == [7] and got[0]["weights"] == [0.5, -1.25] and got[0]["name"] == [b"a"]
+    assert got[1]["label"] == [-3, 1 << 40] and abs(got[1]["weights"][0] - 1e-3) < 1e-9
+    ds = F.TFRecordDataset([tmp_path / "d.tfrecord"], transform=lambda e: (torch.tensor(e["weights"]), e["label"][0]))
+    assert [y for _, y in ds] == [7, -3]
+    raw = bytearray((tmp_path / "d.tfrecord").read_bytes())
+    raw[14] ^= 0xFF
+    (tmp_path / "bad.tfrecord").write_bytes(bytes(raw))
+    with pytest.raises(ValueError):
+        list(F.read_tfrecords(tmp_path / "bad.tfrecord"))
+    assert len(list(F.read_tfrecords(tmp_path / "bad.tfrecord", verify=False))) == 2
+    # IDX / MNIST layout
+    imgs = (torch.rand(10, 28, 28) * 255).to(torch.uint8)
+    labs = torch.arange(10, dtype=torch.uint8)
+    F.write_idx(tmp_path / "train-images-idx3-ubyte", imgs)
+    F.write_idx(tmp_path / "train-labels-idx1-ubyte", labs)
+    assert torch.equal(F.read_idx(tmp_path / "train-images-idx3-ubyte"), imgs)
+    f32 = torch.randn(3, 4)
+    F.write_idx(tmp_path / "f.idx", f32)
+    assert torch.equal(F.read_idx(tmp_path / "f.idx"), f32)
+    mn = F.MNIST(tmp_path, train=True)
+    x, y = mn[3]
+    assert len(mn) == 10 and x.shape == (1, 28, 28) and y == 3 and torch.allclose(x[0], imgs[3].float() / 255)
+    with pytest.raises(FileNotFoundError):
+        F.MNIST(tmp_path, train=False)
+    # CIFAR python batches
+    for name, n in (("data_batch_1", 6), ("data_batch_2", 4), ("test_batch", 5)):
+        with open(tmp_path / name, "wb") as f:
+            pickle.dump({b"data": np.random.randint(0, 255, (n, 3072), dtype=np.uint8), b"labels": list(range(n))}, f)
+    c10 = F.CIFAR(tmp_path, train=True)
+    assert len(c10) == 10 and c10[7][1] == 1 and c10[0][0].shape == (3, 32, 32) and len(F.CIFAR(tmp_path, train=False)) == 5
+    # image folder
+    io = VisionIO()
+    for c in ("cat", "dog"):
+        (tmp_path / "imgs" / c).mkdir(parents=True)
+        for i in range(2):
+            io.save_image((torch.rand(3, 8, 8) * 255).to(torch.uint8), tmp_path / "imgs" / c / f"{i}.png")
+    (tmp_path / "imgs" / "cat" / "notes.txt").write_text("x")
+    fol = F.ImageFolder(tmp_path / "imgs")
+    assert fol.classes == ["cat", "dog"] and len(fol) == 4 and fol[3][1] == 1 and fol[0][0].shape == (3, 8, 8) and fol[0][0].max() <= 1
