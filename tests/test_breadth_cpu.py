@@ -1534,3 +1534,83 @@ def test_data_formats_tfrecord_idx_cifar_image_folder(tmp_path):
     (tmp_path / "imgs" / "cat" / "notes.txt").write_text("x")
     fol = F.ImageFolder(tmp_path / "imgs")
     assert fol.classes == ["cat", "dog"] and len(fol) == 4 and fol[3][1] == 1 and fol[0][0].shape == (3, 8, 8) and fol[0][0].max() <= 1
+
+
+def test_linalg_equations_matrices_solvers_and_special_functions_against_scipy():
+    import math
+    import numpy as np
+    sp = pytest.importorskip("scipy.special")
+    sl = pytest.importorskip("scipy.linalg")
+    st = pytest.importorskip("scipy.stats")
+    from torsh_b200 import linalg as LA, special_functions as SF
+    torch.manual_seed(0)
+    f64 = torch.float64
+    a, b, c = torch.randn(4, 4, dtype=f64), torch.randn(3, 3, dtype=f64), torch.randn(4, 3, dtype=f64)
+    x = LA.solve_sylvester(a, b, c)
+    assert torch.allclose(a @ x + x @ b, c, atol=1e-8)
+    stable = -torch.eye(4, dtype=f64) * 2 + 0.3 * a
+    q = torch.eye(4, dtype=f64)
+    xl = LA.solve_lyapunov(stable, -q)
+    assert torch.allclose(stable @ xl + xl @ stable.mT, -q, atol=1e-8)
+    ad = 0.4 * a / a.norm()
+    xd = LA.solve_discrete_lyapunov(ad, q)
+    assert torch.allclose(ad @ xd @ ad.mT - xd + q, torch.zeros(4, 4, dtype=f64), atol=1e-9)
+    bb, r = torch.randn(4, 2, dtype=f64), torch.eye(2, dtype=f64)
+    xa = LA.solve_continuous_are(a, bb, q, r)
+    assert np.allclose(xa.numpy(), sl.solve_continuous_are(a.numpy(), bb.numpy(), q.numpy(), r.numpy()), atol=1e-6)
+    spd = a @ a.mT + 4 * torch.eye(4, dtype=f64)
+    assert torch.allclose(LA.sqrtm(spd) @ LA.sqrtm(spd), spd, atol=1e-8) and torch.allclose(torch.linalg.matrix_exp(LA.logm(spd)), spd, atol=1e-8)
+    assert torch.allclose(LA.cosm(spd) @ LA.cosm(spd) + LA.sinm(spd) @ LA.sinm(spd), torch.eye(4, dtype=f64), atol=1e-8)
+    assert torch.allclose(LA.signm(spd), torch.eye(4, dtype=f64), atol=1e-8)
+    u, p = LA.polar(a)
+    assert torch.allclose(u @ p, a, atol=1e-10) and torch.allclose(u @ u.mT, torch.eye(4, dtype=f64), atol=1e-10)
+    assert np.allclose(LA.hilbert(5).numpy(), sl.hilbert(5)) and np.allclose(LA.circulant(torch.arange(4.)).numpy(), sl.circulant(np.arange(4.)))
+    cc, rr = torch.tensor([1., 2., 3.]), torch.tensor([1., 5., 6., 7.])
+    assert np.allclose(LA.toeplitz(cc, rr).numpy(), sl.toeplitz(cc.numpy(), rr.numpy())) and np.allclose(LA.hankel(cc, torch.tensor([3., 8., 9.])).numpy(), sl.hankel(cc.numpy(), [3., 8., 9.]))
+    assert np.allclose(LA.vandermonde(cc).numpy(), np.vander(cc.numpy()))
+    coeffs = torch.tensor([6., -5.], dtype=f64)               # x^2 - 5x + 6 = (x - 2)(x - 3)
+    assert sorted(torch.linalg.eigvals(LA.companion(coeffs)).real.tolist()) == pytest.approx([2.0, 3.0])
+    m = torch.randn(30, 30, dtype=f64) + 8 * torch.eye(30, dtype=f64)
+    rhs = torch.randn(30, dtype=f64)
+    ref = torch.linalg.solve(m, rhs)
+    assert torch.allclose(LA.gmres(m, rhs, restart=15), ref, atol=1e-6) and torch.allclose(LA.bicgstab(lambda v: m @ v, rhs), ref, atol=1e-6)
+    fx = lambda v: (v ** 3).sum()
+    v3 = torch.tensor([1., 2., 3.], dtype=f64)
+    assert torch.allclose(LA.jacobian(fx, v3), 3 * v3 ** 2) and torch.allclose(LA.hessian(fx, v3), torch.diag(6 * v3))
+    rep = LA.condition_report(LA.hilbert(8))
+    assert rep["cond"] > 1e9 and rep["rank"] == 8 and rep["forward_error_bound"] > 1e-7
+    # special functions against scipy
+    mm = torch.tensor([0.0, 0.3, 0.7, 0.95], dtype=f64)
+    assert np.allclose(SF.ellipk(mm).numpy(), sp.ellipk(mm.numpy()), rtol=1e-10) and np.allclose(SF.ellipe(mm).numpy(), sp.ellipe(mm.numpy()), rtol=1e-10)
+    ph = torch.tensor([0.2, 0.9, 1.4], dtype=f64)
+    assert np.allclose(SF.ellipkinc(ph, 0.6).numpy(), sp.ellipkinc(ph.numpy(), 0.6), rtol=1e-9) and np.allclose(SF.ellipeinc(ph, 0.6).numpy(), sp.ellipeinc(ph.numpy(), 0.6), rtol=1e-9)
+    xw = torch.tensor([-0.36, -0.2, 0.0, 0.5, 3.0, 100.0], dtype=f64)
+    assert np.allclose(SF.lambertw(xw).numpy(), sp.lambertw(xw.numpy()).real, rtol=1e-9, atol=1e-12)
+    xm = torch.tensor([-0.36, -0.2, -0.01], dtype=f64)
+    assert np.allclose(SF.lambertw(xm, -1).numpy(), sp.lambertw(xm.numpy(), -1).real, rtol=1e-9)
+    assert torch.isnan(SF.lambertw(torch.tensor(-1.0)))
+    xe = torch.tensor([0.05, 0.7, 1.0, 2.5, 12.0], dtype=f64)
+    assert np.allclose(SF.exp1(xe).numpy(), sp.exp1(xe.numpy()), rtol=1e-9) and np.allclose(SF.expi(xe).numpy(), sp.expi(xe.numpy()), rtol=1e-9)
+    assert np.allclose(SF.expn(3, xe).numpy(), sp.expn(3, xe.numpy()), rtol=1e-8)
+    xo = torch.linspace(-0.95, 0.95, 7, dtype=f64)
+    assert np.allclose(SF.legendre(5, xo).numpy(), sp.eval_legendre(5, xo.numpy())) and np.allclose(SF.chebyshev_t(6, xo).numpy(), sp.eval_chebyt(6, xo.numpy()))
+    assert np.allclose(SF.chebyshev_u(4, xo).numpy(), sp.eval_chebyu(4, xo.numpy())) and np.allclose(SF.hermite(5, xo).numpy(), sp.eval_hermite(5, xo.numpy()))
+    assert np.allclose(SF.laguerre(4, xo + 2, 0.5).numpy(), sp.eval_genlaguerre(4, 0.5, xo.numpy() + 2)) and np.allclose(SF.gegenbauer(3, 1.5, xo).numpy(), sp.eval_gegenbauer(3, 1.5, xo.numpy()))
+    assert np.allclose(SF.hyp1f1(1.5, 2.5, xo * 3).numpy(), sp.hyp1f1(1.5, 2.5, xo.numpy() * 3), rtol=1e-10)
+    assert np.allclose(SF.hyp2f1(0.5, 1.0, 1.5, xo * 0.9).numpy(), sp.hyp2f1(0.5, 1.0, 1.5, xo.numpy() * 0.9), rtol=1e-9)
+    xa_ = torch.tensor([-4.0, -1.0, 0.0, 0.5, 2.0, 4.5], dtype=f64)
+    ai, bi = SF.airy(xa_)
+    ref_ai, _, ref_bi, _ = sp.airy(xa_.numpy())
+    assert np.allclose(ai.numpy(), ref_ai, rtol=1e-7, atol=1e-10) and np.allclose(bi.numpy(), ref_bi, rtol=1e-7)
+    far = torch.tensor([8.0, -9.0], dtype=f64)
+    assert np.allclose(SF.airy(far)[0].numpy(), sp.airy(far.numpy())[0], rtol=2e-3, atol=1e-4)
+    xb = torch.tensor([0.0, 0.1, 0.5, 0.9, 1.0], dtype=f64)
+    assert np.allclose(SF.betainc(2.5, 1.5, xb).numpy(), sp.betainc(2.5, 1.5, xb.numpy()), atol=1e-10)
+    tt = torch.tensor([-2.0, 0.0, 0.7, 3.0], dtype=f64)
+    assert np.allclose(SF.student_t_cdf(tt, 5.0).numpy(), st.t.cdf(tt.numpy(), 5), atol=1e-9) and np.allclose(SF.norm_cdf(tt).numpy(), st.norm.cdf(tt.numpy()))
+    assert np.allclose(SF.norm_ppf(torch.tensor([0.025, 0.5, 0.9])).numpy(), st.norm.ppf([0.025, 0.5, 0.9]), atol=1e-9)
+    assert np.allclose(SF.chi2_cdf(torch.tensor([1.0, 4.0]), 3.0).numpy(), st.chi2.cdf([1.0, 4.0], 3), atol=1e-9)
+    assert np.allclose(SF.f_cdf(torch.tensor([0.5, 2.0]), 4.0, 7.0).numpy(), st.f.cdf([0.5, 2.0], 4, 7), atol=1e-9)
+    assert np.allclose(SF.binom_cdf(torch.tensor([2.0, 5.0, 10.0]), 10.0, 0.3).numpy(), st.binom.cdf([2, 5, 10], 10, 0.3), atol=1e-9)
+    xf = torch.linspace(-6, 6, 101)
+    assert (SF.fast_tanh(xf) - torch.tanh(xf)).abs().max() < 1e-3 and ((SF.fast_exp(xf) - torch.exp(xf)).abs() / torch.exp(xf)).max() < 5e-3
