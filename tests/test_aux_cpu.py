@@ -688,3 +688,46 @@ def test_kernel_generator_emits_compilable_source_and_portable_results(tmp_path,
     assert sel.choose("k", 1 << 20, lambda name: name) == "t256_u2" and "k|2^20" in sel.tuner.table
     with pytest.raises(ValueError):
         kg.Expr._wrap(float("inf")).code("j")
+
+
+def test_package_versions_requirements_resolver_lock_and_manifest_migration():
+    from torsh_b200 import package_resolver as R
+    V = R.Version.parse
+    assert V("1.2.3") < V("1.10.0") and V("1.0.0-rc.1") < V("1.0.0") and V("1.0.0-alpha") < V("1.0.0-beta") and V("v2") == R.Version(2)
+    assert V("1.0.0-rc.2") < V("1.0.0-rc.10") and str(V("0.3.1-dev.4")) == "0.3.1-dev.4"
+    with pytest.raises(ValueError):
+        V("one.two")
+    ok = lambda spec, v: R.Requirement(spec).matches(V(v))
+    assert ok("^1.2.3", "1.9.0") and not ok("^1.2.3", "2.0.0") and not ok("^1.2.3", "1.2.2")
+    assert ok("^0.2.3", "0.2.9") and not ok("^0.2.3", "0.3.0") and ok("^0.0.3", "0.0.3") and not ok("^0.0.3", "0.0.4")
+    assert ok("~1.2.3", "1.2.9") and not ok("~1.2.3", "1.3.0") and ok("~1", "1.9.9") and ok("1.2", "1.5.0") and not ok("1.2", "2.0.0")
+    assert ok(">=1.0, <2.0", "1.5.0") and not ok(">=1.0, <2.0", "2.0.0") and ok("*", "9.9.9") and ok("==1.4.0", "1.4.0") and not ok("=1.4.0", "1.4.1")
+    assert not ok("^1.0", "1.1.0-rc.1") and ok(">=1.1.0-rc.1", "1.1.0-rc.2")
+    idx = R.PackageIndex({
+        "vision": {"1.0.0": {"core": "^1.0"}, "1.1.0": {"core": "^1.2"}, "2.0.0": {"core": "^2.0"}},
+        "text": {"0.9.0": {"core": ">=1.0, <1.3"}, "1.0.0": {"core": "^1.3", "tokenizers": "~0.4"}},
+        "tokenizers": {"0.4.2": {}, "0.5.0": {}},
+        "core": {"1.0.0": {}, "1.2.5": {}, "1.3.0": {}, "2.0.0": {}},
+    })
+    sol = R.resolve(idx, {"vision": "^1", "text": "*"})
+    assert sol == {"core": "1.3.0", "text": "1.0.0", "tokenizers": "0.4.2", "vision": "1.1.0"}
+    # a pin on core forces backtracking to older releases of both dependants
+    sol2 = R.resolve(idx, {"vision": "^1", "text": "*", "core": "<1.3"})
+    assert sol2 == {"core": "1.2.5", "text": "0.9.0", "vision": "1.1.0"}
+    with pytest.raises(R.ResolutionError) as ei:
+        R.resolve(idx, {"vision": "^2", "text": "*"})
+    assert "core" in str(ei.value)
+    with pytest.raises(R.ResolutionError) as ei:
+        R.resolve(idx, {"audio": "*"})
+    assert "unknown package 'audio'" in str(ei.value)
+    lock = R.write_lock(sol, idx)
+    assert R.check_lock(lock, idx, {"vision": "^1", "text": "*"}) == []
+    assert any("violates the root requirement" in p for p in R.check_lock(lock, idx, {"vision": "^2", "text": "*"}))
+    del idx.releases["tokenizers"][V("0.4.2")]
+    assert any("no longer in the index" in p for p in R.check_lock(lock, idx, {"vision": "^1", "text": "*"}))
+    old = {"name": "m", "version": "0.3.0", "dependencies": ["core==1.2.5", "text"], "format": 1}
+    new = R.migrate_manifest(old)
+    assert new["format"] == 2 and new["dependencies"] == {"core": "==1.2.5", "text": "*"} and new["requires_torsh"] == "*" and old["format"] == 1
+    assert R.migrate_manifest(new) == new
+    with pytest.raises(ValueError):
+        R.migrate_manifest({"name": "x", "format": 9})
