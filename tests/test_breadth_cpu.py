@@ -1614,3 +1614,48 @@ def test_linalg_equations_matrices_solvers_and_special_functions_against_scipy()
     assert np.allclose(SF.binom_cdf(torch.tensor([2.0, 5.0, 10.0]), 10.0, 0.3).numpy(), st.binom.cdf([2, 5, 10], 10, 0.3), atol=1e-9)
     xf = torch.linspace(-6, 6, 101)
     assert (SF.fast_tanh(xf) - torch.tanh(xf)).abs().max() < 1e-3 and ((SF.fast_exp(xf) - torch.exp(xf)).abs() / torch.exp(xf)).max() < 5e-3
+
+
+def test_onnx_export_import_round_trip(tmp_path):
+    """Export by hand-written protobuf, parse back, evaluate: same outputs as the PyTorch module (MLP on 3-D input,
+    CNN with BatchNorm / pooling, embedding classifier with functional ops)."""
+    from torsh_b200 import onnx_io as O
+    torch.manual_seed(0)
+
+    class MLP(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.ln, self.fc1, self.act, self.fc2 = torch.nn.LayerNorm(16), torch.nn.Linear(16, 32), torch.nn.GELU(approximate="tanh"), torch.nn.Linear(32, 8, bias=False)
+
+        def forward(self, x):
+            h = self.fc2(self.act(self.fc1(self.ln(x))))
+            return torch.softmax(h + h.transpose(1, 2).contiguous().transpose(1, 2) * 0.5, dim=-1)
+    m = MLP()
+    x = torch.randn(3, 5, 16)
+    data = O.export_onnx(m, x, tmp_path / "mlp.onnx")
+    back = O.load_onnx(tmp_path / "mlp.onnx")
+    assert back.opset == 20 and back.producer == "torsh_b200" and back.input_names == ["x"]
+    assert {"LayerNormalization", "MatMul", "Gelu", "Transpose", "Softmax"} <= set(back.op_types())
+    assert torch.allclose(back(x), m.eval()(x), atol=1e-6)
+    assert torch.allclose(back(torch.randn(7, 5, 16)).sum(-1), torch.ones(7, 5), atol=1e-5)        # the batch dimension is dynamic
+    cnn = torch.nn.Sequential(torch.nn.Conv2d(3, 8, 3, stride=2, padding=1), torch.nn.BatchNorm2d(8), torch.nn.ReLU(), torch.nn.MaxPool2d(2),
+                              torch.nn.Conv2d(8, 8, 3, padding=1, groups=2, bias=False), torch.nn.SiLU(), torch.nn.AdaptiveAvgPool2d(1),
+                              torch.nn.Flatten(), torch.nn.Dropout(0.5), torch.nn.Linear(8, 4))
+    cnn[1].running_mean.normal_(); cnn[1].running_var.uniform_(0.5, 2.0)
+    img = torch.randn(2, 3, 16, 16)
+    back2 = O.load_onnx(O.export_onnx(cnn, img))
+    assert torch.allclose(back2(img), cnn.eval()(img), atol=1e-5) and "Gemm" in back2.op_types() and "BatchNormalization" in back2.op_types()
+
+    class Emb(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb, self.out = torch.nn.Embedding(50, 12), torch.nn.Linear(48, 3)
+
+        def forward(self, ids):
+            return self.out(torch.tanh(self.emb(ids)).reshape(-1, 48))
+    e = Emb()
+    ids = torch.randint(0, 50, (6, 4))
+    back4 = O.load_onnx(O.export_onnx(e, ids))
+    assert "Gather" in back4.op_types() and torch.allclose(back4(ids), e(ids), atol=1e-6)
+    with pytest.raises(NotImplementedError):
+        O.export_onnx(torch.nn.Sequential(torch.nn.LSTM(4, 4)), torch.randn(2, 3, 4))
