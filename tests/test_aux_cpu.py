@@ -731,3 +731,85 @@ def test_package_versions_requirements_resolver_lock_and_manifest_migration():
     assert R.migrate_manifest(new) == new
     with pytest.raises(ValueError):
         R.migrate_manifest({"name": "x", "format": 9})
+
+
+def test_extended_metrics_against_sklearn_and_scipy():
+    import math
+    skm = pytest.importorskip("sklearn.metrics")
+    sst = pytest.importorskip("scipy.stats")
+    from torsh_b200.utils import metrics_ext as M
+    torch.manual_seed(0)
+    y = torch.randint(0, 4, (300,))
+    p = torch.where(torch.rand(300) < 0.7, y, torch.randint(0, 4, (300,)))
+    assert M.matthews_corrcoef(p, y) == pytest.approx(skm.matthews_corrcoef(y.numpy(), p.numpy()), abs=1e-9)
+    assert M.cohen_kappa(p, y) == pytest.approx(skm.cohen_kappa_score(y.numpy(), p.numpy()), abs=1e-9)
+    assert M.balanced_accuracy(p, y) == pytest.approx(skm.balanced_accuracy_score(y.numpy(), p.numpy()), abs=1e-9)
+    yb = (torch.rand(200) < 0.3).long()
+    s = (yb.float() * 0.3 + torch.rand(200) * 0.7).round(decimals=2)        # ties included
+    assert M.average_precision(s, yb) == pytest.approx(skm.average_precision_score(yb.numpy(), s.numpy()), abs=1e-9)
+    pr = torch.softmax(torch.randn(300, 4), -1)
+    assert M.log_loss(pr, y) == pytest.approx(skm.log_loss(y.numpy(), pr.numpy(), labels=[0, 1, 2, 3]), abs=1e-6)
+    assert M.log_loss(s.clamp(0.01, 0.99), yb) == pytest.approx(skm.log_loss(yb.numpy(), s.clamp(0.01, 0.99).numpy()), abs=1e-6)
+    assert M.brier_score(s, yb) == pytest.approx(skm.brier_score_loss(yb.numpy(), s.numpy()), abs=1e-6)
+    rel = torch.tensor([0, 1, 0, 1, 1, 0])
+    assert M.precision_at_k(rel, 3) == pytest.approx(1 / 3) and M.recall_at_k(rel, 4) == pytest.approx(2 / 3) and M.hit_rate_at_k(rel, 1) == 0.0
+    assert M.reciprocal_rank(rel) == 0.5 and M.mean_reciprocal_rank([rel, torch.tensor([1, 0]), torch.tensor([0, 0])]) == pytest.approx(0.5)
+    assert M.average_precision_at_k(rel) == pytest.approx((1 / 2 + 2 / 4 + 3 / 5) / 3) and M.mean_average_precision([rel, torch.zeros(3)]) == pytest.approx(M.average_precision_at_k(rel) / 2)
+    t = torch.randn(100) * 3 + 5
+    pd = t + 0.3 * torch.randn(100)
+    assert M.explained_variance(pd, t) == pytest.approx(skm.explained_variance_score(t.numpy(), pd.numpy()), abs=1e-6)
+    assert M.mape(pd, t) == pytest.approx(skm.mean_absolute_percentage_error(t.numpy(), pd.numpy()), rel=1e-6)
+    r2 = skm.r2_score(t.numpy(), pd.numpy())
+    assert M.adjusted_r2(pd, t, 3) == pytest.approx(1 - (1 - r2) * 99 / 96, abs=1e-6) and 0 < M.smape(pd, t) < 0.2
+    diag = M.residual_diagnostics(pd, t)
+    assert 1.0 < diag["durbin_watson"] < 3.0 and abs(diag["skewness"]) < 1 and diag["std"] == pytest.approx(0.3, rel=0.3)
+    conf = torch.tensor([0.95, 0.9, 0.85, 0.6, 0.55, 0.52])
+    corr = torch.tensor([1, 1, 1, 1, 0, 0])
+    assert M.calibration_error(conf, corr, n_bins=2) == pytest.approx(abs(4 / 6 - 4.37 / 6), abs=1e-6)       # all six fall in the upper bin: accuracy 4/6 against mean confidence 4.37/6
+    assert M.calibration_error(conf, corr, n_bins=10, norm="max") >= M.calibration_error(conf, corr, n_bins=10)
+    lo, hi = t - 1, t + 1
+    assert M.interval_coverage(lo, hi, pd) > 0.95 and M.interval_sharpness(lo, hi) == pytest.approx(2.0)
+    assert M.gaussian_nll(t, torch.ones(100), t) == pytest.approx(0.5 * math.log(2 * math.pi))
+    mc = torch.softmax(torch.randn(8, 5, 3), -1)
+    assert (M.mutual_information(mc) >= -1e-9).all() and torch.allclose(M.mutual_information(mc[:1].expand(8, 5, 3)), torch.zeros(5, dtype=torch.float64), atol=1e-9)
+    train = torch.arange(20.)
+    assert M.mase(torch.tensor([21., 22.]), torch.tensor([20., 21.]), train) == pytest.approx(1.0)
+    assert M.directional_accuracy(torch.tensor([1., 2., 1.]), torch.tensor([1., 2., 3.])) == 0.5 and M.theil_u(t, t) == 0.0
+    assert M.aic(-10.0, 3) == 26.0 and M.bic(-10.0, 3, 100) == pytest.approx(3 * math.log(100) + 20)
+    folds = M.k_fold_indices(10, 3)
+    assert [len(v) for _, v in folds] == [4, 3, 3] and sorted(torch.cat([v for _, v in folds]).tolist()) == list(range(10))
+    sf = M.stratified_k_fold_indices(torch.tensor([0] * 6 + [1] * 3), 3)
+    assert all(sorted(torch.tensor([0] * 6 + [1] * 3)[v].tolist()) == [0, 0, 1] for _, v in sf)
+    a, b = torch.randn(500, 6), torch.randn(500, 6) + 0.5
+    assert M.frechet_distance(a, a) == pytest.approx(0.0, abs=1e-6) and 1.0 < M.frechet_distance(a, b) < 2.2
+    assert M.inception_score(torch.eye(4)) == pytest.approx(4.0, rel=1e-6) and M.inception_score(torch.full((5, 4), 0.25)) == pytest.approx(1.0)
+    rm, parts = M.RunningMoments(), torch.randn(1000).split(137)
+    for part in parts:
+        rm.update(part)
+    allv = torch.cat(parts).double()
+    assert rm.n == 1000 and rm.mean == pytest.approx(float(allv.mean()), abs=1e-12) and rm.variance == pytest.approx(float(allv.var()), rel=1e-10)
+    merged = M.RunningMoments().update(parts[0]).merge(M.RunningMoments().update(torch.cat(parts[1:])))
+    assert merged.variance == pytest.approx(rm.variance, rel=1e-10)
+    sc = M.StreamingConfusion(4)
+    for i in range(0, 300, 64):
+        sc.update(p[i:i + 64], y[i:i + 64])
+    assert sc.accuracy() == pytest.approx(float((p == y).float().mean())) and sc.f1_macro() == pytest.approx(skm.f1_score(y.numpy(), p.numpy(), average="macro"), abs=1e-9)
+    sa = M.StreamingAUC(4096)
+    for i in range(0, 200, 50):
+        sa.update(s[i:i + 50], yb[i:i + 50])
+    assert sa.compute() == pytest.approx(skm.roc_auc_score(yb.numpy(), s.numpy()), abs=2e-3)
+    x1, x2 = torch.randn(40) + 0.4, torch.randn(40)
+    tt = M.paired_t_test(x1, x2)
+    ref = sst.ttest_rel(x1.numpy(), x2.numpy())
+    assert tt["t"] == pytest.approx(ref.statistic, rel=1e-6) and tt["p_value"] == pytest.approx(ref.pvalue, rel=1e-5)
+    ca, cb = torch.rand(200) < 0.8, torch.rand(200) < 0.7
+    mc_ = M.mcnemar_test(ca, cb)
+    assert mc_["statistic"] == pytest.approx((abs(mc_["b"] - mc_["c"]) - 1) ** 2 / (mc_["b"] + mc_["c"])) and 0 <= mc_["p_value"] <= 1
+    wx = M.wilcoxon_signed_rank(x1, x2)
+    refw = sst.wilcoxon(x1.numpy(), x2.numpy(), correction=False, mode="approx")
+    assert wx["statistic"] == pytest.approx(refw.statistic) and wx["p_value"] == pytest.approx(refw.pvalue, rel=1e-6)
+    lo_, hi_ = M.bootstrap_ci(x1, n_boot=1000)
+    assert lo_ < float(x1.mean()) < hi_ and hi_ - lo_ < 1.0
+    assert M.permutation_test(torch.randn(30) + 2, torch.randn(30), n_perm=500) < 0.01 and M.permutation_test(x2, x2.flip(0), n_perm=200) > 0.5
+    scorer = M.make_scorer(lambda pr_, y_: (pr_ == y_).float().mean())
+    assert scorer(lambda X: torch.nn.functional.one_hot(X, 4).float(), y, y) == 1.0
