@@ -1659,3 +1659,53 @@ def test_onnx_export_import_round_trip(tmp_path):
     assert "Gather" in back4.op_types() and torch.allclose(back4(ids), e(ids), atol=1e-6)
     with pytest.raises(NotImplementedError):
         O.export_onnx(torch.nn.Sequential(torch.nn.LSTM(4, 4)), torch.randn(2, 3, 4))
+
+
+def test_series_utilities_changepoints_frequency_and_forecasts():
+    import math
+    from torsh_b200 import series as S
+    torch.manual_seed(0)
+    f64 = torch.float64
+    x = torch.arange(30, dtype=f64) ** 2
+    assert torch.allclose(S.difference(x, 2), torch.full((28,), 2.0, dtype=f64)) and torch.allclose(S.undifference(S.difference(x), x[:1]), x)
+    sx = torch.arange(24, dtype=f64) % 4 + torch.arange(24, dtype=f64)
+    assert torch.allclose(S.undifference(S.difference(sx, 1, 4), sx[:4], 4), sx)
+    # AR(1) with phi = 0.7: acf decays geometrically, pacf cuts off after lag 1
+    e = torch.randn(4000, dtype=f64)
+    ar = torch.zeros(4000, dtype=f64)
+    for t in range(1, 4000):
+        ar[t] = 0.7 * ar[t - 1] + e[t]
+    a, pa = S.acf(ar, 3), S.pacf(ar, 3)
+    assert a[0] == 1 and abs(a[1] - 0.7) < 0.05 and abs(a[2] - 0.49) < 0.07 and abs(pa[1] - 0.7) < 0.05 and abs(pa[2]) < 0.06 and abs(pa[3]) < 0.06
+    t = torch.arange(512, dtype=f64)
+    wave = torch.sin(2 * math.pi * t / 16) + 0.1 * torch.randn(512, dtype=f64)
+    assert S.dominant_period(wave) == pytest.approx(16.0, rel=0.02) and S.spectral_entropy(wave) < 0.5 < S.spectral_entropy(torch.randn(512, dtype=f64))
+    freqs, p = S.periodogram(wave, fs=1.0)
+    assert float(p.sum() * (freqs[1] - freqs[0])) == pytest.approx(float(wave.var(unbiased=False)), rel=0.05)       # Parseval
+    steps = torch.cat([torch.zeros(60), torch.full((50,), 4.0), torch.full((70,), -2.0)]).double() + 0.3 * torch.randn(180, dtype=f64)
+    cps = S.binary_segmentation(steps, max_changes=4)
+    assert len(cps) == 2 and abs(cps[0] - 60) <= 2 and abs(cps[1] - 110) <= 2 and S.binary_segmentation(0.3 * torch.randn(150, dtype=f64)) == []
+    drift = torch.cat([torch.zeros(100), torch.full((100,), 2.0)]).double() + 0.5 * torch.randn(200, dtype=f64)
+    alarms = S.cusum(drift, threshold=6.0, drift=0.5)
+    assert alarms and S.cusum(0.5 * torch.randn(200, dtype=f64), threshold=8.0, drift=0.5) == []
+    seas = torch.tensor([1., 5., 2., 8.] * 5)
+    assert S.seasonal_naive(seas, 6, 4).tolist() == [1., 5., 2., 8., 1., 5.]
+    assert float(S.simple_exp_smoothing(torch.full((10,), 3.0), 0.3)[0]) == pytest.approx(3.0)
+    line = 2.0 * torch.arange(40, dtype=f64) + 5
+    th = S.theta_forecast(line, 3)
+    assert abs(float(th[0]) - 85.0) < 3.0 and torch.allclose(th[1:] - th[:-1], torch.ones(2, dtype=f64))   # half the slope: the other half sits in the flat SES line
+    m = S.fit_arima(ar, (1, 0, 0))
+    assert abs(float(m.ar[0]) - 0.7) < 0.05 and abs(m.sigma2 - 1.0) < 0.1
+    fc = S.forecast_arima(m, 5)
+    assert float(fc[0]) == pytest.approx(m.const + float(m.ar[0]) * float(ar[-1]), rel=1e-9) and abs(float(fc[-1])) < abs(float(ar[-1])) + 1
+    ma = e[1:] + 0.6 * e[:-1]
+    m2 = S.fit_arima(ma, (0, 0, 1))
+    assert abs(float(m2.ma[0]) - 0.6) < 0.08
+    rw = (0.5 + torch.randn(600, dtype=f64) * 0.1).cumsum(0)
+    m3 = S.fit_arima(rw, (0, 1, 0))
+    f3 = S.forecast_arima(m3, 4)
+    assert m3.const == pytest.approx(0.5, abs=0.02) and torch.allclose(f3, rw[-1] + m3.const * torch.arange(1, 5, dtype=f64), atol=1e-9)
+    spiky = wave.clone(); spiky[100] += 6; spiky[300] -= 6
+    flags = S.anomaly_seasonal_residual(spiky, 16, z=5.0)
+    assert flags[100] and flags[300] and int(flags.sum()) <= 6
+    assert S.anomaly_iqr(torch.cat([torch.randn(200), torch.tensor([15.0])]))[-1]
