@@ -269,6 +269,14 @@ class PipelineParallel:
         stash: dict[int, tuple] = {}
         losses = []
         pending: list = []  # sends not yet posted: (tensor, dst, tag)
+        timing = self.cfg.measure_idle and self.device.type == "cuda"
+        marks = []
+
+        def mark():
+            if timing:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                return e
 
         def needs_recv(action):
             kind, _ = action
@@ -282,6 +290,7 @@ class PipelineParallel:
                     x = self._exchange(pending, self.prev, self.cfg.base_tag + mb).requires_grad_(True)
                 if self.micro_batch_hook is not None:
                     self.micro_batch_hook(mb, mb % max(self.num_stages, 1))
+                e0 = mark()
                 out = self.module(x)
                 if last:
                     loss = loss_fn(out, ys[mb]) / M if loss_fn is not None else out.mean() / M
@@ -290,19 +299,26 @@ class PipelineParallel:
                 else:
                     pending.append((out.detach().contiguous(), self.next, self.cfg.base_tag + mb))
                     stash[mb] = (x, out)
+                e1 = mark()
             else:
                 x, out = stash.pop(mb)
                 if last:
+                    e0 = mark()
                     out.backward()
                 else:
                     g = self._exchange(pending, self.next, self.cfg.base_tag + 10000 + mb)
+                    e0 = mark()
                     torch.autograd.backward(out, g)
                 if not first:
                     pending.append((x.grad.contiguous(), self.prev, self.cfg.base_tag + 10000 + mb))
+                e1 = mark()
+            if timing:
+                marks.append((e0, e1))
             # a send waits for the next action's receive (they travel as one batch); if the next action
             # receives nothing, post it now
             if pending and (i + 1 == len(actions) or not needs_recv(actions[i + 1])):
                 self._exchange(pending, None)
+        self._marks = marks
         return torch.stack(losses).mean() if losses else None
 
 
