@@ -1709,3 +1709,98 @@ def test_series_utilities_changepoints_frequency_and_forecasts():
     flags = S.anomaly_seasonal_residual(spiky, 16, z=5.0)
     assert flags[100] and flags[300] and int(flags.sum()) <= 6
     assert S.anomaly_iqr(torch.cat([torch.randn(200), torch.tensor([15.0])]))[-1]
+
+
+def _softclip_for_jit_test(t):
+    return 3.0 * torch.tanh(t / 3.0)
+
+
+torch.fx.wrap("_softclip_for_jit_test")       # traced as one call node, which the custom-op rule below picks up
+
+
+def test_jit_compiler_lowering_fusion_specialisation_debugger_and_custom_ops():
+    from torsh_b200 import jit_compiler as J
+    torch.manual_seed(0)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc = torch.nn.Linear(16, 16)
+            self.act = torch.nn.SiLU()
+            self.two = torch.nn.Parameter(torch.tensor(2.0), requires_grad=False)     # a parameter stays a graph node (buffers are folded by the tracer)
+
+        def forward(self, x, y):
+            h = self.fc(x)
+            z = torch.tanh(h) * y + self.act(h) - 0.5            # one element-wise region of five ops
+            dead = torch.exp(z)                                   # noqa: F841  unused: removed
+            scale = torch.sqrt(self.two * 8.0)                    # constant: folded to 4
+            return torch.relu(z / scale).sum(-1)
+    net = Net()
+    x, y = torch.randn(4, 16), torch.randn(4, 16)
+    gm = J.trace_with_source(net)
+    g = J.lower_fx(gm, (x, y))
+    assert any(n.op == "ew:tanh" for n in g.nodes) and any(n.op == "call" for n in g.nodes)
+    tanh = next(n for n in g.nodes if n.op == "ew:tanh")
+    assert tanh.shape == (4, 16) and tanh.dtype == torch.float32 and "test_breadth_cpu.py" in tanh.source
+    assert J.constant_evaluation(g) == 2 and J.dead_code_elimination(g) >= 1 and not any(n.op == "ew:exp" for n in g.nodes)
+    assert J.fuse_elementwise(g) == 1
+    fused = [n for n in g.nodes if n.op == "fused"]
+    assert len(fused) == 1 and fused[0].fused_ops >= 6 and len(fused[0].inputs) == 2 and "fused" in g.to_text() and "lightblue" in g.to_dot()
+    exe = J.Executable(g)
+    assert torch.allclose(exe(x, y), net(x, y), atol=1e-6)
+    # tiered + specialised
+    jf = J.jit(net, hot_threshold=2)
+    for _ in range(4):
+        out = jf(x, y)
+    assert torch.allclose(out, net(x, y), atol=1e-6) and jf.stats.interpreted == 2 and jf.stats.compiled_calls == 2 and jf.stats.specializations == 1
+    x8, y8 = torch.randn(8, 16), torch.randn(8, 16)
+    for _ in range(3):
+        out8 = jf(x8, y8)
+    assert jf.stats.specializations == 2 and torch.allclose(out8, net(x8, y8), atol=1e-6) and jf.graph_for(x8, y8).nodes[0].shape == (8, 16)
+    assert jf.stats.fused_regions == 2 and jf.stats.ops_fused >= 12
+
+    def branchy(a):
+        return a * 2 if a.sum() > 0 else a - 1                     # data-dependent control flow cannot be traced
+    jb = J.jit(branchy, hot_threshold=0)
+    v = torch.ones(3)
+    assert torch.equal(jb(v), v * 2) and torch.equal(jb(-v), -v - 1) and jb.stats.specializations == 0 and jb.errors
+    # debugger: breakpoints, watch statistics, first NaN with its source line
+    def bad(a):
+        b = torch.log(a - 1.0)
+        return torch.relu(b) + 1.0
+    gb = J.lower_fx(J.trace_with_source(bad), (torch.ones(3),))
+    dbg = J.Debugger(J.Executable(gb))
+    dbg.add_breakpoint("ew:log")
+    dbg.run(torch.tensor([3.0, 0.5, 2.0]))
+    assert len(dbg.hits) == 1 and dbg.hits[0][1] == "ew:log" and torch.isnan(dbg.hits[0][2][1])
+    fb = dbg.first_bad_node()
+    assert fb["op"] == "ew:log" and fb["nan"] == 1 and "test_breadth_cpu.py" in fb["source"]
+    # diagnostics point at the node
+    def mism(a, b):
+        return torch.matmul(a, b)
+    gm2 = J.lower_fx(J.trace_with_source(mism), (torch.ones(2, 3), torch.ones(3, 2)))
+    with pytest.raises(J.CompileError) as ei:
+        J.Executable(gm2)(torch.ones(2, 3), torch.ones(4, 2))
+    assert "matmul" in str(ei.value) and "node %" in str(ei.value)
+    # custom operator joining a fused region, plus a plugin pass
+    import torsh_b200.jit_compiler as jc
+
+    softclip = _softclip_for_jit_test
+    jc.registry.register_op(jc.CustomOp("softclip", evaluate=softclip, match=lambda n: n.op == "call_function" and getattr(n.target, "__name__", "") == "_softclip_for_jit_test",
+                                        elementwise_expr=lambda t: 3.0 * jc.kg.tanh(t / 3.0)))
+    seen = []
+    jc.registry.register_pass(lambda graph: seen.append([n.op for n in graph.nodes]) or 0)
+
+    class M2(torch.nn.Module):
+        def forward(self, a, b):
+            return _softclip_for_jit_test(torch.sigmoid(a) * b) + b
+    try:
+        j2 = jc.jit(M2(), hot_threshold=0)
+        a, b = torch.randn(5, 7), torch.randn(5, 7)
+        assert torch.allclose(j2(a, b), softclip(torch.sigmoid(a) * b) + b, atol=1e-6) and seen
+        assert j2.stats.specializations == 1
+        ops = seen[-1]
+        assert "fused" in ops and not any(o.startswith("custom:") for o in ops)            # the custom op was fused with its neighbours
+    finally:
+        jc.registry.passes.clear()
+        jc.registry.ops.clear()
