@@ -653,3 +653,27 @@ def test_gemm_measured_tile_selection():
         assert len(tuner.table) == n                       # second call: table hit, no new measurement
     finally:
         G.gemm_autotune(False)
+
+
+def test_jit_compiler_runs_fused_regions_as_generated_kernels(tmp_path_factory, monkeypatch):
+    from torsh_b200 import jit_compiler as J
+    monkeypatch.setenv("TORSH_JIT_DIR", str(tmp_path_factory.getbasetemp() / "jit"))
+    torch.manual_seed(0)
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc = torch.nn.Linear(256, 256)
+
+        def forward(self, x, y):
+            h = self.fc(x)
+            return (torch.tanh(h) * y + torch.nn.functional.silu(h) - 0.5).sum(-1)
+    net = Net().to(DEV).to(torch.bfloat16)
+    x, y = (torch.randn(512, 256, device=DEV, dtype=torch.bfloat16) for _ in range(2))
+    jf = J.jit(net, hot_threshold=1)
+    outs = [jf(x, y) for _ in range(3)]
+    assert jf.stats.specializations == 1 and jf.stats.fused_regions == 1 and jf.stats.compiled_calls == 2
+    exe = jf.cache[jf.signature((x, y))]
+    assert any(k._libs for k in exe._kernels.values())                    # a generated library was loaded and launched
+    ref = net(x, y).float()
+    assert _rel(outs[-1], ref) < 2e-2
