@@ -1804,3 +1804,111 @@ def test_jit_compiler_lowering_fusion_specialisation_debugger_and_custom_ops():
     finally:
         jc.registry.passes.clear()
         jc.registry.ops.clear()
+
+
+def test_autograd_transforms_implicit_ode_discrete_symbolic_and_analysis():
+    import math
+    from torsh_b200.autograd import transforms as T
+    torch.manual_seed(0)
+    f64 = torch.float64
+    f = lambda x: (x ** 3).sum()
+    x = torch.tensor([1.0, 2.0], dtype=f64)
+    v, g = T.value_and_grad(f)(x)
+    assert float(v) == 9.0 and torch.allclose(g, 3 * x ** 2) and torch.allclose(T.hessian(f)(x), torch.diag(6 * x))
+    assert float(T.nth_derivative(lambda t: t ** 4, 3)(torch.tensor(2.0, dtype=f64))) == pytest.approx(48.0)
+    assert torch.allclose(T.hessian_vector_product(f, x, torch.tensor([1.0, 1.0], dtype=f64)), 6 * x)
+    assert torch.allclose(T.vmap(T.grad(lambda t: torch.sin(t)))(x), torch.cos(x))
+    # meta-gradient of the post-update loss w.r.t. the inner learning-rate-like meta parameter (closed form for a quadratic)
+    w0, a = torch.tensor(2.0, dtype=f64, requires_grad=True), torch.tensor(0.5, dtype=f64, requires_grad=True)
+    inner = lambda th, meta: meta["a"] * th["w"] ** 2
+    outer = lambda th, meta: th["w"] ** 2
+    out, (ga,) = T.unrolled_meta_gradient(inner, outer, {"w": w0}, {"a": a}, inner_lr=0.1, steps=1)
+    w1 = 2.0 * (1 - 0.2 * 0.5)                                   # w - lr * 2 a w
+    assert float(out) == pytest.approx(w1 ** 2) and float(ga) == pytest.approx(2 * w1 * (-0.2 * 2.0))
+    # fixed point z = tanh(W z + b): implicit gradients equal the gradients through 300 unrolled iterations
+    W = (0.3 * torch.randn(4, 4, dtype=f64)).requires_grad_(True)
+    b = torch.randn(4, dtype=f64, requires_grad=True)
+    step = lambda z, W_, b_: torch.tanh(W_ @ z + b_)
+    z = T.fixed_point(step, torch.zeros(4, dtype=f64), W, b, tol=1e-12, max_iter=500)
+    gW, gb = torch.autograd.grad(z.sum(), (W, b))
+    zu = torch.zeros(4, dtype=f64)
+    for _ in range(300):
+        zu = step(zu, W, b)
+    rW, rb = torch.autograd.grad(zu.sum(), (W, b))
+    assert torch.allclose(z, zu, atol=1e-10) and torch.allclose(gW, rW, atol=1e-8) and torch.allclose(gb, rb, atol=1e-8)
+    # argmin_x 0.5 |x - theta|^2 + 0.5 |x|^2  =>  x* = theta / 2, dL/dtheta = 0.5 dL/dx
+    th = torch.tensor([1.0, -2.0], dtype=f64)
+    inner2 = lambda x_, t_: 0.5 * ((x_ - t_) ** 2).sum() + 0.5 * (x_ ** 2).sum()
+    gth = T.argmin_implicit_gradient(inner2, th / 2, th, torch.tensor([1.0, 3.0], dtype=f64))
+    assert torch.allclose(gth, torch.tensor([0.5, 1.5], dtype=f64))
+    # ODE: dy/dt = -k y, exact solution and gradient w.r.t. k through both solvers
+    for method in ("rk4", "dopri5"):
+        k = torch.tensor(0.7, dtype=f64, requires_grad=True)
+        ts = torch.linspace(0, 2, 5, dtype=f64)
+        ys = T.odeint(lambda t, y: -k * y, torch.tensor([1.5], dtype=f64), ts, method=method)
+        assert torch.allclose(ys[:, 0], 1.5 * torch.exp(-0.7 * ts), atol=1e-5)
+        gk, = torch.autograd.grad(ys[-1, 0], k)
+        assert float(gk) == pytest.approx(-2 * 1.5 * math.exp(-1.4), rel=1e-4)
+    rot = T.odeint(lambda t, y: torch.stack([y[1], -y[0]]), torch.tensor([1.0, 0.0], dtype=f64), torch.tensor([0.0, math.pi], dtype=f64), method="dopri5", rtol=1e-8, atol=1e-10)
+    assert torch.allclose(rot[-1], torch.tensor([-1.0, 0.0], dtype=f64), atol=1e-5)
+    # discrete ops
+    xr = torch.tensor([0.2, 1.7, -0.6], requires_grad=True)
+    yr = T.straight_through(xr, torch.round)
+    yr.sum().backward()
+    assert yr.tolist() == [0.0, 2.0, -1.0] and xr.grad.tolist() == [1.0, 1.0, 1.0]
+    logits = torch.tensor([[2.0, 0.5, -1.0]], requires_grad=True)
+    gen = torch.Generator().manual_seed(0)
+    hard = T.gumbel_softmax(logits, tau=0.5, hard=True, generator=gen)
+    (hard * torch.tensor([1.0, 2.0, 3.0])).sum().backward()
+    assert hard.sum() == 1 and set(hard.flatten().tolist()) <= {0.0, 1.0} and logits.grad.abs().sum() > 0
+    counts = torch.stack([T.gumbel_softmax(logits.detach(), 1.0, True, gen)[0] for _ in range(400)]).mean(0)
+    assert torch.allclose(counts, torch.softmax(logits.detach()[0], -1), atol=0.08)
+    # score function: gradient of E_{b ~ Bernoulli(p)}[b] w.r.t. the logit is p (1 - p)
+    lg = torch.tensor(0.3, requires_grad=True)
+    d = torch.distributions.Bernoulli(logits=lg)
+    s = d.sample((20000,))
+    T.score_function_surrogate(d.log_prob(s), s, baseline=s.mean()).backward()
+    p = torch.sigmoid(torch.tensor(0.3))
+    assert float(lg.grad) == pytest.approx(float(p * (1 - p)), abs=0.02)
+    # symbolic
+    X = T.Sym.var("x")
+    e = T.sym_sin(X * X) + 3 * X ** 3 - T.sym_exp(2 * X) / X
+    d1 = e.diff("x").simplify()
+    xv = torch.tensor(0.8, dtype=f64, requires_grad=True)
+    val = e.evaluate({"x": xv})
+    ref, = torch.autograd.grad(val, xv)
+    assert float(d1.evaluate({"x": xv.detach()})) == pytest.approx(float(ref), rel=1e-10)
+    assert str((X * 1 + 0).simplify()) == "x" and str((X ** 2).diff("x").simplify()) == "(2 * x)" and str((T.Sym.const(2) * 3).simplify()) == "6"
+    # analysis tools
+    deep = torch.nn.Sequential(*[m for _ in range(12) for m in (torch.nn.Linear(8, 8), torch.nn.Sigmoid())])
+    deep(torch.randn(4, 8)).sum().backward()
+    rep = T.gradient_flow_report(deep, vanish=1e-6)
+    assert rep["max_over_min"] > 100 and "0.weight" in rep["vanishing"] and len(rep["layers"]) == 24
+    ema = T.GradientFilter("ema", beta=0.5)
+    assert ema(torch.ones(2)).tolist() == [1, 1] and ema(torch.full((2,), 3.0)).tolist() == [2, 2]
+    med = T.GradientFilter("median", window=3)
+    for gvals in (1.0, 100.0, 2.0):
+        mo = med(torch.full((2,), gvals))
+    assert mo.tolist() == [2.0, 2.0]
+    out_f = T.GradientFilter("outlier", k=4.0)
+    for i in range(10):
+        out_f(torch.full((4,), 1.0 + 0.01 * i))
+    assert out_f(torch.full((4,), 500.0)).max() < 2 and out_f.rejected == 1
+    gcomp = T.staleness_compensated_gradient(torch.tensor([2.0]), torch.tensor([1.5]), torch.tensor([1.0]), lam=0.1)
+    assert gcomp.item() == pytest.approx(2 + 0.1 * 4 * 0.5)
+    pq = torch.nn.Parameter(torch.tensor([5.0]))
+    hg = T.HypergradientLR([pq], lr=0.01, hyper_lr=0.001)
+    for _ in range(30):
+        pq.grad = 2 * pq.detach()
+        hg.step()
+    assert hg.lr > 0.01 and abs(float(pq)) < 5 * (1 - 0.02) ** 30               # the rate grew while successive gradients agreed
+    mixed = T.MixedOp({"id": torch.nn.Identity(), "zero": torch.nn.Dropout(1.0), "double": torch.nn.Sequential()})
+    opt = torch.optim.SGD([mixed.alpha], 0.5)
+    xin = torch.randn(64, 4)
+    mixed.train()
+    for _ in range(40):
+        loss = ((mixed(xin) - xin) ** 2).mean()
+        opt.zero_grad(); loss.backward(); opt.step()
+    assert mixed.derive() in ("id", "double") and float(torch.softmax(mixed.alpha, 0)[1]) < 0.2
+    dot = T.autograd_graph_dot(deep(torch.randn(2, 8)).sum())
+    assert dot.startswith("digraph autograd") and "AddmmBackward0" in dot and "->" in dot
