@@ -1912,3 +1912,64 @@ def test_autograd_transforms_implicit_ode_discrete_symbolic_and_analysis():
     assert mixed.derive() in ("id", "double") and float(torch.softmax(mixed.alpha, 0)[1]) < 0.2
     dot = T.autograd_graph_dot(deep(torch.randn(2, 8)).sum())
     assert dot.startswith("digraph autograd") and "AddmmBackward0" in dot and "->" in dot
+
+
+def test_blackwell_low_precision_formats_and_structured_sparsity():
+    from torsh_b200 import quantization_fp as Q
+    torch.manual_seed(0)
+    x = torch.randn(64, 128) * 3
+    q, s = Q.fp8_quantize(x, "e4m3")
+    assert q.dtype == torch.float8_e4m3fn and float(q.float().abs().max()) == 448.0 and Q.quantization_error(x, Q.fp8_dequantize(q, s))["sqnr_db"] > 25
+    big, _ = Q.fp8_quantize(torch.tensor([1e9, -1e9]), "e4m3", scale=1.0)
+    assert big.float().tolist() == [448.0, -448.0]                              # saturation, not NaN
+    q5, s5 = Q.fp8_quantize(x, "e5m2")
+    assert Q.quantization_error(x, Q.fp8_dequantize(q5, s5))["sqnr_db"] < Q.quantization_error(x, Q.fp8_dequantize(q, s))["sqnr_db"]
+    ds = Q.DelayedScaling("e4m3", history=4)
+    for k in range(6):
+        qd, sc = ds.quantize(x * (1 + k))
+    assert float(sc) == pytest.approx(float((x * 6).abs().max()) / 448.0, rel=1e-6) and len(ds.hist) == 4
+    # FP4 grid: exact values survive, ties go to the even code, packing round-trips
+    assert torch.equal(Q.fp4_decode(Q.fp4_encode(torch.tensor([0.0, 0.5, -1.5, 6.0, -6.0, 9.0]))), torch.tensor([0.0, 0.5, -1.5, 6.0, -6.0, 6.0]))
+    assert Q.fp4_decode(Q.fp4_encode(torch.tensor([0.25, 0.75, 2.5, 5.0]))).tolist() == [0.0, 1.0, 2.0, 4.0]
+    codes = torch.randint(0, 16, (5, 32), dtype=torch.uint8)
+    assert torch.equal(Q.unpack_fp4(Q.pack_fp4(codes)), codes) and Q.pack_fp4(codes).shape == (5, 16)
+    # MX formats: power-of-two block scales, error ordered by mantissa bits, exactness on representable data
+    for fmt in ("mxfp8_e4m3", "mxfp8_e5m2", "mxfp6_e2m3", "mxfp6_e3m2", "mxfp4"):
+        t = Q.mx_quantize(x, fmt)
+        assert t.scale_exp.shape == (64, 4) and t.scale_exp.dtype == torch.int8 and Q.mx_dequantize(t).shape == x.shape
+    e8 = Q.quantization_error(x, Q.mx_dequantize(Q.mx_quantize(x, "mxfp8_e4m3")))["sqnr_db"]
+    e6 = Q.quantization_error(x, Q.mx_dequantize(Q.mx_quantize(x, "mxfp6_e2m3")))["sqnr_db"]
+    e4 = Q.quantization_error(x, Q.mx_dequantize(Q.mx_quantize(x, "mxfp4")))["sqnr_db"]
+    e6b = Q.quantization_error(x, Q.mx_dequantize(Q.mx_quantize(x, "mxfp6_e3m2")))["sqnr_db"]
+    # E4M3 and E2M3 both carry three mantissa bits, so inside a scaled block they are equally precise; E3M2 has two, FP4 one
+    assert abs(e8 - e6) < 2 and e6 > e6b > e4 > 8 and e8 > 28
+    exact = torch.tensor([0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -6.0] * 4)[None] * 2.0 ** -5
+    assert torch.equal(Q.mx_dequantize(Q.mx_quantize(exact, "mxfp4")), exact)
+    # one outlier only hurts its own block
+    xo = torch.randn(1, 64) * 0.1
+    xo[0, 3] = 50.0
+    d = Q.mx_dequantize(Q.mx_quantize(xo, "mxfp4"))
+    assert (d[0, 32:] - xo[0, 32:]).abs().max() < 0.05 and (d[0, :32] - xo[0, :32]).abs().max() > 0.05
+    # NVFP4: finer blocks and E4M3 scales beat MXFP4 at half a bit more
+    nv = Q.nvfp4_quantize(x)
+    assert nv.packed.shape == (64, 64) and nv.block_scale.dtype == torch.float8_e4m3fn and nv.block_scale.shape == (64, 8)
+    env = Q.quantization_error(x, Q.nvfp4_dequantize(nv))["sqnr_db"]
+    assert env > e4 and Q.bits_per_element("nvfp4") == 4.5 and Q.bits_per_element("mxfp4") == 4.25
+    rep = Q.compare_formats(x)
+    assert set(rep) == {"fp8", "mxfp8_e4m3", "mxfp6_e2m3", "mxfp6_e3m2", "mxfp4", "nvfp4"} and rep["mxfp4"]["cosine"] > 0.95
+    with pytest.raises(ValueError):
+        Q.mx_quantize(torch.randn(4, 30))
+    # 2:4 sparsity
+    w = torch.randn(8, 32)
+    p = Q.prune_2_4(w)
+    g = p.reshape(8, 8, 4)
+    assert ((g != 0).sum(-1) == 2).all() and torch.equal(g.abs().sum(-1), w.reshape(8, 8, 4).abs().topk(2, -1).values.sum(-1))
+    vals, meta = Q.compress_2_4(p)
+    assert vals.shape == (8, 16) and meta.shape == (8, 8) and meta.dtype == torch.uint8 and torch.equal(Q.expand_2_4(vals, meta), p)
+    sparse_group = torch.tensor([[0.0, 0.0, 0.0, 5.0, 1.0, 0.0, 0.0, 0.0]])
+    v2, m2 = Q.compress_2_4(sparse_group)
+    assert torch.equal(Q.expand_2_4(v2, m2), sparse_group)
+    with pytest.raises(ValueError):
+        Q.compress_2_4(w)
+    xin = torch.randn(5, 32)
+    assert torch.allclose(xin @ Q.expand_2_4(vals, meta).t(), xin @ p.t())
