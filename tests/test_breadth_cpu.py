@@ -1973,3 +1973,75 @@ def test_blackwell_low_precision_formats_and_structured_sparsity():
         Q.compress_2_4(w)
     xin = torch.randn(5, 32)
     assert torch.allclose(xin @ Q.expand_2_4(vals, meta).t(), xin @ p.t())
+
+
+def test_graph_layers_sampling_generators_metrics_and_link_prediction(tmp_path):
+    nx = pytest.importorskip("scipy.sparse.csgraph")
+    import numpy as np
+    import scipy.sparse as sps
+    from torsh_b200 import graph as G
+    torch.manual_seed(0)
+    e = G.erdos_renyi(30, 0.15, seed=1)
+    assert (e[0] != e[1]).all() and torch.equal(torch.sort(e[0] * 30 + e[1]).values, torch.sort(e.flip(0)[0] * 30 + e.flip(0)[1]).values)
+    x = torch.randn(30, 8)
+    # ChebConv with K = 1 is a linear layer; higher orders see neighbours up to K - 1 hops
+    c1 = G.ChebConv(8, 4, K=1)
+    assert torch.allclose(c1(x, e), c1.lins[0](x) + c1.bias)
+    line = torch.tensor([[0, 1, 1, 2, 2, 3], [1, 0, 2, 1, 3, 2]])
+    c3 = G.ChebConv(1, 1, K=3)
+    xi = torch.zeros(4, 1); xi[0] = 1.0
+    base = c3(torch.zeros(4, 1), line)
+    resp = (c3(xi, line) - base).abs().flatten()
+    assert resp[2] > 0 and resp[3] == 0                                      # two hops reached, three not
+    gt = G.GraphTransformerLayer(8, heads=2)
+    out = gt(x, e)
+    out.sum().backward()
+    assert out.shape == (30, 8) and all(p.grad is not None for p in gt.parameters())
+    iso = torch.tensor([[0], [1]])                                          # node 1 attends to node 0 only: attention weight 1
+    h = gt.n1(x[:2])
+    want = x[:2].clone(); want[1] = want[1] + gt.o(gt.v(h)[0])
+    want = want + gt.mlp(gt.n2(want))
+    assert torch.allclose(gt(x[:2], iso)[1], want[1], atol=1e-5)
+    # neighbour sampling: fan-out respected, edges relabelled into the returned node list, seeds first
+    ba = G.barabasi_albert(200, 3, seed=0)
+    deg = torch.bincount(ba[0], minlength=200)
+    assert deg.max() > 4 * deg.float().median() and ba.shape[1] >= 2 * 3 * 190
+    ns = G.NeighborSampler(ba, 200, fanouts=[5, 3])
+    seeds = torch.tensor([10, 20, 30])
+    nodes, layers = ns.sample(seeds)
+    assert nodes[:3].tolist() == [10, 20, 30] and len(layers) == 2
+    inner = layers[1]
+    assert set(inner[1].tolist()) <= {0, 1, 2} and torch.bincount(inner[1]).max() <= 3 and torch.bincount(layers[0][1]).max() <= 5
+    have = set((ba[0] * 200 + ba[1]).tolist())
+    assert all(int(nodes[u]) * 200 + int(nodes[v]) in have for u, v in layers[0].t().tolist())
+    # metrics against scipy / closed forms
+    two = torch.cat([G.grid_graph(3, 3), G.grid_graph(2, 2) + 9], 1)
+    comp = G.connected_components(two, 13)
+    ncomp, ref = nx.connected_components(sps.coo_matrix((np.ones(two.shape[1]), (two[0].numpy(), two[1].numpy())), shape=(13, 13)), directed=False)
+    assert int(comp.max()) + 1 == ncomp == 2 and len(set(zip(comp.tolist(), ref.tolist()))) == 2
+    assert G.modularity(two, comp) == pytest.approx(1 - ((24 / 32) ** 2 + (8 / 32) ** 2))
+    tri = torch.tensor([[0, 1, 1, 2, 2, 0, 2, 3], [1, 0, 2, 1, 0, 2, 3, 2]])
+    assert G.clustering_coefficient(tri, 4).tolist() == pytest.approx([1.0, 1.0, 1 / 3, 0.0])
+    pr = G.pagerank(ba, 200)
+    assert float(pr.sum()) == pytest.approx(1.0) and int(pr.argmax()) == int(deg.argmax())
+    star = torch.tensor([[1, 2, 3], [0, 0, 0]])
+    ps = G.pagerank(star, 4)
+    assert ps[0] > 3 * ps[1] and ps[1] == pytest.approx(float(ps[2]))
+    # link prediction on two cliques: embeddings trained with negative sampling separate inside / outside pairs
+    k = 6
+    a = torch.combinations(torch.arange(k)).t()
+    pos = torch.cat([a, a + k], 1)
+    pos = torch.cat([pos, pos.flip(0)], 1)
+    neg = G.negative_sampling(pos, 2 * k, pos.shape[1], seed=0)
+    assert not set((neg[0] * 12 + neg[1]).tolist()) & set((pos[0] * 12 + pos[1]).tolist()) and (neg[0] != neg[1]).all()
+    z = torch.nn.Parameter(0.1 * torch.randn(2 * k, 4))
+    opt = torch.optim.Adam([z], 0.05)
+    for _ in range(200):
+        l = G.link_prediction_loss(z, pos, neg)
+        opt.zero_grad(); l.backward(); opt.step()
+    s_in = (z[0] * z[1]).sum().item(); s_out = (z[0] * z[k]).sum().item()
+    assert l < 0.2 and s_in > 1 > s_out
+    (tmp_path / "c.content").write_text("p1 1 0 1 ml\np2 0 1 1 db\np3 1 1 0 ml\n")
+    (tmp_path / "c.cites").write_text("p1 p2\np3 p1\np9 p1\n")
+    gd = G.load_planetoid_like(tmp_path / "c.content", tmp_path / "c.cites")
+    assert gd.x.shape == (3, 3) and gd.y.tolist() == [1, 0, 1] and gd.num_edges == 4

@@ -171,3 +171,203 @@ def stochastic_block_model(sizes=(40, 40), p_in=0.3, p_out=0.02, feat=16, seed=0
     adj = (adj | adj.t()) & ~torch.eye(len(lab), dtype=torch.bool)
     x = torch.randn(len(lab), feat, generator=g) + lab[:, None].float()
     return GraphData(x, adj.nonzero().t().contiguous(), y=lab)
+
+
+# ---- further layers, sampling, generators, metrics and link prediction (crates/torsh-graph/src/{conv,sampling,generators,
+#      metrics,link_prediction,transformer}.rs) --------------------------------------------------------------------------
+class ChebConv(nn.Module):
+    """Spectral convolution with Chebyshev polynomials of the scaled Laplacian up to order K (Defferrard et al.)."""
+
+    def __init__(self, cin: int, cout: int, K: int = 3):
+        super().__init__()
+        self.lins = nn.ModuleList(nn.Linear(cin, cout, bias=False) for _ in range(K))
+        self.bias = nn.Parameter(torch.zeros(cout))
+
+    def forward(self, x, edge_index):
+        n = x.shape[0]
+        src, dst = edge_index
+        deg = torch.bincount(dst, minlength=n).to(x.dtype).clamp(min=1)
+        w = -(deg[src] * deg[dst]).rsqrt()                                   # L~ = L - I = -D^-1/2 A D^-1/2 (lambda_max = 2)
+        prop = lambda h: scatter_add(h[src] * w[:, None], dst, n)
+        t0, out = x, self.lins[0](x)
+        if len(self.lins) > 1:
+            t1 = prop(x)
+            out = out + self.lins[1](t1)
+            for lin in self.lins[2:]:
+                t0, t1 = t1, 2 * prop(t1) - t0
+                out = out + lin(t1)
+        return out + self.bias
+
+
+class GraphTransformerLayer(nn.Module):
+    """Multi-head attention restricted to graph edges (softmax over each node's incoming edges), residual + norm + MLP."""
+
+    def __init__(self, dim: int, heads: int = 4, mlp_ratio: float = 2.0):
+        super().__init__()
+        self.h, self.dh = heads, dim // heads
+        self.q, self.k, self.v, self.o = (nn.Linear(dim, dim) for _ in range(4))
+        self.n1, self.n2 = nn.LayerNorm(dim), nn.LayerNorm(dim)
+        self.mlp = nn.Sequential(nn.Linear(dim, int(dim * mlp_ratio)), nn.GELU(), nn.Linear(int(dim * mlp_ratio), dim))
+
+    def forward(self, x, edge_index):
+        n = x.shape[0]
+        src, dst = edge_index
+        h = self.n1(x)
+        q, k, v = (f(h).reshape(n, self.h, self.dh) for f in (self.q, self.k, self.v))
+        score = (q[dst] * k[src]).sum(-1) / self.dh ** 0.5                    # [E, heads]
+        mx = torch.full((n, self.h), float("-inf"), dtype=score.dtype, device=x.device).scatter_reduce(0, dst[:, None].expand_as(score), score, "amax")
+        e = torch.exp(score - mx[dst])
+        den = torch.zeros(n, self.h, dtype=e.dtype, device=x.device).index_add_(0, dst, e)
+        a = e / den[dst].clamp(min=1e-30)
+        agg = torch.zeros(n, self.h, self.dh, dtype=x.dtype, device=x.device).index_add_(0, dst, a[..., None] * v[src])
+        x = x + self.o(agg.reshape(n, -1))
+        return x + self.mlp(self.n2(x))
+
+
+class NeighborSampler:
+    """Samples, for a batch of seed nodes, up to ``fanout[l]`` incoming neighbours per node and layer (GraphSAGE style).
+    Returns the node ids involved (seeds first) and one relabelled edge index per layer, outermost layer first."""
+
+    def __init__(self, edge_index: torch.Tensor, num_nodes: int, fanouts, seed: int = 0):
+        src, dst = edge_index
+        order = torch.argsort(dst, stable=True)
+        self.src = src[order]
+        self.ptr = torch.zeros(num_nodes + 1, dtype=torch.long)
+        self.ptr[1:] = torch.bincount(dst, minlength=num_nodes).cumsum(0)
+        self.fanouts, self.gen = list(fanouts), torch.Generator().manual_seed(seed)
+
+    def sample(self, seeds: torch.Tensor):
+        nodes = seeds.tolist()
+        index = {v: i for i, v in enumerate(nodes)}
+        frontier, layers = list(nodes), []
+        for fan in reversed(self.fanouts):
+            es, ed, nxt = [], [], []
+            for v in frontier:
+                nb = self.src[self.ptr[v]:self.ptr[v + 1]]
+                if len(nb) > fan:
+                    nb = nb[torch.randperm(len(nb), generator=self.gen)[:fan]]
+                for u in nb.tolist():
+                    if u not in index:
+                        index[u] = len(nodes)
+                        nodes.append(u)
+                        nxt.append(u)
+                    es.append(index[u])
+                    ed.append(index[v])
+            layers.append(torch.tensor([es, ed], dtype=torch.long))
+            frontier = frontier + nxt
+        return torch.tensor(nodes), layers[::-1]
+
+
+def erdos_renyi(n: int, p: float, seed: int = 0, directed: bool = False) -> torch.Tensor:
+    g = torch.Generator().manual_seed(seed)
+    m = torch.rand(n, n, generator=g) < p
+    m = m.triu(1) if not directed else m & ~torch.eye(n, dtype=torch.bool)
+    e = m.nonzero().t()
+    return e if directed else torch.cat([e, e.flip(0)], 1)
+
+
+def barabasi_albert(n: int, m: int, seed: int = 0) -> torch.Tensor:
+    """Preferential attachment: every new node links to ``m`` existing nodes chosen in proportion to their degree."""
+    g = torch.Generator().manual_seed(seed)
+    edges, targets = [], list(range(m))
+    repeated: list[int] = []
+    for v in range(m, n):
+        for t in set(targets):
+            edges.append((v, t))
+        repeated += list(set(targets)) + [v] * len(set(targets))
+        pick = torch.randint(0, len(repeated), (m * 3,), generator=g).tolist()
+        targets = []
+        for i in pick:
+            if repeated[i] not in targets:
+                targets.append(repeated[i])
+            if len(targets) == m:
+                break
+    e = torch.tensor(edges, dtype=torch.long).t()
+    return torch.cat([e, e.flip(0)], 1)
+
+
+def grid_graph(h: int, w: int) -> torch.Tensor:
+    idx = torch.arange(h * w).reshape(h, w)
+    e = torch.cat([torch.stack([idx[:, :-1].flatten(), idx[:, 1:].flatten()]), torch.stack([idx[:-1].flatten(), idx[1:].flatten()])], 1)
+    return torch.cat([e, e.flip(0)], 1)
+
+
+def modularity(edge_index: torch.Tensor, labels: torch.Tensor) -> float:
+    """Newman modularity of a partition of an undirected graph given with both edge directions."""
+    src, dst = edge_index
+    m2 = float(edge_index.shape[1])
+    deg = torch.bincount(src, minlength=labels.numel()).double()
+    inside = float((labels[src] == labels[dst]).sum()) / m2
+    k = torch.zeros(int(labels.max()) + 1, dtype=torch.float64).index_add_(0, labels, deg)
+    return inside - float(((k / m2) ** 2).sum())
+
+
+def clustering_coefficient(edge_index: torch.Tensor, n: int) -> torch.Tensor:
+    a = torch.zeros(n, n)
+    a[edge_index[0], edge_index[1]] = 1
+    tri = (a @ a * a).sum(1) / 2
+    deg = a.sum(1)
+    return torch.where(deg > 1, 2 * tri / (deg * (deg - 1)).clamp(min=1), torch.zeros(n))
+
+
+def connected_components(edge_index: torch.Tensor, n: int) -> torch.Tensor:
+    """Component label per node by label propagation (min label over neighbours until nothing changes)."""
+    lab = torch.arange(n)
+    src, dst = edge_index
+    while True:
+        new = lab.clone().scatter_reduce(0, dst, lab[src], "amin")
+        new = new.scatter_reduce(0, src, new[dst], "amin")
+        if torch.equal(new, lab):
+            _, inv = torch.unique(lab, return_inverse=True)
+            return inv
+        lab = new
+
+
+def pagerank(edge_index: torch.Tensor, n: int, damping: float = 0.85, iters: int = 100, tol: float = 1e-10) -> torch.Tensor:
+    src, dst = edge_index
+    out_deg = torch.bincount(src, minlength=n).double()
+    r = torch.full((n,), 1.0 / n, dtype=torch.float64)
+    for _ in range(iters):
+        contrib = r / out_deg.clamp(min=1)
+        new = torch.zeros(n, dtype=torch.float64).index_add_(0, dst, contrib[src])
+        new = damping * (new + r[out_deg == 0].sum() / n) + (1 - damping) / n
+        if (new - r).abs().sum() < tol:
+            return new
+        r = new
+    return r
+
+
+def negative_sampling(edge_index: torch.Tensor, n: int, num: int, seed: int = 0) -> torch.Tensor:
+    """``num`` node pairs that are not edges (and not self loops)."""
+    g = torch.Generator().manual_seed(seed)
+    have = set((edge_index[0] * n + edge_index[1]).tolist())
+    out = []
+    while len(out) < num:
+        c = torch.randint(0, n, (2, 2 * num), generator=g)
+        for u, v in c.t().tolist():
+            if u != v and u * n + v not in have:
+                have.add(u * n + v)
+                out.append((u, v))
+                if len(out) == num:
+                    break
+    return torch.tensor(out).t()
+
+
+def link_prediction_loss(z: torch.Tensor, pos_edges: torch.Tensor, neg_edges: torch.Tensor) -> torch.Tensor:
+    """Binary cross entropy of inner-product edge scores for positive and sampled negative pairs."""
+    score = lambda e: (z[e[0]] * z[e[1]]).sum(-1)
+    return F.binary_cross_entropy_with_logits(torch.cat([score(pos_edges), score(neg_edges)]),
+                                              torch.cat([torch.ones(pos_edges.shape[1]), torch.zeros(neg_edges.shape[1])]).to(z))
+
+
+def load_planetoid_like(content_path, cites_path) -> GraphData:
+    """Cora / CiteSeer in their original text form: ``<id> <features...> <label>`` per line and ``<cited> <citing>`` per line."""
+    ids, feats, labels = [], [], []
+    for ln in open(content_path):
+        p = ln.split()
+        ids.append(p[0]); feats.append([float(v) for v in p[1:-1]]); labels.append(p[-1])
+    idx = {v: i for i, v in enumerate(ids)}
+    classes = {c: i for i, c in enumerate(sorted(set(labels)))}
+    edges = [(idx[a], idx[b]) for a, b in (ln.split() for ln in open(cites_path)) if a in idx and b in idx]
+    e = torch.tensor(edges, dtype=torch.long).t()
+    return GraphData(torch.tensor(feats), torch.cat([e, e.flip(0)], 1), None, torch.tensor([classes[c] for c in labels]))
