@@ -2045,3 +2045,83 @@ def test_graph_layers_sampling_generators_metrics_and_link_prediction(tmp_path):
     (tmp_path / "c.cites").write_text("p1 p2\np3 p1\np9 p1\n")
     gd = G.load_planetoid_like(tmp_path / "c.content", tmp_path / "c.cites")
     assert gd.x.shape == (3, 3) and gd.y.tolist() == [1, 0, 1] and gd.num_edges == 4
+
+
+def test_cluster_hierarchy_optics_streaming_drift_and_evaluation():
+    sk = pytest.importorskip("sklearn")
+    import numpy as np
+    from scipy.cluster import hierarchy as sch
+    from sklearn import metrics as skm
+    from sklearn.cluster import OPTICS as SkOptics
+    from torsh_b200 import cluster as C
+    torch.manual_seed(0)
+    cen = torch.tensor([[0.0, 0.0], [6.0, 0.0], [0.0, 6.0]])
+    x = torch.cat([c + 0.5 * torch.randn(40, 2) for c in cen])
+    truth = torch.arange(3).repeat_interleave(40)
+    # merge distances equal scipy's for each linkage; flat cuts recover the blobs
+    for m in ("single", "complete", "average", "ward"):
+        r = C.linkage(x, m)
+        ref = sch.linkage(x.double().numpy(), m)
+        assert np.allclose(sorted(s[2] for s in r.steps), np.sort(ref[:, 2]), rtol=1e-6), m
+        assert C.adjusted_rand_index(r.flat_clusters(3), truth) == pytest.approx(1.0)
+    assert int(r.clusters_by_distance(15.0).max()) + 1 == 3 and int(r.flat_clusters(1).max()) == 0
+    assert C.AgglomerativeClustering(3).fit(x).labels.unique().numel() == 3
+    with pytest.raises(ValueError):
+        C.linkage(x, "centroidal")
+    # OPTICS: core distances and the multiset of reachabilities match scikit-learn; eps cut finds the blobs
+    o = C.OPTICS(min_samples=5).fit(x)
+    so = SkOptics(min_samples=5, metric="euclidean").fit(x.double().numpy())
+    assert np.allclose(o.core_distances.numpy(), so.core_distances_, rtol=1e-6)
+    fin = torch.isfinite(o.reachability)
+    assert fin.sum() == len(x) - 1
+    same = np.isclose(o.reachability.numpy(), so.reachability_, rtol=1e-6)        # ties in the queue may resolve differently
+    assert same.mean() > 0.97 and o.ordering[:6].tolist() == so.ordering_[:6].tolist()
+    assert C.adjusted_rand_index(o.extract_dbscan(1.0), truth) > 0.95
+    # streaming k-means follows the data; window k-means re-fits on schedule
+    perm = torch.randperm(len(x))
+    ok = C.OnlineKMeans(3)
+    ok.centers, ok.counts = cen + 1.0, torch.ones(3)
+    ok.partial_fit(x[perm])
+    assert torch.cdist(ok.centers, cen).min(1).values.max() < 0.4 and C.adjusted_rand_index(ok.predict(x), truth) == pytest.approx(1.0)
+    sw = C.SlidingWindowKMeans(3, window_size=60, recompute_frequency=30)
+    for i in range(0, 120, 15):
+        sw.partial_fit(x[perm][i:i + 15])
+    assert sw.n_refits == 4 and len(sw.window) == 60 and sw.centers.shape == (3, 2)
+    # drift detectors: quiet on a stationary stream, fire after a mean shift
+    g = torch.Generator().manual_seed(1)
+    stream = torch.cat([torch.randn(300, generator=g) * 0.1, 2 + torch.randn(100, generator=g) * 0.1]).tolist()
+    for det in (C.PageHinkley(lam=5.0), C.ADWIN(delta=0.002, max_window_size=400)):
+        st = [det.update(v) for v in stream]
+        assert C.DRIFT not in st[:300] and C.DRIFT in st[300:], type(det).__name__
+    ddm = C.DDM()
+    errs = (torch.rand(400, generator=g) < torch.cat([torch.full((250,), 0.1), torch.full((150,), 0.6)])).float().tolist()
+    st = [ddm.update(e) for e in errs]
+    assert C.DRIFT not in st[:250] and C.DRIFT in st[250:]
+    comp = C.CompositeDriftDetector()
+    assert C.DRIFT in [comp.update(v) for v in stream]
+    # initialisation, scaling and parameter suggestion
+    for init in (C.init_forgy, C.init_random_partition, C.init_kmeans_plus_plus):
+        assert init(x, 3, seed=0).shape == (3, 2)
+    assert torch.cdist(C.init_kmeans_plus_plus(x, 3), cen).min(0).values.max() < 2.0
+    s = C.standardize_features(x)
+    assert torch.allclose(s.mean(0), torch.zeros(2), atol=1e-5) and torch.allclose(s.std(0, unbiased=False), torch.ones(2), atol=1e-5)
+    assert C.normalize_features(x).min() == 0 and C.normalize_features(x).max() == 1
+    assert torch.allclose(C.unit_normalize(x).norm(dim=1), torch.ones(len(x)))
+    assert torch.allclose(C.robust_scale(x).median(0).values, torch.zeros(2), atol=0.05)
+    eps, ms = C.suggest_dbscan_params(x)
+    assert 0.1 < eps < 2.0 and C.adjusted_rand_index(C.dbscan(x, eps, ms).clamp(min=0), truth) > 0.9
+    assert torch.allclose(C.pairwise_distance(x[:3], x[:3], "cosine").diagonal(), torch.zeros(3), atol=1e-6)
+    with pytest.raises(ValueError):
+        C.validate_cluster_input(torch.tensor([[float("nan"), 1.0]]))
+    # evaluation against scikit-learn
+    pred = truth.clone(); pred[::7] = (pred[::7] + 1) % 3; pred[5:20] = 3
+    t, p = truth.numpy(), pred.numpy()
+    assert C.normalized_mutual_info(truth, pred) == pytest.approx(skm.normalized_mutual_info_score(t, p))
+    assert C.adjusted_mutual_info(truth, pred) == pytest.approx(skm.adjusted_mutual_info_score(t, p), abs=1e-9)
+    assert C.homogeneity_completeness_v_measure(truth, pred) == pytest.approx(skm.homogeneity_completeness_v_measure(t, p))
+    assert C.fowlkes_mallows(truth, pred) == pytest.approx(skm.fowlkes_mallows_score(t, p))
+    assert C.rand_index(truth, pred) == pytest.approx(skm.rand_score(t, p))
+    assert C.mutual_information(truth, pred) == pytest.approx(skm.mutual_info_score(t, p))
+    assert C.calinski_harabasz(x, pred) == pytest.approx(skm.calinski_harabasz_score(x.numpy(), p), rel=1e-4)
+    assert C.purity(truth, truth) == 1.0 and 0 < C.jaccard_index(truth, pred) < 1 and C.dunn_index(x, truth) > C.dunn_index(x, pred)
+    assert C.gap_statistic(x, k_max=5, n_refs=5)[0] == 3
