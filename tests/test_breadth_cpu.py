@@ -2125,3 +2125,155 @@ def test_cluster_hierarchy_optics_streaming_drift_and_evaluation():
     assert C.calinski_harabasz(x, pred) == pytest.approx(skm.calinski_harabasz_score(x.numpy(), p), rel=1e-4)
     assert C.purity(truth, truth) == 1.0 and 0 < C.jaccard_index(truth, pred) < 1 and C.dunn_index(x, truth) > C.dunn_index(x, pred)
     assert C.gap_statistic(x, k_max=5, n_refs=5)[0] == 3
+
+
+def test_fx_tools_codegen_analysis_rewrite_shapes_editor_memory_placement_quant_nas(tmp_path):
+    import ctypes
+    import subprocess
+    import numpy as np
+    from torsh_b200 import fx as tfx_, fx_tools as T
+    torch.manual_seed(0)
+
+    class MLP(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.act, self.b = torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4)
+            self.register_buffer("shift", torch.randn(4))
+
+        def forward(self, x):
+            h = self.act(self.a(x))
+            return torch.tanh(self.b(h)) + self.shift
+
+    m = MLP().eval()
+    gm = tfx_.symbolic_trace(m)
+    x = torch.randn(5, 8)
+    want = m(x)
+    # generated Python and NumPy source reproduce the module; C++ (plain loops) compiles and does too
+    py = T.PythonCodeGen(True).generate(gm)
+    assert "def forward(consts, x)" in py.source and torch.allclose(py.load()(x), want, atol=1e-6)
+    npc = T.PythonCodeGen(False).generate(gm)
+    assert "import numpy as np" in npc.source and np.allclose(npc.load()(x.numpy()), want.detach().numpy(), atol=1e-5)
+    assert "torch::linear" in T.CppCodeGen(True).generate(gm).source
+    tfx_.ShapeProp(gm).run(x)
+    cpp = T.CppCodeGen(False).generate(gm)
+    (tmp_path / "g.cpp").write_text(cpp.source)
+    subprocess.run(["g++", "-O1", "-shared", "-fPIC", str(tmp_path / "g.cpp"), "-o", str(tmp_path / "g.so")], check=True)
+    lib = ctypes.CDLL(str(tmp_path / "g.so"))
+    cs = [c.numpy() for c in cpp.constants.values()]
+    arr = (ctypes.c_void_p * len(cs))(*[c.ctypes.data for c in cs])
+    out = np.zeros((5, 4), np.float32)
+    xin = x.numpy().copy()
+    lib.forward(arr, ctypes.c_void_p(xin.ctypes.data), ctypes.c_void_p(out.ctypes.data))
+    assert np.allclose(out, want.detach().numpy(), atol=1e-5)
+    lc = T.LazyCompiler()
+    assert lc.compile(gm) is lc.compile(gm) and lc.cache_stats() == {"entries": 1, "hits": 1, "misses": 1}
+    # metrics, lint, patterns, diff
+    def messy(x, y):
+        a = x + 0
+        b = torch.relu(x * y)
+        c = torch.relu(x * y)
+        unused = x - y
+        return (a + b + c).reshape(-1).reshape(2, -1)
+    g2 = tfx_.symbolic_trace(messy)
+    rules = {i.rule for i in T.GraphLinter().lint_graph(g2)}
+    assert {"unused-value", "noop-arithmetic", "duplicate-computation", "reshape-chain"} <= rules
+    assert {i.rule for i in T.GraphLinter("error").lint_graph(g2)} == set()
+    mt = T.calculate_graph_metrics(gm)
+    assert mt["compute_nodes"] == 5 and mt["depth"] == 7 and mt["max_width"] == 1
+
+    class Res(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.n, self.l = torch.nn.LayerNorm(8), torch.nn.Linear(8, 8)
+
+        def forward(self, x, k):
+            h = x + torch.relu(self.l(self.n(x)))
+            return torch.matmul(torch.softmax(torch.matmul(h, k.transpose(0, 1)) / 2.0, -1), k)
+    pats = {p["pattern"] for p in T.detect_patterns(tfx_.symbolic_trace(Res()))}
+    assert {"residual", "norm+linear", "linear+activation", "attention"} <= pats
+    import copy
+    ed = T.GraphEditor(copy.deepcopy(gm))
+    before = copy.deepcopy(ed.gm)
+    ed.insert_after("a", torch.neg)
+    assert torch.allclose(ed.gm(x), torch.tanh(m.b(torch.relu(-m.a(x)))) + m.shift, atol=1e-6)
+    d = T.graph_diff(before, ed.gm)
+    assert d["added"] == ["neg"] and d["changed"] == ["act"] and not d["identical"]
+    ed.remove("neg")
+    assert torch.allclose(ed.gm(x), want)
+    assert ed.undo() and "neg" in {n.name for n in ed.gm.graph.nodes} and ed.undo() and torch.allclose(ed.gm(x), want)
+    assert ed.redo() and "neg" in ed.export_graph("json") and not T.GraphEditor(gm).undo()
+    # rewriting: conv+bn fold is exact in eval mode, conv+relu becomes one node, user pattern replaced
+    net = torch.nn.Sequential(torch.nn.Conv2d(3, 6, 3, padding=1, bias=False), torch.nn.BatchNorm2d(6), torch.nn.ReLU(), torch.nn.Conv2d(6, 2, 1)).eval()
+    net[1].running_mean.normal_(); net[1].running_var.uniform_(0.5, 2.0); net[1].weight.data.normal_(); net[1].bias.data.normal_()
+    img = torch.randn(2, 3, 8, 8)
+    ref = net(img)
+    gn = tfx_.symbolic_trace(net)
+    rw = T.SubgraphRewriter().with_common_fusions().add_pattern(lambda v: torch.neg(torch.neg(v)), lambda v: v)
+    rep = rw.apply(gn)
+    assert rep["fold_conv_bn"] == 1 and rep["fuse_module_activation"] == 1 and torch.allclose(gn(img), ref, atol=1e-5)
+    assert sum(n.op == "call_module" for n in gn.graph.nodes) == 2
+    gdn = tfx_.symbolic_trace(lambda v: torch.neg(torch.neg(v)) * 2)
+    assert rw.find_matches(gdn, lambda v: torch.neg(torch.neg(v))) == 1 and T.SubgraphRewriter().add_pattern(lambda v: torch.neg(torch.neg(v)), lambda v: v).apply(gdn)["<lambda>"] == 1
+    assert torch.equal(gdn(x), x * 2)
+    # dynamic shapes
+    B, S = T.DynamicDim.symbolic("B"), T.DynamicDim.symbolic("S")
+    assert repr(T.broadcast_dynamic_shapes(T.DynamicShape([B, 1, 8]), T.DynamicShape([S, 8]))) == "[B, S, 8]"
+    assert repr(T.matmul_dynamic_shape(T.DynamicShape(["B", "S", 8]), T.DynamicShape([8, 32]))) == "[B, S, 32]"
+    with pytest.raises(ValueError):
+        T.matmul_dynamic_shape(T.DynamicShape(["B", 8]), T.DynamicShape([9, 2]))
+    ctx = T.DynamicShapeContext()
+    ctx.register_symbol("B", min=1, max=64)
+    ctx.register_symbol("S", multiple_of=8)
+    ctx.infer(gm, {"x": T.DynamicShape(["B", "S", 8])})
+    assert repr(ctx.get_shape("add")) == "[B, S, 4]" and ctx.get_unresolved_symbols({"B": 2}) == ["S"]
+    assert ctx.resolve_symbols({"B": 2, "S": 16})["add"] == (2, 16, 4)
+    assert len(ctx.validate_constraints({"B": 128, "S": 12})) == 2
+    with pytest.raises(ValueError):
+        T.DynamicShape(["B", 3]).to_static_shape()
+    # checkpoints and resumable execution
+    digest = T.save_graph_checkpoint(gm, tmp_path / "g.pt", {"note": "mlp"})
+    g3, meta = T.load_graph_checkpoint(tmp_path / "g.pt")
+    assert len(digest) == 64 and meta == {"note": "mlp"} and torch.equal(g3(x), want)
+    ri = T.ResumableInterpreter(gm)
+    assert ri.run(x, stop_after="act") is None and ri.saved["at"] == "act"
+    saved = ri.saved
+    assert torch.equal(ri.run(x, resume=saved), want) and "a" not in ri.executed and ri.executed[0] == "b"
+    # memory: peak from liveness, reuse plan smaller than the sum of intermediates
+    chain = tfx_.symbolic_trace(torch.nn.Sequential(*[torch.nn.Linear(32, 32) for _ in range(6)]))
+    rep = T.MemoryAnalyzer(chain).analyze(torch.randn(64, 32))
+    one = 64 * 32 * 4
+    assert rep["peak_bytes"] == 2 * one and rep["total_intermediate_bytes"] == 6 * one and rep["planned_bytes"] == 2 * one and rep["buffers"] == 2
+    # placement: big matmuls go to the fast device, tiny graphs stay where the input is
+    devs = [T.DeviceCapability("cpu", 1e11, 5e10, 64e9), T.DeviceCapability("b200", 1e15, 6e12, 180e9)]
+    big = tfx_.symbolic_trace(torch.nn.Sequential(torch.nn.Linear(512, 512), torch.nn.ReLU(), torch.nn.Linear(512, 512)))
+    plan = T.HeterogeneousPlanner(devs).plan_execution(big, torch.randn(256, 512))
+    assert set(plan["placement"].values()) == {"b200"} and len(plan["transfers"]) == 1
+    tiny = tfx_.symbolic_trace(lambda v: torch.relu(v) + 1)
+    assert set(T.HeterogeneousPlanner(devs).plan_execution(tiny, torch.randn(4))["placement"].values()) == {"cpu"}
+    reg = T.BackendRegistry()
+    name, out = reg.execute_with_auto_backend(gm, x, require={"source"})
+    assert name == "generated-python" and torch.allclose(out, want, atol=1e-6) and "interpreter" in reg.find_backends_with_capability("debug")
+    reg.register("broken", lambda gm, *a: 1 / 0, {"special", "debug"})
+    with pytest.raises(RuntimeError):
+        reg.execute_with_auto_backend(gm, x, require={"special"})
+    gc = T.GraphCache()
+    assert gc.run(gm, x) is gc.run(gm, x) and gc.statistics()["hits"] == 1 and gc.run(gm, x + 1) is not None and gc.statistics()["misses"] == 2
+    # quantisation passes: PTQ error is small but non-zero; QAT ranges receive gradients
+    prep = T.prepare_ptq(gm)
+    with pytest.raises(RuntimeError):
+        T.convert_ptq(prep)
+    for _ in range(4):
+        prep(torch.randn(32, 8))
+    q8, q4 = T.convert_ptq(prep, 8), T.convert_ptq(prep, 4)
+    e8, e4 = T.quantization_error(gm, q8, x), T.quantization_error(gm, q4, x)
+    assert 0 < e8["mse"] < e4["mse"] and e8["sqnr_db"] > 25 > e4["sqnr_db"]
+    qat = T.prepare_qat(gm, torch.randn(32, 8))
+    qat(x).sum().backward()
+    ranges = [p for n, p in qat.named_parameters() if n.endswith("range")]
+    assert len(ranges) == 6 and all(p.grad is not None for p in ranges) and qat.a.weight.grad.abs().sum() > 0
+    # architecture search improves on the initial population and avoids the "zero" op on a learnable target
+    xs = torch.randn(128, 4)
+    ys = torch.tanh(xs @ torch.randn(4, 2))
+    nas = T.ArchitectureSearch(4, 2, dim=8, depth=2, seed=0)
+    best, fit = nas.search((xs[:96], ys[:96]), (xs[96:], ys[96:]), population=6, generations=2, steps=40)
+    assert nas.history[-1] <= nas.history[0] and fit < 0.1 and not all(g["op"] == "zero" and not g["skip"] for g in best)
