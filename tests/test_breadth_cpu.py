@@ -2277,3 +2277,175 @@ def test_fx_tools_codegen_analysis_rewrite_shapes_editor_memory_placement_quant_
     nas = T.ArchitectureSearch(4, 2, dim=8, depth=2, seed=0)
     best, fit = nas.search((xs[:96], ys[:96]), (xs[96:], ys[96:]), population=6, generations=2, steps=40)
     assert nas.history[-1] <= nas.history[0] and fit < 0.1 and not all(g["op"] == "zero" and not g["skip"] for g in best)
+
+
+def test_package_operations_delta_backup_mirrors_replication_security_governance(tmp_path):
+    import json
+    import os
+    from torsh_b200 import package_ops as P
+    from torsh_b200.hub import Package
+    rng = __import__("random").Random(0)
+    blob = bytes(rng.randrange(256) for _ in range(20000))
+    v1 = Package("demo", "1.0.0", {"numlib": "1.2.0"})
+    v1.add_bytes("weights.bin", blob)
+    v1.add_bytes("notes.txt", b"first release\n" * 50)
+    v1.add_source("model", "def f(x):\n    return x + 1\n")
+    v1.add_model(torch.nn.Linear(3, 2))
+    v2 = Package("demo", "1.1.0", {"numlib": "1.3.0"})
+    v2.files = dict(v1.files)
+    v2.files["weights.bin"] = blob[:7000] + b"PATCHED" + blob[7100:] + b"tail"
+    v2.files["new.txt"] = b"added"
+    del v2.files["notes.txt"]
+    patch = P.create_patch(v1, v2)
+    kinds = {op[1]: op[0] for op in patch.operations}
+    assert kinds == {"notes.txt": "delete", "new.txt": "add", "weights.bin": "modify"} and patch.size() < 1500
+    patch.save(tmp_path / "p.delta")
+    back = P.apply_patch(v1, P.DeltaPatch.load(tmp_path / "p.delta"))
+    assert back.files == v2.files and back.version == "1.1.0" and back.dependencies == {"numlib": "1.3.0"}
+    with pytest.raises(ValueError):
+        P.apply_patch(v2, patch)
+    patch.operations = [op for op in patch.operations if op[0] != "add"]
+    with pytest.raises(IOError):
+        P.apply_patch(v1, patch)
+    v3 = Package("demo", "1.2.0"); v3.files = dict(v2.files); v3.files["weights.bin"] = bytes(rng.randrange(256) for _ in range(20000))
+    assert {op[1]: op[0] for op in P.create_patch(v2, v3).operations}["weights.bin"] == "replace"
+    # compression, optimisation, diagnostics
+    comp = P.AdvancedCompressor()
+    assert comp.algorithm_for_resource("weights.bin", blob) == "none" and comp.algorithm_for_resource("a.txt", b"abc" * 5000) != "none"
+    algo, out = comp.compress_resource("a.txt", b"abc" * 5000)
+    assert P.decompress_data(out, algo) == b"abc" * 5000 and comp.overall_ratio() < 0.05 and comp.space_saved() > 14000
+    assert set(P.AdvancedCompressor.benchmark_algorithms(b"hello world " * 400)) == {"zlib", "bz2", "lzma"}
+    v1.add_bytes("copy_of_weights.bin", blob)
+    rep = P.PackageOptimizer().analyze(v1)
+    assert rep["duplicate_groups"] == [["copy_of_weights.bin", "weights.bin"]] or rep["duplicate_groups"] == [["weights.bin", "copy_of_weights.bin"]]
+    assert rep["duplicate_bytes"] == 20000 and "notes.txt" in rep["compressible"]
+    slim, aliases = P.PackageOptimizer().optimize(v1)
+    assert aliases == {"weights.bin": "copy_of_weights.bin"} and P.resolve_alias(slim, "weights.bin") == blob
+    assert P.diagnose(v1)["health"] == "healthy"
+    bad = Package("bad name!", "one"); bad.add_source("m", "def (:"); bad.add_bytes("../evil", b"x")
+    d = P.diagnose(bad)
+    assert d["health"] == "broken" and {i["category"] for i in d["issues"]} >= {"manifest", "code", "security"}
+    # lazy resources under a memory budget
+    v1.save(tmp_path / "demo.zip")
+    lz = P.LazyResourceManager(tmp_path / "demo.zip", memory_limit=25000)
+    assert lz.get_resource("weights.bin") == blob and lz.get_resource("weights.bin") is lz.get_resource("weights.bin") and lz.loads == 1
+    lz.get_resource("copy_of_weights.bin")
+    assert not lz.is_loaded("weights.bin") and lz.memory_usage() <= 25000
+    assert b"".join(lz.stream("notes.txt", 64)) == v1.files["notes.txt"]
+    # audit chain and metrics
+    log = P.AuditLogger(tmp_path / "audit.jsonl")
+    seen = []
+    log.add_listener(seen.append)
+    log.log_upload("demo-1.0.0", "ann"); log.log_download("demo-1.0.0", "bob"); log.log_access_denied("demo-1.0.0", "eve")
+    log.log_security_violation("demo-1.0.0", "bad signature")
+    assert log.validate() == [] and len(seen) == 4 and len(log.query(user="eve")) == 1 and log.get_statistics()["denied"] == 1
+    again = P.AuditLogger(tmp_path / "audit.jsonl")
+    assert again.validate() == [] and len(again.events) == 4
+    again.events[1]["user"] = "mallory"
+    assert again.validate() == [1]
+    del again.events[1]
+    assert again.validate()[0] == 1
+    mc = P.MetricsCollector()
+    mc.set_alert_threshold("error_rate", 0.3)
+    for _ in range(3):
+        mc.record_download("demo", "bob", 100)
+    mc.record_error("demo"); mc.record_error("demo")
+    assert mc.get_package_stats("demo")["downloads"] == 3 and mc.get_active_alerts()[0]["metric"] == "error_rate"
+    assert mc.get_time_series("downloads")["count"] == 3 and mc.generate_report()["top_packages"] == ["demo"]
+    # storage, backups with an incremental chain and retention
+    st = P.LocalStorage(tmp_path / "store")
+    st.put("a/b.bin", b"123")
+    assert st.get("a/b.bin") == b"123" and st.list("a/") == ["a/b.bin"] and st.get_metadata("a/b.bin")["size"] == 3
+    with pytest.raises(PermissionError):
+        st.put("../out.bin", b"x")
+    bm = P.BackupManager(st, "incremental")
+    b1 = bm.create_backup(v1, now=0.0)
+    b2 = bm.create_backup(v2, now=86400.0 * 10)
+    assert b2["parent"] == b1["id"] and b2["stored_files"] == ["new.txt", "weights.bin"]
+    assert bm.restore_backup(b2["id"]).files == v2.files and bm.restore_backup(b1["id"]).files == v1.files
+    assert bm.apply_retention_policy(keep_last=1, now=86400.0 * 10) == [] and len(bm.list_backups("demo")) == 2    # parent is still needed
+    assert P.BackupManager(st).list_backups()[1]["id"] == b2["id"]
+    st.put(f"backups/{b1['id']}.bin", b"garbage")
+    assert not bm.verify_backup(b1["id"])["valid"]
+    with pytest.raises(IOError):
+        bm.restore_backup(b2["id"])
+    full = P.BackupManager(P.MemoryStorage(), "full")
+    ids = [full.create_backup(v1, now=86400.0 * i)["id"] for i in range(4)]
+    assert full.apply_retention_policy(keep_days=1.5, now=86400.0 * 3) == ids[:2] and len(full.list_backups()) == 2
+    # mirrors: fail-over and health
+    class Flaky(P.MemoryStorage):
+        def get(self, key): raise IOError("down")
+    good, flaky = P.MemoryStorage(), Flaky()
+    good.put("demo.zip", b"pkg")
+    mm = P.MirrorManager("priority", max_failures=2)
+    mm.add_mirror(P.Mirror("flaky", flaky, priority=10)); mm.add_mirror(P.Mirror("good", good, priority=1))
+    assert mm.select_mirror().name == "flaky" and mm.fetch("demo.zip") == ("good", b"pkg") and mm.fetch("demo.zip")[0] == "good"
+    assert mm.mirrors["flaky"].health == "unhealthy" and mm.failovers == 1 and mm.select_mirror().name == "good"
+    good.delete("demo.zip")
+    with pytest.raises(IOError):
+        mm.fetch("demo.zip")                                                   # good fails, flaky is the last resort and fails again
+    assert mm.mirrors["flaky"].health == "offline" and mm.mirrors["flaky"].requests == 2
+    good.put("demo.zip", b"pkg")
+    third = P.MemoryStorage()
+    mm.add_mirror(P.Mirror("third", third))
+    assert mm.sync(good) == {"flaky": 1, "third": 1} and third.get("demo.zip") == b"pkg"
+    # replication: quorum commit, stale replica repaired, conflict settled
+    rm = P.ReplicationManager("quorum")
+    for n in "abc":
+        rm.add_node(n, P.MemoryStorage())
+    assert rm.replicate_package("demo", b"v1", now=1.0)["status"] == "committed"
+    rm.set_online("c", False)
+    r2 = rm.replicate_package("demo", b"v2", now=2.0)
+    assert r2["status"] == "committed" and r2["acks"] == ["a", "b"] and r2["version"] == 2
+    rm.set_online("b", False)
+    assert rm.replicate_package("demo", b"v3", now=3.0)["status"] == "failed"
+    rm.set_online("b", True); rm.set_online("c", True)
+    assert rm.get_package("demo") == b"v3"
+    assert sorted(rm.synchronize("demo")["repaired"]) == ["b", "c"] and rm.synchronize("demo") == {"repaired": [], "conflicts": 0}
+    rec = json.loads(rm.nodes["a"]["storage"].get("demo")); rec.update(data=b"fork".hex(), sha256=P._sha(b"fork"), time=9.0)
+    rm.nodes["a"]["storage"].put("demo", json.dumps(rec).encode())
+    assert rm.synchronize("demo")["conflicts"] == 1 and rm.get_package("demo") == b"fork" and len(rm.conflicts) == 1
+    # vulnerability scan and sandbox
+    risky = Package("risky", "0.1.0", {"numlib": "1.2.0", "safe": "2.0.0"})
+    risky.add_source("m", "import os, pickle\napi_key = 'sk-1234567890'\ndef run(c):\n    os.system(c)\n    return eval(c)\n")
+    risky.add_bytes("state.pkl", b"\x80\x04N.")
+    adv = [{"package": "numlib", "affected": ">=1.0.0,<1.2.5", "id": "ADV-1", "severity": "critical"}, {"package": "safe", "affected": "<1.0.0", "id": "ADV-2"}]
+    rep = P.VulnerabilityScanner("standard", adv).scan(risky)
+    assert {i["type"] for i in rep["issues"]} == {"risky_call", "embedded_secret", "pickled_payload", "vulnerable_dependency"}
+    assert rep["critical"] == 2 and not rep["passed"] and rep["risk_score"] > 40 and P.VulnerabilityScanner().scan(v2)["passed"]
+    assert len(P.VulnerabilityScanner("lenient", adv).scan(risky)["issues"]) <= len(P.VulnerabilityScanner("strict", adv).scan(risky)["issues"])
+    (tmp_path / "ok").mkdir(); (tmp_path / "ok" / "in.txt").write_text("41")
+    sb = P.Sandbox(read_paths=[tmp_path / "ok"])
+    src = "import math\ndef go(p):\n    return int(open(p).read()) + int(math.sqrt(1))\n"
+    assert sb.execute(src, "go", str(tmp_path / "ok" / "in.txt"))["value"] == 42
+    for bad_src, kind in (("import os\n", "import"), ("open('/etc/hostname').read()\n", "file_read"), (f"open({str(tmp_path / 'ok' / 'x')!r}, 'w')\n", "file_write"),
+                          ("while True:\n    pass\n", "cpu_budget")):
+        box = P.Sandbox(read_paths=[tmp_path / "ok"], max_lines=10000)
+        with pytest.raises(P.SandboxViolation):
+            box.execute(bad_src)
+        assert box.violations[0]["type"] == kind
+    with pytest.raises(NameError):
+        P.Sandbox().execute("eval('1')\n")
+    assert P.Sandbox().execute_package_module(v1, "model", "f", 2)["value"] == 3
+    # lineage and compliance
+    lt = P.LineageTracker()
+    lt.add_lineage("ft-1", "base-1", "fine_tuned_from", dataset="d1")
+    lt.add_lineage("q-1", "ft-1", "quantized_from")
+    with pytest.raises(ValueError):
+        lt.add_lineage("base-1", "q-1")
+    assert lt.get_ancestors("q-1") == ["ft-1", "base-1"] and lt.get_descendants("base-1") == ["ft-1", "q-1"]
+    lt.set_compliance("base-1", "Apache-2.0", pii=True); lt.set_compliance("ft-1", "MIT"); lt.set_compliance("q-1", "proprietary")
+    lt.record_provenance("q-1", "ci", "ann"); lt.record_transformation("q-1", "int8", bits=8)
+    cr = lt.generate_compliance_report("q-1")
+    assert not cr["compliant"] and sum(i["severity"] == "error" for i in cr["issues"]) == 2
+    lt.set_compliance("q-1", "MIT", pii=True)
+    assert lt.generate_compliance_report("q-1")["compliant"] and '"base-1" -> "ft-1"' in lt.export_to_dot() and lt.get_statistics()["roots"] == ["base-1"]
+    # other layouts round-trip the tensors
+    fm = P.FormatCompatibilityManager()
+    from torsh_b200.serialize import model_state as ms
+    want = ms.decode_binary(v1.files["model.trsm"])["parameters"]
+    for fmt in fm.supported_formats:
+        out = fm.export_package(v1, fmt, tmp_path / f"exp_{fmt}")
+        got = ms.decode_binary(fm.import_package(out, fmt).files["model.trsm"])["parameters"]
+        assert {k: (v["shape"], v["data"]) for k, v in got.items()} == {k: (v["shape"], v["data"]) for k, v in want.items()}, fmt
+    assert "numlib==1.2.0" in (tmp_path / "exp_mlflow" / "requirements.txt").read_text()
