@@ -2449,3 +2449,306 @@ def test_package_operations_delta_backup_mirrors_replication_security_governance
         got = ms.decode_binary(fm.import_package(out, fmt).files["model.trsm"])["parameters"]
         assert {k: (v["shape"], v["data"]) for k, v in got.items()} == {k: (v["shape"], v["data"]) for k, v in want.items()}, fmt
     assert "numlib==1.2.0" in (tmp_path / "exp_mlflow" / "requirements.txt").read_text()
+
+
+def test_advanced_optimizers_continual_dp_online_composition_and_analysis():
+    import math
+    import numpy as np
+    from torsh_b200.optim import advanced as A
+    torch.manual_seed(0)
+    # continual learning: task B pulls the weights task A needs toward zero; a penalty on what mattered for A resists it
+    xa, xb = torch.randn(64, 4), torch.randn(64, 4)
+    xa[:, 2:] = 0
+    xb[:, :2] *= 0.3
+    ya, yb = xa @ torch.tensor([[1.0], [-1.0], [0.0], [0.0]]), xb[:, 2:] @ torch.tensor([[2.0], [1.0]])
+    mse = torch.nn.functional.mse_loss
+    def train(m, opt, x, y, n=150):
+        for _ in range(n):
+            opt.zero_grad(); mse(m(x), y).backward(); opt.step()
+    forgetting = {}
+    for kind in ("none", "ewc", "mas", "si"):
+        torch.manual_seed(1)
+        m = torch.nn.Linear(4, 1, bias=False)
+        base = torch.optim.SGD(m.parameters(), 0.1)
+        opt = {"none": base, "ewc": A.EWCOptimizer(base, 5.0), "mas": A.MASOptimizer(base, 2.0), "si": A.SIOptimizer(base, 5.0)}[kind]
+        train(m, opt, xa, ya)
+        if kind == "ewc":                                                    # per-sample gradients of noisy labels: the empirical Fisher
+            opt.consolidate(m, [(xa[i:i + 1], ya[i:i + 1] + 0.5 * torch.randn(1, 1)) for i in range(64)], mse)
+            assert opt.importance[0][0, :2].min() > 0.3 and opt.importance[0][0, 2:].abs().max() == 0
+        elif kind == "mas":
+            opt.consolidate(m, [xa])
+        elif kind == "si":
+            opt.consolidate()
+        train(m, opt, xb, yb)
+        forgetting[kind] = float(mse(m(xa), ya).detach())
+        assert float(mse(m(xb), yb).detach()) < 0.2, kind                            # task B is still learned
+    assert forgetting["none"] > 0.5 and all(forgetting[k] < 0.3 * forgetting["none"] for k in ("ewc", "mas", "si")), forgetting
+    assert float(opt.penalty().detach()) > 0
+    # differential privacy: clipping bounds each sample, accountant grows with steps and shrinks with noise
+    m = torch.nn.Linear(4, 1)
+    x, y = torch.randn(16, 4), torch.randn(16, 1)
+    psg = A.per_sample_gradients(m, mse, x, y)
+    mse(m(x), y).backward()
+    assert torch.allclose(psg[0].mean(0), m.weight.grad, atol=1e-5) and psg[0].shape == (16, 1, 4)
+    dp = A.DPOptimizer(torch.optim.SGD(m.parameters(), 0.1), noise_multiplier=0.0, max_grad_norm=0.01, sample_rate=0.1, seed=0)
+    w0 = m.weight.detach().clone(); b0 = m.bias.detach().clone()
+    dp.step(psg)
+    moved = math.sqrt(float((m.weight.detach() - w0).pow(2).sum() + (m.bias.detach() - b0).pow(2).sum()))
+    assert moved <= 0.1 * 0.01 + 1e-7 and dp.clipped_fraction == 1.0
+    acc1, acc2 = A.RDPAccountant(), A.RDPAccountant()
+    acc1.step(0.01, 1.1, 1000); acc2.step(0.01, 2.0, 1000)
+    e1, e2 = acc1.get_epsilon(1e-5), acc2.get_epsilon(1e-5)
+    assert 0.5 < e1 < 3.0 and e2 < e1 and A.RDPAccountant().get_epsilon(1e-5) > 0
+    full = A.RDPAccountant(); full.step(1.0, 1.0, 1)
+    assert full.rdp[0] == pytest.approx(2 / 2.0)                             # alpha / (2 sigma^2) at alpha = 2 without sampling
+    # online and proximal methods
+    w = torch.nn.Parameter(torch.tensor([3.0, -3.0]))
+    ogd = A.OnlineGradientDescent([w], lr=1.0, radius=1.0)
+    for _ in range(50):
+        loss = ((w - torch.tensor([0.5, 0.2])) ** 2).sum()
+        ogd.zero_grad(); loss.backward(); ogd.step(loss.item())
+    assert float(w.detach().norm()) <= 1.0 + 1e-6 and torch.allclose(w.detach(), torch.tensor([0.5, 0.2]), atol=0.05) and ogd.regret(0.0) > 0
+    xs = torch.randn(100, 10)
+    true = torch.zeros(10); true[[1, 4]] = torch.tensor([2.0, -3.0])
+    ys = xs @ true
+    for accel in (False, True):
+        w = torch.nn.Parameter(torch.zeros(10))
+        pg = A.ProximalGradient([w], lr=0.05, prox=A.prox_l1, reg=0.1, accelerated=accel)
+        for _ in range(200):
+            pg.zero_grad(); (0.5 * ((xs @ w - ys) ** 2).mean()).backward(); pg.step()
+        assert int((w.detach().abs() > 1e-6).sum()) == 2 and torch.allclose(w.detach()[[1, 4]], torch.tensor([2.0, -3.0]), atol=0.25)
+    assert torch.equal(A.prox_box(-1, 1)(torch.tensor([-3.0, 0.5]), 0.1), torch.tensor([-1.0, 0.5]))
+    assert A.prox_group_lasso(torch.tensor([[0.1, 0.1], [3.0, 4.0]]), 1.0)[0].abs().sum() == 0
+    # SVRG and SAGA reach the least-squares solution with a constant step where plain SGD keeps jittering
+    sol = torch.linalg.lstsq(xs, (ys + 0.5 * torch.randn(100))[:, None]).solution.squeeze()
+    yn = None
+    torch.manual_seed(2)
+    yn = xs @ true + 0.5 * torch.randn(100)
+    sol = torch.linalg.lstsq(xs, yn[:, None]).solution.squeeze()
+    gfn = lambda ps, idx: [(xs[idx] * (xs[idx] @ ps[0] - yn[idx])[:, None]).mean(0)]
+    w = torch.zeros(10)
+    sv = A.SVRG([w], gfn, 100, lr=0.05)
+    for ep in range(30):
+        sv.snapshot()
+        for i in torch.randperm(100).tolist():
+            sv.step(torch.tensor([i]))
+    assert float((w - sol).norm()) < 1e-3
+    w2 = torch.zeros(10)
+    sg = A.SAGA([w2], gfn, 100, lr=0.03)
+    for ep in range(60):
+        for i in torch.randperm(100).tolist():
+            sg.step(i)
+    assert float((w2 - sol).norm()) < 1e-2
+    # composition
+    def quad_run(make, steps=60):
+        p = torch.nn.Parameter(torch.tensor([2.0, -1.5]))
+        o = make([p])
+        for _ in range(steps):
+            l = (p ** 2).sum()
+            o.zero_grad(); l.backward(); o.step(l.item()) if isinstance(o, A.ComposedOptimizer) else o.step()
+        return p, o
+    p, o = quad_run(lambda ps: A.ComposedOptimizer([torch.optim.Adam(ps, 0.1), torch.optim.SGD(ps, 0.1)], "sequential", phases=[20, 40]))
+    assert o.active == 1 and float(p.detach().norm()) < 0.05
+    p, o = quad_run(lambda ps: A.ComposedOptimizer([torch.optim.SGD(ps, 1e-4), torch.optim.SGD(ps, 0.2)], "switch", criterion=lambda h: len(h) >= 5))
+    assert o.switches == [5] and float(p.detach().norm()) < 1e-3
+    p, o = quad_run(lambda ps: A.ComposedOptimizer([torch.optim.SGD(ps, 0.1), torch.optim.SGD(ps, 0.3)], "average"), steps=1)
+    assert torch.allclose(p.detach(), torch.tensor([2.0, -1.5]) * (1 - 2 * 0.2))
+    p, o = quad_run(lambda ps: A.ComposedOptimizer([torch.optim.SGD(ps, 0.1), torch.optim.SGD(ps, 0.2), torch.optim.SGD(ps, 0.1, maximize=True)], "vote"), steps=1)
+    assert torch.allclose(p.detach(), torch.tensor([2.0, -1.5]) * (1 - 2 * 0.1))
+    assert A.plateau_criterion(3, 0.0)([5, 4, 3, 3, 3, 3]) and not A.plateau_criterion(3, 0.0)([5, 4, 3, 2, 1, 0.5])
+    # analysis
+    def analyse(lr):
+        p = torch.nn.Parameter(torch.tensor([2.0, -1.5]))
+        o = torch.optim.SGD([p], lr)
+        an = A.OptimizerAnalyzer(o)
+        for _ in range(30):
+            l = (p ** 2).sum()
+            o.zero_grad(); l.backward(); an.before_step(); o.step(); an.after_step(l.item())
+        return an.report()
+    good, bad, tiny = analyse(0.1), analyse(1.05), analyse(1e-9)
+    assert good["improved"] and good["convergence_rate"] < -0.1 and not good["recommendations"]
+    assert bad["recommendations"][0]["severity"] == "critical" and "raise" in tiny["recommendations"][0]["message"]
+    def run(cfg):
+        p = torch.nn.Parameter(torch.tensor([2.0, -1.5]))
+        o = torch.optim.SGD([p], cfg["lr"], momentum=cfg["momentum"])
+        for _ in range(20):
+            o.zero_grad(); (p ** 2).sum().backward(); o.step()
+        return float((p.detach() ** 2).sum())
+    sens = A.hyperparameter_sensitivity(run, {"lr": 0.05, "momentum": 0.1})
+    assert sens["ranking"][0] == "lr" and sens["parameters"]["lr"]["sensitivity"] > sens["parameters"]["momentum"]["sensitivity"]
+
+
+def test_advanced_optimizers_storage_skipping_search_and_special_methods(tmp_path):
+    import math
+    import numpy as np
+    from torsh_b200.optim import advanced as A
+    torch.manual_seed(0)
+    # 8-bit / bf16 state tracks fp32 Adam closely at a fraction of the state size
+    x = torch.randn(1000) * torch.logspace(-3, 1, 1000)
+    q = A.quantize_blockwise(x, 64)
+    assert (A.dequantize_blockwise(*q) - x).abs().max() <= x.abs().reshape(-1, 8).amax() and q[0].dtype == torch.int8
+    rel = ((A.dequantize_blockwise(*q) - x).abs() / x.abs().clamp(min=1e-6))
+    assert rel.median() < 0.05
+    xs, ys = torch.randn(256, 32), torch.randn(256, 8)
+    finals = {}
+    for kind in ("fp32", "int8", "bf16"):
+        torch.manual_seed(1)
+        m = torch.nn.Linear(32, 8)
+        o = torch.optim.Adam(m.parameters(), 1e-2) if kind == "fp32" else A.LowPrecisionAdam(m.parameters(), 1e-2, state_dtype=kind, block=64)
+        for _ in range(100):
+            o.zero_grad(); torch.nn.functional.mse_loss(m(xs), ys).backward(); o.step()
+        finals[kind] = torch.nn.functional.mse_loss(m(xs), ys).item()
+        if kind != "fp32":
+            assert o.state_bytes() < (0.3 if kind == "int8" else 0.55) * 2 * 4 * sum(p.numel() for p in m.parameters()) + 64
+    assert abs(finals["int8"] - finals["fp32"]) < 0.02 and abs(finals["bf16"] - finals["fp32"]) < 0.02
+    m = torch.nn.Linear(32, 8)
+    fa = A.MemoryEfficientAdam(m.parameters(), lr=0.02)
+    l0 = torch.nn.functional.mse_loss(m(xs), ys).item()
+    for _ in range(150):
+        fa.zero_grad(); torch.nn.functional.mse_loss(m(xs), ys).backward(); fa.step()
+    assert torch.nn.functional.mse_loss(m(xs), ys).item() < 0.8 * l0
+    fa2 = A.MemoryEfficientAdam(m.parameters(), lr=0.02, beta1=None)
+    torch.nn.functional.mse_loss(m(xs), ys).backward(); fa2.step()
+    assert fa2.state_numel() == 32 + 8 + 8                                  # row + column statistics for the matrix, full for the bias
+    cb = A.CircularBuffer(3)
+    for i in range(5):
+        cb.push(i)
+    assert list(cb) == [2, 3, 4] and len(cb) == 3
+    p = torch.nn.Parameter(torch.tensor([-1.2, 1.0]))
+    lb = A.MemoryEfficientLBFGS([p], history=5)
+    def rosen():
+        p.grad = None
+        l = (1 - p[0]) ** 2 + 100 * (p[1] - p[0] ** 2) ** 2
+        l.backward()
+        return l
+    for _ in range(60):
+        lb.step(rosen)
+    assert torch.allclose(p.detach(), torch.ones(2), atol=1e-3) and len(lb.pairs) == 5
+    # memory-mapped state equals in-memory Adam and survives re-opening
+    torch.manual_seed(3)
+    a = torch.nn.Parameter(torch.randn(5, 3)); b = torch.nn.Parameter(a.detach().clone())
+    oa, ob = A.MemoryMappedAdam([a], tmp_path / "adam.state", lr=0.01), torch.optim.Adam([b], 0.01)
+    for i in range(5):
+        g = torch.randn(5, 3)
+        a.grad, b.grad = g.clone(), g.clone()
+        oa.step(); ob.step()
+        if i == 2:
+            oa = A.MemoryMappedAdam([a], tmp_path / "adam.state", lr=0.01)                 # a new process would do the same
+    assert torch.allclose(a, b, atol=1e-6) and (tmp_path / "adam.state").stat().st_size == (2 * 15 + 1) * 4
+    # lazy and sparse updates
+    big, small = torch.nn.Parameter(torch.ones(4) * 100), torch.nn.Parameter(torch.ones(4) * 0.01)
+    lz = A.LazyUpdateOptimizer(torch.optim.SGD([big, small], 0.1), threshold=0.05, max_delay=4)
+    for _ in range(4):
+        big.grad, small.grad = torch.ones(4), torch.ones(4)
+        lz.step()
+    assert lz.statistics() == {"applied": 5, "skipped": 3, "skip_rate": 3 / 8} and torch.allclose(big.detach(), torch.full((4,), 99.9))
+    w = torch.nn.Parameter(torch.zeros(100))
+    target = torch.randn(100)
+    sp = A.SparseUpdateOptimizer(torch.optim.SGD([w], 0.08), density=0.1)     # residuals apply ~10 steps at once: lr * delay < 1
+    for _ in range(400):
+        w.grad = (w.detach() - target)
+        sp.step()
+    st = sp.statistics()
+    assert float((w.detach() - target).norm()) < 0.05 * float(target.norm()) and 0.09 < st["density"] < 0.12 and st["coverage"] == 1.0
+    # state-dict tools
+    m = torch.nn.Linear(16, 16)
+    o = torch.optim.SGD(m.parameters(), 0.1, momentum=0.9)
+    m(torch.randn(2, 16)).sum().backward(); o.step()
+    sd = o.state_dict()
+    blob = A.StateDictManager.compress(sd)
+    assert torch.equal(A.StateDictManager.decompress(blob)["state"][0]["momentum_buffer"], sd["state"][0]["momentum_buffer"])
+    assert A.StateDictManager.memory_estimate(sd) == {"total_bytes": (256 + 16) * 4, "by_key": {"momentum_buffer": (256 + 16) * 4}}
+    conv = A.StateDictManager.convert(sd, {"momentum_buffer": "exp_avg"}, {"exp_avg_sq": lambda st: torch.zeros_like(st["exp_avg"]), "step": lambda st: torch.tensor(1.0)})
+    adam = torch.optim.Adam(m.parameters(), 1e-3)
+    conv["param_groups"] = adam.state_dict()["param_groups"]
+    adam.load_state_dict(conv)
+    assert torch.equal(adam.state[m.weight]["exp_avg"], sd["state"][0]["momentum_buffer"])
+    sd2 = A.StateDictManager.decompress(blob); sd2["state"][0]["momentum_buffer"] = sd2["state"][0]["momentum_buffer"] * 3
+    assert torch.allclose(A.StateDictManager.merge([sd, sd2])["state"][0]["momentum_buffer"], sd["state"][0]["momentum_buffer"] * 2)
+    # hyper-parameter tuner: halving finds a good lr with less budget than random search at full budget
+    def objective(cfg, budget):
+        p = torch.nn.Parameter(torch.tensor([2.0, -1.5]))
+        o = torch.optim.SGD([p], cfg["lr"], momentum=cfg["momentum"])
+        for _ in range(budget):
+            o.zero_grad(); (p ** 2).sum().backward(); o.step()
+        v = float((p.detach() ** 2).sum())
+        return v if math.isfinite(v) else 1e30
+    space = {"lr": ("log", 1e-4, 0.9), "momentum": ("choice", [0.0, 0.5, 0.9])}
+    rnd = A.HyperparameterTuner(space, "random", seed=0).tune(objective, n_trials=9, budget=27)
+    hal = A.HyperparameterTuner(space, "halving", seed=0).tune(objective, n_trials=9, budget=27, min_budget=3, eta=3)
+    assert hal["budget_spent"] == 3 * 9 + 9 * 3 + 27 * 1 < rnd["budget_spent"] == 243 and hal["best_loss"] < 1e-3 and rnd["best_loss"] < 1e-3
+    grid = A.HyperparameterTuner(space, "grid").grid(3)
+    assert len(grid) == 9 and grid[0]["lr"] == pytest.approx(1e-4)
+    assert A.HyperparameterTuner(space, "random", seed=0).tune(objective, n_trials=9, budget=5, early_stopping_patience=2)["trials"] <= 9
+    # learned optimizer: meta-training lowers the unrolled loss, and the trained rule optimises an unseen quadratic
+    no = A.NeuralOptimizer()
+    hist = no.meta_train(iters=120)
+    assert np.mean(hist[-10:]) < 0.7 * np.mean(hist[:10])
+    p = torch.nn.Parameter(torch.tensor([1.5, -2.0, 0.7]))
+    scale, state = torch.tensor([0.5, 1.0, 2.0]), {}
+    start = float((0.5 * scale * p.detach() ** 2).sum())
+    for _ in range(40):
+        p.grad = None
+        (0.5 * scale * p ** 2).sum().backward()
+        no.apply([p], state)
+    assert float((0.5 * scale * p.detach() ** 2).sum()) < 0.5 * start
+    mo = A.MetaOptimizer()
+    assert mo.recommend({"a": 1.0})["optimizer"] == "adam"
+    noisy, clean = torch.randn(8, 50) + 0.1, torch.ones(8, 50) + 0.001 * torch.randn(8, 50)
+    fn, fc = A.MetaOptimizer.characterize(noisy), A.MetaOptimizer.characterize(clean)
+    assert fn["noise"] > 10 * fc["noise"]
+    mo.record(fn, {"optimizer": "adam", "lr": 1e-3}, 0.1); mo.record(fc, {"optimizer": "sgd", "lr": 0.1}, 0.1)
+    assert mo.recommend(A.MetaOptimizer.characterize(torch.randn(8, 50) + 0.1))["optimizer"] == "adam"
+    assert mo.recommend(A.MetaOptimizer.characterize(torch.ones(8, 50)))["optimizer"] == "sgd"
+    # robustness: NaN gradients are skipped, spikes roll back and halve the learning rate
+    p = torch.nn.Parameter(torch.tensor([1.0, 1.0]))
+    rb = A.RobustnessManager(torch.optim.SGD([p], 0.1), max_grad_norm=0.5, snapshot_every=2)
+    p.grad = torch.tensor([float("nan"), 1.0])
+    assert rb.step(1.0) == "skipped" and torch.equal(p.detach(), torch.ones(2))
+    for _ in range(6):
+        p.grad = torch.tensor([3.0, 4.0])
+        assert rb.step(1.0) == "ok"
+    assert rb.stats["clipped"] == 6 and torch.allclose(p.detach(), torch.ones(2) - 6 * 0.1 * torch.tensor([0.3, 0.4]), atol=1e-5)
+    keep = p.detach().clone()
+    p.grad = torch.tensor([1.0, 1.0])
+    assert rb.step(100.0) == "rolled_back" and rb.get_lr() == [0.05] and torch.allclose(p.detach(), keep)
+    # energy accounting with a fake meter and clock
+    clock = iter(np.arange(0, 100, 1.0))
+    watts = iter([500, 1200, 1200, 1200, 1200, 500, 500, 500])
+    p = torch.nn.Parameter(torch.zeros(1)); p.grad = torch.ones(1)
+    ea = A.EnergyAwareOptimizer(torch.optim.SGD([p], 0.1), lambda: next(watts), carbon_intensity=360.0, power_cap=1000.0, clock=lambda: float(next(clock)))
+    did = [ea.step() for _ in range(6)]
+    assert did == [True, False, False, False, True, True] and ea.metrics()["steps"] == 3
+    assert ea.energy_j == pytest.approx(500 + 4 * 1200 + 500) and ea.carbon_g == pytest.approx(5800 / 3.6e6 * 360)
+    ea.budget = 0.0001
+    with pytest.raises(RuntimeError):
+        ea.step()
+    # STDP: pre-before-post potentiates, post-before-pre depresses; event-driven SGD fires only on large accumulations
+    w = torch.full((1, 1), 0.5)
+    st = A.STDPOptimizer(w)
+    st.step(torch.tensor([1]), torch.tensor([0])); st.step(torch.tensor([0]), torch.tensor([1]))
+    assert float(w) > 0.5
+    w2 = torch.full((1, 1), 0.5)
+    st = A.STDPOptimizer(w2)
+    st.step(torch.tensor([0]), torch.tensor([1])); st.step(torch.tensor([1]), torch.tensor([0]))
+    assert float(w2) < 0.5
+    p = torch.nn.Parameter(torch.zeros(2))
+    ev = A.EventDrivenOptimizer([p], lr=1.0, threshold=0.25)
+    for _ in range(3):
+        p.grad = torch.tensor([0.1, 0.3])
+        ev.step()
+    assert torch.allclose(p.detach(), torch.tensor([-0.3, -0.9])) and ev.events == 4 and ev.event_rate() == pytest.approx(4 / 6)
+    # quantum-inspired searches on a multimodal function and a bit-counting problem
+    rast = lambda v: float(10 * len(v) + (v ** 2 - 10 * np.cos(2 * np.pi * v)).sum())
+    for algo in (A.QuantumAnnealing(2, seed=0), A.QuantumPSO(2, seed=0)):
+        r = algo.minimize(rast)
+        assert r["fun"] < 1.1 and np.abs(r["x"]).max() < 1.1, type(algo).__name__
+    pattern = np.array([1, 0, 1, 1, 0, 0, 1, 0, 1, 1, 1, 0])
+    r = A.QuantumGeneticAlgorithm(12, seed=0).maximize(lambda b: float((b == pattern).sum()))
+    assert r["fitness"] >= 11
+    # step-for-step agreement of this package's optimizers with torch.optim
+    from torsh_b200.optim import extra
+    v = A.CrossFrameworkValidator()
+    assert v.validate(lambda ps: extra.RAdam(ps, 1e-2), lambda ps: torch.optim.RAdam(ps, 1e-2))["passed"]
+    assert v.validate(lambda ps: A.LowPrecisionAdam(ps, 1e-2, state_dtype="bf16"), lambda ps: torch.optim.Adam(ps, 1e-2))["max_abs_diff"] < 5e-3
+    assert not v.validate(lambda ps: torch.optim.SGD(ps, 0.1), lambda ps: torch.optim.SGD(ps, 0.2))["passed"]

@@ -5,7 +5,7 @@ from .extra import (ASGD, FTRL, LARS, LBFGS, AccumulatingOptimizer, AdaBelief, A
                     ScheduleFreeSGD, SophiaG, SparseAdam, Yogi)
 from .flat import FlatAdamW, FlatParameters
 from .fused import LAMB, SGD, Adam, AdamW
-from . import checkpointing, distributed, gradient_free, mixed_precision, second_order
+from . import advanced, checkpointing, distributed, gradient_free, mixed_precision, second_order
 from .gradient_free import BayesianOptimizer, EvolutionStrategy, NelderMead, RandomSearch
 from .distributed import AsyncSGD, DistributedOptimizer, ElasticAveragingSGD
 from .mixed_precision import (AutocastModel, BF16Config, BF16Trainer, DynamicLossScaler, GradScaler, MixedPrecisionConfig,
