@@ -2752,3 +2752,171 @@ def test_advanced_optimizers_storage_skipping_search_and_special_methods(tmp_pat
     assert v.validate(lambda ps: extra.RAdam(ps, 1e-2), lambda ps: torch.optim.RAdam(ps, 1e-2))["passed"]
     assert v.validate(lambda ps: A.LowPrecisionAdam(ps, 1e-2, state_dtype="bf16"), lambda ps: torch.optim.Adam(ps, 1e-2))["max_abs_diff"] < 5e-3
     assert not v.validate(lambda ps: torch.optim.SGD(ps, 0.1), lambda ps: torch.optim.SGD(ps, 0.2))["passed"]
+
+
+def test_vision_ops_color_filters_geometry_roi_and_metrics():
+    import colorsys
+    import numpy as np
+    from scipy import ndimage
+    import torchvision
+    from torsh_b200.vision import ops as V
+    torch.manual_seed(0)
+    img = torch.rand(2, 3, 24, 32)
+    # colour spaces against colorsys / round trips
+    hsv = V.rgb_to_hsv(img)
+    px = img[0, :, 5, 7].tolist()
+    assert hsv[0, :, 5, 7].tolist() == pytest.approx(colorsys.rgb_to_hsv(*px), abs=1e-5)
+    assert torch.allclose(V.hsv_to_rgb(hsv), img, atol=1e-5) and torch.allclose(V.yuv_to_rgb(V.rgb_to_yuv(img)), img, atol=1e-5)
+    lab = V.rgb_to_lab(torch.tensor([1.0, 1.0, 1.0]).reshape(3, 1, 1))
+    assert lab.flatten().tolist() == pytest.approx([100.0, 0.0, 0.0], abs=0.01)
+    assert V.rgb_to_lab(torch.tensor([1.0, 0.0, 0.0]).reshape(3, 1, 1)).flatten().tolist() == pytest.approx([53.24, 80.09, 67.20], abs=0.05)
+    assert torch.allclose(V.adjust_hue(img, 1.0), img, atol=1e-5) and torch.allclose(V.adjust_saturation(img, 0.0)[:, 0], V.rgb_to_grayscale(img)[:, 0], atol=1e-6)
+    assert torch.allclose(V.adjust_contrast(img, 1.0), img) and V.adjust_brightness(img, 2.0).max() <= 1.0
+    assert torch.allclose(V.gamma_correction(img, 1.0), img) and V.normalize_imagenet(img).shape == img.shape
+    z = V.zscore(img)
+    assert torch.allclose(z.mean((-2, -1)), torch.zeros(2, 3), atol=1e-5) and torch.allclose(z.std((-2, -1)), torch.ones(2, 3), atol=1e-4)
+    h = V.compute_histogram(img, 16)
+    assert h.shape == (2, 3, 16) and torch.all(h.sum(-1) == 24 * 32)
+    assert np.allclose(h[0, 0].numpy(), np.histogram(img[0, 0].numpy(), 16, (0, 1))[0])
+    dark = img ** 3
+    eq = V.histogram_equalization(dark)
+    assert abs(float(eq.mean()) - 0.5) < 0.1 and float(dark.mean()) < 0.3 and eq.min() >= 0 and eq.max() <= 1
+    assert (eq[0, 0].flatten()[dark[0, 0].flatten().argsort()].diff() >= -1e-6).all()                   # monotone mapping
+    cl = V.clahe(dark, tiles=(2, 2), clip_limit=2.0)
+    assert cl.shape == dark.shape and float(cl.std()) > float(dark.std()) and float(cl.mean()) < float(eq.mean()) + 0.2
+    # filters against scipy.ndimage
+    g = img[0, 0]
+    npg = g.numpy()
+    assert np.allclose(V.gaussian_blur(g[None], 1.5)[0].numpy(), ndimage.gaussian_filter(npg, 1.5, mode="mirror", truncate=3.0 + 1e-6), atol=2e-3)
+    gx, gy = V.sobel(g[None])
+    assert np.allclose(gx[0].numpy(), ndimage.sobel(npg, axis=1, mode="mirror"), atol=1e-5) and np.allclose(gy[0].numpy(), ndimage.sobel(npg, axis=0, mode="mirror"), atol=1e-5)
+    assert np.allclose(V.prewitt(g[None])[0][0].numpy(), ndimage.prewitt(npg, axis=1, mode="mirror"), atol=1e-5)
+    assert np.allclose(V.laplacian(g[None])[0].numpy(), ndimage.laplace(npg, mode="mirror"), atol=1e-5)
+    assert np.allclose(V.median_filter(g[None], 3)[0].numpy(), ndimage.median_filter(npg, 3, mode="mirror"))
+    assert np.allclose(V.erosion(g[None], 3)[0].numpy(), ndimage.grey_erosion(npg, 3, mode="nearest")) and np.allclose(V.dilation(g[None], 5)[0].numpy(), ndimage.grey_dilation(npg, 5, mode="nearest"))
+    assert np.allclose(V.opening(g[None])[0].numpy(), ndimage.grey_opening(npg, 3, mode="nearest")) and np.allclose(V.closing(g[None])[0].numpy(), ndimage.grey_closing(npg, 3, mode="nearest"))
+    assert (V.morphological_gradient(g[None]) >= 0).all() and (V.top_hat(g[None]) >= -1e-7).all() and V.box_blur(img, 3).shape == img.shape
+    step = torch.zeros(1, 20, 20); step[:, :, 10:] = 1.0
+    noisy = (step + 0.05 * torch.randn(1, 20, 20)).clamp(0, 1)
+    bl = V.bilateral_filter(noisy, 5, 2.0, 0.2)
+    assert float(bl[:, :, :8].std()) < 0.6 * float(noisy[:, :, :8].std()) and float(bl[0, 10, 10] - bl[0, 10, 9]) > 0.8     # smooths, keeps the edge
+    assert float((V.unsharp_mask(V.gaussian_blur(step, 1.0), 1.0, 1.0) - step).abs().mean()) < float((V.gaussian_blur(step, 1.0) - step).abs().mean())
+    sq = torch.zeros(1, 32, 32); sq[:, 8:24, 8:24] = 1.0
+    edges = V.canny(sq, 0.1, 0.3, 1.0)
+    ring = (V.dilation(sq, 5) - V.erosion(sq, 5)) > 0
+    assert edges.dtype == torch.bool and 40 <= int(edges.sum()) <= 80 and not (edges & ~ring).any() and not edges[0, 14:18, 14:18].any()
+    assert float(V.sobel_edge_detection(sq)[0, 16, 16]) == 0 and float(V.sobel_edge_detection(sq)[0, 16, 8]) > 1
+    # geometry
+    assert torch.equal(V.horizontal_flip(V.horizontal_flip(img)), img) and V.center_crop(img, (10, 12)).shape == (2, 3, 10, 12)
+    assert torch.equal(V.crop_region(img, 2, 3, 4, 5), img[..., 2:6, 3:8]) and V.pad(img, (1, 2, 3, 4)).shape == (2, 3, 31, 35)
+    assert V.resize(img, (12, 16)).shape == (2, 3, 12, 16) and torch.allclose(V.resize(img, (24, 32)), img, atol=1e-6)
+    sqi = torch.rand(1, 16, 16)
+    assert torch.allclose(V.rotate(sqi, 90.0), torch.rot90(sqi, 1, (-2, -1)), atol=1e-5) and torch.allclose(V.rotate(sqi, 0.0), sqi, atol=1e-6)
+    r180 = V.rotate(img, 180.0)
+    assert torch.allclose(r180, img.flip(-1).flip(-2), atol=1e-5)
+    tr = V.translate(sqi, 3, -2)
+    assert torch.allclose(tr[:, :14, 3:], sqi[:, 2:, :13], atol=1e-5) and float(tr[:, :, :3].abs().sum()) == 0
+    hm = torch.tensor([[1.0, 0, 2.0], [0, 1.0, 1.0], [0, 0, 1.0]])
+    wp = V.warp_perspective(sqi, hm)
+    assert torch.allclose(wp[:, :15, :14], sqi[:, 1:, 2:], atol=1e-5)
+    sc = V.warp_affine(sqi, V.affine_grid_matrix(scale=2.0))
+    assert torch.allclose(sc[:, ::2, ::2][:, 1:-1, 1:-1], F.interpolate(sqi[None], scale_factor=2.0, mode="bilinear", align_corners=False)[0][:, 8:24:2, 8:24:2][:, 1:-1, 1:-1], atol=1e-5) if (F := torch.nn.functional) else True
+    # boxes and RoI ops against torchvision
+    b = torch.tensor([[2.0, 3.0, 10.0, 9.0], [0.0, 0.0, 4.0, 4.0]])
+    for fmt in ("xywh", "cxcywh"):
+        assert torch.allclose(V.convert_bbox_format(V.convert_bbox_format(b, "xyxy", fmt), fmt, "xyxy"), b)
+    assert V.convert_bbox_format(b, "xyxy", "cxcywh")[0].tolist() == [6.0, 6.0, 8.0, 6.0]
+    assert V.clip_bbox(torch.tensor([[-5.0, 2.0, 50.0, 60.0]]), 24, 32).tolist() == [[0.0, 2.0, 32.0, 24.0]] and V.filter_boxes_by_size(b, 5).tolist() == [0]
+    b2 = torch.tensor([[4.0, 4.0, 12.0, 12.0], [20.0, 20.0, 22.0, 25.0]])
+    assert torch.allclose(V.generalized_iou(b, b2), torchvision.ops.generalized_box_iou(b, b2), atol=1e-6)
+    feat = torch.randn(2, 4, 16, 16)
+    rois = torch.tensor([[0, 1.0, 2.0, 9.0, 11.0], [1, 0.0, 0.0, 15.0, 15.0], [0, 3.5, 4.25, 7.75, 12.0]])
+    assert torch.allclose(V.roi_align(feat, rois, (3, 3), 1.0, 2), torchvision.ops.roi_align(feat, rois, (3, 3), 1.0, 2, aligned=True), atol=1e-5)
+    assert torch.allclose(V.roi_align(feat, rois, (2, 4), 0.5, 3), torchvision.ops.roi_align(feat, rois, (2, 4), 0.5, 3, aligned=True), atol=1e-5)
+    irois = torch.tensor([[0, 1.0, 2.0, 9.0, 11.0], [1, 0.0, 0.0, 15.0, 15.0]])
+    assert torch.allclose(V.roi_pool(feat, irois, (3, 3)), torchvision.ops.roi_pool(feat, irois, (3, 3)), atol=1e-6)
+    # losses and metrics
+    logits = torch.randn(2, 3, 8, 8, requires_grad=True)
+    tgt = torch.randint(0, 3, (2, 8, 8))
+    perfect = torch.nn.functional.one_hot(tgt, 3).permute(0, 3, 1, 2).float() * 50
+    assert float(V.dice_loss(perfect, tgt)) < 1e-3 and 0.3 < float(V.dice_loss(logits, tgt).detach()) < 1.0
+    V.dice_loss(logits, tgt).backward()
+    assert logits.grad.abs().sum() > 0
+    assert float(V.focal_loss(logits.detach(), tgt, gamma=0.0)) == pytest.approx(float(torch.nn.functional.cross_entropy(logits.detach(), tgt)), rel=1e-5)
+    assert float(V.focal_loss(logits.detach(), tgt, gamma=2.0)) < float(V.focal_loss(logits.detach(), tgt, gamma=0.0))
+    assert float(V.iou_loss(b, b)) == 0 and float(V.iou_loss(b, b2, "giou")) > float(V.iou_loss(b, b2))
+    pred = tgt.clone(); pred[0, :2] = (pred[0, :2] + 1) % 3
+    sm = V.compute_segmentation_metrics(pred, tgt, 3)
+    assert sm["pixel_accuracy"] == pytest.approx(1 - 16 / 128) and 0.6 < sm["mean_iou"] < sm["mean_dice"] < 1
+    from sklearn.metrics import jaccard_score
+    assert sm["per_class_iou"] == pytest.approx(jaccard_score(tgt.flatten().numpy(), pred.flatten().numpy(), average=None).tolist())
+    gt_b, gt_l = torch.tensor([[0.0, 0, 10, 10], [20.0, 20, 30, 30]]), torch.tensor([1, 1])
+    pb = torch.tensor([[0.0, 0, 10, 9], [50.0, 50, 60, 60], [20.0, 21, 30, 30]])
+    dm = V.compute_detection_metrics(pb, torch.tensor([0.9, 0.8, 0.7]), torch.tensor([1, 1, 1]), gt_b, gt_l)
+    assert dm["precision"] == pytest.approx(2 / 3) and dm["recall"] == 1.0 and dm["map"] == pytest.approx(0.5 * 1.0 + 0.5 * 2 / 3)
+    cmx = V.compute_classification_metrics(torch.tensor([[2.0, 1.0, 0.0], [0.0, 1.0, 2.0], [0.1, 0.3, 0.2]]), torch.tensor([0, 1, 1]), topk=(1, 2))
+    assert cmx["top1"] == pytest.approx(2 / 3) and cmx["top2"] == 1.0 and 0 < cmx["macro_f1"] < 1
+
+
+def test_vision_augmentation_policies_and_self_supervised_views():
+    from torsh_b200.vision import augment as A, ops as V
+    torch.manual_seed(0)
+    img = torch.rand(3, 32, 32)
+    for name in A.OPS:
+        out = A._Random(0).apply_op(img, name, 0.5)
+        assert out.shape == img.shape and torch.isfinite(out).all(), name
+    assert torch.equal(A._Random(0).apply_op(img, "identity", 1.0), img) and torch.allclose(A._Random(0).apply_op(img, "invert", 0.3), 1 - img)
+    assert A._posterize(img, 4).unique().numel() <= 16 and torch.allclose(A._solarize(torch.tensor([0.2, 0.8]), 0.5), torch.tensor([0.2, 0.2]))
+    ac = A._autocontrast(0.25 + 0.5 * img)
+    assert ac.amin((-2, -1)).abs().max() < 1e-6 and (ac.amax((-2, -1)) - 1).abs().max() < 1e-6
+    ra = A.RandAugment(n=3, m=9, seed=1)
+    a, b = ra(img), A.RandAugment(n=3, m=9, seed=1)(img)
+    assert torch.equal(a, b) and len(ra.last) == 3 and not torch.equal(a, A.RandAugment(n=3, m=9, seed=2)(img))
+    weak, strong = A.RandAugment(2, 1, ops=["rotate"], seed=0)(img), A.RandAugment(2, 30, ops=["rotate"], seed=0)(img)
+    assert float((weak - img).abs().mean()) < float((strong - img).abs().mean())
+    for pol in ("imagenet", "cifar10"):
+        aa = A.AutoAugment(pol, seed=0)
+        outs = [aa(img) for _ in range(6)]
+        assert all(o.shape == img.shape and o.min() >= 0 and o.max() <= 1 for o in outs) and any(not torch.equal(o, img) for o in outs)
+    assert torch.equal(A.AutoAugment([[("invert", 1.0, 0)]], seed=0)(img), 1 - img) and torch.equal(A.AutoAugment([[("invert", 0.0, 0)]], seed=0)(img), img)
+    am = A.AugMix(seed=0)(img)
+    assert am.shape == img.shape and 0 < float((am - img).abs().mean()) < float((A.RandAugment(3, 20, seed=0)(img) - img).abs().mean()) + 0.2
+    gm = A.GridMask((8, 8), 0.5, seed=0)
+    mk = gm.mask(32, 32)
+    assert mk.float().mean() == pytest.approx(0.75) and torch.equal(mk[:24, :24], mk[8:, 8:]) and (A.GridMask(seed=0)(img) == 0).any()
+    imgs = [torch.full((3, 20, 30), v) for v in (0.1, 0.4, 0.7, 1.0)]
+    boxes = [torch.tensor([[0.0, 0.0, 30.0, 20.0]])] * 3 + [torch.zeros(0, 4)]
+    canvas, mb, src = A.Mosaic(64, seed=3)(imgs, boxes)
+    assert canvas.shape == (3, 64, 64) and sorted(canvas.mul(100).round().unique().tolist()) == [10, 40, 70, 100] and src.tolist() == [0, 1, 2]
+    area = ((mb[:, 2] - mb[:, 0]) * (mb[:, 3] - mb[:, 1]))
+    for i, v in enumerate((0.1, 0.4, 0.7)):
+        assert float(((canvas[0] - v).abs() < 1e-4).sum()) == pytest.approx(float(area[i]))        # the box still covers its whole image
+    g = torch.Generator().manual_seed(0)
+    flat = torch.full((1, 64, 64), 0.5)
+    assert float(A.add_noise(flat, "gaussian", 0.1, g).std()) == pytest.approx(0.1, rel=0.1)
+    sp = A.add_noise(flat, "salt_pepper", 0.2, g)
+    assert float(((sp == 0) | (sp == 1)).float().mean()) == pytest.approx(0.2, abs=0.03)
+    assert float(A.add_noise(flat, "speckle", 0.1, g).std()) == pytest.approx(0.05, rel=0.15) and float(A.add_noise(flat, "poisson", 0.01, g).mean()) == pytest.approx(0.5, abs=0.01)
+    co = A.cutout(torch.ones(1, 32, 32), 8, g)
+    assert 16 <= int((co == 0).sum()) <= 64
+    assert A.RandomAffine(seed=0)(img).shape == img.shape and A.RandomResizedCrop(16, seed=0)(img).shape == (3, 16, 16)
+    # self-supervised views: shapes, determinism per seed, two views differ, positives score above negatives after a few steps
+    v1, v2 = A.SimCLRAugmentation(16, seed=0).generate_pair(img)
+    assert v1.shape == v2.shape == (3, 16, 16) and not torch.equal(v1, v2) and torch.equal(v1, A.SimCLRAugmentation(16, seed=0).generate_pair(img)[0])
+    assert [tuple(v.shape[-2:]) for v in A.SwAVAugmentation(32, 16, 2, 4).generate_views(img)] == [(32, 32)] * 2 + [(16, 16)] * 4
+    assert len(A.DINOAugmentation(32, 16, 6).generate_views(img)) == 8 and A.BYOLAugmentation(16).generate_pair(img)[0].shape == (3, 16, 16)
+    assert A.MoCoAugmentation(16).generate_pair(img)[1].shape == (3, 16, 16)
+    z = torch.nn.functional.normalize(torch.randn(8, 16), dim=1)
+    assert float(A.nt_xent_loss(z, z, 0.1)) < float(A.nt_xent_loss(z, z.roll(1, 0), 0.1)) and float(A.byol_loss(z, z)) == pytest.approx(0.0, abs=1e-6)
+    assert float(A.byol_loss(z, -z)) == pytest.approx(4.0, abs=1e-5)
+    data = torch.rand(8, 3, 16, 16)
+    enc = torch.nn.Sequential(torch.nn.Flatten(), torch.nn.Linear(768, 32))
+    opt = torch.optim.Adam(enc.parameters(), 1e-2)
+    aug = A.SimCLRAugmentation(16, strength=0.3, seed=0)
+    first = None
+    for _ in range(30):
+        pairs = [aug.generate_pair(d) for d in data]
+        loss = A.nt_xent_loss(enc(torch.stack([p[0] for p in pairs])), enc(torch.stack([p[1] for p in pairs])))
+        opt.zero_grad(); loss.backward(); opt.step()
+        first = first if first is not None else loss.item()
+    assert loss.item() < first
