@@ -2920,3 +2920,156 @@ def test_vision_augmentation_policies_and_self_supervised_views():
         opt.zero_grad(); loss.backward(); opt.step()
         first = first if first is not None else loss.item()
     assert loss.item() < first
+
+
+def test_vision_analysis_segmentation_features_spatial_streaming_and_3d(tmp_path):
+    import numpy as np
+    from scipy import ndimage
+    from scipy.spatial import cKDTree
+    from torsh_b200.vision import analysis as N, ops as V
+    torch.manual_seed(0)
+    # connected components against scipy
+    mask = torch.rand(24, 24) > 0.55
+    for conn, st in ((4, None), (8, np.ones((3, 3)))):
+        lab, n = N.connected_components(mask, conn)
+        ref, nref = ndimage.label(mask.numpy(), structure=st)
+        assert n == nref and len(set(zip(lab.flatten().tolist(), ref.flatten().tolist()))) == n + 1
+    # two flat regions with a ramp: region growing with a fixed reference stops at the step
+    img = torch.zeros(1, 20, 20); img[:, :, 10:] = 1.0
+    img = img + 0.02 * torch.randn(1, 20, 20)
+    rg = N.region_growing(img, [(5, 3), (5, 15)], threshold=0.2)
+    assert (rg[:, :10] == 1).all() and (rg[:, 10:] == 2).all()
+    # watershed splits two touching discs along the neck
+    yy, xx = torch.meshgrid(torch.arange(40.0), torch.arange(60.0), indexing="ij")
+    d1, d2 = ((yy - 20) ** 2 + (xx - 20) ** 2).sqrt(), ((yy - 20) ** 2 + (xx - 40) ** 2).sqrt()
+    blobs = (d1 < 13) | (d2 < 13)
+    height = -torch.from_numpy(ndimage.distance_transform_edt(blobs.numpy())).float()
+    markers = torch.zeros(40, 60, dtype=torch.long); markers[20, 20], markers[20, 40], markers[0, 0] = 1, 2, 3
+    ws = N.watershed(height, markers)
+    left, right = ws[20, 5:29], ws[20, 32:55]
+    assert (left == 1).all() and (right == 2).all() and set(ws[blobs].unique().tolist()) >= {1, 2}
+    auto = N.watershed(height)
+    assert auto[20, 20] != auto[20, 40] and (auto > 0).all()
+    # graph cut recovers a noisy square from a few seeds
+    truth = torch.zeros(24, 24, dtype=torch.bool); truth[6:18, 6:18] = True
+    noisy = (truth.float() * 0.6 + 0.2 + 0.15 * torch.randn(24, 24)).clamp(0, 1)
+    fg = torch.zeros_like(truth); fg[10:14, 10:14] = True
+    bg = torch.zeros_like(truth); bg[:2] = True; bg[:, :2] = True
+    seg = N.graph_cuts(noisy, fg, bg, lam=5.0, sigma=0.2)
+    naive = noisy > 0.5
+    assert float((seg == truth).float().mean()) > 0.97 and float((seg == truth).float().mean()) >= float((naive == truth).float().mean())
+    # corners of a square, descriptors and matching under a known homography
+    sq = torch.zeros(1, 48, 48); sq[:, 12:36, 14:34] = 1.0
+    kp = N.detect_corners(V.gaussian_blur(sq, 1.0), max_points=4, min_distance=5)
+    found = sorted((round(x), round(y)) for x, y in kp.xy.tolist())
+    want = sorted([(14, 12), (33, 12), (14, 35), (33, 35)])
+    assert all(abs(a[0] - b[0]) <= 2 and abs(a[1] - b[1]) <= 2 for a, b in zip(found, want))
+    assert len(N.detect_corners(V.gaussian_blur(sq, 1.0), kind="shi_tomasi", max_points=4, min_distance=5).xy) == 4
+    tex = V.gaussian_blur(torch.rand(1, 96, 96), 1.5)
+    tex = (tex - tex.min()) / (tex.max() - tex.min())
+    hm_true = torch.tensor([[1.0, 0.03, 4.0], [-0.02, 1.0, -3.0], [0.0, 0.0, 1.0]])
+    warped = V.warp_perspective(tex, torch.linalg.inv(hm_true))                                # warped(p') = tex(H^-1 p'), so p' = H p
+    k1, k2 = N.detect_corners(tex, max_points=150, border=12), N.detect_corners(warped, max_points=150, border=12)
+    d1, d2 = N.describe(tex, k1), N.describe(warped, k2)
+    assert d1.shape == (len(k1.xy), 128) and torch.allclose(d1.norm(dim=1), torch.ones(len(d1)), atol=1e-4)
+    m = N.match_features(d1, d2, ratio=0.85)
+    assert len(m) >= 20
+    hm, inl = N.ransac_homography(k1.xy[m[:, 0]], k2.xy[m[:, 1]], threshold=2.0, iters=300)
+    assert inl.float().mean() > 0.6
+    probe = torch.tensor([[20.0, 20.0], [70.0, 30.0], [40.0, 80.0]])
+    assert (N.apply_homography(hm, probe) - N.apply_homography(hm_true, probe)).norm(dim=1).max() < 1.5
+    pts = torch.rand(12, 2) * 50
+    assert torch.allclose(N.fit_homography(pts, N.apply_homography(hm_true, pts)), hm_true, atol=1e-3)
+    ms = N.detect_multiscale(tex, levels=2, max_points=50)
+    assert set(ms.scale.unique().tolist()) == {1.0, 1.5} and ms.xy.max() < 96
+    # template matching: exact location with score 1, matcher keeps peaks above threshold
+    tmpl = tex[0, 30:42, 50:66]
+    ncc = N.match_template(tex, tmpl)
+    assert divmod(int(ncc.argmax()), ncc.shape[1]) == (30, 50) and float(ncc.max()) == pytest.approx(1.0, abs=1e-4) and float(ncc.min()) >= -1.0001
+    tm = N.TemplateMatcher(0.95); tm.add_template("t", tmpl)
+    hits = tm.match_templates(tex)
+    assert hits[0]["x"] == 50 and hits[0]["y"] == 30 and len(hits) == 1
+    assert N.find_similar_patches(tex, tmpl, 1)[0] == [(50, 30)]
+    # k-d tree against scipy
+    cloud = torch.rand(300, 3)
+    tree, ref = N.KDTree(cloud), cKDTree(cloud.numpy())
+    for q in torch.rand(5, 3):
+        idx, dist = tree.find_neighbors(q.numpy(), 5)
+        rd, ri = ref.query(q.numpy(), 5)
+        assert idx == ri.tolist() and dist == pytest.approx(rd.tolist(), abs=1e-6)
+        assert tree.query_region(q.numpy(), 0.2) == sorted(ref.query_ball_point(q.numpy().astype(float), 0.2))
+    # tracker keeps identities through motion, opens and closes tracks
+    tr = N.SpatialObjectTracker(0.3, max_age=1)
+    a, b = torch.tensor([0.0, 0, 10, 10]), torch.tensor([50.0, 50, 60, 60])
+    ids0 = tr.track_objects(torch.stack([a, b]))
+    ids1 = tr.track_objects(torch.stack([b + 2, a + 2]))
+    assert ids0 == [0, 1] and ids1 == [1, 0]
+    ids2 = tr.track_objects(torch.stack([a + 4, torch.tensor([100.0, 100, 110, 110])]))
+    assert ids2 == [0, 2] and tr.get_trajectory(0) == [(5.0, 5.0), (7.0, 7.0), (9.0, 9.0)]
+    tr.track_objects(a[None] + 6); tr.track_objects(a[None] + 8)
+    assert 1 in tr.finished and 0 in tr.tracks and len(tr.get_trajectory(1)) == 2
+    # distortion: correcting with k = 0 is the identity; barrel then its inverse roughly restores the centre
+    assert torch.allclose(N.correct_radial_distortion(tex, 0.0), tex, atol=1e-5)
+    bar = N.correct_radial_distortion(tex, -0.2)
+    assert not torch.allclose(bar, tex, atol=1e-2) and torch.allclose(bar[:, 44:52, 44:52], tex[:, 44:52, 44:52], atol=0.05)
+    flow = torch.zeros(2, 96, 96); flow[0] = 3.0
+    assert torch.allclose(N.warp_by_flow(tex, flow)[:, :, :90], tex[:, :, 3:93], atol=1e-5)
+    shifted = N.warp_by_flow(tex, -flow)                                                          # content moved 3 px to the right
+    mid = N.interpolate_frames(tex, shifted, flow, 0.5)
+    assert float((mid[:, :, 8:88] - N.warp_by_flow(tex, -flow / 2)[:, :, 8:88]).abs().max()) < 1e-4
+    assert N.smooth_flow_field(torch.randn(2, 16, 16)).std() < 0.5
+    pts2 = torch.tensor([[0.0, 0.0], [9.0, 0.0], [0.0, 9.0], [9.0, 9.0]])
+    grid = N.interpolate_to_grid(pts2, torch.tensor([0.0, 1.0, 1.0, 2.0]), 10, 10)
+    assert grid[0, 0] == 0 and grid[9, 9] == 2 and abs(float(grid[4, 5]) - 1.0) < 0.1 and N.interpolate_to_grid(pts2, torch.tensor([0.0, 1.0, 1.0, 2.0]), 10, 10, "nearest")[1, 8] == 1
+    ramp = torch.linspace(0, 1, 20).expand(1, 20, 20).clone()
+    valid = torch.ones(1, 20, 20, dtype=torch.bool); valid[:, 8:12, 8:12] = False
+    filled = N.interpolate_image_gaps(ramp, valid)
+    assert torch.equal(filled[valid], ramp[valid]) and (filled - ramp).abs().max() < 0.03
+    assert N.compute_image_similarity(tex, tex) == pytest.approx(1.0, abs=1e-4) and N.compute_image_similarity(tex, tex.flip(-1)) < 0.5
+    assert N.compute_image_similarity(tex, tex, "psnr") > 100 and N.compute_image_similarity(tex, 1 - tex, "ncc") == pytest.approx(-1.0, abs=1e-4)
+    gal = torch.rand(6, 3, 32, 32)
+    assert N.find_similar_images((gal[4] * 0.9 + 0.05), gal, 2)[0][0] == 4
+    # streaming: drops when full, batches, adapts resolution to a slow consumer with a fake clock
+    now = [0.0]
+    def slow(batch):
+        now[0] += 0.05 * batch.shape[0] * batch.shape[-1] / 64                                   # cost grows with resolution
+        return batch.mean().item()
+    sp = N.StreamProcessor(slow, target_fps=30.0, buffer_size=4, batch_size=2, clock=lambda: now[0])
+    for i in range(6):
+        sp.push_frame(torch.full((3, 80, 80), float(i)))
+    assert sp.dropped == 2 and len(sp) == 4 and [f.index for f in sp.queue] == [2, 3, 4, 5] and sp.is_full()
+    res = sp.process_available()
+    assert [r["indices"] for r in res] == [[2, 3], [4, 5]] and res[0]["resolution"] == (64, 64) and sp.is_empty()
+    for i in range(20):
+        sp.push_frame(torch.rand(3, 80, 80)); sp.push_frame(torch.rand(3, 80, 80)); sp.process_available()
+    st = sp.stats()
+    assert st["resolution"] == (32, 32) and st["processed"] == 44 and st["mean_latency"] < 1 / 30 and sp.is_realtime()
+    keep = N.StreamProcessor(lambda b: 0, buffer_size=2, drop_policy="drop_newest")
+    assert [keep.push_frame(torch.zeros(3, 8, 8)) for _ in range(3)] == [True, True, False] and len(keep.flush()) == 2
+    assert N.FramePreprocessor((8, 8), True, ((0.5,), (0.5,))).preprocess(torch.ones(3, 16, 16)).shape == (1, 8, 8)
+    # 3-D: sphere mesh geometry, sampled cloud, normals, voxel grid, boxes, scene export
+    sph = N.Mesh3D.create_sphere(2.0, 24, 48)
+    assert sph.surface_area() == pytest.approx(4 * np.pi * 4, rel=0.01) and sph.volume() == pytest.approx(4 / 3 * np.pi * 8, rel=0.02)
+    assert (sph.compute_vertex_normals() * torch.nn.functional.normalize(sph.vertices, dim=1)).sum(1).min() > 0.99
+    cube = N.Mesh3D.create_cube(2.0)
+    assert cube.volume() == pytest.approx(8.0) and cube.surface_area() == pytest.approx(24.0) and (cube.compute_face_normals().abs().max(1).values == 1).all()
+    pc = sph.sample_points(2000)
+    assert (pc.points.norm(dim=1) - 2.0).abs().max() < 0.02
+    nrm = pc.estimate_normals(10)
+    assert (nrm * torch.nn.functional.normalize(pc.points, dim=1)).sum(1).mean() > 0.97
+    ds = pc.voxel_downsample(0.5)
+    assert 50 < len(ds) < 400 and ds.points.norm(dim=1).max() <= 2.0 + 1e-5
+    assert len(pc.filter_by_distance((0, 0, 2.0), 1.0)) < 400 and pc.to_tensor().shape == (2000, 6)
+    noisy_pc = N.PointCloud(torch.cat([pc.points, torch.tensor([[30.0, 30.0, 30.0]])]))
+    assert len(noisy_pc.remove_statistical_outliers()) == 2000
+    moved = pc.transform(torch.tensor([[1.0, 0, 0, 5], [0, 1.0, 0, 0], [0, 0, 1.0, 0], [0, 0, 0, 1.0]]))
+    assert moved.centroid()[0] == pytest.approx(5.0, abs=0.1)
+    bb = N.BoundingBox3D.from_points(cube.vertices)
+    assert bb.volume() == 8.0 and bb.contains_point((0.5, 0, 0)) and not bb.contains_point((2, 0, 0)) and bb.corners().shape == (8, 3)
+    assert bb.iou(N.BoundingBox3D(torch.zeros(3), torch.full((3,), 2.0))) == pytest.approx(1 / 15)
+    sc = N.Scene3D(); sc.add_mesh(cube, "cube"); sc.add_point_cloud(ds, "cloud"); sc.add_bounding_box(bb, "box")
+    summ = sc.export_summary()
+    assert summ["faces"] == 12 and summ["points"] == len(ds) and sc.num_objects() == 3
+    sc.export_ply(tmp_path / "s.ply")
+    head = (tmp_path / "s.ply").read_text().splitlines()
+    assert head[2] == f"element vertex {8 + len(ds)}" and head[6] == "element face 12" and len(head) == 9 + 8 + len(ds) + 12
