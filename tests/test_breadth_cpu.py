@@ -3073,3 +3073,175 @@ def test_vision_analysis_segmentation_features_spatial_streaming_and_3d(tmp_path
     sc.export_ply(tmp_path / "s.ply")
     head = (tmp_path / "s.ply").read_text().splitlines()
     assert head[2] == f"element vertex {8 + len(ds)}" and head[6] == "element face 12" and len(head) == 9 + 8 + len(ds) + 12
+
+
+def test_functional_ext_decompositions_wavelets_numerics_interpolation_lazy_and_sampling():
+    import math
+    import numpy as np
+    from scipy import integrate, interpolate, stats
+    from torsh_b200.nn import functional_ext as X
+    torch.manual_seed(0)
+    dd = torch.float64
+    # CP recovers a rank-3 tensor; Tucker recovers a multilinear rank-(2,3,2) tensor; TT-SVD is exact at full rank
+    fac = [torch.randn(n, 3, dtype=dd) for n in (6, 5, 4)]
+    t3 = X.cp_reconstruct(torch.tensor([3.0, 2.0, 1.0], dtype=dd), fac)
+    assert torch.allclose(t3, torch.einsum("r,ir,jr,kr->ijk", torch.tensor([3.0, 2.0, 1.0], dtype=dd), *fac))
+    w, f, err = X.cp_decomposition(t3, 3, iters=500)
+    assert err < 1e-5 and torch.allclose(X.cp_reconstruct(w, f), t3, atol=1e-4) and torch.allclose(f[0].norm(dim=0), torch.ones(3, dtype=dd))
+    assert X.cp_decomposition(t3, 1)[2] > 0.1
+    core0 = torch.randn(2, 3, 2, dtype=dd)
+    mats = [torch.linalg.qr(torch.randn(n, r, dtype=dd)).Q for n, r in ((6, 2), (5, 3), (4, 2))]
+    tk = X.tucker_reconstruct(core0, mats)
+    core, tf, terr = X.tucker_decomposition(tk, (2, 3, 2))
+    assert terr < 1e-10 and core.shape == (2, 3, 2) and all(torch.allclose(m.t() @ m, torch.eye(m.shape[1], dtype=dd), atol=1e-10) for m in tf)
+    assert X.tucker_decomposition(tk, (1, 1, 1))[2] > 0.1
+    full = torch.randn(3, 4, 5, 2, dtype=dd)
+    cores = X.tensor_train(full, max_rank=100)
+    assert torch.allclose(X.tt_reconstruct(cores), full, atol=1e-10) and [c.shape[0] for c in cores] == [1, 3, 10, 2]
+    lowrank = X.tt_reconstruct([torch.randn(1, 3, 2, dtype=dd), torch.randn(2, 4, 2, dtype=dd), torch.randn(2, 5, 1, dtype=dd)])
+    c2 = X.tensor_train(lowrank, max_rank=2)
+    assert torch.allclose(X.tt_reconstruct(c2), lowrank, atol=1e-10) and sum(c.numel() for c in c2) < lowrank.numel()
+    # wavelets: filters are orthonormal, transforms invertible and energy preserving, db2 kills linear trends
+    for name, h in X.WAVELETS.items():
+        h = torch.tensor(h, dtype=dd)
+        assert float(h.sum()) == pytest.approx(math.sqrt(2), abs=1e-10) and float((h * h).sum()) == pytest.approx(1.0, abs=1e-10), name
+        sig = torch.randn(3, 64, dtype=dd)
+        a, d = X.dwt_1d(sig, name)
+        assert torch.allclose(X.idwt_1d(a, d, name), sig, atol=1e-10) and float(a.pow(2).sum() + d.pow(2).sum()) == pytest.approx(float(sig.pow(2).sum()))
+        coeffs = X.wavedec(sig, name, 3)
+        assert [c.shape[-1] for c in coeffs] == [8, 8, 16, 32] and torch.allclose(X.waverec(coeffs, name), sig, atol=1e-10)
+        img = torch.randn(16, 32, dtype=dd)
+        ll, det = X.dwt_2d(img, name)
+        assert ll.shape == (8, 16) and torch.allclose(X.idwt_2d(ll, det, name), img, atol=1e-10)
+    a, d = X.dwt_1d(torch.tensor([1.0, 3.0, 5.0, 9.0]), "haar")
+    assert torch.allclose(a, torch.tensor([4.0, 14.0]) / math.sqrt(2)) and torch.allclose(d.abs(), torch.tensor([2.0, 4.0]) / math.sqrt(2))
+    lin = torch.arange(64, dtype=dd)
+    assert X.dwt_1d(lin, "db2")[1][:-1].abs().max() < 1e-10 and X.dwt_1d(lin, "haar")[1].abs().min() > 0.1     # two vanishing moments
+    n = 512
+    tt = torch.arange(n, dtype=dd)
+    chirp = torch.sin(2 * math.pi * tt / 16) * (tt < 256) + torch.sin(2 * math.pi * tt / 64) * (tt >= 256)
+    scales = [16 * 6 / (2 * math.pi), 64 * 6 / (2 * math.pi)]
+    cw = X.cwt(chirp, scales).abs()
+    assert cw.shape == (2, n) and cw[0, 64:192].mean() > 3 * cw[1, 64:192].mean() and cw[1, 320:448].mean() > 3 * cw[0, 320:448].mean()
+    assert X.cwt(chirp, [4.0], "mexican_hat").shape == (1, n)
+    clean = torch.sin(2 * math.pi * tt / 128)
+    noisy = clean + 0.3 * torch.randn(n, dtype=dd)
+    assert float((X.wavelet_denoise(noisy) - clean).pow(2).mean()) < 0.35 * float((noisy - clean).pow(2).mean())
+    # calculus and roots against scipy
+    xs = torch.linspace(0, math.pi, 101, dtype=dd)
+    assert float(X.trapz(torch.sin(xs), xs)) == pytest.approx(integrate.trapezoid(np.sin(xs.numpy()), xs.numpy()))
+    assert float(X.simps(torch.sin(xs), float(xs[1]))) == pytest.approx(2.0, abs=1e-7) and float(X.simps(torch.sin(xs[:100]), float(xs[1]))) == pytest.approx(float(1 - torch.cos(xs[99])), abs=1e-5)
+    assert torch.allclose(X.cumtrapz(torch.sin(xs), xs), torch.from_numpy(integrate.cumulative_trapezoid(np.sin(xs.numpy()), xs.numpy())))
+    assert float(X.gaussian_quad(lambda z: torch.exp(-z * z), -2.0, 3.0, 24)) == pytest.approx(integrate.quad(lambda z: math.exp(-z * z), -2, 3)[0], abs=1e-12)
+    assert X.adaptive_quad(lambda z: math.sqrt(z), 0.0, 1.0, 1e-10) == pytest.approx(2 / 3, abs=1e-7)
+    assert torch.allclose(X.gradient(xs ** 2, float(xs[1]))[1:-1], 2 * xs[1:-1], atol=1e-10)
+    assert float(X.second_derivative(torch.sin, torch.tensor(0.7, dtype=dd))) == pytest.approx(-math.sin(0.7), abs=1e-6)
+    assert float(X.partial_derivative(lambda v: (v[..., 0] ** 2 * v[..., 1]), torch.tensor([2.0, 3.0], dtype=dd), 0)) == pytest.approx(12.0, abs=1e-6)
+    assert X.bisection(lambda z: z ** 3 - 2, 0.0, 2.0) == pytest.approx(2 ** (1 / 3), abs=1e-9)
+    with pytest.raises(ValueError):
+        X.bisection(lambda z: z * z + 1, -1.0, 1.0)
+    assert float(X.newton_raphson(lambda z: z ** 3 - 2, 1.0)) == pytest.approx(2 ** (1 / 3), abs=1e-10)
+    root = X.newton_raphson(lambda v: torch.stack([v[0] ** 2 + v[1] ** 2 - 4, v[0] - v[1]]), [1.0, 0.5])
+    assert torch.allclose(root, torch.full((2,), math.sqrt(2), dtype=dd), atol=1e-9)
+    # transformations
+    m = torch.arange(6.0).reshape(2, 3)
+    assert torch.equal(X.tensor_map(lambda v: v * v + 1, m), m * m + 1) and torch.equal(X.tensor_map(lambda r: r.flip(0), m, 0), m.flip(1))
+    assert torch.equal(X.tensor_zip(lambda a, b: a * b, m, torch.tensor([1.0, 2.0, 3.0])), m * torch.tensor([1.0, 2.0, 3.0]))
+    assert torch.equal(X.tensor_fold(lambda acc, r: acc + r, m, torch.zeros(3)), m.sum(0)) and torch.equal(X.tensor_scan(torch.maximum, m.t().contiguous(), dim=0), m.t().cummax(0).values)
+    assert torch.equal(X.tensor_reduce(torch.add, torch.arange(7.0)[:, None]), torch.tensor([21.0]))
+    assert X.tensor_outer(torch.ones(2), torch.ones(3), torch.ones(4)).shape == (2, 3, 4)
+    assert X.tensor_contract(torch.randn(2, 3, 4), torch.randn(4, 3, 5), [1, 2], [1, 0]).shape == (2, 5)
+    A_, B_, C_ = torch.randn(8, 30, dtype=dd), torch.randn(30, 4, dtype=dd), torch.randn(4, 50, dtype=dd)
+    res, order, cost = X.einsum_optimized("ij,jk,kl->il", A_, B_, C_)
+    assert torch.allclose(res, A_ @ B_ @ C_) and order[0][:2] == ("ij", "jk") and cost == 8 * 30 * 4 + 8 * 4 * 50
+    # gradient penalties
+    critic = torch.nn.Linear(5, 1, bias=False)
+    real, fake = torch.randn(16, 5), torch.randn(16, 5)
+    wn = float(critic.weight.detach().norm())
+    assert X.gradient_penalty(critic, real, fake).item() == pytest.approx((wn - 1) ** 2, rel=1e-4)
+    assert X.r1_gradient_penalty(critic, real).item() == pytest.approx(0.5 * wn * wn, rel=1e-4) == X.r2_gradient_penalty(critic, fake).item()
+    X.gradient_penalty(critic, real, fake).backward()
+    assert critic.weight.grad is not None
+    wm = torch.randn(6, 9)
+    assert float(X.spectral_gradient_penalty(wm, 200)) == pytest.approx(float(torch.linalg.svdvals(wm)[0]), rel=1e-4)
+    assert X.consistency_penalty(critic, real, lambda z: z).item() == 0
+    # interpolation against scipy
+    xp = torch.linspace(0, 5, 11, dtype=dd); fp = torch.sin(xp)
+    xq = torch.tensor([-1.0, 0.3, 2.26, 4.99, 7.0], dtype=dd)
+    assert torch.allclose(X.interp1d(xq, xp, fp), torch.from_numpy(np.interp(xq.numpy(), xp.numpy(), fp.numpy())))
+    assert torch.equal(X.interp1d(torch.tensor([0.2, 0.3], dtype=dd), xp, fp, "nearest"), fp[[0, 1]])
+    xin = torch.linspace(0.1, 4.9, 23, dtype=dd)
+    assert torch.allclose(X.spline1d(xin, xp, fp), torch.from_numpy(interpolate.CubicSpline(xp.numpy(), fp.numpy(), bc_type="natural")(xin.numpy())), atol=1e-10)
+    samples = torch.sin(torch.arange(40, dtype=dd) * 0.3)
+    pos = torch.tensor([5.5, 10.25, 20.0], dtype=dd)
+    assert torch.allclose(X.lanczos_interp1d(pos, samples), torch.sin(pos * 0.3), atol=1e-2) and float(X.lanczos_interp1d(pos, samples)[2]) == pytest.approx(float(samples[20]))
+    cheb = torch.cos(math.pi * (2 * torch.arange(12, dtype=dd) + 1) / 24)
+    runge = lambda z: 1 / (1 + 25 * z * z)
+    xe = torch.linspace(-0.95, 0.95, 7, dtype=dd)
+    assert torch.allclose(X.barycentric_interp(xe, cheb, runge(cheb)), torch.from_numpy(interpolate.BarycentricInterpolator(cheb.numpy(), runge(cheb).numpy())(xe.numpy())), atol=1e-10)
+    assert torch.allclose(X.barycentric_interp(cheb[:3], cheb, runge(cheb)), runge(cheb[:3]))
+    g2 = torch.arange(12.0).reshape(3, 4)
+    assert torch.allclose(X.interp2d(g2, torch.tensor([1.5, 0.0]), torch.tensor([0.5, 2.0])), torch.tensor([3.5, 8.0]))
+    # counting
+    data = torch.tensor([0.5, 1.5, 1.7, 2.0, 3.9, 4.0])
+    hst, edges = X.histogram(data, 4, (0.0, 4.0))
+    assert hst.tolist() == np.histogram(data.numpy(), 4, (0, 4))[0].tolist() == [1, 2, 1, 2]
+    assert float((X.histogram(data, 4, (0.0, 4.0), density=True)[0] * 1.0).sum()) == pytest.approx(1.0)
+    v, c = X.value_counts(torch.tensor([3, 1, 3, 2, 3, 1]))
+    assert v.tolist() == [3, 1, 2] and c.tolist() == [3, 2, 1] and X.bincount(torch.tensor([0, 2, 2]), 4).tolist() == [1, 0, 2, 0]
+    assert X.unique(torch.tensor([2, 1, 2]), return_counts=True)[1].tolist() == [1, 2]
+    # lazy chains
+    base = torch.randn(4, 5)
+    lz = X.lazy(base).add_scalar(1).add_scalar(2).mul_scalar(2).mul_scalar(0.5).relu().relu().sub_scalar(0).tanh()
+    opt = lz.optimize()
+    assert lz.depth() == 8 and [o[0] for o in opt.ops] == ["add_scalar", "relu", "tanh"] and opt.ops[0][1] == 3
+    assert torch.allclose(opt.evaluate(), torch.tanh(torch.relu(base + 3))) and torch.allclose(lz.evaluate(), opt.evaluate())
+    assert torch.allclose(X.lazy(base).mul(X.lazy(base).exp()).sum(1).evaluate(), (base * base.exp()).sum(1)) and X.lazy(base).transpose(0, 1).reshape(-1).evaluate().shape == (20,)
+    # type promotion
+    assert X.promote_types(torch.int32, torch.float16) == torch.float16 and X.promote_multiple_types([torch.uint8, torch.int8, torch.bfloat16]) == torch.bfloat16
+    assert X.can_cast_safely(torch.int32, torch.int64) and not X.can_cast_safely(torch.float32, torch.int32) and not X.can_cast_safely(torch.int64, torch.int32)
+    assert X.get_type_category(torch.bfloat16) == "floating" and X.get_type_precision(torch.int16) == 16 and X.get_type_precision(torch.float64) == 64
+    assert X.result_type(torch.ones(2, dtype=torch.int32), 2.5) == torch.float32 and X.result_type(torch.ones(2, dtype=torch.float16), 3) == torch.float16
+    assert X.result_type(torch.ones(2, dtype=torch.float16), torch.tensor(1.0, dtype=torch.float64)) == torch.float16
+    assert [t.dtype for t in X.promote_tensors(torch.ones(1, dtype=torch.int8), torch.ones(1, dtype=torch.float32))] == [torch.float32] * 2
+    assert X.reduction_result_type(torch.int32, "mean") == torch.float32 and X.reduction_result_type(torch.int8, "sum") == torch.int64 and X.reduction_result_type(torch.float16, "sum") == torch.float16
+    # fusion analysis
+    pats = X.detect_fusible_patterns(["matmul", "add", "relu", "mul", "softmax", "exp", "neg", "tanh", "matmul", "sigmoid", "mul"])
+    assert [(p["start"], p["kernel"]) for p in pats] == [(1, "fused_add_relu_mul"), (5, "generated_elementwise"), (9, "fused_sigmoid_mul")]
+    est = X.fusion_benefit_estimate(["add", "relu", "mul", "exp"], 1 << 24)
+    assert est["speedup"] == pytest.approx(2.0) and est["fused_s"] < est["unfused_s"]
+    af = X.AdaptiveFusion(threshold=1.1)
+    assert af.should_fuse_adaptive("p")
+    af.record_performance("p", 1.0, 1.0); af.record_performance("q", 2.0, 1.0)
+    assert not af.should_fuse_adaptive("p") and af.should_fuse_adaptive("q") and af.history_size() == 2
+    # optimisation routines on Rosenbrock and a quadratic
+    def rosen(v): return (1 - v[0]) ** 2 + 100 * (v[1] - v[0] ** 2) ** 2
+    def rgrad(v): return torch.stack([-2 * (1 - v[0]) - 400 * v[0] * (v[1] - v[0] ** 2), 200 * (v[1] - v[0] ** 2)])
+    x0 = torch.tensor([-1.2, 1.0], dtype=dd)
+    xb, nb = X.bfgs(rosen, rgrad, x0)
+    assert torch.allclose(xb, torch.ones(2, dtype=dd), atol=1e-6) and nb < 60
+    xc, nc = X.conjugate_gradient_minimize(rosen, rgrad, x0, iters=2000)
+    assert torch.allclose(xc, torch.ones(2, dtype=dd), atol=1e-4)
+    Q = torch.tensor([[3.0, 1.0], [1.0, 2.0]], dtype=dd); bq = torch.tensor([1.0, -1.0], dtype=dd)
+    xg, _ = X.gradient_descent(lambda v: 0.5 * v @ Q @ v - bq @ v, lambda v: Q @ v - bq, torch.zeros(2, dtype=dd), lr=0.3, momentum=0.3)
+    assert torch.allclose(xg, torch.linalg.solve(Q, bq), atol=1e-6)
+    d0 = -rgrad(x0)
+    tb = X.backtracking_line_search(rosen, x0, d0, rgrad(x0))
+    tw = X.wolfe_line_search(rosen, rgrad, x0, d0)
+    assert rosen(x0 + tb * d0) < rosen(x0) and rosen(x0 + tw * d0) < rosen(x0) and abs(float(rgrad(x0 + tw * d0) @ d0)) <= 0.9 * abs(float(rgrad(x0) @ d0))
+    # samplers: moments and Kolmogorov-Smirnov against scipy distributions
+    n = 20000
+    ks = lambda s, dist: stats.kstest(s.numpy().astype(np.float64), dist.cdf).pvalue
+    assert ks(X.exponential((n,), 2.0, seed=0), stats.expon(scale=0.5)) > 1e-3 and ks(X.laplace((n,), 1.0, 2.0, seed=1), stats.laplace(1.0, 2.0)) > 1e-3
+    assert ks(X.cauchy((n,), seed=2), stats.cauchy()) > 1e-3 and ks(X.log_normal((n,), 0.0, 0.5, seed=3), stats.lognorm(0.5)) > 1e-3
+    assert ks(X.gamma((n,), 2.5, 2.0, seed=4), stats.gamma(2.5, scale=0.5)) > 1e-3 and ks(X.gamma((n,), 0.4, seed=5), stats.gamma(0.4)) > 1e-3
+    assert ks(X.beta((n,), 2.0, 5.0, seed=6), stats.beta(2, 5)) > 1e-3 and ks(X.truncated_normal((n,), 0, 1, -1, 2, seed=7), stats.truncnorm(-1, 2)) > 1e-3
+    assert float(X.geometric((n,), 0.25, seed=8).mean()) == pytest.approx(4.0, rel=0.05) and float(X.bernoulli((n,), 0.3, seed=9).mean()) == pytest.approx(0.3, abs=0.02)
+    assert float(X.poisson((n,), 3.5, seed=10).mean()) == pytest.approx(3.5, rel=0.03) and float(X.binomial((n,), 10, 0.3, seed=11).var()) == pytest.approx(2.1, rel=0.06)
+    dr = X.dirichlet(torch.tensor([1.0, 2.0, 3.0]), 5000, seed=12)
+    assert torch.allclose(dr.sum(1), torch.ones(5000)) and torch.allclose(dr.mean(0), torch.tensor([1 / 6, 2 / 6, 3 / 6]), atol=0.02)
+    cov = torch.tensor([[2.0, 0.6], [0.6, 1.0]])
+    mv = X.multivariate_normal(torch.tensor([1.0, -1.0]), cov, n, seed=13)
+    assert torch.allclose(torch.cov(mv.t()), cov, atol=0.08) and torch.allclose(mv.mean(0), torch.tensor([1.0, -1.0]), atol=0.05)
+    assert torch.equal(X.uniform((5,), seed=3), X.uniform((5,), seed=3)) and sorted(X.randperm(6, seed=0).tolist()) == list(range(6)) and X.randint((9,), 2, 5, seed=0).max() < 5
+    assert X.multinomial(torch.tensor([0.0, 1.0]), 4, seed=0).tolist() == [1, 1, 1, 1] and X.normal((3,), seed=1).shape == (3,)
