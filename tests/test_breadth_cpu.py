@@ -3245,3 +3245,231 @@ def test_functional_ext_decompositions_wavelets_numerics_interpolation_lazy_and_
     assert torch.allclose(torch.cov(mv.t()), cov, atol=0.08) and torch.allclose(mv.mean(0), torch.tensor([1.0, -1.0]), atol=0.05)
     assert torch.equal(X.uniform((5,), seed=3), X.uniform((5,), seed=3)) and sorted(X.randperm(6, seed=0).tolist()) == list(range(6)) and X.randint((9,), 2, 5, seed=0).max() < 5
     assert X.multinomial(torch.tensor([0.0, 1.0]), 4, seed=0).tolist() == [1, 1, 1, 1] and X.normal((3,), seed=1).shape == (3,)
+
+
+def test_data_samplers_stratified_importance_curriculum_active_and_batching():
+    from collections import Counter
+    from torsh_b200.data import samplers as S
+    torch.manual_seed(0)
+    labels = torch.tensor([0] * 60 + [1] * 30 + [2] * 10)
+    st = S.StratifiedSampler(labels, seed=0)
+    order = list(st)
+    assert sorted(order) == list(range(100)) and len(st) == 100
+    for s in range(0, 100, 10):                                              # every block of ten holds 6 / 3 / 1
+        assert Counter(labels[order[s:s + 10]].tolist()) == {0: 6, 1: 3, 2: 1}
+    st.set_epoch(1)
+    assert list(st) != order
+    sp = S.StratifiedSplit(labels, 0.2)
+    assert Counter(labels[sp.val].tolist()) == {0: 12, 1: 6, 2: 2} and not set(sp.val) & set(sp.train) and len(sp.train) == 80
+    w = torch.tensor([1.0] * 90 + [10.0] * 10)
+    imp = S.ImportanceSampler(w, num_samples=20000, seed=0)
+    draws = torch.tensor(list(imp))
+    assert float((draws >= 90).float().mean()) == pytest.approx(100 / 190, abs=0.02)
+    corr = imp.correction(torch.tensor([0, 95]))
+    assert corr[0] == 1.0 and float(corr[1]) == pytest.approx(0.1, rel=1e-3)
+    imp.update_weights([0], [1000.0])
+    assert float(imp.probabilities()[0]) > 0.8
+    flat = S.ImportanceSampler(w, alpha=0.0)
+    assert torch.allclose(flat.probabilities(), torch.full((100,), 0.01, dtype=torch.float64))
+    diff = torch.rand(100)
+    cu = S.CurriculumSampler(diff, 0.2, full_epoch=4, seed=0)
+    sizes = []
+    for ep in range(6):
+        cu.set_epoch(ep)
+        idx = list(cu)
+        sizes.append(len(idx))
+        assert float(diff[idx].max()) <= float(diff.sort().values[len(idx) - 1]) + 1e-9
+    assert sizes == [20, 40, 60, 80, 100, 100]
+    assert S.CurriculumSampler(diff, 0.2, 4, "root").fraction() == 0.2 and S.CurriculumSampler(diff, 0.2, 4, reverse=True).order[0] == diff.argmax()
+    ex = S.CurriculumSampler(diff, 0.2, 4, "exponential"); ex.set_epoch(2)
+    li = S.CurriculumSampler(diff, 0.2, 4); li.set_epoch(2)
+    assert ex.fraction() < li.fraction()
+    probs = torch.tensor([[0.99, 0.01], [0.5, 0.5], [0.7, 0.3], [0.55, 0.45], [0.9, 0.1]])
+    for strat in ("uncertainty", "margin", "entropy"):
+        al = S.ActiveLearningSampler(5, strat)
+        assert al.query(probs, 2) == [1, 3] and al.unlabelled == {0, 2, 4} and al.query(probs, 1) == [2]
+    feats = torch.tensor([[0.0, 0], [0.1, 0], [5.0, 5], [0.0, 0.1], [5.1, 5]])
+    dv = S.ActiveLearningSampler(5, "diverse")
+    pick = dv.query(torch.full((5, 2), 0.5), 2, feats)
+    assert len({int(feats[i][0] > 2) for i in pick}) == 2                          # one from each cluster
+    assert len(S.ActiveLearningSampler(5, "random").query(probs, 3)) == 3
+    ad = S.AdaptiveSampler(10, explore=0.1, seed=0)
+    ad.update(list(range(10)), [0.01] * 9 + [5.0])
+    ad.update([9], [5.0])
+    cnt = Counter()
+    for ep in range(200):
+        ad.set_epoch(ep)
+        cnt.update(ad)
+    assert cnt[9] > 5 * max(cnt[i] for i in range(9)) and min(cnt[i] for i in range(9)) > 0
+    lengths = torch.randint(5, 100, (200,)).tolist()
+    bb = S.BucketBatchSampler(lengths, 8, bucket_size=5, seed=0)
+    batches = list(bb)
+    assert sorted(i for b in batches for i in b) == list(range(200)) and len(bb) == 25
+    spread = sum(max(lengths[i] for i in b) - min(lengths[i] for i in b) for b in batches) / len(batches)
+    rand_spread = sum(max(lengths[i:i + 8]) - min(lengths[i:i + 8]) for i in range(0, 200, 8)) / 25
+    assert spread < 0.5 * rand_spread
+    tok = list(S.BucketBatchSampler(lengths, 64, bucket_size=100, max_tokens=400, seed=0))
+    assert all(len(b) * max(lengths[i] for i in b) <= 400 for b in tok) and sorted(i for b in tok for i in b) == list(range(200))
+    bal = S.BalancedBatchSampler(labels, classes_per_batch=2, samples_per_class=4, num_batches=5)
+    for b in bal:
+        c = Counter(labels[b].tolist())
+        assert len(b) == 8 and len(c) == 2 and set(c.values()) == {4}
+    wc = Counter(labels[list(S.WeightedClassSampler(labels, 6000, seed=0))].tolist())
+    assert all(abs(wc[c] - 2000) < 200 for c in range(3))
+    assert sorted(S.SubsetRandomSampler([3, 5, 7])) == [3, 5, 7]
+    it = iter(S.InfiniteSampler(4, seed=0))
+    first8 = [next(it) for _ in range(8)]
+    assert sorted(first8[:4]) == sorted(first8[4:]) == [0, 1, 2, 3]
+
+
+def test_data_pipeline_transforms_datasets_text_sql_privacy_federated_and_collate(tmp_path):
+    import sqlite3
+    import numpy as np
+    from collections import Counter
+    from torsh_b200.data import pipeline as P
+    torch.manual_seed(0)
+    # transform algebra
+    t = P.Lambda(lambda x: x + 1, "inc") | P.Lambda(lambda x: x * 2, "dbl").when(lambda x: x.sum() > 0) | P.ToType(torch.float64)
+    assert t(torch.tensor([1.0])).tolist() == [4.0] and t(torch.tensor([-5.0])).tolist() == [-4.0] and t(torch.tensor([1.0])).dtype == torch.float64 and "inc" in repr(t)
+    assert torch.allclose(P.Normalize([1.0, 2.0], [2.0, 4.0])(torch.ones(2, 3, 3)), torch.tensor([0.0, -0.25]).reshape(2, 1, 1).expand(2, 3, 3))
+    coin = P.Lambda(lambda x: x + 1).with_probability(0.5, seed=0)
+    assert 30 < sum(int(coin(torch.zeros(()))) for _ in range(100)) < 70
+    # datasets
+    ds = P.TensorDataset(torch.arange(10.0), torch.arange(10))
+    assert len(ds) == 10 and ds[3] == (torch.tensor(3.0), torch.tensor(3))
+    with pytest.raises(ValueError):
+        P.TensorDataset(torch.zeros(3), torch.zeros(4))
+    td = P.TransformedDataset(ds, lambda x: x * 10, lambda y: y + 100)
+    assert td[2] == (torch.tensor(20.0), torch.tensor(102))
+    assert list(P.ChainDataset([1, 2], [3])) == [1, 2, 3]
+    inf = iter(P.InfiniteDataset(P.TensorDataset(torch.arange(3)), shuffle=True))
+    got = [int(next(inf)) for _ in range(9)]
+    assert sorted(got[:3]) == sorted(got[3:6]) == [0, 1, 2]
+    sh = list(P.BufferedStreamingDataset(range(100), 20, seed=0))
+    assert sorted(sh) == list(range(100)) and sh != list(range(100)) and max(abs(v - i) for i, v in enumerate(sh)) < 100
+    pipe = P.DataPipeline(range(100)).filter(lambda v: v % 2 == 0).map(lambda v: v * v).skip(2).take(7).batch(3)
+    assert list(pipe) == [[16, 36, 64], [100, 144, 196], [256]] and list(P.DataPipeline(range(10)).shard(3, 1)) == [1, 4, 7]
+    assert list(P.DataPipeline(range(7)).batch(3, drop_last=True, collate=sum)) == [3, 12] and sorted(P.DataPipeline(range(20)).shuffle(5)) == list(range(20))
+    clock = iter(np.arange(0, 100, 0.5))
+    pr = P.ProfiledDataset(ds, clock=lambda: float(next(clock)))
+    _ = [pr[i] for i in (1, 2, 1)]
+    assert pr.stats()["count"] == 3 and pr.stats()["mean"] == 0.5 and pr.stats()["total"] == 1.5
+    rt = P.RealTimeDataset(capacity=3)
+    for i in range(5):
+        rt.push(i)
+    rt.close()
+    assert list(rt) == [2, 3, 4] and rt.dropped == 2
+    shm = P.SharedMemoryDataset(torch.randn(8, 4), torch.arange(8))
+    assert shm.is_shared() and shm[5][1] == 5
+    parts = P.random_split(ds, [0.7, 0.3], seed=0)
+    assert [len(p) for p in parts] == [7, 3] and sorted(int(p[i][1]) for p in parts for i in range(len(p))) == list(range(10))
+    # text cleaning; Porter stemmer against the algorithm's published vocabulary pairs
+    st = P.PorterStemmer()
+    pairs = {"caresses": "caress", "ponies": "poni", "cats": "cat", "feed": "feed", "agreed": "agre", "plastered": "plaster", "motoring": "motor", "sing": "sing",
+             "conflated": "conflat", "troubled": "troubl", "sized": "size", "hopping": "hop", "falling": "fall", "hissing": "hiss", "filing": "file", "happy": "happi",
+             "relational": "relat", "conditional": "condit", "rational": "ration", "digitizer": "digit", "operator": "oper", "feudalism": "feudal", "decisiveness": "decis",
+             "hopefulness": "hope", "formaliti": "formal", "triplicate": "triplic", "formative": "form", "electrical": "electr", "goodness": "good", "revival": "reviv",
+             "allowance": "allow", "inference": "infer", "adjustable": "adjust", "replacement": "replac", "adoption": "adopt", "activate": "activ", "effective": "effect",
+             "probate": "probat", "rate": "rate", "cease": "ceas", "controll": "control", "roll": "roll", "generalization": "gener", "running": "run"}
+    wrong = {w: (st.stem(w), s) for w, s in pairs.items() if st.stem(w) != s}
+    assert not wrong, wrong
+    tp = P.TextPipeline().lowercase().remove_punctuation().remove_numbers().collapse_whitespace().tokenize().remove_stopwords().filter_by_length(3).stem()
+    assert tp("The 3 quick foxes  were JUMPING over the lazy dogs!") == ["quick", "fox", "jump", "over", "lazi", "dog"]
+    assert P.TextPipeline().tokenize().ngrams(2)("a b c") == ["a b", "b c"] and P.TextPipeline().replace_pattern(r"\d+", "<n>")("room 42") == "room <n>"
+    # augmentation schedules
+    pa = P.ProgressiveAugmentation(lambda s: (lambda x: x * (1 + s)), 0.0, 1.0, total_steps=10, mode="linear")
+    vals = []
+    for _ in range(12):
+        vals.append(pa.strength()); pa.step()
+    assert vals[0] == 0 and vals[5] == 0.5 and vals[-1] == 1.0 and float(pa(torch.ones(()))) == 2.0
+    cosv = P.ProgressiveAugmentation(None, 0, 1, 10, "cosine"); cosv.step_count = 5
+    stp = P.ProgressiveAugmentation(None, 0, 1, 10, "step", steps=2); stp.step_count = 4
+    assert cosv.strength() == pytest.approx(0.5) and stp.strength() == 0.0
+    aa = P.AdaptiveAugmentation(lambda s: (lambda x: x), strength=0.3, target_gap=0.05, rate=0.1)
+    aa.update(0.95, 0.80); aa.update(0.95, 0.82)
+    assert aa.strength == pytest.approx(0.5)
+    aa.update(0.85, 0.84)
+    assert aa.strength == pytest.approx(0.4) and len(aa.history) == 3
+    ap = P.AugmentationPipeline(seed=0).add("flip", lambda x: x.flip(-1), 0.5).add("scale", lambda x: x * 2, 1.0)
+    outs = [ap(torch.tensor([1.0, 2.0])) for _ in range(40)]
+    assert ap.stats["scale"] == 40 and 10 < ap.stats["flip"] < 30 and all(o.sum() == 6 for o in outs)
+    # SQL dataset
+    conn = sqlite3.connect(":memory:")
+    conn.execute("CREATE TABLE samples (id INTEGER PRIMARY KEY, a REAL, b REAL, label INTEGER, split TEXT)")
+    conn.executemany("INSERT INTO samples VALUES (?, ?, ?, ?, ?)", [(i, i * 0.5, -i, i % 3, "train" if i % 5 else "val") for i in range(50)])
+    db = P.DatabaseDataset(conn, "samples", ["a", "b"], "label", key="id", where="split = 'train'", page_size=8, cache_pages=2)
+    assert len(db) == 40 and db[0][0].tolist() == [0.5, -1.0] and db[0][1] == 1 and db[39][0].tolist() == [24.5, -49.0]
+    q0 = db.queries
+    _ = [db[i] for i in range(8)]
+    assert db.queries == q0 and len(db.cache) <= 2
+    _ = [db[i] for i in (0, 10, 20, 30, 0)]
+    assert db.queries == q0 + 4
+    with pytest.raises(ValueError):
+        P.DatabaseDataset(conn, "samples; DROP TABLE samples", ["a"])
+    # privacy
+    bud = P.PrivacyBudget(1.0)
+    bud.spend(0.4); bud.spend(0.4)
+    with pytest.raises(PermissionError):
+        bud.spend(0.4)
+    assert bud.remaining()[0] == pytest.approx(0.2) and len(bud.spent) == 2
+    adv = P.PrivacyBudget(100.0, 1e-3, "advanced", 1e-6)
+    for _ in range(100):
+        adv.spend(0.1)
+    assert adv.consumed()[0] < 100 * 0.1 and adv.consumed()[1] == pytest.approx(1e-6)
+    g = torch.Generator().manual_seed(0)
+    lap = P.laplace_mechanism(torch.zeros(20000), 1.0, 0.5, g)
+    assert float(lap.abs().mean()) == pytest.approx(2.0, rel=0.05)
+    gau = P.gaussian_mechanism(torch.zeros(20000), 1.0, 0.5, 1e-5, g)
+    assert float(gau.std()) == pytest.approx(np.sqrt(2 * np.log(1.25e5)) / 0.5, rel=0.05)
+    bits = torch.rand(20000, generator=g) < 0.3
+    noisy, est = P.randomized_response(bits, 1.0, g)
+    assert est == pytest.approx(0.3, abs=0.03) and 0.2 < float((noisy != bits).float().mean()) < 0.35
+    ages = torch.randint(18, 90, (5000,)).float()
+    pd_ = P.PrivateDataset(ages, 0, 100, P.PrivacyBudget(3.0), seed=0)
+    assert pd_.mean(1.0) == pytest.approx(float(ages.mean()), abs=0.5) and pd_.count(lambda d: d > 65, 1.0) == pytest.approx(float((ages > 65).sum()), abs=15)
+    assert pd_.histogram(10, 1.0).shape == (10,)
+    with pytest.raises(PermissionError):
+        pd_.sum(0.5)
+    # federated partitions and aggregation
+    labels = torch.arange(1000) % 10
+    iid = P.partition_iid(1000, 10)
+    assert sorted(i for p in iid for i in p) == list(range(1000)) and all(len(p) == 100 for p in iid)
+    skew = P.partition_dirichlet(labels, 10, alpha=0.1, seed=0)
+    assert sorted(i for p in skew for i in p) == list(range(1000))
+    fd_iid, fd_skew = P.FederatedDataset(labels, iid), P.FederatedDataset(labels, skew)
+    ent = lambda d: float(-(d * d.clamp(min=1e-12).log()).sum(1).mean())
+    assert ent(fd_skew.label_distribution(labels)) < 0.6 * ent(fd_iid.label_distribution(labels))
+    shards = P.partition_shards(labels, 10, 2, seed=0)
+    assert all(len(set(labels[p].tolist())) <= 3 for p in shards) and sorted(i for p in shards for i in p) == list(range(1000))
+    caps = [{"compute": 1.0 + k, "bandwidth": 1.0} for k in range(10)]
+    fd = P.FederatedDataset(labels, iid, caps)
+    assert fd.select_clients(3, "capable") == [9, 8, 7] and len(set(fd.select_clients(4, "random"))) == 4 and len(fd.client(2)) == 100
+    assert len(set(fd.select_clients(5, "weighted"))) == 5
+    states = [{"w": torch.full((3,), float(v))} for v in (1, 2, 3, 100)]
+    assert P.federated_average(states[:3], [1, 1, 2])["w"].tolist() == [2.25] * 3
+    assert P.federated_average(states, strategy="median")["w"].tolist() == [2.0] * 3 and P.federated_average(states, strategy="trimmed_mean", trim=0.25)["w"].tolist() == [2.5] * 3
+    # pooled buffers, memory-mapped batches, device-side preprocessing
+    pool = P.TensorPool()
+    a = pool.acquire((4, 8)); pool.release(a)
+    b = pool.acquire((4, 8)); c = pool.acquire((4, 8))
+    assert b is a and c is not a and pool.allocated == 2 and pool.reused == 1
+    arr = np.arange(100 * 6, dtype=np.float32).reshape(100, 6)
+    np.save(tmp_path / "x.npy", arr)
+    mm = P.MemoryMappedLoader(tmp_path / "x.npy", 32)
+    assert len(mm) == 4 and [len(b) for b in mm] == [32, 32, 32, 4] and np.array_equal(mm.batch(1).numpy(), arr[32:64]) and np.array_equal(mm.gather([5, 2]).numpy(), arr[[2, 5]])
+    u8 = torch.randint(0, 256, (4, 20, 24, 3), dtype=torch.uint8)
+    dp = P.DevicePreprocessingPipeline("cpu", size=(10, 12), flip_p=0.0)
+    out = dp(u8)
+    ref = torch.nn.functional.interpolate(u8.permute(0, 3, 1, 2).float() / 255, size=(10, 12), mode="bilinear", antialias=True, align_corners=False)
+    assert out.shape == (4, 3, 10, 12) and torch.allclose(out, (ref - dp.mean) / dp.std, atol=1e-6) and dp.bytes_uploaded == u8.numel()
+    flipped = P.DevicePreprocessingPipeline("cpu", flip_p=1.0)(u8)
+    assert torch.allclose(flipped, P.DevicePreprocessingPipeline("cpu")(u8).flip(-1))
+    # collation
+    seqs = [(torch.arange(1, 4), 0), (torch.arange(1, 6), 1), (torch.arange(1, 2), 0)]
+    padded, lens, mask, ys = P.pad_sequence_collate(seqs, pad_to_multiple=4)
+    assert padded.shape == (3, 8) and lens.tolist() == [3, 5, 1] and mask.sum(1).tolist() == [3, 5, 1] and padded[0].tolist() == [1, 2, 3, 0, 0, 0, 0, 0] and ys.tolist() == [0, 1, 0]
+    lp, _, lm = P.pad_sequence_collate([s for s, _ in seqs], left=True)
+    assert lp[0].tolist() == [0, 0, 1, 2, 3] and lm[0].tolist() == [False, False, True, True, True]
+    nc = P.nested_collate([{"x": torch.ones(2), "meta": {"id": 1, "name": "a"}, "rag": torch.ones(1)}, {"x": torch.zeros(2), "meta": {"id": 2, "name": "b"}, "rag": torch.ones(3)}])
+    assert nc["x"].shape == (2, 2) and nc["meta"]["id"].tolist() == [1, 2] and nc["meta"]["name"] == ["a", "b"] and isinstance(nc["rag"], list)
+    assert P.nested_collate([(torch.ones(2), 1.0), (torch.ones(2), 2.0)])[1].tolist() == [1.0, 2.0]

@@ -351,3 +351,6 @@ class NativeTokenLoader:
             self.close()
         except Exception:
             pass
+
+
+from . import pipeline, samplers  # noqa: E402,F401  (index samplers and dataset / transform combinators)
