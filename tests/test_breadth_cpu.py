@@ -3473,3 +3473,211 @@ def test_data_pipeline_transforms_datasets_text_sql_privacy_federated_and_collat
     nc = P.nested_collate([{"x": torch.ones(2), "meta": {"id": 1, "name": "a"}, "rag": torch.ones(1)}, {"x": torch.zeros(2), "meta": {"id": 2, "name": "b"}, "rag": torch.ones(3)}])
     assert nc["x"].shape == (2, 2) and nc["meta"]["id"].tolist() == [1, 2] and nc["meta"]["name"] == ["a", "b"] and isinstance(nc["rag"], list)
     assert P.nested_collate([(torch.ones(2), 1.0), (torch.ones(2), 2.0)])[1].tolist() == [1.0, 2.0]
+
+
+def test_nn_research_layers_capsules_hopfield_sparse_training_and_fused_blocks():
+    import math
+    from torsh_b200.nn import research as R
+    torch.manual_seed(0)
+    # Neural ODE: dx/dt = a x integrates to exp(a); rk4 is far more accurate than euler at equal steps; gradients reach a
+    a = torch.nn.Parameter(torch.tensor(0.7))
+    f = lambda t, x: a * x
+    x0 = torch.ones(3)
+    rk, eu = R.NeuralODE(f, steps=10)(x0), R.NeuralODE(f, steps=10, method="euler")(x0)
+    assert abs(rk[0].item() - math.exp(0.7)) < 1e-6 < abs(eu[0].item() - math.exp(0.7)) and abs(R.NeuralODE(f, steps=10, method="midpoint")(x0)[0].item() - math.exp(0.7)) < 2e-3
+    rk.sum().backward()
+    assert float(a.grad) == pytest.approx(3 * math.exp(0.7), rel=1e-5) and R.NeuralODE(f, steps=4)(x0, True).shape == (5, 3)
+    # capsules: outputs have norm < 1, coupling coefficients are a distribution over output capsules, routing sharpens them
+    caps = R.CapsuleLayer(12, 8, 4, 6, routing_iters=3)
+    with torch.no_grad():
+        caps.w.mul_(30)
+    v = caps(torch.randn(5, 12, 8))
+    assert v.shape == (5, 4, 6) and v.norm(dim=-1).max() < 1 and torch.allclose(caps.coupling.sum(2), torch.ones(5, 12), atol=1e-5)
+    one = R.CapsuleLayer(12, 8, 4, 6, routing_iters=1); one.w = caps.w
+    one(torch.randn(5, 12, 8))
+    assert caps.coupling.max() > one.coupling.max() == pytest.approx(0.25)
+    s = R.squash(torch.tensor([[3.0, 4.0]]))
+    assert float(s.norm()) == pytest.approx(25 / 26, rel=1e-5)
+    se = R.SEBlock(16, 4)
+    xi = torch.randn(2, 16, 5, 5)
+    assert se(xi).shape == xi.shape and ((se(xi) / xi).flatten(2).std(-1) < 1e-5).all()                       # one scale per channel
+    ip = R.IPAdapterCrossAttention(32, 24, heads=4, image_ctx_dim=20, scale=0.0)
+    q, txt, im = torch.randn(2, 7, 32), torch.randn(2, 5, 24), torch.randn(2, 3, 20)
+    base = ip(q, txt, im)
+    assert torch.equal(base, ip(q, txt)) and base.shape == (2, 7, 32)
+    ip.scale = 1.0
+    assert not torch.allclose(ip(q, txt, im), base)
+    seq = torch.randn(2, 12, 10)
+    assert torch.equal(R.PixelUnshuffle1d(3)(R.PixelShuffle1d(3)(seq)), seq) and R.PixelShuffle1d(3)(seq).shape == (2, 4, 30)
+    assert R.PixelShuffle1d(2)(torch.arange(4.0).reshape(1, 2, 2)).flatten().tolist() == [0, 2, 1, 3]
+    dc = R.DropConnect(64, 64, p=0.5)
+    xin = torch.randn(512, 64)
+    dc.eval(); ref = dc(xin)
+    dc.train(); outs = torch.stack([dc(xin) for _ in range(40)]).mean(0)
+    assert torch.allclose(outs, ref, atol=0.5) and not torch.equal(dc(xin), dc(xin)) and float((outs - ref).abs().mean()) < 0.15
+    co = R.Cutout(5).train()
+    y = co(torch.ones(8, 3, 16, 16))
+    holes = (y == 0).float().sum((1, 2, 3)) / 3
+    assert (holes >= 9).all() and (holes <= 25).all() and torch.equal(co.eval()(torch.ones(1, 3, 4, 4)), torch.ones(1, 3, 4, 4))
+    # custom RNN equals torch's LSTM when driven by an LSTMCell with the same weights; reversed pass flips time
+    lstm = torch.nn.LSTM(6, 8, batch_first=True)
+    cell = torch.nn.LSTMCell(6, 8)
+    cell.weight_ih, cell.weight_hh, cell.bias_ih, cell.bias_hh = lstm.weight_ih_l0, lstm.weight_hh_l0, lstm.bias_ih_l0, lstm.bias_hh_l0
+    wrap = lambda x, st: (lambda hc: (hc[0], hc))(cell(x, st))
+    xs = torch.randn(3, 5, 6)
+    assert torch.allclose(R.CustomRNN(wrap)(xs)[0], lstm(xs)[0], atol=1e-6)
+    assert torch.allclose(R.CustomRNN(wrap, reverse=True)(xs)[0], lstm(xs.flip(1))[0].flip(1), atol=1e-6)
+    cl = R.ConvLSTM(2, 4)
+    out, (h, c) = cl(torch.randn(2, 6, 2, 8, 8))
+    assert out.shape == (2, 6, 4, 8, 8) and torch.equal(out[:, -1], h) and c.abs().max() < 6
+    # Hopfield retrieval completes a corrupted pattern
+    pats = torch.sign(torch.randn(6, 64))
+    noisy = pats[2].clone(); noisy[:16] *= -1
+    hp = R.HopfieldLayer(64, beta=1.0)
+    rec = hp(noisy[None], pats)
+    assert torch.equal(torch.sign(rec[0]), pats[2]) and R.HopfieldLayer(64, project=True)(noisy[None], pats).shape == (1, 64)
+    # hyper-network: different conditioning vectors give different linear maps; gradients reach the generator
+    hl = R.HyperLinear(4, 10, 3)
+    z = torch.randn(2, 4)
+    xh = torch.randn(2, 7, 10)
+    yh = hl(xh, z)
+    p = hl.net(z)
+    manual = torch.einsum("oi,ti->to", p[1, :30].reshape(3, 10), xh[1]) + p[1, 30:]
+    assert yh.shape == (2, 7, 3) and torch.allclose(yh[1], manual, atol=1e-6)
+    yh.sum().backward()
+    assert hl.net[0].weight.grad.abs().sum() > 0
+    # adaptive softmax: a proper distribution, loss equals the NLL read from the full table
+    ah = R.AdaptiveSoftmaxHead(32, 100, [10, 40])
+    feats, tg = torch.randn(50, 32), torch.randint(0, 100, (50,))
+    lp = ah.log_prob(feats)
+    assert lp.shape == (50, 100) and torch.allclose(lp.exp().sum(1), torch.ones(50), atol=1e-5)
+    assert ah(feats, tg).item() == pytest.approx(-lp.gather(1, tg[:, None]).mean().item(), rel=1e-5)
+    assert sum(p.numel() for p in ah.parameters()) < 32 * 100
+    # sparse layers: masks hold through training, gradual schedule follows the cubic ramp
+    sl = R.SparseLinear(20, 10, sparsity=0.5)
+    assert sl.sparsity() == pytest.approx(0.5) and float((sl.weight * sl.mask == 0).float().mean()) >= 0.5
+    opt = torch.optim.SGD(sl.parameters(), 0.1)
+    dead = sl.mask == 0
+    w_dead = sl.weight.detach()[dead].clone()
+    for _ in range(5):
+        opt.zero_grad(); sl(torch.randn(8, 20)).pow(2).sum().backward(); opt.step()
+    assert torch.equal(sl.weight.detach()[dead], w_dead) and sl.weight.grad[dead].abs().sum() == 0
+    sl.prune_to(0.8)
+    assert sl.sparsity() == pytest.approx(0.8) and (sl.mask[dead] == 0).all()
+    sc = R.SparseConv2d(3, 8, 3, sparsity=0.75)
+    assert sc.sparsity() == pytest.approx(0.75, abs=0.01) and sc(torch.randn(1, 3, 6, 6)).shape == (1, 8, 4, 4)
+    net = torch.nn.Sequential(R.SparseLinear(16, 16), torch.nn.ReLU(), R.SparseLinear(16, 4))
+    gp = R.GradualPruningScheduler(net, final_sparsity=0.9, begin_step=10, end_step=110, frequency=10)
+    assert gp.target(0) == 0 and gp.target(60) == pytest.approx(0.9 * (1 - 0.5 ** 3)) and gp.target(500) == pytest.approx(0.9)
+    hist = []
+    for _ in range(130):
+        gp.step(); hist.append(net[0].sparsity())
+    assert hist[5] == 0 and hist[-1] == pytest.approx(0.9, abs=0.01) and all(b >= a for a, b in zip(hist, hist[1:])) and 0.5 < hist[40] < 0.8
+    # lazily shaped and fused blocks
+    lz = R.LazyLinear(5)
+    assert not lz.is_initialized() and lz(torch.randn(3, 11)).shape == (3, 5) and lz.inner.in_features == 11 and len(list(lz.parameters())) == 2
+    fl = R.FusedLinearActivation(8, 4, "gelu")
+    xin = torch.randn(3, 8)
+    assert torch.allclose(fl(xin), torch.nn.functional.gelu(fl.lin(xin), approximate="tanh"))
+    mlp = R.StaticMLP([8, 16, 16, 2], "relu")
+    assert mlp(xin).shape == (3, 2) and [m.activation for m in mlp] == ["relu", "relu", "none"]
+
+
+def test_nn_tools_stability_export_conversion_zoo_update_policies_and_recording(tmp_path):
+    import math
+    from torsh_b200.nn import tools as T
+    torch.manual_seed(0)
+    # stability: a naive softmax overflows on huge inputs, the built-in one does not
+    class Naive(torch.nn.Module):
+        def forward(self, x): e = torch.exp(x); return e / e.sum(-1, keepdim=True)
+    rep_bad, rep_ok = T.StabilityTester().test(Naive(), (4, 16)), T.StabilityTester().test(torch.nn.Softmax(-1), (4, 16))
+    assert not rep_bad["passed"] and ("huge", "float32") in rep_bad["failed_cases"] and rep_ok["passed"] and len(rep_ok["results"]) == 7
+    half = T.StabilityTester(dtypes=(torch.float32, torch.bfloat16)).test(torch.nn.Sequential(torch.nn.Linear(16, 8), torch.nn.LayerNorm(8)), (4, 16))
+    assert half["passed"] and len(half["results"]) == 14 and half["worst_sensitivity"] < 100
+    # deployment optimisation keeps outputs, folds conv+bn, removes dropout
+    net = torch.nn.Sequential(torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.BatchNorm2d(8), torch.nn.ReLU(), torch.nn.Dropout(0.5), torch.nn.Conv2d(8, 4, 1)).eval()
+    net[1].running_mean.normal_(); net[1].running_var.uniform_(0.5, 2)
+    x = torch.randn(2, 3, 8, 8)
+    opt, rep = T.DeploymentOptimizer().optimize(net)
+    assert rep == {"folded_conv_bn": 1, "fused_activation": 1, "removed_dropout": 1, "traced": True} and torch.allclose(opt(x), net(x), atol=1e-5)
+    assert not any(p.requires_grad for p in opt.parameters()) and T.DeploymentOptimizer().optimize(net, torch.bfloat16)[0](x.bfloat16()).dtype == torch.bfloat16
+    # export formats: sizes, checksums, round trip
+    mlp = torch.nn.Sequential(torch.nn.Linear(6, 12), torch.nn.ReLU(), torch.nn.Linear(12, 3))
+    ex = T.ModelExporter()
+    recs = ex.benchmark(mlp, torch.randn(1, 6), out_dir=tmp_path)
+    assert [r["format"] for r in recs][-1] == "json" and all(r["parameters"] == 6 * 12 + 12 + 12 * 3 + 3 and len(r["sha256"]) == 64 for r in recs)
+    from torsh_b200.serialize import model_state as ms
+    again = torch.nn.Sequential(torch.nn.Linear(6, 12), torch.nn.ReLU(), torch.nn.Linear(12, 3))
+    ms.load_model_state(again, ms.load_safetensors(tmp_path / "model.safetensors"))
+    xin = torch.randn(4, 6)
+    assert torch.equal(again(xin), mlp(xin))
+    ts = ex.export(mlp, tmp_path / "m.pt", "torchscript", torch.randn(1, 6))
+    assert ts["bytes"] > 0 and torch.allclose(torch.jit.load(str(tmp_path / "m.pt"))(xin), mlp(xin))
+    onx = ex.export(mlp, tmp_path / "m.onnx", "onnx", (torch.randn(1, 6),))
+    assert onx["bytes"] > 300
+    with pytest.raises(ValueError):
+        ex.export(mlp, tmp_path / "m.x", "coreml")
+    # TensorFlow-style checkpoint into a PyTorch-layout model
+    conv = torch.nn.Sequential()
+    conv.add_module("block", torch.nn.Sequential())
+    conv.block.add_module("conv", torch.nn.Conv2d(3, 5, 3))
+    conv.block.add_module("bn", torch.nn.BatchNorm2d(5))
+    conv.add_module("head", torch.nn.Linear(5, 2))
+    tfw = {"block/conv/kernel:0": torch.randn(3, 3, 3, 5), "block/conv/bias:0": torch.randn(5), "block/bn/gamma:0": torch.rand(5), "block/bn/beta:0": torch.randn(5),
+           "block/bn/moving_mean:0": torch.randn(5), "block/bn/moving_variance:0": torch.rand(5), "head/kernel:0": torch.randn(5, 2), "head/bias:0": torch.randn(2), "extra/w:0": torch.zeros(1)}
+    mc = T.ModelConverter()
+    st = mc.from_tensorflow(tfw)
+    assert st["block.conv.weight"].shape == (5, 3, 3, 3) and torch.equal(st["block.conv.weight"][4, 2, 1, 0], tfw["block/conv/kernel:0"][1, 0, 2, 4]) and torch.equal(st["head.weight"], tfw["head/kernel:0"].t())
+    fit = mc.fit(conv, st)
+    assert fit["unexpected"] == ["extra.w"] and fit["missing"] == ["block.bn.num_batches_tracked"] and not fit["shape_mismatch"] and torch.equal(conv.block.bn.running_var, tfw["block/bn/moving_variance:0"])
+    assert mc.rename({"encoder.layer.0.w": 1}, [(r"^encoder\.layer\.", "blocks.")]) == {"blocks.0.w": 1} and mc.describe(conv)[0]["name"] == "block"
+    bad = dict(st); bad["head.weight"] = torch.zeros(3, 3)
+    assert mc.fit(conv, bad)["shape_mismatch"] == ["head.weight"]
+    src, notes = T.MigrationHelper().migrate_source("m = tf.keras.layers.Dense(4)\no = torch.optim.AdamW(p)\nz = tf.signal.fft(x)\n")
+    assert "torsh_b200.nn.Linear(4)" in src and "torsh_b200.optim.AdamW" in src and "no mapping for tf.signal.fft" in notes
+    # zoo
+    zoo = T.ModelZoo(tmp_path / "zoo")
+    zoo.register("tiny_mlp", lambda width=12: torch.nn.Sequential(torch.nn.Linear(6, width), torch.nn.ReLU(), torch.nn.Linear(width, 3)), {"width": 12}, "test model")
+    info = zoo.save_weights("tiny_mlp", mlp, "v1", {"acc": 0.9})
+    assert zoo.list_models() == ["tiny_mlp"] and zoo.available_weights("tiny_mlp") == ["v1"] and info["parameters"] == 123
+    assert torch.equal(zoo.create("tiny_mlp", "v1")(xin), mlp(xin)) and zoo.create("tiny_mlp", width=20)[0].out_features == 20
+    wf = tmp_path / "zoo" / "tiny_mlp" / "v1.safetensors"
+    wf.write_bytes(wf.read_bytes()[:-4] + b"\0\0\0\0")
+    with pytest.raises(IOError):
+        zoo.create("tiny_mlp", "v1")
+    # network report
+    rp = T.NetworkOptimizer().analyze(net, x)
+    assert rp["total_flops"] == 2 * (2 * 8 * 8 * 8) * 27 + 2 * (2 * 4 * 8 * 8) * 8 and any("folded" in f for f in rp["findings"]) and any("FLOPs" in f for f in rp["findings"])
+    assert rp["total_params"] == sum(p.numel() for p in net.parameters())
+    # per-layer policies
+    model = torch.nn.ModuleDict({"embed": torch.nn.Embedding(10, 8), "blocks": torch.nn.ModuleList([torch.nn.Linear(8, 8) for _ in range(3)]), "head": torch.nn.Linear(8, 2)})
+    ls = T.LayerSpecificOptimizers(model, [(r"^embed", {"freeze": True}), (r"bias$", {"weight_decay": 0.0}), (r"^head", {"lr_mult": 10.0})])
+    groups = ls.param_groups(1e-3, weight_decay=0.1)
+    by = {tuple(g["names"]): g for g in groups}
+    assert not model["embed"].weight.requires_grad and by[("head.weight",)]["lr"] == pytest.approx(1e-2) and by[("head.weight",)]["weight_decay"] == 0.1
+    assert any(g["weight_decay"] == 0.0 and "blocks.0.bias" in g["names"] and "head.bias" in g["names"] for g in groups)
+    torch.optim.AdamW([{k: v for k, v in g.items() if k != "names"} for g in groups])
+    lw = T.LayerSpecificOptimizers.layerwise_decay(model, 1.0, 0.5)
+    lr_of = {n: g["lr"] for g in lw for n in g["names"]}
+    assert lr_of["head.weight"] == 1.0 and lr_of["blocks.2.weight"] == 1.0 and lr_of["blocks.1.bias"] == 0.5 and lr_of["blocks.0.weight"] == 0.25 and lr_of["embed.weight"] == 0.125
+    w = torch.nn.Parameter(torch.ones(2, 4))
+    up = T.ParameterUpdater([w], lr=1.0, clip_value=0.5, max_weight_norm=1.0, ema_decay=0.5)
+    w.grad = torch.tensor([[2.0, -2.0, 0.1, 0.0], [0.0, 0.0, 0.0, 0.0]])
+    up.step()
+    assert up.stats["value_clipped"] == 2 and up.stats["weights_rescaled"] == 2 and torch.allclose(w.detach().norm(dim=1), torch.ones(2), atol=1e-6)
+    assert torch.allclose(up.ema[0], 0.5 * torch.ones(2, 4) + 0.5 * w.detach())
+    live = w.detach().clone(); up.swap_in_ema()
+    assert torch.allclose(w.detach(), 0.5 + 0.5 * live); up.swap_in_ema()
+    assert torch.equal(w.detach(), live)
+    nc = T.ParameterUpdater([w], lr=0.0, clip_norm=1.0); w.grad = torch.full((2, 4), 10.0); nc.step()
+    assert nc.stats["norm_clipped"] == 1 and float(w.grad.norm()) == pytest.approx(1.0, rel=1e-4)
+    # recording hooks flag a dead ReLU
+    dead = torch.nn.Sequential(torch.nn.Linear(4, 8), torch.nn.ReLU(), torch.nn.Linear(8, 1))
+    with torch.no_grad():
+        dead[0].bias.fill_(-100.0)
+    rec = T.ActivationRecorder(dead)
+    dead(torch.randn(16, 4)).sum().backward()
+    assert rec.stats["1"]["zero_fraction"] == 1.0 and any(f.startswith("1:") for f in rec.findings()) and any("vanishes" in f for f in rec.findings()) and set(rec.grads) == {"0", "1", "2"}
+    rec.remove(); rec.stats.clear()
+    dead(torch.randn(2, 4))
+    assert not rec.stats
