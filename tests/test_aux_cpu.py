@@ -813,3 +813,176 @@ def test_extended_metrics_against_sklearn_and_scipy():
     assert M.permutation_test(torch.randn(30) + 2, torch.randn(30), n_perm=500) < 0.01 and M.permutation_test(x2, x2.flip(0), n_perm=200) > 0.5
     scorer = M.make_scorer(lambda pr_, y_: (pr_ == y_).float().mean())
     assert scorer(lambda X: torch.nn.functional.one_hot(X, 4).float(), y, y) == 1.0
+
+
+def test_profiler_analysis_workload_online_learning_regression_reports_streaming_and_flamegraphs(tmp_path):
+    import asyncio
+    import json
+    import math
+    import zlib
+    import numpy as np
+    from torsh_b200.utils import profiler_analysis as PA
+    from torsh_b200.utils.profiler import ProfileEvent
+    rng = np.random.default_rng(0)
+    # workload characterisation
+    ev, t = [], 0.0
+    for i in range(60):                                                     # memory-bound element-wise phase, then a communication phase
+        ev.append(ProfileEvent("add", "op", t, 10.0, 1, flops=1e6, bytes=1.2e7)); t += 12.0
+    for i in range(60):
+        ev.append(ProfileEvent("all_reduce", "communication", t, 50.0, 1)); t += 50.0
+    wc = PA.WorkloadCharacterizer(window=30)
+    rep = wc.analyze(ev)
+    assert rep["workload_type"] == "communication_bound" and [p["dominant"] for p in rep["phases"]] == ["op", "communication"] and rep["hotspots"][0][0] == "all_reduce"
+    mem = wc.analyze(ev[:60])
+    assert mem["workload_type"] == "memory_bound" and mem["idle_fraction"] == pytest.approx(1 - 600 / 718, abs=1e-6) and mem["parallelism"] == pytest.approx(1.0)
+    gemm = [ProfileEvent("gemm", "op", i * 100.0, 100.0, 1, flops=1.2e11, bytes=1e8) for i in range(10)]
+    cb = wc.analyze(gemm)
+    assert cb["workload_type"] == "compute_bound" and cb["mean_compute_efficiency"] == pytest.approx(1.2e11 / 1e-4 / 1.4e15)
+    par = wc.analyze([{"name": "a", "category": "op", "start_us": 0, "duration_us": 100}, {"name": "b", "category": "op", "start_us": 0, "duration_us": 100}])
+    assert par["parallelism"] == pytest.approx(2.0) and wc.analyze([])["workload_type"] == "empty"
+    length, path = PA.WorkloadCharacterizer.critical_path({"load": 2, "fwd": 5, "aug": 1, "bwd": 7, "log": 1}, {"fwd": ["load", "aug"], "bwd": ["fwd"], "log": ["fwd"]})
+    assert length == 14 and path == ["load", "fwd", "bwd"]
+    # learned analysis
+    ml = PA.MLAnalyzer()
+    names, feats = ml.extract_features(ev)
+    assert names == ["add", "all_reduce"] and feats.shape == (2, 7) and feats[1, 4] == pytest.approx(3000 / 3600)
+    vals = list(rng.normal(100, 2, 200)); vals[50] = 160; vals[120] = 30
+    for m in ("mad", "zscore", "iqr"):
+        assert {50, 120} <= set(ml.detect_anomalies(vals, m, 3.5 if m != "zscore" else 4.0)), m
+    three = np.concatenate([rng.normal([10, 1e3, 1, 1, .1, 1e6, 1e6], 0.01, (8, 7)), rng.normal([1e3, 10, 1, 1, .1, 1e9, 1e3], 0.01, (8, 7)), rng.normal([1, 1, 50, 90, .5, 10, 1e9], 0.01, (8, 7))])
+    lab = ml.cluster_operations(np.abs(three), 3)
+    assert len(set(lab[:8])) == len(set(lab[8:16])) == len(set(lab[16:])) == 1 and len(set(lab)) == 3
+    fl, by = rng.uniform(1e9, 1e12, 200), rng.uniform(1e6, 1e9, 200)
+    dur = (fl / 1e15 + by / 5e12 + 4e-6) * 1e6 * rng.normal(1, 0.01, 200)
+    fit = ml.fit_duration_model(fl, by, dur)
+    assert fit["flops_per_s"] == pytest.approx(1e15, rel=0.05) and fit["bytes_per_s"] == pytest.approx(5e12, rel=0.05) and fit["overhead_s"] == pytest.approx(4e-6, rel=0.3) and fit["r2"] > 0.99
+    assert fit["predict"](1e12, 1e9) == pytest.approx(1e-3 + 2e-4 + 4e-6, rel=0.05)
+    # online statistics
+    os_ = PA.OnlineStats()
+    for v in vals:
+        os_.update(v)
+    assert os_.mean == pytest.approx(np.mean(vals)) and os_.std == pytest.approx(np.std(vals, ddof=1)) and os_.max == 160
+    ew = PA.EWMA(0.5)
+    assert [ew.update(v) for v in (4, 8, 8)] == [4, 6, 7]
+    ad = PA.OnlineAnomalyDetector(4.0, 20)
+    flags = [ad.update(v) for v in vals]
+    assert [i for i, f in enumerate(flags) if f] == [50, 120] and ad.events[0]["kind"] == "spike" and ad.events[1]["kind"] == "drop"
+    dd = PA.DriftDetector(30, 5.0)
+    hits = [i for i, v in enumerate(list(rng.normal(10, 1, 100)) + list(rng.normal(14, 1, 100))) if dd.update(v)]
+    assert len(hits) >= 1 and 100 <= hits[0] <= 135
+    sk = PA.StreamingKMeans(2)
+    for p in rng.permutation(np.concatenate([rng.normal(0, 0.1, (100, 2)), rng.normal(5, 0.1, (100, 2))])):
+        sk.update(p)
+    assert len(sk.centroids) == 2 and sum(sk.counts) == 200
+    op = PA.OnlinePredictor(2)
+    for _ in range(300):
+        x = rng.uniform(0, 1, 2)
+        op.update(x, 3 * x[0] - 2 * x[1] + 0.5)
+    assert op.predict([1.0, 1.0]) == pytest.approx(1.5, abs=1e-3) and op.abs_err.value < 1e-3
+    # memory forecasting and pools
+    mp = PA.MemoryUsagePredictor()
+    for i in range(32):
+        mp.record(float(i), 1000.0 + 50 * i + (20 if i % 7 == 0 else 0))
+    assert mp.predict(40.0) == pytest.approx(1000 + 50 * 40, rel=0.02) and mp.time_to_limit(4000.0) == pytest.approx((4000 - 1000) / 50 - 31, abs=1.0) and mp.leak_suspected(min_slope=10)
+    flat = PA.MemoryUsagePredictor()
+    for i in range(32):
+        flat.record(float(i), 1000.0 + rng.normal(0, 5))
+    assert not flat.leak_suspected(min_slope=10) and flat.time_to_limit(1e9) is None or flat.time_to_limit(1e9) > 1e4
+    pool = PA.AdaptivePoolManager()
+    assert pool.size_class(1000) == 1024 and pool.size_class(10) == 256
+    for _ in range(3):
+        blocks = [pool.allocate(1000) for _ in range(8)]
+        for b in blocks:
+            pool.release(1000)
+    assert pool.stats()["hit_rate"] == pytest.approx(16 / 24) and pool.stats()["cached_bytes"] == 8 * 1024
+    pool.allocate(1000); pool.release(1000)
+    assert pool.trim() == 0                                                 # peak of 8 still justifies the cache
+    pool.allocate(1000); pool.release(1000)
+    assert pool.trim() == (8 - 2) * 1024                                    # demand fell to one block: keep ceil(1 * 1.25) = 2
+    # low-overhead recorder
+    oprof = PA.OptimizedProfiler(capacity=100, sample_every=10)
+    for i in range(1000):
+        oprof.record("k", float(i), 5.0)
+    for i in range(30):
+        oprof.record("rare", float(i), 100.0)
+    st = oprof.stats()
+    assert st["recorded"] == 1030 and st["stored"] == 100 and st["dropped"] == 3 and st["names"] == 2 and st["overhead_per_record_s"] < 1e-3
+    assert oprof.estimated_totals() == {"k": 5000.0, "rare": 3000.0} and oprof.events()[-1]["name"] == "rare"
+    # regression detection
+    rd = PA.RegressionDetector()
+    base = list(rng.normal(100, 1, 30))
+    rd.set_baseline("step_ms", base)
+    assert not rd.check("step_ms", list(rng.normal(100.5, 1, 30)))["regression"]
+    assert rd.check("step_ms", list(rng.normal(110, 1, 30)))["severity"] == "minor" and rd.check("step_ms", list(rng.normal(130, 1, 30)))["severity"] == "major"
+    assert rd.check("step_ms", list(rng.normal(170, 1, 30)))["severity"] == "critical" and rd.check("step_ms", list(rng.normal(80, 1, 30)))["improvement"]
+    rd.save(tmp_path / "b.json")
+    rd2 = PA.RegressionDetector(higher_is_better=True); rd2.load(tmp_path / "b.json")
+    assert rd2.check("step_ms", list(rng.normal(80, 1, 30)))["severity"] == "major"
+    # reports
+    te = PA.TemplateEngine()
+    assert te.render("{{ a.b }}|{{{ a.b }}}|{% for r in rows %}[{{ r.x }}]{% endfor %}", {"a": {"b": "<x>"}, "rows": [{"x": 1}, {"x": 2}]}) == "&lt;x&gt;|<x>|[1][2]"
+    rg = PA.ReportGenerator()
+    r = rg.build(ev, "Run 7")
+    assert r["rows"][0]["name"] == "all_reduce" and r["rows"][0]["share"] == "83.3%" and r["summary"] == {"events": 120, "total_ms": 3.6} and "all_reduce takes" in r["findings"][0]["text"]
+    assert "<td>all_reduce</td><td>60</td>" in rg.render(r, "html") and "| add | 60 | 0.6 | 16.7% |" in rg.render(r, "markdown") and json.loads(rg.render(r, "json"))["rows"][1]["calls"] == 60
+    assert rg.build(ev, category="op")["summary"]["events"] == 60 and rg.build(ev, since_us=720)["summary"]["events"] == 60
+    # streaming with a slow link: quality steps down, low priority is dropped first, frames decode
+    frames = []
+    def send(frame):
+        frames.append(frame)
+        return 0.2                                                          # a link that takes 200 ms per frame
+    es = PA.EventStreamer(send, capacity=300, target_latency=0.05)
+    for i in range(1000):
+        es.push({"name": "tick", "i": i, "payload": "x" * 40}, priority=1 if i % 100 else 3)
+    assert len(es.heap) == 300 and es.dropped == 700 and sum(1 for p, _, _ in es.heap if p == 3) == 10
+    assert es.flush() >= 2 and es.stats()["quality"] != "full" and es.stats()["compression_ratio"] < 0.3
+    first = json.loads(zlib.decompress(frames[0]))
+    assert all(e["i"] % 100 == 0 for e in first[:10]) and es.stats()["sent"] == 300
+    before = es.dropped
+    for i in range(200):
+        es.push({"i": i}, priority=1)
+    assert es.dropped > before                                               # reduced quality samples low-priority events
+    # custom export and tools
+    ce = PA.CustomExporter()
+    schema = [{"header": "op", "field": "name"}, {"header": "ms", "field": "duration_us", "format": "ms"}, {"header": "MiB", "field": "bytes", "format": "mib"}, {"header": "f", "field": "flops", "format": "%.1e"}]
+    csv = ce.export(ev[:2] + [{"name": 'a,"b"', "duration_us": 1500.0, "bytes": 1 << 20, "flops": 0.0}], schema)
+    assert csv.splitlines()[0] == "op,ms,MiB,f" and csv.splitlines()[1] == "add,0.010,11.44,1.0e+06" and csv.splitlines()[3] == '"a,""b""",1.500,1.00,0.0e+00'
+    assert ce.export(ev[:1], schema, "text").splitlines()[1].split() == ["add", "0.010", "11.44", "1.0e+06"] and "\t" in ce.export(ev[:1], schema, "tsv")
+    reg = PA.CustomToolRegistry()
+    reg.register("count", lambda evs, scale=1: len(evs) * scale, scale=2)
+    reg.register("boom", lambda evs: 1 / 0)
+    assert reg.run("count", ev) == 240 and reg.list_tools() == ["boom", "count"]
+    with pytest.raises(ZeroDivisionError):
+        reg.run_all(ev)
+    assert reg.stats["boom"] == {"calls": 1, "seconds": reg.stats["boom"]["seconds"], "errors": 1}
+    # flame graph
+    nested = [{"name": "step", "start_us": 0, "duration_us": 100, "thread_id": 1}, {"name": "fwd", "start_us": 5, "duration_us": 40, "thread_id": 1},
+              {"name": "gemm", "start_us": 10, "duration_us": 30, "thread_id": 1}, {"name": "bwd", "start_us": 50, "duration_us": 45, "thread_id": 1},
+              {"name": "io", "start_us": 0, "duration_us": 20, "thread_id": 2}]
+    stacks = PA.build_stacks(nested)
+    assert stacks == {"step": 15.0, "step;fwd": 10.0, "step;fwd;gemm": 30.0, "step;bwd": 45.0, "io": 20.0} and "step;fwd;gemm 30\n" in PA.folded_text(stacks)
+    ss = json.loads(PA.speedscope_json(stacks))
+    assert ss["profiles"][0]["endValue"] == 120 and {f["name"] for f in ss["shared"]["frames"]} == {"step", "fwd", "gemm", "bwd", "io"}
+    # decorators
+    ar = PA.AttributeRegistry()
+    @ar.profile(category="math", tag="t")
+    def work(n): return sum(range(n))
+    @ar.profile_if(lambda n: n > 5, name="big")
+    def maybe(n): return n
+    @ar.profile()
+    async def aw(n):
+        await asyncio.sleep(0)
+        return n * 2
+    assert work(10) == 45 and maybe(3) == 3 and maybe(9) == 9 and asyncio.run(aw(4)) == 8
+    assert [e["name"] for e in ar.events] == [work.__qualname__, "big", aw.__qualname__] and ar.events[0]["category"] == "math" and ar.events[0]["tag"] == "t"
+    # integrated
+    det = PA.RegressionDetector(); det.set_baseline("matmul", list(rng.normal(100, 1, 30)))
+    ip = PA.IntegratedProfiler(regression=det)
+    tt = 0.0
+    for i in range(200):
+        d = float(rng.normal(125, 1)) if i != 150 else 400.0
+        ip.record({"name": "matmul", "category": "op", "start_us": tt, "duration_us": d}); tt += d
+    ip.pause(); ip.record({"name": "ignored", "category": "op", "start_us": tt, "duration_us": 1.0}); ip.resume()
+    out = ip.report()
+    assert out["events"] == 200 and len(out["anomalies"]["matmul"]) == 1 and out["regressions"][0]["severity"] == "major" and out["trends"]["matmul"] == pytest.approx(125, abs=15)
+    assert any("slower than its baseline" in r for r in out["recommendations"]) and any("outlier" in r for r in out["recommendations"])
