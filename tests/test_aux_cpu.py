@@ -986,3 +986,211 @@ def test_profiler_analysis_workload_online_learning_regression_reports_streaming
     out = ip.report()
     assert out["events"] == 200 and len(out["anomalies"]["matmul"]) == 1 and out["regressions"][0]["severity"] == "major" and out["trends"]["matmul"] == pytest.approx(125, abs=15)
     assert any("slower than its baseline" in r for r in out["recommendations"]) and any("outlier" in r for r in out["recommendations"])
+
+
+def test_mobile_optimizer_and_bottleneck_profiler(tmp_path):
+    from torsh_b200.utils import mobile_optimizer as M
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.BatchNorm2d(8), torch.nn.ReLU(), torch.nn.Dropout(0.3), torch.nn.Flatten(),
+                              torch.nn.Linear(8 * 8 * 8, 64), torch.nn.ReLU(), torch.nn.Linear(64, 10)).eval()
+    net[1].running_mean.normal_(); net[1].running_var.uniform_(0.5, 2)
+    x = torch.randn(4, 3, 8, 8)
+    opt, rep = M.optimize_for_mobile(net, M.MobileOptimizerConfig("android"), x)
+    steps = {s["step"]: s for s in rep["steps"]}
+    assert steps["remove_dropout"]["removed"] == 1 and steps["fold_batch_norm"]["folded"] == 1 and steps["fold_batch_norm"]["relative_error"] < 1e-5
+    assert steps["dynamic_int8"]["layers"] == 2 and steps["dynamic_int8"]["relative_error"] < 0.03 and 3.0 < rep["compression"] < 4.1 and rep["fits_platform"]
+    assert isinstance(opt[5], M.Int8DynamicLinear) and opt[5].qweight.dtype == torch.int8 and torch.allclose(opt(x), net(x), atol=0.05)
+    ios, r2 = M.optimize_for_mobile(net, M.MobileOptimizerConfig("ios"), x)
+    assert r2["compression"] == pytest.approx(2.0, rel=0.02) and r2["steps"][-1]["relative_error"] < 5e-3 and ios(x).dtype == torch.float32
+    pr, r3 = M.optimize_for_mobile(net, M.MobileOptimizerConfig("server", prune_sparsity=0.5, size_target_mb=0.001), x)
+    assert next(s for s in r3["steps"] if s["step"] == "prune")["sparsity"] == pytest.approx(0.5, abs=0.01) and not r3["fits_target"] and r3["optimized_bytes"] < r3["original_bytes"]
+    keep, r4 = M.optimize_for_mobile(net, M.MobileOptimizerConfig("android", preserve_modules=("7",)), x)
+    assert isinstance(keep[7], torch.nn.Linear) and isinstance(keep[5], M.Int8DynamicLinear)
+    assert net[3].p == 0.3 and isinstance(net[1], torch.nn.BatchNorm2d)                                        # the source model is untouched
+    out = M.export_optimized_model(opt, tmp_path / "m.pt")
+    sd = torch.load(tmp_path / "m.pt")
+    assert out["bytes"] < 0.4 * M.model_size_bytes(net) + 4096 and sd["5.qweight"].dtype == torch.int8
+    bm = M.benchmark_mobile_model(opt, x, warmup=1, iters=5, threads=1)
+    assert bm["mean_ms"] > 0 and bm["p95_ms"] >= bm["p50_ms"] and bm["threads"] == 1 and bm["model_bytes"] == M.model_size_bytes(opt)
+    # bottleneck profile with a fake clock: the wide layer dominates
+    wide = torch.nn.Sequential(torch.nn.Linear(16, 16), torch.nn.ReLU(), torch.nn.Linear(16, 2048), torch.nn.ReLU(), torch.nn.Linear(2048, 4), torch.nn.Tanh(), torch.nn.Sigmoid())
+    rep = M.profile_bottlenecks(wide, torch.randn(64, 16), iters=3)
+    assert len(rep.layers) == 7 and {rep.layers[0]["name"], rep.layers[1]["name"]} == {"2", "4"} and rep.memory_peak_layer in ("2", "3")
+    assert abs(sum(l["share"] for l in rep.layers) - 1) < 1e-6 and rep.total_backward_ms > 0 and "total forward" in rep.render() and rep.hotspots[0] in ("2", "4")
+    fwd_only = M.profile_bottlenecks(wide, torch.randn(64, 16), iters=2, backward=False)
+    assert fwd_only.total_backward_ms == 0 and all(l["backward_ms"] == 0 for l in fwd_only.layers) and wide.training
+
+
+def test_hub_services_transfers_cache_cards_analytics_community_enterprise_and_imports(tmp_path):
+    import json
+    from torsh_b200 import hub_services as H
+    torch.manual_seed(0)
+    # token bucket with a fake clock
+    now = [0.0]
+    slept = []
+    bl = H.BandwidthLimiter(1000.0, burst=500.0, clock=lambda: now[0], sleep=lambda s: (slept.append(s), now.__setitem__(0, now[0] + s)))
+    assert bl.acquire(400) == 0 and bl.acquire(600) == pytest.approx(0.5) and bl.acquire(1000) == pytest.approx(1.0) and sum(slept) == pytest.approx(1.5)
+    now[0] += 10
+    assert bl.acquire(500) == 0 and bl.stats()["bytes"] == 2500
+    import os
+    (tmp_path / "blob.bin").write_bytes(os.urandom(300_000))
+    rd = H.BandwidthLimitedReader(open(tmp_path / "blob.bin", "rb"), H.BandwidthLimiter(1e9, sleep=None))
+    assert sum(len(c) for c in rd) == 300_000
+    ab = H.AdaptiveBandwidthLimiter(1000.0, min_rate=100, window=2, sleep=None)
+    ab.report(True); ab.report(True)
+    assert ab.rate == pytest.approx(1100.0)
+    ab.report(False)
+    assert ab.rate == pytest.approx(550.0)
+    # retry with back-off and circuit breaker
+    waits, calls = [], [0]
+    rp = H.RetryPolicy(max_attempts=4, base_delay=1.0, jitter=0.0, breaker_threshold=2, breaker_cooldown=30.0, clock=lambda: now[0], sleep=waits.append)
+    def flaky():
+        calls[0] += 1
+        if calls[0] < 3:
+            raise IOError("reset")
+        return "ok"
+    assert rp.call(flaky) == "ok" and waits == [1.0, 2.0] and rp.attempts_log == [3]
+    def dead(): raise TimeoutError("no route")
+    for _ in range(2):
+        with pytest.raises(TimeoutError):
+            rp.call(dead)
+    with pytest.raises(ConnectionError):
+        rp.call(flaky)
+    now[0] += 31
+    assert rp.call(flaky) == "ok"
+    with pytest.raises(ValueError):
+        H.RetryPolicy(sleep=lambda s: None).call(lambda: (_ for _ in ()).throw(ValueError("not retried")))
+    # resumable verified download
+    src = tmp_path / "blob.bin"
+    digest = H._sha256(src)
+    dm = H.DownloadManager(chunk=50_000)
+    (tmp_path / "out").mkdir()
+    (tmp_path / "out" / "m.bin.part").write_bytes(src.read_bytes()[:120_000])
+    rec = dm.download(f"file://{src}", tmp_path / "out" / "m.bin", digest)
+    assert rec["resumed_from"] == 120_000 and (tmp_path / "out" / "m.bin").read_bytes() == src.read_bytes() and not (tmp_path / "out" / "m.bin.part").exists()
+    with pytest.raises(IOError):
+        dm.download(src, tmp_path / "out" / "bad.bin", "0" * 64)
+    assert not (tmp_path / "out" / "bad.bin").exists() and not (tmp_path / "out" / "bad.bin.part").exists()
+    with pytest.raises(PermissionError):
+        dm.download("https://example.org/m.bin", tmp_path / "x")
+    fails = [0]
+    class Flaky:
+        def __init__(self, p, mode): self.f = open(p, mode)
+        def __enter__(self): return self
+        def __exit__(self, *a): self.f.close()
+        def seek(self, n): self.f.seek(n)
+        def read(self, n):
+            fails[0] += 1
+            if fails[0] == 3:
+                raise IOError("connection reset")
+            return self.f.read(n)
+    rec = dm.download(src, tmp_path / "out" / "r.bin", digest, opener=Flaky)
+    assert rec["attempts"] == 2 and (tmp_path / "out" / "r.bin").read_bytes() == src.read_bytes()
+    # cache
+    t = [0.0]
+    cm = H.CacheManager(tmp_path / "cache", max_bytes=700_000, clock=lambda: t[0])
+    for k in ("a", "b"):
+        t[0] += 1; cm.put(k, src)
+    t[0] += 1
+    assert cm.get("a") is not None and cm.get("zzz") is None
+    t[0] += 1; cm.put("c", src)
+    assert sorted(cm.index) == ["a", "c"] and cm.total_bytes() == 600_000 and cm.stats()["hit_rate"] == 0.5
+    (tmp_path / "cache" / cm.index["a"]["file"]).write_bytes(b"corrupt")
+    (tmp_path / "cache" / "stray.tmp").write_bytes(b"x")
+    v = cm.validate()
+    assert v["corrupt"] == ["a"] and v["untracked"] == ["stray.tmp"]
+    t[0] += 100
+    cl = cm.cleanup(max_age_s=50)
+    assert sorted(cl["removed"]) == ["a", "c"] and cl["untracked_removed"] == ["stray.tmp"] and cm.stats()["entries"] == 0
+    assert H.CacheManager(tmp_path / "cache").index == {}
+    # model cards and search
+    reg = H.ModelRegistry()
+    mk = lambda n, v, task, tags, acc, params, lic="apache-2.0": H.ModelCard(n, v, task, "Net", lic, f"{n} for {task}", tags, {"accuracy": acc}, params)
+    for c in (mk("org/resnet50", "1.0.0", "image-classification", ["vision", "cnn"], 0.76, 25_000_000), mk("org/resnet50", "1.2.0", "image-classification", ["vision", "cnn"], 0.80, 25_000_000),
+              mk("org/vit-b", "1.0.0", "image-classification", ["vision", "transformer"], 0.84, 86_000_000), mk("org/gpt2", "1.0.0", "text-generation", ["nlp", "transformer"], 0.3, 124_000_000, "mit")):
+        reg.register(c)
+    assert reg.versions("org/resnet50") == ["1.0.0", "1.2.0"] and reg.latest("org/resnet50").metrics["accuracy"] == 0.80
+    assert [c.name for c in reg.search("transformer")] == ["org/vit-b", "org/gpt2"] or [c.name for c in reg.search("transformer")] == ["org/gpt2", "org/vit-b"]
+    assert [c.name for c in reg.search(task="image-classification", max_parameters=50_000_000, sort_by="accuracy")] == ["org/resnet50", "org/resnet50"]
+    assert [c.version for c in reg.search("resnet", min_metric=("accuracy", 0.78))] == ["1.2.0"] and [c.name for c in reg.search(license="mit")] == ["org/gpt2"] and reg.search("nothing-like-this") == []
+    with pytest.raises(ValueError):
+        reg.register(H.ModelCard("x", "one"))
+    card = H.ModelCard.from_model("org/tiny", torch.nn.Linear(4, 2), task="regression", license="mit", description="d", metrics={"mse": 0.1}, limitations="small")
+    assert card.parameters == 10 and "| mse | 0.1 |" in card.to_markdown() and "## Limitations" in card.to_markdown() and card.validate() == []
+    # analytics and A/B
+    an = H.AnalyticsManager(clock=lambda: t[0])
+    for i in range(10):
+        t[0] = 86400.0 * (i // 5)
+        an.record("download", "org/gpt2", f"u{i % 3}")
+        an.record("inference", "org/gpt2", f"u{i % 3}", latency_ms=10.0 + i)
+    an.record("error", "org/gpt2", "u0"); an.record("download", "org/vit-b", "u1")
+    s = an.summary("org/gpt2")
+    assert s["events"] == 21 and s["unique_users"] == 3 and s["by_kind"]["download"] == 10 and s["p50_latency_ms"] == 15.0 and s["error_rate"] == pytest.approx(1 / 21)
+    assert an.popular(1) == [("org/gpt2", 10)] and an.trend("org/gpt2") == [(0.0, 5), (86400.0, 5)]
+    an.export(tmp_path / "ev.jsonl")
+    assert len((tmp_path / "ev.jsonl").read_text().splitlines()) == 22
+    abt = H.ABTest("ranker", {"control": 1, "new": 1})
+    g = torch.Generator().manual_seed(0)
+    for i in range(4000):
+        u = f"user{i}"
+        p = 0.10 if abt.assign(u) == "control" else 0.16
+        abt.record(u, float(torch.rand((), generator=g) < p))
+    res = abt.result("control", "new")
+    assert abt.assign("user7") == abt.assign("user7") and 0.45 < res["n"]["new"] / 4000 < 0.55 and res["significant"] and res["winner"] == "new" and 0.3 < res["lift"] < 1.0
+    same = H.ABTest("noop", {"a": 1, "b": 1})
+    for i in range(2000):
+        same.record(f"u{i}", float(torch.rand((), generator=g) < 0.2))
+    assert same.result("a", "b")["winner"] is None
+    # community
+    cmn = H.CommunityManager()
+    for i in range(6):
+        cmn.rate("org/gpt2", f"u{i}", 5)
+    cmn.rate("org/gpt2", "u0", 4)
+    with pytest.raises(ValueError):
+        cmn.rate("org/gpt2", "u9", 6)
+    root = cmn.comment("org/gpt2", "u1", "works well")
+    r1 = cmn.comment("org/gpt2", "u2", "agreed", parent=root); cmn.comment("org/gpt2", "u3", "other topic"); cmn.comment("org/gpt2", "u1", "thanks", parent=r1)
+    assert [c["text"] for c in cmn.thread("org/gpt2", root)] == ["works well", "agreed", "thanks"]
+    cmn.downloads["org/gpt2"] = 1500
+    assert cmn.stats("org/gpt2")["mean_rating"] == pytest.approx(29 / 6) and cmn.badges("org/gpt2") == ["popular", "well_rated"]
+    cmn.create_challenge("fastest", "latency_ms", higher_is_better=False, deadline=100.0)
+    cmn.submit("fastest", "ann", "m1", 12.0, now=1.0); cmn.submit("fastest", "bob", "m2", 9.0, now=2.0); cmn.submit("fastest", "ann", "m3", 8.0, now=3.0)
+    assert [(s["user"], s["score"]) for s in cmn.leaderboard("fastest")] == [("ann", 8.0), ("bob", 9.0)]
+    with pytest.raises(PermissionError):
+        cmn.submit("fastest", "eve", "m4", 1.0, now=101.0)
+    # enterprise
+    em = H.EnterpriseManager()
+    em.create_tenant("acme", storage_quota=1000, monthly_requests=2)
+    em.add_user("acme", "dev", "developer", "internal"); em.add_user("acme", "boss", "admin", "restricted")
+    em.label_model("secret-model", "confidential")
+    assert em.authorize("acme", "dev", "write") and not em.authorize("acme", "dev", "delete") and not em.authorize("acme", "dev", "read", "secret-model")
+    assert em.authorize("acme", "boss", "read", "secret-model") and not em.authorize("acme", "ghost", "read") and not em.authorize("other", "dev", "read")
+    em.charge_storage("acme", 800)
+    with pytest.raises(PermissionError):
+        em.charge_storage("acme", 300)
+    em.charge_request("acme"); em.charge_request("acme")
+    with pytest.raises(PermissionError):
+        em.charge_request("acme")
+    assert em.usage_report("acme") == {"storage": 0.8, "requests": 1.0, "users": 2}
+    # imports and visualisation
+    from torsh_b200 import onnx_io
+    lin = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.ReLU())
+    onnx_io.export_onnx(lin, (torch.randn(1, 4),), tmp_path / "m.onnx")
+    xin = torch.randn(5, 4)
+    got = H.load_onnx_model(tmp_path / "m.onnx")(xin)
+    got = got[0] if isinstance(got, (list, tuple)) else got
+    assert torch.allclose(torch.as_tensor(got), lin(xin), atol=1e-5)
+    dense = torch.nn.Sequential()
+    dense.add_module("fc", torch.nn.Linear(4, 3))
+    tfw = {"fc/kernel:0": torch.randn(4, 3).numpy(), "fc/bias:0": torch.randn(3).numpy()}
+    rp2 = H.import_tensorflow_checkpoint(tfw, dense)
+    assert rp2["loaded"] == ["fc.bias", "fc.weight"] and torch.allclose(dense.fc.weight, torch.as_tensor(tfw["fc/kernel:0"]).t())
+    tree = H.model_tree(torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.Sequential(torch.nn.Linear(3, 2))))
+    assert tree.splitlines()[0] == "Sequential: Sequential (23)" and "    0: Linear (8)" in tree
+    assert H.sparkline([0, 1, 2, 3, 4, 5, 6, 7]) == "▁▂▃▄▅▆▇█" and H.sparkline([2, 2]) == "▁▁"
+    svg = H.line_chart_svg({"train": [1.0, 0.5, 0.3], "val": [1.1, 0.7, 0.6]}, title="loss")
+    assert svg.startswith("<svg") and svg.count("<polyline") == 2 and ">loss<" in svg and svg.endswith("</svg>")
+    a, b = torch.nn.Linear(4, 3), torch.nn.Linear(4, 3)
+    b.bias.data.copy_(a.bias.data)
+    cmpm = H.compare_models(a, b)
+    assert cmpm["identical"] == ["bias"] and cmpm["most_changed"][0] == "weight" and not cmpm["only_in_a"]
