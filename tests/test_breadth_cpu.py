@@ -3681,3 +3681,136 @@ def test_nn_tools_stability_export_conversion_zoo_update_policies_and_recording(
     rec.remove(); rec.stats.clear()
     dead(torch.randn(2, 4))
     assert not rec.stats
+
+
+def test_series_ext_tests_stl_sarima_filters_changepoints_modes_imputation_cv_and_forecasters():
+    import math
+    import numpy as np
+    from scipy import stats as sst
+    from torsh_b200 import series_ext as E
+    g = torch.Generator().manual_seed(0)
+    rn = lambda n, s=1.0: torch.randn(n, generator=g, dtype=torch.float64) * s
+    n = 400
+    white, walk = rn(n), rn(n).cumsum(0)
+    # stationarity and diagnostics
+    assert E.adf_test(white)["stationary"] and not E.adf_test(walk)["stationary"] and E.kpss_test(white)["stationary"] and not E.kpss_test(walk)["stationary"]
+    assert E.stationarity_suite(white)["verdict"] == "stationary" and E.stationarity_suite(walk)["verdict"] == "unit_root" and E.stationarity_suite(walk)["suggested_differences"] == 1
+    assert E.adf_test(torch.arange(n, dtype=torch.float64) * 0.1 + white, regression="ct")["stationary"]
+    ar = torch.zeros(n, dtype=torch.float64)
+    for t in range(1, n):
+        ar[t] = 0.8 * ar[t - 1] + white[t]
+    assert E.ljung_box(white)["white_noise"] and not E.ljung_box(ar)["white_noise"] and E.ljung_box(ar)["p_value"] < 1e-6
+    jb = E.jarque_bera(white)
+    ref = sst.jarque_bera(white.numpy())
+    assert jb["statistic"] == pytest.approx(ref.statistic, rel=1e-6) and jb["p_value"] == pytest.approx(ref.pvalue, rel=1e-5) and jb["normal"] and not E.jarque_bera(white.exp())["normal"]
+    rd = E.residual_diagnostics(white)
+    assert rd["homoscedastic"] and abs(rd["mean"]) < 0.2 and not E.residual_diagnostics(white * torch.linspace(0.2, 3, n, dtype=torch.float64))["homoscedastic"]
+    drive = rn(n)
+    resp = torch.zeros(n, dtype=torch.float64)
+    for t in range(2, n):
+        resp[t] = 0.3 * resp[t - 1] + 0.8 * drive[t - 1] + 0.3 * rn(1)[0]
+    assert E.granger_causality(resp, drive)["causes"] and not E.granger_causality(drive, resp)["causes"]
+    assert E.transfer_entropy(drive, resp) > 5 * max(E.transfer_entropy(resp, drive), 1e-3) and E.transfer_entropy(drive, resp) > 0.1
+    # STL
+    tt = torch.arange(240, dtype=torch.float64)
+    trend, seas = 0.05 * tt + 3, 2 * torch.sin(2 * math.pi * tt / 12)
+    y = trend + seas + rn(240, 0.2)
+    d = E.stl(y, 12)
+    assert float((d["trend"] - trend)[12:-12].abs().mean()) < 0.15 and float((d["seasonal"] - seas)[12:-12].abs().mean()) < 0.2
+    assert torch.allclose(d["trend"] + d["seasonal"] + d["remainder"], y) and float(d["remainder"].std()) < 0.35
+    spiky = y.clone(); spiky[[50, 120, 190]] += 15
+    plain, rob = E.stl(spiky, 12), E.stl(spiky, 12, robust=True)
+    assert float((rob["seasonal"] - seas)[12:-12].abs().max()) < float((plain["seasonal"] - seas)[12:-12].abs().max()) and rob["weights"][[50, 120, 190]].max() < 0.05
+    # seasonal ARIMA
+    m = E.SARIMA((1, 0, 0)).fit(ar)
+    assert float(m.params[0]) == pytest.approx(0.8, abs=0.08) and m.sigma2 == pytest.approx(1.0, abs=0.2) and E.ljung_box(m.residuals, 10, 1)["white_noise"]
+    fc = m.forecast(3)
+    mu, phi = float(m.params[-1]), float(m.params[0])
+    assert float(fc[0]) == pytest.approx(mu + phi * (float(ar[-1]) - mu), abs=1e-6) and abs(float(fc[2]) - mu) < abs(float(fc[0]) - mu) + 1e-9
+    ma_series = white[1:] + 0.6 * white[:-1]
+    mm = E.SARIMA((0, 0, 1)).fit(ma_series)
+    assert float(mm.params[0]) == pytest.approx(0.6, abs=0.1)
+    season = trend[:144] + seas[:144] + rn(144, 0.1)
+    sm = E.SARIMA((0, 1, 1), (0, 1, 1, 12)).fit(season)
+    f12 = sm.forecast(12)
+    truth = 0.05 * torch.arange(144, 156, dtype=torch.float64) + 3 + 2 * torch.sin(2 * math.pi * torch.arange(144, 156, dtype=torch.float64) / 12)
+    assert float((f12 - truth).abs().mean()) < 0.4
+    best = E.auto_arima(walk[:200] * 0.5 + ar[:200], max_p=2, max_q=1)
+    assert best.order[1] == 1 and math.isfinite(best.aic)
+    assert E.auto_arima(ar[:300], max_p=2, max_q=1).order[1] == 0
+    # nonlinear filters on a pendulum-like model observed through a sine
+    dt = 0.05
+    f = lambda s: torch.stack([s[0] + dt * s[1], s[1] - dt * 9.81 * torch.sin(s[0])])
+    h = lambda s: torch.sin(s[0])[None]
+    state, truth_s, obs = torch.tensor([1.0, 0.0], dtype=torch.float64), [], []
+    for _ in range(150):
+        state = f(state)
+        truth_s.append(state); obs.append(h(state) + rn(1, 0.1))
+    truth_s = torch.stack(truth_s)
+    Q, R = torch.eye(2, dtype=torch.float64) * 1e-4, torch.eye(1, dtype=torch.float64) * 0.01
+    for Filt in (E.ExtendedKalmanFilter, E.UnscentedKalmanFilter):
+        est = Filt(f, h, Q, R, torch.tensor([0.5, 0.0]), torch.eye(2) * 0.5).filter(obs)
+        assert float((est[50:, 0] - truth_s[50:, 0]).abs().mean()) < 0.08, Filt.__name__
+    pf = E.ParticleFilter(lambda p, gen: torch.stack([f(s) for s in p]) + torch.randn(p.shape, generator=gen, dtype=torch.float64) * 0.02,
+                          lambda z, p: torch.exp(-0.5 * (z[0] - torch.sin(p[:, 0])) ** 2 / 0.01), torch.tensor([0.5, 0.0]) + 0.5 * torch.randn(300, 2, generator=g, dtype=torch.float64), seed=1)
+    pe = pf.filter(obs[:80])
+    assert float((pe[40:, 0] - truth_s[40:80, 0]).abs().mean()) < 0.15 and pf.resamples > 0
+    # change points
+    seg = torch.cat([rn(80) + 0, rn(60) + 4, rn(100) - 2])
+    cps = E.pelt(seg)
+    assert len(cps) == 2 and abs(cps[0] - 80) <= 3 and abs(cps[1] - 140) <= 3 and E.pelt(rn(200)) == []
+    vs = torch.cat([rn(100, 0.3), rn(100, 3.0)])
+    vc = E.pelt(vs, cost="normal", min_size=10)
+    assert len(vc) >= 1 and min(abs(c - 100) for c in vc) <= 8
+    # mode decompositions separate two tones
+    t2 = torch.arange(1024, dtype=torch.float64)
+    fast, slow = torch.sin(2 * math.pi * t2 / 16), 2 * torch.sin(2 * math.pi * t2 / 200)
+    imfs = E.emd(fast + slow)
+    assert len(imfs) >= 3 and torch.allclose(sum(imfs), fast + slow, atol=1e-9)
+    corr = lambda a, b: float(torch.corrcoef(torch.stack([a, b]))[0, 1])
+    assert corr(imfs[0][100:-100], fast[100:-100]) > 0.95 and max(corr(i[100:-100], slow[100:-100]) for i in imfs[1:]) > 0.9
+    modes, om = E.vmd(fast + slow + rn(1024, 0.05), k=2)
+    assert om[0] == pytest.approx(1 / 200, abs=2e-3) and om[1] == pytest.approx(1 / 16, abs=2e-3) and corr(modes[1][50:-50], fast[50:-50]) > 0.97 and corr(modes[0][50:-50], slow[50:-50]) > 0.97
+    # imputation and outliers
+    base = torch.sin(2 * math.pi * torch.arange(120, dtype=torch.float64) / 12) + 0.01 * torch.arange(120, dtype=torch.float64)
+    holes = base.clone(); holes[[0, 5, 6, 7, 50, 119]] = float("nan")
+    for method, tol in (("linear", 0.6), ("spline", 0.8), ("seasonal", 0.7), ("mean", 2.0), ("ffill", 1.5), ("bfill", 1.5)):
+        filled = E.impute(holes, method, 12)
+        assert not torch.isnan(filled).any() and float((filled - base).abs().max()) < tol, method
+    assert float((E.impute(holes, "spline")[5:8] - base[5:8]).abs().max()) < float((E.impute(holes, "mean")[5:8] - base[5:8]).abs().max())
+    with pytest.raises(ValueError):
+        E.impute(holes, "magic")
+    dirty = base + rn(120, 0.05); dirty[[30, 77]] += torch.tensor([6.0, -5.0], dtype=torch.float64)
+    for method in ("hampel", "zscore", "iqr", "isolation_forest"):
+        mk = E.detect_outliers(dirty, method)
+        assert mk[30] and mk[77] and int(mk.sum()) <= 6, method
+    fixed = E.treat_outliers(dirty, E.detect_outliers(dirty, "hampel"))
+    assert float((fixed - base).abs().max()) < 0.6 and float(E.treat_outliers(dirty, E.detect_outliers(dirty), "clip").max()) < 3
+    cloud = torch.cat([rn(300).reshape(150, 2), torch.tensor([[8.0, 8.0], [-9.0, 7.0]], dtype=torch.float64)])
+    sc = E.IsolationForest(seed=0).fit(cloud).score(cloud)
+    assert set(sc.topk(2).indices.tolist()) == {150, 151} and float(sc[:150].median()) < 0.5 < float(sc[150])
+    # rolling, features, CV, metrics
+    r = E.rolling(torch.arange(10.0), 3)
+    assert torch.isnan(r[:2]).all() and r[2:].tolist() == [1, 2, 3, 4, 5, 6, 7, 8] and E.rolling(torch.arange(10.0), 3, "max")[-1] == 9 and float(E.ewm(torch.ones(5), 0.3)[-1]) == 1.0
+    ft = E.extract_features(y, 12)
+    assert ft["seasonal_strength"] > 0.9 and ft["trend_strength"] > 0.9 and ft["linear_slope"] == pytest.approx(0.05, abs=0.01) and E.extract_features(white)["acf1"] < 0.2
+    assert E.extract_features(rn(240), 12)["seasonal_strength"] < 0.5
+    splits = list(E.TimeSeriesCV(3, test_size=10, gap=2).split(100))
+    assert [te[0] for _, te in splits] == [70, 80, 90] and all(max(tr) == te[0] - 3 for tr, te in splits) and [len(tr) for tr, _ in splits] == [68, 78, 88]
+    sl = list(E.TimeSeriesCV(3, test_size=10, mode="sliding", train_size=30).split(100))
+    assert all(len(tr) == 30 and tr[-1] == te[0] - 1 for tr, te in sl)
+    bl = list(E.TimeSeriesCV(4, mode="blocked").split(100))
+    assert [(tr[0], te[-1]) for tr, te in bl] == [(0, 24), (25, 49), (50, 74), (75, 99)]
+    em = list(E.TimeSeriesCV(3, test_size=10, embargo=5).split(100))
+    assert not set(range(80, 85)) & set(em[2][0]) and set(range(85, 90)) <= set(em[2][0]) and set(range(70, 80)) <= set(em[2][0]) and len(em[2][0]) == 85
+    naive = lambda tr, h: tr[-12:].repeat(h // 12 + 1)[:h]
+    mean_f = lambda tr, h: tr.mean().expand(h)
+    cv = E.TimeSeriesCV(4, test_size=12)
+    assert sum(cv.score(y, naive)) < sum(cv.score(y, mean_f))
+    fm = E.forecast_metrics(torch.tensor([10.0, 20.0]), torch.tensor([12.0, 18.0]), train=torch.tensor([1.0, 3.0, 2.0, 5.0]))
+    assert fm["mae"] == 2 and fm["rmse"] == 2 and fm["mape"] == pytest.approx(15.0) and fm["bias"] == 0 and fm["mase"] == pytest.approx(1.0) and fm["smape"] == pytest.approx((4 / 22 + 4 / 38) / 2 * 100)
+    # neural forecasters learn a seasonal pattern better than the mean
+    wave = (torch.sin(2 * math.pi * torch.arange(200.0) / 12) + 0.05 * torch.randn(200, generator=torch.Generator().manual_seed(1)))
+    for Model, kw in ((E.LSTMForecaster, {}), (E.GRUForecaster, {}), (E.CNNForecaster, {}), (E.TransformerForecaster, {"dim": 16, "heads": 2, "layers": 1})):
+        fcst = Model(window=24, horizon=1, **kw).fit(wave[:176], epochs=120).forecast(24)
+        assert fcst.shape == (24,) and float((fcst - wave[176:]).abs().mean()) < 0.35 < float((wave[:176].mean() - wave[176:]).abs().mean()), Model.__name__
