@@ -684,7 +684,7 @@ class _WindowForecaster(nn.Module):
             loss = nn.functional.mse_loss(self(xs), ys)
             loss.backward()
             opt.step()
-        self.train_loss = float(loss)
+        self.train_loss = float(loss.detach())
         self._tail = z[-self.window:]
         return self
 
