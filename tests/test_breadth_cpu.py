@@ -3814,3 +3814,140 @@ def test_series_ext_tests_stl_sarima_filters_changepoints_modes_imputation_cv_an
     for Model, kw in ((E.LSTMForecaster, {}), (E.GRUForecaster, {}), (E.CNNForecaster, {}), (E.TransformerForecaster, {"dim": 16, "heads": 2, "layers": 1})):
         fcst = Model(window=24, horizon=1, **kw).fit(wave[:176], epochs=120).forecast(24)
         assert fcst.shape == (24,) and float((fcst - wave[176:]).abs().mean()) < 0.35 < float((wave[:176].mean() - wave[176:]).abs().mean()), Model.__name__
+
+
+def test_signal_ext_windows_iir_design_filtering_adaptive_audio_resampling_streaming_and_packets():
+    import math
+    import numpy as np
+    from scipy import signal as ss
+    from torsh_b200 import signal_ext as G
+    torch.manual_seed(0)
+    dd = torch.float64
+    # windows against scipy
+    for name, sci in (("hann", "hann"), ("hamming", "hamming"), ("blackman", "blackman"), ("blackman_harris", "blackmanharris"), ("nuttall", "nuttall"), ("flat_top", "flattop"),
+                      ("bartlett", "bartlett"), ("bohman", "bohman"), ("cosine", "cosine"), ("rectangular", "boxcar")):
+        for n in (16, 33):
+            assert np.allclose(G.get_window(name, n).numpy(), ss.get_window(sci, n, fftbins=False), atol=1e-7), (name, n)
+    assert np.allclose(G.get_window("hann", 16, periodic=True).numpy(), ss.get_window("hann", 16, fftbins=True))
+    assert np.allclose(G.get_window("tukey", 32, alpha=0.4).numpy(), ss.windows.tukey(32, 0.4), atol=1e-12) and np.allclose(G.get_window("gaussian", 21, std=3.0).numpy(), ss.windows.gaussian(21, 3.0))
+    assert np.allclose(G.get_window("kaiser", 25, beta=8.0).numpy(), ss.windows.kaiser(25, 8.0), atol=1e-6) and np.allclose(G.get_window("exponential", 21, tau=4.0).numpy(), ss.windows.exponential(21, tau=4.0))
+    assert float(G.normalize_window(G.get_window("hann", 32)).sum()) == pytest.approx(1.0)
+    nt, beta = G.kaiser_parameters(60.0, 0.1)
+    ref_n, ref_b = ss.kaiserord(60.0, 0.1)
+    assert abs(nt - ref_n) <= 1 and beta == pytest.approx(ref_b, rel=1e-3)
+    # IIR designs against scipy (coefficients and magnitude response)
+    cases = [("butter", dict(N=4, Wn=0.3, btype="lowpass"), lambda: G.butterworth(4, 0.3)), ("butter", dict(N=3, Wn=0.4, btype="highpass"), lambda: G.butterworth(3, 0.4, "highpass")),
+             ("butter", dict(N=2, Wn=[0.2, 0.5], btype="bandpass"), lambda: G.butterworth(2, [0.2, 0.5], "bandpass")), ("butter", dict(N=2, Wn=[0.2, 0.5], btype="bandstop"), lambda: G.butterworth(2, [0.2, 0.5], "bandstop")),
+             ("cheby1", dict(N=4, rp=1.0, Wn=0.3), lambda: G.chebyshev1(4, 1.0, 0.3)), ("cheby1", dict(N=5, rp=0.5, Wn=0.4, btype="highpass"), lambda: G.chebyshev1(5, 0.5, 0.4, "highpass")),
+             ("cheby2", dict(N=4, rs=40.0, Wn=0.3), lambda: G.chebyshev2(4, 40.0, 0.3)), ("cheby2", dict(N=5, rs=30.0, Wn=0.5), lambda: G.chebyshev2(5, 30.0, 0.5)),
+             ("ellip", dict(N=4, rp=1.0, rs=40.0, Wn=0.3), lambda: G.elliptic(4, 1.0, 40.0, 0.3))]
+    for fam, kw, ours in cases:
+        b_ref, a_ref = getattr(ss, fam)(**kw)
+        b, a = ours()
+        assert np.allclose(b.numpy(), b_ref, atol=1e-8) and np.allclose(a.numpy(), a_ref, atol=1e-8), (fam, kw)
+    bb, ab = G.bessel(4, 0.3)
+    w, h = G.freqz(bb, ab, 512)
+    assert abs(float(h.abs()[int(0.3 * 512)]) - 1 / math.sqrt(2)) < 0.03 and float(h.abs()[0]) == pytest.approx(1.0, abs=1e-6) and G.is_stable(ab)
+    gd = G.group_delay(bb, ab)[1]
+    assert float(gd[:100].std()) < 0.05 * float(gd[:100].mean())                                    # maximally flat delay in the pass band
+    b, a = G.butterworth(4, 0.3)
+    w, h = G.freqz(b, a, 256)
+    wr, hr = ss.freqz(b.numpy(), a.numpy(), 256)
+    assert np.allclose(h.numpy(), hr, atol=1e-10) and np.allclose(w.numpy(), wr)
+    sos = G.iir_design(6, 0.25, output="sos")
+    x = torch.randn(300, dtype=dd)
+    b6, a6 = G.butterworth(6, 0.25)
+    assert sos.shape == (3, 6) and torch.allclose(G.sosfilt(sos, x), G.lfilter(b6, a6, x), atol=1e-9)
+    assert np.allclose(G.lfilter(b, a, x).numpy(), ss.lfilter(b.numpy(), a.numpy(), x.numpy()), atol=1e-10)
+    assert np.allclose(G.filtfilt(b, a, x).numpy(), ss.filtfilt(b.numpy(), a.numpy(), x.numpy(), padlen=15), atol=1e-8)
+    assert np.allclose(G.impulse_response(b, a, 32).numpy(), ss.lfilter(b.numpy(), a.numpy(), np.eye(1, 32)[0]), atol=1e-12)
+    st = G.stability_analysis(b, a)
+    assert st["stable"] and st["max_pole_radius"] < 1 and not G.is_stable([1.0, -2.5, 1.0]) and G.is_stable([1.0])
+    # FIR designs
+    h2 = G.firwin2(65, [0, 0.3, 0.4, 1.0], [1, 1, 0, 0])
+    assert np.allclose(h2.numpy(), ss.firwin2(65, [0, 0.3, 0.4, 1.0], [1, 1, 0, 0]), atol=1e-6)
+    hr = G.remez(41, [0, 0.25, 0.35, 1.0], [1, 0], weights=[1, 10])
+    mag = G.freqz(hr, 1.0, 512)[1].abs()
+    assert float((mag[:int(0.25 * 512)] - 1).abs().max()) < 0.05 and float(mag[int(0.36 * 512):].max()) < 0.01 and torch.allclose(hr, hr.flip(0))
+    assert np.allclose(G.savgol_coeffs(7, 2).flip(0).numpy(), ss.savgol_coeffs(7, 2)) and np.allclose(G.savgol_coeffs(7, 3, 1).flip(0).numpy(), ss.savgol_coeffs(7, 3, deriv=1), atol=1e-12)
+    noisy = torch.sin(torch.linspace(0, 6, 120, dtype=dd)) + 0.1 * torch.randn(120, dtype=dd)
+    assert np.allclose(G.savgol_filter(noisy, 11, 3).numpy(), ss.savgol_filter(noisy.numpy(), 11, 3), atol=1e-9)
+    assert np.allclose(G.median_filter1d(noisy, 5)[2:-2].numpy(), ss.medfilt(noisy.numpy(), 5)[2:-2]) and np.allclose(G.convolve1d([1, 2, 3], [0, 1]).numpy(), [0, 1, 2, 3])
+    mp = G.minimum_phase(h2)
+    assert torch.allclose(G.freqz(mp, 1.0, 128)[1].abs()[:30], G.freqz(h2, 1.0, 128)[1].abs()[:30], atol=0.02) and float(mp[:10].abs().sum()) > float(h2[:10].abs().sum())
+    # adaptive filters identify an unknown FIR system
+    unknown = torch.tensor([0.5, -0.3, 0.2, 0.1], dtype=dd)
+    src = torch.randn(3000, dtype=dd)
+    des = torch.from_numpy(np.convolve(src.numpy(), unknown.numpy())[:3000]) + 0.01 * torch.randn(3000, dtype=dd)
+    for fn, kw in ((G.lms_filter, dict(mu=0.01)), (G.nlms_filter, dict(mu=0.5)), (G.rls_filter, dict())):
+        y, e, wts = fn(src, des, taps=4, **kw)
+        assert torch.allclose(wts, unknown, atol=0.03) and float(e[-500:].pow(2).mean()) < 1e-3, fn.__name__
+    assert float(G.rls_filter(src[:200], des[:200], 4)[1][100:].pow(2).mean()) < float(G.lms_filter(src[:200], des[:200], 4, 0.01)[1][100:].pow(2).mean())
+    # scales, cepstra, MFCC, chroma, pitch
+    for fwd, inv in ((G.hz_to_bark, G.bark_to_hz), (G.hz_to_erb, G.erb_to_hz)):
+        assert torch.allclose(inv(fwd(torch.tensor([100.0, 1000.0, 8000.0]))), torch.tensor([100.0, 1000.0, 8000.0], dtype=dd))
+    sr = 16000
+    tt = torch.arange(4096, dtype=dd) / sr
+    tone = torch.sin(2 * math.pi * 220 * tt) + 0.5 * torch.sin(2 * math.pi * 440 * tt) + 0.3 * torch.sin(2 * math.pi * 660 * tt)
+    assert G.autocorr_pitch(tone, sr) == pytest.approx(220, rel=0.01)
+    f0, ap = G.yin_pitch(tone, sr)
+    assert f0 == pytest.approx(220, rel=0.005) and ap < 0.05 and G.yin_pitch(torch.randn(4096, dtype=dd), sr)[0] == 0.0
+    assert float(G.zero_crossing_rate(torch.sin(2 * math.pi * 1000 * tt))) == pytest.approx(2 * 1000 / sr, rel=0.02)
+    echo = torch.randn(1024, dtype=dd); echo[100:] += 0.6 * echo[:-100].clone()
+    cep = G.real_cepstrum(echo)
+    assert int(cep[20:512].argmax()) + 20 == 100 and G.power_cepstrum(echo).shape == (1024,)
+    cc, nd = G.complex_cepstrum(unknown)
+    ccr, ndr = ss.cceps(unknown.numpy()) if hasattr(ss, "cceps") else (cc.numpy(), nd)
+    assert np.allclose(cc.numpy(), ccr, atol=1e-8) and nd == ndr
+    from scipy.fft import dct
+    v = torch.randn(3, 20, dtype=dd)
+    assert np.allclose(G.dct2(v).numpy(), dct(v.numpy(), type=2, norm="ortho"), atol=1e-10)
+    mf = G.compute_mfcc(tone.float(), sr, n_mfcc=13, n_mels=26)
+    assert mf.shape[1] == 13 and torch.isfinite(mf).all() and not torch.allclose(mf[5], G.compute_mfcc(torch.randn(4096), sr, 13, 26)[5], atol=1.0)
+    a440 = torch.sin(2 * math.pi * 440 * torch.arange(8192, dtype=dd) / sr)
+    ch = G.chroma_features(a440.float(), sr)
+    assert int(ch.mean(1).argmax()) == 9                                                             # A
+    # resampling
+    sig = torch.sin(2 * math.pi * 5 * torch.arange(400, dtype=dd) / 400)
+    up = G.polyphase_resample(sig, 3, 2)
+    ref = torch.sin(2 * math.pi * 5 * torch.arange(600, dtype=dd) / 600)
+    assert up.shape == (600,) and float((up - ref)[40:-40].abs().max()) < 5e-3
+    assert np.allclose(up[40:-40].numpy(), ss.resample_poly(sig.numpy(), 3, 2)[40:-40], atol=5e-3)
+    assert float((G.sinc_resample(sig, 1.5) - ref)[40:-40].abs().max()) < 5e-3 and float((G.linear_resample(sig, 1.5) - torch.sin(2 * math.pi * 5 * torch.linspace(0, 399, 600, dtype=dd) / 400)).abs().max()) < 2e-3
+    two = torch.sin(2 * math.pi * 10 * torch.arange(2000, dtype=dd) / 2000) + torch.sin(2 * math.pi * 400 * torch.arange(2000, dtype=dd) / 2000)
+    dec = G.decimate(two, 4)
+    assert dec.shape == (500,) and float((dec - torch.sin(2 * math.pi * 10 * torch.arange(500, dtype=dd) / 500))[30:-30].abs().max()) < 0.02
+    # streaming equals batch
+    rb = G.RingBuffer(5)
+    rb.push(torch.arange(7.0))
+    assert rb.is_full() and rb.peek().tolist() == [2, 3, 4, 5, 6] and rb.pop(2).tolist() == [2, 3] and len(rb) == 3
+    sf = G.StreamingFilter(b, a)
+    chunks = torch.cat([sf.process(c) for c in x.split(37)])
+    assert torch.allclose(chunks, G.lfilter(b, a, x), atol=1e-12)
+    fir = G.firwin2(33, [0, 0.2, 0.3, 1], [1, 1, 0, 0])
+    oa = G.OverlapAddProcessor(fir, block=64)
+    got = torch.cat([oa.process(c) for c in x.split(50)] + [oa.flush()])
+    assert np.allclose(got.numpy(), np.convolve(x.numpy(), fir.numpy()), atol=1e-10)
+    sst = G.StreamingSTFT(64, 16)
+    frames = torch.cat([sst.push(c) for c in x.split(23)], 1)
+    full = torch.stft(x, 64, 16, window=torch.hann_window(64, dtype=dd), center=False, return_complex=True)
+    assert torch.allclose(frames, full, atol=1e-10)
+    smooth = lambda v: G.savgol_filter(v, 11, 2)
+    assert torch.allclose(G.process_chunked(smooth, noisy, 32, overlap=8), smooth(noisy), atol=1e-9)
+    # lifting and packets
+    for wv in ("haar", "cdf53"):
+        for n in (64, 63):
+            s_ = torch.randn(2, n, dtype=dd)
+            a_, d_ = G.lifting_dwt(s_, wv)
+            assert torch.allclose(G.lifting_idwt(a_, d_, wv), s_, atol=1e-12), (wv, n)
+    ramp = torch.arange(64, dtype=dd)
+    assert G.lifting_dwt(ramp, "cdf53")[1][:-1].abs().max() < 1e-12 and G.lifting_dwt(ramp, "haar")[1].abs().min() > 0.5
+    s_ = torch.randn(128, dtype=dd)
+    tree = G.wavelet_packet(s_, "db2", 3)
+    assert len(tree) == 15 and tree["ada"].shape == (16,) and torch.allclose(G.wavelet_packet_reconstruct(tree, "db2"), s_, atol=1e-10)
+    assert sum(float(tree[p].pow(2).sum()) for p in tree if len(p) == 3) == pytest.approx(float(s_.pow(2).sum()))
+    hf = torch.sin(2 * math.pi * 0.45 * torch.arange(256, dtype=dd))
+    basis = G.best_basis(G.wavelet_packet(hf, "db4", 3))
+    leaves_energy = sum(float(G.wavelet_packet(hf, "db4", 3)[p].pow(2).sum()) for p in basis)
+    assert leaves_energy == pytest.approx(float(hf.pow(2).sum()), rel=1e-9) and any(p.startswith("d") for p in basis) and basis != [""]
+    assert G.scale_to_frequency(G.frequency_to_scale(0.1)) == pytest.approx(0.1) and G.cone_of_influence(100, 8.0) == (12, 88) and G.scalogram(hf, [2.0, 4.0]).shape == (2, 256)
