@@ -3951,3 +3951,148 @@ def test_signal_ext_windows_iir_design_filtering_adaptive_audio_resampling_strea
     leaves_energy = sum(float(G.wavelet_packet(hf, "db4", 3)[p].pow(2).sum()) for p in basis)
     assert leaves_energy == pytest.approx(float(hf.pow(2).sum()), rel=1e-9) and any(p.startswith("d") for p in basis) and basis != [""]
     assert G.scale_to_frequency(G.frequency_to_scale(0.1)) == pytest.approx(0.1) and G.cone_of_influence(100, 8.0) == (12, 88) and G.scalogram(hf, [2.0, 4.0]).shape == (2, 256)
+
+
+def test_sparse_ext_arithmetic_factorisations_solvers_exchange_analysis_layers_and_optimizers(tmp_path):
+    import numpy as np
+    import scipy.sparse as sps
+    import scipy.sparse.linalg as spla
+    from torsh_b200 import sparse_ext as Z
+    from torsh_b200.sparse import CooTensor
+    torch.manual_seed(0)
+    dd = torch.float64
+    def rand_sparse(m, n, density, seed):
+        g = torch.Generator().manual_seed(seed)
+        d = torch.randn(m, n, generator=g, dtype=dd) * (torch.rand(m, n, generator=g) < density)
+        return CooTensor.from_dense(d), d
+    a, da = rand_sparse(12, 9, 0.3, 1)
+    b, db = rand_sparse(12, 9, 0.3, 2)
+    c, dc = rand_sparse(9, 7, 0.3, 3)
+    assert torch.allclose(Z.sparse_add(a, b, -2.0).to_dense(), da - 2 * db) and torch.allclose(Z.sparse_mul(a, b).to_dense(), da * db)
+    assert torch.allclose(Z.spgemm(a, c).to_dense(), da @ dc) and Z.spgemm(a, c).nnz == int((da @ dc != 0).sum())
+    assert torch.allclose(Z.sparse_sum(a, 0), da.sum(0)) and torch.allclose(Z.sparse_sum(a, 1), da.sum(1)) and float(Z.sparse_sum(a)) == pytest.approx(float(da.sum()))
+    for k in ("fro", "1", "inf"):
+        assert Z.sparse_norm(a, k) == pytest.approx(float(torch.linalg.matrix_norm(da, {"fro": "fro", "1": 1, "inf": float("inf")}[k])))
+    assert torch.allclose(Z.triu(a, 1).to_dense(), da.triu(1)) and torch.allclose(Z.tril(a, -1).to_dense(), da.tril(-1)) and torch.allclose(Z.diagonal(a), da.diagonal())
+    assert torch.allclose(Z.kron(a, c).to_dense(), torch.kron(da, dc)) and torch.equal(Z.identity(3).to_dense(), torch.eye(3, dtype=dd))
+    # SPD system: 2-D Laplacian
+    n = 8
+    lap = sps.kron(sps.eye(n), sps.diags([-1, 2, -1], [-1, 0, 1], shape=(n, n))) + sps.kron(sps.diags([-1, 2, -1], [-1, 0, 1], shape=(n, n)), sps.eye(n))
+    A = Z.from_scipy(lap.tocoo())
+    rhs = torch.randn(n * n, dtype=dd)
+    exact = torch.from_numpy(spla.spsolve(lap.tocsc(), rhs.numpy()))
+    x, info = Z.conjugate_gradient(A, rhs)
+    assert info["converged"] and torch.allclose(x, exact, atol=1e-8)
+    chol = Z.SparseCholesky(A)
+    Lf = chol.factor().to_dense()
+    assert torch.allclose(Lf @ Lf.t(), A.to_dense(), atol=1e-10) and torch.allclose(chol.solve(rhs), exact, atol=1e-9)
+    ic = Z.SparseCholesky(A, incomplete=True)
+    assert ic.factor().nnz == Z.tril(A).nnz < chol.factor().nnz
+    xp, ip = Z.conjugate_gradient(A, rhs, precond=ic.solve)
+    xj, ij = Z.conjugate_gradient(A, rhs, precond=Z.jacobi_preconditioner(A))
+    assert ip["converged"] and ip["iterations"] < 0.7 * info["iterations"] and torch.allclose(xp, exact, atol=1e-8) and ij["converged"]
+    with pytest.raises(ValueError):
+        Z.SparseCholesky(Z.sparse_add(A, Z.identity(n * n), -10.0))
+    # non-symmetric system: convection-diffusion
+    conv = lap + 0.8 * sps.kron(sps.eye(n), sps.diags([-1, 1], [-1, 1], shape=(n, n)))
+    B = Z.from_scipy(conv.tocoo())
+    exact_b = torch.from_numpy(spla.spsolve(conv.tocsc(), rhs.numpy()))
+    ilu = Z.IncompleteLU(B)
+    L, U = ilu.factors()
+    pat = B.to_dense() != 0
+    assert torch.allclose((L.to_dense() @ U.to_dense())[pat], B.to_dense()[pat], atol=1e-10) and L.nnz + U.nnz == B.nnz + n * n
+    for solver in (Z.bicgstab, Z.gmres):
+        x0, i0 = solver(B, rhs)
+        x1, i1 = solver(B, rhs, precond=ilu.solve)
+        assert i0["converged"] and i1["converged"] and i1["iterations"] < i0["iterations"] and torch.allclose(x1, exact_b, atol=1e-7), solver.__name__
+    tri = Z.tril(B)
+    assert torch.allclose(Z.solve_triangular(tri, rhs), torch.linalg.solve_triangular(tri.to_dense(), rhs[:, None], upper=False)[:, 0], atol=1e-10)
+    assert torch.allclose(Z.solve_triangular(Z.triu(B), rhs, lower=False), torch.linalg.solve_triangular(Z.triu(B).to_dense(), rhs[:, None], upper=True)[:, 0], atol=1e-10)
+    # reordering
+    perm0 = torch.randperm(n * n, generator=torch.Generator().manual_seed(5))
+    shuffled = Z.permute(A, perm0)
+    rcm = Z.reverse_cuthill_mckee(shuffled)
+    again = Z.permute(shuffled, rcm)
+    assert sorted(rcm.tolist()) == list(range(n * n)) and Z.bandwidth(again) < 0.4 * Z.bandwidth(shuffled) and Z.bandwidth(again) <= 2 * n
+    assert torch.allclose(torch.linalg.eigvalsh(again.to_dense()), torch.linalg.eigvalsh(A.to_dense()), atol=1e-9)
+    # exchange formats
+    Z.write_matrix_market(a, tmp_path / "a.mtx", comment="test matrix")
+    back = Z.read_matrix_market(tmp_path / "a.mtx")
+    assert torch.allclose(back.to_dense(), da) and "%test matrix" in (tmp_path / "a.mtx").read_text()
+    from scipy.io import mmread
+    assert np.allclose(mmread(str(tmp_path / "a.mtx")).toarray(), da.numpy())
+    Z.write_matrix_market(A, tmp_path / "s.mtx", symmetric=True)
+    assert "symmetric" in (tmp_path / "s.mtx").read_text().splitlines()[0] and torch.allclose(Z.read_matrix_market(tmp_path / "s.mtx").to_dense(), A.to_dense())
+    (tmp_path / "p.mtx").write_text("%%MatrixMarket matrix coordinate pattern skew-symmetric\n3 3 1\n2 1\n")
+    assert Z.read_matrix_market(tmp_path / "p.mtx").to_dense().tolist() == [[0, -1, 0], [1, 0, 0], [0, 0, 0]]
+    assert np.allclose(Z.to_scipy(a).toarray(), da.numpy()) and torch.allclose(Z.from_scipy(Z.to_scipy(a, "csc")).to_dense(), da)
+    Z.save_matlab(a, tmp_path / "a.mat")
+    assert torch.allclose(Z.load_matlab(tmp_path / "a.mat").to_dense(), da)
+    # analysis
+    rep = Z.analyze_pattern(A)
+    assert rep["symmetric"] and rep["diagonals"] == 5 and rep["bandwidth"] == n and rep["diagonal_dominant"] and rep["recommended_format"] == "dia" and rep["row_nnz_max"] == 5
+    blocks = CooTensor.from_dense(torch.kron((torch.rand(6, 6) < 0.3).double(), torch.ones(4, 4, dtype=dd)) + 0)
+    assert Z.analyze_pattern(blocks)["block_size"] == 4 and Z.analyze_pattern(blocks)["recommended_format"] == "bsr"
+    reg, _ = rand_sparse(200, 200, 0.02, 7)
+    assert Z.analyze_pattern(reg)["recommended_format"] in ("csr", "ell") and not Z.analyze_pattern(reg)["symmetric"]
+    mem = Z.memory_report(reg)
+    assert mem["csr"] < mem["coo"] < mem["dense"] and mem["best"] == "csr"
+    skew = torch.zeros(50, 50, dtype=dd); skew[torch.arange(50), torch.arange(50)] = 1.0; skew[0] = 1.0
+    hy = Z.HybridTensor(CooTensor.from_dense(skew))
+    v = torch.randn(50, 3, dtype=dd)
+    assert hy.k == 1 and hy.coo.nnz == 49 and torch.allclose(hy.matmul(v), skew @ v) and torch.allclose(hy.to_dense(), skew) and torch.allclose(hy.matmul(v[:, 0]), skew @ v[:, 0])
+    sy = Z.SymmetricTensor(A)
+    assert sy.nnz_stored == (A.nnz + n * n) // 2 and torch.allclose(sy.matmul(rhs), A.matmul(rhs)) and torch.allclose(sy.to_coo().to_dense(), A.to_dense())
+    with pytest.raises(ValueError):
+        Z.SymmetricTensor(a if a.shape[0] == a.shape[1] else B)
+    # layers
+    act = Z.SparseActivation("relu")(a)
+    assert torch.allclose(act.to_dense(), da.relu()) and act.nnz == int((da > 0).sum()) and torch.allclose(Z.SparseActivation("tanh")(a).to_dense(), da.tanh())
+    ln = Z.SparseLayerNorm()(a)
+    row = ln.values[ln.rows == 3]
+    assert abs(float(row.mean())) < 1e-9 and float(row.var(unbiased=False)) == pytest.approx(1.0, abs=1e-3)
+    sm = Z.sparse_softmax(a)
+    masked = da.masked_fill(da == 0, float("-inf")).softmax(1).nan_to_num(0.0)
+    assert torch.allclose(sm.to_dense(), masked, atol=1e-12)
+    att = Z.SparseAttention(16, heads=2)
+    xs = torch.randn(10, 16)
+    r_full, c_full = torch.arange(10).repeat_interleave(10), torch.arange(10).repeat(10)
+    q, k, vv = (f(xs).reshape(10, 2, 8).transpose(0, 1) for f in (att.q, att.k, att.v))
+    dense = att.o(torch.nn.functional.scaled_dot_product_attention(q, k, vv).transpose(0, 1).reshape(10, 16))
+    assert torch.allclose(att(xs, r_full, c_full), dense, atol=1e-5)
+    r_loc, c_loc = Z.SparseAttention.local_pattern(10, 1, global_tokens=1)
+    assert len(r_loc) == 28 + 16 and att(xs, r_loc, c_loc).shape == (10, 16)
+    mask = torch.full((10, 10), float("-inf")); mask[r_loc, c_loc] = 0
+    dense_l = att.o(torch.nn.functional.scaled_dot_product_attention(q, k, vv, attn_mask=mask).transpose(0, 1).reshape(10, 16))
+    assert torch.allclose(att(xs, r_loc, c_loc), dense_l, atol=1e-5)
+    sp = torch.sparse_coo_tensor(torch.tensor([[0, 1, 5, 7], [0, 1, 2, 7]]), torch.tensor([1.0, 3.0, 2.0, -1.0]), (8, 8))
+    mp = Z.sparse_max_pool2d(sp, 2).coalesce()
+    assert mp.shape == (4, 4) and mp.indices().t().tolist() == [[0, 0], [2, 1], [3, 3]] and mp.values().tolist() == [3.0, 2.0, -1.0]
+    sc = Z.SparseConv1d(4, 6, 3)
+    pos, feats = torch.tensor([2, 3, 10]), torch.randn(3, 4)
+    op, of = sc(pos, feats)
+    dense_in = torch.zeros(1, 4, 12); dense_in[0, :, pos] = feats.t()
+    ref = torch.nn.functional.conv1d(dense_in, sc.weight.permute(2, 1, 0), sc.bias, padding=1)[0].t()
+    assert op.tolist() == [2, 3, 10] and torch.allclose(of, ref[pos], atol=1e-6)
+    # row-wise optimizers
+    emb = Z.SparseEmbedding(100, 8)
+    before = emb.inner.weight.detach().clone()
+    opt = Z.SparseSGD(emb.parameters(), lr=0.5, momentum=0.9)
+    emb(torch.tensor([3, 7, 3])).sum().backward()
+    assert emb.inner.weight.grad.is_sparse
+    opt.step()
+    changed = (emb.inner.weight.detach() != before).any(1).nonzero().flatten().tolist()
+    assert changed == [3, 7] and opt.rows_touched == 2 and torch.allclose(emb.inner.weight.detach()[3], before[3] - 0.5 * 2)
+    e2 = Z.SparseEmbedding(50, 4); e3 = torch.nn.Embedding(50, 4); e3.weight.data.copy_(e2.inner.weight.data)
+    oa, ob = Z.SparseAdamW(e2.parameters(), lr=0.01), torch.optim.Adam(e3.parameters(), lr=0.01)
+    for _ in range(3):                                                       # rows hit every step follow dense Adam exactly
+        for e, o in ((e2, oa), (e3, ob)):
+            o.zero_grad(); (e(torch.tensor([1, 2])) ** 2).sum().backward(); o.step()
+    assert torch.allclose(e2.inner.weight.detach()[[1, 2]], e3.weight.detach()[[1, 2]], atol=1e-6) and torch.equal(e2.inner.weight.detach()[5], e3.weight.detach()[5])
+    acc = Z.SparseGradientAccumulator((100, 8))
+    for ids in ([1, 2], [2, 9]):
+        emb.inner.weight.grad = None
+        emb(torch.tensor(ids)).sum().backward()
+        acc.add(emb.inner.weight.grad)
+    tot = acc.result()
+    assert tot.indices()[0].tolist() == [1, 2, 9] and tot.values()[1].tolist() == [2.0] * 8
