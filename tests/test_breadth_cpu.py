@@ -4096,3 +4096,171 @@ def test_sparse_ext_arithmetic_factorisations_solvers_exchange_analysis_layers_a
         acc.add(emb.inner.weight.grad)
     tot = acc.result()
     assert tot.indices()[0].tolist() == [1, 2, 9] and tot.values()[1].tolist() == [2.0] * 8
+
+
+def test_graph_ext_pooling_geometric_hetero_kg_explain_kernels_transport_analysis_and_loaders(tmp_path):
+    import json
+    import math
+    import numpy as np
+    nx = pytest.importorskip("scipy")
+    from torsh_b200 import graph as G, graph_ext as X
+    torch.manual_seed(0)
+    # two cliques joined by one edge
+    k = 6
+    a = torch.combinations(torch.arange(k)).t()
+    ei = torch.cat([a, a + k, torch.tensor([[0], [k]])], 1)
+    ei = torch.cat([ei, ei.flip(0)], 1)
+    n = 2 * k
+    truth = torch.arange(n) // k
+    x = torch.randn(n, 8)
+    dp = X.DiffPool(8, 16, 2)
+    xp, ap = dp(x, ei)
+    assert xp.shape == (2, 16) and ap.shape == (2, 2) and torch.allclose(dp.assignment.sum(1), torch.ones(n), atol=1e-6) and dp.link_loss > 0 and dp.entropy_loss > 0
+    mc = X.MinCutPool(8, 2)
+    feats = torch.nn.functional.one_hot(truth, 2).float() @ torch.randn(2, 8) + 0.1 * torch.randn(n, 8)
+    opt = torch.optim.Adam(mc.parameters(), 0.05)
+    for _ in range(150):
+        mc(feats, ei)
+        loss = mc.cut_loss + mc.ortho_loss
+        opt.zero_grad(); loss.backward(); opt.step()
+    assign = mc.assignment.argmax(1)
+    assert (assign[:k] == assign[0]).all() and (assign[k:] == assign[k]).all() and assign[0] != assign[k] and float(mc.cut_loss) < -0.9
+    tk = X.TopKPool(8, 0.5)
+    xs, es, keep = tk(x, ei)
+    assert xs.shape == (6, 8) and es.max() < 6 and len(keep) == 6 and es.shape[1] == int(((torch.isin(ei[0], keep)) & (torch.isin(ei[1], keep))).sum())
+    batch = truth.clone()
+    gap = X.GlobalAttentionPool(8)
+    assert gap(x, batch).shape == (2, 8)
+    perm = torch.randperm(k)
+    s2s = X.Set2Set(8, 3)
+    assert s2s(x, batch).shape == (2, 16) and torch.allclose(s2s(x[:k]), s2s(x[:k][perm]), atol=1e-5)
+    # geometric layers: EGNN is rotation / translation equivariant, SchNet invariant
+    pos = torch.randn(10, 3)
+    h = torch.randn(10, 8)
+    rg = X.radius_graph(pos, 2.5)
+    kg = X.knn_graph(pos, 3)
+    assert (torch.cdist(pos, pos)[rg[0], rg[1]] <= 2.5).all() and (rg[0] != rg[1]).all() and kg.shape == (2, 30) and torch.bincount(kg[1]).tolist() == [3] * 10
+    q, _ = torch.linalg.qr(torch.randn(3, 3))
+    shift = torch.randn(3)
+    eg = X.EGNNLayer(8)
+    h1, p1 = eg(h, pos, kg)
+    h2, p2 = eg(h, pos @ q.t() + shift, kg)
+    assert torch.allclose(h1, h2, atol=1e-4) and torch.allclose(p1 @ q.t() + shift, p2, atol=1e-4)
+    sn = X.SchNetConv(8)
+    assert torch.allclose(sn(h, pos, kg), sn(h, pos @ q.t() + shift, kg), atol=1e-4) and X.RBFLayer(16)(torch.tensor([0.0, 2.5])).shape == (2, 16)
+    mp = X.MPNNConv(8, 4)
+    assert mp(h, kg, torch.randn(30, 4)).shape == (10, 8)
+    # heterogeneous, hypergraph, temporal
+    hg = X.HeteroGraphData()
+    hg.add_nodes("author", torch.randn(4, 5)); hg.add_nodes("paper", torch.randn(6, 7))
+    hg.add_edges("author", "writes", "paper", torch.tensor([[0, 1, 1, 3], [0, 0, 2, 5]]))
+    hg.add_edges("paper", "cites", "paper", torch.tensor([[0, 2], [2, 4]]))
+    out = X.HeteroConv({"author": 5, "paper": 7}, 9, hg.edge_types())(hg)
+    assert out["author"].shape == (4, 9) and out["paper"].shape == (6, 9) and hg.node_types() == ["author", "paper"]
+    reach = hg.metapath_reachable([("author", "writes", "paper"), ("paper", "cites", "paper")])
+    assert sorted(map(tuple, reach.t().tolist())) == [(0, 2), (1, 2), (1, 4)]
+    inc = torch.tensor([[0, 1, 2, 2, 3, 4], [0, 0, 0, 1, 1, 1]])
+    hc = X.HypergraphConv(3, 3)
+    with torch.no_grad():
+        hc.lin.weight.copy_(torch.eye(3)); hc.lin.bias.zero_()
+    xh = torch.randn(5, 3)
+    H = torch.zeros(5, 2); H[inc[0], inc[1]] = 1
+    dv, de = H.sum(1).rsqrt(), H.sum(0)
+    assert torch.allclose(hc(xh, inc), (dv[:, None] * H / de[None]) @ H.t() @ (dv[:, None] * xh), atol=1e-6)
+    tm = X.TemporalGraphMemory(6, 8, 3)
+    tm.update(torch.tensor([0, 1]), torch.tensor([2, 3]), torch.tensor([1.0, 2.0]), torch.randn(2, 3))
+    assert tm.embedding(torch.tensor([0, 2])).abs().sum() > 0 and tm.embedding(torch.tensor([4])).abs().sum() == 0 and tm.last.tolist() == [1, 2, 1, 2, 0, 0]
+    # knowledge graph embeddings rank true tails near the top
+    ents, rels = 12, 2
+    triples = torch.tensor([(i, 0, i + 1) for i in range(ents - 1)] + [(i, 1, i + 3) for i in range(ents - 3)])       # chains: translations can represent them
+    for model in ("transe", "distmult", "rotate"):
+        torch.manual_seed(1)
+        kge = X.KnowledgeGraphEmbedding(ents, rels, 16, model)
+        opt = torch.optim.Adam(kge.parameters(), 0.05)
+        g = torch.Generator().manual_seed(0)
+        for _ in range(300):
+            opt.zero_grad(); kge.loss(triples, g).backward(); opt.step()
+        ranks = [kge.rank_tail(*t) for t in triples.tolist()]
+        assert np.mean(ranks) < (2.5 if model != "distmult" else 5.0), (model, np.mean(ranks))
+    # explanations pick the edges that carry the signal
+    class WGCN(torch.nn.Module):
+        def __init__(self): super().__init__(); self.l1, self.l2 = torch.nn.Linear(2, 8), torch.nn.Linear(8, 2)
+        def forward(self, x, edge_index, edge_weight=None):
+            w = torch.ones(edge_index.shape[1]) if edge_weight is None else edge_weight
+            agg = lambda t: t + torch.zeros_like(t).index_add_(0, edge_index[1], t[edge_index[0]] * w[:, None])
+            return self.l2(torch.relu(agg(self.l1(x))))
+    star = torch.tensor([[1, 2, 3, 4], [0, 0, 0, 0]])
+    xs_ = torch.tensor([[0.0, 0], [5.0, 0], [0.0, 0.1], [0.0, 0.1], [0.0, 0.1]])
+    wg = WGCN()
+    with torch.no_grad():
+        wg.l1.weight.zero_(); wg.l1.weight[0, 0] = 1; wg.l1.bias.zero_(); wg.l2.weight.zero_(); wg.l2.weight[1, 0] = 1; wg.l2.bias.zero_(); wg.l2.bias[0] = 1.0
+    assert wg(xs_, star).argmax(-1)[0] == 1
+    attr = X.gradient_attribution(wg, xs_, star, 0, 1)
+    assert int(attr["grad_x_input"].sum(1).argmax()) == 1 and attr["saliency"].shape == (5, 2)
+    mask = X.GraphExplainer(wg, epochs=300, size_coeff=0.05, entropy_coeff=0.01).explain_node(xs_, star, 0)
+    assert int(mask.argmax()) == 0 and mask[0] > 0.8 and mask[1:].max() < mask[0] - 0.3
+    # kernels: isomorphic graphs are identical under WL, a path and a star differ
+    path4 = (torch.tensor([[0, 1, 1, 2, 2, 3], [1, 0, 2, 1, 3, 2]]), torch.zeros(4, dtype=torch.long))
+    p = torch.tensor([2, 0, 3, 1])
+    path4b = (p[path4[0]], torch.zeros(4, dtype=torch.long))
+    star4 = (torch.tensor([[0, 1, 0, 2, 0, 3], [1, 0, 2, 0, 3, 0]]), torch.zeros(4, dtype=torch.long))
+    for kern in (X.wl_subtree_kernel, X.shortest_path_kernel):
+        K = kern([path4, path4b, star4])
+        assert K[0, 0] == K[1, 1] == K[0, 1] and K[0, 2] / (K[0, 0] * K[2, 2]).sqrt() < 0.99 and torch.linalg.eigvalsh(K).min() > -1e-9, kern.__name__
+    # transport
+    pa, pb = torch.tensor([0.5, 0.5], dtype=torch.float64), torch.tensor([0.25, 0.75], dtype=torch.float64)
+    cost = torch.tensor([[0.0, 1.0], [1.0, 0.0]], dtype=torch.float64)
+    plan = X.sinkhorn(pa, pb, cost, 0.01)
+    assert torch.allclose(plan.sum(1), pa, atol=1e-6) and torch.allclose(plan.sum(0), pb, atol=1e-6) and float((plan * cost).sum()) == pytest.approx(0.25, abs=1e-3)
+    pts = torch.randn(7, 2, dtype=torch.float64)
+    c1 = torch.cdist(pts, pts)
+    pm = torch.randperm(7)
+    rot = torch.tensor([[0.0, -1.0], [1.0, 0.0]], dtype=torch.float64)
+    c2 = torch.cdist(pts[pm] @ rot, pts[pm] @ rot)
+    T, gw = X.gromov_wasserstein(c1, c2)
+    assert gw < 0.02 and (T.argmax(1) == torch.argsort(pm)).float().mean() > 0.8
+    assert X.gromov_wasserstein(c1, torch.cdist(torch.randn(7, 2, dtype=torch.float64) * 3, torch.zeros(7, 2, dtype=torch.float64)) * 0 + c1 * 2)[1] > gw
+    assert X.graph_edit_distance_upper(path4[0], 4, path4b[0], 4) <= 2 and X.graph_edit_distance_upper(path4[0], 4, star4[0], 4) >= 2
+    # analysis against closed forms / scipy
+    from scipy.sparse.csgraph import shortest_path
+    dist = X.floyd_warshall(ei, n)
+    adj = np.zeros((n, n)); adj[ei[0], ei[1]] = 1
+    assert np.allclose(dist.numpy(), shortest_path(adj, unweighted=True)) and float(dist.max()) == 3
+    sa = X.spectral_analysis(ei, n)
+    assert sa["components"] == 1 and 0 < sa["algebraic_connectivity"] < 1 and (torch.sign(sa["fiedler_vector"][:k]) == torch.sign(sa["fiedler_vector"][0])).all()
+    assert torch.sign(sa["fiedler_vector"][0]) != torch.sign(sa["fiedler_vector"][-1])
+    two = torch.cat([a, a + k], 1); two = torch.cat([two, two.flip(0)], 1)
+    assert X.spectral_analysis(two, n)["components"] == 2 and torch.allclose(X.laplacian(ei, n, "rw").sum(1), torch.zeros(n, dtype=torch.float64), atol=1e-12)
+    xf, u = X.graph_fourier_transform(torch.ones(n), two, n)
+    assert torch.allclose(u @ xf, torch.ones(n, dtype=torch.float64), atol=1e-9)
+    ce = X.centrality(ei, n)
+    assert set(ce["betweenness"].topk(2).indices.tolist()) == {0, k} and ce["betweenness"][1] == 0
+    assert float(ce["betweenness"][0]) == pytest.approx((k - 1) * k) and ce["degree"][0] == pytest.approx(6 / 11) and ce["closeness"][0] > ce["closeness"][1] and int(ce["eigenvector"].argmax()) in (0, k)
+    part = X.spectral_partition(ei, n, 2)
+    assert X.edge_cut(ei, part) == 1 and part[:k].unique().numel() == 1 and X.spectral_partition(ei, n, 4).unique().numel() == 4
+    # heads, autoencoder, batching
+    gs = [G.GraphData(torch.randn(5, 4), torch.tensor([[0, 1, 2, 3], [1, 2, 3, 4]]), None, torch.tensor(0)), G.GraphData(torch.randn(3, 4), torch.tensor([[0, 1], [1, 2]]), None, torch.tensor(1))]
+    bx, be, bb, by = X.batch_graphs(gs)
+    assert bx.shape == (8, 4) and be[:, -2:].tolist() == [[5, 6], [6, 7]] and bb.tolist() == [0] * 5 + [1] * 3 and by.tolist() == [0, 1]
+    gc = X.GraphClassifier(4, 8, 2)
+    assert gc(bx, be, bb).shape == (2, 2) and torch.allclose(gc(bx, be, bb)[1], gc(gs[1].x, gs[1].edge_index)[0], atol=1e-5)
+    for var in (False, True):
+        gae = X.GraphAutoEncoder(8, 16, 4, var)
+        opt = torch.optim.Adam(gae.parameters(), 0.02)
+        neg = G.negative_sampling(ei, n, ei.shape[1], seed=0)
+        first = None
+        for _ in range(80):
+            l = gae.loss(x, ei, neg)
+            opt.zero_grad(); l.backward(); opt.step()
+            first = first if first is not None else l.item()
+        assert l.item() < first and gae.eval().encode(x, ei).shape == (n, 4)
+    # loaders
+    (tmp_path / "e.txt").write_text("# comment\na b 1.5\nb c 2.0\n\nc a 0.5\n")
+    e, w, names = X.load_edge_list(tmp_path / "e.txt")
+    assert names == ["a", "b", "c"] and e.shape == (2, 6) and w.tolist() == [1.5, 2.0, 0.5] * 2 and X.load_edge_list(tmp_path / "e.txt", directed=True)[0].shape == (2, 3)
+    (tmp_path / "g.gml").write_text('graph [\n directed 0\n node [ id 10 label "x" value 1.5 ]\n node [ id 11 label "y" ]\n node [ id 12 label "z" ]\n edge [ source 10 target 11 ]\n edge [ source 11 target 12 ]\n]\n')
+    ge, labels, vals = X.load_gml(tmp_path / "g.gml")
+    assert labels == ["x", "y", "z"] and vals == [1.5, None, None] and sorted(map(tuple, ge.t().tolist())) == [(0, 1), (1, 0), (1, 2), (2, 1)]
+    (tmp_path / "g.json").write_text(json.dumps({"nodes": [{"id": "a", "features": [1, 0], "label": 0}, {"id": "b", "features": [0, 1], "label": 1}], "links": [{"source": "a", "target": "b"}]}))
+    jd = X.load_json_graph(tmp_path / "g.json")
+    assert jd.x.tolist() == [[1, 0], [0, 1]] and jd.y.tolist() == [0, 1] and jd.num_edges == 2
