@@ -4264,3 +4264,107 @@ def test_graph_ext_pooling_geometric_hetero_kg_explain_kernels_transport_analysi
     (tmp_path / "g.json").write_text(json.dumps({"nodes": [{"id": "a", "features": [1, 0], "label": 0}, {"id": "b", "features": [0, 1], "label": 1}], "links": [{"source": "a", "target": "b"}]}))
     jd = X.load_json_graph(tmp_path / "g.json")
     assert jd.x.tolist() == [[1, 0], [0, 1]] and jd.y.tolist() == [0, 1] and jd.num_edges == 2
+
+
+def test_text_analysis_readability_ngram_lm_retrieval_keywords_sentiment_language_entities_and_models():
+    import math
+    from sklearn.feature_extraction.text import TfidfVectorizer as SkTfidf
+    from torsh_b200.text import analysis as T
+    torch.manual_seed(0)
+    doc = ("Dr. Smith arrived at 9:30 a.m. on Monday. He met Prof. Jones, who had travelled from Berlin! Did they discuss the 3.5 percent rise? "
+           "Yes. The meeting ended early.")
+    ss = T.sentences(doc)
+    assert len(ss) == 5 and ss[0].endswith("Monday.") and ss[2].endswith("rise?") and ss[3] == "Yes."
+    assert [T.count_syllables(w) for w in ("cat", "table", "beautiful", "the", "wanted", "jumped", "make", "readability", "queue")] == [1, 2, 3, 1, 2, 1, 1, 5, 1]
+    easy = "The cat sat on the mat. The dog ran to the cat. It was a fun day."
+    hard = "Notwithstanding considerable methodological heterogeneity, the epidemiological investigations demonstrated statistically significant associations between environmental contaminants and neurodevelopmental abnormalities."
+    re_, rh = T.readability(easy), T.readability(hard)
+    assert re_["flesch_reading_ease"] > 90 > 10 > rh["flesch_reading_ease"] and rh["flesch_kincaid_grade"] > 15 > 3 > re_["flesch_kincaid_grade"] and rh["gunning_fog"] > re_["gunning_fog"] + 10
+    assert rh["coleman_liau"] > re_["coleman_liau"] and rh["smog"] > re_["smog"] and rh["automated_readability"] > re_["automated_readability"]
+    st = T.text_statistics(easy)
+    assert st["sentences"] == 3 and st["words"] == 17 and st["unique_words"] == 13 and st["syllables"] == 17 and 0.4 < st["stopword_ratio"] < 0.7
+    rep, var = ["a", "b"] * 100, [f"w{i}" for i in range(200)]
+    dr, dv = T.lexical_diversity(rep), T.lexical_diversity(var)
+    assert dr["ttr"] == 0.01 and dv["ttr"] == 1.0 and dv["mattr"] == 1.0 and dr["mattr"] == pytest.approx(0.04) and dv["mtld"] > 10 * dr["mtld"] and dr["yule_k"] > dv["yule_k"] and dv["hapax_ratio"] == 1.0
+    # n-gram language model
+    corpus = [s.split() for s in ["the cat sat on the mat", "the dog sat on the log", "the cat ate the fish", "a dog ate the bone", "the cat sat on the log"]]
+    for sm in ("laplace", "kneser_ney"):
+        lm = T.NGramLM(3, sm).fit(corpus)
+        tot = sum(lm.prob(w, ["the", "cat"]) for w in lm.vocab)
+        assert tot == pytest.approx(1.0, abs=(1e-9 if sm == "laplace" else 0.05)), sm
+        assert lm.prob("sat", ["the", "cat"]) > lm.prob("bone", ["the", "cat"]) and lm.perplexity(corpus) < lm.perplexity([["log", "the", "on", "sat", "cat", "the"]])
+    kn, lap = T.NGramLM(3, "kneser_ney").fit(corpus), T.NGramLM(3, "laplace").fit(corpus)
+    held = [["the", "dog", "sat", "on", "the", "mat"]]
+    assert kn.perplexity(held) < lap.perplexity(held) and kn.prob("zebra", ["the"]) > 0
+    gen = kn.generate(12, seed=3)
+    assert 1 <= len(gen) <= 12 and set(gen) <= kn.vocab
+    uni = T.NGramLM(1, "laplace").fit(corpus)
+    assert uni.prob("the") == pytest.approx((9 + 1) / (28 + 5 + len(uni.vocab))) and len(uni.vocab) == 12
+    # TF-IDF against scikit-learn, BM25 ranking
+    docs = ["the cat sat on the mat", "the dog chased the cat", "dogs and cats are pets", "stock markets fell sharply today"]
+    ours = T.TfidfVectorizer().fit(docs)
+    sk = SkTfidf(token_pattern=r"[A-Za-z0-9]+").fit(docs)
+    assert sorted(ours.vocabulary) == sorted(sk.vocabulary_) and torch.allclose(ours.transform(docs), torch.from_numpy(sk.transform(docs).toarray()), atol=1e-12)
+    bi = T.TfidfVectorizer((1, 2), sublinear_tf=True).fit(docs)
+    skb = SkTfidf(token_pattern=r"[A-Za-z0-9]+", ngram_range=(1, 2), sublinear_tf=True).fit(docs)
+    assert torch.allclose(bi.transform(docs), torch.from_numpy(skb.transform(docs).toarray()), atol=1e-12)
+    bm = T.BM25(docs)
+    assert bm.top_k("cat on a mat", 2) == [0, 1] and bm.top_k("markets today", 1) == [3] and bm.scores("unicorn") == [0.0] * 4
+    assert T.jaccard_similarity("abc", "bcd") == 0.5 and T.dice_similarity("abc", "bcd") == pytest.approx(2 / 3) and T.cosine_similarity_counts("aab", "ab") == pytest.approx(3 / math.sqrt(10))
+    assert T.jaro_winkler("MARTHA", "MARHTA") == pytest.approx(0.9611, abs=1e-4) and T.jaro_winkler("DIXON", "DICKSONX") == pytest.approx(0.8133, abs=1e-4) and T.jaro_winkler("abc", "xyz") == 0.0
+    s1, s2 = set(range(100)), set(range(50, 150))
+    sig1, sig2 = T.minhash_signature(s1, 256), T.minhash_signature(s2, 256)
+    assert abs(sum(a == b for a, b in zip(sig1, sig2)) / 256 - 1 / 3) < 0.1
+    # keywords and summaries
+    article = ("Neural networks learn representations from data. Deep neural networks stack many layers of representations. "
+               "Training deep neural networks requires large data sets and fast hardware. The weather was pleasant on Tuesday. "
+               "Graphics processors provide the fast hardware that training needs. Convolutional neural networks process images with shared weights.")
+    rk = T.rake_keywords(article, 5)
+    assert any("neural networks" in k for k, _ in rk) and rk[0][1] >= rk[-1][1]
+    tr = dict(T.textrank_keywords(article, 6))
+    assert "neural" in tr and "networks" in tr and "tuesday" not in tr
+    for method in ("textrank", "frequency"):
+        summ = T.summarize(article, 2, method)
+        assert len(summ) == 2 and not any("weather" in s for s in summ) and all(s in article for s in summ), method
+    assert T.summarize("One. Two.", 5) == ["One.", "Two."]
+    # sentiment, language, entities, cohesion
+    assert T.sentiment("I love this great phone")["label"] == "positive" and T.sentiment("This is a terrible, useless product")["label"] == "negative"
+    assert T.sentiment("The movie was not good")["score"] < 0 < T.sentiment("The movie was good")["score"] < T.sentiment("The movie was extremely good")["score"]
+    assert T.sentiment("I didn't hate it")["score"] > 0 and T.sentiment("The box is on the table")["label"] == "neutral"
+    samples = {"en": "the quick brown fox jumps over the lazy dog and then runs through the forest while the birds are singing in the trees this is what they have been doing for the whole day",
+               "de": "der schnelle braune fuchs springt über den faulen hund und läuft dann durch den wald während die vögel in den bäumen singen das haben sie den ganzen tag gemacht und nicht aufgehört",
+               "es": "el rápido zorro marrón salta sobre el perro perezoso y luego corre por el bosque mientras los pájaros cantan en los árboles esto es lo que han estado haciendo durante todo el día"}
+    li = T.LanguageIdentifier().fit(samples)
+    assert li.predict("where are the children going this morning") == "en" and li.predict("wohin gehen die kinder heute morgen und warum") == "de" and li.predict("a dónde van los niños esta mañana") == "es"
+    ents = T.extract_entities("Contact Maria Garcia at maria@example.org or visit https://example.org/team on 2026-03-14 at 10:30; budget $1,250.50 (up 12%). #launch @acme")
+    kinds = {e["type"]: e["text"] for e in ents}
+    assert kinds == {"name": "Maria Garcia", "email": "maria@example.org", "url": "https://example.org/team", "date": "2026-03-14", "time": "10:30", "money": "$1,250.50", "percent": "12%", "hashtag": "#launch", "mention": "@acme"}
+    assert [e["start"] for e in ents] == sorted(e["start"] for e in ents) and T.extract_entities("a@b.co", ["email"])[0]["end"] == 6
+    coh = T.lexical_cohesion("Solar panels convert light. Panels need light to work. Bananas are yellow.")
+    assert coh["breaks"] == [2] and coh["per_transition"][0] > 0 and coh["local"] > coh["global"] > 0
+    # models learn a toy task
+    vocab = 20
+    xs = torch.randint(1, vocab, (64, 12)); xs[:, 8:] = 0
+    ys = (xs == 7).any(1).long()
+    xs[:32, 2] = 7; ys[:32] = 1
+    xs[32:][xs[32:] == 7] = 8; ys[32:] = 0
+    for Model in (T.BiLSTMTextClassifier, T.TextCNN, T.TransformerTextClassifier):
+        torch.manual_seed(0)
+        m = Model(vocab, 2, 16) if Model is not T.TransformerTextClassifier else Model(vocab, 2, 16, 2, 1)
+        opt = torch.optim.Adam(m.parameters(), 0.01)
+        for _ in range(60):
+            opt.zero_grad(); torch.nn.functional.cross_entropy(m(xs), ys).backward(); opt.step()
+        assert (m(xs).argmax(1) == ys).float().mean() > 0.95, Model.__name__
+        padded = torch.cat([xs[:4], torch.zeros(4, 5, dtype=torch.long)], 1)
+        assert torch.allclose(m(padded), m(xs[:4]), atol=1e-4) or Model is T.TextCNN
+    tg = T.SequenceTagger(vocab, 3, 16, 16)
+    tags = (xs % 3) * (xs != 0)
+    opt = torch.optim.Adam(tg.parameters(), 0.02)
+    first = None
+    for _ in range(80):
+        l = tg.loss(xs, tags)
+        opt.zero_grad(); l.backward(); opt.step()
+        first = first if first is not None else l.item()
+    dec = tg.decode(xs[:8])
+    acc = sum(int(a == b) for seq, t in zip(dec, tags[:8]) for a, b in zip(seq, t[:8].tolist())) / 64
+    assert l.item() < 0.3 * first and all(len(d) == 8 for d in dec) and acc > 0.9
