@@ -4368,3 +4368,112 @@ def test_text_analysis_readability_ngram_lm_retrieval_keywords_sentiment_languag
     dec = tg.decode(xs[:8])
     acc = sum(int(a == b) for seq, t in zip(dec, tags[:8]) for a, b in zip(seq, t[:8].tolist())) / 64
     assert l.item() < 0.3 * first and all(len(d) == 8 for d in dec) and acc > 0.9
+
+
+def test_quantization_ext_learned_vq_sensitivity_mixed_precision_refinement_packing_and_reports():
+    import math
+    from torsh_b200 import quantization_ext as Q
+    torch.manual_seed(0)
+    # LSQ: step initialises from data, trains, and beats its initial error
+    w = torch.randn(64, 32)
+    lq = Q.LSQQuantizer(3)
+    first = (lq(w) - w).pow(2).mean().item()
+    assert lq(w).unique().numel() <= 8 and float(lq.step) == pytest.approx(2 * w.abs().mean().item() / math.sqrt(3), rel=1e-5)
+    opt = torch.optim.Adam(lq.parameters(), 0.01)
+    for _ in range(200):
+        loss = (lq(w) - w).pow(2).mean()
+        opt.zero_grad(); loss.backward(); opt.step()
+    assert loss.item() < first and lq.step.grad is not None
+    pc = Q.LSQQuantizer(4, per_channel=0)
+    pc(w * torch.logspace(-1, 1, 64)[:, None])
+    assert pc.step.shape == (64, 1) and pc.step[-1] > 20 * pc.step[0]
+    pact = Q.PACT(2, alpha=1.0)
+    y = pact(torch.tensor([-1.0, 0.2, 0.5, 3.0]))
+    assert y.tolist() == pytest.approx([0.0, 1 / 3, 2 / 3, 1.0]) 
+    y.sum().backward()
+    assert pact.alpha.grad is not None and pact.alpha.grad != 0
+    ll = Q.LSQLinear(32, 16, w_bits=4, a_bits=8)
+    xin = torch.randn(8, 32)
+    out = ll(xin)
+    out.sum().backward()
+    assert out.shape == (8, 16) and ll.weight.grad is not None and ll.wq.step.grad is not None and (out - torch.nn.functional.linear(xin, ll.weight, ll.bias)).abs().max() < 1.0
+    # vector quantisation of a matrix with clustered rows
+    centers = torch.randn(8, 4)
+    mat = (centers[torch.randint(0, 8, (256,))] + 0.01 * torch.randn(256, 4)).reshape(64, 16)
+    vq = Q.VectorQuantizedTensor(mat, dim=4, bits=3)
+    assert (vq.dequantize() - mat).abs().max() < 0.06 and vq.compression_ratio() > 7 and vq.dequantize().shape == mat.shape
+    pq = Q.VectorQuantizedTensor(torch.randn(64, 16), dim=4, bits=4, subspaces=2)
+    assert len(pq.codebooks) == 2 and pq.codebooks[0].shape == (16, 2) and pq.dequantize().shape == (64, 16)
+    cb, assign = Q.kmeans_codebook(torch.cat([torch.zeros(10, 2), torch.ones(10, 2) * 5]), 2)
+    assert sorted(cb[:, 0].round().tolist()) == [0.0, 5.0] and assign[:10].unique().numel() == 1
+    # sensitivity, Hessian trace, bit allocation
+    net = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
+    with torch.no_grad():
+        net[4].weight.mul_(5)
+    xs, ys = torch.randn(128, 16), torch.randint(0, 4, (128,))
+    loss_fn = lambda m: torch.nn.functional.cross_entropy(m(xs), ys)
+    sens = Q.layer_sensitivity(net, loss_fn, (8, 4, 2))
+    assert set(sens) == {"0", "2", "4"} and all(abs(sens[n][8]) < abs(sens[n][2]) + 1e-6 for n in sens) and all(abs(v[8]) < 0.05 for v in sens.values())
+    before = {n: p.detach().clone() for n, p in net.named_parameters()}
+    assert all(torch.equal(before[n], p) for n, p in net.named_parameters())
+    quad = torch.nn.Linear(3, 1, bias=False)
+    A = torch.tensor([[2.0, 0, 0], [0, 3.0, 0], [0, 0, 5.0]])
+    tr = Q.hessian_trace(quad, lambda m: 0.5 * (m.weight @ A @ m.weight.t()).sum(), samples=8)
+    assert tr["weight"] == pytest.approx(10 / 3, rel=1e-5)
+    ht = Q.hessian_trace(net, loss_fn, samples=8)
+    assert set(ht) == {"0.weight", "2.weight", "4.weight"} and all(math.isfinite(v) for v in ht.values())
+    sizes = {n: net[int(n)].weight.numel() for n in sens}
+    full = sum(sizes.values()) * 8
+    alloc = Q.allocate_bits(sizes, sens, 0.6 * full)
+    assert sum(sizes[n] * alloc[n] for n in sizes) <= 0.6 * full and set(alloc.values()) <= {8, 4, 2} and Q.allocate_bits(sizes, sens, full) == {n: 8 for n in sizes}
+    mixed = Q.apply_mixed_precision(net, alloc)
+    assert float(loss_fn(mixed)) < float(loss_fn(Q.apply_mixed_precision(net, {n: 2 for n in sizes}))) and torch.equal(net[0].weight, before["0.weight"])
+    # AdaRound beats nearest rounding on the layer output; bias correction removes the mean shift; equalisation preserves the function
+    lin = torch.nn.Linear(32, 16)
+    xcal = torch.randn(512, 32) + 0.5
+    wq_near = Q._fake_quant_weight(lin.weight.detach(), 3)
+    wq_ada = Q.adaround_layer(lin.weight.detach(), xcal, bits=3, iters=300)
+    err = lambda wq: float((xcal @ wq.t() - xcal @ lin.weight.detach().t()).pow(2).mean())
+    steps = (wq_ada / (lin.weight.detach().abs().amax(1, keepdim=True) / 3))
+    assert err(wq_ada) < 0.85 * err(wq_near) and torch.allclose(steps, steps.round(), atol=1e-4)
+    nb = Q.bias_correction(lin, wq_near, xcal)
+    shift = lambda b: (torch.nn.functional.linear(xcal, wq_near, b) - lin(xcal)).mean(0).abs().max().item()
+    assert shift(nb) < 1e-5 < shift(lin.bias.detach())
+    a, b = torch.nn.Linear(8, 16), torch.nn.Linear(16, 4)
+    with torch.no_grad():
+        a.weight[:4] *= 50
+    xq = torch.randn(32, 8)
+    ref = b(torch.relu(a(xq)))
+    spread0 = a.weight.detach().abs().amax(1)
+    Q.cross_layer_equalization(a, b)
+    assert torch.allclose(b(torch.relu(a(xq))), ref, atol=1e-4) and a.weight.detach().abs().amax(1).max() / a.weight.detach().abs().amax(1).min() < 0.3 * (spread0.max() / spread0.min())
+    assert torch.allclose(a.weight.detach().abs().amax(1), b.weight.detach().abs().amax(0), rtol=1e-4)
+    # calibration: heavy tails are clipped by entropy / mse, kept by max
+    cal = Q.HistogramCalibrator(1024)
+    data = torch.cat([torch.randn(100000), torch.tensor([12.0, -10.0])])
+    cal.collect(data[:50000]); cal.collect(data[50000:])
+    assert cal.max == 12.0 and float(cal.hist.sum()) == len(data)
+    t_ent, t_mse, t_pct = cal.threshold("entropy"), cal.threshold("mse"), cal.threshold("percentile", percentile=99.9)
+    assert 2.5 < t_pct < 4.0 and 2.5 < t_mse < 12 and 2.5 < t_ent <= 12 and cal.threshold("mse", bits=4) < t_mse
+    # packing and entropy coding
+    for bits in (1, 2, 4):
+        v = torch.randint(0, 2 ** bits, (37,))
+        p = Q.pack_bits(v, bits)
+        assert len(p) == math.ceil(37 * bits / 8) and torch.equal(Q.unpack_bits(p, bits, 37).long(), v)
+    sym = torch.cat([torch.zeros(700), torch.ones(200), torch.full((80,), 2.0), torch.full((20,), 3.0)]).long()[torch.randperm(1000)]
+    hc = Q.HuffmanCodec().fit(sym.tolist())
+    blob, nbits = hc.encode(sym.tolist())
+    assert hc.decode(blob, nbits) == sym.tolist() and hc.table[0][1] == 1 and hc.table[3][1] == 3
+    H = Q.entropy_bits(sym.tolist())
+    assert H <= hc.mean_code_length(sym.tolist()) < H + 1 and nbits == 700 + 400 + 240 + 60 and len(blob) == 175
+    one = Q.HuffmanCodec().fit([5, 5, 5])
+    assert one.decode(*one.encode([5, 5, 5])) == [5, 5, 5]
+    # metrics and report
+    r = torch.randn(1000)
+    q8, q4 = Q._fake_quant_weight(r[None], 8)[0], Q._fake_quant_weight(r[None], 4)[0]
+    m8, m4 = Q.quantization_metrics(r, q8), Q.quantization_metrics(r, q4)
+    assert m8["sqnr_db"] > m4["sqnr_db"] + 20 and m8["cosine"] > m4["cosine"] > 0.98 and m4["relative_l2"] > m8["relative_l2"] and m8["psnr_db"] > m8["sqnr_db"]
+    assert Q.kl_divergence_hist(r, r) == pytest.approx(0.0, abs=1e-9) and Q.kl_divergence_hist(r, r * 3) > 0.3
+    rep = Q.model_quantization_report(net, alloc)
+    assert len(rep["layers"]) == 3 and rep["mean_bits"] <= 0.6 * 8 + 1e-9 and rep["compression"] == pytest.approx(16 / rep["mean_bits"]) and rep["worst_layer"] in sizes
+    assert Q.model_quantization_report(net, 8)["compression"] == 2.0
