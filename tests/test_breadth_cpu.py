@@ -4477,3 +4477,95 @@ def test_quantization_ext_learned_vq_sensitivity_mixed_precision_refinement_pack
     rep = Q.model_quantization_report(net, alloc)
     assert len(rep["layers"]) == 3 and rep["mean_bits"] <= 0.6 * 8 + 1e-9 and rep["compression"] == pytest.approx(16 / rep["mean_bits"]) and rep["worst_layer"] in sizes
     assert Q.model_quantization_report(net, 8)["compression"] == 2.0
+
+
+def test_linalg_ext_multigrid_pivoting_refinement_randomized_krylov_and_analysis():
+    import math
+    import numpy as np
+    from scipy import linalg as sl
+    from torsh_b200 import linalg_ext as L
+    torch.manual_seed(0)
+    dd = torch.float64
+    # multigrid: grid-independent convergence on Poisson problems
+    for dim, n in ((1, 127), (2, 31), (2, 63)):
+        shape = (n,) * dim
+        xs = torch.linspace(0, 1, n + 2, dtype=dd)[1:-1]
+        exact = torch.sin(math.pi * xs) if dim == 1 else torch.sin(math.pi * xs)[:, None] * torch.sin(2 * math.pi * xs)[None]
+        mg = L.MultigridSolver(dim)
+        f = mg.apply(exact)
+        u, hist = mg.solve(f, 1e-9)
+        assert hist[-1] < 1e-9 and len(hist) <= 14 and float((u - exact).abs().max()) < 1e-7, (dim, n)
+        assert hist[1] / hist[0] < 0.25
+    gs = L.MultigridSolver(2, smoother="gauss_seidel", cycle="W")
+    ex = torch.randn(31, 31, dtype=dd)
+    u, hist = gs.solve(gs.apply(ex), 1e-9)
+    assert hist[-1] < 1e-9 and len(hist) <= 10 and float((u - ex).abs().max()) < 1e-6
+    jac_only = L.MultigridSolver(2)
+    xs31 = torch.linspace(0, 1, 33, dtype=dd)[1:-1]
+    fs = jac_only.apply(torch.sin(math.pi * xs31)[:, None] * torch.sin(math.pi * xs31)[None])
+    v = jac_only._smooth(torch.zeros(31, 31, dtype=dd), fs, 30)
+    assert float((fs - jac_only.apply(v)).norm() / fs.norm()) > 0.5                                      # plain smoothing stalls on smooth error; multigrid does not
+    # equilibration and preconditioners
+    bad = torch.randn(8, 8, dtype=dd) * torch.logspace(-6, 6, 8, dtype=dd)[:, None] * torch.logspace(4, -4, 8, dtype=dd)[None]
+    eq, r, c = L.equilibrate(bad)
+    assert torch.allclose(eq, r[:, None] * bad * c[None]) and torch.linalg.cond(eq) < 1e-6 * torch.linalg.cond(bad) and torch.allclose(eq.abs().amax(1), torch.ones(8, dtype=dd), atol=0.05)
+    spd = torch.randn(20, 20, dtype=dd); spd = spd @ spd.t() + 20 * torch.eye(20, dtype=dd)
+    rhs = torch.randn(20, dtype=dd)
+    M = L.ssor_preconditioner(spd)
+    minv = torch.stack([M(e) for e in torch.eye(20, dtype=dd)], 1)
+    assert torch.allclose(minv, minv.t(), atol=1e-10) and torch.linalg.cond(minv @ spd) < torch.linalg.cond(spd) and torch.allclose(L.diagonal_preconditioner(spd)(rhs), rhs / spd.diagonal())
+    # LU pivoting strategies
+    a = torch.randn(7, 7, dtype=dd)
+    for strat in ("partial", "complete", "rook"):
+        p, l, u, q, growth = L.lu_pivoted(a, strat)
+        assert torch.allclose(l @ u, a[p][:, q], atol=1e-10) and torch.allclose(l, torch.tril(l)) and l.abs().max() <= 1 + 1e-12 and growth < 10, strat
+    wilk = torch.tril(-torch.ones(10, 10, dtype=dd), -1) + torch.eye(10, dtype=dd); wilk[:, -1] = 1                # worst case for partial pivoting
+    assert L.lu_pivoted(wilk, "partial")[4] == pytest.approx(2 ** 9) and L.lu_pivoted(wilk, "complete")[4] < 3 and L.lu_pivoted(wilk, "rook")[4] < 3
+    # mixed-precision refinement reaches double accuracy from a float32 factorisation
+    sysm = torch.randn(50, 50, dtype=dd) + 8 * torch.eye(50, dtype=dd)
+    b = torch.randn(50, dtype=dd)
+    x, hist = L.solve_refined(sysm, b)
+    assert hist[0] > 1e-8 and hist[-1] < 1e-14 and torch.allclose(x, torch.linalg.solve(sysm, b), atol=1e-12)
+    lo, di, up = torch.rand(9, dtype=dd), 4 + torch.rand(10, dtype=dd), torch.rand(9, dtype=dd)
+    tri = torch.diag(di) + torch.diag(lo, -1) + torch.diag(up, 1)
+    r10 = torch.randn(10, dtype=dd)
+    assert torch.allclose(L.solve_tridiagonal(lo, di, up, r10), torch.linalg.solve(tri, r10), atol=1e-12)
+    U, V = torch.randn(20, 3, dtype=dd), torch.randn(20, 3, dtype=dd)
+    dvec = 5 + torch.rand(20, dtype=dd)
+    assert torch.allclose(L.woodbury_solve(lambda y: y / dvec, U, V, rhs), torch.linalg.solve(torch.diag(dvec) + U @ V.t(), rhs), atol=1e-10)
+    # randomised and Krylov methods
+    low = torch.randn(80, 6, dtype=dd) @ torch.randn(6, 60, dtype=dd)
+    qr = L.randomized_range_finder(low, 6)
+    assert float(torch.linalg.matrix_norm(low - qr @ qr.t() @ low)) < 1e-9 * float(torch.linalg.matrix_norm(low))
+    symm = torch.randn(60, 8, dtype=dd); symm = symm @ torch.diag(torch.tensor([50.0, 40, 30, 20, 10, 5, 2, 1], dtype=dd)) @ symm.t()
+    w, vecs = L.randomized_eigh(symm, 4)
+    assert torch.allclose(w, torch.linalg.eigvalsh(symm).flip(0)[:4], rtol=1e-6) and torch.allclose(symm @ vecs, vecs * w, atol=1e-5 * float(w[0]))
+    Fn = L.nystrom(symm, 12)
+    assert float(torch.linalg.matrix_norm(Fn @ Fn.t() - symm) / torch.linalg.matrix_norm(symm)) < 1e-6
+    lam, vec = L.power_iteration(symm)
+    assert lam == pytest.approx(float(torch.linalg.eigvalsh(symm)[-1]), rel=1e-8) and float((symm @ vec - lam * vec).norm()) < 1e-4 * lam
+    rv, rvecs = L.lanczos(lambda z: spd @ z, 20, 20)
+    assert torch.allclose(rv, torch.linalg.eigvalsh(spd), atol=1e-8) and torch.allclose(spd @ rvecs[:, -1], rv[-1] * rvecs[:, -1], atol=1e-7)
+    few = L.lanczos(lambda z: spd @ z, 20, 8)[0]
+    assert few[-1] == pytest.approx(float(torch.linalg.eigvalsh(spd)[-1]), rel=1e-3)
+    g = torch.randn(6, 6, dtype=dd)
+    assert np.allclose(L.expm_taylor(g).numpy(), sl.expm(g.numpy()), atol=1e-10) and np.allclose(L.expm_taylor(10 * g).numpy(), sl.expm(10 * g.numpy()), rtol=1e-8)
+    big = -spd / 20
+    v0 = torch.randn(20, dtype=dd)
+    assert torch.allclose(L.expm_multiply(lambda z: big @ z, v0, 0.7, 20), torch.linalg.matrix_exp(0.7 * big) @ v0, atol=1e-10)
+    # subspaces, alignment, report
+    defc = torch.randn(6, 3, dtype=dd) @ torch.randn(3, 8, dtype=dd)
+    ns = L.null_space(defc)
+    assert ns.shape == (8, 5) and float((defc @ ns).abs().max()) < 1e-10 and torch.allclose(ns.t() @ ns, torch.eye(5, dtype=dd), atol=1e-10) and L.orth(defc).shape == (6, 3)
+    e = torch.eye(4, dtype=dd)
+    ang = L.subspace_angles(e[:, :2], torch.stack([e[:, 0], (e[:, 1] + e[:, 2]) / math.sqrt(2)], 1))
+    assert sorted(ang.tolist()) == pytest.approx([0.0, math.pi / 4], abs=1e-7) and np.allclose(np.sort(ang.numpy()), np.sort(sl.subspace_angles(e[:, :2].numpy(), np.stack([e[:, 0].numpy(), ((e[:, 1] + e[:, 2]) / math.sqrt(2)).numpy()], 1))), atol=1e-7)
+    rot, _ = torch.linalg.qr(torch.randn(5, 5, dtype=dd))
+    pts = torch.randn(30, 5, dtype=dd)
+    R, res = L.procrustes(pts, pts @ rot)
+    assert torch.allclose(R, rot, atol=1e-10) and res < 1e-10
+    rep = L.matrix_analysis(spd)
+    assert rep["symmetric"] and rep["positive_definite"] and rep["definiteness"] == "positive" and rep["rank"] == 20 and rep["condition"] == pytest.approx(float(torch.linalg.cond(spd)), rel=1e-8)
+    tri_rep = L.matrix_analysis(tri)
+    assert tri_rep["bandwidth"] == (1, 1) and tri_rep["diagonally_dominant"] and not tri_rep["symmetric"] and tri_rep["sparsity"] == pytest.approx(72 / 100)
+    assert L.matrix_analysis(rot)["orthogonal"] and L.matrix_analysis(defc)["rank"] == 3 and L.matrix_analysis(-spd)["definiteness"] == "negative" and 1 <= rep["stable_rank"] <= 20
