@@ -1194,3 +1194,72 @@ def test_hub_services_transfers_cache_cards_analytics_community_enterprise_and_i
     b.bias.data.copy_(a.bias.data)
     cmpm = H.compare_models(a, b)
     assert cmpm["identical"] == ["bias"] and cmpm["most_changed"][0] == "weight" and not cmpm["only_in_a"]
+
+
+def test_metrics_more_rank_tests_corrections_uncertainty_faithfulness_continual_and_reports():
+    import math
+    import numpy as np
+    from scipy import stats
+    from statistics import mean
+    from torsh_b200.utils import metrics_more as M
+    g = torch.Generator().manual_seed(0)
+    a, b, c = torch.randn(30, generator=g, dtype=torch.float64), torch.randn(25, generator=g, dtype=torch.float64) + 0.8, torch.randn(28, generator=g, dtype=torch.float64) - 0.3
+    a[3] = a[7]                                                             # a tie
+    mw, ref = M.mann_whitney_u(a, b), stats.mannwhitneyu(a.numpy(), b.numpy(), alternative="two-sided", method="asymptotic")
+    assert mw["u"] == pytest.approx(ref.statistic) and mw["p_value"] == pytest.approx(ref.pvalue, rel=1e-9) and mw["effect_size"] > 0.3
+    kw, refk = M.kruskal_wallis(a, b, c), stats.kruskal(a.numpy(), b.numpy(), c.numpy())
+    assert kw["statistic"] == pytest.approx(refk.statistic) and kw["p_value"] == pytest.approx(refk.pvalue, rel=1e-8)
+    scores = torch.rand(12, 4, generator=g, dtype=torch.float64); scores[:, 0] += 0.6; scores[2, 1] = scores[2, 2]
+    fr, reff = M.friedman_test(scores), stats.friedmanchisquare(*scores.t().numpy())
+    assert fr["statistic"] == pytest.approx(reff.statistic) and fr["p_value"] == pytest.approx(reff.pvalue, rel=1e-8) and int(fr["mean_ranks"].argmax()) == 0
+    nm = M.nemenyi_test(scores)
+    assert nm["critical_difference"] == pytest.approx(2.569 * math.sqrt(4 * 5 / (6 * 12))) and nm["significant"][0, 1:].any() and not nm["significant"].diagonal().any()
+    d52 = torch.tensor([[0.02, 0.03], [0.01, 0.04], [0.03, 0.02], [0.02, 0.02], [0.04, 0.01]])
+    t52 = M.five_by_two_cv_test(d52)
+    s2 = [((x - (x + y) / 2) ** 2 + (y - (x + y) / 2) ** 2) for x, y in d52.tolist()]
+    assert t52["t"] == pytest.approx(0.02 / math.sqrt(mean(s2))) and 0 < t52["p_value"] < 1
+    pv = [0.001, 0.04, 0.03, 0.2, 0.012]
+    from scipy.stats import false_discovery_control
+    assert M.multiple_comparison_correction(pv, "bonferroni")["adjusted"].tolist() == pytest.approx([0.005, 0.2, 0.15, 1.0, 0.06])
+    assert M.multiple_comparison_correction(pv, "holm")["adjusted"].tolist() == pytest.approx([0.005, 0.09, 0.09, 0.2, 0.048]) and M.multiple_comparison_correction(pv, "holm")["reject"].tolist() == [True, False, False, False, True]
+    assert np.allclose(M.multiple_comparison_correction(pv, "fdr_bh")["adjusted"].numpy(), false_discovery_control(pv, method="bh"))
+    assert M.effect_size(b, a) == pytest.approx((float(b.mean() - a.mean())) / math.sqrt((24 * float(b.var()) + 29 * float(a.var())) / 53)) and abs(M.effect_size(b, a, "hedges_g")) < abs(M.effect_size(b, a))
+    assert M.effect_size([3, 4, 5], [0, 1, 2], "cliffs_delta") == 1.0 and M.effect_size([1, 2], [1, 2], "cliffs_delta") == 0.0
+    assert M.aicc(-100.0, 3, 20) == pytest.approx(206 + 24 / 16) and M.hqic(-100.0, 3, 50) == pytest.approx(200 + 6 * math.log(math.log(50))) and M.akaike_weights([100.0, 102.0, 110.0])[0] == pytest.approx(1 / (1 + math.exp(-1) + math.exp(-5)))
+    # uncertainty: members that disagree -> epistemic; members that agree on 50/50 -> aleatoric
+    disagree = torch.tensor([[[0.99, 0.01]], [[0.01, 0.99]]]); unsure = torch.tensor([[[0.5, 0.5]], [[0.5, 0.5]]])
+    ud, uu = M.uncertainty_decomposition(disagree), M.uncertainty_decomposition(unsure)
+    assert ud["epistemic"][0] > 0.6 > 0.1 > ud["aleatoric"][0] and uu["epistemic"][0] < 1e-9 and uu["aleatoric"][0] == pytest.approx(math.log(2)) and ud["variation_ratio"][0] == 0.5
+    net = torch.nn.Sequential(torch.nn.Linear(4, 16), torch.nn.ReLU(), torch.nn.Dropout(0.5), torch.nn.Linear(16, 3), torch.nn.BatchNorm1d(3)).train()
+    mc = M.mc_dropout_predict(net, torch.randn(5, 4), 8)
+    assert mc.shape == (8, 5, 3) and not torch.allclose(mc[0], mc[1]) and net.training and torch.allclose(mc.sum(-1), torch.ones(8, 5))
+    pic = M.prediction_interval_coverage([0, 0, 0, 0], [1, 1, 1, 1], [0.5, 1.5, -0.2, 1.0])
+    assert pic == {"coverage": 0.5, "mean_width": 1.0, "winkler_miss": pytest.approx(0.175)}
+    sr = M.selective_risk_curve([0.9, 0.8, 0.7, 0.6], [1, 1, 0, 1])
+    assert sr["risk"].tolist() == pytest.approx([0, 0, 1 / 3, 0.25]) and sr["aurc"] == pytest.approx((1 / 3 + 0.25) / 4)
+    # faithfulness: the true weights are a better attribution than random ones
+    wts = torch.tensor([5.0, 0.1, 3.0, 0.0, -0.2, 1.0, 0.05, 2.0])
+    fn = lambda v: (wts * v).sum()
+    xin = torch.ones(8)
+    good, bad = M.deletion_insertion_curves(fn, xin, wts, steps=8), M.deletion_insertion_curves(fn, xin, -wts, steps=8)
+    assert good["deletion_auc"] < bad["deletion_auc"] and good["insertion_auc"] > bad["insertion_auc"] and good["deletion"][0] == pytest.approx(float(wts.sum())) and good["deletion"][-1] == 0
+    assert M.attribution_sparsity(torch.tensor([0.0, 0, 0, 1])) == pytest.approx(0.75) and M.attribution_sparsity(torch.ones(4)) == pytest.approx(0.0)
+    clf = lambda v: torch.stack([v[:, 0], -v[:, 0]], 1)
+    xs = torch.cat([torch.full((50, 2), 1.0), torch.full((50, 2), -1.0)]); ys = torch.cat([torch.zeros(50), torch.ones(50)]).long()
+    rc = M.robustness_curve(clf, xs, ys, [0.0, 0.5, 1.0, 3.0, 10.0])
+    assert rc["accuracy"][0] == 1.0 and rc["accuracy"][1] > rc["accuracy"][3] > 0.4 and rc["breakdown_level"] in (None, 10.0) and 0.5 < rc["auc"] < 1
+    ps = M.prediction_stability(torch.tensor([[0, 1, 2, 1], [0, 1, 2, 0], [0, 1, 1, 1]]))
+    assert ps["unanimous"] == 0.5 and ps["pairwise_agreement"] == pytest.approx((0.75 + 0.75 + 0.5) / 3)
+    # continual learning and recommendation quality
+    acc = torch.tensor([[0.9, 0.2, 0.1], [0.7, 0.85, 0.3], [0.6, 0.8, 0.9]])
+    cl = M.continual_learning_metrics(acc, baseline=torch.tensor([0.1, 0.1, 0.1]))
+    assert cl["average_accuracy"] == pytest.approx(2.3 / 3) and cl["forgetting"] == pytest.approx((0.3 + 0.05) / 2) and cl["backward_transfer"] == pytest.approx((-0.3 - 0.05) / 2) and cl["forward_transfer"] == pytest.approx((0.1 + 0.2) / 2)
+    pop = {0: 1000, 1: 500, 2: 10, 3: 5, 4: 1}
+    feats = torch.eye(5)
+    head, tail = M.recommendation_quality([[0, 1], [0, 1]], pop, feats, 5), M.recommendation_quality([[2, 3], [3, 4]], pop, feats, 5)
+    assert tail["novelty"] > head["novelty"] + 4 and tail["coverage"] == 0.6 > head["coverage"] == 0.4 and head["diversity"] == 1.0 and head["exposure_gini"] > tail["exposure_gini"]
+    # reports
+    rb = M.ReportBuilder("Study").add_table("main_results", {"ours": {"acc": 0.91, "err_%": 9.0}, "base_line": {"acc": 0.88, "err_%": 12.0}}, {"err_%": False})
+    md, tex = rb.to_markdown(), rb.to_latex()
+    assert "| ours | **0.910** | **9.000** |" in md and "| base_line | 0.880 | 12.000 |" in md and md.startswith("# Study")
+    assert r"\textbf{0.910}" in tex and r"base\_line" in tex and r"err\_\%" in tex and tex.count(r"\\") == 3 and r"\toprule" in tex
