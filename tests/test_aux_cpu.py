@@ -1263,3 +1263,200 @@ def test_metrics_more_rank_tests_corrections_uncertainty_faithfulness_continual_
     md, tex = rb.to_markdown(), rb.to_latex()
     assert "| ours | **0.910** | **9.000** |" in md and "| base_line | 0.880 | 12.000 |" in md and md.startswith("# Study")
     assert r"\textbf{0.910}" in tex and r"base\_line" in tex and r"err\_\%" in tex and tex.count(r"\\") == 3 and r"\toprule" in tex
+
+
+def test_autograd_services_federated_compression_gc_planning_replay_debugger_vjp_quantum_and_recovery():
+    import math
+    from torsh_b200.autograd import services as S
+    torch.manual_seed(0)
+    dd = torch.float64
+    # robust aggregation under Byzantine clients
+    honest = [torch.ones(10, dtype=dd) + 0.05 * torch.randn(10, dtype=dd) for _ in range(7)]
+    bad = [torch.full((10,), -50.0, dtype=dd) for _ in range(2)]
+    ups = honest + bad
+    target = torch.ones(10, dtype=dd)
+    errs = {m: float((S.aggregate_updates(ups, method=m, f=2, trim=0.25) - target).norm()) for m in ("fedavg", "median", "trimmed_mean", "krum", "multi_krum", "norm_clipping", "geometric_median")}
+    assert errs["fedavg"] > 10 and all(errs[m] < 0.5 for m in ("median", "trimmed_mean", "krum", "multi_krum", "geometric_median")) and errs["norm_clipping"] < errs["fedavg"] / 5
+    assert torch.allclose(S.aggregate_updates(honest[:2], [1, 3]), 0.25 * honest[0] + 0.75 * honest[1])
+    total, masked = S.secure_aggregate(honest)
+    assert torch.allclose(total, sum(honest), atol=1e-9) and all((m - u).norm() > 1 for m, u in zip(masked, honest))
+    total_d, _ = S.secure_aggregate(honest, dropped=[2, 5])
+    assert torch.allclose(total_d, sum(h for i, h in enumerate(honest) if i not in (2, 5)), atol=1e-9)
+    # federated rounds converge on shards with different local optima; FedProx keeps local models closer
+    w_true = torch.tensor([1.0, -2.0, 0.5])
+    clients = []
+    for c in range(6):
+        x = torch.randn(40, 3) + 0.3 * c
+        clients.append((x, x @ w_true + 0.01 * torch.randn(40)))
+    def local_train(model, data, mu=0.0, ref=None):
+        x, y = data
+        opt = torch.optim.SGD(model.parameters(), 0.05)
+        g = {n: p.detach().clone() for n, p in model.named_parameters()}
+        for _ in range(5):
+            loss = torch.nn.functional.mse_loss(model(x).squeeze(-1), y) + (S.fedprox_penalty(model, g, mu) if mu else 0.0)
+            opt.zero_grad(); loss.backward(); opt.step()
+        return len(x)
+    glob = torch.nn.Linear(3, 1, bias=False)
+    srv = S.FederatedServer(glob, seed=0)
+    for r in range(40):
+        srv.round(srv.select(clients, 3), local_train)
+    assert torch.allclose(glob.weight.detach()[0], w_true, atol=0.05) and srv.history[-1]["update_norm"] < srv.history[0]["update_norm"] and len(srv.select(clients, 2, "round_robin")) == 2
+    plain, prox = torch.nn.Linear(3, 1, bias=False), torch.nn.Linear(3, 1, bias=False)
+    prox.load_state_dict(plain.state_dict())
+    s1, s2 = S.FederatedServer(plain, seed=1), S.FederatedServer(prox, seed=1)
+    d1 = s1.round(clients[:3], local_train)["divergence"]
+    d2 = s2.round(clients[:3], lambda m, c: local_train(m, c, mu=5.0))["divergence"]
+    assert d2 < d1
+    dp = S.FederatedServer(torch.nn.Linear(3, 1, bias=False), dp_clip=0.1, dp_noise=0.0)
+    assert max(dp.round(clients[:3], local_train)["client_norms"]) <= 0.1 + 1e-9
+    imp = S.FederatedServer(glob, seed=0).select(list(range(6)), 2, "importance", {5: 100.0, 4: 100.0})
+    assert sorted(imp) == [4, 5]
+    body = torch.nn.Sequential(torch.nn.Linear(3, 4), torch.nn.ReLU(), torch.nn.Linear(4, 1))
+    pers = S.personalize(body, clients[0], lambda m, d: local_train(m, d), shared_prefixes=("0.",))
+    assert torch.equal(pers[0].weight, body[0].weight) and not torch.equal(pers[2].weight, body[2].weight)
+    # update encoding
+    delta = torch.randn(1000)
+    tk = S.encode_update(delta, "topk", 0.1)
+    assert (S.decode_update(tk) != 0).sum() == 100 and torch.allclose(S.decode_update(tk)[delta.abs().topk(100).indices], delta[delta.abs().topk(100).indices]) and tk["bytes"] == 800
+    g = torch.Generator().manual_seed(0)
+    rk = torch.stack([S.decode_update(S.encode_update(delta, "randk", 0.1, generator=g)) for _ in range(400)]).mean(0)
+    assert float((rk - delta).abs().mean()) < 0.2
+    sg = S.decode_update(S.encode_update(delta, "sign"))
+    assert torch.equal(torch.sign(sg), torch.sign(delta)) and S.encode_update(delta, "sign")["bytes"] == 129
+    q8 = S.decode_update(S.encode_update(delta, "quantize", bits=8, generator=g))
+    assert float((q8 - delta).abs().max()) <= float(delta.max() - delta.min()) / 255 + 1e-6 and S.encode_update(delta, "quantize", bits=4)["bytes"] == 508
+    ctl = S.LocalSGDController(period=4)
+    syncs = [ctl.should_sync() for _ in range(8)]
+    assert syncs == [False, False, False, True] * 2
+    ctl.after_sync(0.5); assert ctl.period == 2
+    ctl.after_sync(0.001); ctl.after_sync(0.001); assert ctl.period == 8 and ctl.syncs == 3
+    # gradient garbage collection
+    gcx = S.GradientGarbageCollector(max_idle=2, thresholds=(1, 1, 1))
+    a, b = torch.nn.Parameter(torch.randn(100)), torch.nn.Parameter(torch.randn(50))
+    a.grad, b.grad = torch.ones(100), torch.ones(50)
+    gcx.track(a); gcx.track(b)
+    tmp = torch.nn.Parameter(torch.randn(5)); gcx.track(tmp); del tmp
+    for _ in range(3):
+        gcx.tick(); gcx.touch(a)
+    res = gcx.collect()
+    assert a.grad is not None and b.grad is None and res["freed_bytes"] == 200 and res["dead_refs"] == 1 and res["tracked"] == 2
+    assert gcx.collect(force=True)["freed_grads"] == 1 and a.grad is None and gcx.stats["freed_grads"] == 2
+    # capacity planning and cost analysis
+    cp = S.CapacityPlanner(capacity=100.0, headroom=0.2)
+    for d in range(28):
+        cp.record_day(40 + 1.0 * d + (5 if d % 7 == 5 else 0))
+    fc = cp.forecast(30)
+    assert fc["direction"] == "growing" and fc["trend_per_day"] == pytest.approx(1.0, abs=0.05) and 5 <= fc["days_until_exhausted"] <= 13 and fc["urgency"] in ("high", "medium") and fc["action"] == "scale_up" and fc["recommended_capacity"] > 100
+    idle = S.CapacityPlanner(100.0)
+    for d in range(20):
+        idle.record_day(10.0)
+    assert idle.forecast()["action"] == "scale_down" and idle.forecast()["days_until_exhausted"] is None
+    oc = S.OperationCostAnalyzer()
+    for _ in range(100):
+        oc.record("add", 5e-6, 4e5, 1e5); oc.record("matmul", 2e-4, 1e6, 1e9, "forward")
+    oc.record("allreduce", 0.05, 1e8, 0, "backward")
+    agg = oc.aggregate()
+    kinds = {(s["op"], s["kind"]) for s in oc.suggestions()}
+    assert agg["matmul"]["intensity"] == 1000 and agg["allreduce"]["share"] > 0.6 and {("allreduce", "hotspot"), ("add", "launch_bound")} <= kinds and oc.phase_breakdown()["backward"] == 0.05
+    # record / replay
+    rec = S.OperationRecorder()
+    x = torch.randn(8, 8)
+    y = rec.call("matmul", torch.matmul, x, x)
+    z = rec.call("noise", lambda t: t + torch.rand_like(t), y)
+    rp = S.OperationReplayer(rec.session).replay()
+    assert rp["operations"] == 2 and not rp["deterministic"] and rp["mismatches"][0]["name"] == "noise" and S.OperationReplayer(rec.session[:1]).replay()["deterministic"]
+    assert S.OperationReplayer(rec.session).replay(substitute={1: [torch.zeros(8, 8)]})["mismatches"] == []
+    # health, progress, debugger
+    net = torch.nn.Sequential(torch.nn.Linear(4, 8), torch.nn.ReLU(), torch.nn.Linear(8, 2))
+    unused = torch.nn.Linear(2, 2)
+    both = torch.nn.ModuleDict({"net": net, "unused": unused})
+    hd = S.HealthDiagnostics()
+    net(torch.randn(3, 4)).sum().backward()
+    rep = hd.check(both)
+    assert rep["status"] == "degraded" and sum("no gradient" in i["message"] for i in rep["issues"]) == 2
+    net[0].weight.grad[0, 0] = float("nan")
+    assert hd.check(net)["status"] == "critical"
+    net.zero_grad(); net(torch.randn(3, 4)).sum().backward()
+    for i in range(12):
+        hd.record_step(0.1 if i < 11 else 0.5, 1e6 * (1 + 0.1 * i))
+    cats = {i["category"] for i in hd.check(net)["issues"]}
+    assert cats == {"memory", "performance"}
+    clk = iter(range(1000))
+    seen = []
+    pr = S.ProgressReporter(10, seen.append, clock=lambda: float(next(clk)))
+    for _ in range(10):
+        pr.update(1, loss=0.5)
+    assert seen[-1]["fraction"] == 1.0 and seen[-1]["eta_s"] == 0 and seen[4]["rate"] == pytest.approx(1.0) and seen[4]["eta_s"] == pytest.approx(5.0) and seen[0]["loss"] == 0.5
+    child = pr.scope("eval", 2); child.update(2)
+    assert seen[-1]["scope"] == "eval" and pr.statistics()["steps"] == 10
+    dbg = S.InteractiveDebugger(net, ["stats", "watch 0", "continue"]).attach()
+    dbg.add_breakpoint(module="1", condition="norm_above", threshold=0.0)
+    dbg.add_breakpoint(condition="nan")
+    dbg.add_breakpoint(module="2", on="backward")
+    net(torch.randn(3, 4)).sum().backward()
+    assert [(h["kind"], h["module"]) for h in dbg.hits] == [("forward", "1"), ("backward", "2")] and dbg.log[0]["shape"] == (3, 8) and dbg.log[0]["nan"] == 0
+    net(torch.randn(3, 4))
+    assert dbg.watch["0"].shape == (3, 8)
+    with torch.no_grad():
+        net[0].weight[0, 0] = float("nan")
+    net(torch.randn(3, 4))
+    assert ("forward", "0") in [(h["kind"], h["module"]) for h in dbg.hits]
+    ab = S.InteractiveDebugger(net, ["abort"]).attach(); ab.add_breakpoint(module="2")
+    dbg.detach()
+    with pytest.raises(RuntimeError):
+        net(torch.randn(3, 4))
+    ab.detach()
+    # VJP chains
+    A1, A2, A3 = torch.randn(50, 20, dtype=dd), torch.randn(5, 50, dtype=dd), torch.randn(30, 5, dtype=dd)
+    dvec = torch.rand(50, dtype=dd)
+    vo = S.VjpOptimizer().add_matrix(A1).add_diagonal(dvec).add_matrix(A2).add_matrix(A3)
+    v, xx = torch.randn(30, dtype=dd), torch.randn(20, dtype=dd)
+    J = A3 @ A2 @ torch.diag(dvec) @ A1
+    fused = vo.fuse()
+    assert torch.allclose(vo.vjp(v), v @ J) and torch.allclose(vo.jvp(xx), J @ xx) and len(fused.ops) == 3 and torch.allclose(fused.vjp(v), v @ J)
+    assert S.VjpOptimizer.chain_order([10, 30, 5, 60]) == (4500, "((A1 A2) A3)") and S.VjpOptimizer.chain_order([40, 20, 30, 10, 30])[0] == 26000
+    co = fused.costs()
+    assert co["vjp_flops"] == 2 * (1000 + 250 + 150) and co["materialized_vjp_flops"] == 2 * 20 * 30 and co["break_even_batch"] >= 1
+    # quantum circuits
+    qc = S.QuantumCircuit(2).h(0).cnot(0, 1)
+    bell = qc.run(torch.zeros(0))
+    assert torch.allclose(bell.abs() ** 2, torch.tensor([0.5, 0, 0, 0.5], dtype=dd)) and float(qc.expectation(torch.zeros(0), S.pauli_string("ZZ"))) == pytest.approx(1.0)
+    assert torch.allclose((S.QuantumCircuit(2).x(1).cnot(1, 0).run(torch.zeros(0)).abs() ** 2), torch.tensor([0.0, 0, 0, 1], dtype=dd))
+    ry = S.QuantumCircuit(1).ry(0, 0)
+    th = torch.tensor([0.7], dtype=dd, requires_grad=True)
+    e = ry.expectation(th, S.pauli_string("Z"))
+    e.backward()
+    assert float(e) == pytest.approx(math.cos(0.7)) and float(th.grad) == pytest.approx(-math.sin(0.7)) and float(ry.parameter_shift(th.detach(), S.pauli_string("Z"))) == pytest.approx(-math.sin(0.7))
+    rz = S.QuantumCircuit(1).h(0).rz(0, 0).h(0)
+    assert float(rz.expectation(torch.tensor([1.1], dtype=dd), S.pauli_string("Z"))) == pytest.approx(math.cos(1.1))
+    ham = S.pauli_string("ZZ") + 0.5 * (S.pauli_string("XI") + S.pauli_string("IX"))
+    ans = S.QuantumCircuit(2).ry(0, 0).ry(1, 1).cnot(0, 1).ry(0, 2).ry(1, 3)
+    res = S.vqe(ans, ham, 4, steps=250, lr=0.1)
+    assert res["energy"] == pytest.approx(res["exact"], abs=5e-3) and res["history"][-1] < res["history"][0]
+    # Wirtinger derivatives
+    z = torch.tensor([1.0 + 2.0j, -0.5 + 0.3j], dtype=torch.complex128)
+    dz, dzc = S.wirtinger_grad(lambda t: (t * t).sum(), z)
+    assert torch.allclose(dz, 2 * z) and dzc.abs().max() < 1e-12 and S.is_holomorphic(lambda t: (t ** 3).sum(), z)
+    dz, dzc = S.wirtinger_grad(lambda t: (t * t.conj()).real.sum(), z)
+    assert torch.allclose(dz, z.conj()) and torch.allclose(dzc, z) and not S.is_holomorphic(lambda t: (t * t.conj()).sum(), z)
+    # edge cases and recovery
+    eh = S.EdgeCaseHandler()
+    out, found = eh.handle(torch.tensor([1.0, float("nan"), float("inf"), 1e-42, -float("inf")]))
+    assert found == ["nan", "inf", "denormal"] and out.tolist() == pytest.approx([1.0, 0.0, 1e30, 0.0, -1e30]) and eh.handle(torch.zeros(0))[0] is None and eh.handle(torch.tensor(3.0))[1] == ["scalar"]
+    with pytest.raises(FloatingPointError):
+        S.EdgeCaseHandler(nan="error").handle(torch.tensor([float("nan")]))
+    assert eh.stats["nan"] == 1 and eh.stats["inf"] == 2 and eh.handle(torch.tensor([1, 2]))[1] == []
+    state = {"w": 1.0, "lr": 0.1, "batch": 8}
+    script = iter([RuntimeError("CUDA out of memory"), float("nan"), RuntimeError("connection reset"), 0.25])
+    def step():
+        v = next(script)
+        if isinstance(v, Exception):
+            raise v
+        state["w"] += 1
+        return v
+    rcv = S.AutomaticErrorRecovery(lambda: {"w": state["w"]}, lambda s: state.update(s), shrink=lambda: state.update(batch=state["batch"] // 2), lower_lr=lambda: state.update(lr=state["lr"] / 2), sleep=lambda s: None)
+    assert rcv.run(step) == 0.25 and [a["action"] for a in rcv.attempts] == ["shrink_batch", "restore_and_lower_lr", "backoff_retry"]
+    assert state["batch"] == 4 and state["lr"] == 0.05 and state["w"] == 2.0 and rcv.good["w"] == 2.0
+    always = S.AutomaticErrorRecovery(lambda: 0, lambda s: None, max_attempts=2, sleep=lambda s: None)
+    with pytest.raises(RuntimeError):
+        always.run(lambda: (_ for _ in ()).throw(RuntimeError("still broken")))
