@@ -4569,3 +4569,119 @@ def test_linalg_ext_multigrid_pivoting_refinement_randomized_krylov_and_analysis
     tri_rep = L.matrix_analysis(tri)
     assert tri_rep["bandwidth"] == (1, 1) and tri_rep["diagonally_dominant"] and not tri_rep["symmetric"] and tri_rep["sparsity"] == pytest.approx(72 / 100)
     assert L.matrix_analysis(rot)["orthogonal"] and L.matrix_analysis(defc)["rank"] == 3 and L.matrix_analysis(-spd)["definiteness"] == "negative" and 1 <= rep["stable_rank"] <= 20
+
+
+def test_tensor_ext_expressions_graph_comprehension_registries_shapes_views_and_backend_services():
+    import math
+    from scipy import stats as sst
+    from torsh_b200 import tensor_ext as E
+    torch.manual_seed(0)
+    a, b = torch.randn(4, 5), torch.randn(4, 5)
+    ex = (E.expr(a) * 2.0 + E.expr(b)).apply("relu") - 1 + (-E.expr(a)) / 4
+    assert torch.allclose(ex.eval(), torch.relu(a * 2 + b) - 1 - a / 4) and ex.count_nodes() == 13
+    assert ex.to_source() == "((relu(((x0 * 2.0) + x1)) - 1.0) + ((-x0) / 4.0))" and torch.allclose((3 * E.expr(a)).eval(), 3 * a) and torch.allclose((1 - E.expr(a)).eval(), 1 - a)
+    # expression graph
+    g = E.ExpressionGraph()
+    g.add_input("x", (8, 16)); g.add_input("w", (16, 4))
+    g.add_node("h", "matmul", ["x", "w"], (8, 4)); g.add_node("h2", "matmul", ["x", "w"], (8, 4))
+    g.add_node("s1", "add", ["h", "h2"]); g.add_node("s2", "add", ["h2", "h"])
+    g.add_node("r", "relu", ["s1"]); g.add_node("t", "tanh", ["r"]); g.add_node("sc", "scale", ["t"], attr=0.5); g.add_node("dead", "exp", ["s2"])
+    g.mark_output("sc")
+    feeds = {"x": torch.randn(8, 16), "w": torch.randn(16, 4)}
+    want = 0.5 * torch.tanh(torch.relu(2 * feeds["x"] @ feeds["w"]))
+    assert torch.allclose(g.execute(feeds)["sc"], want, atol=1e-6)
+    rep = g.optimize()
+    assert rep == {"removed": 3, "merged": 2} and set(g.nodes) == {"x", "w", "h", "s1", "r", "t", "sc"} and torch.allclose(g.execute(feeds)["sc"], want, atol=1e-6)
+    assert g.detect_fusable_chains() == [["s1", "r", "t", "sc"]] and g.topological_sort().index("h") < g.topological_sort().index("s1")
+    co = g.costs()
+    assert co["flops"] == 2 * 32 * 16 + 4 * 32 and co["memory_bytes"] - co["memory_bytes_fused"] == 3 * 32 * 4 and '"h" -> "s1"' in g.to_dot()
+    cyc = E.ExpressionGraph(); cyc.nodes = {"a": {"op": "neg", "inputs": ["b"], "shape": (1,), "attr": None}, "b": {"op": "neg", "inputs": ["a"], "shape": (1,), "attr": None}}
+    with pytest.raises(ValueError):
+        cyc.topological_sort()
+    # comprehensions
+    tc = E.TensorComprehension((3, 4))
+    assert torch.equal(tc.build(lambda i, j: i * 10 + j), torch.arange(3)[:, None].float() * 10 + torch.arange(4)[None].float())
+    assert torch.equal(tc.where(lambda i, j: i == j, lambda i, j: 1.0, lambda i, j: 0.0), torch.eye(3, 4)) and torch.equal(tc.build(lambda i, j: 7), torch.full((3, 4), 7.0))
+    assert E.TensorComprehension.from_iter((k * k for k in range(6)), (2, 3)).tolist() == [[0, 1, 4], [9, 16, 25]] and E.logspace(0, 2, 3).tolist() == pytest.approx([1, 10, 100])
+    # registries
+    reg = E.CustomTypeRegistry()
+    reg.register_type(E.fixed_point_type("q8_8", 16, 8)); reg.register_type(E.fixed_point_type("q4_4", 8, 4))
+    v = torch.tensor([1.5, -2.25, 0.004, 200.0])
+    enc = reg.encode("q8_8", v)
+    assert enc.dtype == torch.int16 and reg.decode("q8_8", enc).tolist() == pytest.approx([1.5, -2.25, 0.00390625, 127.99609375]) and reg.registered_types() == ["q4_4", "q8_8"]
+    assert reg.decode("q4_4", reg.convert(enc, "q8_8", "q4_4")).tolist() == pytest.approx([1.5, -2.25, 0.0, 7.9375]) and reg.has_conversion("q8_8", "q4_4")
+    assert reg.decode("q8_8", reg.apply("q8_8", "add", enc, enc))[:2].tolist() == [3.0, -4.5]
+    reg.register_operation("q8_8", "neg", lambda s: -s)
+    assert reg.list_operations("q8_8") == ["neg"] and reg.apply("q8_8", "neg", enc)[0] == -enc[0] and reg.stats() == {"types": 2, "conversions": 0, "operations": 1}
+    with pytest.raises(ValueError):
+        reg.register_type(E.fixed_point_type("q8_8"))
+    ops = E.CustomOperationRegistry()
+    ops.register("scale", lambda t, factor=1.0: t * factor, 1, "multiply by a constant", factor=2.0)
+    ops.register("lerp", lambda p, q, w=0.5: p + w * (q - p), 2, w=0.5)
+    assert torch.equal(ops.call("scale", a), a * 2) and torch.equal(ops.call("scale", a, factor=3.0), a * 3) and torch.allclose(ops.call("lerp", a, b, w=0.25), a + 0.25 * (b - a))
+    assert ops.get_metadata("scale")["description"] == "multiply by a constant" and ops.list_operations() == ["lerp", "scale"]
+    for bad in (lambda: ops.call("scale", a, b), lambda: ops.call("scale", a, gain=2)):
+        with pytest.raises(TypeError):
+            bad()
+    # shape inference with a trace
+    sd = E.ShapeInferenceDebugger()
+    assert sd.infer_broadcast_shape((4, 1, 3), (5, 1)) == (4, 5, 3) and sd.infer_matmul_shape((2, 3, 4), (4, 5)) == (2, 3, 5) and sd.infer_matmul_shape((4,), (4, 5)) == (5,) and sd.infer_matmul_shape((7, 2, 3, 4), (2, 4, 6)) == (7, 2, 3, 6)
+    assert sd.infer_concat_shape([(2, 3), (4, 3)], 0) == (6, 3) and sd.infer_reshape_shape((4, 6), (-1, 8)) == (3, 8)
+    for bad in (lambda: sd.infer_broadcast_shape((3, 4), (5, 4)), lambda: sd.infer_matmul_shape((2, 3), (4, 5)), lambda: sd.infer_concat_shape([(2, 3), (2, 4)], 0), lambda: sd.infer_reshape_shape((4, 6), (5, -1))):
+        with pytest.raises(ValueError):
+            bad()
+    st = sd.get_statistics()
+    assert st["steps"] == 10 and st["errors"] == 4 and st["by_op"]["matmul"] == 4 and "not broadcastable" in sd.trace[6]["error"]
+    # statistics against scipy
+    x = torch.randn(200) ** 3
+    y = x + torch.randn(200)
+    d = E.describe(x)
+    assert d["skewness"] == pytest.approx(float(sst.skew(x.numpy())), rel=1e-4) and d["kurtosis"] == pytest.approx(float(sst.kurtosis(x.numpy())), rel=1e-4) and d["median"] == pytest.approx(float(x.median()), abs=0.05)
+    assert E.correlation(x, y) == pytest.approx(sst.pearsonr(x.numpy(), y.numpy())[0], rel=1e-5) and E.correlation(x, y, "spearman") == pytest.approx(sst.spearmanr(x.numpy(), y.numpy())[0], rel=1e-5)
+    assert E.correlation(x, y, "kendall") == pytest.approx(sst.kendalltau(x.numpy(), y.numpy())[0], rel=1e-5) and float(E.percentile(x, 90)) == pytest.approx(float(torch.quantile(x.double(), 0.9))) and E.mode(torch.tensor([1, 3, 3, 2])) == 3
+    # fluent wrapper and views
+    assert torch.allclose(E.fluent(a).add_scalar(1).relu().mul_scalar(2).sum_dim(1).unwrap(), (torch.relu(a + 1) * 2).sum(1)) and torch.allclose(E.fluent(a).matmul(E.fluent(b).t()).unwrap(), a @ b.t())
+    base = torch.arange(24.0)
+    tv = E.TensorView(base, (3, 4), (8, 2), 1)
+    assert tv.view.tolist()[1] == [9.0, 11.0, 13.0, 15.0] and not tv.is_contiguous() and tv.shares_storage_with(base) and tv.is_view() and not tv.overlaps_itself()
+    assert E.TensorView(base, (3, 4), (0, 1)).overlaps_itself() and tv.memory_usage() == {"view_bytes": 48, "storage_bytes": 96} and tv.to_owned().is_contiguous() and not tv.to_owned().data_ptr() == base.data_ptr()
+    assert E.TensorView.calculate_strides((2, 3, 4)) == (12, 4, 1) and E.TensorView.calculate_strides((2, 3, 4), "F") == (1, 2, 6) and tv.slice(1, 0, 4, 2).view.shape == (3, 2)
+    # backend services
+    pm = E.PerformanceModel()
+    for n in (64, 128, 256, 512, 1024):
+        pm.record("matmul", n, 2e-9 * n ** 3 * (1 + 0.01 * ((n // 64) % 3 - 1)))
+        pm.record("copy", n, 1e-6 * n)
+    fm = pm.fit("matmul")
+    assert fm["exponent"] == pytest.approx(3.0, abs=0.05) and fm["complexity_class"] == "cubic" and pm.fit("copy")["complexity_class"] == "linear" and pm.predict("matmul", 2048) == pytest.approx(2e-9 * 2048 ** 3, rel=0.1)
+    pm.record("copy", 2048, 1.0)
+    assert pm.anomalies("copy", z=1.5) == [5]
+    vc = E.VersionCompatibilityChecker()
+    vc.require("torch", ">=2.4,<3"); vc.require("cuda", ">=12.8"); vc.require("triton", ">=3", "warning")
+    ok = vc.check({"torch": "2.11.0+cu128", "cuda": "12.9", "triton": None})
+    assert ok["compatible"] and [c["ok"] for c in ok["components"]] == [True, True, False] and ok["components"][2]["message"] == "not installed"
+    assert not vc.check({"torch": "1.13.1", "cuda": "12.9", "triton": "3.6"})["compatible"] and E.VersionCompatibilityChecker.detect()["torch"] == torch.__version__
+    dp = E.DefragmentationPlanner(1000)
+    dp.add_block("a", 0, 100); dp.add_block("b", 300, 100); dp.add_block("pin", 500, 50, movable=False); dp.add_block("c", 800, 100)
+    plan = dp.plan()
+    assert [(m["name"], m["to"]) for m in plan["moves"]] == [("b", 100), ("c", 550)] and plan["largest_free_after"] == 350 > plan["largest_free_before"] == 250 and plan["fragmentation_after"] < plan["fragmentation_before"]
+    clock = iter(range(10000))
+    sel = E.AdaptiveKernelSelector(timer=lambda: float(next(clock)))
+    cost = {"slow": 5, "fast": 1}
+    def make(name):
+        def fn(t):
+            for _ in range(cost[name]):
+                next(clock)
+            return t * 2
+        return fn
+    sel.register("double", "slow", make("slow")); sel.register("double", "fast", make("fast")); sel.register("double", "big_only", make("fast"), predicate=lambda t: t.numel() > 10 ** 6)
+    outs = [sel.run("double", a) for _ in range(5)]
+    assert all(torch.equal(o, a * 2) for o in outs) and sel.best("double", a) == "fast" and sel.last == "fast" and sel.best("double", torch.zeros(3)) is None
+    tp = E.TransferPlanner()
+    tp.add_link("pageable", "device", 6e9, 10e-6); tp.add_link("pageable", "pinned", 20e9, 1e-6); tp.add_link("pinned", "device", 55e9, 8e-6)
+    route = tp.plan("pageable", "device", 1 << 30)
+    assert route["path"] == ["pageable", "pinned", "device"] and route["seconds"] == pytest.approx((1 << 30) / 20e9 + (1 << 30) / 55e9 + 9e-6)
+    piped = tp.plan("pageable", "device", 1 << 30, chunk=1 << 24)
+    assert piped["seconds"] < route["seconds"] and piped["seconds"] == pytest.approx(63 * ((1 << 24) / 20e9 + 1e-6) + ((1 << 24) / 20e9 + 1e-6) + ((1 << 24) / 55e9 + 8e-6))
+    assert tp.plan("pageable", "device", 1024)["path"] == ["pageable", "device"] or tp.plan("pageable", "device", 1024)["seconds"] < 2e-5
+    with pytest.raises(ValueError):
+        tp.plan("device", "pageable", 10)

@@ -633,6 +633,18 @@ def test_generated_fused_elementwise_kernel(dtype, n, tmp_path_factory, monkeypa
         assert any(k.startswith(f.expr.key()) for k in table)          # a variant was measured and remembered
 
 
+def test_deferred_expression_runs_as_one_generated_kernel(tmp_path_factory, monkeypatch):
+    from torsh_b200 import tensor_ext as E
+    monkeypatch.setenv("TORSH_JIT_DIR", str(tmp_path_factory.getbasetemp() / "jit_expr"))
+    E.Expr._KERNELS.clear()
+    torch.manual_seed(0)
+    a, b = torch.randn(1 << 18, device=DEV), torch.randn(1 << 18, device=DEV)
+    ex = (E.expr(a) * 2.0 + E.expr(b)).apply("relu") - 1 + (-E.expr(a)) / 4
+    out = ex.eval()
+    assert len(E.Expr._KERNELS) == 1 and _rel_elem(out, torch.relu(a * 2 + b) - 1 - a / 4) < 1e-4
+    assert ex.eval().shape == a.shape and len(E.Expr._KERNELS) == 1                      # second call reuses the compiled kernel
+
+
 def test_gemm_measured_tile_selection():
     """With autotuning on, every candidate tile / raster choice is timed once per shape, the winner is remembered and
     the product is unchanged."""
