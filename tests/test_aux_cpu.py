@@ -1460,3 +1460,164 @@ def test_autograd_services_federated_compression_gc_planning_replay_debugger_vjp
     always = S.AutomaticErrorRecovery(lambda: 0, lambda s: None, max_attempts=2, sleep=lambda s: None)
     with pytest.raises(RuntimeError):
         always.run(lambda: (_ for _ in ()).throw(RuntimeError("still broken")))
+
+
+def test_core_extras_deprecation_chunking_compression_ieee_inspection_layout_ir_spikes_networks_shapes_orders_and_monitor():
+    import warnings as _w
+    from torsh_b200.core import extras as X
+    from torsh_b200 import fx as tfx
+    # deprecation registry
+    api = X.ApiCompat("0.2.0")
+    @api.deprecated("0.1.0", "0.3.0", "new_add")
+    def old_add(a, b): return a + b
+    @api.deprecated("0.1.0", "0.2.0")
+    def gone(): return 1
+    with pytest.warns(DeprecationWarning, match="new_add"):
+        assert old_add(1, 2) == 3
+    with pytest.raises(RuntimeError, match="removed in 0.2.0"):
+        gone()
+    rep = api.report()
+    assert {r["name"].split(".")[-1] for r in rep} == {"old_add", "gone"} and rep[0]["calls"] == 1
+    # chunking
+    c = X.optimal_chunk(1 << 30, 4, working_tensors=3)
+    assert c % 128 == 0 and 3 * 4 * c <= 126 << 20 < 3 * 4 * (c + 128) and X.optimal_chunk(1000, 4) == 1000
+    x = torch.randn(100, 7)
+    assert torch.equal(X.chunked_apply(lambda t: t * 2, x, chunk=13), x * 2)
+    # compression round trips
+    r = torch.tensor([[1, 1, 1, 2], [2, 2, 3, 3]])
+    v, l, shp = X.rle_encode(r)
+    assert v.tolist() == [1, 2, 3] and l.tolist() == [3, 3, 2] and torch.equal(X.rle_decode(v, l, shp), r)
+    idx = torch.tensor([3, 7, 8, 20, 21])
+    assert torch.equal(X.delta_decode(*X.delta_encode(idx), idx.shape), idx)
+    sp = torch.randn(37, 5) * (torch.rand(37, 5) < 0.1)
+    enc = X.bitmask_encode(sp)
+    assert torch.equal(X.bitmask_decode(enc), sp) and enc["bytes"] < enc["dense_bytes"] / 3
+    w24 = torch.tensor([[1.0, 0, 2, 0, 0, 0, 3, 4], [0, 0, 0, 0, 5, 0, 0, 6]])
+    pm = X.pruning_metadata(w24)
+    assert pm["is_2_4"] and pm["sparsity"] == 10 / 16 and pm["block_sparsity"] == 0.25 and not X.pruning_metadata(torch.ones(2, 8))["is_2_4"]
+    # error codes
+    assert X.error_name(X.error_code("SHAPE_MISMATCH")) == "SHAPE_MISMATCH" and X.error_category(2001) == "memory" and X.is_retryable(6001) and not X.is_retryable(1002)
+    assert X.classify_exception(RuntimeError("CUDA out of memory")) == 2001 and X.classify_exception(IndexError("x")) == 1005 and X.classify_exception(ValueError("bad")) == 1001
+    try:
+        torch.zeros(2, 3) @ torch.zeros(4, 5)
+    except RuntimeError as e:
+        assert X.error_category(X.classify_exception(e)) == "user"
+    assert len(set(X.ERROR_CODES.values())) == len(X.ERROR_CODES)
+    # IEEE 754
+    one = torch.tensor([1.0, -1.0, 0.0, 1.0])
+    nxt = torch.tensor([np.nextafter(np.float32(1), np.float32(2)), np.nextafter(np.float32(-1), np.float32(-2)), -0.0, 1.0 + 4 * 2 ** -23])
+    assert X.ulp_distance(one, nxt).tolist() == [1, 1, 0, 4]
+    assert int(X.ulp_distance(torch.tensor([-1e-45]), torch.tensor([1e-45]))) == 2 and X.float_bits(1.0) == 0x3F800000 and X.float_bits(1.0, True) == 0x3FF0000000000000
+    cl = X.classify_floats(torch.tensor([float("nan"), float("inf"), 0.0, -0.0, 1e-40, 1.0, -2.0]))
+    assert cl == {"nan": 1, "inf": 1, "zero": 2, "negative_zero": 1, "subnormal": 1, "normal": 2}
+    for dt in (torch.float32, torch.float64, torch.bfloat16):
+        assert all(v for v in X.ieee754_compliance_report(dt).values() if v is not None)
+    # inspector
+    base = torch.arange(10000.0)
+    info = X.inspect_tensor(base[:4], "slice")
+    assert info["is_view"] and "small view keeps a large storage alive" in info["issues"] and info["max"] == 3.0 and sum(info["histogram"]) == 4
+    bad = X.inspect_tensor(torch.tensor([1.0, float("nan"), 3e38]), "bad")
+    assert bad["nan"] == 1 and bad["issues"][:2] == ["non-finite values", "values close to the dtype's range"]
+    txt = X.format_inspection(X.inspect_tensor(torch.randn(4, 6).t(), "wt"))
+    assert "non-contiguous" in txt and "float32[6, 4]" in txt and "█" in txt
+    # layout advice
+    lo = X.LayoutOptimizer()
+    img = torch.randn(2, 8, 5, 5)
+    lo.record_access("img", 1, 9); lo.record_access("img", 3, 1)
+    rec = lo.recommend("img", img)
+    assert rec["action"] == "channels_last" and rec["apply"](img).stride(1) == 1 and rec["share"] == 0.9
+    assert lo.recommend("img", rec["apply"](img))["action"] == "none" and lo.recommend("other", img)["action"] == "none"
+    m = torch.randn(6, 4)
+    lo.record_access("m", 0)
+    rec = lo.recommend("m", m)
+    assert rec["action"] == "permute_contiguous" and rec["permutation"] == [1, 0] and rec["apply"](m).shape == (4, 6)
+    # memory maps
+    mm = X.memory_map([("weights", 0, 512), ("acts", 768, 256)], 1024, width=16)
+    assert mm.splitlines()[0] == "|wwwwwwww....aaaa|" and "75%" in mm
+    tl = X.memory_timeline([(i * 0.1, i * 100) for i in range(20)], height=4, width=10)
+    assert tl.splitlines()[0].rstrip("|").count("#") < tl.splitlines()[3].rstrip("|").count("#") and "peak 1,900 B" in tl
+    # MLIR / StableHLO text
+    net = torch.nn.Sequential(torch.nn.Linear(8, 16, bias=False), torch.nn.ReLU(), torch.nn.Linear(16, 4, bias=False), torch.nn.Tanh())
+    gm = tfx.symbolic_trace(net)
+    mlir = X.emit_mlir(gm, [torch.randn(2, 8)])
+    assert "func.func @forward(%arg0: tensor<2x8xf32>) -> tensor<2x4xf32>" in mlir and mlir.count("linalg.matmul_transpose_b") == 2 and "arith.maximumf" in mlir and "math.tanh" in mlir
+    assert mlir.count("{") == mlir.count("}") and "return %" in mlir
+    hlo = X.emit_mlir(gm, [torch.randn(2, 8)], dialect="stablehlo")
+    assert hlo.count("stablehlo.dot_general") == 2 and "stablehlo.maximum" in hlo and "contracting_dims = [1] x [1]" in hlo and "tensor<16x8xf32>" in hlo
+    # every SSA value is defined before use
+    defined = {"%arg0"}
+    for line in hlo.splitlines():
+        if " = " in line:
+            lhs, rhs = line.split(" = ", 1)
+            assert all(tok.rstrip(",") in defined for tok in rhs.split() if tok.startswith("%")), line
+            defined.add(lhs.strip())
+    # spiking neurons
+    lif = X.LIFNeurons(3, tau=10.0, threshold=1.0, refractory=2)
+    spikes = lif.run(torch.tensor([0.5, 1.5, 3.0]).repeat(2000, 1))
+    rates = spikes.float().mean(0)
+    assert rates[0] == 0 and rates[1] < rates[2]
+    for i, cur in ((1, 1.5), (2, 3.0)):
+        assert float(rates[i]) == pytest.approx(lif.rate_for_constant_input(cur), rel=0.15)
+    gaps = torch.diff(spikes[:, 2].nonzero().flatten())
+    assert gaps.min() > 2
+    g = torch.Generator().manual_seed(0)
+    p = torch.tensor([0.1, 0.5, 0.9])
+    assert torch.allclose(X.rate_decode(X.rate_encode(p, 4000, g)), p, atol=0.03)
+    lat = X.latency_encode(torch.tensor([1.0, 0.5, 0.0, 0.1]), 11)
+    assert lat.sum(0).tolist() == [1, 1, 0, 1] and lat.float().argmax(0).tolist() == [0, 5, 0, 9]
+    # matrix product states
+    torch.manual_seed(0)
+    psi = torch.randn(2, 3, 2, 3, 2, dtype=torch.float64)
+    mps = X.MatrixProductState.from_tensor(psi)
+    assert torch.allclose(mps.to_tensor(), psi, atol=1e-12) and float(mps.norm()) == pytest.approx(float(psi.norm())) and mps.bond_dimensions() == [2, 6, 6, 2]
+    assert float(mps.amplitude((1, 2, 0, 1, 1))) == pytest.approx(float(psi[1, 2, 0, 1, 1]))
+    other = X.MatrixProductState.from_tensor(torch.randn_like(psi))
+    assert float(mps.inner(other)) == pytest.approx(float((psi * other.to_tensor()).sum()))
+    ghz = torch.zeros(2, 2, 2, 2, 2, 2, dtype=torch.float64); ghz[0, 0, 0, 0, 0, 0] = ghz[1, 1, 1, 1, 1, 1] = 2 ** -0.5
+    g_mps = X.MatrixProductState.from_tensor(ghz, cutoff=1e-12)
+    assert g_mps.bond_dimensions() == [2] * 5 and g_mps.num_parameters() < ghz.numel() and g_mps.truncation_error < 1e-12
+    lossy = X.MatrixProductState.from_tensor(psi, max_bond=3)
+    assert (lossy.to_tensor() - psi).norm() == pytest.approx(lossy.truncation_error, rel=0.5) and lossy.truncation_error > 0
+    order, cost = X.contraction_order({"A": {"i": 2, "j": 1000}, "B": {"j": 1000, "k": 1000}, "C": {"k": 1000, "l": 2}}, output=("i", "l"))
+    assert cost < 2 * 1000 * 1000 * 2 + 2 * 1000 * 2 + 1 and len(order) == 2 and order[0] in (("A", "B"), ("B", "C"))
+    # shape validation
+    X.validate_shapes("matmul", a=torch.zeros(2, 3), b=torch.zeros(3, 4))
+    with pytest.raises(X.ShapeError, match=r"inner dimensions differ \(3 vs 4\).*a\[2, 3\], b\[4, 3\].*transpose b"):
+        X.validate_shapes("matmul", a=torch.zeros(2, 3), b=torch.zeros(4, 3))
+    with pytest.raises(X.ShapeError, match="not broadcastable"):
+        X.validate_shapes("elementwise", x=(2, 3), y=(4, 3))
+    X.validate_shapes("cat:1", a=(2, 3), b=(2, 9))
+    with pytest.raises(X.ShapeError, match="except 1"):
+        X.validate_shapes("cat:1", a=(2, 3), b=(3, 3))
+    with pytest.raises(X.ShapeError, match="bias must have 5"):
+        X.validate_shapes("linear", x=(7, 3), w=(5, 3), b=(4,))
+    with pytest.raises(X.ShapeError, match="kernel is larger"):
+        X.validate_shapes("conv2d", x=(1, 3, 2, 2), w=(8, 3, 3, 3))
+    with pytest.raises(X.ShapeError, match="key and value lengths"):
+        X.validate_shapes("attention", q=(2, 4, 10, 64), k=(2, 4, 12, 64), v=(2, 4, 11, 64))
+    ex = X.explain_broadcast((3, 1, 5), (4, 2))
+    assert "dim 1: 1 vs 4 -> 4" in ex and "dim 2: 5 vs 2 -> INCOMPATIBLE" in ex
+    # cache-oblivious orders
+    ys, xs = torch.tensor([0, 0, 1, 1, 5]), torch.tensor([0, 1, 0, 1, 3])
+    code = X.morton_encode(ys, xs)
+    assert code.tolist() == [0, 1, 2, 3, 0b100111] and [t.tolist() for t in X.morton_decode(code)] == [ys.tolist(), xs.tolist()]
+    order = X.morton_order(4, 4)
+    assert order[:8].tolist() == [0, 1, 4, 5, 2, 3, 6, 7] and sorted(order.tolist()) == list(range(16))
+    a = torch.randn(70, 45)
+    assert torch.equal(X.cache_oblivious_transpose(a, base=8), a.t())
+    # performance monitor
+    now = [0.0]
+    alerts = []
+    mon = X.PerfMonitor(window=50, on_alert=alerts.append, clock=lambda: now[0])
+    mon.set_threshold("step", p95_above=0.5)
+    for i in range(20):
+        now[0] += 0.1
+        mon.record("step", 0.1)
+    assert not alerts and mon.summary("step")["rate_per_s"] == pytest.approx(10.0) and mon.summary("step")["p50"] == 0.1
+    for _ in range(3):
+        now[0] += 1.0
+        mon.record("step", 1.0)
+    assert alerts and alerts[0]["kind"] == "p95" and alerts[0]["metric"] == "step"
+    with mon.time("io"):
+        now[0] += 0.25
+    assert mon.summary("io")["mean"] == pytest.approx(0.25) and set(mon.snapshot()) == {"step", "io"} and mon.summary("none") == {"count": 0}
