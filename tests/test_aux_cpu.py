@@ -1,5 +1,6 @@
 """Auxiliary subsystems on the CPU: optimizer checkpoints, monitoring, debug checks, property-based fuzzing of the
 host-side planners and codecs."""
+import math
 import os
 import threading
 
@@ -1621,3 +1622,142 @@ def test_core_extras_deprecation_chunking_compression_ieee_inspection_layout_ir_
     with mon.time("io"):
         now[0] += 0.25
     assert mon.summary("io")["mean"] == pytest.approx(0.25) and set(mon.snapshot()) == {"step", "io"} and mon.summary("none") == {"count": 0}
+
+
+def test_bench_suite_runner_analysis_cache_comparison_validation_ci_regressions_scaling_reports_and_probes(tmp_path):
+    import xml.etree.ElementTree as ET
+    from torsh_b200.utils import bench_suite as B
+    # runner on the host, with a synthetic workload whose cost is controlled by a fake clock-free sleep-less loop
+    gen = B.DataGenerator(0)
+    assert gen.tensor((1000,), "uniform", low=2, high=3).min() >= 2 and float((gen.tensor((4000,), sparsity=0.75) == 0).float().mean()) == pytest.approx(0.75, abs=0.03)
+    assert gen.tensor((2, 3), "sequential").tolist() == [[0, 1, 2], [3, 4, 5]] and gen.tensor((3,), "constant", value=7).tolist() == [7, 7, 7]
+    mm = B.FunctionBench(lambda n, cfg: (gen.tensor((n, n)), gen.tensor((n, n))), torch.matmul, flops=lambda n: 2 * n ** 3, nbytes=lambda n: 3 * n * n * 4)
+    runner = B.BenchRunner()
+    cfg = B.BenchConfig("matmul", sizes=(32, 64), warmup=1, iterations=4)
+    res = runner.run(mm, cfg)
+    assert [r.size for r in res] == [32, 64] and all(len(r.times) == 4 and r.gflops() > 0 and r.gbps() > 0 for r in res) and res[0].to_dict()["median"] == res[0].median
+    assert cfg.key() == B.BenchConfig("matmul", sizes=(32, 64), warmup=1, iterations=4).key() != B.BenchConfig("matmul", sizes=(32,)).key()
+    # statistics and roofline placement
+    s = B.summarize([1.0, 1.1, 0.9, 1.0, 1.05, 5.0])
+    assert s["outliers"] == [5.0] and s["median"] == pytest.approx(1.025) and s["ci"][0] < s["mean"] < s["ci"][1]
+    an = B.BenchmarkAnalyzer(peak_gflops=1000.0, peak_gbps=100.0)
+    memb = B.BenchResult("copy", 1, [1e-3] * 5, flops=1e6, bytes=8e7)          # 0.0125 flop/B, 80 GB/s of 100
+    a = an.analyze(memb)
+    assert a["bottleneck"] == "memory" and a["efficiency"] == pytest.approx(0.8) and a["rating"] == "good" and a["stable"] and not a["recommendations"]
+    comp = an.analyze(B.BenchResult("gemm", 1, [1e-3, 1.3e-3, 0.8e-3, 1e-3], flops=2e8, bytes=1e6))      # 200 GFLOP/s of 1000
+    assert comp["bottleneck"] == "compute" and comp["rating"] == "poor" and len(comp["recommendations"]) == 2
+    assert an.analyze(B.BenchResult("tiny", 1, [5e-6] * 4, flops=1e3, bytes=1e3))["bottleneck"] == "launch"
+    # complexity classes
+    ns = [64, 128, 256, 512, 1024, 2048]
+    for name, f in (("O(n)", lambda n: 3e-9 * n + 1e-7), ("O(n log n)", lambda n: 2e-9 * n * math.log2(n)), ("O(n^2)", lambda n: 1e-10 * n * n + 1e-7), ("O(1)", lambda n: 5e-6)):
+        assert B.fit_complexity(ns, [f(n) for n in ns])["class"] == name
+    assert B.fit_complexity(ns, [1e-10 * n ** 3 for n in ns])["loglog_slope"] == pytest.approx(3.0)
+    # cache
+    now = [1000.0]
+    cache = B.BenchmarkCache(tmp_path / "cache", ttl=60, environment={"host": "a"}, clock=lambda: now[0])
+    calls = []
+    counted = B.FunctionBench(lambda n, c: (torch.ones(n),), lambda t: calls.append(1) or t.sum())
+    cr = B.CachedBenchRunner(cache)
+    small = B.BenchConfig("sum", sizes=(8,), warmup=0, iterations=2)
+    r1 = cr.run(counted, small); n_calls = len(calls)
+    r2 = cr.run(counted, small)
+    assert len(calls) == n_calls and r2[0].times == r1[0].times and cache.stats == {"hits": 1, "misses": 1, "expired": 0}
+    now[0] += 120
+    cr.run(counted, small)
+    assert cache.stats["expired"] == 1 and len(calls) == 2 * n_calls
+    assert B.BenchmarkCache(tmp_path / "cache", environment={"host": "b"}).get(small) is None
+    # comparison with significance
+    rng = np.random.default_rng(0)
+    base = B.BenchResult("op", 1, (1.0 + 0.01 * rng.standard_normal(20)).tolist())
+    fast = B.BenchResult("op", 1, (0.8 + 0.01 * rng.standard_normal(20)).tolist())
+    same = B.BenchResult("op", 1, (1.0 + 0.01 * rng.standard_normal(20)).tolist())
+    cmp = B.BenchmarkComparator()
+    assert cmp.compare(base, fast)["verdict"] == "faster" and cmp.compare(fast, base)["verdict"] == "slower" and cmp.compare(base, same)["verdict"] == "equivalent"
+    from scipy import stats as sst
+    t, p = B.welch_t(base.times, fast.times)
+    ref = sst.ttest_ind(base.times, fast.times, equal_var=False)
+    assert t == pytest.approx(ref.statistic) and p == pytest.approx(ref.pvalue, rel=1e-6, abs=1e-300)
+    sets = cmp.compare_sets([base, B.BenchResult("other", 2, base.times)], [fast, B.BenchResult("other", 2, same.times)])
+    assert sets["faster"] == 1 and sets["equivalent"] == 1 and sets["geomean_speedup"] == pytest.approx(math.sqrt(1.25), rel=0.02)
+    # validation of what was timed
+    val = B.BenchmarkValidator()
+    x, y = torch.randn(16, 16), torch.randn(16, 16)
+    assert val.validate("mm", torch.matmul, torch.matmul, [x, y], times=[1.0, 1.01, 0.99])["status"] == "passed"
+    wrong = val.validate("mm", lambda a, b: a @ b + 1e-2, torch.matmul, [x, y], times=[1.0, 2.0, 0.5])
+    assert wrong["status"] == "failed" and {i["category"] for i in wrong["issues"]} == {"accuracy", "consistency"}
+    noisy = val.validate("rand", lambda a: a + torch.rand_like(a) * 1e-9, lambda a: a, [x.double()])
+    assert noisy["status"] == "warning" and noisy["issues"][0]["category"] == "determinism"
+    assert B.cancellation_risk(torch.tensor([1.0, 1.0]), torch.tensor([1.0 + 1e-6, 0.5])) == 0.5
+    # CI gate
+    ci = B.CIBenchmarkRunner(B.CIConfig(warn_slowdown=0.05, fail_slowdown=0.15))
+    slow10 = B.BenchResult("op", 1, (1.1 + 0.01 * rng.standard_normal(20)).tolist())
+    slow30 = B.BenchResult("op", 1, (1.3 + 0.01 * rng.standard_normal(20)).tolist())
+    assert ci.evaluate([base], [same])["status"] == "pass" and ci.evaluate([base], [slow10])["status"] == "warn" and ci.evaluate([base], [fast])["rows"][0]["status"] == "improved"
+    dec = ci.evaluate([base], [slow30])
+    assert dec["status"] == "fail" and dec["exit_code"] == 1
+    suite = ET.fromstring(ci.junit_xml(dec))
+    assert suite.attrib["failures"] == "1" and suite.find("testcase/failure") is not None and "FAIL" in ci.markdown(dec) and ci.annotations(dec)[0].startswith("::error title=benchmark op::+")
+    # regressions in a history
+    det = B.AdvancedRegressionDetector()
+    hist = (1.0 + 0.01 * rng.standard_normal(15)).tolist() + (1.3 + 0.01 * rng.standard_normal(8)).tolist()
+    r = det.analyze(hist)
+    assert r["status"] == "regression" and r["change_point"] == 15 and r["shift"] == pytest.approx(0.3, abs=0.02) and r["severity"] == "major" and r["trend"] == "degrading"
+    assert det.analyze((1.0 + 0.01 * rng.standard_normal(25)).tolist())["status"] == "stable" and det.analyze([1.0] * 3)["status"] == "insufficient_history"
+    assert det.analyze(hist[::-1])["kind"] == "improvement"
+    z, p = det.mann_kendall(list(range(10)))
+    assert z > 3 and p < 0.01
+    # scalability
+    assert B.size_progression("power_of_two", 100, 2000) == [128, 256, 512, 1024] and B.size_progression("linear", 10, 50, 5) == [10, 20, 30, 40, 50] and B.size_progression("exponential", 1, 1000, 4) == [1, 10, 100, 1000]
+    workers = [1, 2, 4, 8, 16]
+    am = B.amdahl_fit(workers, [10 * (0.1 + 0.9 / p) for p in workers])
+    assert am["serial_fraction"] == pytest.approx(0.1) and am["max_speedup"] == pytest.approx(10.0) and am["speedup"][-1] == pytest.approx(1 / (0.1 + 0.9 / 16)) and am["efficiency"][0] == 1.0
+    assert B.ScalabilityTestSuite.weak_scaling([1, 2, 4], [100, 190, 360]) == pytest.approx([1.0, 0.95, 0.9])
+    assert B.ScalabilityTestSuite._knee([1, 2, 4, 8, 16], [1.0, 1.0, 0.9, 2.0, 2.1]) == 8
+    sweep = B.ScalabilityTestSuite().size_sweep(B.FunctionBench(lambda n, c: (torch.ones(n),), lambda t: t.sum()), B.BenchConfig("sum", sizes=(1 << 10, 1 << 12, 1 << 14), warmup=1, iterations=3))
+    assert len(sweep["results"]) == 3 and sweep["complexity"]["class"] in B.COMPLEXITY_CLASSES
+    # system information
+    info = B.system_info()
+    assert info["torch"] == torch.__version__ and info["cpu_count"] >= 1 and len(info["fingerprint"]) == 12 and B.system_info()["fingerprint"] == info["fingerprint"]
+    # charts, reports, dashboards
+    line = B.Chart("scaling", x_label="n", y_label="ms", log_x=True).add_series("ours", [1, 10, 100], [1.0, 2.0, 4.0]).add_series("ref", [1, 10, 100], [1.5, 3.0, 6.0]).annotate(10, 2.0, "knee")
+    svg = ET.fromstring(line.to_svg())
+    nsx = "{http://www.w3.org/2000/svg}"
+    polys = svg.findall(f"{nsx}polyline")
+    assert len(polys) == 2 and len(polys[0].attrib["points"].split()) == 3
+    xs = [float(p.split(",")[0]) for p in polys[0].attrib["points"].split()]
+    assert xs[1] - xs[0] == pytest.approx(xs[2] - xs[1])                      # log axis: decades evenly spaced
+    bars = ET.fromstring(B.Chart("t", kind="bar").add_series("a", ["x", "y"], [1.0, 2.0]).to_svg()).findall(f"{nsx}rect[@class='bar']")
+    assert len(bars) == 2 and float(bars[1].attrib["height"]) == pytest.approx(2 * float(bars[0].attrib["height"]), rel=1e-2)
+    page = B.HtmlReportGenerator("Report", theme="dark").add_results("GEMM", [memb], an).add_chart(line).add_text("notes", "a < b").add_system(info).render()
+    assert page.startswith("<!doctype html>") and "<td>memory</td><td>80%</td>" in page and "a &lt; b" in page and "<svg" in page and "#111" in page
+    dash = B.PerformanceDashboard(tmp_path / "hist.jsonl")
+    for i, v in enumerate(hist):
+        dash.record(f"run{i}", {"step_ms": v, "tokens_per_s": 1000.0}, timestamp=float(i))
+    h = dash.history()
+    assert len(h["step_ms"]) == 23 and h["step_ms"][0][0] == "run0"
+    out = dash.render()
+    assert "step_ms: regression" in out and "tokens_per_s: stable" in out and "regression +" in out and out.count("<svg") == 2
+    # library comparisons
+    cmpr = B.ComparisonRunner(iterations=2, warmup=1).with_defaults()
+    rows = cmpr.run("matmul", [x, y])
+    assert set(rows) == {"numpy", "torch"} and rows["numpy"]["max_diff_vs_baseline"] < 1e-4 and rows["torch"]["speedup_vs_baseline"] == 1.0
+    # precision / quantisation / pruning
+    pb = B.precision_benchmark(torch.matmul, [torch.randn(64, 64), torch.randn(64, 64)], iterations=2)
+    assert pb["float32"]["rel_error"] < 1e-6 < pb["float16"]["rel_error"] < pb["bfloat16"]["rel_error"] < 0.05
+    w, xin = torch.randn(32, 64), torch.randn(8, 64)
+    qb = B.quantization_benchmark(w, xin)
+    assert qb["int8"]["sqnr_db"] > qb["int4"]["sqnr_db"] + 20 and qb["int4"]["compression"] > qb["int8"]["compression"] > 3.5 and qb["int8"]["output_rel_error"] < 0.02
+    pr = B.pruning_benchmark(w, xin)
+    assert pr[0.5]["achieved_sparsity"] == pytest.approx(0.5, abs=0.01) and pr[0.5]["output_rel_error"] < pr[0.9]["output_rel_error"] and pr[0.9]["sparse_flops"] < 0.11 * pr[0.9]["dense_flops"]
+    p24 = B.pruning_benchmark(w, xin, sparsities=(0.5,), method="2:4")[0.5]
+    assert p24["achieved_sparsity"] == 0.5 and p24["output_rel_error"] < B.pruning_benchmark(w, xin, sparsities=(0.5,), method="random")[0.5]["output_rel_error"]
+    # edge deployment
+    net = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.ReLU(), torch.nn.Linear(128, 10))
+    eb = B.edge_inference_benchmark(net, torch.randn(1, 64), B.EdgeProfile(memory_limit_mb=1.0, power_watts=2.0, battery_wh=10.0), iterations=3, inferences_per_hour=3600)
+    assert eb["fits_memory"] and eb["model_mb"] == pytest.approx((64 * 128 + 128 + 1280 + 10) * 4 / 2 ** 20) and eb["energy_mj"] == pytest.approx(2.0 * eb["latency_ms"]) and eb["battery_hours"] == pytest.approx(10.0 / (eb["energy_mj"] * 1e-3))
+    assert not B.edge_inference_benchmark(net, torch.randn(1, 64), B.EdgeProfile(memory_limit_mb=0.01), iterations=1)["fits_memory"]
+    hp = B.hardware_probes(mb=4, n=64, iterations=2)
+    assert hp["copy_gbps"] > 0 and hp["matmul_gflops"] > 0 and hp["ridge_flops_per_byte"] > 0
+    mon = B.MemoryMonitor()
+    mon.sample("a"); keep = torch.ones(1 << 22); mon.sample("b")
+    assert mon.peak() >= mon.samples[0][1] and isinstance(mon.growth(), int)
