@@ -1,8 +1,11 @@
 """Auxiliary subsystems on the CPU: optimizer checkpoints, monitoring, debug checks, property-based fuzzing of the
 host-side planners and codecs."""
+import json
 import math
 import os
+import re
 import threading
+from collections import Counter
 
 import numpy as np
 import pytest
@@ -1761,3 +1764,203 @@ def test_bench_suite_runner_analysis_cache_comparison_validation_ci_regressions_
     mon = B.MemoryMonitor()
     mon.sample("a"); keep = torch.ones(1 << 22); mon.sample("b")
     assert mon.peak() >= mon.samples[0][1] and isinstance(mon.growth(), int)
+
+
+def test_jit_analysis_intervals_paths_partial_eval_generics_templates_advisor_pgo_loops_uncertainty_synthesis_speculation_learned_costs_symbols_tuning_and_llvm():
+    from torsh_b200 import jit_analysis as J
+    # interval abstract interpretation: bounds hold for samples, domain problems are reported
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc = torch.nn.Linear(4, 3)
+        def forward(self, x):
+            h = torch.relu(self.fc(x))
+            return torch.sigmoid(h) / (h - 0.5), torch.log(h)
+    torch.manual_seed(0)
+    net = Net()
+    gm = torch.fx.symbolic_trace(net)
+    ai = J.AbstractInterpreter(gm)
+    env = ai.run(J.Interval(-1.0, 1.0))
+    xs = torch.rand(500, 4) * 2 - 1
+    pre = net.fc(xs).detach()
+    assert env["fc"].lo <= float(pre.min()) and float(pre.max()) <= env["fc"].hi and env["relu"].lo >= 0 and env["relu"].sign() == "non-negative"
+    assert 0.5 <= env["sigmoid"].lo and env["sigmoid"].hi <= 1.0 and {w["kind"] for w in ai.warnings} == {"division_by_zero", "domain"}
+    iv = J.Interval(-2, 3)
+    assert (iv * iv) == J.Interval(-6, 9) and (iv - iv) == J.Interval(-5, 5) and (J.Interval(1, 2) / J.Interval(4, 8)) == J.Interval(0.125, 0.5) and iv.join(J.Interval(5, 6)) == J.Interval(-2, 6)
+    assert iv.meet(J.Interval(4, 5)).is_empty() and J.Interval(0, 1).widen(J.Interval(0, 2)) == J.Interval(0, math.inf) and J.Interval(1, 2).sign() == "positive"
+    safe = J.AbstractInterpreter(torch.fx.symbolic_trace(lambda x: torch.exp(x) / (torch.abs(x) + 1.0)))
+    out = safe.run(J.Interval(-3, 3))
+    assert not safe.warnings and safe.output.lo > 0 and safe.output.hi <= math.exp(3) + 1e-9
+    # symbolic execution enumerates the feasible paths with witnesses
+    def f(x, y):
+        if x > 10:
+            if y < x:
+                return x - y
+            return y * 2
+        if x > 20:                      # unreachable: x <= 10 here
+            return 0
+        return 1 / (x - 5)
+    paths = J.SymbolicExecutor().explore(f)
+    feas = [p for p in paths if p.feasible]
+    assert len(paths) == 4 and len(feas) == 3 and [p for p in paths if not p.feasible][0].conditions == ["not (x > 10)", "x > 20"]
+    for p in feas:
+        w = p.witness
+        if p.conditions == ["x > 10", "y < x"]:
+            assert w["x"] > 10 and w["y"] < w["x"] and p.result == "(x - y)"
+    assert any(p.conditions == ["x > 10", "not (y < x)"] and p.result == "(y * 2)" for p in feas)
+    # partial evaluation removes the branch on a static argument
+    def poly(x, degree, scale):
+        out = x * 0
+        for d in range(degree):
+            out = out + x ** d
+        return out * scale if scale != 1 else out
+    g3, rep = J.partial_evaluate(poly, degree=3, scale=1)
+    t = torch.randn(5)
+    assert torch.allclose(g3(t, 3, 1), 1 + t + t * t) and "mul_1" not in g3.code and rep["static"] == ["degree", "scale"]
+    g2, _ = J.partial_evaluate(poly, degree=2, scale=2)
+    assert torch.allclose(g2(t, 2, 2), 2 * (1 + t)) and len(list(g2.graph.nodes)) < len(list(g3.graph.nodes)) + 2
+    # generics
+    @J.generic(T=(torch.float32, torch.float64))
+    def axpy(a: "T", b: "T", types=None):
+        return a * 2 + b, types["T"]
+    r32, t32 = axpy(torch.ones(2), torch.ones(2))
+    r64, t64 = axpy(torch.ones(2, dtype=torch.float64), torch.ones(2, dtype=torch.float64))
+    axpy(torch.zeros(2), torch.zeros(2))
+    assert t32 == torch.float32 and t64 == torch.float64 and axpy.instantiations() == ["axpy<float32>", "axpy<float64>"]
+    with pytest.raises(TypeError, match="bound to both"):
+        axpy(torch.ones(2), torch.ones(2, dtype=torch.float64))
+    with pytest.raises(TypeError, match="constraint"):
+        axpy(torch.ones(2, dtype=torch.int32), torch.ones(2, dtype=torch.int32))
+    # templates, unrolling, reflection
+    tpl = J.CodeTemplate("def act(x):\n    return torch.${fn}(x) * ${scale}\n", "act")
+    assert torch.equal(tpl.instantiate(fn="relu", scale=2)(torch.tensor([-1.0, 3.0])), torch.tensor([0.0, 6.0])) and tpl.instantiate(fn="relu", scale=2) is tpl.instantiate(fn="relu", scale=2) and len(tpl.generated) == 1
+    fn, src = J.unroll_loop("x = x * 2 + k", "k", 3)
+    assert fn(1) == ((1 * 2 + 0) * 2 + 1) * 2 + 2 and src.count("x = x * 2") == 3 and "for" not in src
+    refl = J.reflect(gm)
+    assert refl["inputs"] == ["x"] and refl["operations"]["call_module:Linear"] == 1 and refl["parameters"]["fc.weight"] == (3, 4) and refl["depth"] >= 5
+    # advisor
+    class Block(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.fc, self.act = torch.nn.Linear(8, 8), torch.nn.GELU()
+        def forward(self, x):
+            h = self.act(self.fc(x))
+            a, b = torch.exp(x), torch.exp(x)
+            unused = x + 1
+            return torch.tanh(torch.relu(h * 2.0) + 1.0) + a + b
+    bgm = torch.fx.symbolic_trace(Block())
+    recs = J.OptimizationAdvisor(bgm).advise()
+    kinds = [r["kind"] for r in recs]
+    assert {"fuse_elementwise", "fuse_epilogue", "common_subexpression", "dead_code", "precision"} <= set(kinds) and recs[0]["gain"] >= recs[-1]["gain"]
+    assert [r for r in recs if r["kind"] == "dead_code"][0]["nodes"] == ["add"] and sorted([r for r in recs if r["kind"] == "common_subexpression"][0]["nodes"]) == ["exp", "exp_1"]
+    prof = J.ProfilingInterpreter(bgm)
+    for _ in range(3):
+        prof.run(torch.randn(4, 8))
+    p = prof.profile()
+    assert p["counts"]["fc"] == 3 and p["shapes"]["fc"] == {(4, 8): 3} and all(v > 0 for v in p["times"].values())
+    hot = J.OptimizationAdvisor(bgm, {**{k: 1e-6 for k in p["times"]}, "fc": 1.0}).advise()
+    assert any(r["kind"] == "hotspot" and r["nodes"] == ["fc"] for r in hot)
+    # profile-guided dispatch
+    d = J.ProfileGuidedDispatcher(lambda x: "general", hot_threshold=5)
+    d.add("tiny", lambda x: x.shape[0] <= 4, lambda x: "tiny").add("aligned", lambda x: x.shape[0] % 128 == 0, lambda x: "aligned")
+    for _ in range(20):
+        assert d(torch.empty(256)) == "aligned"
+    assert d(torch.empty(3)) == "tiny" and d(torch.empty(77)) == "general" and d.guard_evals == 20 * 2 + 1 + 2
+    assert d.reoptimize() == ["aligned", "tiny"] and (256,) in d.table
+    before = d.guard_evals
+    assert d(torch.empty(256)) == "aligned" and d.guard_evals == before and d(torch.empty(128)) == "aligned" and d.guard_evals == before + 1
+    # loop nests: A[i][j] = A[i-1][j+1] + 1 has distance (1, -1): interchange and tiling are illegal, skewless stencil (1, 0) is fine
+    bad = J.LoopNest([("i", 1, 6), ("j", 0, 5)], [J.Access("A", [{"i": 1}, {"j": 1}], True), J.Access("A", [{"i": 1, "": -1}, {"j": 1, "": 1}])], "A[i][j] = A[i - 1][j + 1] + 1")
+    assert bad.dependences() == [(1, -1)] and not bad.can_permute([1, 0]) and not bad.can_tile() and bad.parallel_loops() == []
+    with pytest.raises(ValueError):
+        bad.generate(order=[1, 0])
+    good = J.LoopNest([("i", 1, 9), ("j", 1, 9)], [J.Access("A", [{"i": 1}, {"j": 1}], True), J.Access("A", [{"i": 1, "": -1}, {"j": 1}]), J.Access("A", [{"i": 1}, {"j": 1, "": -1}])], "A[i][j] = A[i - 1][j] + A[i][j - 1]")
+    assert good.dependences() == [(0, 1), (1, 0)] and good.can_permute([1, 0]) and good.can_tile()
+    base_fn, _ = good.generate()
+    tiled_fn, tsrc = good.generate(order=[1, 0], tiles={"i": 3, "j": 4})
+    A0 = [[1] * 9 for _ in range(9)]
+    A1, A2 = [r[:] for r in A0], [r[:] for r in A0]
+    base_fn(A1); tiled_fn(A2)
+    assert A1 == A2 and A1[8][8] == math.comb(16, 8) and "for j_t in range(1, 9, 4)" in tsrc and tsrc.index("j_t") < tsrc.index("i_t")
+    par = J.LoopNest([("i", 0, 4), ("j", 1, 4)], [J.Access("B", [{"i": 1}, {"j": 1}], True), J.Access("B", [{"i": 1}, {"j": 1, "": -1}])], "B[i][j] = B[i][j - 1] * 2")
+    assert par.parallel_loops() == ["i"]
+    none = J.LoopNest([("i", 0, 8)], [J.Access("C", [{"i": 2}], True), J.Access("C", [{"i": 2, "": 1}])], "C[2 * i] = C[2 * i + 1]")
+    assert none.dependences() == [] and none.parallel_loops() == ["i"]
+    # uncertain shapes
+    dist = J.ShapeDistribution.from_observations([128] * 90 + [8192] * 10)
+    variants = {"small_tiles": lambda n: 1.0 + n / 512, "large_tiles": lambda n: 6.0 + n / 4096}
+    ch = J.choose_variant(variants, dist)
+    assert ch["choice"] == "small_tiles" and ch["table"]["small_tiles"]["mean"] == pytest.approx(0.9 * 1.25 + 0.1 * 17.0)
+    assert J.choose_variant(variants, dist, risk_aversion=1.0)["choice"] == "large_tiles" and J.choose_variant(variants, dist, tail=0.99)["choice"] == "large_tiles"
+    # synthesis from examples
+    gsyn = torch.Generator().manual_seed(1)
+    ex = [((a, b), torch.relu(a - b)) for a, b in ((torch.randn(6, generator=gsyn), torch.randn(6, generator=gsyn)) for _ in range(4))]
+    syn = J.synthesize(ex, 2)
+    a, b = torch.randn(9), torch.randn(9)
+    assert syn is not None and syn["depth"] == 3 and torch.allclose(syn["fn"](a, b), torch.relu(a - b)) and "x0" in syn["expression"] and "x1" in syn["expression"]
+    assert J.synthesize([((a,), torch.cos(a))], 1, max_depth=2) is None
+    sq = J.synthesize([((a,), a * a + 1.0)], 1, constants=(1.0,))
+    assert torch.allclose(sq["fn"](b), b * b + 1)
+    # speculation
+    calls = Counter()
+    def general(x): calls["general"] += 1; return x.contiguous().sum()
+    def fast(x): calls["fast"] += 1; return x.sum()
+    sp = J.SpeculativeFunction(general, max_failure_rate=0.3, min_calls=10).speculate("contiguous", lambda x: x.is_contiguous(), fast)
+    cont, strided = torch.ones(4, 4), torch.ones(4, 8)[:, ::2]
+    for _ in range(8):
+        sp(cont)
+    sp(strided)
+    assert calls == {"fast": 8, "general": 1} and sp.stats["contiguous"]["active"]
+    for _ in range(6):
+        sp(strided)
+    assert not sp.stats["contiguous"]["active"]
+    sp(cont)
+    assert calls["fast"] == 8
+    # differentiable selection and continuous knobs
+    torch.manual_seed(0)
+    costs = {"a": 3.0, "b": 1.0, "c": 2.0}
+    sched = J.DifferentiableScheduler(list(costs))
+    noise = torch.Generator().manual_seed(0)
+    hist = sched.fit(lambda k: costs[k] * (1 + 0.05 * float(torch.randn((), generator=noise))), steps=150)
+    assert sched.best() == "b" and float(sched.probabilities()[1].detach()) > 0.8 and hist[-1] < hist[5]
+    knob = J.optimise_continuous_knob(lambda t: (t - 96.0) ** 2 / 1e3 + 1.0, init=32.0, lo=16.0, hi=256.0, steps=400, lr=0.1)
+    assert knob == pytest.approx(96.0, abs=2.0)
+    # learned cost model ranks unseen programs
+    feats, secs = [], []
+    for width in (16, 32, 64, 128, 256, 512):
+        for depth in (1, 2, 3):
+            m = torch.nn.Sequential(*[l for _ in range(depth) for l in (torch.nn.Linear(width, width), torch.nn.ReLU())])
+            fv = J.graph_features(torch.fx.symbolic_trace(m), [torch.randn(8, width)])
+            feats.append(fv); secs.append(1e-6 + 1e-10 * math.expm1(float(fv[0])))
+    feats, secs = torch.stack(feats), torch.tensor(secs)
+    lcm = J.LearnedCostModel()
+    assert lcm.fit(feats, secs, steps=800) < 0.05
+    test_f = torch.stack([J.graph_features(torch.fx.symbolic_trace(torch.nn.Sequential(torch.nn.Linear(w, w), torch.nn.ReLU(), torch.nn.Linear(w, w))), [torch.randn(8, w)]) for w in (24, 384, 96)])
+    assert lcm.rank(test_f) == [0, 2, 1] and (lcm.predict_seconds(test_f) > 0).all()
+    # debug symbols
+    def user_fn(x):
+        y = torch.relu(x)
+        return y * 3
+    ugm, sym = J.DebugSymbolTable.trace(user_fn)
+    s = sym.lookup("relu")
+    assert s and s["file"].endswith("test_aux_cpu.py") and s["source"] == "y = torch.relu(x)" and sym.lookup("mul")["line"] == s["line"] + 1 and s["function"] == "user_fn"
+    gen_line = next(i for i, l in enumerate(ugm.code.splitlines(), 1) if l.strip().startswith("relu"))
+    assert sym.source_of_generated_line(gen_line)["source"] == "y = torch.relu(x)" and "test_aux_cpu.py" in sym.annotate_error("mul", ValueError("boom")) and json.loads(sym.to_json())["symbols"]["relu"]["line"] == s["line"]
+    # hardware tuning tables
+    big = J.tune_gemm_tiles(8192, 8192, 8192)
+    assert big["tile"] == (128, 256, 64) and big["tmem_columns"] == 512 and big["smem_bytes"] <= 227 * 1024 and big["stages"] >= 3 and big["split_k"] == 1 and big["double_buffered_accumulator"]
+    skinny = J.tune_gemm_tiles(256, 512, 16384)
+    assert skinny["ctas"] < 74 and skinny["split_k"] > 1
+    odd = J.tune_gemm_tiles(148 * 128, 128, 512)
+    assert odd["wave_efficiency"] == 1.0 and odd["tile"][1] == 128
+    ew = J.tune_elementwise(1 << 28)
+    assert ew["vector_width"] == 8 and ew["persistent"] and ew["grid"] == 148 * 8 and not ew["fits_l2"] and J.tune_elementwise(1000)["grid"] == 1
+    # LLVM IR text for a fused chain: relu(a * b + 1.5) / exp(a)
+    ir = J.emit_llvm_ir([("mul", "in0", "in1"), ("add", "t0", 1.5), ("relu", "t1"), ("exp", "in0"), ("div", "t2", "t3")], 2)
+    assert ir.startswith("declare float @llvm.exp.f32(float)\ndeclare float @llvm.maxnum.f32(float, float)\ndefine void @fused(float* noalias %in0") and ir.count("{") == ir.count("}") == 1
+    defs = re.findall(r"^\s*(%[\w.]+) =", ir, re.M)
+    assert len(defs) == len(set(defs)) and "%i = phi i64 [ 0, %entry ], [ %i.next, %loop ]" in ir and "store float %t4" in ir
+    used = set(re.findall(r"(%[\w.]+)", ir.split("{", 1)[1])) - {"%entry", "%loop", "%exit"}
+    assert used <= set(defs) | {"%in0", "%in1", "%out", "%n"}
+    a, b = torch.randn(32), torch.randn(32)
+    assert torch.allclose(J.interpret_llvm_ir(ir, [a, b]), torch.relu(a * b + 1.5) / torch.exp(a))
