@@ -6,6 +6,7 @@ import os
 import re
 import threading
 from collections import Counter
+from pathlib import Path
 
 import numpy as np
 import pytest
@@ -1964,3 +1965,134 @@ def test_jit_analysis_intervals_paths_partial_eval_generics_templates_advisor_pg
     assert used <= set(defs) | {"%in0", "%in1", "%out", "%n"}
     a, b = torch.randn(32), torch.randn(32)
     assert torch.allclose(J.interpret_llvm_ir(ir, [a, b]), torch.relu(a * b + 1.5) / torch.exp(a))
+
+
+def test_ffi_header_model_generated_bindings_docs_tests_batching_numpy_pandas_scipy_views_and_migration(tmp_path):
+    import subprocess
+    import sys
+    import importlib.util
+    import pandas as pd
+    from torsh_b200 import ffi
+    from torsh_b200 import _native as nv
+    fns = ffi.parse_header()
+    by = {f.name: f for f in fns}
+    assert len(fns) == 98 and by["torsh_init"].doc == "" and by["torsh_tensor_conv2d"].params[2].ctype == "const TorshTensor*" and [p.name for p in by["torsh_tensor_conv2d"].params] == ["input", "weight", "bias", "stride", "padding"]
+    assert by["torsh_tensor_dtype"].doc == "always 0 = f32" and "optional bias" in by["torsh_tensor_conv2d"].doc and by["torsh_version"].ret == "const char*" and by["torsh_cleanup"].params == []
+    assert ffi.canonical("const int64_t*") == "int64ptr" and ffi.lang_type("TorshTensor*", "go") == "unsafe.Pointer" and ffi.lang_type("size_t", "julia") == "Csize_t" and by["torsh_tensor_add"].group == "tensor" and by["torsh_init"].group == "runtime"
+    gen = ffi.BindingGenerator(fns)
+    files = gen.generate_all(tmp_path / "bindings")
+    assert set(files) == set(gen.LANGUAGES)
+    for lang, path in files.items():
+        text = path.read_text()
+        for f in fns:                                                            # every function of the header reaches every language
+            if lang == "swift":
+                continue
+            assert (gen._lower_camel(f.name) + "(" if lang in ("java", "typescript") else f.name) in text, (lang, f.name)
+    cs, go, jl = files["csharp"].read_text(), files["go"].read_text(), files["julia"].read_text()
+    assert 'EntryPoint = "torsh_tensor_matmul"' in cs and "public static extern IntPtr TensorMatmul(IntPtr a, IntPtr b);" in cs and cs.count("{") == cs.count("}")
+    assert "func TensorMatmul(a *C.TorshTensor, b *C.TorshTensor) *C.TorshTensor { return C.torsh_tensor_matmul(a, b) }" in go and "func SetDevice(index int) error {" in go and go.count("{") == go.count("}")
+    assert "tensor_add_scalar(a, s) = ccall((:torsh_tensor_add_scalar, lib), Ptr{Cvoid}, (Ptr{Cvoid}, Cfloat), a, s)" in jl and "init() = ccall((:torsh_init, lib), Cint, ())" in jl
+    assert "tensor_relu(a) = ccall((:torsh_tensor_relu, lib), Ptr{Cvoid}, (Ptr{Cvoid},), a)" in jl
+    assert "attach_function :torsh_tensor_new, [:pointer, :pointer, :int], :pointer" in files["ruby"].read_text() and "public static native long tensorNew(float[] data, long[] shape, int ndim);" in files["java"].read_text()
+    assert "TorshTensor* torsh_tensor_new(const float* data" not in files["lua"].read_text() and "void* torsh_tensor_new(float* data, int64_t* shape, int ndim);" in files["lua"].read_text()
+    assert "tensorSoftmax(a: unknown, dim: number): unknown;" in files["typescript"].read_text() and "api.tensorSoftmax = lib.func('torsh_tensor_softmax', 'void*', ['void*', 'int']);" in files["nodejs"].read_text()
+    assert "public func softmax(_ dim: Int32) throws -> Tensor { try Tensor(torsh_tensor_softmax(handle, dim)) }" in files["swift"].read_text() and "'_torsh_tensor_add'" in files["wasm"].read_text()
+    assert 'torsh_tensor_add <- function(a, b) .Call("R_torsh_tensor_add", a, b)' in files["r"].read_text() and "fcns.name{1} = 'torsh_init'; fcns.calltype{1} = 'cdecl'; fcns.LHS{1} = 'int32'; fcns.RHS{1} = {};" in files["matlab"].read_text()
+    jni = gen.jni_stubs()
+    assert jni.count("JNIEXPORT") == 98 and "Java_org_torsh_Torsh_tensorNew(JNIEnv* env, jclass cls, jfloatArray data, jlongArray shape, jint ndim)" in jni and jni.count("GetFloatArrayElements") == jni.count("ReleaseFloatArrayElements") and jni.count("{") == jni.count("}")
+    # the generated Python binding runs against the built library
+    nv.host()
+    lib_path = str(next(p for p in (Path(ffi.__file__).parent / "lib").glob("libtorsh_b200_host*.so")))
+    spec = importlib.util.spec_from_file_location("torsh_ffi", files["python"])
+    mod = importlib.util.module_from_spec(spec); spec.loader.exec_module(mod)
+    api = mod.load(lib_path)
+    import ctypes
+    mk = lambda vals, shape: api.tensor_new((ctypes.c_float * len(vals))(*vals), (ctypes.c_int64 * len(shape))(*shape), len(shape))
+    a, b = mk([1, 2, 3, 4], [2, 2]), mk([1, 0, 0, 1], [2, 2])
+    c = api.tensor_matmul(a, b)
+    assert [api.tensor_data(c)[i] for i in range(4)] == [1, 2, 3, 4] and api.tensor_numel(c) == 4 and "torsh_tensor_matmul" in api.tensor_matmul.__doc__
+    with pytest.raises(mod.TorshError, match="mismatch"):
+        api.tensor_matmul(a, mk([1, 2, 3], [3, 1]))
+    with pytest.raises(ctypes.ArgumentError):
+        api.tensor_add_scalar(a, "x")
+    # generated documentation and generated tests (the tests run in a child interpreter against the library)
+    docs = ffi.generate_api_docs(fns)
+    assert docs.startswith("# C API reference") and docs.count("### `torsh_") == 98 and "| `grad_output` | `const TorshTensor*` |" in docs and "## tensor" in docs and "always 0 = f32" in docs
+    (tmp_path / "bindings" / "test_generated.py").write_text(ffi.generate_tests(fns))
+    run = subprocess.run([sys.executable, "-m", "pytest", "-q", "-p", "no:cacheprovider", str(tmp_path / "bindings" / "test_generated.py")], env={**os.environ, "TORSH_LIBRARY": lib_path, "PYTHONPATH": str(tmp_path / "bindings")}, capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0 and re.search(r"(\d+) passed", run.stdout) and int(re.search(r"(\d+) passed", run.stdout).group(1)) > 25, run.stdout[-2000:] + run.stderr[-2000:]
+    # batching: duplicate sub-calls run once, dead intermediates are freed inside the batch
+    class FakeApi:
+        def __init__(self): self.live, self.n, self.log = set(), 0, []
+        def _new(self): self.n += 1; self.live.add(self.n); return self.n
+        def tensor_relu(self, a): self.log.append("relu"); return self._new()
+        def tensor_exp(self, a): self.log.append("exp"); return self._new()
+        def tensor_add(self, a, b): self.log.append("add"); return self._new()
+        def tensor_free(self, h): self.live.discard(h)
+    fa = FakeApi()
+    cb = ffi.CallBatcher(fa)
+    r1 = cb.call("tensor_relu", 100); r2 = cb.call("tensor_relu", 100); e = cb.call("tensor_exp", cb.ref(r1)); s = cb.call("tensor_add", cb.ref(e), cb.ref(r2))
+    out, = cb.run(keep=[s])
+    assert fa.log == ["relu", "exp", "add"] and fa.live == {out} and cb.crossings == 5
+    # NumPy protocols
+    x = ffi.NumpyCompatibleTensor(torch.tensor([[1.0, 2.0], [3.0, 4.0]]))
+    y = np.add(x, np.ones((2, 2), dtype=np.float32))
+    assert isinstance(y, ffi.NumpyCompatibleTensor) and isinstance(np.exp(x), ffi.NumpyCompatibleTensor) and np.asarray(y).tolist() == [[2, 3], [4, 5]]
+    assert isinstance(np.sum(x, axis=0), ffi.NumpyCompatibleTensor) and np.asarray(np.sum(x, axis=0)).tolist() == [4, 6] and float(np.asarray(np.mean(x))) == 2.5 and np.concatenate([x, x], axis=1).shape == (2, 4)
+    assert np.asarray(np.matmul(x, x)).tolist() == [[7, 10], [15, 22]] and np.asarray(np.add.reduce(x, axis=1)).tolist() == [3, 7] and np.asarray(np.transpose(x)).tolist() == [[1, 3], [2, 4]] and np.allclose(x, np.asarray(x))
+    assert float(np.asarray(np.linalg.norm(x))) == pytest.approx(30 ** 0.5) and np.asarray(np.where(np.greater(x, 2), x, 0)).tolist() == [[0, 0], [3, 4]] and x.dtype == np.float32 and np.asarray(x.T @ x).shape == (2, 2)
+    with pytest.raises(TypeError):
+        np.fft.fft(x)
+    arr = np.arange(6, dtype=np.float32).reshape(2, 3)
+    shared = ffi.from_numpy(arr); shared[0, 0] = 9
+    assert arr[0, 0] == 9 and ffi.from_numpy(arr[:, ::-1]).tolist() == arr[:, ::-1].tolist() and ffi.from_numpy(arr, copy=True).data_ptr() != shared.data_ptr()
+    with pytest.raises(TypeError):
+        ffi.from_numpy(np.array(["a"]))
+    # pandas
+    df = pd.DataFrame({"age": [31.0, None, 45.0, 22.0], "city": ["rome", "oslo", "rome", None], "vip": [True, False, False, True], "when": pd.to_datetime(["2024-01-01", "2024-01-02", "2024-01-03", "2024-01-04"]), "label": ["no", "yes", "no", "yes"]})
+    d = ffi.dataframe_to_tensors(df, target="label", dtype=torch.float64)
+    assert d["features"].shape == (4, 4) and d["columns"] == ["age", "city", "vip", "when"] and torch.isnan(d["features"][1, 0]) and d["features"][:, 1].tolist() == [1, 0, 1, -1] and d["categories"]["city"] == ["oslo", "rome"]
+    assert d["features"][:, 2].tolist() == [1, 0, 0, 1] and float(d["features"][1, 3] - d["features"][0, 3]) == pytest.approx(86400.0, rel=1e-4) and d["target"].tolist() == [0, 1, 0, 1] and d["target_classes"] == ["no", "yes"]
+    oh = ffi.dataframe_to_tensors(df[["city"]], categorical="onehot")
+    assert oh["columns"] == ["city=oslo", "city=rome"] and oh["features"].tolist() == [[0, 1], [1, 0], [0, 1], [0, 0]]
+    back = ffi.tensor_to_dataframe(torch.tensor([[1.0, 0.0], [2.0, 1.0]]), ["v", "city"], {"city": ["oslo", "rome"]})
+    assert list(back["city"]) == ["oslo", "rome"] and back["v"].tolist() == [1.0, 2.0]
+    ds = ffi.DataFrameDataset(df, "label")
+    assert len(ds) == 4 and ds[2][1] == 0 and ds[2][0].shape == (4,)
+    # SciPy
+    res = ffi.scipy_minimize(lambda v: ((v - torch.tensor([1.0, -2.0, 3.0])) ** 2).sum() + 0.1 * (v[0] * v[1]) ** 2, torch.zeros(3))
+    assert res.success and res.x_tensor.dtype == torch.float32 and res.x_tensor[2] == pytest.approx(3.0, abs=1e-4) and res.fun < 0.4
+    tt, yy = ffi.scipy_solve_ivp(lambda t, y: -y, (0.0, 1.0), torch.tensor([1.0, 2.0]), rtol=1e-8, atol=1e-10)
+    assert yy[-1].tolist() == pytest.approx([math.exp(-1), 2 * math.exp(-1)], rel=1e-6)
+    dense = torch.tensor([[0.0, 2.0, 0.0], [1.0, 0.0, 3.0]])
+    sp = ffi.to_scipy_sparse(dense)
+    assert sp.nnz == 3 and torch.equal(ffi.from_scipy_sparse(sp).to_dense(), dense) and torch.equal(ffi.from_scipy_sparse(sp @ sp.T).to_dense(), dense @ dense.T)
+    assert ffi.scipy_function("special.gammaln")(torch.tensor([5.0])).item() == pytest.approx(math.log(24)) and len(ffi.scipy_function("signal.butter")(2, 0.3)) == 2
+    # plots and notebook views
+    grad = torch.arange(12.0).reshape(3, 4)
+    hm = ffi.ascii_heatmap(grad)
+    assert hm.splitlines()[0][0] == " " and hm.splitlines()[-1][-1] == "@" and len(hm.splitlines()) == 3
+    hist = ffi.ascii_histogram(torch.tensor([0.0] * 8 + [1.0] * 2), bins=2, width=8)
+    assert hist.splitlines()[0].endswith("######## 8") and hist.splitlines()[1].endswith("## 2")
+    svg = ffi.heatmap_svg(grad, title="g")
+    assert svg.count("<rect") == 12 and "#0000ff" in svg and "#ff0000" in svg and "[2,3] 11" in svg
+    assert ffi.training_curves_svg({"loss": [3, 2, 1], "acc": [0.1, 0.5, 0.9]}).count("<polyline") == 2
+    view = ffi.TensorView(grad, "weights")._repr_html_()
+    assert "<th>shape</th><td>[3, 4]</td>" in view and "<svg" in view and "<th>mean</th><td>5.5</td>" in view and "<pre>" in ffi.TensorView(torch.randn(100, 100), max_cells=10)._repr_html_()
+    assert set(ffi.TensorView(grad)._repr_mimebundle_()) == {"text/html", "text/plain"}
+    pv = ffi.ProgressView(10, "epoch").update(4)
+    assert "value='4' max='10'" in pv._repr_html_() and str(pv).endswith("4/10") and str(pv).count("=") == 12
+    # migration
+    src = "import numpy as np\nfrom numpy.linalg import norm\na = np.array([[1.0, 2.0], [3.0, 4.0]])\nb = np.dot(a, a)\nc = np.expand_dims(b, axis=0)\nshape = tuple(c.shape)\n"
+    mig = ffi.migrate_source(src, "numpy")
+    assert "import rstorch as np" in mig["source"] and "from torsh_b200.linalg import norm" in mig["source"] and "np.tensor(" in mig["source"] and "np.matmul(a, a)" in mig["source"] and "np.unsqueeze(b, dim=0)" in mig["source"]
+    ns = {}
+    exec(mig["source"], ns)
+    assert ns["shape"] == (1, 2, 2) and len(mig["changes"]) >= 5 and not mig["manual"]
+    pt = ffi.migrate_source("import torch\nimport torch.nn as nn\nfrom torch.optim import SGD\nlayer = nn.Linear(4, 2)\nopt = SGD(layer.parameters(), lr=0.1)\nx = torch.ones(3, 4)\ny = layer(x)\n", "pytorch")
+    assert "import rstorch as torch" in pt["source"] and "import torsh_b200.nn as nn" in pt["source"] and "from torsh_b200.optim import SGD" in pt["source"]
+    ns = {}
+    exec(pt["source"], ns)
+    assert tuple(ns["y"].shape) == (3, 2)
+    tf = ffi.migrate_source("import tensorflow as tf\nx = tf.constant([1.0, 2.0])\ny = tf.reduce_sum(tf.math.exp(x), axis=0, keepdims=True)\nwith tf.GradientTape() as tape:\n    pass\n", "tensorflow")
+    assert "tf.tensor([1.0, 2.0])" in tf["source"] and "tf.sum(tf.exp(x), dim=0, keepdim=True)" in tf["source"] and tf["manual"] and "GradientTape" in tf["manual"][0][1]
