@@ -2096,3 +2096,213 @@ def test_ffi_header_model_generated_bindings_docs_tests_batching_numpy_pandas_sc
     assert tuple(ns["y"].shape) == (3, 2)
     tf = ffi.migrate_source("import tensorflow as tf\nx = tf.constant([1.0, 2.0])\ny = tf.reduce_sum(tf.math.exp(x), axis=0, keepdims=True)\nwith tf.GradientTape() as tape:\n    pass\n", "tensorflow")
     assert "tf.tensor([1.0, 2.0])" in tf["source"] and "tf.sum(tf.exp(x), dim=0, keepdim=True)" in tf["source"] and tf["manual"] and "GradientTape" in tf["manual"][0][1]
+
+
+def test_autograd_runtime_alerts_transactions_degradation_scaling_scheduling_tracing_buffers_backends_and_compat_layers(tmp_path):
+    from torsh_b200.autograd import runtime_ext as R
+    # alerts with channels and cool-down
+    pager, log = [], []
+    am = R.AnomalyAlertManager(cooldown=5).with_default_rules().add_channel(log.append).add_channel(pager.append, "critical")
+    assert am.check(1, {"name": "w", "norm": 1.0, "nan": 0, "inf": 0}) == []
+    assert [a.kind for a in am.check(2, {"name": "w", "norm": 5e3, "nan": 0, "inf": 0})] == ["exploding"] and not pager and len(log) == 1
+    assert am.check(3, {"name": "w", "norm": 5e3, "nan": 0, "inf": 0}) == [] and am.suppressed[("exploding", "w")] == 1
+    assert [a.kind for a in am.check(4, {"name": "w", "norm": 0.0, "nan": 2, "inf": 0})] == ["non_finite", "vanishing"] and len(pager) == 1 and pager[0].severity == "critical"
+    assert len(am.check(8, {"name": "w", "norm": 5e3, "nan": 0, "inf": 0})) == 1 and len(am.history) == 4
+    # error rates
+    er = R.ErrorRateMonitor(window=20, warn=0.1, critical=0.4)
+    for i in range(20):
+        er.record("backward", i < 14 or i % 2 == 0, "NaN")
+    assert er.rate("backward") == pytest.approx(0.15) and er.status("backward") == "warning" and er.trend("backward") == "rising" and er.report()["backward"]["kinds"] == {"NaN": 3}
+    with pytest.raises(ZeroDivisionError):
+        with er.watch("div"):
+            1 / 0
+    with er.watch("div"):
+        pass
+    assert er.rate("div") == 0.5 and er.status("div") == "critical" and er.kinds["div"] == {"ZeroDivisionError": 1}
+    # audit log with hash chain
+    audit = R.AutogradAuditLog(tmp_path / "audit.jsonl")
+    audit.record("backward", actor="trainer", tensors={"loss": torch.tensor(1.5)}, step=1)
+    audit.record("grad_clip", actor="trainer", max_norm=1.0)
+    audit.record("backward", actor="eval")
+    assert audit.verify() and len(audit.query(operation="backward")) == 2 and len(audit.query(actor="trainer")) == 2 and len((tmp_path / "audit.jsonl").read_text().splitlines()) == 3
+    audit.entries[1]["details"]["max_norm"] = 100.0
+    assert not audit.verify()
+    # gradient metrics and structured log
+    net = torch.nn.Linear(3, 2)
+    net(torch.ones(4, 3)).sum().backward()
+    gm = R.GradientMetricsCollector()
+    m = gm.collect(net.named_parameters(), lr=0.1)
+    assert m["global_norm"] == pytest.approx(float(torch.cat([p.grad.flatten() for p in net.parameters()]).norm())) and m["parameters"]["weight"]["abs_max"] == 4.0 and m["parameters"]["bias"]["update_ratio"] > 0
+    gm.collect(net.named_parameters())
+    assert gm.summary()["count"] == 2 and gm.summary("weight")["last"] == pytest.approx(float(net.weight.grad.norm()))
+    bad = R.GradientMetricsCollector.stats("g", torch.tensor([1.0, float("nan"), float("inf"), 0.0]))
+    assert bad["nan"] == 1 and bad["inf"] == 1 and bad["norm"] == 1.0 and bad["zero_fraction"] == 0.25
+    lines = []
+    sl = R.StructuredLogger(lines.append, level="info", clock=lambda: 7.0).bind(run="r1")
+    sl.debug("hidden"); sl.bind(step=3).warning("clip", norm=torch.tensor(2.5), grad=torch.zeros(2, 3))
+    assert len(lines) == 1 and json.loads(lines[0]) == {"ts": 7.0, "level": "warning", "event": "clip", "run": "r1", "step": 3, "norm": 2.5, "grad": [2, 3]} and sl.records[0]["event"] == "clip"
+    # transactions and guards
+    p = torch.nn.Parameter(torch.tensor([1.0, 2.0])); p.grad = torch.tensor([0.5, 0.5])
+    with pytest.raises(RuntimeError):
+        with R.ParameterTransaction([p]):
+            p.data.add_(10); p.grad.zero_()
+            raise RuntimeError("step failed")
+    assert p.tolist() == [1.0, 2.0] and p.grad.tolist() == [0.5, 0.5]
+    with R.ParameterTransaction([p]) as tx:
+        p.data.mul_(float("inf"))
+        assert not tx.commit_if(bool(torch.isfinite(p).all()))
+    assert p.tolist() == [1.0, 2.0] and tx.rolled_back
+    with R.ParameterTransaction([p]):
+        p.data.add_(1)
+    assert p.tolist() == [2.0, 3.0]
+    order = []
+    with pytest.raises(ValueError):
+        with R.ResourceGuard() as g:
+            g.acquire("a", lambda: 1, lambda r: order.append("a")); g.acquire("b", lambda: 2, lambda r: order.append("b"))
+            raise ValueError("body")
+    assert order == ["b", "a"]
+    # graceful degradation
+    def fused(x): raise NotImplementedError("no fused kernel for float64")
+    gd = R.GracefulDegradation("gelu").add("fused", fused).add("eager", torch.nn.functional.gelu).add("approx", lambda x: x * torch.sigmoid(1.702 * x), exact=False)
+    xx = torch.randn(5, dtype=torch.float64)
+    assert torch.equal(gd(xx), torch.nn.functional.gelu(xx)) and gd.disabled == {"fused"} and gd.events[0]["reason"].startswith("no fused")
+    gd(xx)
+    assert len(gd.events) == 1
+    with pytest.raises(RuntimeError, match="every implementation failed"):
+        R.GracefulDegradation("x").add("only", fused)(xx)
+    assert torch.allclose(R.numeric_gradient(lambda v: (v ** 3).sum(), torch.tensor([1.0, 2.0])), torch.tensor([3.0, 12.0], dtype=torch.float64), atol=1e-6)
+    # validation
+    lin = torch.nn.Linear(2, 2)
+    lin.weight.grad = torch.tensor([[1.0, float("nan")], [0.0, 0.0]])
+    kinds = [i["kind"] for i in R.validate_gradients(lin.named_parameters(), require_all=True, max_norm=0.5)]
+    assert kinds == ["non_finite", "missing"]
+    lin.weight.grad = torch.full((2, 2), 3.0); lin.bias.grad = torch.zeros(2)
+    assert [i["kind"] for i in R.validate_gradients(lin.named_parameters(), max_norm=0.5)] == ["norm"]
+    # optimizer-aware scaling
+    w = torch.nn.Parameter(torch.ones(4)); w.grad = torch.full((4,), 5.0)
+    assert R.OptimizerAwareGradientScaler(torch.optim.SGD([w], lr=0.1), clip=1.0).apply()["strategy"] == "global_clip" and float(w.grad.norm()) == pytest.approx(1.0, rel=1e-5)
+    w.grad = torch.full((4,), 5.0)
+    assert R.OptimizerAwareGradientScaler(torch.optim.SGD([w], lr=0.1, momentum=0.9), clip=1.0).apply()["strategy"] == "momentum_clip" and float(w.grad.norm()) == pytest.approx(0.5, rel=1e-5)
+    w.grad = torch.tensor([5.0, float("nan"), float("inf"), 1.0])
+    r = R.OptimizerAwareGradientScaler(torch.optim.Adam([w]), clip=1.0).apply()
+    assert r["strategy"] == "guard_only" and r["zeroed"] == 2 and w.grad.tolist() == [5.0, 0.0, 0.0, 1.0]
+    w.grad = torch.full((4,), 4.0)
+    r = R.OptimizerAwareGradientScaler(torch.optim.SGD([w], lr=0.1), layerwise=True).apply()
+    assert r["ratios"] == [pytest.approx(0.25)] and float(w.grad.norm()) == pytest.approx(float(w.detach().norm()))
+    # backward scheduling
+    gs = R.GradientScheduler().add("head", 1.0, frees=4.0).add("branch_a", 5.0, frees=1.0, allocates=2.0, after=["head"]).add("branch_b", 1.0, frees=3.0, allocates=1.0, after=["head"]).add("tail_a", 4.0, frees=2.0, after=["branch_a"])
+    s = gs.schedule()
+    assert s["order"] == ["head", "branch_a", "tail_a", "branch_b"] and s["critical_path"] == 10.0 and s["total_cost"] == 11.0
+    tight = gs.schedule(memory_budget=5.5, start_memory=8.0)
+    assert tight["order"][0] == "head" and tight["order"][1] == "branch_b" and tight["peak_memory"] <= 8.0
+    with pytest.raises(ValueError):
+        R.GradientScheduler().add("a", 1, after=["b"]).add("b", 1, after=["a"]).schedule()
+    # tracing the backward graph
+    a, b = torch.tensor([1.0, 2.0], requires_grad=True), torch.tensor([3.0, 4.0], requires_grad=True)
+    out = (torch.tanh(a * b) * 1e-4 + b).sum()
+    tr = R.GradientTracer(out, {"a": a, "b": b}).attach()
+    out.backward(); tr.detach()
+    assert tr.leaves() == ["a", "b"] and tr.operations()["TanhBackward0"] == 1 and tr.depth() >= 5 and tr.path_to("a")[0] == "SumBackward0" and tr.path_to("a")[-1] == "leaf:a" and "TanhBackward0" in tr.path_to("a")
+    flows = {r["label"]: r["flow"] for r in tr.report()}
+    assert flows["SumBackward0"] == pytest.approx(1.0) and flows["TanhBackward0"] == pytest.approx(1e-4 * math.sqrt(2), rel=1e-4)
+    bn = tr.bottleneck()
+    assert bn["ratio"] < 1e-3
+    # introspection
+    xi = torch.randn(4, 8, requires_grad=True)
+    info = R.introspect_operation(lambda t, w: torch.tanh(t @ w), xi, torch.randn(8, 3, requires_grad=True))
+    assert info["grad_fn"] == "TanhBackward0" and info["output_shape"] == (4, 3) and info["saved_tensors"] >= 3 and info["saved_bytes"] >= (32 + 24 + 12) * 4 and info["receives_gradient"] == [True, True] and info["twice_differentiable"]
+    assert R.introspect_operation(lambda t: t.detach() * 2, xi)["grad_fn"] is None
+    # buffer reuse
+    plan = R.plan_buffer_reuse([("a", 1000, 0, 2), ("b", 1000, 3, 5), ("c", 500, 1, 4), ("d", 400, 5, 6), ("e", 2000, 6, 8)])
+    assert plan["assignment"]["a"] == plan["assignment"]["b"] and plan["assignment"]["c"] == plan["assignment"]["d"] and plan["bytes"] == 2048 + 512 and plan["saved"] == plan["naive_bytes"] - plan["bytes"] > 0
+    assert plan["assignment"]["a"] == plan["assignment"]["e"] != plan["assignment"]["c"] and plan["assignment"]["d"] != plan["assignment"]["e"]
+    # chunked gradients equal the full-batch gradient
+    wt = torch.randn(6, requires_grad=True)
+    data = torch.randn(50, 6)
+    loss_fn = lambda d: torch.tanh(d @ wt) ** 2
+    full, = torch.autograd.grad(loss_fn(data).sum(), wt)
+    val, (chunked,) = R.chunked_gradient(loss_fn, [wt], data, memory_budget=7 * 1024, bytes_per_sample=1024)
+    assert torch.allclose(chunked, full, atol=1e-5) and float(val) == pytest.approx(float(loss_fn(data).sum().detach()), rel=1e-5)
+    # auto tuning with a fake clock
+    clock = [0.0]
+    tuner = R.AutoTuner(repeats=3, clock=lambda: clock[0])
+    cost = {16: 0.4, 64: 0.1, 256: 0.3}
+    assert tuner.get(("matmul", 512), [16, 64, 256], lambda c: clock.__setitem__(0, clock[0] + cost[c])) == 64 and tuner.get(("matmul", 512), [16], None) == 64
+    assert not tuner.observe(("matmul", 512), 0.12) and tuner.observe(("matmul", 512), 0.3) and ("matmul", 512) not in tuner.best
+    # gradient regression baselines
+    suite = R.GradientRegressionSuite(tmp_path / "grads.pt").add_case("tanh", lambda t: torch.tanh(t), [torch.linspace(-1, 1, 5)])
+    factor = [1.0]
+    suite.add_case("scaled", lambda t: t * t * factor[0], [torch.arange(3.0)])
+    suite.record()
+    assert {k: v["status"] for k, v in suite.check().items()} == {"tanh": "ok", "scaled": "ok"}
+    factor[0] = 1.001
+    chk = suite.add_case("fresh", lambda t: t, [torch.ones(1)]).check()
+    assert chk["scaled"]["status"] == "regressed" and chk["scaled"]["max_abs_diff"] == pytest.approx(0.004, rel=1e-3) and chk["fresh"]["status"] == "new" and chk["tanh"]["status"] == "ok"
+    # stress graphs
+    for kind, n in (("deep", 2000), ("wide", 500), ("shared", 300), ("diamond", 40)):
+        sg = R.stress_graph(kind, n)
+        assert sg["correct"] and sg["nodes"] >= (n if kind != "shared" else 3), kind
+    # differentiation backends agree
+    reg = R.BackendRegistry()
+    fn = lambda u, v: (torch.sin(u) * v).sum() + (u * u).sum()
+    u, v = torch.randn(3, dtype=torch.float64), torch.randn(3, dtype=torch.float64)
+    assert reg.cross_check(fn, [u, v]) == {"reverse": True, "forward": True, "finite_difference": True}
+    class Wrong(R.AutogradBackend):
+        name = "wrong"
+        def grad(self, fn, inputs): return [torch.zeros_like(i) for i in inputs]
+    reg.register(Wrong())
+    assert reg.cross_check(fn, [u, v])["wrong"] is False and torch.allclose(reg.get("forward").grad(fn, [u, v])[1], torch.sin(u))
+    # compatibility layers
+    x = torch.tensor([1.0, 2.0, 3.0])
+    with R.GradientTape() as tape:
+        tape.watch(x)
+        y = (x ** 2).sum()
+    assert tape.gradient(y, x).tolist() == [2.0, 4.0, 6.0]
+    with pytest.raises(RuntimeError):
+        tape.gradient(y, x)
+    with R.GradientTape(persistent=True) as tape:
+        tape.watch(x)
+        y, z = (x ** 2).sum(), (x ** 3).sum()
+    assert tape.gradient(y, [x])[0].tolist() == [2.0, 4.0, 6.0] and tape.gradient(z, x).tolist() == [3.0, 12.0, 27.0]
+    vg = R.value_and_grad(lambda params, inp: ((inp @ params["w"] + params["b"]) ** 2).sum())
+    params = {"w": torch.tensor([[1.0], [2.0]]), "b": torch.tensor([0.5])}
+    val, grads = vg(params, torch.tensor([[1.0, 1.0]]))
+    assert float(val) == 12.25 and grads["w"].tolist() == [[7.0], [7.0]] and grads["b"].tolist() == [7.0] and not params["w"].requires_grad
+    v2, (ga, gb) = R.value_and_grad(lambda p, q: (p * q).sum(), argnums=(0, 1))(torch.tensor([2.0]), torch.tensor([5.0]))
+    assert ga.tolist() == [5.0] and gb.tolist() == [2.0]
+    var = R.Variable(torch.tensor([2.0]), requires_grad=True)
+    (var.tensor ** 2).sum().backward()
+    assert var.grad.tolist() == [4.0] and var.data.tolist() == [2.0] and var.shape == (1,)
+    env = R.VariableEnvironment()
+    env.define("w", torch.tensor(2.0)); inner = env.child(); inner.define("b", torch.tensor(1.0)); inner.define("const", torch.tensor(9.0), requires_grad=False)
+    g = inner.gradients(inner.lookup("w") ** 2 * inner.lookup("b") + inner.lookup("const"))
+    assert {k: float(v) for k, v in g.items()} == {"w": 4.0, "b": 4.0} and set(env.visible()) == {"w"}
+    with pytest.raises(KeyError):
+        env.lookup("b")
+    # fused chain: one saved tensor, same values and gradients
+    xc = torch.randn(64, requires_grad=True)
+    saved = []
+    with torch.autograd.graph.saved_tensors_hooks(lambda t: saved.append(1) or t, lambda t: t):
+        yf = R.fused_chain(xc, "tanh", "square", "exp", "softplus")
+    n_fused = len(saved); saved.clear()
+    with torch.autograd.graph.saved_tensors_hooks(lambda t: saved.append(1) or t, lambda t: t):
+        ye = torch.nn.functional.softplus(torch.exp(torch.square(torch.tanh(xc))))
+    gf, = torch.autograd.grad(yf.sum(), xc); ge, = torch.autograd.grad(ye.sum(), xc)
+    assert n_fused == 1 < len(saved) and torch.allclose(yf, ye) and torch.allclose(gf, ge, atol=1e-6)
+    # GEMM-form gradients for all transposition cases, and for a solve
+    for ta in (False, True):
+        for tb in (False, True):
+            A = torch.randn(*((5, 3) if ta else (3, 5)), dtype=torch.float64, requires_grad=True)
+            Bm = torch.randn(*((4, 5) if tb else (5, 4)), dtype=torch.float64, requires_grad=True)
+            out = (A.mT if ta else A) @ (Bm.mT if tb else Bm)
+            go = torch.randn_like(out)
+            ra, rb = torch.autograd.grad(out, [A, Bm], go)
+            ga_, gb_ = R.matmul_gradients(A.detach(), Bm.detach(), go, ta, tb)
+            assert torch.allclose(ga_, ra) and torch.allclose(gb_, rb)
+    A = (torch.randn(4, 4, dtype=torch.float64) + 4 * torch.eye(4, dtype=torch.float64)).requires_grad_(True)
+    Bm = torch.randn(4, 2, dtype=torch.float64, requires_grad=True)
+    X = torch.linalg.solve(A, Bm)
+    go = torch.randn_like(X)
+    ra, rb = torch.autograd.grad(X, [A, Bm], go)
+    ga_, gb_ = R.solve_gradients(A.detach(), X.detach(), go)
+    assert torch.allclose(ga_, ra) and torch.allclose(gb_, rb)
