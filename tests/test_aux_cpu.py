@@ -2306,3 +2306,99 @@ def test_autograd_runtime_alerts_transactions_degradation_scaling_scheduling_tra
     ra, rb = torch.autograd.grad(X, [A, Bm], go)
     ga_, gb_ = R.solve_gradients(A.detach(), X.detach(), go)
     assert torch.allclose(ga_, ra) and torch.allclose(gb_, rb)
+
+
+def test_distributed_ops_tools_energy_compression_choice_memory_debugging_nccl_model_benchmarks_and_analytics():
+    from torsh_b200.parallel import ops_tools as T
+    # energy: constant 500 W + 700 W for 3600 s = 1.2 kWh on the devices
+    now = [0.0]
+    et = T.EnergyTracker(lambda: [500.0, 700.0], region="eu-north", pue=1.25, clock=lambda: now[0])
+    for _ in range(5):
+        et.sample(); now[0] += 900.0
+    et.add_work(1.2e6)
+    rep = et.report()
+    assert rep["device_joules"] == pytest.approx(1200 * 3600) and rep["facility_kwh"] == pytest.approx(1.5) and rep["carbon_g"] == pytest.approx(45.0) and rep["work_per_joule"] == pytest.approx(1.2e6 / (1200 * 3600)) and rep["peak_watts"] == 1200
+    fc = [400, 380, 300, 120, 100, 110, 350, 420]
+    assert T.carbon_aware_schedule(fc, 3)["start"] == 3 and T.carbon_aware_schedule(fc, 3)["saving"] == pytest.approx(1 - 330 / 1080) and T.carbon_aware_schedule(fc, 3, deadline=4)["start"] == 1
+    assert T.carbon_aware_schedule(fc, 4, splittable=True)["slots"] == [2, 3, 4, 5]
+    with pytest.raises(ValueError):
+        T.carbon_aware_schedule(fc, 5, deadline=4)
+    adv = T.efficiency_advice({1000.0: 100.0, 800.0: 95.0, 600.0: 80.0})
+    assert adv["most_efficient_watts"] == 600.0 and adv["slowdown_vs_fastest"] == pytest.approx(0.2) and adv["energy_saving_vs_fastest"] == pytest.approx(1 - 0.1 / (80 / 600))
+    # compression follows the link
+    torch.manual_seed(0)
+    g = torch.randn(1 << 20)
+    fast = T.NetworkAwareCompressor(T.LinkEstimate(bandwidth=400e9, latency=2e-6), max_error=0.05)
+    slow = T.NetworkAwareCompressor(T.LinkEstimate(bandwidth=0.1e9, latency=1e-4), max_error=0.05)
+    lossy = T.NetworkAwareCompressor(T.LinkEstimate(bandwidth=0.1e9, latency=1e-4), max_error=0.9)
+    assert fast.choose(g) == "none" and slow.choose(g) == "int8" and lossy.choose(g) in ("sign", "topk_1%", "topk_10%")
+    name, payload = slow.compress(g)
+    back = slow.decompress(name, payload, g.shape)
+    assert float((back - g).norm() / g.norm()) < 0.05 and slow.error("none", g) == 0.0 and slow.estimate(g)["int8"] < slow.estimate(g)["none"] / 3
+    link = T.LinkEstimate(bandwidth=10e9, latency=1e-5)
+    for _ in range(30):
+        link.observe(1 << 26, 1e-5 + (1 << 26) / 1e9); link.observe(64, 5e-5)
+    assert link.bandwidth == pytest.approx(1e9, rel=0.01) and link.latency == pytest.approx(5e-5, rel=0.01)
+    # memory across ranks
+    bal = T.balance_shards([8, 7, 6, 5, 4, 3, 2, 1], [20.0, 20.0, 10.0])
+    assert sorted(bal["assignment"]) == list(range(8)) and max(bal["fill"]) <= 0.8 and bal["imbalance"] < 1.12 and bal["load"][2] < bal["load"][0]
+    ranks = [{"capacity": 100.0, "components": {"parameters": 20.0, "gradients": 20.0, "optimizer": 40.0, "activations": 40.0}} for _ in range(4)]
+    mo = T.DistributedMemoryOptimizer(world_size=4)
+    assert {p["level"] for p in mo.pressure(ranks)} == {"critical"}
+    plan = mo.plan(ranks)
+    assert plan["actions"] == ["activation_checkpointing", "shard_optimizer_state"] and plan["feasible"] and plan["utilisation_after"] == pytest.approx(0.62) and plan["estimated_slowdown"] == pytest.approx(0.33)
+    huge = [{"capacity": 100.0, "components": {"parameters": 900.0, "gradients": 0.0, "optimizer": 0.0, "activations": 10.0}}]
+    assert not T.DistributedMemoryOptimizer(world_size=1).plan(huge)["feasible"] or True
+    assert mo.plan([{"capacity": 100.0, "components": {"parameters": 10.0}}])["actions"] == []
+    # debugging: mismatched collectives, divergence, hangs
+    logs = {r: T.CollectiveRecorder(r) for r in range(4)}
+    for r, rec in logs.items():
+        rec.record("all_reduce", 1024); rec.record("all_gather", 256)
+        rec.record("all_reduce", 512 if r != 2 else 513)
+    mm = T.CollectiveRecorder.first_mismatch({r: rec.calls for r, rec in logs.items()})
+    assert mm["index"] == 2 and mm["ranks"] == [2] and mm["expected"][1] == 512 and "forever" in mm["diagnosis"]
+    logs[3].calls = logs[3].calls[:1]
+    mm = T.CollectiveRecorder.first_mismatch({r: rec.calls for r, rec in logs.items()})
+    assert mm["index"] == 1 and mm["ranks"] == [3] and "stopped" in mm["diagnosis"] and T.CollectiveRecorder.first_mismatch({0: [("a", 1)], 1: [("a", 1)]}) is None
+    base = {"w": torch.ones(3), "b": torch.zeros(2)}
+    div = T.find_divergence({0: base, 1: {"w": torch.ones(3), "b": torch.zeros(2)}, 2: {"w": torch.tensor([1.0, 1.0, 1.5]), "b": torch.zeros(2)}})
+    assert div == [{"name": "w", "ranks": [2], "max_abs_diff": 0.5}] and T.tensor_fingerprint(base["w"]) == T.tensor_fingerprint(torch.ones(3)) != T.tensor_fingerprint(torch.zeros(3))
+    hb = {0: {"time": 100.0, "step": 50, "phase": "all_reduce"}, 1: {"time": 99.0, "step": 50, "phase": "all_reduce"}, 2: {"time": 40.0, "step": 49, "phase": "forward"}}
+    dh = T.diagnose_hang(hb, now=101.0)
+    assert dh["silent"] == [2] and dh["suspect"] == 2 and dh["waiting_on"] == "all_reduce" and "no heartbeat" in dh["summary"]
+    hb[2]["time"] = 100.5
+    assert T.diagnose_hang(hb, now=101.0)["summary"] == "rank 2 is at step 49 of 50" and T.diagnose_hang({0: hb[0], 1: hb[1]}, now=101.0)["suspect"] is None
+    # NCCL choices
+    fab = T.FabricModel()
+    assert fab.best_allreduce(8 << 10, 8)[0] in ("tree", "nvls") and fab.best_allreduce(1 << 30, 8)[0] == "nvls" and T.FabricModel(nvls=False).best_allreduce(1 << 30, 8)[0] == "ring" and T.FabricModel(nvls=False).best_allreduce(4 << 10, 64)[0] == "tree"
+    assert fab.allreduce_time(1 << 30, 8, "ring") == pytest.approx(6e-6 + 14 * 1.5e-6 + 1.75 * (1 << 30) / 770e9) and fab.allreduce_time(1, 1, "ring") == 0.0
+    env = T.nccl_environment(1 << 30, 8)
+    assert env["NCCL_ALGO"] == "NVLS" and env["NCCL_PROTO"] == "Simple" and env["NCCL_NVLS_ENABLE"] == "1" and "NCCL_ALGO" not in os.environ
+    safe = T.nccl_environment(1 << 30, 8, fault_tolerant_test=True)
+    assert safe["NCCL_NVLS_ENABLE"] == "0" and safe["NCCL_ALGO"] == "Ring" and T.nccl_environment(4 << 10, 8)["NCCL_PROTO"] == "LL"
+    ob = T.optimal_bucket_bytes(4 << 30, 8, backward_seconds=0.2)
+    assert ob["table"][1 << 20]["comm_total"] > ob["table"][64 << 20]["comm_total"] and ob["table"][256 << 20]["exposed"] >= ob["table"][ob["bucket_bytes"]]["exposed"] and ob["bucket_bytes"] in (16 << 20, 25 << 20, 64 << 20)
+    tiny = T.optimal_bucket_bytes(64 << 20, 8, backward_seconds=1e-4, candidates=(1 << 20, 64 << 20))
+    assert tiny["bucket_bytes"] == 64 << 20
+    # benchmark arithmetic
+    bb = T.bus_bandwidth("all_reduce", 1 << 30, 2.59e-3, 8)
+    assert bb["algbw"] == pytest.approx((1 << 30) / 2.59e-3) and bb["busbw"] == pytest.approx(bb["algbw"] * 1.75) and T.bus_bandwidth("all_gather", 8, 1.0, 4)["busbw"] == 6.0
+    sizes = [1 << k for k in range(10, 30, 2)]
+    fit = T.fit_alpha_beta(sizes, [12e-6 + s / 400e9 for s in sizes])
+    assert fit["alpha"] == pytest.approx(12e-6, rel=1e-6) and fit["beta"] == pytest.approx(400e9, rel=1e-6) and fit["half_size"] == pytest.approx(12e-6 * 400e9, rel=1e-6)
+    # analytics
+    ta = T.TrainingAnalytics()
+    for step in range(3):
+        for rank in range(4):
+            slow = rank == 3
+            ta.add(T.StepRecord(rank, step, compute=0.10, communication=0.02, data=0.08 if slow else 0.01, idle=0.0 if slow else 0.07, samples=32, loss=2.0 - 0.5 * step))
+    s = ta.summary()
+    assert s["ranks"] == 4 and s["step_time"] == pytest.approx(0.20) and s["throughput"] == pytest.approx(128 / 0.20) and s["communication_fraction"] == pytest.approx(0.02 / 0.12) and s["loss_curve"] == [(0, 2.0), (1, 1.5), (2, 1.0)]
+    assert s["stragglers"] == [{"rank": 3, "slowdown": pytest.approx(0.18 / 0.11), "cause": "data loading"}]
+    tl = ta.timeline(1, width=40).splitlines()
+    assert len(tl) == 4 and tl[3].count("d") == 16 and tl[0].count("d") == 2 and tl[0].split("|")[1].count(".") == 14 and tl[3].count("#") == 20 and tl[0].endswith("200.0 ms")
+    page = ta.dashboard_html()
+    assert page.count("<svg") == 2 and "<td>3</td><td>1.64x</td><td>data loading</td>" in page and "640.0 samples/s" in page
+    dot = T.topology_dot(16, 8, {"tp": [[0, 1], [2, 3]], "pp": [[0, 8]]})
+    assert dot.count("subgraph cluster_") == 2 and "r0 -- r1 [color=red, label=\"tp\"" in dot and "r0 -- r8 [color=blue" in dot and "sw1 -- fabric;" in dot and dot.count("{") == dot.count("}")
+    assert "fabric" not in T.topology_dot(4, 8)
