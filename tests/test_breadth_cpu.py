@@ -4685,3 +4685,236 @@ def test_tensor_ext_expressions_graph_comprehension_registries_shapes_views_and_
     assert tp.plan("pageable", "device", 1024)["path"] == ["pageable", "device"] or tp.plan("pageable", "device", 1024)["seconds"] < 2e-5
     with pytest.raises(ValueError):
         tp.plan("device", "pageable", 10)
+
+
+def test_domain_models_unet_pinn_fno_and_multiview_diffusion_parts():
+    from torsh_b200.models import domain as D
+    torch.manual_seed(0)
+    # U-Net with gates and deep supervision
+    net = D.UNet(in_channels=1, out_channels=2, base_features=4, num_levels=2, attention=True, deep_supervision=True)
+    x = torch.randn(2, 1, 16, 16)
+    out, aux = net(x)
+    assert out.shape == (2, 2, 16, 16) and len(aux) == 1 and aux[0].shape == out.shape and 0 <= float(net.gates[0].last_alpha.detach().min()) and float(net.gates[0].last_alpha.detach().max()) <= 1 and net.gates[1].last_alpha.shape == (2, 1, 16, 16)
+    net.eval()
+    assert net(x).shape == (2, 2, 16, 16)
+    with pytest.raises(ValueError):
+        net(torch.randn(1, 1, 10, 10))
+    net.train()
+    target = (x[:, 0] > 0).long()
+    opt = torch.optim.Adam(net.parameters(), lr=2e-2)
+    first = None
+    for _ in range(60):
+        o, a = net(x)
+        loss = D.UNet.deep_supervision_loss(o, a, target) + D.dice_loss(o, target)
+        first = first if first is not None else float(loss.detach())
+        opt.zero_grad(); loss.backward(); opt.step()
+    assert float(loss.detach()) < 0.5 * first and float((net(x)[0].argmax(1) == target).float().mean()) > 0.9
+    perfect = torch.nn.functional.one_hot(target, 2).movedim(-1, 1).float() * 50
+    assert float(D.dice_loss(perfect, target)) < 1e-4 and float(D.dice_loss(-perfect, target)) > 0.9
+    v3 = D.UNet3D(in_channels=2, out_channels=3, base_features=2, num_levels=2)
+    assert v3(torch.randn(1, 2, 8, 8, 8)).shape == (1, 3, 8, 8, 8)
+    # physics-informed network: u' = -u, u(0) = 1
+    pinn = D.PINN(input_dim=1, output_dim=1, hidden_dims=(16, 16), adaptive_weights=False, boundary_weight=10.0)
+    xs = torch.linspace(0, 1, 32)[:, None]
+    res = lambda m, p: D.PINN.derivative(m(p), p, 0) + m(p)
+    opt = torch.optim.Adam(pinn.parameters(), lr=1e-2)
+    for _ in range(600):
+        total, parts = pinn.compute_total_loss(pinn.physics_loss(xs, res), pinn.boundary_loss(torch.zeros(1, 1), torch.ones(1, 1)))
+        opt.zero_grad(); total.backward(); opt.step()
+    assert set(parts) == {"physics", "boundary"} and float((pinn(xs).detach() - torch.exp(-xs)).abs().max()) < 0.03
+    xg = torch.tensor([[0.3], [0.7]], requires_grad=True)
+    assert torch.allclose(D.PINN.derivative(xg ** 3, xg, 0, order=2), 6 * xg)
+    ad = D.PINN(input_dim=1, hidden_dims=(4,), adaptive_weights=True)
+    tot, _ = ad.compute_total_loss(torch.tensor(2.0), torch.tensor(3.0), torch.tensor(4.0))
+    assert float(tot.detach()) == 9.0 and ad.log_vars.requires_grad
+    tot.backward()
+    assert ad.log_vars.grad.tolist() == [-1.0, -2.0, -3.0]
+    # Fourier neural operator: learns the antiderivative of band-limited functions and transfers to a finer grid
+    def batch(n, res, gen):
+        xs = torch.linspace(0, 1, res + 1)[:-1]
+        k = torch.arange(1, 4)[None, :, None].float()
+        a, b = torch.randn(n, 3, 1, generator=gen), torch.randn(n, 3, 1, generator=gen)
+        f = (a * torch.sin(2 * math.pi * k * xs) + b * torch.cos(2 * math.pi * k * xs)).sum(1)
+        F_ = (-a / (2 * math.pi * k) * torch.cos(2 * math.pi * k * xs) + b / (2 * math.pi * k) * torch.sin(2 * math.pi * k * xs)).sum(1)
+        return f[..., None], F_[..., None]
+    gen = torch.Generator().manual_seed(0)
+    fno = D.FNO(input_dim=1, output_dim=1, num_layers=2, hidden_dim=32, modes=(6,), width=16)
+    opt = torch.optim.Adam(fno.parameters(), lr=5e-3)
+    for _ in range(300):
+        f, Fx = batch(32, 32, gen)
+        loss = torch.nn.functional.mse_loss(fno(f), Fx)
+        opt.zero_grad(); loss.backward(); opt.step()
+    with torch.no_grad():
+        f, Fx = batch(64, 32, gen); e32 = float((fno(f) - Fx).norm() / Fx.norm())
+        f, Fx = batch(64, 128, gen); e128 = float((fno(f) - Fx).norm() / Fx.norm())
+    assert e32 < 0.15 and e128 < 0.2
+    f2 = D.FNO(input_dim=2, output_dim=1, num_layers=2, hidden_dim=8, modes=(3, 3), width=4)
+    assert f2(torch.randn(2, 12, 10, 2)).shape == (2, 12, 10, 1) and f2(torch.randn(1, 20, 16, 2)).shape == (1, 20, 16, 1)
+    # guidance
+    c, u = torch.ones(2, 4, 8, 8), torch.zeros(2, 4, 8, 8)
+    assert torch.equal(D.apply_classifier_free_guidance(c, u, 2.0), 2 * c) and torch.equal(D.apply_classifier_free_guidance(c, u, 1.0), c) and torch.equal(D.apply_classifier_free_guidance(c, c * 3, 0.0), c * 3)
+    with pytest.raises(ValueError):
+        D.apply_classifier_free_guidance(c, u[:1], 2.0)
+    both = D.prepare_cfg_batch(c, u)
+    uu, cc = D.split_cfg_batch(both, 2)
+    assert both.shape[0] == 4 and torch.equal(uu, u) and torch.equal(cc, c)
+    with pytest.raises(ValueError):
+        D.split_cfg_batch(both, 3)
+    assert D.guidance_scale_with_warmup(5, 50, 15.0, 10) == 8.0 and D.guidance_scale_with_warmup(10, 50, 15.0, 10) == 15.0 and D.guidance_scale_with_warmup(0, 50, 15.0) == 1.0 and D.guidance_scale_with_warmup(5, 50, 7.5) == 7.5
+    cond = torch.randn(2, 4, 8, 8)
+    guided = D.apply_classifier_free_guidance(cond, torch.randn(2, 4, 8, 8), 12.0)
+    resc = D.rescale_guidance(guided, cond, phi=1.0)
+    assert torch.allclose(resc.std((1, 2, 3)), cond.std((1, 2, 3)), rtol=1e-4) and guided.std() > 3 * cond.std()
+    # conditioning modules
+    cam = D.CameraEmbedding(embed_dim=32, hidden_dims=(16,))
+    params = D.CameraEmbedding.pack(500.0, 500.0, 128.0, 128.0, torch.eye(3).expand(6, 3, 3), torch.zeros(6, 3))
+    assert params.shape == (6, 16) and params[0, :4].tolist() == [500.0, 500.0, 128.0, 128.0] and cam(params).shape == (6, 32)
+    with pytest.raises(ValueError):
+        cam(torch.zeros(2, 12))
+    cfg = D.IPAdapterProjectionConfig.sd15_vit_l()
+    assert (cfg.num_tokens, cfg.cross_attn_dim, cfg.clip_feature_dim, cfg.hidden_dim) == (16, 768, 1024, 2048) and D.IPAdapterProjectionConfig.sdxl_vit_g().cross_attn_dim == 2048
+    ip = D.IPAdapterProjection(num_tokens=4, cross_attn_dim=8, clip_feature_dim=12, hidden_dim=16)
+    tok = ip(torch.randn(3, 12))
+    assert tok.shape == (3, 4, 8) and ip.num_parameters() == 12 * 16 + 16 + 16 * 32 + 32 + 16 and torch.allclose(tok.mean(-1), torch.zeros(3, 4), atol=1e-5)
+    with pytest.raises(ValueError):
+        D.IPAdapterProjection(num_tokens=0)
+    lu = D.LatentUpsampler(channels=4, timestep_dim=16, base_dim=8)
+    lat = torch.randn(2, 4, 6, 6)
+    up = lu(lat, torch.tensor([10, 500]))
+    assert up.shape == (2, 4, 12, 12) and torch.allclose(up, torch.nn.functional.interpolate(lat, scale_factor=2.0, mode="bilinear", align_corners=False))
+    up.sum().backward()
+    assert lu.out.weight.grad.abs().sum() > 0
+    cva = D.CrossViewAttention(num_heads=2, channels=8)
+    feats = torch.randn(4, 8, 3, 3)                                              # 2 samples x 2 views
+    assert torch.equal(cva(feats, 2), feats)
+    torch.nn.init.normal_(cva.proj.weight, std=0.5)
+    base = cva(feats, 2)
+    moved = feats.clone(); moved[1] = torch.randn(8, 3, 3)                          # change view 1 of sample 0
+    out2 = cva(moved, 2)
+    assert not torch.allclose(out2[0], base[0]) and torch.allclose(out2[2:], base[2:], atol=1e-6)
+    single = cva(moved, 1)
+    assert torch.allclose(single[0], cva(feats, 1)[0], atol=1e-6)
+    with pytest.raises(ValueError):
+        cva(feats[:3], 2)
+    mv = D.MultiviewUNet(in_channels=4, num_heads=2, base_dim=8, timestep_dim=16, camera_embed_dim=16)
+    xin = torch.randn(4, 4, 8, 8)
+    eps = mv(xin, torch.tensor([5, 5, 90, 90]), params[:4], num_views=2)
+    assert eps.shape == xin.shape
+    eps.pow(2).mean().backward()
+    assert all(p.grad is not None for n, p in mv.named_parameters() if "attn" not in n or "proj" in n)
+    other_cam = params[:4].clone(); other_cam[:, 13:] = 1.0
+    assert not torch.allclose(mv(xin, torch.tensor([5, 5, 90, 90]), other_cam, 2), eps)
+
+
+def test_model_tooling_factory_lazy_loading_validation_comparison_and_benchmark(tmp_path):
+    from safetensors.torch import load_file, save_file
+    from scipy import stats as sst
+    from sklearn.metrics import precision_recall_fscore_support
+    from torsh_b200.models import tooling as T
+    torch.manual_seed(0)
+    # configs and factory
+    fac = T.ModelFactory()
+    assert "vit_base" in fac.list_all_models()["vision"] and "bert_large" in fac.list_all_models()["nlp"]
+    info = fac.get_model_info("nlp", "gpt2")
+    assert 120e6 < info["parameters"] < 130e6 and info["architecture"] == "gpt" and fac.get_model_info("vision", "nope") is None
+    assert 85e6 < fac.get_model_info("vision", "vit_base")["parameters"] < 88e6
+    small = fac.build_vision_model("resnet18", num_classes=5, widths=(4, 8, 8, 8), depths=(1, 1, 1, 1))
+    assert small(torch.randn(2, 3, 16, 16)).shape == (2, 5)
+    vit = fac.build_vision_model("vit_tiny", image_size=16, patch_size=8, embed_dim=16, num_heads=2, depths=(1,), num_classes=3)
+    assert vit(torch.randn(2, 3, 16, 16)).shape == (2, 3)
+    fac.add_config("nlp", "nano", T.NlpModelConfig("gpt", vocab_size=50, max_position=16, hidden=8, layers=1, heads=2, dropout=0.0))
+    gpt = fac.build_nlp_model("nano").eval()
+    ids = torch.randint(0, 50, (2, 6))
+    lg = gpt(ids)
+    ids2 = ids.clone(); ids2[:, -1] = (ids2[:, -1] + 1) % 50
+    assert lg.shape == (2, 6, 50) and torch.allclose(gpt(ids2)[:, :-1], lg[:, :-1], atol=1e-5) and gpt.head.weight is gpt.tok.weight
+    assert fac.build_nlp_model("nano", architecture="bert", num_labels=4)(ids).shape == (2, 4)
+    with pytest.raises(ValueError):
+        T.NlpModelConfig(hidden=10, heads=3).validate()
+    with pytest.raises(ValueError):
+        T.VisionModelConfig("vit", image_size=30, patch_size=16).validate()
+    assert T.compare_configs(T.NLP_PRESETS["gpt2"], T.NLP_PRESETS["gpt2_medium"]) == {"heads": (12, 16), "hidden": (768, 1024), "layers": (12, 24)}
+    # safetensors both ways with the reference package, lazy cache, streaming
+    tensors = {"a.weight": torch.randn(8, 4), "a.bias": torch.randn(8).to(torch.bfloat16), "idx": torch.arange(5), "flag": torch.tensor([True, False]), "half": torch.randn(3, 3).half()}
+    T.write_safetensors(tensors, tmp_path / "m.safetensors", {"format": "pt"})
+    theirs = load_file(str(tmp_path / "m.safetensors"))
+    assert all(torch.equal(theirs[k], v) and theirs[k].dtype == v.dtype for k, v in tensors.items())
+    save_file(tensors, str(tmp_path / "theirs.safetensors"))
+    with T.LazyModelLoader(tmp_path / "theirs.safetensors", max_cache_bytes=8 * 4 * 4 + 16) as ld:
+        assert ld.tensor_names() == sorted(tensors) and ld.tensor_metadata("a.bias") == ((8,), torch.bfloat16) and ld.tensor_metadata("zzz") is None and not ld.is_cached("a.weight")
+        assert torch.equal(ld.get_tensor("a.weight"), tensors["a.weight"]) and ld.is_cached("a.weight") and torch.equal(ld.get_tensor("a.weight"), tensors["a.weight"])
+        assert ld.cache_stats().hits == 1 and ld.cache_stats().misses == 1 and ld.cache_stats().hit_rate() == 0.5
+        assert torch.equal(ld.get_tensor("a.bias"), tensors["a.bias"]) and torch.equal(ld.get_tensor("idx"), tensors["idx"])
+        assert ld.cache_stats().evictions >= 1 and not ld.is_cached("a.weight") and ld.cache_stats().bytes_cached <= ld.cache_stats().capacity and 0 < ld.cache_stats().utilization() <= 1
+        seen = {}
+        ld.stream_tensors(lambda n, t: seen.__setitem__(n, t))
+        assert set(seen) == set(tensors) and torch.equal(seen["half"], tensors["half"]) and torch.equal(seen["flag"], tensors["flag"])
+        chunks = list(ld.stream_tensor_chunks("a.weight", 48))
+        assert [c.numel() for c in chunks] == [12, 12, 8] and torch.equal(torch.cat(chunks).reshape(8, 4), tensors["a.weight"])
+        with pytest.raises(KeyError):
+            ld.get_tensor("missing")
+        ld.clear_cache()
+        assert ld.cache_stats().bytes_cached == 0
+    lin = torch.nn.Linear(4, 8)
+    T.write_safetensors({"weight": tensors["a.weight"], "bias": torch.zeros(8)}, tmp_path / "lin.safetensors")
+    with T.LazyModelLoader(tmp_path / "lin.safetensors") as ld:
+        assert ld.load_into(lin) == {"missing": [], "unexpected": []} and torch.equal(lin.weight, tensors["a.weight"]) and ld.metadata == {}
+        with pytest.raises(KeyError):
+            ld.load_into(torch.nn.Linear(4, 8, bias=False))
+        assert ld.load_into(torch.nn.Linear(4, 8, bias=False), strict=False)["unexpected"] == ["bias"]
+    # confusion matrix against scikit-learn
+    y = torch.randint(0, 4, (300,)); pred = torch.where(torch.rand(300) < 0.7, y, torch.randint(0, 4, (300,)))
+    cm = T.ConfusionMatrix(4).update(pred[:150], y[:150]).update(pred[150:], y[150:])
+    p, r, f, s = precision_recall_fscore_support(y.numpy(), pred.numpy(), average=None)
+    for i, c in enumerate(cm.class_metrics()):
+        assert c["precision"] == pytest.approx(p[i]) and c["recall"] == pytest.approx(r[i]) and c["f1"] == pytest.approx(f[i]) and c["support"] == s[i]
+    for avg in ("macro", "weighted"):
+        pp, rr, ff, _ = precision_recall_fscore_support(y.numpy(), pred.numpy(), average=avg)
+        sm = cm.summary(avg)
+        assert sm["precision"] == pytest.approx(pp) and sm["recall"] == pytest.approx(rr) and sm["f1"] == pytest.approx(ff)
+    assert cm.summary("micro")["f1"] == pytest.approx(float((pred == y).float().mean()))
+    # splits
+    labels = torch.tensor([0] * 40 + [1] * 10)
+    folds = T.make_splits(50, "stratified", k=5, labels=labels)
+    assert len(folds) == 5 and all(int((labels[te] == 1).sum()) == 2 and len(te) == 10 and not set(tr.tolist()) & set(te.tolist()) for tr, te in folds) and sorted(torch.cat([te for _, te in folds]).tolist()) == list(range(50))
+    assert len(T.make_splits(20, "kfold", k=4, repeats=2)) == 8 and [len(te) for _, te in T.make_splits(10, "leave_one_out")] == [1] * 10
+    ts = T.make_splits(60, "time_series", k=5)
+    assert all(int(tr.max()) < int(te.min()) for tr, te in ts) and len(ts[0][0]) == 10 and len(ts[4][0]) == 50
+    btr, bte = T.make_splits(100, "bootstrap", k=3)[0]
+    assert len(btr) == 100 and not set(btr.tolist()) & set(bte.tolist()) and 25 < len(bte) < 50
+    htr, hte = T.make_splits(100, "holdout", test_fraction=0.25)[0]
+    assert len(htr) == 75 and len(hte) == 25
+    # validator on a separable problem, and a regression
+    X = torch.randn(200, 5); W = torch.randn(5, 3); Y = (X @ W).argmax(1)
+    def fit(m, xs, ys, loss_fn=torch.nn.functional.cross_entropy):
+        opt = torch.optim.Adam(m.parameters(), lr=0.05)
+        for _ in range(80):
+            opt.zero_grad(); loss_fn(m(xs), ys).backward(); opt.step()
+    res = T.ModelValidator("stratified", k=4).validate(lambda: torch.nn.Linear(5, 3), fit, X, Y)
+    assert len(res["splits"]) == 4 and res["summary"]["accuracy"]["mean"] > 0.9 and res["summary"]["accuracy"]["ci95"][0] <= res["summary"]["accuracy"]["mean"] <= res["summary"]["accuracy"]["ci95"][1] and 48 <= res["splits"][0]["test_size"] <= 52
+    yr = X @ torch.randn(5) + 0.01 * torch.randn(200)
+    reg = T.ModelValidator("kfold", k=3, task="regression").validate(lambda: torch.nn.Linear(5, 1), lambda m, a, b: fit(m, a, b, lambda o, t: torch.nn.functional.mse_loss(o.squeeze(-1), t)), X, yr)
+    assert reg["summary"]["r2"]["mean"] > 0.98 and reg["summary"]["mae"]["mean"] < 0.2
+    assert T.tensors_close(torch.ones(4), torch.ones(4) + 1e-9) and not T.tensors_close(torch.ones(4), torch.ones(5)) and T.tensors_close(torch.tensor([1.0, 2.0, 3.0, 9.0]), torch.tensor([1.0, 2.0, 3.0, 4.0]), max_mismatch_fraction=0.25)
+    half = torch.nn.Linear(5, 3); ref = lambda t: torch.nn.functional.linear(t.double(), half.weight.double(), half.bias.double())
+    assert T.validate_model_correctness(half, ref, [X[:4], X[4:8]], rtol=1e-4, atol=1e-5)["passed"] and not T.validate_model_correctness(half, lambda t: ref(t) + 0.1, [X[:4]])["passed"]
+    # ANOVA and comparison
+    g = [[0.90, 0.91, 0.92, 0.93, 0.90], [0.85, 0.86, 0.84, 0.87, 0.85], [0.905, 0.915, 0.92, 0.925, 0.91]]
+    an = T.one_way_anova(g)
+    ref_an = sst.f_oneway(*g)
+    assert an["f"] == pytest.approx(ref_an.statistic) and an["p"] == pytest.approx(ref_an.pvalue) and (an["df_between"], an["df_within"]) == (2, 12)
+    cmpr = T.ModelComparator().add("big", g[0], latency_ms=20.0, size_mb=400.0).add("small", g[1], latency_ms=5.0, size_mb=50.0).add("mid", g[2], latency_ms=12.0, size_mb=200.0).add("bad", [0.80, 0.81, 0.79, 0.80, 0.82], latency_ms=25.0, size_mb=500.0)
+    out = cmpr.compare()
+    assert out["rankings"]["quality"][0] in ("big", "mid") and out["rankings"]["latency"][0] == "small" and out["overall"][-1] == "bad" and set(out["pareto"]) == {"small", "mid"} or set(out["pareto"]) == {"small", "mid", "big"}
+    pw = {(p["a"], p["b"]): p for p in out["pairwise"]}
+    assert pw[("big", "small")]["significant"] and pw[("big", "small")]["preferred"] == "big" and not pw[("big", "mid")]["significant"] and pw[("big", "mid")]["preferred"] == "no clear preference"
+    assert all(p["p_adjusted"] >= p["p"] for p in out["pairwise"]) and out["anova"]["p"] < 1e-6
+    csv_text = cmpr.export_csv(out)
+    assert csv_text.splitlines()[0] == "model,quality,latency_ms,size_mb,score,pareto" and len(csv_text.splitlines()) == 5 and "<td>bad</td>" in cmpr.html_report(out) and "ANOVA: F =" in cmpr.html_report(out)
+    # benchmark and recommendations
+    b = T.benchmark_model(torch.nn.Sequential(torch.nn.Linear(64, 64), torch.nn.ReLU(), torch.nn.Linear(64, 8)), torch.randn(1, 64), warmup=1, iterations=5, batch_sizes=(1, 16))
+    assert b["parameters"] == 64 * 64 + 64 + 64 * 8 + 8 and set(b["latency"]) == {1, 16} and b["latency"][16]["p99_ms"] >= b["latency"][16]["p50_ms"] > 0
+    fake = {"size_mb": 400.0, "latency": {1: {"p50_ms": 30.0, "throughput": 33.0}, 8: {"p50_ms": 220.0, "throughput": 36.0}}}
+    recs = T.optimization_recommendations(fake, {"size_mb": 120.0, "latency_ms": 10.0, "throughput": 100.0})
+    assert [r["priority"] for r in recs] == ["high", "high", "medium", "low"] and "int8" in recs[0]["action"] and "CUDA graph" in recs[1]["action"]
+    assert T.optimization_recommendations(fake, {"size_mb": 1000.0}) == [recs[-1]]
