@@ -4918,3 +4918,108 @@ def test_model_tooling_factory_lazy_loading_validation_comparison_and_benchmark(
     recs = T.optimization_recommendations(fake, {"size_mb": 120.0, "latency_ms": 10.0, "throughput": 100.0})
     assert [r["priority"] for r in recs] == ["high", "high", "medium", "low"] and "int8" in recs[0]["action"] and "CUDA graph" in recs[1]["action"]
     assert T.optimization_recommendations(fake, {"size_mb": 1000.0}) == [recs[-1]]
+
+
+def test_nn_structure_lookup_activations_combinators_views_parameters_conventions_profiling_threads_harness_and_diagnostics():
+    from collections import OrderedDict
+    from torsh_b200.nn import structure as S
+    torch.manual_seed(0)
+    # table-driven activations
+    for make, fn, bound in ((S.LookupActivation.gelu, torch.nn.functional.gelu, 5e-5), (S.LookupActivation.sigmoid, torch.sigmoid, 4e-4), (S.LookupActivation.tanh, torch.tanh, 1e-4), (S.LookupActivation.silu, torch.nn.functional.silu, 3e-3)):
+        lut = make()
+        assert lut.max_error() < bound, (fn.__name__, lut.max_error())
+    coarse, fine = S.LookupActivation.gelu(size=64), S.LookupActivation.gelu(size=4096)
+    assert coarse.max_error() > 10 * fine.max_error()
+    xg = torch.linspace(-3, 3, 50, requires_grad=True)
+    gl, = torch.autograd.grad(S.LookupActivation.gelu()(xg).sum(), xg); gx, = torch.autograd.grad(torch.nn.functional.gelu(xg).sum(), xg)
+    assert torch.allclose(gl, gx, atol=2e-2) and S.LookupActivation.gelu()(torch.tensor([100.0, -100.0])).tolist() == [100.0, 0.0] and S.LookupActivation.gelu()(torch.randn(4).bfloat16()).dtype == torch.bfloat16
+    # combinators
+    x = torch.randn(3, 8)
+    lin = torch.nn.Linear(8, 8)
+    assert torch.allclose(S.Residual(lin, scale=0.5)(x), x + 0.5 * lin(x)) and S.Residual(torch.nn.Linear(8, 4), torch.nn.Linear(8, 4))(x).shape == (3, 4)
+    a, b = torch.nn.Linear(8, 2), torch.nn.Linear(8, 3)
+    assert S.Parallel(a, b)(x).shape == (3, 5) and torch.allclose(S.Parallel(a, a, merge="mean")(x), a(x)) and S.Parallel(a, a, merge="stack", dim=0)(x).shape == (2, 3, 2) and len(S.Parallel(a, b, merge="tuple")(x)) == 2
+    rep, shared = S.Repeat(lambda i: torch.nn.Linear(8, 8), 3), S.Repeat(lambda i: torch.nn.Linear(8, 8), 3, share=True)
+    assert len(list(rep.parameters())) == 6 and len(list(shared.parameters())) == 2 and torch.allclose(shared(x), shared.blocks[0](shared.blocks[0](shared.blocks[0](x))))
+    cond = S.Conditional(lambda t: "long" if t.shape[0] > 4 else "short", {"long": torch.nn.Linear(8, 1), "short": torch.nn.Linear(8, 2)})
+    assert cond(x).shape == (3, 2) and cond(torch.randn(6, 8)).shape == (6, 1) and "double" in repr(S.Lambda(lambda t: t * 2, "double")) and torch.equal(S.Lambda(lambda t: t * 2)(x), x * 2)
+    net = S.SequentialBuilder(8).linear(16).gelu().layer_norm().residual(lambda bld: bld.linear(32).relu().linear(16)).dropout(0.1).linear(4).build()
+    assert net(x).shape == (3, 4) and isinstance(net[3], S.Residual) and len(net) == 6
+    with pytest.raises(ValueError, match="keep the feature size"):
+        S.SequentialBuilder(8).residual(lambda bld: bld.linear(4))
+    # views
+    tree = S.model_tree(net, x)
+    assert tree.splitlines()[0].startswith("Sequential (") and "├─ 0: Linear [3, 16] [144]" in tree and "│  ├─ body: Sequential [3, 16]" in tree and "└─ 5: Linear [3, 4] [68]" in tree
+    assert len(S.model_tree(net, max_depth=1).splitlines()) == 7
+    table = S.layer_table(net, x)
+    total = sum(p.numel() for p in net.parameters())
+    assert table.splitlines()[0].startswith("layer") and f"{total:,}" in table.splitlines()[-1] and "3.body.0" in table and "Dropout" in table
+    dot = S.model_to_dot(net, x)
+    assert dot.startswith("digraph model {") and "Linear" in dot and "[3, 4]" in dot and dot.count("->") >= 7 and "add" in dot
+    class Branchy(torch.nn.Module):
+        def __init__(self): super().__init__(); self.a, self.b = torch.nn.Linear(8, 8), torch.nn.Linear(8, 8)
+        def forward(self, t): return self.a(t) if t.sum() > 0 else self.b(self.a(t))
+    assert "input ->" in S.model_to_dot(Branchy(), x)
+    # parameter management
+    model = torch.nn.Sequential(OrderedDict(embed=torch.nn.Embedding(10, 8), body=torch.nn.Linear(8, 8), head=torch.nn.Linear(8, 10, bias=False)))
+    pm = S.ParameterManager(model).group("no_decay", "*.bias", "embed.*", weight_decay=0.0).group("head", "head.*", lr=1e-2)
+    groups = pm.optimizer_groups(lr=1e-3, weight_decay=0.1)
+    assert [g["name"] for g in groups] == ["no_decay", "head", "default"] and groups[0]["weight_decay"] == 0.0 and groups[1]["lr"] == 1e-2 and groups[2]["lr"] == 1e-3 and len(groups[0]["params"]) == 2
+    opt = torch.optim.AdamW([{k: v for k, v in g.items() if k != "name"} for g in groups])
+    assert len(opt.param_groups) == 3 and sum(len(g["params"]) for g in opt.param_groups) == 4
+    assert pm.freeze("embed.*", "body.*") == 3 and pm.statistics()["frozen"] == 80 + 64 + 8 and [g["name"] for g in pm.optimizer_groups()] == ["head"] and pm.unfreeze("body.*") == 2
+    pm.constrain("non_negative", "body.bias").constrain("max_norm", "head.weight", value=0.5).constrain("clip", "body.weight", value=0.1)
+    pm.apply_constraints()
+    assert float(model.body.bias.detach().min()) >= 0 and float(model.head.weight.detach().norm(dim=1).max()) <= 0.5 + 1e-6 and float(model.body.weight.detach().abs().max()) <= 0.1 + 1e-6
+    S.ParameterManager(model).constrain("unit_norm", "head.weight").apply_constraints()
+    assert torch.allclose(model.head.weight.norm(dim=1), torch.ones(10), atol=1e-5)
+    tied = torch.nn.Sequential(OrderedDict(embed=torch.nn.Embedding(10, 8), head=torch.nn.Linear(8, 10, bias=False)))
+    S.ParameterManager(tied).tie("embed.weight", "head.weight")
+    assert tied.head.weight is tied.embed.weight and len(list(tied.parameters())) == 1
+    with pytest.raises(ValueError):
+        S.ParameterManager(model).tie("embed.weight", "body.weight")
+    st = pm.statistics()
+    assert st["total"] == 80 + 64 + 8 + 80 and st["parameters"]["head.weight"]["shape"] == (10, 8) and st["parameters"]["body.bias"]["grad_norm"] is None
+    # conventions
+    @S.validated(p="probability", k="positive", mode=("choice", ["a", "b"]), t=("ndim", 2), u="floating")
+    def op(t, u, p=0.5, k=1, mode="a"): return t
+    assert op(x, x) is x
+    for bad, msg in ((dict(p=1.5), "'p' must be in"), (dict(k=0), "'k' must be positive"), (dict(mode="c"), "one of"),):
+        with pytest.raises(ValueError, match=msg):
+            op(x, x, **bad)
+    with pytest.raises(ValueError, match="op: argument 't' must have 2 dimensions"):
+        op(x[0], x)
+    with pytest.raises(ValueError, match="floating"):
+        op(x, torch.ones(2, dtype=torch.long))
+    v, w = torch.tensor([1.0, 2.0, 3.0]), torch.tensor([1.0, 0.0, 1.0])
+    assert float(S.apply_reduction(v, "mean")) == 2.0 and float(S.apply_reduction(v, "sum", w)) == 4.0 and float(S.apply_reduction(v, "mean", w)) == 2.0 and S.apply_reduction(v, "none", w).tolist() == [1.0, 0.0, 3.0]
+    with pytest.raises(ValueError):
+        S.apply_reduction(v, "avg")
+    # profiling and comparison
+    A, B = torch.randn(64, 64), torch.randn(64, 64)
+    pr = S.profile_function(torch.matmul, A, B, iterations=5, flops=2 * 64 ** 3)
+    assert pr["median_s"] > 0 and pr["input_bytes"] == 2 * 64 * 64 * 4 and pr["output_bytes"] == 64 * 64 * 4 and pr["gflops"] > 0
+    cmp = S.compare_implementations({"matmul": torch.matmul, "einsum": lambda p, q: torch.einsum("ij,jk->ik", p, q), "wrong": lambda p, q: p @ q + 1}, A, B, iterations=3)
+    assert cmp["rows"]["einsum"]["matches"] and not cmp["rows"]["wrong"]["matches"] and cmp["fastest"] in ("matmul", "einsum") and cmp["rows"]["matmul"]["speedup"] == 1.0
+    # threads
+    big = torch.randn(8192, 16)
+    assert torch.equal(S.parallel_chunks(torch.tanh, big, threads=4), torch.tanh(big)) and torch.equal(S.parallel_chunks(torch.tanh, big[:100], threads=4), torch.tanh(big[:100]))
+    assert torch.allclose(S.parallel_reduce(lambda p: p.sum(0), torch.add, big.double(), threads=4), big.double().sum(0))
+    # harness
+    rep_ok = S.check_against_reference(torch.nn.functional.gelu, lambda t: 0.5 * t * (1 + torch.erf(t / math.sqrt(2))), lambda dt, g: [torch.randn(32, generator=g)], check_grad=True)
+    assert rep_ok["passed"] and rep_ok["float64"]["max_abs_error"] < 1e-12 and rep_ok["bfloat16"]["max_abs_error"] > rep_ok["float32"]["max_abs_error"] and "max_grad_error" in rep_ok["float32"]
+    rep_bad = S.check_against_reference(lambda t: torch.nn.functional.gelu(t, approximate="tanh"), lambda t: 0.5 * t * (1 + torch.erf(t / math.sqrt(2))), lambda dt, g: [torch.randn(64, generator=g) * 2], dtypes=(torch.float64, torch.bfloat16))
+    assert not rep_bad["float64"]["passed"] and rep_bad["bfloat16"]["passed"] and not rep_bad["passed"]
+    xs = torch.randn(4, 6)
+    assert S.check_properties(torch.relu, xs, ["idempotent", "monotone", "positive_homogeneous", "non_negative", "odd", "linear"]) == {"idempotent": True, "monotone": True, "positive_homogeneous": True, "non_negative": True, "odd": False, "linear": False}
+    assert S.check_properties(lambda t: t.softmax(-1), xs, ["shift_invariant", "permutation_equivariant", "bounded01", "sums_to_one", "idempotent"]) == {"shift_invariant": True, "permutation_equivariant": True, "bounded01": True, "sums_to_one": True, "idempotent": False}
+    assert S.check_properties(torch.tanh, xs, ["odd", "even", "monotone"]) == {"odd": True, "even": False, "monotone": True} and S.check_properties(lambda t: t * 3, xs, ["linear"])["linear"] and S.check_properties(torch.abs, xs, ["even"])["even"]
+    # diagnostics
+    healthy = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Tanh(), torch.nn.Linear(16, 4))
+    assert S.diagnose_module(healthy, torch.randn(32, 8))["healthy"]
+    sick = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 16), torch.nn.Sigmoid(), torch.nn.Linear(16, 4))
+    with torch.no_grad():
+        sick[0].bias.fill_(-100.0); sick[2].bias.fill_(50.0)
+    d = S.diagnose_module(sick, torch.randn(32, 8))
+    kinds = {i["kind"] for i in d["issues"]}
+    assert {"dead_units", "saturated", "no_gradient"} <= kinds and not d["healthy"] and [i for i in d["issues"] if i["kind"] == "dead_units"][0]["layer"] == "1"
