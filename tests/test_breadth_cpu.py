@@ -5023,3 +5023,102 @@ def test_nn_structure_lookup_activations_combinators_views_parameters_convention
     d = S.diagnose_module(sick, torch.randn(32, 8))
     kinds = {i["kind"] for i in d["issues"]}
     assert {"dead_units", "saturated", "no_gradient"} <= kinds and not d["healthy"] and [i for i in d["issues"] if i["kind"] == "dead_units"][0]["layer"] == "1"
+
+
+def test_special_ext_bessel_struve_coulomb_elliptic_faddeeva_integrals_zeta_mathieu_spheroidal_harmonics_tables_and_reports():
+    import mpmath
+    import numpy as np
+    import scipy.special as sp
+    from torsh_b200 import special_ext as E
+    close = lambda a, b, rtol=1e-9, atol=1e-12: np.allclose(np.asarray(a), np.asarray(b), rtol=rtol, atol=atol)
+    x = torch.tensor([0.05, 0.7, 2.5, 9.0, 31.0], dtype=torch.float64)
+    for n in (0, 1, 2, 5, 12, 30):
+        assert close(E.bessel_j(n, x), sp.jv(n, x.numpy()), 1e-11, 1e-15), n
+        assert close(E.bessel_i(n, x), sp.iv(n, x.numpy()), 1e-7, 1e-300), n
+    for n in (0, 1, 3, 8):
+        assert close(E.bessel_y(n, x), sp.yv(n, x.numpy()), 1e-11) and close(E.bessel_k(n, x), sp.kv(n, x.numpy()), 1e-7, 1e-300), n
+    assert close(E.bessel_j(3, -x), sp.jv(3, -x.numpy()), 1e-7) and close(E.bessel_j(-2, x), sp.jv(-2, x.numpy()), 1e-7) and float(E.bessel_j(4, torch.tensor(0.0))) == 0.0 and close(E.bessel_i(3, -x), sp.iv(3, -x.numpy()), 1e-7, 1e-300)
+    xs = torch.tensor([1e-5, 0.3, 2.0, 11.0, 40.0], dtype=torch.float64)
+    for n in (0, 1, 2, 6, 15):
+        assert close(E.spherical_jn(n, xs), sp.spherical_jn(n, xs.numpy()), 1e-6, 1e-300), n
+    for n in (0, 1, 4):
+        assert close(E.spherical_yn(n, xs[1:]), sp.spherical_yn(n, xs[1:].numpy()), 1e-8), n
+    # Struve, Lommel, Coulomb against scipy / mpmath
+    xm = torch.tensor([0.2, 1.5, 6.0, 15.0], dtype=torch.float64)
+    assert close(E.struve_h(0, xm), sp.struve(0, xm.numpy()), 1e-7) and close(E.struve_h(1, xm), sp.struve(1, xm.numpy()), 1e-7) and close(E.struve_h(0.5, xm), sp.struve(0.5, xm.numpy()), 1e-7)
+    for mu, nu in ((0.5, 0.3), (2.0, 0.0), (1.5, 1.0)):
+        assert close(E.lommel_s1(mu, nu, xm[:3]), [float(mpmath.lommels1(mu, nu, float(v))) for v in xm[:3]], 1e-8), (mu, nu)
+    z = torch.tensor(2.0, dtype=torch.float64, requires_grad=True)
+    s = E.lommel_s1(0.5, 0.3, z); d1, = torch.autograd.grad(s, z, create_graph=True); d2, = torch.autograd.grad(d1, z)
+    assert float((z * z * d2 + z * d1 + (z * z - 0.09) * s - z ** 1.5).detach().abs()) < 1e-9
+    rho = torch.tensor([0.3, 1.0, 4.0, 9.0], dtype=torch.float64)
+    for l, eta in ((0, 0.0), (0, 0.5), (1, 0.5), (2, -1.0), (3, 2.0)):
+        assert close(E.coulomb_f(l, eta, rho), [float(mpmath.coulombf(l, eta, float(r))) for r in rho], 1e-7, 1e-12), (l, eta)
+    assert close(E.coulomb_f(0, 0.0, rho), torch.sin(rho), 1e-10)
+    # Jacobi elliptic
+    u, m = torch.tensor([0.1, 0.8, 2.0, -1.3, 5.0], dtype=torch.float64), torch.tensor([0.0, 0.3, 0.7, 0.99, 1.0], dtype=torch.float64)
+    ours, theirs = E.ellipj(u, m), sp.ellipj(u.numpy(), m.numpy())
+    assert all(close(a, b, 1e-9, 1e-12) for a, b in zip(ours, theirs))
+    sn, cn, dn, _ = E.ellipj(torch.linspace(-3, 3, 50, dtype=torch.float64), 0.6)
+    assert close(sn ** 2 + cn ** 2, np.ones(50)) and close(dn ** 2 + 0.6 * sn ** 2, np.ones(50))
+    # Faddeeva and the error-function family
+    zs = torch.tensor([0.3 + 0.2j, -1.5 + 2.0j, 4.0 + 0.01j, 2.0 - 1.0j, -0.5 - 0.5j, 0.0 + 6.0j, 10.0 + 10.0j], dtype=torch.complex128)
+    assert close(E.wofz(zs), sp.wofz(zs.numpy()), 1e-10, 1e-13) and close(E.erf_complex(zs[:6]), sp.erf(zs[:6].numpy()), 1e-9, 1e-12)
+    xr = torch.tensor([-3.0, -0.5, 0.0, 0.8, 3.0, 12.0, 30.0, 200.0], dtype=torch.float64)
+    assert close(E.erfcx(xr), sp.erfcx(xr.numpy()), 1e-10) and close(E.erfi(xr[:5]), sp.erfi(xr[:5].numpy()), 1e-10, 1e-13) and close(E.dawsn(xr), sp.dawsn(xr.numpy()), 1e-9, 1e-13)
+    assert close(E.voigt_profile(xr[:5], 0.7, 0.4), sp.voigt_profile(xr[:5].numpy(), 0.7, 0.4), 1e-10)
+    S, C = E.fresnel(xr[:7]); Ss, Cs = sp.fresnel(xr[:7].numpy())
+    assert close(S, Ss, 1e-8, 1e-10) and close(C, Cs, 1e-8, 1e-10)
+    # sine / cosine integrals
+    xi = torch.tensor([0.01, 0.5, 3.0, 20.0, 90.0], dtype=torch.float64)
+    si, ci = E.sici(xi); sis, cis = sp.sici(xi.numpy())
+    assert close(si, sis, 1e-11) and close(ci, cis, 1e-9, 1e-12) and close(E.sici(-xi)[0], -sis, 1e-11)
+    # complex gamma, zeta, polylogarithm
+    zg = torch.tensor([0.5 + 0.0j, 3.2 + 1.5j, -1.5 + 0.7j, 0.1 - 4.0j, 20.0 + 5.0j], dtype=torch.complex128)
+    assert close(E.gamma_complex(zg), sp.gamma(zg.numpy()), 1e-10) and close(E.loggamma_complex(zg).real, sp.loggamma(zg.numpy()).real, 1e-10)
+    sv = torch.tensor([-5.0, -2.5, -1.0, 0.0, 0.5, 0.9, 2.0, 4.0, 15.5], dtype=torch.float64)
+    assert close(E.zeta(sv), [float(mpmath.zeta(float(v))) for v in sv], 1e-9, 1e-12) and float(E.zeta(torch.tensor(2.0))) == pytest.approx(math.pi ** 2 / 6) and float(E.zeta(torch.tensor(-1.0))) == pytest.approx(-1 / 12)
+    zp = torch.tensor([-0.9, -0.3, 0.2, 0.7], dtype=torch.float64)
+    assert close(E.polylog(2, zp), [float(mpmath.polylog(2, float(v))) for v in zp], 1e-10) and close(E.polylog(3.5, torch.tensor(1.0, dtype=torch.float64), terms=200000), float(mpmath.zeta(3.5)), 1e-5) and close(E.polylog(1, zp), -torch.log(1 - zp), 1e-10)
+    # Mathieu and spheroidal characteristic values
+    for mm in range(0, 6):
+        for q in (0.0, 0.5, 3.0, 12.0, 40.0):
+            assert E.mathieu_a(mm, q) == pytest.approx(sp.mathieu_a(mm, q), rel=1e-8, abs=1e-8), (mm, q)
+            if mm:
+                assert E.mathieu_b(mm, q) == pytest.approx(sp.mathieu_b(mm, q), rel=1e-8, abs=1e-8), (mm, q)
+    ang = torch.tensor([0.0, 0.4, 1.1, 2.5, 4.0], dtype=torch.float64)
+    for mm, q in ((0, 1.0), (1, 2.0), (2, 5.0), (3, 0.5)):
+        assert close(E.mathieu_cem(mm, q, ang), sp.mathieu_cem(mm, q, np.degrees(ang.numpy()))[0], 1e-7, 1e-9), (mm, q)
+    for mm, nn, c in ((0, 0, 1.0), (0, 2, 3.0), (1, 1, 2.0), (1, 4, 5.0), (2, 3, 0.5), (0, 1, 8.0)):
+        assert E.spheroidal_cv(mm, nn, c) == pytest.approx(sp.pro_cv(mm, nn, c), rel=1e-9), (mm, nn, c)
+        assert E.spheroidal_cv(mm, nn, c, oblate=True) == pytest.approx(sp.obl_cv(mm, nn, c), rel=1e-8, abs=1e-9), (mm, nn, c)
+    # polynomials and harmonics
+    xp = torch.linspace(-0.95, 0.95, 7, dtype=torch.float64)
+    assert close(E.jacobi(4, 0.5, 1.5, xp), sp.eval_jacobi(4, 0.5, 1.5, xp.numpy())) and close(E.jacobi(3, 0.0, 0.0, xp), sp.eval_legendre(3, xp.numpy())) and close(E.jacobi(0, 1.0, 2.0, xp), np.ones(7))
+    for mm, ll in ((0, 0), (0, 3), (1, 1), (2, 5), (4, 4)):
+        assert close(E.assoc_legendre(mm, ll, xp), sp.lpmv(mm, ll, xp.numpy()), 1e-10), (mm, ll)
+    th, ph = torch.tensor([0.3, 2.0, 5.5], dtype=torch.float64), torch.tensor([0.4, 1.6, 2.9], dtype=torch.float64)
+    harm = getattr(sp, "sph_harm_y", None)
+    for mm, ll in ((0, 0), (1, 2), (-1, 2), (3, 3), (-2, 4)):
+        ref = harm(ll, mm, ph.numpy(), th.numpy()) if harm else sp.sph_harm(mm, ll, th.numpy(), ph.numpy())
+        assert close(E.sph_harm(mm, ll, th, ph), ref, 1e-10, 1e-13), (mm, ll)
+    assert E.sinpi(torch.tensor([0.0, 0.5, 1.0, 1.5, 1e6, 0.25])).tolist() == pytest.approx([0, 1, 0, -1, 0, math.sqrt(0.5)]) and E.cospi(torch.tensor([0.0, 0.5, 1.0, 2.5, 1 / 3])).tolist() == pytest.approx([1, 0, -1, 0, 0.5])
+    assert float(E.sinc_pi(torch.tensor(0.0))) == 1.0 and float(E.sinc_pi(torch.tensor(0.5))) == pytest.approx(2 / math.pi) and float(E.haversine(torch.tensor(math.pi))) == pytest.approx(1.0) and float(E.gudermannian(torch.tensor(1.0))) == pytest.approx(2 * math.atan(math.tanh(0.5)))
+    assert E.EULER_GAMMA == pytest.approx(float(mpmath.euler)) and E.CATALAN == pytest.approx(float(mpmath.catalan)) and E.APERY == pytest.approx(float(mpmath.apery)) and E.GLAISHER == pytest.approx(float(mpmath.glaisher)) and E.OMEGA == pytest.approx(float(mpmath.lambertw(1)))
+    # domain handling, tables, caching, accuracy report
+    assert E.check_domain("f", torch.tensor([0.0, 0.5, 1.0]), 0.0, 1.0, open_hi=True).tolist() == [True, True, False]
+    with pytest.raises(E.SpecialFunctionError, match=r"ellipk: argument 1.5 outside the domain \[0, 1\)"):
+        E.check_domain("ellipk", torch.tensor([0.2, 1.5]), 0, 1, mode="raise", open_hi=True)
+    tab = E.TabulatedFunction(lambda t: E.bessel_j(0, t), 0.0, 20.0, points=2048)
+    xt = torch.rand(500, dtype=torch.float64) * 20
+    assert float((tab(xt) - E.bessel_j(0, xt)).abs().max()) < 1e-7 and close(tab(torch.tensor([25.0], dtype=torch.float64)), sp.j0(25.0))
+    cache, calls = E.SmartCache(capacity=2), []
+    def slow(t): calls.append(1); return E.bessel_j(7, t)
+    a1, a2 = cache(slow, xt), cache(slow, xt.clone())
+    assert a1 is a2 and len(calls) == 1 and cache.hit_rate() == 0.5
+    cache(slow, xt + 1); cache(slow, xt + 2); cache(slow, xt)
+    assert len(calls) == 4 and len(cache.store) == 2
+    rep = E.accuracy_report(lambda t: E.bessel_j(2, t), lambda t: torch.as_tensor(sp.jv(2, t.numpy())), 0.1, 30.0)
+    assert rep["max_abs"] < 1e-12 and len(rep["profile"]) == 10 and len(rep["chart"].splitlines()) == 10 and rep["max_ulp"] >= rep["median_ulp"] and 0.1 <= rep["argmax_abs"] <= 30.0
+    crude = E.accuracy_report(lambda t: t - t ** 3 / 6, torch.sin, 0.0, 2.0)
+    assert crude["argmax_abs"] == 2.0 and crude["profile"][-1] > crude["profile"][0] and crude["max_abs"] == pytest.approx(abs(2 - 8 / 6 - math.sin(2)))
