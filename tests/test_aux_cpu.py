@@ -2402,3 +2402,50 @@ def test_distributed_ops_tools_energy_compression_choice_memory_debugging_nccl_m
     dot = T.topology_dot(16, 8, {"tp": [[0, 1], [2, 3]], "pp": [[0, 8]]})
     assert dot.count("subgraph cluster_") == 2 and "r0 -- r1 [color=red, label=\"tp\"" in dot and "r0 -- r8 [color=blue" in dot and "sw1 -- fabric;" in dot and dot.count("{") == dot.count("}")
     assert "fabric" not in T.topology_dot(4, 8)
+
+
+def test_cli_model_prune_optimize_compress_extract_merge(tmp_path, capsys):
+    import gzip
+    from torsh_b200 import cli
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Conv2d(3, 4, 3, bias=False), torch.nn.BatchNorm2d(4), torch.nn.ReLU(), torch.nn.Flatten(), torch.nn.Linear(4 * 6 * 6, 5)).eval()
+    with torch.no_grad():
+        net[1].running_mean.uniform_(-1, 1); net[1].running_var.uniform_(0.5, 2); net[1].weight.uniform_(0.5, 1.5); net[1].bias.uniform_(-0.5, 0.5)
+    src = tmp_path / "net.pt"
+    torch.save(net.state_dict(), src)
+    run = lambda *argv: (cli.main(["--json", *argv]), json.loads(capsys.readouterr().out))
+    # optimize: conv-bn folding preserves the function
+    code, out = run("model", "optimize", str(src), "-o", str(tmp_path / "folded.pt"), "--fold", "0=1")
+    assert code == 0 and out["folded"] == ["0"] and out["dropped"] == []
+    sd = torch.load(tmp_path / "folded.pt")
+    assert set(sd) == {"0.weight", "0.bias", "4.weight", "4.bias"}
+    fused = torch.nn.Sequential(torch.nn.Conv2d(3, 4, 3), torch.nn.Identity(), torch.nn.ReLU(), torch.nn.Flatten(), torch.nn.Linear(144, 5)).eval()
+    fused.load_state_dict(sd)
+    x = torch.randn(2, 3, 8, 8)
+    assert torch.allclose(fused(x), net(x), atol=1e-5)
+    # prune: unstructured and structured
+    code, out = run("model", "prune", str(src), "-o", str(tmp_path / "pruned.pt"), "--sparsity", "0.75")
+    pr = torch.load(tmp_path / "pruned.pt")
+    assert out["sparsity"] == pytest.approx(0.75, abs=0.01) and float((pr["4.weight"] == 0).float().mean()) == pytest.approx(0.75, abs=0.01) and torch.equal(pr["4.bias"], net[4].bias.detach())
+    kept = pr["4.weight"][pr["4.weight"] != 0].abs().min(); dropped = net[4].weight.detach()[pr["4.weight"] == 0].abs().max()
+    assert kept >= dropped
+    code, out = run("model", "prune", str(src), "-o", str(tmp_path / "rows.pt"), "--sparsity", "0.4", "--structured")
+    rows = torch.load(tmp_path / "rows.pt")["4.weight"]
+    assert out["structured"] and int((rows.abs().sum(1) == 0).sum()) == 2 and int((torch.load(tmp_path / "rows.pt")["0.weight"].flatten(1).abs().sum(1) == 0).sum()) == 1
+    # compress
+    code, out = run("model", "compress", str(tmp_path / "pruned.pt"), "-o", str(tmp_path / "pruned.pt.gz"), "--level", "9")
+    assert out["ratio"] > 1.5 and gzip.decompress((tmp_path / "pruned.pt.gz").read_bytes()) == (tmp_path / "pruned.pt").read_bytes()
+    # extract
+    code, out = run("model", "extract", str(src), "-o", str(tmp_path / "head.pt"), "--pattern", "4.*")
+    assert out["extracted"] == 2 and out["names"] == ["4.bias", "4.weight"] and set(torch.load(tmp_path / "head.pt")) == {"4.weight", "4.bias"}
+    with pytest.raises(SystemExit):
+        cli.main(["model", "extract", str(src), "-o", str(tmp_path / "none.pt"), "--pattern", "zzz*"])
+    # merge
+    other = {k: v * 3 if v.is_floating_point() else v for k, v in net.state_dict().items()}
+    torch.save(other, tmp_path / "other.pt")
+    code, out = run("model", "merge", str(src), str(tmp_path / "other.pt"), "-o", str(tmp_path / "avg.pt"))
+    assert out["weights"] == [0.5, 0.5] and torch.allclose(torch.load(tmp_path / "avg.pt")["4.weight"], 2 * net[4].weight.detach())
+    code, out = run("model", "merge", str(src), str(tmp_path / "other.pt"), "-o", str(tmp_path / "w.pt"), "--weights", "0.9,0.1")
+    assert torch.allclose(torch.load(tmp_path / "w.pt")["4.bias"], 1.2 * net[4].bias.detach())
+    with pytest.raises(SystemExit):
+        cli.main(["model", "merge", str(src), str(tmp_path / "head.pt"), "-o", str(tmp_path / "bad.pt")])

@@ -174,6 +174,78 @@ def cmd_model(a, cfg):
         with torch.no_grad():
             r = benchmark(lambda: m(x), warmup=cfg["benchmark"]["warmup"], iters=a.iters)
         return {"model": a.path, "device": str(dev), **r}
+    if a.action == "prune":
+        st = _load_state(a.path)
+        kept = total = 0
+        for k, v in st["parameters"].items():
+            t = _t(v).float()
+            if t.dim() >= 2:
+                if a.structured:                                                   # whole output rows, smallest L2 norm first
+                    norms = t.flatten(1).norm(dim=1)
+                    n_drop = int(a.sparsity * len(norms))
+                    mask = torch.ones_like(norms, dtype=torch.bool)
+                    if n_drop:
+                        mask[norms.argsort()[:n_drop]] = False
+                    t = t * mask.reshape(-1, *[1] * (t.dim() - 1))
+                else:
+                    n_drop = int(a.sparsity * t.numel())
+                    if n_drop:
+                        t = t * (t.abs() > t.abs().flatten().kthvalue(n_drop).values)
+                st["parameters"][k] = _entry(t)
+                kept += int((t != 0).sum()); total += t.numel()
+        _save_state(st, a.output)
+        return {"pruned": a.path, "output": a.output, "sparsity": round(1 - kept / max(total, 1), 4), "structured": bool(a.structured)}
+    if a.action == "optimize":
+        # folds every "<prefix>.weight" / "<bn>.running_mean, running_var, weight, bias" pair named with --fold "conv=bn" and
+        # drops buffers that inference does not need
+        st = _load_state(a.path)
+        params, folded = st["parameters"], []
+        for pair in (a.fold or "").split(","):
+            if "=" not in pair:
+                continue
+            conv, bn = pair.split("=")
+            w, mean, var = _t(params[conv + ".weight"]).float(), _t(params[bn + ".running_mean"]).float(), _t(params[bn + ".running_var"]).float()
+            g = _t(params[bn + ".weight"]).float() if bn + ".weight" in params else torch.ones_like(mean)
+            beta = _t(params[bn + ".bias"]).float() if bn + ".bias" in params else torch.zeros_like(mean)
+            b = _t(params[conv + ".bias"]).float() if conv + ".bias" in params else torch.zeros_like(mean)
+            scale = g / torch.sqrt(var + 1e-5)
+            params[conv + ".weight"] = _entry(w * scale.reshape(-1, *[1] * (w.dim() - 1)))
+            params[conv + ".bias"] = _entry((b - mean) * scale + beta)
+            for suffix in (".running_mean", ".running_var", ".weight", ".bias", ".num_batches_tracked"):
+                params.pop(bn + suffix, None)
+            folded.append(conv)
+        dropped = [k for k in list(params) if k.endswith("num_batches_tracked")]
+        for k in dropped:
+            params.pop(k)
+        _save_state(st, a.output)
+        return {"optimized": a.path, "output": a.output, "folded": folded, "dropped": dropped}
+    if a.action == "compress":
+        import gzip
+        raw = Path(a.path).read_bytes()
+        Path(a.output).write_bytes(gzip.compress(raw, compresslevel=a.level))
+        return {"compressed": a.path, "output": a.output, "bytes": len(raw), "compressed_bytes": Path(a.output).stat().st_size, "ratio": round(len(raw) / max(Path(a.output).stat().st_size, 1), 3)}
+    if a.action == "extract":
+        import fnmatch
+        st = _load_state(a.path)
+        pats = (a.pattern or "*").split(",")
+        st["parameters"] = {k: v for k, v in st["parameters"].items() if any(fnmatch.fnmatch(k, p_) for p_ in pats)}
+        if not st["parameters"]:
+            raise SystemExit(f"no tensor matches {a.pattern!r}")
+        _save_state(st, a.output)
+        return {"extracted": len(st["parameters"]), "output": a.output, "names": sorted(st["parameters"])[: a.limit]}
+    if a.action == "merge":
+        paths = [a.path, *(a.others or [])]
+        states = [_load_state(p_) for p_ in paths]
+        weights = [float(w) for w in a.weights.split(",")] if a.weights else [1.0 / len(states)] * len(states)
+        if len(weights) != len(states):
+            raise SystemExit("one weight per model is required")
+        keys = set(states[0]["parameters"])
+        if any(set(s_["parameters"]) != keys for s_ in states[1:]):
+            raise SystemExit("the models do not have the same tensors")
+        merged = states[0]
+        merged["parameters"] = {k: _entry(sum(w * _t(s_["parameters"][k]).float() for w, s_ in zip(weights, states))) for k in sorted(keys)}
+        _save_state(merged, a.output)
+        return {"merged": paths, "weights": weights, "output": a.output}
     raise SystemExit(f"unknown model action {a.action}")
 
 
@@ -453,8 +525,9 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--no-color", action="store_true")
     sub = p.add_subparsers(dest="command", required=True)
 
-    m = sub.add_parser("model"); m.add_argument("action", choices=["list", "create", "inspect", "convert", "validate", "quantize", "benchmark"])
-    m.add_argument("path", nargs="?"); m.add_argument("-o", "--output"); m.add_argument("--name"); m.add_argument("--dtype", choices=["f32", "f16", "bf16"])
+    m = sub.add_parser("model"); m.add_argument("action", choices=["list", "create", "inspect", "convert", "validate", "quantize", "benchmark", "prune", "optimize", "compress", "extract", "merge"])
+    m.add_argument("path", nargs="?"); m.add_argument("others", nargs="*"); m.add_argument("--sparsity", type=float, default=0.5); m.add_argument("--structured", action="store_true")
+    m.add_argument("--fold"); m.add_argument("--level", type=int, default=6); m.add_argument("--pattern"); m.add_argument("--weights"); m.add_argument("-o", "--output"); m.add_argument("--name"); m.add_argument("--dtype", choices=["f32", "f16", "bf16"])
     m.add_argument("--bits", type=int, default=8); m.add_argument("--limit", type=int, default=20); m.add_argument("--device")
     m.add_argument("--batch", type=int, default=2); m.add_argument("--seq", type=int, default=128); m.add_argument("--iters", type=int, default=10)
 
