@@ -5122,3 +5122,114 @@ def test_special_ext_bessel_struve_coulomb_elliptic_faddeeva_integrals_zeta_math
     assert rep["max_abs"] < 1e-12 and len(rep["profile"]) == 10 and len(rep["chart"].splitlines()) == 10 and rep["max_ulp"] >= rep["median_ulp"] and 0.1 <= rep["argmax_abs"] <= 30.0
     crude = E.accuracy_report(lambda t: t - t ** 3 / 6, torch.sin, 0.0, 2.0)
     assert crude["argmax_abs"] == 2.0 and crude["profile"][-1] > crude["profile"][0] and crude["max_abs"] == pytest.approx(abs(2 - 8 / 6 - math.sin(2)))
+
+
+def test_text_quality_metrics_distances_overlap_rouge_bleu_embedding_perplexity_coherence_fluency_semantics():
+    from torsh_b200.text import quality_metrics as Q
+    from torsh_b200.text.analysis import NGramLM, words
+    # edit distances
+    assert Q.levenshtein("kitten", "sitting") == 3 and Q.levenshtein("abc", "", deletion=2) == 6 and Q.levenshtein("abc", "abd", substitution=0.5) == 0.5 and Q.levenshtein("a b c".split(), "a c".split()) == 1
+    assert Q.damerau_levenshtein("ca", "abc") == 2 and Q.optimal_string_alignment("ca", "abc") == 3 and Q.damerau_levenshtein("abcd", "acbd") == 1 == Q.optimal_string_alignment("abcd", "acbd") and Q.hamming("karolin", "kathrin") == 3
+    with pytest.raises(ValueError):
+        Q.hamming("ab", "abc")
+    assert Q.jaro("martha", "marhta") == pytest.approx(0.9444, abs=1e-4) and Q.jaro("dixon", "dicksonx") == pytest.approx(0.7667, abs=1e-4) and Q.jaro("abc", "xyz") == 0.0 and Q.jaro("same", "same") == 1.0
+    assert Q.normalized_distance(Q.levenshtein, "kitten", "sitting") == pytest.approx(3 / 7) and Q.similarity(Q.levenshtein, "", "") == 1.0
+    pd = Q.pairwise_distances(["abc", "abd", "xyz"])
+    assert pd.tolist() == [[0, 1, 3], [1, 0, 3], [3, 3, 0]] and Q.find_most_similar("helo", ["world", "hello", "help"], top=2) == [(1, pytest.approx(0.2)), (2, pytest.approx(0.25))]
+    # overlap
+    a, b = "the cat sat on the mat".split(), "the cat lay on the rug".split()
+    ov = Q.ngram_overlap(a, b)
+    assert ov["precision"] == pytest.approx(4 / 6) and ov["jaccard"] == pytest.approx(4 / 8) and ov["dice"] == pytest.approx(8 / 12) and Q.ngram_overlap(a, b, 2)["overlap_coefficient"] == pytest.approx(2 / 5)
+    assert Q.positional_overlap(a, b) == pytest.approx(4 / 6) and Q.positional_overlap(a, a[::-1]) < 0.5 and Q.positional_overlap([], a) == 0.0
+    texts = [a, b, "stocks fell sharply today".split(), "stocks rose sharply today".split()]
+    assert Q.cluster_by_overlap(texts, 0.4) == [[0, 1], [2, 3]] and Q.overlap_matrix(texts)[0, 2] == 0
+    # ROUGE
+    cand, ref = "the cat was found under the bed".split(), "the cat was under the bed".split()
+    r1, r2, rl = Q.rouge(cand, ref, "rouge-1"), Q.rouge(cand, ref, "rouge-2"), Q.rouge(cand, ref, "rouge-l")
+    assert (r1["precision"], r1["recall"]) == (pytest.approx(6 / 7), 1.0) and (r2["precision"], r2["recall"]) == (pytest.approx(4 / 6), pytest.approx(4 / 5)) and (rl["precision"], rl["recall"]) == (pytest.approx(6 / 7), 1.0)
+    rs = Q.rouge("police killed the gunman".split(), "police kill the gunman".split(), "rouge-s")
+    assert rs["precision"] == pytest.approx(3 / 6) and Q.rouge("police killed the gunman".split(), "police kill the gunman".split(), "rouge-s", stem=True)["f"] == 1.0
+    assert Q.rouge("a b".split(), "a b".split(), "rouge-su")["f"] == 1.0 and Q.rouge("a b c d".split(), "a c".split(), "rouge-s", skip=0)["precision"] == 0.0
+    w_contig, w_spread = Q.rouge("a b c d x y z".split(), "a b c d e f g".split(), "rouge-w"), Q.rouge("a x b y c z d".split(), "a b c d e f g".split(), "rouge-w")
+    assert w_contig["f"] > w_spread["f"] and Q.rouge("a x b y c z d".split(), "a b c d e f g".split(), "rouge-l")["f"] == Q.rouge("a b c d x y z".split(), "a b c d e f g".split(), "rouge-l")["f"]
+    multi = Q.rouge(cand, ["a dog barked".split(), ref], "rouge-1")
+    assert multi["recall"] == 1.0 and Q.rouge(cand, ["a dog barked".split(), ref], "rouge-1", multi="mean")["recall"] == 0.5
+    assert Q.rouge("the the cat".split(), "cat".split(), "rouge-1", remove_stopwords=True)["f"] == 1.0
+    summ = Q.rouge_l_summary(["w1 w2 w6 w7 w8".split(), "w1 w3 w8 w9 w5".split()], ["w1 w2 w3 w4 w5".split()])
+    assert summ["recall"] == pytest.approx(4 / 5) and summ["precision"] == pytest.approx(4 / 10)
+    bi = Q.bootstrap_interval([0.4, 0.5, 0.6, 0.45, 0.55] * 4)
+    assert bi["lower"] < bi["mean"] < bi["upper"] and bi["mean"] == pytest.approx(0.5) and bi["width"] < 0.1 and bi["margin_of_error"] == pytest.approx(bi["width"] / 2)
+    # BLEU variants, chrF, METEOR-style, TER
+    hyp, refs = "the quick brown fox jumps over the dog".split(), ["the quick brown fox jumps over the lazy dog".split()]
+    bd = Q.bleu_detailed(hyp, refs)
+    assert bd["precisions"][0] == 1.0 and bd["precisions"][3] == pytest.approx(4 / 5) and bd["brevity_penalty"] == pytest.approx(math.exp(1 - 9 / 8)) and bd["bleu"] == pytest.approx(bd["brevity_penalty"] * (1 * 6 / 7 * 5 / 6 * 4 / 5) ** 0.25)
+    short = "the fox jumps high today".split()
+    assert Q.bleu_detailed(short, refs)["bleu"] == 0.0 and 0 < Q.bleu_detailed(short, refs, smoothing="epsilon")["bleu"] < Q.bleu_detailed(short, refs, smoothing="add_one")["bleu"] and Q.bleu_detailed(short, refs, smoothing="exponential")["bleu"] > 0
+    assert Q.bleu_detailed("the the the".split(), ["the cat".split()], max_n=1)["precisions"] == [pytest.approx(1 / 3)]
+    assert Q.chrf("hello world", "hello world") == 1.0 and Q.chrf("abc", "xyz") == 0.0 and 0.5 < Q.chrf("the cat sat", "the cat sits") < 1.0 and 0 < Q.chrf("the cat sat", "cat the sat") < Q.chrf("the cat sat", "cat the sat", word_n=1) < 1
+    m_same, m_scr = Q.meteor_like("the cat sat on the mat".split(), "the cat sat on the mat".split()), Q.meteor_like("mat the on sat cat the".split(), "the cat sat on the mat".split())
+    assert m_same["chunks"] == 1 and m_same["score"] == pytest.approx(1 - 0.5 / 6 ** 3) and m_scr["precision"] == 1.0 and m_scr["score"] < 0.8 * m_same["score"]
+    assert Q.meteor_like("cats running".split(), "cat runs".split())["recall"] >= 0.5 and Q.meteor_like("big house".split(), "large house".split(), synonyms={"big": {"large"}})["recall"] == 1.0 and Q.meteor_like(["x"], ["y"])["score"] == 0.0
+    assert Q.translation_edit_rate("a b c d e".split(), "a b c d e".split()) == 0.0 and Q.translation_edit_rate("d e a b c".split(), "a b c d e".split()) == pytest.approx(1 / 5) and Q.translation_edit_rate("a b x".split(), "a b c d".split()) == pytest.approx(2 / 4)
+    # embedding matching
+    E = torch.eye(4)
+    assert Q.embedding_score(E[[0, 1, 2]], E[[2, 0, 1]])["f"] == pytest.approx(1.0) and Q.embedding_score(E[[0, 1]], E[[0, 3]])["precision"] == pytest.approx(0.5)
+    w = Q.embedding_score(E[[0, 1]], E[[0, 3]], cand_idf=torch.tensor([3.0, 1.0]))
+    assert w["precision"] == pytest.approx(0.75) and Q.embedding_score(E[[0, 1]], E[[0, 3]], baseline=0.2)["recall"] == pytest.approx((0.5 - 0.2) / 0.8)
+    idf = Q.idf_weights([["a", "b"], ["a", "c"], ["a"]])
+    assert idf["a"] == pytest.approx(0.0) and idf["b"] == pytest.approx(math.log(2)) and idf["zzz"] == pytest.approx(math.log(4))
+    # perplexity
+    logits = torch.zeros(2, 5, 7)
+    assert Q.perplexity_from_logits(logits, torch.randint(0, 7, (2, 5))) == pytest.approx(7.0, rel=1e-5)
+    tg = torch.tensor([[1, 2, -100, -100, -100], [0, 1, 2, 3, 4]])
+    sharp = torch.full((2, 5, 7), -20.0); sharp[0, :, 1] = 20.0; sharp[1] = 0.0
+    per = Q.perplexity_from_logits(sharp, tg, per_sequence=True)
+    assert per[1] == pytest.approx(7.0, rel=1e-5) and per[0] == pytest.approx(math.exp(20.0), rel=1e-3)
+    assert Q.perplexity_from_probabilities([0.25] * 8) == pytest.approx(4.0) and Q.perplexity_from_cross_entropy(3.0, base=2) == 8.0 and Q.bits_per_character(math.log(2) * 100, 50) == pytest.approx(2.0) and Q.perplexity_quality(35.0) == "good"
+    cmpm = Q.compare_perplexities([50.0, 60, 55, 70, 65, 58, 62, 66], [40.0, 45, 50, 52, 51, 47, 49, 50])
+    assert cmpm["model2_win_rate"] == 1.0 and cmpm["is_model2_better"] and cmpm["improvement_percentage"] == pytest.approx(100 * (60.75 - 48.0) / 60.75) and not Q.compare_perplexities([50.0, 60, 55, 52], [51.0, 59, 56, 51])["is_model2_better"]
+    # coherence
+    good = "The river flooded the village last night. The flood destroyed several houses near the river. Residents of the village left their houses quickly. They returned when the river fell again."
+    bad = "The river flooded the village last night. Quantum computers use qubits. My favourite recipe needs three eggs. Stock markets closed higher on Friday."
+    eg, eb = Q.entity_grid(good), Q.entity_grid(bad)
+    assert {"river", "village", "houses"} <= set(eg["entities"]) and eb["entities"] == [] and eg["coherence"] > 0.1 > eb["coherence"] and abs(sum(eg["transitions"].values()) - 1) < 1e-9 and eg["grid"]["river"][2] == "-"
+    ch = Q.lexical_chains(good)
+    assert ch[0]["word"] == "river" and ch[0]["sentences"] == [0, 1, 3] and any(c["word"] in ("flood", "hous") for c in ch) and Q.lexical_chains(bad) == []
+    lc_g, lc_b = Q.local_coherence(good), Q.local_coherence(bad)
+    assert lc_g["mean"] > 0.2 > 0.1 > lc_b["mean"] and len(lc_g["adjacent"]) == 3 and lc_g["adjacent"][2] >= 0.15
+    dm = Q.discourse_markers("First we measured it. However, the signal was weak. Therefore we repeated it. For example, run two failed. In conclusion, it works.")
+    assert dm["counts"]["adversative"] == 1 and dm["counts"]["causal"] == 1 and dm["counts"]["exemplifying"] == 1 and dm["counts"]["summarising"] == 1 and dm["per_sentence"] >= 1.0 and 0.8 < dm["diversity"] <= 1.0
+    st = Q.structural_coherence("This essay introduces tides. Tides follow the moon.\n\nTides rise twice a day. The moon pulls the tides along.\n\nIn conclusion, tides track the moon. The moon matters.")
+    assert st["paragraphs"] == 3 and st["balance"] > 0.8 and st["has_introduction_marker"] and st["has_conclusion_marker"] and st["topic_sentence_support"] > 0.2
+    assert Q.coherence_report(good)["score"] > 2 * Q.coherence_report(bad)["score"] and Q.coherence_report(bad)["chains"] == 0
+    # fluency
+    lr = Q.lexical_richness("a a a b b c".split())
+    assert lr["ttr"] == 0.5 and lr["hapax_ratio"] == pytest.approx(1 / 3) and lr["yule_k"] == pytest.approx(1e4 * (1 + 4 + 9 - 6) / 36) and lr["simpson_d"] == pytest.approx((6 + 2) / 30) and lr["dis_legomena_ratio"] == pytest.approx(1 / 3)
+    sf = Q.syntactic_fluency("this sentence starts lowercase. The the cat sat on a apple. She walked (quickly home. Because rain.")
+    kinds = [i["kind"] for i in sf["issues"]]
+    assert {"capitalisation", "doubled_word", "article_agreement", "unbalanced", "fragment"} <= set(kinds) and sf["score"] < 0.5 and Q.syntactic_fluency("The cat sat on an apple. It was an honest hour of work.")["issues"] == []
+    verse = "The cat sat still\nUpon the hill\nAnd watched the night\nGrow slowly bright"
+    prose = "Go. The extraordinarily complicated administrative reorganisation continued unexpectedly throughout the following year. Stop."
+    rv, rp = Q.rhythm_analysis(verse), Q.rhythm_analysis(prose)
+    assert rv["end_rhyme"] == pytest.approx(2 / 3) and rp["cadence_variability"] > 100 and rp["polysyllabic_ratio"] > 0.4 and rv["syllables_per_word"] < 1.4 and Q.rhythm_analysis("big bad bears bite")["alliteration"] == 1.0
+    pf, pi = Q.pragmatic_analysis("Therefore, the committee consequently recommends additional investigation regarding the aforementioned discrepancies."), Q.pragmatic_analysis("Hey guys, that's gonna be awesome! Can't wait, lol!")
+    assert pf["register"] == "formal" and pi["register"] == "informal" and Q.pragmatic_analysis("Perhaps it might possibly work.")["hedging"] == pytest.approx(3 / 5) and Q.pragmatic_analysis("Could you please help? Thanks!")["politeness"] > 0.5
+    lm = NGramLM(2).fit([words(good)] * 3)
+    fr_in, fr_out = Q.fluency_report(good, lm), Q.fluency_report("village the night flooded river last the. houses several the near destroyed flood river the.", lm)
+    assert fr_in["components"]["statistical"] > fr_out["components"]["statistical"] and fr_in["score"] > fr_out["score"]
+    # semantics
+    assert Q.sentence_sentiment("This is a great film") > 0 > Q.sentence_sentiment("This is not a great film") and Q.sentence_sentiment("This is really terrible") == -1.0 and Q.sentence_sentiment("The table is round") == 0.0
+    traj = Q.sentiment_trajectory("The start was terrible. The middle was bad. Then it became good. The ending was wonderful and brilliant.")
+    assert traj["trend"] == "improving" and traj["polarity_flips"] == 1 and traj["per_sentence"][0] < 0 < traj["per_sentence"][-1] and Q.sentiment_trajectory("Great. Awful. Great. Awful.")["volatility"] == 1.0
+    em = Q.emotion_scores("She was afraid and full of dread, panic rising; later she smiled.")
+    assert em["dominant"] == "fear" and em["scores"]["fear"] == 0.75 and em["scores"]["joy"] == 0.25
+    docs = [d.split() for d in ("stock market investors shares profit", "market shares investors bank profit", "bank profit stock market", "football team player goal match", "team goal player league match", "match football league team")]
+    tp = Q.nmf_topics(docs, k=2, top=5)
+    assert len(set(tp["assignments"][:3])) == 1 and len(set(tp["assignments"][3:])) == 1 and tp["assignments"][0] != tp["assignments"][3] and tp["reconstruction_error"] < 0.7
+    fin_topic = tp["topics"][tp["assignments"][0]]
+    assert {"market", "profit"} <= set(fin_topic) and not {"team", "goal"} & set(fin_topic[:3]) and all(c > -2.5 for c in tp["coherence"])
+    assert Q.classify_domain("The patient received treatment after the diagnosis at the hospital.")["domain"] == "medical" and Q.classify_domain("The defendant appealed to the court under the statute.")["domain"] == "legal" and Q.classify_domain("Hello there.")["domain"] == "general"
+    ss = Q.syntactic_similarity("The dog chased the ball quickly.", "The cat watched the bird quietly.")
+    assert ss["structure"] == 1.0 and ss["score"] > 0.95 > Q.syntactic_similarity("The dog chased the ball quickly.", "Running fast, are 12 people happy?")["score"]
+    lsa = Q.latent_semantic_similarity(docs + ["investors shares".split(), "league player".split()], rank=2)
+    assert lsa[6, 2] > 0.9 > 0.3 > lsa[6, 5] and lsa[7, 5] > 0.9 and torch.allclose(lsa.diag(), torch.ones(8, dtype=torch.float64))
