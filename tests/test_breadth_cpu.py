@@ -5233,3 +5233,113 @@ def test_text_quality_metrics_distances_overlap_rouge_bleu_embedding_perplexity_
     assert ss["structure"] == 1.0 and ss["score"] > 0.95 > Q.syntactic_similarity("The dog chased the ball quickly.", "Running fast, are 12 people happy?")["score"]
     lsa = Q.latent_semantic_similarity(docs + ["investors shares".split(), "league player".split()], rank=2)
     assert lsa[6, 2] > 0.9 > 0.3 > lsa[6, 5] and lsa[7, 5] > 0.9 and torch.allclose(lsa.diag(), torch.ones(8, dtype=torch.float64))
+
+
+def test_vision_tools_drawing_annotations_attribution_tiling_video_flow_stabilisation_and_apng():
+    import json
+    import xml.etree.ElementTree as ET
+    from torsh_b200.vision import tools as V
+    from torsh_b200.vision.io import decode_png
+    torch.manual_seed(0)
+    # drawing
+    img = torch.zeros(3, 20, 30)
+    d = V.draw_boxes(img, torch.tensor([[2.0, 3.0, 10.0, 12.0]]), colors=torch.tensor([[255, 0, 0]]), width=2)
+    assert d.dtype == torch.uint8 and d[:, 3, 2:11].float().mean(1).tolist() == [255, 0, 0] and d[0, 4, 5] == 255 and d[0, 5, 5] == 0 and d[0, 12, 10] == 255 and d[0, 13, 10] == 0
+    filled = V.draw_boxes(torch.ones(3, 20, 30), torch.tensor([[0.0, 0.0, 5.0, 5.0]]), colors=torch.tensor([[0, 0, 255]]), fill_alpha=0.5)
+    assert filled[:, 3, 3].tolist() == [128, 128, 255] and V.draw_boxes(img, torch.tensor([[-5.0, -5.0, 50.0, 50.0]])).shape == (3, 20, 30)
+    kp = V.draw_keypoints(img, torch.tensor([[5.0, 5.0], [20.0, 15.0]]), radius=1, connections=[(0, 1)], color=(0, 255, 0))
+    assert kp[1, 5, 5] == 255 and kp[1, 15, 20] == 255 and int(kp[1, 10, 12]) + int(kp[1, 10, 13]) + int(kp[1, 9, 12]) + int(kp[1, 10, 11]) >= 255 and kp[0].sum() == 0
+    m = torch.zeros(2, 20, 30, dtype=torch.bool); m[0, :5] = True; m[1, 10:] = True
+    seg = V.draw_segmentation_masks(torch.full((3, 20, 30), 100, dtype=torch.uint8), m, alpha=0.5)
+    assert seg[:, 0, 0].tolist() == [165, 62, 88] and seg[:, 7, 0].tolist() == [100, 100, 100] and seg[:, 15, 0].tolist() == [80, 140, 88]
+    grid = V.make_grid(torch.arange(5.0).reshape(5, 1, 1, 1).expand(5, 1, 4, 6), nrow=3, padding=1, pad_value=-1.0)
+    assert grid.shape == (1, 2 * 5 + 1, 3 * 7 + 1) and grid[0, 1, 1] == 0 and grid[0, 1, 8] == 1 and grid[0, 6, 8] == 4 and grid[0, 0, 0] == -1 and grid[0, 6, 15] == -1
+    assert V.make_grid(torch.rand(2, 3, 4, 4) * 10, normalize=True).max() <= 1.0
+    # annotation session
+    s = V.AnnotationSession(100, 80, "a.png")
+    b1 = s.add("box", "cat", [10, 10, 50, 40], score=0.9); p1 = s.add("polygon", "dog", [60, 10, 90, 10, 90, 40]); k1 = s.add("point", "eye", [20, 20])
+    with pytest.raises(ValueError):
+        s.add("box", "bad", [10, 10, 5, 40])
+    s.relabel(b1, "tiger"); s.move(b1, 5, -5); s.remove(k1)
+    assert s.items[b1].coords == [15, 5, 55, 35] and s.statistics()["labels"] == {"tiger": 1, "dog": 1}
+    assert s.undo() and k1 in s.items and s.undo() and s.items[b1].coords == [10, 10, 50, 40] and s.undo() and s.items[b1].label == "cat"
+    coco = s.to_coco()
+    by = {a["id"]: a for a in coco["annotations"]}
+    assert by[b1]["bbox"] == [10, 10, 40, 30] and by[b1]["area"] == 1200 and by[p1]["area"] == 450 and by[p1]["bbox"] == [60, 10, 30, 30] and by[k1]["keypoints"] == [20, 20, 2] and by[b1]["score"] == 0.9 and len(coco["categories"]) == 3
+    back = V.AnnotationSession.from_coco(json.loads(json.dumps(coco)))
+    assert back.statistics() == s.statistics() and not back.undo()
+    svg = ET.fromstring(s.to_svg("a.png"))
+    ns = "{http://www.w3.org/2000/svg}"
+    assert svg.find(f"{ns}rect").attrib["width"] == "40" and svg.find(f"{ns}polygon") is not None and svg.find(f"{ns}circle").attrib["cx"] == "20" and svg.find(f"{ns}image").attrib["href"] == "a.png" and "cat 0.90" in s.to_svg()
+    page = V.html_gallery([s, back], hrefs=["a.png", "b.png"])
+    assert page.count("<svg") == 2 and "a.png: 3 annotations" in page
+    # attribution: a model that looks only at one patch
+    class PatchModel(torch.nn.Module):
+        def forward(self, x): return torch.stack([x[:, :, 4:8, 8:12].sum((1, 2, 3)), x[:, :, :4, :4].sum((1, 2, 3))], 1)
+    pm, xin = PatchModel(), torch.ones(1, 16, 16)
+    occ = V.occlusion_sensitivity(pm, xin, target=0, patch=4)
+    assert occ[4:8, 8:12].min() == 16.0 and occ.sum() == 16.0 * 16 and V.occlusion_sensitivity(pm, xin, 1, patch=4, stride=2)[:4, :4].min() > 0
+    sg = V.smooth_grad(pm, torch.rand(1, 16, 16), 0, samples=4, generator=torch.Generator().manual_seed(0))
+    assert torch.equal(sg[4:8, 8:12], torch.ones(4, 4)) and sg.sum() == 16
+    att = [torch.softmax(torch.randn(2, 5, 5), -1) for _ in range(3)]
+    roll = V.attention_rollout(att)
+    assert torch.allclose(roll.sum(-1), torch.ones(5), atol=1e-6) and (roll >= 0).all() and torch.allclose(V.attention_rollout([torch.zeros(1, 4, 4)]), torch.eye(4)) and V.attention_rollout(att, discard_ratio=0.5).shape == (5, 5)
+    lin = torch.nn.Linear(6, 3, bias=False)
+    am = V.activation_maximization(lin, (6,), lambda o: o[:, 1], steps=200, lr=0.05, l2=0.05, generator=torch.Generator().manual_seed(0))
+    assert torch.nn.functional.cosine_similarity(am, lin.weight[1].detach(), dim=0) > 0.99
+    # tiled processing equals whole-image processing for a local operator away from tile artefacts; upscaling too
+    big = torch.rand(3, 150, 210)
+    blur = lambda t: torch.nn.functional.avg_pool2d(torch.nn.functional.pad(t, (1, 1, 1, 1), mode="replicate"), 3, 1)
+    tp = V.TiledProcessor(blur, tile=64, overlap=16)
+    tiled = tp(big)
+    assert tiled.shape == big.shape and tp.tiles >= 12 and float((tiled - blur(big[None])[0]).abs().max()) < 0.05 and float((tiled - blur(big[None])[0])[:, 20:40, 20:40].abs().max()) < 1e-6
+    assert torch.allclose(V.TiledProcessor(lambda t: t * 2, tile=64, overlap=8)(big), big * 2, atol=1e-6)
+    up = V.TiledProcessor(lambda t: torch.nn.functional.interpolate(t, scale_factor=2, mode="nearest"), tile=64, overlap=8, scale=2)(big)
+    assert up.shape == (3, 300, 420) and torch.allclose(up, torch.nn.functional.interpolate(big[None], scale_factor=2, mode="nearest")[0], atol=1e-6)
+    pool = V.ImageBufferPool(max_per_key=1)
+    t1 = pool.acquire((3, 8, 8)); pool.release(t1); t2 = pool.acquire((3, 8, 8)); pool.release(t2); pool.release(torch.empty(3, 8, 8))
+    assert t2 is t1 and (pool.hits, pool.misses) == (1, 1) and pool.bytes_held() == 3 * 64 * 4
+    cnn = torch.nn.Sequential(torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.ReLU(), torch.nn.Flatten(), torch.nn.Linear(8 * 16 * 16, 4))
+    est = V.estimate_batch_memory(cnn, torch.randn(2, 3, 16, 16))
+    assert est["per_sample_bytes"] == (8 * 256 * 3 + 4 + 3 * 256) * 4 and est["fixed_bytes"] == 4 * est["parameters_bytes"]
+    assert V.auto_batch_size(cnn, torch.randn(1, 3, 16, 16), memory_budget=est["fixed_bytes"] + 100 * est["per_sample_bytes"], safety=1.0) == 96 and V.auto_batch_size(cnn, torch.randn(1, 3, 16, 16), memory_budget=1) == 1
+    pol = V.HardwarePolicy.detect()
+    assert pol.device in ("cpu", "cuda") and pol.prepare(cnn)(pol.prepare_input(torch.randn(1, 3, 16, 16))).shape == (1, 4)
+    # video clips
+    clip = V.VideoClip(torch.arange(60.0).reshape(60, 1, 1, 1).expand(60, 1, 2, 2), fps=30.0)
+    assert clip.duration == 2.0 and clip.subclip(0.5, 1.0).frames[:, 0, 0, 0].tolist() == list(range(15, 30)) and clip.subsample(3).fps == 10.0 and clip.reverse().frames[0, 0, 0, 0] == 59
+    assert len(clip.speed(2.0).frames) == 30 and len(clip.resample_fps(15).frames) == 30 and clip.resample_fps(15).frames[1, 0, 0, 0] == 2 and len(clip.temporal_crop(16).frames) == 16 and clip.map(lambda f: f * 2).frames[3, 0, 0, 0] == 6
+    # optical flow on a smooth pattern shifted by a known amount
+    yy, xx = torch.meshgrid(torch.arange(64.0), torch.arange(64.0), indexing="ij")
+    pattern = lambda dx, dy: (torch.sin((xx - dx) / 5.0) + torch.cos((yy - dy) / 7.0) + torch.sin((xx - dx + yy - dy) / 9.0))[None]
+    a, b = pattern(0, 0), pattern(1.0, 0.5)
+    hs = V.horn_schunck(a, b, alpha=0.5, iters=300)
+    lk = V.lucas_kanade(a, b, window=9, levels=2)
+    for flow in (hs, lk):
+        inner = flow[:, 8:-8, 8:-8]
+        assert float(inner[0].mean()) == pytest.approx(1.0, abs=0.15) and float(inner[1].mean()) == pytest.approx(0.5, abs=0.15)
+    assert float((V.warp_by_flow(b, lk) - a)[:, 8:-8, 8:-8].abs().mean()) < 0.02 < float((b - a)[:, 8:-8, 8:-8].abs().mean())
+    mid = V.interpolate_frames(a, pattern(2.0, 0.0), 0.5)
+    assert float((mid - pattern(1.0, 0.0))[:, 8:-8, 8:-8].abs().mean()) < 0.03 < float((0.5 * (a + pattern(2.0, 0.0)) - pattern(1.0, 0.0))[:, 8:-8, 8:-8].abs().mean()) + 0.02
+    # shots, phase correlation, stabilisation
+    dark, bright = torch.rand(6, 3, 16, 16) * 0.2, 0.7 + torch.rand(5, 3, 16, 16) * 0.3
+    assert V.detect_shots(torch.cat([dark, bright, dark[:4]])) == [6, 11] and V.detect_shots(dark) == []
+    base = torch.rand(1, 48, 48)
+    assert V.phase_correlation(base, torch.roll(base, (3, -5), (-2, -1))) == (-5, 3) and V.phase_correlation(base, base) == (0, 0)
+    jitter = [(0, 0), (2, -1), (-1, 2), (1, 1), (-2, -2), (0, 1), (2, 0), (-1, -1)]
+    shaky = torch.stack([torch.roll(base, (dy, dx), (-2, -1)) for dx, dy in jitter])
+    stab, corr = V.stabilize(shaky, smoothing=5)
+    resid = lambda fr: sum(abs(v) for i in range(len(fr) - 1) for v in V.phase_correlation(fr[i], fr[i + 1]))
+    assert resid(stab) < 0.5 * resid(shaky) and corr.shape == (8, 2)
+    # animated PNG
+    anim = (torch.rand(4, 3, 6, 5) * 255).to(torch.uint8)
+    data = V.encode_apng(anim, fps=8.0)
+    frames, fps = V.decode_apng(data)
+    assert torch.equal(frames, anim) and fps == pytest.approx(8.0) and data[:8] == b"\x89PNG\r\n\x1a\n" and data.count(b"fdAT") == 3 and data.count(b"fcTL") == 4
+    assert torch.equal(decode_png(data)[:3], anim[0]) or torch.equal((decode_png(data)[:3] * 255).round().to(torch.uint8), anim[0])
+    gray = V.decode_apng(V.encode_apng(torch.rand(2, 1, 4, 4)))[0]
+    assert gray.shape == (2, 1, 4, 4)
+    with pytest.raises(ValueError):
+        V.decode_apng(data[:40] + bytes([data[40] ^ 1]) + data[41:])
+    bt = V.benchmark_transforms({"flip": lambda t: t.flip(-1), "half": lambda t: t[:, ::2, ::2]}, torch.rand(3, 64, 64), iterations=3)
+    assert bt["half"]["output_shape"] == (3, 32, 32) and bt["flip"]["images_per_s"] > 0
