@@ -1,5 +1,6 @@
 """Auxiliary subsystems on the CPU: optimizer checkpoints, monitoring, debug checks, property-based fuzzing of the
 host-side planners and codecs."""
+import hashlib
 import json
 import math
 import os
@@ -2449,3 +2450,119 @@ def test_cli_model_prune_optimize_compress_extract_merge(tmp_path, capsys):
     assert torch.allclose(torch.load(tmp_path / "w.pt")["4.bias"], 1.2 * net[4].bias.detach())
     with pytest.raises(SystemExit):
         cli.main(["model", "merge", str(src), str(tmp_path / "head.pt"), "-o", str(tmp_path / "bad.pt")])
+
+
+def test_package_infra_lockfile_installer_cdn_object_store_syslog_and_audit_storage(tmp_path):
+    import socket
+    from torsh_b200 import package_infra as P
+    from torsh_b200.package_resolver import PackageIndex
+    # lock file
+    index = PackageIndex({"app": {"1.0.0": {"core": ">=1.0.0", "io": "^2.0.0"}}, "core": {"1.0.0": {}, "1.2.0": {}}, "io": {"2.0.0": {"core": ">=1.1.0"}, "2.1.0": {"core": ">=1.1.0"}, "3.0.0": {}}})
+    blobs = lambda n, v: f"{n}@{v}".encode() * 10
+    lock = P.Lockfile.generate(index, {"app": "1.0.0"}, blobs)
+    assert {n: p["version"] for n, p in lock.packages.items()} == {"app": "1.0.0", "core": "1.2.0", "io": "2.1.0"} and lock.packages["io"]["dependencies"] == {"core": ">=1.1.0"}
+    text = lock.dumps()
+    again = P.Lockfile.loads(text)
+    assert again.packages == lock.packages and again.is_current({"app": "1.0.0"}) and not again.is_current({"app": "1.0.0", "x": "*"}) and again.verify(blobs) == []
+    with pytest.raises(ValueError, match="edited by hand"):
+        P.Lockfile.loads(text.replace('"1.2.0"', '"1.0.0"'))
+    assert again.verify(lambda n, v: b"tampered" if n == "io" else blobs(n, v)) == ["io"]
+    index.add("io", "2.2.0", {"core": ">=1.1.0"}); index.add("extra", "0.1.0", {})
+    newer = P.Lockfile.generate(index, {"app": "1.0.0", "extra": "*"}, blobs)
+    assert lock.diff(newer) == {"added": ["extra"], "removed": [], "changed": {"io": ("2.1.0", "2.2.0")}}
+    # installer
+    inst = P.DependencyInstaller(tmp_path / "site", blobs)
+    assert inst.plan(lock) == ["core", "io", "app"]
+    hooks = []
+    res = inst.install(lock, post_install=lambda n, d: hooks.append(n))
+    assert res["installed"] == ["core-1.2.0", "io-2.1.0", "app-1.0.0"] and hooks == ["core", "io", "app"] and inst.installed() == {"core": "1.2.0", "io": "2.1.0", "app": "1.0.0"} and (tmp_path / "site" / "io-2.1.0" / "payload.bin").read_bytes() == blobs("io", "2.1.0")
+    assert inst.install(lock) == {"installed": [], "skipped": ["core", "io", "app"]}
+    up = inst.install(newer)
+    assert up["installed"] == ["io-2.2.0", "extra-0.1.0"] and inst.installed()["io"] == "2.2.0" and not (tmp_path / "site" / "io-2.1.0").exists()
+    assert inst.uninstall_unlisted(lock) == ["extra"]
+    bad = P.DependencyInstaller(tmp_path / "site2", lambda n, v: b"evil" if n == "io" else blobs(n, v))
+    with pytest.raises(P.InstallError, match="io 2.1.0: artefact hash differs"):
+        bad.install(lock)
+    assert bad.installed() == {} and bad.log[-1][0] == "rolled_back" and bad.log[-1][1] == ["core-1.2.0"]
+    cyc = P.Lockfile({"a": {"version": "1", "sha256": "", "dependencies": {"b": "*"}}, "b": {"version": "1", "sha256": "", "dependencies": {"a": "*"}}}, {})
+    with pytest.raises(P.InstallError, match="cycle"):
+        inst.plan(cyc)
+    # CDN
+    now = [0.0]
+    cdn = P.ContentDeliveryNetwork(lambda k: k.encode() * 100, ttl=60.0, clock=lambda: now[0])
+    cdn.add_edge(P.EdgeNode("fra", "eu", {"eu": 10, "us": 90}, capacity=1000)).add_edge(P.EdgeNode("nyc", "us", {"eu": 85, "us": 8}, capacity=1000))
+    d, m = cdn.get("model", "eu")
+    assert m == {"edge": "fra", "cache": "miss", "latency_ms": 10} and cdn.get("model", "eu")[1]["cache"] == "hit" and cdn.get("model", "us")[1] == {"edge": "nyc", "cache": "miss", "latency_ms": 8} and cdn.origin_fetches == 2
+    now[0] = 100.0
+    assert cdn.get("model", "eu")[1]["cache"] == "miss"
+    cdn.get("aa", "eu"); cdn.get("bb", "eu"); cdn.get("cc", "eu")                    # 500 + 200 + 200 + 200 > 1000: the oldest leaves
+    assert "model" not in cdn.edges[0].cache and cdn.edges[0].used == 600
+    cdn.edges[0].online = False
+    assert cdn.get("aa", "eu")[1]["edge"] == "nyc"
+    cdn.edges[0].online = True
+    assert cdn.invalidate("a") == 2 and cdn.get("aa", "eu")[1]["cache"] == "miss"
+    cdn.prefetch(["p1", "p2"], ["eu", "us"])
+    assert cdn.get("p1", "us")[1]["cache"] == "hit" and 0 < cdn.statistics()["hit_rate"] < 1 and cdn.statistics()["edges"]["nyc"]["online"]
+    for e in cdn.edges:
+        e.online = False
+    with pytest.raises(ConnectionError):
+        cdn.get("x", "eu")
+    # object store
+    clock = [1000.0]
+    st = P.ObjectStore(tmp_path / "bucket", versioning=True, clock=lambda: clock[0])
+    r1 = st.put("models", "gpt/weights.bin", b"version one", {"stage": "dev"}); r2 = st.put("models", "gpt/weights.bin", b"version two!")
+    assert (r1["version"], r2["version"]) == (1, 2) and st.get("models", "gpt/weights.bin") == b"version two!" and st.get("models", "gpt/weights.bin", version=1) == b"version one" and st.versions("models", "gpt/weights.bin") == [1, 2]
+    assert st.get("models", "gpt/weights.bin", byte_range=(8, 10)) == b"two" and st.head("models", "gpt/weights.bin")["size"] == 12 and st.head("models", "gpt/weights.bin")["etag"] == hashlib.md5(b"version two!").hexdigest()
+    st.put("models", "gpt/config.json", b"{}"); st.put("models", "bert/weights.bin", b"b")
+    assert st.list("models", "gpt/") == ["gpt/config.json", "gpt/weights.bin"] and st.list("models") == ["bert/weights.bin", "gpt/config.json", "gpt/weights.bin"] and st.list("none") == []
+    up = st.create_multipart("models", "big.bin")
+    e2, e1 = st.upload_part(up, 2, b"world"), st.upload_part(up, 1, b"hello ")
+    with pytest.raises(ValueError):
+        st.complete_multipart(up, [(1, e1), (2, "wrong")])
+    st.complete_multipart(up, [(2, e2), (1, e1)])
+    assert st.get("models", "big.bin") == b"hello world"
+    url = st.presign("models", "big.bin", expires_in=60)
+    assert st.open_presigned(url) == b"hello world"
+    with pytest.raises(PermissionError, match="signature"):
+        st.open_presigned(url.replace("big.bin", "gpt/config.json"))
+    with pytest.raises(PermissionError, match="signature"):
+        st.open_presigned(url, method="PUT")
+    clock[0] += 120
+    with pytest.raises(PermissionError, match="expired"):
+        st.open_presigned(url)
+    st.delete("models", "big.bin")
+    with pytest.raises(KeyError):
+        st.get("models", "big.bin")
+    flat = P.ObjectStore(tmp_path / "flat")
+    flat.put("b", "k", b"1"); flat.put("b", "k", b"2")
+    assert flat.versions("b", "k") == [2] and flat.get("b", "k") == b"2"
+    # syslog
+    rec = P.format_syslog("package installed", "notice", "local1", app="torsh-pkg", hostname="host1", procid=42, msgid="INSTALL", structured={"pkg@1": {"name": 'a"b', "path": "x]y\\z"}}, timestamp=0.25)
+    assert rec == '<141>1 1970-01-01T00:00:00.250Z host1 torsh-pkg 42 INSTALL [pkg@1 name="a\\"b" path="x\\]y\\\\z"] package installed'
+    back = P.parse_syslog(rec)
+    assert back["facility"] == "local1" and back["severity"] == "notice" and back["structured"] == {"pkg@1": {"name": 'a"b', "path": "x]y\\z"}} and back["message"] == "package installed" and back["procid"] == "42"
+    assert P.parse_syslog(P.format_syslog("plain", "error", hostname="h", procid=1, timestamp=1.0))["structured"] == {}
+    srv = socket.socket(socket.AF_INET, socket.SOCK_DGRAM); srv.bind(("127.0.0.1", 0)); srv.settimeout(2)
+    snd = P.SyslogSender(srv.getsockname(), min_severity="warning", app="t", hostname="h")
+    assert not snd.send("noise", "info") and snd.send("disk full", "critical")
+    got = P.parse_syslog(srv.recv(4096).decode())
+    assert got["message"] == "disk full" and got["severity"] == "critical" and snd.sent == 1
+    snd.close(); srv.close()
+    # audit storage
+    t = [0.0]
+    aud = P.AuditStorage(tmp_path / "audit", segment_bytes=600, clock=lambda: t[0])
+    for i in range(12):
+        t[0] = float(i)
+        aud.append("alice" if i % 2 == 0 else "bob", "publish" if i % 3 == 0 else "download", f"pkg-{i}", outcome="failure" if i == 7 else "success", size=i)
+    assert len(aud._segments()) >= 3 and aud.verify() == {"valid": True, "records_checked": 12}
+    assert [r["seq"] for r in aud.query(actor="alice")] == [0, 2, 4, 6, 8, 10] and [r["seq"] for r in aud.query(action="publish", since=4.0)] == [6, 9] and [r["resource"] for r in aud.query(outcome="failure")] == ["pkg-7"] and len(aud.query()) == 12
+    reopened = P.AuditStorage(tmp_path / "audit", segment_bytes=600, clock=lambda: t[0])
+    reopened.append("carol", "delete", "pkg-1")
+    assert reopened.verify()["records_checked"] == 13 and [r["seq"] for r in reopened.query(actor="carol")] == [12] and len(reopened.query(actor="bob")) == 6
+    assert reopened.export(tmp_path / "a.csv", "csv") == 13 and (tmp_path / "a.csv").read_text().splitlines()[0] == "seq,time,actor,action,resource,outcome" and reopened.export(tmp_path / "a.jsonl") == 13
+    t[0] = 100.0
+    removed = reopened.apply_retention(max_age=95.0)
+    assert removed >= 1 and reopened.verify()["valid"] and reopened.verify()["records_checked"] < 13 and all(r["seq"] >= 3 for r in reopened.query(actor="bob"))
+    seg = reopened._file(reopened._segments()[0])
+    seg.write_text(seg.read_text().replace('"success"', '"failure"', 1))
+    assert not reopened.verify()["valid"] and reopened.verify()["line"] == 0
