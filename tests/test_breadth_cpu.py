@@ -5343,3 +5343,95 @@ def test_vision_tools_drawing_annotations_attribution_tiling_video_flow_stabilis
         V.decode_apng(data[:40] + bytes([data[40] ^ 1]) + data[41:])
     bt = V.benchmark_transforms({"flip": lambda t: t.flip(-1), "half": lambda t: t[:, ::2, ::2]}, torch.rand(3, 64, 64), iterations=3)
     assert bt["half"]["output_shape"] == (3, 32, 32) and bt["flip"]["images_per_s"] > 0
+
+
+def test_quantization_adaptive_patterns_fused_blocks_engine_codec_autoconfig_and_annealing():
+    from torsh_b200 import quantization_adaptive as A
+    torch.manual_seed(0)
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.c1, self.b1, self.r1 = torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.BatchNorm2d(8), torch.nn.ReLU()
+            self.c2, self.b2 = torch.nn.Conv2d(8, 8, 3, padding=1), torch.nn.BatchNorm2d(8)
+            self.r2, self.pool, self.fc, self.act, self.out = torch.nn.ReLU(), torch.nn.AdaptiveAvgPool2d(1), torch.nn.Linear(8, 16), torch.nn.GELU(), torch.nn.Linear(16, 4)
+        def forward(self, x):
+            h = self.r1(self.b1(self.c1(x)))
+            h = self.r2(self.b2(self.c2(h)) + h)
+            return self.out(self.act(self.fc(torch.flatten(self.pool(h), 1))))
+    net = Net().eval()
+    with torch.no_grad():
+        for bn in (net.b1, net.b2):
+            bn.running_mean.normal_(0, 0.2); bn.running_var.uniform_(0.5, 1.5); bn.weight.uniform_(0.5, 1.5); bn.bias.normal_(0, 0.2)
+    gm = torch.fx.symbolic_trace(net)
+    pm = A.PatternMatcher()
+    found = {m["pattern"]: m["nodes"] for m in pm.match(gm)}
+    assert found == {"conv_bn_relu": ["c1", "b1", "r1"], "conv_bn": ["c2", "b2"], "add_relu": ["add", "r2"], "linear_relu": ["fc", "act"], "linear": ["out"]}
+    cov = pm.coverage(gm)
+    assert cov["unmatched"] == ["pool", "flatten"] and cov["fraction"] == pytest.approx(10 / 12)
+    only_wide = A.PatternMatcher([A.GraphPattern("wide_linear", ("Linear",), constraints=[lambda chain, mods: mods[chain[0].target].out_features >= 16])])
+    assert [m["nodes"] for m in only_wide.match(gm)] == [["fc"]]
+    # rewriting: fused int8 blocks stay close to the float model
+    x = torch.randn(4, 3, 12, 12)
+    qgm, done = A.fuse_and_quantize(net)
+    assert {d["pattern"] for d in done} == {"conv_bn_relu", "conv_bn", "linear_relu", "linear"} and not any(isinstance(m, torch.nn.BatchNorm2d) for m in qgm.modules()) and sum(isinstance(m, A.FusedQuantBlock) for m in qgm.modules()) == 4
+    ref, got = net(x).detach(), qgm(x).detach()
+    assert float((got - ref).norm() / ref.norm()) < 0.05 and qgm.fused_c1.qweight.dtype == torch.int8 and qgm.fused_c1.act is not None and qgm.fused_c2.act is None
+    q4, _ = A.fuse_and_quantize(net, bits=4)
+    assert float((q4(x).detach() - ref).norm() / ref.norm()) > float((got - ref).norm() / ref.norm())
+    # run-time engine
+    feats = A.tensor_features(torch.tensor([0.0, 0.0, 1.0, -1.0, 8.0]))
+    assert feats["sparsity"] == pytest.approx(0.4) and feats["abs_max"] == 8.0 and feats["numel"] == 5 and feats["dynamic_range_db"] == pytest.approx(20 * math.log10(8))
+    eng = A.AdaptiveQuantizationEngine(A.AdaptiveQuantConfig(candidate_bits=(4, 6, 8), min_sqnr_db=28.0, target_mean_bits=8.0))
+    g = torch.Generator().manual_seed(0)
+    r = eng.quantize(torch.randn(4096, generator=g))
+    assert r["bits"] in (6, 8) and r["sqnr_db"] > 25 and abs(r["sqnr_db"] - r["predicted_db"]) < 6 and r["q"].dtype == torch.int8
+    lax = A.AdaptiveQuantizationEngine(A.AdaptiveQuantConfig(min_sqnr_db=12.0, target_mean_bits=4.0))
+    assert lax.quantize(torch.randn(4096, generator=g))["bits"] == 4
+    heavy = torch.randn(4096, generator=g); heavy[::512] *= 40
+    clipped, plain = A.AdaptiveQuantizationEngine(A.AdaptiveQuantConfig(candidate_bits=(8,))), A.AdaptiveQuantizationEngine(A.AdaptiveQuantConfig(candidate_bits=(8,), clip_outliers=False))
+    core = heavy.abs() < 4
+    e_clip, e_plain = (clipped.quantize(heavy)["dequantized"] - heavy)[core].pow(2).mean(), (plain.quantize(heavy)["dequantized"] - heavy)[core].pow(2).mean()
+    assert e_clip < e_plain / 4
+    ctl = A.AdaptiveQuantizationEngine(A.AdaptiveQuantConfig(candidate_bits=(4, 6, 8), min_sqnr_db=45.0, target_mean_bits=5.0))
+    for _ in range(60):
+        ctl.quantize(torch.randn(2048, generator=g))
+    s = ctl.summary()
+    assert s["floor_db"] < 45.0 and s["mean_bits"] < 8.0 and len(s["bits_histogram"]) >= 2
+    det = A.AdaptiveQuantizationEngine(A.AdaptiveQuantConfig(candidate_bits=(8,), degradation_window=10, degradation_drop_db=5.0))
+    for i in range(40):
+        t = torch.randn(2048, generator=g)
+        if i >= 20:
+            t[0] = 2000.0                                                             # an outlier the fixed 8 bits now have to cover
+            det.cfg.clip_outliers = False
+        det.quantize(t)
+    assert det.summary()["alerts"] >= 1 and det.alerts[0]["drop_db"] > 5
+    # learned codec
+    weights = [torch.randn(64, 64, generator=g) * 0.1, torch.randn(32, 48, generator=g) * 0.1]
+    codec = A.NeuralCodec(block=8, latent=4, codebook=256, hidden=32)
+    hist = codec.fit(weights, steps=400, generator=g)
+    c = codec.compress(weights[0])
+    back = codec.decompress(c)
+    rel = float((back - weights[0]).norm() / weights[0].norm())
+    assert hist[-1] < hist[0] and back.shape == weights[0].shape and c["ratio"] == 32.0 and c["payload_bits"] == 8 * 512 and rel < 0.85
+    structured = [torch.outer(torch.randn(64, generator=g), torch.ones(64)) * 0.1]
+    codec2 = A.NeuralCodec(block=8, latent=2, codebook=64, hidden=32)
+    codec2.fit(structured, steps=400, generator=g)
+    assert float((codec2.decompress(codec2.compress(structured[0])) - structured[0]).norm() / structured[0].norm()) < 0.2
+    odd = torch.randn(5, 7, generator=g) * 0.1
+    assert codec.decompress(codec.compress(odd)).shape == (5, 7) and codec.compress(odd)["pad"] == 5
+    # automatic configuration
+    model = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.ReLU(), torch.nn.Linear(128, 128), torch.nn.ReLU(), torch.nn.Linear(128, 10))
+    auto = A.AutoConfigurator(A.HardwareConstraints(supported_bits=(4, 8, 16), max_error_db=30.0))
+    cfg = auto.configure(model)
+    assert set(cfg["bits"].values()) == {8} and cfg["fits"] and cfg["min_sqnr_db"] >= 30 and cfg["estimated_speedup"] == pytest.approx(2.0) and cfg["table"]["0.weight"][4]["sqnr_db"] < 30 < cfg["table"]["0.weight"][8]["sqnr_db"] < cfg["table"]["0.weight"][16]["sqnr_db"]
+    tight = A.AutoConfigurator(A.HardwareConstraints(memory_bytes=0.7 * cfg["bytes"], supported_bits=(4, 8, 16), max_error_db=30.0)).configure(model)
+    assert tight["fits"] and 4 in tight["bits"].values() and tight["relaxed_layers"] and tight["bytes"] <= 0.7 * cfg["bytes"] and tight["estimated_speedup"] > 2.0
+    assert not A.AutoConfigurator(A.HardwareConstraints(memory_bytes=100.0, supported_bits=(4, 8))).configure(model)["fits"]
+    front = auto.pareto_front(model)
+    assert [c["name"] for c in front][0] == "uniform-4" and front[-1]["name"] == "uniform-16" and all(a["bytes"] < b["bytes"] and a["min_sqnr_db"] < b["min_sqnr_db"] for a, b in zip(front, front[1:]))
+    # annealing: sensitive layers get more bits, the budget holds, and the result beats a uniform split
+    sizes, sens = [1000, 1000, 1000, 1000], [100.0, 1.0, 0.01, 10.0]
+    res = A.anneal_bit_allocation(sizes, sens, budget_bits=4 * 1000 * 4.5, choices=(2, 4, 8))
+    uniform4 = sum(s * 4.0 ** -4 for s in sens)
+    assert res["feasible"] and res["bits"][0] == 8 and res["bits"][2] == 2 and res["cost"] < uniform4 and res["used_bits"] <= 18000
+    assert A.anneal_bit_allocation(sizes, sens, budget_bits=8000, choices=(2, 4, 8), schedule="linear")["bits"] == [2, 2, 2, 2] and A.anneal_bit_allocation(sizes, sens, budget_bits=1e9, schedule="logarithmic", steps=6000)["bits"] == [8, 8, 8, 8]
