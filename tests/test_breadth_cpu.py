@@ -5435,3 +5435,108 @@ def test_quantization_adaptive_patterns_fused_blocks_engine_codec_autoconfig_and
     uniform4 = sum(s * 4.0 ** -4 for s in sens)
     assert res["feasible"] and res["bits"][0] == 8 and res["bits"][2] == 2 and res["cost"] < uniform4 and res["used_bits"] <= 18000
     assert A.anneal_bit_allocation(sizes, sens, budget_bits=8000, choices=(2, 4, 8), schedule="linear")["bits"] == [2, 2, 2, 2] and A.anneal_bit_allocation(sizes, sens, budget_bits=1e9, schedule="logarithmic", steps=6000)["bits"] == [8, 8, 8, 8]
+
+
+def test_fx_deploy_torchscript_custom_ops_types_cloud_manifests_accelerators_spiking_and_quantum_layer():
+    import yaml
+    from torsh_b200 import fx_deploy as D
+    torch.manual_seed(0)
+    # TorchScript round trip
+    net = torch.nn.Sequential(torch.nn.Linear(6, 8), torch.nn.ReLU(), torch.nn.Linear(8, 3))
+    gm = torch.fx.symbolic_trace(net)
+    x = torch.randn(4, 6)
+    sm = D.to_torchscript(gm, [x])
+    desc = D.describe_torchscript(sm)
+    assert torch.allclose(sm(x), net(x)) and desc["operators"]["aten::linear"] == 2 and desc["operators"]["aten::relu"] == 1 and len(desc["inputs"]) == 1
+    back = D.from_torchscript(sm, [x])
+    assert torch.allclose(back(x), net(x)) and [n.op for n in back.graph.nodes] == ["placeholder", "call_module", "output"]
+    # custom operations
+    reg = D.CustomOperationRegistry()
+    swish2 = reg.register("swish2", lambda t: t * torch.sigmoid(2 * t), infer_shape=lambda s: s, cost=lambda s: 4.0 * math.prod(s), doc="x sigmoid(2x)")
+    clipped = reg.register("clipped_identity", lambda t: t.clamp(-1, 1), backward=lambda g, t: g)       # straight-through gradient
+    with pytest.raises(ValueError):
+        reg.register("swish2", lambda t: t)
+    def fn(a): return clipped(swish2(a) + 1.0)
+    cg = torch.fx.symbolic_trace(fn)
+    assert reg.nodes_in(cg) == ["swish2", "clipped_identity"] and torch.allclose(cg(x), (x * torch.sigmoid(2 * x) + 1).clamp(-1, 1))
+    assert reg.infer_shapes(cg, [(4, 6)])["clipped_identity"] == (4, 6) and reg.total_cost(cg, [(4, 6)]) == 96.0
+    xr = (torch.randn(5) * 3).requires_grad_(True)
+    clipped(xr).sum().backward()
+    assert torch.equal(xr.grad, torch.ones(5))
+    reg.unregister("swish2")
+    assert "swish2" not in reg.ops
+    # custom types
+    types = D.CustomTypeRegistry().with_defaults()
+    t = torch.randn(1000)
+    assert types.roundtrip_error("fixed<16,8>", t) < types.roundtrip_error("fixed<8,4>", t) < 0.05 and types.roundtrip_error("log8", t) < 0.05 and types.roundtrip_error("bfp16x8", t) < 0.02 and types.types["bfp16x8"].bits == 8.5
+    assert types.types["fixed<8,4>"].validate(types.types["fixed<8,4>"].pack(t * 100)) and float(types.types["fixed<8,4>"].unpack(types.types["fixed<8,4>"].pack(torch.tensor([100.0])))) == pytest.approx(127 / 16)
+    ann = {"_0": ("float32", "fixed<8,4>"), "_1": ("fixed<8,4>", "fixed<8,4>"), "_2": ("float32", "float32")}
+    issues = types.check_graph(gm, ann)
+    assert issues == [{"edge": ("_1", "_2"), "producer": "fixed<8,4>", "consumer": "float32"}]
+    types.register_conversion("fixed<8,4>", "float32", types.types["fixed<8,4>"].unpack)
+    assert types.check_graph(gm, ann) == []
+    # cloud deployment
+    spec = D.ServingSpec("llm", "registry.local/llm:1", "/models/llm.safetensors", gpus_per_replica=2, max_batch=16, max_replicas=12)
+    docs = list(yaml.safe_load_all(D.kubernetes_manifests(spec)))
+    assert [d["kind"] for d in docs] == ["Deployment", "Service", "HorizontalPodAutoscaler"] and docs[0]["spec"]["template"]["spec"]["containers"][0]["resources"]["limits"]["nvidia.com/gpu"] == 2 and docs[2]["spec"]["maxReplicas"] == 12 and docs[1]["spec"]["ports"][0]["targetPort"] == 8080
+    df = D.dockerfile(spec, extra_packages=["einops"])
+    assert df.startswith("FROM nvcr.io") and "pip install --no-cache-dir einops" in df and "EXPOSE 8080" in df and "HEALTHCHECK" in df
+    plan = D.plan_capacity(400.0, {1: 12.0, 4: 20.0, 8: 30.0, 16: 60.0, 32: 110.0}, slo_ms=50.0, spec=spec)
+    assert plan["batch"] == 8 and plan["replica_qps"] == pytest.approx(8 / 0.03) and plan["replicas"] == 2 and plan["instances"] == 1 and plan["feasible"] and plan["monthly_cost"] == pytest.approx(98.0 * 730) and 0.7 < plan["utilisation"] < 0.8
+    assert not D.plan_capacity(10.0, {1: 80.0}, slo_ms=50.0, spec=spec)["feasible"] and not D.plan_capacity(50000.0, {8: 30.0}, slo_ms=50.0, spec=spec)["feasible"]
+    # accelerators
+    cnn = torch.nn.Sequential(torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.ReLU(), torch.nn.Flatten(), torch.nn.Linear(8 * 8 * 8, 10)).eval()
+    cgm = torch.fx.symbolic_trace(cnn)
+    img = torch.randn(2, 3, 8, 8)
+    mp = D.map_to_accelerator(cgm, img, D.ACCELERATORS["analog_in_memory"])
+    assert mp["on_accelerator"] == ["_0", "_3"] and mp["on_host"] == ["_1", "_2"] and mp["macs_on"] == 2 * 8 * 64 * 27 + 2 * 10 * 512 and mp["boundary_bytes"] == 2 * 512 * 2 and mp["energy_saving"] > 0.8
+    npu = D.map_to_accelerator(cgm, img, D.ACCELERATORS["digital_npu"])
+    assert "_1" in npu["on_accelerator"] and npu["boundary_bytes"] < mp["boundary_bytes"] + 1 and D.map_to_accelerator(cgm, img, D.ACCELERATORS["photonic"])["on_accelerator"] == ["_3"]
+    g = torch.Generator().manual_seed(0)
+    clean = D.evaluate_with_device_noise(cnn, img, D.AcceleratorModel("ideal", ("Linear", "Conv2d"), 16, 16, 0.0), trials=2, generator=g)
+    noisy = D.evaluate_with_device_noise(cnn, img, D.ACCELERATORS["analog_in_memory"], trials=4, generator=g)
+    assert clean["mean_deviation"] < 1e-3 < noisy["mean_deviation"] < 0.5 and noisy["worst_deviation"] >= noisy["mean_deviation"] and clean["argmax_agreement"] == 1.0
+    # spiking conversion approaches the rectifier network as the number of steps grows
+    mlp = torch.nn.Sequential(torch.nn.Linear(10, 32), torch.nn.ReLU(), torch.nn.Linear(32, 32), torch.nn.ReLU(), torch.nn.Linear(32, 5)).eval()
+    data = torch.rand(64, 10)
+    snn = D.SpikingNetwork(mlp, data, percentile=99.9)
+    with torch.no_grad():
+        ref = mlp(data)
+        o16, s16 = snn(data, steps=16)
+        o256, s256 = snn(data, steps=256)
+    e16, e256 = float((o16 - ref).norm() / ref.norm()), float((o256 - ref).norm() / ref.norm())
+    assert e256 < 0.05 < e16 and e256 < e16 / 3 and float((o256.argmax(1) == ref.argmax(1)).float().mean()) > 0.9 and 0 < s256["spikes_per_neuron_per_step"] < 1 and s256["neurons"] == 64 and len(snn.scales) == 2
+    en = D.snn_energy_estimate(s16, synaptic_ops_per_spike=32, ann_macs=64 * (10 * 32 + 32 * 32 + 32 * 5))
+    assert en["snn_energy_pj"] > 0 and en["ratio"] == pytest.approx(en["snn_energy_pj"] / en["ann_energy_pj"])
+    # variational quantum layer: probabilities stay normalised, gradients flow, a small regression is learnable
+    vq = D.VariationalQuantumLayer(n_qubits=3, depth=2)
+    inp = torch.rand(16, 3) * math.pi
+    out = vq(inp)
+    assert out.shape == (16, 3) and float(out.detach().abs().max()) <= 1.0 + 1e-5 and vq.circuit_summary() == {"qubits": 3, "depth": 2, "parameters": 12, "two_qubit_gates": 6, "single_qubit_gates": 15}
+    with torch.no_grad():
+        vq0 = D.VariationalQuantumLayer(2, 1); vq0.theta.zero_()
+        z = vq0(torch.tensor([[0.0, 0.0], [math.pi, 0.0], [math.pi / 2, math.pi]]))
+    assert torch.allclose(z, torch.tensor([[1.0, 1.0], [1.0, -1.0], [-1.0, 0.0]]), atol=1e-5)     # CNOT ring: (q0 -> q1) then (q1 -> q0)
+    th = vq.theta.detach().clone().requires_grad_(True)
+    def f(theta):
+        vq.theta.data = theta.data
+        return vq(inp).sum()
+    loss = vq(inp).sum(); loss.backward()
+    shift = torch.zeros_like(vq.theta); shift[0, 1, 0] = math.pi / 2
+    with torch.no_grad():
+        base = vq.theta.detach().clone()
+        vq.theta.copy_(base + shift); plus = vq(inp).sum()
+        vq.theta.copy_(base - shift); minus = vq(inp).sum()
+        vq.theta.copy_(base)
+    assert float(vq.theta.grad[0, 1, 0]) == pytest.approx(float((plus - minus) / 2), abs=1e-4)
+    target = torch.cos(inp[:, :1])
+    model = torch.nn.Sequential(D.VariationalQuantumLayer(2, 2), torch.nn.Linear(2, 1))
+    opt = torch.optim.Adam(model.parameters(), lr=0.1)
+    first = None
+    for _ in range(150):
+        l = torch.nn.functional.mse_loss(model(inp[:, :2]), target)
+        first = first if first is not None else float(l.detach())
+        opt.zero_grad(); l.backward(); opt.step()
+    assert float(l.detach()) < 0.05 * first
+    with pytest.raises(ValueError):
+        D.VariationalQuantumLayer(13)
