@@ -5540,3 +5540,121 @@ def test_fx_deploy_torchscript_custom_ops_types_cloud_manifests_accelerators_spi
     assert float(l.detach()) < 0.05 * first
     with pytest.raises(ValueError):
         D.VariationalQuantumLayer(13)
+
+
+def test_graph_learning_continuous_time_lottery_tickets_and_pretraining():
+    from torsh_b200 import graph_learning as G
+    from torsh_b200.graph import GCN, stochastic_block_model
+    torch.manual_seed(0)
+    # time encoding: inner products depend on the time difference only (zero phases)
+    te = G.TimeEncoder(32)
+    t = torch.tensor([0.0, 5.0, 100.0, 105.0])
+    e = te(t)
+    e = e.detach()
+    assert e.shape == (4, 32) and float(e[0] @ e[0]) == pytest.approx(32.0) and float((e[0] * e[1]).sum() - (e[2] * e[3]).sum()) != 0 and float(e.abs().max()) <= 1.0
+    w = te.w.detach()
+    assert float((torch.cos(5.0 * w)).sum()) == pytest.approx(float(((torch.cos(100 * w) * torch.cos(105 * w)) + (torch.sin(100 * w) * torch.sin(105 * w))).sum()), rel=1e-4)
+    store = G.TemporalNeighborStore(k=2)
+    store.insert(0, 1, 1.0, 0); store.insert(0, 2, 2.0, 1); store.insert(0, 3, 3.0, 2)
+    assert [u for u, _, _ in store.recent(0, 10.0)] == [2, 3] and store.recent(0, 2.5) == [(2, 2.0, 1)] and store.recent(3, 3.0) == []
+    att = G.TemporalAttentionLayer(8, 4, 8, 16)
+    hs, hn, en, dt = torch.randn(3, 8), torch.randn(3, 5, 8), torch.randn(3, 5, 4), torch.rand(3, 5)
+    mask = torch.tensor([[True] * 5, [True, True, False, False, False], [False] * 5])
+    out = att(hs, hn, en, dt, mask)
+    hn2 = hn.clone(); hn2[1, 3] += 10                                               # a masked neighbour does not matter
+    assert out.shape == (3, 16) and torch.allclose(att(hs, hn2, en, dt, mask), out, atol=1e-6) and torch.isfinite(out).all()
+    # event stream with a repeating pattern: node i talks to node (i + 1) mod n; the model learns to rank the true partner
+    n = 8
+    g = torch.Generator().manual_seed(0)
+    def stream(T):
+        src = torch.randint(0, n, (T,), generator=g)
+        return src, (src + 1) % n, torch.arange(T, dtype=torch.float32), torch.ones(T, 2)
+    model = G.ContinuousTimeGraphNetwork(n, edge_dim=2, memory_dim=16, time_dim=8, embed_dim=16, neighbors=5)
+    opt = torch.optim.Adam(model.parameters(), lr=5e-3)
+    def run(train: bool, T=200, batch=20):
+        model.reset_state()
+        src, dst, tt, ef = stream(T)
+        correct = total = 0
+        for s in range(0, T, batch):
+            sl = slice(s, s + batch)
+            neg = (dst[sl] + torch.randint(1, n - 1, (len(src[sl]),), generator=g)) % n
+            pos_s, neg_s = model.score(src[sl], dst[sl], tt[sl]), model.score(src[sl], neg, tt[sl])
+            if train:
+                loss = torch.nn.functional.binary_cross_entropy_with_logits(pos_s, torch.ones_like(pos_s)) + torch.nn.functional.binary_cross_entropy_with_logits(neg_s, torch.zeros_like(neg_s))
+                opt.zero_grad(); loss.backward(); opt.step()
+            if s >= T // 2:
+                correct += int((pos_s > neg_s).sum()); total += len(pos_s)
+            with torch.no_grad() if not train else torch.enable_grad():
+                model.update(src[sl], dst[sl], tt[sl], ef[sl])
+            model.detach_state()
+        return correct / total
+    before = run(False)
+    for _ in range(6):
+        run(True)
+    after = run(False)
+    assert after > 0.85 and after > before + 0.2 and model.memory.abs().sum() > 0 and len(model.edge_feats) == 200
+    # graph ODE: heat diffusion matches the matrix exponential, conserves the degree-weighted mean, and smooths
+    ei = torch.tensor([[0, 1, 2, 3, 4, 0], [1, 2, 3, 4, 5, 5]])
+    h0 = torch.randn(6, 3, dtype=torch.float64)
+    ode = G.GraphODE(mode="heat", steps=40)
+    L = G.GraphODE.laplacian(ei, 6).double()
+    assert torch.allclose(ode(h0, ei, t=1.5), torch.linalg.matrix_exp(-1.5 * L) @ h0, atol=1e-6)
+    rough = lambda h: float((h.T @ L @ h).trace())
+    assert rough(ode(h0, ei, 3.0)) < 0.2 * rough(h0) and torch.allclose(ode(h0, ei, 0.0), h0)
+    learned = G.GraphODE(dim=3, mode="gcn", steps=8)
+    y = learned(h0.float(), ei, t=1.0)
+    y.sum().backward()
+    assert y.shape == (6, 3) and learned.conv.lin.weight.grad.abs().sum() > 0 and learned.gate.grad is not None
+    # lottery ticket on a two-block graph
+    data = stochastic_block_model(sizes=(30, 30), p_in=0.3, p_out=0.02, feat=8, seed=1)
+    net = GCN(8, 16, 2)
+    lt = G.GraphLotteryTicket(net, data.edge_index, weight_rate=0.3, edge_rate=0.1)
+    init = {k: v.clone() for k, v in net.state_dict().items()}
+    def train(model, edges, reapply):
+        opt = torch.optim.Adam(model.parameters(), lr=0.05)
+        for _ in range(60):
+            loss = torch.nn.functional.cross_entropy(model(data.x, edges), data.y)
+            opt.zero_grad(); loss.backward(); opt.step(); reapply()
+        return float((model(data.x, edges).argmax(1) == data.y).float().mean())
+    def importance(model, edges):
+        with torch.no_grad():
+            z = model(data.x, edges)
+        return (z[edges[0]] * z[edges[1]]).sum(1)                                   # edges inside a block agree, edges across disagree
+    recs = [lt.round(train, importance) for _ in range(4)]
+    assert recs[-1]["weight_sparsity"] == pytest.approx(1 - 0.7 ** 4, abs=0.02) and recs[-1]["edge_sparsity"] == pytest.approx(1 - 0.9 ** 4, abs=0.02) and recs[-1]["score"] > 0.9 and recs[0]["score"] > 0.9
+    for name, p in net.named_parameters():
+        if name in lt.masks:
+            assert torch.equal(p.detach(), init[name] * lt.masks[name]) and float((p == 0).float().mean()) >= recs[-1]["weight_sparsity"] - 0.3
+    cross = (data.y[data.edge_index[0]] != data.y[data.edge_index[1]])
+    assert float(cross[lt.edge_mask].float().mean()) < float(cross.float().mean()) and lt.masked_edges().shape[1] == int(lt.edge_mask.sum())
+    # augmentations
+    x, edges = data.x, data.edge_index
+    gen = torch.Generator().manual_seed(0)
+    xd, ed = G.augment_graph(x, edges, "node_drop", 0.3, gen)
+    assert 30 <= xd.shape[0] <= 52 and int(ed.max()) < xd.shape[0] and ed.shape[1] < edges.shape[1]
+    xp, ep = G.augment_graph(x, edges, "edge_perturb", 0.2, gen)
+    assert ep.shape == edges.shape and not torch.equal(ep, edges) and torch.equal(xp, x)
+    xm, em = G.augment_graph(x, edges, "feature_mask", 0.5, gen)
+    assert torch.equal(em, edges) and 1 <= int((xm.abs().sum(0) == 0).sum()) <= 7
+    xs, es = G.augment_graph(x, edges, "subgraph", 0.5, gen)
+    assert xs.shape[0] == 30 and int(es.max()) < 30
+    with pytest.raises(ValueError):
+        G.augment_graph(x, edges, "rotate")
+    z = torch.randn(6, 4)
+    assert float(G.nt_xent(z, z + 0.01 * torch.randn(6, 4), 0.1)) < float(G.nt_xent(z, torch.randn(6, 4), 0.1))
+    # pre-training, then prompt tuning on the frozen encoder
+    enc = G.GraphEncoder(8, 16)
+    graphs = [(stochastic_block_model((15, 15), 0.4, 0.02, 8, seed=s).x, stochastic_block_model((15, 15), 0.4, 0.02, 8, seed=s).edge_index) for s in range(4)]
+    hist = G.pretrain_contrastive(enc, graphs, steps=30, generator=gen)
+    assert sum(hist[-5:]) / 5 < sum(hist[:5]) / 5
+    smooth_x = torch.cat([torch.randn(1, 8).expand(30, 8), torch.randn(1, 8).expand(30, 8)]) + 0.05 * torch.randn(60, 8)
+    mh = G.pretrain_masked_features(enc, smooth_x, data.edge_index, steps=150, generator=gen)
+    assert sum(mh[-10:]) / 10 < 0.3 * sum(mh[:10]) / 10
+    frozen = {k: v.clone() for k, v in enc.state_dict().items()}
+    pt = G.GraphPromptTuning(enc, 8, 2)
+    assert pt.trainable_parameters() == 8 + 16 * 2 + 2
+    opt = torch.optim.Adam([p for p in pt.parameters() if p.requires_grad], lr=0.05)
+    for _ in range(100):
+        loss = torch.nn.functional.cross_entropy(pt(data.x, data.edge_index), data.y)
+        opt.zero_grad(); loss.backward(); opt.step()
+    assert float((pt(data.x, data.edge_index).argmax(1) == data.y).float().mean()) > 0.9 and all(torch.equal(frozen[k], v) for k, v in enc.state_dict().items()) and pt.prompt.abs().sum() > 0
