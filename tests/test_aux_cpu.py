@@ -2566,3 +2566,107 @@ def test_package_infra_lockfile_installer_cdn_object_store_syslog_and_audit_stor
     seg = reopened._file(reopened._segments()[0])
     seg.write_text(seg.read_text().replace('"success"', '"failure"', 1))
     assert not reopened.verify()["valid"] and reopened.verify()["line"] == 0
+
+
+def test_core_shapes_symbolic_inference_shape_graph_indexing_typed_signatures_allocation_analysis_and_capabilities():
+    from torsh_b200.core import shapes_ext as S
+    # symbolic arithmetic
+    n, d = S.Sym.dim("n"), S.Sym.dim("d")
+    assert repr(n * 2) == repr(2 * n) == "(2 * n)" and (n * 2) == (2 * n) and (n + 0) == n and (n * 1) == n and (n * 0) == 0 and (n - n) == 0 and (n // n) == 1 and ((n * d) // d) == n and (S.Sym.lift(6) * 7) == 42
+    assert (n * d + 3).evaluate({"n": 4, "d": 5}) == 23 and (n * d + 3).free() == {"n", "d"} and ((n + 7) // 2 % 3).evaluate({"n": 10}) == 2 and hash(n * 2) == hash(2 * n)
+    with pytest.raises(KeyError):
+        (n + 1).evaluate({})
+    # unification
+    env = S.ShapeEnv().constrain("n", 1, 1024)
+    env.unify(n, 128); env.unify(d, n * 2)
+    assert env.resolve(d) == 256 and env.concrete([n, d, 3]) == (128, 256, 3)
+    with pytest.raises(ValueError, match="violates its range"):
+        S.ShapeEnv().constrain("n", 1, 64).unify(n, 128)
+    with pytest.raises(ValueError, match="shape mismatch in test: 3 != 4"):
+        S.ShapeEnv().unify(3, 4, "test")
+    with pytest.raises(ValueError, match="occurs"):
+        S.ShapeEnv().unify(n, n + 1)
+    with pytest.raises(KeyError, match="unbound"):
+        S.ShapeEnv().concrete([n])
+    late = S.ShapeEnv(); late.unify(n * 2, d + 2)
+    late.unify(n, 5); late.unify(d, 8)
+    assert late.concrete([n, d]) == (5, 8)
+    bad = S.ShapeEnv(); bad.unify(n * 2, d + 2); bad.unify(n, 5); bad.unify(d, 9)
+    with pytest.raises(ValueError, match="shape mismatch"):
+        bad.concrete([n])
+    # inference rules against real tensors
+    B, T, D, K = S.sym_shape("B", "T", "D", "K")
+    e = S.ShapeEnv()
+    assert S.infer_shape("matmul", e, (B, T, D), (D, K)) == (B, T, K) and S.infer_shape("linear", e, (B, T, D), (K, D)) == (B, T, K) and S.infer_shape("transpose", e, (B, T, D), dims=(0, 2)) == (D, T, B)
+    e2 = S.ShapeEnv()
+    out = S.infer_shape("matmul", e2, (B, 4, D), (S.Sym.dim("E"), 7))
+    assert e2.resolve(S.Sym.dim("E")) == D or e2.resolve(D) == S.Sym.dim("E")
+    assert S.infer_shape("broadcast", S.ShapeEnv(), (B, 1, D), (T, 1)) == (B, T, D) and S.infer_shape("cat", S.ShapeEnv(), (B, T, D), (B, K, D), dim=1) == (B, T + K, D) and S.infer_shape("flatten", S.ShapeEnv(), (B, 3, T, D)) == (B, 3 * T * D)
+    assert S.infer_shape("reduce", S.ShapeEnv(), (B, T, D), dim=1) == (B, D) and S.infer_shape("reduce", S.ShapeEnv(), (B, T, D), dim=1, keepdim=True) == (B, 1, D)
+    rs = S.infer_shape("reshape", S.ShapeEnv(), (B, T, 8, 64), shape=(B, T, -1))
+    assert rs == (B, T, 512)
+    conv = S.infer_shape("conv2d", S.ShapeEnv(), (B, 3, S.Sym.dim("H"), S.Sym.dim("W")), (64, 3, 7, 7), kernel=7, stride=2, padding=3)
+    ce = S.ShapeEnv()
+    assert ce.concrete([v if not isinstance(v, S.Sym) else v for v in [conv[0].evaluate({"B": 2}) if False else 2, conv[1], conv[2].evaluate({"H": 224}), conv[3].evaluate({"W": 200})]]) == tuple(torch.nn.Conv2d(3, 64, 7, 2, 3)(torch.zeros(2, 3, 224, 200)).shape)
+    assert S.infer_shape("pool2d", S.ShapeEnv(), (2, 8, 17, 17), kernel=3, stride=2, padding=1) == tuple(torch.nn.MaxPool2d(3, 2, 1)(torch.zeros(2, 8, 17, 17)).shape)
+    with pytest.raises(ValueError, match="conv2d channels"):
+        S.infer_shape("conv2d", S.ShapeEnv(), (1, 4, 8, 8), (8, 3, 3, 3))
+    # shape graph: an attention block
+    g = S.ShapeGraph()
+    g.input("x", "B", "T", "D"); g.input("wq", "D", "D"); g.input("wo", "D", "V")
+    g.op("q", "matmul", "x", "wq"); g.op("qt", "transpose", "q", dims=(1, 2)); g.op("scores", "matmul", "q", "qt"); g.op("ctx", "matmul", "scores", "q"); g.op("logits", "matmul", "ctx", "wo"); g.op("flat", "reshape", "logits", shape=(-1, S.Sym.dim("V")))
+    sym = g.infer()
+    assert [repr(v) for v in sym["scores"]] == ["B", "T", "T"] and [repr(v) for v in sym["flat"]] == ["(B * T)", "V"]
+    conc = g.specialize(B=2, T=5, D=16, V=100)
+    x, wq, wo = torch.zeros(2, 5, 16), torch.zeros(16, 16), torch.zeros(16, 100)
+    q = x @ wq
+    assert conc["scores"] == tuple((q @ q.transpose(1, 2)).shape) and conc["flat"] == (10, 100) and conc["logits"] == (2, 5, 100) and g.specialize(B=1, T=3, D=8, V=7)["flat"] == (3, 7)
+    g.infer()
+    assert g.cache_hits == 6 * 3 and g.explain("scores")[0] == "scores: [B, T, T] = matmul(q, qt)" and any(l.endswith("(input)") for l in g.explain("scores"))
+    # strides and indices
+    assert S.contiguous_strides((2, 3, 4)) == (12, 4, 1) == torch.empty(2, 3, 4).stride() and S.is_contiguous((2, 3, 4), (12, 4, 1)) and not S.is_contiguous((2, 3, 4), (1, 2, 6)) and S.is_contiguous((1, 3), (99, 1))
+    assert S.ravel_index((1, 2, 3), (2, 3, 4)) == 23 and S.unravel_index(23, (2, 3, 4)) == (1, 2, 3) and S.normalize_dim(-1, 3) == 2
+    with pytest.raises(IndexError):
+        S.normalize_dim(3, 3)
+    t = torch.arange(3.0).reshape(3, 1)
+    assert S.broadcast_strides((3, 1), t.stride(), (2, 3, 4)) == t.expand(2, 3, 4).stride()
+    with pytest.raises(ValueError):
+        S.broadcast_strides((3, 2), (2, 1), (3, 4))
+    assert S.can_view((4, 6), (6, 1), (24,)) and not S.can_view((4, 6), (1, 4), (24,)) and S.can_view((4, 6), (1, 4), (4, 2, 3))
+    # shape-annotated signatures
+    @S.typed_shapes("x: B T D, w: D K -> B T K")
+    def project(x, w): return x @ w
+    assert project(torch.zeros(2, 3, 4), torch.zeros(4, 5)).shape == (2, 3, 5) and project.shape_spec.startswith("x: B T D")
+    with pytest.raises(TypeError, match="w: dimension D = 6 but it was 4"):
+        project(torch.zeros(2, 3, 4), torch.zeros(6, 5))
+    with pytest.raises(TypeError, match="x: expected 3 dimensions"):
+        project(torch.zeros(3, 4), torch.zeros(4, 5))
+    @S.typed_shapes("x: ... 3, y: ... 3 -> ...")
+    def dot3(x, y): return (x * y).sum(-1)
+    assert dot3(torch.zeros(5, 2, 3), torch.zeros(5, 2, 3)).shape == (5, 2)
+    with pytest.raises(TypeError, match="dimension 3 expected"):
+        dot3(torch.zeros(5, 4), torch.zeros(5, 4))
+    with pytest.raises(TypeError, match="leading dimensions"):
+        dot3(torch.zeros(5, 3), torch.zeros(6, 3))
+    @S.typed_shapes("x: N -> N N")
+    def wrong(x): return x
+    with pytest.raises(TypeError, match="result: expected 2 dimensions"):
+        wrong(torch.zeros(4))
+    # allocation traces
+    ev, t_ = [], 0.0
+    for i in range(100):
+        ev.append(S.AllocEvent(t_, 256, "alloc", i)); ev.append(S.AllocEvent(t_ + 0.001, 256, "free", i)); t_ += 0.01
+    for i in range(100, 110):
+        ev.append(S.AllocEvent(t_, 1 << 20, "alloc", i)); t_ += 0.01
+    for i in range(100, 108):
+        ev.append(S.AllocEvent(t_ + 5, 1 << 20, "free", i))
+    rep = S.analyze_allocations(sorted(ev, key=lambda e: e.time))
+    kinds = [r["kind"] for r in rep["recommendations"]]
+    assert rep["peak_bytes"] == 10 << 20 and rep["leaked"] == 2 and rep["allocations"] == 110 and kinds[0] == "arena" and "free_list" in kinds and kinds[-1] == "leak_check" and rep["repeated_sizes"] == {256: 100, 1 << 20: 10}
+    assert rep["size_classes"][256]["count"] == 100 and rep["size_classes"][1 << 20]["median_lifetime"] > 4 and rep["small_short_fraction"] > 0.8
+    # capabilities
+    caps = S.detect_capabilities("processor : 0\nmodel name : Test CPU 9000\nflags : fpu sse4_2 avx avx2 fma avx512f avx512_bf16\n")
+    assert caps["cpu_model"] == "Test CPU 9000" and caps["simd"] == ["sse4_2", "avx", "avx2", "fma", "avx512f", "avx512_bf16"] and caps["best_simd_bits"] == 512 and caps["preferred_device"] in ("cpu", "cuda")
+    assert S.detect_capabilities("Features : fp asimd sve\n")["simd"] == ["neon", "sve"] and isinstance(S.detect_capabilities()["logical_cores"], int)
+    b200, h100, a100 = S.features_for_capability(10, 0), S.features_for_capability(9, 0), S.features_for_capability(8, 0)
+    assert b200["tcgen05_tensor_memory"] and not b200["wgmma"] and b200["arch_flag"] == "sm_100a" and h100["wgmma"] and h100["tma"] and not h100["tcgen05_tensor_memory"] and a100["bf16_tensor_cores"] and not a100["tma"] and a100["arch_flag"] == "sm_80" and a100["max_shared_memory_kb"] == 163
