@@ -5658,3 +5658,80 @@ def test_graph_learning_continuous_time_lottery_tickets_and_pretraining():
         loss = torch.nn.functional.cross_entropy(pt(data.x, data.edge_index), data.y)
         opt.zero_grad(); loss.backward(); opt.step()
     assert float((pt(data.x, data.edge_index).argmax(1) == data.y).float().mean()) > 0.9 and all(torch.equal(frozen[k], v) for k, v in enc.state_dict().items()) and pt.prompt.abs().sum() > 0
+
+
+def test_sparse_tools_kernels_profiler_memory_analysis_format_choice_and_locality():
+    import json
+    from torsh_b200 import sparse_tools as T
+    from torsh_b200.sparse import CooTensor
+    torch.manual_seed(0)
+    dense = torch.randn(40, 30) * (torch.rand(40, 30) < 0.15)
+    dense[7] = 0                                                                     # an empty row
+    csr = CooTensor.from_dense(dense).to_csr()
+    crow, col, val = csr.indptr, csr.indices, csr.values
+    B = torch.randn(30, 6)
+    # kernels against dense algebra
+    assert torch.allclose(T.csr_spmm(crow, col, val, B), dense @ B, atol=1e-5) and torch.allclose(T.csr_spmm_blocked(crow, col, val, B, row_block=7), dense @ B, atol=1e-5) and torch.allclose(T.csr_spmm(crow, col, val, B[:, 0]), dense @ B[:, 0], atol=1e-5)
+    Q, K = torch.randn(40, 8), torch.randn(30, 8)
+    mask = dense != 0
+    assert torch.allclose(T.sddmm(crow, col, Q, K), (Q @ K.T)[mask], atol=1e-5) and torch.allclose(T.sddmm(crow, col, Q, K, val), (Q @ K.T * dense)[mask], atol=1e-5)
+    sm = T.csr_row_softmax(crow, val)
+    ref = torch.where(mask, dense, torch.full_like(dense, -float("inf"))).softmax(1)
+    assert torch.allclose(sm, ref[mask], atol=1e-6) and torch.allclose(T.csr_row_reduce(crow, sm), mask.any(1).float(), atol=1e-6)
+    assert torch.allclose(T.csr_row_reduce(crow, val, "norm2"), dense.norm(dim=1), atol=1e-5) and torch.allclose(T.csr_row_reduce(crow, val, "max")[mask.any(1)], torch.where(mask, dense, torch.full_like(dense, -1e9)).max(1).values[mask.any(1)]) and T.csr_row_reduce(crow, val, "max")[7] == -float("inf")
+    out, keep = T.apply_with_threshold(val, torch.tanh, 0.5)
+    assert torch.equal(out, torch.tanh(val)) and torch.equal(keep, torch.tanh(val).abs() > 0.5)
+    V = torch.randn(30, 5)
+    scores = (Q @ K.T / 8 ** 0.5).masked_fill(~mask, -float("inf"))
+    att_ref = torch.nan_to_num(scores.softmax(1), nan=0.0) @ V
+    assert torch.allclose(T.sparse_attention(crow, col, Q, K, V), att_ref, atol=1e-5)
+    # profiler with a fake clock
+    now = [0.0]
+    prof = T.SparseProfiler(clock=lambda: now[0])
+    def work(cost): now[0] += cost; return cost
+    for i in range(10):
+        prof.track("spmm_csr", work, 0.010, nnz=1000)
+        prof.track("spmm_coo", work, 0.020 + 0.002 * i, nnz=1000)
+    s = prof.statistics("spmm_csr")
+    assert s["count"] == 10 and s["mean"] == pytest.approx(0.010) and s["consistent"] and s["nnz_per_second"] == pytest.approx(1e5) and prof.statistics("none") == {"count": 0}
+    assert prof.trend("spmm_coo")["direction"] == "degrading" and prof.trend("spmm_csr")["direction"] == "stable" and prof.fastest() == "spmm_csr" and prof.top_by_throughput(1) == ["spmm_csr"]
+    base = T.SparseProfiler()
+    for i in range(5):
+        base.add(T.Measurement("spmm_coo", 0.015, 1000, step=i)); base.add(T.Measurement("spmm_csr", 0.010, 1000, step=i))
+    reg = prof.detect_regressions(base)
+    assert [r["operation"] for r in reg] == ["spmm_coo"] and reg[0]["slowdown"] == pytest.approx(0.029 / 0.015)
+    assert prof.to_csv().splitlines()[0] == "operation,step,seconds,nnz,bytes" and len(prof.to_csv().splitlines()) == 21 and json.loads(prof.to_json())["summary"]["spmm_csr"]["count"] == 10 and "degrading" in prof.report() and prof.report().count("\n") == 2
+    # memory per format
+    assert T.format_bytes((100, 100), 500, "csr") == 500 * 12 + 101 * 8 and T.format_bytes((100, 100), 500, "coo") == 500 * 20 and T.format_bytes((100, 100), 500, "dense") == 40000 and T.format_bytes((100, 100), 500, "ell", max_row_nnz=9) == 100 * 9 * 12
+    tri = torch.diag(torch.ones(64)) * 2 + torch.diag(torch.ones(63), 1) + torch.diag(torch.ones(63), -1)
+    mt = T.analyze_memory(tri)
+    assert mt["most_compact"] == "dia" and mt["profile"]["diagonals"] == 3 and mt["profile"]["bandwidth"] == 1 and mt["compression_vs_dense"] > 15 and any("DIA" in r for r in mt["recommendations"])
+    blocky = torch.kron((torch.rand(16, 16) < 0.1).float(), torch.ones(4, 4)) * torch.randn(64, 64)
+    mb = T.analyze_memory(blocky)
+    assert mb["most_compact"] == "bsr" and mb["profile"]["block_fill"] > 0.95 and any("BSR" in r for r in mb["recommendations"])
+    skew = torch.zeros(64, 64); skew[0] = 1.0; skew[torch.arange(1, 64), torch.arange(1, 64)] = 1.0
+    ms = T.analyze_memory(skew)
+    assert ms["bytes"]["ell"] > 2 * ms["bytes"]["csr"] and any("ELL" in r for r in ms["recommendations"]) and ms["profile"]["max_row_nnz"] == 64
+    assert any("too dense" in r for r in T.analyze_memory(torch.randn(16, 16))["recommendations"])
+    # format choice
+    assert T.suggest_format(T.structure_profile(tri))["format"] == "dia" and T.suggest_format(T.structure_profile(blocky))["format"] == "bsr" and T.suggest_format(T.structure_profile(torch.randn(8, 8)))["format"] == "dense"
+    assert T.suggest_format(T.structure_profile(skew))["format"] == "csr" and T.suggest_format(T.structure_profile(skew), "build")["format"] == "coo" and T.suggest_format(T.structure_profile(skew), "transpose_matmul")["format"] == "csc"
+    regular = torch.zeros(64, 64)
+    for r in range(64):
+        regular[r, [(r * 7 + k * 13) % 64 for k in range(4)]] = 1.0
+    assert T.suggest_format(T.structure_profile(regular))["format"] == "ell"
+    cmp = T.compare_formats(dense[:, :28], torch.randn(28, 4), repeats=2)
+    assert set(cmp["results"]) == {"dense", "coo", "csr", "ell", "bsr"} and all(v["max_error"] < 1e-4 for v in cmp["results"].values()) and cmp["fastest"] == cmp["ranking"][0]
+    tuner = T.FormatAutoTuner()
+    assert tuner.choose(tri) == "dia" and tuner.trials == 0
+    first = tuner.choose(regular, torch.randn(64, 4), measure=True)
+    assert tuner.trials == 1 and tuner.choose(regular.roll(1, 0)) == first and tuner.trials == 1
+    tuner.learn(T.structure_profile(skew), "coo")
+    assert tuner.choose(skew) == "coo"
+    # locality
+    acc = T.benchmark_access_patterns(n=1 << 16, repeats=2, generator=torch.Generator().manual_seed(0))
+    assert acc["sequential"]["gb_per_s"] > 0 and acc["random_penalty"] > 0
+    band = CooTensor.from_dense(tri).to_csr()
+    scat = CooTensor.from_dense(regular).to_csr()
+    lb, ls = T.column_locality(band.indptr, band.indices), T.column_locality(scat.indptr, scat.indices)
+    assert lb["same_line_fraction"] == 1.0 and lb["mean_gap"] == 1.0 and ls["mean_gap"] > 10 and ls["same_line_fraction"] < lb["same_line_fraction"]
