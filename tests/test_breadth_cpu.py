@@ -5735,3 +5735,51 @@ def test_sparse_tools_kernels_profiler_memory_analysis_format_choice_and_localit
     scat = CooTensor.from_dense(regular).to_csr()
     lb, ls = T.column_locality(band.indptr, band.indices), T.column_locality(scat.indptr, scat.indices)
     assert lb["same_line_fraction"] == 1.0 and lb["mean_gap"] == 1.0 and ls["mean_gap"] > 10 and ls["same_line_fraction"] < lb["same_line_fraction"]
+
+
+def test_dynamic_linear_model_filter_smoother_forecast_and_likelihood_fit():
+    from torsh_b200.series_ext import DynamicLinearModel
+    g = torch.Generator().manual_seed(0)
+    # local level: with a huge signal-to-noise ratio the filter follows the data, with a tiny one it averages
+    y = torch.cumsum(torch.randn(200, generator=g, dtype=torch.float64) * 0.5, 0) + torch.randn(200, generator=g, dtype=torch.float64)
+    follow = DynamicLinearModel(1, obs_var=1e-6, level_var=1.0).filter(y)
+    flat = DynamicLinearModel(1, obs_var=1.0, level_var=1e-10).filter(y)
+    assert torch.allclose(follow["m"][:, 0], y, atol=1e-3) and float(flat["m"][-1, 0]) == pytest.approx(float(y.mean()), abs=1e-3)
+    # steady-state gain of the local level model: K = (-r + sqrt(r^2 + 4 r)) / 2 with r = W / V
+    dlm = DynamicLinearModel(1, obs_var=1.0, level_var=0.25)
+    f = dlm.filter(y)
+    r = 0.25
+    gain = (-r + math.sqrt(r * r + 4 * r)) / 2
+    assert float(f["C"][-1, 0, 0]) == pytest.approx(gain * 1.0, rel=1e-6)
+    sm = dlm.smooth(f)
+    assert float(sm["cov"][100, 0, 0]) < float(f["C"][100, 0, 0]) and torch.allclose(sm["state"][-1], f["m"][-1]) and float((sm["level"].diff() ** 2).mean()) < float((f["m"][:, 0].diff() ** 2).mean())
+    # the likelihood matches the sum of Gaussian one-step densities
+    ll = sum(-0.5 * (math.log(2 * math.pi * float(q)) + float(yy - p) ** 2 / float(q)) for yy, p, q in zip(y, f["pred"], f["pred_var"]))
+    assert float(f["loglik"]) == pytest.approx(ll, rel=1e-9)
+    # missing observations are skipped and the uncertainty grows over the gap
+    yg = y.clone(); yg[50:60] = float("nan")
+    fg = dlm.filter(yg)
+    assert float(fg["C"][59, 0, 0]) > 5 * float(fg["C"][49, 0, 0]) and torch.isfinite(fg["m"]).all()
+    # trend + seasonality: components are recovered and the forecast continues both
+    t = torch.arange(120, dtype=torch.float64)
+    season = torch.tensor([3.0, -1.0, -2.0, 0.0], dtype=torch.float64).repeat(30)
+    ys = 0.5 * t + season + 0.1 * torch.randn(120, generator=g, dtype=torch.float64)
+    m2 = DynamicLinearModel(2, seasonal_period=4, obs_var=0.01, level_var=1e-6, slope_var=1e-8, seasonal_var=1e-8)
+    f2 = m2.filter(ys); s2 = m2.smooth(f2)
+    assert m2.n == 5 and float(s2["slope"][60]) == pytest.approx(0.5, abs=0.01) and torch.allclose(s2["seasonal"][40:44], season[40:44], atol=0.15) and torch.allclose(s2["level"][20:100], 0.5 * t[20:100], atol=0.2)
+    fc = m2.forecast(f2, 8)
+    truth = 0.5 * torch.arange(120, 128, dtype=torch.float64) + season[:8]
+    assert torch.allclose(fc["mean"], truth, atol=0.3) and (fc["upper"] > fc["mean"]).all() and float(fc["std"][-1]) >= float(fc["std"][0])
+    # regression component with a time-invariant coefficient
+    X = torch.randn(150, 1, generator=g, dtype=torch.float64)
+    yr = 2.0 + 3.0 * X[:, 0] + 0.1 * torch.randn(150, generator=g, dtype=torch.float64)
+    m3 = DynamicLinearModel(1, regressors=1, obs_var=0.01, level_var=1e-8)
+    f3 = m3.filter(yr, X)
+    assert float(f3["m"][-1, 1]) == pytest.approx(3.0, abs=0.05) and float(f3["m"][-1, 0]) == pytest.approx(2.0, abs=0.05) and float(m3.forecast(f3, 1, torch.tensor([[2.0]]))["mean"][0]) == pytest.approx(8.0, abs=0.2)
+    # maximum likelihood recovers the variances of a simulated local level model
+    lvl = torch.cumsum(torch.randn(400, generator=g, dtype=torch.float64) * math.sqrt(0.3), 0)
+    obs = lvl + torch.randn(400, generator=g, dtype=torch.float64) * math.sqrt(2.0)
+    est = DynamicLinearModel(1, obs_var=1.0, level_var=1.0)
+    start_nll = -float(est.filter(obs)["loglik"])
+    res = est.fit(obs)
+    assert res["variances"]["obs"] == pytest.approx(2.0, rel=0.35) and res["variances"]["level"] == pytest.approx(0.3, rel=0.6) and res["neg_loglik"] < start_nll and res["signal_to_noise"] == pytest.approx(0.15, rel=0.8)

@@ -737,3 +737,121 @@ class TransformerForecaster(_WindowForecaster):
         self.head = nn.Linear(dim, horizon)
 
     def forward(self, x): return self.head(self.enc(self.inp(x[..., None]) + self.pos)[:, -1])
+
+
+# ================================================================================================ dynamic linear models
+class DynamicLinearModel:
+    """Structural time-series model in state-space form (``crates/torsh-series/src/state_space/dlm.rs``): the state stacks a
+    polynomial trend block (order 1 = local level, 2 = local linear trend), optional seasonal dummies of period ``s`` and
+    regression coefficients; ``y_t = F_t' x_t + v_t``, ``x_t = G x_{t-1} + w_t``.  Kalman filter, Rauch-Tung-Striebel smoother,
+    forecasts with intervals, the exact Gaussian log-likelihood and maximum-likelihood variances."""
+
+    def __init__(self, trend_order: int = 1, seasonal_period: int | None = None, regressors: int = 0, obs_var: float = 1.0, level_var: float = 0.1, slope_var: float = 0.01, seasonal_var: float = 0.01, reg_var: float = 0.0):
+        self.order, self.s, self.k = trend_order, seasonal_period, regressors
+        self.vars = {"obs": obs_var, "level": level_var, "slope": slope_var, "seasonal": seasonal_var, "reg": reg_var}
+        self.n = trend_order + ((seasonal_period - 1) if seasonal_period else 0) + regressors
+
+    def _matrices(self, v: dict | None = None):
+        v = v or self.vars
+        G, W, F = torch.zeros(self.n, self.n, dtype=torch.float64), torch.zeros(self.n, dtype=torch.float64), torch.zeros(self.n, dtype=torch.float64)
+        for i in range(self.order):
+            G[i, i:self.order] = 1.0
+        F[0] = 1.0
+        W = W.clone(); W[0] = v["level"]
+        Wd = [W[0]] + ([v["slope"]] * (self.order - 1))
+        pos = self.order
+        if self.s:
+            m = self.s - 1
+            G[pos, pos:pos + m] = -1.0
+            for i in range(1, m):
+                G[pos + i, pos + i - 1] = 1.0
+            F[pos] = 1.0
+            Wd += [v["seasonal"]] + [0.0] * (m - 1)
+            pos += m
+        for i in range(self.k):
+            G[pos + i, pos + i] = 1.0
+            Wd.append(v["reg"])
+        Wm = torch.diag(torch.stack([torch.as_tensor(w, dtype=torch.float64) for w in Wd]))
+        return G, Wm, F
+
+    def filter(self, y: torch.Tensor, X: torch.Tensor | None = None, variances: dict | None = None, m0: torch.Tensor | None = None, c0: float = 1e6) -> dict:
+        v = variances or self.vars
+        G, W, F0 = self._matrices(v)
+        y = y.double()
+        m, C = (m0.double() if m0 is not None else torch.zeros(self.n, dtype=torch.float64)), torch.eye(self.n, dtype=torch.float64) * c0
+        ms, Cs, as_, Rs, ll, preds, pvars = [], [], [], [], 0.0, [], []
+        for t in range(len(y)):
+            F = F0.clone()
+            if self.k:
+                F[self.n - self.k:] = X[t].double()
+            a, R = G @ m, G @ C @ G.T + W
+            f, q = F @ a, F @ R @ F + v["obs"]
+            preds.append(f); pvars.append(q)
+            if not torch.isnan(y[t]):
+                e = y[t] - f
+                A = R @ F / q
+                m, C = a + A * e, R - torch.outer(A, A) * q
+                ll = ll - 0.5 * (torch.log(2 * math.pi * q) + e * e / q)
+            else:
+                m, C = a, R
+            ms.append(m); Cs.append(C); as_.append(a); Rs.append(R)
+        return {"m": torch.stack(ms), "C": torch.stack(Cs), "a": torch.stack(as_), "R": torch.stack(Rs), "loglik": ll, "pred": torch.stack(preds), "pred_var": torch.stack(pvars), "G": G, "F": F0}
+
+    def smooth(self, filt: dict) -> dict:
+        m, C, a, R, G = filt["m"], filt["C"], filt["a"], filt["R"], filt["G"]
+        sm, sC = [m[-1]], [C[-1]]
+        for t in range(len(m) - 2, -1, -1):
+            B = C[t] @ G.T @ torch.linalg.inv(R[t + 1])
+            sm.insert(0, m[t] + B @ (sm[0] - a[t + 1])); sC.insert(0, C[t] + B @ (sC[0] - R[t + 1]) @ B.T)
+        s = torch.stack(sm)
+        out = {"state": s, "cov": torch.stack(sC), "level": s[:, 0]}
+        if self.order > 1:
+            out["slope"] = s[:, 1]
+        if self.s:
+            out["seasonal"] = s[:, self.order]
+        return out
+
+    def forecast(self, filt: dict, steps: int, X_future: torch.Tensor | None = None, z: float = 1.96) -> dict:
+        G, W, F0 = self._matrices()
+        m, C = filt["m"][-1], filt["C"][-1]
+        mean, var = [], []
+        for h in range(steps):
+            m, C = G @ m, G @ C @ G.T + W
+            F = F0.clone()
+            if self.k:
+                F[self.n - self.k:] = X_future[h].double()
+            mean.append(F @ m); var.append(F @ C @ F + self.vars["obs"])
+        mean, sd = torch.stack(mean), torch.stack(var).sqrt()
+        return {"mean": mean, "lower": mean - z * sd, "upper": mean + z * sd, "std": sd}
+
+    def fit(self, y: torch.Tensor, X: torch.Tensor | None = None, steps: int = 60, burn_in: int | None = None) -> dict:
+        """Maximum-likelihood variances (log-parameterised, L-BFGS); the first ``burn_in`` observations, which only resolve the
+        diffuse prior, are left out of the likelihood."""
+        names = ["obs", "level"] + (["slope"] if self.order > 1 else []) + (["seasonal"] if self.s else [])
+        scale = float(torch.nan_to_num(y.double()).var()) or 1.0
+        theta = torch.tensor([math.log(max(self.vars[n], 1e-8) * 1.0) for n in names], dtype=torch.float64, requires_grad=True)
+        burn = self.n if burn_in is None else burn_in
+        opt = torch.optim.LBFGS([theta], max_iter=steps, line_search_fn="strong_wolfe")
+        def nll():
+            v = {**self.vars, **{n: torch.exp(theta[i]) for i, n in enumerate(names)}}
+            G, W, F0 = self._matrices(v)
+            m, C, ll = torch.zeros(self.n, dtype=torch.float64), torch.eye(self.n, dtype=torch.float64) * 1e6, 0.0
+            yy = y.double()
+            for t in range(len(yy)):
+                F = F0.clone()
+                if self.k:
+                    F[self.n - self.k:] = X[t].double()
+                a, R = G @ m, G @ C @ G.T + W
+                f, q = F @ a, F @ R @ F + v["obs"]
+                e = yy[t] - f
+                A = R @ F / q
+                m, C = a + A * e, R - torch.outer(A, A) * q
+                if t >= burn:
+                    ll = ll - 0.5 * (torch.log(2 * math.pi * q) + e * e / q)
+            return -ll
+        def closure():
+            opt.zero_grad(); l = nll(); l.backward(); return l
+        opt.step(closure)
+        for i, n in enumerate(names):
+            self.vars[n] = float(torch.exp(theta[i].detach()))
+        return {"variances": dict(self.vars), "neg_loglik": float(nll().detach()), "signal_to_noise": self.vars["level"] / self.vars["obs"], "data_variance": scale}
