@@ -2670,3 +2670,70 @@ def test_core_shapes_symbolic_inference_shape_graph_indexing_typed_signatures_al
     assert S.detect_capabilities("Features : fp asimd sve\n")["simd"] == ["neon", "sve"] and isinstance(S.detect_capabilities()["logical_cores"], int)
     b200, h100, a100 = S.features_for_capability(10, 0), S.features_for_capability(9, 0), S.features_for_capability(8, 0)
     assert b200["tcgen05_tensor_memory"] and not b200["wgmma"] and b200["arch_flag"] == "sm_100a" and h100["wgmma"] and h100["tma"] and not h100["tcgen05_tensor_memory"] and a100["bf16_tensor_cores"] and not a100["tma"] and a100["arch_flag"] == "sm_80" and a100["max_shared_memory_kb"] == 163
+
+
+def test_autograd_graph_opt_backward_graph_memory_planning_onnx_gradients_api_levels_and_device_choice():
+    from torsh_b200.autograd import graph_opt as G
+    torch.manual_seed(0)
+    # backward graph
+    a, b = torch.randn(4, 3, requires_grad=True), torch.randn(3, 5, requires_grad=True)
+    frozen = torch.randn(4, 5)
+    fn = lambda p, q: (torch.tanh(torch.relu(p @ q) * 2.0 + 1.0) + frozen).sum()
+    g = G.BackwardGraph.from_function(fn, a, b)
+    s = g.summary()
+    assert s["leaves"] == 2 and s["operations"]["MmBackward0"] == 1 and s["operations"]["TanhBackward0"] == 1 and s["depth"] >= 6 and s["saved_bytes"] >= (12 + 15 + 20) * 4 and g.saved_tensor_count >= 4
+    order = g.execution_order()
+    pos = {v: i for i, v in enumerate(order)}
+    assert len(order) == g.node_count() and order[0] == g.root and all(pos[n.id] < pos[i] for n in g.nodes.values() for i in n.inputs)
+    chains = g.fusable_chains()
+    assert chains == [["AddBackward0", "TanhBackward0", "AddBackward0", "MulBackward0", "ReluBackward0"]]
+    assert g.dead_branches() == [] and g.edge_count() >= g.node_count() - 1
+    x = torch.randn(3, requires_grad=True)
+    dead = G.BackwardGraph((x * 2).sum() + (x.detach() * 3).sum())
+    assert dead.dead_branches() == []
+    dups = G.duplicate_subexpressions(lambda t: torch.exp(t) * torch.exp(t) + torch.sin(t))
+    assert dups == [["exp", "exp_1"]] and G.duplicate_subexpressions(lambda t: torch.exp(t) + torch.sin(t)) == []
+    # memory planning
+    model = torch.nn.Sequential(*[m for _ in range(8) for m in (torch.nn.Linear(64, 64), torch.nn.Tanh())])
+    xin = torch.randn(32, 64, requires_grad=True)
+    costs = G.profile_layers(model, xin)
+    assert len(costs) == 16 and all(c.activation_bytes >= 32 * 64 * 4 for c in costs) and costs[0].output_bytes == 32 * 64 * 4
+    base = G.memory_timeline(costs)
+    assert base["peak_bytes"] == sum(c.activation_bytes for c in costs) and base["timeline"][15][1] == base["peak_bytes"] and base["timeline"][-1][1] == costs[0].activation_bytes and base["recompute_flops"] == 0
+    plan = G.plan_checkpoints(costs)
+    assert plan["checkpoints"] == [4, 8, 12] and plan["peak_bytes"] < 0.5 * plan["baseline_peak"] and plan["recompute_flops"] == pytest.approx(sum(c.flops for c in costs))
+    tight = G.plan_checkpoints(costs, budget_bytes=0.4 * base["peak_bytes"])
+    assert tight["fits"] and tight["peak_bytes"] <= 0.4 * base["peak_bytes"] and len(tight["checkpoints"]) >= 3
+    assert G.plan_checkpoints(costs, budget_bytes=2 * base["peak_bytes"])["checkpoints"] == [] and not G.plan_checkpoints(costs, budget_bytes=1.0)["fits"]
+    uneven = [G.LayerCost("a", 100, 10), G.LayerCost("b", 10, 10), G.LayerCost("c", 10, 10), G.LayerCost("d", 100, 10)]
+    assert G.plan_checkpoints(uneven, segments=2)["checkpoints"] == [2] and G.plan_checkpoints(uneven, segments=3)["checkpoints"] in ([1, 3], [1, 2], [2, 3])
+    ck = G.apply_checkpoints(model, plan["checkpoints"])
+    x1, x2 = xin.detach().clone().requires_grad_(True), xin.detach().clone().requires_grad_(True)
+    saved_plain, saved_ck = [], []
+    with torch.autograd.graph.saved_tensors_hooks(lambda t: saved_plain.append(t.numel()) or t, lambda t: t):
+        y1 = model(x1)
+    with torch.autograd.graph.saved_tensors_hooks(lambda t: saved_ck.append(t.numel()) or t, lambda t: t):
+        y2 = ck(x2)
+    y1.sum().backward(); y2.sum().backward()
+    assert torch.allclose(y1, y2) and torch.allclose(x1.grad, x2.grad, atol=1e-6) and sum(saved_ck) < 0.5 * sum(saved_plain) and len(ck.segments) == 4
+    # ONNX round trip keeps gradients
+    net = torch.nn.Sequential(torch.nn.Linear(6, 8), torch.nn.ReLU(), torch.nn.Linear(8, 3), torch.nn.Tanh())
+    rt = G.verify_roundtrip_gradients(net, torch.randn(5, 6))
+    assert rt["ok"] and rt["gradient_max_diff"] < 1e-5 and rt["bytes"] > 300
+    # API stability levels
+    api = G.ApiCompatibilityChecker("0.1.3").with_defaults()
+    assert api.is_stable("backward") and api.is_experimental("forward_ad") and api.is_deprecated("Variable")
+    ok = api.check(["backward", "grad", "functional.hessian"])
+    assert ok["compatible"] and not api.check(["forward_ad"])["compatible"] and api.check(["forward_ad"], allow=("stable", "beta", "experimental"))["compatible"]
+    old = api.check(["graph_opt"], written_for="0.1.1")
+    assert not old["compatible"] and "introduced in 0.1.2" in old["problems"][0]["problem"] and api.check(["nonsense"])["problems"][0]["problem"] == "unknown"
+    dep = api.check(["Variable"])
+    assert dep["problems"][0]["replacement"] == "Tensor.requires_grad_" and "deprecated" in dep["problems"][0]["problem"]
+    later = G.ApiCompatibilityChecker("0.2.0").with_defaults()
+    assert "removed in 0.2.0" in later.check(["Variable"])["problems"][0]["problem"]
+    with pytest.raises(ValueError):
+        api.register("x", "alpha", "0.1.0")
+    # device choice
+    devs = [{"name": "cpu", "tflops": 0.5, "resident": True}, {"name": "cuda", "tflops": 60.0, "resident": False}]
+    small, big = G.select_device_for_workload(1000, devices=devs), G.select_device_for_workload(50_000_000, flops_per_element=200, devices=devs)
+    assert small["device"] == "cpu" and big["device"] == "cuda" and big["speedup_over_cpu"] > 2 and G.select_device_for_workload(10)["device"] in ("cpu", "cuda")
