@@ -5783,3 +5783,92 @@ def test_dynamic_linear_model_filter_smoother_forecast_and_likelihood_fit():
     start_nll = -float(est.filter(obs)["loglik"])
     res = est.fit(obs)
     assert res["variances"]["obs"] == pytest.approx(2.0, rel=0.35) and res["variances"]["level"] == pytest.approx(0.3, rel=0.6) and res["neg_loglik"] < start_nll and res["signal_to_noise"] == pytest.approx(0.15, rel=0.8)
+
+
+def test_ensembles_voting_fitted_weights_stacking_bagging_snapshots_online_selection_and_model_file_ops(tmp_path):
+    import numpy as np
+    from torsh_b200.models import ensembles as E
+    from torsh_b200.models.tooling import write_safetensors
+    torch.manual_seed(0)
+    # combining
+    p = torch.tensor([[[0.9, 0.1], [0.4, 0.6]], [[0.6, 0.4], [0.45, 0.55]], [[0.2, 0.8], [0.9, 0.1]]])
+    assert torch.allclose(E.combine_predictions(p, "soft"), p.mean(0)) and E.combine_predictions(p, "hard").tolist() == [[pytest.approx(2 / 3), pytest.approx(1 / 3)], [pytest.approx(1 / 3), pytest.approx(2 / 3)]]
+    w = torch.tensor([0.0, 0.0, 1.0])
+    assert torch.allclose(E.combine_predictions(p, "weighted", w), p[2]) and E.combine_predictions(p, "hard", torch.tensor([1.0, 1.0, 5.0])).argmax(1).tolist() == [1, 0] and torch.allclose(E.combine_predictions(p, "max"), torch.tensor([[0.9, 0.1], [0.9, 0.1]]))
+    geo = E.combine_predictions(p, "geometric")
+    assert torch.allclose(geo.sum(1), torch.ones(2)) and geo[0, 0] == pytest.approx((0.9 * 0.6 * 0.2) ** (1 / 3) / ((0.9 * 0.6 * 0.2) ** (1 / 3) + (0.1 * 0.4 * 0.8) ** (1 / 3)))
+    # data: three informative views of a 3-class problem
+    g = torch.Generator().manual_seed(0)
+    n, k = 600, 3
+    y = torch.randint(0, k, (n,), generator=g)
+    centers = torch.randn(k, 6, generator=g) * 1.5
+    x = centers[y] + torch.randn(n, 6, generator=g) * 1.6
+    xtr, ytr, xva, yva = x[:400], y[:400], x[400:], y[400:]
+    def fit(m, a, b, steps=150):
+        opt = torch.optim.Adam(m.parameters(), lr=0.05)
+        for _ in range(steps):
+            opt.zero_grad(); torch.nn.functional.cross_entropy(m(a), b).backward(); opt.step()
+    class View(torch.nn.Module):
+        def __init__(self, cols): super().__init__(); self.cols, self.lin = cols, torch.nn.Linear(len(cols), k)
+        def forward(self, t): return self.lin(t[:, self.cols])
+    views = [[0, 1], [2, 3], [4, 5], [0]]
+    base = []
+    for c in views:
+        m = View(c); fit(m, xtr, ytr); base.append(m.eval())
+    with torch.no_grad():
+        probs = torch.stack([m(xva).softmax(-1) for m in base])
+    acc = lambda pr: float((pr.argmax(-1) == yva).float().mean())
+    singles = [acc(q) for q in probs]
+    assert acc(E.combine_predictions(probs, "soft")) > max(singles)
+    wfit = E.fit_ensemble_weights(probs, yva)
+    nll = lambda pr: float(torch.nn.functional.nll_loss(pr.clamp_min(1e-12).log(), yva))
+    assert float(wfit.sum()) == pytest.approx(1.0, abs=1e-5) and wfit[3] < 0.1 and nll(E.combine_predictions(probs, "weighted", wfit)) <= nll(E.combine_predictions(probs, "soft")) + 1e-6
+    # stacking beats every base model's out-of-fold accuracy
+    st = E.StackingEnsemble([lambda c=c: View(c) for c in views[:3]], lambda m, a, b: fit(m, a, b, 80), folds=3).fit(xtr, ytr)
+    assert acc(st.predict_proba(xva)) > max(st.oof_accuracy) and len(st.models) == 3 and st.predict_proba(xva).sum(1).allclose(torch.ones(200))
+    # bagging
+    models, oob = E.bagging(lambda: View([0, 1, 2, 3, 4, 5]), lambda m, a, b: fit(m, a, b, 60), xtr, ytr, n_models=4)
+    oob_acc = E.out_of_bag_accuracy(models, oob, xtr, ytr)
+    with torch.no_grad():
+        bag_val = acc(torch.stack([m(xva).softmax(-1) for m in models]).mean(0))
+    assert all(0.3 * 400 < len(o) < 0.45 * 400 for o in oob) and abs(oob_acc - bag_val) < 0.08 and bag_val > 0.6
+    # snapshots
+    snap = E.SnapshotEnsemble(View([0, 1, 2, 3, 4, 5]), cycles=3, steps_per_cycle=40, max_lr=0.2)
+    hist = snap.fit(lambda m: torch.nn.functional.cross_entropy(m(xtr), ytr))
+    assert len(snap.snapshots) == 3 and snap.lr_at(0) == 0.2 and snap.lr_at(39) < 0.01 and snap.lr_at(40) == 0.2 and hist[-1] < hist[0] and acc(snap.predict_proba(xva)) > 0.6 and snap.predict_proba(xva, last=1).shape == (200, 3)
+    # online adaptive weights follow the better model, and a drift
+    on = E.OnlineAdaptiveEnsemble(2, eta=0.5, forget=0.02)
+    good, bad = torch.tensor([0.9, 0.1]), torch.tensor([0.3, 0.7])
+    for _ in range(30):
+        on.update(torch.stack([good, bad]), 0)
+    assert on.w[0] > 0.9 and on.predict(torch.stack([good, bad]))[0] > 0.8
+    for _ in range(60):
+        on.update(torch.stack([good, bad]), 1)
+    assert on.w[1] > 0.9 and on.cum_loss[0] > 0
+    # diversity
+    t = torch.tensor([0, 0, 0, 0, 1, 1, 1, 1])
+    same = torch.stack([torch.tensor([0, 0, 0, 1, 1, 1, 1, 0])] * 2)
+    comp = torch.stack([torch.tensor([0, 0, 0, 1, 1, 1, 1, 0]), torch.tensor([1, 0, 0, 0, 0, 1, 1, 1])])
+    ds, dc = E.diversity_measures(same, t), E.diversity_measures(comp, t)
+    assert ds["disagreement"] == 0 and ds["q_statistic"] == 1.0 and ds["correlation"] == pytest.approx(1.0) and dc["disagreement"] == 0.5 and dc["q_statistic"] == -1.0 and dc["double_fault"] == 0.0 and ds["double_fault"] == 0.25
+    # greedy selection
+    sel = E.greedy_ensemble_selection(probs, yva)
+    assert sel["validation_loss"] <= sel["best_single_loss"] and sel["improvement"] > 0 and sel["weights"].sum() == pytest.approx(1.0) and sel["trace"] == sorted(sel["trace"], reverse=True) and sel["members"][0] == int(torch.tensor([nll(q) for q in probs]).argmin())
+    assert len(E.greedy_ensemble_selection(probs, yva, max_size=2, with_replacement=False)["members"]) <= 2
+    assert E.estimate_ensemble_gain(0.7, 0.0, 11) == pytest.approx(sum(math.comb(11, j) * 0.7 ** j * 0.3 ** (11 - j) for j in range(6, 12))) and E.estimate_ensemble_gain(0.7, 1.0, 11) == pytest.approx(0.7) and E.estimate_ensemble_gain(0.7, 0.0, 11) > E.estimate_ensemble_gain(0.7, 0.5, 11)
+    assert E.optimal_ensemble_size(0.7, 0.0) > E.optimal_ensemble_size(0.7, 0.6) >= 1 and E.optimal_ensemble_size(0.7, 1.0) == 1
+    # model file operations
+    a = {"w": torch.randn(4, 4), "b": torch.zeros(4), "old": torch.ones(2), "emb": torch.randn(10, 4)}
+    b = {"w": a["w"] + 0.1 * torch.eye(4), "b": torch.zeros(4), "new": torch.ones(3), "emb": torch.randn(12, 4)}
+    diff = E.compare_state_dicts(a, b)
+    assert diff["only_in_a"] == ["old"] and diff["only_in_b"] == ["new"] and diff["shape_differences"] == [{"name": "emb", "a": (10, 4), "b": (12, 4)}] and diff["identical_tensors"] == 1 and diff["changed_tensors"] == 1
+    assert diff["value_differences"][0]["name"] == "w" and diff["value_differences"][0]["max_abs"] == pytest.approx(0.1, rel=1e-4) and diff["value_differences"][0]["changed_fraction"] == 0.25 and not diff["same_architecture"] and E.compare_state_dicts(a, a)["identical"]
+    sd = {"w": torch.randn(3, 3), "b": torch.arange(3.0)}
+    torch.save(sd, tmp_path / "m.pt"); write_safetensors(sd, tmp_path / "m.safetensors"); np.savez(tmp_path / "m.npz", **{k_: v.numpy() for k_, v in sd.items()})
+    for name in ("m.pt", "m.safetensors", "m.npz"):
+        assert E.compare_state_dicts(E.load_model_auto(tmp_path / name), sd)["identical"], name
+    with pytest.raises(ValueError, match="supported: .pt"):
+        E.load_model_auto(tmp_path / "m.xyz")
+    big = {"lin.weight": torch.randn(64, 64), "lin.bias": torch.randn(64), "spiky.weight": torch.cat([torch.randn(63, 64) * 0.01, torch.full((1, 64), 5.0)])}
+    qs = E.quantization_stats(big)
+    assert qs["tensors"] == 2 and qs["worst"][0]["name"] == "spiky.weight" and qs["worst"][0]["relative_error"] > qs["worst"][1]["relative_error"] and 3.5 < qs["compression"] < 4.0
