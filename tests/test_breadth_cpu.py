@@ -5872,3 +5872,78 @@ def test_ensembles_voting_fitted_weights_stacking_bagging_snapshots_online_selec
     big = {"lin.weight": torch.randn(64, 64), "lin.bias": torch.randn(64), "spiky.weight": torch.cat([torch.randn(63, 64) * 0.01, torch.full((1, 64), 5.0)])}
     qs = E.quantization_stats(big)
     assert qs["tensors"] == 2 and qs["worst"][0]["name"] == "spiky.weight" and qs["worst"][0]["relative_error"] > qs["worst"][1]["relative_error"] and 3.5 < qs["compression"] < 4.0
+
+
+def test_tensor_tuning_algorithms_blocking_tuner_bottlenecks_validation_plan_bf16_and_operation_log(tmp_path):
+    from torsh_b200 import tensor_tuning as T
+    torch.manual_seed(0)
+    # Strassen
+    a, b = torch.randn(150, 131, dtype=torch.float64), torch.randn(131, 97, dtype=torch.float64)
+    assert torch.allclose(T.strassen_matmul(a, b, leaf=16), a @ b, atol=1e-9) and torch.allclose(T.strassen_matmul(a[:8, :8], b[:8, :8]), a[:8, :8] @ b[:8, :8])
+    # Winograd and FFT convolution against the library
+    x, w = torch.randn(2, 5, 13, 10, dtype=torch.float64), torch.randn(4, 5, 3, 3, dtype=torch.float64)
+    ref = torch.nn.functional.conv2d(x, w)
+    assert torch.allclose(T.winograd_conv2d(x, w), ref, atol=1e-10) and torch.allclose(T.fft_conv2d(x, w), ref, atol=1e-10)
+    w7 = torch.randn(3, 5, 7, 5, dtype=torch.float64)
+    assert torch.allclose(T.fft_conv2d(x, w7), torch.nn.functional.conv2d(x, w7), atol=1e-10)
+    assert T.choose_conv_algorithm(3, 64, 56) == "winograd" and T.choose_conv_algorithm(3, 3, 224) == "implicit_gemm" and T.choose_conv_algorithm(11, 3, 224) == "fft" and T.choose_conv_algorithm(3, 64, 56, stride=2) == "implicit_gemm"
+    # summation accuracy: one large value followed by many small ones
+    v = torch.cat([torch.tensor([1e8]), torch.full((100000,), 0.01)]).float()
+    exact = 1e8 + 1000.0
+    import numpy as np
+    naive = float(np.cumsum(v.numpy())[-1])                                          # strictly sequential float32 accumulation
+    assert abs(float(T.kahan_sum(v)) - exact) <= 8 and abs(float(T.pairwise_sum(v)) - exact) <= 64 < abs(naive - exact)
+    r = torch.randn(10007, dtype=torch.float64)
+    assert float(T.pairwise_sum(r)) == pytest.approx(float(r.sum()), abs=1e-9) and float(T.kahan_sum(r)) == pytest.approx(float(r.sum()), abs=1e-9)
+    # cache blocking
+    tm, tn, tk = T.tile_sizes(4096, 4096, 4096, 4, cache_bytes=1 << 20)
+    assert tm == tn == tk and tm % 16 == 0 and 3 * tm * tm * 4 <= 1 << 20 < 3 * (tm + 16) ** 2 * 4 and T.tile_sizes(8, 8, 8) == (8, 8, 8)
+    assert torch.allclose(T.blocked_matmul(a, b, (32, 48, 64)), a @ b, atol=1e-9)
+    small_t, big_t = T.memory_traffic_model(1024, 1024, 1024, (32, 32, 32)), T.memory_traffic_model(1024, 1024, 1024, (256, 256, 256))
+    assert small_t["bytes"] > 4 * big_t["bytes"] and big_t["arithmetic_intensity"] > 4 * small_t["arithmetic_intensity"] and T.memory_traffic_model(64, 64, 64, (64, 64, 64))["reuse_factor"] == pytest.approx(4 / 3)
+    # tuner
+    now, calls = [0.0], []
+    tuner = T.AdaptiveTuner(repeats=2, clock=lambda: now[0])
+    mk = lambda name, cost: (lambda: (calls.append(name), now.__setitem__(0, now[0] + cost)))
+    cands = {"direct": mk("direct", 0.3), "blocked": mk("blocked", 0.1), "strassen": mk("strassen", 0.2)}
+    assert tuner.select("matmul", (1000, 1000, 1000), cands) == "blocked" and tuner.measurements == 3
+    n_calls = len(calls)
+    assert tuner.select("matmul", (1100, 900, 1024), cands) == "blocked" and len(calls) == n_calls and T.AdaptiveTuner.problem_class("matmul", (1000, 1000), torch.bfloat16) == "matmul|10,10|bfloat16"
+    assert tuner.select("matmul", (16, 16, 16), {"direct": mk("direct", 0.01), "blocked": mk("blocked", 0.05)}) == "direct"
+    tuner.save(tmp_path / "tune.json")
+    assert T.AdaptiveTuner().load(tmp_path / "tune.json").select("matmul", (1000, 1000, 1000), {}) == "blocked"
+    # bottleneck classification with a stated machine
+    bp = T.BottleneckProfiler(calibrate=False, bandwidth=100e9, flops=1e12, overhead=5e-6)
+    bp.record("copy", 2e-3, flops=0, nbytes=1e8); bp.record("gemm", 4e-3, flops=2e9, nbytes=1e7); bp.record("tiny_add", 6e-6, flops=100, nbytes=1200); bp.record("slow_gemm", 20e-3, flops=2e9, nbytes=1e7)
+    an = {r["name"]: r for r in bp.analyze()}
+    assert an["copy"]["bound"] == "memory" and an["copy"]["efficiency"] == pytest.approx(0.5) and an["gemm"]["bound"] == "compute" and an["gemm"]["efficiency"] == pytest.approx(0.5) and an["tiny_add"]["bound"] == "overhead" and bp.analyze()[0]["name"] == "slow_gemm"
+    assert "100.0 GB/s" in bp.report() and "slow_gemm" in bp.report().splitlines()[2]
+    live = T.BottleneckProfiler()
+    live.measure("mm", lambda: a.float() @ b.float(), flops=2 * 150 * 131 * 97, nbytes=4 * (150 * 131 + 131 * 97 + 150 * 97))
+    assert live.bandwidth > 0 and live.flops > 0 and live.overhead > 0 and live.analyze()[0]["bound"] in ("memory", "compute", "overhead")
+    # validation across dtypes and layouts; a kernel that assumes contiguity is caught
+    ok = T.validate_across_configurations(lambda p, q: p @ q, lambda g: [torch.randn(12, 9, generator=g), torch.randn(9, 7, generator=g)], devices=["cpu"])
+    assert ok["passed"] and ok["checked"] == 12
+    def assumes_contiguous(p, q):
+        flat = torch.as_strided(p, (p.numel(),), (1,))                              # wrong for any non-contiguous input
+        return flat.view(p.shape) @ q
+    bad = T.validate_across_configurations(assumes_contiguous, lambda g: [torch.randn(12, 9, generator=g), torch.randn(9, 7, generator=g)], dtypes=(torch.float32,), devices=["cpu"])
+    assert not bad["passed"] and {f["layout"] for f in bad["failures"]} == {"transposed", "strided"} and all(r["ok"] for r in bad["rows"] if r["layout"] == "contiguous")
+    # plan for a workload
+    plan = T.optimize_workload({"matmuls": [(4096, 4096, 4096), (64, 64, 64)], "convs": [(3, 64, 56), (11, 3, 224), (1, 256, 14)], "reductions": [1000, 1 << 20, 1 << 26], "dtype": torch.bfloat16, "allow_fast_algorithms": True})
+    assert [m["algorithm"] for m in plan["matmul"]] == ["strassen", "direct"] and [c["algorithm"] for c in plan["conv"]] == ["winograd", "fft", "implicit_gemm"] and [r["method"] for r in plan["reduction"]] == ["direct", "pairwise", "kahan"] and any("float32" in n for n in plan["notes"])
+    # bfloat16 rounding
+    t = torch.randn(10000)
+    assert torch.equal(T.bf16_round(t), t.to(torch.bfloat16)) and (T.bf16_round(t, "truncate").float().abs() <= t.abs()).all()
+    vals = torch.full((200000,), 1.0 + 2.0 ** -10)
+    st = T.bf16_round(vals, "stochastic", torch.Generator().manual_seed(0)).float()
+    assert set(st.unique().tolist()) == {1.0, 1.0078125} and float(st.mean()) == pytest.approx(1.0 + 2.0 ** -10, abs=2e-5) and float(T.bf16_round(vals).float().mean()) == 1.0
+    assert torch.isinf(T.bf16_round(torch.tensor([float("inf")]))).all() and torch.isnan(T.bf16_round(torch.tensor([float("nan")]))).all() and T.bf16_error_bound(1024) == pytest.approx(2 ** -7 + 1024 * 2 ** -24)
+    # operation log
+    with T.OperationLog() as log:
+        y = torch.relu(torch.ones(4, 3) @ torch.ones(3, 2)) + 1
+    ops = [e["op"] for e in log.entries]
+    assert "matmul" in ops and "relu" in ops and log.summary()["matmul"]["count"] == 1 and [e for e in log.entries if e["op"] == "matmul"][0]["shapes"] == [(4, 3), (3, 2)] and len(log.to_jsonl().splitlines()) == len(log.entries)
+    with T.OperationLog(only=["relu"]) as log2:
+        torch.relu(torch.ones(2)); torch.exp(torch.ones(2))
+    assert [e["op"] for e in log2.entries] == ["relu"]
