@@ -2737,3 +2737,68 @@ def test_autograd_graph_opt_backward_graph_memory_planning_onnx_gradients_api_le
     devs = [{"name": "cpu", "tflops": 0.5, "resident": True}, {"name": "cuda", "tflops": 60.0, "resident": False}]
     small, big = G.select_device_for_workload(1000, devices=devs), G.select_device_for_workload(50_000_000, flops_per_element=200, devices=devs)
     assert small["device"] == "cpu" and big["device"] == "cuda" and big["speedup_over_cpu"] > 2 and G.select_device_for_workload(10)["device"] in ("cpu", "cuda")
+
+
+def test_function_transformations_grad_vjp_jvp_jacobians_hessian_vmap_remat_and_control_flow():
+    from torsh_b200.autograd import transforms as J
+    torch.manual_seed(0)
+    f = lambda x: (x ** 3).sum() + torch.sin(x).sum()
+    x = torch.randn(5, dtype=torch.float64)
+    assert torch.allclose(J.grad(f)(x), 3 * x ** 2 + torch.cos(x)) and torch.allclose(J.grad(lambda v: J.grad(f)(v).sum())(x), 6 * x - torch.sin(x))
+    ga, gb = J.grad(lambda a, b: (a * b).sum(), argnums=(0, 1))(x, 2 * x)
+    assert torch.allclose(ga, 2 * x) and torch.allclose(gb, x)
+    A = torch.randn(3, 5, dtype=torch.float64)
+    g = lambda v: torch.tanh(A @ v)
+    jac = torch.autograd.functional.jacobian(g, x)
+    out, pull = J.vjp(g, x)
+    ct = torch.randn(3, dtype=torch.float64)
+    assert torch.allclose(out, g(x)) and torch.allclose(pull(ct)[0], ct @ jac)
+    tang = torch.randn(5, dtype=torch.float64)
+    o, jv = J.jvp(g, (x,), (tang,))
+    assert torch.allclose(o, g(x)) and torch.allclose(jv, jac @ tang)
+    assert torch.allclose(J.jacrev(g)(x), jac) and torch.allclose(J.jacfwd(g)(x), jac)
+    two = lambda a, b: a * b.sum()
+    assert torch.allclose(J.jacrev(two, 1)(x, x), torch.autograd.functional.jacobian(lambda b: two(x, b), x)) and torch.allclose(J.jacfwd(two, 0)(x, x), torch.diag(torch.full((5,), float(x.sum()), dtype=torch.float64)))
+    M = torch.randn(2, 3, dtype=torch.float64)
+    assert J.jacrev(lambda m: m @ m.T)(M).shape == (2, 2, 2, 3) and torch.allclose(J.jacrev(lambda m: m @ m.T)(M), J.jacfwd(lambda m: m @ m.T)(M))
+    assert torch.allclose(J.hessian(f)(x), torch.diag(6 * x - torch.sin(x))) and torch.allclose(J.hessian(lambda v: (v @ A.T @ A @ v))(x), 2 * A.T @ A)
+    # vmap: batched Jacobians, broadcast arguments, fallback for data-dependent code
+    xs = torch.randn(7, 5, dtype=torch.float64)
+    per = J.vmap(J.grad(f))(xs)
+    assert torch.allclose(per, 3 * xs ** 2 + torch.cos(xs))
+    assert torch.allclose(J.vmap(lambda v, m: m @ v, in_dims=(0, None))(xs, A), xs @ A.T) and J.vmap(lambda v: v.sum(), out_dims=0)(xs).shape == (7,)
+    assert torch.allclose(J.vmap(lambda a, b: a @ b, in_dims=(1, 0))(xs.T.contiguous(), xs), (xs * xs).sum(1))
+    def branchy(v): return v * 2 if float(v.sum()) > 0 else v * -1                    # cannot be batched by the interpreter
+    looped = J.vmap(branchy)(xs)
+    assert torch.allclose(looped, torch.where(xs.sum(1, keepdim=True) > 0, xs * 2, -xs))
+    a1, a2 = J.vmap(lambda v: (v.sum(), v * 2))(xs)
+    assert a1.shape == (7,) and a2.shape == (7, 5)
+    # remat keeps values and gradients, saves fewer tensors
+    net = torch.nn.Sequential(torch.nn.Linear(5, 64), torch.nn.Tanh(), torch.nn.Linear(64, 64), torch.nn.Tanh(), torch.nn.Linear(64, 1)).double()
+    xa, xb = xs.clone().requires_grad_(True), xs.clone().requires_grad_(True)
+    c1, c2 = [], []
+    with torch.autograd.graph.saved_tensors_hooks(lambda t: c1.append(1) or t, lambda t: t):
+        y1 = net(xa).sum()
+    with torch.autograd.graph.saved_tensors_hooks(lambda t: c2.append(1) or t, lambda t: t):
+        y2 = J.remat(net)(xb).sum()
+    y1.backward(); y2.backward()
+    assert torch.allclose(y1, y2) and torch.allclose(xa.grad, xb.grad) and len(c2) < len(c1)
+    # control flow
+    carry, ys = J.scan(lambda c, v: (c + v, c * v), torch.tensor(0.0), torch.arange(1.0, 5.0))
+    assert float(carry) == 10.0 and ys.tolist() == [0.0, 2.0, 9.0, 24.0]
+    rc, rys = J.scan(lambda c, v: (c + v, c), torch.tensor(0.0), torch.arange(1.0, 4.0), reverse=True)
+    assert float(rc) == 6.0 and rys.tolist() == [5.0, 3.0, 0.0]
+    assert J.fori_loop(0, 5, lambda i, v: v + i, 0) == 10 and J.while_loop(lambda v: v < 100, lambda v: v * 2, 1) == 128
+    with pytest.raises(RuntimeError):
+        J.while_loop(lambda v: True, lambda v: v, 0, max_iterations=10)
+    assert float(J.cond(True, lambda v: v * 2, lambda v: v * 3, torch.tensor(1.0))) == 2.0 and float(J.cond(torch.tensor(False), lambda v: v * 2, lambda v: v * 3, torch.tensor(1.0))) == 3.0
+    pv = torch.tensor([True, False, True])
+    xv = torch.ones(3, 2, requires_grad=True)
+    sel = J.cond(pv, lambda v: v * 2, lambda v: v * 3, xv)
+    sel.sum().backward()
+    assert sel[:, 0].tolist() == [2.0, 3.0, 2.0] and xv.grad[:, 0].tolist() == [2.0, 3.0, 2.0]
+    # a decaying scan is differentiable end to end
+    w = torch.tensor(0.5, requires_grad=True)
+    final, _ = J.scan(lambda c, v: (c * w + v, c), torch.tensor(0.0), torch.ones(4))
+    final.backward()
+    assert float(final.detach()) == pytest.approx(1 + 0.5 + 0.25 + 0.125) and float(w.grad) == pytest.approx(1 + 2 * 0.5 + 3 * 0.25)

@@ -396,3 +396,141 @@ def autograd_graph_dot(output: torch.Tensor, max_nodes: int = 500) -> str:
             if nxt in seen:
                 lines.append(f"  n{seen[nxt]} -> n{i};")
     return "\n".join(lines + ["}"])
+
+
+# ---- function transformations in the JAX style (``crates/torsh-autograd/src/jax_transformations.rs``, ``crates/torsh-core/src/jax_transforms.rs``) ----
+def grad(fn, argnums=0):
+    """``grad(f)(x)`` is the gradient of the scalar ``f`` with respect to the selected positional argument(s); the result is
+    itself differentiable, so ``grad(grad(f))`` works."""
+    nums = (argnums,) if isinstance(argnums, int) else tuple(argnums)
+    def wrapped(*args, **kw):
+        args = list(args)
+        for n in nums:
+            args[n] = args[n] if args[n].requires_grad else args[n].detach().requires_grad_(True)
+        out = fn(*args, **kw)
+        gs = torch.autograd.grad(out, [args[n] for n in nums], create_graph=True)
+        return gs[0] if isinstance(argnums, int) else gs
+    return wrapped
+
+
+def vjp(fn, *primals):
+    """``out, pullback = vjp(f, x...)``; ``pullback(cotangent)`` returns one cotangent per primal."""
+    xs = [p.detach().requires_grad_(True) for p in primals]
+    out = fn(*xs)
+    def pullback(ct):
+        gs = torch.autograd.grad(out, xs, ct, retain_graph=True, allow_unused=True)
+        return tuple(torch.zeros_like(x) if g is None else g for g, x in zip(gs, xs))
+    return out.detach(), pullback
+
+
+def jvp(fn, primals, tangents):
+    """Forward-mode: ``(f(x), J v)`` in one pass with dual numbers."""
+    import torch.autograd.forward_ad as fwd
+    with fwd.dual_level():
+        out = fn(*[fwd.make_dual(p, t) for p, t in zip(primals, tangents)])
+        o = fwd.unpack_dual(out)
+        return o.primal.detach(), (o.tangent if o.tangent is not None else torch.zeros_like(o.primal)).detach()
+
+
+def jacrev(fn, argnum: int = 0):
+    """Jacobian by reverse mode: one batched backward pass per output element (good for few outputs)."""
+    def wrapped(*args):
+        args = list(args)
+        x = args[argnum].detach().requires_grad_(True); args[argnum] = x
+        y = fn(*args)
+        eye = torch.eye(y.numel(), dtype=y.dtype, device=y.device).reshape(y.numel(), *y.shape)
+        j, = torch.autograd.grad(y, x, eye, is_grads_batched=True, create_graph=torch.is_grad_enabled() and y.requires_grad)
+        return j.reshape(*y.shape, *x.shape)
+    return wrapped
+
+
+def jacfwd(fn, argnum: int = 0):
+    """Jacobian by forward mode: one pass per input element (good for few inputs)."""
+    def wrapped(*args):
+        x = args[argnum]
+        cols = []
+        for i in range(x.numel()):
+            t = torch.zeros_like(x).reshape(-1); t[i] = 1
+            tang = [t.reshape(x.shape) if k == argnum else torch.zeros_like(a) for k, a in enumerate(args)]
+            cols.append(jvp(fn, args, tang)[1])
+        j = torch.stack(cols, -1)
+        return j.reshape(*cols[0].shape, *x.shape)
+    return wrapped
+
+
+def hessian(fn, argnum: int = 0):
+    """Forward-over-reverse: the Jacobian (forward mode) of the gradient (reverse mode)."""
+    def wrapped(*args):
+        x = args[argnum].detach()
+        n = x.numel()
+        def g(v):
+            a = list(args); a[argnum] = v
+            return grad(fn, argnum)(*a)
+        rows = []
+        for i in range(n):
+            t = torch.zeros(n, dtype=x.dtype, device=x.device); t[i] = 1
+            xv = x.clone().requires_grad_(True)
+            gv = g(xv)
+            hv, = torch.autograd.grad(gv, xv, t.reshape(x.shape))
+            rows.append(hv.reshape(-1))
+        return torch.stack(rows).reshape(*x.shape, *x.shape)
+    return wrapped
+
+
+def vmap(fn, in_dims=0, out_dims: int = 0):
+    """Maps ``fn`` over one axis of its arguments (``in_dims``: an int for all, or one entry per argument with ``None`` for
+    broadcast arguments).  Uses the batching interpreter when the function supports it and an explicit loop otherwise, with
+    the same result."""
+    def wrapped(*args):
+        dims = (in_dims,) * len(args) if isinstance(in_dims, int) or in_dims is None else tuple(in_dims)
+        try:
+            return torch.vmap(fn, in_dims=dims, out_dims=out_dims)(*args)
+        except Exception:                                                           # data-dependent control flow, in-place ops, ...
+            n = next(a.shape[d] for a, d in zip(args, dims) if d is not None)
+            outs = [fn(*[a.select(d, i) if d is not None else a for a, d in zip(args, dims)]) for i in range(n)]
+            if isinstance(outs[0], tuple):
+                return tuple(torch.stack([o[k] for o in outs], out_dims) for k in range(len(outs[0])))
+            return torch.stack(outs, out_dims)
+    return wrapped
+
+
+def remat(fn):
+    """Recomputes ``fn``'s intermediates in the backward pass instead of storing them."""
+    from torch.utils.checkpoint import checkpoint
+    return lambda *a: checkpoint(fn, *a, use_reentrant=False)
+
+
+def scan(f, init, xs, reverse: bool = False):
+    """``carry, y_t = f(carry, x_t)`` along the first axis; returns the final carry and the stacked ``y``."""
+    carry, ys = init, []
+    idx = range(len(xs) - 1, -1, -1) if reverse else range(len(xs))
+    for i in idx:
+        carry, y = f(carry, xs[i]); ys.append(y)
+    if reverse:
+        ys.reverse()
+    return carry, torch.stack(ys) if ys and isinstance(ys[0], torch.Tensor) else ys
+
+
+def fori_loop(lower: int, upper: int, body, init):
+    val = init
+    for i in range(lower, upper):
+        val = body(i, val)
+    return val
+
+
+def while_loop(cond_fn, body, init, max_iterations: int = 1_000_000):
+    val, n = init, 0
+    while cond_fn(val):
+        val, n = body(val), n + 1
+        if n >= max_iterations:
+            raise RuntimeError(f"while_loop exceeded {max_iterations} iterations")
+    return val
+
+
+def cond(pred, true_fn, false_fn, *operands):
+    """Evaluates one branch for a Python or zero-dimensional predicate; for a batched predicate both branches run and the
+    results are selected element-wise (so that the expression stays differentiable and mappable)."""
+    if isinstance(pred, torch.Tensor) and pred.dim() > 0:
+        a, b = true_fn(*operands), false_fn(*operands)
+        return torch.where(pred.reshape(pred.shape + (1,) * (a.dim() - pred.dim())), a, b)
+    return true_fn(*operands) if bool(pred) else false_fn(*operands)
