@@ -19,8 +19,9 @@ from . import autograd, data, distributed, functional, nn, optim  # noqa: E402,F
 from . import functional as F  # noqa: E402,F401,N812
 
 float32, float64, float16, bfloat16 = dtype.F32, dtype.F64, dtype.F16, dtype.BF16
-int8, int16, int32, int64, uint8, uint32, uint64 = dtype.I8, dtype.I16, dtype.I32, dtype.I64, dtype.U8, dtype.U32, dtype.U64
-bool = dtype.BOOL  # noqa: A001
+int8, int16, int32, int64, uint8, uint16, uint32, uint64 = dtype.I8, dtype.I16, dtype.I32, dtype.I64, dtype.U8, dtype.U16, dtype.U32, dtype.U64
+bool = bool_dtype = dtype.BOOL  # noqa: A001
+FloatTensor = DoubleTensor = HalfTensor = LongTensor = IntTensor = ByteTensor = BoolTensor = Tensor  # typed names of the reference all alias Tensor
 __version__ = _t.__version__
 
 

@@ -2802,3 +2802,23 @@ def test_function_transformations_grad_vjp_jvp_jacobians_hessian_vmap_remat_and_
     final, _ = J.scan(lambda c, v: (c * w + v, c), torch.tensor(0.0), torch.ones(4))
     final.backward()
     assert float(final.detach()) == pytest.approx(1 + 0.5 + 0.25 + 0.125) and float(w.grad) == pytest.approx(1 + 2 * 0.5 + 3 * 0.25)
+
+
+def test_rstorch_surface_matches_the_reference_python_package_names():
+    """Every public name of the reference's ``python/rstorch`` modules (``__all__`` and the names imported from its native
+    extension, transcribed below) resolves in this package."""
+    import rstorch
+    names = {"__init__": ["BoolTensor", "ByteTensor", "FloatTensor", "IntTensor", "LongTensor", "Tensor", "TorshError", "add", "arange", "bmm", "bool_dtype", "cpu", "cuda_is_available", "device", "device_count", "div", "dtype", "empty", "empty_like",
+                          "flatten", "float32", "float64", "full", "full_like", "get_default_device", "get_default_dtype", "get_device_name", "int16", "int32", "int64", "int8", "is_available", "linspace", "matmul", "mm", "mps_is_available", "mul",
+                          "ones", "ones_like", "permute", "rand", "rand_like", "randn", "randn_like", "reshape", "set_default_device", "set_default_dtype", "squeeze", "sub", "tensor", "transpose", "uint16", "uint32", "uint64", "uint8", "unsqueeze",
+                          "view", "zeros", "zeros_like"],
+             "nn": ["Linear", "Module", "ModuleList", "Parameter", "Sequential", "cross_entropy", "log_softmax", "mse_loss", "parameter", "relu", "sigmoid", "softmax", "tanh"], "optim": ["Adam", "AdamW", "Optimizer", "SGD"],
+             "autograd": ["Function", "backward", "detect_anomaly", "enable_grad", "grad", "is_grad_enabled", "no_grad", "set_grad_enabled"],
+             "distributed": ["DDP", "DistributedDataParallel", "ProcessGroup", "all_gather", "all_reduce", "barrier", "broadcast", "destroy_process_group", "gather", "get_rank", "get_world_size", "init_process_group", "is_available", "is_initialized",
+                             "reduce", "scatter"]}
+    for mod, wanted in names.items():
+        ours = rstorch if mod == "__init__" else getattr(rstorch, mod)
+        missing = sorted(n for n in wanted if not hasattr(ours, n))
+        assert not missing, (mod, missing)
+    x = rstorch.tensor([[1.0, -2.0], [0.5, 3.0]])
+    assert rstorch.nn.relu(x).tolist() == [[1.0, 0.0], [0.5, 3.0]] and float(rstorch.nn.mse_loss(x, x)) == 0.0 and type(rstorch.nn.parameter(x)).__name__ == "Parameter" and rstorch.FloatTensor is rstorch.Tensor and rstorch.uint16.size_bytes == 2
