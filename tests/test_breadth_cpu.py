@@ -5947,3 +5947,98 @@ def test_tensor_tuning_algorithms_blocking_tuner_bottlenecks_validation_plan_bf1
     with T.OperationLog(only=["relu"]) as log2:
         torch.relu(torch.ones(2)); torch.exp(torch.ones(2))
     assert [e["op"] for e in log2.entries] == ["relu"]
+
+
+def test_nn_blocks_factories_positions_attention_conv_blocks_backbones_pooling_and_cells():
+    import torsh_b200.nn as tnn
+    from torsh_b200.nn import blocks as B
+    torch.manual_seed(0)
+    # factories
+    assert isinstance(B.ActivationFactory.create("GELU"), torch.nn.GELU) and B.ActivationFactory.create("leaky-relu", negative_slope=0.3).negative_slope == 0.3 and "geglu" in B.ActivationFactory.available() and tnn.ActivationFactory is B.ActivationFactory
+    with pytest.raises(ValueError, match="unknown activation"):
+        B.ActivationFactory.create("nope")
+    act = B.ActivationBuilder("leaky_relu").negative_slope(0.2).inplace().build()
+    assert act.negative_slope == 0.2 and act.inplace
+    x = torch.randn(4, 7, 16)
+    ln = B.AdvancedLayerNorm(16)
+    assert torch.allclose(ln(x), torch.nn.functional.layer_norm(x, (16,)), atol=1e-6)
+    rms = B.AdvancedLayerNorm(16, rms=True, eps=1e-6)
+    assert rms.bias is None and torch.allclose(rms(x), x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6), atol=1e-6)
+    r = torch.randn_like(x)
+    assert torch.allclose(ln(x, residual=r), torch.nn.functional.layer_norm(x + r, (16,)), atol=1e-6) and ln(x.bfloat16()).dtype == torch.bfloat16
+    NF = B.NormalizationFactory
+    assert isinstance(NF.create("batch", 8, dims=1), torch.nn.BatchNorm1d) and isinstance(NF.create(B.NormalizationPresets.resnet(), 8), torch.nn.BatchNorm2d) and NF.create("group", 48).num_groups == 16 and isinstance(NF.create("none", 3), torch.nn.Identity)
+    assert NF.create(B.NormalizationPresets.llama(), 16).rms and isinstance(NF.create(B.NormalizationPresets.style_transfer(), 4), torch.nn.InstanceNorm2d) and B.NormalizationPresets.diffusion_unet().groups == 32
+    bn = NF.create("batch", 16, dims=1)
+    stats = B.NormalizationStats(bn)
+    bn(torch.randn(64, 16) * 3 + 5)
+    s = stats.summary()
+    assert abs(s["in_mean"] - 5) < 0.5 and abs(s["out_mean"]) < 1e-5 and abs(s["out_var"] - 1) < 0.05
+    stats.remove()
+    # positions
+    pe = B.PositionalEncoding(16)
+    out = pe(torch.zeros(2, 10, 16))
+    assert out[0, 0, 0::2].abs().sum() == 0 and torch.allclose(out[0, 0, 1::2], torch.ones(8)) and out[0, 3, 0] == pytest.approx(math.sin(3.0))
+    te = B.SinusoidalPositionEmbedding(8)(torch.tensor([0.0, 10.0]))
+    assert te.shape == (2, 8) and te[0].tolist() == [0, 0, 0, 0, 1, 1, 1, 1] and te[1, 0] == pytest.approx(math.sin(10.0))
+    rel = B.RelativePositionalEncoding(4, max_distance=3)
+    rb = rel(5, 5)
+    assert rb.shape == (4, 5, 5) and torch.equal(rb[:, 0, 1], rb[:, 2, 3]) and torch.equal(rb[:, 0, 3], rb[:, 0, 4]) and not torch.equal(rb[:, 0, 1], rb[:, 1, 0])
+    ali = B.AlibiPositionalBias(8)
+    ab = ali(4, 4)
+    assert ali.slopes.tolist() == pytest.approx([2 ** -(i + 1) for i in range(8)]) and ab[0, 3, 1] == pytest.approx(-0.5 * 2) and torch.isinf(ab[0, 1, 2]) and ab[:, 2, 2].abs().sum() == 0 and len(B.AlibiPositionalBias(12).slopes) == 12
+    assert not torch.isinf(B.AlibiPositionalBias(4, causal=False)(3, 3)).any() and B.AlibiPositionalBias(4)(1, 5)[0, 0].tolist() == pytest.approx([-1.0, -0.75, -0.5, -0.25, 0.0])
+    # attention equals the library layer given the same weights
+    mha, ref = B.MultiHeadAttention(16, 4), torch.nn.MultiheadAttention(16, 4, batch_first=True)
+    with torch.no_grad():
+        ref.in_proj_weight.copy_(torch.cat([mha.q_proj.weight, mha.k_proj.weight, mha.v_proj.weight])); ref.in_proj_bias.copy_(torch.cat([mha.q_proj.bias, mha.k_proj.bias, mha.v_proj.bias]))
+        ref.out_proj.weight.copy_(mha.out_proj.weight); ref.out_proj.bias.copy_(mha.out_proj.bias)
+    pad = torch.zeros(4, 7, dtype=torch.bool); pad[1, 5:] = True
+    o1, w1 = mha(x, key_padding_mask=pad, need_weights=True)
+    o2, w2 = ref(x, x, x, key_padding_mask=pad)
+    assert torch.allclose(o1, o2, atol=1e-5) and torch.allclose(w1, w2, atol=1e-5) and torch.allclose(mha(x, key_padding_mask=pad), o1, atol=1e-5)
+    cm = torch.nn.Transformer.generate_square_subsequent_mask(7)
+    assert torch.allclose(mha(x, causal=True), ref(x, x, x, attn_mask=cm)[0], atol=1e-5) and mha(x, attn_bias=B.AlibiPositionalBias(4)(7, 7)).shape == x.shape
+    mem = torch.randn(4, 3, 16)
+    assert mha(x, mem).shape == (4, 7, 16)
+    with pytest.raises(ValueError):
+        B.MultiHeadAttention(10, 3)
+    gg = B.GEGLU(16, 32)
+    assert gg(x).shape == (4, 7, 32) and torch.allclose(B.GEGLU()(x), torch.nn.functional.gelu(x[..., :8]) * x[..., 8:])
+    # convolutional blocks
+    img = torch.randn(2, 16, 8, 8)
+    assert B.BasicBlock(16, 16)(img).shape == img.shape and B.BasicBlock(16, 32, 2)(img).shape == (2, 32, 4, 4) and B.BasicBlock(16, 16).short is None and B.BottleneckBlock(16, 8, 2)(img).shape == (2, 32, 4, 4) and B.BottleneckBlock.expansion == 4
+    assert B.BasicBlock(16, 16, cfg=B.BlockConfig(norm="group", activation="silu"))(img).shape == img.shape
+    assert B.DenseLayer(16, growth_rate=12)(img).shape == (2, 28, 8, 8) and B.TransitionLayer(28)(torch.randn(2, 28, 8, 8)).shape == (2, 14, 4, 4)
+    ds = B.DepthwiseSeparableConv(16, 32, 3, 2)
+    full = torch.nn.Conv2d(16, 32, 3, 2, 1)
+    assert ds(img).shape == (2, 32, 4, 4) and ds.multiply_adds(8, 8) == 16 * (16 * 9 + 16 * 32) and sum(p.numel() for p in ds.parameters() if p.dim() == 4) < 0.2 * full.weight.numel() and B.MobileNetV1Block is B.DepthwiseSeparableConv
+    ir = B.InvertedResidual(16, 16)
+    assert ir.use_res and ir(img).shape == img.shape and not B.InvertedResidual(16, 24, 2).use_res and B.InvertedResidual(16, 24, 2)(img).shape == (2, 24, 4, 4) and len(B.InvertedResidual(16, 16, expand_ratio=1).body) == 2
+    mb = B.MBConvWithStochasticDepth(16, 16, drop_rate=0.5).eval()
+    base = mb(img)
+    mb.train()
+    torch.manual_seed(1)
+    dropped = [bool(torch.allclose(mb(img)[i], img[i])) for _ in range(20) for i in range(2)]
+    assert 5 < sum(dropped) < 35 and base.shape == img.shape
+    # backbones
+    mn = B.MobileNetV1(num_classes=10, width_multiplier=0.25)
+    assert mn(torch.randn(2, 3, 64, 64)).shape == (2, 10) and 150_000 < sum(p.numel() for p in mn.parameters()) < 300_000
+    cfg = B.EfficientNetConfig(width_coefficient=1.1, depth_coefficient=1.2)
+    assert cfg.round_channels(32) == 32 and cfg.round_channels(40) == 48 and cfg.round_repeats(3) == 4
+    eff = B.EfficientNetBackbone(B.EfficientNetConfig(width_coefficient=0.25, depth_coefficient=0.35, num_classes=7))
+    assert eff(torch.randn(2, 3, 64, 64)).shape == (2, 7) and eff.forward_features(torch.randn(1, 3, 64, 64)).shape == (1, eff.out_channels, 2, 2)
+    b0 = sum(p.numel() for p in B.EfficientNetBackbone().parameters())
+    assert 5.0e6 < b0 < 5.6e6                                                       # EfficientNet-B0 has 5.3 M parameters
+    # pooling and cells
+    v = torch.arange(24.0).reshape(1, 2, 3, 4)
+    assert B.GlobalPool("avg")(v).tolist() == [[5.5, 17.5]] and B.GlobalPool("max")(v).tolist() == [[11.0, 23.0]] and B.GlobalPool("avgmax")(v).tolist() == [[8.25, 20.25]] and B.GlobalPool("catavgmax")(v).shape == (1, 4)
+    fp = B.FractionalMaxPool1d(2, 0.7).eval()
+    seq = torch.arange(20.0).reshape(1, 1, 20)
+    po = fp(seq)
+    assert po.shape == (1, 1, 14) and (po.diff() >= 0).all() and po[0, 0, -1] == 19 and po[0, 0, 0] == 1
+    cell = B.CustomRNNCell(5, 8, activation="relu", layer_norm=True, learn_initial_state=True)
+    hs, last = cell.unroll(torch.randn(3, 6, 5))
+    assert hs.shape == (3, 6, 8) and torch.equal(hs[:, -1], last) and (hs >= 0).all() and cell.initial_state(3).shape == (3, 8)
+    last.sum().backward()
+    assert cell.h0.grad is not None and cell.hh.weight.grad.abs().sum() > 0
