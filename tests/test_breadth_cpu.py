@@ -6042,3 +6042,120 @@ def test_nn_blocks_factories_positions_attention_conv_blocks_backbones_pooling_a
     assert hs.shape == (3, 6, 8) and torch.equal(hs[:, -1], last) and (hs >= 0).all() and cell.initial_state(3).shape == (3, 8)
     last.sum().backward()
     assert cell.h0.grad is not None and cell.hh.weight.grad.abs().sum() > 0
+
+
+def test_optim_more_adam_variants_population_methods_gp_benchmarks_stress_wrappers_and_builders():
+    import torsh_b200.optim as O
+    from scipy.optimize import rosen
+    torch.manual_seed(0)
+    assert O.AdaDelta is torch.optim.Adadelta and O.AdaGrad is torch.optim.Adagrad and O.AdaMax is torch.optim.Adamax
+    # AdvancedAdam with the switches off is AdamW; the switches do what they say
+    w1, w2 = torch.nn.Parameter(torch.randn(4, 3)), None
+    w2 = torch.nn.Parameter(w1.detach().clone())
+    a, b = O.AdvancedAdam([w1], lr=0.01, weight_decay=0.1), torch.optim.AdamW([w2], lr=0.01, weight_decay=0.1)
+    for _ in range(5):
+        for w, o in ((w1, a), (w2, b)):
+            o.zero_grad(); (w ** 2).sum().backward(); o.step()
+    assert torch.allclose(w1, w2, atol=1e-6)
+    w3 = torch.nn.Parameter(torch.ones(2, 3)); w3.grad = torch.ones(2, 3)
+    before = w3.detach().clone()
+    O.AdvancedAdam([w3], centralize=True).step()
+    assert torch.allclose(w3, before)                                               # a constant gradient per row is centred away
+    w4 = torch.nn.Parameter(torch.zeros(3)); w4.grad = torch.tensor([1.0, -1.0, 1e-9])
+    O.AdvancedAdam([w4], lr=1.0, max_update=0.1).step()
+    assert w4.abs().max() <= 0.1 + 1e-6
+    ams = O.AdvancedAdam([torch.nn.Parameter(torch.ones(1))], amsgrad=True)
+    p = ams.param_groups[0]["params"][0]
+    for gval in (10.0, 0.1, 0.1):
+        p.grad = torch.tensor([gval]); ams.step()
+    assert float(ams.state[p]["vmax"]) >= float(ams.state[p]["v"])
+    # schedule-free AdamW: trains without a schedule; the averaged weights are at least as good
+    X = torch.randn(200, 5); yt = X @ torch.tensor([1.0, -2.0, 0.5, 0.0, 3.0]) + 0.05 * torch.randn(200)
+    lin = torch.nn.Linear(5, 1)
+    sf = O.ScheduleFreeAdamW(lin.parameters(), lr=0.05, warmup_steps=10)
+    for i in range(300):
+        idx = torch.randint(0, 200, (32,))
+        sf.zero_grad(); torch.nn.functional.mse_loss(lin(X[idx]).squeeze(-1), yt[idx]).backward(); sf.step()
+    train_loss = float(torch.nn.functional.mse_loss(lin(X).squeeze(-1), yt).detach())
+    sf.eval_mode(); eval_loss = float(torch.nn.functional.mse_loss(lin(X).squeeze(-1), yt).detach()); y_params = lin.weight.detach().clone()
+    sf.train_mode()
+    assert eval_loss < 0.05 and eval_loss <= train_loss * 1.5 and not torch.equal(y_params, lin.weight.detach()) and type(O.Sophia(lin.parameters())).__name__ == "SophiaG"
+    # population methods on standard functions
+    ros, sph, ras = O.Rosenbrock(), O.Sphere(), O.Rastrigin()
+    xr = torch.tensor([-1.2, 1.0, 0.5], dtype=torch.float64)
+    assert float(ros(xr)) == pytest.approx(rosen(xr.numpy())) and float(ras(torch.zeros(3))) == 0.0 and float(O.Branin()(O.Branin().optimum())) == pytest.approx(O.Branin.minimum, abs=1e-6)
+    cma = O.CMAES(torch.tensor([-1.5, 1.5, -0.5, 0.8]), sigma=0.5, seed=1).minimize(ros, generations=400)
+    assert cma["value"] < 1e-8 and torch.allclose(cma["x"], torch.ones(4, dtype=torch.float64), atol=1e-3)
+    es = O.OpenAIES(torch.full((5,), 2.0), sigma=0.1, population=40, lr=0.1, seed=0).minimize(sph, iterations=150)
+    assert es["value"] < 0.05 and es["history"][-1] < es["history"][0]
+    pso = O.ParticleSwarmOptimizer(3, particles=40, bounds=ras.bounds, seed=0).minimize(ras, iterations=150)
+    assert pso["value"] < 1.5 and pso["x"].abs().max() <= 5.12
+    # Gaussian process: interpolates, is uncertain away from data, EI prefers the promising gap
+    xs = torch.tensor([[0.0], [1.0], [2.0], [4.0]]); ys = torch.sin(xs[:, 0])
+    gp = O.GaussianProcess(length_scale=1.0, noise_var=1e-8).fit(xs, ys)
+    mu, var = gp.predict(xs)
+    assert torch.allclose(mu, ys.double(), atol=1e-5) and var.max() < 1e-6
+    mu2, var2 = gp.predict(torch.tensor([[3.0], [10.0]]))
+    assert var2[1] > 0.99 and var2[0] < var2[1] and abs(float(mu2[1]) - float(ys.mean())) < 1e-6
+    from sklearn.gaussian_process import GaussianProcessRegressor
+    from sklearn.gaussian_process.kernels import RBF
+    sk = GaussianProcessRegressor(RBF(1.0), alpha=1e-8, optimizer=None, normalize_y=False).fit(xs.numpy(), (ys - ys.mean()).numpy())
+    assert float(mu2[0]) == pytest.approx(float(sk.predict([[3.0]])[0] + ys.mean()), abs=1e-5) and gp.log_marginal_likelihood() == pytest.approx(sk.log_marginal_likelihood_value_, rel=1e-5)
+    ei = gp.expected_improvement(torch.tensor([[1.0], [3.0], [5.0]]))
+    assert ei[0] < 1e-6 and ei[2] > ei[0]
+    # convergence tracker
+    ct = O.ConvergenceTracker(patience=3, min_delta=1e-3)
+    assert [ct.update(v) for v in (1.0, 0.5, 0.4999, 0.4999, 0.4999)] == [None, None, None, None, "stalled"] and O.ConvergenceTracker().update(float("nan")) == "diverged" and O.ConvergenceTracker(grad_tol=1e-3).update(1.0, 1e-5) == "gradient_tolerance"
+    ct2 = O.ConvergenceTracker()
+    for i in range(10):
+        ct2.update(math.exp(-0.5 * i))
+    assert ct2.rate() == pytest.approx(0.5) and ct2.update(1e9) == "diverged"
+    # benchmarks and stress tests
+    res = O.OptimizerBenchmarks(dim=3, steps=300, tol=1e-3).run({"sgd": lambda p: torch.optim.SGD(p, lr=1e-3), "lbfgs": lambda p: torch.optim.LBFGS(p, lr=1.0, max_iter=5, line_search_fn="strong_wolfe")})
+    assert res["rosenbrock"]["winner"] == "lbfgs" and res["rosenbrock"]["lbfgs"]["steps_to_tolerance"] is not None and res["sphere"]["lbfgs"]["final"] < 1e-6
+    st_adam = O.OptimizerStressTester(lambda p: torch.optim.Adam(p, lr=0.05)).run()
+    st_sgd = O.OptimizerStressTester(lambda p: torch.optim.SGD(p, lr=0.05)).run()
+    assert st_adam["ill_conditioned"]["finite"] and st_adam["spike"]["finite"] and not st_sgd["ill_conditioned"]["finite"] and not st_adam["non_finite"]["finite"] and "ill_conditioned" in st_adam["passed"]
+    # wrappers
+    ci = [500.0]
+    wp = torch.nn.Parameter(torch.zeros(1))
+    cc = O.CarbonConsciousOptimizer(torch.optim.SGD([wp], lr=1.0), lambda: ci[0], threshold=400, defer_factor=4)
+    for _ in range(8):
+        wp.grad = (wp.grad if wp.grad is not None else 0) + torch.ones(1)
+        cc.step()
+    assert cc.report()["applied"] == 2 and float(wp.detach()) == -8.0                      # accumulated gradients are applied later: nothing is lost
+    ci[0] = 100.0
+    wp.grad = torch.ones(1)
+    assert cc.step() and cc.report()["grams_co2"] > 0
+    pauses, watts = [], [900.0]
+    pc = O.PowerCappedOptimizer(torch.optim.SGD([wp], lr=0.0), lambda: watts[0], cap_watts=700.0, sleep=pauses.append)
+    wp.grad = torch.zeros(1)
+    pc.step(); watts[0] = 500.0
+    for _ in range(10):
+        pc.step()
+    assert pauses and pauses[0] == pytest.approx(0.01 * 200 / 700) and pc.avg < 700 and len(pauses) < 5
+    wq = torch.nn.Parameter(torch.tensor([5.0]))
+    ck = O.CheckpointingOptimizer(torch.optim.SGD([wq], lr=0.1, momentum=0.9), every=5, keep=2)
+    for i in range(12):
+        ck.zero_grad(); (wq ** 2).sum().backward(); ck.step()
+        if i == 9:
+            good = wq.detach().clone()
+    wq.data.fill_(1e9)
+    assert ck.rollback() == 10 and torch.equal(wq.detach(), good) and len(ck.snapshots) == 2 and ck.n == 10
+    wt = torch.nn.Parameter(torch.zeros(2))
+    tc = O.TemporalCreditOptimizer([wt], lr=1.0, trace_decay=0.5)
+    for gr in ([1.0, 0.0], [0.0, 1.0]):
+        wt.grad = torch.tensor(gr); tc.accumulate()
+    tc.step(reward=2.0)
+    assert wt.tolist() == [1.0, 2.0] and type(O.LowPrecisionOptimizer([torch.nn.Parameter(torch.zeros(2))])).__name__ == "LowPrecisionAdam"
+    # builders and task matching
+    model = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.LayerNorm(4))
+    groups = O.ParamGroupBuilder().no_decay_for(model, 0.1).build()
+    assert len(groups[0]["params"]) == 1 and len(groups[1]["params"]) == 3 and groups[1]["weight_decay"] == 0.0
+    opt = O.OptimizerBuilder("adamw").lr(3e-4).weight_decay(0.1).betas((0.9, 0.95)).build(model.parameters())
+    assert isinstance(opt, torch.optim.AdamW) and opt.defaults["betas"] == (0.9, 0.95) and type(O.OptimizerBuilder("lion").lr(1e-4).build(model.parameters())).__name__ == "Lion"
+    with pytest.raises(ValueError):
+        O.OptimizerBuilder("nope").build(model.parameters())
+    tm = O.TaskMatcher().with_defaults()
+    assert tm.suggest({"parameters": 7e9, "samples": 1e10, "gradient_noise": 0.3})["optimizer"] == "adamw" and tm.suggest({"parameters": 1.1e7, "samples": 1e6})["optimizer"] == "sgd" and tm.suggest({"parameters": 5e5, "samples": 1e5, "gradient_sparsity": 0.9})["optimizer"] == "adagrad"
+    assert tm.suggest({"parameters": 5e3, "samples": 500}, k=2)["optimizer"] == "lbfgs" and len(tm.suggest({"parameters": 5e3, "samples": 500}, k=2)["alternatives"]) == 2

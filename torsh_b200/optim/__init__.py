@@ -11,3 +11,6 @@ from .distributed import AsyncSGD, DistributedOptimizer, ElasticAveragingSGD
 from .mixed_precision import (AutocastModel, BF16Config, BF16Trainer, DynamicLossScaler, GradScaler, MixedPrecisionConfig,
                               MixedPrecisionOptimizer, MixedPrecisionTrainer)
 from .second_order import KFAC, AdaHessian, NaturalGradient, NewtonCG, Shampoo, TrustRegion, YellowFin
+from .more import (AdaDelta, AdaGrad, AdaMax, AdvancedAdam, Branin, CarbonConsciousOptimizer, CheckpointingOptimizer, CMAES, ConvergenceTracker, GaussianProcess,  # noqa: E402,F401
+                   LowPrecisionOptimizer, OpenAIES, OptimizerBenchmarks, OptimizerBuilder, OptimizerStressTester, ParamGroupBuilder, ParticleSwarmOptimizer, PowerCappedOptimizer, Rastrigin,
+                   Rosenbrock, ScheduleFreeAdamW, Sophia, Sphere, TaskMatcher, TemporalCreditOptimizer)
