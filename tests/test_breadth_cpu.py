@@ -6159,3 +6159,240 @@ def test_optim_more_adam_variants_population_methods_gp_benchmarks_stress_wrappe
     tm = O.TaskMatcher().with_defaults()
     assert tm.suggest({"parameters": 7e9, "samples": 1e10, "gradient_noise": 0.3})["optimizer"] == "adamw" and tm.suggest({"parameters": 1.1e7, "samples": 1e6})["optimizer"] == "sgd" and tm.suggest({"parameters": 5e5, "samples": 1e5, "gradient_sparsity": 0.9})["optimizer"] == "adagrad"
     assert tm.suggest({"parameters": 5e3, "samples": 500}, k=2)["optimizer"] == "lbfgs" and len(tm.suggest({"parameters": 5e3, "samples": 500}, k=2)["alternatives"]) == 2
+
+
+def test_series_models_var_vecm_x11_mice_wavelets_and_purged_validation():
+    import itertools
+    import numpy as np
+    from scipy import signal as sps
+    from torsh_b200 import series_models as sm
+
+    g = torch.Generator().manual_seed(0)
+    # ---- VAR: recover known matrices, stability, forecasts converge to the mean, FEVD rows sum to one, causality
+    A1 = torch.tensor([[0.5, 0.2], [0.0, 0.4]], dtype=torch.float64)
+    A2 = torch.tensor([[0.1, 0.0], [0.0, -0.2]], dtype=torch.float64)
+    c = torch.tensor([1.0, -0.5], dtype=torch.float64)
+    y = [torch.zeros(2, dtype=torch.float64)] * 2
+    for _ in range(6000):
+        y.append(c + A1 @ y[-1] + A2 @ y[-2] + 0.5 * torch.randn(2, generator=g, dtype=torch.float64))
+    y = torch.stack(y[200:])
+    var = sm.VAR(2).fit(y)
+    assert torch.allclose(var.coefs[0], A1, atol=0.05) and torch.allclose(var.coefs[1], A2, atol=0.05)
+    assert torch.allclose(var.intercept, c, atol=0.1) and var.is_stable()
+    assert torch.allclose(var.sigma_u, 0.25 * torch.eye(2, dtype=torch.float64), atol=0.03)
+    mean = torch.linalg.solve(torch.eye(2, dtype=torch.float64) - A1 - A2, c)
+    assert torch.allclose(var.forecast(200)[-1], mean, atol=0.15)
+    assert sm.VAR.select_order(y, 5, "bic") == 2
+    irf = var.impulse_response(8, orthogonal=False)
+    assert torch.allclose(irf[0], torch.eye(2, dtype=torch.float64)) and torch.allclose(irf[1], var.coefs[0])
+    assert torch.allclose(irf[2], var.coefs[0] @ var.coefs[0] + var.coefs[1])
+    fe = var.fevd(6)
+    assert torch.allclose(fe.sum(2), torch.ones(6, 2, dtype=torch.float64))
+    assert var.test_causality(y, caused=0, causing=1)["p_value"] < 1e-6           # y1 drives y0 through A1[0, 1]
+    assert var.test_causality(y, caused=1, causing=0)["p_value"] > 0.001
+
+    # ---- Johansen / VECM: two series sharing one random walk have rank one with vector proportional to (1, -2)
+    w = torch.randn(1500, generator=g, dtype=torch.float64).cumsum(0)
+    yy = torch.stack([2 * w + torch.randn(1500, generator=g, dtype=torch.float64), w + torch.randn(1500, generator=g, dtype=torch.float64)], 1)
+    jo = sm.johansen_test(yy, 1)
+    assert jo.rank == 1 and float(jo.trace_stat[0]) > jo.trace_crit_95[0] and float(jo.trace_stat[1]) < jo.trace_crit_95[1]
+    b = jo.eigenvectors[:, 0]
+    assert abs(float(b[1] / b[0]) + 2.0) < 0.1
+    indep = torch.randn(1500, 2, generator=g, dtype=torch.float64).cumsum(0)
+    assert sm.johansen_test(indep, 1).rank == 0
+    ve = sm.VECM(1).fit(yy)
+    assert ve.rank == 1 and abs(float(ve.beta[1, 0]) + 2.0) < 0.1 and float(ve.beta[0, 0]) == pytest.approx(1.0)
+    assert float(ve.alpha[0, 0]) < 0 or float(ve.alpha[1, 0]) > 0                 # error correction pulls back to equilibrium
+    fc = ve.forecast(50)
+    assert abs(float(fc[-1, 0] - 2 * fc[-1, 1])) < abs(float(yy[-1, 0] - 2 * yy[-1, 1])) + 0.5
+    Avar = ve.to_var()
+    lvl = Avar[0] @ yy[-1] + Avar[1] @ yy[-2] + ve.const                          # level form reproduces the one-step forecast
+    assert torch.allclose(lvl, fc[0], atol=1e-8)
+    eg = sm.engle_granger(yy[:, 0], yy[:, 1])
+    assert eg.cointegrated and abs(float(eg.beta[1]) - 2.0) < 0.1
+    assert not sm.engle_granger(indep[:, 0], indep[:, 1]).cointegrated
+    assert sm.phillips_perron(torch.randn(800, generator=g, dtype=torch.float64)).stationary
+    assert not sm.phillips_perron(w).stationary
+
+    # ---- Henderson and X-11
+    for L in (5, 9, 13, 23):
+        hw = sm.henderson_weights(L)
+        j = torch.arange(-(L // 2), L // 2 + 1, dtype=torch.float64)
+        assert float(hw.sum()) == pytest.approx(1.0, abs=1e-12) and abs(float((hw * j ** 2).sum())) < 1e-12
+    assert float(sm.henderson_weights(13)[6]) == pytest.approx(0.24006, abs=1e-5)
+    t = torch.arange(240, dtype=torch.float64)
+    season = torch.tensor([3.0, 1, -2, -4, -1, 2, 5, 3, -1, -3, -2, -1], dtype=torch.float64)
+    season = season - season.mean()
+    trend = 50 + 0.3 * t + 0.001 * t ** 2
+    x = trend + season.repeat(20) + 0.2 * torch.randn(240, generator=g, dtype=torch.float64)
+    d = sm.X11Decomposition(12).decompose(x)
+    assert float((d["seasonal"][24:-24] - season.repeat(20)[24:-24]).abs().max()) < 0.5
+    assert float((d["trend"][24:-24] - trend[24:-24]).abs().max()) < 0.6
+    assert torch.allclose(d["trend"] + d["seasonal"] + d["irregular"], x, atol=1e-9)
+    xm = trend * (1 + season.repeat(20) / 20)
+    dm = sm.X11Decomposition(12, "multiplicative").decompose(xm)
+    assert torch.allclose(dm["trend"] * dm["seasonal"] * dm["irregular"], xm, rtol=1e-9)
+    assert float((dm["seasonal"][24:-24] - (1 + season.repeat(20) / 20)[24:-24]).abs().max()) < 0.02
+    md = sm.MultiplicativeDecomposition(12).decompose(xm)
+    assert torch.allclose(md["trend"] * md["seasonal"] * md["residual"], xm, rtol=1e-9)
+    assert set(sm.STLDecomposition(12).decompose(x)) >= {"trend", "seasonal", "remainder"}
+    ms = sm.MSTLDecomposition([12, 4]).decompose(x)
+    assert set(ms["seasonal"]) == {4, 12}
+
+    # ---- SSA: a sine plus trend is captured by a few components and forecast by the recurrence
+    xs = 0.02 * t[:200] + torch.sin(2 * math.pi * t[:200] / 20)
+    ssa = sm.SSA(40).fit(xs)
+    assert float(ssa.explained()[:4].sum()) > 0.999
+    assert torch.allclose(ssa.reconstruct(range(len(ssa.S))), xs, atol=1e-8)
+    truth = 0.02 * t[200:210] + torch.sin(2 * math.pi * t[200:210] / 20)
+    assert float((ssa.forecast(10, rank=4) - truth).abs().max()) < 0.05
+
+    # ---- MICE: a column that is a linear function of the others is recovered
+    X = torch.randn(300, 3, generator=g, dtype=torch.float64)
+    full = torch.cat([X, (X @ torch.tensor([1.0, -2.0, 0.5], dtype=torch.float64) + 3)[:, None]], 1)
+    holes = full.clone()
+    holes[::7, 3] = float("nan")
+    holes[5::14, 0] = float("nan")
+    filled = sm.MICEImputer(iters=15).fit_transform(holes)
+    assert not torch.isnan(filled).any() and float((filled - full).abs().max()) < 1e-3
+    assert torch.equal(filled[~torch.isnan(holes)], full[~torch.isnan(holes)])
+    col = torch.arange(10, dtype=torch.float64).clone()
+    col[4] = float("nan")
+    assert float(sm.TimeSeriesImputer("linear").fit_transform(torch.stack([col, col], 1))[4, 1]) == pytest.approx(4.0)
+
+    # ---- smoothing classes
+    hw_x = 20 + 0.5 * t[:120] + season.repeat(10)
+    hw = sm.HoltWinters(12).fit(hw_x, optimize=True)
+    want = 20 + 0.5 * t[120:132] + season
+    assert float((hw.forecast(12) - want).abs().max()) < 0.5
+    hm = sm.HoltWinters(12, seasonal="multiplicative").fit((20 + 0.5 * t[:120]) * (1 + season.repeat(10) / 20))
+    assert float((hm.forecast(12) / ((20 + 0.5 * t[120:132]) * (1 + season / 20)) - 1).abs().max()) < 0.05
+    ses = sm.SimpleExpSmoothing().fit(torch.cat([torch.zeros(30), torch.ones(30) * 5]).double() + 0.01 * torch.randn(60, generator=g, dtype=torch.float64))
+    assert ses.alpha > 0.8 and float(ses.forecast(3)[0]) == pytest.approx(5.0, abs=0.1)
+    des = sm.DoubleExpSmoothing(0.8, 0.5).fit(3 + 2 * t[:50])
+    assert torch.allclose(des.forecast(3), 3 + 2 * t[50:53], atol=1e-6)
+    damped = sm.DoubleExpSmoothing(0.8, 0.5, phi=0.8).fit(3 + 2 * t[:50]).forecast(40)
+    assert float(damped[-1] - damped[-2]) < 0.01
+    ar = torch.zeros(600, dtype=torch.float64)
+    e = torch.randn(600, generator=g, dtype=torch.float64)
+    for i in range(1, 600):
+        ar[i] = 0.7 * ar[i - 1] + e[i]
+    arima = sm.ARIMA(1, 0, 0).fit(ar)
+    assert arima.forecast(5).shape == (5,) and abs(float(arima.forecast(1)[0]) - 0.7 * float(ar[-1])) < 0.3
+    assert sm.AutoARIMA(max_p=2, max_q=1).fit(ar).order[1] == 0
+
+    # ---- change points
+    steps = torch.cat([torch.zeros(80), torch.ones(70) * 4, torch.ones(90) * -1]).double() + 0.3 * torch.randn(240, generator=g, dtype=torch.float64)
+    for method in ("pelt", "binseg"):
+        r = sm.ChangePointDetector(method).detect(steps)
+        assert len(r["change_points"]) == 2 and abs(r["change_points"][0] - 80) <= 2 and abs(r["change_points"][1] - 150) <= 2
+        assert r["segment_means"][1] == pytest.approx(4.0, abs=0.2)
+
+    # ---- spectra against scipy
+    fs = 100.0
+    tt = torch.arange(4096, dtype=torch.float64) / fs
+    sig = torch.sin(2 * math.pi * 12 * tt) + 0.5 * torch.randn(4096, generator=g, dtype=torch.float64)
+    f, p = sm.PSDEstimator(fs, 512).estimate(sig)
+    f_ref, p_ref = sps.welch(sig.numpy(), fs, nperseg=512)
+    assert np.allclose(f.numpy(), f_ref) and np.allclose(p.numpy(), p_ref, rtol=1e-9)
+    other = torch.sin(2 * math.pi * 12 * tt + 0.7) + 0.5 * torch.randn(4096, generator=g, dtype=torch.float64)
+    co = sm.CoherenceAnalyzer(fs, 512).analyze(sig, other)
+    _, c_ref = sps.coherence(sig.numpy(), other.numpy(), fs, nperseg=512)
+    assert np.allclose(co["coherence"].numpy(), c_ref, rtol=1e-8)
+    k12 = int(torch.argmin((co["freqs"] - 12).abs()))
+    assert float(co["coherence"][k12]) > 0.9 and float(co["phase"][k12]) == pytest.approx(0.7, abs=0.1)
+    fa = sm.FFTAnalyzer(fs).analyze(3 * torch.sin(2 * math.pi * 12.5 * tt[:4000]))
+    assert fa["dominant_frequency"] == pytest.approx(12.5, abs=0.03) and fa["dominant_amplitude"] == pytest.approx(3.0, rel=0.02)
+    assert sm.PeriodogramAnalyzer().analyze(torch.sin(2 * math.pi * t / 24))["dominant_period"] == pytest.approx(24, rel=0.05)
+
+    # ---- CWT: a chirp's ridge follows its instantaneous frequency
+    cw = sm.CWTAnalyzer(6.0, fs)
+    freqs = torch.linspace(4, 30, 40, dtype=torch.float64)
+    scales = cw.frequency_to_scale(freqs)
+    assert torch.allclose(cw.scale_to_frequency(scales), freqs)
+    res = cw.analyze(torch.sin(2 * math.pi * 12 * tt), scales)
+    assert res["dominant_frequency"] == pytest.approx(12, abs=0.7)
+    chirp = torch.sin(2 * math.pi * (5 * tt + 0.25 * tt ** 2))                      # 5 Hz rising 0.5 Hz/s
+    P = cw.transform(chirp, scales).abs() / scales.sqrt()[:, None]
+    for sample in (1000, 2000, 3000):
+        assert float(freqs[int(P[:, sample].argmax())]) == pytest.approx(5 + 0.5 * sample / fs, abs=1.0)
+
+    # ---- wavelets: perfect reconstruction, energy conservation, polynomial cancellation, denoising, packets
+    for name in ("haar", "db2", "db4"):
+        wd = sm.WaveletDecomposer(name, 3)
+        z = torch.randn(256, generator=g, dtype=torch.float64)
+        cs = wd.decompose(z)
+        assert [len(v) for v in cs] == [32, 32, 64, 128]
+        assert torch.allclose(wd.reconstruct(cs), z, atol=1e-10)
+        assert float(sum((v ** 2).sum() for v in cs)) == pytest.approx(float((z ** 2).sum()), rel=1e-10)
+    lin = sm.WaveletDecomposer("db2", 1).decompose(torch.arange(64, dtype=torch.float64))[1]
+    assert float(lin[:-1].abs().max()) < 1e-10                                     # two vanishing moments (wrap-around aside)
+    clean = torch.sin(2 * math.pi * torch.arange(512, dtype=torch.float64) / 128)
+    noisy = clean + 0.3 * torch.randn(512, generator=g, dtype=torch.float64)
+    den = sm.WaveletDecomposer("db4", 4).denoise(noisy)
+    assert float((den - clean).pow(2).mean()) < 0.35 * float((noisy - clean).pow(2).mean())
+    assert float(sm.WaveletDecomposer("db4", 4).energy_by_level(clean)[0]) > 0.9
+    wp = sm.WaveletPacketDecomposer("db2", 3)
+    leaves = wp.decompose(noisy)
+    assert len(leaves) == 8 and torch.allclose(wp.reconstruct(leaves), noisy, atol=1e-10)
+    bb = wp.best_basis(clean)
+    assert torch.allclose(wp.reconstruct(bb), clean, atol=1e-10) and len(bb) <= 8
+
+    # ---- transfer entropy with a common driver
+    n = 4000
+    z = torch.randn(n, generator=g, dtype=torch.float64)
+    xa = torch.roll(z, 1) + 0.3 * torch.randn(n, generator=g, dtype=torch.float64)
+    yb = torch.roll(z, 2) + 0.3 * torch.randn(n, generator=g, dtype=torch.float64)  # both driven by z; x leads y only through z
+    te = sm.TransferEntropyEstimator(3).estimate(xa, yb)
+    cte = sm.ConditionalTransferEntropy(3).estimate(xa, yb, torch.roll(z, 1))
+    assert te > 0.1 and cte < 0.5 * te
+    assert sm.TransferEntropyEstimator(3).net_flow(xa, yb) > 0
+    assert sm.GrangerCausality(2).test(yb, xa)["p_value"] < 1e-6
+    assert "pp" in sm.StationarityTestSuite().run(z[:500]) and "ljung_box" in sm.ResidualDiagnostics().run(z[:500])
+    rs = sm.RollingStatistics(5)
+    assert float(rs.mean(t[:10])[-1]) == pytest.approx(7.0) and torch.isnan(rs.zscore(t[:10])[0])
+
+    # ---- detectors
+    base = torch.sin(2 * math.pi * t / 24) + 0.05 * torch.randn(240, generator=g, dtype=torch.float64)
+    spiked = base.clone()
+    spiked[100] += 4.0
+    assert bool(sm.OutlierDetector("hampel").detect(spiked)[100]) and int(sm.OutlierDetector("hampel").detect(spiked).sum()) <= 3
+    assert abs(float(sm.OutlierDetector("hampel").treat(spiked)[100] - base[100])) < 0.3
+    for m in ("zscore", "mad", "iqr"):
+        assert bool(sm.StatisticalDetector(m, 3.0).detect(spiked)[100])
+    wdet = sm.WindowDetector(24, 3.5).detect(spiked)
+    assert bool(wdet[100]) and int(wdet.sum()) <= 3
+    torch.manual_seed(0)
+    la = sm.LSTMAnomaly(12, 16).fit(base, epochs=80)
+    sc = la.scores(spiked)
+    assert int(sc.argmax()) in (100, 101) and bool(la.detect(spiked)[int(sc.argmax())])
+    assert int(la.detect(base).sum()) <= 6
+
+    # ---- container and validation splitters
+    ts = sm.TimeSeries(torch.arange(10.0), torch.arange(10.0) * 30, frequency=1 / 30)
+    r = ts.resample(60, "mean")
+    assert len(r) == 5 and torch.allclose(r.values, torch.tensor([0.5, 2.5, 4.5, 6.5, 8.5], dtype=torch.float64))
+    xi, yo = ts.windows(4, 2)
+    assert xi.shape == (5, 4) and yo.shape == (5, 2) and float(yo[0, 0]) == 4
+    assert torch.isnan(ts.lag(2).values[:2]).all() and float(ts.lag(2).values[2]) == 0 and len(ts.diff(2)) == 8
+    a, b2 = ts.split(0.7)
+    assert len(a) == 7 and len(b2) == 3
+    for tr, te_ in sm.BlockedTimeSeriesCV(4, 0.25, gap=1).split(100):
+        assert max(tr) + 1 < min(te_) and min(tr) // 25 == max(te_) // 25
+    pcv = sm.PurgedTimeSeriesCV(5, label_horizon=3, embargo=4)
+    for tr, te_ in pcv.split(100):
+        lo, hi = te_[0], te_[-1] + 1
+        assert not set(tr) & set(range(lo - 3, hi + 4)) and set(tr) | set(range(max(0, lo - 3), min(100, hi + 4))) == set(range(100))
+    ccv = sm.CombinatorialPurgedCV(6, 2, label_horizon=1, embargo=1)
+    splits = list(ccv.split(60))
+    assert len(splits) == 15 and ccv.num_paths() == 5
+    assert all(len(te_) == 20 and not set(tr) & set(te_) for tr, te_ in splits)
+    ff = lambda tr, h, alpha: sm.SimpleExpSmoothing(alpha).fit(tr).forecast(h)
+    walk = torch.randn(300, generator=g, dtype=torch.float64).cumsum(0)
+    ramp = 0.5 * torch.arange(300, dtype=torch.float64) + 0.1 * torch.randn(300, generator=g, dtype=torch.float64)
+    nested = sm.NestedTimeSeriesCV(3, 3).run(ramp, [0.05, 0.95], ff)
+    assert nested["chosen"] == [0.95] * 3 and len(nested["scores"]) == 3         # a ramp wants the most recent level
+    sc = sm.ScoredTimeSeriesCV(4).score(walk, lambda tr, h: tr[-1].repeat(h))
+    assert len(sc["scores"]) == 4 and sc["std"] >= 0
+    fm = sm.ForecastMetrics.compute(torch.tensor([1.0, 2, 3]), torch.tensor([1.0, 2, 4]))
+    assert fm["mae"] == pytest.approx(1 / 3)
