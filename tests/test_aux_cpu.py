@@ -2822,3 +2822,244 @@ def test_rstorch_surface_matches_the_reference_python_package_names():
         assert not missing, (mod, missing)
     x = rstorch.tensor([[1.0, -2.0], [0.5, 3.0]])
     assert rstorch.nn.relu(x).tolist() == [[1.0, 0.0], [0.5, 3.0]] and float(rstorch.nn.mse_loss(x, x)) == 0.0 and type(rstorch.nn.parameter(x)).__name__ == "Parameter" and rstorch.FloatTensor is rstorch.Tensor and rstorch.uint16.size_bytes == 2
+
+
+def test_metric_objects_accumulate_like_sklearn_and_merge_across_shards():
+    import numpy as np
+    from sklearn import metrics as skm
+    from torsh_b200.utils import metric_objects as mo
+
+    g = torch.Generator().manual_seed(0)
+    n, C = 1200, 4
+    logits = torch.randn(n, C, generator=g)
+    y = torch.randint(0, C, (n,), generator=g)
+    logits[torch.arange(n), y] += 1.0
+    pred = logits.argmax(1)
+    coll = mo.MetricCollection({"acc": mo.Accuracy(), "top2": mo.TopKAccuracy(2), "prec": mo.Precision(C, "macro"), "rec": mo.Recall(C, "weighted"),
+                                "f1": mo.F1Score(C, "macro"), "multi": mo.MultiClassMetrics(C)})
+    for lo in range(0, n, 100):
+        coll.update(logits[lo:lo + 100], y[lo:lo + 100])
+    out = coll.compute()
+    assert out["acc"] == pytest.approx(skm.accuracy_score(y, pred))
+    assert out["top2"] == pytest.approx(skm.top_k_accuracy_score(y, logits, k=2))
+    assert out["prec"] == pytest.approx(skm.precision_score(y, pred, average="macro"))
+    assert out["rec"] == pytest.approx(skm.recall_score(y, pred, average="weighted"))
+    assert out["f1"] == pytest.approx(skm.f1_score(y, pred, average="macro"))
+    assert out["multi/cohen_kappa"] == pytest.approx(skm.cohen_kappa_score(y, pred))
+    assert out["multi/mcc"] == pytest.approx(skm.matthews_corrcoef(y, pred))
+    assert out["multi/balanced_accuracy"] == pytest.approx(skm.balanced_accuracy_score(y, pred))
+    cm = mo.ConfusionMatrix(C)
+    cm.update(logits, y)
+    assert np.array_equal(cm.compute().numpy(), skm.confusion_matrix(y, pred))
+    assert torch.allclose(cm.normalized("true").sum(1), torch.ones(C, dtype=torch.float64))
+    a, b = mo.Accuracy(), mo.Accuracy()                                           # two shards merge to the global value
+    a.update(logits[:500], y[:500]); b.update(logits[500:], y[500:])
+    assert a.merge(b).compute() == pytest.approx(out["acc"])
+    batch_value = a(logits[:10], y[:10])                                          # call = batch value, state keeps accumulating
+    assert batch_value == pytest.approx(float((pred[:10] == y[:10]).float().mean())) and float(a._state["total"]) == n + 10
+    assert a.sync().compute() == a.compute() and a.reset().compute() == 0.0
+
+    # ---- binary scores: histogram curves against the exact ones
+    s = torch.sigmoid(torch.randn(4000, generator=g) + 1.5 * (torch.arange(4000) % 2))
+    t = (torch.arange(4000) % 2)
+    tm = mo.ThresholdMetrics(2000)
+    tm.update(s[:2000], t[:2000]); tm.update(s[2000:], t[2000:])
+    assert tm.auroc() == pytest.approx(skm.roc_auc_score(t, s), abs=2e-4)
+    assert tm.average_precision() == pytest.approx(skm.average_precision_score(t, s), abs=2e-3)
+    thr, f1 = tm.best_threshold("f1")
+    assert f1 == pytest.approx(max(skm.f1_score(t, s >= c) for c in np.linspace(0.05, 0.95, 91)), abs=5e-3) and 0.2 < thr < 0.8
+    sa = mo.StreamingAUROC(2000); sa.update(s, t)
+    assert sa.compute() == pytest.approx(tm.auroc())
+    svg = mo.ROCCurvePlot().render({"model": tm})
+    assert svg.startswith("<svg") and "AUC 0." in svg and "polyline" in svg and "AP 0." in mo.PRCurvePlot().render({"m": tm})
+
+    # ---- regression
+    p = torch.randn(900, generator=g, dtype=torch.float64)
+    tt = 0.7 * p + 0.3 * torch.randn(900, generator=g, dtype=torch.float64) + 2
+    reg = mo.MetricCollection([mo.MSE(), mo.RMSE(), mo.MAE(), mo.MAPE(), mo.SMAPE(), mo.R2Score(), mo.ExplainedVariance(), mo.HuberLoss(0.5), mo.LogCoshLoss(), mo.QuantileLoss(0.9)])
+    for lo in range(0, 900, 300):
+        reg.update(p[lo:lo + 300], tt[lo:lo + 300])
+    r = reg.compute()
+    assert r["MSE"] == pytest.approx(skm.mean_squared_error(tt, p)) and r["RMSE"] == pytest.approx(math.sqrt(r["MSE"]))
+    assert r["MAE"] == pytest.approx(skm.mean_absolute_error(tt, p)) and r["MAPE"] == pytest.approx(100 * skm.mean_absolute_percentage_error(tt, p))
+    assert r["R2Score"] == pytest.approx(skm.r2_score(tt, p)) and r["ExplainedVariance"] == pytest.approx(skm.explained_variance_score(tt, p))
+    assert r["QuantileLoss"] == pytest.approx(skm.mean_pinball_loss(tt, p, alpha=0.9))
+    assert r["HuberLoss"] == pytest.approx(float(torch.nn.functional.huber_loss(p, tt, delta=0.5)))
+    assert r["LogCoshLoss"] == pytest.approx(float(torch.log(torch.cosh(p - tt)).mean()))
+    r2 = mo.R2Score(); r2.update(p, tt)
+    assert r2.adjusted(3) < r2.compute()
+
+    # ---- ranking
+    scores = torch.rand(50, 20, generator=g)
+    rel = torch.randint(0, 4, (50, 20), generator=g).float() * (torch.rand(50, 20, generator=g) > 0.5)
+    nd = mo.NDCG(10, exponential=False); nd.update(scores[:25], rel[:25]); nd.update(scores[25:], rel[25:])
+    assert nd.compute() == pytest.approx(skm.ndcg_score(rel.numpy(), scores.numpy(), k=10), abs=1e-9)
+    binrel = (rel > 0).float()
+    mp = mo.MeanAveragePrecision(); mp.update(scores, binrel)
+    assert mp.compute() == pytest.approx(np.mean([skm.average_precision_score(binrel[i], scores[i]) for i in range(50)]), abs=1e-9)
+    ra = mo.RankingAUC(); ra.update(scores, binrel)
+    assert ra.compute() == pytest.approx(np.mean([skm.roc_auc_score(binrel[i], scores[i]) for i in range(50)]), abs=1e-9)
+    one = torch.tensor([[0.9, 0.8, 0.7, 0.1]]); relone = torch.tensor([[0.0, 0, 1, 1]])
+    for cls, want in ((mo.MeanReciprocalRank, 1 / 3), (mo.PrecisionAtK, 1 / 3), (mo.RecallAtK, 0.5), (mo.HitRateAtK, 1.0), (mo.F1AtK, 0.4)):
+        m = cls(3); m.update(one, relone)
+        assert m.compute() == pytest.approx(want), cls.__name__
+    cov = mo.Coverage(10); cov.update(torch.tensor([[0, 1, 2], [0, 1, 3]]))
+    assert cov.compute() == pytest.approx(0.4) and 0 < cov.gini() < 1
+    feats = torch.eye(4)
+    dv = mo.Diversity(feats); dv.update(torch.tensor([[0, 1, 2]])); dv.update(torch.tensor([[0, 0, 0]]))
+    assert dv.compute() == pytest.approx(0.5)
+    nv = mo.Novelty(torch.tensor([8.0, 4, 2, 2])); nv.update(torch.tensor([[0, 3]]))
+    assert nv.compute() == pytest.approx((1 + 3) / 2)
+
+    # ---- clustering objects wrap the functions
+    pts = torch.cat([torch.randn(60, 2, generator=g) * 0.3, torch.randn(60, 2, generator=g) * 0.3 + 4])
+    lab = torch.cat([torch.zeros(60), torch.ones(60)]).long()
+    sil = mo.SilhouetteScore(); sil.update(pts[:60], lab[:60]); sil.update(pts[60:], lab[60:])
+    assert sil.compute() == pytest.approx(skm.silhouette_score(pts.numpy(), lab.numpy()), abs=1e-5)
+    ari = mo.AdjustedRandIndex(); ari.update(lab, 1 - lab)
+    vm = mo.VMeasure(); vm.update(lab, 1 - lab)
+    assert ari.compute() == pytest.approx(1.0) and vm.compute() == pytest.approx(1.0)
+    db = mo.DaviesBouldin(); db.update(pts, lab)
+    assert db.compute() == pytest.approx(skm.davies_bouldin_score(pts.numpy(), lab.numpy()), rel=1e-4) and not db.higher_is_better
+
+    # ---- language model and calibration
+    lm_logits = torch.randn(6, 9, 30, generator=g)
+    lm_t = torch.randint(0, 30, (6, 9), generator=g)
+    lm_t[0, :3] = -100
+    ppl = mo.Perplexity(); ppl.update(lm_logits[:3], lm_t[:3]); ppl.update(lm_logits[3:], lm_t[3:])
+    assert ppl.compute() == pytest.approx(float(torch.exp(torch.nn.functional.cross_entropy(lm_logits.reshape(-1, 30), lm_t.reshape(-1), ignore_index=-100))), rel=1e-5)
+    probs = torch.softmax(2.5 * logits, 1)                                          # over-confident
+    ece = mo.ExpectedCalibrationError(10); ece.update(probs[:600], y[:600]); ece.update(probs[600:], y[600:])
+    from torsh_b200.utils.metrics_ext import calibration_error
+    conf, hit = probs.max(1).values, (probs.argmax(1) == y)
+    assert ece.compute() == pytest.approx(calibration_error(conf, hit, 10), abs=1e-9)
+    mce = mo.MaximumCalibrationError(10); mce.update(probs, y)
+    assert mce.compute() >= ece.compute() > 0.02
+    rd = mo.ReliabilityDiagram(10); rd.update(probs, y)
+    assert "ECE 0." in mo.CalibrationCurvePlot().render({"net": rd})
+    bs = mo.BrierScore(); bs.update(probs, y)
+    assert bs.compute() == pytest.approx(float(((probs - torch.nn.functional.one_hot(y, C)) ** 2).sum(1).mean()), rel=1e-6)
+    bsb = mo.BrierScore(); bsb.update(s, t)
+    assert bsb.compute() == pytest.approx(skm.brier_score_loss(t, s))
+    pic = mo.PredictionIntervalCoverage(); pic.update(p - 1, p + 1, p + 0.5 * torch.randn(900, generator=g, dtype=torch.float64))
+    assert pic.compute()["coverage"] == pytest.approx(0.954, abs=0.03) and pic.compute()["mean_width"] == pytest.approx(2.0)
+    members = torch.softmax(torch.randn(5, 40, 3, generator=g) * 2, -1)
+    eu = mo.EnsembleUncertainty.decompose(members)
+    assert bool((eu["epistemic"] >= -1e-6).all()) and torch.allclose(eu["total"], eu["aleatoric"] + eu["epistemic"])
+    agree = members[:1].expand(5, -1, -1)
+    assert float(mo.EnsembleUncertainty.decompose(agree)["epistemic"].abs().max()) < 1e-6
+    assert float(mo.EntropyMeasures.normalized_entropy(torch.full((1, 4), 0.25))) == pytest.approx(1.0)
+
+    # ---- fairness
+    grp = torch.randint(0, 2, (3000,), generator=g)
+    truth = (torch.rand(3000, generator=g) < 0.5).long()
+    biased = torch.where(grp == 1, truth | (torch.rand(3000, generator=g) < 0.4).long(), truth & (torch.rand(3000, generator=g) < 0.7).long())
+    fm = mo.FairnessMetrics(2); fm.update(biased[:1500], truth[:1500], grp[:1500]); fm.update(biased[1500:], truth[1500:], grp[1500:])
+    fr = fm.compute()
+    rate = lambda m: float(biased[m].double().mean())
+    assert fr["demographic_parity"]["difference"] == pytest.approx(abs(rate(grp == 1) - rate(grp == 0)), abs=1e-9)
+    assert fr["equalized_odds"]["tpr_gap"] == pytest.approx(abs(rate((grp == 1) & (truth == 1)) - rate((grp == 0) & (truth == 1))), abs=1e-9)
+    assert fr["equalized_odds"]["fpr_gap"] == pytest.approx(0.4, abs=0.05) and fr["demographic_parity"]["ratio"] < 0.8
+    fair = mo.DemographicParity(2); fair.update(truth, truth, grp)
+    assert fair.compute()["difference"] < 0.06
+    gc = mo.GroupCalibration(2, 5); gc.update(s[:3000], t[:3000], grp)
+    assert len(gc.compute()["ece_per_group"]) == 2
+    x_f = torch.randn(200, 3, generator=g)
+    smooth = mo.IndividualFairness(1.0).evaluate(x_f, 0.5 * x_f[:, :1])
+    rough = mo.IndividualFairness(1.0).evaluate(x_f, 5.0 * x_f[:, :1])
+    assert smooth["violation_rate"] == 0.0 and smooth["max_ratio"] <= 0.5 + 1e-9 and rough["violation_rate"] > 0.5
+    lab3 = torch.randint(0, 3, (3000,), generator=g)
+    g3 = ((torch.rand(3000, generator=g) < 0.5 + 0.1 * (lab3 == 0)) * 1).long()
+    amplified = torch.where((g3 == 1) & (torch.rand(3000, generator=g) < 0.3), torch.zeros_like(lab3), lab3)
+    assert mo.BiasAmplification.compute(amplified, lab3, g3, 3) > 0.01 and abs(mo.BiasAmplification.compute(lab3, lab3, g3, 3)) < 1e-12
+
+    # ---- streaming statistics and chunked evaluation
+    data = torch.randn(1000, generator=g, dtype=torch.float64) * 3 + 1
+    s1, s2 = mo.StreamingStats(), mo.StreamingStats()
+    for lo in range(0, 600, 50):
+        s1.update(data[lo:lo + 50])
+    s2.update(data[600:])
+    st = s1.merge(s2).compute()
+    assert st["count"] == 1000 and st["mean"] == pytest.approx(float(data.mean())) and st["variance"] == pytest.approx(float(data.var()))
+    assert st["min"] == float(data.min()) and st["max"] == float(data.max())
+    lin = torch.nn.Linear(8, C)
+    xin = torch.randn(1000, 8, generator=g)
+    ylab = lin(xin).argmax(1)
+    ev = mo.ChunkedEvaluator({"acc": mo.Accuracy(), "cm": mo.ConfusionMatrix(C)}, chunk_size=128).evaluate(lin, xin, ylab)
+    assert ev["acc"] == 1.0 and float(ev["cm"].sum()) == 1000
+
+    # ---- hypothesis tests, resampling, cross-validation, stability
+    base = torch.rand(60, generator=g, dtype=torch.float64)
+    better = base + 0.05 + 0.01 * torch.randn(60, generator=g, dtype=torch.float64)
+    for cls in (mo.PairedTTest, mo.WilcoxonTest):
+        res = cls(0.05).test(better, base)
+        assert res.significant and res.p_value < 1e-6 and res.name == cls.__name__
+    assert not mo.PairedTTest().test(base, base + 0.001 * torch.randn(60, generator=g, dtype=torch.float64)).significant
+    ca, cb = torch.rand(500, generator=g) < 0.9, torch.rand(500, generator=g) < 0.6
+    assert mo.McNemarTest().test(ca, cb).significant and mo.McNemarTest().test(ca, ca).p_value == 1.0
+    assert mo.MannWhitneyTest().test(better, base - 0.3).significant
+    assert mo.KruskalWallisTest().test(base, base + 1, base + 2).significant
+    table = torch.stack([base, base + 0.2, base + 0.4], 1)
+    assert mo.FriedmanTest().test(table).p_value < 1e-6 and mo.NemenyiTest().test(table)["significant"][0, 2]
+    assert mo.PermutationTest().test(better, base - 0.3, 500).significant
+    assert mo.FiveByTwoCVTest().test(torch.tensor([[0.1, 0.12], [0.09, 0.11], [0.1, 0.1], [0.12, 0.1], [0.11, 0.09]])).p_value < 0.05
+    ci = mo.BootstrapCI(300).interval(lambda a, b: float((a == b).float().mean()), pred, y)
+    assert ci["lower"] < ci["estimate"] < ci["upper"] and ci["upper"] - ci["lower"] < 0.08
+    assert mo.EffectSize.compute(better, base) > 0.1
+    mc = mo.MultipleComparisonCorrection("holm").correct([0.001, 0.04, 0.03])
+    assert list(mc["reject"]) == [True, False, False]
+    cv = mo.CrossValidator(5).run(100, lambda tr, te: len(te) / 100)
+    assert cv["scores"] == [0.2] * 5 and cv["std"] == 0.0
+    strat = mo.CrossValidator(4, stratified=True).run(torch.arange(80) % 4, lambda tr, te: float(len(te)))
+    assert strat["mean"] == 20.0
+    stab = mo.StabilityAnalyzer(0.02)
+    assert stab.analyze([0.91, 0.915, 0.905, 0.91])["stable"] and not stab.analyze([0.9, 0.8, 0.95])["stable"]
+
+    # ---- model selection
+    assert mo.AIC.compute(-100.0, 3) == 206.0 and mo.BIC.compute(-100.0, 3, 50) == pytest.approx(3 * math.log(50) + 200)
+    assert mo.AICc.compute(-100.0, 3, 50) == pytest.approx(206 + 24 / 46) and mo.HQIC.compute(-100.0, 3, 50) == pytest.approx(6 * math.log(math.log(50)) + 200)
+    mmc = mo.MultiModelComparison("bic").add("small", -120.0, 2, 200).add("right", -100.0, 4, 200).add("big", -99.5, 12, 200).report()
+    assert mmc["ranking"][0] == "right" and sum(mmc["weights"].values()) == pytest.approx(1.0) and mmc["evidence_ratio"]["big"] > 100
+
+    # ---- few-shot, meta-learning, domain shift, continual learning
+    fs = mo.FewShotMetrics()
+    for e in range(40):
+        yy = torch.randint(0, 5, (25,), generator=g)
+        fs.update(torch.where(torch.rand(25, generator=g) < 0.8, yy, (yy + 1) % 5), yy)
+    f = fs.compute()
+    assert f["episodes"] == 40 and f["mean_accuracy"] == pytest.approx(0.8, abs=0.05) and 0 < f["ci95"] < 0.05
+    ml = mo.MetaLearningMetrics()
+    for k in range(6):
+        ml.update([2.0, 1.0, 0.6, 0.5, 0.48 + 0.01 * k])
+    mlr = ml.compute(0.9)
+    assert mlr["adaptation_gain"] == pytest.approx(1.495, abs=0.01) and mlr["steps_to_fraction"] == 2 and mlr["tasks_improved"] == 1.0
+    src = torch.randn(300, 5, generator=g)
+    same, shifted = torch.randn(300, 5, generator=g), torch.randn(300, 5, generator=g) + 1.5
+    da_same = mo.DomainAdaptationMetrics.compute(src, same, 0.9, 0.88)
+    da_shift = mo.DomainAdaptationMetrics.compute(src, shifted, 0.9, 0.6)
+    assert da_shift["mmd_rbf"] > 10 * abs(da_same["mmd_rbf"]) and da_shift["proxy_a_distance"] > 1.5 > 0.8 > da_same["proxy_a_distance"]
+    assert da_shift["accuracy_gap"] == pytest.approx(0.3) and da_shift["mmd_linear"] == pytest.approx(5 * 1.5 ** 2, rel=0.25)
+    cl = mo.ContinualLearningMetrics.compute([[0.9, 0.1, 0.1], [0.7, 0.9, 0.1], [0.6, 0.8, 0.9]])
+    assert cl["forgetting"] > 0 and cl["average_accuracy"] == pytest.approx((0.6 + 0.8 + 0.9) / 3)
+
+    # ---- plots, LaTeX and experiment tracking
+    cm_svg = mo.ConfusionMatrixPlot().render(cm.compute(), ["a", "b", "c", "d"])
+    assert cm_svg.count("<rect") == 1 + 16 and ">a<" in cm_svg
+    assert "loss" in mo.LearningCurvePlot().render({"loss": [1.0, 0.5, 0.3], "val": [1.1, 0.7, 0.6]})
+    fi = mo.FeatureImportancePlot().render({"age": 0.5, "income": -0.2, "zip": 0.05})
+    assert fi.index("age") < fi.index("income") < fi.index("zip") and "#d62728" in fi
+    tex = mo.LatexReportBuilder("Main results").add("base_line", {"acc": 0.81, "ece": 0.09}, {"ece": False}).add("ours", {"acc": 0.86, "ece": 0.04}).build()
+    assert r"\textbf{0.860}" in tex and r"\textbf{0.040}" in tex and r"base\_line" in tex and r"\toprule" in tex and r"\textbf{0.810}" not in tex
+    import tempfile
+    with tempfile.TemporaryDirectory() as d:
+        tr = mo.ExperimentTracker(d)
+        for name, lr, final in (("a", 0.1, 0.8), ("b", 0.01, 0.9)):
+            rid = tr.start_run(name, {"lr": lr})
+            for step, v in enumerate((0.5, final)):
+                tr.log_metrics({"acc": v, "loss": 1 - v}, step)
+            tr.end_run()
+        assert tr.best_run("acc") == "0001-b" and tr.best_run("loss", "min") == "0001-b" and tr.compare("acc")[0][0] == "0001-b"
+        saved = json.loads((Path(d) / "0000-a.json").read_text())
+        assert saved["params"] == {"lr": 0.1} and saved["metrics"]["acc"][-1] == [1, 0.8] and saved["status"] == "finished"
+        tr.to_mlflow("0001-b", Path(d) / "mlruns")
+        assert len(list((Path(d) / "mlruns").rglob("metrics/acc"))) == 1

@@ -1,5 +1,5 @@
 """Utilities: profiler, metrics, environment report, benchmarking helpers."""
-from . import metrics, profiler
+from . import metric_objects, metrics, profiler
 from .metrics import MetricsLogger
 from .profiler import CommunicationProfiler, Profiler, profile_block
 
