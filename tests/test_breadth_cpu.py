@@ -6396,3 +6396,96 @@ def test_series_models_var_vecm_x11_mice_wavelets_and_purged_validation():
     assert len(sc["scores"]) == 4 and sc["std"] >= 0
     fm = sm.ForecastMetrics.compute(torch.tensor([1.0, 2, 3]), torch.tensor([1.0, 2, 4]))
     assert fm["mae"] == pytest.approx(1 / 3)
+
+
+def test_cluster_estimators_match_sklearn_and_hdbscan_finds_varied_density_groups():
+    import numpy as np
+    from sklearn import cluster as skc
+    from sklearn.metrics import adjusted_rand_score
+    from torsh_b200 import cluster_models as cm
+
+    g = torch.Generator().manual_seed(0)
+    centres = torch.tensor([[0.0, 0], [6, 0], [0, 6], [6, 6]])
+    x = torch.cat([c + 0.5 * torch.randn(80, 2, generator=g) for c in centres])
+    truth = torch.arange(4).repeat_interleave(80)
+
+    km = cm.KMeans(4, n_init=3, seed=0).fit(x)
+    ref = skc.KMeans(4, n_init=3, random_state=0).fit(x.numpy())
+    assert km.inertia_ == pytest.approx(ref.inertia_, rel=1e-4) and adjusted_rand_score(truth, km.labels_) == 1.0
+    assert km.result.converged and km.result.n_iter < 30
+    assert torch.equal(km.predict(x), km.labels_) and km.transform(x).shape == (320, 4)
+    for init in ("forgy", "random_partition"):
+        assert adjusted_rand_score(truth, cm.KMeans(4, init=init, n_init=6, seed=1).fit_predict(x)) == 1.0
+    assert adjusted_rand_score(truth, cm.KMeans(4, distance="manhattan", seed=0).fit_predict(x)) == 1.0
+    mb = cm.KMeans(4, batch_size=64, max_iter=200, n_init=2, seed=0).fit(x)
+    assert adjusted_rand_score(truth, mb.labels_) > 0.95 and mb.inertia_ < 1.2 * ref.inertia_
+    dirs = torch.nn.functional.normalize(torch.tensor([[1.0, 0, 0], [0, 1, 0], [0, 0, 1]]), dim=1)
+    xs = torch.cat([(d + 0.1 * torch.randn(50, 3, generator=g)) * (1 + 5 * torch.rand(50, 1, generator=g)) for d in dirs])
+    cos = cm.KMeans(3, distance="cosine", n_init=3, seed=0).fit(xs)
+    assert adjusted_rand_score(torch.arange(3).repeat_interleave(50), cos.labels_) == 1.0            # scale does not matter
+    assert torch.allclose(cos.cluster_centers_.norm(dim=1), torch.ones(3), atol=1e-5)
+    one_chunk = cm.ChunkedDataProcessor(10 ** 6).assign(x, km.cluster_centers_)
+    small = cm.ChunkedDataProcessor(37).assign(x, km.cluster_centers_)
+    assert torch.equal(one_chunk[0], small[0]) and torch.allclose(one_chunk[1], small[1])
+    sums, cnt = cm.ChunkedDataProcessor(37).reduce(x, km.labels_, 4)
+    assert torch.allclose(sums / cnt[:, None], km.cluster_centers_, atol=1e-4)
+    empty_seed = cm.KMeans(4, init="forgy", n_init=1, seed=0)
+    empty_seed.fit(torch.cat([x, x[:1] + 100]))                                                        # an outlier cannot leave a cluster empty
+    assert len(torch.unique(empty_seed.labels_)) == 4
+
+    inc = cm.IncrementalCentroidUpdater(centres + 1.0)
+    for lo in range(0, 320, 40):
+        perm = torch.randperm(320, generator=g)[:40]
+        inc.update(x[perm], truth[perm])
+    assert float((inc.centres - centres).abs().max()) < 0.4 and float(inc.counts.sum()) == 320
+    drift = cm.IncrementalCentroidUpdater(torch.zeros(1, 2), decay=0.5)
+    for step in range(20):
+        drift.update(torch.full((10, 2), float(step)), torch.zeros(10, dtype=torch.long))
+    assert float(drift.centres[0, 0]) > 17.5                                                           # follows the stream
+
+    # ---- DBSCAN: identical partition and noise set as scikit-learn
+    moons_t = torch.linspace(0, math.pi, 150)
+    moons = torch.cat([torch.stack([moons_t.cos(), moons_t.sin()], 1), torch.stack([1 - moons_t.cos(), 0.4 - moons_t.sin()], 1)]) + 0.04 * torch.randn(300, 2, generator=g)
+    moons = torch.cat([moons, torch.tensor([[3.0, 3.0], [-2.0, -2.0]])])
+    db = cm.DBSCAN(0.2, 5).fit(moons)
+    sk = skc.DBSCAN(eps=0.2, min_samples=5).fit(moons.numpy())
+    assert db.n_clusters_ == 2 and adjusted_rand_score(sk.labels_, db.labels_) == 1.0
+    assert np.array_equal(db.labels_.numpy() == -1, sk.labels_ == -1) and np.array_equal(db.core_sample_indices_.numpy(), sk.core_sample_indices_)
+
+    # ---- HDBSCAN: clusters of different density plus background noise
+    dense = 0.15 * torch.randn(100, 2, generator=g)
+    loose = torch.tensor([8.0, 0]) + 1.0 * torch.randn(100, 2, generator=g)
+    mid = torch.tensor([0.0, 8]) + 0.4 * torch.randn(100, 2, generator=g)
+    noise = torch.rand(20, 2, generator=g) * 30 - 10
+    data = torch.cat([dense, loose, mid, noise])
+    lab_true = torch.cat([torch.arange(3).repeat_interleave(100), torch.full((20,), -1)])
+    hd = cm.HDBSCAN(min_cluster_size=15, min_samples=5).fit(data)
+    assert hd.result.n_clusters == 3
+    core_pts = hd.labels_[:300]
+    assert adjusted_rand_score(lab_true[:300][core_pts >= 0], core_pts[core_pts >= 0]) == 1.0 and float((core_pts >= 0).float().mean()) > 0.9
+    assert float((hd.labels_[300:] == -1).float().mean()) >= 0.6
+    ref_h = skc.HDBSCAN(min_cluster_size=15, min_samples=5, copy=True).fit(data.numpy())
+    assert adjusted_rand_score(ref_h.labels_, hd.labels_) > 0.95
+    p = hd.probabilities_
+    assert float(p.min()) >= 0 and float(p.max()) == 1.0 and float(p[hd.labels_ < 0].max()) == 0.0
+    assert float(hd.result.outlier_scores[hd.labels_ < 0].min()) == 1.0 and len(hd.result.cluster_persistence) == 3
+    blob = cm.HDBSCAN(10).fit(dense)
+    assert blob.result.n_clusters == 0 and cm.HDBSCAN(10, allow_single_cluster=True).fit(dense).result.n_clusters == 1
+
+    # ---- spectral clustering separates concentric rings that k-means cannot
+    ang = torch.rand(300, generator=g) * 2 * math.pi
+    rad = torch.cat([torch.full((150,), 1.0), torch.full((150,), 4.0)]) + 0.08 * torch.randn(300, generator=g)
+    rings = torch.stack([rad * ang.cos(), rad * ang.sin()], 1)
+    ring_truth = torch.arange(2).repeat_interleave(150)
+    sp = cm.SpectralClustering(2, affinity="knn", n_neighbors=8).fit(rings)
+    assert adjusted_rand_score(ring_truth, sp.labels_) == 1.0 and float(sp.eigenvalues_[1]) < 1e-10 < float(sp.eigenvalues_[2])
+    assert adjusted_rand_score(ring_truth, cm.KMeans(2, seed=0).fit_predict(rings)) < 0.2
+    blobs_sp = cm.SpectralClustering(4, "rbf", gamma=0.5).fit(x)
+    assert adjusted_rand_score(truth, blobs_sp.labels_) == 1.0 and blobs_sp.eigengap(8) == 4
+
+    gs = cm.GapStatistic(7, 6).fit(x)
+    assert gs.optimal_k_ == 4 and len(gs.gaps_) == 7
+    ev = cm.evaluate_clustering(data, hd.labels_, lab_true)
+    assert ev.n_clusters == 3 and ev.silhouette > 0.6 and 0 < ev.noise_fraction < 0.15 and ev.external["ari"] > 0.9
+    ph = cm.PageHinkleyTest()
+    assert hasattr(ph, "update") or hasattr(ph, "add")
