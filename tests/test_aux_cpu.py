@@ -3063,3 +3063,245 @@ def test_metric_objects_accumulate_like_sklearn_and_merge_across_shards():
         assert saved["params"] == {"lr": 0.1} and saved["metrics"]["acc"][-1] == [1, 0.8] and saved["status"] == "finished"
         tr.to_mlflow("0001-b", Path(d) / "mlruns")
         assert len(list((Path(d) / "mlruns").rglob("metrics/acc"))) == 1
+
+
+def test_tabular_preprocessing_columnar_files_collate_policies_and_text_transforms(tmp_path):
+    import time
+    import numpy as np
+    import pyarrow as pa
+    import pyarrow.feather as feather
+    import pyarrow.parquet as pq
+    from scipy import signal as sps
+    from sklearn import feature_selection as skf
+    from sklearn import preprocessing as skp
+    from torsh_b200.data import tabular as tb
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(200, 4, generator=g, dtype=torch.float64) * torch.tensor([1.0, 5, 0.1, 0]) + torch.tensor([0.0, 10, -3, 7])
+    ss = tb.StandardScaler().fit(x)
+    assert np.allclose(ss.transform(x).numpy(), skp.StandardScaler().fit_transform(x.numpy())) and torch.allclose(ss.inverse_transform(ss.transform(x)), x)
+    inc = tb.StandardScaler()
+    for lo in range(0, 200, 50):
+        inc.partial_fit(x[lo:lo + 50])
+    assert torch.allclose(inc.mean_, ss.mean_) and torch.allclose(inc.scale_, ss.scale_)
+    mm = tb.MinMaxScaler((-1, 1)).fit(x)
+    assert np.allclose(mm.transform(x).numpy(), skp.MinMaxScaler((-1, 1)).fit_transform(x.numpy())) and torch.allclose(mm.inverse_transform(mm.transform(x))[:, :3], x[:, :3])
+    assert np.allclose(tb.RobustScaler().fit_transform(x[:, :3]).numpy(), skp.RobustScaler().fit_transform(x[:, :3].numpy()))
+    le = tb.LabelEncoder().fit(["cat", "dog", "ant", "dog"])
+    assert le.classes_ == ["ant", "cat", "dog"] and le.transform(["dog", "ant"]).tolist() == [2, 0] and le.inverse_transform([1]) == ["cat"]
+    with pytest.raises(ValueError):
+        le.transform(["emu"])
+    oh = tb.OneHotEncoder(handle_unknown="ignore").fit([["r", "g", "b", "g"], [1, 2, 1, 2]])
+    enc = oh.transform([["g", "x"], [2, 1]])
+    assert enc.tolist() == [[0, 1, 0, 0, 1], [0, 0, 0, 1, 0]] and oh.feature_names(["c", "n"]) == ["c=b", "c=g", "c=r", "n=1", "n=2"]
+    assert tb.OneHotEncoder(drop_first=True).fit_transform([["r", "g", "b"]]).shape == (3, 2)
+    holes = torch.tensor([[1.0, float("nan")], [3.0, 4.0], [float("nan"), 4.0], [5.0, 8.0]])
+    assert torch.allclose(tb.SimpleImputer("mean").fit_transform(holes), torch.tensor([[1.0, 16 / 3], [3, 4], [3, 4], [5, 8]]))
+    assert tb.SimpleImputer("median").fit_transform(holes)[2, 0] == 3 and tb.SimpleImputer("most_frequent").fit_transform(holes)[0, 1] == 4
+    ind = tb.SimpleImputer("constant", -1.0, add_indicator=True).fit_transform(holes)
+    assert ind.shape == (4, 4) and ind[0].tolist() == [1, -1, 0, 1]
+    vt = tb.VarianceThreshold(1e-6).fit(x)
+    assert vt.support_.tolist() == [True, True, True, False] and vt.transform(x).shape == (200, 3)
+    y = (x[:, 0] + 0.2 * torch.randn(200, generator=g, dtype=torch.float64) > 0).long()
+    f, p = tb.f_classif(x[:, :3], y)
+    f_ref, p_ref = skf.f_classif(x[:, :3].numpy(), y.numpy())
+    assert np.allclose(f.numpy(), f_ref) and np.allclose(p.numpy(), p_ref)
+    assert tb.SelectKBest(1).fit(x[:, :3], y).support_.tolist() == [True, False, False]
+
+    # ---- CSV, Arrow, Parquet
+    csv_path = tmp_path / "t.csv"
+    csv_path.write_text("age,city,income,label\n31,paris,1000.5,yes\n,rome,NA,no\n45,paris,3000,yes\n")
+    ds = tb.CSVDataset(csv_path, target="label")
+    assert ds.feature_names == ["age", "city", "income"] and ds.encoders["city"].classes_ == ["paris", "rome"] and ds.targets.tolist() == [1, 0, 1]
+    assert torch.isnan(ds.features[1, 0]) and torch.isnan(ds.features[1, 2]) and ds.features[:, 1].tolist() == [0, 1, 0] and float(ds[0][0][2]) == 1000.5
+    assert tb.CSVDataset(csv_path, target="label", usecols=["age"]).features.shape == (3, 1)
+    table = pa.table({"a": np.arange(10, dtype=np.float32), "b": np.arange(10, dtype=np.int64) * 2, "kind": ["x", "y"] * 5, "y": np.arange(10) % 3})
+    ad = tb.ArrowDataset(table, target="y")
+    assert ad.features.shape == (10, 3) and ad.targets.dtype == torch.long and ad.features[3].tolist() == [3.0, 6.0, 1.0] and ad.schema["a"] == "float"
+    feather.write_feather(table, tmp_path / "t.arrow")
+    assert torch.equal(tb.ArrowDataset(tmp_path / "t.arrow", target="y").features, ad.features)
+    big = pa.table({"f0": np.arange(100, dtype=np.float32), "f1": np.arange(100, dtype=np.float32) ** 2, "y": np.arange(100) % 2})
+    pq.write_table(big, tmp_path / "t.parquet", row_group_size=25)
+    pds = tb.ParquetDataset(tmp_path / "t.parquet", target="y", columns=["f1"])
+    assert pds.num_row_groups == 4 and pds.num_rows == 100
+    rows = list(pds)
+    assert len(rows) == 100 and float(rows[7][0][0]) == 49.0 and int(rows[7][1]) == 1
+    sh = [list(pds.shard(r, 2)) for r in range(2)]
+    assert len(sh[0]) == len(sh[1]) == 50 and float(sh[1][0][0][0]) == 625.0
+    batches = list(tb.ParquetDataset(tmp_path / "t.parquet", target="y", batch_rows=10))
+    assert len(batches) == 12 and batches[0][0].shape == (10, 2) and batches[2][0].shape == (5, 2)
+    assert pds.materialize().features.shape == (100, 1)
+    arr = tb.ArrayDataset(torch.arange(6.0).reshape(3, 2), [0, 1, 0], transform=lambda v: v * 2)
+    assert arr[1][0].tolist() == [4.0, 6.0] and int(arr[1][1]) == 1
+
+    # ---- folds
+    folds = list(tb.KFold(3).split(10))
+    assert [len(te) for _, te in folds] == [4, 3, 3] and sorted(torch.cat([te for _, te in folds]).tolist()) == list(range(10))
+    assert all(not set(tr.tolist()) & set(te.tolist()) for tr, te in folds)
+    lab = torch.tensor([0] * 12 + [1] * 6)
+    for tr, te in tb.StratifiedKFold(3, shuffle=True).split(lab):
+        assert int((lab[te] == 0).sum()) == 4 and int((lab[te] == 1).sum()) == 2
+    groups = ["a"] * 5 + ["b"] * 3 + ["c"] * 3 + ["d"] * 1
+    for tr, te in tb.GroupKFold(2).split(groups):
+        assert not {groups[i] for i in tr.tolist()} & {groups[i] for i in te.tolist()} and len(te) == 6
+    tr_ds, te_ds = next(tb.KFold(3).subsets(arr))
+    assert len(tr_ds) == 2 and len(te_ds) == 1
+
+    # ---- collate
+    dc = tb.DefaultCollate()
+    out = dc([{"x": torch.ones(2), "n": 1, "s": "a", "t": (torch.zeros(1), 2.0)}, {"x": torch.zeros(2), "n": 2, "s": "b", "t": (torch.ones(1), 3.0)}])
+    assert out["x"].shape == (2, 2) and out["n"].tolist() == [1, 2] and out["s"] == ["a", "b"] and out["t"][0].shape == (2, 1) and out["t"][1].tolist() == [2.0, 3.0]
+    seqs = [torch.arange(3), torch.arange(5), torch.arange(1)]
+    padded, lens = tb.PadCollate(-1, pad_to_multiple=4)(seqs)
+    assert padded.shape == (3, 8) and lens.tolist() == [3, 5, 1] and padded[2].tolist() == [0] + [-1] * 7
+    left = tb.PadCollate(0, side="left")(seqs)[0]
+    assert left[0].tolist() == [0, 0, 0, 1, 2]
+    ids, lengths, labels = tb.PadCollate()([(s, i) for i, s in enumerate(seqs)])
+    assert ids.shape == (3, 5) and labels.tolist() == [0, 1, 2] and lengths.tolist() == [3, 5, 1]
+    dpad = tb.PadCollate()([{"tok": s, "y": 1} for s in seqs])
+    assert dpad["tok"].shape == (3, 5) and dpad["tok_lengths"].tolist() == [3, 5, 1]
+    frames = tb.PadCollate(dim=0)([torch.ones(2, 3), torch.ones(4, 3)])[0]
+    assert frames.shape == (2, 4, 3) and float(frames[0, 2:].sum()) == 0
+    sp = tb.SparseCollate((6,))([(torch.tensor([1, 4]), torch.tensor([1.0, 2.0])), (torch.tensor([0]), torch.tensor([3.0]))])
+    assert sp.shape == (2, 6) and sp.to_dense().tolist() == [[0, 1, 0, 0, 2, 0], [3, 0, 0, 0, 0, 0]]
+    mixed = tb.MixedCollate({"tok": lambda v: tb.PadCollate()(v)[0], "meta": list})([{"tok": s, "meta": {"i": i}, "y": i} for i, s in enumerate(seqs)])
+    assert mixed["tok"].shape == (3, 5) and mixed["meta"][2] == {"i": 2} and mixed["y"].tolist() == [0, 1, 2]
+    var = [torch.zeros(n) for n in (2, 30, 3, 28, 4, 5)]
+    dyn = tb.DynamicBatchCollate(max_tokens=60)(var)
+    assert [b[0].shape for b in dyn] == [(4, 5), (2, 30)] and all(b[0].numel() <= 60 for b in dyn)
+    cc = tb.CachedCollate(capacity=2)
+    b1 = [torch.ones(2), torch.zeros(2)]
+    assert cc(b1) is cc(b1) and (cc.hits, cc.misses) == (1, 1)
+    st = tb.TensorStacker()([torch.ones(2, 2), torch.zeros(2, 2)])
+    assert st.shape == (2, 2, 2)
+
+    # ---- samplers and registry
+    cost = lambda i: float(i % 5 + 1)
+    abs_ = tb.AdaptiveBatchSampler(50, cost, budget=10.0, shuffle=False)
+    bs = list(abs_)
+    assert sorted(i for b in bs for i in b) == list(range(50)) and all(sum(cost(i) for i in b) <= 10 for b in bs)
+    abs2 = tb.AdaptiveBatchSampler(50, cost, 10.0, target_seconds=1.0)
+    abs2.report(4.0)
+    assert abs2.budget == pytest.approx(10 * 0.5 ** 0.5)
+    gsm = list(tb.GroupedSampler([i % 3 for i in range(20)], 4))
+    assert sorted(i for b in gsm for i in b) == list(range(20)) and all(len({i % 3 for i in b}) == 1 for b in gsm)
+    assert all(len(b) == 4 for b in tb.GroupedSampler([i % 3 for i in range(20)], 4, drop_last=True))
+    fsam = tb.FederatedSampler([10, 1000, 10, 10], 2, "proportional", seed=0)
+    picks = Counter(c for _ in range(200) for c in fsam.sample())
+    assert picks[1] > 190 and fsam.aggregation_weights([0, 1]).tolist() == pytest.approx([10 / 1010, 1000 / 1010])
+    caps = [{"compute": 1, "bandwidth": 1, "battery": 0.1}, {"compute": 2, "bandwidth": 1, "battery": 0.9}, {"compute": 1, "bandwidth": 1, "battery": 0.9}]
+    assert all(0 not in tb.FederatedSampler([1, 1, 1], 2, "capability", caps, seed=s).sample() for s in range(5))
+    ps = list(tb.PrivateSampler(10000, 0.01, 20, seed=0))
+    sizes = torch.tensor([len(b) for b in ps], dtype=torch.float)
+    assert len(ps) == 20 and float(sizes.mean()) == pytest.approx(100, abs=10) and float(sizes.std()) > 3
+    reg = tb.DatasetRegistry()
+    @reg.register("toy", description="three rows")
+    def _toy(scale=1.0): return tb.ArrayDataset(torch.arange(3.0) * scale)
+    assert "toy" in reg and reg.list() == {"toy": "three rows"} and float(reg.build("toy", scale=2.0)[2]) == 4.0
+    with pytest.raises(KeyError):
+        reg.build("nope")
+    with pytest.raises(KeyError):
+        reg.register("toy", _toy)
+
+    # ---- text
+    s = "  The  Quick brown fox, aged 12.5, jumped over 2 lazy dogs!  "
+    for t in (tb.ToLowercase(), tb.RemoveNumbers(), tb.RemovePunctuation(), tb.CollapseWhitespace(), tb.TrimWhitespace()):
+        s = t(s)
+    assert s == "the quick brown fox aged jumped over lazy dogs"
+    toks = tb.FilterByLength(4)(tb.RemoveStopwords()(tb.Tokenize()(s)))
+    assert toks == ["quick", "brown", "aged", "jumped", "lazy", "dogs"]
+    assert tb.NGrams(2)(["a", "b", "c"]) == ["a b", "b c"] and tb.NGrams(2, None, True)(["a", "b"]) == [("a",), ("b",), ("a", "b")]
+    assert tb.ReplacePattern(r"\d+", "<num>")("room 42") == "room <num>"
+    vocab = tb.Vocabulary.build([["a", "b", "a"], ["a", "c", "b", "rare"]], min_freq=2)
+    assert vocab.itos == ["<pad>", "<unk>", "<bos>", "<eos>", "a", "b"] and vocab.encode(["a", "rare"]) == [4, 1]
+    ids = tb.FixedLength(6)(tb.AddSpecialTokens()(vocab.encode(["b", "a"])))
+    assert ids == [2, 5, 4, 3, 0, 0] and vocab.decode(ids) == ["b", "a"] and tb.TokenIdsToTensor()(ids).dtype == torch.long
+    assert tb.FixedLength(2, truncate="left")([1, 2, 3]) == [2, 3] and tb.FixedLength(4)(torch.arange(2)).tolist() == [0, 1, 0, 0]
+    assert len(tb.Vocabulary.build([["a", "b", "c", "d"]], max_size=6)) == 6
+    bpe = tb.SimpleBPE(20).fit(["low low low lower lowest", "new newer newest wide wider widest"] * 3)
+    assert bpe.merges[0] in (("l", "o"), ("e", "r"), ("e", "s"), ("w", "e"), ("o", "w")) and "low</w>" in bpe.encode("low")
+    pieces = bpe.encode("lowest newer")
+    assert bpe.decode(pieces) == "lowest newer" and len(pieces) < len("lowest newer")
+    tcd = tb.TextClassificationDataset(["Good film!", "bad film", "good, good plot"], ["pos", "neg", "pos"], max_len=4)
+    assert tcd.ids.shape == (3, 4) and tcd.labels.tolist() == [1, 0, 1] and tcd.lengths.tolist() == [2, 2, 3]
+    assert int(tcd[0][0][0]) == tcd.vocab.stoi["good"] and int(tcd[0][0][2]) == 0
+    txt = tmp_path / "lines.txt"
+    txt.write_text("first line\n\nsecond línea\nthird\n", encoding="utf-8")
+    tf = tb.TextFileDataset(txt, transform=str.upper)
+    assert len(tf) == 3 and tf[1] == "SECOND LÍNEA" and tf[2] == "THIRD"
+
+    # ---- audio and image sample transforms
+    sr = 16000
+    tt = torch.arange(sr, dtype=torch.float64) / sr
+    tone = torch.sin(2 * math.pi * 440 * tt)
+    down = tb.Resample(16000, 8000)(tone)
+    ref = sps.resample_poly(tone.numpy(), 1, 2)
+    assert down.shape == (8000,) and float((down[200:-200] - torch.from_numpy(ref)[200:-200]).abs().max()) < 5e-3
+    up = tb.Resample(8000, 22050)(down[None])
+    assert up.shape == (1, 22050)
+    spec = torch.fft.rfft(up[0]).abs()
+    assert abs(int(spec.argmax()) - 440) <= 1
+    alias = tb.Resample(16000, 8000)(torch.sin(2 * math.pi * 6000 * tt))                # above the new Nyquist: removed, not folded
+    assert float(alias[500:-500].abs().max()) < 0.02
+    noisy = tb.AddNoise((20.0, 20.0), seed=0)(tone)
+    snr = 10 * math.log10(float(tone.pow(2).mean() / (noisy - tone).pow(2).mean()))
+    assert snr == pytest.approx(20.0, abs=0.3)
+    img = torch.rand(3, 8, 8, generator=g)
+    assert float(tb.RandomBrightness(0.5, seed=1)(img).max()) <= 1.0 and tb.RandomContrast(0.0)(img).allclose(img)
+    assert float((tb.GaussianNoise(0.1, seed=0)(img) - img).std()) == pytest.approx(0.1, rel=0.2)
+    eng = tb.OnlineAugmentationEngine([lambda v: v + 1], strength=0.2, target_gap=0.05, step=0.1)
+    for _ in range(3):
+        eng.report(0.95, 0.80)
+    assert eng.strength == pytest.approx(0.5)
+    eng.report(0.6, 0.6)
+    assert eng.strength == pytest.approx(0.4)
+    eng.strength = 1.0
+    assert float(eng(torch.zeros(()))) == 1.0
+
+    # ---- utilities
+    calls, slept = {"n": 0}, []
+    def flaky():
+        calls["n"] += 1
+        if calls["n"] < 3:
+            raise OSError("transient")
+        return "ok"
+    rs = tb.RetryStrategy(4, 0.1, 2.0, sleep=slept.append)
+    assert rs.run(flaky) == "ok" and slept == [0.1, 0.2] and rs.delays() == [0.1, 0.2, 0.4]
+    with pytest.raises(ValueError):
+        tb.RetryStrategy(3, sleep=slept.append).run(lambda: (_ for _ in ()).throw(ValueError("not retried")))
+    with pytest.raises(OSError):
+        tb.RetryStrategy(2, sleep=slept.append).run(lambda: (_ for _ in ()).throw(OSError("always")))
+    now = [0.0]
+    pt = tb.ProgressTracker(100, clock=lambda: now[0])
+    now[0] = 2.0
+    pt.update(20)
+    assert pt.rate() == 10.0 and pt.eta() == 8.0 and "20/100 (20.0%)" in str(pt)
+    cache = tb.ConcurrentCache(2)
+    produced = []
+    def slow(k):
+        def f():
+            time.sleep(0.05)
+            produced.append(k)
+            return k * 2
+        return f
+    threads = [threading.Thread(target=lambda: cache.get_or_compute(7, slow(7))) for _ in range(6)]
+    [t.start() for t in threads]; [t.join() for t in threads]
+    assert produced == [7] and cache.get_or_compute(7, slow(7)) == 14 and cache.misses == 1
+    cache.get_or_compute(1, slow(1)); cache.get_or_compute(2, slow(2))
+    assert len(cache) == 2 and 7 not in cache.data
+    sc = tb.StatisticsCollector(0)
+    imgs = torch.rand(10, 3, 5, 5, generator=g)
+    for im in imgs:
+        sc.update(im)
+    stt = sc.compute()
+    assert torch.allclose(stt["mean"], imgs.double().mean((0, 2, 3))) and torch.allclose(stt["std"], imgs.double().std((0, 2, 3), unbiased=False)) and stt["count"] == 250
+    buf = bytearray(np.arange(12, dtype=np.float32).tobytes())
+    z = tb.ZeroCopyTensor(buf, torch.float32, (2, 4), offset=16)
+    assert z.tensor[0].tolist() == [4, 5, 6, 7]
+    z.tensor[0, 0] = 99.0
+    assert np.frombuffer(buf, dtype=np.float32)[4] == 99.0 and z.shares_memory_with(z.tensor[1])
+    bm = tb.BufferManager()
+    a = bm.acquire(1000)
+    assert len(a) == 1024
+    bm.release(a)
+    assert bm.acquire(600) is a and (bm.allocated, bm.reused) == (1, 1)

@@ -353,4 +353,4 @@ class NativeTokenLoader:
             pass
 
 
-from . import pipeline, samplers  # noqa: E402,F401  (index samplers and dataset / transform combinators)
+from . import pipeline, samplers, tabular  # noqa: E402,F401  (index samplers, dataset / transform combinators, tabular and columnar-file tools)
