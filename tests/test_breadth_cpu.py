@@ -6489,3 +6489,236 @@ def test_cluster_estimators_match_sklearn_and_hdbscan_finds_varied_density_group
     assert ev.n_clusters == 3 and ev.silhouette > 0.6 and 0 < ev.noise_fraction < 0.15 and ev.external["ari"] > 0.9
     ph = cm.PageHinkleyTest()
     assert hasattr(ph, "update") or hasattr(ph, "add")
+
+
+def test_advanced_graph_models_generative_quantum_spiking_operators_and_matching():
+    from torch import nn
+    from torsh_b200 import graph_advanced as ga
+    from torsh_b200.graph import erdos_renyi, grid_graph, stochastic_block_model
+
+    torch.manual_seed(0)
+    g = torch.Generator().manual_seed(0)
+
+    # ---- graph-level prediction: rings versus cliques; regression of edge count
+    def ring(n): return torch.stack([torch.arange(n), (torch.arange(n) + 1) % n]).repeat(1, 1)
+    def clique(n): return torch.tensor([[i, j] for i in range(n) for j in range(n) if i != j]).T
+    def batchify(graphs):
+        xs, eis, bs, off = [], [], [], 0
+        for b, (n, ei) in enumerate(graphs):
+            und = torch.cat([ei, ei.flip(0)], 1)
+            deg = torch.bincount(und[0], minlength=n).float()
+            xs.append(torch.stack([torch.ones(n), deg / 10], 1)); eis.append(und + off); bs.append(torch.full((n,), b)); off += n
+        return torch.cat(xs), torch.cat(eis, 1), torch.cat(bs)
+    graphs = [(n, ring(n)) for n in range(5, 11)] + [(n, clique(n)) for n in range(5, 11)]
+    x, ei, batch = batchify(graphs)
+    y = torch.tensor([0] * 6 + [1] * 6)
+    for model in (ga.GraphClassificationGCN(2, 16, 2), ga.GraphClassificationGAT(2, 16, 2), ga.HierarchicalGraphClassifier(2, 16, 2)):
+        opt = torch.optim.Adam(model.parameters(), 0.02)
+        for _ in range(80):
+            opt.zero_grad(); loss = nn.functional.cross_entropy(model(x, ei, batch), y); loss.backward(); opt.step()
+        assert (model(x, ei, batch).argmax(1) == y).all(), type(model).__name__
+    hier = ga.HierarchicalGraphClassifier(2, 8, 2, levels=2, ratio=0.5)
+    hier(x, ei, batch)
+    assert len(hier.kept[0]) == sum(math.ceil(n / 2) for n, _ in graphs) and len(hier.kept[1]) < len(hier.kept[0])
+    reg = ga.GraphRegressor(2, 16)
+    target = torch.tensor([[float(e.shape[1])] for _, e in graphs]) / 10
+    opt = torch.optim.Adam(reg.parameters(), 0.01)
+    for _ in range(300):
+        opt.zero_grad(); loss = ((reg(x, ei, batch) - target) ** 2).mean(); loss.backward(); opt.step()
+    assert float(loss) < 0.15 * float(target.var())
+    mt = ga.MultiTaskGraphNetwork(2, 8, {"node_cls": ("node", 3), "graph_reg": ("graph", 1)})
+    out = mt(x, ei, batch)
+    assert out["node_cls"].shape == (len(x), 3) and out["graph_reg"].shape == (12, 1)
+    total = mt.loss({"node_cls": torch.tensor(2.0), "graph_reg": torch.tensor(0.5)})
+    assert float(total) == pytest.approx(2.5) and {n for n, _ in mt.named_parameters() if "log_vars" in n} == {"log_vars.node_cls", "log_vars.graph_reg"}
+
+    # ---- VGAE recovers community structure; GAN statistics are permutation invariant
+    sbm = stochastic_block_model((20, 20), 0.5, 0.02, feat=8, seed=0)
+    vae = ga.GraphVAE(8, 16, 8)
+    opt = torch.optim.Adam(vae.parameters(), 0.02)
+    first = None
+    for _ in range(150):
+        opt.zero_grad(); loss = vae.loss(sbm.x, sbm.edge_index); loss.backward(); opt.step()
+        first = first if first is not None else float(loss)
+    vae.eval()
+    logits, mu, _ = vae(sbm.x, sbm.edge_index)
+    adj = ga.dense_adjacency(sbm.edge_index, 40)
+    iu = torch.triu_indices(40, 40, 1)
+    from torsh_b200.utils.metrics import roc_auc
+    assert float(loss) < first and roc_auc(logits[iu[0], iu[1]].detach(), adj[iu[0], iu[1]]) > 0.85
+    assert vae.sample(10).shape == (10, 10) and float(vae.sample(10).diagonal().sum()) == 0
+    gan = ga.GraphGAN(8)
+    fake = gan.generate(5)
+    assert fake.shape == (5, 8, 8) and torch.allclose(fake, fake.transpose(1, 2)) and float(fake.diagonal(dim1=1, dim2=2).abs().sum()) == 0
+    perm = torch.randperm(8, generator=g)
+    assert torch.allclose(gan.statistics(fake), gan.statistics(fake[:, perm][:, :, perm]), atol=1e-6)
+    tri = ga.dense_adjacency(clique(8), 8)[None]
+    assert gan.statistics(tri)[0, 3] == pytest.approx(1.0) and gan.statistics(tri)[0, 4] == pytest.approx(1.0)
+    d_loss, g_loss = gan.losses(torch.stack([ga.dense_adjacency(ring(8), 8)] * 4))
+    d_loss.backward(); assert gan.disc[0].weight.grad is not None and float(g_loss) > 0
+    cg = ga.ConditionalGraphGenerator(6, cond_dim=2)
+    assert cg.generate_conditioned(torch.rand(3, 2)).shape == (3, 6, 6)
+
+    # ---- discrete diffusion: marginals, posterior consistency, training signal
+    diff = ga.DiscreteGraphDiffusion(steps=20, hidden=16, rho=0.2)
+    a0 = ga.dense_adjacency(ring(12), 12)
+    assert torch.allclose(diff.q_prob(a0, 19), torch.full_like(a0, 0.2), atol=0.1) and float(diff.q_prob(a0, 0)[0, 1]) > 0.99
+    emp = torch.stack([diff.q_sample(a0, 10, g) for _ in range(300)]).mean(0)
+    assert float((emp - diff.q_prob(a0, 10))[iu[0][:66] % 12, iu[1][:66] % 12].abs().mean()) < 0.06
+    samp = diff.q_sample(a0, 5, g)
+    assert torch.equal(samp, samp.T) and float(samp.diagonal().sum()) == 0
+    # posterior marginalised over a_t must give back q(a_{t-1} | a_0)
+    t = 7
+    for a0v in (0.0, 1.0):
+        p_t = diff.abar[t] * a0v + (1 - diff.abar[t]) * 0.2
+        marg = p_t * diff.posterior(torch.ones(1), torch.tensor([a0v]), t) + (1 - p_t) * diff.posterior(torch.zeros(1), torch.tensor([a0v]), t)
+        assert float(marg) == pytest.approx(float(diff.abar[t - 1] * a0v + (1 - diff.abar[t - 1]) * 0.2), abs=1e-6)
+    opt = torch.optim.Adam(diff.parameters(), 0.01)
+    losses = []
+    for _ in range(60):
+        opt.zero_grad(); l = diff.loss(a0, g); l.backward(); opt.step(); losses.append(float(l))
+    assert sum(losses[-10:]) < sum(losses[:10])
+    gen = diff.sample(12, g)
+    assert gen.shape == (12, 12) and torch.equal(gen, gen.T) and set(gen.unique().tolist()) <= {0.0, 1.0}
+
+    # ---- LRP conserves relevance; gradients identify the informative neighbour
+    adj = ga.dense_adjacency(torch.tensor([[0, 1, 2], [1, 2, 3]]), 4, dtype=torch.float64)
+    w = [torch.rand(3, 5, generator=g, dtype=torch.float64), torch.rand(5, 2, generator=g, dtype=torch.float64)]
+    xin = torch.rand(4, 3, generator=g, dtype=torch.float64)
+    lrp = ga.GraphLRP(w).explain(xin, adj, node=1, target=0)
+    assert float(lrp["feature_relevance"].sum()) == pytest.approx(lrp["output"], rel=1e-6)
+    assert float(lrp["node_relevance"][3]) > 0 and float(lrp["node_relevance"][1]) > float(lrp["node_relevance"][3])      # two hops reach node 3
+    one_layer = ga.GraphLRP(w[:1]).explain(xin, adj, node=0, target=0)
+    assert float(one_layer["node_relevance"][2].abs()) < 1e-15                                                         # one hop does not reach node 2
+    lin = nn.Linear(3, 2).double()
+    model = lambda xx, ee: ga.GraphLRP.a_hat(ga.dense_adjacency(ee, 4, dtype=torch.float64)) @ lin(xx)
+    attr = ga.GraphGradientAttribution(model)
+    e4 = torch.tensor([[0, 1, 2], [1, 2, 3]])
+    ig = attr.integrated_gradients(xin, e4, 1, 0)
+    assert float(ig.sum()) == pytest.approx(float(model(xin, e4)[1, 0] - model(torch.zeros_like(xin), e4)[1, 0]), abs=1e-9)
+    assert float(attr.saliency(xin, e4, 0, 0)[3].sum()) == 0 and torch.allclose(attr.gradient_x_input(xin, e4, 1, 0), ig)
+    dense_model = lambda xx, aa: ga.GraphLRP.a_hat(aa) @ lin(xx)
+    imp = attr.edge_importance(dense_model, xin, adj, 0, 0)
+    assert float(imp[0, 1]) > 0 and float(imp[2, 3]) == 0
+
+    # ---- quantum walk and QAOA
+    c4 = ga.dense_adjacency(ring(4), 4, dtype=torch.float64)
+    qw = ga.QuantumWalk(c4)
+    for tt in (0.3, 1.7):
+        p = qw.probabilities(0, tt)
+        assert float(p.sum()) == pytest.approx(1.0) and float(p[1]) == pytest.approx(float(p[3]))
+    assert float(qw.probabilities(0, math.pi / 2)[2]) == pytest.approx(1.0, abs=1e-9)                                   # perfect transfer on the 4-cycle
+    from scipy.linalg import expm
+    assert torch.allclose(qw.evolve(0, 0.9), torch.from_numpy(expm(-1j * c4.numpy() * 0.9))[:, 0])
+    assert qw.node_features([0.5, 1.0]).shape == (4, 2) and float(qw.average_distribution(0, 20.0).sum()) == pytest.approx(1.0)
+    qaoa = ga.QuantumQAOA(ring(4), 4, depth=2)
+    assert qaoa.max_cut() == 4.0 and float(qaoa.state().abs().pow(2).sum()) == pytest.approx(1.0)
+    before = float(qaoa())
+    after = qaoa.optimize(120, 0.05)
+    bits, cut = qaoa.best_assignment()
+    assert after > before and after > 3.5 and cut == 4.0 and bits.tolist() in ([0, 1, 0, 1], [1, 0, 1, 0])
+    p1 = ga.QuantumQAOA(torch.tensor([[0], [1]]), 2, depth=1)
+    with torch.no_grad():
+        p1.gamma.fill_(math.pi / 2); p1.beta.fill_(math.pi / 8)
+    assert float(p1()) == pytest.approx(1.0, abs=1e-9)                                                                  # single edge: depth one reaches the optimum
+    with pytest.raises(ValueError):
+        ga.QuantumQAOA(ring(17), 17)
+    ql = ga.QuantumGraphLayer(3, 5)
+    out = ql(torch.rand(4, 3), c4.float())
+    out.sum().backward()
+    assert out.shape == (4, 5) and ql.times.grad is not None
+
+    # ---- spiking network trains; liquid state machine remembers
+    sbm2 = stochastic_block_model((15, 15), 0.5, 0.03, feat=6, seed=1)
+    adj2 = ga.dense_adjacency(sbm2.edge_index, 30)
+    snn = ga.SpikingGraphNetwork(6, 16, 2, steps=10)
+    opt = torch.optim.Adam(snn.parameters(), 0.02)
+    for _ in range(60):
+        opt.zero_grad(); loss = nn.functional.cross_entropy(snn(sbm2.x, adj2), sbm2.y); loss.backward(); opt.step()
+    assert float((snn(sbm2.x, adj2).argmax(1) == sbm2.y).float().mean()) > 0.9
+    assert 0 <= float(snn.spike_rate.min()) and float(snn.spike_rate.max()) <= 1 and 0 < float(snn.spike_rate.mean()) < 1
+    res_adj = (torch.rand(60, 60, generator=g) < 0.1).double()
+    lsm = ga.LiquidStateMachine(res_adj, 1, spectral_radius=0.9, leak=0.5)
+    u = torch.rand(600, 1, generator=g) - 0.5
+    delayed = torch.roll(u, 2, 0)
+    lsm.fit(u[:400], delayed[:400])
+    pred = lsm.predict(u)[420:]
+    assert float(((pred - delayed[420:]) ** 2).mean()) < 0.3 * float(delayed.var())
+    assert float(torch.linalg.eigvals(lsm.w).abs().max()) == pytest.approx(0.9, rel=1e-6)
+
+    # ---- operators
+    grid = grid_graph(8, 8)
+    gadj = ga.dense_adjacency(grid, 64)
+    lap = ga.normalized_laplacian(gadj)
+    fno = ga.GraphFNO(1, 16, 1, modes=12, layers=2)
+    basis = fno.basis(gadj)
+    assert torch.allclose(basis.T @ basis, torch.eye(12), atol=1e-4)
+    heat = torch.matrix_exp(-2.0 * lap)
+    u0 = torch.randn(40, 64, generator=g) @ basis @ basis.T
+    opt = torch.optim.Adam(fno.parameters(), 0.01)
+    for _ in range(150):
+        opt.zero_grad(); loss = sum(((fno(v[:, None], gadj, basis)[:, 0] - heat @ v) ** 2).mean() for v in u0[:8]) / 8; loss.backward(); opt.step()
+    test_err = float(((fno(u0[20][:, None], gadj, basis)[:, 0] - heat @ u0[20]) ** 2).mean() / (heat @ u0[20]).pow(2).mean())
+    assert test_err < 0.2
+    coords = torch.stack(torch.meshgrid(torch.linspace(0, 1, 8), torch.linspace(0, 1, 8), indexing="ij"), -1).reshape(64, 2)
+    don = ga.GraphDeepONet(64, 2, 32, 16)
+    assert don(u0[:5], coords).shape == (5, 64)
+    opt = torch.optim.Adam(don.parameters(), 0.01)
+    start = None
+    for _ in range(100):
+        opt.zero_grad(); loss = ((don(u0[:30], coords) - u0[:30] @ heat.T) ** 2).mean(); loss.backward(); opt.step()
+        start = start if start is not None else float(loss)
+    assert float(loss) < 0.5 * start
+    pinn = ga.PhysicsInformedGNN(16, dt=0.1)
+    u_now = torch.randn(64, generator=g)
+    u_next = u_now - 0.1 * 1.5 * (lap @ u_now)                                                                       # explicit Euler with kappa = 1.5
+    assert float(pinn.residual(u_now, u_next, lap).abs().max()) > 1e-3
+    with torch.no_grad():
+        pinn.log_kappa.fill_(math.log(1.5))
+    assert float(pinn.residual(u_now, u_next, lap).abs().max()) < 1e-5
+    pinn.loss(u_now, u_next, grid, lap).backward()
+    assert pinn.log_kappa.grad is not None
+
+    # ---- barycentre and matching
+    def sp(adj):
+        d = torch.where(adj > 0, torch.ones_like(adj), torch.full_like(adj, 99.0)).fill_diagonal_(0)
+        for k in range(len(adj)):
+            d = torch.minimum(d, d[:, k:k + 1] + d[k:k + 1])
+        return d.double()
+    r6 = sp(ga.dense_adjacency(ring(6), 6))
+    bary = ga.GraphBarycenter(6, iters=8, reg=0.05).fit([r6, r6[torch.randperm(6, generator=g)][:, torch.randperm(6, generator=g)] * 0 + r6])
+    assert bary.shape == (6, 6) and torch.allclose(bary, bary.T, atol=1e-8)
+    assert sorted(round(v, 1) for v in torch.linalg.eigvalsh(bary).tolist())[-1] == pytest.approx(sorted(torch.linalg.eigvalsh(r6).tolist())[-1], rel=0.15)
+    sia = ga.SiameseGraphNetwork(2, 8)
+    xr, eir, _ = batchify([(6, ring(6))]); xc, eic, _ = batchify([(6, clique(6))])
+    permn = torch.randperm(6, generator=g)
+    inv = torch.argsort(permn)
+    assert float(sia((xr, eir), (xr[permn], inv[eir]))) == pytest.approx(1.0, abs=1e-5)                                 # isomorphic copies embed identically
+    assert float(sia.contrastive_loss((xr, eir), (xr, eir), True)) < 1e-8
+    gmn = ga.GraphMatchingNetwork(2, 8, 2)
+    same = gmn((xr, eir), (xr, eir)); diff_ = gmn((xr, eir), (xc, eic))
+    assert float(same) == pytest.approx(0.0, abs=1e-8) and float(diff_) < float(same) and gmn.attention.shape == (6, 6)
+
+    # ---- foundation model and modalities
+    fm = ga.GraphFoundationModel(8, 16, 2).add_head("cls", "node", 2).add_head("link", "link").add_head("prop", "regression", 1)
+    pl = fm.pretrain_loss(sbm.x, sbm.edge_index, 0.2, g)
+    assert set(pl) == {"masked_features", "structure", "total"} and float(pl["total"]) == pytest.approx(float(pl["masked_features"] + pl["structure"]))
+    pl["total"].backward()
+    assert fm.mask_token.grad is not None
+    assert fm("cls", sbm.x, sbm.edge_index).shape == (40, 2) and fm("link", sbm.x, sbm.edge_index, pairs=sbm.edge_index[:, :7]).shape == (7,)
+    assert fm("prop", sbm.x, sbm.edge_index).shape == (1, 1)
+    fm.freeze_encoder()
+    assert not any(p.requires_grad for p in fm.encoder.parameters()) and all(p.requires_grad for p in fm.heads.parameters())
+    feats = {"text": torch.randn(5, 12), "image": torch.randn(5, 20), "audio": torch.randn(5, 6)}
+    path = ga.dense_adjacency(torch.tensor([[0, 1, 2, 3], [1, 2, 3, 4]]), 5)
+    cma = ga.CrossModalGraphAttention({"text": 12, "image": 20, "audio": 6}, 16, 4)
+    o1 = cma(feats, path)
+    feats2 = {k: v.clone() for k, v in feats.items()}
+    feats2["image"][4] += 10.0                                                                                        # node 4 is not adjacent to node 0
+    o2 = cma(feats2, path)
+    assert o1["text"].shape == (5, 16) and torch.allclose(o1["text"][0], o2["text"][0], atol=1e-6) and not torch.allclose(o1["text"][3], o2["text"][3])
+    for mode in ("gated", "concat", "bilinear"):
+        assert ga.MultiModalFusion({"text": 12, "image": 20, "audio": 6}, 10, mode)(feats).shape == (5, 10)
+    fus = ga.MultiModalFusion({"text": 12, "image": 20, "audio": 6}, 10, "gated")
+    fus({"text": feats["text"], "image": None, "audio": feats["audio"]})
+    assert set(fus.last_gates) == {"text", "audio"} and torch.allclose(fus.last_gates["text"] + fus.last_gates["audio"], torch.ones(5))
