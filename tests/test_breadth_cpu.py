@@ -6722,3 +6722,144 @@ def test_advanced_graph_models_generative_quantum_spiking_operators_and_matching
     fus = ga.MultiModalFusion({"text": 12, "image": 20, "audio": 6}, 10, "gated")
     fus({"text": feats["text"], "image": None, "audio": feats["audio"]})
     assert set(fus.last_gates) == {"text", "audio"} and torch.allclose(fus.last_gates["text"] + fus.last_gates["audio"], torch.ones(5))
+
+
+def test_vision_geometry_hough_binary_features_alignment_pose_and_efficientnet_v2():
+    from torch import nn
+    from torsh_b200.vision import geometry as vg
+    from torsh_b200.vision import ops as V
+
+    g = torch.Generator().manual_seed(0)
+    # ---- Hough lines: a horizontal and a diagonal line
+    img = torch.zeros(100, 120)
+    img[30, 10:110] = 1
+    for i in range(80):
+        img[10 + i, 20 + i] = 1
+    lines = vg.hough_lines(img, max_lines=2)
+    assert len(lines) == 2
+    horiz = min(lines, key=lambda l: abs(l.theta - math.pi / 2))
+    diag = min(lines, key=lambda l: abs(l.theta - 3 * math.pi / 4))
+    assert horiz.rho == pytest.approx(30, abs=1.5) and horiz.theta == pytest.approx(math.pi / 2, abs=0.02) and horiz.votes >= 95
+    assert diag.theta == pytest.approx(3 * math.pi / 4, abs=0.02) and abs(diag.rho - (20 * math.cos(diag.theta) + 10 * math.sin(diag.theta))) < 1.5
+    # ---- Hough circles
+    yy, xx = torch.meshgrid(torch.arange(100.0), torch.arange(120.0), indexing="ij")
+    ring = lambda cx, cy, r: ((torch.hypot(xx - cx, yy - cy) - r).abs() < 0.6).float()
+    edges = torch.maximum(ring(40, 50, 20), ring(85, 40, 12))
+    circles = vg.hough_circles(edges, radii=range(10, 24, 2), max_circles=2)
+    found = sorted((c.cx, c.cy, c.radius) for c in circles)
+    assert len(found) == 2 and abs(found[0][0] - 40) <= 1 and abs(found[0][1] - 50) <= 1 and found[0][2] == 20 and abs(found[1][0] - 85) <= 1 and found[1][2] == 12
+
+    # ---- binary descriptors: match a translated copy; orientation makes them survive a rotation
+    base = V.gaussian_blur(torch.rand(1, 160, 160, generator=g), 1.5)[0]
+    kps = torch.stack([torch.randint(40, 120, (40,), generator=g), torch.randint(40, 120, (40,), generator=g)], 1)
+    shifted = torch.roll(base, (7, -5), (0, 1))
+    d1 = vg.brief_descriptors(base, kps)
+    d2 = vg.brief_descriptors(shifted, kps + torch.tensor([-5, 7]))
+    assert d1.shape == (40, 32) and d1.dtype == torch.uint8
+    hd = vg.hamming_distance(d1, d2)
+    assert hd.shape == (40, 40) and int(hd.diagonal().max()) == 0 and float(hd[~torch.eye(40, dtype=torch.bool)].float().mean()) > 90
+    ref_pop = sum(bin(int(a) ^ int(b)).count("1") for a, b in zip(d1[0].tolist(), d1[1].tolist()))
+    assert int(vg.hamming_distance(d1[:1], d1[1:2])) == ref_pop
+    noisy = shifted + 0.02 * torch.randn(160, 160, generator=g)
+    matches = vg.BruteForceMatcher(0.8).match(d1, vg.brief_descriptors(noisy, kps + torch.tensor([-5, 7])))
+    assert len(matches) >= 30 and all(m.query == m.train for m in matches)
+    rot90 = torch.rot90(base, 1, (0, 1))                                                   # (x, y) -> (y, 159 - x)
+    kps_r = torch.stack([kps[:, 1], 159 - kps[:, 0]], 1)
+    plain = vg.hamming_distance(d1, vg.brief_descriptors(rot90, kps_r)).diagonal().float().mean()
+    orient = vg.hamming_distance(vg.brief_descriptors(base, kps, oriented=True), vg.brief_descriptors(rot90, kps_r, oriented=True)).diagonal().float().mean()
+    assert float(orient) < 0.35 * float(plain)
+    fl = vg.BruteForceMatcher(0.9, cross_check=False).match(torch.tensor([[0.0, 0], [5, 5]]), torch.tensor([[5.1, 5], [0, 0.1], [9, 9]]))
+    assert [(m.query, m.train) for m in fl] == [(0, 1), (1, 0)]
+
+    # ---- Kabsch, ICP
+    ang = 0.4
+    R = torch.tensor([[math.cos(ang), -math.sin(ang), 0], [math.sin(ang), math.cos(ang), 0], [0, 0, 1]], dtype=torch.float64)
+    pts = torch.randn(200, 3, generator=g, dtype=torch.float64)
+    t = torch.tensor([0.5, -1.0, 2.0], dtype=torch.float64)
+    Rk, tk, sk = vg.kabsch(pts, 1.7 * pts @ R.T + t, with_scale=True)
+    assert torch.allclose(Rk, R, atol=1e-9) and torch.allclose(tk, t, atol=1e-9) and float(sk) == pytest.approx(1.7)
+    mirrored = pts * torch.tensor([1.0, 1.0, -1.0], dtype=torch.float64)
+    assert float(torch.linalg.det(vg.kabsch(pts, mirrored)[0])) == pytest.approx(1.0)         # never a reflection
+    small = 0.15
+    Rs = torch.tensor([[math.cos(small), -math.sin(small), 0], [math.sin(small), math.cos(small), 0], [0, 0, 1]], dtype=torch.float64)
+    target = pts @ Rs.T + torch.tensor([0.1, 0.05, -0.1], dtype=torch.float64)
+    Ri, ti, hist = vg.icp(pts, target[torch.randperm(200, generator=g)])
+    assert torch.allclose(Ri, Rs, atol=1e-6) and hist[-1] < 1e-6 and hist[0] > hist[-1]
+    Rp, tp, hp = vg.icp(pts[:150], target, trim=0.9)
+    assert torch.allclose(Rp, Rs, atol=1e-3)
+
+    # ---- intensity registration recovers a known affine warp
+    smooth = V.gaussian_blur(torch.rand(1, 96, 96, generator=g), 4.0)[0].double()
+    smooth = (smooth - smooth.min()) / (smooth.max() - smooth.min())
+    p_true = torch.tensor([0.03, -0.02, 0.02, 0.01, 2.5, -1.5], dtype=torch.float64)
+    fixed = vg.ImageRegistrar._warp(smooth, p_true)
+    reg = vg.ImageRegistrar("affine", levels=3, iters=40).register(fixed, smooth)
+    assert reg["rmse"] < 0.01 and reg["rmse"] < 0.2 * float((smooth - fixed).pow(2).mean().sqrt())
+    assert torch.allclose(reg["matrix"], torch.tensor([[1.03, 0.02, 2.5], [-0.02, 1.01, -1.5]], dtype=torch.float64), atol=0.05)
+    shift_only = vg.ImageRegistrar._warp(smooth, torch.tensor([0, 0, 0, 0, 3.0, -2.0], dtype=torch.float64))
+    tr = vg.ImageRegistrar("translation", levels=2).register(shift_only, smooth)
+    assert float(tr["matrix"][0, 2]) == pytest.approx(3.0, abs=0.3) and float(tr["matrix"][1, 2]) == pytest.approx(-2.0, abs=0.3)
+
+    # ---- camera pose
+    K = torch.tensor([[800.0, 0, 320], [0, 800, 240], [0, 0, 1]])
+    pe = vg.PoseEstimator(K)
+    world = torch.rand(30, 3, generator=g, dtype=torch.float64) * 2 - 1
+    tc = torch.tensor([0.2, -0.1, 6.0], dtype=torch.float64)
+    uv = pe.project(world, R, tc)
+    est = pe.estimate(world, uv)
+    assert torch.allclose(est["rotation"], R, atol=1e-6) and torch.allclose(est["translation"], tc, atol=1e-5) and est["reprojection_error"] < 1e-6
+    noisy_est = pe.estimate(world, uv + 0.5 * torch.randn(30, 2, generator=g, dtype=torch.float64))
+    assert noisy_est["reprojection_error"] < 2.0 and float((noisy_est["translation"] - tc).norm()) < 0.3
+
+    # ---- EfficientNetV2
+    net = vg.EfficientNetV2(10, "tiny", drop_path=0.1, head_dim=64)
+    out = net(torch.randn(2, 3, 64, 64, generator=g))
+    out.sum().backward()
+    assert out.shape == (2, 10) and net.features[0].weight.grad is not None
+    full = vg.EfficientNetV2(1000, "s")
+    n_params = sum(p.numel() for p in full.parameters())
+    assert 20.5e6 < n_params < 22.5e6
+    fused, classic = vg.FusedMBConv(24, 24, 4, 1, True), vg.FusedMBConv(24, 24, 4, 1, False)
+    assert not any(isinstance(m, nn.Conv2d) and m.groups > 1 for m in fused.modules()) and any(isinstance(m, nn.Conv2d) and m.groups > 1 for m in classic.modules())
+    fused.eval()
+    xin = torch.randn(1, 24, 8, 8, generator=g)
+    assert fused.residual and fused(xin).shape == xin.shape and not vg.FusedMBConv(24, 48, 4, 2).residual
+
+    # ---- transforms and registry
+    rgb = torch.rand(3, 16, 16, generator=g)
+    assert vg.Grayscale()(rgb).shape == (1, 16, 16) and vg.Grayscale(3)(rgb).shape == (3, 16, 16)
+    assert torch.equal(vg.RandomGrayscale(0.0)(rgb), rgb) and torch.allclose(vg.RandomGrayscale(1.0)(rgb)[0], vg.RandomGrayscale(1.0)(rgb)[2])
+    assert float(vg.GaussianBlur(2.0)(rgb).std()) < float(rgb.std()) and torch.equal(vg.GaussianBlur(2.0, p=0.0)(rgb), rgb)
+    sol = vg.Solarize(0.5)(rgb)
+    assert torch.equal(sol[rgb < 0.5], rgb[rgb < 0.5]) and torch.allclose(sol[rgb >= 0.5], 1 - rgb[rgb >= 0.5])
+    assert vg.Pad(2)(rgb).shape == (3, 20, 20) and vg.Pad((1, 3))(rgb).shape == (3, 22, 18)
+    assert torch.allclose(vg.Rotation(0.0)(rgb), rgb, atol=1e-5)
+    rr = vg.RandomRotation(30, seed=0)
+    rr(rgb)
+    assert -30 <= rr.last_angle <= 30
+    mu = vg.MixUp(0.4, 5, seed=0)
+    xb, yb = torch.rand(8, 3, 4, 4, generator=g), torch.randint(0, 5, (8,), generator=g)
+    xm, ym = mu(xb, yb)
+    assert xm.shape == xb.shape and torch.allclose(ym.sum(1), torch.ones(8)) and 0 <= mu.last_lambda <= 1
+    regy = vg.TransformRegistry()
+    pipe = regy.build([{"name": "GaussianBlur", "sigma": 1.0}, "Grayscale", {"name": "Pad", "padding": 1}])
+    assert pipe(rgb).shape == (1, 18, 18) and len(pipe.steps) == 3 and "Solarize" in regy.names()
+    regy.register("Invert", lambda: (lambda v: 1 - v))
+    assert torch.allclose(regy.create("Invert")(rgb), 1 - rgb)
+    with pytest.raises(KeyError):
+        regy.create("Nope")
+
+    # ---- cache, prefetcher, batch loader
+    loads = []
+    def loader(k):
+        loads.append(k)
+        return torch.full((3, 8 + k % 2, 8), float(k))
+    cache = vg.ImageCache(capacity_bytes=3 * 3 * 9 * 8 * 4)
+    for k in (0, 1, 0, 2, 3, 0):
+        cache.get(k, lambda k=k: loader(k))
+    assert loads == [0, 1, 2, 3] and cache.hit_rate() == pytest.approx(2 / 6) and 1 not in cache.data and cache.used <= cache.cap
+    order = [k for k, _ in vg.ImagePrefetcher(range(10), lambda k: torch.tensor(k), depth=3)]
+    assert order == list(range(10))
+    bl = vg.BatchImageLoader(range(7), loader, batch_size=3, size=(8, 8), cache=vg.ImageCache())
+    batches = list(bl)
+    assert [b.shape for b in batches] == [(3, 3, 8, 8), (3, 3, 8, 8), (1, 3, 8, 8)] and len(bl) == 3 and float(batches[1][0].mean()) == pytest.approx(3.0)
